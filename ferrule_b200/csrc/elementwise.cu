@@ -1,0 +1,701 @@
+// Bandwidth-bound small operators of the decode / prefill step, each fused as far as
+// its neighbours allow (sm_100a):
+//
+//   fb_embedding        token ids -> bf16 rows
+//   fb_add_rmsnorm      (residual add) + RMSNorm, bf16 in/out, fp32 math
+//   fb_mla_prep         per token: RMSNorm(latent kv) + RoPE(k_rope) -> paged KV append,
+//                       RoPE(q_rope) per head -> query buffer
+//   fb_router_topk      softmax / sigmoid(+bias, group-limited) / sqrt-softplus(+bias) / hash
+//                       scoring + stable top-k + weight normalisation, one warp per token
+//   fb_moe_plan         count -> scan -> scatter of routes into expert-major order plus the
+//                       row-tile table the grouped GEMM walks (device side, no host sync)
+//   fb_gather_rows      expert-major activation gather
+//   fb_moe_reduce       fixed-order sum of a token's route rows (+ shared expert, + residual)
+//   fb_argmax           greedy token (ties -> lower id) over fp32 logits
+//   fb_topk_logits      top-k (k <= 64) logits + ids, sorted logit-desc / id-asc
+//   fb_copy_pages       copy-on-write page copy for the paged KV pool
+//
+// Counterparts in the reference: portable/entrypoints.cu embedding_kernel :631-649,
+// norm_kernel :651-712, rope_kernel :714-768, router_kernel :793-884,
+// expert_group_route_plan_kernel :1382-1513, moe_kernel :1515-1612, data_kernel :478-629
+// (crates/ferrule-backend/native/cuda/implementations/portable/entrypoints.cu).
+#include "common.cuh"
+#include "ferrule_b200.h"
+
+namespace fb {
+
+// ---------------------------------------------------------------------------------
+// embedding
+// ---------------------------------------------------------------------------------
+__global__ void embedding_kernel(const int* __restrict__ ids, const __nv_bfloat16* __restrict__ table,
+                                 __nv_bfloat16* __restrict__ out, int rows, int dim, int vocab,
+                                 DeviceStatus* st) {
+  const int r = blockIdx.x;
+  if (r >= rows) return;
+  int id = ids[r];
+  if (id < 0 || id >= vocab) {
+    if (threadIdx.x == 0) report_status(st, kStatusBadIndex, 0x10, r, id);
+    id = 0;
+  }
+  const uint4* src = reinterpret_cast<const uint4*>(table + static_cast<size_t>(id) * dim);
+  uint4* dst = reinterpret_cast<uint4*>(out + static_cast<size_t>(r) * dim);
+  for (int i = threadIdx.x; i < dim / 8; i += blockDim.x) dst[i] = src[i];
+}
+
+// ---------------------------------------------------------------------------------
+// (add +) RMSNorm.  One CTA per row, 256 threads, 8 bf16 per thread per step.
+// ---------------------------------------------------------------------------------
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  v = warp_sum(v);
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+  if (l == 0) red[w] = v;
+  __syncthreads();
+  float t = (l < (blockDim.x >> 5)) ? red[l] : 0.f;
+  t = warp_sum(t);
+  __syncthreads();
+  return t;
+}
+
+__global__ void __launch_bounds__(256)
+add_rmsnorm_kernel(const __nv_bfloat16* __restrict__ x, long long ldx,
+                   const __nv_bfloat16* __restrict__ delta, long long ldd,
+                   const __nv_bfloat16* __restrict__ weight, __nv_bfloat16* __restrict__ res_out,
+                   long long ldr, __nv_bfloat16* __restrict__ norm_out, long long ldn, int rows,
+                   int dim, float eps) {
+  __shared__ float red[8];
+  extern __shared__ float row[];  // dim floats
+  const int r = blockIdx.x;
+  if (r >= rows) return;
+  const __nv_bfloat16* xr = x + r * ldx;
+  const __nv_bfloat16* dr = delta ? delta + r * ldd : nullptr;
+  float ss = 0.f;
+  for (int i = threadIdx.x * 8; i < dim; i += blockDim.x * 8) {
+    uint4 a = *reinterpret_cast<const uint4*>(xr + i);
+    const __nv_bfloat16* ap = reinterpret_cast<const __nv_bfloat16*>(&a);
+    float v[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] = __bfloat162float(ap[j]);
+    if (dr) {
+      uint4 d = *reinterpret_cast<const uint4*>(dr + i);
+      const __nv_bfloat16* dp = reinterpret_cast<const __nv_bfloat16*>(&d);
+      // the residual stream is kept in bf16: round the sum before it is normalised
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] = bf16_round(v[j] + __bfloat162float(dp[j]));
+      if (res_out) {
+        __nv_bfloat16 o[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] = __float2bfloat16_rn(v[j]);
+        *reinterpret_cast<uint4*>(res_out + r * ldr + i) = *reinterpret_cast<uint4*>(o);
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      row[i + j] = v[j];
+      ss += v[j] * v[j];
+    }
+  }
+  ss = block_sum(ss, red);
+  const float inv = rsqrtf(ss / dim + eps);
+  if (norm_out == nullptr) return;
+  for (int i = threadIdx.x * 8; i < dim; i += blockDim.x * 8) {
+    uint4 wv = *reinterpret_cast<const uint4*>(weight + i);
+    const __nv_bfloat16* wp = reinterpret_cast<const __nv_bfloat16*>(&wv);
+    __nv_bfloat16 o[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) o[j] = __float2bfloat16_rn(row[i + j] * inv * __bfloat162float(wp[j]));
+    *reinterpret_cast<uint4*>(norm_out + r * ldn + i) = *reinterpret_cast<uint4*>(o);
+  }
+}
+
+// ---------------------------------------------------------------------------------
+// MLA prep: latent-KV norm + RoPE + paged append, and query RoPE.
+//   q row   : heads x [ nope (q_head_dim - rope_dim) | rope (rope_dim) ]
+//   ckv row : [ c_kv (kv_lora) | k_rope (rope_dim) ]
+//   q_out row     : per head [ latent slot (kv_lora, filled later by the absorb GEMM) | rope ]
+// cos/sin tables are [max_pos, rope_dim/2] fp32 (any frequency scaling baked in).
+// Rotation acts on interleaved pairs (x[2i], x[2i+1]).
+// ---------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+mla_prep_kernel(const __nv_bfloat16* __restrict__ q, long long ldq, int q_head_dim,
+                const __nv_bfloat16* __restrict__ ckv_in, long long ldckv, int heads, int kv_lora,
+                int rope_dim,
+                const __nv_bfloat16* __restrict__ kv_norm_w, float eps,
+                const float* __restrict__ cos_t, const float* __restrict__ sin_t, int max_pos,
+                const int* __restrict__ positions, const long long* __restrict__ write_slot,
+                __nv_bfloat16* __restrict__ kv_pool, long long pool_rows,
+                __nv_bfloat16* __restrict__ q_out, long long ldq_out, int rows, DeviceStatus* st) {
+  __shared__ float red[8];
+  const int r = blockIdx.x;
+  if (r >= rows) return;
+  int pos = positions[r];
+  if (pos < 0 || pos >= max_pos) {
+    if (threadIdx.x == 0) report_status(st, kStatusBadIndex, 0x20, r, pos);
+    pos = 0;
+  }
+  const int half = rope_dim / 2;
+  const float* cr = cos_t + static_cast<size_t>(pos) * half;
+  const float* sr = sin_t + static_cast<size_t>(pos) * half;
+
+  // query rope
+  const int nope = q_head_dim - rope_dim;
+  for (int i = threadIdx.x; i < heads * half; i += blockDim.x) {
+    const int h = i / half, p = i - h * half;
+    const __nv_bfloat16* qh = q + r * ldq + h * q_head_dim + nope;
+    const float a = __bfloat162float(qh[2 * p]), b = __bfloat162float(qh[2 * p + 1]);
+    const float c = cr[p], s = sr[p];
+    __nv_bfloat16* o = q_out + r * ldq_out + static_cast<long long>(h) * (kv_lora + rope_dim) + kv_lora;
+    o[2 * p] = __float2bfloat16_rn(a * c - b * s);
+    o[2 * p + 1] = __float2bfloat16_rn(a * s + b * c);
+  }
+
+  // latent kv: RMSNorm then append; k_rope: rotate then append
+  const long long slot = write_slot[r];
+  const bool slot_ok = slot >= 0 && slot < pool_rows;
+  if (!slot_ok && slot != -1 && threadIdx.x == 0)
+    report_status(st, kStatusBadIndex, 0x21, r, static_cast<uint32_t>(slot));
+  const __nv_bfloat16* ckv = ckv_in + r * ldckv;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < kv_lora; i += blockDim.x) {
+    const float v = __bfloat162float(ckv[i]);
+    ss += v * v;
+  }
+  ss = block_sum(ss, red);
+  const float inv = rsqrtf(ss / kv_lora + eps);
+  if (!slot_ok) return;
+  __nv_bfloat16* dst = kv_pool + slot * (kv_lora + rope_dim);
+  for (int i = threadIdx.x; i < kv_lora; i += blockDim.x)
+    dst[i] = __float2bfloat16_rn(__bfloat162float(ckv[i]) * inv * __bfloat162float(kv_norm_w[i]));
+  for (int p = threadIdx.x; p < half; p += blockDim.x) {
+    const float a = __bfloat162float(ckv[kv_lora + 2 * p]), b = __bfloat162float(ckv[kv_lora + 2 * p + 1]);
+    const float c = cr[p], s = sr[p];
+    dst[kv_lora + 2 * p] = __float2bfloat16_rn(a * c - b * s);
+    dst[kv_lora + 2 * p + 1] = __float2bfloat16_rn(a * s + b * c);
+  }
+}
+
+// ---------------------------------------------------------------------------------
+// router: one warp per token, experts <= 256 (8 per lane)
+// ---------------------------------------------------------------------------------
+enum { kScoreSoftmax = 0, kScoreSigmoid = 1, kScoreSqrtSoftplus = 2 };
+
+__global__ void __launch_bounds__(128)
+router_topk_kernel(const float* __restrict__ logits, long long ldl, const float* __restrict__ bias,
+                   const long long* __restrict__ hash_table, const int* __restrict__ token_ids,
+                   int rows, int experts, int topk, int score_fn, int n_groups, int topk_groups,
+                   int normalize, float route_scale, int* __restrict__ out_idx,
+                   float* __restrict__ out_w) {
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (warp >= rows) return;
+  const float* lr = logits + warp * ldl;
+  constexpr int kPer = 8;
+  float score[kPer];   // the value weights are taken from
+  float select[kPer];  // the value top-k is taken on (score + bias)
+  // scores
+  float mx = -INFINITY;
+#pragma unroll
+  for (int j = 0; j < kPer; ++j) {
+    const int e = lane + 32 * j;
+    score[j] = e < experts ? lr[e] : -INFINITY;
+    mx = fmaxf(mx, score[j]);
+  }
+  if (score_fn == kScoreSoftmax) {
+    mx = warp_max(mx);
+    float sum = 0.f;
+#pragma unroll
+    for (int j = 0; j < kPer; ++j) {
+      const int e = lane + 32 * j;
+      score[j] = e < experts ? __expf(score[j] - mx) : 0.f;
+      sum += score[j];
+    }
+    sum = warp_sum(sum);
+#pragma unroll
+    for (int j = 0; j < kPer; ++j) score[j] /= sum;
+  } else if (score_fn == kScoreSigmoid) {
+#pragma unroll
+    for (int j = 0; j < kPer; ++j) score[j] = 1.f / (1.f + __expf(-score[j]));
+  } else {
+#pragma unroll
+    for (int j = 0; j < kPer; ++j) {
+      const float x = score[j];
+      const float sp = x > 20.f ? x : log1pf(__expf(x));
+      score[j] = sqrtf(sp);
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < kPer; ++j) {
+    const int e = lane + 32 * j;
+    select[j] = e < experts ? score[j] + (bias ? bias[e] : 0.f) : -INFINITY;
+  }
+
+  int* oi = out_idx + static_cast<size_t>(warp) * topk;
+  float* ow = out_w + static_cast<size_t>(warp) * topk;
+
+  if (hash_table != nullptr) {
+    // hash routing: experts come from the table row of the token id; weights from the scores
+    const long long* hr = hash_table + static_cast<size_t>(token_ids[warp]) * topk;
+    float wsum = 0.f;
+    float mine = 0.f;
+    for (int k = 0; k < topk; ++k) {
+      int e = static_cast<int>(hr[k]);
+      if (e < 0 || e >= experts) e = 0;
+      float val = 0.f;
+#pragma unroll
+      for (int j = 0; j < kPer; ++j)
+        if (j == (e >> 5)) val = __shfl_sync(0xffffffffu, score[j], e & 31);
+      wsum += val;
+      if (lane == k) { mine = val; oi[k] = e; }
+    }
+    if (lane < topk) ow[lane] = (normalize ? mine / wsum : mine) * route_scale;
+    return;
+  }
+
+  // group-limited selection (sigmoid family): keep the topk_groups groups with the largest
+  // sum of their two best selection values, mask the rest.
+  if (n_groups > 1 && topk_groups < n_groups) {
+    const int per_group = experts / n_groups;
+    float gscore_mine = -INFINITY;  // lane g holds group g's score
+    for (int g = 0; g < n_groups; ++g) {
+      float b1 = -INFINITY, b2 = -INFINITY;
+#pragma unroll
+      for (int j = 0; j < kPer; ++j) {
+        const int e = lane + 32 * j;
+        if (e < experts && e / per_group == g) {
+          const float v = select[j];
+          if (v > b1) { b2 = b1; b1 = v; } else if (v > b2) { b2 = v; }
+        }
+      }
+      // merge (b1, b2) across lanes
+      for (int o = 16; o > 0; o >>= 1) {
+        const float o1 = __shfl_xor_sync(0xffffffffu, b1, o), o2 = __shfl_xor_sync(0xffffffffu, b2, o);
+        const float n1 = fmaxf(b1, o1);
+        const float n2 = fmaxf(fminf(b1, o1), fmaxf(b2, o2));
+        b1 = n1; b2 = n2;
+      }
+      if (lane == g) gscore_mine = b1 + b2;
+    }
+    // pick topk_groups groups (ties -> lower group id)
+    uint32_t keep = 0;
+    for (int it = 0; it < topk_groups; ++it) {
+      float v = (lane < n_groups && !((keep >> lane) & 1u)) ? gscore_mine : -INFINITY;
+      int idx = lane;
+      for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, v, o);
+        const int oidx = __shfl_xor_sync(0xffffffffu, idx, o);
+        if (ov > v || (ov == v && oidx < idx)) { v = ov; idx = oidx; }
+      }
+      keep |= 1u << idx;
+    }
+#pragma unroll
+    for (int j = 0; j < kPer; ++j) {
+      const int e = lane + 32 * j;
+      if (e < experts && !((keep >> (e / per_group)) & 1u)) select[j] = -INFINITY;
+    }
+  }
+
+  // stable top-k: largest selection value, ties -> lower expert id
+  float wsum = 0.f;
+  float mine = 0.f;
+  for (int k = 0; k < topk; ++k) {
+    float v = -INFINITY;
+    int idx = 0x7fffffff;
+#pragma unroll
+    for (int j = 0; j < kPer; ++j) {
+      const int e = lane + 32 * j;
+      if (e < experts && (select[j] > v || (select[j] == v && e < idx))) { v = select[j]; idx = e; }
+    }
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, v, o);
+      const int oidx = __shfl_xor_sync(0xffffffffu, idx, o);
+      if (ov > v || (ov == v && oidx < idx)) { v = ov; idx = oidx; }
+    }
+    if (idx == 0x7fffffff) idx = 0;
+    float val = 0.f;
+#pragma unroll
+    for (int j = 0; j < kPer; ++j) {
+      const float cand = __shfl_sync(0xffffffffu, score[j], idx & 31);
+      if (j == (idx >> 5)) val = cand;
+      if (j == (idx >> 5) && lane == (idx & 31)) select[j] = -INFINITY;
+    }
+    wsum += val;
+    if (lane == k) { mine = val; oi[k] = idx; }
+  }
+  if (lane < topk) ow[lane] = (normalize ? mine / (wsum + 1e-20f) : mine) * route_scale;
+}
+
+// ---------------------------------------------------------------------------------
+// MoE plan: single CTA (routes are at most tokens * topk; the kernel is latency-bound)
+//   topk_idx[route] in [0, experts) ; local experts are [e_lo, e_hi)
+//   outputs (expert-major position p):
+//     src_token[p], dst_row[p] = route id, row_scale[p] = weight
+//     tile table for row tiles of `ntok` rows: tile_group (local expert id), row0, rows
+//     counts[local experts], meta = {num_tiles, num_rows}
+// ---------------------------------------------------------------------------------
+__global__ void __launch_bounds__(1024)
+moe_plan_kernel(const int* __restrict__ topk_idx, const float* __restrict__ topk_w, int routes,
+                int topk, int e_lo, int e_hi, int ntok, int* __restrict__ src_token,
+                int* __restrict__ dst_row, float* __restrict__ row_scale,
+                int* __restrict__ tile_group, int* __restrict__ tile_row0,
+                int* __restrict__ tile_rows, int max_tiles, int* __restrict__ counts,
+                int* __restrict__ meta, DeviceStatus* st) {
+  __shared__ int cnt[256];
+  __shared__ int off[257];
+  const int local = e_hi - e_lo;
+  for (int i = threadIdx.x; i < 256; i += blockDim.x) cnt[i] = 0;
+  __syncthreads();
+  for (int r = threadIdx.x; r < routes; r += blockDim.x) {
+    const int e = topk_idx[r];
+    if (e >= e_lo && e < e_hi) atomicAdd(&cnt[e - e_lo], 1);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int acc = 0, tiles = 0;
+    for (int e = 0; e < local; ++e) {
+      off[e] = acc;
+      const int c = cnt[e];
+      for (int r0 = 0; r0 < c; r0 += ntok) {
+        if (tiles < max_tiles) {
+          tile_group[tiles] = e;
+          tile_row0[tiles] = acc + r0;
+          tile_rows[tiles] = min(ntok, c - r0);
+        }
+        ++tiles;
+      }
+      acc += c;
+      counts[e] = c;
+    }
+    off[local] = acc;
+    if (tiles > max_tiles) {
+      report_status(st, kStatusBadShape, 0x30, tiles, max_tiles);
+      tiles = max_tiles;
+    }
+    meta[0] = tiles;
+    meta[1] = acc;
+  }
+  __syncthreads();
+  // Placement keeps the routes of one expert in ascending route order (bit-stable buffers
+  // from run to run): each warp walks all routes for its experts and ranks hits by ballot.
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+  for (int e = warp; e < local; e += nwarps) {
+    int base = off[e];
+    for (int r0 = 0; r0 < routes; r0 += 32) {
+      const int r = r0 + lane;
+      const bool hit = r < routes && topk_idx[r] == e + e_lo;
+      const uint32_t mask = __ballot_sync(0xffffffffu, hit);
+      if (hit) {
+        const int p = base + __popc(mask & ((1u << lane) - 1u));
+        src_token[p] = r / topk;
+        dst_row[p] = r;
+        row_scale[p] = topk_w ? topk_w[r] : 1.f;
+      }
+      base += __popc(mask);
+    }
+  }
+}
+
+__global__ void gather_rows_kernel(const __nv_bfloat16* __restrict__ x, long long ldx,
+                                   const int* __restrict__ src_token, const int* __restrict__ meta,
+                                   __nv_bfloat16* __restrict__ out, long long ldo, int cap_rows,
+                                   int dim, int src_rows, DeviceStatus* st) {
+  const int r = blockIdx.x;
+  const int valid = min(meta[1], cap_rows);
+  if (r >= valid) return;
+  int t = src_token[r];
+  if (t < 0 || t >= src_rows) {
+    if (threadIdx.x == 0) report_status(st, kStatusBadIndex, 0x40, r, t);
+    return;
+  }
+  const uint4* src = reinterpret_cast<const uint4*>(x + t * ldx);
+  uint4* dst = reinterpret_cast<uint4*>(out + r * ldo);
+  for (int i = threadIdx.x; i < dim / 8; i += blockDim.x) dst[i] = src[i];
+}
+
+// out[t] = residual[t] + sum_{slot} route_out[t*slots + slot] (only slots whose expert is local,
+// or every slot >= topk, which carry dense contributions such as the shared expert)
+__global__ void __launch_bounds__(256)
+moe_reduce_kernel(const __nv_bfloat16* __restrict__ route_out, int slots, int topk,
+                  const int* __restrict__ topk_idx, int e_lo, int e_hi,
+                  const __nv_bfloat16* __restrict__ extra, long long lde,
+                  const __nv_bfloat16* __restrict__ residual, long long ldr, void* __restrict__ out,
+                  long long ldo, int out_fp32, int rows, int dim) {
+  const int t = blockIdx.x;
+  if (t >= rows) return;
+  for (int i = threadIdx.x * 8; i < dim; i += blockDim.x * 8) {
+    float acc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+    for (int s = 0; s < slots; ++s) {
+      if (s < topk) {
+        const int e = topk_idx[t * topk + s];
+        if (e < e_lo || e >= e_hi) continue;
+      }
+      const uint4 v = *reinterpret_cast<const uint4*>(route_out + (static_cast<size_t>(t) * slots + s) * dim + i);
+      const __nv_bfloat16* vp = reinterpret_cast<const __nv_bfloat16*>(&v);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] += __bfloat162float(vp[j]);
+    }
+    if (extra) {
+      const uint4 v = *reinterpret_cast<const uint4*>(extra + t * lde + i);
+      const __nv_bfloat16* vp = reinterpret_cast<const __nv_bfloat16*>(&v);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] += __bfloat162float(vp[j]);
+    }
+    if (residual) {
+      const uint4 v = *reinterpret_cast<const uint4*>(residual + t * ldr + i);
+      const __nv_bfloat16* vp = reinterpret_cast<const __nv_bfloat16*>(&v);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] += __bfloat162float(vp[j]);
+    }
+    if (out_fp32) {
+      float* o = reinterpret_cast<float*>(out) + t * ldo + i;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = acc[j];
+    } else {
+      __nv_bfloat16 o[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = __float2bfloat16_rn(acc[j]);
+      *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(out) + t * ldo + i) =
+          *reinterpret_cast<uint4*>(o);
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------
+// greedy argmax / top-k over the vocabulary.  One CTA per row.
+// ---------------------------------------------------------------------------------
+__device__ __forceinline__ bool better(float v, int i, float ov, int oi) {
+  return v > ov || (v == ov && i < oi);
+}
+
+__global__ void __launch_bounds__(1024)
+argmax_kernel(const float* __restrict__ logits, long long ldl, int rows, int vocab,
+              int* __restrict__ out_id, float* __restrict__ out_val) {
+  __shared__ float sv[32];
+  __shared__ int si[32];
+  const int r = blockIdx.x;
+  if (r >= rows) return;
+  const float* lr = logits + r * ldl;
+  float best = -INFINITY;
+  int bi = 0x7fffffff;
+  for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+    const float v = lr[i];
+    if (v == v && better(v, i, best, bi)) { best = v; bi = i; }  // NaN never wins
+  }
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    if (better(ov, oi, best, bi)) { best = ov; bi = oi; }
+  }
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+  if (l == 0) { sv[w] = best; si[w] = bi; }
+  __syncthreads();
+  if (w == 0) {
+    best = l < (blockDim.x >> 5) ? sv[l] : -INFINITY;
+    bi = l < (blockDim.x >> 5) ? si[l] : 0x7fffffff;
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (better(ov, oi, best, bi)) { best = ov; bi = oi; }
+    }
+    if (l == 0) {
+      out_id[r] = bi == 0x7fffffff ? -1 : bi;  // -1: no finite candidate
+      if (out_val) out_val[r] = best;
+    }
+  }
+}
+
+// top-k by k rounds of block argmax with a "already taken" threshold (k small, rows few)
+__global__ void __launch_bounds__(1024)
+topk_logits_kernel(const float* __restrict__ logits, long long ldl, int rows, int vocab, int k,
+                   int* __restrict__ out_id, float* __restrict__ out_val) {
+  __shared__ float sv[32];
+  __shared__ int si[32];
+  __shared__ float last_v;
+  __shared__ int last_i;
+  const int r = blockIdx.x;
+  if (r >= rows) return;
+  const float* lr = logits + r * ldl;
+  if (threadIdx.x == 0) { last_v = INFINITY; last_i = -1; }
+  __syncthreads();
+  for (int it = 0; it < k; ++it) {
+    const float lv = last_v;
+    const int li = last_i;
+    float best = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+      const float v = lr[i];
+      // candidates strictly after (lv, li) in (logit desc, id asc) order
+      const bool after = v < lv || (v == lv && i > li);
+      if (v == v && after && better(v, i, best, bi)) { best = v; bi = i; }
+    }
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (better(ov, oi, best, bi)) { best = ov; bi = oi; }
+    }
+    const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+    if (l == 0) { sv[w] = best; si[w] = bi; }
+    __syncthreads();
+    if (w == 0) {
+      best = l < (blockDim.x >> 5) ? sv[l] : -INFINITY;
+      bi = l < (blockDim.x >> 5) ? si[l] : 0x7fffffff;
+      for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (better(ov, oi, best, bi)) { best = ov; bi = oi; }
+      }
+      if (l == 0) {
+        out_id[r * k + it] = bi == 0x7fffffff ? -1 : bi;
+        out_val[r * k + it] = best;
+        last_v = best;
+        last_i = bi;
+      }
+    }
+    __syncthreads();
+  }
+}
+
+// ---------------------------------------------------------------------------------
+// paged pool: copy whole pages (all layers) for copy-on-write.  pool is
+// [layers, pages, page_elems]; pairs = (src_page, dst_page).
+// ---------------------------------------------------------------------------------
+__global__ void copy_pages_kernel(__nv_bfloat16* pool, long long layer_stride, long long page_elems,
+                                  const int* __restrict__ pairs, int n_pairs, int n_pages, int layers,
+                                  DeviceStatus* st) {
+  const int pair = blockIdx.x, layer = blockIdx.y;
+  if (pair >= n_pairs || layer >= layers) return;
+  const int src = pairs[2 * pair], dst = pairs[2 * pair + 1];
+  if (src < 0 || src >= n_pages || dst < 0 || dst >= n_pages) {
+    if (threadIdx.x == 0) report_status(st, kStatusBadIndex, 0x50, src, dst);
+    return;
+  }
+  const uint4* s = reinterpret_cast<const uint4*>(pool + layer * layer_stride + src * page_elems);
+  uint4* d = reinterpret_cast<uint4*>(pool + layer * layer_stride + dst * page_elems);
+  for (long long i = threadIdx.x; i < page_elems / 8; i += blockDim.x) d[i] = s[i];
+}
+
+}  // namespace fb
+
+using namespace fb;
+
+#define FB_CHECK_LAUNCH() (cudaGetLastError() == cudaSuccess ? FB_OK : FB_ERR_LAUNCH)
+
+extern "C" int fb_status_bytes(void) { return static_cast<int>(sizeof(DeviceStatus)); }
+
+extern "C" int fb_embedding(const int* ids, const void* table, void* out, int rows, int dim,
+                            int vocab, void* status, void* stream) {
+  if (rows <= 0 || dim % 8 != 0) return FB_ERR_SHAPE;
+  embedding_kernel<<<rows, 128, 0, static_cast<cudaStream_t>(stream)>>>(
+      ids, static_cast<const __nv_bfloat16*>(table), static_cast<__nv_bfloat16*>(out), rows, dim,
+      vocab, static_cast<DeviceStatus*>(status));
+  return FB_CHECK_LAUNCH();
+}
+
+extern "C" int fb_add_rmsnorm(const void* x, long long ldx, const void* delta, long long ldd,
+                              const void* weight, void* res_out, long long ldr, void* norm_out,
+                              long long ldn, int rows, int dim, float eps, void* stream) {
+  if (rows <= 0 || dim % 8 != 0 || dim > 16384) return FB_ERR_SHAPE;
+  if ((ldx | ldd | ldr | ldn) % 8 != 0) return FB_ERR_ALIGN;
+  static bool attr = false;
+  if (!attr) {
+    cudaFuncSetAttribute(add_rmsnorm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 65536);
+    attr = true;
+  }
+  add_rmsnorm_kernel<<<rows, 256, dim * sizeof(float), static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(x), ldx, static_cast<const __nv_bfloat16*>(delta), ldd,
+      static_cast<const __nv_bfloat16*>(weight), static_cast<__nv_bfloat16*>(res_out), ldr,
+      static_cast<__nv_bfloat16*>(norm_out), ldn, rows, dim, eps);
+  return FB_CHECK_LAUNCH();
+}
+
+extern "C" int fb_mla_prep(const void* q, long long ldq, int q_head_dim, const void* ckv,
+                           long long ldckv, int heads, int kv_lora, int rope_dim,
+                           const void* kv_norm_w, float eps,
+                           const float* cos_t, const float* sin_t, int max_pos,
+                           const int* positions, const long long* write_slot, void* kv_pool,
+                           long long pool_rows, void* q_out, long long ldq_out, int rows,
+                           void* status, void* stream) {
+  if (rows <= 0 || rope_dim % 2 != 0 || heads <= 0) return FB_ERR_SHAPE;
+  mla_prep_kernel<<<rows, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(q), ldq, q_head_dim,
+      static_cast<const __nv_bfloat16*>(ckv), ldckv, heads, kv_lora, rope_dim, static_cast<const __nv_bfloat16*>(kv_norm_w), eps, cos_t, sin_t, max_pos, positions,
+      write_slot, static_cast<__nv_bfloat16*>(kv_pool), pool_rows,
+      static_cast<__nv_bfloat16*>(q_out), ldq_out, rows, static_cast<DeviceStatus*>(status));
+  return FB_CHECK_LAUNCH();
+}
+
+extern "C" int fb_router_topk(const float* logits, long long ldl, const float* bias,
+                              const long long* hash_table, const int* token_ids, int rows,
+                              int experts, int topk, int score_fn, int n_groups, int topk_groups,
+                              int normalize, float route_scale, int* out_idx, float* out_w,
+                              void* stream) {
+  if (rows <= 0 || experts <= 0 || experts > 256 || topk <= 0 || topk > 32 || topk > experts)
+    return FB_ERR_SHAPE;
+  if (n_groups > 32 || (n_groups > 1 && experts % n_groups != 0)) return FB_ERR_SHAPE;
+  const int blocks = (rows + 3) / 4;
+  router_topk_kernel<<<blocks, 128, 0, static_cast<cudaStream_t>(stream)>>>(
+      logits, ldl, bias, hash_table, token_ids, rows, experts, topk, score_fn, n_groups,
+      topk_groups, normalize, route_scale, out_idx, out_w);
+  return FB_CHECK_LAUNCH();
+}
+
+extern "C" int fb_moe_plan(const int* topk_idx, const float* topk_w, int routes, int topk, int e_lo,
+                           int e_hi, int ntok, int* src_token, int* dst_row, float* row_scale,
+                           int* tile_group, int* tile_row0, int* tile_rows, int max_tiles,
+                           int* counts, int* meta, void* status, void* stream) {
+  if (routes <= 0 || topk <= 0 || e_hi <= e_lo || e_hi - e_lo > 256 || ntok <= 0) return FB_ERR_SHAPE;
+  moe_plan_kernel<<<1, 1024, 0, static_cast<cudaStream_t>(stream)>>>(
+      topk_idx, topk_w, routes, topk, e_lo, e_hi, ntok, src_token, dst_row, row_scale, tile_group,
+      tile_row0, tile_rows, max_tiles, counts, meta, static_cast<DeviceStatus*>(status));
+  return FB_CHECK_LAUNCH();
+}
+
+extern "C" int fb_gather_rows(const void* x, long long ldx, const int* src_token, const int* meta,
+                              void* out, long long ldo, int cap_rows, int dim, int src_rows,
+                              void* status, void* stream) {
+  if (cap_rows <= 0 || dim % 8 != 0) return FB_ERR_SHAPE;
+  gather_rows_kernel<<<cap_rows, 128, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(x), ldx, src_token, meta, static_cast<__nv_bfloat16*>(out),
+      ldo, cap_rows, dim, src_rows, static_cast<DeviceStatus*>(status));
+  return FB_CHECK_LAUNCH();
+}
+
+extern "C" int fb_moe_reduce(const void* route_out, int slots, int topk, const int* topk_idx,
+                             int e_lo, int e_hi, const void* extra, long long lde,
+                             const void* residual, long long ldr, void* out, long long ldo,
+                             int out_fp32, int rows, int dim, void* stream) {
+  if (rows <= 0 || dim % 8 != 0 || slots < topk) return FB_ERR_SHAPE;
+  moe_reduce_kernel<<<rows, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(route_out), slots, topk, topk_idx, e_lo, e_hi,
+      static_cast<const __nv_bfloat16*>(extra), lde, static_cast<const __nv_bfloat16*>(residual),
+      ldr, out, ldo, out_fp32, rows, dim);
+  return FB_CHECK_LAUNCH();
+}
+
+extern "C" int fb_argmax(const float* logits, long long ldl, int rows, int vocab, int* out_id,
+                         float* out_val, void* stream) {
+  if (rows <= 0 || vocab <= 0) return FB_ERR_SHAPE;
+  argmax_kernel<<<rows, 1024, 0, static_cast<cudaStream_t>(stream)>>>(logits, ldl, rows, vocab,
+                                                                      out_id, out_val);
+  return FB_CHECK_LAUNCH();
+}
+
+extern "C" int fb_topk_logits(const float* logits, long long ldl, int rows, int vocab, int k,
+                              int* out_id, float* out_val, void* stream) {
+  if (rows <= 0 || vocab <= 0 || k <= 0 || k > 64) return FB_ERR_SHAPE;
+  topk_logits_kernel<<<rows, 1024, 0, static_cast<cudaStream_t>(stream)>>>(logits, ldl, rows, vocab,
+                                                                           k, out_id, out_val);
+  return FB_CHECK_LAUNCH();
+}
+
+extern "C" int fb_copy_pages(void* pool, long long layer_stride, long long page_elems,
+                             const int* pairs, int n_pairs, int n_pages, int layers, void* status,
+                             void* stream) {
+  if (n_pairs <= 0) return FB_OK;
+  if (page_elems % 8 != 0 || layers <= 0) return FB_ERR_SHAPE;
+  dim3 grid(n_pairs, layers);
+  copy_pages_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<__nv_bfloat16*>(pool), layer_stride, page_elems, pairs, n_pairs, n_pages, layers,
+      static_cast<DeviceStatus*>(status));
+  return FB_CHECK_LAUNCH();
+}

@@ -1,0 +1,137 @@
+// C ABI of libferrule_b200.so.  Every entry point is `extern "C"`, takes plain
+// pointers / integers plus the CUDA stream as `void*`, launches asynchronously on
+// that stream and returns an FB_* code.  Python binds these through ctypes
+// (ferrule_b200/ops/_lib.py); argument structs are mirrored there field for field.
+//
+// Plays the role of the reference's same-checkout POD ABI between its device runtime
+// and native kernels (crates/ferrule-backend/native/cuda/abi/core_provider.h:477-557,
+// cutlass_provider.h:390-456).
+#pragma once
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum {
+  FB_OK = 0,
+  FB_ERR_SHAPE = 1,   // launcher rejected the arguments (nothing was launched)
+  FB_ERR_ALIGN = 2,   // pointer or stride not 16-byte aligned for TMA
+  FB_ERR_DRIVER = 3,  // driver entry point missing or tensor-map encode failed
+  FB_ERR_LAUNCH = 4,  // cudaLaunch / attribute error
+  FB_ERR_RUNTIME = 5, // other CUDA runtime error
+  FB_ERR_LIMIT = 6,   // size beyond a fixed capacity
+};
+
+// ---- status word -----------------------------------------------------------------
+// 16 bytes: {code, where, detail0, detail1}.  code 0 = ok.
+int fb_status_bytes(void);
+
+// ---- tcgen05 GEMM ------------------------------------------------------------------
+typedef struct FbGemmArgs {
+  const void* w;            // bf16 [groups, w_rows_per_group, k] (row pitch ldw elements)
+  const void* x;            // bf16 [x_rows, k] (row pitch ldx elements)
+  void* out;
+  long long ldw;
+  long long w_group_stride; // elements between groups
+  long long ldx;
+  long long ldo;
+  int n_out;                // output channels per group
+  int k;
+  int groups;
+  int w_rows_per_group;
+  int x_rows;
+  int ntok;                 // rows per tile: 16, 32, 64, 128 or 256
+  int epilogue;             // 0 store, 1 swiglu (dual weights), 2 scatter, 3 all-reduce
+  int dual_offset;          // row of the "up" block inside a group (epilogue 1)
+  int out_fp32;
+  int max_tok_tiles;        // capacity of the tile table (grouped mode)
+  int x_group_koff;         // batched mode (groups > 1, no tile table): X column offset per group
+  int out_group_coff;       // batched mode: output column offset per group
+  const int* tile_group;    // grouped mode: per row-tile expert id, first row, row count
+  const int* tile_row0;
+  const int* tile_rows;
+  const int* num_tok_tiles; // device scalar
+  const int* dst_row;       // epilogue 2
+  const float* row_scale;   // epilogue 2
+  float act_limit;          // epilogue 1: clamp (0 = off)
+  int rank;                 // epilogue 3
+  int world;
+  int rows_cap;
+  int flag_capacity;
+  void* peer_recv[8];
+  void* peer_flags[8];
+  void* local_ctr;
+  const void* residual;
+  long long ldr;
+  unsigned long long peer_wait_ns;
+  void* status;
+} FbGemmArgs;
+
+int fb_gemm_bf16(const FbGemmArgs* args, void* stream);
+
+// ---- paged latent-KV attention -------------------------------------------------------
+typedef struct FbAttnArgs {
+  const void* q;            // bf16 [rows, heads, kv_lora + rope_dim]
+  const void* kv;           // bf16 [pool_rows, kv_lora + rope_dim] (one layer of the pool)
+  void* out;                // bf16 [rows, heads, kv_lora]
+  const int* block_table;   // [num_seqs, max_blocks]
+  const int* row_seq;       // [rows] sequence of each query row
+  const int* row_pos;       // [rows] last kv position the row may see
+  const float* sink;        // optional [heads]
+  float* part_o;            // split scratch [rows, splits, heads, kv_lora] fp32
+  float* part_ml;           // split scratch [rows, splits, heads, 2] fp32
+  void* status;
+  long long ldq;
+  long long ldo;
+  long long pool_rows;
+  int rows;
+  int heads;
+  int kv_lora;
+  int rope_dim;
+  int num_seqs;
+  int max_blocks;
+  int page_size;
+  int group_rows;           // consecutive query rows of one sequence sharing a CTA tile (1,2,4,8,16)
+  int splits;
+  int split_tokens;         // multiple of 64
+  float softmax_scale;
+} FbAttnArgs;
+
+int fb_mla_attention(const FbAttnArgs* args, void* stream);
+
+// ---- small fused operators ------------------------------------------------------------
+int fb_embedding(const int* ids, const void* table, void* out, int rows, int dim, int vocab,
+                 void* status, void* stream);
+int fb_add_rmsnorm(const void* x, long long ldx, const void* delta, long long ldd,
+                   const void* weight, void* res_out, long long ldr, void* norm_out, long long ldn,
+                   int rows, int dim, float eps, void* stream);
+int fb_mla_prep(const void* q, long long ldq, int q_head_dim, const void* ckv, long long ldckv,
+                int heads, int kv_lora, int rope_dim, const void* kv_norm_w, float eps,
+                const float* cos_t,
+                const float* sin_t, int max_pos, const int* positions, const long long* write_slot,
+                void* kv_pool, long long pool_rows, void* q_out, long long ldq_out, int rows,
+                void* status, void* stream);
+int fb_router_topk(const float* logits, long long ldl, const float* bias,
+                   const long long* hash_table, const int* token_ids, int rows, int experts,
+                   int topk, int score_fn, int n_groups, int topk_groups, int normalize,
+                   float route_scale, int* out_idx, float* out_w, void* stream);
+int fb_moe_plan(const int* topk_idx, const float* topk_w, int routes, int topk, int e_lo, int e_hi,
+                int ntok, int* src_token, int* dst_row, float* row_scale, int* tile_group,
+                int* tile_row0, int* tile_rows, int max_tiles, int* counts, int* meta, void* status,
+                void* stream);
+int fb_gather_rows(const void* x, long long ldx, const int* src_token, const int* meta, void* out,
+                   long long ldo, int cap_rows, int dim, int src_rows, void* status, void* stream);
+int fb_moe_reduce(const void* route_out, int slots, int topk, const int* topk_idx, int e_lo,
+                  int e_hi, const void* extra, long long lde, const void* residual, long long ldr,
+                  void* out, long long ldo, int out_fp32, int rows, int dim, void* stream);
+int fb_argmax(const float* logits, long long ldl, int rows, int vocab, int* out_id, float* out_val,
+              void* stream);
+int fb_topk_logits(const float* logits, long long ldl, int rows, int vocab, int k, int* out_id,
+                   float* out_val, void* stream);
+int fb_copy_pages(void* pool, long long layer_stride, long long page_elems, const int* pairs,
+                  int n_pairs, int n_pages, int layers, void* status, void* stream);
+
+#ifdef __cplusplus
+}
+#endif

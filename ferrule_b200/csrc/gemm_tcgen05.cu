@@ -1,0 +1,528 @@
+// Weight-stationary ("swap-AB") grouped GEMM for sm_100a.
+//
+//   out[row, n] = sum_k X[row, k] * W[group(row), n, k]
+//
+// The weight tile is the UMMA A operand (M = 128 output channels), the activation
+// rows are the B operand (UMMA N = NTOK rows, 16..256), so a decode step with a
+// handful of rows per expert still fills the 128-lane datapath and streams every
+// weight byte exactly once.  Accumulators live in TMEM (double buffered), operands
+// arrive by TMA into 128-byte-swizzled shared memory, one thread issues
+// tcgen05.mma, four warps drain TMEM and run the fused epilogue:
+//
+//   kEpiStore   : out[row, n]            = acc                      (bf16 or fp32)
+//   kEpiSwiGLU  : out[row, n]            = silu(gate) * up          (two weight tiles per k-block)
+//   kEpiScatter : out[dst_row[row], n]   = acc * row_scale[row]     (MoE down projection)
+//   kEpiAllReduce: partial tiles are pushed into every rank's receive buffer over
+//                 NVLink peer stores, then summed in rank order once all have landed
+//                 (one-shot all-reduce fused behind the GEMM, tile by tile).
+//
+// Counterpart of the reference's row-dot linear and mma.sync projection kernels
+// (crates/ferrule-backend/native/cuda/implementations/portable/entrypoints.cu:208-340,
+//  .../cutlass/capabilities/fp8_projection.cuh:421-497, bf16_compressor.cuh:223-313) and of
+// its CUTLASS grouped expert GEMM (.../architectures/sm103/grouped_fp4_moe.cuh:1115-1222).
+#include <cuda.h>
+
+#include "common.cuh"
+#include "ferrule_b200.h"
+
+namespace fb {
+
+constexpr int kTileN = 128;   // output channels per tile (UMMA M)
+constexpr int kBlockK = 64;   // bf16 elements per k-block = one 128-byte swizzle row
+constexpr int kUmmaK = 16;
+constexpr int kGemmThreads = 192;
+
+enum { kEpiStore = 0, kEpiSwiGLU = 1, kEpiScatter = 2, kEpiAllReduce = 3 };
+
+struct GemmParams {
+  int n_out;          // output channels per group
+  int k;              // reduction length
+  int n_tiles;        // ceil(n_out / 128)
+  int dual_offset;    // row offset of the "up" block inside a group (SwiGLU mode)
+  int dense_rows;     // rows of X when no tile table is given
+  int max_tok_tiles;  // capacity of the tile table
+  int batched;        // every group multiplies all dense rows (per-head projections)
+  int x_group_koff;   // batched: column offset of group g inside an X row = g * x_group_koff
+  int out_group_coff; // batched: column offset of group g inside an output row
+  int groups;
+  const int* tile_group;
+  const int* tile_row0;
+  const int* tile_rows;
+  const int* num_tok_tiles;  // device scalar
+  void* out;
+  long long ldo;
+  int out_fp32;
+  const int* dst_row;
+  const float* row_scale;
+  float act_limit;  // SwiGLU clamp (0 = none)
+  DeviceStatus* status;
+  // fused all-reduce
+  int rank;
+  int world;
+  int rows_cap;              // rows per source slot in the receive buffer
+  float* peer_recv[8];       // receive buffer of every rank, in this rank's address space
+  uint32_t* peer_flags[8];   // per-tile arrival counters of every rank
+  uint32_t* local_ctr;       // [0] = calls completed, [1] = CTAs finished this call
+  const __nv_bfloat16* residual;  // optional, added after the reduction
+  long long ldr;
+  unsigned long long peer_wait_ns;
+};
+
+template <int NTOK, bool DUAL>
+struct GemmCfg {
+  static constexpr int kWBytes = kTileN * kBlockK * 2;
+  static constexpr int kXBytes = NTOK * kBlockK * 2;
+  static constexpr int kStageBytes = kWBytes * (DUAL ? 2 : 1) + kXBytes;
+  static constexpr int kBudget = 200 * 1024;
+  static constexpr int kStagesRaw = kBudget / kStageBytes;
+  static constexpr int kStages = kStagesRaw > 10 ? 10 : kStagesRaw;
+  static constexpr int kAccCols = NTOK * (DUAL ? 2 : 1);
+  static constexpr int kTmemCols = (2 * kAccCols) < 32 ? 32 : (2 * kAccCols);
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align*/ + 256 /*barriers*/;
+  static_assert(kTmemCols <= 512, "accumulators exceed TMEM");
+  static_assert((kTmemCols & (kTmemCols - 1)) == 0, "TMEM columns must be a power of two");
+  static_assert(kStages >= 2, "not enough shared memory for a pipeline");
+};
+
+struct TileInfo {
+  int g, row0, rows, nt;
+};
+
+template <int NTOK>
+__device__ __forceinline__ TileInfo decode_tile(const GemmParams& p, int t, int tiles_per_group) {
+  TileInfo ti;
+  const int m = t / p.n_tiles;
+  ti.nt = t - m * p.n_tiles;
+  if (p.tile_group) {
+    ti.g = p.tile_group[m];
+    ti.row0 = p.tile_row0[m];
+    ti.rows = min(p.tile_rows[m], NTOK);
+  } else if (p.batched) {
+    ti.g = m / tiles_per_group;
+    ti.row0 = (m - ti.g * tiles_per_group) * NTOK;
+    ti.rows = min(NTOK, p.dense_rows - ti.row0);
+  } else {
+    ti.g = 0;
+    ti.row0 = m * NTOK;
+    ti.rows = min(NTOK, p.dense_rows - ti.row0);
+  }
+  return ti;
+}
+
+__device__ __forceinline__ float silu_f(float x) { return x / (1.f + __expf(-x)); }
+
+template <int NTOK, bool DUAL, int EPI>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_swapab_kernel(const __grid_constant__ CUtensorMap tmap_w,
+                   const __grid_constant__ CUtensorMap tmap_x, const GemmParams p) {
+  using Cfg = GemmCfg<NTOK, DUAL>;
+  extern __shared__ uint8_t smem_raw[];
+  // 1024-byte alignment is required by the 128-byte swizzle atoms.
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::kStages * Cfg::kStageBytes);
+  uint64_t* full_bar = bars;
+  uint64_t* empty_bar = bars + Cfg::kStages;
+  uint64_t* acc_full = bars + 2 * Cfg::kStages;
+  uint64_t* acc_empty = acc_full + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < Cfg::kStages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&acc_full[a], 1);
+      mbar_init(&acc_empty[a], 4);
+    }
+    *abort_flag = 0;
+    fence_barrier_init();
+    tma_prefetch_desc(&tmap_w);
+    tma_prefetch_desc(&tmap_x);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, Cfg::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int tiles_per_group = (p.dense_rows + NTOK - 1) / NTOK;
+  const int num_tok_tiles = p.tile_group ? min(*p.num_tok_tiles, p.max_tok_tiles)
+                                         : tiles_per_group * (p.batched ? p.groups : 1);
+  const int total = num_tok_tiles * p.n_tiles;
+  const int kblocks = (p.k + kBlockK - 1) / kBlockK;
+
+  uint32_t call = 0;
+  if (EPI == kEpiAllReduce) call = *reinterpret_cast<volatile uint32_t*>(p.local_ctr);
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    if (lane == 0) {
+      int s = 0;
+      uint32_t ph = 0;
+      bool ok = true;
+      long long issued = 0;
+      for (int t = blockIdx.x; t < total && ok; t += gridDim.x) {
+        const TileInfo ti = decode_tile<NTOK>(p, t, tiles_per_group);
+        const int g = ti.g, nt = ti.nt, row0 = ti.row0;
+        const int xk0 = p.batched ? g * p.x_group_koff : 0;
+        for (int kb = 0; kb < kblocks; ++kb) {
+          ok = mbar_wait(&empty_bar[s], ph ^ 1u, abort_flag, p.status, 0x100);
+          if (!ok) break;
+          uint8_t* stage = smem + s * Cfg::kStageBytes;
+          mbar_arrive_expect_tx(&full_bar[s], Cfg::kStageBytes);
+          tma_load_3d(stage, &tmap_w, &full_bar[s], kb * kBlockK, nt * kTileN, g);
+          if (DUAL)
+            tma_load_3d(stage + Cfg::kWBytes, &tmap_w, &full_bar[s], kb * kBlockK,
+                        p.dual_offset + nt * kTileN, g);
+          tma_load_2d(stage + Cfg::kWBytes * (DUAL ? 2 : 1), &tmap_x, &full_bar[s],
+                      xk0 + kb * kBlockK, row0);
+          ++issued;
+          if (++s == Cfg::kStages) { s = 0; ph ^= 1u; }
+        }
+      }
+      // Drain after an abort: copies this thread issued may still be in flight, and the
+      // CTA may not exit under them.  Wait (bounded) for the full barrier of each of
+      // the last kStages issues to complete the phase it was armed for.
+      if (*abort_flag) {
+        const long long first = issued > Cfg::kStages ? issued - Cfg::kStages : 0;
+        for (long long i = first; i < issued; ++i) {
+          const int si = static_cast<int>(i % Cfg::kStages);
+          const uint32_t pi = static_cast<uint32_t>((i / Cfg::kStages) & 1);
+          const uint64_t t0 = globaltimer_ns();
+          while (!mbar_try_wait(&full_bar[si], pi) && globaltimer_ns() - t0 < 2000000ull) {
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer --------------------------------
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc(kTileN, NTOK, 1, 1);
+      int s = 0;
+      uint32_t ph = 0;
+      int a = 0;
+      uint32_t aph = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < total && ok; t += gridDim.x) {
+        ok = mbar_wait(&acc_empty[a], aph ^ 1u, abort_flag, p.status, 0x200);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t d0 = tmem_base + a * Cfg::kAccCols;
+        for (int kb = 0; kb < kblocks; ++kb) {
+          ok = mbar_wait(&full_bar[s], ph, abort_flag, p.status, 0x201);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t sw = smem_u32(smem + s * Cfg::kStageBytes);
+          const uint32_t sx = sw + Cfg::kWBytes * (DUAL ? 2 : 1);
+#pragma unroll
+          for (int kk = 0; kk < kBlockK / kUmmaK; ++kk) {
+            const uint32_t koff = kk * kUmmaK * 2;
+            const uint64_t db = umma_desc_k128(sx + koff);
+            const uint32_t acc = (kb | kk) ? 1u : 0u;
+            umma_bf16(d0, umma_desc_k128(sw + koff), db, idesc, acc);
+            if (DUAL) umma_bf16(d0 + NTOK, umma_desc_k128(sw + Cfg::kWBytes + koff), db, idesc, acc);
+          }
+          umma_commit(&empty_bar[s]);
+          if (++s == Cfg::kStages) { s = 0; ph ^= 1u; }
+        }
+        if (ok) umma_commit(&acc_full[a]);
+        a ^= 1;
+        if (a == 0) aph ^= 1u;
+      }
+    }
+  } else {
+    // ------------------------------ epilogue (4 warps) -------------------------
+    const int q = warp & 3;  // TMEM lane quarter this warp may read
+    const int ch_in_tile = q * 32 + lane;
+    const int epi_tid = (warp - 2) * 32 + lane;
+    int a = 0;
+    uint32_t aph = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < total && ok; t += gridDim.x) {
+      const TileInfo ti = decode_tile<NTOK>(p, t, tiles_per_group);
+      const int row0 = ti.row0, rows = ti.rows;
+      const int n = ti.nt * kTileN + ch_in_tile;
+      const bool n_ok = n < p.n_out;
+      const long long ocol = (p.batched ? static_cast<long long>(ti.g) * p.out_group_coff : 0) + n;
+      ok = mbar_wait(&acc_full[a], aph, abort_flag, p.status, 0x300);
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t tbase = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + a * Cfg::kAccCols;
+#pragma unroll 1
+      for (int c0 = 0; c0 < NTOK; c0 += 16) {
+        if (c0 >= rows) break;  // uniform across the CTA: nothing valid beyond `rows`
+        uint32_t v[16];
+        tmem_ld16(tbase + c0, v);
+        uint32_t u[16];
+        if (DUAL) tmem_ld16(tbase + NTOK + c0, u);
+        tmem_ld_wait();
+        if (n_ok) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const int r = c0 + j;
+            if (r < rows) {
+              float x = __uint_as_float(v[j]);
+              if (EPI == kEpiSwiGLU) {
+                float up = __uint_as_float(u[j]);
+                if (p.act_limit > 0.f) {
+                  x = fminf(x, p.act_limit);
+                  up = fminf(fmaxf(up, -p.act_limit), p.act_limit);
+                }
+                x = silu_f(x) * up;
+              }
+              long long orow = row0 + r;
+              if (EPI == kEpiScatter) {
+                if (p.row_scale) x *= p.row_scale[row0 + r];
+                orow = p.dst_row ? p.dst_row[row0 + r] : orow;
+              }
+              if (EPI == kEpiAllReduce) {
+                const size_t slot =
+                    (static_cast<size_t>((call & 1u) * p.world + p.rank) * p.rows_cap + orow) *
+                        p.n_out + n;
+                for (int pr = 0; pr < p.world; ++pr) p.peer_recv[pr][slot] = x;
+              } else if (orow >= 0) {
+                if (p.out_fp32)
+                  reinterpret_cast<float*>(p.out)[orow * p.ldo + ocol] = x;
+                else
+                  reinterpret_cast<__nv_bfloat16*>(p.out)[orow * p.ldo + ocol] = __float2bfloat16_rn(x);
+              }
+            }
+          }
+        }
+      }
+      // TMEM buffer is free once every warp's loads have completed.
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty[a]);
+      if (EPI == kEpiAllReduce) {
+        // Publish this tile: all 128 epilogue threads' peer stores, then one counter
+        // bump per rank (release at system scope).
+        __threadfence_system();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (epi_tid < p.world) flag_add_release_sys(p.peer_flags[epi_tid] + t, 1u);
+      }
+      a ^= 1;
+      if (a == 0) aph ^= 1u;
+    }
+    if (EPI == kEpiAllReduce) {
+      // Second pass over this CTA's tiles: wait for all ranks' partials, sum in rank
+      // order (identical on every rank), add the residual, write the result.
+      const uint32_t target = static_cast<uint32_t>(p.world) * (call + 1u);
+      for (int t = blockIdx.x; t < total; t += gridDim.x) {
+        const int m = t / p.n_tiles, nt = t - m * p.n_tiles;
+        const int row0 = m * NTOK;
+        const int rows = min(NTOK, p.dense_rows - row0);
+        const int n = nt * kTileN + ch_in_tile;
+        const bool arrived =
+            ok && flag_wait_ge(p.peer_flags[p.rank] + t, target, p.peer_wait_ns, p.status, 0x400 + t);
+        if (!arrived) { ok = false; }
+        if (ok && n < p.n_out) {
+          const float* base = p.peer_recv[p.rank];
+          for (int r = 0; r < rows; ++r) {
+            const long long orow = row0 + r;
+            float acc = 0.f;
+            for (int src = 0; src < p.world; ++src)
+              acc += base[(static_cast<size_t>((call & 1u) * p.world + src) * p.rows_cap + orow) *
+                              p.n_out + n];
+            if (p.residual) acc += __bfloat162float(p.residual[orow * p.ldr + n]);
+            if (p.out_fp32)
+              reinterpret_cast<float*>(p.out)[orow * p.ldo + n] = acc;
+            else
+              reinterpret_cast<__nv_bfloat16*>(p.out)[orow * p.ldo + n] = __float2bfloat16_rn(acc);
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, Cfg::kTmemCols);
+  }
+  if (EPI == kEpiAllReduce && threadIdx.x == 0) {
+    __threadfence();
+    const uint32_t done = atomicAdd(p.local_ctr + 1, 1u);
+    if (done == gridDim.x - 1) {
+      p.local_ctr[1] = 0;
+      __threadfence();
+      p.local_ctr[0] = call + 1u;
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) ==
+            cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  }
+  return fn;
+}
+
+// rank-3 bf16 map: dims (k, rows, groups), box (64, box_rows, 1), 128-byte swizzle.
+static int make_map(CUtensorMap* map, const void* base, uint64_t k, uint64_t rows, uint64_t groups,
+                    uint64_t row_stride_bytes, uint64_t group_stride_bytes, uint32_t box_rows,
+                    int rank) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return FB_ERR_DRIVER;
+  if ((reinterpret_cast<uintptr_t>(base) & 15) || (row_stride_bytes & 15) ||
+      (group_stride_bytes & 15))
+    return FB_ERR_ALIGN;
+  cuuint64_t dims[3] = {k, rows, groups};
+  cuuint64_t strides[2] = {row_stride_bytes, group_stride_bytes};
+  cuuint32_t box[3] = {static_cast<cuuint32_t>(kBlockK), box_rows, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, rank, const_cast<void*>(base), dims,
+                  strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? FB_OK : FB_ERR_DRIVER;
+}
+
+static int g_num_sms = 0;
+static int num_sms() {
+  if (g_num_sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
+    if (g_num_sms <= 0) g_num_sms = 148;
+  }
+  return g_num_sms;
+}
+
+template <int NTOK, bool DUAL, int EPI>
+static int launch_cfg(const CUtensorMap& mw, const CUtensorMap& mx, const GemmParams& p,
+                      int max_tiles, cudaStream_t stream) {
+  using Cfg = GemmCfg<NTOK, DUAL>;
+  auto kern = gemm_swapab_kernel<NTOK, DUAL, EPI>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             Cfg::kSmemBytes) != cudaSuccess)
+      return FB_ERR_LAUNCH;
+    attr_set = true;
+  }
+  int grid = max_tiles < num_sms() ? max_tiles : num_sms();
+  if (grid < 1) grid = 1;
+  kern<<<grid, kGemmThreads, Cfg::kSmemBytes, stream>>>(mw, mx, p);
+  return cudaGetLastError() == cudaSuccess ? FB_OK : FB_ERR_LAUNCH;
+}
+
+template <bool DUAL, int EPI>
+static int launch_ntok(int ntok, const CUtensorMap& mw, const CUtensorMap& mx, const GemmParams& p,
+                       int max_tiles, cudaStream_t stream) {
+  switch (ntok) {
+    case 16: return launch_cfg<16, DUAL, EPI>(mw, mx, p, max_tiles, stream);
+    case 32: return launch_cfg<32, DUAL, EPI>(mw, mx, p, max_tiles, stream);
+    case 64: return launch_cfg<64, DUAL, EPI>(mw, mx, p, max_tiles, stream);
+    case 128: return launch_cfg<128, DUAL, EPI>(mw, mx, p, max_tiles, stream);
+    case 256:
+      if constexpr (!DUAL) return launch_cfg<256, DUAL, EPI>(mw, mx, p, max_tiles, stream);
+      return FB_ERR_SHAPE;
+    default: return FB_ERR_SHAPE;
+  }
+}
+
+}  // namespace fb
+
+using namespace fb;
+
+extern "C" int fb_gemm_bf16(const FbGemmArgs* a, void* stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (a == nullptr || a->w == nullptr || a->x == nullptr || a->out == nullptr) return FB_ERR_SHAPE;
+  if (a->n_out <= 0 || a->k <= 0 || a->groups <= 0 || (a->k % 8) != 0) return FB_ERR_SHAPE;
+  if (a->epilogue < 0 || a->epilogue > 3) return FB_ERR_SHAPE;
+  const bool dual = a->epilogue == kEpiSwiGLU;
+  const int ntok = a->ntok;
+  if (ntok != 16 && ntok != 32 && ntok != 64 && ntok != 128 && ntok != 256) return FB_ERR_SHAPE;
+  if (dual && ntok > 128) return FB_ERR_SHAPE;
+  const bool grouped = a->tile_group != nullptr;
+  if (grouped && (!a->tile_row0 || !a->tile_rows || !a->num_tok_tiles || a->max_tok_tiles <= 0))
+    return FB_ERR_SHAPE;
+  const bool batched = !grouped && a->groups > 1;
+  if (batched && (a->epilogue != kEpiStore || a->x_group_koff % 8 != 0)) return FB_ERR_SHAPE;
+  if (a->x_rows <= 0) return FB_ERR_SHAPE;
+
+  CUtensorMap mw, mx;
+  const uint64_t w_rows = static_cast<uint64_t>(a->w_rows_per_group);
+  int rc = make_map(&mw, a->w, a->k, w_rows, a->groups, static_cast<uint64_t>(a->ldw) * 2,
+                    static_cast<uint64_t>(a->w_group_stride) * 2, kTileN, 3);
+  if (rc != FB_OK) return rc;
+  const uint64_t x_cols = batched ? static_cast<uint64_t>(a->x_group_koff) * (a->groups - 1) + a->k : a->k;
+  rc = make_map(&mx, a->x, x_cols, a->x_rows, 1, static_cast<uint64_t>(a->ldx) * 2, 0, ntok, 2);
+  if (rc != FB_OK) return rc;
+
+  GemmParams p{};
+  p.n_out = a->n_out;
+  p.k = a->k;
+  p.n_tiles = (a->n_out + kTileN - 1) / kTileN;
+  p.dual_offset = a->dual_offset;
+  p.dense_rows = a->x_rows;
+  p.batched = batched ? 1 : 0;
+  p.x_group_koff = a->x_group_koff;
+  p.out_group_coff = a->out_group_coff;
+  p.groups = a->groups;
+  p.max_tok_tiles = a->max_tok_tiles;
+  p.tile_group = a->tile_group;
+  p.tile_row0 = a->tile_row0;
+  p.tile_rows = a->tile_rows;
+  p.num_tok_tiles = a->num_tok_tiles;
+  p.out = a->out;
+  p.ldo = a->ldo;
+  p.out_fp32 = a->out_fp32;
+  p.dst_row = a->dst_row;
+  p.row_scale = a->row_scale;
+  p.act_limit = a->act_limit;
+  p.status = static_cast<DeviceStatus*>(a->status);
+  const int tok_tiles = grouped ? a->max_tok_tiles
+                                : ((a->x_rows + ntok - 1) / ntok) * (batched ? a->groups : 1);
+  const int max_tiles = tok_tiles * p.n_tiles;
+
+  if (a->epilogue == kEpiAllReduce) {
+    if (grouped || a->world < 1 || a->world > 8 || a->rank < 0 || a->rank >= a->world ||
+        a->x_rows > a->rows_cap || a->local_ctr == nullptr)
+      return FB_ERR_SHAPE;
+    if (max_tiles > a->flag_capacity) return FB_ERR_SHAPE;
+    // Every tile's owner CTA waits for its peers' copy of the same tile: all of them
+    // must be resident at once on every rank, so the grid may not exceed one wave.
+    p.rank = a->rank;
+    p.world = a->world;
+    p.rows_cap = a->rows_cap;
+    for (int i = 0; i < a->world; ++i) {
+      if (!a->peer_recv[i] || !a->peer_flags[i]) return FB_ERR_SHAPE;
+      p.peer_recv[i] = static_cast<float*>(a->peer_recv[i]);
+      p.peer_flags[i] = static_cast<uint32_t*>(a->peer_flags[i]);
+    }
+    p.local_ctr = static_cast<uint32_t*>(a->local_ctr);
+    p.residual = static_cast<const __nv_bfloat16*>(a->residual);
+    p.ldr = a->ldr;
+    p.peer_wait_ns = a->peer_wait_ns ? a->peer_wait_ns : 3000000000ull;
+    return launch_ntok<false, kEpiAllReduce>(ntok, mw, mx, p, max_tiles, stream);
+  }
+  if (dual) return launch_ntok<true, kEpiSwiGLU>(ntok, mw, mx, p, max_tiles, stream);
+  if (a->epilogue == kEpiScatter)
+    return launch_ntok<false, kEpiScatter>(ntok, mw, mx, p, max_tiles, stream);
+  return launch_ntok<false, kEpiStore>(ntok, mw, mx, p, max_tiles, stream);
+}

@@ -1,0 +1,43 @@
+"""Declarations for the optional entry-point groups of the native library (collectives,
+quantised GEMMs, DeepSeek-V4 operators, host runtime).  Each group is declared only if
+its symbols are present, so a partial build still loads."""
+from __future__ import annotations
+
+import ctypes as C
+
+
+def _has(lib, name: str) -> bool:
+    try:
+        getattr(lib, name)
+        return True
+    except AttributeError:
+        return False
+
+
+def declare(lib) -> None:
+    vp, i, ll, f, ull = C.c_void_p, C.c_int, C.c_longlong, C.c_float, C.c_ulonglong
+    table = {
+        # comm.cu
+        "fb_ipc_handle_bytes": ([], i),
+        "fb_ipc_alloc": ([C.POINTER(vp), ll, vp], i),
+        "fb_ipc_open": ([vp, C.POINTER(vp)], i),
+        "fb_ipc_close": ([vp], i),
+        "fb_ipc_free": ([vp], i),
+        "fb_enable_peer_access": ([i], i),
+        "fb_allreduce_oneshot": ([vp, ll, vp, ll, vp, ll, i, i, i, i, i, C.POINTER(vp),
+                                  C.POINTER(vp), vp, i, ull, vp, vp], i),
+        "fb_moe_reduce_allreduce": ([vp, i, i, vp, i, i, vp, ll, vp, ll, vp, ll, i, i, i, i, i,
+                                     C.POINTER(vp), C.POINTER(vp), vp, i, ull, vp, vp], i),
+        "fb_flag_wait_probe": ([vp, i, ull, vp, vp], i),
+        "fb_peer_barrier": ([C.POINTER(vp), vp, i, i, ull, vp, vp], i),
+        # quant.cu
+        "fb_quant_fp8_rows": ([vp, ll, vp, ll, vp, ll, i, i, i, vp], i),
+        "fb_dequant_fp8_block": ([vp, vp, vp, i, i, i, vp], i),
+        "fb_dequant_mxfp4": ([vp, vp, vp, i, i, vp], i),
+        "fb_quant_mxfp4_rows": ([vp, ll, vp, vp, i, i, vp], i),
+    }
+    for name, (args, res) in table.items():
+        if _has(lib, name):
+            fn = getattr(lib, name)
+            fn.argtypes = args
+            fn.restype = res

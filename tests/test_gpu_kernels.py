@@ -1,0 +1,301 @@
+"""Numerics of every CUDA kernel against the plain PyTorch fp32 reference of the same op."""
+import math
+
+import pytest
+import torch
+
+from ferrule_b200.ops import reference as ref
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def K():
+    from ferrule_b200.ops import kernels
+    return kernels
+
+
+@pytest.fixture(autouse=True)
+def _status_clean():
+    yield
+    if torch.cuda.is_available():
+        from ferrule_b200.ops import _lib
+        torch.cuda.synchronize()
+        code = _lib.read_status()
+        assert code[0] == 0, f"device status word set: {code}"
+
+
+def rnd(*shape, scale=1.0, seed=0):
+    g = torch.Generator(device="cuda").manual_seed(seed + sum(shape))
+    return (torch.randn(*shape, generator=g, device="cuda") * scale).to(torch.bfloat16)
+
+
+def close(a, b, rtol=2e-2, atol=2e-2):
+    a, b = a.float(), b.float()
+    err = (a - b).abs()
+    tol = atol + rtol * b.abs()
+    bad = err > tol
+    assert not bad.any(), f"{int(bad.sum())}/{bad.numel()} mismatches, max err {float(err.max()):.4g}, ref max {float(b.abs().max()):.4g}"
+
+
+@pytest.mark.parametrize("rows,n,k", [(1, 128, 64), (7, 128, 512), (32, 576, 2048), (32, 2048, 1408),
+                                      (100, 3648, 2048), (300, 2048, 2048), (16, 64, 2048),
+                                      (700, 1000, 1024)])
+def test_gemm_dense(K, rows, n, k):
+    x, w = rnd(rows, k), rnd(n, k, scale=0.05)
+    out = K.gemm(x, w)
+    close(out, x.float() @ w.float().T)
+
+
+def test_gemm_fp32_out_and_strided_x(K):
+    big = rnd(40, 4096)
+    x = big[:, 1024:3072]           # row stride 4096, 16-byte aligned start
+    w = rnd(64, 2048, scale=0.05)
+    out = K.gemm(x, w, out_dtype=torch.float32)
+    assert out.dtype == torch.float32
+    close(out, x.float() @ w.float().T, rtol=1e-3, atol=1e-3)
+
+
+@pytest.mark.parametrize("rows,inter,k", [(32, 1408, 2048), (5, 256, 512), (200, 352, 2048)])
+def test_gemm_swiglu_dense(K, rows, inter, k):
+    x, w13 = rnd(rows, k), rnd(2 * inter, k, scale=0.05)
+    out = K.gemm(x, w13, epilogue=K.EPI_SWIGLU)
+    y = x.float() @ w13.float().T
+    close(out, ref.swiglu(y[:, :inter], y[:, inter:]))
+
+
+def test_gemm_swiglu_clamp(K):
+    x, w13 = rnd(8, 512, scale=2.0), rnd(256, 512, scale=0.3)
+    out = K.gemm(x, w13, epilogue=K.EPI_SWIGLU, act_limit=7.0)
+    y = x.float() @ w13.float().T
+    close(out, ref.swiglu(y[:, :128], y[:, 128:], limit=7.0))
+
+
+def test_gemm_batched_heads(K):
+    heads, nope, lat, rows = 16, 128, 512, 33
+    q = rnd(rows, heads * 192)
+    w = rnd(heads, lat, nope, scale=0.05)
+    out = torch.zeros(rows, heads * 576, dtype=torch.bfloat16, device="cuda")
+    K.gemm(q, w, out=out, x_group_koff=192, out_group_coff=576)
+    qv = q.view(rows, heads, 192)[:, :, :nope].float()
+    expect = torch.einsum("rhk,hnk->rhn", qv, w.float())
+    close(out.view(rows, heads, 576)[:, :, :lat], expect)
+    assert float(out.view(rows, heads, 576)[:, :, lat:].abs().max()) == 0.0
+
+
+def _route_setup(K, T, E, topk, e_lo, e_hi, ntok, seed=1):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    logits = torch.randn(T, E, generator=g, device="cuda")
+    idx, w = ref.route(logits, topk, ref.SCORE_SOFTMAX)
+    plan = K.MoePlan.allocate(T * topk, e_hi - e_lo, ntok, "cuda")
+    K.moe_plan(idx, w, plan, e_lo, e_hi)
+    return idx, w, plan
+
+
+@pytest.mark.parametrize("T,E,topk,e_lo,e_hi,ntok", [(32, 64, 6, 0, 64, 32), (32, 64, 6, 8, 16, 16),
+                                                      (257, 16, 2, 0, 16, 64), (4, 8, 2, 0, 8, 16)])
+def test_moe_plan(K, T, E, topk, e_lo, e_hi, ntok):
+    idx, w, plan = _route_setup(K, T, E, topk, e_lo, e_hi, ntok)
+    torch.cuda.synchronize()
+    flat = idx.flatten().cpu()
+    local = (flat >= e_lo) & (flat < e_hi)
+    n_rows = int(local.sum())
+    tiles, rows = plan.meta.cpu().tolist()
+    assert rows == n_rows
+    counts = torch.bincount(flat[local] - e_lo, minlength=e_hi - e_lo)
+    assert plan.counts.cpu().tolist() == counts.tolist()
+    assert tiles == int(((counts + ntok - 1) // ntok).sum())
+    dst = plan.dst_row.cpu()[:n_rows]
+    # expert-major, ascending route id inside an expert
+    experts_sorted = flat[dst.long()]
+    assert (experts_sorted[1:] >= experts_sorted[:-1]).all()
+    for e in range(e_lo, e_hi):
+        seg = dst[experts_sorted == e]
+        assert (seg[1:] > seg[:-1]).all()
+    assert sorted(dst.tolist()) == torch.nonzero(local).flatten().tolist()
+    assert torch.equal(plan.src_token.cpu()[:n_rows], dst // topk)
+    assert torch.allclose(plan.row_scale.cpu()[:n_rows], w.flatten().cpu()[dst.long()])
+    # tile table
+    tg, t0, tr = (t.cpu()[:tiles] for t in (plan.tile_group, plan.tile_row0, plan.tile_rows))
+    assert int(tr.sum()) == n_rows and int(tr.max() if tiles else 0) <= ntok
+    off = torch.cumsum(counts, 0) - counts
+    for g_, r0, r in zip(tg.tolist(), t0.tolist(), tr.tolist()):
+        assert off[g_] <= r0 and r0 + r <= off[g_] + counts[g_]
+
+
+@pytest.mark.parametrize("T,E,topk,e_lo,e_hi,ntok,H,I", [(32, 64, 6, 0, 64, 32, 2048, 1408),
+                                                          (32, 64, 6, 16, 24, 16, 512, 256),
+                                                          (300, 8, 2, 0, 8, 128, 512, 384)])
+def test_moe_grouped_pipeline(K, T, E, topk, e_lo, e_hi, ntok, H, I):
+    """gather -> grouped gate/up SwiGLU -> grouped down with weighted scatter -> reduce."""
+    idx, w, plan = _route_setup(K, T, E, topk, e_lo, e_hi, ntok)
+    L = e_hi - e_lo
+    x = rnd(T, H)
+    w13 = rnd(L, 2 * I, H, scale=0.03)
+    w2 = rnd(L, H, I, scale=0.03)
+    xg = torch.zeros(T * topk, H, dtype=torch.bfloat16, device="cuda")
+    K.gather_rows(x, plan, xg)
+    hmid = torch.zeros(T * topk, I, dtype=torch.bfloat16, device="cuda")
+    K.gemm(xg, w13, out=hmid, epilogue=K.EPI_SWIGLU, plan=plan)
+    slots = topk + 1
+    route_out = torch.zeros(T * slots, H, dtype=torch.bfloat16, device="cuda")
+    # route r = t*topk + s lands in row t*slots + s: give the GEMM a [T, slots*H] view trick via ldo
+    ro_view = route_out.view(T, slots, H)
+    dst_fix = (plan.dst_row // topk) * slots + plan.dst_row % topk
+    plan2 = K.MoePlan(plan.ntok, plan.max_tiles, plan.cap_rows, plan.src_token, dst_fix.to(torch.int32),
+                      plan.row_scale, plan.tile_group, plan.tile_row0, plan.tile_rows, plan.counts, plan.meta)
+    K.gemm(hmid, w2, out=route_out, epilogue=K.EPI_SCATTER, plan=plan2)
+    extra = rnd(T, H)
+    resid = rnd(T, H)
+    ro_view[:, topk] = extra
+    out = K.moe_reduce(route_out, slots, topk, idx, e_lo, e_hi, T, H, residual=resid)
+    # reference
+    expect = resid.float() + extra.float()
+    xf = x.float()
+    for t in range(T):
+        for s in range(topk):
+            e = int(idx[t, s])
+            if e_lo <= e < e_hi:
+                y = w13[e - e_lo].float() @ xf[t]
+                h = ref.bf16_round(ref.swiglu(y[:I], y[I:]))
+                expect[t] += ref.bf16_round((w2[e - e_lo].float() @ h) * w[t, s])
+    close(out, expect, rtol=3e-2, atol=3e-2)
+
+
+@pytest.mark.parametrize("score_fn,bias,groups,tg,norm", [(0, False, 1, 1, False), (1, True, 8, 4, True),
+                                                         (2, True, 1, 1, True), (1, False, 1, 1, True)])
+def test_router_topk(K, score_fn, bias, groups, tg, norm):
+    T, E, k = 37, 256 if groups > 1 else 64, 8 if groups > 1 else 6
+    g = torch.Generator(device="cuda").manual_seed(3)
+    logits = torch.randn(T, E, generator=g, device="cuda")
+    b = torch.randn(E, generator=g, device="cuda") * 0.1 if bias else None
+    idx, w = K.router_topk(logits, k, score_fn, bias=b, n_groups=groups, topk_groups=tg, normalize=norm,
+                           route_scale=2.5)
+    ridx, rw = ref.route(logits, k, score_fn, bias=b, n_groups=groups, topk_groups=tg, normalize=norm,
+                         route_scale=2.5)
+    assert torch.equal(idx.cpu(), ridx.cpu())
+    assert torch.allclose(w, rw, rtol=1e-4, atol=1e-6)
+
+
+def test_router_hash_and_ties(K):
+    T, E, k, V = 9, 64, 6, 50
+    logits = torch.zeros(T, E, device="cuda")            # all tied -> lowest ids win
+    idx, w = K.router_topk(logits, k, 0)
+    assert idx.cpu().tolist() == [list(range(k))] * T
+    g = torch.Generator(device="cuda").manual_seed(4)
+    logits = torch.randn(T, E, generator=g, device="cuda")
+    table = torch.randint(0, E, (V, k), generator=g, device="cuda", dtype=torch.int64)
+    toks = torch.randint(0, V, (T,), generator=g, device="cuda", dtype=torch.int32)
+    idx, w = K.router_topk(logits, k, 2, hash_table=table, token_ids=toks, normalize=True, route_scale=1.5)
+    ridx, rw = ref.route(logits, k, 2, hash_table=table, token_ids=toks, normalize=True, route_scale=1.5)
+    assert torch.equal(idx.cpu(), ridx.cpu())
+    assert torch.allclose(w, rw, rtol=1e-4, atol=1e-6)
+
+
+def test_add_rmsnorm_and_embedding(K):
+    rows, dim = 33, 2048
+    x, d, w = rnd(rows, dim), rnd(rows, dim), rnd(dim)
+    res, nrm = K.add_rmsnorm(x, w, 1e-6, delta=d)
+    r = ref.bf16_round(x.float() + d.float())
+    close(res, r, rtol=0, atol=0)
+    close(nrm, ref.rmsnorm(r, w, 1e-6), rtol=1e-2, atol=1e-2)
+    _, nrm2 = K.add_rmsnorm(x, w, 1e-6)
+    close(nrm2, ref.rmsnorm(x, w, 1e-6), rtol=1e-2, atol=1e-2)
+    table = rnd(1000, 512)
+    ids = torch.randint(0, 1000, (17,), device="cuda", dtype=torch.int32)
+    assert torch.equal(K.embedding(ids, table), table[ids.long()])
+
+
+def test_argmax_topk(K):
+    g = torch.Generator(device="cuda").manual_seed(5)
+    logits = torch.randn(6, 102400, generator=g, device="cuda")
+    logits[0, 7] = logits[0, 90000] = 50.0          # tie -> lower id
+    logits[1] = float("nan")
+    logits[2, 5] = float("nan")
+    ids = K.argmax(logits)
+    assert torch.equal(ids.cpu(), ref.greedy_argmax(logits).cpu())
+    assert int(ids[0]) == 7 and int(ids[1]) == -1
+    ti, tv = K.topk_logits(logits[3:], 40)
+    ri, rv = ref.topk_logits(logits[3:], 40)
+    assert torch.equal(ti.cpu(), ri.cpu()) and torch.allclose(tv, rv)
+
+
+def _attn_case(K, heads, dl, dr, page, ctx_lens, q_per_seq, splits, split_tokens, sink=False, seed=0):
+    D = dl + dr
+    S = len(ctx_lens)
+    max_blocks = (max(ctx_lens) + page - 1) // page + 1
+    n_pages = S * max_blocks + 3
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    pool = (torch.randn(n_pages * page, D, generator=g, device="cuda") * 0.5).to(torch.bfloat16)
+    perm = torch.randperm(n_pages, generator=g, device="cuda")[: S * max_blocks].to(torch.int32)
+    bt = perm.view(S, max_blocks).contiguous()
+    row_seq, row_pos = [], []
+    for s, n in enumerate(ctx_lens):
+        for j in range(q_per_seq):
+            row_seq.append(s)
+            row_pos.append(n - q_per_seq + j)
+    rows = len(row_seq)
+    row_seq = torch.tensor(row_seq, dtype=torch.int32, device="cuda")
+    row_pos = torch.tensor(row_pos, dtype=torch.int32, device="cuda")
+    q = (torch.randn(rows, heads, D, generator=g, device="cuda") * 0.5).to(torch.bfloat16)
+    sk = torch.randn(heads, generator=g, device="cuda") if sink else None
+    out = torch.zeros(rows, heads, dl, dtype=torch.bfloat16, device="cuda")
+    ws = None
+    if splits > 1:
+        ws = K.AttnWorkspace(torch.zeros(rows, splits, heads, dl, device="cuda"),
+                             torch.zeros(rows, splits, heads, 2, device="cuda"), rows, splits)
+    scale = 1.0 / math.sqrt(dl // 4 + dr)
+    K.mla_attention(q, pool, bt, row_seq, row_pos, page, dl, dr, scale, out, splits=splits,
+                    split_tokens=split_tokens, ws=ws, sink=sk)
+    expect = ref.mla_paged_attention(q, pool, bt, row_seq, row_pos, page, dl, scale, sink=sk)
+    close(out, expect, rtol=2e-2, atol=1e-2)
+
+
+@pytest.mark.parametrize("heads,dl,dr,page,ctx,qps,splits,st,sink", [
+    (16, 512, 64, 64, [1, 64, 65, 700], 1, 1, 1 << 20, False),
+    (16, 512, 64, 64, [513, 768, 40], 1, 4, 256, False),
+    (16, 512, 64, 16, [100, 300], 3, 2, 192, True),
+    (4, 64, 16, 16, [17, 64, 33], 2, 1, 1 << 20, False),
+    (2, 512, 64, 64, [130], 1, 3, 64, True),
+    (32, 512, 64, 64, [200, 90], 1, 1, 1 << 20, False),
+    (128, 512, 64, 64, [150], 1, 2, 128, False),
+])
+def test_mla_attention(K, heads, dl, dr, page, ctx, qps, splits, st, sink):
+    _attn_case(K, heads, dl, dr, page, ctx, qps, splits, st, sink)
+
+
+def test_mla_prep(K):
+    rows, heads, qhd, lora, rope = 11, 16, 192, 512, 64
+    D = lora + rope
+    q = rnd(rows, heads * qhd)
+    ckv = rnd(rows, D)
+    wn = rnd(lora)
+    cos, sin = (t.cuda() for t in ref.rope_tables(4096, rope, 10000.0))
+    pos = torch.randint(0, 4096, (rows,), device="cuda", dtype=torch.int32)
+    pool = torch.zeros(64 * 4, D, dtype=torch.bfloat16, device="cuda")
+    slots = torch.randperm(64 * 4, device="cuda")[:rows].to(torch.int64)
+    slots[3] = -1                                      # "do not write" marker
+    q_out = torch.zeros(rows, heads, D, dtype=torch.bfloat16, device="cuda")
+    K.mla_prep(q, qhd, ckv, heads, lora, rope, wn, 1e-6, cos, sin, pos, slots, pool, q_out.view(rows, -1))
+    c, s = cos[pos.long()], sin[pos.long()]
+    qr = ref.apply_rope(q.view(rows, heads, qhd)[:, :, qhd - rope:], c[:, None, :], s[:, None, :])
+    close(q_out[:, :, lora:], qr, rtol=1e-2, atol=1e-2)
+    kvn = ref.rmsnorm(ckv[:, :lora], wn, 1e-6)
+    kr = ref.apply_rope(ckv[:, lora:], c, s)
+    for r in range(rows):
+        if int(slots[r]) < 0:
+            continue
+        close(pool[int(slots[r]), :lora], kvn[r], rtol=1e-2, atol=1e-2)
+        close(pool[int(slots[r]), lora:], kr[r], rtol=1e-2, atol=1e-2)
+    written = torch.zeros(pool.shape[0], dtype=torch.bool, device="cuda")
+    written[slots[slots >= 0]] = True
+    assert float(pool[~written].abs().max()) == 0.0
+
+
+def test_copy_pages(K):
+    pool = rnd(3, 10, 16, 80)
+    before = pool.clone()
+    pairs = torch.tensor([[1, 7], [2, 9]], dtype=torch.int32, device="cuda")
+    K.copy_pages(pool, pairs)
+    assert torch.equal(pool[:, 7], before[:, 1]) and torch.equal(pool[:, 9], before[:, 2])
+    assert torch.equal(pool[:, :7], before[:, :7])
