@@ -327,13 +327,14 @@ router_topk_kernel(const float* __restrict__ logits, long long ldl, const float*
 // MoE plan: single CTA (routes are at most tokens * topk; the kernel is latency-bound)
 //   topk_idx[route] in [0, experts) ; local experts are [e_lo, e_hi)
 //   outputs (expert-major position p):
-//     src_token[p], dst_row[p] = route id, row_scale[p] = weight
+//     src_token[p], dst_row[p] = token * dst_slots + slot (route id when dst_slots == topk),
+//     row_scale[p] = weight
 //     tile table for row tiles of `ntok` rows: tile_group (local expert id), row0, rows
 //     counts[local experts], meta = {num_tiles, num_rows}
 // ---------------------------------------------------------------------------------
 __global__ void __launch_bounds__(1024)
 moe_plan_kernel(const int* __restrict__ topk_idx, const float* __restrict__ topk_w, int routes,
-                int topk, int e_lo, int e_hi, int ntok, int* __restrict__ src_token,
+                int topk, int e_lo, int e_hi, int ntok, int dst_slots, int* __restrict__ src_token,
                 int* __restrict__ dst_row, float* __restrict__ row_scale,
                 int* __restrict__ tile_group, int* __restrict__ tile_row0,
                 int* __restrict__ tile_rows, int max_tiles, int* __restrict__ counts,
@@ -385,7 +386,7 @@ moe_plan_kernel(const int* __restrict__ topk_idx, const float* __restrict__ topk
       if (hit) {
         const int p = base + __popc(mask & ((1u << lane) - 1u));
         src_token[p] = r / topk;
-        dst_row[p] = r;
+        dst_row[p] = (r / topk) * dst_slots + (r - (r / topk) * topk);
         row_scale[p] = topk_w ? topk_w[r] : 1.f;
       }
       base += __popc(mask);
@@ -640,12 +641,12 @@ extern "C" int fb_router_topk(const float* logits, long long ldl, const float* b
 }
 
 extern "C" int fb_moe_plan(const int* topk_idx, const float* topk_w, int routes, int topk, int e_lo,
-                           int e_hi, int ntok, int* src_token, int* dst_row, float* row_scale,
+                           int e_hi, int ntok, int dst_slots, int* src_token, int* dst_row, float* row_scale,
                            int* tile_group, int* tile_row0, int* tile_rows, int max_tiles,
                            int* counts, int* meta, void* status, void* stream) {
   if (routes <= 0 || topk <= 0 || e_hi <= e_lo || e_hi - e_lo > 256 || ntok <= 0) return FB_ERR_SHAPE;
   moe_plan_kernel<<<1, 1024, 0, static_cast<cudaStream_t>(stream)>>>(
-      topk_idx, topk_w, routes, topk, e_lo, e_hi, ntok, src_token, dst_row, row_scale, tile_group,
+      topk_idx, topk_w, routes, topk, e_lo, e_hi, ntok, dst_slots < topk ? topk : dst_slots, src_token, dst_row, row_scale, tile_group,
       tile_row0, tile_rows, max_tiles, counts, meta, static_cast<DeviceStatus*>(status));
   return FB_CHECK_LAUNCH();
 }

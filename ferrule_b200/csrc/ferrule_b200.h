@@ -117,7 +117,7 @@ int fb_router_topk(const float* logits, long long ldl, const float* bias,
                    int topk, int score_fn, int n_groups, int topk_groups, int normalize,
                    float route_scale, int* out_idx, float* out_w, void* stream);
 int fb_moe_plan(const int* topk_idx, const float* topk_w, int routes, int topk, int e_lo, int e_hi,
-                int ntok, int* src_token, int* dst_row, float* row_scale, int* tile_group,
+                int ntok, int dst_slots, int* src_token, int* dst_row, float* row_scale, int* tile_group,
                 int* tile_row0, int* tile_rows, int max_tiles, int* counts, int* meta, void* status,
                 void* stream);
 int fb_gather_rows(const void* x, long long ldx, const int* src_token, const int* meta, void* out,

@@ -1,0 +1,505 @@
+"""DeepSeek-family forward pass over a packed ragged batch with a paged latent-KV pool.
+
+Two implementations of the same math:
+
+* `forward_reference` - plain PyTorch (fp32 math on bf16-rounded activations at the same
+  boundaries as the kernels).  Runs anywhere; it is the CPU execution path and the oracle.
+* `forward_cuda`      - the sm_100a kernel pipeline (tcgen05 GEMMs, MLA attention, fused
+  small ops), allocation-free over a preallocated workspace so a decode step can be
+  captured in a CUDA graph.
+
+Layer structure (weight-absorbed MLA, pre-norm residual):
+  h -> RMSNorm -> [q | c_kv,k_rope] -> (q_norm, q_b) -> RoPE, KV append -> q_nope @ W_UK
+    -> paged attention over latent rows -> @ W_UV -> o_proj (+ all-reduce) -> + h
+    -> RMSNorm -> dense SwiGLU FFN | router -> top-k -> grouped experts (+ shared) -> + h
+
+Layer-level counterpart of crates/ferrule-model/src/models/deepseek_v4/layer.rs:391-470 and
+attention.rs:1194-1364 in the reference (whose V4-only extras live in `v4.py`).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import List, Optional
+
+import torch
+
+from ..ops import reference as ref
+from .config import ModelConfig
+from .weights import LayerWeights, ModelWeights
+
+
+@dataclass
+class DeviceBatch:
+    """Device-side view of one packed execution batch (all tensors on the model's device).
+
+    rows may exceed n_rows (padding up to a graph bucket): padded rows carry write_slot = -1
+    and row_pos = -1 and never touch the KV pool.
+    """
+    token_ids: torch.Tensor     # [rows] int32
+    positions: torch.Tensor     # [rows] int32 absolute position of each token
+    write_slot: torch.Tensor    # [rows] int64 pool row the token's KV is written to (-1: none)
+    row_seq: torch.Tensor       # [rows] int32 index into block_table
+    row_pos: torch.Tensor       # [rows] int32 last KV position visible to the row (= position)
+    block_table: torch.Tensor   # [seqs, max_blocks] int32 page ids
+    logit_rows: torch.Tensor    # [n_logit] int32 rows whose logits are wanted
+    n_rows: int
+    n_logit: int
+
+
+class KvPool:
+    """Physical paged latent-KV pool: [layers, pages, page_size, kv_lora + rope] bf16 (fp32 on CPU)."""
+
+    def __init__(self, cfg: ModelConfig, n_pages: int, page_size: int, device, dtype=torch.bfloat16,
+                 n_layers: Optional[int] = None):
+        self.cfg, self.n_pages, self.page_size = cfg, n_pages, page_size
+        self.n_layers = cfg.n_layers + cfg.n_mtp_layers if n_layers is None else n_layers
+        self.data = torch.zeros(self.n_layers, n_pages, page_size, cfg.kv_row_dim, dtype=dtype, device=device)
+
+    def layer(self, i: int) -> torch.Tensor:
+        return self.data[i]
+
+    @property
+    def bytes_per_page(self) -> int:
+        return self.n_layers * self.page_size * self.cfg.kv_row_dim * self.data.element_size()
+
+    def copy_pages(self, pairs) -> None:
+        """Copy whole pages (all layers): pairs = [(src, dst), ...] (copy-on-write)."""
+        if not pairs:
+            return
+        if self.data.is_cuda:
+            from ..ops import kernels as K
+            K.copy_pages(self.data, torch.tensor(pairs, dtype=torch.int32, device=self.data.device))
+        else:
+            for s, d in pairs:
+                self.data[:, d] = self.data[:, s]
+
+    def snapshot_pages(self, pages) -> torch.Tensor:
+        """Device -> host copy of pages (session preemption)."""
+        idx = torch.tensor(list(pages), dtype=torch.long, device=self.data.device)
+        return self.data[:, idx].to("cpu", copy=True)
+
+    def restore_pages(self, pages, snap: torch.Tensor) -> None:
+        idx = torch.tensor(list(pages), dtype=torch.long, device=self.data.device)
+        self.data[:, idx] = snap.to(self.data.device)
+
+
+# ======================================================================================
+# reference forward (PyTorch)
+# ======================================================================================
+class ReferenceForward:
+    """fp32 PyTorch implementation; `emulate_bf16` rounds activations where the kernels do."""
+
+    def __init__(self, weights: ModelWeights, pool: KvPool, emulate_bf16: bool = False):
+        self.w, self.cfg, self.pool = weights, weights.cfg, pool
+        self.rnd = ref.bf16_round if emulate_bf16 else (lambda t: t)
+        cfg = self.cfg
+        dev = weights.embed.device
+        cos, sin = ref.rope_tables(min(cfg.max_position, 1 << 16), cfg.qk_rope_dim, cfg.rope_theta,
+                                   cfg.rope_factor, cfg.rope_orig_max_pos, cfg.rope_beta_fast,
+                                   cfg.rope_beta_slow)
+        self.cos, self.sin = cos.to(dev), sin.to(dev)
+
+    # -- pieces ------------------------------------------------------------------------
+    def _attention(self, lw: LayerWeights, layer: int, xn: torch.Tensor, b: DeviceBatch) -> torch.Tensor:
+        cfg, rnd = self.cfg, self.rnd
+        T = xn.shape[0]
+        hl = self.w.heads_local
+        qhd, lora, rope, nope = cfg.q_head_dim, cfg.kv_lora_rank, cfg.qk_rope_dim, cfg.qk_nope_dim
+        qkv = rnd(xn @ lw.w_qkv_a.float().T)
+        if cfg.q_lora_rank:
+            qa, ckv = qkv[:, :cfg.q_lora_rank], qkv[:, cfg.q_lora_rank:]
+            qn = rnd(ref.rmsnorm(qa, lw.q_norm, cfg.rms_eps))
+            q = rnd(qn @ lw.w_q_b.float().T)
+        else:
+            q, ckv = qkv[:, :hl * qhd], qkv[:, hl * qhd:]
+        q = q.view(T, hl, qhd)
+        pos = b.positions[:T].long()
+        c, s = self.cos[pos], self.sin[pos]
+        q_rope = rnd(ref.apply_rope(q[:, :, nope:], c[:, None], s[:, None]))
+        kv_lat = rnd(ref.rmsnorm(ckv[:, :lora], lw.kv_norm, cfg.rms_eps))
+        k_rope = rnd(ref.apply_rope(ckv[:, lora:], c, s))
+        kv_row = torch.cat([kv_lat, k_rope], dim=-1)
+        pool_l = self.pool.layer(layer).view(-1, cfg.kv_row_dim)
+        slots = b.write_slot[:T]
+        ok = slots >= 0
+        pool_l[slots[ok]] = kv_row[ok].to(pool_l.dtype)
+        q_lat = rnd(torch.einsum("thk,hnk->thn", q[:, :, :nope], lw.w_uk_t.float()))
+        q_full = torch.cat([q_lat, q_rope], dim=-1)
+        o_lat = rnd(ref.mla_paged_attention(q_full, pool_l, b.block_table, b.row_seq[:T], b.row_pos[:T],
+                                            self.pool.page_size, lora, cfg.softmax_scale, sink=lw.attn_sink))
+        o = rnd(torch.einsum("thk,hnk->thn", o_lat, lw.w_uv.float())).reshape(T, -1)
+        return o @ lw.w_o.float().T          # partial sum over this rank's heads
+
+    def _ffn(self, w13: torch.Tensor, w2: torch.Tensor, x: torch.Tensor) -> torch.Tensor:
+        inter = w13.shape[-2] // 2
+        y = x @ w13[0].float().T
+        h = self.rnd(ref.swiglu(y[:, :inter], y[:, inter:], self.cfg.swiglu_limit))
+        return h @ w2[0].float().T
+
+    def _moe(self, lw: LayerWeights, xn: torch.Tensor, token_ids: torch.Tensor) -> torch.Tensor:
+        cfg, rnd = self.cfg, self.rnd
+        logits = xn @ lw.router_w.float().T
+        idx, wts = ref.route(logits, cfg.topk, cfg.score_fn, bias=lw.router_bias, n_groups=cfg.n_groups,
+                             topk_groups=cfg.topk_groups, normalize=cfg.norm_topk_prob,
+                             route_scale=cfg.route_scale, hash_table=lw.hash_table, token_ids=token_ids)
+        I = cfg.moe_inter
+        out = torch.zeros_like(xn)
+        for e in range(self.w.e_lo, self.w.e_hi):
+            hit = (idx == e)
+            rows = hit.any(-1).nonzero().flatten()
+            if rows.numel() == 0:
+                continue
+            wsel = (wts * hit)[rows].sum(-1, keepdim=True)
+            y = xn[rows] @ lw.e_w13[e - self.w.e_lo].float().T
+            h = rnd(ref.swiglu(y[:, :I], y[:, I:], cfg.swiglu_limit))
+            out[rows] += rnd((h @ lw.e_w2[e - self.w.e_lo].float().T) * wsel)
+        if lw.w13 is not None:
+            out = out + rnd(self._ffn(lw.w13, lw.w2, xn))
+        return out
+
+    def layer(self, lw: LayerWeights, layer: int, h: torch.Tensor, b: DeviceBatch, allreduce=None) -> torch.Tensor:
+        cfg, rnd = self.cfg, self.rnd
+        T = h.shape[0]
+        xn = rnd(ref.rmsnorm(h, lw.attn_norm, cfg.rms_eps))
+        a = self._attention(lw, layer, xn, b)
+        if allreduce is not None:
+            a = allreduce(a)
+        else:
+            a = rnd(a)
+        h = rnd(h + a)
+        xn = rnd(ref.rmsnorm(h, lw.ffn_norm, cfg.rms_eps))
+        f = self._moe(lw, xn, b.token_ids[:T]) if lw.is_moe else self._ffn(lw.w13, lw.w2, xn)
+        if allreduce is not None:
+            f = allreduce(f)
+        elif not lw.is_moe:
+            f = rnd(f)
+        return rnd(h + f)
+
+    def hidden_states(self, b: DeviceBatch, allreduce=None) -> torch.Tensor:
+        T = b.n_rows
+        h = self.w.embed[b.token_ids[:T].long()].float()
+        for i, lw in enumerate(self.w.layers):
+            h = self.layer(lw, i, h, b, allreduce)
+        return h
+
+    def logits_from_hidden(self, h: torch.Tensor, b: DeviceBatch, final_norm=None) -> torch.Tensor:
+        rows = b.logit_rows[:b.n_logit].long()
+        hn = self.rnd(ref.rmsnorm(h[rows], self.w.final_norm if final_norm is None else final_norm,
+                                  self.cfg.rms_eps))
+        return hn @ self.w.lm_head.float().T
+
+    def forward(self, b: DeviceBatch, allreduce=None, gather_vocab=None, return_hidden: bool = False):
+        """-> fp32 logits [n_logit, vocab_local] (or gathered vocab with `gather_vocab`)."""
+        h = self.hidden_states(b, allreduce)
+        logits = self.logits_from_hidden(h, b)
+        if gather_vocab is not None:
+            logits = gather_vocab(logits)
+        return (logits, h) if return_hidden else logits
+
+    def mtp_forward(self, stage: int, h_prev: torch.Tensor, b: DeviceBatch, allreduce=None):
+        """One MTP stage: rows carry the *next* token ids; h_prev are the main-model hidden states
+        of the same rows.  Returns (logits over logit_rows, hidden)."""
+        m = self.w.mtp[stage]
+        cfg, rnd = self.cfg, self.rnd
+        T = b.n_rows
+        e = self.w.embed[b.token_ids[:T].long()].float()
+        x = torch.cat([rnd(ref.rmsnorm(h_prev, m.hnorm, cfg.rms_eps)), rnd(ref.rmsnorm(e, m.enorm, cfg.rms_eps))], -1)
+        h = rnd(x @ m.eh_proj.float().T)
+        h = self.layer(m.layer, cfg.n_layers + stage, h, b, allreduce)
+        return self.logits_from_hidden(h, b, final_norm=m.final_norm), h
+
+
+# ======================================================================================
+# CUDA forward (sm_100a kernels)
+# ======================================================================================
+def _pow2_at_least(x: float, lo: int, hi: int) -> int:
+    n = lo
+    while n < x and n < hi:
+        n *= 2
+    return n
+
+
+class CudaWorkspace:
+    """Preallocated activations for up to `max_rows` packed rows (no allocation while stepping)."""
+
+    def __init__(self, w: ModelWeights, max_rows: int, max_logit_rows: int, decode_rows: int,
+                 attn_splits: int, device):
+        cfg = w.cfg
+        hl = w.heads_local
+        H, D = cfg.hidden, cfg.kv_row_dim
+        bf = dict(dtype=torch.bfloat16, device=device)
+        f32 = dict(dtype=torch.float32, device=device)
+        i32 = dict(dtype=torch.int32, device=device)
+        R = max_rows
+        self.max_rows, self.max_logit_rows = R, max_logit_rows
+        self.h = [torch.zeros(R, H, **bf), torch.zeros(R, H, **bf)]
+        self.xn = torch.zeros(R, H, **bf)
+        self.qkv = torch.zeros(R, w.layers[0].w_qkv_a.shape[0], **bf)
+        self.q = torch.zeros(R, hl * cfg.q_head_dim, **bf) if cfg.q_lora_rank else None
+        self.qn = torch.zeros(R, cfg.q_lora_rank, **bf) if cfg.q_lora_rank else None
+        self.q_full = torch.zeros(R, hl, D, **bf)
+        self.o_lat = torch.zeros(R, hl, cfg.kv_lora_rank, **bf)
+        self.attn_out = torch.zeros(R, hl * cfg.v_head_dim, **bf)
+        self.delta = torch.zeros(R, H, **bf)
+        inter_max = 0
+        for lw in list(w.layers) + [m.layer for m in w.mtp]:
+            if lw.w13 is not None:
+                inter_max = max(inter_max, lw.w13.shape[1] // 2)
+        self.ffn_mid = torch.zeros(R, max(inter_max, 8), **bf)
+        self.attn_splits = attn_splits
+        self.decode_rows = decode_rows
+        from ..ops.kernels import AttnWorkspace, MoePlan
+        self.attn_ws = AttnWorkspace(torch.zeros(decode_rows, attn_splits, hl, cfg.kv_lora_rank, **f32),
+                                     torch.zeros(decode_rows, attn_splits, hl, 2, **f32), decode_rows,
+                                     attn_splits) if attn_splits > 1 else None
+        self.has_moe = cfg.n_routed_experts > 0
+        if self.has_moe:
+            E, k = cfg.n_routed_experts, cfg.topk
+            el = w.e_hi - w.e_lo
+            self.router_logits = torch.zeros(R, E, **f32)
+            self.topk_idx = torch.zeros(R, k, **i32)
+            self.topk_w = torch.zeros(R, k, **f32)
+            self.slots = k + 1
+            self.plans = {}
+            for ntok in (16, 32, 64, 128):
+                self.plans[ntok] = MoePlan.allocate(R * k, el, ntok, device)
+            self.xg = torch.zeros(R * k, H, **bf)
+            self.hmid = torch.zeros(R * k, cfg.moe_inter, **bf)
+            self.route_out = torch.zeros(R, self.slots, H, **bf)
+        L = max_logit_rows
+        self.h_last = torch.zeros(L, H, **bf)
+        self.hn_last = torch.zeros(L, H, **bf)
+        self.logits = torch.zeros(L, w.lm_head.shape[0], **f32)
+        self.next_id = torch.zeros(L, **i32)
+        self.next_val = torch.zeros(L, **f32)
+        self.mtp_x = torch.zeros(R, 2 * H, **bf) if w.mtp else None
+
+    def nbytes(self) -> int:
+        tot = 0
+        for v in vars(self).values():
+            ts = v if isinstance(v, (list, tuple)) else [v]
+            for t in ts:
+                if isinstance(t, torch.Tensor):
+                    tot += t.numel() * t.element_size()
+        return tot
+
+
+class CudaForward:
+    """The kernel pipeline.  `tp` (parallel.tp.TensorParallel) supplies the fused collectives;
+    None means a single GPU."""
+
+    def __init__(self, weights: ModelWeights, pool: KvPool, max_rows: int = 4096,
+                 max_logit_rows: int = 256, decode_rows: int = 64, max_seq_len: int = 4096,
+                 attn_splits: int = 8, tp=None):
+        from ..ops import kernels as K
+        self.K = K
+        self.w, self.cfg, self.pool, self.tp = weights, weights.cfg, pool, tp
+        dev = weights.embed.device
+        self.device = dev
+        cfg = self.cfg
+        self.max_seq_len = max_seq_len
+        self.split_tokens = max(64, ((max_seq_len + attn_splits - 1) // attn_splits + 63) // 64 * 64)
+        self.ws = CudaWorkspace(weights, max_rows, max_logit_rows, decode_rows, attn_splits, dev)
+        cos, sin = ref.rope_tables(min(cfg.max_position, max(max_seq_len, 16)), cfg.qk_rope_dim, cfg.rope_theta,
+                                   cfg.rope_factor, cfg.rope_orig_max_pos, cfg.rope_beta_fast, cfg.rope_beta_slow)
+        self.cos, self.sin = cos.to(dev).contiguous(), sin.to(dev).contiguous()
+        self.launches = 0          # kernels launched by the last forward (for reporting)
+
+    # -- sublayers -----------------------------------------------------------------------
+    def _attention(self, lw: LayerWeights, layer: int, xn: torch.Tensor, b: DeviceBatch, T: int) -> torch.Tensor:
+        K, cfg, ws = self.K, self.cfg, self.ws
+        hl = self.w.heads_local
+        qhd, lora, rope, nope, vd = cfg.q_head_dim, cfg.kv_lora_rank, cfg.qk_rope_dim, cfg.qk_nope_dim, cfg.v_head_dim
+        qkv = ws.qkv[:T]
+        K.gemm(xn, lw.w_qkv_a, out=qkv)
+        if cfg.q_lora_rank:
+            qa, ckv = qkv[:, :cfg.q_lora_rank], qkv[:, cfg.q_lora_rank:]
+            K.add_rmsnorm(qa, lw.q_norm, cfg.rms_eps, norm_out=ws.qn[:T])
+            q = K.gemm(ws.qn[:T], lw.w_q_b, out=ws.q[:T])
+            self.launches += 2
+        else:
+            q, ckv = qkv[:, :hl * qhd], qkv[:, hl * qhd:]
+        q_full = ws.q_full[:T]
+        K.mla_prep(q, qhd, ckv, hl, lora, rope, lw.kv_norm, cfg.rms_eps, self.cos, self.sin,
+                   b.positions, b.write_slot, self.pool.layer(layer), q_full.view(T, -1))
+        K.gemm(q, lw.w_uk_t, out=q_full.view(T, -1), x_group_koff=qhd, out_group_coff=lora + rope, k=nope)
+        use_split = ws.attn_ws is not None and T <= ws.decode_rows
+        K.mla_attention(q_full, self.pool.layer(layer), b.block_table, b.row_seq, b.row_pos,
+                        self.pool.page_size, lora, rope, cfg.softmax_scale, ws.o_lat[:T],
+                        splits=ws.attn_splits if use_split else 1,
+                        split_tokens=self.split_tokens if use_split else (1 << 30) // 64 * 64,
+                        ws=ws.attn_ws if use_split else None, sink=lw.attn_sink)
+        K.gemm(ws.o_lat[:T].view(T, -1), lw.w_uv, out=ws.attn_out[:T], x_group_koff=lora, out_group_coff=vd)
+        self.launches += 5 + (1 if use_split else 0)
+        return ws.attn_out[:T]
+
+    def _moe_ntok(self, T: int) -> int:
+        cfg = self.cfg
+        est = T * cfg.topk / max(cfg.n_routed_experts, 1)
+        return _pow2_at_least(2 * est, 16, 128)
+
+    def _moe_local(self, lw: LayerWeights, xn: torch.Tensor, b: DeviceBatch, T: int):
+        """Router + local routed experts + shared experts -> ws.route_out filled for this rank."""
+        K, cfg, ws = self.K, self.cfg, self.ws
+        k, H = cfg.topk, cfg.hidden
+        K.gemm(xn, lw.router_w, out=ws.router_logits[:T])
+        idx, wts = ws.topk_idx[:T], ws.topk_w[:T]
+        K.router_topk(ws.router_logits[:T], k, cfg.score_fn, bias=lw.router_bias, n_groups=cfg.n_groups,
+                      topk_groups=cfg.topk_groups, normalize=cfg.norm_topk_prob, route_scale=cfg.route_scale,
+                      hash_table=lw.hash_table, token_ids=b.token_ids, out_idx=idx, out_w=wts)
+        plan = ws.plans[self._moe_ntok(T)]
+        K.moe_plan(idx, wts, plan, self.w.e_lo, self.w.e_hi, dst_slots=ws.slots)
+        K.gather_rows(xn, plan, ws.xg, cap_rows=T * k)
+        K.gemm(ws.xg[:T * k], lw.e_w13, out=ws.hmid[:T * k], epilogue=K.EPI_SWIGLU, plan=plan,
+               act_limit=cfg.swiglu_limit)
+        route_out = ws.route_out[:T]
+        # route r = t*k + s is written to row t*slots + s (the plan kernel emits that row index)
+        K.gemm(ws.hmid[:T * k], lw.e_w2, out=route_out.view(T * ws.slots, H), epilogue=K.EPI_SCATTER,
+               plan=plan, scatter_rows=T * ws.slots)
+        self.launches += 6
+        if lw.w13 is not None:
+            inter = lw.w13.shape[1] // 2
+            mid = ws.ffn_mid[:T, :inter]
+            K.gemm(xn, lw.w13, out=mid, epilogue=K.EPI_SWIGLU, act_limit=cfg.swiglu_limit)
+            K.gemm(mid, lw.w2, out=route_out[:, k])
+            self.launches += 2
+        return idx
+
+    def layer(self, lw: LayerWeights, layer: int, h_in: torch.Tensor, h_out: torch.Tensor, b: DeviceBatch,
+              T: int, first_norm_done: bool = False) -> torch.Tensor:
+        """h_in -> h_out (both bf16 [T, H]); returns h_out."""
+        K, cfg, ws, tp = self.K, self.cfg, self.ws, self.tp
+        xn = ws.xn[:T]
+        K.add_rmsnorm(h_in, lw.attn_norm, cfg.rms_eps, norm_out=xn)
+        a = self._attention(lw, layer, xn, b, T)
+        if tp is None:
+            K.gemm(a, lw.w_o, out=ws.delta[:T])
+            K.add_rmsnorm(h_in, lw.ffn_norm, cfg.rms_eps, delta=ws.delta[:T], res_out=h_out, norm_out=xn)
+            h_mid = h_out
+            self.launches += 3
+        else:
+            tp.gemm_allreduce(a, lw.w_o, residual=h_in, out=h_out, T=T)
+            K.add_rmsnorm(h_out, lw.ffn_norm, cfg.rms_eps, norm_out=xn)
+            h_mid = h_out
+            self.launches += 3
+        if lw.is_moe:
+            idx = self._moe_local(lw, xn, b, T)
+            # slot `topk` holds the shared-expert row (zeros when the model has none)
+            if tp is None:
+                K.moe_reduce(ws.route_out[:T].view(T * ws.slots, cfg.hidden), ws.slots, cfg.topk, idx,
+                             self.w.e_lo, self.w.e_hi, T, cfg.hidden, residual=h_mid, out=h_in)
+            else:
+                tp.moe_reduce_allreduce(ws.route_out[:T].view(T * ws.slots, cfg.hidden), ws.slots, cfg.topk,
+                                        idx, self.w.e_lo, self.w.e_hi, residual=h_mid, out=h_in, T=T)
+            self.launches += 1
+            return h_in            # the layer's result lands back in the input buffer
+        inter = lw.w13.shape[1] // 2
+        mid = ws.ffn_mid[:T, :inter]
+        K.gemm(xn, lw.w13, out=mid, epilogue=K.EPI_SWIGLU, act_limit=cfg.swiglu_limit)
+        if tp is None:
+            K.gemm(mid, lw.w2, out=ws.delta[:T])
+            # residual add is folded into the next consumer through a plain add+norm without a norm output
+            K.add_rmsnorm(h_mid, None, cfg.rms_eps, delta=ws.delta[:T], res_out=h_in, want_norm=False)
+            self.launches += 3
+        else:
+            tp.gemm_allreduce(mid, lw.w2, residual=h_mid, out=h_in, T=T)
+            self.launches += 2
+        return h_in
+
+    # -- whole model ---------------------------------------------------------------------
+    def hidden_states(self, b: DeviceBatch, T: int) -> torch.Tensor:
+        K, ws = self.K, self.ws
+        h, other = ws.h[0][:T], ws.h[1][:T]
+        K.embedding(b.token_ids[:T], self.w.embed, out=h)
+        self.launches += 1
+        for i, lw in enumerate(self.w.layers):
+            h = self.layer(lw, i, h, other, b, T)
+        return h
+
+    def head(self, h: torch.Tensor, b: DeviceBatch, final_norm: torch.Tensor, want_logits: bool = False):
+        """Final norm + LM head + greedy token on the requested rows -> (next_id, next_val[, logits])."""
+        K, cfg, ws, tp = self.K, self.cfg, self.ws, self.tp
+        L = b.n_logit
+        hl = ws.h_last[:L]
+        torch.index_select(h, 0, b.logit_rows[:L], out=hl)
+        K.add_rmsnorm(hl, final_norm, cfg.rms_eps, norm_out=ws.hn_last[:L])
+        logits = ws.logits[:L]
+        K.gemm(ws.hn_last[:L], self.w.lm_head, out=logits)
+        K.argmax(logits, out_id=ws.next_id[:L], out_val=ws.next_val[:L])
+        self.launches += 4
+        if tp is not None:
+            tp.argmax_across_vocab(ws.next_id[:L], ws.next_val[:L], self.w.vocab_lo, L)
+            self.launches += 1
+        return ws.next_id[:L], ws.next_val[:L], (logits if want_logits else None)
+
+    def forward(self, b: DeviceBatch, want_logits: bool = False):
+        """Runs the batch; returns (next_id [n_logit] int32, next_val, logits or None)."""
+        T = b.token_ids.shape[0]
+        assert T <= self.ws.max_rows and b.n_logit <= self.ws.max_logit_rows
+        self.launches = 0
+        h = self.hidden_states(b, T)
+        self.last_hidden = h
+        return self.head(h, b, self.w.final_norm, want_logits)
+
+    def mtp_forward(self, stage: int, h_prev: torch.Tensor, b: DeviceBatch):
+        """MTP stage over rows carrying the next token ids; h_prev: main hidden states of those rows."""
+        K, cfg, ws = self.K, self.cfg, self.ws
+        m = self.w.mtp[stage]
+        T = b.token_ids.shape[0]
+        H = cfg.hidden
+        x = ws.mtp_x[:T]
+        K.add_rmsnorm(h_prev, m.hnorm, cfg.rms_eps, norm_out=x[:, :H])
+        e = ws.h[1][:T]
+        K.embedding(b.token_ids[:T], self.w.embed, out=e)
+        K.add_rmsnorm(e, m.enorm, cfg.rms_eps, norm_out=x[:, H:])
+        # h_prev (usually ws.h[0]) is consumed by now, so the projection may overwrite it
+        h0 = ws.h[0][:T]
+        K.gemm(x, m.eh_proj, out=h0)
+        self.launches = 4
+        h = self.layer(m.layer, cfg.n_layers + stage, h0, ws.h[1][:T], b, T)
+        self.last_hidden = h
+        return self.head(h, b, m.final_norm)
+
+
+class DecodeGraph:
+    """One captured decode step for a fixed row bucket.
+
+    Inputs live in static device buffers (`self.batch`); `replay()` runs the whole step
+    (embedding -> layers -> LM head -> greedy token) as one graph launch.  States mirror
+    the reference's Cold -> Warm -> Captured graph cache
+    (crates/ferrule-backend/src/cuda/graph.rs:70-150).
+    """
+
+    def __init__(self, fwd: CudaForward, rows: int, n_seqs: int, max_blocks: int):
+        dev = fwd.device
+        i32 = dict(dtype=torch.int32, device=dev)
+        self.fwd, self.rows = fwd, rows
+        self.batch = DeviceBatch(torch.zeros(rows, **i32), torch.zeros(rows, **i32),
+                                 torch.full((rows,), -1, dtype=torch.int64, device=dev),
+                                 torch.zeros(rows, **i32), torch.full((rows,), -1, **i32),
+                                 torch.zeros(n_seqs, max_blocks, **i32), torch.arange(rows, **i32), rows, rows)
+        self.graph: Optional[torch.cuda.CUDAGraph] = None
+        self.state = "cold"
+        self.launches = 0
+
+    def warm(self) -> None:
+        self.fwd.forward(self.batch)
+        self.launches = self.fwd.launches
+        self.state = "warm"
+
+    def capture(self) -> None:
+        if self.state == "cold":
+            s = torch.cuda.Stream()
+            s.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(s):
+                self.warm()
+            torch.cuda.current_stream().wait_stream(s)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            self.out = self.fwd.forward(self.batch)
+        self.graph, self.state = g, "captured"
+
+    def replay(self):
+        self.graph.replay()
+        return self.out

@@ -1,0 +1,216 @@
+"""Device-resident weight image of a DeepSeek-family model, laid out for the kernels.
+
+Weights are re-packed once at load time into the shapes the tcgen05 GEMM consumes
+(K-major bf16 `[groups, out, in]`):
+
+  w_qkv_a   [q_or_qlora + kv_lora + rope, hidden]   q (or q_a) and kv_a fused: one GEMM per token
+  w_q_b     [heads_local * q_head_dim, q_lora]      only with a q low-rank projection
+  w_uk_t    [heads_local, kv_lora, nope]            absorbed key up-projection (transposed)
+  w_uv      [heads_local, v_head, kv_lora]          absorbed value up-projection
+  w_o       [hidden, heads_local * v_head]
+  w13/w2    dense or shared FFN: [1, 2*inter_local, hidden] / [1, hidden, inter_local]
+  e_w13/e_w2 routed experts of this rank: [E_local, 2*I, hidden] / [E_local, hidden, I]
+
+Tensor parallelism shards heads, FFN inner dims and the vocabulary; routed experts are
+sharded by expert id (activations are replicated between the collectives, so expert
+parallelism needs no token dispatch).  The static-weight "execution image" role matches
+crates/ferrule-model/src/models/deepseek_v4/cuda_cache.rs:2905-3160; tensor naming for
+checkpoints follows the HuggingFace DeepSeek layout (see `families.py`).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional
+
+import torch
+
+from .config import ModelConfig
+
+
+@dataclass
+class LayerWeights:
+    attn_norm: torch.Tensor
+    w_qkv_a: torch.Tensor
+    q_norm: Optional[torch.Tensor]
+    w_q_b: Optional[torch.Tensor]
+    kv_norm: torch.Tensor
+    w_uk_t: torch.Tensor
+    w_uv: torch.Tensor
+    w_o: torch.Tensor
+    ffn_norm: torch.Tensor
+    # dense FFN or shared experts (None if absent)
+    w13: Optional[torch.Tensor] = None
+    w2: Optional[torch.Tensor] = None
+    # routed MoE
+    router_w: Optional[torch.Tensor] = None
+    router_bias: Optional[torch.Tensor] = None
+    hash_table: Optional[torch.Tensor] = None
+    e_w13: Optional[torch.Tensor] = None
+    e_w2: Optional[torch.Tensor] = None
+    attn_sink: Optional[torch.Tensor] = None
+    is_moe: bool = False
+
+
+@dataclass
+class MtpWeights:
+    """One multi-token-prediction stage: norms + projection over [hidden ; embedding] + a layer body."""
+    enorm: torch.Tensor
+    hnorm: torch.Tensor
+    eh_proj: torch.Tensor         # [hidden, 2*hidden]
+    layer: LayerWeights
+    final_norm: torch.Tensor
+
+
+@dataclass
+class ModelWeights:
+    cfg: ModelConfig
+    embed: torch.Tensor           # [vocab, hidden] (replicated)
+    layers: List[LayerWeights]
+    final_norm: torch.Tensor
+    lm_head: torch.Tensor         # [vocab_local, hidden]
+    mtp: List[MtpWeights] = field(default_factory=list)
+    tp_rank: int = 0
+    tp_world: int = 1
+    e_lo: int = 0
+    e_hi: int = 0
+    vocab_lo: int = 0
+
+    @property
+    def heads_local(self) -> int:
+        return self.cfg.n_heads // self.tp_world
+
+    def nbytes(self) -> int:
+        total = 0
+        seen = set()
+
+        def add(t):
+            nonlocal total
+            if isinstance(t, torch.Tensor) and t.data_ptr() not in seen:
+                seen.add(t.data_ptr())
+                total += t.numel() * t.element_size()
+
+        for t in (self.embed, self.final_norm, self.lm_head):
+            add(t)
+        for lw in list(self.layers) + [m.layer for m in self.mtp]:
+            for v in vars(lw).values():
+                add(v)
+        for m in self.mtp:
+            for t in (m.enorm, m.hnorm, m.eh_proj, m.final_norm):
+                add(t)
+        return total
+
+
+def _shard_range(n: int, rank: int, world: int):
+    assert n % world == 0, f"{n} not divisible by {world}"
+    per = n // world
+    return rank * per, (rank + 1) * per
+
+
+class _Init:
+    """Deterministic N(0, std) initialiser that produces identical full tensors on every rank
+    (generated on CPU from a per-tensor seed) so sharded replicas agree with a single-GPU run."""
+
+    def __init__(self, seed: int, std: float, device, dtype, on_device: bool):
+        self.seed, self.std, self.device, self.dtype, self.on_device = seed, std, device, dtype, on_device
+        self.counter = 0
+
+    def normal(self, *shape) -> torch.Tensor:
+        self.counter += 1
+        if self.on_device and torch.device(self.device).type == "cuda":
+            g = torch.Generator(device=self.device).manual_seed(self.seed * 100003 + self.counter)
+            t = torch.empty(*shape, device=self.device, dtype=torch.float32)
+            t.normal_(0.0, self.std, generator=g)
+            return t.to(self.dtype)
+        g = torch.Generator().manual_seed(self.seed * 100003 + self.counter)
+        return (torch.randn(*shape, generator=g) * self.std).to(self.dtype).to(self.device)
+
+    def ones(self, *shape) -> torch.Tensor:
+        return torch.ones(*shape, dtype=self.dtype, device=self.device)
+
+
+def _layer_random(cfg: ModelConfig, layer: int, init: _Init, tp_rank: int, tp_world: int,
+                  force_moe: Optional[bool] = None) -> LayerWeights:
+    H = cfg.hidden
+    h_lo, h_hi = _shard_range(cfg.n_heads, tp_rank, tp_world)
+    hl = h_hi - h_lo
+    qhd, lora, rope, nope, vd = cfg.q_head_dim, cfg.kv_lora_rank, cfg.qk_rope_dim, cfg.qk_nope_dim, cfg.v_head_dim
+    # full tensors are drawn first and sliced, so every TP layout sees the same model
+    if cfg.q_lora_rank:
+        w_q_a = init.normal(cfg.q_lora_rank, H)
+        w_q_b_full = init.normal(cfg.n_heads * qhd, cfg.q_lora_rank)
+        q_norm = init.ones(cfg.q_lora_rank)
+        w_q_b = w_q_b_full[h_lo * qhd:h_hi * qhd].contiguous()
+        q_part = w_q_a
+    else:
+        w_q_full = init.normal(cfg.n_heads * qhd, H)
+        q_part = w_q_full[h_lo * qhd:h_hi * qhd]
+        q_norm, w_q_b = None, None
+    w_kv_a = init.normal(lora + rope, H)
+    w_qkv_a = torch.cat([q_part, w_kv_a], dim=0).contiguous()
+    w_kv_b = init.normal(cfg.n_heads, nope + vd, lora)[h_lo:h_hi]
+    w_uk_t = w_kv_b[:, :nope, :].transpose(1, 2).contiguous()      # [hl, lora, nope]
+    w_uv = w_kv_b[:, nope:, :].contiguous()                         # [hl, vd, lora]
+    w_o = init.normal(H, cfg.n_heads * vd)[:, h_lo * vd:h_hi * vd].contiguous()
+    lw = LayerWeights(attn_norm=init.ones(H), w_qkv_a=w_qkv_a, q_norm=q_norm, w_q_b=w_q_b,
+                      kv_norm=init.ones(lora), w_uk_t=w_uk_t, w_uv=w_uv, w_o=w_o, ffn_norm=init.ones(H))
+    if cfg.attn_sink:
+        lw.attn_sink = init.normal(cfg.n_heads).float()[h_lo:h_hi].contiguous()
+    is_moe = cfg.is_moe_layer(layer) if force_moe is None else force_moe
+    lw.is_moe = is_moe
+
+    def ffn(inter: int):
+        i_lo, i_hi = _shard_range(inter, tp_rank, tp_world)
+        gate, up, down = init.normal(inter, H), init.normal(inter, H), init.normal(H, inter)
+        w13 = torch.cat([gate[i_lo:i_hi], up[i_lo:i_hi]], dim=0).unsqueeze(0).contiguous()
+        w2 = down[:, i_lo:i_hi].unsqueeze(0).contiguous()
+        return w13, w2
+
+    if not is_moe:
+        lw.w13, lw.w2 = ffn(cfg.dense_inter)
+        return lw
+    E, I = cfg.n_routed_experts, cfg.moe_inter
+    lw.router_w = init.normal(E, H)
+    if cfg.router_bias:
+        lw.router_bias = init.normal(E).float()
+    if layer < cfg.n_dense_layers + cfg.n_hash_layers and cfg.n_hash_layers:
+        g = torch.Generator().manual_seed(init.seed + 7919 * (layer + 1))
+        lw.hash_table = torch.randint(0, E, (cfg.vocab_size, cfg.topk), generator=g).to(init.device)
+    e_lo, e_hi = _shard_range(E, tp_rank, tp_world)
+    # experts are drawn one by one so only the local ones are ever materialised
+    w13s, w2s = [], []
+    for e in range(E):
+        if e_lo <= e < e_hi:
+            gate, up, down = init.normal(I, H), init.normal(I, H), init.normal(H, I)
+            w13s.append(torch.cat([gate, up], dim=0))
+            w2s.append(down)
+        else:
+            init.counter += 3
+    lw.e_w13 = torch.stack(w13s).contiguous()
+    lw.e_w2 = torch.stack(w2s).contiguous()
+    if cfg.n_shared_experts:
+        lw.w13, lw.w2 = ffn(cfg.n_shared_experts * I)
+    return lw
+
+
+def random_weights(cfg: ModelConfig, device="cpu", dtype=torch.bfloat16, seed: int = 0, std: float = 0.02,
+                   tp_rank: int = 0, tp_world: int = 1, fast_device_init: bool = False) -> ModelWeights:
+    """Random-init weights N(0, std), norms = 1.
+
+    fast_device_init draws on the GPU (much faster for multi-GB models; values then differ
+    between TP layouts, which is fine for throughput runs but not for parity tests).
+    """
+    init = _Init(seed, std, device, dtype, fast_device_init)
+    embed = init.normal(cfg.vocab_size, cfg.hidden)
+    layers = [_layer_random(cfg, i, init, tp_rank, tp_world) for i in range(cfg.n_layers)]
+    v_lo, v_hi = _shard_range(cfg.vocab_size, tp_rank, tp_world)
+    lm_head = init.normal(cfg.vocab_size, cfg.hidden)[v_lo:v_hi].contiguous()
+    mtp = []
+    for m in range(cfg.n_mtp_layers):
+        mtp.append(MtpWeights(enorm=init.ones(cfg.hidden), hnorm=init.ones(cfg.hidden),
+                              eh_proj=init.normal(cfg.hidden, 2 * cfg.hidden),
+                              layer=_layer_random(cfg, cfg.n_layers + m, init, tp_rank, tp_world,
+                                                  force_moe=cfg.n_routed_experts > 0),
+                              final_norm=init.ones(cfg.hidden)))
+    e_lo, e_hi = _shard_range(cfg.n_routed_experts, tp_rank, tp_world) if cfg.n_routed_experts else (0, 0)
+    return ModelWeights(cfg, embed, layers, init.ones(cfg.hidden), lm_head, mtp, tp_rank, tp_world,
+                        e_lo, e_hi, v_lo)

@@ -82,7 +82,7 @@ def _declare(lib: C.CDLL) -> None:
     lib.fb_mla_prep.argtypes = [vp, ll, i, vp, ll, i, i, i, vp, f, vp, vp, i, vp, vp, vp, ll, vp,
                                 ll, i, vp, vp]
     lib.fb_router_topk.argtypes = [vp, ll, vp, vp, vp, i, i, i, i, i, i, i, f, vp, vp, vp]
-    lib.fb_moe_plan.argtypes = [vp, vp, i, i, i, i, i, vp, vp, vp, vp, vp, vp, i, vp, vp, vp, vp]
+    lib.fb_moe_plan.argtypes = [vp, vp, i, i, i, i, i, i, vp, vp, vp, vp, vp, vp, i, vp, vp, vp, vp]
     lib.fb_gather_rows.argtypes = [vp, ll, vp, vp, vp, ll, i, i, i, vp, vp]
     lib.fb_moe_reduce.argtypes = [vp, i, i, vp, i, i, vp, ll, vp, ll, vp, ll, i, i, i, vp]
     lib.fb_argmax.argtypes = [vp, ll, i, i, vp, vp, vp]

@@ -186,11 +186,11 @@ def router_topk(logits: torch.Tensor, topk: int, score_fn: int, bias: Optional[t
 
 
 def moe_plan(topk_idx: torch.Tensor, topk_w: Optional[torch.Tensor], plan: MoePlan, e_lo: int,
-             e_hi: int) -> MoePlan:
+             e_hi: int, dst_slots: int = 0) -> MoePlan:
     lib = get_lib(True)
     rows, topk = topk_idx.shape
     assert rows * topk <= plan.cap_rows
-    check(lib.fb_moe_plan(topk_idx.data_ptr(), ptr(topk_w), rows * topk, topk, e_lo, e_hi, plan.ntok,
+    check(lib.fb_moe_plan(topk_idx.data_ptr(), ptr(topk_w), rows * topk, topk, e_lo, e_hi, plan.ntok, dst_slots,
                           plan.src_token.data_ptr(), plan.dst_row.data_ptr(), plan.row_scale.data_ptr(),
                           plan.tile_group.data_ptr(), plan.tile_row0.data_ptr(), plan.tile_rows.data_ptr(),
                           plan.max_tiles, plan.counts.data_ptr(), plan.meta.data_ptr(),

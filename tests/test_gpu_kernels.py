@@ -139,12 +139,10 @@ def test_moe_grouped_pipeline(K, T, E, topk, e_lo, e_hi, ntok, H, I):
     K.gemm(xg, w13, out=hmid, epilogue=K.EPI_SWIGLU, plan=plan)
     slots = topk + 1
     route_out = torch.zeros(T * slots, H, dtype=torch.bfloat16, device="cuda")
-    # route r = t*topk + s lands in row t*slots + s: give the GEMM a [T, slots*H] view trick via ldo
+    # route r = t*topk + s lands in row t*slots + s
     ro_view = route_out.view(T, slots, H)
-    dst_fix = (plan.dst_row // topk) * slots + plan.dst_row % topk
-    plan2 = K.MoePlan(plan.ntok, plan.max_tiles, plan.cap_rows, plan.src_token, dst_fix.to(torch.int32),
-                      plan.row_scale, plan.tile_group, plan.tile_row0, plan.tile_rows, plan.counts, plan.meta)
-    K.gemm(hmid, w2, out=route_out, epilogue=K.EPI_SCATTER, plan=plan2)
+    K.moe_plan(idx, w, plan, e_lo, e_hi, dst_slots=slots)
+    K.gemm(hmid, w2, out=route_out, epilogue=K.EPI_SCATTER, plan=plan)
     extra = rnd(T, H)
     resid = rnd(T, H)
     ro_view[:, topk] = extra
