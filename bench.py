@@ -1,0 +1,257 @@
+#!/usr/bin/env python
+"""Headline benchmark: greedy decode throughput of the DeepSeek-V2-Lite-shape MoE model.
+
+  python bench.py --gpus N --steps K --warmup W          (N > 1: launched by torch.distributed.run)
+  python bench.py --impl reference ...                   (the reference arm)
+
+Config: 27 layers, hidden 2048, 16 heads, MLA (kv_lora 512, nope 128, rope 64, v 128), layer 0
+dense (inter 10944), 26 MoE layers (64 routed + 2 shared experts, top-6, inter 1408), vocab
+102400, bf16, random-init N(0, 0.02), batch 32, 512-token uniform-random prompts, paged KV with
+64-token pages.  One "step" is one decode step of the whole batch (32 new tokens).  N > 1 runs
+tensor parallel over N ranks on the same batch (strong scaling).
+
+Two numbers:
+  value : K decode steps replayed back to back as the captured CUDA graph, timed with CUDA events
+          (device time of the kernels only).
+  e2e   : the same K decode steps driven through the public engine API (`Engine.step`): scheduler,
+          KV reservation/commit, one pinned host->device copy of the step's inputs, the graph, one
+          device->host read of the greedy tokens, token publication.
+Every step streams the full weight set (31 GB, far larger than the 126 MB L2), so no L2 flush is
+needed between iterations.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+BASELINE_TOK_S = 16.0        # the reference's only stated throughput figure (a target, not a measurement)
+
+
+def reference_arm() -> None:
+    print(json.dumps({
+        "impl": "reference",
+        "unavailable": "the reference is a Rust workspace (no setup.py/pyproject.toml; pip install fails with "
+                       "'not installable'), needs cargo nightly-2026-08-01 and a network CUTLASS checkout, and "
+                       "its plan compiler fails closed on sm_100",
+    }))
+
+
+class ClockSampler:
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.path = tempfile.mktemp(prefix="clocks_", suffix=".csv")
+        self.proc = None
+        self.gpu_index = gpu_index
+
+    def start(self) -> None:
+        try:
+            self.f = open(self.path, "w")
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                                          "-lms", "100", "-i", str(self.gpu_index)], stdout=self.f,
+                                         stderr=subprocess.DEVNULL)
+        except Exception:  # noqa: BLE001 - sampling is best effort
+            self.proc = None
+
+    def stop(self) -> dict:
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if self.proc is None:
+            return out
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:  # noqa: BLE001
+            self.proc.kill()
+        self.f.close()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in open(self.path):
+            p = [x.strip() for x in line.split(",")]
+            if len(p) < 9:
+                continue
+            try:
+                sm.append(float(p[1]))
+                mx.append(float(p[2]))
+            except ValueError:
+                continue
+            for name, v in zip(names, p[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        os.unlink(self.path)
+        if sm:
+            out.update(sm_mhz=statistics.median(sm), sm_max_mhz=max(mx), reasons=sorted(reasons), samples=len(sm))
+        return out
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours")
+    ap.add_argument("--batch", type=int, default=32)
+    ap.add_argument("--prompt-len", type=int, default=512)
+    ap.add_argument("--model", default="deepseek-v2-lite")
+    ap.add_argument("--layers", type=int, default=0, help="debug only: override layer count (result is marked invalid)")
+    ap.add_argument("--no-fused", action="store_true", help="use the NCCL baseline collectives instead of fused kernels")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        reference_arm()
+        return
+
+    import torch
+    import torch.distributed as dist
+
+    from ferrule_b200.models import config as C
+    from ferrule_b200.models import weights as W
+    from ferrule_b200.models.runner import DeepSeekRunner
+    from ferrule_b200.runtime.engine import Engine, EngineConfig, FinishEvent, TokenEvent
+    from ferrule_b200.runtime.scheduler import SchedulerConfig
+    from ferrule_b200.runtime.session import GenerateRequest
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.gpus != world:
+        if world == 1 and args.gpus > 1:
+            raise SystemExit("for --gpus N > 1 launch with: python -m torch.distributed.run --nproc-per-node N bench.py ...")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    tp = None
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+        from ferrule_b200.parallel.tp import TensorParallel
+        tp = TensorParallel(rank, world, dev, fused=not args.no_fused)
+
+    cfg = C.PRESETS[args.model]()
+    if args.layers:
+        cfg = cfg.with_(n_layers=args.layers)
+    B, P, K, Wm = args.batch, args.prompt_len, args.steps, args.warmup
+    page = 64
+    margin = 64                      # sequences that finish prefill early decode ahead of the others
+    max_seq = P + K + Wm + margin + 2 * page
+    pages_per_seq = (max_seq + page - 1) // page
+    weights = W.random_weights(cfg, device=dev, seed=0, tp_rank=rank, tp_world=world, fast_device_init=True)
+    runner = DeepSeekRunner(weights, n_pages=B * pages_per_seq + 8, page_size=page, max_rows=2048, max_seqs=B,
+                            max_seq_len=pages_per_seq * page, device=dev, tp=tp)
+    if tp is not None:
+        tp.attach(runner.fwd)
+    sched = SchedulerConfig(max_active_sequences=B, max_decode_batch=B, max_batch_tokens=2048, prefill_chunk_size=512,
+                            mixed_batches=True, ctx_size=pages_per_seq * page)
+    engine = Engine(runner, EngineConfig(scheduler=sched, kv_pages=B * pages_per_seq + 8, page_size=page))
+
+    # synthetic prompts: token ids uniform over the vocabulary, identical on every rank
+    g = torch.Generator().manual_seed(1234)
+    prompts = torch.randint(0, cfg.vocab_size, (B, P), generator=g)
+    t_submit = time.perf_counter()
+    for i in range(B):
+        engine.submit(GenerateRequest(f"req{i}", prompts[i].tolist(), max_new_tokens=K + Wm + margin, ignore_eos=True))
+    first_token_t, token_times = {}, {}
+
+    def emit(ev) -> None:
+        if isinstance(ev, TokenEvent):
+            now = time.perf_counter()
+            first_token_t.setdefault(ev.request_id, now)
+            token_times.setdefault(ev.request_id, []).append(now)
+
+    def barrier() -> None:
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- prefill (untimed for the decode metric; TTFT is reported from it) ----
+    while any(s.prefill_remaining > 0 for s in engine.scheduler.active.values()) or engine.scheduler.waiting:
+        engine.step(emit)
+    # one decode step so that every sequence has emitted its first token
+    engine.step(emit)
+    ttft = sorted(first_token_t[r] - t_submit for r in first_token_t)
+    for _ in range(Wm):
+        engine.step(emit)
+
+    # ---- e2e: K engine steps, device-timed around the whole loop ----
+    sampler = ClockSampler(local_rank)
+    barrier()
+    sampler.start()
+    h2d0, d2h0, l0 = runner.stats.h2d_bytes, runner.stats.d2h_bytes, runner.stats.kernel_launches
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    steps_before = engine.stats.decode_steps
+    e0.record()
+    for _ in range(K):
+        engine.step(emit)
+    e1.record()
+    barrier()
+    e2e_ms = e0.elapsed_time(e1)
+    assert engine.stats.decode_steps - steps_before == K, "a timed engine step was not a decode step"
+    h2d = (runner.stats.h2d_bytes - h2d0) // K
+    d2h = (runner.stats.d2h_bytes - d2h0) // K
+    e2e_launches = runner.stats.kernel_launches - l0
+
+    # ---- device-only: replay the captured decode graph K times ----
+    st, graph = runner.graphs[B]
+    for _ in range(3):
+        graph.replay()
+    barrier()
+    d0, d1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    d0.record()
+    for _ in range(K):
+        graph.replay()
+    d1.record()
+    barrier()
+    clocks = sampler.stop()
+    dev_ms = d0.elapsed_time(d1)
+
+    from ferrule_b200.ops import _lib
+    status = _lib.read_status()
+    times = torch.tensor([dev_ms, e2e_ms], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    dev_ms, e2e_ms = times.tolist()
+    tpots = []
+    for r, ts in token_times.items():
+        if len(ts) > 2:
+            tpots.append((ts[-1] - ts[1]) / (len(ts) - 2))
+    if rank == 0:
+        value = B * K / (dev_ms / 1e3)
+        e2e_value = B * K / (e2e_ms / 1e3)
+        par = "tp%d" % world if world > 1 else "single-gpu"
+        line = {
+            "metric": "decode tokens/s (whole job, max over ranks)",
+            "value": round(value, 1), "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": Wm,
+            "ms_per_step": round(dev_ms / K, 4), "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": round(value / BASELINE_TOK_S, 1), "dtype": "bf16",
+            "data": "synthetic (uniform-random token ids, random-init N(0,0.02) weights)",
+            "config": {"model": cfg.name, "global_batch": B, "seq_len": P, "decode_context": P + Wm + 1,
+                       "parallelism": par, "kv_page_size": page, "layers": cfg.n_layers,
+                       "l2_policy": "inputs larger than L2: each step streams %.1f GB of weights per GPU"
+                                    % (weights.nbytes() / 1e9),
+                       "collectives": "none" if world == 1 else ("nccl" if args.no_fused else "fused-p2p")},
+            "e2e": {"value": round(e2e_value, 1), "unit": "tokens/s", "ms_per_step": round(e2e_ms / K, 4),
+                    "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h),
+                    "path": "Engine.step (scheduler + KV transactions + pinned H2D + graph + D2H)"},
+            "gpu_launches": int(graph.launches * K),
+            "gpu_launches_e2e": int(e2e_launches),
+            "clocks": {"sm_mhz": clocks["sm_mhz"], "sm_max_mhz": clocks["sm_max_mhz"], "reasons": clocks["reasons"],
+                       "samples": clocks["samples"]},
+            "ttft_p50_s": round(ttft[len(ttft) // 2], 4) if ttft else None,
+            "tpot_p50_s": round(statistics.median(tpots), 6) if tpots else None,
+            "device_status": list(status),
+            "impl": "ours",
+        }
+        if args.layers:
+            line["invalid"] = "debug run with a reduced layer count"
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -270,8 +270,10 @@ class CudaWorkspace:
         self.h_last = torch.zeros(L, H, **bf)
         self.hn_last = torch.zeros(L, H, **bf)
         self.logits = torch.zeros(L, w.lm_head.shape[0], **f32)
-        self.next_id = torch.zeros(L, **i32)
-        self.next_val = torch.zeros(L, **f32)
+        # greedy result packed for a single device->host copy: [ids (int32) | values (fp32 bits)]
+        self.out_buf = torch.zeros(2 * L, **i32)
+        self.next_id = self.out_buf[:L]
+        self.next_val = self.out_buf[L:].view(torch.float32)
         self.mtp_x = torch.zeros(R, 2 * H, **bf) if w.mtp else None
 
     def nbytes(self) -> int:
@@ -439,6 +441,8 @@ class CudaForward:
         self.launches = 0
         h = self.hidden_states(b, T)
         self.last_hidden = h
+        if b.n_logit == 0:
+            return None, None, None
         return self.head(h, b, self.w.final_norm, want_logits)
 
     def mtp_forward(self, stage: int, h_prev: torch.Tensor, b: DeviceBatch):
@@ -470,11 +474,12 @@ class DecodeGraph:
     (crates/ferrule-backend/src/cuda/graph.rs:70-150).
     """
 
-    def __init__(self, fwd: CudaForward, rows: int, n_seqs: int, max_blocks: int):
+    def __init__(self, fwd: CudaForward, rows: int, n_seqs: int, max_blocks: int,
+                 batch: Optional[DeviceBatch] = None):
         dev = fwd.device
         i32 = dict(dtype=torch.int32, device=dev)
         self.fwd, self.rows = fwd, rows
-        self.batch = DeviceBatch(torch.zeros(rows, **i32), torch.zeros(rows, **i32),
+        self.batch = batch if batch is not None else DeviceBatch(torch.zeros(rows, **i32), torch.zeros(rows, **i32),
                                  torch.full((rows,), -1, dtype=torch.int64, device=dev),
                                  torch.zeros(rows, **i32), torch.full((rows,), -1, **i32),
                                  torch.zeros(n_seqs, max_blocks, **i32), torch.arange(rows, **i32), rows, rows)

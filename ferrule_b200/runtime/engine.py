@@ -1,0 +1,625 @@
+"""The resident engine: owner of requests, scheduling, execution transactions and KV custody.
+
+`step()` runs one owner-loop turn: drive transaction endings -> retire pages -> flush the
+committed-token outbox -> progress materializations -> resume ready transactions -> ask the
+scheduler for an action -> execute it as an ordinary or speculative transaction.
+
+An ordinary transaction: lower the action to an `ExecutionBatch` -> claim the sessions ->
+reserve KV pages (one hard credit per physical page) -> bind write slots -> runner
+`prepare_batch` -> `execute` -> on `Complete`: prepare the logical commit ->
+`end_transaction(PUBLISH)` until `COMPLETE` -> publish KV -> commit the scheduler state ->
+move tokens to the outbox -> stage the next greedy token.  On `Waiting` the transaction parks
+as a continuation until its dependencies are published.  An abort keeps every page, slot and
+credit until the backend answers `COMPLETE`.
+
+Tokens become visible outside only from the outbox, i.e. after their KV rows and the
+scheduler state are committed.
+
+Counterpart of crates/ferrule-runtime/src/engine/driver.rs (step :4192-4284, ordinary
+transaction :3049-3204/:3282-3444, abort :3667-3775, finish rules :3858-4026, fork/preempt/
+restore :1679-1795/:2310-2440, shutdown :4034-4190).
+"""
+from __future__ import annotations
+
+import time
+from collections import deque
+from dataclasses import dataclass, field
+from enum import Enum
+from typing import Callable, Deque, Dict, List, Optional, Sequence, Tuple
+
+from .execution import (ExecutionBatch, ExecutionOutput, Intent, LogitsRequest, Phase, SequenceSlice)
+from .kv_pages import KvPageManager, KvRetirement, OutOfPages
+from .resources import Grant, PhysicalResourceBroker, ResourceKind
+from .runner import Complete, EndIntent, EndStatus, ModelRunner, Waiting
+from .scheduler import (Cancel, DecodeBatch, Execute, Finish, PrefillChunk, ResidentScheduler, SchedulerConfig)
+from .session import FinishReason, GenerateRequest, SeqStatus, SequenceState
+
+
+@dataclass
+class EngineConfig:
+    scheduler: SchedulerConfig = field(default_factory=SchedulerConfig)
+    kv_pages: int = 256
+    page_size: int = 16
+    speculative: bool = False
+    max_draft: int = 1
+    confidence_threshold: float = 0.2
+    auto_preempt: bool = False          # preempt the youngest decode sequence when pages run out
+
+
+@dataclass
+class TokenEvent:
+    request_id: str
+    token: int
+    text: str
+    index: int                          # 0-based index among generated tokens
+
+
+@dataclass
+class FinishEvent:
+    request_id: str
+    reason: FinishReason
+    prompt_tokens: int
+    generated_tokens: int
+    text: str
+    ttft_s: float = 0.0
+    tpot_s: float = 0.0
+
+
+class TxnState(Enum):
+    EXECUTING = "executing"
+    WAITING = "waiting"
+    PUBLISHING = "publishing"
+    ABORTING = "aborting"
+    DONE = "done"
+
+
+@dataclass
+class TxnSeq:
+    seq: SequenceState
+    res_id: int
+    rows: int
+    is_prefill: bool
+    query_start: int = 0
+
+
+@dataclass
+class Transaction:
+    txn_id: int
+    members: List[TxnSeq]
+    batch: Optional[ExecutionBatch] = None
+    grant: Optional[Grant] = None
+    state: TxnState = TxnState.EXECUTING
+    output: Optional[ExecutionOutput] = None
+    commit_id: Optional[int] = None
+    speculative: object = None          # speculation.SpecCohort for verification transactions
+    error: Optional[BaseException] = None
+    t_start_ns: int = 0
+
+
+@dataclass
+class EngineStats:
+    steps: int = 0
+    actions: int = 0
+    transactions: int = 0
+    aborted_transactions: int = 0
+    prefill_chunks: int = 0
+    prefill_tokens: int = 0
+    decode_steps: int = 0
+    decode_rows: int = 0
+    emitted_tokens: int = 0
+    staged_tokens: int = 0
+    finished: int = 0
+    kv_stalls: int = 0
+    auto_preemptions: int = 0
+    waits: int = 0
+    resumes: int = 0
+    host_ns: int = 0
+    runner_ns: int = 0
+    ttft_sum_s: float = 0.0
+    tpot_sum_s: float = 0.0
+    e2e_sum_s: float = 0.0
+
+
+EmitFn = Callable[[object], None]
+
+
+class Engine:
+    def __init__(self, runner: ModelRunner, cfg: Optional[EngineConfig] = None,
+                 detokenize: Optional[Callable[[List[int]], str]] = None,
+                 registry=None, broker: Optional[PhysicalResourceBroker] = None):
+        self.runner = runner
+        self.cfg = cfg or EngineConfig()
+        self.scheduler = ResidentScheduler(self.cfg.scheduler)
+        self.kv = KvPageManager(self.cfg.kv_pages, self.cfg.page_size, self.cfg.scheduler.ctx_size + 8)
+        self.broker = broker or PhysicalResourceBroker()
+        self.broker.set_limit(ResourceKind.KV_PAGES, self.cfg.kv_pages)
+        self.registry = registry
+        self.detokenize = detokenize
+        self.stats = EngineStats()
+        self._next_txn = 0
+        self._ending: Deque[Transaction] = deque()
+        self._waiting: Dict[int, Transaction] = {}
+        self._outbox: Deque[object] = deque()
+        self._retired: KvRetirement = KvRetirement()
+        self._sessions: Dict[str, SequenceState] = {}
+        self._snapshots: Dict[str, Tuple[object, list]] = {}
+        self._shutdown = False
+        self.spec = None
+        if self.cfg.speculative:
+            from .speculation import SpeculativeDecoder
+            self.spec = SpeculativeDecoder(self)
+
+    # ------------------------------------------------------------------ public API
+    def submit(self, req: GenerateRequest) -> SequenceState:
+        if self._shutdown:
+            raise RuntimeError("engine is shut down")
+        if req.max_new_tokens < 0:
+            raise ValueError("max_new_tokens must be >= 0")
+        prev = self._sessions.pop(req.session_id, None) if req.session_id else None
+        now = time.perf_counter_ns()
+        if prev is not None:
+            seq = SequenceState(req, kv_seq=prev.kv_seq, tokens=prev.tokens + list(req.prompt_tokens),
+                                position=prev.position, arrival_ns=now)
+        else:
+            if not req.prompt_tokens:
+                raise ValueError("empty prompt")
+            seq = SequenceState(req, kv_seq=self.kv.alloc_sequence(), tokens=list(req.prompt_tokens),
+                                arrival_ns=now)
+        seq.prompt_len = len(seq.tokens)
+        if seq.prompt_len + 1 > self.cfg.scheduler.ctx_size:
+            self.kv.free_sequence_pages(seq.kv_seq)
+            raise ValueError("prompt does not fit the context window")
+        self.scheduler.submit(seq)
+        return seq
+
+    def cancel_request(self, request_id: str) -> bool:
+        seq = self.scheduler.cancel(request_id)
+        if seq is None:
+            return False
+        if seq.status == SeqStatus.FINISHED:       # was still waiting: nothing else to release
+            self._release_sequence(seq, FinishReason.CANCELLED)
+        return True
+
+    def has_work(self) -> bool:
+        return bool(self.scheduler.has_work() or self._ending or self._waiting or self._outbox
+                    or self._retired)
+
+    def fork_session_exact(self, request_id: str, new_req: GenerateRequest) -> SequenceState:
+        """New request that continues from an exact copy of a live sequence's committed state.
+        Pages are shared by refcount; the partially filled tail page is copied on first write."""
+        src = self.scheduler.active.get(request_id) or self._sessions.get(request_id)
+        if src is None:
+            raise KeyError(request_id)
+        if src.status == SeqStatus.RUNNING:
+            raise RuntimeError("cannot fork a sequence inside a transaction")
+        child_kv = self.kv.publish_fork_sequence_exact(src.kv_seq)
+        committed = src.tokens[:src.position]
+        seq = SequenceState(new_req, kv_seq=child_kv, tokens=committed + list(new_req.prompt_tokens),
+                            position=src.position, arrival_ns=time.perf_counter_ns())
+        seq.prompt_len = len(seq.tokens)
+        if seq.prefill_remaining == 0:
+            # nothing new to run: re-run the last committed token to obtain logits
+            raise ValueError("a fork needs at least one new prompt token")
+        self.scheduler.submit(seq)
+        return seq
+
+    def preempt_session(self, request_id: str) -> None:
+        seq = self.scheduler.active.get(request_id)
+        if seq is None or seq.status == SeqStatus.RUNNING:
+            raise RuntimeError("sequence not preemptible now")
+        rec = self.kv.preempt_sequence(seq.kv_seq)
+        pages = [p for _, p in rec.exclusive]
+        snap = self.runner.snapshot_pages(pages) if pages else None
+        self._snapshots[request_id] = (snap, pages)
+        self._retire(self.kv.release_preempted_pages(seq.kv_seq))
+        self.scheduler.suspend(seq)
+
+    def restore_session(self, request_id: str) -> None:
+        seq = self.scheduler.suspended.get(request_id)
+        if seq is None:
+            raise KeyError(request_id)
+        self._drive_retirements()
+        mapping = self.kv.restore_sequence(seq.kv_seq)          # may raise OutOfPages
+        snap, old_pages = self._snapshots.pop(request_id)
+        if mapping:
+            self.runner.restore_pages([p for _, p in mapping], snap)
+        self.scheduler.resume(seq)
+
+    def shutdown(self) -> bool:
+        """Non-blocking: returns True once nothing is in flight and all custody is returned."""
+        self._shutdown = True
+        for s in list(self.scheduler.waiting) + list(self.scheduler.active.values()):
+            self.cancel_request(s.request_id)
+        self.step(lambda ev: None)
+        idle = not (self._ending or self._waiting)
+        if idle:
+            for s in list(self._sessions.values()):
+                self._retire(self.kv.free_sequence_pages(s.kv_seq))
+            self._sessions.clear()
+            self._drive_retirements()
+            self.runner.shutdown()
+        return idle
+
+    # ------------------------------------------------------------------ owner loop
+    def step(self, emit: EmitFn) -> bool:
+        t0 = time.perf_counter_ns()
+        self.stats.steps += 1
+        progressed = self._drive_endings()
+        progressed |= self._drive_retirements()
+        progressed |= self._flush_outbox(emit)
+        if self.registry is not None:
+            progressed |= bool(self.registry.drive())
+            progressed |= self._resume_ready()
+        action = self.scheduler.next_action()
+        if action is not None:
+            self.stats.actions += 1
+            self._execute_action(action)
+            progressed = True
+        progressed |= self._flush_outbox(emit)
+        self.stats.host_ns += time.perf_counter_ns() - t0
+        return progressed
+
+    def run_until_idle(self, emit: EmitFn, max_steps: int = 1_000_000) -> int:
+        n = 0
+        while self.has_work() and n < max_steps:
+            if not self.step(emit) and not self.has_work():
+                break
+            n += 1
+        return n
+
+    # ------------------------------------------------------------------ actions
+    def _execute_action(self, action) -> None:
+        if isinstance(action, Cancel):
+            self._finish(action.seq, FinishReason.CANCELLED)
+            return
+        if isinstance(action, Finish):
+            self._finish(action.seq, action.reason)
+            return
+        if isinstance(action, PrefillChunk):
+            prefills, decodes = [(action.seq, action.tokens)], []
+        elif isinstance(action, DecodeBatch):
+            prefills, decodes = [], action.seqs
+        else:
+            prefills, decodes = action.prefills, action.decodes
+        if not prefills and self.spec is not None and self.runner.proposals_enabled():
+            if self.spec.try_execute(decodes):
+                return
+        self._execute_ordinary(prefills, decodes)
+
+    def _reserve(self, seq: SequenceState, n: int, members: List[TxnSeq], is_prefill: bool,
+                 claimed: Dict[ResourceKind, int]) -> bool:
+        need = self.kv.required_physical_pages(seq.kv_seq, n)
+        if need > self.kv.free_pages or need > self.broker.available(ResourceKind.KV_PAGES) - claimed[ResourceKind.KV_PAGES]:
+            return False
+        r = self.kv.reserve(seq.kv_seq, n)
+        claimed[ResourceKind.KV_PAGES] += need
+        members.append(TxnSeq(seq, r.res_id, n, is_prefill))
+        return True
+
+    def _execute_ordinary(self, prefills, decodes) -> None:
+        self._drive_retirements()
+        members: List[TxnSeq] = []
+        claimed = {ResourceKind.KV_PAGES: 0}
+        stalled: List[SequenceState] = []
+        for seq in decodes:
+            if not self._reserve(seq, 1, members, False, claimed):
+                stalled.append(seq)
+        for seq, n in prefills:
+            if not self._reserve(seq, n, members, True, claimed):
+                stalled.append(seq)
+        for seq in stalled:
+            self.stats.kv_stalls += 1
+            self.scheduler.requeue_unchanged(seq)
+        if not members:
+            if stalled and self.cfg.auto_preempt:
+                self._auto_preempt(stalled)
+            return
+        grant = self.broker.try_claim(claimed, required=True)
+        txn = Transaction(self._next_txn, members, grant=grant, t_start_ns=time.perf_counter_ns())
+        self._next_txn += 1
+        self.stats.transactions += 1
+        try:
+            txn.batch = self._lower(txn)
+            self.runner.prepare_batch(txn.txn_id, txn.batch)
+            if grant is not None:
+                self.broker.mark_submitted(grant)
+            t0 = time.perf_counter_ns()
+            progress = self.runner.execute(txn.txn_id)
+            self.stats.runner_ns += time.perf_counter_ns() - t0
+        except Exception as exc:  # noqa: BLE001 - every backend failure aborts the transaction
+            self._abort(txn, exc)
+            return
+        self._on_progress(txn, progress)
+
+    def _lower(self, txn: Transaction) -> ExecutionBatch:
+        ps = self.cfg.page_size
+        token_ids: List[int] = []
+        positions: List[int] = []
+        write_slots: List[int] = []
+        logits: List[LogitsRequest] = []
+        seqs: List[SequenceSlice] = []
+        block_ids: List[int] = []
+        none, top1 = LogitsRequest.none(), LogitsRequest.topk(1)
+        for m in txn.members:
+            seq = m.seq
+            r = self.kv.reservation(m.res_id)
+            self.kv.bind_reservation_execution(m.res_id, txn.txn_id)
+            blocks, slots = self.kv.reservation_bindings(m.res_id)
+            m.query_start = len(token_ids)
+            start = seq.position
+            if m.is_prefill:
+                toks = seq.tokens[start:start + m.rows]
+                last_chunk = start + m.rows >= seq.prompt_len
+                token_ids.extend(toks)
+                logits.extend([none] * (m.rows - 1))
+                logits.append(top1 if last_chunk else none)
+            else:
+                token_ids.append(seq.staged_token)
+                logits.append(top1)
+            positions.extend(range(start, start + m.rows))
+            write_slots.extend(slots)
+            seqs.append(SequenceSlice(seq.slot, Phase.PREFILL if m.is_prefill else Phase.DECODE, m.query_start,
+                                      m.rows, start, start + m.rows, len(block_ids), len(blocks),
+                                      (r.cow,) if r.cow is not None else ()))
+            block_ids.extend(blocks)
+        return ExecutionBatch(token_ids, positions, write_slots, logits, seqs, block_ids, Intent.COMMITTED, ps)
+
+    # ------------------------------------------------------------------ progress / endings
+    def _on_progress(self, txn: Transaction, progress) -> None:
+        if isinstance(progress, Waiting):
+            self.stats.waits += 1
+            txn.state = TxnState.WAITING
+            self._waiting[txn.txn_id] = txn
+            if self.registry is None:
+                self._abort(txn, RuntimeError("runner is waiting on materializations but no registry is attached"))
+                self._waiting.pop(txn.txn_id, None)
+                return
+            self.registry.register_continuation(txn.txn_id, progress.dependencies)
+            return
+        assert isinstance(progress, Complete)
+        try:
+            progress.output.validate(txn.batch)
+        except Exception as exc:  # noqa: BLE001
+            self._abort(txn, exc)
+            return
+        txn.output = progress.output
+        if txn.speculative is not None:
+            self.spec.on_verified(txn)
+            return
+        txn.commit_id = self.kv.prepare_commit([(m.res_id, m.rows) for m in txn.members])
+        txn.state = TxnState.PUBLISHING
+        self._end(txn)
+
+    def _resume_ready(self) -> bool:
+        did = False
+        for txn_id in self.registry.pop_ready():
+            txn = self._waiting.pop(txn_id, None)
+            if txn is None:
+                continue
+            self.stats.resumes += 1
+            did = True
+            try:
+                t0 = time.perf_counter_ns()
+                progress = self.runner.resume(txn_id)
+                self.stats.runner_ns += time.perf_counter_ns() - t0
+            except Exception as exc:  # noqa: BLE001
+                self._abort(txn, exc)
+                continue
+            txn.state = TxnState.EXECUTING
+            self._on_progress(txn, progress)
+        return did
+
+    def _end(self, txn: Transaction) -> None:
+        """Ask the backend to end the transaction; publish or roll back once it is COMPLETE."""
+        intent = EndIntent.PUBLISH if txn.state == TxnState.PUBLISHING else EndIntent.ABORT
+        try:
+            status = self.runner.end_transaction(txn.txn_id, intent)
+        except Exception as exc:  # noqa: BLE001
+            if intent == EndIntent.PUBLISH:
+                txn.error = exc
+                if txn.commit_id is not None:
+                    self.kv.abort_prepared_commit(txn.commit_id)
+                    txn.commit_id = None
+                txn.state = TxnState.ABORTING
+                self._ending.append(txn)
+                return
+            status = EndStatus.COMPLETE       # an abort that fails has nothing more to undo
+        if status == EndStatus.PENDING:
+            if txn not in self._ending:
+                self._ending.append(txn)
+            return
+        if txn in self._ending:
+            self._ending.remove(txn)
+        if txn.state == TxnState.PUBLISHING:
+            self._publish(txn)
+        else:
+            self._rollback(txn)
+
+    def _drive_endings(self) -> bool:
+        if not self._ending:
+            return False
+        for txn in list(self._ending):
+            self._end(txn)
+        return True
+
+    def _abort(self, txn: Transaction, exc: BaseException) -> None:
+        self.stats.aborted_transactions += 1
+        txn.error = exc
+        if txn.commit_id is not None:
+            self.kv.abort_prepared_commit(txn.commit_id)
+            txn.commit_id = None
+        txn.state = TxnState.ABORTING
+        self._end(txn)
+
+    def _rollback(self, txn: Transaction) -> None:
+        """Backend is done with the aborted transaction: now ownership may be returned."""
+        self._retire(self.kv.abort_reservations([m.res_id for m in txn.members]))
+        if txn.grant is not None:
+            self.broker.complete(txn.grant)
+        txn.state = TxnState.DONE
+        for m in txn.members:
+            seq = m.seq
+            if seq.finish == FinishReason.CANCELLED:
+                self._finish(seq, FinishReason.CANCELLED)
+            elif txn.error is not None and not getattr(txn.error, "retryable", False):
+                self._finish(seq, FinishReason.ERROR)
+            else:
+                self.scheduler.requeue_unchanged(seq)
+
+    # ------------------------------------------------------------------ publish
+    def _publish(self, txn: Transaction) -> None:
+        """Backend confirmed the publish: commit KV, scheduler, tokens; stage the next greedy tokens."""
+        ret = self.kv.publish_commit(txn.commit_id)
+        txn.commit_id = None
+        self._retire(ret)
+        if txn.grant is not None:
+            self.broker.complete(txn.grant)      # pages are now accounted by the page manager itself
+        txn.state = TxnState.DONE
+        out = txn.output.by_row()
+        now = time.perf_counter_ns()
+        n_prefill = n_decode = 0
+        for m in txn.members:
+            seq = m.seq
+            if m.is_prefill:
+                n_prefill += m.rows
+                self.scheduler.commit_prefill(seq, m.rows)
+                last_row = m.query_start + m.rows - 1
+            else:
+                n_decode += 1
+                tok = seq.staged_token
+                self.scheduler.commit_decode(seq, tok)
+                self._emit_token(seq, tok, now)
+                last_row = m.query_start
+            if seq.finish == FinishReason.CANCELLED:
+                self._finish(seq, FinishReason.CANCELLED)
+                continue
+            if not m.is_prefill and self._post_commit_finish(seq):
+                continue                             # its fresh logits are discarded
+            ro = out.get(last_row)
+            if ro is not None:
+                self._apply_output(seq, ro.top1)
+        if n_prefill:
+            self.stats.prefill_chunks += sum(1 for m in txn.members if m.is_prefill)
+            self.stats.prefill_tokens += n_prefill
+        if n_decode:
+            self.stats.decode_steps += 1
+            self.stats.decode_rows += n_decode
+
+    def _post_commit_finish(self, seq: SequenceState) -> bool:
+        req = seq.request
+        if seq.generated >= req.max_new_tokens:
+            self._finish(seq, FinishReason.MAX_TOKENS)
+            return True
+        if req.stop and seq.text:
+            for s in req.stop:
+                if s and seq.text.endswith(s):
+                    self._finish(seq, FinishReason.STOP_STRING)
+                    return True
+        return False
+
+    def _apply_output(self, seq: SequenceState, top1: Optional[int]) -> None:
+        """Post-forward finish rules, in order, else stage the greedy token."""
+        req = seq.request
+        if seq.generated >= req.max_new_tokens:
+            self._finish(seq, FinishReason.MAX_TOKENS)
+        elif seq.position >= self.cfg.scheduler.ctx_size:
+            self._finish(seq, FinishReason.CONTEXT)
+        elif top1 is None or top1 < 0:
+            self._finish(seq, FinishReason.NO_CANDIDATE)
+        elif top1 == self.runner.eos_token_id and not req.ignore_eos:
+            self._finish(seq, FinishReason.EOS)
+        else:
+            self.scheduler.stage(seq, top1)
+            self.stats.staged_tokens += 1
+
+    def _emit_token(self, seq: SequenceState, tok: int, now_ns: int) -> None:
+        delta = ""
+        if self.detokenize is not None:
+            full = self.detokenize(seq.tokens[seq.prompt_len:])
+            # hold back an incomplete UTF-8 tail (replacement char) until it completes
+            if full.endswith("�"):
+                full = full[:len(seq.text)] if len(full) <= len(seq.text) else full.rstrip("�")
+            delta = full[len(seq.text):]
+            seq.text = seq.text + delta
+        if seq.first_token_ns == 0:
+            seq.first_token_ns = now_ns
+        seq.last_token_ns = now_ns
+        self._outbox.append(TokenEvent(seq.request_id, tok, delta, seq.generated - 1))
+        self.stats.emitted_tokens += 1
+
+    def _finish(self, seq: SequenceState, reason: FinishReason) -> None:
+        if seq.status == SeqStatus.FINISHED and seq.slot < 0 and seq.kv_seq < 0:
+            return
+        self.scheduler.finish(seq, reason)
+        self._release_sequence(seq, reason)
+
+    def _release_sequence(self, seq: SequenceState, reason: FinishReason) -> None:
+        seq.staged_token = None
+        ttft = (seq.first_token_ns - seq.arrival_ns) / 1e9 if seq.first_token_ns else 0.0
+        tpot = ((seq.last_token_ns - seq.first_token_ns) / 1e9 / (seq.generated - 1)) if seq.generated > 1 else 0.0
+        keep = seq.request.retain_session and reason not in (FinishReason.CANCELLED, FinishReason.ERROR)
+        if keep:
+            # the session keeps its committed KV; uncommitted staged state is dropped
+            seq.tokens = seq.tokens[:seq.position]
+            self._sessions[seq.request.session_id or seq.request_id] = seq
+        elif seq.kv_seq >= 0:
+            self._retire(self.kv.free_sequence_pages(seq.kv_seq))
+            seq.kv_seq = -1
+        if seq.slot >= 0:
+            self.runner.release_slot(seq.slot)
+        self.stats.finished += 1
+        self.stats.ttft_sum_s += ttft
+        self.stats.tpot_sum_s += tpot
+        self.stats.e2e_sum_s += (time.perf_counter_ns() - seq.arrival_ns) / 1e9
+        self._outbox.append(FinishEvent(seq.request_id, reason, seq.prompt_len, seq.generated, seq.text, ttft, tpot))
+
+    def _flush_outbox(self, emit: EmitFn) -> bool:
+        if not self._outbox:
+            return False
+        while self._outbox:
+            emit(self._outbox.popleft())
+        return True
+
+    # ------------------------------------------------------------------ page retirement
+    def _retire(self, ret: KvRetirement) -> None:
+        if ret:
+            self._retired.extend(ret)
+
+    def _drive_retirements(self) -> bool:
+        """Hand retired pages to the backend; once it returns they are reusable."""
+        if not self._retired:
+            return False
+        pages = self._retired.pages
+        self._retired = KvRetirement()
+        self.runner.release_pages(pages)
+        self.kv.confirm_page_retirement(pages)
+        return True
+
+    def _auto_preempt(self, stalled: List[SequenceState]) -> None:
+        """Free pages by swapping out the youngest idle decode sequence."""
+        cands = [s for s in self.scheduler.decode_ready if s not in stalled]
+        if not cands:
+            return
+        victim = max(cands, key=lambda s: s.arrival_ns)
+        self.preempt_session(victim.request_id)
+        self.stats.auto_preemptions += 1
+
+    def maybe_restore_suspended(self) -> int:
+        """Bring suspended sequences back while pages allow (oldest first)."""
+        n = 0
+        for rid, seq in sorted(self.scheduler.suspended.items(), key=lambda kv: kv[1].arrival_ns):
+            try:
+                self.restore_session(rid)
+                n += 1
+            except OutOfPages:
+                break
+        return n
+
+    def snapshot_stats(self) -> Dict[str, object]:
+        st = dict(vars(self.stats))
+        st["kv"] = dict(vars(self.kv.stats()))
+        st["scheduler"] = dict(vars(self.scheduler.stats))
+        st["resources"] = self.broker.snapshot()
+        if self.spec is not None:
+            st["speculative"] = self.spec.metrics.to_dict()
+        return st
