@@ -132,6 +132,24 @@ int fb_topk_logits(const float* logits, long long ldl, int rows, int vocab, int 
 int fb_copy_pages(void* pool, long long layer_stride, long long page_elems, const int* pairs,
                   int n_pairs, int n_pages, int layers, void* status, void* stream);
 
+// ---- peer memory and collectives --------------------------------------------------------
+int fb_ipc_handle_bytes(void);
+int fb_ipc_alloc(void** ptr, long long bytes, void* handle_out);   // zero-filled device buffer + IPC handle
+int fb_ipc_open(const void* handle, void** ptr);                   // map a peer rank's buffer
+int fb_ipc_close(void* ptr);
+int fb_ipc_free(void* ptr);
+// ctr: private device words {calls, ctas_done, consumed arrivals per flag ...}
+int fb_moe_reduce_allreduce(const void* route_out, int slots, int topk, const int* topk_idx, int e_lo,
+                            int e_hi, const void* residual, long long ldr, void* out, long long ldo,
+                            int rows, int dim, int rank, int world, int rows_cap,
+                            void* const* peer_recv, void* const* peer_flags, void* ctr,
+                            int flag_capacity, unsigned long long wait_ns, void* status, void* stream);
+int fb_argmax_allgather(int* ids, float* vals, int vocab_lo, int rows, int rank, int world, int rows_cap,
+                        void* const* peer_recv, void* const* peer_flags, void* ctr,
+                        unsigned long long wait_ns, void* status, void* stream);
+int fb_flag_wait_probe(const void* flag, int target, unsigned long long wait_ns, void* status,
+                       int* result, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

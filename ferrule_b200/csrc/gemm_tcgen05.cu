@@ -62,7 +62,7 @@ struct GemmParams {
   int rows_cap;              // rows per source slot in the receive buffer
   float* peer_recv[8];       // receive buffer of every rank, in this rank's address space
   uint32_t* peer_flags[8];   // per-tile arrival counters of every rank
-  uint32_t* local_ctr;       // [0] = calls completed, [1] = CTAs finished this call
+  uint32_t* local_ctr;       // [0] = calls completed, [1] = CTAs finished this call, [2..] = consumed arrivals per tile
   const __nv_bfloat16* residual;  // optional, added after the reduction
   long long ldr;
   unsigned long long peer_wait_ns;
@@ -316,15 +316,23 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tmap_w,
     if (EPI == kEpiAllReduce) {
       // Second pass over this CTA's tiles: wait for all ranks' partials, sum in rank
       // order (identical on every rank), add the residual, write the result.
-      const uint32_t target = static_cast<uint32_t>(p.world) * (call + 1u);
+      uint32_t* seen = p.local_ctr + 2;   // arrivals already consumed, per tile (private to this rank)
+      volatile uint32_t* ar_ok = abort_flag + 1;
       for (int t = blockIdx.x; t < total; t += gridDim.x) {
         const int m = t / p.n_tiles, nt = t - m * p.n_tiles;
         const int row0 = m * NTOK;
         const int rows = min(NTOK, p.dense_rows - row0);
         const int n = nt * kTileN + ch_in_tile;
-        const bool arrived =
-            ok && flag_wait_ge(p.peer_flags[p.rank] + t, target, p.peer_wait_ns, p.status, 0x400 + t);
-        if (!arrived) { ok = false; }
+        if (epi_tid == 0) {
+          const uint32_t target = seen[t] + static_cast<uint32_t>(p.world);
+          const bool arrived =
+              ok && flag_wait_ge(p.peer_flags[p.rank] + t, target, p.peer_wait_ns, p.status, 0x400 + t);
+          seen[t] = target;
+          *ar_ok = arrived ? 1u : 0u;
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (*ar_ok == 0u) ok = false;
+        asm volatile("bar.sync 1, 128;" ::: "memory");
         if (ok && n < p.n_out) {
           const float* base = p.peer_recv[p.rank];
           for (int r = 0; r < rows; ++r) {

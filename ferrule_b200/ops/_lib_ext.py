@@ -23,13 +23,10 @@ def declare(lib) -> None:
         "fb_ipc_open": ([vp, C.POINTER(vp)], i),
         "fb_ipc_close": ([vp], i),
         "fb_ipc_free": ([vp], i),
-        "fb_enable_peer_access": ([i], i),
-        "fb_allreduce_oneshot": ([vp, ll, vp, ll, vp, ll, i, i, i, i, i, C.POINTER(vp),
-                                  C.POINTER(vp), vp, i, ull, vp, vp], i),
-        "fb_moe_reduce_allreduce": ([vp, i, i, vp, i, i, vp, ll, vp, ll, vp, ll, i, i, i, i, i,
-                                     C.POINTER(vp), C.POINTER(vp), vp, i, ull, vp, vp], i),
-        "fb_flag_wait_probe": ([vp, i, ull, vp, vp], i),
-        "fb_peer_barrier": ([C.POINTER(vp), vp, i, i, ull, vp, vp], i),
+        "fb_moe_reduce_allreduce": ([vp, i, i, vp, i, i, vp, ll, vp, ll, i, i, i, i, i, C.POINTER(vp),
+                                     C.POINTER(vp), vp, i, ull, vp, vp], i),
+        "fb_argmax_allgather": ([vp, vp, i, i, i, i, i, C.POINTER(vp), C.POINTER(vp), vp, ull, vp, vp], i),
+        "fb_flag_wait_probe": ([vp, i, ull, vp, vp, vp], i),
         # quant.cu
         "fb_quant_fp8_rows": ([vp, ll, vp, ll, vp, ll, i, i, i, vp], i),
         "fb_dequant_fp8_block": ([vp, vp, vp, i, i, i, vp], i),

@@ -1,0 +1,84 @@
+"""Symmetric peer memory: one device buffer per rank, mapped into every rank of the node.
+
+Buffers come from `cudaMalloc` inside the native library (not from the PyTorch caching
+allocator), their CUDA IPC handles are exchanged through the process group's store, and
+every rank opens every peer's handle, which yields NVLink peer pointers usable from kernels
+(plain loads/stores; no multicast objects are bound, so a rank that exits between steps
+cannot fault its peers).
+
+A `Channel` bundles what one fused collective call site needs: a double-buffered receive
+area (one slot per source rank), arrival counters, and private call/consumed counters.
+
+The reference has no counterpart (single GPU); this is the communication substrate the
+tensor/expert-parallel paths stand on.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import List, Optional
+
+import torch
+import torch.distributed as dist
+
+from ..ops._lib import check, get_lib
+
+
+class SymmetricBuffer:
+    def __init__(self, nbytes: int, rank: int, world: int, group=None):
+        lib = get_lib(True)
+        self.lib, self.rank, self.world, self.nbytes = lib, rank, world, nbytes
+        hb = lib.fb_ipc_handle_bytes()
+        handle = C.create_string_buffer(hb)
+        local = C.c_void_p()
+        check(lib.fb_ipc_alloc(C.byref(local), nbytes, handle), "fb_ipc_alloc")
+        self.local_ptr = local.value
+        handles: List[Optional[bytes]] = [None] * world
+        dist.all_gather_object(handles, bytes(handle.raw), group=group)
+        self.ptrs: List[int] = []
+        self._opened: List[int] = []
+        for r in range(world):
+            if r == rank:
+                self.ptrs.append(self.local_ptr)
+                continue
+            p = C.c_void_p()
+            buf = C.create_string_buffer(handles[r], hb)
+            check(lib.fb_ipc_open(buf, C.byref(p)), f"fb_ipc_open(rank {r})")
+            self.ptrs.append(p.value)
+            self._opened.append(p.value)
+        dist.barrier(group=group)
+
+    def ptr_array(self, offset: int = 0):
+        arr = (C.c_void_p * 8)()
+        for r in range(self.world):
+            arr[r] = self.ptrs[r] + offset
+        return arr
+
+    def close(self) -> None:
+        for p in self._opened:
+            self.lib.fb_ipc_close(C.c_void_p(p))
+        self._opened = []
+        if self.local_ptr:
+            self.lib.fb_ipc_free(C.c_void_p(self.local_ptr))
+            self.local_ptr = 0
+
+
+class Channel:
+    """Receive area + arrival flags for one call-site family.
+
+    payload_floats: floats per source slot (rows_cap * width).  n_flags: arrival counters.
+    """
+
+    def __init__(self, rank: int, world: int, device, payload_floats: int, n_flags: int, group=None,
+                 wait_ns: int = 3_000_000_000):
+        self.rank, self.world, self.wait_ns = rank, world, wait_ns
+        self.payload_floats, self.n_flags = payload_floats, n_flags
+        self.flag_bytes = ((n_flags * 4 + 255) // 256) * 256
+        recv_bytes = 2 * world * payload_floats * 4
+        self.buf = SymmetricBuffer(self.flag_bytes + recv_bytes, rank, world, group)
+        self.flags = self.buf.ptr_array(0)
+        self.recv = self.buf.ptr_array(self.flag_bytes)
+        # private: [calls, ctas_done, consumed[n_flags]]
+        self.ctr = torch.zeros(2 + n_flags, dtype=torch.int32, device=device)
+
+    def close(self) -> None:
+        self.buf.close()

@@ -1,0 +1,152 @@
+"""Tensor / expert parallel execution of one model replica over the GPUs of a node.
+
+Sharding: attention heads, dense/shared FFN inner dimension and the vocabulary are split
+across ranks; routed experts are split by expert id while activations stay replicated
+between the two collectives of a layer, so expert parallelism needs no token dispatch.
+Each layer therefore has two reductions of a [rows, hidden] tensor:
+
+  attention o_proj -> all-reduce (+ residual)   : fused into the tcgen05 GEMM epilogue
+  MoE / FFN output -> all-reduce (+ residual)   : fused into the route-reduce kernel (MoE) or
+                                                  the down-projection GEMM epilogue (dense)
+
+Decode-sized batches use the fused one-shot kernels over NVLink peer stores; larger batches
+(prefill) and `fused=False` use NCCL, which is also the baseline the fused path is measured
+against.  The greedy token of a vocabulary-sharded LM head is resolved by a (logit, id)
+all-gather between ranks.
+
+The reference is single-GPU (crates/ferrule-model/src/support/policies.rs:56-77 keeps an inert
+parallelism plan; docs/ROADMAP.md:34-41 lists distributed execution as future work).
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+
+from ..ops import kernels as K
+from ..ops._lib import check, get_lib, ptr, status_tensor, stream_ptr
+from .symm import Channel
+
+
+class TensorParallel:
+    def __init__(self, rank: int, world: int, device, fused: bool = True, fused_max_rows: int = 64,
+                 group=None, wait_ns: int = 3_000_000_000):
+        self.rank, self.world, self.device, self.group = rank, world, torch.device(device), group
+        self.fused = fused and self.device.type == "cuda"
+        self.fused_max_rows = fused_max_rows
+        self.wait_ns = wait_ns
+        self.gemm_ch: Optional[Channel] = None
+        self.moe_ch: Optional[Channel] = None
+        self.arg_ch: Optional[Channel] = None
+        self.hidden = 0
+        self.calls_fused = 0
+        self.calls_nccl = 0
+
+    # ------------------------------------------------------------------ setup
+    def attach(self, fwd) -> None:
+        """Allocate the channels for a CudaForward (hidden size and decode row capacity)."""
+        H = fwd.cfg.hidden
+        self.hidden = H
+        rows = self.fused_max_rows
+        self._tmp32 = torch.zeros(fwd.ws.max_rows, H, dtype=torch.float32, device=self.device)
+        self._pairs = torch.zeros(self.world, fwd.ws.max_logit_rows, 2, dtype=torch.float32, device=self.device)
+        if not self.fused:
+            return
+        n_tiles = (H + 127) // 128
+        self.gemm_ch = Channel(self.rank, self.world, self.device, rows * H, n_tiles * ((rows + 15) // 16),
+                               self.group, self.wait_ns)
+        self.moe_ch = Channel(self.rank, self.world, self.device, rows * H, rows, self.group, self.wait_ns)
+        self.arg_ch = Channel(self.rank, self.world, self.device, max(fwd.ws.max_logit_rows, 1) * 2, 1, self.group,
+                              self.wait_ns)
+
+    def close(self) -> None:
+        for ch in (self.gemm_ch, self.moe_ch, self.arg_ch):
+            if ch is not None:
+                ch.close()
+
+    def fill_gemm_args(self, a, rows: int, n_out: int, ntok: int) -> None:
+        ch = self.gemm_ch
+        a.rank, a.world, a.rows_cap, a.flag_capacity = self.rank, self.world, self.fused_max_rows, ch.n_flags
+        for r in range(self.world):
+            a.peer_recv[r] = ch.recv[r]
+            a.peer_flags[r] = ch.flags[r]
+        a.local_ctr = ch.ctr.data_ptr()
+        a.peer_wait_ns = self.wait_ns
+
+    # ------------------------------------------------------------------ fused collectives
+    def gemm_allreduce(self, x: torch.Tensor, w: torch.Tensor, residual: torch.Tensor, out: torch.Tensor,
+                       T: int) -> torch.Tensor:
+        """out = bf16(residual + sum over ranks of x @ w^T)."""
+        if self.fused and T <= self.fused_max_rows and w.shape[-2] == self.hidden:
+            K.gemm(x, w, out=out, epilogue=K.EPI_ALLREDUCE, comm=self, residual=residual, ntok=K.pick_ntok(T))
+            self.calls_fused += 1
+            return out
+        tmp = self._tmp32[:T]
+        K.gemm(x, w, out=tmp)
+        dist.all_reduce(tmp, group=self.group)
+        torch.add(tmp, residual, out=tmp)
+        out.copy_(tmp)
+        self.calls_nccl += 1
+        return out
+
+    def moe_reduce_allreduce(self, route_out: torch.Tensor, slots: int, topk: int, idx: torch.Tensor,
+                             e_lo: int, e_hi: int, residual: torch.Tensor, out: torch.Tensor, T: int) -> torch.Tensor:
+        H = self.hidden
+        if self.fused and T <= self.fused_max_rows:
+            ch = self.moe_ch
+            lib = get_lib(True)
+            check(lib.fb_moe_reduce_allreduce(route_out.data_ptr(), slots, topk, idx.data_ptr(), e_lo, e_hi,
+                                              residual.data_ptr(), residual.stride(0), out.data_ptr(),
+                                              out.stride(0), T, H, self.rank, self.world, self.fused_max_rows,
+                                              ch.recv, ch.flags, ch.ctr.data_ptr(), ch.n_flags, self.wait_ns,
+                                              status_tensor(self.device).data_ptr(), stream_ptr()),
+                  "fb_moe_reduce_allreduce")
+            self.calls_fused += 1
+            return out
+        tmp = self._tmp32[:T]
+        K.moe_reduce(route_out, slots, topk, idx, e_lo, e_hi, T, H, out=tmp)
+        dist.all_reduce(tmp, group=self.group)
+        torch.add(tmp, residual, out=tmp)
+        out.copy_(tmp)
+        self.calls_nccl += 1
+        return out
+
+    def argmax_across_vocab(self, ids: torch.Tensor, vals: torch.Tensor, vocab_lo: int, L: int) -> None:
+        """In place: local (id, logit) of a vocabulary shard -> global greedy token on every rank."""
+        if self.fused and self.arg_ch is not None:
+            ch = self.arg_ch
+            lib = get_lib(True)
+            check(lib.fb_argmax_allgather(ids.data_ptr(), vals.data_ptr(), vocab_lo, L, self.rank, self.world,
+                                          ch.payload_floats // 2, ch.recv, ch.flags, ch.ctr.data_ptr(),
+                                          self.wait_ns, status_tensor(self.device).data_ptr(), stream_ptr()),
+                  "fb_argmax_allgather")
+            return
+        pairs = self._pairs[:, :L]
+        mine = torch.stack([vals[:L], torch.where(ids[:L] < 0, -1.0, (ids[:L] + vocab_lo).float())], dim=-1)
+        self._gather_pairs(pairs, mine)
+        v, gid = pairs[..., 0], pairs[..., 1]
+        v = torch.where(gid < 0, torch.full_like(v, float("-inf")), v)
+        best = v.max(0).values
+        cand = torch.where((v == best) & (gid >= 0), gid, torch.full_like(gid, 3.0e38))
+        win = cand.min(0).values
+        ids[:L] = torch.where(win > 1.0e38, torch.full_like(win, -1.0), win).to(torch.int32)
+        vals[:L] = best
+
+    def _gather_pairs(self, pairs: torch.Tensor, mine: torch.Tensor) -> None:
+        bufs = [torch.empty_like(mine) for _ in range(self.world)]
+        dist.all_gather(bufs, mine.contiguous(), group=self.group)
+        for r, b in enumerate(bufs):
+            pairs[r].copy_(b)
+
+    # ------------------------------------------------------------------ reference path (any backend)
+    def allreduce_reference(self, t: torch.Tensor) -> torch.Tensor:
+        t = t.contiguous()
+        dist.all_reduce(t, group=self.group)
+        return t
+
+    def gather_vocab_reference(self, logits: torch.Tensor) -> torch.Tensor:
+        bufs = [torch.empty_like(logits) for _ in range(self.world)]
+        dist.all_gather(bufs, logits.contiguous(), group=self.group)
+        return torch.cat(bufs, dim=-1)

@@ -1,0 +1,24 @@
+"""Tensor-parallel path on 2 GPUs: fused collectives vs NCCL and TP model vs single GPU."""
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+
+pytestmark = [pytest.mark.gpu, pytest.mark.multigpu]
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_selftest_two_ranks():
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", PYTHONPATH=ROOT)
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
+           "--master-addr", "127.0.0.1", "--master-port", "29517", "-m", "ferrule_b200.parallel.selftest"]
+    p = subprocess.run(cmd, capture_output=True, text=True, timeout=600, cwd=ROOT, env=env)
+    lines = [l for l in p.stdout.splitlines() if l.startswith("{")]
+    assert lines, p.stdout[-2000:] + p.stderr[-4000:]
+    res = json.loads(lines[-1])
+    assert res["ok"], res
+    assert p.returncode == 0
+    assert res["fused_calls"] > 0
