@@ -24,6 +24,7 @@
 // (crates/ferrule-backend/native/cuda/implementations/portable/entrypoints.cu:1515-1612).
 #include "common.cuh"
 #include "ferrule_b200.h"
+#include "launch.cuh"
 
 namespace fb {
 
@@ -50,6 +51,8 @@ moe_reduce_allreduce_kernel(const __nv_bfloat16* __restrict__ route_out, int slo
                             __nv_bfloat16* __restrict__ out, long long ldo, int rows, int dim,
                             int rank, int world, int rows_cap, PeerPtrs peers, uint32_t* ctr,
                             uint32_t* seen, unsigned long long wait_ns, DeviceStatus* st) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int t = blockIdx.x;
   const uint32_t call = *reinterpret_cast<volatile uint32_t*>(ctr);
   const size_t slot_elems = static_cast<size_t>(rows_cap) * dim;
@@ -110,6 +113,8 @@ __global__ void __launch_bounds__(1024)
 argmax_allgather_kernel(int* __restrict__ ids, float* __restrict__ vals, int vocab_lo, int rows,
                         int rank, int world, int rows_cap, PeerPtrs peers, uint32_t* ctr,
                         uint32_t* seen, unsigned long long wait_ns, DeviceStatus* st) {
+  pdl_launch_dependents();
+  pdl_wait();
   const uint32_t call = *reinterpret_cast<volatile uint32_t*>(ctr);
   const size_t slot_elems = static_cast<size_t>(rows_cap) * 2;
   const size_t base = (static_cast<size_t>(call & 1u) * world) * slot_elems;
@@ -145,6 +150,8 @@ argmax_allgather_kernel(int* __restrict__ ids, float* __restrict__ vals, int voc
 
 __global__ void flag_wait_probe_kernel(const uint32_t* flag, uint32_t target, unsigned long long wait_ns,
                                        DeviceStatus* st, int* result) {
+  pdl_launch_dependents();
+  pdl_wait();
   if (threadIdx.x == 0 && blockIdx.x == 0) *result = flag_wait_ge(flag, target, wait_ns, st, 0x700) ? 1 : 0;
 }
 
@@ -200,7 +207,7 @@ extern "C" int fb_moe_reduce_allreduce(const void* route_out, int slots, int top
   const int rc = fill_peers(&p, peer_recv, peer_flags, world);
   if (rc != FB_OK) return rc;
   uint32_t* c = static_cast<uint32_t*>(ctr);
-  moe_reduce_allreduce_kernel<<<rows, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+  launch_pdl(moe_reduce_allreduce_kernel, dim3(rows), dim3(256), 0, static_cast<cudaStream_t>(stream), 
       static_cast<const __nv_bfloat16*>(route_out), slots, topk, topk_idx, e_lo, e_hi,
       static_cast<const __nv_bfloat16*>(residual), ldr, static_cast<__nv_bfloat16*>(out), ldo, rows, dim,
       rank, world, rows_cap, p, c, c + 2, wait_ns ? wait_ns : 3000000000ull,
@@ -216,7 +223,7 @@ extern "C" int fb_argmax_allgather(int* ids, float* vals, int vocab_lo, int rows
   const int rc = fill_peers(&p, peer_recv, peer_flags, world);
   if (rc != FB_OK) return rc;
   uint32_t* c = static_cast<uint32_t*>(ctr);
-  argmax_allgather_kernel<<<1, 1024, 0, static_cast<cudaStream_t>(stream)>>>(
+  launch_pdl(argmax_allgather_kernel, dim3(1), dim3(1024), 0, static_cast<cudaStream_t>(stream), 
       ids, vals, vocab_lo, rows, rank, world, rows_cap, p, c, c + 2, wait_ns ? wait_ns : 3000000000ull,
       static_cast<DeviceStatus*>(status));
   return cudaGetLastError() == cudaSuccess ? FB_OK : FB_ERR_LAUNCH;
@@ -224,7 +231,7 @@ extern "C" int fb_argmax_allgather(int* ids, float* vals, int vocab_lo, int rows
 
 extern "C" int fb_flag_wait_probe(const void* flag, int target, unsigned long long wait_ns, void* status,
                                   int* result, void* stream) {
-  flag_wait_probe_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(
+  launch_pdl(flag_wait_probe_kernel, dim3(1), dim3(32), 0, static_cast<cudaStream_t>(stream), 
       static_cast<const uint32_t*>(flag), static_cast<uint32_t>(target), wait_ns,
       static_cast<DeviceStatus*>(status), result);
   return cudaGetLastError() == cudaSuccess ? FB_OK : FB_ERR_LAUNCH;

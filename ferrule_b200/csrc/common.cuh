@@ -58,6 +58,18 @@ __device__ __forceinline__ uint32_t lane_id() {
 }
 
 // ---------------------------------------------------------------------------------
+// programmatic dependent launch: a kernel launched with the programmatic-serialization
+// attribute may start while its predecessor in the stream still runs.  `pdl_wait` blocks until
+// the predecessor grid has completed and its writes are visible; everything before it must touch
+// only memory the predecessor neither reads nor writes (barriers, TMEM, constant weights).
+// Without the launch attribute both instructions do nothing.
+// ---------------------------------------------------------------------------------
+__device__ __forceinline__ void pdl_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+// ---------------------------------------------------------------------------------
 // mbarrier
 // ---------------------------------------------------------------------------------
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
@@ -110,6 +122,82 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity,
   uint32_t spins = 0;
   while (true) {
     if (mbar_try_wait(bar, parity)) return true;
+    if ((++spins & 0xffu) == 0u) {
+      if (*abort_flag != 0u) return false;
+      if (globaltimer_ns() - t0 > kPipeWaitNs) {
+        *abort_flag = 1u;
+        report_status(st, kStatusMbarTimeout, where, parity, blockIdx.x);
+        return false;
+      }
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------
+// thread-block clusters / distributed shared memory
+// ---------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ uint32_t cluster_nctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(r));
+  return r;
+}
+// All threads of all CTAs of the cluster (hardware barrier, cannot wait on a missing peer:
+// CTAs of one cluster are co-scheduled).
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// shared::cta address of this CTA -> shared::cluster address of the same offset in CTA `rank`
+__device__ __forceinline__ uint32_t mapa_shared(uint32_t local_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void st_cluster_f32(uint32_t cluster_addr, float v) {
+  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(cluster_addr), "f"(v) : "memory");
+}
+__device__ __forceinline__ float ld_cluster_f32(uint32_t cluster_addr) {
+  float v;
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(cluster_addr) : "memory");
+  return v;
+}
+__device__ __forceinline__ float4 ld_cluster_f32x4(uint32_t cluster_addr) {
+  float4 v;
+  asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+               : "r"(cluster_addr)
+               : "memory");
+  return v;
+}
+__device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_bar_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar_addr)
+               : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n"
+      "selp.b32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity,
+                                                  volatile uint32_t* abort_flag, DeviceStatus* st,
+                                                  uint32_t where) {
+  const uint64_t t0 = globaltimer_ns();
+  uint32_t spins = 0;
+  while (true) {
+    if (mbar_try_wait_cluster(bar, parity)) return true;
     if ((++spins & 0xffu) == 0u) {
       if (*abort_flag != 0u) return false;
       if (globaltimer_ns() - t0 > kPipeWaitNs) {

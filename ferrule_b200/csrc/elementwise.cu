@@ -21,6 +21,7 @@
 // (crates/ferrule-backend/native/cuda/implementations/portable/entrypoints.cu).
 #include "common.cuh"
 #include "ferrule_b200.h"
+#include "launch.cuh"
 
 namespace fb {
 
@@ -30,6 +31,8 @@ namespace fb {
 __global__ void embedding_kernel(const int* __restrict__ ids, const __nv_bfloat16* __restrict__ table,
                                  __nv_bfloat16* __restrict__ out, int rows, int dim, int vocab,
                                  DeviceStatus* st) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int r = blockIdx.x;
   if (r >= rows) return;
   int id = ids[r];
@@ -62,6 +65,8 @@ add_rmsnorm_kernel(const __nv_bfloat16* __restrict__ x, long long ldx,
                    const __nv_bfloat16* __restrict__ weight, __nv_bfloat16* __restrict__ res_out,
                    long long ldr, __nv_bfloat16* __restrict__ norm_out, long long ldn, int rows,
                    int dim, float eps) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ float red[8];
   extern __shared__ float row[];  // dim floats
   const int r = blockIdx.x;
@@ -124,6 +129,8 @@ mla_prep_kernel(const __nv_bfloat16* __restrict__ q, long long ldq, int q_head_d
                 const int* __restrict__ positions, const long long* __restrict__ write_slot,
                 __nv_bfloat16* __restrict__ kv_pool, long long pool_rows,
                 __nv_bfloat16* __restrict__ q_out, long long ldq_out, int rows, DeviceStatus* st) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ float red[8];
   const int r = blockIdx.x;
   if (r >= rows) return;
@@ -178,16 +185,14 @@ mla_prep_kernel(const __nv_bfloat16* __restrict__ q, long long ldq, int q_head_d
 // ---------------------------------------------------------------------------------
 enum { kScoreSoftmax = 0, kScoreSigmoid = 1, kScoreSqrtSoftplus = 2 };
 
-__global__ void __launch_bounds__(128)
-router_topk_kernel(const float* __restrict__ logits, long long ldl, const float* __restrict__ bias,
-                   const long long* __restrict__ hash_table, const int* __restrict__ token_ids,
-                   int rows, int experts, int topk, int score_fn, int n_groups, int topk_groups,
-                   int normalize, float route_scale, int* __restrict__ out_idx,
-                   float* __restrict__ out_w) {
-  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-  const int lane = threadIdx.x & 31;
-  if (warp >= rows) return;
-  const float* lr = logits + warp * ldl;
+// One warp routes one token.  `lr` points at the token's `experts` logits (global or shared).
+__device__ __forceinline__ void route_one_token(const float* lr, int warp, int lane,
+                                                const float* __restrict__ bias,
+                                                const long long* __restrict__ hash_table,
+                                                const int* __restrict__ token_ids, int experts, int topk,
+                                                int score_fn, int n_groups, int topk_groups, int normalize,
+                                                float route_scale, int* __restrict__ out_idx,
+                                                float* __restrict__ out_w) {
   constexpr int kPer = 8;
   float score[kPer];   // the value weights are taken from
   float select[kPer];  // the value top-k is taken on (score + bias)
@@ -323,6 +328,21 @@ router_topk_kernel(const float* __restrict__ logits, long long ldl, const float*
   if (lane < topk) ow[lane] = (normalize ? mine / (wsum + 1e-20f) : mine) * route_scale;
 }
 
+__global__ void __launch_bounds__(128)
+router_topk_kernel(const float* __restrict__ logits, long long ldl, const float* __restrict__ bias,
+                   const long long* __restrict__ hash_table, const int* __restrict__ token_ids,
+                   int rows, int experts, int topk, int score_fn, int n_groups, int topk_groups,
+                   int normalize, float route_scale, int* __restrict__ out_idx,
+                   float* __restrict__ out_w) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (warp >= rows) return;
+  route_one_token(logits + warp * ldl, warp, lane, bias, hash_table, token_ids, experts, topk, score_fn,
+                  n_groups, topk_groups, normalize, route_scale, out_idx, out_w);
+}
+
 // ---------------------------------------------------------------------------------
 // MoE plan: single CTA (routes are at most tokens * topk; the kernel is latency-bound)
 //   topk_idx[route] in [0, experts) ; local experts are [e_lo, e_hi)
@@ -332,20 +352,41 @@ router_topk_kernel(const float* __restrict__ logits, long long ldl, const float*
 //     tile table for row tiles of `ntok` rows: tile_group (local expert id), row0, rows
 //     counts[local experts], meta = {num_tiles, num_rows}
 // ---------------------------------------------------------------------------------
-__global__ void __launch_bounds__(1024)
-moe_plan_kernel(const int* __restrict__ topk_idx, const float* __restrict__ topk_w, int routes,
-                int topk, int e_lo, int e_hi, int ntok, int dst_slots, int* __restrict__ src_token,
-                int* __restrict__ dst_row, float* __restrict__ row_scale,
-                int* __restrict__ tile_group, int* __restrict__ tile_row0,
-                int* __restrict__ tile_rows, int max_tiles, int* __restrict__ counts,
-                int* __restrict__ meta, DeviceStatus* st) {
+struct PlanOut {
+  int* src_token;
+  int* dst_row;
+  float* row_scale;
+  int* tile_group;
+  int* tile_row0;
+  int* tile_rows;
+  int max_tiles;
+  int* counts;
+  int* meta;
+};
+
+// Executed by one whole CTA (any block size that is a multiple of 32).
+__device__ __forceinline__ void moe_plan_body(const int* topk_idx, const float* topk_w, int routes,
+                                              int topk, int e_lo, int e_hi, int ntok, int dst_slots,
+                                              const PlanOut& o, DeviceStatus* st) {
+  int* const src_token = o.src_token;
+  int* const dst_row = o.dst_row;
+  float* const row_scale = o.row_scale;
+  int* const tile_group = o.tile_group;
+  int* const tile_row0 = o.tile_row0;
+  int* const tile_rows = o.tile_rows;
+  const int max_tiles = o.max_tiles;
+  int* const counts = o.counts;
+  int* const meta = o.meta;
   __shared__ int cnt[256];
   __shared__ int off[257];
+  __shared__ int s_idx[2048];   // decode-sized route lists are walked from shared memory
+  const bool staged = routes <= 2048;
   const int local = e_hi - e_lo;
   for (int i = threadIdx.x; i < 256; i += blockDim.x) cnt[i] = 0;
   __syncthreads();
   for (int r = threadIdx.x; r < routes; r += blockDim.x) {
     const int e = topk_idx[r];
+    if (staged) s_idx[r] = e;
     if (e >= e_lo && e < e_hi) atomicAdd(&cnt[e - e_lo], 1);
   }
   __syncthreads();
@@ -381,7 +422,7 @@ moe_plan_kernel(const int* __restrict__ topk_idx, const float* __restrict__ topk
     int base = off[e];
     for (int r0 = 0; r0 < routes; r0 += 32) {
       const int r = r0 + lane;
-      const bool hit = r < routes && topk_idx[r] == e + e_lo;
+      const bool hit = r < routes && (staged ? s_idx[r] : topk_idx[r]) == e + e_lo;
       const uint32_t mask = __ballot_sync(0xffffffffu, hit);
       if (hit) {
         const int p = base + __popc(mask & ((1u << lane) - 1u));
@@ -394,10 +435,77 @@ moe_plan_kernel(const int* __restrict__ topk_idx, const float* __restrict__ topk
   }
 }
 
+__global__ void __launch_bounds__(1024)
+moe_plan_kernel(const int* __restrict__ topk_idx, const float* __restrict__ topk_w, int routes,
+                int topk, int e_lo, int e_hi, int ntok, int dst_slots, PlanOut o, DeviceStatus* st) {
+  pdl_launch_dependents();
+  pdl_wait();
+  moe_plan_body(topk_idx, topk_w, routes, topk, e_lo, e_hi, ntok, dst_slots, o, st);
+}
+
+// ---------------------------------------------------------------------------------
+// Fused router for decode-sized batches: router logits (x . W_e, fp32 accumulate) + scoring +
+// top-k per token (one CTA per token), then the CTA that finishes last builds the MoE plan.
+// One launch instead of three (logit GEMM, top-k, plan).
+// ---------------------------------------------------------------------------------
+__global__ void __launch_bounds__(1024)
+router_plan_fused_kernel(const __nv_bfloat16* __restrict__ x, long long ldx,
+                         const __nv_bfloat16* __restrict__ w, int hidden,
+                         const float* __restrict__ bias, const long long* __restrict__ hash_table,
+                         const int* __restrict__ token_ids, int rows, int experts, int topk, int score_fn,
+                         int n_groups, int topk_groups, int normalize, float route_scale,
+                         int* __restrict__ out_idx, float* __restrict__ out_w, int e_lo, int e_hi, int ntok,
+                         int dst_slots, PlanOut o, unsigned int* done_ctr, DeviceStatus* st) {
+  pdl_launch_dependents();
+  pdl_wait();
+  extern __shared__ float xs[];            // hidden floats, then `experts` logits
+  float* logits = xs + hidden;
+  __shared__ int is_last;
+  const int t = blockIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+  for (int i = threadIdx.x * 8; i < hidden; i += blockDim.x * 8) {
+    const uint4 v = *reinterpret_cast<const uint4*>(x + t * ldx + i);
+    const __nv_bfloat16* vp = reinterpret_cast<const __nv_bfloat16*>(&v);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) xs[i + j] = __bfloat162float(vp[j]);
+  }
+  __syncthreads();
+  for (int e = warp; e < experts; e += nwarps) {
+    const __nv_bfloat16* wr = w + static_cast<size_t>(e) * hidden;
+    float acc = 0.f;
+    for (int i = lane * 8; i < hidden; i += 256) {
+      const uint4 v = *reinterpret_cast<const uint4*>(wr + i);
+      const __nv_bfloat16* vp = reinterpret_cast<const __nv_bfloat16*>(&v);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc = fmaf(__bfloat162float(vp[j]), xs[i + j], acc);
+    }
+    acc = warp_sum(acc);
+    if (lane == 0) logits[e] = acc;
+  }
+  __syncthreads();
+  if (warp == 0)
+    route_one_token(logits, t, lane, bias, hash_table, token_ids, experts, topk, score_fn, n_groups,
+                    topk_groups, normalize, route_scale, out_idx, out_w);
+  // last CTA to finish plans for everyone
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned int done = atomicAdd(done_ctr, 1u);
+    is_last = done == gridDim.x - 1;
+    if (is_last) *done_ctr = 0;
+  }
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  moe_plan_body(out_idx, out_w, rows * topk, topk, e_lo, e_hi, ntok, dst_slots, o, st);
+}
+
 __global__ void gather_rows_kernel(const __nv_bfloat16* __restrict__ x, long long ldx,
                                    const int* __restrict__ src_token, const int* __restrict__ meta,
                                    __nv_bfloat16* __restrict__ out, long long ldo, int cap_rows,
                                    int dim, int src_rows, DeviceStatus* st) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int r = blockIdx.x;
   const int valid = min(meta[1], cap_rows);
   if (r >= valid) return;
@@ -419,6 +527,8 @@ moe_reduce_kernel(const __nv_bfloat16* __restrict__ route_out, int slots, int to
                   const __nv_bfloat16* __restrict__ extra, long long lde,
                   const __nv_bfloat16* __restrict__ residual, long long ldr, void* __restrict__ out,
                   long long ldo, int out_fp32, int rows, int dim) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int t = blockIdx.x;
   if (t >= rows) return;
   for (int i = threadIdx.x * 8; i < dim; i += blockDim.x * 8) {
@@ -471,6 +581,8 @@ __device__ __forceinline__ bool better(float v, int i, float ov, int oi) {
 __global__ void __launch_bounds__(1024)
 argmax_kernel(const float* __restrict__ logits, long long ldl, int rows, int vocab,
               int* __restrict__ out_id, float* __restrict__ out_val) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ float sv[32];
   __shared__ int si[32];
   const int r = blockIdx.x;
@@ -505,10 +617,82 @@ argmax_kernel(const float* __restrict__ logits, long long ldl, int rows, int voc
   }
 }
 
+// Two-level argmax: grid (chunks, rows).  Every CTA scans one slice of the vocabulary and writes
+// its (value, id) candidate; the CTA that finishes last for a row reduces the candidates.
+__global__ void __launch_bounds__(256)
+argmax_chunked_kernel(const float* __restrict__ logits, long long ldl, int rows, int vocab, int chunk,
+                      float* __restrict__ part_val, int* __restrict__ part_id,
+                      unsigned int* __restrict__ row_ctr, int* __restrict__ out_id,
+                      float* __restrict__ out_val) {
+  pdl_launch_dependents();
+  pdl_wait();
+  __shared__ float sv[8];
+  __shared__ int si[8];
+  __shared__ int is_last;
+  const int c = blockIdx.x, r = blockIdx.y, chunks = gridDim.x;
+  const float* lr = logits + r * ldl;
+  const int lo = c * chunk, hi = min(vocab, lo + chunk);
+  float best = -INFINITY;
+  int bi = 0x7fffffff;
+  for (int i = lo + threadIdx.x * 4; i < hi; i += blockDim.x * 4) {
+    if (i + 3 < hi) {
+      const float4 v = *reinterpret_cast<const float4*>(lr + i);
+      const float vv[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        if (vv[j] == vv[j] && better(vv[j], i + j, best, bi)) { best = vv[j]; bi = i + j; }
+    } else {
+      for (int j = i; j < hi; ++j) {
+        const float v = lr[j];
+        if (v == v && better(v, j, best, bi)) { best = v; bi = j; }
+      }
+    }
+  }
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    if (better(ov, oi, best, bi)) { best = ov; bi = oi; }
+  }
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+  if (l == 0) { sv[w] = best; si[w] = bi; }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int k = 1; k < (blockDim.x >> 5); ++k)
+      if (better(sv[k], si[k], best, bi)) { best = sv[k]; bi = si[k]; }
+    part_val[r * chunks + c] = best;
+    part_id[r * chunks + c] = bi;
+    __threadfence();
+    const unsigned int done = atomicAdd(row_ctr + r, 1u);
+    is_last = done == static_cast<unsigned int>(chunks - 1);
+    if (is_last) row_ctr[r] = 0;
+  }
+  __syncthreads();
+  if (!is_last || w != 0) return;
+  __threadfence();
+  best = -INFINITY;
+  bi = 0x7fffffff;
+  for (int k = l; k < chunks; k += 32) {
+    const float v = part_val[r * chunks + k];
+    const int id = part_id[r * chunks + k];
+    if (better(v, id, best, bi)) { best = v; bi = id; }
+  }
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    if (better(ov, oi, best, bi)) { best = ov; bi = oi; }
+  }
+  if (l == 0) {
+    out_id[r] = bi == 0x7fffffff ? -1 : bi;
+    if (out_val) out_val[r] = best;
+  }
+}
+
 // top-k by k rounds of block argmax with a "already taken" threshold (k small, rows few)
 __global__ void __launch_bounds__(1024)
 topk_logits_kernel(const float* __restrict__ logits, long long ldl, int rows, int vocab, int k,
                    int* __restrict__ out_id, float* __restrict__ out_val) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ float sv[32];
   __shared__ int si[32];
   __shared__ float last_v;
@@ -563,6 +747,8 @@ topk_logits_kernel(const float* __restrict__ logits, long long ldl, int rows, in
 __global__ void copy_pages_kernel(__nv_bfloat16* pool, long long layer_stride, long long page_elems,
                                   const int* __restrict__ pairs, int n_pairs, int n_pages, int layers,
                                   DeviceStatus* st) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int pair = blockIdx.x, layer = blockIdx.y;
   if (pair >= n_pairs || layer >= layers) return;
   const int src = pairs[2 * pair], dst = pairs[2 * pair + 1];
@@ -586,7 +772,7 @@ extern "C" int fb_status_bytes(void) { return static_cast<int>(sizeof(DeviceStat
 extern "C" int fb_embedding(const int* ids, const void* table, void* out, int rows, int dim,
                             int vocab, void* status, void* stream) {
   if (rows <= 0 || dim % 8 != 0) return FB_ERR_SHAPE;
-  embedding_kernel<<<rows, 128, 0, static_cast<cudaStream_t>(stream)>>>(
+  launch_pdl(embedding_kernel, dim3(rows), dim3(128), 0, static_cast<cudaStream_t>(stream), 
       ids, static_cast<const __nv_bfloat16*>(table), static_cast<__nv_bfloat16*>(out), rows, dim,
       vocab, static_cast<DeviceStatus*>(status));
   return FB_CHECK_LAUNCH();
@@ -602,7 +788,7 @@ extern "C" int fb_add_rmsnorm(const void* x, long long ldx, const void* delta, l
     cudaFuncSetAttribute(add_rmsnorm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 65536);
     attr = true;
   }
-  add_rmsnorm_kernel<<<rows, 256, dim * sizeof(float), static_cast<cudaStream_t>(stream)>>>(
+  launch_pdl(add_rmsnorm_kernel, dim3(rows), dim3(256), dim * sizeof(float), static_cast<cudaStream_t>(stream), 
       static_cast<const __nv_bfloat16*>(x), ldx, static_cast<const __nv_bfloat16*>(delta), ldd,
       static_cast<const __nv_bfloat16*>(weight), static_cast<__nv_bfloat16*>(res_out), ldr,
       static_cast<__nv_bfloat16*>(norm_out), ldn, rows, dim, eps);
@@ -617,7 +803,7 @@ extern "C" int fb_mla_prep(const void* q, long long ldq, int q_head_dim, const v
                            long long pool_rows, void* q_out, long long ldq_out, int rows,
                            void* status, void* stream) {
   if (rows <= 0 || rope_dim % 2 != 0 || heads <= 0) return FB_ERR_SHAPE;
-  mla_prep_kernel<<<rows, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+  launch_pdl(mla_prep_kernel, dim3(rows), dim3(256), 0, static_cast<cudaStream_t>(stream), 
       static_cast<const __nv_bfloat16*>(q), ldq, q_head_dim,
       static_cast<const __nv_bfloat16*>(ckv), ldckv, heads, kv_lora, rope_dim, static_cast<const __nv_bfloat16*>(kv_norm_w), eps, cos_t, sin_t, max_pos, positions,
       write_slot, static_cast<__nv_bfloat16*>(kv_pool), pool_rows,
@@ -634,7 +820,7 @@ extern "C" int fb_router_topk(const float* logits, long long ldl, const float* b
     return FB_ERR_SHAPE;
   if (n_groups > 32 || (n_groups > 1 && experts % n_groups != 0)) return FB_ERR_SHAPE;
   const int blocks = (rows + 3) / 4;
-  router_topk_kernel<<<blocks, 128, 0, static_cast<cudaStream_t>(stream)>>>(
+  launch_pdl(router_topk_kernel, dim3(blocks), dim3(128), 0, static_cast<cudaStream_t>(stream), 
       logits, ldl, bias, hash_table, token_ids, rows, experts, topk, score_fn, n_groups,
       topk_groups, normalize, route_scale, out_idx, out_w);
   return FB_CHECK_LAUNCH();
@@ -645,9 +831,33 @@ extern "C" int fb_moe_plan(const int* topk_idx, const float* topk_w, int routes,
                            int* tile_group, int* tile_row0, int* tile_rows, int max_tiles,
                            int* counts, int* meta, void* status, void* stream) {
   if (routes <= 0 || topk <= 0 || e_hi <= e_lo || e_hi - e_lo > 256 || ntok <= 0) return FB_ERR_SHAPE;
-  moe_plan_kernel<<<1, 1024, 0, static_cast<cudaStream_t>(stream)>>>(
-      topk_idx, topk_w, routes, topk, e_lo, e_hi, ntok, dst_slots < topk ? topk : dst_slots, src_token, dst_row, row_scale, tile_group,
-      tile_row0, tile_rows, max_tiles, counts, meta, static_cast<DeviceStatus*>(status));
+  PlanOut o{src_token, dst_row, row_scale, tile_group, tile_row0, tile_rows, max_tiles, counts, meta};
+  launch_pdl(moe_plan_kernel, dim3(1), dim3(1024), 0, static_cast<cudaStream_t>(stream), 
+      topk_idx, topk_w, routes, topk, e_lo, e_hi, ntok, dst_slots < topk ? topk : dst_slots, o,
+      static_cast<DeviceStatus*>(status));
+  return FB_CHECK_LAUNCH();
+}
+
+extern "C" int fb_router_plan_fused(const void* x, long long ldx, const void* w, int hidden,
+                                    const float* bias, const long long* hash_table,
+                                    const int* token_ids, int rows, int experts, int topk, int score_fn,
+                                    int n_groups, int topk_groups, int normalize, float route_scale,
+                                    int* out_idx, float* out_w, int e_lo, int e_hi, int ntok, int dst_slots,
+                                    int* src_token, int* dst_row, float* row_scale, int* tile_group,
+                                    int* tile_row0, int* tile_rows, int max_tiles, int* counts, int* meta,
+                                    void* done_ctr, void* status, void* stream) {
+  if (rows <= 0 || experts <= 0 || experts > 256 || topk <= 0 || topk > 32 || topk > experts)
+    return FB_ERR_SHAPE;
+  if (hidden % 256 != 0 || hidden > 8192 || (ldx % 8) != 0) return FB_ERR_SHAPE;
+  if (n_groups > 32 || (n_groups > 1 && experts % n_groups != 0)) return FB_ERR_SHAPE;
+  if (e_hi <= e_lo || e_hi - e_lo > 256 || ntok <= 0 || !done_ctr) return FB_ERR_SHAPE;
+  PlanOut o{src_token, dst_row, row_scale, tile_group, tile_row0, tile_rows, max_tiles, counts, meta};
+  const size_t smem = static_cast<size_t>(hidden + experts) * sizeof(float);
+  launch_pdl(router_plan_fused_kernel, dim3(rows), dim3(experts > 128 ? 1024 : 512), smem, static_cast<cudaStream_t>(stream), 
+      static_cast<const __nv_bfloat16*>(x), ldx, static_cast<const __nv_bfloat16*>(w), hidden, bias,
+      hash_table, token_ids, rows, experts, topk, score_fn, n_groups, topk_groups, normalize, route_scale,
+      out_idx, out_w, e_lo, e_hi, ntok, dst_slots < topk ? topk : dst_slots, o,
+      static_cast<unsigned int*>(done_ctr), static_cast<DeviceStatus*>(status));
   return FB_CHECK_LAUNCH();
 }
 
@@ -655,7 +865,7 @@ extern "C" int fb_gather_rows(const void* x, long long ldx, const int* src_token
                               void* out, long long ldo, int cap_rows, int dim, int src_rows,
                               void* status, void* stream) {
   if (cap_rows <= 0 || dim % 8 != 0) return FB_ERR_SHAPE;
-  gather_rows_kernel<<<cap_rows, 128, 0, static_cast<cudaStream_t>(stream)>>>(
+  launch_pdl(gather_rows_kernel, dim3(cap_rows), dim3(128), 0, static_cast<cudaStream_t>(stream), 
       static_cast<const __nv_bfloat16*>(x), ldx, src_token, meta, static_cast<__nv_bfloat16*>(out),
       ldo, cap_rows, dim, src_rows, static_cast<DeviceStatus*>(status));
   return FB_CHECK_LAUNCH();
@@ -666,7 +876,7 @@ extern "C" int fb_moe_reduce(const void* route_out, int slots, int topk, const i
                              const void* residual, long long ldr, void* out, long long ldo,
                              int out_fp32, int rows, int dim, void* stream) {
   if (rows <= 0 || dim % 8 != 0 || slots < topk) return FB_ERR_SHAPE;
-  moe_reduce_kernel<<<rows, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+  launch_pdl(moe_reduce_kernel, dim3(rows), dim3(256), 0, static_cast<cudaStream_t>(stream), 
       static_cast<const __nv_bfloat16*>(route_out), slots, topk, topk_idx, e_lo, e_hi,
       static_cast<const __nv_bfloat16*>(extra), lde, static_cast<const __nv_bfloat16*>(residual),
       ldr, out, ldo, out_fp32, rows, dim);
@@ -676,15 +886,30 @@ extern "C" int fb_moe_reduce(const void* route_out, int slots, int topk, const i
 extern "C" int fb_argmax(const float* logits, long long ldl, int rows, int vocab, int* out_id,
                          float* out_val, void* stream) {
   if (rows <= 0 || vocab <= 0) return FB_ERR_SHAPE;
-  argmax_kernel<<<rows, 1024, 0, static_cast<cudaStream_t>(stream)>>>(logits, ldl, rows, vocab,
+  launch_pdl(argmax_kernel, dim3(rows), dim3(1024), 0, static_cast<cudaStream_t>(stream), logits, ldl, rows, vocab,
                                                                       out_id, out_val);
+  return FB_CHECK_LAUNCH();
+}
+
+// scratch: part_val [rows * chunks] floats, part_id [rows * chunks] ints, row_ctr [rows] zeroed once
+extern "C" int fb_argmax_chunked(const float* logits, long long ldl, int rows, int vocab, int chunks,
+                                 float* part_val, int* part_id, void* row_ctr, int* out_id,
+                                 float* out_val, void* stream) {
+  if (rows <= 0 || vocab <= 0 || chunks <= 0 || chunks > 1024 || !part_val || !part_id || !row_ctr)
+    return FB_ERR_SHAPE;
+  if ((ldl % 4) != 0 || (reinterpret_cast<uintptr_t>(logits) & 15)) return FB_ERR_ALIGN;
+  const int chunk = ((vocab + chunks - 1) / chunks + 3) / 4 * 4;
+  dim3 grid(chunks, rows);
+  launch_pdl(argmax_chunked_kernel, dim3(grid), dim3(256), 0, static_cast<cudaStream_t>(stream), 
+      logits, ldl, rows, vocab, chunk, part_val, part_id, static_cast<unsigned int*>(row_ctr), out_id,
+      out_val);
   return FB_CHECK_LAUNCH();
 }
 
 extern "C" int fb_topk_logits(const float* logits, long long ldl, int rows, int vocab, int k,
                               int* out_id, float* out_val, void* stream) {
   if (rows <= 0 || vocab <= 0 || k <= 0 || k > 64) return FB_ERR_SHAPE;
-  topk_logits_kernel<<<rows, 1024, 0, static_cast<cudaStream_t>(stream)>>>(logits, ldl, rows, vocab,
+  launch_pdl(topk_logits_kernel, dim3(rows), dim3(1024), 0, static_cast<cudaStream_t>(stream), logits, ldl, rows, vocab,
                                                                            k, out_id, out_val);
   return FB_CHECK_LAUNCH();
 }
@@ -695,7 +920,7 @@ extern "C" int fb_copy_pages(void* pool, long long layer_stride, long long page_
   if (n_pairs <= 0) return FB_OK;
   if (page_elems % 8 != 0 || layers <= 0) return FB_ERR_SHAPE;
   dim3 grid(n_pairs, layers);
-  copy_pages_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+  launch_pdl(copy_pages_kernel, dim3(grid), dim3(256), 0, static_cast<cudaStream_t>(stream), 
       static_cast<__nv_bfloat16*>(pool), layer_stride, page_elems, pairs, n_pairs, n_pages, layers,
       static_cast<DeviceStatus*>(status));
   return FB_CHECK_LAUNCH();

@@ -48,6 +48,7 @@ typedef struct FbGemmArgs {
   int max_tok_tiles;        // capacity of the tile table (grouped mode)
   int x_group_koff;         // batched mode (groups > 1, no tile table): X column offset per group
   int out_group_coff;       // batched mode: output column offset per group
+  int force_split;          // 0 = choose automatically; else split-K factor (1, 2, 4, 8)
   const int* tile_group;    // grouped mode: per row-tile expert id, first row, row count
   const int* tile_row0;
   const int* tile_rows;
@@ -66,6 +67,7 @@ typedef struct FbGemmArgs {
   long long ldr;
   unsigned long long peer_wait_ns;
   void* status;
+  void* trace;              // optional: 8 x uint64 globaltimer stamps written by CTA 0 (profiling)
 } FbGemmArgs;
 
 int fb_gemm_bf16(const FbGemmArgs* args, void* stream);
@@ -96,6 +98,7 @@ typedef struct FbAttnArgs {
   int splits;
   int split_tokens;         // multiple of 64
   float softmax_scale;
+  void* merge_ctr;          // optional: zeroed uint32 [ceil(rows/group_rows) * head blocks]; merges in-kernel
 } FbAttnArgs;
 
 int fb_mla_attention(const FbAttnArgs* args, void* stream);
@@ -120,6 +123,13 @@ int fb_moe_plan(const int* topk_idx, const float* topk_w, int routes, int topk, 
                 int ntok, int dst_slots, int* src_token, int* dst_row, float* row_scale, int* tile_group,
                 int* tile_row0, int* tile_rows, int max_tiles, int* counts, int* meta, void* status,
                 void* stream);
+int fb_router_plan_fused(const void* x, long long ldx, const void* w, int hidden, const float* bias,
+                         const long long* hash_table, const int* token_ids, int rows, int experts,
+                         int topk, int score_fn, int n_groups, int topk_groups, int normalize,
+                         float route_scale, int* out_idx, float* out_w, int e_lo, int e_hi, int ntok,
+                         int dst_slots, int* src_token, int* dst_row, float* row_scale, int* tile_group,
+                         int* tile_row0, int* tile_rows, int max_tiles, int* counts, int* meta,
+                         void* done_ctr, void* status, void* stream);
 int fb_gather_rows(const void* x, long long ldx, const int* src_token, const int* meta, void* out,
                    long long ldo, int cap_rows, int dim, int src_rows, void* status, void* stream);
 int fb_moe_reduce(const void* route_out, int slots, int topk, const int* topk_idx, int e_lo,
@@ -127,6 +137,9 @@ int fb_moe_reduce(const void* route_out, int slots, int topk, const int* topk_id
                   void* out, long long ldo, int out_fp32, int rows, int dim, void* stream);
 int fb_argmax(const float* logits, long long ldl, int rows, int vocab, int* out_id, float* out_val,
               void* stream);
+int fb_argmax_chunked(const float* logits, long long ldl, int rows, int vocab, int chunks,
+                      float* part_val, int* part_id, void* row_ctr, int* out_id, float* out_val,
+                      void* stream);
 int fb_topk_logits(const float* logits, long long ldl, int rows, int vocab, int k, int* out_id,
                    float* out_val, void* stream);
 int fb_copy_pages(void* pool, long long layer_stride, long long page_elems, const int* pairs,

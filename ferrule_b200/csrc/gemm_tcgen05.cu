@@ -24,6 +24,7 @@
 
 #include "common.cuh"
 #include "ferrule_b200.h"
+#include "launch.cuh"
 
 namespace fb {
 
@@ -45,6 +46,9 @@ struct GemmParams {
   int x_group_koff;   // batched: column offset of group g inside an X row = g * x_group_koff
   int out_group_coff; // batched: column offset of group g inside an output row
   int groups;
+  int stages;         // pipeline depth actually used (<= GemmCfg::kStages)
+  int force_split;    // > 0: use exactly this split-K factor (tests)
+  unsigned long long* trace;  // optional: CTA 0 writes globaltimer stamps of its pipeline milestones
   const int* tile_group;
   const int* tile_row0;
   const int* tile_rows;
@@ -116,23 +120,36 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_swapab_kernel(const __grid_constant__ CUtensorMap tmap_w,
                    const __grid_constant__ CUtensorMap tmap_x, const GemmParams p) {
   using Cfg = GemmCfg<NTOK, DUAL>;
+  pdl_launch_dependents();
+  const bool tracing = p.trace != nullptr && blockIdx.x == 0;
+  if (tracing && threadIdx.x == 0) p.trace[0] = globaltimer_ns();   // kernel entry
   extern __shared__ uint8_t smem_raw[];
   // 1024-byte alignment is required by the 128-byte swizzle atoms.
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::kStages * Cfg::kStageBytes);
+  const int nstages = p.stages;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + nstages * Cfg::kStageBytes);
   uint64_t* full_bar = bars;
-  uint64_t* empty_bar = bars + Cfg::kStages;
-  uint64_t* acc_full = bars + 2 * Cfg::kStages;
+  uint64_t* empty_bar = bars + nstages;
+  uint64_t* acc_full = bars + 2 * nstages;
   uint64_t* acc_empty = acc_full + 2;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  uint64_t* red_bar = acc_empty + 2;  // split-K: peers' partial tiles have landed in `red`
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(red_bar + 1);
   volatile uint32_t* abort_flag = tmem_slot + 1;
+  // split-K reduction area (leader CTA only): [peer - 1][accumulator column][128 lanes] fp32
+  float* red = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(bars) + 256);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  // Split-K: the S CTAs of a cluster share one output tile, each reducing a slice of K; the
+  // partial accumulators travel to the leader (cluster rank 0) through distributed shared memory.
+  const int S = static_cast<int>(cluster_nctarank());
+  const int crank = static_cast<int>(cluster_ctarank());
+  const int tile_first = blockIdx.x / S;
+  const int tile_stride = gridDim.x / S;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < Cfg::kStages; ++s) {
+    for (int s = 0; s < nstages; ++s) {
       mbar_init(&full_bar[s], 1);
       mbar_init(&empty_bar[s], 1);
     }
@@ -140,6 +157,7 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tmap_w,
       mbar_init(&acc_full[a], 1);
       mbar_init(&acc_empty[a], 4);
     }
+    mbar_init(red_bar, 128 * (S > 1 ? S - 1 : 1));
     *abort_flag = 0;
     fence_barrier_init();
     tma_prefetch_desc(&tmap_w);
@@ -152,16 +170,26 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tmap_w,
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
+  if (S > 1) cluster_sync_all();  // the leader's barrier is initialised before any peer arrives on it
+  if (tracing && threadIdx.x == 0) p.trace[1] = globaltimer_ns();   // prologue done (barriers, TMEM)
   const uint32_t tmem_base = *tmem_slot;
 
+  // Everything above touched only this CTA's barriers and TMEM.  From here on global memory that
+  // the preceding kernel may still be writing is read, so every thread waits for it - except the
+  // producer thread of a dense GEMM, which first requests the (constant) weight tiles.
+  const bool grouped_mode = p.tile_group != nullptr;
+  const bool is_producer = warp == 0 && lane == 0;
+  if (!is_producer || grouped_mode) pdl_wait();
   const int tiles_per_group = (p.dense_rows + NTOK - 1) / NTOK;
-  const int num_tok_tiles = p.tile_group ? min(*p.num_tok_tiles, p.max_tok_tiles)
+  const int num_tok_tiles = grouped_mode ? min(*p.num_tok_tiles, p.max_tok_tiles)
                                          : tiles_per_group * (p.batched ? p.groups : 1);
   const int total = num_tok_tiles * p.n_tiles;
   const int kblocks = (p.k + kBlockK - 1) / kBlockK;
+  const int kb_begin = static_cast<int>(static_cast<long long>(crank) * kblocks / S);
+  const int kb_end = static_cast<int>(static_cast<long long>(crank + 1) * kblocks / S);
 
   uint32_t call = 0;
-  if (EPI == kEpiAllReduce) call = *reinterpret_cast<volatile uint32_t*>(p.local_ctr);
+  if (EPI == kEpiAllReduce && !is_producer) call = *reinterpret_cast<volatile uint32_t*>(p.local_ctr);
 
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
@@ -170,33 +198,57 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tmap_w,
       uint32_t ph = 0;
       bool ok = true;
       long long issued = 0;
-      for (int t = blockIdx.x; t < total && ok; t += gridDim.x) {
+      // Weight tiles do not depend on the preceding kernel: request the first pipeline-full of
+      // them before waiting for it, so they stream while that kernel drains.
+      int pre = 0;
+      if (!grouped_mode) {
+        if (tile_first < total) {
+          const TileInfo ti = decode_tile<NTOK>(p, tile_first, tiles_per_group);
+          const int npre = min(nstages, kb_end - kb_begin);
+          for (pre = 0; pre < npre; ++pre) {
+            uint8_t* stage = smem + pre * Cfg::kStageBytes;
+            const int kb = kb_begin + pre;
+            mbar_arrive_expect_tx(&full_bar[pre], Cfg::kStageBytes);
+            tma_load_3d(stage, &tmap_w, &full_bar[pre], kb * kBlockK, ti.nt * kTileN, ti.g);
+            if (DUAL)
+              tma_load_3d(stage + Cfg::kWBytes, &tmap_w, &full_bar[pre], kb * kBlockK,
+                          p.dual_offset + ti.nt * kTileN, ti.g);
+          }
+        }
+        pdl_wait();
+      }
+      if (tracing) p.trace[2] = globaltimer_ns();                     // dependency wait passed
+      for (int t = tile_first; t < total && ok; t += tile_stride) {
         const TileInfo ti = decode_tile<NTOK>(p, t, tiles_per_group);
         const int g = ti.g, nt = ti.nt, row0 = ti.row0;
         const int xk0 = p.batched ? g * p.x_group_koff : 0;
-        for (int kb = 0; kb < kblocks; ++kb) {
-          ok = mbar_wait(&empty_bar[s], ph ^ 1u, abort_flag, p.status, 0x100);
-          if (!ok) break;
+        for (int kb = kb_begin; kb < kb_end; ++kb) {
           uint8_t* stage = smem + s * Cfg::kStageBytes;
-          mbar_arrive_expect_tx(&full_bar[s], Cfg::kStageBytes);
-          tma_load_3d(stage, &tmap_w, &full_bar[s], kb * kBlockK, nt * kTileN, g);
-          if (DUAL)
-            tma_load_3d(stage + Cfg::kWBytes, &tmap_w, &full_bar[s], kb * kBlockK,
-                        p.dual_offset + nt * kTileN, g);
+          if (t == tile_first && kb - kb_begin < pre) {
+            // barrier armed and weights requested above; only the activation tile is missing
+          } else {
+            ok = mbar_wait(&empty_bar[s], ph ^ 1u, abort_flag, p.status, 0x100);
+            if (!ok) break;
+            mbar_arrive_expect_tx(&full_bar[s], Cfg::kStageBytes);
+            tma_load_3d(stage, &tmap_w, &full_bar[s], kb * kBlockK, nt * kTileN, g);
+            if (DUAL)
+              tma_load_3d(stage + Cfg::kWBytes, &tmap_w, &full_bar[s], kb * kBlockK,
+                          p.dual_offset + nt * kTileN, g);
+          }
           tma_load_2d(stage + Cfg::kWBytes * (DUAL ? 2 : 1), &tmap_x, &full_bar[s],
                       xk0 + kb * kBlockK, row0);
           ++issued;
-          if (++s == Cfg::kStages) { s = 0; ph ^= 1u; }
+          if (++s == nstages) { s = 0; ph ^= 1u; }
         }
       }
       // Drain after an abort: copies this thread issued may still be in flight, and the
       // CTA may not exit under them.  Wait (bounded) for the full barrier of each of
-      // the last kStages issues to complete the phase it was armed for.
+      // the last `nstages` issues to complete the phase it was armed for.
       if (*abort_flag) {
-        const long long first = issued > Cfg::kStages ? issued - Cfg::kStages : 0;
+        const long long first = issued > nstages ? issued - nstages : 0;
         for (long long i = first; i < issued; ++i) {
-          const int si = static_cast<int>(i % Cfg::kStages);
-          const uint32_t pi = static_cast<uint32_t>((i / Cfg::kStages) & 1);
+          const int si = static_cast<int>(i % nstages);
+          const uint32_t pi = static_cast<uint32_t>((i / nstages) & 1);
           const uint64_t t0 = globaltimer_ns();
           while (!mbar_try_wait(&full_bar[si], pi) && globaltimer_ns() - t0 < 2000000ull) {
           }
@@ -212,14 +264,15 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tmap_w,
       int a = 0;
       uint32_t aph = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < total && ok; t += gridDim.x) {
+      for (int t = tile_first; t < total && ok; t += tile_stride) {
         ok = mbar_wait(&acc_empty[a], aph ^ 1u, abort_flag, p.status, 0x200);
         if (!ok) break;
         tc_fence_after();
         const uint32_t d0 = tmem_base + a * Cfg::kAccCols;
-        for (int kb = 0; kb < kblocks; ++kb) {
+        for (int kb = kb_begin; kb < kb_end; ++kb) {
           ok = mbar_wait(&full_bar[s], ph, abort_flag, p.status, 0x201);
           if (!ok) break;
+          if (tracing && kb == kb_begin) p.trace[3] = globaltimer_ns();  // first stage landed
           tc_fence_after();
           const uint32_t sw = smem_u32(smem + s * Cfg::kStageBytes);
           const uint32_t sx = sw + Cfg::kWBytes * (DUAL ? 2 : 1);
@@ -227,14 +280,15 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tmap_w,
           for (int kk = 0; kk < kBlockK / kUmmaK; ++kk) {
             const uint32_t koff = kk * kUmmaK * 2;
             const uint64_t db = umma_desc_k128(sx + koff);
-            const uint32_t acc = (kb | kk) ? 1u : 0u;
+            const uint32_t acc = (kb > kb_begin || kk) ? 1u : 0u;
             umma_bf16(d0, umma_desc_k128(sw + koff), db, idesc, acc);
             if (DUAL) umma_bf16(d0 + NTOK, umma_desc_k128(sw + Cfg::kWBytes + koff), db, idesc, acc);
           }
           umma_commit(&empty_bar[s]);
-          if (++s == Cfg::kStages) { s = 0; ph ^= 1u; }
+          if (++s == nstages) { s = 0; ph ^= 1u; }
         }
         if (ok) umma_commit(&acc_full[a]);
+        if (tracing) p.trace[4] = globaltimer_ns();                   // last MMA issued
         a ^= 1;
         if (a == 0) aph ^= 1u;
       }
@@ -244,10 +298,11 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tmap_w,
     const int q = warp & 3;  // TMEM lane quarter this warp may read
     const int ch_in_tile = q * 32 + lane;
     const int epi_tid = (warp - 2) * 32 + lane;
+    const bool leader = crank == 0;
     int a = 0;
     uint32_t aph = 0;
     bool ok = true;
-    for (int t = blockIdx.x; t < total && ok; t += gridDim.x) {
+    for (int t = tile_first; t < total && ok; t += tile_stride) {
       const TileInfo ti = decode_tile<NTOK>(p, t, tiles_per_group);
       const int row0 = ti.row0, rows = ti.rows;
       const int n = ti.nt * kTileN + ch_in_tile;
@@ -255,8 +310,41 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tmap_w,
       const long long ocol = (p.batched ? static_cast<long long>(ti.g) * p.out_group_coff : 0) + n;
       ok = mbar_wait(&acc_full[a], aph, abort_flag, p.status, 0x300);
       if (!ok) break;
+      if (tracing && epi_tid == 0) p.trace[5] = globaltimer_ns();     // accumulator complete
       tc_fence_after();
       const uint32_t tbase = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + a * Cfg::kAccCols;
+      if (S > 1 && !leader) {
+        // ---- split-K peer: ship the partial accumulator to the leader's shared memory ----
+        const uint32_t red_remote =
+            mapa_shared(smem_u32(red), 0) +
+            (static_cast<uint32_t>((crank - 1) * Cfg::kAccCols) * 128u + static_cast<uint32_t>(ch_in_tile)) * 4u;
+#pragma unroll 1
+        for (int c0 = 0; c0 < NTOK; c0 += 16) {
+          if (c0 >= rows) break;
+          uint32_t v[16];
+          tmem_ld16(tbase + c0, v);
+          uint32_t u[16];
+          if (DUAL) tmem_ld16(tbase + NTOK + c0, u);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            st_cluster_f32(red_remote + static_cast<uint32_t>(c0 + j) * 512u, __uint_as_float(v[j]));
+            if (DUAL)
+              st_cluster_f32(red_remote + static_cast<uint32_t>(NTOK + c0 + j) * 512u, __uint_as_float(u[j]));
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&acc_empty[a]);
+        mbar_arrive_remote(mapa_shared(smem_u32(red_bar), 0));
+        a ^= 1;
+        if (a == 0) aph ^= 1u;
+        continue;
+      }
+      if (S > 1) {
+        ok = mbar_wait_cluster(red_bar, 0, abort_flag, p.status, 0x301);
+        if (!ok) break;
+      }
 #pragma unroll 1
       for (int c0 = 0; c0 < NTOK; c0 += 16) {
         if (c0 >= rows) break;  // uniform across the CTA: nothing valid beyond `rows`
@@ -265,6 +353,18 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tmap_w,
         uint32_t u[16];
         if (DUAL) tmem_ld16(tbase + NTOK + c0, u);
         tmem_ld_wait();
+        if (S > 1) {
+          // fixed summation order: own slice, then peers by cluster rank
+          for (int pr = 1; pr < S; ++pr) {
+            const float* rp = red + (static_cast<size_t>(pr - 1) * Cfg::kAccCols) * 128 + ch_in_tile;
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              v[j] = __float_as_uint(__uint_as_float(v[j]) + rp[static_cast<size_t>(c0 + j) * 128]);
+              if (DUAL)
+                u[j] = __float_as_uint(__uint_as_float(u[j]) + rp[static_cast<size_t>(NTOK + c0 + j) * 128]);
+            }
+          }
+        }
         if (n_ok) {
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
@@ -313,12 +413,12 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tmap_w,
       a ^= 1;
       if (a == 0) aph ^= 1u;
     }
-    if (EPI == kEpiAllReduce) {
+    if (EPI == kEpiAllReduce && leader) {
       // Second pass over this CTA's tiles: wait for all ranks' partials, sum in rank
       // order (identical on every rank), add the residual, write the result.
       uint32_t* seen = p.local_ctr + 2;   // arrivals already consumed, per tile (private to this rank)
       volatile uint32_t* ar_ok = abort_flag + 1;
-      for (int t = blockIdx.x; t < total; t += gridDim.x) {
+      for (int t = tile_first; t < total; t += tile_stride) {
         const int m = t / p.n_tiles, nt = t - m * p.n_tiles;
         const int row0 = m * NTOK;
         const int rows = min(NTOK, p.dense_rows - row0);
@@ -354,6 +454,7 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tmap_w,
 
   tc_fence_before();
   __syncthreads();
+  if (tracing && threadIdx.x == 0) p.trace[6] = globaltimer_ns();   // epilogue done
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, Cfg::kTmemCols);
@@ -420,34 +521,74 @@ static int num_sms() {
   return g_num_sms;
 }
 
+constexpr int kSmemLimit = 227 * 1024;
+
+// Split-K factor: spread a GEMM with few output tiles over more SMs.  The S CTAs of a cluster
+// each take 1/S of the k-blocks of one tile; only used when every tile gets its own cluster.
+static int pick_split(int tiles, int kblocks, bool grouped, int acc_cols, int stage_bytes) {
+  if (grouped) return 1;
+  int best = 1;
+  for (int s = 2; s <= 4; s *= 2) {  // measured: 8-way costs more in the DSMEM reduction than it saves
+    if (tiles * s > num_sms()) break;
+    if (kblocks / s < 4) break;
+    const int red = (s - 1) * acc_cols * 128 * 4;
+    if (kSmemLimit - 2048 - red < 2 * stage_bytes) break;
+    best = s;
+  }
+  return best;
+}
+
 template <int NTOK, bool DUAL, int EPI>
-static int launch_cfg(const CUtensorMap& mw, const CUtensorMap& mx, const GemmParams& p,
-                      int max_tiles, cudaStream_t stream) {
+static int launch_cfg(const CUtensorMap& mw, const CUtensorMap& mx, GemmParams p, int max_tiles,
+                      bool grouped, cudaStream_t stream) {
   using Cfg = GemmCfg<NTOK, DUAL>;
   auto kern = gemm_swapab_kernel<NTOK, DUAL, EPI>;
   static bool attr_set = false;
   if (!attr_set) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             Cfg::kSmemBytes) != cudaSuccess)
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit) !=
+        cudaSuccess)
       return FB_ERR_LAUNCH;
     attr_set = true;
   }
-  int grid = max_tiles < num_sms() ? max_tiles : num_sms();
-  if (grid < 1) grid = 1;
-  kern<<<grid, kGemmThreads, Cfg::kSmemBytes, stream>>>(mw, mx, p);
+  const int kblocks = (p.k + kBlockK - 1) / kBlockK;
+  const int split = p.force_split > 0 ? p.force_split
+                                      : pick_split(max_tiles, kblocks, grouped, Cfg::kAccCols, Cfg::kStageBytes);
+  const int red_bytes = split > 1 ? (split - 1) * Cfg::kAccCols * 128 * 4 : 0;
+  int stages = (kSmemLimit - 2048 - red_bytes) / Cfg::kStageBytes;
+  if (stages > Cfg::kStages) stages = Cfg::kStages;
+  if (stages < 2 || (split > 1 && (max_tiles * split > num_sms() || kblocks < split))) return FB_ERR_SHAPE;
+  p.stages = stages;
+  const size_t smem = static_cast<size_t>(stages) * Cfg::kStageBytes + 1024 + 256 + red_bytes;
+  int clusters = max_tiles < num_sms() ? max_tiles : num_sms();
+  if (clusters < 1) clusters = 1;
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(clusters * split, 1, 1);
+  cfg.blockDim = dim3(kGemmThreads, 1, 1);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = split;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 2 : 1;
+  if (cudaLaunchKernelEx(&cfg, kern, mw, mx, p) != cudaSuccess) return FB_ERR_LAUNCH;
   return cudaGetLastError() == cudaSuccess ? FB_OK : FB_ERR_LAUNCH;
 }
 
 template <bool DUAL, int EPI>
 static int launch_ntok(int ntok, const CUtensorMap& mw, const CUtensorMap& mx, const GemmParams& p,
-                       int max_tiles, cudaStream_t stream) {
+                       int max_tiles, bool grouped, cudaStream_t stream) {
   switch (ntok) {
-    case 16: return launch_cfg<16, DUAL, EPI>(mw, mx, p, max_tiles, stream);
-    case 32: return launch_cfg<32, DUAL, EPI>(mw, mx, p, max_tiles, stream);
-    case 64: return launch_cfg<64, DUAL, EPI>(mw, mx, p, max_tiles, stream);
-    case 128: return launch_cfg<128, DUAL, EPI>(mw, mx, p, max_tiles, stream);
+    case 16: return launch_cfg<16, DUAL, EPI>(mw, mx, p, max_tiles, grouped, stream);
+    case 32: return launch_cfg<32, DUAL, EPI>(mw, mx, p, max_tiles, grouped, stream);
+    case 64: return launch_cfg<64, DUAL, EPI>(mw, mx, p, max_tiles, grouped, stream);
+    case 128: return launch_cfg<128, DUAL, EPI>(mw, mx, p, max_tiles, grouped, stream);
     case 256:
-      if constexpr (!DUAL) return launch_cfg<256, DUAL, EPI>(mw, mx, p, max_tiles, stream);
+      if constexpr (!DUAL) return launch_cfg<256, DUAL, EPI>(mw, mx, p, max_tiles, grouped, stream);
       return FB_ERR_SHAPE;
     default: return FB_ERR_SHAPE;
   }
@@ -492,6 +633,8 @@ extern "C" int fb_gemm_bf16(const FbGemmArgs* a, void* stream_) {
   p.x_group_koff = a->x_group_koff;
   p.out_group_coff = a->out_group_coff;
   p.groups = a->groups;
+  p.force_split = a->force_split;
+  p.trace = static_cast<unsigned long long*>(a->trace);
   p.max_tok_tiles = a->max_tok_tiles;
   p.tile_group = a->tile_group;
   p.tile_row0 = a->tile_row0;
@@ -527,10 +670,10 @@ extern "C" int fb_gemm_bf16(const FbGemmArgs* a, void* stream_) {
     p.residual = static_cast<const __nv_bfloat16*>(a->residual);
     p.ldr = a->ldr;
     p.peer_wait_ns = a->peer_wait_ns ? a->peer_wait_ns : 3000000000ull;
-    return launch_ntok<false, kEpiAllReduce>(ntok, mw, mx, p, max_tiles, stream);
+    return launch_ntok<false, kEpiAllReduce>(ntok, mw, mx, p, max_tiles, grouped, stream);
   }
-  if (dual) return launch_ntok<true, kEpiSwiGLU>(ntok, mw, mx, p, max_tiles, stream);
+  if (dual) return launch_ntok<true, kEpiSwiGLU>(ntok, mw, mx, p, max_tiles, grouped, stream);
   if (a->epilogue == kEpiScatter)
-    return launch_ntok<false, kEpiScatter>(ntok, mw, mx, p, max_tiles, stream);
-  return launch_ntok<false, kEpiStore>(ntok, mw, mx, p, max_tiles, stream);
+    return launch_ntok<false, kEpiScatter>(ntok, mw, mx, p, max_tiles, grouped, stream);
+  return launch_ntok<false, kEpiStore>(ntok, mw, mx, p, max_tiles, grouped, stream);
 }

@@ -9,8 +9,8 @@
 // memory, so one HBM read of a KV row serves every head.  QK^T and PV run on warp-level
 // bf16 MMA (m16n8k16): a 16-row tile is below the 64-row minimum of tcgen05, and the
 // kernel is bound by the KV stream, not by math.  Online softmax in the log2 domain,
-// optional per-head sink logit in the denominator, split-KV partials merged by a second
-// kernel.  Every page id and slot is range-checked; a bad one masks the row and sets the
+// optional per-head sink logit in the denominator, split-KV partials merged by whichever
+// CTA of a (query tile, head block) finishes last (or by a second kernel when no counter is given).  Every page id and slot is range-checked; a bad one masks the row and sets the
 // status word instead of faulting.
 //
 // Counterpart of the reference's explicit-selection sparse MLA attention and hybrid
@@ -19,6 +19,7 @@
 // its CPU sink-softmax reference (crates/ferrule-model/src/attention_backend.rs:47-160).
 #include "common.cuh"
 #include "ferrule_b200.h"
+#include "launch.cuh"
 
 namespace fb {
 
@@ -47,6 +48,8 @@ struct AttnParams {
   long long ldo;
   float* part_o;            // [rows, splits, heads, DL] (splits > 1)
   float* part_ml;           // [rows, splits, heads, 2]
+  unsigned int* merge_ctr;  // [q groups * head blocks] zeroed once: last split CTA merges in-kernel
+  int cluster_merge;        // splits form one thread-block cluster and merge through distributed smem
   DeviceStatus* status;
 };
 
@@ -89,13 +92,15 @@ struct AttnSmem {
   static constexpr int kQBytes = 16 * kRowPad * 2;
   static constexpr int kKvBytes = kKvTile * kRowPad * 2;
   static constexpr int kPBytes = 16 * kPPad * 2;
-  static constexpr int kRedBytes = 4 * 16 * 4 * 2;
+  static constexpr int kRedBytes = 4 * 16 * 4 * 2 + 32 * 4;   // smax, ssum, cluster-merge statistics
   static constexpr int kTotal = kQBytes + kKvBytes + kPBytes + kRedBytes + 64;
 };
 
 template <int DL, int DR>
 __global__ void __launch_bounds__(kAttnThreads)
 mla_attention_kernel(const AttnParams p) {
+  pdl_launch_dependents();
+  pdl_wait();
   using S = AttnSmem<DL, DR>;
   constexpr int D = S::D;
   constexpr int kRowPad = S::kRowPad;
@@ -302,6 +307,76 @@ mla_attention_kernel(const AttnParams p) {
   l_lo = ssum[g] + ssum[16 + g] + ssum[32 + g] + ssum[48 + g];
   l_hi = ssum[g + 8] + ssum[24 + g] + ssum[40 + g] + ssum[56 + g];
 
+  if (p.cluster_merge) {
+    // ---- split merge inside the cluster: every CTA parks its unnormalised partial and softmax
+    // statistics in its own shared memory, then merges one slice of the latent dims for all rows,
+    // reading the peers' partials through distributed shared memory.  No global scratch. ----
+    float* Osm = reinterpret_cast<float*>(smem_attn + S::kQBytes);          // [16][DL] over the dead KV tile
+    float* Msm = ssum + 64;                                                  // [16] m, [16] l (after smax/ssum)
+    __syncthreads();
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const int r = g + half * 8;
+      float* o = Osm + r * DL + warp * kDimsPerWarp + t4 * 2;
+#pragma unroll
+      for (int i = 0; i < kNT; ++i)
+        *reinterpret_cast<float2*>(o + i * 8) = make_float2(o_acc[i][half * 2], o_acc[i][half * 2 + 1]);
+      if (warp == 0 && t4 == 0) {
+        Msm[r] = ok ? (half ? m_hi : m_lo) : -INFINITY;
+        Msm[16 + r] = ok ? (half ? l_hi : l_lo) : 0.f;
+      }
+    }
+    cluster_sync_all();
+    const int CS = static_cast<int>(cluster_nctarank());
+    const int crank = static_cast<int>(cluster_ctarank());
+    const int slice = DL / CS;                       // latent dims merged by this CTA
+    const uint32_t osm_addr = smem_u32(Osm), msm_addr = smem_u32(Msm);
+    float* wsm = smax;                               // [16][CS] normalised split weights (CS <= 8)
+    if (tid < 16) {
+      const int r = tid;
+      const int h = hblock * Hb + r % Hb;
+      float mv[8], lv[8];
+      float M = -INFINITY;
+      for (int c = 0; c < CS; ++c) {
+        const uint32_t ra = mapa_shared(msm_addr, c);
+        mv[c] = ld_cluster_f32(ra + r * 4);
+        lv[c] = ld_cluster_f32(ra + (16 + r) * 4);
+        M = fmaxf(M, mv[c]);
+      }
+      float L = 0.f;
+      if (p.sink && h < p.heads) {
+        const float sk = p.sink[h] * 1.4426950408889634f;
+        M = fmaxf(M, sk);
+        L = exp2f(sk - M);
+      }
+      for (int c = 0; c < CS; ++c) {
+        const float w = (mv[c] == -INFINITY || lv[c] == 0.f) ? 0.f : exp2f(mv[c] - M);
+        mv[c] = w;
+        L += lv[c] * w;
+      }
+      const float inv = L > 0.f ? 1.f / L : 0.f;
+      for (int c = 0; c < CS; ++c) wsm[r * 8 + c] = mv[c] * inv;
+    }
+    __syncthreads();
+    const int vec_per_row = slice / 4;
+    for (int item = tid; item < 16 * vec_per_row; item += kAttnThreads) {
+      const int r = item / vec_per_row, d = crank * slice + (item - r * vec_per_row) * 4;
+      const int qr = qrow0 + r / Hb, h = hblock * Hb + r % Hb;
+      if (r / Hb >= G || qr >= p.rows || h >= p.heads) continue;
+      float acc[4] = {0.f, 0.f, 0.f, 0.f};
+      for (int c = 0; c < CS; ++c) {
+        const float w = wsm[r * 8 + c];
+        const float4 v = ld_cluster_f32x4(mapa_shared(osm_addr, c) + (r * DL + d) * 4);
+        acc[0] += v.x * w; acc[1] += v.y * w; acc[2] += v.z * w; acc[3] += v.w * w;
+      }
+      __nv_bfloat16* o = p.out + qr * p.ldo + static_cast<long long>(h) * DL + d;
+      *reinterpret_cast<uint32_t*>(o) = pack_bf16(acc[0], acc[1]);
+      *reinterpret_cast<uint32_t*>(o + 2) = pack_bf16(acc[2], acc[3]);
+    }
+    cluster_sync_all();   // peers may still be reading this CTA's shared memory
+    return;
+  }
+
   // ---- write ----
 #pragma unroll
   for (int half = 0; half < 2; ++half) {
@@ -336,6 +411,69 @@ mla_attention_kernel(const AttnParams p) {
       }
     }
   }
+  if (p.splits == 1 || p.merge_ctr == nullptr) return;
+
+  // ---- in-kernel merge: the CTA that finishes last for this (query group, head block) combines
+  // the split partials, so no second launch is needed ----
+  __shared__ int is_last;
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) {
+    unsigned int* c = p.merge_ctr + static_cast<size_t>(qgroup) * gridDim.z + hblock;
+    const unsigned int done = atomicAdd(c, 1u);
+    is_last = done == static_cast<unsigned int>(p.splits - 1);
+    if (is_last) *c = 0;
+  }
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  // per-row softmax statistics of all splits -> shared memory (weights w_s = 2^(m_s - M) / L)
+  float* wts = reinterpret_cast<float*>(smem_attn);        // [16][splits], the tiles are dead by now
+  for (int i = tid; i < 16 * p.splits; i += kAttnThreads) wts[i] = 0.f;
+  __syncthreads();
+  if (tid < 16) {
+    const int r = tid;
+    const int qr = qrow0 + r / Hb, h = hblock * Hb + r % Hb;
+    if (r / Hb < G && qr < p.rows && h < p.heads) {
+      float M = -INFINITY;
+      for (int s2 = 0; s2 < p.splits; ++s2)
+        M = fmaxf(M, p.part_ml[((static_cast<size_t>(qr) * p.splits + s2) * p.heads + h) * 2]);
+      float L = 0.f;
+      if (p.sink) {
+        const float sk = p.sink[h] * 1.4426950408889634f;
+        M = fmaxf(M, sk);
+        L = exp2f(sk - M);
+      }
+      for (int s2 = 0; s2 < p.splits; ++s2) {
+        const size_t idx = (static_cast<size_t>(qr) * p.splits + s2) * p.heads + h;
+        const float m = p.part_ml[idx * 2], l = p.part_ml[idx * 2 + 1];
+        const float w = (m == -INFINITY || l == 0.f) ? 0.f : exp2f(m - M);
+        wts[r * p.splits + s2] = w;
+        L += l * w;
+      }
+      const float inv = L > 0.f ? 1.f / L : 0.f;
+      for (int s2 = 0; s2 < p.splits; ++s2) wts[r * p.splits + s2] *= inv;
+    }
+  }
+  __syncthreads();
+  // every thread combines independent (row, 4-dim) items; the split loads are independent
+  constexpr int kVecPerRow = DL / 4;
+  for (int item = tid; item < 16 * kVecPerRow; item += kAttnThreads) {
+    const int r = item / kVecPerRow, d = (item - r * kVecPerRow) * 4;
+    const int qr = qrow0 + r / Hb, h = hblock * Hb + r % Hb;
+    if (r / Hb >= G || qr >= p.rows || h >= p.heads) continue;
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 4
+    for (int s2 = 0; s2 < p.splits; ++s2) {
+      const float w = wts[r * p.splits + s2];
+      const float4 v = *reinterpret_cast<const float4*>(
+          p.part_o + ((static_cast<size_t>(qr) * p.splits + s2) * p.heads + h) * DL + d);
+      acc[0] += v.x * w; acc[1] += v.y * w; acc[2] += v.z * w; acc[3] += v.w * w;
+    }
+    __nv_bfloat16* o = p.out + qr * p.ldo + static_cast<long long>(h) * DL + d;
+    *reinterpret_cast<uint32_t*>(o) = pack_bf16(acc[0], acc[1]);
+    *reinterpret_cast<uint32_t*>(o + 2) = pack_bf16(acc[2], acc[3]);
+  }
 }
 
 // merge split partials: grid (rows, heads), DL/4 threads each handling 4 dims
@@ -343,6 +481,8 @@ template <int DL>
 __global__ void mla_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                  const float* __restrict__ sink, __nv_bfloat16* __restrict__ out,
                                  long long ldo, int rows, int heads, int splits) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int r = blockIdx.x, h = blockIdx.y;
   if (r >= rows || h >= heads) return;
   float M = -INFINITY;
@@ -386,11 +526,29 @@ static int launch_attn(const AttnParams& p, cudaStream_t stream) {
   }
   const int Hb = 16 / p.group_rows;
   dim3 grid((p.rows + p.group_rows - 1) / p.group_rows, p.splits, (p.heads + Hb - 1) / Hb);
-  kern<<<grid, kAttnThreads, S::kTotal, stream>>>(p);
+  if (p.cluster_merge) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(kAttnThreads);
+    cfg.dynamicSmemBytes = S::kTotal;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = p.splits;
+    attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 2 : 1;
+    if (cudaLaunchKernelEx(&cfg, kern, p) != cudaSuccess) return FB_ERR_LAUNCH;
+    return cudaGetLastError() == cudaSuccess ? FB_OK : FB_ERR_LAUNCH;
+  }
+  launch_pdl(kern, dim3(grid), dim3(kAttnThreads), S::kTotal, stream, p);
   if (cudaGetLastError() != cudaSuccess) return FB_ERR_LAUNCH;
-  if (p.splits > 1) {
+  if (p.splits > 1 && p.merge_ctr == nullptr) {
     dim3 mg(p.rows, p.heads);
-    mla_merge_kernel<DL><<<mg, DL / 4, 0, stream>>>(p.part_o, p.part_ml, p.sink, p.out, p.ldo, p.rows,
+    launch_pdl(mla_merge_kernel<DL>, dim3(mg), dim3(DL / 4), 0, stream, p.part_o, p.part_ml, p.sink, p.out, p.ldo, p.rows,
                                                    p.heads, p.splits);
     if (cudaGetLastError() != cudaSuccess) return FB_ERR_LAUNCH;
   }
@@ -408,7 +566,10 @@ extern "C" int fb_mla_attention(const FbAttnArgs* a, void* stream_) {
       a->group_rows != 16)
     return FB_ERR_SHAPE;
   if (a->splits < 1 || a->split_tokens <= 0 || a->split_tokens % kKvTile != 0) return FB_ERR_SHAPE;
-  if (a->splits > 1 && (!a->part_o || !a->part_ml)) return FB_ERR_SHAPE;
+  // splits > 1 without scratch: the splits of a query tile form one cluster and merge on chip
+  const bool cluster_merge = a->splits > 1 && !a->part_o;
+  if (cluster_merge && a->splits != 2 && a->splits != 4 && a->splits != 8) return FB_ERR_SHAPE;
+  if (a->splits > 1 && !cluster_merge && !a->part_ml) return FB_ERR_SHAPE;
   if ((a->ldq % 8) != 0 || (a->ldo % 2) != 0) return FB_ERR_ALIGN;
   if ((reinterpret_cast<uintptr_t>(a->kv) & 15) || (reinterpret_cast<uintptr_t>(a->q) & 15)) return FB_ERR_ALIGN;
   AttnParams p{};
@@ -433,6 +594,8 @@ extern "C" int fb_mla_attention(const FbAttnArgs* a, void* stream_) {
   p.ldo = a->ldo;
   p.part_o = a->part_o;
   p.part_ml = a->part_ml;
+  p.merge_ctr = static_cast<unsigned int*>(a->merge_ctr);
+  p.cluster_merge = cluster_merge ? 1 : 0;
   p.status = static_cast<DeviceStatus*>(a->status);
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   if (a->kv_lora == 512 && a->rope_dim == 64) return launch_attn<512, 64>(p, stream);

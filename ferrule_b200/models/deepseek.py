@@ -251,8 +251,12 @@ class CudaWorkspace:
         from ..ops.kernels import AttnWorkspace, MoePlan
         self.attn_ws = AttnWorkspace(torch.zeros(decode_rows, attn_splits, hl, cfg.kv_lora_rank, **f32),
                                      torch.zeros(decode_rows, attn_splits, hl, 2, **f32), decode_rows,
-                                     attn_splits) if attn_splits > 1 else None
+                                     attn_splits,
+                                     torch.zeros(decode_rows * ((hl + 15) // 16), **i32)) if attn_splits > 1 else None
         self.has_moe = cfg.n_routed_experts > 0
+        self.router_ctr = torch.zeros(4, **i32)
+        from ..ops.kernels import ArgmaxScratch
+        self.argmax_scratch = ArgmaxScratch.allocate(max(max_logit_rows, 1), device)
         if self.has_moe:
             E, k = cfg.n_routed_experts, cfg.topk
             el = w.e_hi - w.e_lo
@@ -306,6 +310,8 @@ class CudaForward:
                                    cfg.rope_factor, cfg.rope_orig_max_pos, cfg.rope_beta_fast, cfg.rope_beta_slow)
         self.cos, self.sin = cos.to(dev).contiguous(), sin.to(dev).contiguous()
         self.launches = 0          # kernels launched by the last forward (for reporting)
+        self.fused_router_rows = 256
+        self.side_stream = torch.cuda.Stream(device=dev)      # shared experts run beside the routed path
 
     # -- sublayers -----------------------------------------------------------------------
     def _attention(self, lw: LayerWeights, layer: int, xn: torch.Tensor, b: DeviceBatch, T: int) -> torch.Tensor:
@@ -318,21 +324,20 @@ class CudaForward:
             qa, ckv = qkv[:, :cfg.q_lora_rank], qkv[:, cfg.q_lora_rank:]
             K.add_rmsnorm(qa, lw.q_norm, cfg.rms_eps, norm_out=ws.qn[:T])
             q = K.gemm(ws.qn[:T], lw.w_q_b, out=ws.q[:T])
-            self.launches += 2
         else:
             q, ckv = qkv[:, :hl * qhd], qkv[:, hl * qhd:]
         q_full = ws.q_full[:T]
         K.mla_prep(q, qhd, ckv, hl, lora, rope, lw.kv_norm, cfg.rms_eps, self.cos, self.sin,
                    b.positions, b.write_slot, self.pool.layer(layer), q_full.view(T, -1))
         K.gemm(q, lw.w_uk_t, out=q_full.view(T, -1), x_group_koff=qhd, out_group_coff=lora + rope, k=nope)
-        use_split = ws.attn_ws is not None and T <= ws.decode_rows
+        use_split = ws.attn_splits > 1 and T <= ws.decode_rows
+        cluster = ws.attn_splits in (2, 4, 8)       # splits merge through distributed shared memory
         K.mla_attention(q_full, self.pool.layer(layer), b.block_table, b.row_seq, b.row_pos,
                         self.pool.page_size, lora, rope, cfg.softmax_scale, ws.o_lat[:T],
                         splits=ws.attn_splits if use_split else 1,
                         split_tokens=self.split_tokens if use_split else (1 << 30) // 64 * 64,
-                        ws=ws.attn_ws if use_split else None, sink=lw.attn_sink)
+                        ws=ws.attn_ws if (use_split and not cluster) else None, sink=lw.attn_sink)
         K.gemm(ws.o_lat[:T].view(T, -1), lw.w_uv, out=ws.attn_out[:T], x_group_koff=lora, out_group_coff=vd)
-        self.launches += 5 + (1 if use_split else 0)
         return ws.attn_out[:T]
 
     def _moe_ntok(self, T: int) -> int:
@@ -344,13 +349,33 @@ class CudaForward:
         """Router + local routed experts + shared experts -> ws.route_out filled for this rank."""
         K, cfg, ws = self.K, self.cfg, self.ws
         k, H = cfg.topk, cfg.hidden
-        K.gemm(xn, lw.router_w, out=ws.router_logits[:T])
         idx, wts = ws.topk_idx[:T], ws.topk_w[:T]
-        K.router_topk(ws.router_logits[:T], k, cfg.score_fn, bias=lw.router_bias, n_groups=cfg.n_groups,
-                      topk_groups=cfg.topk_groups, normalize=cfg.norm_topk_prob, route_scale=cfg.route_scale,
-                      hash_table=lw.hash_table, token_ids=b.token_ids, out_idx=idx, out_w=wts)
         plan = ws.plans[self._moe_ntok(T)]
-        K.moe_plan(idx, wts, plan, self.w.e_lo, self.w.e_hi, dst_slots=ws.slots)
+        side = None
+        if lw.w13 is not None:
+            # The shared experts only need the normalised activations: fork them onto a second stream
+            # (a parallel branch when captured in a graph) so they fill the SMs that the latency-bound
+            # routing / planning kernels leave idle, and join before the reduction.
+            side = self.side_stream
+            main = torch.cuda.current_stream()
+            side.wait_stream(main)
+            with torch.cuda.stream(side):
+                inter = lw.w13.shape[1] // 2
+                mid = ws.ffn_mid[:T, :inter]
+                K.gemm(xn, lw.w13, out=mid, epilogue=K.EPI_SWIGLU, act_limit=cfg.swiglu_limit)
+                K.gemm(mid, lw.w2, out=ws.route_out[:T][:, k])
+        if T <= self.fused_router_rows and H % 256 == 0:
+            K.router_plan_fused(xn, lw.router_w, k, cfg.score_fn, plan, self.w.e_lo, self.w.e_hi, idx, wts,
+                                ws.router_ctr, bias=lw.router_bias, n_groups=cfg.n_groups,
+                                topk_groups=cfg.topk_groups, normalize=cfg.norm_topk_prob,
+                                route_scale=cfg.route_scale, hash_table=lw.hash_table, token_ids=b.token_ids,
+                                dst_slots=ws.slots)
+        else:
+            K.gemm(xn, lw.router_w, out=ws.router_logits[:T])
+            K.router_topk(ws.router_logits[:T], k, cfg.score_fn, bias=lw.router_bias, n_groups=cfg.n_groups,
+                          topk_groups=cfg.topk_groups, normalize=cfg.norm_topk_prob, route_scale=cfg.route_scale,
+                          hash_table=lw.hash_table, token_ids=b.token_ids, out_idx=idx, out_w=wts)
+            K.moe_plan(idx, wts, plan, self.w.e_lo, self.w.e_hi, dst_slots=ws.slots)
         K.gather_rows(xn, plan, ws.xg, cap_rows=T * k)
         K.gemm(ws.xg[:T * k], lw.e_w13, out=ws.hmid[:T * k], epilogue=K.EPI_SWIGLU, plan=plan,
                act_limit=cfg.swiglu_limit)
@@ -358,13 +383,8 @@ class CudaForward:
         # route r = t*k + s is written to row t*slots + s (the plan kernel emits that row index)
         K.gemm(ws.hmid[:T * k], lw.e_w2, out=route_out.view(T * ws.slots, H), epilogue=K.EPI_SCATTER,
                plan=plan, scatter_rows=T * ws.slots)
-        self.launches += 6
-        if lw.w13 is not None:
-            inter = lw.w13.shape[1] // 2
-            mid = ws.ffn_mid[:T, :inter]
-            K.gemm(xn, lw.w13, out=mid, epilogue=K.EPI_SWIGLU, act_limit=cfg.swiglu_limit)
-            K.gemm(mid, lw.w2, out=route_out[:, k])
-            self.launches += 2
+        if side is not None:
+            torch.cuda.current_stream().wait_stream(side)
         return idx
 
     def layer(self, lw: LayerWeights, layer: int, h_in: torch.Tensor, h_out: torch.Tensor, b: DeviceBatch,
@@ -378,12 +398,10 @@ class CudaForward:
             K.gemm(a, lw.w_o, out=ws.delta[:T])
             K.add_rmsnorm(h_in, lw.ffn_norm, cfg.rms_eps, delta=ws.delta[:T], res_out=h_out, norm_out=xn)
             h_mid = h_out
-            self.launches += 3
         else:
             tp.gemm_allreduce(a, lw.w_o, residual=h_in, out=h_out, T=T)
             K.add_rmsnorm(h_out, lw.ffn_norm, cfg.rms_eps, norm_out=xn)
             h_mid = h_out
-            self.launches += 3
         if lw.is_moe:
             idx = self._moe_local(lw, xn, b, T)
             # slot `topk` holds the shared-expert row (zeros when the model has none)
@@ -393,7 +411,6 @@ class CudaForward:
             else:
                 tp.moe_reduce_allreduce(ws.route_out[:T].view(T * ws.slots, cfg.hidden), ws.slots, cfg.topk,
                                         idx, self.w.e_lo, self.w.e_hi, residual=h_mid, out=h_in, T=T)
-            self.launches += 1
             return h_in            # the layer's result lands back in the input buffer
         inter = lw.w13.shape[1] // 2
         mid = ws.ffn_mid[:T, :inter]
@@ -402,10 +419,8 @@ class CudaForward:
             K.gemm(mid, lw.w2, out=ws.delta[:T])
             # residual add is folded into the next consumer through a plain add+norm without a norm output
             K.add_rmsnorm(h_mid, None, cfg.rms_eps, delta=ws.delta[:T], res_out=h_in, want_norm=False)
-            self.launches += 3
         else:
             tp.gemm_allreduce(mid, lw.w2, residual=h_mid, out=h_in, T=T)
-            self.launches += 2
         return h_in
 
     # -- whole model ---------------------------------------------------------------------
@@ -413,7 +428,6 @@ class CudaForward:
         K, ws = self.K, self.ws
         h, other = ws.h[0][:T], ws.h[1][:T]
         K.embedding(b.token_ids[:T], self.w.embed, out=h)
-        self.launches += 1
         for i, lw in enumerate(self.w.layers):
             h = self.layer(lw, i, h, other, b, T)
         return h
@@ -427,23 +441,22 @@ class CudaForward:
         K.add_rmsnorm(hl, final_norm, cfg.rms_eps, norm_out=ws.hn_last[:L])
         logits = ws.logits[:L]
         K.gemm(ws.hn_last[:L], self.w.lm_head, out=logits)
-        K.argmax(logits, out_id=ws.next_id[:L], out_val=ws.next_val[:L])
-        self.launches += 4
+        K.argmax_chunked(logits, ws.argmax_scratch, ws.next_id[:L], ws.next_val[:L])
         if tp is not None:
             tp.argmax_across_vocab(ws.next_id[:L], ws.next_val[:L], self.w.vocab_lo, L)
-            self.launches += 1
         return ws.next_id[:L], ws.next_val[:L], (logits if want_logits else None)
 
     def forward(self, b: DeviceBatch, want_logits: bool = False):
         """Runs the batch; returns (next_id [n_logit] int32, next_val, logits or None)."""
         T = b.token_ids.shape[0]
         assert T <= self.ws.max_rows and b.n_logit <= self.ws.max_logit_rows
-        self.launches = 0
+        from ..ops import _lib
+        start = _lib.LAUNCHES[0]
         h = self.hidden_states(b, T)
         self.last_hidden = h
-        if b.n_logit == 0:
-            return None, None, None
-        return self.head(h, b, self.w.final_norm, want_logits)
+        out = (None, None, None) if b.n_logit == 0 else self.head(h, b, self.w.final_norm, want_logits)
+        self.launches = _lib.LAUNCHES[0] - start
+        return out
 
     def mtp_forward(self, stage: int, h_prev: torch.Tensor, b: DeviceBatch):
         """MTP stage over rows carrying the next token ids; h_prev: main hidden states of those rows."""
@@ -459,7 +472,6 @@ class CudaForward:
         # h_prev (usually ws.h[0]) is consumed by now, so the projection may overwrite it
         h0 = ws.h[0][:T]
         K.gemm(x, m.eh_proj, out=h0)
-        self.launches = 4
         h = self.layer(m.layer, cfg.n_layers + stage, h0, ws.h[1][:T], b, T)
         self.last_hidden = h
         return self.head(h, b, m.final_norm)

@@ -42,14 +42,14 @@ class GemmArgs(C.Structure):
         ("n_out", C.c_int), ("k", C.c_int), ("groups", C.c_int), ("w_rows_per_group", C.c_int),
         ("x_rows", C.c_int), ("ntok", C.c_int), ("epilogue", C.c_int), ("dual_offset", C.c_int),
         ("out_fp32", C.c_int), ("max_tok_tiles", C.c_int), ("x_group_koff", C.c_int),
-        ("out_group_coff", C.c_int),
+        ("out_group_coff", C.c_int), ("force_split", C.c_int),
         ("tile_group", C.c_void_p), ("tile_row0", C.c_void_p), ("tile_rows", C.c_void_p),
         ("num_tok_tiles", C.c_void_p), ("dst_row", C.c_void_p), ("row_scale", C.c_void_p),
         ("act_limit", C.c_float), ("rank", C.c_int), ("world", C.c_int), ("rows_cap", C.c_int),
         ("flag_capacity", C.c_int),
         ("peer_recv", C.c_void_p * 8), ("peer_flags", C.c_void_p * 8),
         ("local_ctr", C.c_void_p), ("residual", C.c_void_p), ("ldr", C.c_longlong),
-        ("peer_wait_ns", C.c_ulonglong), ("status", C.c_void_p),
+        ("peer_wait_ns", C.c_ulonglong), ("status", C.c_void_p), ("trace", C.c_void_p),
     ]
 
 
@@ -63,7 +63,7 @@ class AttnArgs(C.Structure):
         ("rows", C.c_int), ("heads", C.c_int), ("kv_lora", C.c_int), ("rope_dim", C.c_int),
         ("num_seqs", C.c_int), ("max_blocks", C.c_int), ("page_size", C.c_int),
         ("group_rows", C.c_int), ("splits", C.c_int), ("split_tokens", C.c_int),
-        ("softmax_scale", C.c_float),
+        ("softmax_scale", C.c_float), ("merge_ctr", C.c_void_p),
     ]
 
 
@@ -135,9 +135,13 @@ def native_available() -> bool:
     return torch.cuda.is_available() and get_lib(required=False) is not None
 
 
+LAUNCHES = [0]      # native kernel-launching calls that returned FB_OK (one launch each)
+
+
 def check(rc: int, what: str) -> None:
     if rc != FB_OK:
         raise NativeLibraryError(f"{what}: {_ERR_NAMES.get(rc, rc)}")
+    LAUNCHES[0] += 1
 
 
 def stream_ptr() -> int:

@@ -71,7 +71,8 @@ def gemm(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None, *
          dual_offset: int = 0, plan: Optional[MoePlan] = None, scatter_rows: Optional[int] = None,
          use_row_scale: bool = True, act_limit: float = 0.0, ntok: Optional[int] = None,
          x_group_koff: int = 0, out_group_coff: int = 0, k: Optional[int] = None,
-         comm=None, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+         comm=None, residual: Optional[torch.Tensor] = None, split_k: int = 0,
+         trace: Optional[torch.Tensor] = None) -> torch.Tensor:
     """out = x @ w^T on the tcgen05 path.
 
     x [rows, K] bf16 (row stride arbitrary multiple of 8), w [N, K] or [groups, N, K] bf16.
@@ -107,6 +108,8 @@ def gemm(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None, *
     a.out_fp32 = 1 if out.dtype == torch.float32 else 0
     a.x_group_koff, a.out_group_coff = x_group_koff, out_group_coff
     a.act_limit = act_limit
+    a.force_split = split_k
+    a.trace = ptr(trace)
     if plan is not None:
         a.max_tok_tiles = plan.max_tiles
         a.tile_group, a.tile_row0, a.tile_rows = (plan.tile_group.data_ptr(), plan.tile_row0.data_ptr(),
@@ -232,6 +235,54 @@ def argmax(logits: torch.Tensor, out_id: Optional[torch.Tensor] = None,
     return out_id
 
 
+@dataclass
+class ArgmaxScratch:
+    chunks: int
+    part_val: torch.Tensor
+    part_id: torch.Tensor
+    row_ctr: torch.Tensor
+
+    @staticmethod
+    def allocate(max_rows: int, device, chunks: int = 64) -> "ArgmaxScratch":
+        return ArgmaxScratch(chunks, torch.zeros(max_rows * chunks, dtype=torch.float32, device=device),
+                             torch.zeros(max_rows * chunks, dtype=torch.int32, device=device),
+                             torch.zeros(max_rows, dtype=torch.int32, device=device))
+
+
+def argmax_chunked(logits: torch.Tensor, scratch: ArgmaxScratch, out_id: torch.Tensor,
+                   out_val: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Greedy token with the vocabulary scan spread over rows x chunks CTAs (one launch)."""
+    lib = get_lib(True)
+    rows, vocab = logits.shape
+    assert rows * scratch.chunks <= scratch.part_val.numel()
+    check(lib.fb_argmax_chunked(logits.data_ptr(), logits.stride(0), rows, vocab, scratch.chunks,
+                                scratch.part_val.data_ptr(), scratch.part_id.data_ptr(),
+                                scratch.row_ctr.data_ptr(), out_id.data_ptr(), ptr(out_val), stream_ptr()),
+          "fb_argmax_chunked")
+    return out_id
+
+
+def router_plan_fused(x: torch.Tensor, w: torch.Tensor, topk: int, score_fn: int, plan: "MoePlan", e_lo: int,
+                      e_hi: int, out_idx: torch.Tensor, out_w: torch.Tensor, done_ctr: torch.Tensor, *,
+                      bias: Optional[torch.Tensor] = None, n_groups: int = 1, topk_groups: int = 1,
+                      normalize: bool = False, route_scale: float = 1.0,
+                      hash_table: Optional[torch.Tensor] = None, token_ids: Optional[torch.Tensor] = None,
+                      dst_slots: int = 0) -> None:
+    """Router logits + scoring + top-k + MoE plan in one launch (one CTA per token)."""
+    lib = get_lib(True)
+    rows, hidden = x.shape
+    experts = w.shape[0]
+    assert rows * topk <= plan.cap_rows and w.is_contiguous()
+    check(lib.fb_router_plan_fused(x.data_ptr(), x.stride(0), w.data_ptr(), hidden, ptr(bias), ptr(hash_table),
+                                   ptr(token_ids), rows, experts, topk, score_fn, n_groups, topk_groups,
+                                   1 if normalize else 0, route_scale, out_idx.data_ptr(), out_w.data_ptr(),
+                                   e_lo, e_hi, plan.ntok, dst_slots, plan.src_token.data_ptr(),
+                                   plan.dst_row.data_ptr(), plan.row_scale.data_ptr(), plan.tile_group.data_ptr(),
+                                   plan.tile_row0.data_ptr(), plan.tile_rows.data_ptr(), plan.max_tiles,
+                                   plan.counts.data_ptr(), plan.meta.data_ptr(), done_ctr.data_ptr(),
+                                   status_tensor(x.device).data_ptr(), stream_ptr()), "fb_router_plan_fused")
+
+
 def topk_logits(logits: torch.Tensor, k: int):
     lib = get_lib(True)
     rows, vocab = logits.shape
@@ -258,6 +309,7 @@ class AttnWorkspace:
     part_ml: torch.Tensor
     max_rows: int
     splits: int
+    merge_ctr: Optional[torch.Tensor] = None      # zeroed int32 [max_rows * head blocks]: in-kernel merge
 
 
 def mla_attention(q: torch.Tensor, kv_layer: torch.Tensor, block_table: torch.Tensor,
@@ -273,9 +325,10 @@ def mla_attention(q: torch.Tensor, kv_layer: torch.Tensor, block_table: torch.Te
     a.q, a.kv, a.out = q.data_ptr(), kv_layer.data_ptr(), out.data_ptr()
     a.block_table, a.row_seq, a.row_pos = block_table.data_ptr(), row_seq.data_ptr(), row_pos.data_ptr()
     a.sink = ptr(sink)
-    if splits > 1:
-        assert ws is not None and ws.max_rows >= rows and ws.splits >= splits
+    if splits > 1 and ws is not None:      # ws=None: the splits merge on chip through a thread-block cluster
+        assert ws.max_rows >= rows and ws.splits >= splits
         a.part_o, a.part_ml = ws.part_o.data_ptr(), ws.part_ml.data_ptr()
+        a.merge_ctr = ptr(ws.merge_ctr)
     a.status = status_tensor(q.device).data_ptr()
     a.ldq, a.ldo = q.stride(0), out.stride(0)
     a.pool_rows = kv_layer.numel() // D

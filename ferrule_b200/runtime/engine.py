@@ -469,6 +469,9 @@ class Engine:
     # ------------------------------------------------------------------ publish
     def _publish(self, txn: Transaction) -> None:
         """Backend confirmed the publish: commit KV, scheduler, tokens; stage the next greedy tokens."""
+        if txn.speculative is not None:
+            self.spec.publish(txn)
+            return
         ret = self.kv.publish_commit(txn.commit_id)
         txn.commit_id = None
         self._retire(ret)
