@@ -380,39 +380,69 @@ __device__ __forceinline__ void moe_plan_body(const int* topk_idx, const float* 
   __shared__ int cnt[256];
   __shared__ int off[257];
   __shared__ int s_idx[2048];   // decode-sized route lists are walked from shared memory
+  __shared__ float s_w[2048];
   const bool staged = routes <= 2048;
   const int local = e_hi - e_lo;
   for (int i = threadIdx.x; i < 256; i += blockDim.x) cnt[i] = 0;
   __syncthreads();
   for (int r = threadIdx.x; r < routes; r += blockDim.x) {
     const int e = topk_idx[r];
-    if (staged) s_idx[r] = e;
+    if (staged) {
+      s_idx[r] = e;
+      s_w[r] = topk_w ? topk_w[r] : 1.f;
+    }
     if (e >= e_lo && e < e_hi) atomicAdd(&cnt[e - e_lo], 1);
   }
   __syncthreads();
-  if (threadIdx.x == 0) {
-    int acc = 0, tiles = 0;
-    for (int e = 0; e < local; ++e) {
-      off[e] = acc;
-      const int c = cnt[e];
-      for (int r0 = 0; r0 < c; r0 += ntok) {
-        if (tiles < max_tiles) {
-          tile_group[tiles] = e;
-          tile_row0[tiles] = acc + r0;
-          tile_rows[tiles] = min(ntok, c - r0);
+  // Exclusive scans over experts (row offsets and tile offsets) by one warp: lane l owns experts
+  // 8l .. 8l+7, so a serial walk over all experts (slow on one thread) is avoided.
+  if (threadIdx.x < 32) {
+    const int lane = threadIdx.x;
+    int c[8], rows_sum = 0, tiles_sum = 0;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int e = lane * 8 + j;
+      c[j] = e < local ? cnt[e] : 0;
+      rows_sum += c[j];
+      tiles_sum += (c[j] + ntok - 1) / ntok;
+    }
+    int row_off = rows_sum, tile_off = tiles_sum;       // inclusive warp scans
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int r = __shfl_up_sync(0xffffffffu, row_off, o);
+      const int t = __shfl_up_sync(0xffffffffu, tile_off, o);
+      if (lane >= o) { row_off += r; tile_off += t; }
+    }
+    const int total_rows = __shfl_sync(0xffffffffu, row_off, 31);
+    int total_tiles = __shfl_sync(0xffffffffu, tile_off, 31);
+    row_off -= rows_sum;
+    tile_off -= tiles_sum;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int e = lane * 8 + j;
+      if (e < local) {
+        off[e] = row_off;
+        counts[e] = c[j];
+        for (int r0 = 0; r0 < c[j]; r0 += ntok) {
+          if (tile_off < max_tiles) {
+            tile_group[tile_off] = e;
+            tile_row0[tile_off] = row_off + r0;
+            tile_rows[tile_off] = min(ntok, c[j] - r0);
+          }
+          ++tile_off;
         }
-        ++tiles;
+        row_off += c[j];
       }
-      acc += c;
-      counts[e] = c;
     }
-    off[local] = acc;
-    if (tiles > max_tiles) {
-      report_status(st, kStatusBadShape, 0x30, tiles, max_tiles);
-      tiles = max_tiles;
+    if (lane == 0) {
+      off[local] = total_rows;
+      if (total_tiles > max_tiles) {
+        report_status(st, kStatusBadShape, 0x30, total_tiles, max_tiles);
+        total_tiles = max_tiles;
+      }
+      meta[0] = total_tiles;
+      meta[1] = total_rows;
     }
-    meta[0] = tiles;
-    meta[1] = acc;
   }
   __syncthreads();
   // Placement keeps the routes of one expert in ascending route order (bit-stable buffers
@@ -428,7 +458,7 @@ __device__ __forceinline__ void moe_plan_body(const int* topk_idx, const float* 
         const int p = base + __popc(mask & ((1u << lane) - 1u));
         src_token[p] = r / topk;
         dst_row[p] = (r / topk) * dst_slots + (r - (r / topk) * topk);
-        row_scale[p] = topk_w ? topk_w[r] : 1.f;
+        row_scale[p] = staged ? s_w[r] : (topk_w ? topk_w[r] : 1.f);
       }
       base += __popc(mask);
     }
@@ -853,7 +883,7 @@ extern "C" int fb_router_plan_fused(const void* x, long long ldx, const void* w,
   if (e_hi <= e_lo || e_hi - e_lo > 256 || ntok <= 0 || !done_ctr) return FB_ERR_SHAPE;
   PlanOut o{src_token, dst_row, row_scale, tile_group, tile_row0, tile_rows, max_tiles, counts, meta};
   const size_t smem = static_cast<size_t>(hidden + experts) * sizeof(float);
-  launch_pdl(router_plan_fused_kernel, dim3(rows), dim3(experts > 128 ? 1024 : 512), smem, static_cast<cudaStream_t>(stream), 
+  launch_pdl(router_plan_fused_kernel, dim3(rows), dim3(1024), smem, static_cast<cudaStream_t>(stream), 
       static_cast<const __nv_bfloat16*>(x), ldx, static_cast<const __nv_bfloat16*>(w), hidden, bias,
       hash_table, token_ids, rows, experts, topk, score_fn, n_groups, topk_groups, normalize, route_scale,
       out_idx, out_w, e_lo, e_hi, ntok, dst_slots < topk ? topk : dst_slots, o,
