@@ -32,6 +32,7 @@ CUDA_SOURCES = [
     "quant.cu",
     "v4_ops.cu",
     "comm.cu",
+    "no_alloc.cu",
 ]
 CXX_SOURCES = [
     "host/kv_page_manager.cpp",
