@@ -392,6 +392,11 @@ class Engine:
 
     def _resume_ready(self) -> bool:
         did = False
+        for txn_id in self.registry.pop_failed():
+            txn = self._waiting.pop(txn_id, None)
+            if txn is not None:
+                did = True
+                self._abort(txn, RuntimeError("a required materialization failed"))
         for txn_id in self.registry.pop_ready():
             txn = self._waiting.pop(txn_id, None)
             if txn is None:
@@ -456,6 +461,8 @@ class Engine:
         self._retire(self.kv.abort_reservations([m.res_id for m in txn.members]))
         if txn.grant is not None:
             self.broker.complete(txn.grant)
+        if self.registry is not None:
+            self.registry.release_transaction(txn.txn_id)
         txn.state = TxnState.DONE
         for m in txn.members:
             seq = m.seq
@@ -469,6 +476,8 @@ class Engine:
     # ------------------------------------------------------------------ publish
     def _publish(self, txn: Transaction) -> None:
         """Backend confirmed the publish: commit KV, scheduler, tokens; stage the next greedy tokens."""
+        if self.registry is not None:
+            self.registry.release_transaction(txn.txn_id)
         if txn.speculative is not None:
             self.spec.publish(txn)
             return

@@ -222,3 +222,29 @@ def test_shutdown_drains():
     assert eng.kv.stats().used_pages == 0 and eng.broker.outstanding() == 0
     with pytest.raises(RuntimeError):
         eng.submit(GenerateRequest("b", [1], max_new_tokens=1))
+
+
+def test_waiting_transaction_resumes_after_materialization():
+    from ferrule_b200.runtime.io_protocol import MaterializationKey, ResourceId, ResourceKind
+    from ferrule_b200.runtime.provider import FakeMaterializationProvider
+    from ferrule_b200.runtime.registry import LoadRegistry
+    key = lambda e: MaterializationKey("m", b"s", bytes([e]), ResourceId(ResourceKind.ROUTED_EXPERT, 1, e), 1, "cuda", 0, 0, 0)
+    r = MockRunner()
+    prov = FakeMaterializationProvider(auto=True)
+    sched = SchedulerConfig(max_active_sequences=4, max_decode_batch=4, max_batch_tokens=64, prefill_chunk_size=16, ctx_size=256)
+    eng = Engine(r, EngineConfig(scheduler=sched, kv_pages=32, page_size=16), registry=LoadRegistry(prov))
+    r.wait_next = [[key(1), key(2)], [key(3)]]            # the first batch suspends twice
+    eng.submit(GenerateRequest("w", [5, 6, 7], max_new_tokens=3))
+    ev = run(eng)
+    assert tokens_of(ev, "w") == expected_tokens(r, [5, 6, 7], 3)
+    assert eng.stats.waits == 2 and eng.stats.resumes == 2
+    assert eng.registry.stats.published == 3
+    assert [c[0] for c in r.calls if c[1] == 0][:4] == ["prepare", "execute", "resume", "resume"]
+    # a failed dependency aborts the transaction and fails the request, custody returned
+    r.wait_next = [[key(9)]]
+    prov.script_next("fail")
+    eng.submit(GenerateRequest("x", [1, 2], max_new_tokens=2))
+    ev = run(eng)
+    assert finish_of(ev, "x").reason == FinishReason.ERROR
+    eng.kv.check_invariants()
+    assert eng.kv.stats().used_pages == 0 and eng.broker.outstanding() == 0
