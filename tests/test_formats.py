@@ -1,0 +1,112 @@
+"""Number formats, safetensors IO and checkpoint round trips (CPU)."""
+import json
+
+import pytest
+import torch
+
+from ferrule_b200.io import encoding as enc
+from ferrule_b200.io.checkpoint import export_hf, infer_weight_format, load_deepseek_hf, read_linear
+from ferrule_b200.io.safetensors import CheckpointError, SafetensorsFile, ShardedCheckpoint, save_file
+from ferrule_b200.models import config as C
+from ferrule_b200.models import weights as W
+
+
+def test_e8m0_e4m3_e2m1_codecs():
+    b = torch.tensor([0, 1, 126, 127, 128, 254, 255], dtype=torch.uint8)
+    s = enc.e8m0_decode(b)
+    assert s[3] == 1.0 and s[2] == 0.5 and s[4] == 2.0 and s[0] == 2.0 ** -127 and torch.isnan(s[6])
+    assert enc.e8m0_encode_ceil(torch.tensor([1.0, 1.1, 0.24, 448.0])).tolist() == [127, 128, 125, 136]
+    all_codes = torch.arange(256, dtype=torch.uint8)
+    v = enc.e4m3_decode(all_codes)
+    assert v[0x7e] == 448.0 and torch.isnan(v[0x7f]) and torch.isnan(v[0xff]) and v[0x38] == 1.0
+    finite = ~torch.isnan(v)
+    rt = enc.e4m3_encode(v[finite])
+    assert torch.equal(rt & 0x7f, all_codes[finite] & 0x7f)            # every finite code survives a round trip
+    assert enc.e4m3_decode(enc.e4m3_encode(torch.tensor([1e6, -1e6]))).tolist() == [448.0, -448.0]
+    nib = torch.arange(16, dtype=torch.uint8)
+    vals = enc.fp4_decode_nibbles(nib)
+    assert vals.tolist() == [0, .5, 1, 1.5, 2, 3, 4, 6, -0.0, -.5, -1, -1.5, -2, -3, -4, -6]
+    assert enc.fp4_encode_nibbles(vals[:8]).tolist() == list(range(8))
+    assert enc.fp4_encode_nibbles(torch.tensor([0.25, 0.75, 2.5, 5.0, 100.0, -2.4])).tolist() == [0, 2, 4, 6, 7, 12]
+    x = torch.tensor([[0.5, -1.0, 6.0, 0.0]])
+    p = enc.fp4_pack(x)
+    assert p.tolist() == [[0x01 | (0x0a << 4), 0x07 | (0x00 << 4)]]          # low nibble first
+    assert torch.equal(enc.fp4_unpack(p), x)
+
+
+def test_activation_and_weight_quantisation():
+    g = torch.Generator().manual_seed(0)
+    x = torch.randn(5, 256, generator=g) * 3
+    q, sb = enc.act_quant_fp8(x)
+    assert q.shape == (5, 256) and sb.shape == (5, 2)
+    back = enc.act_dequant_fp8(q, sb)
+    assert float(((back - x).abs() / (x.abs() + 0.1)).max()) < 0.08
+    # power-of-two scale with ceil: the block max never saturates
+    scale = enc.e8m0_decode(sb)
+    assert float((x.view(5, 2, 128).abs().amax(-1) / scale).max()) <= 448.0
+    tiny = torch.full((1, 128), 1e-7)
+    _, sbt = enc.act_quant_fp8(tiny)
+    assert float(enc.e8m0_decode(sbt)) == 2.0 ** -22              # amax floor 1e-4 / 448 -> 2^-22
+    w = torch.randn(200, 300, generator=g) * 0.05
+    qw, sw = enc.weight_quant_fp8_block(w)
+    assert qw.shape == w.shape and sw.shape == (2, 3)
+    assert float(((enc.weight_dequant_fp8_block(qw, sw) - w).abs()).max()) < 0.01
+    w4 = torch.randn(16, 128, generator=g)
+    p4, s4 = enc.weight_quant_mxfp4(w4)
+    assert p4.shape == (16, 64) and s4.shape == (16, 4)
+    err = (enc.weight_dequant_mxfp4(p4, s4) - w4).abs() / (w4.view(16, 4, 32).abs().amax(-1, keepdim=True).expand(16, 4, 32).reshape(16, 128) + 1e-6)
+    assert float(err.max()) < 0.26
+    h = enc.hadamard(torch.eye(8))
+    assert torch.allclose(h @ h.T, torch.eye(8), atol=1e-6)
+    y = torch.randn(3, 64, generator=g)
+    assert torch.allclose(enc.hadamard(enc.hadamard(y)), y, atol=1e-5)
+    assert torch.equal(enc.fp8_qat(y.repeat(1, 2)), enc.fp8_qat(y.repeat(1, 2)).bfloat16().float())
+
+
+def test_safetensors_roundtrip_and_validation(tmp_path):
+    t = {"a": torch.arange(12, dtype=torch.float32).view(3, 4), "b": torch.randn(5, 6).bfloat16(),
+         "q": torch.arange(8, dtype=torch.uint8), "i": torch.tensor([[1, -2]], dtype=torch.int64)}
+    p = tmp_path / "x.safetensors"
+    save_file(t, p, {"q": "F8_E4M3"}, {"format": "pt"})
+    f = SafetensorsFile(p)
+    assert f.tensors["q"].dtype == "F8_E4M3" and f.metadata == {"format": "pt"}
+    for k in t:
+        assert torch.equal(f.read(k), t[k])
+    assert torch.equal(f.read_rows("a", 1, 3), t["a"][1:3])
+    with pytest.raises(CheckpointError):
+        f.read("a", max_bytes=8)
+    with pytest.raises(CheckpointError):
+        f.read("nope")
+    f.close()
+    bad = tmp_path / "bad.safetensors"
+    bad.write_bytes((10 ** 9).to_bytes(8, "little") + b"{}")
+    with pytest.raises(CheckpointError):
+        SafetensorsFile(bad)
+
+
+@pytest.mark.parametrize("dense,expert", [("plain", "plain"), ("fp8_block", "mxfp4")])
+def test_checkpoint_export_load_roundtrip(tmp_path, dense, expert):
+    cfg = C.tiny_fixture()
+    w = W.random_weights(cfg, dtype=torch.bfloat16, seed=3)
+    export_hf(w, tmp_path, dense_format=dense, expert_format=expert, shard_bytes=1 << 20)
+    ck = ShardedCheckpoint(tmp_path)
+    assert len(set(ck.weight_map.values())) > 1                      # really sharded
+    fmt = infer_weight_format(ck, "model.layers.1.mlp.experts.0.gate_proj")
+    assert fmt[0] == ("plain" if expert == "plain" else "mxfp4") and (expert == "plain" or fmt[2] == 32)
+    assert infer_weight_format(ck, "model.layers.0.self_attn.o_proj")[0] == dense
+    plan = ck.read_plan([n for n in ck.names() if "experts.3." in n and "layers.1." in n])
+    assert plan and all(off % 4096 == 0 and ln % 4096 == 0 for _, off, ln in plan)
+    assert ck.source_identity() == ShardedCheckpoint(tmp_path).source_identity()
+    w2 = load_deepseek_hf(tmp_path)
+    assert w2.cfg.n_routed_experts == cfg.n_routed_experts and len(w2.mtp) == 1
+    tol = 0.0 if dense == "plain" else 0.02
+    for a, b in zip(w.layers, w2.layers):
+        assert float((a.w_o.float() - b.w_o.float()).abs().max()) <= tol * 0.2 + 1e-9
+        assert float((a.w_uk_t.float() - b.w_uk_t.float()).abs().max()) <= tol * 0.2 + 1e-9
+        if a.is_moe:
+            d = (a.e_w13.float() - b.e_w13.float()).abs().max()
+            assert float(d) <= (0.0 if expert == "plain" else 0.03)
+    # tensor-parallel load takes the matching slices
+    w_tp = load_deepseek_hf(tmp_path, tp_rank=1, tp_world=2)
+    assert torch.equal(w_tp.layers[1].e_w2, w2.layers[1].e_w2[4:])
+    assert torch.equal(w_tp.lm_head, w2.lm_head[512:])
