@@ -1,0 +1,155 @@
+"""Tokenizer handle, UTF-8-safe incremental detokenisation and chat templates.
+
+`load_tokenizer(dir)` uses the HuggingFace `tokenizers` file (`tokenizer.json`) when present and
+falls back to a byte-level tokenizer (ids 0..255 = bytes, 256 = BOS, 257 = EOS), which is what the
+synthetic benchmarks and tests use.  `IncrementalDecodeState.push(token)` returns only text that
+can no longer change: a multi-byte character split across tokens is held back until complete.
+
+Counterpart of crates/ferrule-model/src/tokenizer.rs:8-60 and chat.rs:75-130 (ChatML, Llama3,
+Qwen, DeepSeek, Plain templates).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from enum import Enum
+from pathlib import Path
+from typing import Dict, List, Optional, Sequence
+
+
+class ByteTokenizer:
+    """ids 0..255 are raw bytes; BOS = 256, EOS = 257."""
+    bos_token_id, eos_token_id, vocab_size = 256, 257, 258
+
+    def encode(self, text: str, add_bos: bool = False) -> List[int]:
+        ids = list(text.encode("utf-8"))
+        return ([self.bos_token_id] + ids) if add_bos else ids
+
+    def decode(self, ids: Sequence[int]) -> str:
+        return bytes(i for i in ids if 0 <= i < 256).decode("utf-8", errors="replace")
+
+    def decode_bytes(self, ids: Sequence[int]) -> bytes:
+        return bytes(i for i in ids if 0 <= i < 256)
+
+
+class HfTokenizer:
+    def __init__(self, path):
+        from tokenizers import Tokenizer as _T
+        self._t = _T.from_file(str(path))
+        self.vocab_size = self._t.get_vocab_size()
+        self.bos_token_id = self._id_of(["<｜begin▁of▁sentence｜>", "<|begin_of_text|>", "<s>", "<|im_start|>"])
+        self.eos_token_id = self._id_of(["<｜end▁of▁sentence｜>", "<|end_of_text|>", "</s>", "<|im_end|>", "<|endoftext|>"])
+
+    def _id_of(self, names) -> int:
+        for n in names:
+            i = self._t.token_to_id(n)
+            if i is not None:
+                return i
+        return -1
+
+    def encode(self, text: str, add_bos: bool = False) -> List[int]:
+        ids = self._t.encode(text, add_special_tokens=False).ids
+        return ([self.bos_token_id] + ids) if (add_bos and self.bos_token_id >= 0) else ids
+
+    def decode(self, ids: Sequence[int]) -> str:
+        return self._t.decode(list(ids), skip_special_tokens=True)
+
+
+def load_tokenizer(directory=None):
+    if directory is not None:
+        p = Path(directory) / "tokenizer.json"
+        if p.exists():
+            return HfTokenizer(p)
+    return ByteTokenizer()
+
+
+class IncrementalDecodeState:
+    """Streams text deltas that are stable: never emits half of a multi-byte character."""
+
+    def __init__(self, tokenizer, hold_back: int = 6):
+        self.tok = tokenizer
+        self.ids: List[int] = []
+        self.emitted = ""
+        self._stable_prefix = 0           # tokens whose text is final and already folded into `emitted`
+        self.hold_back = hold_back
+
+    def push(self, token: int) -> str:
+        self.ids.append(token)
+        text = self.tok.decode(self.ids)
+        # an incomplete UTF-8 sequence decodes to U+FFFD at the end: hold it back
+        cut = len(text)
+        while cut > 0 and text[cut - 1] == "�":
+            cut -= 1
+        stable = text[:cut]
+        if not stable.startswith(self.emitted):
+            # tokenizer normalisation changed earlier text (rare): emit nothing until it settles
+            common = 0
+            for a, b in zip(stable, self.emitted):
+                if a != b:
+                    break
+                common += 1
+            if common < len(self.emitted):
+                return ""
+        delta = stable[len(self.emitted):]
+        self.emitted = stable
+        return delta
+
+    def finish(self) -> str:
+        text = self.tok.decode(self.ids)
+        delta = text[len(self.emitted):] if text.startswith(self.emitted) else ""
+        self.emitted = text
+        return delta
+
+
+class ChatTemplate(Enum):
+    CHATML = "chatml"
+    LLAMA3 = "llama3"
+    QWEN = "qwen"
+    DEEPSEEK = "deepseek"
+    PLAIN = "plain"
+
+
+@dataclass
+class ChatMessage:
+    role: str
+    content: str
+
+
+def render_chat(messages: Sequence[ChatMessage], template: ChatTemplate = ChatTemplate.DEEPSEEK,
+                add_generation_prompt: bool = True) -> str:
+    if template in (ChatTemplate.CHATML, ChatTemplate.QWEN):
+        out = ""
+        if template == ChatTemplate.QWEN and not any(m.role == "system" for m in messages):
+            out += "<|im_start|>system\nYou are a helpful assistant.<|im_end|>\n"
+        for m in messages:
+            out += f"<|im_start|>{m.role}\n{m.content}<|im_end|>\n"
+        return out + ("<|im_start|>assistant\n" if add_generation_prompt else "")
+    if template == ChatTemplate.LLAMA3:
+        out = "<|begin_of_text|>"
+        for m in messages:
+            out += f"<|start_header_id|>{m.role}<|end_header_id|>\n\n{m.content}<|eot_id|>"
+        return out + ("<|start_header_id|>assistant<|end_header_id|>\n\n" if add_generation_prompt else "")
+    if template == ChatTemplate.DEEPSEEK:
+        out = "<｜begin▁of▁sentence｜>"
+        for m in messages:
+            if m.role == "system":
+                out += m.content
+            elif m.role == "user":
+                out += f"<｜User｜>{m.content}"
+            else:
+                out += f"<｜Assistant｜>{m.content}<｜end▁of▁sentence｜>"
+        return out + ("<｜Assistant｜>" if add_generation_prompt else "")
+    out = ""
+    for m in messages:
+        out += f"{m.role}: {m.content}\n"
+    return out + ("assistant: " if add_generation_prompt else "")
+
+
+def template_for_model(name: str) -> ChatTemplate:
+    n = name.lower()
+    if "deepseek" in n:
+        return ChatTemplate.DEEPSEEK
+    if "qwen" in n:
+        return ChatTemplate.QWEN
+    if "llama" in n:
+        return ChatTemplate.LLAMA3
+    return ChatTemplate.CHATML

@@ -1,0 +1,114 @@
+"""utils: tokenizer streaming, chat templates, LRU, completion hub, failpoints, metrics, families."""
+import asyncio
+import threading
+import time
+
+import pytest
+
+from ferrule_b200.models.families import Family, TensorRole, classify, detect_family, layout_summary
+from ferrule_b200.utils.async_wake import CompletionHub
+from ferrule_b200.utils.errors import ErrorKind, FerruleError, quant_type
+from ferrule_b200.utils.failpoints import FAILPOINTS, FailpointTriggered, OpCounters
+from ferrule_b200.utils.memory import MemoryPoolLimits, OwnerMemoryLru
+from ferrule_b200.utils.observability import METRICS, Metrics
+from ferrule_b200.utils.tokenizer import (ByteTokenizer, ChatMessage, ChatTemplate, IncrementalDecodeState,
+                                          render_chat, template_for_model)
+
+
+def test_incremental_decode_never_splits_utf8():
+    tok = ByteTokenizer()
+    text = "héllo 世界 🙂!"
+    st = IncrementalDecodeState(tok)
+    out = []
+    for t in tok.encode(text):
+        d = st.push(t)
+        assert "�" not in d
+        out.append(d)
+    assert "".join(out) + st.finish() == text
+    assert sum(1 for d in out if d == "") >= 6          # continuation bytes were held back
+
+
+def test_chat_templates():
+    msgs = [ChatMessage("system", "S"), ChatMessage("user", "hi")]
+    assert render_chat(msgs, ChatTemplate.CHATML).endswith("<|im_start|>user\nhi<|im_end|>\n<|im_start|>assistant\n")
+    assert "<|start_header_id|>user<|end_header_id|>\n\nhi<|eot_id|>" in render_chat(msgs, ChatTemplate.LLAMA3)
+    assert render_chat(msgs, ChatTemplate.DEEPSEEK) == "<｜begin▁of▁sentence｜>S<｜User｜>hi<｜Assistant｜>"
+    assert render_chat(msgs[1:], ChatTemplate.QWEN).startswith("<|im_start|>system\nYou are a helpful assistant.")
+    assert render_chat(msgs, ChatTemplate.PLAIN, add_generation_prompt=False) == "system: S\nuser: hi\n"
+    assert template_for_model("DeepSeek-V3") == ChatTemplate.DEEPSEEK and template_for_model("x") == ChatTemplate.CHATML
+
+
+def test_owner_lru_bytes_entries_and_pins():
+    evicted = []
+    lru = OwnerMemoryLru(MemoryPoolLimits(max_bytes=100, max_entries=3, reserve_bytes=10), lambda k, v: evicted.append(k))
+    assert lru.put("a", 1, 40) and lru.put("b", 2, 40)
+    assert lru.get("a") == 1                       # a becomes most recent
+    assert lru.put("c", 3, 40) and evicted == ["b"] and lru.bytes == 80
+    lru.pin("a")
+    assert lru.put("d", 4, 50) and evicted == ["b", "c"]
+    assert not lru.put("e", 5, 60) and "a" in lru   # only the pinned entry is left to evict
+    assert not lru.put("big", 0, 95)
+    lru.unpin("a")
+    assert lru.put("e", 5, 60) and "a" not in lru
+
+
+def test_completion_hub_no_lost_wakeup():
+    hub = CompletionHub()
+    t = hub.listen()
+    hub.notify()                                     # notified between listen and wait
+    assert hub.wait(t, timeout=0.0)
+    t2 = hub.listen()
+    assert not hub.wait(t2, timeout=0.01)
+    threading.Timer(0.02, hub.notify).start()
+    assert hub.wait(t2, timeout=2.0)
+
+    async def main():
+        tk = hub.listen()
+        threading.Timer(0.02, hub.notify).start()
+        assert await hub.wait_async(tk, timeout=2.0)
+        assert not await hub.wait_async(hub.listen(), timeout=0.01)
+    asyncio.run(main())
+
+
+def test_failpoints_counters_errors_metrics():
+    FAILPOINTS.disarm_all()
+    FAILPOINTS.check("expert_upload")
+    FAILPOINTS.arm("expert_upload", 2)
+    for _ in range(2):
+        with pytest.raises(FailpointTriggered):
+            FAILPOINTS.check("expert_upload")
+    FAILPOINTS.check("expert_upload")
+    with pytest.raises(KeyError):
+        FAILPOINTS.arm("nope")
+    c = OpCounters()
+    c.add("gemm", 3); c.add("gemm")
+    assert c.snapshot() == {"gemm": 4}
+    e = FerruleError(ErrorKind.IO, "short read", cleanup=[RuntimeError("x")]).context("expert 3").context("layer 1")
+    assert str(e) == "[io] layer 1: expert 3: short read (+1 clean-up failure(s))"
+    assert quant_type(12).bytes_for(512) == 288
+    m = Metrics()
+    m.add(requests_finished=2, ttft_sum_s=1.0)
+    assert m.snapshot()["ttft_mean_s"] == 0.5
+
+
+def test_family_classification():
+    hf = ["model.embed_tokens.weight", "model.layers.3.self_attn.kv_a_proj_with_mqa.weight",
+          "model.layers.3.mlp.experts.17.down_proj.weight_scale_inv", "model.layers.3.mlp.gate.weight",
+          "model.layers.3.mlp.gate.e_score_correction_bias", "model.layers.0.mlp.up_proj.weight",
+          "model.layers.61.eh_proj.weight", "lm_head.weight"]
+    assert detect_family(hf) == Family.DEEPSEEK_HF
+    c = classify(hf[2], Family.DEEPSEEK_HF, 61)
+    assert (c.role, c.layer, c.expert, c.is_scale) == (TensorRole.EXPERT_DOWN, 3, 17, True)
+    assert classify(hf[4], Family.DEEPSEEK_HF).role == TensorRole.ROUTER_BIAS
+    assert classify(hf[5], Family.DEEPSEEK_HF).role == TensorRole.DENSE_UP
+    assert classify(hf[6], Family.DEEPSEEK_HF, 61).mtp_stage == 0
+    v4 = ["embed.weight", "layers.2.attn.wq_a.weight", "layers.2.attn.wq_a.scale", "layers.2.ffn.experts.5.w2.weight",
+          "layers.0.ffn.gate.tid2eid", "layers.2.hc_attn_fn", "layers.2.attn.compressor.wkv.weight",
+          "mtp.0.main_proj.weight", "mtp.0.ffn.experts.1.w1.scale", "layers.2.attn.attn_sink"]
+    assert detect_family(v4) == Family.DEEPSEEK_V4
+    roles = [classify(n, Family.DEEPSEEK_V4).role for n in v4]
+    assert roles == [TensorRole.EMBEDDING, TensorRole.ATTN_Q_A, TensorRole.ATTN_Q_A, TensorRole.EXPERT_DOWN,
+                     TensorRole.ROUTER_HASH, TensorRole.HYPER_CONNECTION, TensorRole.COMPRESSOR, TensorRole.MTP,
+                     TensorRole.EXPERT_GATE, TensorRole.ATTN_SINK]
+    assert classify(v4[8], Family.DEEPSEEK_V4).mtp_stage == 0
+    assert layout_summary(hf, Family.DEEPSEEK_HF, 61)["expert_down"] == 1
