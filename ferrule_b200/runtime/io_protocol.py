@@ -214,6 +214,7 @@ class PinnedSlabLease:
     alignment: int = 4096
     state: SlabLeaseState = SlabLeaseState.FREE
     operation: Optional[int] = None
+    base_address: int = 0           # address of the slab buffer; offset is relative to it
 
     def advance(self, nxt: SlabLeaseState) -> None:
         if nxt not in _SLAB_NEXT[self.state]:
@@ -221,7 +222,7 @@ class PinnedSlabLease:
         self.state = nxt
 
     def validate(self) -> None:
-        if self.offset % self.alignment or self.nbytes % self.alignment:
+        if (self.base_address + self.offset) % self.alignment or self.nbytes % self.alignment:
             raise IoProtocolError("slab lease is not aligned for direct I/O")
 
 

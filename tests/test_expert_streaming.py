@@ -1,0 +1,101 @@
+"""Expert streaming end to end on the CPU: checkpoint -> slabs -> arena frames through the LoadRegistry."""
+import time
+
+import pytest
+import torch
+
+from ferrule_b200.io.checkpoint import export_hf
+from ferrule_b200.io.safetensors import ShardedCheckpoint
+from ferrule_b200.models import config as C
+from ferrule_b200.models import weights as W
+from ferrule_b200.runtime.expert_residency import ExpertResidencyController
+from ferrule_b200.runtime.expert_streaming import (ExpertArena, ExpertMaterializationProvider, ExpertSourceCatalog,
+                                                   HostStagedExpertCache, PinnedSlabPool)
+from ferrule_b200.runtime.registry import LoadRegistry, OwnerKind
+from ferrule_b200.utils.failpoints import FAILPOINTS
+
+
+@pytest.fixture()
+def rig(tmp_path):
+    cfg = C.tiny_fixture()
+    w = W.random_weights(cfg, dtype=torch.bfloat16, seed=5)
+    export_hf(w, tmp_path, expert_format="mxfp4")
+    ck = ShardedCheckpoint(tmp_path)
+    cat = ExpertSourceCatalog("tiny", ck, [1], cfg.n_routed_experts, device=0, backend="cpu")
+    res = ExpertResidencyController([1], {1: 3}, cfg.n_routed_experts)
+    arena = ExpertArena([1], {1: 3}, cat.max_payload_bytes(), "cpu")
+    slabs = PinnedSlabPool(cat.max_payload_bytes(), 2, pin=False)
+    installed = []
+    prov = ExpertMaterializationProvider(cat, res, arena, slabs, HostStagedExpertCache(1 << 20, 1 << 20),
+                                         on_install=lambda *a: installed.append(a[:4]))
+    reg = LoadRegistry(prov)
+    yield cfg, w, ck, cat, res, arena, slabs, prov, reg, installed
+    prov.close()
+    ck.close()
+    FAILPOINTS.disarm_all()
+
+
+def drive(reg, pred, limit=2.0):
+    t0 = time.time()
+    while not pred() and time.time() - t0 < limit:
+        reg.drive()
+        time.sleep(0.001)
+    assert pred()
+
+
+def test_stream_experts_into_slots_and_bytes_match_checkpoint(rig):
+    cfg, w, ck, cat, res, arena, slabs, prov, reg, installed = rig
+    keys = [cat.key(1, e) for e in (0, 5)]
+    assert keys[0] != keys[1] and keys[0] == cat.key(1, 0)
+    reg.register_continuation(1, keys)
+    drive(reg, lambda: bool(reg._ready))
+    assert reg.pop_ready() == [1] and len(installed) == 2
+    coord = res.layer(1)
+    for e in (0, 5):
+        slot, gen = coord.resolve(e)
+        src = cat.source(1, e)
+        frame = arena.frame(1, slot)
+        for s in src.slices:
+            info = ck.info(s.name)
+            raw = ck.read(s.name).contiguous().view(torch.uint8).flatten()
+            assert torch.equal(frame[s.payload_offset:s.payload_offset + s.length], raw), s.name
+    assert slabs.in_use == 0 and prov.bytes_uploaded == sum(cat.source(1, e).payload_bytes for e in (0, 5))
+    assert reg.broker.outstanding() == 2            # two resident-byte grants
+
+
+def test_capacity_eviction_restream_hits_host_cache(rig):
+    cfg, w, ck, cat, res, arena, slabs, prov, reg, installed = rig
+    for txn, e in enumerate((0, 1, 2)):
+        reg.register_continuation(txn, [cat.key(1, e)])
+        drive(reg, lambda: bool(reg._ready))
+        reg.pop_ready(); reg.release_transaction(txn)
+    assert res.layer(1).resident() == [0, 1, 2]
+    read_before = prov.bytes_read
+    # a fourth expert needs a slot: the registry must retire an unleased one first
+    assert reg.evict(1) == 1
+    reg.register_continuation(10, [cat.key(1, 3)])
+    drive(reg, lambda: bool(reg._ready))
+    assert 3 in res.layer(1).resident() and len(res.layer(1).resident()) == 3
+    evicted = ({0, 1, 2} - set(res.layer(1).resident())).pop()
+    reg.pop_ready(); reg.release_transaction(10)
+    reg.evict(1)
+    reg.register_continuation(11, [cat.key(1, evicted)])
+    drive(reg, lambda: bool(reg._ready))
+    assert prov.cache_served == 1 and prov.bytes_read == read_before + cat.source(1, 3).payload_bytes
+
+
+def test_failpoints_fail_the_waiter_and_leave_no_residue(rig):
+    cfg, w, ck, cat, res, arena, slabs, prov, reg, installed = rig
+    FAILPOINTS.arm("expert_upload")
+    reg.register_continuation(1, [cat.key(1, 4)])
+    drive(reg, lambda: bool(reg._failed))
+    assert reg.pop_failed() == [1]
+    reg.release_transaction(1)
+    assert not res.layer(1).in_flight(4) and res.layer(1).resident() == [] and slabs.in_use == 0
+    FAILPOINTS.arm("checkpoint_read")
+    reg.register_continuation(2, [cat.key(1, 4)])
+    drive(reg, lambda: bool(reg._failed))
+    reg.pop_failed(); reg.release_transaction(2)
+    reg.register_continuation(3, [cat.key(1, 4)])          # third time lucky: nothing armed
+    drive(reg, lambda: bool(reg._ready))
+    assert res.layer(1).resident() == [4] and reg.broker.outstanding() == 1
