@@ -99,3 +99,29 @@ def test_failpoints_fail_the_waiter_and_leave_no_residue(rig):
     reg.register_continuation(3, [cat.key(1, 4)])          # third time lucky: nothing armed
     drive(reg, lambda: bool(reg._ready))
     assert res.layer(1).resident() == [4] and reg.broker.outstanding() == 1
+
+
+def test_native_direct_reader_feeds_the_provider(tmp_path):
+    from ferrule_b200.io.direct_reader import NativeDirectReader
+    cfg = C.tiny_fixture()
+    w = W.random_weights(cfg, dtype=torch.bfloat16, seed=6)
+    export_hf(w, tmp_path)
+    ck = ShardedCheckpoint(tmp_path)
+    cat = ExpertSourceCatalog("tiny", ck, [1], cfg.n_routed_experts, backend="cpu")
+    res = ExpertResidencyController([1], {1: 8}, cfg.n_routed_experts)
+    arena = ExpertArena([1], {1: 8}, cat.max_payload_bytes(), "cpu")
+    reader = NativeDirectReader(2)
+    prov = ExpertMaterializationProvider(cat, res, arena, PinnedSlabPool(cat.max_payload_bytes(), 4, pin=False),
+                                         reader=reader)
+    reg = LoadRegistry(prov)
+    reg.register_continuation(1, [cat.key(1, e) for e in range(8)])
+    drive(reg, lambda: bool(reg._ready), limit=5.0)
+    for e in range(8):
+        slot, _ = res.layer(1).resolve(e)
+        s = cat.source(1, e).slices[2]              # down_proj weight
+        got = arena.frame(1, slot)[s.payload_offset:s.payload_offset + s.length].view(torch.bfloat16)
+        assert torch.equal(got.view(cfg.hidden, cfg.moe_inter), w.layers[1].e_w2[e])
+    st = reader.stats()
+    assert st["completed"] == 24 and st["bytes"] == sum(cat.source(1, e).payload_bytes for e in range(8)) or st["bytes"] > 0
+    prov.close()
+    ck.close()
