@@ -243,6 +243,7 @@ class ExpertMaterializationProvider(MaterializationProvider):
         self._done: Deque[CompletionEvent] = deque()
         self._lock = threading.Lock()
         self._uploads: List[_OpState] = []
+        self._waiting_reads: Deque[int] = deque()
         self.cuda = arena.device.type == "cuda"
         self.upload_stream = torch.cuda.Stream(device=arena.device, priority=0) if self.cuda else None
         self.bytes_read = self.bytes_uploaded = self.cache_served = 0
@@ -287,7 +288,12 @@ class ExpertMaterializationProvider(MaterializationProvider):
             return self._push(self._ev(st, LoadStage.READ_SUBMITTED, True, st.source.payload_bytes))
         slab = self.slabs.acquire(op)
         if slab is None:
-            return self._push(self._ev(st, LoadStage.READ_SUBMITTED, False, 0, FailureReason.RESOURCE_EXHAUSTED))
+            # every slab is on loan: the read starts as soon as an upload gives one back
+            self._waiting_reads.append(op)
+            return
+        self._start_read(st, slab)
+
+    def _start_read(self, st: _OpState, slab: PinnedSlabLease) -> None:
         st.slab = slab
         dst = self.slabs.view(slab, st.source.payload_bytes)
 
@@ -331,9 +337,24 @@ class ExpertMaterializationProvider(MaterializationProvider):
         if st.slab is not None:
             if self.cache is not None:
                 self.cache.put((st.key.resource.group, st.key.resource.item), self.slabs.view(st.slab, n).clone())
-            self.slabs.release(st.slab)
-            st.slab = None
+            self._release_slab(st)
         self._push(self._ev(st, LoadStage.UPLOAD_SUBMITTED, True, n))
+
+    def _release_slab(self, st: _OpState) -> None:
+        self.slabs.release(st.slab)
+        st.slab = None
+        while self._waiting_reads:
+            nxt = self.ops.get(self._waiting_reads.popleft())
+            if nxt is None or nxt.cancelled:
+                if nxt is not None:
+                    self._push(self._ev(nxt, LoadStage.READ_SUBMITTED, False, 0))
+                continue
+            slab = self.slabs.acquire(nxt.op)
+            if slab is None:
+                self._waiting_reads.appendleft(nxt.op)
+            else:
+                self._start_read(nxt, slab)
+            break
 
     def poll_install(self, op: int, key: MaterializationKey, generation: int) -> None:
         st = self.ops[op]
@@ -354,13 +375,18 @@ class ExpertMaterializationProvider(MaterializationProvider):
         st = self.ops.get(op)
         if st is not None:
             st.cancelled = True
+            if op in self._waiting_reads:          # never started: answer the owed completion now
+                self._waiting_reads.remove(op)
+                self._push(self._ev(st, LoadStage.READ_SUBMITTED, False, 0))
 
     def retire(self, op: int, key: MaterializationKey) -> None:
         st = self.ops.pop(op, None)
         if st is None:
             return
+        if op in self._waiting_reads:
+            self._waiting_reads.remove(op)
         if st.slab is not None and st.slab.state in (SlabLeaseState.LEASED, SlabLeaseState.FILLED):
-            self.slabs.release(st.slab)
+            self._release_slab(st)
         coord = self.residency.layer(st.ticket.layer)
         if coord.in_flight(st.ticket.expert):
             try:
