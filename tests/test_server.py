@@ -1,0 +1,180 @@
+"""HTTP front end against an engine with the mock runner (CPU): protocol validation, SSE framing,
+greedy-only rejection, disconnect cancel, overload, fatal latch."""
+import asyncio
+import json
+
+import httpx
+import pytest
+
+from ferrule_b200.runtime.engine import Engine, EngineConfig
+from ferrule_b200.runtime.runner import MockRunner
+from ferrule_b200.runtime.scheduler import SchedulerConfig
+from ferrule_b200.server import openai as oa
+from ferrule_b200.server.http import build_app
+from ferrule_b200.server.worker import ModelWorker, WorkerConfig
+from ferrule_b200.utils.tokenizer import ByteTokenizer
+
+
+def make_worker(runner=None, **wcfg):
+    runner = runner or MockRunner(vocab=258, eos=257, next_token_fn=lambda t, p: 97 + (t + p) % 26)
+
+    def factory():
+        sched = SchedulerConfig(max_active_sequences=8, max_decode_batch=8, max_batch_tokens=256, prefill_chunk_size=64,
+                                ctx_size=512)
+        return Engine(runner, EngineConfig(scheduler=sched, kv_pages=128, page_size=16))
+    return ModelWorker(factory, ByteTokenizer(), WorkerConfig(**wcfg), model_name="mock").start(), runner
+
+
+def client(app):
+    return httpx.AsyncClient(transport=httpx.ASGITransport(app=app), base_url="http://t")
+
+
+def run(coro):
+    return asyncio.run(coro)
+
+
+def test_validation_rules():
+    ok = oa.parse_chat_request({"messages": [{"role": "user", "content": "x"}], "temperature": 0, "top_k": -1})
+    assert ok.max_tokens == 16 and ok.stop == [] and not ok.stream
+    for bad in ({"messages": [{"role": "user", "content": "x"}], "temperature": 0.7},
+                {"messages": [{"role": "user", "content": "x"}], "n": 2},
+                {"messages": [{"role": "user", "content": "x"}], "top_p": 0.9},
+                {"messages": [{"role": "user", "content": "x"}], "logprobs": True},
+                {"messages": [{"role": "user", "content": "x"}], "tools": [{"type": "function"}]},
+                {"messages": [{"role": "user", "content": "x"}], "response_format": {"type": "json_object"}},
+                {"messages": [{"role": "user", "content": "x"}], "stop": ["a", "b", "c", "d", "e"]},
+                {"messages": [{"role": "user", "content": "x"}], "stop": [""]},
+                {"messages": [{"role": "user", "content": "x"}], "bogus": 1},
+                {"messages": [], },
+                {"messages": [{"role": "tool", "content": "x"}]},
+                {"messages": [{"role": "user", "content": "x"}], "stream_options": {"include_usage": True}},
+                {"messages": [{"role": "user", "content": "x"}], "max_tokens": 0}):
+        with pytest.raises(oa.RequestError):
+            oa.parse_chat_request(bad)
+    c = oa.parse_completion_request({"prompt": [1, 2, 3], "max_tokens": 5, "stop": "z"})
+    assert c.prompt_tokens == [1, 2, 3] and c.stop == ["z"]
+    for bad in ({"prompt": "x", "echo": True}, {"prompt": "x", "best_of": 3}, {"prompt": 5}, {"prompt": "x", "messages": []}):
+        with pytest.raises(oa.RequestError):
+            oa.parse_completion_request(bad)
+
+
+def test_completion_chat_models_health_tokenize():
+    worker, runner = make_worker()
+    app = build_app(worker)
+
+    async def main():
+        async with client(app) as c:
+            assert (await c.get("/health")).json() == {"status": "ok"}
+            assert (await c.get("/v1/models")).json()["data"][0]["id"] == "mock"
+            r = await c.post("/v1/completions", json={"prompt": "hello", "max_tokens": 5})
+            assert r.status_code == 200
+            b = r.json()
+            assert b["object"] == "text_completion" and b["choices"][0]["finish_reason"] == "length"
+            assert b["usage"] == {"prompt_tokens": 5, "completion_tokens": 5, "total_tokens": 10}
+            assert len(b["choices"][0]["text"]) == 5
+            r = await c.post("/v1/chat/completions", json={"model": "mock", "messages": [{"role": "user", "content": "hi"}],
+                                                           "max_tokens": 4})
+            b = r.json()
+            assert b["object"] == "chat.completion" and b["choices"][0]["message"]["role"] == "assistant"
+            assert b["usage"]["completion_tokens"] == 4
+            r = await c.post("/v1/tokenize", json={"prompt": "abc"})
+            assert r.json()["tokens"] == [97, 98, 99] and r.json()["count"] == 3
+            assert (await c.post("/tokenize", json={"prompt": "é"})).json()["count"] == 2
+            r = await c.post("/v1/chat/completions", json={"messages": [{"role": "user", "content": "x"}], "temperature": 1})
+            assert r.status_code == 400 and r.json()["error"]["param"] == "temperature"
+            assert r.json()["error"]["type"] == "invalid_request_error"
+            r = await c.post("/v1/completions", content=b"{not json")
+            assert r.status_code == 400 and r.json()["error"]["code"] == "invalid_json"
+            r = await c.post("/v1/completions", json={"prompt": "x", "model": "other"})
+            assert r.status_code == 404
+    try:
+        run(main())
+    finally:
+        worker.stop()
+
+
+def test_sse_stream_framing_usage_and_stop_string():
+    worker, runner = make_worker()
+    app = build_app(worker)
+
+    async def main():
+        async with client(app) as c:
+            async with c.stream("POST", "/v1/chat/completions",
+                                json={"messages": [{"role": "user", "content": "hi"}], "max_tokens": 6, "stream": True,
+                                      "stream_options": {"include_usage": True}}) as r:
+                assert r.headers["content-type"].startswith("text/event-stream")
+                raw = (await r.aread()).decode()
+            events = [l[6:] for l in raw.split("\n\n") if l.startswith("data: ")]
+            assert events[-1] == "[DONE]"
+            objs = [json.loads(e) for e in events[:-1]]
+            assert objs[0]["choices"][0]["delta"] == {"role": "assistant", "content": ""}
+            text = "".join(o["choices"][0]["delta"].get("content", "") for o in objs if o["choices"])
+            assert len(text) == 6
+            fin = [o for o in objs if o["choices"] and o["choices"][0]["finish_reason"]]
+            assert len(fin) == 1 and fin[0]["choices"][0]["finish_reason"] == "length"
+            assert objs[-1]["choices"] == [] and objs[-1]["usage"]["completion_tokens"] == 6
+            assert all(o["object"] == "chat.completion.chunk" for o in objs)
+            # stop string: generation ends right after it
+            r = await c.post("/v1/completions", json={"prompt": "hello", "max_tokens": 40, "stop": [text[2:4]]})
+            # (different prompt, so just check the mechanism with its own output)
+            full = (await c.post("/v1/completions", json={"prompt": "hello", "max_tokens": 12})).json()["choices"][0]["text"]
+            r = await c.post("/v1/completions", json={"prompt": "hello", "max_tokens": 12, "stop": [full[3:5]]})
+            b = r.json()["choices"][0]
+            assert b["finish_reason"] == "stop" and b["text"] == full[:5]
+    try:
+        run(main())
+    finally:
+        worker.stop()
+
+
+def test_disconnect_cancels_and_fatal_latch():
+    slow = MockRunner(vocab=258, eos=257, next_token_fn=lambda t, p: 97 + (t + p) % 26)
+    worker, _ = make_worker(slow)
+    app = build_app(worker)
+
+    async def main():
+        async with client(app) as c:
+            stream = await worker.submit(text="abc", token_ids=None, max_tokens=400, stop=[])
+            first = await stream.next()
+            assert first.kind == "token"
+            stream.close()                                   # what the HTTP layer does on disconnect
+            for _ in range(200):
+                await asyncio.sleep(0.01)
+                if not worker._live:
+                    break
+            assert not worker._live
+            eng = worker.engine
+            assert eng.kv.stats().used_pages == 0
+            # fatal latch: the next engine step raises
+            orig = eng.step
+            eng.step = lambda emit: (_ for _ in ()).throw(RuntimeError("boom"))
+            s2 = await worker.submit(text="abc", token_ids=None, max_tokens=5, stop=[])
+            ev = await asyncio.wait_for(s2.next(), 5)
+            assert ev.kind == "error" and "boom" in ev.message
+            r = await c.post("/v1/completions", json={"prompt": "x"})
+            assert r.status_code == 503 and r.json()["error"]["code"] == "worker_failed"
+            assert (await c.get("/health")).status_code == 503
+            eng.step = orig
+    try:
+        run(main())
+    finally:
+        worker.stop()
+
+
+def test_slow_consumer_is_cancelled_and_admission_timeout():
+    worker, _ = make_worker(event_queue=4)
+
+    async def main():
+        s = await worker.submit(text="abc", token_ids=None, max_tokens=300, stop=[])
+        await asyncio.sleep(0.5)                               # never read: the queue fills, the worker cancels
+        kinds = []
+        while True:
+            ev = await asyncio.wait_for(s.next(), 5)
+            kinds.append(ev.kind)
+            if ev.kind != "token":
+                break
+        assert kinds[-1] == "finish" and ev.reason.value == "cancelled" and len(kinds) < 300
+    try:
+        run(main())
+    finally:
+        worker.stop()
