@@ -1,0 +1,404 @@
+"""Command line: `python -m ferrule_b200 <command>`.
+
+  info                 package, device and library status; model presets or a checkpoint's layout
+  cuda                 smoke benchmark of the native kernels (GEMV-sized GEMM, RMSNorm, launch overhead)
+  make-fixture         write a random-init (or zero) checkpoint directory in the HF DeepSeek layout
+  inspect-weightpack   tensor names / dtypes / shapes / inferred quant formats / role histogram
+  generate             load a checkpoint (or a random-init preset) and greedily generate from token ids or text
+  chat                 interactive REPL on top of the same engine
+  serve                OpenAI-compatible HTTP server
+  bench-interactive    multi-turn timing report (JSON) with engine, KV and speculative statistics
+  bench-serve          synthetic serving sweep against a running server (Poisson arrivals, shared prefixes)
+  expert-stream-smoke  stream routed experts of a checkpoint through the materialization stack
+
+Counterpart of crates/ferrule-cli/src/args.rs:34-230, commands/serve.rs:20-168,
+commands/bench_interactive.rs:57-235 and scripts/bench_vllm_serve.sh, dsv4_synthetic_fixture.py.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import time
+from typing import List, Optional
+
+
+def _add_model_args(p: argparse.ArgumentParser) -> None:
+    p.add_argument("--model-dir", help="HF checkpoint directory (config.json + safetensors)")
+    p.add_argument("--preset", default="tiny-fixture", help="random-init preset when no --model-dir is given")
+    p.add_argument("--device", default=None, help="cuda[:N] or cpu (default: cuda when available)")
+    p.add_argument("--kv-cache-mb", type=int, default=0, help="KV pool size; 0 = from --max-seqs x --ctx-size")
+    p.add_argument("--page-size", type=int, default=64)
+    p.add_argument("--ctx-size", type=int, default=4096)
+    p.add_argument("--max-seqs", type=int, default=32)
+    p.add_argument("--max-batch-tokens", type=int, default=2048)
+    p.add_argument("--prefill-chunk", type=int, default=512)
+    p.add_argument("--speculative", action="store_true")
+    p.add_argument("--max-draft", type=int, default=1)
+    p.add_argument("--seed", type=int, default=0)
+
+
+def build_engine(args):
+    """-> (engine, tokenizer, model name).  Shared by generate / chat / serve / bench-interactive."""
+    import torch
+
+    from ..models import config as C
+    from ..models import weights as W
+    from ..models.runner import DeepSeekRunner
+    from ..runtime.engine import Engine, EngineConfig
+    from ..runtime.scheduler import SchedulerConfig
+    from ..utils.tokenizer import load_tokenizer
+    dev = args.device or ("cuda" if torch.cuda.is_available() else "cpu")
+    if args.model_dir:
+        from ..io.checkpoint import load_deepseek_hf
+        weights = load_deepseek_hf(args.model_dir, device=dev, dtype=torch.bfloat16 if dev != "cpu" else torch.float32)
+        name = os.path.basename(os.path.normpath(args.model_dir))
+    else:
+        cfg = C.PRESETS[args.preset]()
+        weights = W.random_weights(cfg, device=dev, dtype=torch.bfloat16 if dev != "cpu" else torch.float32,
+                                   seed=args.seed, fast_device_init=dev != "cpu")
+        name = cfg.name
+    cfg = weights.cfg
+    ctx = min(args.ctx_size, cfg.max_position)
+    pages_per_seq = (ctx + args.page_size - 1) // args.page_size
+    if args.kv_cache_mb:
+        per_page = (cfg.n_layers + cfg.n_mtp_layers) * args.page_size * cfg.kv_row_dim * 2
+        n_pages = max(args.kv_cache_mb * (1 << 20) // per_page, pages_per_seq + 1)
+    else:
+        n_pages = args.max_seqs * pages_per_seq + 8
+    runner = DeepSeekRunner(weights, n_pages=n_pages, page_size=args.page_size, max_rows=args.max_batch_tokens,
+                            max_seqs=args.max_seqs, max_seq_len=pages_per_seq * args.page_size, device=dev)
+    sched = SchedulerConfig(max_active_sequences=args.max_seqs, max_decode_batch=args.max_seqs,
+                            max_batch_tokens=args.max_batch_tokens, prefill_chunk_size=args.prefill_chunk,
+                            ctx_size=pages_per_seq * args.page_size)
+    eng = Engine(runner, EngineConfig(scheduler=sched, kv_pages=n_pages, page_size=args.page_size,
+                                      speculative=args.speculative, max_draft=args.max_draft))
+    return eng, load_tokenizer(args.model_dir), name
+
+
+# ------------------------------------------------------------------------------------------ commands
+def cmd_info(args) -> int:
+    import torch
+
+    from .. import __version__, _build
+    from ..models import config as C
+    out = {"version": __version__, "torch": torch.__version__, "cuda_available": torch.cuda.is_available(),
+           "native_library": str(_build.LIB_PATH), "native_library_built": _build.LIB_PATH.exists(),
+           "native_library_current": _build.is_current()}
+    if torch.cuda.is_available():
+        p = torch.cuda.get_device_properties(0)
+        out["device"] = {"name": p.name, "sm": f"{p.major}{p.minor}", "sms": p.multi_processor_count,
+                         "memory_gb": round(p.total_memory / 2 ** 30, 1)}
+    if args.model_dir:
+        from ..io.safetensors import ShardedCheckpoint
+        from ..models.families import detect_family, layout_summary
+        ck = ShardedCheckpoint(args.model_dir)
+        cfg = C.from_hf_config(args.model_dir) if os.path.exists(os.path.join(args.model_dir, "config.json")) else None
+        fam = detect_family(ck.names(), cfg.name if cfg else "")
+        out["checkpoint"] = {"family": fam.value, "tensors": len(ck.names()), "shards": len(set(ck.weight_map.values())),
+                             "roles": layout_summary(ck.names(), fam, cfg.n_layers if cfg else None),
+                             "config": cfg.to_dict() if cfg else None}
+    else:
+        out["presets"] = {k: {"params_b": round(f().param_count() / 1e9, 3), "layers": f().n_layers,
+                              "hidden": f().hidden} for k, f in C.PRESETS.items()}
+    print(json.dumps(out, indent=1))
+    return 0
+
+
+def cmd_cuda(args) -> int:
+    import torch
+    if not torch.cuda.is_available():
+        print(json.dumps({"error": "no CUDA device"}))
+        return 1
+    from ..ops import kernels as K
+    dev = "cuda"
+
+    def timed(fn, n=50):
+        for _ in range(5):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / n * 1e3
+    res = {}
+    for rows, n, k in ((1, 4096, 4096), (32, 4096, 4096), (32, 16384, 4096)):
+        ws = [torch.randn(n, k, device=dev).bfloat16() for _ in range(8)]
+        x = torch.randn(rows, k, device=dev).bfloat16()
+        out = torch.empty(rows, n, device=dev, dtype=torch.bfloat16)
+        i = [0]
+
+        def f():
+            K.gemm(x, ws[i[0] % 8], out=out)
+            i[0] += 1
+        us = timed(f)
+        res[f"gemm_{rows}x{n}x{k}_us"] = round(us, 2)
+        res[f"gemm_{rows}x{n}x{k}_gbs"] = round(n * k * 2 / us / 1e3, 1)
+    x = torch.randn(32, 4096, device=dev).bfloat16()
+    w = torch.ones(4096, device=dev).bfloat16()
+    o = torch.empty_like(x)
+    res["rmsnorm_32x4096_us"] = round(timed(lambda: K.add_rmsnorm(x, w, 1e-6, norm_out=o)), 2)
+    ids = torch.zeros(1, dtype=torch.int32, device=dev)
+    tab = torch.zeros(8, 64, device=dev).bfloat16()
+    eo = torch.empty(1, 64, device=dev, dtype=torch.bfloat16)
+    res["launch_overhead_us"] = round(timed(lambda: K.embedding(ids, tab, out=eo), 200), 2)
+    print(json.dumps(res, indent=1))
+    return 0
+
+
+def cmd_make_fixture(args) -> int:
+    import torch
+
+    from ..io.checkpoint import export_hf
+    from ..models import config as C
+    from ..models import weights as W
+    cfg = C.PRESETS[args.preset]()
+    if args.layers:
+        cfg = cfg.with_(n_layers=args.layers)
+    w = W.random_weights(cfg, dtype=torch.bfloat16, seed=args.seed, std=0.0 if args.zeros else 0.02)
+    export_hf(w, args.out, dense_format=args.dense_format, expert_format=args.expert_format,
+              shard_bytes=args.shard_mb << 20)
+    print(json.dumps({"written": args.out, "params": cfg.param_count(), "dense_format": args.dense_format,
+                      "expert_format": args.expert_format}))
+    return 0
+
+
+def cmd_inspect(args) -> int:
+    from ..io.checkpoint import infer_weight_format
+    from ..io.safetensors import ShardedCheckpoint
+    from ..models.families import detect_family, layout_summary
+    ck = ShardedCheckpoint(args.model_dir)
+    fam = detect_family(ck.names())
+    rows, total = [], 0
+    for n in sorted(ck.names()):
+        i = ck.info(n)
+        total += i.nbytes
+        fmt = ""
+        if n.endswith(".weight"):
+            try:
+                fmt = infer_weight_format(ck, n[:-7])[0]
+            except Exception:  # noqa: BLE001
+                fmt = "?"
+        rows.append((n, i.dtype, list(i.shape), i.nbytes, fmt))
+    if args.json:
+        print(json.dumps({"family": fam.value, "bytes": total, "roles": layout_summary(ck.names(), fam),
+                          "tensors": [dict(name=r[0], dtype=r[1], shape=r[2], bytes=r[3], format=r[4]) for r in rows[:args.limit]]}))
+    else:
+        print(f"family {fam.value}, {len(rows)} tensors, {total / 2 ** 20:.1f} MiB")
+        for r in rows[:args.limit]:
+            print(f"{r[0]:70s} {r[1]:8s} {str(r[2]):20s} {r[4]}")
+    return 0
+
+
+def _collect(eng, emit_text=None):
+    from ..runtime.engine import FinishEvent, TokenEvent
+    toks, fin = {}, {}
+
+    def emit(ev):
+        if isinstance(ev, TokenEvent):
+            toks.setdefault(ev.request_id, []).append(ev.token)
+            if emit_text and ev.text:
+                emit_text(ev.text)
+        elif isinstance(ev, FinishEvent):
+            fin[ev.request_id] = ev
+    eng.run_until_idle(emit)
+    return toks, fin
+
+
+def cmd_generate(args) -> int:
+    from ..runtime.session import GenerateRequest
+    eng, tok, name = build_engine(args)
+    eng.detokenize = tok.decode
+    prompt = [int(t) for t in args.tokens.split(",")] if args.tokens else tok.encode(args.prompt)
+    prompt = [t % eng.runner.vocab_size for t in prompt]
+    t0 = time.perf_counter()
+    eng.submit(GenerateRequest("gen", prompt, max_new_tokens=args.max_tokens, ignore_eos=args.ignore_eos))
+    toks, fin = _collect(eng)
+    dt = time.perf_counter() - t0
+    f = fin["gen"]
+    print(json.dumps({"model": name, "prompt_tokens": len(prompt), "tokens": toks.get("gen", []), "text": f.text,
+                      "finish_reason": f.reason.openai(), "seconds": round(dt, 4), "ttft_s": round(f.ttft_s, 4),
+                      "tpot_s": round(f.tpot_s, 6)}))
+    return 0
+
+
+def cmd_chat(args) -> int:
+    from ..runtime.session import GenerateRequest
+    from ..utils.tokenizer import ChatMessage, render_chat, template_for_model
+    eng, tok, name = build_engine(args)
+    eng.detokenize = tok.decode
+    history: List[ChatMessage] = []
+    tmpl = template_for_model(name)
+    print(f"{name}: empty line or Ctrl-D to quit")
+    turn = 0
+    while True:
+        try:
+            line = input("> ")
+        except EOFError:
+            break
+        if not line.strip():
+            break
+        history.append(ChatMessage("user", line))
+        ids = [t % eng.runner.vocab_size for t in tok.encode(render_chat(history, tmpl))]
+        eng.submit(GenerateRequest(f"turn{turn}", ids, max_new_tokens=args.max_tokens))
+        _, fin = _collect(eng, lambda s: (sys.stdout.write(s), sys.stdout.flush()))
+        print()
+        history.append(ChatMessage("assistant", fin[f"turn{turn}"].text))
+        turn += 1
+    return 0
+
+
+def cmd_serve(args) -> int:
+    from ..server.http import serve
+    from ..server.worker import ModelWorker, WorkerConfig
+    from ..utils.observability import init_tracing, start_periodic_dump
+    init_tracing()
+    start_periodic_dump()
+    holder = {}
+
+    def factory():
+        eng, tok, name = build_engine(args)
+        holder["tok"], holder["name"] = tok, name
+        return eng
+    # the engine is built on the worker thread (it owns the CUDA context and every graph)
+    from ..utils.tokenizer import load_tokenizer
+    tok = load_tokenizer(args.model_dir)
+    worker = ModelWorker(factory, tok, WorkerConfig(command_queue=args.command_queue, event_queue=args.event_queue,
+                                                    admission_timeout_s=args.admission_timeout),
+                         model_name=args.served_name or args.preset).start()
+    print(json.dumps({"serving": holder.get("name"), "host": args.host, "port": args.port}), flush=True)
+    serve(worker, args.host, args.port, args.served_name or holder.get("name"))
+    return 0
+
+
+def cmd_bench_interactive(args) -> int:
+    import random
+
+    from ..runtime.session import GenerateRequest
+    eng, tok, name = build_engine(args)
+    rng = random.Random(args.seed)
+    V = eng.runner.vocab_size
+    report = {"report_version": 2, "model": name, "turns": []}
+    sid = "bench-session"
+    for turn in range(args.turns):
+        prompt = [rng.randrange(V) for _ in range(args.prompt_len)]
+        t0 = time.perf_counter()
+        eng.submit(GenerateRequest(f"t{turn}", prompt, max_new_tokens=args.max_tokens, ignore_eos=True,
+                                   session_id=sid, retain_session=True))
+        toks, fin = _collect(eng)
+        f = fin[f"t{turn}"]
+        report["turns"].append({"turn": turn, "prompt_tokens": f.prompt_tokens, "generated": f.generated_tokens,
+                                "seconds": round(time.perf_counter() - t0, 4), "ttft_s": round(f.ttft_s, 4),
+                                "tpot_s": round(f.tpot_s, 6), "tokens": toks.get(f"t{turn}", [])[:8]})
+    report["engine"] = eng.snapshot_stats()
+    report["runner"] = eng.runner.observability()
+    if args.golden:
+        golden = json.load(open(args.golden))
+        got = [t["tokens"] for t in report["turns"]]
+        want = [t["tokens"] for t in golden.get("turns", [])]
+        report["golden_match"] = got == want
+    eng.shutdown()
+    report["shutdown_residual"] = {"kv_used_pages": eng.kv.stats().used_pages, "grants": eng.broker.outstanding()}
+    print(json.dumps(report))
+    return 0 if report.get("golden_match", True) else 2
+
+
+def cmd_bench_serve(args) -> int:
+    from ..server.bench_serve import run_sweep
+    print(json.dumps(run_sweep(args.url, args.model, args.concurrency, args.requests, args.seed, args.vocab,
+                               args.min_in, args.max_in, args.min_out, args.max_out, args.shared_prefix,
+                               args.shared_fraction)))
+    return 0
+
+
+def cmd_expert_stream_smoke(args) -> int:
+    import torch
+
+    from ..io.safetensors import ShardedCheckpoint
+    from ..models import config as C
+    from ..runtime.expert_residency import ExpertResidencyController, plan_residency
+    from ..runtime.expert_streaming import (ExpertArena, ExpertMaterializationProvider, ExpertSourceCatalog,
+                                            HostStagedExpertCache, PinnedSlabPool)
+    from ..runtime.registry import LoadRegistry
+    cfg = C.from_hf_config(args.model_dir)
+    ck = ShardedCheckpoint(args.model_dir)
+    layers = [l for l in range(cfg.n_layers) if cfg.is_moe_layer(l)]
+    dev = args.device or ("cuda" if torch.cuda.is_available() else "cpu")
+    cat = ExpertSourceCatalog(cfg.name, ck, layers, cfg.n_routed_experts, backend=dev)
+    caps = plan_residency(args.device_mb << 20, cat.max_payload_bytes(), layers, cfg.n_routed_experts, cfg.topk,
+                          args.residency)
+    res = ExpertResidencyController(layers, caps, cfg.n_routed_experts)
+    arena = ExpertArena(layers, caps, cat.max_payload_bytes(), dev)
+    try:
+        from ..io.direct_reader import NativeDirectReader
+        reader = NativeDirectReader(args.threads)
+    except Exception:  # noqa: BLE001
+        reader = None
+    prov = ExpertMaterializationProvider(cat, res, arena, PinnedSlabPool(cat.max_payload_bytes(), args.slabs),
+                                         HostStagedExpertCache(args.host_cache_mb << 20, args.host_cache_mb << 20), reader)
+    reg = LoadRegistry(prov)
+    t0 = time.perf_counter()
+    want = [(l, e) for l in layers for e in range(min(caps[l], cfg.n_routed_experts))]
+    reg.register_continuation(0, [cat.key(l, e) for l, e in want])
+    while not reg._ready and not reg._failed and time.perf_counter() - t0 < args.timeout:
+        reg.drive()
+        time.sleep(0.0005)
+    dt = time.perf_counter() - t0
+    print(json.dumps({"experts": len(want), "ok": bool(reg._ready), "seconds": round(dt, 3),
+                      "gib_per_s": round(prov.bytes_uploaded / dt / 2 ** 30, 3), "bytes": prov.bytes_uploaded,
+                      "registry": vars(reg.stats), "slab_high_water": prov.slabs.high_water,
+                      "arena_mb": arena.nbytes() >> 20}))
+    prov.close()
+    return 0 if reg._ready else 1
+
+
+def main(argv: Optional[List[str]] = None) -> int:
+    ap = argparse.ArgumentParser(prog="ferrule_b200")
+    sub = ap.add_subparsers(dest="cmd", required=True)
+    p = sub.add_parser("info"); p.add_argument("--model-dir"); p.set_defaults(fn=cmd_info)
+    p = sub.add_parser("cuda"); p.set_defaults(fn=cmd_cuda)
+    p = sub.add_parser("make-fixture")
+    p.add_argument("--preset", default="tiny-fixture"); p.add_argument("--out", required=True)
+    p.add_argument("--layers", type=int, default=0); p.add_argument("--seed", type=int, default=0)
+    p.add_argument("--zeros", action="store_true"); p.add_argument("--shard-mb", type=int, default=1024)
+    p.add_argument("--dense-format", default="plain", choices=["plain", "fp8_block"])
+    p.add_argument("--expert-format", default="plain", choices=["plain", "fp8_block", "mxfp4"])
+    p.set_defaults(fn=cmd_make_fixture)
+    p = sub.add_parser("inspect-weightpack"); p.add_argument("model_dir"); p.add_argument("--json", action="store_true")
+    p.add_argument("--limit", type=int, default=40); p.set_defaults(fn=cmd_inspect)
+    p = sub.add_parser("generate"); _add_model_args(p)
+    p.add_argument("--prompt", default="hello"); p.add_argument("--tokens"); p.add_argument("--max-tokens", type=int, default=16)
+    p.add_argument("--ignore-eos", action="store_true"); p.set_defaults(fn=cmd_generate)
+    p = sub.add_parser("chat"); _add_model_args(p); p.add_argument("--max-tokens", type=int, default=128)
+    p.set_defaults(fn=cmd_chat)
+    p = sub.add_parser("serve"); _add_model_args(p)
+    p.add_argument("--host", default="127.0.0.1"); p.add_argument("--port", type=int, default=8000)
+    p.add_argument("--served-name"); p.add_argument("--command-queue", type=int, default=256)
+    p.add_argument("--event-queue", type=int, default=32); p.add_argument("--admission-timeout", type=float, default=30.0)
+    p.set_defaults(fn=cmd_serve)
+    p = sub.add_parser("bench-interactive"); _add_model_args(p)
+    p.add_argument("--turns", type=int, default=2); p.add_argument("--prompt-len", type=int, default=32)
+    p.add_argument("--max-tokens", type=int, default=16); p.add_argument("--golden"); p.set_defaults(fn=cmd_bench_interactive)
+    p = sub.add_parser("bench-serve")
+    p.add_argument("--url", default="http://127.0.0.1:8000"); p.add_argument("--model", default="")
+    p.add_argument("--concurrency", type=int, nargs="+", default=[1, 8, 32]); p.add_argument("--requests", type=int, default=64)
+    p.add_argument("--seed", type=int, default=0); p.add_argument("--vocab", type=int, default=1024)
+    p.add_argument("--min-in", type=int, default=128); p.add_argument("--max-in", type=int, default=8192)
+    p.add_argument("--min-out", type=int, default=64); p.add_argument("--max-out", type=int, default=1024)
+    p.add_argument("--shared-prefix", type=int, default=2048); p.add_argument("--shared-fraction", type=float, default=0.3)
+    p.set_defaults(fn=cmd_bench_serve)
+    p = sub.add_parser("expert-stream-smoke"); p.add_argument("model_dir"); p.add_argument("--device")
+    p.add_argument("--device-mb", type=int, default=1024); p.add_argument("--residency", type=float, default=0.5)
+    p.add_argument("--slabs", type=int, default=8); p.add_argument("--threads", type=int, default=4)
+    p.add_argument("--host-cache-mb", type=int, default=256); p.add_argument("--timeout", type=float, default=120.0)
+    p.set_defaults(fn=cmd_expert_stream_smoke)
+    args = ap.parse_args(argv)
+    return args.fn(args)
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,0 +1,33 @@
+"""Command-line entry points on the CPU."""
+import json
+import subprocess
+import sys
+
+
+def run(*args):
+    p = subprocess.run([sys.executable, "-m", "ferrule_b200", *args], capture_output=True, text=True, timeout=300)
+    assert p.returncode == 0, p.stderr[-2000:]
+    return p.stdout
+
+
+def test_cli_fixture_inspect_generate_bench(tmp_path):
+    d = str(tmp_path / "fx")
+    out = json.loads(run("make-fixture", "--out", d, "--expert-format", "mxfp4", "--dense-format", "fp8_block"))
+    assert out["params"] > 0
+    ins = json.loads(run("inspect-weightpack", d, "--json", "--limit", "500"))
+    fmts = {t["name"]: t["format"] for t in ins["tensors"]}
+    assert fmts["model.layers.1.mlp.experts.0.gate_proj.weight"] == "mxfp4"
+    assert fmts["model.layers.0.self_attn.o_proj.weight"] == "fp8_block" and ins["family"] == "deepseek_hf"
+    info = json.loads(run("info", "--model-dir", d))
+    assert info["checkpoint"]["roles"]["expert_gate"] == 16 and info["native_library_built"]
+    common = ["--device", "cpu", "--ctx-size", "256", "--max-seqs", "2", "--page-size", "16"]
+    g1 = json.loads(run("generate", "--model-dir", d, "--tokens", "5,6,7", "--max-tokens", "4", *common))
+    g2 = json.loads(run("generate", "--model-dir", d, "--tokens", "5,6,7", "--max-tokens", "4", *common))
+    assert g1["tokens"] == g2["tokens"] and len(g1["tokens"]) == 4 and g1["finish_reason"] == "length"
+    rep = json.loads(run("bench-interactive", "--preset", "tiny-fixture", "--turns", "2", "--prompt-len", "6",
+                         "--max-tokens", "3", *common))
+    assert rep["report_version"] == 2 and len(rep["turns"]) == 2
+    assert rep["turns"][1]["prompt_tokens"] > rep["turns"][0]["prompt_tokens"]        # the session was continued
+    assert rep["shutdown_residual"] == {"kv_used_pages": 0, "grants": 0}
+    sm = json.loads(run("expert-stream-smoke", d, "--device", "cpu", "--device-mb", "8"))
+    assert sm["ok"] and sm["registry"]["published"] == sm["experts"]
