@@ -19,7 +19,7 @@ def test_cli_fixture_inspect_generate_bench(tmp_path):
     assert fmts["model.layers.1.mlp.experts.0.gate_proj.weight"] == "mxfp4"
     assert fmts["model.layers.0.self_attn.o_proj.weight"] == "fp8_block" and ins["family"] == "deepseek_hf"
     info = json.loads(run("info", "--model-dir", d))
-    assert info["checkpoint"]["roles"]["expert_gate"] == 16 and info["native_library_built"]
+    assert info["checkpoint"]["roles"]["expert_gate"] == 32 and info["native_library_built"]
     common = ["--device", "cpu", "--ctx-size", "256", "--max-seqs", "2", "--page-size", "16"]
     g1 = json.loads(run("generate", "--model-dir", d, "--tokens", "5,6,7", "--max-tokens", "4", *common))
     g2 = json.loads(run("generate", "--model-dir", d, "--tokens", "5,6,7", "--max-tokens", "4", *common))
