@@ -145,6 +145,16 @@ int fb_topk_logits(const float* logits, long long ldl, int rows, int vocab, int 
 int fb_copy_pages(void* pool, long long layer_stride, long long page_elems, const int* pairs,
                   int n_pairs, int n_pages, int layers, void* status, void* stream);
 
+// ---- quantisation / packing ---------------------------------------------------------------
+int fb_quant_fp8_rows(const void* x, long long ldx, void* q, long long ldq, void* scale, long long lds,
+                      int rows, int n, int writeback_bf16, void* stream);
+int fb_dequant_fp8_block(const void* q, const void* scale, void* out, int rows, int cols, int block,
+                         void* stream);
+int fb_quant_mxfp4_rows(const void* x, long long ldx, void* packed, void* scale, int rows, int n,
+                        void* stream);
+int fb_dequant_mxfp4(const void* packed, const void* scale, void* out, int rows, int n, void* stream);
+int fb_hadamard_rows(void* x, long long ldx, int rows, int n, void* stream);
+
 // ---- peer memory and collectives --------------------------------------------------------
 int fb_ipc_handle_bytes(void);
 int fb_ipc_alloc(void** ptr, long long bytes, void* handle_out);   // zero-filled device buffer + IPC handle

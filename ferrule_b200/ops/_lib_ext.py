@@ -34,8 +34,9 @@ def declare(lib) -> None:
         # quant.cu
         "fb_quant_fp8_rows": ([vp, ll, vp, ll, vp, ll, i, i, i, vp], i),
         "fb_dequant_fp8_block": ([vp, vp, vp, i, i, i, vp], i),
-        "fb_dequant_mxfp4": ([vp, vp, vp, i, i, vp], i),
         "fb_quant_mxfp4_rows": ([vp, ll, vp, vp, i, i, vp], i),
+        "fb_dequant_mxfp4": ([vp, vp, vp, i, i, vp], i),
+        "fb_hadamard_rows": ([vp, ll, i, i, vp], i),
     }
     for name, (args, res) in table.items():
         if _has(lib, name):
