@@ -72,6 +72,40 @@ typedef struct FbGemmArgs {
 
 int fb_gemm_bf16(const FbGemmArgs* args, void* stream);
 
+// ---- block-scaled FP8 GEMM ---------------------------------------------------------------
+typedef struct FbGemmFp8Args {
+  const void* w;            // e4m3 [groups, w_rows_per_group, k]
+  const void* x;            // e4m3 [x_rows, k]
+  const void* w_scale;      // UE8M0 [groups, ceil(w_rows_per_group/128), ceil(k/128)]
+  const void* x_scale;      // UE8M0 [x_rows, ldxs] (one per 1 x 128 block)
+  void* out;
+  long long ldw;            // bytes = elements
+  long long w_group_stride;
+  long long ldx;
+  long long ldxs;
+  long long ldo;
+  int n_out;
+  int k;
+  int groups;
+  int w_rows_per_group;
+  int x_rows;
+  int ntok;                 // 16, 32 or 64 (swiglu: 16 or 32)
+  int epilogue;             // 0 store, 1 swiglu, 2 scatter
+  int dual_offset;          // multiple of 128
+  int out_fp32;
+  int max_tok_tiles;
+  const int* tile_group;
+  const int* tile_row0;
+  const int* tile_rows;
+  const int* num_tok_tiles;
+  const int* dst_row;
+  const float* row_scale;
+  float act_limit;
+  void* status;
+} FbGemmFp8Args;
+
+int fb_gemm_fp8(const FbGemmFp8Args* args, void* stream);
+
 // ---- paged latent-KV attention -------------------------------------------------------
 typedef struct FbAttnArgs {
   const void* q;            // bf16 [rows, heads, kv_lora + rope_dim]

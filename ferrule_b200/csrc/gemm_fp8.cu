@@ -1,0 +1,384 @@
+// Block-scaled FP8 (e4m3) weight-stationary GEMM for sm_100a, dense or grouped.
+//
+//   out[row, n] = sum_kb  sx[row, kb] * sw[g, n/128, kb] * sum_{k in block kb} X[row, k] * W[g, n, k]
+//
+// Weights: e4m3 [groups, N, K] with one UE8M0 scale per 128 x 128 block; activations: e4m3
+// [rows, K] with one UE8M0 scale per 1 x 128 block (fb_quant_fp8_rows).  Same orientation as the
+// bf16 kernel (weight tile = UMMA A operand, M = 128; rows = UMMA N), operands by TMA into
+// 128-byte-swizzled shared memory (one k-block = 128 fp8 = one swizzle row), `tcgen05.mma
+// kind::f8f6f4` (K = 32 per instruction).  Every 128-wide k-block is accumulated on its own into one
+// of four TMEM buffers; the epilogue warps drain a buffer while the next k-blocks are multiplied,
+// apply the two block scales in fp32 and keep the running sum in registers - the exact scaling
+// order of the reference (scale per block, single fp32 accumulation, one rounding at the end).
+// Epilogues: store, SwiGLU (gate / up weight tiles), weighted scatter.
+//
+// Counterpart of the reference's FP8 projection kernels
+// (crates/ferrule-backend/native/cuda/implementations/cutlass/capabilities/fp8_projection.cuh:421-497,
+// shared_ffn.cuh:477-594) and of the FP8 kinds of its row-dot linear (portable/entrypoints.cu:208-284).
+#include <cuda.h>
+
+#include "common.cuh"
+#include "ferrule_b200.h"
+#include "launch.cuh"
+
+namespace fb {
+namespace fp8 {
+
+constexpr int kTileN = 128;
+constexpr int kBlockK = 128;   // fp8 elements per k-block = 128 bytes = one swizzle row = one scale block
+constexpr int kUmmaK = 32;
+constexpr int kThreads = 192;
+constexpr int kAccBufs = 4;
+
+struct Params {
+  int n_out, k, n_tiles, dual_offset, dense_rows, max_tok_tiles, stages;
+  const int* tile_group;
+  const int* tile_row0;
+  const int* tile_rows;
+  const int* num_tok_tiles;
+  const uint8_t* w_scale;      // [groups, w_scale_rows, k_blocks]
+  int w_scale_rows;            // scale rows per group = ceil(weight rows per group / 128)
+  const uint8_t* x_scale;      // [rows, ldxs]
+  long long ldxs;
+  void* out;
+  long long ldo;
+  int out_fp32;
+  int epilogue;                // 0 store, 1 swiglu, 2 scatter
+  const int* dst_row;
+  const float* row_scale;
+  float act_limit;
+  DeviceStatus* status;
+};
+
+__device__ __forceinline__ float e8m0(uint8_t b) {
+  return b == 0 ? __uint_as_float(1u << 22) : __uint_as_float(static_cast<uint32_t>(b) << 23);
+}
+__device__ __forceinline__ float silu(float x) { return x / (1.f + __expf(-x)); }
+
+template <int NTOK, bool DUAL>
+struct Cfg {
+  static constexpr int kWBytes = kTileN * kBlockK;
+  static constexpr int kXBytes = NTOK * kBlockK;
+  static constexpr int kStageBytes = kWBytes * (DUAL ? 2 : 1) + kXBytes;
+  static constexpr int kAccCols = NTOK * (DUAL ? 2 : 1);
+  static constexpr int kTmemCols = kAccBufs * kAccCols < 32 ? 32 : kAccBufs * kAccCols;
+  static_assert(kTmemCols <= 512 && (kTmemCols & (kTmemCols - 1)) == 0, "TMEM budget");
+};
+
+template <int NTOK, bool DUAL>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
+                const Params p) {
+  using C = Cfg<NTOK, DUAL>;
+  pdl_launch_dependents();
+  extern __shared__ uint8_t smem_raw8[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw8) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  const int nstages = p.stages;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + nstages * C::kStageBytes);
+  uint64_t* full_bar = bars;
+  uint64_t* empty_bar = bars + nstages;
+  uint64_t* acc_full = bars + 2 * nstages;
+  uint64_t* acc_empty = acc_full + kAccBufs;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + kAccBufs);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+  uint8_t* xs_tile = reinterpret_cast<uint8_t*>(bars) + 256;      // [NTOK][k_blocks] activation scales of the tile
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < nstages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int a = 0; a < kAccBufs; ++a) {
+      mbar_init(&acc_full[a], 1);
+      mbar_init(&acc_empty[a], 4);
+    }
+    *abort_flag = 0;
+    fence_barrier_init();
+    tma_prefetch_desc(&tmap_w);
+    tma_prefetch_desc(&tmap_x);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, C::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  pdl_wait();
+
+  const bool grouped = p.tile_group != nullptr;
+  const int num_tok_tiles = grouped ? min(*p.num_tok_tiles, p.max_tok_tiles) : (p.dense_rows + NTOK - 1) / NTOK;
+  const int total = num_tok_tiles * p.n_tiles;
+  const int kblocks = (p.k + kBlockK - 1) / kBlockK;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int s = 0;
+      uint32_t ph = 0;
+      bool ok = true;
+      long long issued = 0;
+      for (int t = blockIdx.x; t < total && ok; t += gridDim.x) {
+        const int m = t / p.n_tiles, nt = t - m * p.n_tiles;
+        const int g = grouped ? p.tile_group[m] : 0;
+        const int row0 = grouped ? p.tile_row0[m] : m * NTOK;
+        for (int kb = 0; kb < kblocks; ++kb) {
+          ok = mbar_wait(&empty_bar[s], ph ^ 1u, abort_flag, p.status, 0x800);
+          if (!ok) break;
+          uint8_t* stage = smem + s * C::kStageBytes;
+          mbar_arrive_expect_tx(&full_bar[s], C::kStageBytes);
+          tma_load_3d(stage, &tmap_w, &full_bar[s], kb * kBlockK, nt * kTileN, g);
+          if (DUAL) tma_load_3d(stage + C::kWBytes, &tmap_w, &full_bar[s], kb * kBlockK, p.dual_offset + nt * kTileN, g);
+          tma_load_2d(stage + C::kWBytes * (DUAL ? 2 : 1), &tmap_x, &full_bar[s], kb * kBlockK, row0);
+          ++issued;
+          if (++s == nstages) { s = 0; ph ^= 1u; }
+        }
+      }
+      if (*abort_flag) {
+        const long long first = issued > nstages ? issued - nstages : 0;
+        for (long long i = first; i < issued; ++i) {
+          const uint64_t t0 = globaltimer_ns();
+          while (!mbar_try_wait(&full_bar[i % nstages], static_cast<uint32_t>((i / nstages) & 1)) &&
+                 globaltimer_ns() - t0 < 2000000ull) {
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc(kTileN, NTOK, 0, 0);   // e4m3 x e4m3 -> f32
+      int s = 0;
+      uint32_t ph = 0;
+      long long kbg = 0;    // k-blocks issued by this CTA: selects the TMEM buffer and its phase
+      bool ok = true;
+      for (int t = blockIdx.x; t < total && ok; t += gridDim.x) {
+        for (int kb = 0; kb < kblocks; ++kb, ++kbg) {
+          const int a = static_cast<int>(kbg % kAccBufs);
+          const uint32_t aph = static_cast<uint32_t>((kbg / kAccBufs) & 1);
+          ok = mbar_wait(&acc_empty[a], aph ^ 1u, abort_flag, p.status, 0x810);
+          if (!ok) break;
+          ok = mbar_wait(&full_bar[s], ph, abort_flag, p.status, 0x811);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t d0 = tmem_base + a * C::kAccCols;
+          const uint32_t sw = smem_u32(smem + s * C::kStageBytes);
+          const uint32_t sx = sw + C::kWBytes * (DUAL ? 2 : 1);
+#pragma unroll
+          for (int kk = 0; kk < kBlockK / kUmmaK; ++kk) {
+            const uint32_t koff = kk * kUmmaK;     // bytes (1 byte per element)
+            const uint64_t db = umma_desc_k128(sx + koff);
+            umma_f8(d0, umma_desc_k128(sw + koff), db, idesc, kk ? 1u : 0u);
+            if (DUAL) umma_f8(d0 + NTOK, umma_desc_k128(sw + C::kWBytes + koff), db, idesc, kk ? 1u : 0u);
+          }
+          umma_commit(&empty_bar[s]);
+          umma_commit(&acc_full[a]);
+          if (++s == nstages) { s = 0; ph ^= 1u; }
+        }
+      }
+    }
+  } else {
+    const int q = warp & 3;
+    const int ch = q * 32 + lane;
+    const int epi_tid = (warp - 2) * 32 + lane;
+    long long kbg = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < total && ok; t += gridDim.x) {
+      const int m = t / p.n_tiles, nt = t - m * p.n_tiles;
+      const int g = grouped ? p.tile_group[m] : 0;
+      const int row0 = grouped ? p.tile_row0[m] : m * NTOK;
+      const int rows = grouped ? min(p.tile_rows[m], NTOK) : min(NTOK, p.dense_rows - row0);
+      const int n = nt * kTileN + ch;
+      // activation scales of this tile -> shared memory (rows beyond the tile read as scale 0)
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      for (int i = epi_tid; i < NTOK * kblocks; i += 128) {
+        const int j = i / kblocks, kb = i - j * kblocks;
+        xs_tile[i] = j < rows ? p.x_scale[(row0 + j) * p.ldxs + kb] : 0;
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      const uint8_t* wsg = p.w_scale + (static_cast<size_t>(g) * p.w_scale_rows + nt) * kblocks;
+      const uint8_t* wsu = DUAL ? p.w_scale + (static_cast<size_t>(g) * p.w_scale_rows + p.dual_offset / 128 + nt) * kblocks
+                                : nullptr;
+      float acc[NTOK];
+      float accu[DUAL ? NTOK : 1];
+#pragma unroll
+      for (int j = 0; j < NTOK; ++j) acc[j] = 0.f;
+      if (DUAL) {
+#pragma unroll
+        for (int j = 0; j < NTOK; ++j) accu[j] = 0.f;
+      }
+      for (int kb = 0; kb < kblocks; ++kb, ++kbg) {
+        const int a = static_cast<int>(kbg % kAccBufs);
+        const uint32_t aph = static_cast<uint32_t>((kbg / kAccBufs) & 1);
+        ok = mbar_wait(&acc_full[a], aph, abort_flag, p.status, 0x820);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t tb = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + a * C::kAccCols;
+        const float swg = e8m0(wsg[kb]);
+        const float swu = DUAL ? e8m0(wsu[kb]) : 0.f;
+#pragma unroll
+        for (int c0 = 0; c0 < NTOK; c0 += 16) {
+          uint32_t v[16], u[16];
+          tmem_ld16(tb + c0, v);
+          if (DUAL) tmem_ld16(tb + NTOK + c0, u);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const float sxj = e8m0(xs_tile[(c0 + j) * kblocks + kb]);
+            acc[c0 + j] = fmaf(__uint_as_float(v[j]), swg * sxj, acc[c0 + j]);
+            if (DUAL) accu[c0 + j] = fmaf(__uint_as_float(u[j]), swu * sxj, accu[c0 + j]);
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&acc_empty[a]);
+      }
+      if (!ok) break;
+      if (n < p.n_out) {
+#pragma unroll
+        for (int j = 0; j < NTOK; ++j) {
+          if (j < rows) {
+            float x = acc[j];
+            if (DUAL) {
+              float up = accu[j];
+              if (p.act_limit > 0.f) {
+                x = fminf(x, p.act_limit);
+                up = fminf(fmaxf(up, -p.act_limit), p.act_limit);
+              }
+              x = silu(x) * up;
+            }
+            long long orow = row0 + j;
+            if (p.epilogue == 2) {
+              if (p.row_scale) x *= p.row_scale[row0 + j];
+              if (p.dst_row) orow = p.dst_row[row0 + j];
+            }
+            if (p.out_fp32) reinterpret_cast<float*>(p.out)[orow * p.ldo + n] = x;
+            else reinterpret_cast<__nv_bfloat16*>(p.out)[orow * p.ldo + n] = __float2bfloat16_rn(x);
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, C::kTmemCols);
+  }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encoder() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  }
+  return fn;
+}
+
+static int make_map_u8(CUtensorMap* map, const void* base, uint64_t k, uint64_t rows, uint64_t groups,
+                       uint64_t row_stride, uint64_t group_stride, uint32_t box_rows, int rank) {
+  EncodeTiledFn fn = encoder();
+  if (!fn) return FB_ERR_DRIVER;
+  if ((reinterpret_cast<uintptr_t>(base) & 15) || (row_stride & 15) || (group_stride & 15)) return FB_ERR_ALIGN;
+  cuuint64_t dims[3] = {k, rows, groups};
+  cuuint64_t strides[2] = {row_stride, group_stride};
+  cuuint32_t box[3] = {static_cast<cuuint32_t>(kBlockK), box_rows, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, rank, const_cast<void*>(base), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS ? FB_OK : FB_ERR_DRIVER;
+}
+
+template <int NTOK, bool DUAL>
+static int launch(const CUtensorMap& mw, const CUtensorMap& mx, Params p, int max_tiles, int kblocks,
+                  cudaStream_t stream) {
+  using C = Cfg<NTOK, DUAL>;
+  auto kern = gemm_fp8_kernel<NTOK, DUAL>;
+  constexpr int kLimit = 227 * 1024;
+  static bool attr = false;
+  if (!attr) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kLimit) != cudaSuccess)
+      return FB_ERR_LAUNCH;
+    attr = true;
+  }
+  const int xs_bytes = (NTOK * kblocks + 15) / 16 * 16;
+  int stages = (kLimit - 2048 - xs_bytes) / C::kStageBytes;
+  if (stages > 10) stages = 10;
+  if (stages < 2) return FB_ERR_SHAPE;
+  p.stages = stages;
+  const size_t smem = static_cast<size_t>(stages) * C::kStageBytes + 1024 + 256 + xs_bytes;
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const int grid = max_tiles < sms ? (max_tiles < 1 ? 1 : max_tiles) : sms;
+  if (launch_pdl(kern, dim3(grid), dim3(kThreads), smem, stream, mw, mx, p) != cudaSuccess) return FB_ERR_LAUNCH;
+  return cudaGetLastError() == cudaSuccess ? FB_OK : FB_ERR_LAUNCH;
+}
+
+}  // namespace fp8
+}  // namespace fb
+
+using namespace fb;
+using namespace fb::fp8;
+
+extern "C" int fb_gemm_fp8(const FbGemmFp8Args* a, void* stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (!a || !a->w || !a->x || !a->out || !a->w_scale || !a->x_scale) return FB_ERR_SHAPE;
+  if (a->n_out <= 0 || a->k <= 0 || a->k % 16 != 0 || a->groups <= 0 || a->x_rows <= 0) return FB_ERR_SHAPE;
+  if (a->epilogue < 0 || a->epilogue > 2) return FB_ERR_SHAPE;
+  const bool dual = a->epilogue == 1;
+  if (a->ntok != 16 && a->ntok != 32 && a->ntok != 64) return FB_ERR_SHAPE;
+  if (dual && (a->ntok > 32 || a->dual_offset % 128 != 0)) return FB_ERR_SHAPE;
+  const bool grouped = a->tile_group != nullptr;
+  if (grouped && (!a->tile_row0 || !a->tile_rows || !a->num_tok_tiles || a->max_tok_tiles <= 0)) return FB_ERR_SHAPE;
+  if (!grouped && a->groups != 1) return FB_ERR_SHAPE;
+  CUtensorMap mw, mx;
+  int rc = make_map_u8(&mw, a->w, a->k, a->w_rows_per_group, a->groups, a->ldw, a->w_group_stride, kTileN, 3);
+  if (rc != FB_OK) return rc;
+  rc = make_map_u8(&mx, a->x, a->k, a->x_rows, 1, a->ldx, 0, a->ntok, 2);
+  if (rc != FB_OK) return rc;
+  Params p{};
+  p.n_out = a->n_out;
+  p.k = a->k;
+  p.n_tiles = (a->n_out + kTileN - 1) / kTileN;
+  p.dual_offset = a->dual_offset;
+  p.dense_rows = a->x_rows;
+  p.max_tok_tiles = a->max_tok_tiles;
+  p.tile_group = a->tile_group;
+  p.tile_row0 = a->tile_row0;
+  p.tile_rows = a->tile_rows;
+  p.num_tok_tiles = a->num_tok_tiles;
+  p.w_scale = static_cast<const uint8_t*>(a->w_scale);
+  p.w_scale_rows = (a->w_rows_per_group + 127) / 128;
+  p.x_scale = static_cast<const uint8_t*>(a->x_scale);
+  p.ldxs = a->ldxs;
+  p.out = a->out;
+  p.ldo = a->ldo;
+  p.out_fp32 = a->out_fp32;
+  p.epilogue = a->epilogue;
+  p.dst_row = a->dst_row;
+  p.row_scale = a->row_scale;
+  p.act_limit = a->act_limit;
+  p.status = static_cast<DeviceStatus*>(a->status);
+  const int kblocks = (a->k + kBlockK - 1) / kBlockK;
+  const int tok_tiles = grouped ? a->max_tok_tiles : (a->x_rows + a->ntok - 1) / a->ntok;
+  const int max_tiles = tok_tiles * p.n_tiles;
+  if (dual) {
+    if (a->ntok == 16) return launch<16, true>(mw, mx, p, max_tiles, kblocks, stream);
+    return launch<32, true>(mw, mx, p, max_tiles, kblocks, stream);
+  }
+  switch (a->ntok) {
+    case 16: return launch<16, false>(mw, mx, p, max_tiles, kblocks, stream);
+    case 32: return launch<32, false>(mw, mx, p, max_tiles, kblocks, stream);
+    default: return launch<64, false>(mw, mx, p, max_tiles, kblocks, stream);
+  }
+}

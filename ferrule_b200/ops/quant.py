@@ -5,7 +5,9 @@ from typing import Optional, Tuple
 
 import torch
 
-from ._lib import check, get_lib, ptr, stream_ptr
+import ctypes as C
+
+from ._lib import check, get_lib, ptr, status_tensor, stream_ptr
 
 
 def quant_fp8_rows(x: torch.Tensor, writeback: bool = False) -> Tuple[torch.Tensor, torch.Tensor]:
@@ -60,3 +62,58 @@ def hadamard_(x: torch.Tensor) -> torch.Tensor:
     rows, n = x.shape
     check(lib.fb_hadamard_rows(x.data_ptr(), x.stride(0), rows, n, stream_ptr()), "fb_hadamard_rows")
     return x
+
+
+class GemmFp8Args(C.Structure):
+    _fields_ = [
+        ("w", C.c_void_p), ("x", C.c_void_p), ("w_scale", C.c_void_p), ("x_scale", C.c_void_p), ("out", C.c_void_p),
+        ("ldw", C.c_longlong), ("w_group_stride", C.c_longlong), ("ldx", C.c_longlong), ("ldxs", C.c_longlong),
+        ("ldo", C.c_longlong),
+        ("n_out", C.c_int), ("k", C.c_int), ("groups", C.c_int), ("w_rows_per_group", C.c_int), ("x_rows", C.c_int),
+        ("ntok", C.c_int), ("epilogue", C.c_int), ("dual_offset", C.c_int), ("out_fp32", C.c_int),
+        ("max_tok_tiles", C.c_int),
+        ("tile_group", C.c_void_p), ("tile_row0", C.c_void_p), ("tile_rows", C.c_void_p), ("num_tok_tiles", C.c_void_p),
+        ("dst_row", C.c_void_p), ("row_scale", C.c_void_p), ("act_limit", C.c_float), ("status", C.c_void_p),
+    ]
+
+
+def gemm_fp8(xq: torch.Tensor, xs: torch.Tensor, wq: torch.Tensor, ws: torch.Tensor, out: Optional[torch.Tensor] = None,
+             *, out_dtype=torch.bfloat16, epilogue: int = 0, plan=None, scatter_rows: Optional[int] = None,
+             act_limit: float = 0.0, ntok: Optional[int] = None) -> torch.Tensor:
+    """Block-scaled FP8 GEMM on the tcgen05 path.
+
+    xq uint8 e4m3 [rows, K] + xs UE8M0 [rows, K/128]; wq uint8 e4m3 [N, K] or [groups, N, K] + ws UE8M0
+    [(groups,) ceil(N/128), ceil(K/128)].  epilogue 0 store, 1 SwiGLU (rows = [gate | up]), 2 scatter (plan).
+    """
+    lib = get_lib(True)
+    if not hasattr(lib.fb_gemm_fp8, "_declared"):
+        lib.fb_gemm_fp8.argtypes = [C.POINTER(GemmFp8Args), C.c_void_p]
+        lib.fb_gemm_fp8.restype = C.c_int
+        lib.fb_gemm_fp8._declared = True
+    if wq.dim() == 2:
+        wq, ws = wq.unsqueeze(0), ws.unsqueeze(0)
+    groups, w_rows, K = wq.shape
+    rows = xq.shape[0]
+    dual = epilogue == 1
+    n_out = w_rows // 2 if dual else w_rows
+    if ntok is None:
+        ntok = plan.ntok if plan is not None else (16 if rows <= 16 else (32 if (rows <= 32 or dual) else 64))
+    if out is None:
+        orow = scatter_rows if (epilogue == 2 and scatter_rows) else rows
+        out = torch.empty(orow, n_out, dtype=out_dtype, device=xq.device)
+    a = GemmFp8Args()
+    a.w, a.x, a.w_scale, a.x_scale, a.out = wq.data_ptr(), xq.data_ptr(), ws.data_ptr(), xs.data_ptr(), out.data_ptr()
+    a.ldw, a.w_group_stride, a.ldx, a.ldxs, a.ldo = wq.stride(1), wq.stride(0), xq.stride(0), xs.stride(0), out.stride(0)
+    a.n_out, a.k, a.groups, a.w_rows_per_group, a.x_rows = n_out, K, groups, w_rows, rows
+    a.ntok, a.epilogue, a.dual_offset = ntok, epilogue, (w_rows // 2 if dual else 0)
+    a.out_fp32 = 1 if out.dtype == torch.float32 else 0
+    a.act_limit = act_limit
+    if plan is not None:
+        a.max_tok_tiles = plan.max_tiles
+        a.tile_group, a.tile_row0, a.tile_rows = plan.tile_group.data_ptr(), plan.tile_row0.data_ptr(), plan.tile_rows.data_ptr()
+        a.num_tok_tiles = plan.meta.data_ptr()
+        if epilogue == 2:
+            a.dst_row, a.row_scale = plan.dst_row.data_ptr(), plan.row_scale.data_ptr()
+    a.status = status_tensor(xq.device).data_ptr()
+    check(lib.fb_gemm_fp8(C.byref(a), stream_ptr()), "fb_gemm_fp8")
+    return out
