@@ -101,6 +101,7 @@ typedef struct FbGemmFp8Args {
   const int* dst_row;
   const float* row_scale;
   float act_limit;
+  int scale_group32;        // 1: w_scale is UE8M0 [groups, w_rows_per_group, k/32] (MXFP4 values in e4m3 containers)
   void* status;
 } FbGemmFp8Args;
 

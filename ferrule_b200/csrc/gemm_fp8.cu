@@ -12,6 +12,10 @@
 // order of the reference (scale per block, single fp32 accumulation, one rounding at the end).
 // Epilogues: store, SwiGLU (gate / up weight tiles), weighted scatter.
 //
+// `scale_group32`: the weight scales are per row and per 32 elements (MXFP4: e2m1 values, which e4m3
+// represents exactly, expanded to one byte each at load time).  Each K = 32 instruction of a k-block then
+// writes its own accumulator and the epilogue applies the lane's own group scale.
+//
 // Counterpart of the reference's FP8 projection kernels
 // (crates/ferrule-backend/native/cuda/implementations/cutlass/capabilities/fp8_projection.cuh:421-497,
 // shared_ffn.cuh:477-594) and of the FP8 kinds of its row-dot linear (portable/entrypoints.cu:208-284).
@@ -38,6 +42,7 @@ struct Params {
   const int* num_tok_tiles;
   const uint8_t* w_scale;      // [groups, w_scale_rows, k_blocks]
   int w_scale_rows;            // scale rows per group = ceil(weight rows per group / 128)
+  int w_rows_total;            // weight rows per group (G32: scales are [groups, rows, k/32])
   const uint8_t* x_scale;      // [rows, ldxs]
   long long ldxs;
   void* out;
@@ -55,21 +60,26 @@ __device__ __forceinline__ float e8m0(uint8_t b) {
 }
 __device__ __forceinline__ float silu(float x) { return x / (1.f + __expf(-x)); }
 
-template <int NTOK, bool DUAL>
+template <int NTOK, bool DUAL, bool G32>
 struct Cfg {
   static constexpr int kWBytes = kTileN * kBlockK;
   static constexpr int kXBytes = NTOK * kBlockK;
   static constexpr int kStageBytes = kWBytes * (DUAL ? 2 : 1) + kXBytes;
-  static constexpr int kAccCols = NTOK * (DUAL ? 2 : 1);
-  static constexpr int kTmemCols = kAccBufs * kAccCols < 32 ? 32 : kAccBufs * kAccCols;
+  // G32 (weights scaled per row and per 32 elements, i.e. MXFP4 values held in e4m3 containers): each of the
+  // four K = 32 instructions of a k-block gets its own accumulator so the epilogue can scale them apart.
+  static constexpr int kSub = G32 ? 4 : 1;
+  static constexpr int kRing = G32 ? 2 : kAccBufs;             // k-blocks in flight between MMA and epilogue
+  static constexpr int kSubCols = NTOK * (DUAL ? 2 : 1);
+  static constexpr int kAccCols = kSubCols * kSub;             // TMEM columns per ring slot
+  static constexpr int kTmemCols = kRing * kAccCols < 32 ? 32 : kRing * kAccCols;
   static_assert(kTmemCols <= 512 && (kTmemCols & (kTmemCols - 1)) == 0, "TMEM budget");
 };
 
-template <int NTOK, bool DUAL>
+template <int NTOK, bool DUAL, bool G32>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
                 const Params p) {
-  using C = Cfg<NTOK, DUAL>;
+  using C = Cfg<NTOK, DUAL, G32>;
   pdl_launch_dependents();
   extern __shared__ uint8_t smem_raw8[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw8) + 1023) &
@@ -79,7 +89,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
   uint64_t* full_bar = bars;
   uint64_t* empty_bar = bars + nstages;
   uint64_t* acc_full = bars + 2 * nstages;
-  uint64_t* acc_empty = acc_full + kAccBufs;
+  uint64_t* acc_empty = acc_full + kAccBufs;   // kRing <= kAccBufs slots are used
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + kAccBufs);
   volatile uint32_t* abort_flag = tmem_slot + 1;
   uint8_t* xs_tile = reinterpret_cast<uint8_t*>(bars) + 256;      // [NTOK][k_blocks] activation scales of the tile
@@ -155,8 +165,8 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
       bool ok = true;
       for (int t = blockIdx.x; t < total && ok; t += gridDim.x) {
         for (int kb = 0; kb < kblocks; ++kb, ++kbg) {
-          const int a = static_cast<int>(kbg % kAccBufs);
-          const uint32_t aph = static_cast<uint32_t>((kbg / kAccBufs) & 1);
+          const int a = static_cast<int>(kbg % C::kRing);
+          const uint32_t aph = static_cast<uint32_t>((kbg / C::kRing) & 1);
           ok = mbar_wait(&acc_empty[a], aph ^ 1u, abort_flag, p.status, 0x810);
           if (!ok) break;
           ok = mbar_wait(&full_bar[s], ph, abort_flag, p.status, 0x811);
@@ -169,8 +179,10 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
           for (int kk = 0; kk < kBlockK / kUmmaK; ++kk) {
             const uint32_t koff = kk * kUmmaK;     // bytes (1 byte per element)
             const uint64_t db = umma_desc_k128(sx + koff);
-            umma_f8(d0, umma_desc_k128(sw + koff), db, idesc, kk ? 1u : 0u);
-            if (DUAL) umma_f8(d0 + NTOK, umma_desc_k128(sw + C::kWBytes + koff), db, idesc, kk ? 1u : 0u);
+            const uint32_t dk = d0 + (G32 ? kk * C::kSubCols : 0);
+            const uint32_t accf = (G32 || kk == 0) ? 0u : 1u;
+            umma_f8(dk, umma_desc_k128(sw + koff), db, idesc, accf);
+            if (DUAL) umma_f8(dk + NTOK, umma_desc_k128(sw + C::kWBytes + koff), db, idesc, accf);
           }
           umma_commit(&empty_bar[s]);
           umma_commit(&acc_full[a]);
@@ -209,25 +221,39 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
         for (int j = 0; j < NTOK; ++j) accu[j] = 0.f;
       }
       for (int kb = 0; kb < kblocks; ++kb, ++kbg) {
-        const int a = static_cast<int>(kbg % kAccBufs);
-        const uint32_t aph = static_cast<uint32_t>((kbg / kAccBufs) & 1);
+        const int a = static_cast<int>(kbg % C::kRing);
+        const uint32_t aph = static_cast<uint32_t>((kbg / C::kRing) & 1);
         ok = mbar_wait(&acc_full[a], aph, abort_flag, p.status, 0x820);
         if (!ok) break;
         tc_fence_after();
         const uint32_t tb = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + a * C::kAccCols;
-        const float swg = e8m0(wsg[kb]);
-        const float swu = DUAL ? e8m0(wsu[kb]) : 0.f;
+        uint32_t g4 = 0, u4 = 0;     // G32: this lane's four group scales of the k-block (one per K = 32 slice)
+        if (G32) {
+          const size_t srow = static_cast<size_t>(g) * p.w_rows_total + static_cast<size_t>(nt) * kTileN + ch;
+          const int sw_cols = kblocks * 4;
+          const bool row_ok = nt * kTileN + ch < p.w_rows_total;
+          g4 = row_ok ? *reinterpret_cast<const uint32_t*>(p.w_scale + srow * sw_cols + kb * 4) : 0u;
+          if (DUAL) {
+            const bool rowu_ok = p.dual_offset + nt * kTileN + ch < p.w_rows_total;
+            u4 = rowu_ok ? *reinterpret_cast<const uint32_t*>(p.w_scale + (srow + p.dual_offset) * sw_cols + kb * 4) : 0u;
+          }
+        }
 #pragma unroll
-        for (int c0 = 0; c0 < NTOK; c0 += 16) {
-          uint32_t v[16], u[16];
-          tmem_ld16(tb + c0, v);
-          if (DUAL) tmem_ld16(tb + NTOK + c0, u);
-          tmem_ld_wait();
+        for (int sub = 0; sub < C::kSub; ++sub) {
+          const float swg = G32 ? e8m0(static_cast<uint8_t>(g4 >> (8 * sub))) : e8m0(wsg[kb]);
+          const float swu = DUAL ? (G32 ? e8m0(static_cast<uint8_t>(u4 >> (8 * sub))) : e8m0(wsu[kb])) : 0.f;
 #pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            const float sxj = e8m0(xs_tile[(c0 + j) * kblocks + kb]);
-            acc[c0 + j] = fmaf(__uint_as_float(v[j]), swg * sxj, acc[c0 + j]);
-            if (DUAL) accu[c0 + j] = fmaf(__uint_as_float(u[j]), swu * sxj, accu[c0 + j]);
+          for (int c0 = 0; c0 < NTOK; c0 += 16) {
+            uint32_t v[16], u[16];
+            tmem_ld16(tb + sub * C::kSubCols + c0, v);
+            if (DUAL) tmem_ld16(tb + sub * C::kSubCols + NTOK + c0, u);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const float sxj = e8m0(xs_tile[(c0 + j) * kblocks + kb]);
+              acc[c0 + j] = fmaf(__uint_as_float(v[j]), swg * sxj, acc[c0 + j]);
+              if (DUAL) accu[c0 + j] = fmaf(__uint_as_float(u[j]), swu * sxj, accu[c0 + j]);
+            }
           }
         }
         tc_fence_before();
@@ -298,11 +324,11 @@ static int make_map_u8(CUtensorMap* map, const void* base, uint64_t k, uint64_t 
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS ? FB_OK : FB_ERR_DRIVER;
 }
 
-template <int NTOK, bool DUAL>
+template <int NTOK, bool DUAL, bool G32>
 static int launch(const CUtensorMap& mw, const CUtensorMap& mx, Params p, int max_tiles, int kblocks,
                   cudaStream_t stream) {
-  using C = Cfg<NTOK, DUAL>;
-  auto kern = gemm_fp8_kernel<NTOK, DUAL>;
+  using C = Cfg<NTOK, DUAL, G32>;
+  auto kern = gemm_fp8_kernel<NTOK, DUAL, G32>;
   constexpr int kLimit = 227 * 1024;
   static bool attr = false;
   if (!attr) {
@@ -359,6 +385,7 @@ extern "C" int fb_gemm_fp8(const FbGemmFp8Args* a, void* stream_) {
   p.num_tok_tiles = a->num_tok_tiles;
   p.w_scale = static_cast<const uint8_t*>(a->w_scale);
   p.w_scale_rows = (a->w_rows_per_group + 127) / 128;
+  p.w_rows_total = a->w_rows_per_group;
   p.x_scale = static_cast<const uint8_t*>(a->x_scale);
   p.ldxs = a->ldxs;
   p.out = a->out;
@@ -372,13 +399,19 @@ extern "C" int fb_gemm_fp8(const FbGemmFp8Args* a, void* stream_) {
   const int kblocks = (a->k + kBlockK - 1) / kBlockK;
   const int tok_tiles = grouped ? a->max_tok_tiles : (a->x_rows + a->ntok - 1) / a->ntok;
   const int max_tiles = tok_tiles * p.n_tiles;
+  const bool g32 = a->scale_group32 != 0;
+  if (g32 && (a->k % 128 != 0 || a->ntok > 32)) return FB_ERR_SHAPE;
   if (dual) {
-    if (a->ntok == 16) return launch<16, true>(mw, mx, p, max_tiles, kblocks, stream);
-    return launch<32, true>(mw, mx, p, max_tiles, kblocks, stream);
+    if (g32) return a->ntok == 16 ? launch<16, true, true>(mw, mx, p, max_tiles, kblocks, stream)
+                                  : launch<32, true, true>(mw, mx, p, max_tiles, kblocks, stream);
+    return a->ntok == 16 ? launch<16, true, false>(mw, mx, p, max_tiles, kblocks, stream)
+                         : launch<32, true, false>(mw, mx, p, max_tiles, kblocks, stream);
   }
+  if (g32) return a->ntok == 16 ? launch<16, false, true>(mw, mx, p, max_tiles, kblocks, stream)
+                                : launch<32, false, true>(mw, mx, p, max_tiles, kblocks, stream);
   switch (a->ntok) {
-    case 16: return launch<16, false>(mw, mx, p, max_tiles, kblocks, stream);
-    case 32: return launch<32, false>(mw, mx, p, max_tiles, kblocks, stream);
-    default: return launch<64, false>(mw, mx, p, max_tiles, kblocks, stream);
+    case 16: return launch<16, false, false>(mw, mx, p, max_tiles, kblocks, stream);
+    case 32: return launch<32, false, false>(mw, mx, p, max_tiles, kblocks, stream);
+    default: return launch<64, false, false>(mw, mx, p, max_tiles, kblocks, stream);
   }
 }

@@ -73,13 +73,14 @@ class GemmFp8Args(C.Structure):
         ("ntok", C.c_int), ("epilogue", C.c_int), ("dual_offset", C.c_int), ("out_fp32", C.c_int),
         ("max_tok_tiles", C.c_int),
         ("tile_group", C.c_void_p), ("tile_row0", C.c_void_p), ("tile_rows", C.c_void_p), ("num_tok_tiles", C.c_void_p),
-        ("dst_row", C.c_void_p), ("row_scale", C.c_void_p), ("act_limit", C.c_float), ("status", C.c_void_p),
+        ("dst_row", C.c_void_p), ("row_scale", C.c_void_p), ("act_limit", C.c_float), ("scale_group32", C.c_int),
+        ("status", C.c_void_p),
     ]
 
 
 def gemm_fp8(xq: torch.Tensor, xs: torch.Tensor, wq: torch.Tensor, ws: torch.Tensor, out: Optional[torch.Tensor] = None,
              *, out_dtype=torch.bfloat16, epilogue: int = 0, plan=None, scatter_rows: Optional[int] = None,
-             act_limit: float = 0.0, ntok: Optional[int] = None) -> torch.Tensor:
+             act_limit: float = 0.0, ntok: Optional[int] = None, group32: bool = False) -> torch.Tensor:
     """Block-scaled FP8 GEMM on the tcgen05 path.
 
     xq uint8 e4m3 [rows, K] + xs UE8M0 [rows, K/128]; wq uint8 e4m3 [N, K] or [groups, N, K] + ws UE8M0
@@ -97,7 +98,7 @@ def gemm_fp8(xq: torch.Tensor, xs: torch.Tensor, wq: torch.Tensor, ws: torch.Ten
     dual = epilogue == 1
     n_out = w_rows // 2 if dual else w_rows
     if ntok is None:
-        ntok = plan.ntok if plan is not None else (16 if rows <= 16 else (32 if (rows <= 32 or dual) else 64))
+        ntok = plan.ntok if plan is not None else (16 if rows <= 16 else (32 if (rows <= 32 or dual or group32) else 64))
     if out is None:
         orow = scatter_rows if (epilogue == 2 and scatter_rows) else rows
         out = torch.empty(orow, n_out, dtype=out_dtype, device=xq.device)
@@ -108,6 +109,7 @@ def gemm_fp8(xq: torch.Tensor, xs: torch.Tensor, wq: torch.Tensor, ws: torch.Ten
     a.ntok, a.epilogue, a.dual_offset = ntok, epilogue, (w_rows // 2 if dual else 0)
     a.out_fp32 = 1 if out.dtype == torch.float32 else 0
     a.act_limit = act_limit
+    a.scale_group32 = 1 if group32 else 0
     if plan is not None:
         a.max_tok_tiles = plan.max_tiles
         a.tile_group, a.tile_row0, a.tile_rows = plan.tile_group.data_ptr(), plan.tile_row0.data_ptr(), plan.tile_rows.data_ptr()
@@ -117,3 +119,10 @@ def gemm_fp8(xq: torch.Tensor, xs: torch.Tensor, wq: torch.Tensor, ws: torch.Ten
     a.status = status_tensor(xq.device).data_ptr()
     check(lib.fb_gemm_fp8(C.byref(a), stream_ptr()), "fb_gemm_fp8")
     return out
+
+
+def mxfp4_to_e4m3_containers(packed: torch.Tensor) -> torch.Tensor:
+    """Packed e2m1 [.., n/2] -> uint8 e4m3 codes [.., n] holding exactly the same values (load-time expansion
+    for the group-scaled FP8 GEMM)."""
+    from ..io import encoding as enc
+    return enc.e4m3_encode(enc.fp4_unpack(packed.cpu())).to(packed.device)

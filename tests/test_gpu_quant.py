@@ -110,3 +110,21 @@ def test_gemm_fp8_swiglu_and_grouped_scatter():
         wd = enc.weight_dequant_fp8_block(*packs[e])
         exp[route] = (wd @ xgd[pos]) * float(wts.flatten()[route])
     assert float((out.cpu() - exp).abs().max()) <= 3e-3 * float(exp.abs().max()) + 1e-4
+
+
+@pytest.mark.parametrize("rows,n,k,dual", [(32, 1408, 2048, False), (7, 256, 512, True), (32, 2048, 1408 - 1408 % 128, False)])
+def test_gemm_mxfp4_weights_group_scaled(rows, n, k, dual):
+    """MXFP4 weights (e2m1 + UE8M0 per 32) expanded to e4m3 containers, FP8 activations."""
+    from ferrule_b200.ops import quant as Q
+    from ferrule_b200.ops import reference as ref
+    x = rnd(rows, k, scale=1.5, seed=41)
+    xq, xs = Q.quant_fp8_rows(x)
+    w = torch.randn(n * (2 if dual else 1), k, generator=torch.Generator().manual_seed(42)) * 0.05
+    packed, sb = enc.weight_quant_mxfp4(w)
+    wq = Q.mxfp4_to_e4m3_containers(packed).cuda()
+    out = Q.gemm_fp8(xq, xs, wq, sb.cuda(), epilogue=1 if dual else 0, out_dtype=torch.float32, group32=True)
+    xd = enc.act_dequant_fp8(xq.cpu(), xs.cpu())
+    wd = enc.weight_dequant_mxfp4(packed, sb)
+    y = xd @ wd.T
+    r = ref.swiglu(y[:, :n], y[:, n:]) if dual else y
+    assert float((out.cpu() - r).abs().max()) <= 3e-3 * float(r.abs().max()) + 1e-4
