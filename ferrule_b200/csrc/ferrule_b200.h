@@ -134,6 +134,8 @@ typedef struct FbAttnArgs {
   int split_tokens;         // multiple of 64
   float softmax_scale;
   void* merge_ctr;          // optional: zeroed uint32 [ceil(rows/group_rows) * head blocks]; merges in-kernel
+  const int* selection;     // optional [rows, sel_width] explicit pool rows per query row, -1 = masked
+  int sel_width;            //   (then block_table / row_seq / row_pos are unused and group_rows must be 1)
 } FbAttnArgs;
 
 int fb_mla_attention(const FbAttnArgs* args, void* stream);
@@ -189,6 +191,26 @@ int fb_quant_mxfp4_rows(const void* x, long long ldx, void* packed, void* scale,
                         void* stream);
 int fb_dequant_mxfp4(const void* packed, const void* scale, void* out, int rows, int n, void* stream);
 int fb_hadamard_rows(void* x, long long ldx, int rows, int n, void* stream);
+
+// ---- DeepSeek-V4 operators ---------------------------------------------------------------
+// hyper-connections: state bf16 [tokens, hc, hidden], fn fp32 [nmix, hc * hidden]; coeff fp32 [tokens, nmix]
+// = [pre | post | comb]; nmix = hc (head reduction) or 2 hc + hc^2; hc in {2, 4}
+int fb_hc_pre(const void* state, const float* fn, const float* scale, const float* base, void* hidden_out,
+              int out_fp32, float* coeff, int tokens, int hc, int hidden, int nmix, float eps, float norm_eps,
+              int sinkhorn_iters, void* stream);
+int fb_hc_post(const void* hidden_in, const void* residual, const float* coeff, void* out, int tokens, int hc,
+               int hidden, void* stream);
+// group g pools rows row0 + g * ratio + [0, window); rows outside [0, n_rows) are masked
+int fb_compressor_pool(const float* kv, const float* gate, long long ld, const float* ape, void* out, long long ldo,
+                       int groups, int dim, int ratio, int window, int row0, int n_rows, void* stream);
+int fb_rope_rows(void* x, long long ld_row, long long ld_head, int rows, int heads, int off, int rdim,
+                 const int* positions, const float* cos_t, const float* sin_t, int max_pos, int inverse,
+                 void* status, void* stream);
+int fb_indexer_scores(const void* q, const void* plane, long long ldp, const float* head_w, float* scores,
+                      long long ld_s, int queries, int heads, int d, int n, void* stream);
+// n_visible (per query) may be NULL, then n_fixed applies; k <= 512
+int fb_indexer_topk(const float* scores, long long ld_s, const int* n_visible, int n_fixed, int k, int* out_idx,
+                    long long ldo, int queries, void* stream);
 
 // ---- peer memory and collectives --------------------------------------------------------
 int fb_ipc_handle_bytes(void);

@@ -50,6 +50,8 @@ struct AttnParams {
   float* part_ml;           // [rows, splits, heads, 2]
   unsigned int* merge_ctr;  // [q groups * head blocks] zeroed once: last split CTA merges in-kernel
   int cluster_merge;        // splits form one thread-block cluster and merge through distributed smem
+  const int* selection;     // optional [rows, sel_width] pool rows per query row (-1 = masked); group_rows == 1
+  int sel_width;
   DeviceStatus* status;
 };
 
@@ -132,17 +134,19 @@ mla_attention_kernel(const AttnParams p) {
   }
 
   // ---- query tile -> smem (rows beyond the valid set are zero) ----
-  int seq = p.row_seq[qrow0];
-  bool seq_ok = seq >= 0 && seq < p.num_seqs;
+  const bool by_selection = p.selection != nullptr;
+  const int* sel = by_selection ? p.selection + static_cast<long long>(qrow0) * p.sel_width : nullptr;
+  int seq = by_selection ? 0 : p.row_seq[qrow0];
+  bool seq_ok = by_selection || (seq >= 0 && seq < p.num_seqs);
   if (!seq_ok) {
     if (tid == 0) report_status(p.status, kStatusBadIndex, 0x60, qrow0, seq);
     seq = 0;
   }
   int kv_len_max = 0;
-  for (int r = 0; r < G; ++r)
+  for (int r = 0; r < G && !by_selection; ++r)
     if (qrow0 + r < p.rows) kv_len_max = max(kv_len_max, p.row_pos[qrow0 + r] + 1);
   if (!seq_ok) kv_len_max = 0;
-  kv_len_max = min(kv_len_max, p.max_blocks * p.page_size);
+  kv_len_max = by_selection ? p.sel_width : min(kv_len_max, p.max_blocks * p.page_size);
 
   for (int i = tid; i < 16 * (D / 8); i += kAttnThreads) {
     const int r = i / (D / 8), c = i - r * (D / 8);
@@ -156,8 +160,8 @@ mla_attention_kernel(const AttnParams p) {
   int kvlen_lo = 0, kvlen_hi = 0;
   {
     const int qr_lo = qrow0 + g / Hb, qr_hi = qrow0 + (g + 8) / Hb;
-    if (seq_ok && qr_lo < p.rows && g / Hb < G) kvlen_lo = p.row_pos[qr_lo] + 1;
-    if (seq_ok && qr_hi < p.rows && (g + 8) / Hb < G) kvlen_hi = p.row_pos[qr_hi] + 1;
+    if (seq_ok && qr_lo < p.rows && g / Hb < G) kvlen_lo = by_selection ? p.sel_width : p.row_pos[qr_lo] + 1;
+    if (seq_ok && qr_hi < p.rows && (g + 8) / Hb < G) kvlen_hi = by_selection ? p.sel_width : p.row_pos[qr_hi] + 1;
   }
   __syncthreads();
 
@@ -181,7 +185,16 @@ mla_attention_kernel(const AttnParams p) {
       const int tok = tile0 + tid;
       __nv_bfloat16* dst = KVs + tid * kRowPad;
       bool issued = false;
-      if (tok < kv_end) {
+      if (tok < kv_end && by_selection) {
+        const long long slot = sel[tok];
+        if (slot >= 0 && slot < p.pool_rows) {
+          mbar_arrive_expect_tx(bar, D * 2);
+          bulk_copy_g2s(dst, p.kv + slot * D, D * 2, bar);
+          issued = true;
+        } else if (slot >= 0) {
+          report_status(p.status, kStatusBadIndex, 0x63, qrow0, tok);
+        }
+      } else if (tok < kv_end) {
         const int page = p.block_table[static_cast<long long>(seq) * p.max_blocks + tok / p.page_size];
         const long long slot = static_cast<long long>(page) * p.page_size + tok % p.page_size;
         if (page >= 0 && slot < p.pool_rows) {
@@ -224,10 +237,13 @@ mla_attention_kernel(const AttnParams p) {
     for (int j = 0; j < 2; ++j) {
       const int tok0 = tok_base + j;
       const int tok1 = tok_base + 8 + j;
-      s0[j] = tok0 < kvlen_lo ? s0[j] * p.scale_log2 : -INFINITY;
-      s0[2 + j] = tok0 < kvlen_hi ? s0[2 + j] * p.scale_log2 : -INFINITY;
-      s1[j] = tok1 < kvlen_lo ? s1[j] * p.scale_log2 : -INFINITY;
-      s1[2 + j] = tok1 < kvlen_hi ? s1[2 + j] * p.scale_log2 : -INFINITY;
+      // an explicit selection masks its -1 entries (their rows were zero-filled above)
+      const bool v0 = !by_selection || (tok0 < p.sel_width && sel[tok0] >= 0);
+      const bool v1 = !by_selection || (tok1 < p.sel_width && sel[tok1] >= 0);
+      s0[j] = (v0 && tok0 < kvlen_lo) ? s0[j] * p.scale_log2 : -INFINITY;
+      s0[2 + j] = (v0 && tok0 < kvlen_hi) ? s0[2 + j] * p.scale_log2 : -INFINITY;
+      s1[j] = (v1 && tok1 < kvlen_lo) ? s1[j] * p.scale_log2 : -INFINITY;
+      s1[2 + j] = (v1 && tok1 < kvlen_hi) ? s1[2 + j] * p.scale_log2 : -INFINITY;
       tmax_lo = fmaxf(tmax_lo, fmaxf(s0[j], s1[j]));
       tmax_hi = fmaxf(tmax_hi, fmaxf(s0[2 + j], s1[2 + j]));
     }
@@ -560,8 +576,14 @@ static int launch_attn(const AttnParams& p, cudaStream_t stream) {
 using namespace fb;
 
 extern "C" int fb_mla_attention(const FbAttnArgs* a, void* stream_) {
-  if (!a || !a->q || !a->kv || !a->block_table || !a->row_seq || !a->row_pos || !a->out) return FB_ERR_SHAPE;
-  if (a->rows <= 0 || a->heads <= 0 || a->page_size <= 0 || a->max_blocks <= 0) return FB_ERR_SHAPE;
+  if (!a || !a->q || !a->kv || !a->out) return FB_ERR_SHAPE;
+  if (a->selection) {
+    if (a->sel_width <= 0 || a->group_rows != 1) return FB_ERR_SHAPE;
+  } else {
+    if (!a->block_table || !a->row_seq || !a->row_pos) return FB_ERR_SHAPE;
+    if (a->page_size <= 0 || a->max_blocks <= 0) return FB_ERR_SHAPE;
+  }
+  if (a->rows <= 0 || a->heads <= 0) return FB_ERR_SHAPE;
   if (a->group_rows != 1 && a->group_rows != 2 && a->group_rows != 4 && a->group_rows != 8 &&
       a->group_rows != 16)
     return FB_ERR_SHAPE;
@@ -596,6 +618,8 @@ extern "C" int fb_mla_attention(const FbAttnArgs* a, void* stream_) {
   p.part_ml = a->part_ml;
   p.merge_ctr = static_cast<unsigned int*>(a->merge_ctr);
   p.cluster_merge = cluster_merge ? 1 : 0;
+  p.selection = a->selection;
+  p.sel_width = a->sel_width;
   p.status = static_cast<DeviceStatus*>(a->status);
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   if (a->kv_lora == 512 && a->rope_dim == 64) return launch_attn<512, 64>(p, stream);

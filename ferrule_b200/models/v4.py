@@ -1,0 +1,160 @@
+"""DeepSeek-V4-only operators: hyper-connections, KV compressor pooling, learned indexer,
+explicit-selection sink attention.  PyTorch reference math (fp32 with the bf16 write-backs of the
+checkpoint's computation contract) plus dispatch to the CUDA kernels of `csrc/v4_ops.cu`.
+
+* Hyper-connections keep `hc` copies of the residual stream.  `hc_pre` reduces them to one hidden
+  vector: mixes = (W_fn . state) * rms(state); pre = sigmoid(mix*s0 + b) + eps; post = 2*sigmoid(.);
+  comb = Sinkhorn(softmax rows + eps); hidden = sum_j pre_j * state_j.  `hc_post` writes the copies
+  back: out_j = post_j * hidden + sum_i comb[i, j] * residual_i.  `hc_head` is the final reduction.
+* The compressor emits one pooled KV row per `ratio` tokens: a per-dimension softmax over the
+  window (the group, plus the previous group when `overlap`), scores = gate + position embedding,
+  entries before the start of the sequence count as score -inf / value 0; result rounded to bf16.
+* The indexer scores compressed rows for a query: per head bf16(q_h . row) -> bf16(relu * w_h) ->
+  fp32 sum over heads -> bf16, then a stable top-k (ties -> lower row, non-finite excluded, unused
+  slots = -1).
+* Selection = sliding window rows U chosen compressed rows; attention runs over that explicit row
+  list with a per-head sink logit in the softmax denominator.
+
+Counterpart of crates/ferrule-model/src/hyper_connection.rs:175-420, attention_backend.rs:47-185,
+models/deepseek_v4/attention.rs:1194-1364, :2831-3395 and the device kernels hc_kernel /
+compressor_kernel / indexer_kernel (portable/entrypoints.cu:912-1266, :1614-1840).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Optional, Tuple
+
+import torch
+
+from ..ops import reference as ref
+
+
+@dataclass(frozen=True)
+class HcConfig:
+    hc: int = 4
+    hidden: int = 4096
+    eps: float = 1e-6
+    norm_eps: float = 1e-6
+    sinkhorn_iters: int = 20
+
+    @property
+    def mix(self) -> int:
+        return 2 * self.hc + self.hc * self.hc
+
+
+def hc_split_sinkhorn(mixes: torch.Tensor, scale: torch.Tensor, base: torch.Tensor, cfg: HcConfig):
+    """mixes [T, 2hc + hc*hc] -> (pre [T,hc], post [T,hc], comb [T,hc,hc])."""
+    hc, eps = cfg.hc, cfg.eps
+    m = mixes.float()
+    pre = torch.sigmoid(m[:, :hc] * scale[0] + base[:hc]) + eps
+    post = 2.0 * torch.sigmoid(m[:, hc:2 * hc] * scale[1] + base[hc:2 * hc])
+    c = (m[:, 2 * hc:] * scale[2] + base[2 * hc:]).view(-1, hc, hc)
+    c = torch.softmax(c, dim=-1) + eps
+    c = c / (c.sum(1, keepdim=True) + eps)                     # columns
+    for _ in range(1, cfg.sinkhorn_iters):
+        c = c / (c.sum(2, keepdim=True) + eps)                 # rows
+        c = c / (c.sum(1, keepdim=True) + eps)                 # columns
+    return pre, post, c
+
+
+def hc_pre(state: torch.Tensor, fn: torch.Tensor, scale: torch.Tensor, base: torch.Tensor, cfg: HcConfig):
+    """state [T, hc, hidden], fn [mix, hc*hidden] -> (hidden [T, hidden] fp32, (pre, post, comb))."""
+    T = state.shape[0]
+    x = state.float().reshape(T, -1)
+    rms = torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + cfg.norm_eps)
+    mixes = (x @ fn.float().T) * rms
+    pre, post, comb = hc_split_sinkhorn(mixes, scale.float(), base.float(), cfg)
+    hidden = (pre.unsqueeze(-1) * state.float()).sum(1)
+    return hidden, (pre, post, comb)
+
+
+def hc_post(hidden: torch.Tensor, residual: torch.Tensor, post: torch.Tensor, comb: torch.Tensor) -> torch.Tensor:
+    """hidden [T, hidden], residual [T, hc, hidden] -> [T, hc, hidden]: out_j = post_j*hidden + sum_i comb[i,j]*res_i."""
+    mix = torch.einsum("tij,tid->tjd", comb.float(), residual.float())
+    return post.float().unsqueeze(-1) * hidden.float().unsqueeze(1) + mix
+
+
+def hc_head(state: torch.Tensor, fn: torch.Tensor, scale: torch.Tensor, base: torch.Tensor, cfg: HcConfig) -> torch.Tensor:
+    T = state.shape[0]
+    x = state.float().reshape(T, -1)
+    rms = torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + cfg.norm_eps)
+    pre = torch.sigmoid((x @ fn.float().T) * rms * scale[0] + base[:cfg.hc].float()) + cfg.eps
+    return (pre.unsqueeze(-1) * state.float()).sum(1)
+
+
+def compressor_pool(kv: torch.Tensor, gate: torch.Tensor, ape: torch.Tensor, ratio: int, overlap: bool) -> torch.Tensor:
+    """kv, gate [tokens, D] (projected rows of one sequence, position 0 first), ape [window, D] with
+    window = ratio * (2 if overlap else 1) -> pooled [tokens // ratio, D], rounded to bf16."""
+    tokens, D = kv.shape
+    groups = tokens // ratio
+    W = ratio * (2 if overlap else 1)
+    out = torch.zeros(groups, D, dtype=torch.float32, device=kv.device)
+    for g in range(groups):
+        end = (g + 1) * ratio
+        start = end - W
+        idx = torch.arange(start, end, device=kv.device)
+        ok = idx >= 0
+        rows = kv.float()[idx.clamp(min=0)] * ok[:, None]
+        score = gate.float()[idx.clamp(min=0)] + ape.float()
+        score = torch.where(ok[:, None], score, torch.full_like(score, float("-inf")))
+        out[g] = (torch.softmax(score, dim=0) * rows).sum(0)
+    return ref.bf16_round(out)
+
+
+def indexer_topk(q: torch.Tensor, rows: torch.Tensor, head_w: torch.Tensor, k: int, n_visible: int):
+    """q [heads, d], rows [n, d] (compressed indexer plane), head_w [heads] -> (indices [k] int32 (-1 = unused),
+    scores [n] fp32 holding bf16 values).  Only the first `n_visible` rows may be chosen."""
+    b = ref.bf16_round
+    dots = b(q.float() @ rows.float().T)                                   # [heads, n]
+    contrib = b(torch.relu(dots) * b(head_w.float())[:, None])
+    score = b(contrib.sum(0))
+    cand = score[:n_visible].clone()
+    cand = torch.where(torch.isfinite(cand), cand, torch.full_like(cand, float("-inf")))
+    take = min(k, n_visible)
+    idx = torch.full((k,), -1, dtype=torch.int32, device=q.device)
+    if take > 0:
+        order = torch.sort(cand, descending=True, stable=True).indices[:take]
+        good = torch.isfinite(cand[order])
+        idx[:take] = torch.where(good, order.to(torch.int32), torch.full_like(order, -1).to(torch.int32))
+    return idx, score
+
+
+def sliding_window_indices(position: int, window: int) -> torch.Tensor:
+    """Rows visible through the window at `position` (inclusive): [window] int32, -1 where none."""
+    lo = position - window + 1
+    idx = torch.arange(lo, position + 1, dtype=torch.int32)
+    return torch.where(idx >= 0, idx, torch.full_like(idx, -1))
+
+
+def sparse_sink_attention(q: torch.Tensor, table: torch.Tensor, selection: torch.Tensor, kv_lora: int, scale: float,
+                          sink: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """q [rows, heads, D]; table [n, D]; selection [rows, W] int32 row ids (-1 = masked) -> [rows, heads, kv_lora].
+    probabilities are rounded to bf16 before the value product, like the device contract."""
+    rows, heads, _ = q.shape
+    out = torch.zeros(rows, heads, kv_lora, dtype=torch.float32, device=q.device)
+    for r in range(rows):
+        sel = selection[r]
+        ok = sel >= 0
+        if not bool(ok.any()):
+            continue
+        kv = table.float()[sel[ok].long()]
+        logits = q[r].float() @ kv.T * scale
+        if sink is not None:
+            m = torch.maximum(logits.max(-1).values, sink.float())
+            p = torch.exp(logits - m[:, None])
+            p = p / (p.sum(-1) + torch.exp(sink.float() - m))[:, None]
+        else:
+            p = torch.softmax(logits, -1)
+        out[r] = p @ kv[:, :kv_lora]
+    return out
+
+
+# ------------------------------------------------------------------------------------------ CUDA dispatch
+def hc_pre_cuda(state, fn, scale, base, cfg: HcConfig):
+    from ..ops import v4 as K4
+    return K4.hc_pre(state, fn, scale, base, cfg)
+
+
+def hc_post_cuda(hidden, residual, post, comb):
+    from ..ops import v4 as K4
+    return K4.hc_post(hidden, residual, post, comb)

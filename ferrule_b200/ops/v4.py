@@ -1,0 +1,124 @@
+"""ctypes wrappers of the DeepSeek-V4 operator kernels (`csrc/v4_ops.cu`) and of the attention
+kernel's explicit-selection mode.  Shapes and math are those of `models/v4.py`, which holds the
+PyTorch oracle each wrapper is tested against."""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional, Tuple
+
+import torch
+
+from ._lib import AttnArgs, check, get_lib, ptr, status_tensor, stream_ptr
+
+
+def hc_pre(state: torch.Tensor, fn: torch.Tensor, scale: torch.Tensor, base: torch.Tensor, cfg,
+           out_fp32: bool = False, head_only: bool = False) -> Tuple[torch.Tensor, torch.Tensor]:
+    """state bf16 [T, hc, hidden]; fn fp32 [nmix, hc*hidden] -> (hidden [T, hidden], coeff fp32 [T, nmix])."""
+    lib = get_lib(True)
+    T, hc, hidden = state.shape
+    nmix = hc if head_only else 2 * hc + hc * hc
+    assert state.dtype == torch.bfloat16 and state.is_contiguous()
+    assert fn.dtype == torch.float32 and fn.shape == (nmix, hc * hidden) and fn.is_contiguous()
+    out = torch.empty(T, hidden, dtype=torch.float32 if out_fp32 else torch.bfloat16, device=state.device)
+    coeff = torch.empty(T, nmix, dtype=torch.float32, device=state.device)
+    check(lib.fb_hc_pre(state.data_ptr(), fn.data_ptr(), scale.data_ptr(), base.data_ptr(), out.data_ptr(),
+                        int(out_fp32), coeff.data_ptr(), T, hc, hidden, nmix, cfg.eps, cfg.norm_eps,
+                        cfg.sinkhorn_iters, stream_ptr()), "fb_hc_pre")
+    return out, coeff
+
+
+def hc_post(hidden: torch.Tensor, residual: torch.Tensor, coeff: torch.Tensor) -> torch.Tensor:
+    """hidden bf16 [T, hidden]; residual bf16 [T, hc, hidden]; coeff fp32 [T, 2hc + hc^2] -> bf16 [T, hc, hidden]."""
+    lib = get_lib(True)
+    T, hc, dim = residual.shape
+    assert hidden.dtype == residual.dtype == torch.bfloat16 and hidden.is_contiguous() and residual.is_contiguous()
+    assert coeff.shape == (T, 2 * hc + hc * hc) and coeff.dtype == torch.float32
+    out = torch.empty_like(residual)
+    check(lib.fb_hc_post(hidden.data_ptr(), residual.data_ptr(), coeff.data_ptr(), out.data_ptr(), T, hc, dim,
+                         stream_ptr()), "fb_hc_post")
+    return out
+
+
+def compressor_pool(kv: torch.Tensor, gate: torch.Tensor, ape: torch.Tensor, ratio: int, overlap: bool,
+                    groups: Optional[int] = None, row0: Optional[int] = None) -> torch.Tensor:
+    """kv, gate fp32 [n_rows, D] -> bf16 [groups, D].  `row0` is the row where group 0's window starts
+    (default: ratio - window, i.e. the rows are a sequence from position 0)."""
+    lib = get_lib(True)
+    n_rows, D = kv.shape
+    W = ratio * (2 if overlap else 1)
+    assert kv.dtype == gate.dtype == ape.dtype == torch.float32 and kv.stride() == gate.stride() and kv.stride(1) == 1
+    assert ape.shape == (W, D) and ape.is_contiguous()
+    groups = n_rows // ratio if groups is None else groups
+    row0 = ratio - W if row0 is None else row0
+    out = torch.empty(groups, D, dtype=torch.bfloat16, device=kv.device)
+    check(lib.fb_compressor_pool(kv.data_ptr(), gate.data_ptr(), kv.stride(0), ape.data_ptr(), out.data_ptr(),
+                                 out.stride(0), groups, D, ratio, W, row0, n_rows, stream_ptr()), "fb_compressor_pool")
+    return out
+
+
+def rope_rows(x: torch.Tensor, positions: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, off: int, rdim: int,
+              inverse: bool = False) -> torch.Tensor:
+    """In place on x bf16 [rows, heads, head_dim]: rotate x[..., off:off+rdim] (interleaved pairs)."""
+    lib = get_lib(True)
+    rows, heads, hd = x.shape
+    assert x.dtype == torch.bfloat16 and x.stride(2) == 1 and positions.dtype == torch.int32
+    assert cos.dtype == sin.dtype == torch.float32 and cos.shape[1] == rdim // 2 and cos.is_contiguous()
+    check(lib.fb_rope_rows(x.data_ptr(), x.stride(0), x.stride(1), rows, heads, off, rdim, positions.data_ptr(),
+                           cos.data_ptr(), sin.data_ptr(), cos.shape[0], int(inverse),
+                           status_tensor(x.device).data_ptr(), stream_ptr()), "fb_rope_rows")
+    return x
+
+
+def indexer_scores(q: torch.Tensor, plane: torch.Tensor, head_w: torch.Tensor,
+                   out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """q bf16 [queries, heads, d]; plane bf16 [n, d]; head_w fp32 [queries, heads] -> fp32 [queries, n]."""
+    lib = get_lib(True)
+    Q, H, d = q.shape
+    n = plane.shape[0]
+    assert q.dtype == plane.dtype == torch.bfloat16 and q.is_contiguous() and plane.stride(1) == 1
+    assert head_w.dtype == torch.float32 and head_w.shape == (Q, H) and head_w.is_contiguous()
+    if out is None:
+        out = torch.empty(Q, n, dtype=torch.float32, device=q.device)
+    check(lib.fb_indexer_scores(q.data_ptr(), plane.data_ptr(), plane.stride(0), head_w.data_ptr(), out.data_ptr(),
+                                out.stride(0), Q, H, d, n, stream_ptr()), "fb_indexer_scores")
+    return out
+
+
+def indexer_topk(scores: torch.Tensor, k: int, n_visible: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """scores fp32 [queries, n] holding bf16 values -> int32 [queries, k]; rows past n_visible[q] are not eligible."""
+    lib = get_lib(True)
+    Q, n = scores.shape
+    assert scores.dtype == torch.float32 and scores.stride(1) == 1 and k <= 512
+    if n_visible is not None:
+        assert n_visible.dtype == torch.int32 and n_visible.numel() == Q
+    out = torch.empty(Q, k, dtype=torch.int32, device=scores.device)
+    check(lib.fb_indexer_topk(scores.data_ptr(), scores.stride(0), ptr(n_visible), n, k, out.data_ptr(), out.stride(0),
+                              Q, stream_ptr()), "fb_indexer_topk")
+    return out
+
+
+def sparse_sink_attention(q: torch.Tensor, table: torch.Tensor, selection: torch.Tensor, kv_lora: int, rope_dim: int,
+                          scale: float, sink: Optional[torch.Tensor] = None, splits: int = 1,
+                          out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """q bf16 [rows, heads, D]; table bf16 [n, D]; selection int32 [rows, W] (pool rows, -1 = masked).
+    `splits` in (1, 2, 4, 8): the splits of one query merge on chip through a thread-block cluster."""
+    lib = get_lib(True)
+    rows, heads, D = q.shape
+    W = selection.shape[1]
+    assert D == kv_lora + rope_dim and q.stride(2) == 1 and q.stride(1) == D
+    assert selection.dtype == torch.int32 and selection.is_contiguous() and table.is_contiguous()
+    if out is None:
+        out = torch.empty(rows, heads, kv_lora, dtype=torch.bfloat16, device=q.device)
+    a = AttnArgs()
+    a.q, a.kv, a.out = q.data_ptr(), table.data_ptr(), out.data_ptr()
+    a.sink = ptr(sink)
+    a.status = status_tensor(q.device).data_ptr()
+    a.ldq, a.ldo = q.stride(0), out.stride(0)
+    a.pool_rows = table.numel() // D
+    a.rows, a.heads, a.kv_lora, a.rope_dim = rows, heads, kv_lora, rope_dim
+    a.group_rows, a.splits = 1, splits
+    a.split_tokens = ((W + splits - 1) // splits + 63) // 64 * 64
+    a.softmax_scale = scale
+    a.selection, a.sel_width = selection.data_ptr(), W
+    check(lib.fb_mla_attention(C.byref(a), stream_ptr()), "fb_mla_attention(selection)")
+    return out

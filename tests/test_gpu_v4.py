@@ -1,0 +1,119 @@
+"""DeepSeek-V4 operator kernels against their fp32 PyTorch oracles."""
+import pytest
+import torch
+
+from ferrule_b200.models import v4
+from ferrule_b200.ops import reference as ref
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+@pytest.mark.parametrize("hc,hidden,tokens", [(4, 4096, 5), (2, 256, 3)])
+def test_hc_pre_post_match_reference(hc, hidden, tokens):
+    from ferrule_b200.ops import v4 as K
+    torch.manual_seed(0)
+    cfg = v4.HcConfig(hc=hc, hidden=hidden, sinkhorn_iters=20)
+    state = torch.randn(tokens, hc, hidden, device=DEV).bfloat16()
+    fn = torch.randn(cfg.mix, hc * hidden, device=DEV) * 0.02
+    scale = torch.tensor([0.7, 1.1, 0.9], device=DEV)
+    base = torch.randn(cfg.mix, device=DEV) * 0.3
+    hidden_ref, (pre, post, comb) = v4.hc_pre(state, fn, scale, base, cfg)
+    got, coeff = K.hc_pre(state, fn, scale, base, cfg, out_fp32=True)
+    torch.cuda.synchronize()
+    assert torch.allclose(coeff[:, :hc], pre, atol=2e-5, rtol=1e-4)
+    assert torch.allclose(coeff[:, hc:2 * hc], post, atol=2e-5, rtol=1e-4)
+    assert torch.allclose(coeff[:, 2 * hc:].view(tokens, hc, hc), comb, atol=2e-5, rtol=1e-4)
+    assert torch.allclose(got, hidden_ref, atol=1e-4, rtol=1e-4)
+    hid_bf = got.bfloat16()
+    out = K.hc_post(hid_bf, state, coeff)
+    want = v4.hc_post(hid_bf, state, post, comb)
+    assert torch.allclose(out.float(), want, atol=2e-2, rtol=1e-2)
+    head_fn = fn[:hc].contiguous()
+    hgot, _ = K.hc_pre(state, head_fn, scale, base, cfg, out_fp32=True, head_only=True)
+    hwant = v4.hc_head(state, head_fn, scale, base, cfg)
+    assert torch.allclose(hgot, hwant, atol=1e-4, rtol=1e-4)
+
+
+@pytest.mark.parametrize("ratio,overlap", [(4, True), (128, False)])
+def test_compressor_pool_matches_reference(ratio, overlap):
+    from ferrule_b200.ops import v4 as K
+    torch.manual_seed(1)
+    tokens, D = ratio * 5, 576
+    kv, gate = torch.randn(tokens, D, device=DEV), torch.randn(tokens, D, device=DEV) * 2
+    ape = torch.randn(ratio * (2 if overlap else 1), D, device=DEV)
+    got = K.compressor_pool(kv, gate, ape, ratio, overlap)
+    want = v4.compressor_pool(kv, gate, ape, ratio, overlap)
+    assert torch.allclose(got.float(), want, atol=1e-2, rtol=1e-2)
+    exact = (got.float() == want).float().mean().item()
+    assert exact > 0.98       # bf16 rounding of an fp32 sum: only last-ulp ties may differ
+
+
+def test_rope_rows_forward_then_inverse_is_identity():
+    from ferrule_b200.ops import v4 as K
+    torch.manual_seed(2)
+    cos, sin = ref.rope_tables(64, 64, 10000.0)
+    cos, sin = cos.to(DEV), sin.to(DEV)
+    x = torch.randn(7, 3, 192, device=DEV).bfloat16()
+    pos = torch.tensor([0, 5, 9, 63, 1, 2, 33], dtype=torch.int32, device=DEV)
+    y = x.clone()
+    K.rope_rows(y, pos, cos, sin, off=128, rdim=64)
+    want = x.float().clone()
+    want[..., 128:] = ref.apply_rope(x[..., 128:], cos[pos.long()][:, None], sin[pos.long()][:, None])
+    assert torch.allclose(y.float(), want, atol=2e-2, rtol=1e-2)
+    assert torch.equal(y[..., :128], x[..., :128])
+    K.rope_rows(y, pos, cos, sin, off=128, rdim=64, inverse=True)
+    assert torch.allclose(y.float(), x.float(), atol=3e-2, rtol=2e-2)
+
+
+def test_indexer_scores_and_topk_match_reference():
+    from ferrule_b200.ops import v4 as K
+    torch.manual_seed(3)
+    Q, H, d, n, k = 3, 64, 128, 3000, 512
+    q = torch.randn(Q, H, d, device=DEV).bfloat16()
+    plane = torch.randn(n, d, device=DEV).bfloat16()
+    w = torch.randn(Q, H, device=DEV)
+    scores = K.indexer_scores(q, plane, w)
+    vis = torch.tensor([n, 700, 100], dtype=torch.int32, device=DEV)
+    idx = K.indexer_topk(scores, k, vis)
+    torch.cuda.synchronize()
+    for i in range(Q):
+        _, s_ref = v4.indexer_topk(q[i], plane, w[i], k, int(vis[i]))
+        # scores: fp32 accumulation order differs -> allow one bf16 ulp on a small share
+        close = torch.isclose(scores[i], s_ref, rtol=1.6e-2, atol=1e-2)
+        assert close.float().mean() > 0.999
+        # top-k exactness is checked on the kernel's own scores (the selection contract)
+        cand = scores[i, :int(vis[i])]
+        order = torch.sort(cand, descending=True, stable=True).indices[:k].int()
+        want = torch.full((k,), -1, dtype=torch.int32, device=DEV)
+        want[:order.numel()] = order
+        assert torch.equal(idx[i], want)
+
+
+def test_indexer_topk_ties_and_nonfinite():
+    from ferrule_b200.ops import v4 as K
+    s = torch.zeros(1, 2000, device=DEV)
+    s[0, 5] = float("nan")
+    s[0, 100:110] = 2.0
+    s[0, 7] = float("inf")
+    s[0, 1500] = -1.0
+    idx = K.indexer_topk(s, 16)
+    assert idx[0].tolist() == list(range(100, 110)) + [0, 1, 2, 3, 4, 6]
+
+
+@pytest.mark.parametrize("splits", [1, 4])
+def test_selection_attention_matches_reference(splits):
+    from ferrule_b200.ops import v4 as K
+    torch.manual_seed(4)
+    rows, heads, DL, DR, n, W = 5, 16, 512, 64, 4096, 640
+    D = DL + DR
+    table = (torch.randn(n, D, device=DEV) * 0.5).bfloat16()
+    q = (torch.randn(rows, heads, D, device=DEV) * 0.5).bfloat16()
+    sel = torch.stack([torch.randperm(n, device=DEV)[:W] for _ in range(rows)]).int()
+    sel[:, 17] = -1
+    sel[2, 300:] = -1
+    sink = torch.randn(heads, device=DEV)
+    got = K.sparse_sink_attention(q, table, sel, DL, DR, 0.07, sink=sink, splits=splits)
+    want = v4.sparse_sink_attention(q, table, sel, DL, 0.07, sink=sink)
+    torch.cuda.synchronize()
+    assert torch.allclose(got.float(), want, atol=2e-2, rtol=2e-2)
