@@ -249,10 +249,11 @@ class CudaWorkspace:
         self.attn_splits = attn_splits
         self.decode_rows = decode_rows
         from ..ops.kernels import AttnWorkspace, MoePlan
-        self.attn_ws = AttnWorkspace(torch.zeros(decode_rows, attn_splits, hl, cfg.kv_lora_rank, **f32),
-                                     torch.zeros(decode_rows, attn_splits, hl, 2, **f32), decode_rows,
-                                     attn_splits,
-                                     torch.zeros(decode_rows * ((hl + 15) // 16), **i32)) if attn_splits > 1 else None
+        sr = 4 * decode_rows        # split attention also serves verification batches (see _attention)
+        self.attn_ws = AttnWorkspace(torch.zeros(sr, attn_splits, hl, cfg.kv_lora_rank, **f32),
+                                     torch.zeros(sr, attn_splits, hl, 2, **f32), sr, attn_splits,
+                                     torch.zeros(sr * ((hl + 15) // 16), **i32)) \
+            if attn_splits > 1 and attn_splits not in (2, 4, 8) else None
         self.has_moe = cfg.n_routed_experts > 0
         self.router_ctr = torch.zeros(4, **i32)
         from ..ops.kernels import ArgmaxScratch
@@ -330,7 +331,9 @@ class CudaForward:
         K.mla_prep(q, qhd, ckv, hl, lora, rope, lw.kv_norm, cfg.rms_eps, self.cos, self.sin,
                    b.positions, b.write_slot, self.pool.layer(layer), q_full.view(T, -1))
         K.gemm(q, lw.w_uk_t, out=q_full.view(T, -1), x_group_koff=qhd, out_group_coff=lora + rope, k=nope)
-        use_split = ws.attn_splits > 1 and T <= ws.decode_rows
+        # verification batches (a few rows per decoding sequence) must take the same split path as plain
+        # decode steps: equal split boundaries give bit-equal merges, hence the same greedy tokens
+        use_split = ws.attn_splits > 1 and T <= 4 * ws.decode_rows
         cluster = ws.attn_splits in (2, 4, 8)       # splits merge through distributed shared memory
         K.mla_attention(q_full, self.pool.layer(layer), b.block_table, b.row_seq, b.row_pos,
                         self.pool.page_size, lora, rope, cfg.softmax_scale, ws.o_lat[:T],
@@ -515,6 +518,7 @@ class DecodeGraph:
         g = torch.cuda.CUDAGraph()
         with torch.cuda.graph(g):
             self.out = self.fwd.forward(self.batch)
+        self.hidden = self.fwd.last_hidden          # static buffer the replay leaves the hidden states in
         self.graph, self.state = g, "captured"
 
     def replay(self):

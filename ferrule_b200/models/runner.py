@@ -99,12 +99,22 @@ class RunnerStats:
     graph_captures: int = 0
     cow_copies: int = 0
     forward_ns: int = 0
+    mtp_proposals: int = 0
+
+
+class _MtpTrack:
+    """Published rows of one sequence that still lack their MTP row: `hidden[j]` / `tokens[j]` belong
+    to position `next_pos + j`."""
+    __slots__ = ("next_pos", "hidden", "tokens", "blocks")
+
+    def __init__(self, next_pos: int):
+        self.next_pos, self.hidden, self.tokens, self.blocks = next_pos, [], [], []
 
 
 class DeepSeekRunner(ModelRunner):
     def __init__(self, weights: ModelWeights, n_pages: int, page_size: int, max_rows: int = 2048,
                  max_seqs: int = 64, max_seq_len: int = 4096, device=None, tp=None, use_graphs: bool = True,
-                 emulate_bf16: bool = False, attn_splits: int = 8):
+                 emulate_bf16: bool = False, attn_splits: int = 8, enable_mtp: bool = True, max_draft: int = 1):
         self.w, self.cfg = weights, weights.cfg
         self.device = torch.device(device if device is not None else weights.embed.device)
         self.is_cuda = self.device.type == "cuda"
@@ -118,7 +128,9 @@ class DeepSeekRunner(ModelRunner):
         self.stats = RunnerStats()
         self.staging = BatchStaging(max_rows, max_seqs, self.max_blocks, self.device)
         if self.is_cuda:
-            self.fwd = CudaForward(weights, self.pool, max_rows=max_rows, max_logit_rows=max(max_seqs, 1),
+            # a verification batch asks for logits on the anchor and on every draft row of each sequence
+            logit_rows = max(max_seqs, 1) * (1 + (max_draft if weights.mtp and enable_mtp else 0))
+            self.fwd = CudaForward(weights, self.pool, max_rows=max_rows, max_logit_rows=logit_rows,
                                    decode_rows=max_seqs, max_seq_len=max_seq_len, attn_splits=attn_splits, tp=tp)
             L = self.fwd.ws.max_logit_rows
             self.out_host = torch.zeros(2 * L, dtype=torch.int32).pin_memory()
@@ -126,7 +138,12 @@ class DeepSeekRunner(ModelRunner):
             self.fwd = ReferenceForward(weights, self.pool, emulate_bf16=emulate_bf16)
         self.graphs: Dict[int, tuple] = {}
         self.txns: Dict[int, ExecutionBatch] = {}
-        self._hidden_rows: Dict[int, torch.Tensor] = {}     # state slot -> last hidden state (MTP input)
+        # multi-token prediction: per state slot, the hidden rows whose MTP row is not written yet
+        self.mtp_enabled = bool(enable_mtp and weights.mtp)
+        self._mtp: Dict[int, _MtpTrack] = {}
+        self._txn_hidden: Dict[int, torch.Tensor] = {}
+        self._txn_keep: Dict[int, Dict[int, int]] = {}
+        self._mtp_staging: Optional[BatchStaging] = None
 
     # ------------------------------------------------------------------ contract
     def capabilities(self) -> ExecutionCapabilities:
@@ -169,13 +186,24 @@ class DeepSeekRunner(ModelRunner):
         else:
             out = self._execute_cuda(b)
         self.stats.forward_ns += time.perf_counter_ns() - t0
+        if self.mtp_enabled:
+            self._txn_hidden[txn_id] = self._last_hidden[:b.rows].clone()
         return Complete(out)
 
     def resume(self, txn_id: int):
         return self.execute(txn_id)
 
+    def retain_provisional_prefixes(self, txn_id: int, rows_by_slot: Dict[int, int]) -> None:
+        # rejected rows stay in the pool as dead rows past the committed length; only the MTP
+        # bookkeeping needs to know how many rows of each sequence survive
+        self._txn_keep[txn_id] = dict(rows_by_slot)
+
     def end_transaction(self, txn_id: int, intent: EndIntent) -> EndStatus:
-        self.txns.pop(txn_id, None)
+        b = self.txns.pop(txn_id, None)
+        h = self._txn_hidden.pop(txn_id, None)
+        keep = self._txn_keep.pop(txn_id, None)
+        if b is not None and h is not None and intent == EndIntent.PUBLISH:
+            self._mtp_track(b, h, keep)
         return EndStatus.COMPLETE
 
     def release_pages(self, pages: Sequence[int]) -> None:
@@ -188,7 +216,92 @@ class DeepSeekRunner(ModelRunner):
         self.pool.restore_pages(pages, snapshot)
 
     def release_slot(self, state_slot: int) -> None:
-        self._hidden_rows.pop(state_slot, None)
+        self._mtp.pop(state_slot, None)
+
+    # ------------------------------------------------------------------ multi-token prediction
+    def _mtp_track(self, b: ExecutionBatch, h: torch.Tensor, keep: Optional[Dict[int, int]]) -> None:
+        """Queue the published rows: MTP row i pairs hidden state i with token i + 1, so a row can
+        only be written once its successor token is known (at the next `propose`)."""
+        for s in b.sequences:
+            n = s.query_len if keep is None else min(s.query_len, keep.get(s.state_slot, 0))
+            if n <= 0:
+                continue
+            q0 = s.query_start
+            first = b.positions[q0]
+            tr = self._mtp.get(s.state_slot)
+            if tr is None or tr.next_pos + len(tr.tokens) != first:
+                # no history for this slot (or a gap, e.g. after a fork): start from here; earlier
+                # MTP rows keep whatever the shared pages hold, which only affects draft quality
+                tr = self._mtp[s.state_slot] = _MtpTrack(first)
+            tr.hidden.append(h[q0:q0 + n])
+            tr.tokens.extend(b.token_ids[q0:q0 + n])
+            tr.blocks = list(b.block_ids[s.block_start:s.block_start + s.block_len])
+
+    def proposals_enabled(self) -> bool:
+        return self.mtp_enabled
+
+    def propose(self, slots, anchors, positions, views, max_draft):
+        """One draft token per sequence from the first MTP stage.  Writes the MTP layer's KV rows for
+        every published position that has none yet, then reads the stage's greedy token at the last one.
+        Mirrors the reference's hidden-tap driven proposal (crates/ferrule-engine/src/engine.rs:618-730)."""
+        out = [Proposal([], []) for _ in slots]
+        if not self.mtp_enabled or max_draft < 1:
+            return out
+        todo = []
+        for i, (slot, pos) in enumerate(zip(slots, positions)):
+            tr = self._mtp.get(slot)
+            if tr is not None and tr.tokens and tr.next_pos + len(tr.tokens) == pos:
+                todo.append((i, slot, tr))
+        ps = self.page_size
+        while todo:
+            group, rows = [], 0
+            while todo and len(group) < self.max_seqs and rows + len(todo[0][2].tokens) <= self.max_rows:
+                rows += len(todo[0][2].tokens)
+                group.append(todo.pop(0))
+            if not group:
+                todo.pop(0)       # a single backlog larger than the row budget: skip drafting for it
+                continue
+            if self._mtp_staging is None:
+                self._mtp_staging = BatchStaging(self.max_rows, self.max_seqs, self.max_blocks, self.device)
+            st = self._mtp_staging
+            r = 0
+            hs = []
+            for j, (i, slot, tr) in enumerate(group):
+                k = len(tr.tokens)
+                pos0 = tr.next_pos
+                st.np_ids[r:r + k] = tr.tokens[1:] + [anchors[i]]
+                pp = np.arange(pos0, pos0 + k)
+                st.np_pos[r:r + k] = pp
+                st.np_rpos[r:r + k] = pp
+                st.np_seq[r:r + k] = j
+                blocks = np.asarray(tr.blocks, dtype=np.int64)
+                st.np_slot[r:r + k] = blocks[pp // ps] * ps + pp % ps
+                st.np_bt[j, :len(tr.blocks)] = tr.blocks
+                st.np_lrows[j] = r + k - 1
+                hs.extend(tr.hidden)
+                r += k
+            self.stats.h2d_bytes += st.upload()
+            db = st.device_batch(r, len(group))
+            h_prev = torch.cat(hs, 0) if len(hs) > 1 else hs[0]
+            if self.is_cuda:
+                ids, vals, _ = self.fwd.mtp_forward(0, h_prev, db)
+                ids_h, vals_h = ids.tolist(), vals.tolist()
+            else:
+                allreduce = self.tp.allreduce_reference if self.tp is not None else None
+                with torch.no_grad():
+                    logits, _ = self.fwd.mtp_forward(0, h_prev.float(), db, allreduce)
+                    if self.tp is not None:
+                        logits = self.tp.gather_vocab_reference(logits)
+                vals_t, ids_t = logits.max(-1)
+                ids_h, vals_h = ids_t.tolist(), vals_t.tolist()
+            for j, (i, slot, tr) in enumerate(group):
+                # every queued row now has its MTP row; the anchor's own row follows once it is published
+                tr.next_pos += len(tr.tokens)
+                tr.tokens, tr.hidden = [], []
+                if ids_h[j] >= 0 and vals_h[j] == vals_h[j]:
+                    out[i] = Proposal([int(ids_h[j])], [float(vals_h[j])])
+            self.stats.mtp_proposals += len(group)
+        return out
 
     # ------------------------------------------------------------------ execution paths
     def _is_pure_decode(self, b: ExecutionBatch) -> bool:
@@ -202,6 +315,7 @@ class DeepSeekRunner(ModelRunner):
             T, R, lrows = st.fill(b)
             self.stats.h2d_bytes += st.upload()
             graph.replay()
+            self._last_hidden = graph.hidden
             self.stats.graph_steps += 1
             self.stats.kernel_launches += graph.launches
             L = len(lrows)
@@ -215,6 +329,7 @@ class DeepSeekRunner(ModelRunner):
                 raise ValueError("more logit rows than the runner was sized for")
             want_topk = any(b.logits[r].k > 1 for r in lrows)
             fwd.forward(st.device_batch(T, L), want_logits=want_topk)
+            self._last_hidden = fwd.last_hidden
             self.stats.eager_steps += 1
             self.stats.kernel_launches += fwd.launches
         rows: List[RowOutput] = []
@@ -255,6 +370,7 @@ class DeepSeekRunner(ModelRunner):
         gather = self.tp.gather_vocab_reference if self.tp is not None else None
         with torch.no_grad():
             h = self.fwd.hidden_states(db, allreduce)
+            self._last_hidden = h
             if L == 0:
                 return ExecutionOutput(rows)
             logits = self.fwd.logits_from_hidden(h, db)

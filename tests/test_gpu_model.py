@@ -105,3 +105,39 @@ def test_decode_graph_replay_matches_eager():
     assert torch.equal(nid.cpu(), eager_id.cpu())
     assert torch.allclose(nval, eager_val)
     assert g.launches > 0
+
+
+def test_mtp_speculative_decoding_on_gpu_equals_greedy():
+    """Engine-level: MTP drafts + packed verification emit the greedy stream (smoke shape with one MTP stage)."""
+    from ferrule_b200.models.runner import DeepSeekRunner
+    from ferrule_b200.ops import _lib
+    from ferrule_b200.runtime.engine import Engine, EngineConfig, TokenEvent
+    from ferrule_b200.runtime.scheduler import SchedulerConfig
+    from ferrule_b200.runtime.session import GenerateRequest
+    cfg = C.smoke_gpu().with_(n_mtp_layers=1)
+    w = W.random_weights(cfg, device="cuda", seed=4, std=0.05)
+    assert w.mtp
+    g = torch.Generator().manual_seed(0)
+    prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (40, 75, 23)]
+
+    def run(spec):
+        runner = DeepSeekRunner(w, n_pages=32, page_size=64, max_rows=256, max_seqs=4, max_seq_len=512, device="cuda")
+        sched = SchedulerConfig(max_active_sequences=4, max_decode_batch=4, max_batch_tokens=256,
+                                prefill_chunk_size=128, ctx_size=512)
+        eng = Engine(runner, EngineConfig(scheduler=sched, kv_pages=32, page_size=64, speculative=spec, max_draft=1,
+                                          confidence_threshold=0.0))
+        for i, p in enumerate(prompts):
+            eng.submit(GenerateRequest(f"r{i}", p, max_new_tokens=10, ignore_eos=True))
+        ev = []
+        eng.run_until_idle(ev.append, max_steps=2000)
+        toks = {f"r{i}": [e.token for e in ev if isinstance(e, TokenEvent) and e.request_id == f"r{i}"]
+                for i in range(len(prompts))}
+        return toks, eng, runner
+
+    want, _, _ = run(False)
+    got, eng, runner = run(True)
+    _lib.raise_on_status()
+    assert runner.stats.mtp_proposals > 0 and eng.spec.metrics.drafted > 0
+    # verification rows run through the same split-KV attention and the same per-row GEMM order as
+    # decode rows, so the streams are equal token for token
+    assert got == want
