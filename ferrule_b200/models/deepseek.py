@@ -25,7 +25,7 @@ import torch
 
 from ..ops import reference as ref
 from .config import ModelConfig
-from .weights import LayerWeights, ModelWeights
+from .weights import LayerWeights, ModelWeights, QuantWeight
 
 
 @dataclass
@@ -98,10 +98,17 @@ class ReferenceForward:
                                    cfg.rope_factor, cfg.rope_orig_max_pos, cfg.rope_beta_fast,
                                    cfg.rope_beta_slow)
         self.cos, self.sin = cos.to(dev), sin.to(dev)
+        # oracle of an FP8 model: inputs of quantised linears go through the 1 x 128 FP8 round trip
+        if getattr(weights, "act_quant", False):
+            from ..io import encoding as enc
+            self.aq = lambda x: enc.act_dequant_fp8(*enc.act_quant_fp8(x))
+        else:
+            self.aq = lambda x: x
 
     # -- pieces ------------------------------------------------------------------------
     def _attention(self, lw: LayerWeights, layer: int, xn: torch.Tensor, b: DeviceBatch) -> torch.Tensor:
         cfg, rnd = self.cfg, self.rnd
+        xn = self.aq(xn)
         T = xn.shape[0]
         hl = self.w.heads_local
         qhd, lora, rope, nope = cfg.q_head_dim, cfg.kv_lora_rank, cfg.qk_rope_dim, cfg.qk_nope_dim
@@ -109,7 +116,7 @@ class ReferenceForward:
         if cfg.q_lora_rank:
             qa, ckv = qkv[:, :cfg.q_lora_rank], qkv[:, cfg.q_lora_rank:]
             qn = rnd(ref.rmsnorm(qa, lw.q_norm, cfg.rms_eps))
-            q = rnd(qn @ lw.w_q_b.float().T)
+            q = rnd(self.aq(qn) @ lw.w_q_b.float().T)
         else:
             q, ckv = qkv[:, :hl * qhd], qkv[:, hl * qhd:]
         q = q.view(T, hl, qhd)
@@ -128,13 +135,13 @@ class ReferenceForward:
         o_lat = rnd(ref.mla_paged_attention(q_full, pool_l, b.block_table, b.row_seq[:T], b.row_pos[:T],
                                             self.pool.page_size, lora, cfg.softmax_scale, sink=lw.attn_sink))
         o = rnd(torch.einsum("thk,hnk->thn", o_lat, lw.w_uv.float())).reshape(T, -1)
-        return o @ lw.w_o.float().T          # partial sum over this rank's heads
+        return self.aq(o) @ lw.w_o.float().T          # partial sum over this rank's heads
 
     def _ffn(self, w13: torch.Tensor, w2: torch.Tensor, x: torch.Tensor) -> torch.Tensor:
         inter = w13.shape[-2] // 2
-        y = x @ w13[0].float().T
+        y = self.aq(x) @ w13[0].float().T
         h = self.rnd(ref.swiglu(y[:, :inter], y[:, inter:], self.cfg.swiglu_limit))
-        return h @ w2[0].float().T
+        return self.aq(h) @ w2[0].float().T
 
     def _moe(self, lw: LayerWeights, xn: torch.Tensor, token_ids: torch.Tensor) -> torch.Tensor:
         cfg, rnd = self.cfg, self.rnd
@@ -150,9 +157,9 @@ class ReferenceForward:
             if rows.numel() == 0:
                 continue
             wsel = (wts * hit)[rows].sum(-1, keepdim=True)
-            y = xn[rows] @ lw.e_w13[e - self.w.e_lo].float().T
+            y = self.aq(xn[rows]) @ lw.e_w13[e - self.w.e_lo].float().T
             h = rnd(ref.swiglu(y[:, :I], y[:, I:], cfg.swiglu_limit))
-            out[rows] += rnd((h @ lw.e_w2[e - self.w.e_lo].float().T) * wsel)
+            out[rows] += rnd((self.aq(h) @ lw.e_w2[e - self.w.e_lo].float().T) * wsel)
         if lw.w13 is not None:
             out = out + rnd(self._ffn(lw.w13, lw.w2, xn))
         return out
@@ -280,6 +287,21 @@ class CudaWorkspace:
         self.next_id = self.out_buf[:L]
         self.next_val = self.out_buf[L:].view(torch.float32)
         self.mtp_x = torch.zeros(R, 2 * H, **bf) if w.mtp else None
+        # FP8 models: e4m3 codes + UE8M0 scales (one per 1 x 128) of the activation rows feeding each linear
+        self.act_q = {}
+        if w.weight_format != "bf16":
+            u8 = dict(dtype=torch.uint8, device=device)
+
+            def pair(rows, width):
+                width = (max(width, 128) + 127) // 128 * 128
+                return torch.zeros(rows, width, **u8), torch.zeros(rows, width // 128, **u8)
+
+            self.act_q["xn"] = pair(R, H)
+            self.act_q["a"] = pair(R, max(cfg.q_lora_rank, hl * cfg.v_head_dim, 2 * H if w.mtp else 0))
+            self.act_q["mid"] = pair(R, inter_max)
+            if self.has_moe:
+                self.act_q["xg"] = pair(R * cfg.topk, H)
+                self.act_q["hmid"] = pair(R * cfg.topk, cfg.moe_inter)
 
     def nbytes(self) -> int:
         tot = 0
@@ -299,7 +321,8 @@ class CudaForward:
                  max_logit_rows: int = 256, decode_rows: int = 64, max_seq_len: int = 4096,
                  attn_splits: int = 8, tp=None):
         from ..ops import kernels as K
-        self.K = K
+        from ..ops import quant as Q
+        self.K, self.Q = K, Q
         self.w, self.cfg, self.pool, self.tp = weights, weights.cfg, pool, tp
         dev = weights.embed.device
         self.device = dev
@@ -315,16 +338,34 @@ class CudaForward:
         self.side_stream = torch.cuda.Stream(device=dev)      # shared experts run beside the routed path
 
     # -- sublayers -----------------------------------------------------------------------
+    # -- linear dispatch -------------------------------------------------------------------
+    def _quant(self, x: torch.Tensor, slot: str):
+        """1 x 128 FP8 quantisation of activation rows into the workspace pair named `slot`."""
+        q, s = self.ws.act_q[slot]
+        rows, n = x.shape
+        q, s = q[:rows, :n], s[:rows, :n // 128]
+        self.Q.quant_fp8_rows(x, out=(q, s))
+        return q, s
+
+    def _gemm(self, x, w, out, slot: str = "a", xq=None, **kw):
+        """bf16 weight -> bf16 tcgen05 GEMM; QuantWeight -> quantise the rows (unless `xq` is given)
+        and run the block-scaled FP8 GEMM."""
+        if isinstance(w, QuantWeight):
+            if xq is None:
+                xq = self._quant(x, slot)
+            return self.Q.gemm_fp8(xq[0], xq[1], w.q, w.scale, out=out, group32=w.group32, **kw)
+        return self.K.gemm(x, w, out=out, **kw)
+
     def _attention(self, lw: LayerWeights, layer: int, xn: torch.Tensor, b: DeviceBatch, T: int) -> torch.Tensor:
         K, cfg, ws = self.K, self.cfg, self.ws
         hl = self.w.heads_local
         qhd, lora, rope, nope, vd = cfg.q_head_dim, cfg.kv_lora_rank, cfg.qk_rope_dim, cfg.qk_nope_dim, cfg.v_head_dim
         qkv = ws.qkv[:T]
-        K.gemm(xn, lw.w_qkv_a, out=qkv)
+        self._gemm(xn, lw.w_qkv_a, qkv, slot="xn")
         if cfg.q_lora_rank:
             qa, ckv = qkv[:, :cfg.q_lora_rank], qkv[:, cfg.q_lora_rank:]
             K.add_rmsnorm(qa, lw.q_norm, cfg.rms_eps, norm_out=ws.qn[:T])
-            q = K.gemm(ws.qn[:T], lw.w_q_b, out=ws.q[:T])
+            q = self._gemm(ws.qn[:T], lw.w_q_b, ws.q[:T], slot="a")
         else:
             q, ckv = qkv[:, :hl * qhd], qkv[:, hl * qhd:]
         q_full = ws.q_full[:T]
@@ -353,8 +394,13 @@ class CudaForward:
         K, cfg, ws = self.K, self.cfg, self.ws
         k, H = cfg.topk, cfg.hidden
         idx, wts = ws.topk_idx[:T], ws.topk_w[:T]
-        plan = ws.plans[self._moe_ntok(T)]
+        ntok = self._moe_ntok(T)
+        if isinstance(lw.e_w13, QuantWeight):
+            ntok = min(ntok, 32)            # row-tile limit of the FP8 SwiGLU / group-scaled kernels
+        plan = ws.plans[ntok]
         side = None
+        # FP8 shared experts read the quantised normed rows: quantise before the fork
+        xq_n = self._quant(xn, "xn") if isinstance(lw.w13, QuantWeight) else None
         if lw.w13 is not None:
             # The shared experts only need the normalised activations: fork them onto a second stream
             # (a parallel branch when captured in a graph) so they fill the SMs that the latency-bound
@@ -365,8 +411,8 @@ class CudaForward:
             with torch.cuda.stream(side):
                 inter = lw.w13.shape[1] // 2
                 mid = ws.ffn_mid[:T, :inter]
-                K.gemm(xn, lw.w13, out=mid, epilogue=K.EPI_SWIGLU, act_limit=cfg.swiglu_limit)
-                K.gemm(mid, lw.w2, out=ws.route_out[:T][:, k])
+                self._gemm(xn, lw.w13, mid, xq=xq_n, epilogue=K.EPI_SWIGLU, act_limit=cfg.swiglu_limit)
+                self._gemm(mid, lw.w2, ws.route_out[:T][:, k], slot="mid")
         if T <= self.fused_router_rows and H % 256 == 0:
             K.router_plan_fused(xn, lw.router_w, k, cfg.score_fn, plan, self.w.e_lo, self.w.e_hi, idx, wts,
                                 ws.router_ctr, bias=lw.router_bias, n_groups=cfg.n_groups,
@@ -380,12 +426,12 @@ class CudaForward:
                           hash_table=lw.hash_table, token_ids=b.token_ids, out_idx=idx, out_w=wts)
             K.moe_plan(idx, wts, plan, self.w.e_lo, self.w.e_hi, dst_slots=ws.slots)
         K.gather_rows(xn, plan, ws.xg, cap_rows=T * k)
-        K.gemm(ws.xg[:T * k], lw.e_w13, out=ws.hmid[:T * k], epilogue=K.EPI_SWIGLU, plan=plan,
-               act_limit=cfg.swiglu_limit)
+        self._gemm(ws.xg[:T * k], lw.e_w13, ws.hmid[:T * k], slot="xg", epilogue=K.EPI_SWIGLU, plan=plan,
+                   act_limit=cfg.swiglu_limit)
         route_out = ws.route_out[:T]
         # route r = t*k + s is written to row t*slots + s (the plan kernel emits that row index)
-        K.gemm(ws.hmid[:T * k], lw.e_w2, out=route_out.view(T * ws.slots, H), epilogue=K.EPI_SCATTER,
-               plan=plan, scatter_rows=T * ws.slots)
+        self._gemm(ws.hmid[:T * k], lw.e_w2, route_out.view(T * ws.slots, H), slot="hmid", epilogue=K.EPI_SCATTER,
+                   plan=plan, scatter_rows=T * ws.slots)
         if side is not None:
             torch.cuda.current_stream().wait_stream(side)
         return idx
@@ -398,8 +444,13 @@ class CudaForward:
         K.add_rmsnorm(h_in, lw.attn_norm, cfg.rms_eps, norm_out=xn)
         a = self._attention(lw, layer, xn, b, T)
         if tp is None:
-            K.gemm(a, lw.w_o, out=ws.delta[:T])
+            self._gemm(a, lw.w_o, ws.delta[:T], slot="a")
             K.add_rmsnorm(h_in, lw.ffn_norm, cfg.rms_eps, delta=ws.delta[:T], res_out=h_out, norm_out=xn)
+            h_mid = h_out
+        elif isinstance(lw.w_o, QuantWeight):
+            self._gemm(a, lw.w_o, ws.delta[:T], slot="a")
+            tp.add_allreduce(ws.delta[:T], residual=h_in, out=h_out, T=T)
+            K.add_rmsnorm(h_out, lw.ffn_norm, cfg.rms_eps, norm_out=xn)
             h_mid = h_out
         else:
             tp.gemm_allreduce(a, lw.w_o, residual=h_in, out=h_out, T=T)
@@ -417,11 +468,14 @@ class CudaForward:
             return h_in            # the layer's result lands back in the input buffer
         inter = lw.w13.shape[1] // 2
         mid = ws.ffn_mid[:T, :inter]
-        K.gemm(xn, lw.w13, out=mid, epilogue=K.EPI_SWIGLU, act_limit=cfg.swiglu_limit)
+        self._gemm(xn, lw.w13, mid, slot="xn", epilogue=K.EPI_SWIGLU, act_limit=cfg.swiglu_limit)
         if tp is None:
-            K.gemm(mid, lw.w2, out=ws.delta[:T])
+            self._gemm(mid, lw.w2, ws.delta[:T], slot="mid")
             # residual add is folded into the next consumer through a plain add+norm without a norm output
             K.add_rmsnorm(h_mid, None, cfg.rms_eps, delta=ws.delta[:T], res_out=h_in, want_norm=False)
+        elif isinstance(lw.w2, QuantWeight):
+            self._gemm(mid, lw.w2, ws.delta[:T], slot="mid")
+            tp.add_allreduce(ws.delta[:T], residual=h_mid, out=h_in, T=T)
         else:
             tp.gemm_allreduce(mid, lw.w2, residual=h_mid, out=h_in, T=T)
         return h_in
@@ -474,7 +528,7 @@ class CudaForward:
         K.add_rmsnorm(e, m.enorm, cfg.rms_eps, norm_out=x[:, H:])
         # h_prev (usually ws.h[0]) is consumed by now, so the projection may overwrite it
         h0 = ws.h[0][:T]
-        K.gemm(x, m.eh_proj, out=h0)
+        self._gemm(x, m.eh_proj, h0, slot="a")
         h = self.layer(m.layer, cfg.n_layers + stage, h0, ws.h[1][:T], b, T)
         self.last_hidden = h
         return self.head(h, b, m.final_norm)

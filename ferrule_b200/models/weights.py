@@ -27,6 +27,113 @@ import torch
 from .config import ModelConfig
 
 
+class QuantWeight:
+    """A linear weight held as FP8 e4m3 codes plus UE8M0 scales, `[groups, out, in]`.
+
+    group32 = False: one scale per 128 x 128 block, `scale [groups, ceil(out/128), ceil(in/128)]`
+    (the DeepSeek-V3 checkpoint format).  group32 = True: one scale per row per 32 inputs,
+    `scale [groups, out, in/32]`: MXFP4 expert weights whose e2m1 values were expanded to e4m3
+    codes at load time (every e2m1 value is exactly representable), so the tensor-core path is
+    the FP8 one while the scale grid stays MXFP4's.
+    """
+    __slots__ = ("q", "scale", "group32")
+
+    def __init__(self, q: torch.Tensor, scale: torch.Tensor, group32: bool = False):
+        self.q, self.scale, self.group32 = q, scale, group32
+
+    @property
+    def shape(self):
+        return self.q.shape
+
+    def nbytes(self) -> int:
+        return self.q.numel() + self.scale.numel()
+
+    def dequant(self) -> torch.Tensor:
+        """bf16 tensor with exactly the values the quantised GEMM multiplies by."""
+        from ..io import encoding as enc
+        two_d = self.q.dim() == 2
+        q, scale = (self.q.unsqueeze(0), self.scale.unsqueeze(0)) if two_d else (self.q, self.scale)
+        G, O, I = q.shape
+        v = enc.e4m3_decode(q)
+        sc = enc.e8m0_decode(scale)
+        if self.group32:
+            out = (v.view(G, O, I // 32, 32) * sc.unsqueeze(-1)).view(G, O, I)
+        else:
+            out = v * sc.repeat_interleave(128, 1)[:, :O].repeat_interleave(128, 2)[:, :, :I]
+        out = out.to(torch.bfloat16)
+        return out[0] if two_d else out
+
+    @staticmethod
+    def from_bf16(w: torch.Tensor, fmt: str) -> "QuantWeight":
+        """fmt 'fp8_block' or 'mxfp4'; w [groups, out, in] (or [out, in])."""
+        from ..io import encoding as enc
+        two_d = w.dim() == 2
+        if two_d:
+            w = w.unsqueeze(0)
+        qs, ss = [], []
+        for g in range(w.shape[0]):
+            if fmt == "fp8_block":
+                q, sb = enc.weight_quant_fp8_block(w[g])
+            elif fmt == "mxfp4":
+                # quantise in row chunks: the nearest-code search expands every element eightfold
+                parts = [enc.weight_quant_mxfp4(w[g][r:r + 1024]) for r in range(0, w.shape[1], 1024)]
+                packed, sb = torch.cat([a for a, _ in parts]), torch.cat([b for _, b in parts])
+                q = enc.e4m3_encode(enc.fp4_unpack(packed))
+            else:
+                raise ValueError(f"unknown weight format {fmt}")
+            qs.append(q)
+            ss.append(sb)
+        q, sc = torch.stack(qs).contiguous(), torch.stack(ss).contiguous()
+        return QuantWeight(q[0] if two_d else q, sc[0] if two_d else sc, fmt == "mxfp4")
+
+
+WEIGHT_FORMATS = ("bf16", "fp8_block", "fp8_mxfp4")
+_DENSE_FIELDS = ("w_qkv_a", "w_q_b", "w_o", "w13", "w2")
+_EXPERT_FIELDS = ("e_w13", "e_w2")
+
+
+def quantize_layer_(lw: "LayerWeights", fmt: str) -> "LayerWeights":
+    """In place: dense / attention projections -> FP8 128 x 128 blocks; routed experts -> FP8 blocks
+    ('fp8_block') or MXFP4 ('fp8_mxfp4').  Norms, router, absorbed W_UK / W_UV stay bf16."""
+    if fmt == "bf16":
+        return lw
+    assert fmt in WEIGHT_FORMATS
+    for name in _DENSE_FIELDS:
+        t = getattr(lw, name)
+        if isinstance(t, torch.Tensor):
+            setattr(lw, name, QuantWeight.from_bf16(t, "fp8_block"))
+    for name in _EXPERT_FIELDS:
+        t = getattr(lw, name)
+        if isinstance(t, torch.Tensor):
+            setattr(lw, name, QuantWeight.from_bf16(t, "mxfp4" if fmt == "fp8_mxfp4" else "fp8_block"))
+    return lw
+
+
+def dequantized_copy(w: "ModelWeights") -> "ModelWeights":
+    """bf16 model holding the values a quantised model computes with (oracle for parity tests)."""
+    import copy
+
+    def layer(lw):
+        c = copy.copy(lw)
+        for name in _DENSE_FIELDS + _EXPERT_FIELDS:
+            t = getattr(c, name)
+            if isinstance(t, QuantWeight):
+                d = t.dequant()
+                setattr(c, name, d)
+        return c
+
+    out = copy.copy(w)
+    out.layers = [layer(l) for l in w.layers]
+    out.mtp = []
+    for m in w.mtp:
+        mc = copy.copy(m)
+        mc.layer = layer(m.layer)
+        out.mtp.append(mc)
+    out.weight_format = "bf16"
+    out.act_quant = w.weight_format != "bf16"
+    return out
+
+
 @dataclass
 class LayerWeights:
     attn_norm: torch.Tensor
@@ -74,6 +181,8 @@ class ModelWeights:
     e_lo: int = 0
     e_hi: int = 0
     vocab_lo: int = 0
+    weight_format: str = "bf16"
+    act_quant: bool = False       # oracle only: emulate the 1 x 128 FP8 activation quantisation of the FP8 path
 
     @property
     def heads_local(self) -> int:
@@ -85,7 +194,10 @@ class ModelWeights:
 
         def add(t):
             nonlocal total
-            if isinstance(t, torch.Tensor) and t.data_ptr() not in seen:
+            if isinstance(t, QuantWeight):
+                add(t.q)
+                add(t.scale)
+            elif isinstance(t, torch.Tensor) and t.data_ptr() not in seen:
                 seen.add(t.data_ptr())
                 total += t.numel() * t.element_size()
 
@@ -193,7 +305,8 @@ def _layer_random(cfg: ModelConfig, layer: int, init: _Init, tp_rank: int, tp_wo
 
 
 def random_weights(cfg: ModelConfig, device="cpu", dtype=torch.bfloat16, seed: int = 0, std: float = 0.02,
-                   tp_rank: int = 0, tp_world: int = 1, fast_device_init: bool = False) -> ModelWeights:
+                   tp_rank: int = 0, tp_world: int = 1, fast_device_init: bool = False,
+                   weight_format: str = "bf16") -> ModelWeights:
     """Random-init weights N(0, std), norms = 1.
 
     fast_device_init draws on the GPU (much faster for multi-GB models; values then differ
@@ -201,16 +314,19 @@ def random_weights(cfg: ModelConfig, device="cpu", dtype=torch.bfloat16, seed: i
     """
     init = _Init(seed, std, device, dtype, fast_device_init)
     embed = init.normal(cfg.vocab_size, cfg.hidden)
-    layers = [_layer_random(cfg, i, init, tp_rank, tp_world) for i in range(cfg.n_layers)]
+    # quantise layer by layer so that at most one layer exists in bf16 at a time
+    layers = [quantize_layer_(_layer_random(cfg, i, init, tp_rank, tp_world), weight_format)
+              for i in range(cfg.n_layers)]
     v_lo, v_hi = _shard_range(cfg.vocab_size, tp_rank, tp_world)
     lm_head = init.normal(cfg.vocab_size, cfg.hidden)[v_lo:v_hi].contiguous()
     mtp = []
     for m in range(cfg.n_mtp_layers):
         mtp.append(MtpWeights(enorm=init.ones(cfg.hidden), hnorm=init.ones(cfg.hidden),
                               eh_proj=init.normal(cfg.hidden, 2 * cfg.hidden),
-                              layer=_layer_random(cfg, cfg.n_layers + m, init, tp_rank, tp_world,
-                                                  force_moe=cfg.n_routed_experts > 0),
+                              layer=quantize_layer_(_layer_random(cfg, cfg.n_layers + m, init, tp_rank, tp_world,
+                                                                  force_moe=cfg.n_routed_experts > 0),
+                                                    weight_format),
                               final_norm=init.ones(cfg.hidden)))
     e_lo, e_hi = _shard_range(cfg.n_routed_experts, tp_rank, tp_world) if cfg.n_routed_experts else (0, 0)
     return ModelWeights(cfg, embed, layers, init.ones(cfg.hidden), lm_head, mtp, tp_rank, tp_world,
-                        e_lo, e_hi, v_lo)
+                        e_lo, e_hi, v_lo, weight_format=weight_format)

@@ -10,13 +10,19 @@ import ctypes as C
 from ._lib import check, get_lib, ptr, status_tensor, stream_ptr
 
 
-def quant_fp8_rows(x: torch.Tensor, writeback: bool = False) -> Tuple[torch.Tensor, torch.Tensor]:
+def quant_fp8_rows(x: torch.Tensor, writeback: bool = False,
+                   out: Optional[Tuple[torch.Tensor, torch.Tensor]] = None) -> Tuple[torch.Tensor, torch.Tensor]:
     """bf16 [rows, n] -> (uint8 e4m3 codes, uint8 UE8M0 scales [rows, n/128]); writeback=True also
-    overwrites x with the dequantised values (QAT)."""
+    overwrites x with the dequantised values (QAT).  `out` = preallocated (codes, scales) views."""
     lib = get_lib(True)
     rows, n = x.shape
-    q = torch.empty(rows, n, dtype=torch.uint8, device=x.device)
-    s = torch.empty(rows, n // 128, dtype=torch.uint8, device=x.device)
+    assert n % 128 == 0 and x.stride(1) == 1
+    if out is None:
+        q = torch.empty(rows, n, dtype=torch.uint8, device=x.device)
+        s = torch.empty(rows, n // 128, dtype=torch.uint8, device=x.device)
+    else:
+        q, s = out
+        assert q.shape == (rows, n) and s.shape == (rows, n // 128) and q.stride(1) == 1 and s.stride(1) == 1
     check(lib.fb_quant_fp8_rows(x.data_ptr(), x.stride(0), q.data_ptr(), q.stride(0), s.data_ptr(), s.stride(0), rows, n,
                                 1 if writeback else 0, stream_ptr()), "fb_quant_fp8_rows")
     return q, s
@@ -125,4 +131,4 @@ def mxfp4_to_e4m3_containers(packed: torch.Tensor) -> torch.Tensor:
     """Packed e2m1 [.., n/2] -> uint8 e4m3 codes [.., n] holding exactly the same values (load-time expansion
     for the group-scaled FP8 GEMM)."""
     from ..io import encoding as enc
-    return enc.e4m3_encode(enc.fp4_unpack(packed.cpu())).to(packed.device)
+    return enc.e4m3_encode(enc.fp4_unpack(packed))

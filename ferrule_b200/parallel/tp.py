@@ -51,6 +51,7 @@ class TensorParallel:
         self.hidden = H
         rows = self.fused_max_rows
         self._tmp32 = torch.zeros(fwd.ws.max_rows, H, dtype=torch.float32, device=self.device)
+        self._no_idx = torch.zeros(8, dtype=torch.int32, device=self.device)     # top-k table of a route-free reduce
         self._pairs = torch.zeros(self.world, fwd.ws.max_logit_rows, 2, dtype=torch.float32, device=self.device)
         if not self.fused:
             return
@@ -112,6 +113,12 @@ class TensorParallel:
         out.copy_(tmp)
         self.calls_nccl += 1
         return out
+
+    def add_allreduce(self, delta: torch.Tensor, residual: torch.Tensor, out: torch.Tensor, T: int) -> torch.Tensor:
+        """out = residual + sum over ranks of delta [T, hidden]: the partial result of a row-parallel linear
+        whose GEMM has no collective epilogue (FP8 weights).  Runs the one-shot push all-reduce with a single
+        dense slot per token."""
+        return self.moe_reduce_allreduce(delta, 1, 0, self._no_idx, 0, 0, residual, out, T)
 
     def argmax_across_vocab(self, ids: torch.Tensor, vals: torch.Tensor, vocab_lo: int, L: int) -> None:
         """In place: local (id, logit) of a vocabulary shard -> global greedy token on every rank."""

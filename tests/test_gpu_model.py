@@ -141,3 +141,51 @@ def test_mtp_speculative_decoding_on_gpu_equals_greedy():
     # verification rows run through the same split-KV attention and the same per-row GEMM order as
     # decode rows, so the streams are equal token for token
     assert got == want
+
+
+@pytest.mark.parametrize("fmt,preset", [("fp8_block", "smoke-gpu"), ("fp8_mxfp4", "smoke-gpu"),
+                                        ("fp8_block", "smoke-qlora")])
+def test_quantised_forward_matches_dequantised_oracle(fmt, preset):
+    """FP8 block-scaled dense / attention weights and FP8 or MXFP4 routed experts: the kernel pipeline against
+    the reference forward run on the dequantised weights with the same 1 x 128 activation quantisation."""
+    cfg = C.smoke_gpu()
+    if preset == "smoke-qlora":
+        cfg = cfg.with_(q_lora_rank=256, score_fn=C.SCORE_SIGMOID, n_groups=4, topk_groups=2, router_bias=True,
+                        norm_topk_prob=True, route_scale=2.5, n_mtp_layers=1)
+    dev = "cuda"
+    w = W.random_weights(cfg, device=dev, seed=3, std=0.05, weight_format=fmt)
+    assert isinstance(w.layers[1].e_w13, W.QuantWeight) and w.layers[1].e_w13.group32 == (fmt == "fp8_mxfp4")
+    assert w.nbytes() < 0.75 * W.random_weights(cfg, device=dev, seed=3, std=0.05).nbytes()
+    oracle = W.dequantized_copy(w)
+    page = 16
+    pool_a, pool_b = D.KvPool(cfg, 64, page, dev), D.KvPool(cfg, 64, page, dev)
+    fwd = D.CudaForward(w, pool_a, max_rows=256, max_logit_rows=16, decode_rows=16, max_seq_len=512, attn_splits=4)
+    reff = D.ReferenceForward(oracle, pool_b, emulate_bf16=True)
+    lens, new = [0, 0, 0], [37, 16, 5]
+    for step in range(3):
+        b = _batch(dev, lens, new, page, 8, cfg.vocab_size, seed=step)
+        nid, nval, logits = fwd.forward(b, want_logits=True)
+        rl, rh = reff.forward(b, return_hidden=True)
+        torch.cuda.synchronize()
+        scale = float(rl.abs().max())
+        err = float((logits.float() - rl).abs().max())
+        # Every GEMM is exact to bf16 rounding against the dequantised operands, but a one-ulp bf16 difference in
+        # an activation can move its FP8 code by a whole step (6 %), and a near-tied routing decision can flip:
+        # compare in the RMS sense per row (a wrong scale or layout is off by the full logit scale).
+        diff = logits.float() - rl
+        rel = diff.norm(dim=-1) / rl.norm(dim=-1)
+        # the low-rank-q variant routes with sigmoid scores, group limits and a 2.5x route scale: flips weigh more
+        lim = (0.20, 0.45) if preset == "smoke-qlora" else (0.10, 0.30)
+        assert float(rel.median()) <= lim[0] and float(rel.max()) <= lim[1], f"step {step}: rel rms {rel.tolist()}"
+        top2 = rl.topk(2, dim=-1).values
+        clear = (top2[:, 0] - top2[:, 1]) > 2.5 * err
+        assert torch.equal(nid[clear].long().cpu(), rl.argmax(-1)[clear].cpu())
+        if cfg.n_mtp_layers and step == 0:
+            ml, _ = reff.mtp_forward(0, rh, b)
+            mid, mval, _ = fwd.mtp_forward(0, fwd.last_hidden, b)
+            torch.cuda.synchronize()
+            assert float((mval - ml.max(-1).values).abs().max()) <= 0.25 * float(ml.abs().max()) + 1e-3
+        lens = [l + n for l, n in zip(lens, new)]
+        new = [1, 1, 1]
+    from ferrule_b200.ops import _lib
+    _lib.raise_on_status()
