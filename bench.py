@@ -100,6 +100,8 @@ def main() -> None:
     ap.add_argument("--batch", type=int, default=32)
     ap.add_argument("--prompt-len", type=int, default=512)
     ap.add_argument("--model", default="deepseek-v2-lite")
+    ap.add_argument("--weight-format", default="bf16", choices=["bf16", "fp8_block", "fp8_mxfp4"],
+                    help="bf16 is the headline configuration; the FP8 formats are reported with their own dtype")
     ap.add_argument("--layers", type=int, default=0, help="debug only: override layer count (result is marked invalid)")
     ap.add_argument("--no-fused", action="store_true", help="use the NCCL baseline collectives instead of fused kernels")
     args = ap.parse_args()
@@ -140,7 +142,8 @@ def main() -> None:
     margin = 64                      # sequences that finish prefill early decode ahead of the others
     max_seq = P + K + Wm + margin + 2 * page
     pages_per_seq = (max_seq + page - 1) // page
-    weights = W.random_weights(cfg, device=dev, seed=0, tp_rank=rank, tp_world=world, fast_device_init=True)
+    weights = W.random_weights(cfg, device=dev, seed=0, tp_rank=rank, tp_world=world, fast_device_init=True,
+                               weight_format=args.weight_format)
     runner = DeepSeekRunner(weights, n_pages=B * pages_per_seq + 8, page_size=page, max_rows=2048, max_seqs=B,
                             max_seq_len=pages_per_seq * page, device=dev, tp=tp)
     if tp is not None:
@@ -190,7 +193,8 @@ def main() -> None:
     e1.record()
     barrier()
     e2e_ms = e0.elapsed_time(e1)
-    assert engine.stats.decode_steps - steps_before == K, "a timed engine step was not a decode step"
+    assert engine.stats.decode_steps - steps_before == K, \
+        "a timed engine step was not a decode step (last engine error: %r)" % (engine.last_error,)
     h2d = (runner.stats.h2d_bytes - h2d0) // K
     d2h = (runner.stats.d2h_bytes - d2h0) // K
     e2e_launches = runner.stats.kernel_launches - l0
@@ -227,7 +231,7 @@ def main() -> None:
             "metric": "decode tokens/s (whole job, max over ranks)",
             "value": round(value, 1), "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": Wm,
             "ms_per_step": round(dev_ms / K, 4), "higher_is_better": True, "scaling": "strong",
-            "vs_baseline": round(value / BASELINE_TOK_S, 1), "dtype": "bf16",
+            "vs_baseline": round(value / BASELINE_TOK_S, 1), "dtype": {"bf16": "bf16", "fp8_block": "fp8 e4m3 weights (128x128 scales) + fp8 activations (1x128), bf16 elsewhere", "fp8_mxfp4": "mxfp4 experts + fp8 dense, bf16 elsewhere"}[args.weight_format],
             "data": "synthetic (uniform-random token ids, random-init N(0,0.02) weights)",
             "config": {"model": cfg.name, "global_batch": B, "seq_len": P, "decode_context": P + Wm + 1,
                        "parallelism": par, "kv_page_size": page, "layers": cfg.n_layers,

@@ -31,6 +31,7 @@ CUDA_SOURCES = [
     "elementwise.cu",
     "quant.cu",
     "v4_ops.cu",
+    "ep_moe.cu",
     "comm.cu",
     "no_alloc.cu",
 ]

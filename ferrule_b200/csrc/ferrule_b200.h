@@ -68,6 +68,9 @@ typedef struct FbGemmArgs {
   unsigned long long peer_wait_ns;
   void* status;
   void* trace;              // optional: 8 x uint64 globaltimer stamps written by CTA 0 (profiling)
+  const int* remap_rank;    // epilogue 2, expert-parallel combine: output row -> destination rank and row of
+  const int* remap_row;     //   that rank's bf16 combine buffer (peer_recv[rank], pitch ldo); peer_flags[r][rank]
+                            //   is bumped once per call when all of this rank's rows are stored
 } FbGemmArgs;
 
 int fb_gemm_bf16(const FbGemmArgs* args, void* stream);
@@ -211,6 +214,31 @@ int fb_indexer_scores(const void* q, const void* plane, long long ldp, const flo
 // n_visible (per query) may be NULL, then n_fixed applies; k <= 512
 int fb_indexer_topk(const float* scores, long long ld_s, const int* n_visible, int n_fixed, int k, int* out_idx,
                     long long ldo, int queries, void* stream);
+
+// ---- expert-parallel MoE over peer memory -------------------------------------------------
+// Every rank owns one symmetric buffer with the same layout (byte offsets below):
+//   recv_x    bf16 [world][cap][hidden]   rows dispatched to this rank, one segment per source
+//   recv_meta int4 [world][cap]           {local expert, return row (token * topk + slot), weight bits, 1}
+//   recv_cnt  u32  [world]                rows each source sent in the current call
+//   comb      bf16 [tcap * topk][hidden]  weighted expert outputs returned to this rank
+//   disp_flag / comb_flag / gath_flag  u32 [world]   arrival counters (one per source rank, only grow)
+//   gath_out  bf16 [world][tcap][hidden]  all-gathered layer outputs (optional)
+typedef struct FbEpArgs {
+  void* base[8];
+  long long off_recv_x, off_recv_meta, off_recv_cnt, off_comb, off_disp_flag, off_comb_flag, off_gath_flag,
+      off_gath_out;
+  int rank, world, cap, hidden, topk, experts_local, tcap;
+  unsigned long long wait_ns;
+  void* status;
+} FbEpArgs;
+// cnt_local: u32 [world] zeroed once; every ctr: u32 [2] zeroed once, private to its call site
+int fb_ep_dispatch(const FbEpArgs* a, const void* x, long long ldx, const int* idx, const float* wts, int tokens,
+                   void* cnt_local, void* ctr, void* stream);
+int fb_ep_collect(const FbEpArgs* a, void* ctr, int e_lo, int* r_idx, float* r_w, int* remap_rank, int* remap_row,
+                  void* stream);
+int fb_ep_combine_reduce(const FbEpArgs* a, void* ctr, const void* extra, long long lde, const void* residual,
+                         long long ldr, void* out, long long ldo, int tokens, int allgather, void* stream);
+int fb_ep_gather_wait(const FbEpArgs* a, void* ctr, void* stream);
 
 // ---- peer memory and collectives --------------------------------------------------------
 int fb_ipc_handle_bytes(void);

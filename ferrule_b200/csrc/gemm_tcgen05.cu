@@ -67,6 +67,8 @@ struct GemmParams {
   float* peer_recv[8];       // receive buffer of every rank, in this rank's address space
   uint32_t* peer_flags[8];   // per-tile arrival counters of every rank
   uint32_t* local_ctr;       // [0] = calls completed, [1] = CTAs finished this call, [2..] = consumed arrivals per tile
+  const int* remap_rank;     // kEpiScatter, expert-parallel combine: output row -> destination rank ...
+  const int* remap_row;      // ... and row in that rank's combine buffer (peer_recv[rank], bf16, pitch ldo)
   const __nv_bfloat16* residual;  // optional, added after the reduction
   long long ldr;
   unsigned long long peer_wait_ns;
@@ -384,7 +386,14 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tmap_w,
                 if (p.row_scale) x *= p.row_scale[row0 + r];
                 orow = p.dst_row ? p.dst_row[row0 + r] : orow;
               }
-              if (EPI == kEpiAllReduce) {
+              if (EPI == kEpiScatter && p.remap_rank != nullptr) {
+                // expert-parallel combine: the weighted expert output goes straight into the combine
+                // buffer of the rank that owns the token (plain peer stores over NVLink)
+                if (orow >= 0) {
+                  __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.peer_recv[p.remap_rank[orow]]);
+                  dst[static_cast<long long>(p.remap_row[orow]) * p.ldo + ocol] = __float2bfloat16_rn(x);
+                }
+              } else if (EPI == kEpiAllReduce) {
                 const size_t slot =
                     (static_cast<size_t>((call & 1u) * p.world + p.rank) * p.rows_cap + orow) *
                         p.n_out + n;
@@ -466,6 +475,20 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tmap_w,
       p.local_ctr[1] = 0;
       __threadfence();
       p.local_ctr[0] = call + 1u;
+    }
+  }
+  if (EPI == kEpiScatter && p.remap_rank != nullptr) {
+    // Each thread fences its own peer stores at system scope, the CTA counts itself in, and the last CTA
+    // bumps every rank's flag: this rank's share of the combine is complete.
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      const uint32_t done = atomicAdd(p.local_ctr + 1, 1u);
+      if (done == gridDim.x * gridDim.y * gridDim.z - 1) {
+        p.local_ctr[1] = 0;
+        __threadfence_system();
+        for (int pr = 0; pr < p.world; ++pr) flag_add_release_sys(p.peer_flags[pr] + p.rank, 1u);
+      }
     }
   }
 }
@@ -673,7 +696,23 @@ extern "C" int fb_gemm_bf16(const FbGemmArgs* a, void* stream_) {
     return launch_ntok<false, kEpiAllReduce>(ntok, mw, mx, p, max_tiles, grouped, stream);
   }
   if (dual) return launch_ntok<true, kEpiSwiGLU>(ntok, mw, mx, p, max_tiles, grouped, stream);
-  if (a->epilogue == kEpiScatter)
+  if (a->epilogue == kEpiScatter) {
+    if (a->remap_rank != nullptr) {
+      if (!a->remap_row || !a->local_ctr || a->world < 1 || a->world > 8 || a->rank < 0 || a->rank >= a->world ||
+          a->out_fp32)
+        return FB_ERR_SHAPE;
+      p.rank = a->rank;
+      p.world = a->world;
+      p.remap_rank = a->remap_rank;
+      p.remap_row = a->remap_row;
+      p.local_ctr = static_cast<uint32_t*>(a->local_ctr);
+      for (int i = 0; i < a->world; ++i) {
+        if (!a->peer_recv[i] || !a->peer_flags[i]) return FB_ERR_SHAPE;
+        p.peer_recv[i] = static_cast<float*>(a->peer_recv[i]);
+        p.peer_flags[i] = static_cast<uint32_t*>(a->peer_flags[i]);
+      }
+    }
     return launch_ntok<false, kEpiScatter>(ntok, mw, mx, p, max_tiles, grouped, stream);
+  }
   return launch_ntok<false, kEpiStore>(ntok, mw, mx, p, max_tiles, grouped, stream);
 }

@@ -98,13 +98,20 @@ def quantize_layer_(lw: "LayerWeights", fmt: str) -> "LayerWeights":
     if fmt == "bf16":
         return lw
     assert fmt in WEIGHT_FORMATS
+    def fits(name: str, t: torch.Tensor) -> bool:
+        # 1 x 128 activation blocks need in % 128 == 0; the SwiGLU pair splits at a 128-row boundary
+        out_dim, in_dim = t.shape[-2], t.shape[-1]
+        return in_dim % 128 == 0 and (name not in ("w13", "e_w13") or (out_dim // 2) % 128 == 0)
+
+    ffn_ok = all(fits(n, getattr(lw, n)) for n in ("w13", "w2") if isinstance(getattr(lw, n), torch.Tensor))
     for name in _DENSE_FIELDS:
         t = getattr(lw, name)
-        if isinstance(t, torch.Tensor):
+        if isinstance(t, torch.Tensor) and fits(name, t) and (ffn_ok or name not in ("w13", "w2")):
             setattr(lw, name, QuantWeight.from_bf16(t, "fp8_block"))
+    experts_ok = all(fits(n, getattr(lw, n)) for n in _EXPERT_FIELDS if isinstance(getattr(lw, n), torch.Tensor))
     for name in _EXPERT_FIELDS:
         t = getattr(lw, name)
-        if isinstance(t, torch.Tensor):
+        if isinstance(t, torch.Tensor) and experts_ok:
             setattr(lw, name, QuantWeight.from_bf16(t, "mxfp4" if fmt == "fp8_mxfp4" else "fp8_block"))
     return lw
 

@@ -50,6 +50,7 @@ class GemmArgs(C.Structure):
         ("peer_recv", C.c_void_p * 8), ("peer_flags", C.c_void_p * 8),
         ("local_ctr", C.c_void_p), ("residual", C.c_void_p), ("ldr", C.c_longlong),
         ("peer_wait_ns", C.c_ulonglong), ("status", C.c_void_p), ("trace", C.c_void_p),
+        ("remap_rank", C.c_void_p), ("remap_row", C.c_void_p),
     ]
 
 

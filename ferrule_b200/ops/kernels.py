@@ -72,7 +72,7 @@ def gemm(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None, *
          use_row_scale: bool = True, act_limit: float = 0.0, ntok: Optional[int] = None,
          x_group_koff: int = 0, out_group_coff: int = 0, k: Optional[int] = None,
          comm=None, residual: Optional[torch.Tensor] = None, split_k: int = 0,
-         trace: Optional[torch.Tensor] = None) -> torch.Tensor:
+         trace: Optional[torch.Tensor] = None, ep_combine=None) -> torch.Tensor:
     """out = x @ w^T on the tcgen05 path.
 
     x [rows, K] bf16 (row stride arbitrary multiple of 8), w [N, K] or [groups, N, K] bf16.
@@ -81,6 +81,9 @@ def gemm(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None, *
                   EPI_ALLREDUCE (comm = a parallel.symm.AllReduceChannel).
     x_group_koff: batched mode (groups > 1 without a plan): group g reads x[:, g*koff : g*koff+K]
                   and writes out[:, g*out_group_coff : +N].
+    ep_combine  : EPI_SCATTER only, (rank, world, peer buffers, peer flags, ctr, remap_rank, remap_row, pitch):
+                  output row r is stored as bf16 into rank remap_rank[r]'s buffer at row remap_row[r]
+                  (expert-parallel combine over peer memory); `out` is then unused.
     """
     lib = get_lib(True)
     assert x.dtype == torch.bfloat16 and x.dim() == 2 and x.stride(1) == 1
@@ -122,6 +125,15 @@ def gemm(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None, *
         comm.fill_gemm_args(a, rows, n_out, ntok)
         if residual is not None:
             a.residual, a.ldr = residual.data_ptr(), residual.stride(0)
+    if ep_combine is not None:
+        assert epilogue == EPI_SCATTER
+        rank, world, bufs, flags, ctr, remap_rank, remap_row, pitch = ep_combine
+        a.rank, a.world = rank, world
+        for r in range(world):
+            a.peer_recv[r], a.peer_flags[r] = bufs[r], flags[r]
+        a.local_ctr = ctr.data_ptr()
+        a.remap_rank, a.remap_row = remap_rank.data_ptr(), remap_row.data_ptr()
+        a.ldo = pitch
     a.status = status_tensor(x.device).data_ptr()
     check(lib.fb_gemm_bf16(C.byref(a), stream_ptr()), "fb_gemm_bf16")
     return out

@@ -128,6 +128,7 @@ class Engine:
                  detokenize: Optional[Callable[[List[int]], str]] = None,
                  registry=None, broker: Optional[PhysicalResourceBroker] = None):
         self.runner = runner
+        self.last_error: Optional[BaseException] = None
         self.cfg = cfg or EngineConfig()
         self.scheduler = ResidentScheduler(self.cfg.scheduler)
         self.kv = KvPageManager(self.cfg.kv_pages, self.cfg.page_size, self.cfg.scheduler.ctx_size + 8)
@@ -450,6 +451,7 @@ class Engine:
     def _abort(self, txn: Transaction, exc: BaseException) -> None:
         self.stats.aborted_transactions += 1
         txn.error = exc
+        self.last_error = exc            # for callers that want to report why requests ended in ERROR
         if txn.commit_id is not None:
             self.kv.abort_prepared_commit(txn.commit_id)
             txn.commit_id = None

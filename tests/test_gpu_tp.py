@@ -22,3 +22,18 @@ def test_selftest_two_ranks():
     assert res["ok"], res
     assert p.returncode == 0
     assert res["fused_calls"] > 0
+
+
+def test_expert_parallel_dispatch_combine_two_ranks():
+    """Token-sharded expert parallelism: fused peer-memory dispatch/combine and the NCCL all-to-all baseline
+    against a single-device oracle (ragged token counts, skewed routing, all-gather of the outputs)."""
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", PYTHONPATH=ROOT)
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
+           "--master-addr", "127.0.0.1", "--master-port", "29519", "-m", "ferrule_b200.parallel.ep_selftest"]
+    p = subprocess.run(cmd, capture_output=True, text=True, timeout=600, cwd=ROOT, env=env)
+    lines = [l for l in p.stdout.splitlines() if l.startswith("{")]
+    assert lines, p.stdout[-2000:] + p.stderr[-4000:]
+    res = json.loads(lines[-1])
+    assert res["ok"], res
+    assert p.returncode == 0
+    assert res["device_status"][0] == 0
