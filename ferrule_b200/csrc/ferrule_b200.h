@@ -203,9 +203,10 @@ int fb_hc_pre(const void* state, const float* fn, const float* scale, const floa
               int sinkhorn_iters, void* stream);
 int fb_hc_post(const void* hidden_in, const void* residual, const float* coeff, void* out, int tokens, int hc,
                int hidden, void* stream);
-// group g pools rows row0 + g * ratio + [0, window); rows outside [0, n_rows) are masked
+// group g pools rows row0 + g * ratio + [0, window); rows outside [0, n_rows) are masked; kv / gate rows have
+// pitch ld, ape is contiguous [ratio, cur_col + dim]; rows of the current group read columns [cur_col, cur_col + dim), rows of the previous one [0, dim)
 int fb_compressor_pool(const float* kv, const float* gate, long long ld, const float* ape, void* out, long long ldo,
-                       int groups, int dim, int ratio, int window, int row0, int n_rows, void* stream);
+                       int groups, int dim, int ratio, int window, int row0, int n_rows, int cur_col, void* stream);
 int fb_rope_rows(void* x, long long ld_row, long long ld_head, int rows, int heads, int off, int rdim,
                  const int* positions, const float* cos_t, const float* sin_t, int max_pos, int inverse,
                  void* status, void* stream);

@@ -625,5 +625,8 @@ extern "C" int fb_mla_attention(const FbAttnArgs* a, void* stream_) {
   if (a->kv_lora == 512 && a->rope_dim == 64) return launch_attn<512, 64>(p, stream);
   if (a->kv_lora == 64 && a->rope_dim == 16) return launch_attn<64, 16>(p, stream);
   if (a->kv_lora == 128 && a->rope_dim == 32) return launch_attn<128, 32>(p, stream);
+  // single shared K = V head (DeepSeek-V4): scores and values both span the whole row
+  if (a->kv_lora == 512 && a->rope_dim == 0) return launch_attn<512, 0>(p, stream);
+  if (a->kv_lora == 64 && a->rope_dim == 0) return launch_attn<64, 0>(p, stream);
   return FB_ERR_SHAPE;
 }

@@ -182,26 +182,32 @@ hc_post_kernel(const __nv_bfloat16* __restrict__ hidden_in, const __nv_bfloat16*
 }
 
 // ---------------------------------------------------------------------------------
-// Compressor pooling.  Group g pools window rows r = row0 + g * ratio + w (w < W); rows outside
-// [0, n_rows) count as score -inf / value 0.  kv, gate fp32 [n_rows, dim]; ape fp32 [W, dim];
-// out bf16 [groups, dim].  One thread per (group, dim); online softmax over the window.
+// Compressor pooling.  Group g pools window rows r = row0 + g * ratio + w (w < window); rows outside
+// [0, n_rows) count as score -inf / value 0.  kv, gate fp32 [n_rows, ld] projected rows; ape fp32
+// [ratio, cur_col + dim] contiguous; out bf16 [groups, dim].  With an overlapping window (window = 2 * ratio) the rows of the
+// previous group are read from columns [0, dim) and the rows of the current group from columns
+// [cur_col, cur_col + dim) of the projection (cur_col = dim), each with the position embedding of
+// its position inside its group.  One thread per (group, dim); online softmax over the window.
 // ---------------------------------------------------------------------------------
 __global__ void __launch_bounds__(256)
 compressor_pool_kernel(const float* __restrict__ kv, const float* __restrict__ gate, long long ld,
                        const float* __restrict__ ape, __nv_bfloat16* __restrict__ out, long long ldo,
-                       int groups, int dim, int ratio, int window, int row0, int n_rows) {
+                       int groups, int dim, int ratio, int window, int row0, int n_rows, int cur_col) {
   pdl_launch_dependents();
   pdl_wait();
   const int g = blockIdx.y;
   const int d = blockIdx.x * blockDim.x + threadIdx.x;
   if (g >= groups || d >= dim) return;
   const int first = row0 + g * ratio;
+  const int prev_rows = window - ratio;
   float m = -INFINITY, den = 0.f, num = 0.f;
   for (int w = 0; w < window; ++w) {
     const int r = first + w;
     if (r < 0 || r >= n_rows) continue;
-    const float s = gate[r * ld + d] + ape[static_cast<size_t>(w) * dim + d];
-    const float v = kv[r * ld + d];
+    const int col = (w < prev_rows ? 0 : cur_col) + d;
+    const int in_group = w < prev_rows ? w : w - prev_rows;
+    const float s = gate[r * ld + col] + ape[static_cast<size_t>(in_group) * (cur_col + dim) + col];
+    const float v = kv[r * ld + col];
     if (s > m) {
       const float c = __expf(m - s);   // exp(-inf) = 0 on the first valid row
       den *= c;
@@ -445,10 +451,12 @@ extern "C" int fb_hc_post(const void* hidden_in, const void* residual, const flo
 
 extern "C" int fb_compressor_pool(const float* kv, const float* gate, long long ld, const float* ape, void* out,
                                   long long ldo, int groups, int dim, int ratio, int window, int row0, int n_rows,
-                                  void* stream) {
-  if (groups <= 0 || dim <= 0 || ratio <= 0 || window < ratio || groups > 65535) return FB_ERR_SHAPE;
+                                  int cur_col, void* stream) {
+  if (groups <= 0 || dim <= 0 || ratio <= 0 || window < ratio || window > 2 * ratio || groups > 65535 ||
+      cur_col < 0 || cur_col + dim > ld)
+    return FB_ERR_SHAPE;
   launch_pdl(compressor_pool_kernel, dim3((dim + 255) / 256, groups), dim3(256), 0, static_cast<cudaStream_t>(stream),
-             kv, gate, ld, ape, static_cast<__nv_bfloat16*>(out), ldo, groups, dim, ratio, window, row0, n_rows);
+             kv, gate, ld, ape, static_cast<__nv_bfloat16*>(out), ldo, groups, dim, ratio, window, row0, n_rows, cur_col);
   return FB_CHECK_LAUNCH();
 }
 

@@ -82,21 +82,26 @@ def hc_head(state: torch.Tensor, fn: torch.Tensor, scale: torch.Tensor, base: to
     return (pre.unsqueeze(-1) * state.float()).sum(1)
 
 
-def compressor_pool(kv: torch.Tensor, gate: torch.Tensor, ape: torch.Tensor, ratio: int, overlap: bool) -> torch.Tensor:
-    """kv, gate [tokens, D] (projected rows of one sequence, position 0 first), ape [window, D] with
-    window = ratio * (2 if overlap else 1) -> pooled [tokens // ratio, D], rounded to bf16."""
-    tokens, D = kv.shape
+def compressor_pool(kv: torch.Tensor, gate: torch.Tensor, ape: torch.Tensor, ratio: int, overlap: bool,
+                    dim: Optional[int] = None) -> torch.Tensor:
+    """kv, gate [tokens, out_dim] projected rows of one sequence (position 0 first); ape [ratio, out_dim].
+    out_dim = dim without overlap, 2 * dim with it: rows of the previous group are read from columns [0, dim),
+    rows of the current group from [dim, 2 dim), each with the embedding of its position inside its group.
+    Returns pooled [tokens // ratio, dim], rounded to bf16."""
+    tokens, out_dim = kv.shape
+    dim = (out_dim // 2 if overlap else out_dim) if dim is None else dim
     groups = tokens // ratio
-    W = ratio * (2 if overlap else 1)
-    out = torch.zeros(groups, D, dtype=torch.float32, device=kv.device)
+    out = torch.zeros(groups, dim, dtype=torch.float32, device=kv.device)
+    kvf, gf, af = kv.float(), gate.float(), ape.float()
+    cur = dim if overlap else 0
     for g in range(groups):
-        end = (g + 1) * ratio
-        start = end - W
-        idx = torch.arange(start, end, device=kv.device)
-        ok = idx >= 0
-        rows = kv.float()[idx.clamp(min=0)] * ok[:, None]
-        score = gate.float()[idx.clamp(min=0)] + ape.float()
-        score = torch.where(ok[:, None], score, torch.full_like(score, float("-inf")))
+        lo = g * ratio
+        rows = [kvf[lo:lo + ratio, cur:cur + dim]]
+        score = [gf[lo:lo + ratio, cur:cur + dim] + af[:, cur:cur + dim]]
+        if overlap and g > 0:
+            rows.insert(0, kvf[lo - ratio:lo, :dim])
+            score.insert(0, gf[lo - ratio:lo, :dim] + af[:, :dim])
+        rows, score = torch.cat(rows), torch.cat(score)
         out[g] = (torch.softmax(score, dim=0) * rows).sum(0)
     return ref.bf16_round(out)
 

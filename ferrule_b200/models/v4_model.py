@@ -1,0 +1,530 @@
+"""DeepSeek-V4 family model: hyper-connected residual streams, hybrid sparse attention over a sliding
+window plus compressed KV (ratio-4 layers pick compressed rows with a learned indexer, ratio-128 layers
+see all of them), grouped low-rank output projection, hash / sqrt-softplus routed MoE.
+
+    layer:  hc_pre -> RMSNorm -> attention -> hc_post -> hc_pre -> RMSNorm -> MoE (+ shared) -> hc_post
+    attention (one shared K = V head of `head_dim`, RoPE on its tail):
+        q = per-head-RMS(wq_b . RMS(wq_a . x)), RoPE tail        kv = RoPE tail(RMS(wkv . x)) -> window
+        compressor: softmax-pool every `ratio` projected rows (overlapping for ratio 4) -> RMS -> RoPE
+        selection = last `window` rows U (indexer top-k | all) compressed rows, sink in the denominator
+        out = wo_b . grouped(wo_a)(inverse-RoPE tail(attn))
+
+`V4Reference` is the fp32 PyTorch oracle (token by token, explicit caches); `V4Cuda` runs decode steps for
+a batch of sequences on the sm_100a kernels (`ops/v4.py`, the tcgen05 GEMMs and the MoE kernels) with
+device-resident tables.  Weights bind to checkpoint names through `TENSOR_NAMES`.
+
+Counterpart of crates/ferrule-model/src/models/deepseek_v4/{config.rs:118-272, attention.rs:1194-1364,
+layer.rs:391-470, helpers.rs:395-505, checkpoint_binding.rs:31-700}; family constants from
+crates/ferrule-model/src/families/deepseek_v4.rs:9-38.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass, field, replace
+from typing import Dict, List, Optional, Tuple
+
+import torch
+
+from ..ops import reference as ref
+from . import v4
+from .config import SCORE_SQRT_SOFTPLUS
+
+
+@dataclass(frozen=True)
+class V4Config:
+    hidden: int = 4096
+    hc_mult: int = 4
+    hc_sinkhorn_iters: int = 20
+    hc_eps: float = 1e-6
+    norm_eps: float = 1e-6
+    n_layers: int = 43
+    n_hash_layers: int = 3
+    n_heads: int = 64
+    head_dim: int = 512
+    q_lora_rank: int = 1024
+    rope_dim: int = 64
+    o_groups: int = 8
+    o_lora_rank: int = 1024
+    window: int = 128
+    vocab_size: int = 129_280
+    n_routed_experts: int = 256
+    topk: int = 6
+    moe_inter: int = 2048
+    n_shared_experts: int = 1
+    swiglu_limit: float = 10.0
+    route_scale: float = 1.5
+    rope_theta: float = 10_000.0
+    compress_rope_theta: float = 160_000.0
+    rope_factor: float = 16.0
+    rope_orig_max_pos: int = 65_536
+    index_n_heads: int = 64
+    index_head_dim: int = 128
+    index_topk: int = 512
+    compress_ratios: Tuple[int, ...] = ()          # per layer: 0 (window only), 4 (indexer) or 128 (all rows)
+    indexer_ratio: int = 4                          # the ratio whose layers overlap windows and use the indexer
+    proposal_block_size: int = 5
+    max_position: int = 4096
+
+    def ratio(self, layer: int) -> int:
+        return self.compress_ratios[layer] if layer < len(self.compress_ratios) else 0
+
+    def has_indexer(self, layer: int) -> bool:
+        return self.ratio(layer) == self.indexer_ratio and self.indexer_ratio > 0
+
+    @property
+    def group_in(self) -> int:
+        return self.n_heads // self.o_groups * self.head_dim
+
+    @property
+    def hc(self) -> v4.HcConfig:
+        return v4.HcConfig(self.hc_mult, self.hidden, self.hc_eps, self.norm_eps, self.hc_sinkhorn_iters)
+
+    @property
+    def softmax_scale(self) -> float:
+        return self.head_dim ** -0.5
+
+    def with_(self, **kw) -> "V4Config":
+        return replace(self, **kw)
+
+
+def deepseek_v4_flash() -> V4Config:
+    """Family defaults; the per-layer compression schedule alternates ratio 4 and ratio 128 after a window-only
+    first layer (the checkpoint's config.json overrides it)."""
+    ratios = tuple(0 if i == 0 else (4 if i % 2 else 128) for i in range(43))
+    return V4Config(compress_ratios=ratios)
+
+
+def tiny_v4() -> V4Config:
+    """Small shape that exercises every branch: window-only, ratio-4 + indexer, direct ratio-8 layers, one
+    hash-routed layer."""
+    return V4Config(hidden=256, hc_mult=4, n_layers=3, n_hash_layers=1, n_heads=4, head_dim=64, q_lora_rank=128,
+                    rope_dim=16, o_groups=2, o_lora_rank=64, window=8, vocab_size=512, n_routed_experts=8, topk=2,
+                    moe_inter=128, index_n_heads=4, index_head_dim=32, index_topk=4, compress_ratios=(0, 4, 8),
+                    rope_factor=1.0, max_position=512)
+
+
+# checkpoint tensor names (HuggingFace DeepSeek-V4 layout) -> attribute of V4LayerWeights / V4Weights
+TENSOR_NAMES: Dict[str, str] = {
+    "embed.weight": "embed", "norm.weight": "final_norm", "head.weight": "lm_head",
+    "hc_head_fn": "hc_head_fn", "hc_head_scale": "hc_head_scale", "hc_head_base": "hc_head_base",
+    "layers.{i}.attn_norm.weight": "attn_norm", "layers.{i}.attn.wq_a.weight": "wq_a",
+    "layers.{i}.attn.q_norm.weight": "q_norm", "layers.{i}.attn.wq_b.weight": "wq_b",
+    "layers.{i}.attn.wkv.weight": "wkv", "layers.{i}.attn.kv_norm.weight": "kv_norm",
+    "layers.{i}.attn.attn_sink": "sink", "layers.{i}.attn.wo_a.weight": "wo_a", "layers.{i}.attn.wo_b.weight": "wo_b",
+    "layers.{i}.attn.compressor.wkv.weight": "c_wkv", "layers.{i}.attn.compressor.wgate.weight": "c_wgate",
+    "layers.{i}.attn.compressor.ape": "c_ape", "layers.{i}.attn.compressor.norm.weight": "c_norm",
+    "layers.{i}.attn.indexer.wq_b.weight": "i_wq_b", "layers.{i}.attn.indexer.weights_proj.weight": "i_weights",
+    "layers.{i}.attn.indexer.compressor.wkv.weight": "ic_wkv", "layers.{i}.attn.indexer.compressor.wgate.weight": "ic_wgate",
+    "layers.{i}.attn.indexer.compressor.ape": "ic_ape", "layers.{i}.attn.indexer.compressor.norm.weight": "ic_norm",
+    "layers.{i}.ffn_norm.weight": "ffn_norm", "layers.{i}.ffn.gate.weight": "router_w", "layers.{i}.ffn.gate.bias": "router_bias",
+    "layers.{i}.ffn.gate.tid2eid": "hash_table", "layers.{i}.hc_attn_fn": "hc_attn_fn", "layers.{i}.hc_attn_scale": "hc_attn_scale",
+    "layers.{i}.hc_attn_base": "hc_attn_base", "layers.{i}.hc_ffn_fn": "hc_ffn_fn", "layers.{i}.hc_ffn_scale": "hc_ffn_scale",
+    "layers.{i}.hc_ffn_base": "hc_ffn_base",
+}
+
+
+@dataclass
+class V4LayerWeights:
+    hc_attn_fn: torch.Tensor
+    hc_attn_scale: torch.Tensor
+    hc_attn_base: torch.Tensor
+    hc_ffn_fn: torch.Tensor
+    hc_ffn_scale: torch.Tensor
+    hc_ffn_base: torch.Tensor
+    attn_norm: torch.Tensor
+    wq_a: torch.Tensor
+    q_norm: torch.Tensor
+    wq_b: torch.Tensor
+    wkv: torch.Tensor
+    kv_norm: torch.Tensor
+    sink: torch.Tensor
+    wo_a: torch.Tensor            # [o_groups, o_lora, group_in]
+    wo_b: torch.Tensor
+    ffn_norm: torch.Tensor
+    router_w: torch.Tensor
+    e_w13: torch.Tensor
+    e_w2: torch.Tensor
+    w13: torch.Tensor
+    w2: torch.Tensor
+    router_bias: Optional[torch.Tensor] = None
+    hash_table: Optional[torch.Tensor] = None
+    c_wkv: Optional[torch.Tensor] = None
+    c_wgate: Optional[torch.Tensor] = None
+    c_ape: Optional[torch.Tensor] = None
+    c_norm: Optional[torch.Tensor] = None
+    i_wq_b: Optional[torch.Tensor] = None
+    i_weights: Optional[torch.Tensor] = None
+    ic_wkv: Optional[torch.Tensor] = None
+    ic_wgate: Optional[torch.Tensor] = None
+    ic_ape: Optional[torch.Tensor] = None
+    ic_norm: Optional[torch.Tensor] = None
+
+
+@dataclass
+class V4Weights:
+    cfg: V4Config
+    embed: torch.Tensor
+    layers: List[V4LayerWeights]
+    hc_head_fn: torch.Tensor
+    hc_head_scale: torch.Tensor
+    hc_head_base: torch.Tensor
+    final_norm: torch.Tensor
+    lm_head: torch.Tensor
+
+
+def random_v4_weights(cfg: V4Config, device="cpu", seed: int = 0, std: float = 0.05) -> V4Weights:
+    g = torch.Generator().manual_seed(seed)
+    bf = torch.bfloat16
+
+    def n(*shape, dtype=bf, s=std):
+        return (torch.randn(*shape, generator=g) * s).to(dtype).to(device)
+
+    def ones(*shape):
+        return torch.ones(*shape, dtype=bf, device=device)
+
+    H, hc, hd = cfg.hidden, cfg.hc_mult, cfg.head_dim
+    mix = 2 * hc + hc * hc
+    layers = []
+    for i in range(cfg.n_layers):
+        E, I = cfg.n_routed_experts, cfg.moe_inter
+        sI = cfg.n_shared_experts * I
+        lw = V4LayerWeights(
+            hc_attn_fn=n(mix, hc * H, dtype=torch.float32, s=0.02), hc_attn_scale=torch.tensor([0.7, 1.1, 0.9], device=device),
+            hc_attn_base=n(mix, dtype=torch.float32, s=0.3),
+            hc_ffn_fn=n(mix, hc * H, dtype=torch.float32, s=0.02), hc_ffn_scale=torch.tensor([0.9, 0.8, 1.2], device=device),
+            hc_ffn_base=n(mix, dtype=torch.float32, s=0.3),
+            attn_norm=ones(H), wq_a=n(cfg.q_lora_rank, H), q_norm=ones(cfg.q_lora_rank), wq_b=n(cfg.n_heads * hd, cfg.q_lora_rank),
+            wkv=n(hd, H), kv_norm=ones(hd), sink=n(cfg.n_heads, dtype=torch.float32, s=0.5),
+            wo_a=n(cfg.o_groups, cfg.o_lora_rank, cfg.group_in), wo_b=n(H, cfg.o_groups * cfg.o_lora_rank),
+            ffn_norm=ones(H), router_w=n(E, H),
+            e_w13=n(E, 2 * I, H), e_w2=n(E, H, I), w13=n(1, 2 * sI, H), w2=n(1, H, sI))
+        if i < cfg.n_hash_layers:
+            lw.hash_table = torch.randint(0, E, (cfg.vocab_size, cfg.topk), generator=g).to(device)
+        else:
+            lw.router_bias = n(E, dtype=torch.float32, s=0.1)
+        r = cfg.ratio(i)
+        if r:
+            od = hd * (2 if cfg.has_indexer(i) else 1)
+            lw.c_wkv, lw.c_wgate = n(od, H), n(od, H)
+            lw.c_ape, lw.c_norm = n(r, od, dtype=torch.float32, s=0.5), ones(hd)
+        if cfg.has_indexer(i):
+            idim = cfg.index_head_dim
+            lw.i_wq_b, lw.i_weights = n(cfg.index_n_heads * idim, cfg.q_lora_rank), n(cfg.index_n_heads, H)
+            lw.ic_wkv, lw.ic_wgate = n(2 * idim, H), n(2 * idim, H)
+            lw.ic_ape, lw.ic_norm = n(r, 2 * idim, dtype=torch.float32, s=0.5), ones(idim)
+        layers.append(lw)
+    return V4Weights(cfg, n(cfg.vocab_size, H, s=0.5), layers, n(hc, hc * H, dtype=torch.float32, s=0.02),
+                     torch.tensor([1.0], device=device), n(hc, dtype=torch.float32, s=0.3), ones(H), n(cfg.vocab_size, H))
+
+
+def _rope_tables(cfg: V4Config, theta: float, dim: int, device):
+    cos, sin = ref.rope_tables(cfg.max_position, dim, theta, cfg.rope_factor, cfg.rope_orig_max_pos)
+    return cos.to(device), sin.to(device)
+
+
+def _rope_tail(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, pos: int, rdim: int, inverse: bool = False):
+    """x [..., head_dim]: rotate the last `rdim` entries at position `pos`."""
+    out = x.clone()
+    out[..., -rdim:] = ref.apply_rope(x[..., -rdim:], cos[pos], sin[pos], inverse=inverse)
+    return out
+
+
+class _CompressorState:
+    """Projected rows of one sequence for one compressor (the oracle keeps all of them)."""
+
+    def __init__(self):
+        self.kv: List[torch.Tensor] = []
+        self.gate: List[torch.Tensor] = []
+
+
+class V4SeqCache:
+    """Per-sequence oracle state: per layer raw KV rows, compressed rows, indexer rows, compressor inputs."""
+
+    def __init__(self, cfg: V4Config):
+        L = cfg.n_layers
+        self.kv = [[] for _ in range(L)]
+        self.comp = [[] for _ in range(L)]
+        self.icomp = [[] for _ in range(L)]
+        self.cstate = [_CompressorState() for _ in range(L)]
+        self.istate = [_CompressorState() for _ in range(L)]
+        self.position = 0
+
+
+class V4Reference:
+    def __init__(self, w: V4Weights):
+        self.w, self.cfg = w, w.cfg
+        dev = w.embed.device
+        cfg = self.cfg
+        self.rope = _rope_tables(cfg, cfg.rope_theta, cfg.rope_dim, dev)
+        self.crope = _rope_tables(cfg, cfg.compress_rope_theta, cfg.rope_dim, dev)
+        self.irope = _rope_tables(cfg, cfg.compress_rope_theta, min(cfg.rope_dim, cfg.index_head_dim), dev)
+        self.rnd = ref.bf16_round
+
+    def _compress(self, st: _CompressorState, wkv, wgate, ape, norm, xn, pos: int, ratio: int, overlap: bool, dim: int,
+                  rope, rdim: int) -> Optional[torch.Tensor]:
+        st.kv.append(xn @ wkv.float().T)
+        st.gate.append(xn @ wgate.float().T)
+        if (pos + 1) % ratio:
+            return None
+        pooled = v4.compressor_pool(torch.stack(st.kv), torch.stack(st.gate), ape, ratio, overlap, dim)[-1]
+        row = self.rnd(ref.rmsnorm(pooled[None], norm, self.cfg.norm_eps))[0]
+        return self.rnd(_rope_tail(row, rope[0], rope[1], pos + 1 - ratio, rdim))
+
+    def _attention(self, lw: V4LayerWeights, layer: int, x: torch.Tensor, c: V4SeqCache, pos: int) -> torch.Tensor:
+        cfg, rnd = self.cfg, self.rnd
+        hd, rd, nh = cfg.head_dim, cfg.rope_dim, cfg.n_heads
+        q_lat = rnd(x @ lw.wq_a.float().T)
+        qn = rnd(ref.rmsnorm(q_lat[None], lw.q_norm, cfg.norm_eps))[0]
+        q = rnd(qn @ lw.wq_b.float().T).view(nh, hd)
+        q = rnd(ref.rmsnorm(q, None, cfg.norm_eps))
+        q = rnd(_rope_tail(q, self.rope[0], self.rope[1], pos, rd))
+        kv = rnd(x @ lw.wkv.float().T)
+        kv = rnd(ref.rmsnorm(kv[None], lw.kv_norm, cfg.norm_eps))[0]
+        kv = rnd(_rope_tail(kv, self.rope[0], self.rope[1], pos, rd))
+        c.kv[layer].append(kv)
+        ratio = cfg.ratio(layer)
+        sel_comp: List[int] = []
+        if ratio:
+            if cfg.has_indexer(layer):
+                idim = cfg.index_head_dim
+                new_i = self._compress(c.istate[layer], lw.ic_wkv, lw.ic_wgate, lw.ic_ape, lw.ic_norm, x, pos, ratio, True,
+                                       idim, self.irope, min(rd, idim))
+                if new_i is not None:
+                    c.icomp[layer].append(new_i)
+            new_c = self._compress(c.cstate[layer], lw.c_wkv, lw.c_wgate, lw.c_ape, lw.c_norm, x, pos, ratio,
+                                   cfg.has_indexer(layer), hd, self.crope, rd)
+            if new_c is not None:
+                c.comp[layer].append(new_c)
+            n_c = len(c.comp[layer])
+            if cfg.has_indexer(layer) and n_c:
+                idim, ih = cfg.index_head_dim, cfg.index_n_heads
+                iq = rnd(qn @ lw.i_wq_b.float().T).view(ih, idim)
+                iq = rnd(_rope_tail(iq, self.irope[0], self.irope[1], pos, min(rd, idim)))
+                wts = rnd(x @ lw.i_weights.float().T)
+                wts = rnd(wts * (idim ** -0.5 * ih ** -0.5))
+                idx, _ = v4.indexer_topk(iq, torch.stack(c.icomp[layer]), wts, cfg.index_topk, n_c)
+                sel_comp = [int(i) for i in idx.tolist() if i >= 0]
+            else:
+                sel_comp = list(range(n_c))
+        win = [p for p in range(pos - cfg.window + 1, pos + 1) if p >= 0]
+        rows = [c.kv[layer][p] for p in win] + [c.comp[layer][j] for j in sel_comp]
+        table = torch.stack(rows)
+        sel = torch.arange(len(rows), dtype=torch.int32, device=table.device)[None]
+        o = v4.sparse_sink_attention(q[None], table, sel, hd, cfg.softmax_scale, sink=lw.sink)[0]      # [heads, hd]
+        o = rnd(o)
+        o = rnd(_rope_tail(o, self.rope[0], self.rope[1], pos, rd, inverse=True))
+        og = o.reshape(cfg.o_groups, cfg.group_in)
+        lat = rnd(torch.einsum("gk,gnk->gn", og, lw.wo_a.float())).reshape(-1)
+        return rnd(lat @ lw.wo_b.float().T)
+
+    def _moe(self, lw: V4LayerWeights, x: torch.Tensor, token: int) -> torch.Tensor:
+        cfg, rnd = self.cfg, self.rnd
+        logits = (x @ lw.router_w.float().T)[None]
+        tok = torch.tensor([token], device=x.device)
+        idx, wts = ref.route(logits, cfg.topk, SCORE_SQRT_SOFTPLUS, bias=lw.router_bias, normalize=True,
+                             route_scale=cfg.route_scale, hash_table=lw.hash_table, token_ids=tok)
+        I = cfg.moe_inter
+        out = torch.zeros_like(x)
+        for s in range(cfg.topk):
+            e = int(idx[0, s])
+            y = x @ lw.e_w13[e].float().T
+            h = rnd(ref.swiglu(y[:I], y[I:], cfg.swiglu_limit))
+            out = out + rnd((h @ lw.e_w2[e].float().T) * wts[0, s])
+        y = x @ lw.w13[0].float().T
+        sI = y.shape[0] // 2
+        h = rnd(ref.swiglu(y[:sI], y[sI:], cfg.swiglu_limit))
+        return rnd(out + rnd(h @ lw.w2[0].float().T))
+
+    def step(self, c: V4SeqCache, token: int) -> torch.Tensor:
+        """Feed one token of one sequence; returns fp32 logits [vocab]."""
+        cfg, rnd, w = self.cfg, self.rnd, self.w
+        pos = c.position
+        state = w.embed[token].float()[None, None].repeat(1, cfg.hc_mult, 1)            # [1, hc, H]
+        for i, lw in enumerate(w.layers):
+            x, (_, post, comb) = v4.hc_pre(state, lw.hc_attn_fn, lw.hc_attn_scale, lw.hc_attn_base, cfg.hc)
+            x = rnd(x)
+            xn = rnd(ref.rmsnorm(x, lw.attn_norm, cfg.norm_eps))[0]
+            a = self._attention(lw, i, xn, c, pos)
+            state = rnd(v4.hc_post(a[None], state, post, comb))
+            x, (_, post, comb) = v4.hc_pre(state, lw.hc_ffn_fn, lw.hc_ffn_scale, lw.hc_ffn_base, cfg.hc)
+            x = rnd(x)
+            xn = rnd(ref.rmsnorm(x, lw.ffn_norm, cfg.norm_eps))[0]
+            f = self._moe(lw, xn, token)
+            state = rnd(v4.hc_post(f[None], state, post, comb))
+        h = rnd(v4.hc_head(state, w.hc_head_fn, w.hc_head_scale, w.hc_head_base, cfg.hc))
+        hn = rnd(ref.rmsnorm(h, w.final_norm, cfg.norm_eps))[0]
+        c.position += 1
+        return hn @ w.lm_head.float().T
+
+
+class V4Cuda:
+    """Decode steps for a batch of sequences on the sm_100a kernels.
+
+    Device-resident per layer: one combined KV table per sequence (`[max_len raw rows | max_len / ratio
+    compressed rows]`, bf16), the compressors' projected rows (fp32, pooled at every group boundary) and the
+    indexer's compressed plane.  Every step runs one token per active sequence; sequence slots are fixed.
+    """
+
+    def __init__(self, w: V4Weights, max_seqs: int, max_len: int):
+        from ..ops import kernels as K
+        from ..ops import v4 as K4
+        self.K, self.K4 = K, K4
+        self.w, self.cfg = w, w.cfg
+        cfg = self.cfg
+        dev = w.embed.device
+        self.device, self.max_seqs, self.max_len = dev, max_seqs, max_len
+        bf = dict(dtype=torch.bfloat16, device=dev)
+        f32 = dict(dtype=torch.float32, device=dev)
+        self.rope = _rope_tables(cfg, cfg.rope_theta, cfg.rope_dim, dev)
+        self.crope = _rope_tables(cfg, cfg.compress_rope_theta, cfg.rope_dim, dev)
+        self.irope = _rope_tables(cfg, cfg.compress_rope_theta, min(cfg.rope_dim, cfg.index_head_dim), dev)
+        hd = cfg.head_dim
+        self.tables, self.proj, self.iproj, self.iplane, self.stride = [], [], [], [], []
+        for i in range(cfg.n_layers):
+            r = cfg.ratio(i)
+            n_c = max_len // r if r else 0
+            self.stride.append(max_len + n_c)
+            self.tables.append(torch.zeros(max_seqs, max_len + n_c, hd, **bf))
+            od = hd * (2 if cfg.has_indexer(i) else 1)
+            self.proj.append((torch.zeros(max_seqs, max_len, od, **f32), torch.zeros(max_seqs, max_len, od, **f32)) if r else None)
+            if cfg.has_indexer(i):
+                idim = cfg.index_head_dim
+                self.iproj.append((torch.zeros(max_seqs, max_len, 2 * idim, **f32), torch.zeros(max_seqs, max_len, 2 * idim, **f32)))
+                self.iplane.append(torch.zeros(max_seqs, n_c, idim, **bf))
+            else:
+                self.iproj.append(None)
+                self.iplane.append(None)
+        E, k = cfg.n_routed_experts, cfg.topk
+        R = max_seqs
+        self.plan = K.MoePlan.allocate(R * k, E, 16, dev)
+        self.ones_hd = torch.ones(hd, **bf)
+        self.ones_id = torch.ones(cfg.index_head_dim, **bf)
+        self.positions = [0] * max_seqs
+        self.launch_note = "decode: one token per sequence per step"
+
+    # -- helpers ---------------------------------------------------------------------------
+    def _norm(self, x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+        out = torch.empty_like(x)
+        self.K.add_rmsnorm(x, weight, self.cfg.norm_eps, norm_out=out)
+        return out
+
+    def _compress(self, layer: int, proj, wkv, wgate, ape, norm_w, xn, seqs, pos, ratio, overlap, dim, rope, rdim):
+        """Append the projected rows of this step; return [(sequence, group, bf16 row)] for finished groups."""
+        K, K4, cfg = self.K, self.K4, self.cfg
+        pk = K.gemm(xn, wkv, out_dtype=torch.float32)
+        pg = K.gemm(xn, wgate, out_dtype=torch.float32)
+        sl = torch.tensor(seqs, device=self.device)
+        pl = torch.tensor(pos, device=self.device)
+        proj[0][sl, pl] = pk
+        proj[1][sl, pl] = pg
+        done = []
+        W = ratio * (2 if overlap else 1)
+        for s, p in zip(seqs, pos):
+            if (p + 1) % ratio:
+                continue
+            g = (p + 1) // ratio - 1
+            pooled = K4.compressor_pool(proj[0][s], proj[1][s], ape, ratio, overlap, groups=1,
+                                        row0=(g + 1) * ratio - W)
+            row = self._norm(pooled, norm_w)
+            cp = torch.tensor([p + 1 - ratio], dtype=torch.int32, device=self.device)
+            K4.rope_rows(row.view(1, 1, dim), cp, rope[0], rope[1], off=dim - rdim, rdim=rdim)
+            done.append((s, g, row[0]))
+        return done
+
+    def step(self, seqs: List[int], tokens: List[int]):
+        """One decode step for the sequences in slots `seqs` -> (next token ids [B] int32, fp32 logits [B, vocab])."""
+        K, K4, cfg, w = self.K, self.K4, self.cfg, self.w
+        dev = self.device
+        B = len(seqs)
+        hd, rd, nh, H, hc = cfg.head_dim, cfg.rope_dim, cfg.n_heads, cfg.hidden, cfg.hc_mult
+        pos = [self.positions[s] for s in seqs]
+        assert max(pos) < self.max_len
+        pos_t = torch.tensor(pos, dtype=torch.int32, device=dev)
+        seq_t = torch.tensor(seqs, dtype=torch.int64, device=dev)
+        tok_t = torch.tensor(tokens, dtype=torch.int32, device=dev)
+        emb = K.embedding(tok_t, w.embed)
+        state = emb[:, None, :].expand(B, hc, H).contiguous()
+        for i, lw in enumerate(w.layers):
+            x, coeff = K4.hc_pre(state, lw.hc_attn_fn, lw.hc_attn_scale, lw.hc_attn_base, cfg.hc)
+            xn = self._norm(x, lw.attn_norm)
+            # ---- attention ----
+            qn = self._norm(K.gemm(xn, lw.wq_a), lw.q_norm)
+            q = K.gemm(qn, lw.wq_b)
+            q = self._norm(q.view(B * nh, hd), self.ones_hd).view(B, nh, hd)
+            K4.rope_rows(q, pos_t, self.rope[0], self.rope[1], off=hd - rd, rdim=rd)
+            kv = self._norm(K.gemm(xn, lw.wkv), lw.kv_norm)
+            K4.rope_rows(kv.view(B, 1, hd), pos_t, self.rope[0], self.rope[1], off=hd - rd, rdim=rd)
+            table = self.tables[i]
+            table[seq_t, pos_t.long()] = kv
+            ratio = cfg.ratio(i)
+            stride = self.stride[i]
+            base = seq_t * stride
+            wpos = pos_t.long()[:, None] - torch.arange(cfg.window - 1, -1, -1, device=dev)[None]      # [B, window]
+            sel = [torch.where(wpos >= 0, base[:, None] + wpos, torch.full_like(wpos, -1))]
+            if ratio:
+                if cfg.has_indexer(i):
+                    idim = cfg.index_head_dim
+                    for s, g, row in self._compress(i, self.iproj[i], lw.ic_wkv, lw.ic_wgate, lw.ic_ape, lw.ic_norm, xn,
+                                                    seqs, pos, ratio, True, idim, self.irope, min(rd, idim)):
+                        self.iplane[i][s, g] = row
+                for s, g, row in self._compress(i, self.proj[i], lw.c_wkv, lw.c_wgate, lw.c_ape, lw.c_norm, xn, seqs,
+                                                pos, ratio, cfg.has_indexer(i), hd, self.crope, rd):
+                    table[s, self.max_len + g] = row
+                n_c = [(p + 1) // ratio for p in pos]
+                n_max = max(n_c)
+                if n_max:
+                    if cfg.has_indexer(i):
+                        idim, ih = cfg.index_head_dim, cfg.index_n_heads
+                        iq = K.gemm(qn, lw.i_wq_b).view(B, ih, idim)
+                        K4.rope_rows(iq, pos_t, self.irope[0], self.irope[1], off=idim - min(rd, idim), rdim=min(rd, idim))
+                        wts = K.gemm(xn, lw.i_weights, out_dtype=torch.float32)
+                        wts = (wts.bfloat16().float() * (idim ** -0.5 * ih ** -0.5)).bfloat16().float().contiguous()
+                        scores = torch.full((B, n_max), float("-inf"), dtype=torch.float32, device=dev)
+                        for b, s in enumerate(seqs):           # every sequence scores its own plane
+                            if n_c[b]:
+                                K4.indexer_scores(iq[b:b + 1], self.iplane[i][s, :n_c[b]], wts[b:b + 1],
+                                                  out=scores[b:b + 1, :n_c[b]])
+                        vis = torch.tensor(n_c, dtype=torch.int32, device=dev)
+                        idx = K4.indexer_topk(scores, min(cfg.index_topk, 512), vis).long()
+                    else:
+                        idx = torch.arange(n_max, device=dev)[None].expand(B, n_max)
+                        idx = torch.where(idx < torch.tensor(n_c, device=dev)[:, None], idx, torch.full_like(idx, -1))
+                    sel.append(torch.where(idx >= 0, base[:, None] + self.max_len + idx, torch.full_like(idx, -1)))
+            selection = torch.cat(sel, dim=1).int().contiguous()
+            o = K4.sparse_sink_attention(q, table.view(-1, hd), selection, hd, 0, cfg.softmax_scale, sink=lw.sink)
+            K4.rope_rows(o, pos_t, self.rope[0], self.rope[1], off=hd - rd, rdim=rd, inverse=True)
+            lat = K.gemm(o.view(B, nh * hd), lw.wo_a, x_group_koff=cfg.group_in, out_group_coff=cfg.o_lora_rank)
+            a = K.gemm(lat, lw.wo_b)
+            state = K4.hc_post(a, state, coeff)
+            # ---- MoE ----
+            x, coeff = K4.hc_pre(state, lw.hc_ffn_fn, lw.hc_ffn_scale, lw.hc_ffn_base, cfg.hc)
+            xn = self._norm(x, lw.ffn_norm)
+            f = self._moe(lw, xn, tok_t, B)
+            state = K4.hc_post(f, state, coeff)
+        h, _ = K4.hc_pre(state, w.hc_head_fn, w.hc_head_scale, w.hc_head_base, cfg.hc, head_only=True)
+        hn = self._norm(h, w.final_norm)
+        logits = K.gemm(hn, w.lm_head, out_dtype=torch.float32)
+        nxt = K.argmax(logits)
+        for s in seqs:
+            self.positions[s] += 1
+        return nxt, logits
+
+    def _moe(self, lw: V4LayerWeights, xn: torch.Tensor, tok_t: torch.Tensor, B: int) -> torch.Tensor:
+        K, cfg = self.K, self.cfg
+        k, H, E = cfg.topk, cfg.hidden, cfg.n_routed_experts
+        logits = K.gemm(xn, lw.router_w, out_dtype=torch.float32)
+        idx = torch.empty(B, k, dtype=torch.int32, device=self.device)
+        wts = torch.empty(B, k, dtype=torch.float32, device=self.device)
+        K.router_topk(logits, k, SCORE_SQRT_SOFTPLUS, bias=lw.router_bias, normalize=True, route_scale=cfg.route_scale,
+                      hash_table=lw.hash_table, token_ids=tok_t, out_idx=idx, out_w=wts)
+        slots = k + 1
+        plan = self.plan
+        K.moe_plan(idx, wts, plan, 0, E, dst_slots=slots)
+        xg = torch.empty(B * k, H, dtype=torch.bfloat16, device=self.device)
+        K.gather_rows(xn, plan, xg, cap_rows=B * k)
+        hmid = K.gemm(xg, lw.e_w13, epilogue=K.EPI_SWIGLU, plan=plan, act_limit=cfg.swiglu_limit)
+        route_out = torch.zeros(B, slots, H, dtype=torch.bfloat16, device=self.device)
+        K.gemm(hmid, lw.e_w2, out=route_out.view(B * slots, H), epilogue=K.EPI_SCATTER, plan=plan, scatter_rows=B * slots)
+        mid = K.gemm(xn, lw.w13, epilogue=K.EPI_SWIGLU, act_limit=cfg.swiglu_limit)
+        K.gemm(mid, lw.w2, out=route_out[:, k])
+        return K.moe_reduce(route_out.view(B * slots, H), slots, k, idx, 0, E, B, H)

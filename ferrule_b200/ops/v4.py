@@ -40,19 +40,23 @@ def hc_post(hidden: torch.Tensor, residual: torch.Tensor, coeff: torch.Tensor) -
 
 
 def compressor_pool(kv: torch.Tensor, gate: torch.Tensor, ape: torch.Tensor, ratio: int, overlap: bool,
-                    groups: Optional[int] = None, row0: Optional[int] = None) -> torch.Tensor:
-    """kv, gate fp32 [n_rows, D] -> bf16 [groups, D].  `row0` is the row where group 0's window starts
+                    groups: Optional[int] = None, row0: Optional[int] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """kv, gate fp32 [n_rows, out_dim] projected rows; ape fp32 [ratio, out_dim] -> bf16 [groups, dim] with
+    dim = out_dim (no overlap) or out_dim / 2.  `row0` is the row where group 0's window starts
     (default: ratio - window, i.e. the rows are a sequence from position 0)."""
     lib = get_lib(True)
-    n_rows, D = kv.shape
+    n_rows, out_dim = kv.shape
+    dim = out_dim // 2 if overlap else out_dim
     W = ratio * (2 if overlap else 1)
     assert kv.dtype == gate.dtype == ape.dtype == torch.float32 and kv.stride() == gate.stride() and kv.stride(1) == 1
-    assert ape.shape == (W, D) and ape.is_contiguous()
+    assert ape.shape == (ratio, out_dim) and ape.is_contiguous()
     groups = n_rows // ratio if groups is None else groups
     row0 = ratio - W if row0 is None else row0
-    out = torch.empty(groups, D, dtype=torch.bfloat16, device=kv.device)
+    if out is None:
+        out = torch.empty(groups, dim, dtype=torch.bfloat16, device=kv.device)
     check(lib.fb_compressor_pool(kv.data_ptr(), gate.data_ptr(), kv.stride(0), ape.data_ptr(), out.data_ptr(),
-                                 out.stride(0), groups, D, ratio, W, row0, n_rows, stream_ptr()), "fb_compressor_pool")
+                                 out.stride(0), groups, dim, ratio, W, row0, n_rows, dim if overlap else 0,
+                                 stream_ptr()), "fb_compressor_pool")
     return out
 
 

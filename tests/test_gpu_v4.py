@@ -39,11 +39,13 @@ def test_hc_pre_post_match_reference(hc, hidden, tokens):
 def test_compressor_pool_matches_reference(ratio, overlap):
     from ferrule_b200.ops import v4 as K
     torch.manual_seed(1)
-    tokens, D = ratio * 5, 576
-    kv, gate = torch.randn(tokens, D, device=DEV), torch.randn(tokens, D, device=DEV) * 2
-    ape = torch.randn(ratio * (2 if overlap else 1), D, device=DEV)
+    tokens, D = ratio * 5, 512
+    od = D * (2 if overlap else 1)
+    kv, gate = torch.randn(tokens, od, device=DEV), torch.randn(tokens, od, device=DEV) * 2
+    ape = torch.randn(ratio, od, device=DEV)
     got = K.compressor_pool(kv, gate, ape, ratio, overlap)
     want = v4.compressor_pool(kv, gate, ape, ratio, overlap)
+    assert got.shape == want.shape == (5, D)
     assert torch.allclose(got.float(), want, atol=1e-2, rtol=1e-2)
     exact = (got.float() == want).float().mean().item()
     assert exact > 0.98       # bf16 rounding of an fp32 sum: only last-ulp ties may differ
@@ -117,3 +119,39 @@ def test_selection_attention_matches_reference(splits):
     want = v4.sparse_sink_attention(q, table, sel, DL, 0.07, sink=sink)
     torch.cuda.synchronize()
     assert torch.allclose(got.float(), want, atol=2e-2, rtol=2e-2)
+
+
+def test_v4_model_decode_matches_reference():
+    """The assembled DeepSeek-V4 layer stack (hyper-connections, window + compressed + indexed attention, grouped
+    output projection, hash / sqrt-softplus MoE): CUDA decode steps of two ragged sequences against the oracle."""
+    from ferrule_b200.models import v4_model as M
+    from ferrule_b200.ops import _lib
+    cfg = M.tiny_v4()
+    w_cpu = M.random_v4_weights(cfg, device="cpu", seed=0)
+    w_gpu = M.random_v4_weights(cfg, device=DEV, seed=0)
+    ref_model = M.V4Reference(w_cpu)
+    caches = [M.V4SeqCache(cfg), M.V4SeqCache(cfg)]
+    cuda_model = M.V4Cuda(w_gpu, max_seqs=2, max_len=64)
+    g = torch.Generator().manual_seed(0)
+    toks = torch.randint(0, cfg.vocab_size, (2, 30), generator=g)
+    worst = 0.0
+    agree = total = 0
+    for t in range(30):
+        seqs = [0, 1] if t < 22 else [0]                      # the second sequence stops early
+        want = torch.stack([ref_model.step(caches[s], int(toks[s, t])) for s in seqs])
+        nxt, logits = cuda_model.step(seqs, [int(toks[s, t]) for s in seqs])
+        torch.cuda.synchronize()
+        err = float((logits.cpu() - want).abs().max())
+        scale = float(want.abs().max())
+        worst = max(worst, err / scale)
+        top2 = want.topk(2, dim=-1).values
+        clear = (top2[:, 0] - top2[:, 1]) > 3 * err
+        agree += int((nxt.cpu()[clear].long() == want.argmax(-1)[clear]).sum())
+        total += int(clear.sum())
+    _lib.raise_on_status()
+    assert worst <= 0.08, worst
+    assert agree == total and total > 20
+    # the compressed tables were filled: ratio-4 layer has 30 // 4 rows, ratio-8 layer 30 // 8
+    assert len(caches[0].comp[1]) == 7 and len(caches[0].comp[2]) == 3
+    got = cuda_model.tables[1][0, 64:64 + 7].float().cpu()
+    assert torch.allclose(got, torch.stack(caches[0].comp[1]), atol=0.08, rtol=0.05)

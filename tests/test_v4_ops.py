@@ -40,10 +40,14 @@ def test_compressor_window_and_overlap_masking():
     plain = v4.compressor_pool(kv, gate, torch.zeros(4, 4), ratio=4, overlap=False)
     want = (torch.softmax(gate[:4], 0) * kv[:4]).sum(0)
     assert torch.allclose(plain[0], ref.bf16_round(want))
-    over = v4.compressor_pool(kv, gate, torch.zeros(8, 4), ratio=4, overlap=True)
-    assert torch.allclose(over[0], plain[0])                    # nothing before the sequence start
-    want1 = (torch.softmax(gate, 0) * kv).sum(0)
-    assert torch.allclose(over[1], ref.bf16_round(want1))        # second group sees the first one too
+    # overlap: projection rows are [previous-window half | current-window half]
+    kv2, gate2 = torch.randn(8, 8), torch.randn(8, 8)
+    over = v4.compressor_pool(kv2, gate2, torch.zeros(4, 8), ratio=4, overlap=True)
+    want0 = (torch.softmax(gate2[:4, 4:], 0) * kv2[:4, 4:]).sum(0)          # nothing before the sequence start
+    assert torch.allclose(over[0], ref.bf16_round(want0))
+    sc = torch.cat([gate2[:4, :4], gate2[4:, 4:]])
+    vals = torch.cat([kv2[:4, :4], kv2[4:, 4:]])
+    assert torch.allclose(over[1], ref.bf16_round((torch.softmax(sc, 0) * vals).sum(0)))
 
 
 def test_indexer_topk_is_stable_and_marks_unused_slots():
