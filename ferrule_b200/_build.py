@@ -32,6 +32,7 @@ CUDA_SOURCES = [
     "quant.cu",
     "v4_ops.cu",
     "ep_moe.cu",
+    "expert_table.cu",
     "comm.cu",
     "no_alloc.cu",
 ]

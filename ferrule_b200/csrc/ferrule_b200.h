@@ -216,6 +216,14 @@ int fb_indexer_scores(const void* q, const void* plane, long long ldp, const flo
 int fb_indexer_topk(const float* scores, long long ld_s, const int* n_visible, int n_fixed, int k, int* out_idx,
                     long long ldo, int queries, void* stream);
 
+// ---- stable-slot expert table (streamed routed experts) -------------------------------------
+// updates: int4 records {slot, expert, generation, evicted expert or -1}, applied in order
+int fb_expert_table_apply(int* expert_to_slot, int* slot_expert, int* slot_gen, const void* updates, int n,
+                          int n_experts, int n_slots, void* status, void* stream);
+// tile_group: expert ids -> arena slots in place; miss[0] counts tiles of absent experts, miss[1..63] lists them
+int fb_expert_table_resolve(int* tile_group, int* tile_rows, const int* num_tiles, int max_tiles,
+                            const int* expert_to_slot, int n_experts, int* miss, void* stream);
+
 // ---- expert-parallel MoE over peer memory -------------------------------------------------
 // Every rank owns one symmetric buffer with the same layout (byte offsets below):
 //   recv_x    bf16 [world][cap][hidden]   rows dispatched to this rank, one segment per source

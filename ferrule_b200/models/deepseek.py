@@ -336,6 +336,7 @@ class CudaForward:
         self.launches = 0          # kernels launched by the last forward (for reporting)
         self.fused_router_rows = 256
         self.side_stream = torch.cuda.Stream(device=dev)      # shared experts run beside the routed path
+        self.arena = None          # models.expert_arena.ExpertArena when routed experts are streamed
 
     # -- sublayers -----------------------------------------------------------------------
     # -- linear dispatch -------------------------------------------------------------------
@@ -389,7 +390,7 @@ class CudaForward:
         est = T * cfg.topk / max(cfg.n_routed_experts, 1)
         return _pow2_at_least(2 * est, 16, 128)
 
-    def _moe_local(self, lw: LayerWeights, xn: torch.Tensor, b: DeviceBatch, T: int):
+    def _moe_local(self, lw: LayerWeights, xn: torch.Tensor, b: DeviceBatch, T: int, layer: int = -1):
         """Router + local routed experts + shared experts -> ws.route_out filled for this rank."""
         K, cfg, ws = self.K, self.cfg, self.ws
         k, H = cfg.topk, cfg.hidden
@@ -425,13 +426,46 @@ class CudaForward:
                           topk_groups=cfg.topk_groups, normalize=cfg.norm_topk_prob, route_scale=cfg.route_scale,
                           hash_table=lw.hash_table, token_ids=b.token_ids, out_idx=idx, out_w=wts)
             K.moe_plan(idx, wts, plan, self.w.e_lo, self.w.e_hi, dst_slots=ws.slots)
+        streamed = self.arena is not None and layer in self.arena.layers
         K.gather_rows(xn, plan, ws.xg, cap_rows=T * k)
+        if streamed:
+            return self._moe_streamed(lw, plan, layer, T, side, idx)
         self._gemm(ws.xg[:T * k], lw.e_w13, ws.hmid[:T * k], slot="xg", epilogue=K.EPI_SWIGLU, plan=plan,
                    act_limit=cfg.swiglu_limit)
         route_out = ws.route_out[:T]
         # route r = t*k + s is written to row t*slots + s (the plan kernel emits that row index)
         self._gemm(ws.hmid[:T * k], lw.e_w2, route_out.view(T * ws.slots, H), slot="hmid", epilogue=K.EPI_SCATTER,
                    plan=plan, scatter_rows=T * ws.slots)
+        if side is not None:
+            torch.cuda.current_stream().wait_stream(side)
+        return idx
+
+    def _moe_streamed(self, lw: LayerWeights, plan, layer: int, T: int, side, idx):
+        """Routed experts of a layer whose weights live in an arena smaller than the expert set.  The batch's
+        experts must be resident before the grouped GEMMs index the arena: read the per-expert row counts (one
+        small device->host copy), then run the GEMM pair in waves of at most `frames` experts; in every wave the
+        plan's tiles are translated from experts to slots, tiles of experts outside the wave get zero rows."""
+        K, cfg, ws, arena = self.K, self.cfg, self.ws, self.arena
+        k, H = cfg.topk, cfg.hidden
+        counts = plan.counts[:self.w.e_hi - self.w.e_lo].cpu()
+        need = counts.nonzero().flatten().tolist()
+        frames = arena.frames(layer)
+        tg0, tr0 = plan.tile_group.clone(), plan.tile_rows.clone()
+        route_out = ws.route_out[:T]
+        for w0 in range(0, max(len(need), 1), frames):
+            wave = need[w0:w0 + frames]
+            if not wave:
+                break
+            if w0:
+                plan.tile_group.copy_(tg0)
+                plan.tile_rows.copy_(tr0)
+            arena.ensure(layer, wave)
+            arena.resolve_plan(layer, plan)
+            K.gemm(ws.xg[:T * k], lw.e_w13, out=ws.hmid[:T * k], epilogue=K.EPI_SWIGLU, plan=plan,
+                   act_limit=cfg.swiglu_limit)
+            K.gemm(ws.hmid[:T * k], lw.e_w2, out=route_out.view(T * ws.slots, H), epilogue=K.EPI_SCATTER,
+                   plan=plan, scatter_rows=T * ws.slots)
+            arena.release(layer)
         if side is not None:
             torch.cuda.current_stream().wait_stream(side)
         return idx
@@ -457,7 +491,7 @@ class CudaForward:
             K.add_rmsnorm(h_out, lw.ffn_norm, cfg.rms_eps, norm_out=xn)
             h_mid = h_out
         if lw.is_moe:
-            idx = self._moe_local(lw, xn, b, T)
+            idx = self._moe_local(lw, xn, b, T, layer)
             # slot `topk` holds the shared-expert row (zeros when the model has none)
             if tp is None:
                 K.moe_reduce(ws.route_out[:T].view(T * ws.slots, cfg.hidden), ws.slots, cfg.topk, idx,

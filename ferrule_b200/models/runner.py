@@ -114,7 +114,8 @@ class _MtpTrack:
 class DeepSeekRunner(ModelRunner):
     def __init__(self, weights: ModelWeights, n_pages: int, page_size: int, max_rows: int = 2048,
                  max_seqs: int = 64, max_seq_len: int = 4096, device=None, tp=None, use_graphs: bool = True,
-                 emulate_bf16: bool = False, attn_splits: int = 8, enable_mtp: bool = True, max_draft: int = 1):
+                 emulate_bf16: bool = False, attn_splits: int = 8, enable_mtp: bool = True, max_draft: int = 1,
+                 expert_residency: Optional[float] = None):
         self.w, self.cfg = weights, weights.cfg
         self.device = torch.device(device if device is not None else weights.embed.device)
         self.is_cuda = self.device.type == "cuda"
@@ -124,6 +125,13 @@ class DeepSeekRunner(ModelRunner):
         self.pool = KvPool(self.cfg, n_pages, page_size, self.device,
                            dtype=torch.bfloat16 if self.is_cuda else weights.embed.dtype)
         self.tp = tp
+        # streamed routed experts: a fraction of every layer's experts is resident, the rest comes from pinned host
+        # memory on demand; the step then synchronises with the host per MoE layer, so it cannot be one graph
+        self.arena = None
+        if expert_residency is not None and self.is_cuda:
+            from .expert_arena import ExpertArena
+            self.arena = ExpertArena(weights, expert_residency)
+            use_graphs = False
         self.use_graphs = use_graphs and self.is_cuda
         self.stats = RunnerStats()
         self.staging = BatchStaging(max_rows, max_seqs, self.max_blocks, self.device)
@@ -132,6 +140,7 @@ class DeepSeekRunner(ModelRunner):
             logit_rows = max(max_seqs, 1) * (1 + (max_draft if weights.mtp and enable_mtp else 0))
             self.fwd = CudaForward(weights, self.pool, max_rows=max_rows, max_logit_rows=logit_rows,
                                    decode_rows=max_seqs, max_seq_len=max_seq_len, attn_splits=attn_splits, tp=tp)
+            self.fwd.arena = self.arena
             L = self.fwd.ws.max_logit_rows
             self.out_host = torch.zeros(2 * L, dtype=torch.int32).pin_memory()
         else:
@@ -390,4 +399,6 @@ class DeepSeekRunner(ModelRunner):
         d["graphs"] = sorted(self.graphs)
         d["weights_bytes"] = self.w.nbytes()
         d["kv_pool_bytes"] = self.pool.data.numel() * self.pool.data.element_size()
+        if self.arena is not None:
+            d["expert_arena"] = dict(vars(self.arena.stats))
         return d

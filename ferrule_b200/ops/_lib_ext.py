@@ -37,6 +37,9 @@ def declare(lib) -> None:
         "fb_quant_mxfp4_rows": ([vp, ll, vp, vp, i, i, vp], i),
         "fb_dequant_mxfp4": ([vp, vp, vp, i, i, vp], i),
         "fb_hadamard_rows": ([vp, ll, i, i, vp], i),
+        # expert_table.cu
+        "fb_expert_table_apply": ([vp, vp, vp, vp, i, i, i, vp, vp], i),
+        "fb_expert_table_resolve": ([vp, vp, vp, i, vp, i, vp, vp], i),
         # v4_ops.cu
         "fb_hc_pre": ([vp, vp, vp, vp, vp, i, vp, i, i, i, i, f, f, i, vp], i),
         "fb_hc_post": ([vp, vp, vp, vp, i, i, i, vp], i),

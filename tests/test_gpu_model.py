@@ -189,3 +189,38 @@ def test_quantised_forward_matches_dequantised_oracle(fmt, preset):
         new = [1, 1, 1]
     from ferrule_b200.ops import _lib
     _lib.raise_on_status()
+
+
+def test_streamed_experts_at_half_residency_equal_resident_run():
+    """Half of every layer's routed experts fit on the device; the rest stream from pinned host memory through
+    stable slots.  The greedy streams must equal those of the fully resident model (same kernels, same weights)."""
+    from ferrule_b200.models.runner import DeepSeekRunner
+    from ferrule_b200.ops import _lib
+    from ferrule_b200.runtime.engine import Engine, EngineConfig, TokenEvent
+    from ferrule_b200.runtime.scheduler import SchedulerConfig
+    from ferrule_b200.runtime.session import GenerateRequest
+    cfg = C.smoke_gpu()
+    g = torch.Generator().manual_seed(3)
+    prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (33, 70)]
+
+    def run(residency):
+        w = W.random_weights(cfg, device="cuda", seed=6, std=0.05)
+        runner = DeepSeekRunner(w, n_pages=32, page_size=64, max_rows=256, max_seqs=4, max_seq_len=512, device="cuda",
+                                expert_residency=residency, use_graphs=False)
+        sched = SchedulerConfig(max_active_sequences=4, max_decode_batch=4, max_batch_tokens=256,
+                                prefill_chunk_size=64, ctx_size=512)
+        eng = Engine(runner, EngineConfig(scheduler=sched, kv_pages=32, page_size=64))
+        for i, p in enumerate(prompts):
+            eng.submit(GenerateRequest(f"r{i}", p, max_new_tokens=8, ignore_eos=True))
+        ev = []
+        eng.run_until_idle(ev.append, max_steps=2000)
+        assert eng.last_error is None, eng.last_error
+        return {f"r{i}": [e.token for e in ev if isinstance(e, TokenEvent) and e.request_id == f"r{i}"]
+                for i in range(len(prompts))}, runner
+
+    want, _ = run(None)
+    got, runner = run(0.5)
+    _lib.raise_on_status()
+    assert got == want
+    st = runner.arena.stats
+    assert runner.arena.frames(1) == 8 and st.uploads > 8 and st.evictions > 0 and st.hits > 0
