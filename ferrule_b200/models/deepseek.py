@@ -182,12 +182,17 @@ class ReferenceForward:
             f = rnd(f)
         return rnd(h + f)
 
-    def hidden_states(self, b: DeviceBatch, allreduce=None) -> torch.Tensor:
-        T = b.n_rows
-        h = self.w.embed[b.token_ids[:T].long()].float()
+    def embed_rows(self, b: DeviceBatch) -> torch.Tensor:
+        return self.w.embed[b.token_ids[:b.n_rows].long()].float()
+
+    def run_layers(self, h: torch.Tensor, b: DeviceBatch, allreduce=None) -> torch.Tensor:
+        """The layers this weight image holds (all of them, or one pipeline stage's share)."""
         for i, lw in enumerate(self.w.layers):
             h = self.layer(lw, i, h, b, allreduce)
         return h
+
+    def hidden_states(self, b: DeviceBatch, allreduce=None) -> torch.Tensor:
+        return self.run_layers(self.embed_rows(b), b, allreduce)
 
     def logits_from_hidden(self, h: torch.Tensor, b: DeviceBatch, final_norm=None) -> torch.Tensor:
         rows = b.logit_rows[:b.n_logit].long()
@@ -515,13 +520,24 @@ class CudaForward:
         return h_in
 
     # -- whole model ---------------------------------------------------------------------
-    def hidden_states(self, b: DeviceBatch, T: int) -> torch.Tensor:
-        K, ws = self.K, self.ws
+    def embed_rows(self, b: DeviceBatch, T: int) -> torch.Tensor:
+        h = self.ws.h[0][:T]
+        self.K.embedding(b.token_ids[:T], self.w.embed, out=h)
+        return h
+
+    def run_layers(self, h: torch.Tensor, b: DeviceBatch, T: int) -> torch.Tensor:
+        """The layers this weight image holds (all of them, or one pipeline stage's share).  `h` is
+        `ws.h[0][:T]` or is copied there."""
+        ws = self.ws
+        if h.data_ptr() != ws.h[0].data_ptr():
+            ws.h[0][:T].copy_(h)
         h, other = ws.h[0][:T], ws.h[1][:T]
-        K.embedding(b.token_ids[:T], self.w.embed, out=h)
         for i, lw in enumerate(self.w.layers):
             h = self.layer(lw, i, h, other, b, T)
         return h
+
+    def hidden_states(self, b: DeviceBatch, T: int) -> torch.Tensor:
+        return self.run_layers(self.embed_rows(b, T), b, T)
 
     def head(self, h: torch.Tensor, b: DeviceBatch, final_norm: torch.Tensor, want_logits: bool = False):
         """Final norm + LM head + greedy token on the requested rows -> (next_id, next_val[, logits])."""

@@ -1,0 +1,130 @@
+"""Multi-process host-side parallel paths on the gloo backend (no GPU): pipeline stages over send/recv,
+tensor-parallel reference collectives, rank-failure detection through a short process-group timeout."""
+import os
+import subprocess
+import sys
+import textwrap
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _run(script: str, world: int, port: int, timeout: int = 180):
+    path = os.path.join(ROOT, "tests", f"_tmp_pp_{port}.py")
+    with open(path, "w") as f:
+        f.write(textwrap.dedent(script))
+    try:
+        env = dict(os.environ, PYTHONPATH=ROOT, FERRULE_NO_CUDA="1")
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", str(world),
+               "--master-addr", "127.0.0.1", "--master-port", str(port), path]
+        return subprocess.run(cmd, capture_output=True, text=True, timeout=timeout, cwd=ROOT, env=env)
+    finally:
+        os.remove(path)
+
+
+def test_pipeline_two_stages_equal_single_process():
+    p = _run('''
+        import os, torch, torch.distributed as dist
+        from ferrule_b200.models import config as C, weights as W, deepseek as D
+        from ferrule_b200.parallel.pp import PipelineParallel, stage_weights
+        dist.init_process_group("gloo")
+        rank, world = dist.get_rank(), dist.get_world_size()
+        cfg = C.tiny_fixture()
+        w = W.random_weights(cfg, device="cpu", seed=0)
+        page = 16
+        def batch(lens, new, seed):
+            g = torch.Generator().manual_seed(seed)
+            ids, pos, slot, rseq, lrows = [], [], [], [], []
+            bt = torch.zeros(len(lens), 8, dtype=torch.int32)
+            pc = 1
+            for s, (n0, nn) in enumerate(zip(lens, new)):
+                for j in range((n0 + nn + page - 1) // page):
+                    bt[s, j] = pc; pc += 1
+                for j in range(nn):
+                    p_ = n0 + j
+                    ids.append(int(torch.randint(0, cfg.vocab_size, (1,), generator=g))); pos.append(p_)
+                    slot.append(int(bt[s, p_ // page]) * page + p_ % page); rseq.append(s)
+                lrows.append(len(ids) - 1)
+            t = lambda v, dt: torch.tensor(v, dtype=dt)
+            return D.DeviceBatch(t(ids, torch.int32), t(pos, torch.int32), t(slot, torch.int64), t(rseq, torch.int32),
+                                 t(pos, torch.int32), bt, t(lrows, torch.int32), len(ids), len(lrows))
+        full = D.ReferenceForward(w, D.KvPool(cfg, 32, page, "cpu", dtype=torch.float32))
+        ws = stage_weights(w, rank, world)
+        stage = D.ReferenceForward(ws, D.KvPool(ws.cfg, 32, page, "cpu", dtype=torch.float32))
+        pp = PipelineParallel(rank, world)
+        ok = True
+        lens, new = [0, 0], [19, 7]
+        for step in range(3):
+            b = batch(lens, new, step)
+            want = full.forward(b)
+            ids, vals = pp.step(stage, b, cfg.hidden, torch.float32, cuda=False)
+            ok &= bool(torch.equal(ids.long(), want.argmax(-1))) and bool(torch.allclose(vals, want.max(-1).values, atol=1e-4))
+            lens = [l + n for l, n in zip(lens, new)]; new = [1, 1]
+        # micro-batched decode: two row ranges in flight
+        pp2 = PipelineParallel(rank, world, microbatches=2)
+        b = batch(lens, [1, 1], 9)
+        want = full.forward(b)
+        ids, vals = pp2.step(stage, b, cfg.hidden, torch.float32, cuda=False)
+        ok &= bool(torch.equal(ids.long(), want.argmax(-1)))
+        print("PP_OK" if ok else "PP_BAD", rank, flush=True)
+        dist.destroy_process_group()
+    ''', 2, 29611)
+    assert p.stdout.count("PP_OK") == 2, p.stdout[-2000:] + p.stderr[-3000:]
+
+
+def test_rank_that_never_joins_is_detected_by_timeout():
+    """Failure made on the host: rank 1 exits between steps; rank 0's next collective ends with an error after the
+    short process-group timeout instead of hanging."""
+    p = _run('''
+        import datetime, os, sys, torch, torch.distributed as dist
+        dist.init_process_group("gloo", timeout=datetime.timedelta(seconds=5))
+        rank = dist.get_rank()
+        t = torch.ones(4)
+        dist.all_reduce(t)                       # step 0: everyone is here
+        if rank == 1:
+            print("RANK1_LEAVES", flush=True)
+            os._exit(0)                          # leaves between steps, nothing in flight
+        try:
+            dist.all_reduce(t)                   # step 1: the peer is gone
+            print("NO_ERROR", flush=True)
+        except Exception as exc:
+            print("DETECTED", type(exc).__name__, flush=True)
+        os._exit(0)
+    ''', 2, 29612, timeout=120)
+    assert "DETECTED" in p.stdout and "NO_ERROR" not in p.stdout, p.stdout[-2000:] + p.stderr[-2000:]
+
+
+def test_tensor_parallel_reference_on_gloo_equals_single_process():
+    """Heads, FFN inner dims, experts and the vocabulary sharded over two CPU ranks: the engine's greedy stream
+    equals the single-process one (reference forward + gloo all-reduce / all-gather)."""
+    p = _run('''
+        import torch, torch.distributed as dist
+        from ferrule_b200.models import config as C, weights as W
+        from ferrule_b200.models.runner import DeepSeekRunner
+        from ferrule_b200.parallel.tp import TensorParallel
+        from ferrule_b200.runtime.engine import Engine, EngineConfig, TokenEvent
+        from ferrule_b200.runtime.scheduler import SchedulerConfig
+        from ferrule_b200.runtime.session import GenerateRequest
+        dist.init_process_group("gloo")
+        rank, world = dist.get_rank(), dist.get_world_size()
+        cfg = C.tiny_fixture()
+        def run(w, tp):
+            runner = DeepSeekRunner(w, n_pages=32, page_size=16, max_rows=128, max_seqs=4, max_seq_len=256, device="cpu",
+                                    tp=tp, enable_mtp=False)
+            sched = SchedulerConfig(max_active_sequences=4, max_decode_batch=4, max_batch_tokens=64, prefill_chunk_size=32,
+                                    ctx_size=256)
+            eng = Engine(runner, EngineConfig(scheduler=sched, kv_pages=32, page_size=16))
+            g = torch.Generator().manual_seed(5)
+            for i, n in enumerate((21, 40)):
+                eng.submit(GenerateRequest(f"r{i}", torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist(),
+                                           max_new_tokens=6, ignore_eos=True))
+            ev = []
+            eng.run_until_idle(ev.append, max_steps=2000)
+            assert eng.last_error is None, eng.last_error
+            return [(e.request_id, e.token) for e in ev if isinstance(e, TokenEvent)]
+        want = run(W.random_weights(cfg, device="cpu", seed=0, dtype=torch.float32), None)
+        got = run(W.random_weights(cfg, device="cpu", seed=0, dtype=torch.float32, tp_rank=rank, tp_world=world),
+                  TensorParallel(rank, world, "cpu", fused=False))
+        print("TP_OK" if got == want and len(want) == 12 else "TP_BAD", rank, flush=True)
+        dist.destroy_process_group()
+    ''', 2, 29613)
+    assert p.stdout.count("TP_OK") == 2, p.stdout[-2000:] + p.stderr[-3000:]
