@@ -375,3 +375,33 @@ def test_router_plan_fused(K, T, E, k, H, score, groups, tg):
     assert torch.equal(plan.dst_row[:n].cpu(), plan2.dst_row[:n].cpu())
     assert torch.equal(plan.src_token[:n].cpu(), plan2.src_token[:n].cpu())
     assert torch.equal(plan.counts.cpu(), plan2.counts.cpu())
+
+
+def test_bounded_wait_reports_timeout_and_context_stays_usable():
+    """Failure detection on the device: a wait on a flag that nothing sets gives up after its limit, records a
+    status word (no trap, no hang) and later kernels still run."""
+    import ctypes as C
+    from ferrule_b200.ops import _lib
+    lib = _lib.get_lib(True)
+    flag = torch.zeros(4, dtype=torch.int32, device="cuda")
+    result = torch.full((1,), -1, dtype=torch.int32, device="cuda")
+    _lib.read_status()                                        # start clean
+    st = _lib.status_tensor("cuda")
+    t0 = torch.cuda.Event(enable_timing=True)
+    t1 = torch.cuda.Event(enable_timing=True)
+    t0.record()
+    rc = lib.fb_flag_wait_probe(flag.data_ptr(), 1, 50_000_000, st.data_ptr(), result.data_ptr(), _lib.stream_ptr())
+    t1.record()
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert 30.0 <= t0.elapsed_time(t1) <= 1000.0              # waited about the 50 ms limit, then returned
+    assert int(result[0]) == 0                                # the wait reported failure to its caller
+    code, where, seen, target = _lib.read_status()
+    assert code == 2 and target == 1 and seen == 0           # "peer flag timeout"
+    assert _lib.read_status()[0] == 0                         # reading cleared it
+    x = torch.arange(8, device="cuda").float()
+    assert float((x * 2).sum()) == 56.0                       # the context is alive
+    flag[0] = 1                                               # now the same wait succeeds at once
+    lib.fb_flag_wait_probe(flag.data_ptr(), 1, 50_000_000, st.data_ptr(), result.data_ptr(), _lib.stream_ptr())
+    torch.cuda.synchronize()
+    assert int(result[0]) == 1 and _lib.read_status()[0] == 0
