@@ -212,6 +212,13 @@ int fb_rope_rows(void* x, long long ld_row, long long ld_head, int rows, int hea
                  void* status, void* stream);
 int fb_indexer_scores(const void* q, const void* plane, long long ldp, const float* head_w, float* scores,
                       long long ld_s, int queries, int heads, int d, int n, void* stream);
+// one draft step of the Markov proposal head: id = argmax_t(logits[t] + W2[t] . W1[*prev_token]), ties -> lower id
+int fb_markov_step(const float* logits, const void* w1, const void* w2, int vocab, int rank, int chunks,
+                   const int* prev_token, float* part_val, int* part_id, void* ctr, int* out_id, float* out_val,
+                   void* status, void* stream);
+// taps[t][tap_off : +hidden] = bf16(mean over the hc copies of state[t])
+int fb_hc_mean_scatter(const void* state, void* taps, long long ld_taps, int tap_off, int tokens, int hc, int hidden,
+                       void* stream);
 // n_visible (per query) may be NULL, then n_fixed applies; k <= 512
 int fb_indexer_topk(const float* scores, long long ld_s, const int* n_visible, int n_fixed, int k, int* out_idx,
                     long long ldo, int queries, void* stream);

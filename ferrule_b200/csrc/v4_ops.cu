@@ -415,6 +415,104 @@ indexer_topk_kernel(const float* __restrict__ scores, long long ld_s, const int*
     out[i] = static_cast<int>(0xffffffffu - static_cast<uint32_t>(win[i] & 0xffffffffull));
 }
 
+// ---------------------------------------------------------------------------------
+// Markov proposal head, one draft step: id = argmax_t (logits[t] + W2[t] . W1[prev]) with ties to the
+// lower id; prev is read from device memory (the anchor or the previous step's draft), so a block of
+// draft steps needs no host round trip.  Grid = vocabulary chunks; the CTA that finishes last reduces
+// the chunk candidates and writes (id, biased logit).
+// ---------------------------------------------------------------------------------
+__device__ __forceinline__ bool better_cand(float v, int i, float bv, int bi) { return v > bv || (v == bv && i < bi); }
+
+__global__ void __launch_bounds__(256)
+markov_step_kernel(const float* __restrict__ logits, const __nv_bfloat16* __restrict__ w1,
+                   const __nv_bfloat16* __restrict__ w2, int vocab, int rank, int chunk,
+                   const int* __restrict__ prev_token, float* __restrict__ part_val, int* __restrict__ part_id,
+                   unsigned int* __restrict__ ctr, int* __restrict__ out_id, float* __restrict__ out_val,
+                   DeviceStatus* st) {
+  pdl_launch_dependents();
+  pdl_wait();
+  extern __shared__ float w1_prev[];       // [rank]
+  __shared__ float sv[8];
+  __shared__ int si[8];
+  __shared__ int is_last;
+  int prev = *prev_token;
+  if (prev < 0 || prev >= vocab) {
+    if (threadIdx.x == 0 && blockIdx.x == 0) report_status(st, kStatusBadIndex, 0xB00, prev, vocab);
+    prev = 0;
+  }
+  for (int i = threadIdx.x; i < rank; i += blockDim.x) w1_prev[i] = __bfloat162float(w1[static_cast<size_t>(prev) * rank + i]);
+  __syncthreads();
+  const int c = blockIdx.x, chunks = gridDim.x;
+  const int lo = c * chunk, hi = min(vocab, lo + chunk);
+  float best = -INFINITY;
+  int bi = 0x7fffffff;
+  for (int t = lo + threadIdx.x; t < hi; t += blockDim.x) {
+    const uint4* row = reinterpret_cast<const uint4*>(w2 + static_cast<size_t>(t) * rank);
+    float bias = 0.f;
+    for (int i = 0; i < rank / 8; ++i) {
+      const uint4 v = row[i];
+      const __nv_bfloat16* b = reinterpret_cast<const __nv_bfloat16*>(&v);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) bias = fmaf(__bfloat162float(b[j]), w1_prev[i * 8 + j], bias);
+    }
+    const float v = logits[t] + bias;
+    if (v == v && better_cand(v, t, best, bi)) { best = v; bi = t; }
+  }
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    if (better_cand(ov, oi, best, bi)) { best = ov; bi = oi; }
+  }
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+  if (l == 0) { sv[w] = best; si[w] = bi; }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int k = 1; k < 8; ++k)
+      if (better_cand(sv[k], si[k], best, bi)) { best = sv[k]; bi = si[k]; }
+    part_val[c] = best;
+    part_id[c] = bi;
+    __threadfence();
+    const unsigned int done = atomicAdd(ctr, 1u);
+    is_last = done == static_cast<unsigned int>(chunks - 1);
+    if (is_last) *ctr = 0;
+  }
+  __syncthreads();
+  if (!is_last || w != 0) return;
+  __threadfence();
+  best = -INFINITY;
+  bi = 0x7fffffff;
+  for (int k = l; k < chunks; k += 32) {
+    const float v = part_val[k];
+    const int id = part_id[k];
+    if (better_cand(v, id, best, bi)) { best = v; bi = id; }
+  }
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    if (better_cand(ov, oi, best, bi)) { best = ov; bi = oi; }
+  }
+  if (l == 0) {
+    *out_id = bi == 0x7fffffff ? -1 : bi;
+    *out_val = best;
+  }
+}
+
+// Mean over the hc copies of the residual stream, scattered into a proposal tap:
+// taps[t][tap_off : tap_off + hidden] = bf16(sum_j state[t][j][:] / hc)
+__global__ void __launch_bounds__(256)
+hc_mean_scatter_kernel(const __nv_bfloat16* __restrict__ state, __nv_bfloat16* __restrict__ taps, long long ld_taps,
+                       int tap_off, int tokens, int hc, int hidden) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x;
+  if (t >= tokens) return;
+  for (int d = threadIdx.x; d < hidden; d += blockDim.x) {
+    float s = 0.f;
+    for (int j = 0; j < hc; ++j) s += __bfloat162float(state[(static_cast<size_t>(t) * hc + j) * hidden + d]);
+    taps[t * ld_taps + tap_off + d] = __float2bfloat16(s / static_cast<float>(hc));
+  }
+}
+
 }  // namespace fb
 
 using namespace fb;
@@ -497,5 +595,28 @@ extern "C" int fb_indexer_topk(const float* scores, long long ld_s, const int* n
   if (queries <= 0 || k <= 0 || k > kTopkMax) return FB_ERR_SHAPE;
   launch_pdl(indexer_topk_kernel, dim3(queries), dim3(1024), 0, static_cast<cudaStream_t>(stream), scores, ld_s,
              n_visible, n_fixed, k, out_idx, ldo);
+  return FB_CHECK_LAUNCH();
+}
+
+// scratch: part_val [chunks] floats, part_id [chunks] ints, ctr one zeroed uint32; chunks <= 1024
+extern "C" int fb_markov_step(const float* logits, const void* w1, const void* w2, int vocab, int rank, int chunks,
+                              const int* prev_token, float* part_val, int* part_id, void* ctr, int* out_id,
+                              float* out_val, void* status, void* stream) {
+  if (vocab <= 0 || rank <= 0 || rank % 8 != 0 || rank > 4096 || chunks <= 0 || chunks > 1024 || !prev_token || !ctr)
+    return FB_ERR_SHAPE;
+  const int chunk = (vocab + chunks - 1) / chunks;
+  launch_pdl(markov_step_kernel, dim3(chunks), dim3(256), rank * sizeof(float), static_cast<cudaStream_t>(stream),
+             logits, static_cast<const __nv_bfloat16*>(w1), static_cast<const __nv_bfloat16*>(w2), vocab, rank, chunk,
+             prev_token, part_val, part_id, static_cast<unsigned int*>(ctr), out_id, out_val,
+             static_cast<DeviceStatus*>(status));
+  return FB_CHECK_LAUNCH();
+}
+
+extern "C" int fb_hc_mean_scatter(const void* state, void* taps, long long ld_taps, int tap_off, int tokens, int hc,
+                                  int hidden, void* stream) {
+  if (tokens <= 0 || hc <= 0 || hidden <= 0 || tap_off < 0) return FB_ERR_SHAPE;
+  launch_pdl(hc_mean_scatter_kernel, dim3(tokens), dim3(256), 0, static_cast<cudaStream_t>(stream),
+             static_cast<const __nv_bfloat16*>(state), static_cast<__nv_bfloat16*>(taps), ld_taps, tap_off, tokens, hc,
+             hidden);
   return FB_CHECK_LAUNCH();
 }

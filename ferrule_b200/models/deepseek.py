@@ -342,6 +342,7 @@ class CudaForward:
         self.fused_router_rows = 256
         self.side_stream = torch.cuda.Stream(device=dev)      # shared experts run beside the routed path
         self.arena = None          # models.expert_arena.ExpertArena when routed experts are streamed
+        self.telemetry = None      # utils.telemetry.ExpertTelemetry fed by the streamed path
 
     # -- sublayers -----------------------------------------------------------------------
     # -- linear dispatch -------------------------------------------------------------------
@@ -454,6 +455,8 @@ class CudaForward:
         k, H = cfg.topk, cfg.hidden
         counts = plan.counts[:self.w.e_hi - self.w.e_lo].cpu()
         need = counts.nonzero().flatten().tolist()
+        if self.telemetry is not None:
+            self.telemetry.record_counts(layer, counts.tolist(), T)
         frames = arena.frames(layer)
         tg0, tr0 = plan.tile_group.clone(), plan.tile_rows.clone()
         route_out = ws.route_out[:T]

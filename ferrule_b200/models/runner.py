@@ -141,6 +141,10 @@ class DeepSeekRunner(ModelRunner):
             self.fwd = CudaForward(weights, self.pool, max_rows=max_rows, max_logit_rows=logit_rows,
                                    decode_rows=max_seqs, max_seq_len=max_seq_len, attn_splits=attn_splits, tp=tp)
             self.fwd.arena = self.arena
+            if self.arena is not None:
+                from ..utils.telemetry import ExpertTelemetry
+                self.fwd.telemetry = ExpertTelemetry(self.cfg.n_layers + len(weights.mtp),
+                                                     max(weights.e_hi - weights.e_lo, 1))
             L = self.fwd.ws.max_logit_rows
             self.out_host = torch.zeros(2 * L, dtype=torch.int32).pin_memory()
         else:
@@ -401,4 +405,5 @@ class DeepSeekRunner(ModelRunner):
         d["kv_pool_bytes"] = self.pool.data.numel() * self.pool.data.element_size()
         if self.arena is not None:
             d["expert_arena"] = dict(vars(self.arena.stats))
+            d["expert_telemetry"] = self.fwd.telemetry.snapshot()
         return d

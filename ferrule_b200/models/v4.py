@@ -154,6 +154,28 @@ def sparse_sink_attention(q: torch.Tensor, table: torch.Tensor, selection: torch
     return out
 
 
+def markov_head(logits: torch.Tensor, w1: torch.Tensor, w2: torch.Tensor, anchor: int):
+    """Sequential Markov proposal head over a block of draft rows.  logits [gamma, vocab] fp32 (LM head of the
+    block's backbone rows), w1 / w2 [vocab, rank]: draft_j = argmax_t(logits[j, t] + w2[t] . w1[prev]) with
+    prev = anchor for j = 0 and draft_{j-1} after; ties go to the lower id.  Returns (drafts, biased logits)."""
+    prev = int(anchor)
+    ids, vals = [], []
+    for j in range(logits.shape[0]):
+        biased = logits[j].float() + w2.float() @ w1[prev].float()
+        best = torch.max(biased)
+        tok = int(torch.nonzero(biased == best)[0])
+        ids.append(tok)
+        vals.append(float(best))
+        prev = tok
+    return ids, vals
+
+
+def hc_mean_taps(states, hc: int) -> torch.Tensor:
+    """Proposal target taps: for every tapped layer the mean over the hc copies, concatenated along the feature
+    dimension and rounded to bf16.  states: list of [T, hc, hidden]."""
+    return torch.cat([ref.bf16_round(s.float().sum(1) / hc) for s in states], dim=-1)
+
+
 # ------------------------------------------------------------------------------------------ CUDA dispatch
 def hc_pre_cuda(state, fn, scale, base, cfg: HcConfig):
     from ..ops import v4 as K4

@@ -47,6 +47,8 @@ def declare(lib) -> None:
         "fb_rope_rows": ([vp, ll, ll, i, i, i, i, vp, vp, vp, i, i, vp, vp], i),
         "fb_indexer_scores": ([vp, vp, ll, vp, vp, ll, i, i, i, i, vp], i),
         "fb_indexer_topk": ([vp, ll, vp, i, i, vp, ll, i, vp], i),
+        "fb_markov_step": ([vp, vp, vp, i, i, i, vp, vp, vp, vp, vp, vp, vp, vp], i),
+        "fb_hc_mean_scatter": ([vp, vp, ll, i, i, i, i, vp], i),
     }
     for name, (args, res) in table.items():
         if _has(lib, name):

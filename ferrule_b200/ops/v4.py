@@ -126,3 +126,43 @@ def sparse_sink_attention(q: torch.Tensor, table: torch.Tensor, selection: torch
     a.selection, a.sel_width = selection.data_ptr(), W
     check(lib.fb_mla_attention(C.byref(a), stream_ptr()), "fb_mla_attention(selection)")
     return out
+
+
+class MarkovScratch:
+    def __init__(self, device, chunks: int = 296):
+        self.chunks = chunks
+        self.part_val = torch.empty(chunks, dtype=torch.float32, device=device)
+        self.part_id = torch.empty(chunks, dtype=torch.int32, device=device)
+        self.ctr = torch.zeros(1, dtype=torch.int32, device=device)
+
+
+def markov_head(logits: torch.Tensor, w1: torch.Tensor, w2: torch.Tensor, anchor: torch.Tensor,
+                scratch: Optional[MarkovScratch] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+    """logits fp32 [gamma, vocab]; w1, w2 bf16 [vocab, rank]; anchor int32 [1] on the device.  One launch per
+    draft step; each step reads the previous draft from device memory.  Returns (ids [gamma], values [gamma])."""
+    lib = get_lib(True)
+    gamma, vocab = logits.shape
+    rank = w1.shape[1]
+    assert logits.dtype == torch.float32 and logits.stride(1) == 1 and w1.dtype == w2.dtype == torch.bfloat16
+    assert w1.is_contiguous() and w2.is_contiguous() and anchor.dtype == torch.int32
+    scratch = scratch or MarkovScratch(logits.device)
+    ids = torch.empty(gamma, dtype=torch.int32, device=logits.device)
+    vals = torch.empty(gamma, dtype=torch.float32, device=logits.device)
+    st = status_tensor(logits.device).data_ptr()
+    for j in range(gamma):
+        prev = anchor if j == 0 else ids[j - 1:j]
+        check(lib.fb_markov_step(logits[j].data_ptr(), w1.data_ptr(), w2.data_ptr(), vocab, rank, scratch.chunks,
+                                 prev.data_ptr(), scratch.part_val.data_ptr(), scratch.part_id.data_ptr(),
+                                 scratch.ctr.data_ptr(), ids[j:j + 1].data_ptr(), vals[j:j + 1].data_ptr(), st,
+                                 stream_ptr()), "fb_markov_step")
+    return ids, vals
+
+
+def hc_mean_scatter(state: torch.Tensor, taps: torch.Tensor, tap_index: int) -> torch.Tensor:
+    """state bf16 [T, hc, hidden] -> taps[:, tap_index * hidden : +hidden] = bf16(mean over hc)."""
+    lib = get_lib(True)
+    T, hc, hidden = state.shape
+    assert state.is_contiguous() and state.dtype == taps.dtype == torch.bfloat16 and taps.stride(1) == 1
+    check(lib.fb_hc_mean_scatter(state.data_ptr(), taps.data_ptr(), taps.stride(0), tap_index * hidden, T, hc, hidden,
+                                 stream_ptr()), "fb_hc_mean_scatter")
+    return taps

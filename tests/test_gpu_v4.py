@@ -155,3 +155,23 @@ def test_v4_model_decode_matches_reference():
     assert len(caches[0].comp[1]) == 7 and len(caches[0].comp[2]) == 3
     got = cuda_model.tables[1][0, 64:64 + 7].float().cpu()
     assert torch.allclose(got, torch.stack(caches[0].comp[1]), atol=0.08, rtol=0.05)
+
+
+def test_markov_head_and_mean_taps_match_reference():
+    from ferrule_b200.ops import v4 as K
+    torch.manual_seed(5)
+    vocab, rank, gamma = 129280, 64, 5
+    logits = torch.randn(gamma, vocab, device=DEV)
+    w1 = (torch.randn(vocab, rank, device=DEV) * 0.3).bfloat16()
+    w2 = (torch.randn(vocab, rank, device=DEV) * 0.3).bfloat16()
+    anchor = torch.tensor([1234], dtype=torch.int32, device=DEV)
+    ids, vals = K.markov_head(logits, w1, w2, anchor)
+    want_ids, want_vals = v4.markov_head(logits, w1, w2, 1234)
+    torch.cuda.synchronize()
+    assert ids.tolist() == want_ids
+    assert torch.allclose(vals.cpu(), torch.tensor(want_vals), atol=1e-3)
+    state = torch.randn(7, 4, 256, device=DEV).bfloat16()
+    taps = torch.zeros(7, 3 * 256, dtype=torch.bfloat16, device=DEV)
+    K.hc_mean_scatter(state, taps, 1)
+    want = v4.hc_mean_taps([state], 4)
+    assert torch.equal(taps[:, 256:512].float(), want) and float(taps[:, :256].abs().max()) == 0.0

@@ -74,3 +74,22 @@ def test_sparse_attention_ignores_masked_rows_and_honours_sink():
     assert torch.allclose(out[0], want, atol=1e-6)
     sunk = v4.sparse_sink_attention(q, table, sel, kv_lora=8, scale=0.3, sink=torch.tensor([50.0, 50.0]))
     assert sunk.abs().max() < 1e-6                                # a huge sink absorbs the mass
+
+
+def test_markov_head_chains_drafts_and_breaks_ties_low():
+    vocab, rank = 12, 4
+    w1 = torch.zeros(vocab, rank)
+    w2 = torch.zeros(vocab, rank)
+    w1[3, 0] = 1.0          # after token 3 ...
+    w2[7, 0] = 5.0          # ... token 7 gets a bonus
+    logits = torch.zeros(3, vocab)
+    logits[0, 3] = 1.0      # first draft: 3
+    logits[2, 5] = logits[2, 9] = 2.0
+    ids, vals = v4.markov_head(logits, w1, w2, anchor=0)
+    assert ids == [3, 7, 5] and vals[1] == 5.0 and vals[2] == 2.0
+
+
+def test_hc_mean_taps_concatenates_layer_means():
+    a = torch.arange(24, dtype=torch.float32).view(1, 4, 6)
+    taps = v4.hc_mean_taps([a, 2 * a], 4)
+    assert taps.shape == (1, 12) and torch.allclose(taps[0, :6], a[0].mean(0)) and torch.allclose(taps[0, 6:], 2 * a[0].mean(0))
