@@ -165,6 +165,8 @@ _STATUS_NAMES = {1: "pipeline barrier timeout", 2: "peer flag timeout", 3: "inde
 
 def status_tensor(device=None) -> torch.Tensor:
     dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    if dev.type == "cuda" and dev.index is None:          # "cuda" and "cuda:N" must name the same status word
+        dev = torch.device("cuda", torch.cuda.current_device())
     t = _status.get(dev)
     if t is None:
         t = torch.zeros(4, dtype=torch.int32, device=dev)

@@ -386,7 +386,7 @@ def test_bounded_wait_reports_timeout_and_context_stays_usable():
     flag = torch.zeros(4, dtype=torch.int32, device="cuda")
     result = torch.full((1,), -1, dtype=torch.int32, device="cuda")
     _lib.read_status()                                        # start clean
-    st = _lib.status_tensor("cuda")
+    st = _lib.status_tensor()
     t0 = torch.cuda.Event(enable_timing=True)
     t1 = torch.cuda.Event(enable_timing=True)
     t0.record()
