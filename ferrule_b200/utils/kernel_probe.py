@@ -1,0 +1,182 @@
+"""Small, self-ending workloads of one kernel family each, for profiler captures and quick timings.
+
+    python -m ferrule_b200.utils.kernel_probe <case> [reps]
+
+Cases use decode-step shapes of the DeepSeek-V2-Lite configuration (batch 32, context about 640) unless
+noted; weight sets are rotated through more buffers than fit in L2 where the kernel is bandwidth-bound, and
+no case holds more than about 2 GB on the device.  Each case prints one JSON line with the CUDA-event time
+per call.
+"""
+from __future__ import annotations
+
+import json
+import sys
+
+import torch
+
+from ferrule_b200.ops import kernels as K
+
+DEV = "cuda"
+
+
+def rnd(*s, scale=1.0, dtype=torch.bfloat16):
+    return (torch.randn(*s, device=DEV) * scale).to(dtype)
+
+
+def timed(fn, reps):
+    for i in range(3):
+        fn(i)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(reps):
+        fn(3 + i)
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / reps * 1e3
+
+
+def case_attention(reps):
+    """Paged MLA decode attention: 32 sequences x 16 heads, context 640, 8 KV splits merged in a cluster."""
+    B, H, DL, DR, page, ctx = 32, 16, 512, 64, 64, 640
+    D = DL + DR
+    blocks = (ctx + page - 1) // page
+    pool = rnd(B * blocks + 1, page, D, scale=0.3)
+    bt = (torch.arange(B * blocks, device=DEV, dtype=torch.int32) + 1).view(B, blocks)
+    q = rnd(B, H, D, scale=0.3)
+    out = torch.zeros(B, H, DL, dtype=torch.bfloat16, device=DEV)
+    rseq = torch.arange(B, device=DEV, dtype=torch.int32)
+    rpos = torch.full((B,), ctx - 1, device=DEV, dtype=torch.int32)
+    fn = lambda i: K.mla_attention(q, pool, bt, rseq, rpos, page, DL, DR, 0.07, out, splits=8, split_tokens=128)
+    return timed(fn, reps), {"kv_bytes": B * ctx * D * 2}
+
+
+def case_gemm_dense(reps):
+    """q|kv_a projection: [32 x 2048] x [3648 x 2048]^T, weights rotated over 24 copies (360 MB)."""
+    ws = [rnd(3648, 2048, scale=0.02) for _ in range(24)]
+    x = rnd(32, 2048)
+    out = torch.zeros(32, 3648, dtype=torch.bfloat16, device=DEV)
+    return timed(lambda i: K.gemm(x, ws[i % 24], out=out), reps), {"weight_bytes": 3648 * 2048 * 2}
+
+
+def _plan(T, k, E, ntok):
+    idx = torch.stack([torch.randperm(E, device=DEV)[:k] for _ in range(T)]).int()
+    w = torch.rand(T, k, device=DEV)
+    plan = K.MoePlan.allocate(T * k, E, ntok, DEV)
+    K.moe_plan(idx, w, plan, 0, E, dst_slots=k + 1)
+    return idx, w, plan
+
+
+def case_gemm_grouped(reps):
+    """Routed experts of one layer: 192 routes over 64 experts, gate|up + SwiGLU then down + scatter (1.1 GB of weights)."""
+    T, k, E, H, I = 32, 6, 64, 2048, 1408
+    idx, w, plan = _plan(T, k, E, 16)
+    w13 = [rnd(E, 2 * I, H, scale=0.02) for _ in range(2)]
+    w2 = [rnd(E, H, I, scale=0.02) for _ in range(2)]
+    xg = rnd(T * k, H)
+    hmid = torch.zeros(T * k, I, dtype=torch.bfloat16, device=DEV)
+    out = torch.zeros(T * (k + 1), H, dtype=torch.bfloat16, device=DEV)
+
+    def fn(i):
+        K.gemm(xg, w13[i % 2], out=hmid, epilogue=K.EPI_SWIGLU, plan=plan)
+        K.gemm(hmid, w2[i % 2], out=out, epilogue=K.EPI_SCATTER, plan=plan, scatter_rows=T * (k + 1))
+    return timed(fn, reps), {"weight_bytes": E * 3 * H * I * 2}
+
+
+def case_gemm_fp8(reps):
+    """Block-scaled FP8 grouped gate|up + SwiGLU on the same expert shape (weights 0.37 GB per copy)."""
+    from ferrule_b200.models.weights import QuantWeight
+    from ferrule_b200.ops import quant as Q
+    T, k, E, H, I = 32, 6, 64, 2048, 1408
+    idx, w, plan = _plan(T, k, E, 16)
+    qw = [QuantWeight.from_bf16(rnd(E, 2 * I, H, scale=0.02), "fp8_block") for _ in range(3)]
+    xg = rnd(T * k, H)
+    xq = Q.quant_fp8_rows(xg)
+    hmid = torch.zeros(T * k, I, dtype=torch.bfloat16, device=DEV)
+    fn = lambda i: Q.gemm_fp8(xq[0], xq[1], qw[i % 3].q, qw[i % 3].scale, out=hmid, epilogue=1, plan=plan)
+    return timed(fn, reps), {"weight_bytes": E * 2 * I * H}
+
+
+def case_small(reps):
+    """The latency-bound kernels of one layer back to back: add+RMSNorm, MLA prep, fused router + plan, gather,
+    MoE reduce, chunked arg-max."""
+    T, H, E, k = 32, 2048, 64, 6
+    x, d = rnd(T, H), rnd(T, H)
+    nw = torch.ones(H, dtype=torch.bfloat16, device=DEV)
+    res, xn = torch.zeros_like(x), torch.zeros_like(x)
+    rw = rnd(E, H, scale=0.05)
+    plan = K.MoePlan.allocate(T * k, E, 16, DEV)
+    idx = torch.zeros(T, k, dtype=torch.int32, device=DEV)
+    wts = torch.zeros(T, k, dtype=torch.float32, device=DEV)
+    ctr = torch.zeros(4, dtype=torch.int32, device=DEV)
+    xg = torch.zeros(T * k, H, dtype=torch.bfloat16, device=DEV)
+    route_out = rnd(T * (k + 1), H)
+    logits = torch.randn(T, 102400, device=DEV)
+    scratch = K.ArgmaxScratch.allocate(T, DEV)
+    nid = torch.zeros(T, dtype=torch.int32, device=DEV)
+    nval = torch.zeros(T, dtype=torch.float32, device=DEV)
+
+    def fn(i):
+        K.add_rmsnorm(x, nw, 1e-6, delta=d, res_out=res, norm_out=xn)
+        K.router_plan_fused(xn, rw, k, 0, plan, 0, E, idx, wts, ctr, dst_slots=k + 1)
+        K.gather_rows(xn, plan, xg, cap_rows=T * k)
+        K.moe_reduce(route_out, k + 1, k, idx, 0, E, T, H, residual=res, out=x)
+        K.argmax_chunked(logits, scratch, nid, nval)
+    return timed(fn, reps), {}
+
+
+def case_v4(reps):
+    """DeepSeek-V4 operators at family size: hc_pre (4 x 4096), compressor pooling (ratio 4, overlap), indexer
+    scores over 16384 compressed rows + top-512, selection attention over 128 + 512 rows."""
+    from ferrule_b200.models import v4
+    from ferrule_b200.ops import v4 as K4
+    cfg = v4.HcConfig(4, 4096)
+    T = 32
+    state = rnd(T, 4, 4096)
+    fn_w = torch.randn(cfg.mix, 4 * 4096, device=DEV) * 0.02
+    scale = torch.tensor([0.7, 1.1, 0.9], device=DEV)
+    base = torch.randn(cfg.mix, device=DEV) * 0.3
+    kvp, gp = torch.randn(64, 1024, device=DEV), torch.randn(64, 1024, device=DEV)
+    ape = torch.randn(4, 1024, device=DEV)
+    n = 16384
+    iq = rnd(T, 64, 128, scale=0.3)
+    plane = rnd(n, 128, scale=0.3)
+    hw = torch.randn(T, 64, device=DEV)
+    table = rnd(n + 4096, 512, scale=0.3)
+    q = rnd(T, 64, 512, scale=0.1)
+    scores = torch.zeros(T, n, device=DEV)
+
+    def fn(i):
+        hid, coeff = K4.hc_pre(state, fn_w, scale, base, cfg)
+        K4.hc_post(hid, state, coeff)
+        K4.compressor_pool(kvp, gp, ape, 4, True)
+        K4.indexer_scores(iq, plane, hw, out=scores)
+        idx = K4.indexer_topk(scores, 512)
+        win = torch.arange(n, n + 128, device=DEV, dtype=torch.int32)[None].expand(T, 128)
+        sel = torch.cat([win, idx], dim=1).contiguous()
+        K4.sparse_sink_attention(q, table, sel, 512, 0, 0.044, splits=4)
+    return timed(fn, reps), {}
+
+
+CASES = {"attention": case_attention, "gemm_dense": case_gemm_dense, "gemm_grouped": case_gemm_grouped,
+         "gemm_fp8": case_gemm_fp8, "small": case_small, "v4": case_v4}
+
+
+def main() -> int:
+    name = sys.argv[1] if len(sys.argv) > 1 else "attention"
+    reps = int(sys.argv[2]) if len(sys.argv) > 2 else 20
+    torch.manual_seed(0)
+    us, extra = CASES[name](reps)
+    out = {"case": name, "reps": reps, "us_per_call": round(us, 2)}
+    out.update(extra)
+    for key in ("weight_bytes", "kv_bytes"):
+        if key in extra:
+            out["gb_per_s"] = round(extra[key] / us / 1e3, 1)
+    from ferrule_b200.ops import _lib
+    out["device_status"] = _lib.read_status()[0]
+    print(json.dumps(out))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())
