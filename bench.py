@@ -102,7 +102,12 @@ def main() -> None:
     ap.add_argument("--model", default="deepseek-v2-lite")
     ap.add_argument("--weight-format", default="bf16", choices=["bf16", "fp8_block", "fp8_mxfp4"],
                     help="bf16 is the headline configuration; the FP8 formats are reported with their own dtype")
+    ap.add_argument("--shard-as", type=int, default=0,
+                    help="debug only: on one GPU, hold rank 0's shard of a TP-N layout and skip the collectives "
+                         "(compute-only time of one rank; the result is marked invalid)")
     ap.add_argument("--layers", type=int, default=0, help="debug only: override layer count (result is marked invalid)")
+    ap.add_argument("--ar-payload", default="bf16", choices=["fp32", "bf16"],
+                    help="what the fused all-reduces push over NVLink: bf16 partials (default, as bf16 all-reduces do) or fp32")
     ap.add_argument("--no-fused", action="store_true", help="use the NCCL baseline collectives instead of fused kernels")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -132,7 +137,7 @@ def main() -> None:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=dev)
         from ferrule_b200.parallel.tp import TensorParallel
-        tp = TensorParallel(rank, world, dev, fused=not args.no_fused)
+        tp = TensorParallel(rank, world, dev, fused=not args.no_fused, payload=args.ar_payload)
 
     cfg = C.PRESETS[args.model]()
     if args.layers:
@@ -142,7 +147,7 @@ def main() -> None:
     margin = 64                      # sequences that finish prefill early decode ahead of the others
     max_seq = P + K + Wm + margin + 2 * page
     pages_per_seq = (max_seq + page - 1) // page
-    weights = W.random_weights(cfg, device=dev, seed=0, tp_rank=rank, tp_world=world, fast_device_init=True,
+    weights = W.random_weights(cfg, device=dev, seed=0, tp_rank=rank, tp_world=args.shard_as or world, fast_device_init=True,
                                weight_format=args.weight_format)
     runner = DeepSeekRunner(weights, n_pages=B * pages_per_seq + 8, page_size=page, max_rows=2048, max_seqs=B,
                             max_seq_len=pages_per_seq * page, device=dev, tp=tp)
@@ -204,6 +209,8 @@ def main() -> None:
     for _ in range(3):
         graph.replay()
     barrier()
+    from ferrule_b200.ops import _lib
+    _lib.read_peer_wait()
     d0, d1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     d0.record()
     for _ in range(K):
@@ -212,13 +219,13 @@ def main() -> None:
     barrier()
     clocks = sampler.stop()
     dev_ms = d0.elapsed_time(d1)
+    wait_ns, wait_n = _lib.read_peer_wait()
 
-    from ferrule_b200.ops import _lib
     status = _lib.read_status()
-    times = torch.tensor([dev_ms, e2e_ms], dtype=torch.float64, device=dev)
+    times = torch.tensor([dev_ms, e2e_ms, wait_ns / 1e6], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
-    dev_ms, e2e_ms = times.tolist()
+    dev_ms, e2e_ms, wait_ms = times.tolist()
     tpots = []
     for r, ts in token_times.items():
         if len(ts) > 2:
@@ -237,10 +244,13 @@ def main() -> None:
                        "parallelism": par, "kv_page_size": page, "layers": cfg.n_layers,
                        "l2_policy": "inputs larger than L2: each step streams %.1f GB of weights per GPU"
                                     % (weights.nbytes() / 1e9),
-                       "collectives": "none" if world == 1 else ("nccl" if args.no_fused else "fused-p2p")},
+                       "collectives": "none" if world == 1 else ("nccl" if args.no_fused else "fused-p2p, %s partials" % args.ar_payload)},
             "e2e": {"value": round(e2e_value, 1), "unit": "tokens/s", "ms_per_step": round(e2e_ms / K, 4),
                     "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h),
                     "path": "Engine.step (scheduler + KV transactions + pinned H2D + graph + D2H)"},
+            "peer_wait": {"ms_per_step_max_rank": round(wait_ms / K, 4), "waits_per_step": wait_n // max(K, 1),
+                          "avg_wait_us": round(wait_ns / 1e3 / max(wait_n, 1), 2),
+                          "note": "time one thread per waiting CTA spent spinning on peer arrival flags; CTAs wait concurrently"},
             "gpu_launches": int(graph.launches * K),
             "gpu_launches_e2e": int(e2e_launches),
             "clocks": {"sm_mhz": clocks["sm_mhz"], "sm_max_mhz": clocks["sm_max_mhz"], "reasons": clocks["reasons"],
@@ -252,6 +262,8 @@ def main() -> None:
         }
         if args.layers:
             line["invalid"] = "debug run with a reduced layer count"
+        if args.shard_as:
+            line["invalid"] = "debug run: one rank's shard of a TP-%d layout without collectives" % args.shard_as
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()

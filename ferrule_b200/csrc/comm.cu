@@ -3,19 +3,20 @@
 //   fb_ipc_*                 symmetric buffers: cudaMalloc + CUDA IPC handles, opened by every
 //                            peer rank of the node (NVLink peer access through NVSwitch)
 //   fb_moe_reduce_allreduce  per token: fixed-order sum of this rank's route rows (+ shared
-//                            expert row) -> push the fp32 partial into every rank's receive
-//                            buffer with plain peer stores -> bump the peers' arrival counters ->
-//                            wait (bounded) for all ranks -> sum in rank order + residual -> bf16.
+//                            expert row) -> push the partial (fp32 or bf16) into every rank's receive
+//                            slot as tagged words {value, call tag} with plain peer stores -> poll the
+//                            tagged words of all ranks (bounded) -> sum in rank order + residual -> bf16.
+//                            No fence and no flag: only the one-way NVLink latency is paid.
 //                            With slots = 1 and topk = 0 it is a plain one-shot all-reduce.
 //   fb_argmax_allgather      vocabulary-parallel greedy token: every rank pushes its local
 //                            (logit, id) per row to all peers, then picks the global winner
 //                            (ties -> lower id) identically on every rank.
 //   fb_flag_wait_probe       a wait on a flag nobody sets, to exercise the timeout path
 //
-// Synchronisation: per-CTA arrival counters that only grow.  A waiter keeps the count it has
-// already consumed in a private array, so kernels of different shapes can share a channel.
-// Payload slots are double buffered by the channel's call counter: a peer can be at most one
-// call ahead of this rank, because finishing a call needs this rank's arrivals.
+// Synchronisation: the all-reduce payloads carry their own arrival tag (call counter + 1); the small
+// all-gather of arg-max candidates uses arrival counters that only grow.  Payload slots are double
+// buffered by the channel's call counter: a peer can be at most one call ahead of this rank, because
+// finishing a call needs this rank's pushes.
 // Every wait is bounded; on timeout the kernel records a status code and returns.
 //
 // The reference has no multi-GPU path (its ParallelismPlan is inert:
@@ -44,21 +45,28 @@ __device__ __forceinline__ void channel_finish(uint32_t* ctr, uint32_t call) {
   }
 }
 
-__global__ void __launch_bounds__(256)
+// grid = (rows, channel chunks of 512), 128 threads: one 4-channel group per thread.  More, smaller CTAs keep
+// more peer stores in flight than one CTA per row would.
+__global__ void __launch_bounds__(128)
 moe_reduce_allreduce_kernel(const __nv_bfloat16* __restrict__ route_out, int slots, int topk,
                             const int* __restrict__ topk_idx, int e_lo, int e_hi,
                             const __nv_bfloat16* __restrict__ residual, long long ldr,
                             __nv_bfloat16* __restrict__ out, long long ldo, int rows, int dim,
                             int rank, int world, int rows_cap, PeerPtrs peers, uint32_t* ctr,
-                            uint32_t* seen, unsigned long long wait_ns, DeviceStatus* st) {
+                            int payload_bf16, unsigned long long wait_ns, DeviceStatus* st) {
   pdl_launch_dependents();
   pdl_wait();
   const int t = blockIdx.x;
+  const int i = (blockIdx.y * blockDim.x + threadIdx.x) * 4;      // first of this thread's 4 channels
   const uint32_t call = *reinterpret_cast<volatile uint32_t*>(ctr);
-  const size_t slot_elems = static_cast<size_t>(rows_cap) * dim;
-  const size_t base = (static_cast<size_t>(call & 1u) * world) * slot_elems + static_cast<size_t>(t) * dim;
-  // ---- partial -> every rank's receive slot [parity][rank][t] ----
-  for (int i = threadIdx.x * 4; i < dim; i += blockDim.x * 4) {
+  const uint32_t tag = call + 1u;
+  const bool bf16 = payload_bf16 != 0;
+  // slot geometry in bytes: [parity][source rank][rows_cap][dim] tagged values, 8 bytes each (4 when bf16)
+  const size_t slot_bytes = static_cast<size_t>(rows_cap) * dim * 8;
+  const size_t parity_off = static_cast<size_t>(call & 1u) * world * slot_bytes;
+  const size_t ch = static_cast<size_t>(t) * dim + i;
+  if (i < dim) {
+    // ---- this rank's partial of the 4 channels -> every rank's slot for this source ----
     float acc[4] = {0.f, 0.f, 0.f, 0.f};
     for (int s = 0; s < slots; ++s) {
       if (s < topk) {
@@ -70,41 +78,33 @@ moe_reduce_allreduce_kernel(const __nv_bfloat16* __restrict__ route_out, int slo
 #pragma unroll
       for (int j = 0; j < 4; ++j) acc[j] += __bfloat162float(vp[j]);
     }
-    const float4 v4 = make_float4(acc[0], acc[1], acc[2], acc[3]);
     for (int pr = 0; pr < world; ++pr)
-      *reinterpret_cast<float4*>(peers.recv[pr] + base + static_cast<size_t>(rank) * slot_elems + i) = v4;
-  }
-  __threadfence_system();
-  __syncthreads();
-  if (threadIdx.x < world) flag_add_release_sys(peers.flags[threadIdx.x] + t, 1u);
-  // ---- wait for all ranks' copies of this row ----
-  __shared__ int ok_s;
-  if (threadIdx.x == 0) {
-    const uint32_t target = seen[t] + static_cast<uint32_t>(world);
-    ok_s = flag_wait_ge(peers.flags[rank] + t, target, wait_ns, st, 0x500 + t) ? 1 : 0;
-    seen[t] = target;
-  }
-  __syncthreads();
-  if (ok_s) {
-    const float* mine = peers.recv[rank] + base;
-    for (int i = threadIdx.x * 4; i < dim; i += blockDim.x * 4) {
-      float acc[4] = {0.f, 0.f, 0.f, 0.f};
-      for (int src = 0; src < world; ++src) {
-        const float4 v = *reinterpret_cast<const float4*>(mine + static_cast<size_t>(src) * slot_elems + i);
-        acc[0] += v.x; acc[1] += v.y; acc[2] += v.z; acc[3] += v.w;
-      }
+      ll_push4(reinterpret_cast<uint8_t*>(peers.recv[pr]) + parity_off + rank * slot_bytes, ch, acc, tag, bf16);
+    // ---- all ranks' partials: poll the tagged words, sum in rank order, add the residual ----
+    const uint64_t w0 = globaltimer_ns();
+    float sum[4] = {0.f, 0.f, 0.f, 0.f};
+    int bad_src = 0;
+    if (ll_gather4(reinterpret_cast<const uint8_t*>(peers.recv[rank]) + parity_off, ch, slot_bytes, world, tag,
+                   wait_ns, sum, bad_src, bf16)) {
       if (residual) {
         const uint2 v = *reinterpret_cast<const uint2*>(residual + t * ldr + i);
         const __nv_bfloat16* vp = reinterpret_cast<const __nv_bfloat16*>(&v);
 #pragma unroll
-        for (int j = 0; j < 4; ++j) acc[j] += __bfloat162float(vp[j]);
+        for (int j = 0; j < 4; ++j) sum[j] += __bfloat162float(vp[j]);
       }
       __nv_bfloat16 o[4];
 #pragma unroll
-      for (int j = 0; j < 4; ++j) o[j] = __float2bfloat16_rn(acc[j]);
+      for (int j = 0; j < 4; ++j) o[j] = __float2bfloat16_rn(sum[j]);
       *reinterpret_cast<uint2*>(out + t * ldo + i) = *reinterpret_cast<uint2*>(o);
+    } else {
+      report_status(st, kStatusPeerTimeout, 0x500 + bad_src, static_cast<uint32_t>(t), tag);
+    }
+    if (threadIdx.x == 0 && st != nullptr) {
+      atomicAdd(reinterpret_cast<unsigned long long*>(st) + 2, globaltimer_ns() - w0);
+      atomicAdd(reinterpret_cast<unsigned int*>(st) + 6, 1u);
     }
   }
+  __syncthreads();
   if (threadIdx.x == 0) channel_finish(ctr, call);
 }
 
@@ -125,7 +125,6 @@ argmax_allgather_kernel(int* __restrict__ ids, float* __restrict__ vals, int voc
     for (int pr = 0; pr < world; ++pr)
       *reinterpret_cast<float2*>(peers.recv[pr] + base + static_cast<size_t>(rank) * slot_elems + 2 * r) = v;
   }
-  __threadfence_system();
   __syncthreads();
   if (threadIdx.x < world) flag_add_release_sys(peers.flags[threadIdx.x], 1u);
   __shared__ int ok_s;
@@ -153,6 +152,29 @@ __global__ void flag_wait_probe_kernel(const uint32_t* flag, uint32_t target, un
   pdl_launch_dependents();
   pdl_wait();
   if (threadIdx.x == 0 && blockIdx.x == 0) *result = flag_wait_ge(flag, target, wait_ns, st, 0x700) ? 1 : 0;
+}
+
+// Peer-memory latency probe: two ranks bounce a counter through each other's memory `iters` times.
+// mine = word in this rank's buffer (the peer writes it), theirs = word in the peer's buffer.
+// out_ns[0] = total time seen by this rank.  Every wait is bounded.
+__global__ void pingpong_kernel(volatile uint32_t* mine, volatile uint32_t* theirs, int iters, int initiator,
+                                unsigned long long limit_ns, unsigned long long* out_ns, DeviceStatus* st) {
+  if (threadIdx.x != 0 || blockIdx.x != 0) return;
+  const uint64_t t0 = globaltimer_ns();
+  for (int i = 1; i <= iters; ++i) {
+    if (initiator) *theirs = static_cast<uint32_t>(i);
+    const uint64_t w0 = globaltimer_ns();
+    uint32_t spins = 0;
+    while (*mine != static_cast<uint32_t>(i)) {
+      if ((++spins & 0x3fu) == 0u && globaltimer_ns() - w0 > limit_ns) {
+        report_status(st, kStatusPeerTimeout, 0x710, static_cast<uint32_t>(i), *mine);
+        out_ns[0] = 0;
+        return;
+      }
+    }
+    if (!initiator) *theirs = static_cast<uint32_t>(i);
+  }
+  out_ns[0] = globaltimer_ns() - t0;
 }
 
 }  // namespace fb
@@ -198,19 +220,19 @@ extern "C" int fb_moe_reduce_allreduce(const void* route_out, int slots, int top
                                        int e_lo, int e_hi, const void* residual, long long ldr,
                                        void* out, long long ldo, int rows, int dim, int rank,
                                        int world, int rows_cap, void* const* peer_recv,
-                                       void* const* peer_flags, void* ctr, int flag_capacity,
+                                       void* const* peer_flags, void* ctr, int payload_bf16,
                                        unsigned long long wait_ns, void* status, void* stream) {
-  if (rows <= 0 || rows > rows_cap || rows > flag_capacity || dim % 4 != 0 || slots < 1 || slots < topk)
+  if (rows <= 0 || rows > rows_cap || dim % 4 != 0 || slots < 1 || slots < topk)
     return FB_ERR_SHAPE;
   if (rank < 0 || rank >= world || !ctr) return FB_ERR_SHAPE;
   PeerPtrs p{};
   const int rc = fill_peers(&p, peer_recv, peer_flags, world);
   if (rc != FB_OK) return rc;
   uint32_t* c = static_cast<uint32_t*>(ctr);
-  launch_pdl(moe_reduce_allreduce_kernel, dim3(rows), dim3(256), 0, static_cast<cudaStream_t>(stream), 
+  launch_pdl(moe_reduce_allreduce_kernel, dim3(rows, (dim + 511) / 512), dim3(128), 0, static_cast<cudaStream_t>(stream),
       static_cast<const __nv_bfloat16*>(route_out), slots, topk, topk_idx, e_lo, e_hi,
       static_cast<const __nv_bfloat16*>(residual), ldr, static_cast<__nv_bfloat16*>(out), ldo, rows, dim,
-      rank, world, rows_cap, p, c, c + 2, wait_ns ? wait_ns : 3000000000ull,
+      rank, world, rows_cap, p, c, payload_bf16, wait_ns ? wait_ns : 3000000000ull,
       static_cast<DeviceStatus*>(status));
   return cudaGetLastError() == cudaSuccess ? FB_OK : FB_ERR_LAUNCH;
 }
@@ -234,5 +256,14 @@ extern "C" int fb_flag_wait_probe(const void* flag, int target, unsigned long lo
   launch_pdl(flag_wait_probe_kernel, dim3(1), dim3(32), 0, static_cast<cudaStream_t>(stream), 
       static_cast<const uint32_t*>(flag), static_cast<uint32_t>(target), wait_ns,
       static_cast<DeviceStatus*>(status), result);
+  return cudaGetLastError() == cudaSuccess ? FB_OK : FB_ERR_LAUNCH;
+}
+
+extern "C" int fb_peer_pingpong(void* mine, void* theirs, int iters, int initiator, unsigned long long limit_ns,
+                                void* out_ns, void* status, void* stream) {
+  if (!mine || !theirs || iters <= 0 || !out_ns) return FB_ERR_SHAPE;
+  pingpong_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<volatile uint32_t*>(mine), static_cast<volatile uint32_t*>(theirs), iters, initiator,
+      limit_ns ? limit_ns : 2000000000ull, static_cast<unsigned long long*>(out_ns), static_cast<DeviceStatus*>(status));
   return cudaGetLastError() == cudaSuccess ? FB_OK : FB_ERR_LAUNCH;
 }

@@ -364,7 +364,14 @@ __device__ __forceinline__ bool flag_wait_ge(const uint32_t* flag, uint32_t targ
   uint32_t spins = 0;
   while (true) {
     v = flag_ld_acquire_sys(flag);
-    if (static_cast<int32_t>(v - target) >= 0) return true;
+    if (static_cast<int32_t>(v - target) >= 0) {
+      // words 4..6 of the status block: time spent waiting for peers (ns, 64-bit) and number of waits
+      if (st != nullptr) {
+        atomicAdd(reinterpret_cast<unsigned long long*>(st) + 2, globaltimer_ns() - t0);
+        atomicAdd(reinterpret_cast<unsigned int*>(st) + 6, 1u);
+      }
+      return true;
+    }
     if ((++spins & 0x3fu) == 0u) {
       if (globaltimer_ns() - t0 > limit_ns) {
         report_status(st, kStatusPeerTimeout, where, v, target);
@@ -372,6 +379,118 @@ __device__ __forceinline__ bool flag_wait_ge(const uint32_t* flag, uint32_t targ
       }
     }
   }
+}
+
+// ---------------------------------------------------------------------------------
+// Tagged pushes ("data + flag in one word"): every fp32 travels as the 8-byte pair {bits, tag}, two pairs
+// per 16-byte store.  The receiver polls the words themselves until the tag equals the call's tag, so a
+// push needs no separate fence / flag round trip: the one-way NVLink latency is all that is paid.  An
+// 8-byte aligned pair is written atomically, so a store torn at 8 bytes is still consistent.  Tags are
+// the call counter + 1 (never 0: buffers start zeroed); slots are double buffered by call parity.
+// ---------------------------------------------------------------------------------
+__device__ __forceinline__ void ll_store2(void* dst, float a, float b, uint32_t tag) {
+  asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "r"(__float_as_uint(a)), "r"(tag),
+               "r"(__float_as_uint(b)), "r"(tag)
+               : "memory");
+}
+__device__ __forceinline__ uint4 ll_load_raw(const void* src) {
+  uint4 v;
+  asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(src) : "memory");
+  return v;
+}
+// Poll one 16-byte word until both tags match; false after limit_ns (status recorded by the caller).
+__device__ __forceinline__ bool ll_wait2(const void* src, uint32_t tag, uint64_t limit_ns, float& a, float& b) {
+  uint4 v = ll_load_raw(src);
+  if (v.y != tag || v.w != tag) {
+    const uint64_t t0 = globaltimer_ns();
+    uint32_t spins = 0;
+    while (true) {
+      v = ll_load_raw(src);
+      if (v.y == tag && v.w == tag) break;
+      if ((++spins & 0x3fu) == 0u && globaltimer_ns() - t0 > limit_ns) return false;
+    }
+  }
+  a = __uint_as_float(v.x);
+  b = __uint_as_float(v.z);
+  return true;
+}
+
+// A slot holds `channels` values per row either as fp32 pairs {bits, tag} (8 bytes per channel) or as packed
+// bf16 pairs {bf16x2, tag} (4 bytes per channel; halves the NVLink bytes, partials are rounded to bf16).
+// Channel offsets are multiples of 4, so 4 channels are two (fp32) or one (bf16) aligned 16-byte words.
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+  const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&v);
+}
+__device__ __forceinline__ void ll_store_words(void* dst, uint32_t w0, uint32_t w1, uint32_t tag) {
+  asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "r"(w0), "r"(tag), "r"(w1), "r"(tag)
+               : "memory");
+}
+// base: start of the destination slot (this source's [rows_cap][channels] area); ch: row * channels + channel
+__device__ __forceinline__ void ll_push4(void* base, size_t ch, const float (&v)[4], uint32_t tag, bool bf16) {
+  if (bf16) {
+    ll_store_words(static_cast<uint8_t*>(base) + ch * 4, pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]), tag);
+  } else {
+    uint8_t* d = static_cast<uint8_t*>(base) + ch * 8;
+    ll_store_words(d, __float_as_uint(v[0]), __float_as_uint(v[1]), tag);
+    ll_store_words(d + 16, __float_as_uint(v[2]), __float_as_uint(v[3]), tag);
+  }
+}
+
+// Gather 4 consecutive channels from the slots of `world` (<= 8) source ranks and add them in rank order.
+// The loads of all ranks are issued together (one L2 round trip when everything has arrived); words whose
+// tag is not the call's yet are re-polled.  first = source 0's slot, ch as in ll_push4, stride = bytes between
+// consecutive sources' slots.  Returns false after limit_ns (bad_src = a source that was missing).
+__device__ __forceinline__ bool ll_gather4(const void* first, size_t ch, size_t stride, int world, uint32_t tag,
+                                           uint64_t limit_ns, float (&acc)[4], int& bad_src, bool bf16) {
+  uint4 v[16];
+  const uint8_t* p0 = static_cast<const uint8_t*>(first) + ch * (bf16 ? 4 : 8);
+#pragma unroll
+  for (int s = 0; s < 8; ++s) {
+    if (s < world) {
+      v[2 * s] = ll_load_raw(p0 + s * stride);
+      if (!bf16) v[2 * s + 1] = ll_load_raw(p0 + s * stride + 16);
+    }
+  }
+  uint64_t t0 = 0;
+  uint32_t spins = 0;
+  while (true) {
+    bool all = true;
+#pragma unroll
+    for (int s = 0; s < 8; ++s) {
+      if (s < world) {
+        if (v[2 * s].y != tag || v[2 * s].w != tag) {
+          v[2 * s] = ll_load_raw(p0 + s * stride);
+          all = false;
+          bad_src = s;
+        }
+        if (!bf16 && (v[2 * s + 1].y != tag || v[2 * s + 1].w != tag)) {
+          v[2 * s + 1] = ll_load_raw(p0 + s * stride + 16);
+          all = false;
+          bad_src = s;
+        }
+      }
+    }
+    if (all) break;
+    if (t0 == 0) t0 = globaltimer_ns();
+    if ((++spins & 0x3fu) == 0u && globaltimer_ns() - t0 > limit_ns) return false;
+  }
+#pragma unroll
+  for (int s = 0; s < 8; ++s) {
+    if (s < world) {
+      if (bf16) {
+        const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v[2 * s].x));
+        const float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v[2 * s].z));
+        acc[0] += lo.x; acc[1] += lo.y; acc[2] += hi.x; acc[3] += hi.y;
+      } else {
+        acc[0] += __uint_as_float(v[2 * s].x);
+        acc[1] += __uint_as_float(v[2 * s].z);
+        acc[2] += __uint_as_float(v[2 * s + 1].x);
+        acc[3] += __uint_as_float(v[2 * s + 1].z);
+      }
+    }
+  }
+  return true;
 }
 
 }  // namespace fb

@@ -68,6 +68,7 @@ typedef struct FbGemmArgs {
   unsigned long long peer_wait_ns;
   void* status;
   void* trace;              // optional: 8 x uint64 globaltimer stamps written by CTA 0 (profiling)
+  int ar_payload_bf16;      // epilogue 3: push partials as bf16 pairs (half the NVLink bytes) instead of fp32
   const int* remap_rank;    // epilogue 2, expert-parallel combine: output row -> destination rank and row of
   const int* remap_row;     //   that rank's bf16 combine buffer (peer_recv[rank], pitch ldo); peer_flags[r][rank]
                             //   is bumped once per call when all of this rank's rows are stored
@@ -267,10 +268,13 @@ int fb_moe_reduce_allreduce(const void* route_out, int slots, int topk, const in
                             int e_hi, const void* residual, long long ldr, void* out, long long ldo,
                             int rows, int dim, int rank, int world, int rows_cap,
                             void* const* peer_recv, void* const* peer_flags, void* ctr,
-                            int flag_capacity, unsigned long long wait_ns, void* status, void* stream);
+                            int payload_bf16, unsigned long long wait_ns, void* status, void* stream);
 int fb_argmax_allgather(int* ids, float* vals, int vocab_lo, int rows, int rank, int world, int rows_cap,
                         void* const* peer_recv, void* const* peer_flags, void* ctr,
                         unsigned long long wait_ns, void* status, void* stream);
+// two ranks bounce a counter through each other's memory; out_ns[0] = total ns for `iters` round trips
+int fb_peer_pingpong(void* mine, void* theirs, int iters, int initiator, unsigned long long limit_ns, void* out_ns,
+                     void* status, void* stream);
 int fb_flag_wait_probe(const void* flag, int target, unsigned long long wait_ns, void* status,
                        int* result, void* stream);
 

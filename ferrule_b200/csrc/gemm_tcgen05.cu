@@ -67,6 +67,7 @@ struct GemmParams {
   float* peer_recv[8];       // receive buffer of every rank, in this rank's address space
   uint32_t* peer_flags[8];   // per-tile arrival counters of every rank
   uint32_t* local_ctr;       // [0] = calls completed, [1] = CTAs finished this call, [2..] = consumed arrivals per tile
+  int ar_bf16;               // kEpiAllReduce: partials travel as bf16 pairs instead of fp32
   const int* remap_rank;     // kEpiScatter, expert-parallel combine: output row -> destination rank ...
   const int* remap_row;      // ... and row in that rank's combine buffer (peer_recv[rank], bf16, pitch ldo)
   const __nv_bfloat16* residual;  // optional, added after the reduction
@@ -147,6 +148,10 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tmap_w,
   // partial accumulators travel to the leader (cluster rank 0) through distributed shared memory.
   const int S = static_cast<int>(cluster_nctarank());
   const int crank = static_cast<int>(cluster_ctarank());
+  // all-reduce epilogue: receive-slot geometry in bytes ([parity][source][rows_cap][n_out] tagged values, 8 bytes
+  // each) and the [NTOK][128] fp32 staging tile behind the split-K area
+  const size_t ar_slot_bytes = static_cast<size_t>(p.rows_cap) * p.n_out * 8;
+  float* ar_stage = red + static_cast<size_t>(S > 1 ? S - 1 : 0) * Cfg::kAccCols * 128;
   const int tile_first = blockIdx.x / S;
   const int tile_stride = gridDim.x / S;
 
@@ -192,6 +197,7 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tmap_w,
 
   uint32_t call = 0;
   if (EPI == kEpiAllReduce && !is_producer) call = *reinterpret_cast<volatile uint32_t*>(p.local_ctr);
+  const size_t ar_parity_off = static_cast<size_t>(call & 1u) * p.world * ar_slot_bytes;
 
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
@@ -394,10 +400,7 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tmap_w,
                   dst[static_cast<long long>(p.remap_row[orow]) * p.ldo + ocol] = __float2bfloat16_rn(x);
                 }
               } else if (EPI == kEpiAllReduce) {
-                const size_t slot =
-                    (static_cast<size_t>((call & 1u) * p.world + p.rank) * p.rows_cap + orow) *
-                        p.n_out + n;
-                for (int pr = 0; pr < p.world; ++pr) p.peer_recv[pr][slot] = x;
+                ar_stage[r * 128 + ch_in_tile] = x;     // staged row-major, pushed below in 512-byte rows
               } else if (orow >= 0) {
                 if (p.out_fp32)
                   reinterpret_cast<float*>(p.out)[orow * p.ldo + ocol] = x;
@@ -413,50 +416,76 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tmap_w,
       __syncwarp();
       if (lane == 0) mbar_arrive(&acc_empty[a]);
       if (EPI == kEpiAllReduce) {
-        // Publish this tile: all 128 epilogue threads' peer stores, then one counter
-        // bump per rank (release at system scope).
-        __threadfence_system();
+        // Publish this tile.  The partial sits row-major in shared memory; each epilogue warp pushes whole
+        // rows into every rank's receive slot as tagged pairs (value, call tag): 4 channels per lane = two
+        // 16-byte stores, 1 KB contiguous per warp, row and peer.  No fence and no flag: receivers poll the tags.
         asm volatile("bar.sync 1, 128;" ::: "memory");
-        if (epi_tid < p.world) flag_add_release_sys(p.peer_flags[epi_tid] + t, 1u);
+        {
+          const int n4 = ti.nt * kTileN + lane * 4;
+          const uint32_t tag = call + 1u;
+          if (n4 < p.n_out) {
+            for (int r = warp - 2; r < rows; r += 4) {
+              const float4 val = *reinterpret_cast<const float4*>(ar_stage + r * 128 + lane * 4);
+              const float vals[4] = {val.x, val.y, val.z, val.w};
+              const size_t ch = static_cast<size_t>(row0 + r) * p.n_out + n4;
+              for (int pr = 0; pr < p.world; ++pr)
+                ll_push4(reinterpret_cast<uint8_t*>(p.peer_recv[pr]) + ar_parity_off + p.rank * ar_slot_bytes, ch,
+                         vals, tag, p.ar_bf16 != 0);
+            }
+          }
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");    // the staging tile may be overwritten by the next tile
+        if (tracing && epi_tid == 0) p.trace[7] = globaltimer_ns();   // partial tile pushed
       }
       a ^= 1;
       if (a == 0) aph ^= 1u;
     }
     if (EPI == kEpiAllReduce && leader) {
-      // Second pass over this CTA's tiles: wait for all ranks' partials, sum in rank
-      // order (identical on every rank), add the residual, write the result.
-      uint32_t* seen = p.local_ctr + 2;   // arrivals already consumed, per tile (private to this rank)
-      volatile uint32_t* ar_ok = abort_flag + 1;
-      for (int t = tile_first; t < total; t += tile_stride) {
+      // Second pass over this CTA's tiles: every lane polls the tagged pairs of its 4 channels from all
+      // ranks' slots (arrival = tag of this call), sums in rank order (identical on every rank), adds the
+      // residual, writes bf16.  Loads of all ranks are in flight together; nothing is stored in between.
+      const uint32_t tag = call + 1u;
+      bool waited = false;
+      const uint64_t w0 = globaltimer_ns();
+      for (int t = tile_first; t < total && ok; t += tile_stride) {
         const int m = t / p.n_tiles, nt = t - m * p.n_tiles;
         const int row0 = m * NTOK;
         const int rows = min(NTOK, p.dense_rows - row0);
-        const int n = nt * kTileN + ch_in_tile;
-        if (epi_tid == 0) {
-          const uint32_t target = seen[t] + static_cast<uint32_t>(p.world);
-          const bool arrived =
-              ok && flag_wait_ge(p.peer_flags[p.rank] + t, target, p.peer_wait_ns, p.status, 0x400 + t);
-          seen[t] = target;
-          *ar_ok = arrived ? 1u : 0u;
-        }
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        if (*ar_ok == 0u) ok = false;
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        if (ok && n < p.n_out) {
-          const float* base = p.peer_recv[p.rank];
-          for (int r = 0; r < rows; ++r) {
-            const long long orow = row0 + r;
-            float acc = 0.f;
-            for (int src = 0; src < p.world; ++src)
-              acc += base[(static_cast<size_t>((call & 1u) * p.world + src) * p.rows_cap + orow) *
-                              p.n_out + n];
-            if (p.residual) acc += __bfloat162float(p.residual[orow * p.ldr + n]);
-            if (p.out_fp32)
-              reinterpret_cast<float*>(p.out)[orow * p.ldo + n] = acc;
-            else
-              reinterpret_cast<__nv_bfloat16*>(p.out)[orow * p.ldo + n] = __float2bfloat16_rn(acc);
+        const int n4 = nt * kTileN + lane * 4;
+        if (n4 >= p.n_out) continue;
+        for (int r = warp - 2; r < rows && ok; r += 4) {
+          const long long orow = row0 + r;
+          float acc[4] = {0.f, 0.f, 0.f, 0.f};
+          int bad_src = 0;
+          if (!ll_gather4(reinterpret_cast<const uint8_t*>(p.peer_recv[p.rank]) + ar_parity_off,
+                          static_cast<size_t>(orow) * p.n_out + n4, ar_slot_bytes, p.world, tag, p.peer_wait_ns, acc,
+                          bad_src, p.ar_bf16 != 0)) {
+            report_status(p.status, kStatusPeerTimeout, 0x400 + bad_src, static_cast<uint32_t>(t), tag);
+            ok = false;
+          }
+          waited = true;
+          if (!ok) break;
+          if (p.residual) {
+            const uint2 rv = *reinterpret_cast<const uint2*>(p.residual + orow * p.ldr + n4);
+            const __nv_bfloat16* rb = reinterpret_cast<const __nv_bfloat16*>(&rv);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) acc[j] += __bfloat162float(rb[j]);
+          }
+          if (p.out_fp32) {
+            *reinterpret_cast<float4*>(reinterpret_cast<float*>(p.out) + orow * p.ldo + n4) =
+                make_float4(acc[0], acc[1], acc[2], acc[3]);
+          } else {
+            __nv_bfloat16 ob[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) ob[j] = __float2bfloat16_rn(acc[j]);
+            *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(p.out) + orow * p.ldo + n4) =
+                *reinterpret_cast<const uint2*>(ob);
           }
         }
+      }
+      if (waited && epi_tid == 0 && p.status != nullptr) {
+        atomicAdd(reinterpret_cast<unsigned long long*>(p.status) + 2, globaltimer_ns() - w0);
+        atomicAdd(reinterpret_cast<unsigned int*>(p.status) + 6, 1u);
       }
     }
   }
@@ -474,7 +503,8 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tmap_w,
     if (done == gridDim.x - 1) {
       p.local_ctr[1] = 0;
       __threadfence();
-      p.local_ctr[0] = call + 1u;
+      // every CTA of this launch has read the call number already; this thread (the TMA producer) never did
+      p.local_ctr[0] = *reinterpret_cast<volatile uint32_t*>(p.local_ctr) + 1u;
     }
   }
   if (EPI == kEpiScatter && p.remap_rank != nullptr) {
@@ -576,7 +606,9 @@ static int launch_cfg(const CUtensorMap& mw, const CUtensorMap& mx, GemmParams p
   const int kblocks = (p.k + kBlockK - 1) / kBlockK;
   const int split = p.force_split > 0 ? p.force_split
                                       : pick_split(max_tiles, kblocks, grouped, Cfg::kAccCols, Cfg::kStageBytes);
-  const int red_bytes = split > 1 ? (split - 1) * Cfg::kAccCols * 128 * 4 : 0;
+  // the all-reduce epilogue stages one [NTOK x 128] fp32 tile behind the split-K reduction area
+  const int red_bytes = (split > 1 ? (split - 1) * Cfg::kAccCols * 128 * 4 : 0) +
+                        (EPI == kEpiAllReduce ? NTOK * 128 * 4 : 0);
   int stages = (kSmemLimit - 2048 - red_bytes) / Cfg::kStageBytes;
   if (stages > Cfg::kStages) stages = Cfg::kStages;
   if (stages < 2 || (split > 1 && (max_tiles * split > num_sms() || kblocks < split))) return FB_ERR_SHAPE;
@@ -676,7 +708,7 @@ extern "C" int fb_gemm_bf16(const FbGemmArgs* a, void* stream_) {
 
   if (a->epilogue == kEpiAllReduce) {
     if (grouped || a->world < 1 || a->world > 8 || a->rank < 0 || a->rank >= a->world ||
-        a->x_rows > a->rows_cap || a->local_ctr == nullptr)
+        a->x_rows > a->rows_cap || a->local_ctr == nullptr || a->n_out % 4 != 0)
       return FB_ERR_SHAPE;
     if (max_tiles > a->flag_capacity) return FB_ERR_SHAPE;
     // Every tile's owner CTA waits for its peers' copy of the same tile: all of them
@@ -692,6 +724,7 @@ extern "C" int fb_gemm_bf16(const FbGemmArgs* a, void* stream_) {
     p.local_ctr = static_cast<uint32_t*>(a->local_ctr);
     p.residual = static_cast<const __nv_bfloat16*>(a->residual);
     p.ldr = a->ldr;
+    p.ar_bf16 = a->ar_payload_bf16;
     p.peer_wait_ns = a->peer_wait_ns ? a->peer_wait_ns : 3000000000ull;
     return launch_ntok<false, kEpiAllReduce>(ntok, mw, mx, p, max_tiles, grouped, stream);
   }

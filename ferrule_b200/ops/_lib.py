@@ -50,6 +50,7 @@ class GemmArgs(C.Structure):
         ("peer_recv", C.c_void_p * 8), ("peer_flags", C.c_void_p * 8),
         ("local_ctr", C.c_void_p), ("residual", C.c_void_p), ("ldr", C.c_longlong),
         ("peer_wait_ns", C.c_ulonglong), ("status", C.c_void_p), ("trace", C.c_void_p),
+        ("ar_payload_bf16", C.c_int),
         ("remap_rank", C.c_void_p), ("remap_row", C.c_void_p),
     ]
 
@@ -169,7 +170,8 @@ def status_tensor(device=None) -> torch.Tensor:
         dev = torch.device("cuda", torch.cuda.current_device())
     t = _status.get(dev)
     if t is None:
-        t = torch.zeros(4, dtype=torch.int32, device=dev)
+        # words 0..3: status {code, site, detail0, detail1}; 4..5: ns spent waiting on peer flags; 6: waits that spun
+        t = torch.zeros(8, dtype=torch.int32, device=dev)
         _status[dev] = t
     return t
 
@@ -177,10 +179,19 @@ def status_tensor(device=None) -> torch.Tensor:
 def read_status(device=None, reset: bool = True):
     """Synchronising read of the status word -> (code, where, d0, d1)."""
     t = status_tensor(device)
-    vals = [int(v) & 0xFFFFFFFF for v in t.tolist()]
+    vals = [int(v) & 0xFFFFFFFF for v in t[:4].tolist()]
     if reset and vals[0] != 0:
-        t.zero_()
+        t[:4].zero_()
     return tuple(vals)
+
+
+def read_peer_wait(device=None, reset: bool = True):
+    """(nanoseconds kernels of this device spent spinning on peer flags, number of such waits) since the last reset."""
+    t = status_tensor(device)
+    w = [int(v) & 0xFFFFFFFF for v in t[4:7].tolist()]
+    if reset:
+        t[4:7].zero_()
+    return (w[1] << 32) | w[0], w[2]
 
 
 def raise_on_status(device=None) -> None:

@@ -27,6 +27,7 @@ def declare(lib) -> None:
                                      C.POINTER(vp), vp, i, ull, vp, vp], i),
         "fb_argmax_allgather": ([vp, vp, i, i, i, i, i, C.POINTER(vp), C.POINTER(vp), vp, ull, vp, vp], i),
         "fb_flag_wait_probe": ([vp, i, ull, vp, vp, vp], i),
+        "fb_peer_pingpong": ([vp, vp, i, i, ull, vp, vp, vp], i),
         # elementwise.cu (fused variants)
         "fb_router_plan_fused": ([vp, ll, vp, i, vp, vp, vp, i, i, i, i, i, i, i, f, vp, vp, i, i, i, i,
                                   vp, vp, vp, vp, vp, vp, i, vp, vp, vp, vp, vp], i),

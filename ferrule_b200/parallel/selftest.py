@@ -39,10 +39,40 @@ def _time_ms(fn, iters: int, world: int) -> float:
     return float(t)
 
 
+def _graph_time_us(fn, world: int, per_graph: int = 20, reps: int = 20) -> float:
+    """Per-call time with `per_graph` calls captured in one CUDA graph (no host launch overhead), max over ranks.
+    Only for fused (peer-memory) paths: NCCL collectives are not captured here."""
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for _ in range(3):
+            fn()
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    dist.barrier()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        for _ in range(per_graph):
+            fn()
+    g.replay()
+    torch.cuda.synchronize()
+    dist.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        g.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    t = torch.tensor([e0.elapsed_time(e1) / (per_graph * reps) * 1e3], device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t)
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--bench", action="store_true")
     ap.add_argument("--rows", type=int, default=32)
+    ap.add_argument("--payload", default="fp32", choices=["fp32", "bf16"])
     args = ap.parse_args()
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     local = int(os.environ.get("LOCAL_RANK", rank))
@@ -63,7 +93,7 @@ def main() -> int:
     H = cfg.hidden
     w_tp = W.random_weights(cfg, device=dev, seed=3, std=0.05, tp_rank=rank, tp_world=world)
     pool = D.KvPool(cfg, 32, 64, dev)
-    tp = TensorParallel(rank, world, dev, fused=True)
+    tp = TensorParallel(rank, world, dev, fused=True, payload=args.payload)
     fwd = D.CudaForward(w_tp, pool, max_rows=256, max_logit_rows=8, decode_rows=64, max_seq_len=512, attn_splits=2, tp=tp)
     tp.attach(fwd)
     tp_nccl = TensorParallel(rank, world, dev, fused=False)
@@ -87,7 +117,7 @@ def main() -> int:
         worst = max(worst, float((out_f.float() - out_n.float()).abs().max()))
         scale = float(out_n.float().abs().max())
     res["checks"]["gemm_allreduce_max_err"] = worst
-    ok &= worst <= 0.02 * scale + 1e-2
+    ok &= worst <= (0.03 if args.payload == "bf16" else 0.02) * scale + 1e-2
 
     # 2. MoE reduce + all-reduce
     slots, topk = 5, 4
@@ -170,7 +200,7 @@ def main() -> int:
 
     if args.bench:
         Hb, Tb = 2048, 32
-        tpb = TensorParallel(rank, world, dev, fused=True)
+        tpb = TensorParallel(rank, world, dev, fused=True, payload=args.payload)
 
         class _F:  # minimal stand-in carrying the sizes attach() needs
             pass
@@ -195,6 +225,15 @@ def main() -> int:
         res["bench"]["moe_allreduce_nccl_us"] = 1e3 * _time_ms(
             lambda: tpn.moe_reduce_allreduce(ro, 7, 6, idx, 0, 64 // world, resid, o, Tb), 200, world)
         res["bench"]["payload_bytes"] = Tb * Hb * 4
+        # the same fused calls inside a CUDA graph (what a decode step sees), and their single-GPU counterparts
+        from ferrule_b200.ops import kernels as K
+        res["bench"]["gemm_allreduce_fused_graph_us"] = _graph_time_us(lambda: tpb.gemm_allreduce(x, wt, resid, o, Tb), world)
+        res["bench"]["moe_allreduce_fused_graph_us"] = _graph_time_us(
+            lambda: tpb.moe_reduce_allreduce(ro, 7, 6, idx, 0, 64 // world, resid, o, Tb), world)
+        dl = torch.zeros(Tb, Hb, dtype=torch.bfloat16, device=dev)
+        res["bench"]["gemm_local_graph_us"] = _graph_time_us(lambda: K.gemm(x, wt, out=dl), world)
+        res["bench"]["moe_reduce_local_graph_us"] = _graph_time_us(
+            lambda: K.moe_reduce(ro, 7, 6, idx, 0, 64 // world, Tb, Hb, residual=resid, out=o), world)
 
     status = _lib.read_status()
     res["device_status"] = list(status)

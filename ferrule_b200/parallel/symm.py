@@ -73,7 +73,8 @@ class Channel:
         self.rank, self.world, self.wait_ns = rank, world, wait_ns
         self.payload_floats, self.n_flags = payload_floats, n_flags
         self.flag_bytes = ((n_flags * 4 + 255) // 256) * 256
-        recv_bytes = 2 * world * payload_floats * 4
+        # every fp32 travels as an 8-byte (value, tag) pair; two parities; one slot per source rank
+        recv_bytes = 2 * world * payload_floats * 8
         self.buf = SymmetricBuffer(self.flag_bytes + recv_bytes, rank, world, group)
         self.flags = self.buf.ptr_array(0)
         self.recv = self.buf.ptr_array(self.flag_bytes)

@@ -32,10 +32,14 @@ from .symm import Channel
 
 class TensorParallel:
     def __init__(self, rank: int, world: int, device, fused: bool = True, fused_max_rows: int = 64,
-                 group=None, wait_ns: int = 3_000_000_000):
+                 group=None, wait_ns: int = 3_000_000_000, payload: str = "fp32"):
         self.rank, self.world, self.device, self.group = rank, world, torch.device(device), group
         self.fused = fused and self.device.type == "cuda"
         self.fused_max_rows = fused_max_rows
+        # what the fused all-reduces push over NVLink: fp32 partials (as exact as an fp32 all-reduce) or bf16
+        # partials (half the bytes; each rank's partial is rounded to bf16 before the fixed-order sum)
+        assert payload in ("fp32", "bf16")
+        self.payload_bf16 = 1 if payload == "bf16" else 0
         self.wait_ns = wait_ns
         self.gemm_ch: Optional[Channel] = None
         self.moe_ch: Optional[Channel] = None
@@ -75,6 +79,7 @@ class TensorParallel:
             a.peer_flags[r] = ch.flags[r]
         a.local_ctr = ch.ctr.data_ptr()
         a.peer_wait_ns = self.wait_ns
+        a.ar_payload_bf16 = self.payload_bf16
 
     # ------------------------------------------------------------------ fused collectives
     def gemm_allreduce(self, x: torch.Tensor, w: torch.Tensor, residual: torch.Tensor, out: torch.Tensor,
@@ -101,7 +106,7 @@ class TensorParallel:
             check(lib.fb_moe_reduce_allreduce(route_out.data_ptr(), slots, topk, idx.data_ptr(), e_lo, e_hi,
                                               residual.data_ptr(), residual.stride(0), out.data_ptr(),
                                               out.stride(0), T, H, self.rank, self.world, self.fused_max_rows,
-                                              ch.recv, ch.flags, ch.ctr.data_ptr(), ch.n_flags, self.wait_ns,
+                                              ch.recv, ch.flags, ch.ctr.data_ptr(), self.payload_bf16, self.wait_ns,
                                               status_tensor(self.device).data_ptr(), stream_ptr()),
                   "fb_moe_reduce_allreduce")
             self.calls_fused += 1
