@@ -500,17 +500,32 @@ router_plan_fused_kernel(const __nv_bfloat16* __restrict__ x, long long ldx,
     for (int j = 0; j < 8; ++j) xs[i + j] = __bfloat162float(vp[j]);
   }
   __syncthreads();
-  for (int e = warp; e < experts; e += nwarps) {
+  // two experts per warp pass and four 16-byte loads per expert in flight: the weight rows come from L2 and
+  // a serial chain of dependent-looking loads is what this phase would otherwise wait on
+  for (int e = warp; e < experts; e += 2 * nwarps) {
+    const int e2 = e + nwarps;
+    const bool two = e2 < experts;
     const __nv_bfloat16* wr = w + static_cast<size_t>(e) * hidden;
-    float acc = 0.f;
+    const __nv_bfloat16* wr2 = w + static_cast<size_t>(two ? e2 : e) * hidden;
+    float acc = 0.f, acc2 = 0.f;
+#pragma unroll 4
     for (int i = lane * 8; i < hidden; i += 256) {
       const uint4 v = *reinterpret_cast<const uint4*>(wr + i);
+      const uint4 v2 = *reinterpret_cast<const uint4*>(wr2 + i);
       const __nv_bfloat16* vp = reinterpret_cast<const __nv_bfloat16*>(&v);
+      const __nv_bfloat16* vp2 = reinterpret_cast<const __nv_bfloat16*>(&v2);
 #pragma unroll
-      for (int j = 0; j < 8; ++j) acc = fmaf(__bfloat162float(vp[j]), xs[i + j], acc);
+      for (int j = 0; j < 8; ++j) {
+        acc = fmaf(__bfloat162float(vp[j]), xs[i + j], acc);
+        acc2 = fmaf(__bfloat162float(vp2[j]), xs[i + j], acc2);
+      }
     }
     acc = warp_sum(acc);
-    if (lane == 0) logits[e] = acc;
+    acc2 = warp_sum(acc2);
+    if (lane == 0) {
+      logits[e] = acc;
+      if (two) logits[e2] = acc2;
+    }
   }
   __syncthreads();
   if (warp == 0)
@@ -528,6 +543,19 @@ router_plan_fused_kernel(const __nv_bfloat16* __restrict__ x, long long ldx,
   if (!is_last) return;
   __threadfence();
   moe_plan_body(out_idx, out_w, rows * topk, topk, e_lo, e_hi, ntok, dst_slots, o, st);
+}
+
+// Asynchronous L2 prefetch of a byte range (weights that a later kernel will stream): every thread issues
+// bulk prefetch requests of 8 KB; nothing is written and nothing waits.
+__global__ void __launch_bounds__(128)
+l2_prefetch_kernel(const uint8_t* __restrict__ base, long long bytes) {
+  constexpr long long kChunk = 8192;
+  const long long n = (bytes + kChunk - 1) / kChunk;
+  for (long long c = blockIdx.x * blockDim.x + threadIdx.x; c < n; c += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long off = c * kChunk;
+    const unsigned int sz = static_cast<unsigned int>(min(kChunk, bytes - off) & ~15ll);
+    if (sz) asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(base + off), "r"(sz) : "memory");
+  }
 }
 
 __global__ void gather_rows_kernel(const __nv_bfloat16* __restrict__ x, long long ldx,
@@ -888,6 +916,12 @@ extern "C" int fb_router_plan_fused(const void* x, long long ldx, const void* w,
       hash_table, token_ids, rows, experts, topk, score_fn, n_groups, topk_groups, normalize, route_scale,
       out_idx, out_w, e_lo, e_hi, ntok, dst_slots < topk ? topk : dst_slots, o,
       static_cast<unsigned int*>(done_ctr), static_cast<DeviceStatus*>(status));
+  return FB_CHECK_LAUNCH();
+}
+
+extern "C" int fb_l2_prefetch(const void* ptr, long long bytes, void* stream) {
+  if (!ptr || bytes <= 0 || (reinterpret_cast<uintptr_t>(ptr) & 15)) return FB_ERR_SHAPE;
+  l2_prefetch_kernel<<<8, 128, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const uint8_t*>(ptr), bytes);
   return FB_CHECK_LAUNCH();
 }
 

@@ -171,6 +171,8 @@ int fb_router_plan_fused(const void* x, long long ldx, const void* w, int hidden
                          int dst_slots, int* src_token, int* dst_row, float* row_scale, int* tile_group,
                          int* tile_row0, int* tile_rows, int max_tiles, int* counts, int* meta,
                          void* done_ctr, void* status, void* stream);
+// asynchronous L2 prefetch of [ptr, ptr + bytes) (ptr 16-byte aligned)
+int fb_l2_prefetch(const void* ptr, long long bytes, void* stream);
 int fb_gather_rows(const void* x, long long ldx, const int* src_token, const int* meta, void* out,
                    long long ldo, int cap_rows, int dim, int src_rows, void* status, void* stream);
 int fb_moe_reduce(const void* route_out, int slots, int topk, const int* topk_idx, int e_lo,
@@ -220,6 +222,9 @@ int fb_markov_step(const float* logits, const void* w1, const void* w2, int voca
 // taps[t][tap_off : +hidden] = bf16(mean over the hc copies of state[t])
 int fb_hc_mean_scatter(const void* state, void* taps, long long ld_taps, int tap_off, int tokens, int hc, int hidden,
                        void* stream);
+// head reduction over GEMM-produced dots bf16 [queries * heads, n] (pitch ld): same score chain as fb_indexer_scores
+int fb_indexer_reduce(const void* dots, long long ld, const float* head_w, float* scores, long long ld_s, int queries,
+                      int heads, int n, void* stream);
 // n_visible (per query) may be NULL, then n_fixed applies; k <= 512
 int fb_indexer_topk(const float* scores, long long ld_s, const int* n_visible, int n_fixed, int k, int* out_idx,
                     long long ldo, int queries, void* stream);

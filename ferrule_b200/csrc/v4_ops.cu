@@ -295,6 +295,37 @@ indexer_scores_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* 
   }
 }
 
+// Head reduction of the indexer when the per-head dots come from the tensor-core GEMM
+// (dots bf16 [queries * heads, n] = q . plane^T, already rounded to bf16 by the GEMM epilogue):
+// score[q][n] = bf16(sum_h bf16(relu(dots[q*heads + h][n]) * bf16(w[q][h]))), heads summed in index order.
+__global__ void __launch_bounds__(256)
+indexer_reduce_kernel(const __nv_bfloat16* __restrict__ dots, long long ld, const float* __restrict__ head_w,
+                      float* __restrict__ scores, long long ld_s, int heads, int n) {
+  pdl_launch_dependents();
+  pdl_wait();
+  extern __shared__ float w_s[];           // [heads] bf16-rounded weights of this query
+  const int qi = blockIdx.y;
+  for (int h = threadIdx.x; h < heads; h += blockDim.x) w_s[h] = bf16r(head_w[static_cast<size_t>(qi) * heads + h]);
+  __syncthreads();
+  const int c = (blockIdx.x * blockDim.x + threadIdx.x) * 2;
+  if (c >= n) return;
+  const __nv_bfloat16* col = dots + static_cast<size_t>(qi) * heads * ld + c;
+  float s0 = 0.f, s1 = 0.f;
+  if (c + 1 < n) {
+#pragma unroll 8
+    for (int h = 0; h < heads; ++h) {
+      const float2 d = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(col + h * ld));
+      s0 += bf16r(fmaxf(d.x, 0.f) * w_s[h]);
+      s1 += bf16r(fmaxf(d.y, 0.f) * w_s[h]);
+    }
+    scores[qi * ld_s + c] = bf16r(s0);
+    scores[qi * ld_s + c + 1] = bf16r(s1);
+  } else {
+    for (int h = 0; h < heads; ++h) s0 += bf16r(fmaxf(__bfloat162float(col[h * ld]), 0.f) * w_s[h]);
+    scores[qi * ld_s + c] = bf16r(s0);
+  }
+}
+
 // ---------------------------------------------------------------------------------
 // Stable top-k of one score row per CTA (1024 threads).  Scores hold bf16 values, so the 16-bit
 // orderable key decides; ties go to the lower row id.  Non-finite scores never win.
@@ -618,5 +649,13 @@ extern "C" int fb_hc_mean_scatter(const void* state, void* taps, long long ld_ta
   launch_pdl(hc_mean_scatter_kernel, dim3(tokens), dim3(256), 0, static_cast<cudaStream_t>(stream),
              static_cast<const __nv_bfloat16*>(state), static_cast<__nv_bfloat16*>(taps), ld_taps, tap_off, tokens, hc,
              hidden);
+  return FB_CHECK_LAUNCH();
+}
+
+extern "C" int fb_indexer_reduce(const void* dots, long long ld, const float* head_w, float* scores, long long ld_s,
+                                 int queries, int heads, int n, void* stream) {
+  if (queries <= 0 || heads <= 0 || heads > 4096 || n <= 0 || ld % 2 != 0 || queries > 65535) return FB_ERR_SHAPE;
+  launch_pdl(indexer_reduce_kernel, dim3((n + 511) / 512, queries), dim3(256), heads * sizeof(float),
+             static_cast<cudaStream_t>(stream), static_cast<const __nv_bfloat16*>(dots), ld, head_w, scores, ld_s, heads, n);
   return FB_CHECK_LAUNCH();
 }

@@ -342,6 +342,10 @@ class CudaForward:
         self.fused_router_rows = 256
         self.side_stream = torch.cuda.Stream(device=dev)      # shared experts run beside the routed path
         self.arena = None          # models.expert_arena.ExpertArena when routed experts are streamed
+        # bytes of each MoE layer's routed-expert weights to prefetch into L2 during the attention half of a decode
+        # layer (0 = off); the L2 holds 126 MB, the prefetch must leave room for the attention's own traffic
+        import os
+        self.l2_prefetch_bytes = int(float(os.environ.get("FERRULE_L2_PREFETCH_MB", "0")) * (1 << 20))
         self.telemetry = None      # utils.telemetry.ExpertTelemetry fed by the streamed path
 
     # -- sublayers -----------------------------------------------------------------------
@@ -483,6 +487,16 @@ class CudaForward:
         """h_in -> h_out (both bf16 [T, H]); returns h_out."""
         K, cfg, ws, tp = self.K, self.cfg, self.ws, self.tp
         xn = ws.xn[:T]
+        if self.l2_prefetch_bytes and lw.is_moe and isinstance(lw.e_w13, torch.Tensor) and T <= ws.decode_rows:
+            # Decode: the attention half of the layer is latency-bound and leaves HBM idle, and nearly every routed
+            # expert will be read a few tens of microseconds from now.  Pull the head of the expert weights into
+            # L2 meanwhile (side stream: a parallel branch of the graph), so the grouped GEMM starts on L2 hits.
+            side, main = self.side_stream, torch.cuda.current_stream()
+            side.wait_stream(main)
+            with torch.cuda.stream(side):
+                K.l2_prefetch(lw.e_w13, self.l2_prefetch_bytes)
+            if lw.w13 is None:                      # no shared-expert branch will join the side stream later
+                main.wait_stream(side)
         K.add_rmsnorm(h_in, lw.attn_norm, cfg.rms_eps, norm_out=xn)
         a = self._attention(lw, layer, xn, b, T)
         if tp is None:

@@ -32,6 +32,7 @@ def declare(lib) -> None:
         "fb_router_plan_fused": ([vp, ll, vp, i, vp, vp, vp, i, i, i, i, i, i, i, f, vp, vp, i, i, i, i,
                                   vp, vp, vp, vp, vp, vp, i, vp, vp, vp, vp, vp], i),
         "fb_argmax_chunked": ([vp, ll, i, i, i, vp, vp, vp, vp, vp, vp], i),
+        "fb_l2_prefetch": ([vp, ll, vp], i),
         # quant.cu
         "fb_quant_fp8_rows": ([vp, ll, vp, ll, vp, ll, i, i, i, vp], i),
         "fb_dequant_fp8_block": ([vp, vp, vp, i, i, i, vp], i),
@@ -48,6 +49,7 @@ def declare(lib) -> None:
         "fb_rope_rows": ([vp, ll, ll, i, i, i, i, vp, vp, vp, i, i, vp, vp], i),
         "fb_indexer_scores": ([vp, vp, ll, vp, vp, ll, i, i, i, i, vp], i),
         "fb_indexer_topk": ([vp, ll, vp, i, i, vp, ll, i, vp], i),
+        "fb_indexer_reduce": ([vp, ll, vp, vp, ll, i, i, i, vp], i),
         "fb_markov_step": ([vp, vp, vp, i, i, i, vp, vp, vp, vp, vp, vp, vp, vp], i),
         "fb_hc_mean_scatter": ([vp, vp, ll, i, i, i, i, vp], i),
     }

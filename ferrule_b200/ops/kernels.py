@@ -213,6 +213,13 @@ def moe_plan(topk_idx: torch.Tensor, topk_w: Optional[torch.Tensor], plan: MoePl
     return plan
 
 
+def l2_prefetch(t: torch.Tensor, nbytes: int) -> None:
+    """Ask the memory system to pull the first `nbytes` of `t` into L2 (asynchronous, on the current stream)."""
+    lib = get_lib(True)
+    nbytes = min(nbytes, t.numel() * t.element_size())
+    check(lib.fb_l2_prefetch(t.data_ptr(), nbytes, stream_ptr()), "fb_l2_prefetch")
+
+
 def gather_rows(x: torch.Tensor, plan: MoePlan, out: torch.Tensor, cap_rows: Optional[int] = None) -> torch.Tensor:
     lib = get_lib(True)
     cap = plan.cap_rows if cap_rows is None else cap_rows

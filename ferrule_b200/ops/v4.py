@@ -74,8 +74,14 @@ def rope_rows(x: torch.Tensor, positions: torch.Tensor, cos: torch.Tensor, sin: 
 
 
 def indexer_scores(q: torch.Tensor, plane: torch.Tensor, head_w: torch.Tensor,
-                   out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """q bf16 [queries, heads, d]; plane bf16 [n, d]; head_w fp32 [queries, heads] -> fp32 [queries, n]."""
+                   out: Optional[torch.Tensor] = None, use_gemm: Optional[bool] = None,
+                   scratch: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """q bf16 [queries, heads, d]; plane bf16 [n, d]; head_w fp32 [queries, heads] -> fp32 [queries, n].
+
+    Two paths with the same rounding chain: for a large plane the per-head dots are one tcgen05 GEMM
+    ([queries * heads, d] x plane^T -> bf16) followed by the head-reduction kernel; small planes use the SIMT
+    kernel that keeps the query heads in shared memory.  `scratch` (bf16 [queries * heads, >= n]) avoids the
+    allocation of the GEMM path."""
     lib = get_lib(True)
     Q, H, d = q.shape
     n = plane.shape[0]
@@ -83,6 +89,16 @@ def indexer_scores(q: torch.Tensor, plane: torch.Tensor, head_w: torch.Tensor,
     assert head_w.dtype == torch.float32 and head_w.shape == (Q, H) and head_w.is_contiguous()
     if out is None:
         out = torch.empty(Q, n, dtype=torch.float32, device=q.device)
+    if use_gemm is None:
+        use_gemm = n >= 1024 and d % 8 == 0 and plane.stride(0) % 8 == 0
+    if use_gemm:
+        from . import kernels as K
+        np2 = (n + 7) // 8 * 8
+        dots = scratch[:Q * H, :np2] if scratch is not None else torch.empty(Q * H, np2, dtype=torch.bfloat16, device=q.device)
+        K.gemm(q.view(Q * H, d), plane, out=dots, n_out=n)
+        check(lib.fb_indexer_reduce(dots.data_ptr(), dots.stride(0), head_w.data_ptr(), out.data_ptr(), out.stride(0),
+                                    Q, H, n, stream_ptr()), "fb_indexer_reduce")
+        return out
     check(lib.fb_indexer_scores(q.data_ptr(), plane.data_ptr(), plane.stride(0), head_w.data_ptr(), out.data_ptr(),
                                 out.stride(0), Q, H, d, n, stream_ptr()), "fb_indexer_scores")
     return out

@@ -68,14 +68,15 @@ def test_rope_rows_forward_then_inverse_is_identity():
     assert torch.allclose(y.float(), x.float(), atol=3e-2, rtol=2e-2)
 
 
-def test_indexer_scores_and_topk_match_reference():
+@pytest.mark.parametrize("use_gemm", [False, True])
+def test_indexer_scores_and_topk_match_reference(use_gemm):
     from ferrule_b200.ops import v4 as K
     torch.manual_seed(3)
     Q, H, d, n, k = 3, 64, 128, 3000, 512
     q = torch.randn(Q, H, d, device=DEV).bfloat16()
     plane = torch.randn(n, d, device=DEV).bfloat16()
     w = torch.randn(Q, H, device=DEV)
-    scores = K.indexer_scores(q, plane, w)
+    scores = K.indexer_scores(q, plane, w, use_gemm=use_gemm)       # SIMT kernel / tcgen05 GEMM + head reduction
     vis = torch.tensor([n, 700, 100], dtype=torch.int32, device=DEV)
     idx = K.indexer_topk(scores, k, vis)
     torch.cuda.synchronize()
