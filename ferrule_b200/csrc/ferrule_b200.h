@@ -204,6 +204,11 @@ int fb_hadamard_rows(void* x, long long ldx, int rows, int n, void* stream);
 int fb_hc_pre(const void* state, const float* fn, const float* scale, const float* base, void* hidden_out,
               int out_fp32, float* coeff, int tokens, int hc, int hidden, int nmix, float eps, float norm_eps,
               int sinkhorn_iters, void* stream);
+// same result with the hc * hidden reduction split over `chunks` CTAs per token (part: tokens * chunks * 32 floats,
+// ctr: zeroed uint32 [tokens])
+int fb_hc_pre_split(const void* state, const float* fn, const float* scale, const float* base, void* hidden_out,
+                    int out_fp32, float* coeff, int tokens, int hc, int hidden, int nmix, float eps, float norm_eps,
+                    int sinkhorn_iters, int chunks, float* part, void* ctr, void* stream);
 int fb_hc_post(const void* hidden_in, const void* residual, const float* coeff, void* out, int tokens, int hc,
                int hidden, void* stream);
 // group g pools rows row0 + g * ratio + [0, window); rows outside [0, n_rows) are masked; kv / gate rows have

@@ -136,6 +136,134 @@ hc_pre_kernel(const __nv_bfloat16* __restrict__ state, const float* __restrict__
   }
 }
 
+// Split variant for large hc * hidden: grid (tokens, chunks).  Every CTA reduces one chunk of the hc * hidden
+// axis (partial dot products with the mixing rows + partial sum of squares) into scratch; the CTA that
+// finishes last for a token adds the partials in chunk order, runs the split / Sinkhorn step and forms the
+// weighted sum.  scratch: part [tokens][chunks][32] floats, ctr [tokens] zeroed once.
+template <int HC>
+__global__ void __launch_bounds__(256)
+hc_pre_split_kernel(const __nv_bfloat16* __restrict__ state, const float* __restrict__ fn,
+                    const float* __restrict__ scale, const float* __restrict__ base, void* __restrict__ hidden_out,
+                    int out_fp32, float* __restrict__ coeff, int tokens, int hidden, int nmix, float eps,
+                    float norm_eps, int sinkhorn_iters, float* __restrict__ part, unsigned int* __restrict__ ctr) {
+  pdl_launch_dependents();
+  pdl_wait();
+  __shared__ float red[8][kHcMaxMix + 1];
+  __shared__ float mix[kHcMaxMix + 1];
+  __shared__ float pre_s[HC];
+  __shared__ int is_last;
+  const int t = blockIdx.x, c = blockIdx.y, chunks = gridDim.y;
+  const int n = HC * hidden;
+  const int per = ((n + chunks - 1) / chunks + 3) / 4 * 4;
+  const int lo = c * per, hi = min(n, lo + per);
+  const __nv_bfloat16* x = state + static_cast<size_t>(t) * n;
+  float acc[kHcMaxMix + 1];
+#pragma unroll
+  for (int m = 0; m <= kHcMaxMix; ++m) acc[m] = 0.f;
+  for (int i = lo + threadIdx.x * 4; i < hi; i += blockDim.x * 4) {
+    const uint2 raw = *reinterpret_cast<const uint2*>(x + i);
+    const __nv_bfloat16* v = reinterpret_cast<const __nv_bfloat16*>(&raw);
+    float f[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) f[j] = __bfloat162float(v[j]);
+    acc[kHcMaxMix] += f[0] * f[0] + f[1] * f[1] + f[2] * f[2] + f[3] * f[3];
+#pragma unroll
+    for (int m = 0; m < kHcMaxMix; ++m) {
+      if (m < nmix) {
+        const float4 w = *reinterpret_cast<const float4*>(fn + static_cast<size_t>(m) * n + i);
+        acc[m] += f[0] * w.x + f[1] * w.y + f[2] * w.z + f[3] * w.w;
+      }
+    }
+  }
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+#pragma unroll
+  for (int m = 0; m <= kHcMaxMix; ++m) {
+    const float s = warp_sum(acc[m]);
+    if (lane == 0) red[warp][m] = s;
+  }
+  __syncthreads();
+  float* mine = part + (static_cast<size_t>(t) * chunks + c) * 32;
+  if (threadIdx.x <= kHcMaxMix) {
+    float s = 0.f;
+    for (int w = 0; w < 8; ++w) s += red[w][threadIdx.x];
+    mine[threadIdx.x] = s;
+  }
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned int done = atomicAdd(ctr + t, 1u);
+    is_last = done == static_cast<unsigned int>(chunks - 1);
+    if (is_last) ctr[t] = 0;
+  }
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  if (threadIdx.x <= kHcMaxMix) {
+    float s = 0.f;
+    for (int k = 0; k < chunks; ++k) s += part[(static_cast<size_t>(t) * chunks + k) * 32 + threadIdx.x];
+    mix[threadIdx.x] = s;
+  }
+  __syncthreads();
+  if (warp == 0) {
+    const float rms = rsqrtf(mix[kHcMaxMix] / static_cast<float>(n) + norm_eps);
+    float* out = coeff + static_cast<size_t>(t) * nmix;
+    if (lane < HC) {
+      const float p = sigmoidf_(mix[lane] * rms * scale[0] + base[lane]) + eps;
+      pre_s[lane] = p;
+      out[lane] = p;
+      if (nmix > HC) out[HC + lane] = 2.f * sigmoidf_(mix[HC + lane] * rms * scale[1] + base[HC + lane]);
+    }
+    if (nmix > HC) {
+      const bool on = lane < HC * HC;
+      float cv = on ? mix[2 * HC + lane] * rms * scale[2] + base[2 * HC + lane] : -INFINITY;
+      float mx = cv;
+#pragma unroll
+      for (int o = 1; o < HC; o <<= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+      float e = on ? __expf(cv - mx) : 0.f, s = e;
+#pragma unroll
+      for (int o = 1; o < HC; o <<= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+      cv = on ? e / s + eps : 0.f;
+      for (int it = 0; it < sinkhorn_iters; ++it) {
+        if (it > 0) {
+          float rs = cv;
+#pragma unroll
+          for (int o = 1; o < HC; o <<= 1) rs += __shfl_xor_sync(0xffffffffu, rs, o);
+          cv = cv / (rs + eps);
+        }
+        float cs = cv;
+#pragma unroll
+        for (int o = HC; o < HC * HC; o <<= 1) cs += __shfl_xor_sync(0xffffffffu, cs, o);
+        cv = cv / (cs + eps);
+      }
+      if (on) out[2 * HC + lane] = cv;
+    }
+  }
+  __syncthreads();
+  float p[HC];
+#pragma unroll
+  for (int j = 0; j < HC; ++j) p[j] = pre_s[j];
+  for (int d = threadIdx.x * 4; d < hidden; d += blockDim.x * 4) {
+    float h[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int j = 0; j < HC; ++j) {
+      const uint2 raw = *reinterpret_cast<const uint2*>(x + static_cast<size_t>(j) * hidden + d);
+      const __nv_bfloat16* v = reinterpret_cast<const __nv_bfloat16*>(&raw);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) h[q] += p[j] * __bfloat162float(v[q]);
+    }
+    if (out_fp32) {
+      *reinterpret_cast<float4*>(static_cast<float*>(hidden_out) + static_cast<size_t>(t) * hidden + d) =
+          make_float4(h[0], h[1], h[2], h[3]);
+    } else {
+      __nv_bfloat16 o[4];
+#pragma unroll
+      for (int q = 0; q < 4; ++q) o[q] = __float2bfloat16(h[q]);
+      *reinterpret_cast<uint2*>(static_cast<__nv_bfloat16*>(hidden_out) + static_cast<size_t>(t) * hidden + d) =
+          *reinterpret_cast<const uint2*>(o);
+    }
+  }
+}
+
 // out[t][j][d] = post[j] * hidden[t][d] + sum_i comb[i][j] * residual[t][i][d]; coeff = [pre | post | comb] per token
 template <int HC>
 __global__ void __launch_bounds__(256)
@@ -657,5 +785,27 @@ extern "C" int fb_indexer_reduce(const void* dots, long long ld, const float* he
   if (queries <= 0 || heads <= 0 || heads > 4096 || n <= 0 || ld % 2 != 0 || queries > 65535) return FB_ERR_SHAPE;
   launch_pdl(indexer_reduce_kernel, dim3((n + 511) / 512, queries), dim3(256), heads * sizeof(float),
              static_cast<cudaStream_t>(stream), static_cast<const __nv_bfloat16*>(dots), ld, head_w, scores, ld_s, heads, n);
+  return FB_CHECK_LAUNCH();
+}
+
+// scratch (optional): part = floats [tokens * chunks * 32], ctr = zeroed uint32 [tokens]; with both given and
+// chunks > 1 the reduction over hc * hidden is split over `chunks` CTAs per token
+extern "C" int fb_hc_pre_split(const void* state, const float* fn, const float* scale, const float* base,
+                               void* hidden_out, int out_fp32, float* coeff, int tokens, int hc, int hidden, int nmix,
+                               float eps, float norm_eps, int sinkhorn_iters, int chunks, float* part, void* ctr,
+                               void* stream) {
+  if (tokens <= 0 || hidden % 4 != 0 || (hc != 2 && hc != 4) || chunks < 1 || chunks > 64 || !part || !ctr ||
+      tokens > 65535)
+    return FB_ERR_SHAPE;
+  if (nmix != hc && nmix != 2 * hc + hc * hc) return FB_ERR_SHAPE;
+  auto st = static_cast<cudaStream_t>(stream);
+  auto s = static_cast<const __nv_bfloat16*>(state);
+  auto c = static_cast<unsigned int*>(ctr);
+  if (hc == 4)
+    launch_pdl(hc_pre_split_kernel<4>, dim3(tokens, chunks), dim3(256), 0, st, s, fn, scale, base, hidden_out, out_fp32,
+               coeff, tokens, hidden, nmix, eps, norm_eps, sinkhorn_iters, part, c);
+  else
+    launch_pdl(hc_pre_split_kernel<2>, dim3(tokens, chunks), dim3(256), 0, st, s, fn, scale, base, hidden_out, out_fp32,
+               coeff, tokens, hidden, nmix, eps, norm_eps, sinkhorn_iters, part, c);
   return FB_CHECK_LAUNCH();
 }

@@ -44,6 +44,7 @@ def declare(lib) -> None:
         "fb_expert_table_resolve": ([vp, vp, vp, i, vp, i, vp, vp], i),
         # v4_ops.cu
         "fb_hc_pre": ([vp, vp, vp, vp, vp, i, vp, i, i, i, i, f, f, i, vp], i),
+        "fb_hc_pre_split": ([vp, vp, vp, vp, vp, i, vp, i, i, i, i, f, f, i, i, vp, vp, vp], i),
         "fb_hc_post": ([vp, vp, vp, vp, i, i, i, vp], i),
         "fb_compressor_pool": ([vp, vp, ll, vp, vp, ll, i, i, i, i, i, i, i, vp], i),
         "fb_rope_rows": ([vp, ll, ll, i, i, i, i, vp, vp, vp, i, i, vp, vp], i),

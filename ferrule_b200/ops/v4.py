@@ -21,10 +21,33 @@ def hc_pre(state: torch.Tensor, fn: torch.Tensor, scale: torch.Tensor, base: tor
     assert fn.dtype == torch.float32 and fn.shape == (nmix, hc * hidden) and fn.is_contiguous()
     out = torch.empty(T, hidden, dtype=torch.float32 if out_fp32 else torch.bfloat16, device=state.device)
     coeff = torch.empty(T, nmix, dtype=torch.float32, device=state.device)
+    chunks = 16 if hc * hidden >= 8192 else 1
+    if chunks > 1:
+        part, ctr = _hc_scratch(state.device, T, chunks)
+        check(lib.fb_hc_pre_split(state.data_ptr(), fn.data_ptr(), scale.data_ptr(), base.data_ptr(), out.data_ptr(),
+                                  int(out_fp32), coeff.data_ptr(), T, hc, hidden, nmix, cfg.eps, cfg.norm_eps,
+                                  cfg.sinkhorn_iters, chunks, part.data_ptr(), ctr.data_ptr(), stream_ptr()),
+              "fb_hc_pre_split")
+        return out, coeff
     check(lib.fb_hc_pre(state.data_ptr(), fn.data_ptr(), scale.data_ptr(), base.data_ptr(), out.data_ptr(),
                         int(out_fp32), coeff.data_ptr(), T, hc, hidden, nmix, cfg.eps, cfg.norm_eps,
                         cfg.sinkhorn_iters, stream_ptr()), "fb_hc_pre")
     return out, coeff
+
+
+_HC_SCRATCH = {}
+
+
+def _hc_scratch(device, tokens: int, chunks: int):
+    """Partial-sum scratch + per-token arrival counters of the split hyper-connection reduction (grown on demand)."""
+    key = torch.device(device)
+    cur = _HC_SCRATCH.get(key)
+    if cur is None or cur[0].numel() < tokens * chunks * 32 or cur[1].numel() < tokens:
+        cap = max(tokens, 64)
+        cur = (torch.empty(cap * chunks * 32, dtype=torch.float32, device=device),
+               torch.zeros(cap, dtype=torch.int32, device=device))
+        _HC_SCRATCH[key] = cur
+    return cur
 
 
 def hc_post(hidden: torch.Tensor, residual: torch.Tensor, coeff: torch.Tensor) -> torch.Tensor:
