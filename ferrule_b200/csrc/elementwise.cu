@@ -473,6 +473,105 @@ moe_plan_kernel(const int* __restrict__ topk_idx, const float* __restrict__ topk
   moe_plan_body(topk_idx, topk_w, routes, topk, e_lo, e_hi, ntok, dst_slots, o, st);
 }
 
+// Prefill-sized route lists: one CTA per local expert.  Every CTA counts all experts (cheap, coalesced),
+// derives the row / tile offsets with the same warp scan as above, CTA 0 writes the tile table, and CTA e
+// places expert e's routes in ascending route order with a block-wide ordered scan (1024 routes per step).
+__global__ void __launch_bounds__(1024)
+moe_plan_wide_kernel(const int* __restrict__ topk_idx, const float* __restrict__ topk_w, int routes, int topk,
+                     int e_lo, int e_hi, int ntok, int dst_slots, PlanOut o, DeviceStatus* st) {
+  pdl_launch_dependents();
+  pdl_wait();
+  __shared__ int cnt[256];
+  __shared__ int off[257];
+  __shared__ int warp_tot[32];
+  __shared__ int s_base;
+  const int local = e_hi - e_lo;
+  const int me = blockIdx.x;
+  for (int i = threadIdx.x; i < 256; i += blockDim.x) cnt[i] = 0;
+  __syncthreads();
+  for (int r = threadIdx.x; r < routes; r += blockDim.x) {
+    const int e = topk_idx[r];
+    if (e >= e_lo && e < e_hi) atomicAdd(&cnt[e - e_lo], 1);
+  }
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    const int lane = threadIdx.x;
+    int c[8], rows_sum = 0, tiles_sum = 0;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int e = lane * 8 + j;
+      c[j] = e < local ? cnt[e] : 0;
+      rows_sum += c[j];
+      tiles_sum += (c[j] + ntok - 1) / ntok;
+    }
+    int row_off = rows_sum, tile_off = tiles_sum;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      const int r = __shfl_up_sync(0xffffffffu, row_off, d);
+      const int t = __shfl_up_sync(0xffffffffu, tile_off, d);
+      if (lane >= d) { row_off += r; tile_off += t; }
+    }
+    const int total_rows = __shfl_sync(0xffffffffu, row_off, 31);
+    int total_tiles = __shfl_sync(0xffffffffu, tile_off, 31);
+    row_off -= rows_sum;
+    tile_off -= tiles_sum;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int e = lane * 8 + j;
+      if (e < local) {
+        off[e] = row_off;
+        if (me == 0) {
+          o.counts[e] = c[j];
+          for (int r0 = 0; r0 < c[j]; r0 += ntok) {
+            if (tile_off < o.max_tiles) {
+              o.tile_group[tile_off] = e;
+              o.tile_row0[tile_off] = row_off + r0;
+              o.tile_rows[tile_off] = min(ntok, c[j] - r0);
+            }
+            ++tile_off;
+          }
+        }
+        row_off += c[j];
+      }
+    }
+    if (lane == 0 && me == 0) {
+      if (total_tiles > o.max_tiles) {
+        report_status(st, kStatusBadShape, 0x30, total_tiles, o.max_tiles);
+        total_tiles = o.max_tiles;
+      }
+      o.meta[0] = total_tiles;
+      o.meta[1] = total_rows;
+    }
+  }
+  if (threadIdx.x == 0) s_base = 0;
+  __syncthreads();
+  if (me >= local) return;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int first = off[me];
+  for (int r0 = 0; r0 < routes; r0 += blockDim.x) {
+    const int r = r0 + threadIdx.x;
+    const bool hit = r < routes && topk_idx[r] == me + e_lo;
+    const uint32_t mask = __ballot_sync(0xffffffffu, hit);
+    if (lane == 0) warp_tot[warp] = __popc(mask);
+    __syncthreads();
+    if (hit) {
+      int before = s_base;
+      for (int w = 0; w < warp; ++w) before += warp_tot[w];
+      const int pidx = first + before + __popc(mask & ((1u << lane) - 1u));
+      o.src_token[pidx] = r / topk;
+      o.dst_row[pidx] = (r / topk) * dst_slots + (r - (r / topk) * topk);
+      o.row_scale[pidx] = topk_w ? topk_w[r] : 1.f;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      int tot = 0;
+      for (int w = 0; w < 32; ++w) tot += warp_tot[w];
+      s_base += tot;
+    }
+    __syncthreads();
+  }
+}
+
 // ---------------------------------------------------------------------------------
 // Fused router for decode-sized batches: router logits (x . W_e, fp32 accumulate) + scoring +
 // top-k per token (one CTA per token), then the CTA that finishes last builds the MoE plan.
@@ -890,9 +989,14 @@ extern "C" int fb_moe_plan(const int* topk_idx, const float* topk_w, int routes,
                            int* counts, int* meta, void* status, void* stream) {
   if (routes <= 0 || topk <= 0 || e_hi <= e_lo || e_hi - e_lo > 256 || ntok <= 0) return FB_ERR_SHAPE;
   PlanOut o{src_token, dst_row, row_scale, tile_group, tile_row0, tile_rows, max_tiles, counts, meta};
-  launch_pdl(moe_plan_kernel, dim3(1), dim3(1024), 0, static_cast<cudaStream_t>(stream), 
-      topk_idx, topk_w, routes, topk, e_lo, e_hi, ntok, dst_slots < topk ? topk : dst_slots, o,
-      static_cast<DeviceStatus*>(status));
+  if (routes > 2048)
+    launch_pdl(moe_plan_wide_kernel, dim3(e_hi - e_lo), dim3(1024), 0, static_cast<cudaStream_t>(stream),
+        topk_idx, topk_w, routes, topk, e_lo, e_hi, ntok, dst_slots < topk ? topk : dst_slots, o,
+        static_cast<DeviceStatus*>(status));
+  else
+    launch_pdl(moe_plan_kernel, dim3(1), dim3(1024), 0, static_cast<cudaStream_t>(stream),
+        topk_idx, topk_w, routes, topk, e_lo, e_hi, ntok, dst_slots < topk ? topk : dst_slots, o,
+        static_cast<DeviceStatus*>(status));
   return FB_CHECK_LAUNCH();
 }
 

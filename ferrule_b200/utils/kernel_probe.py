@@ -158,7 +158,27 @@ def case_v4(reps):
     return timed(fn, reps), {}
 
 
-CASES = {"attention": case_attention, "gemm_dense": case_gemm_dense, "gemm_grouped": case_gemm_grouped,
+def case_prefill(reps):
+    """One 2048-token prefill chunk (4 sequences x 512 new tokens, empty cache) through 2 layers (one dense, one
+    MoE) of the DeepSeek-V2-Lite shape: the per-kernel launch list of this case is the prefill profile."""
+    from ferrule_b200.models import config as C, deepseek as D, weights as W
+    cfg = C.deepseek_v2_lite().with_(n_layers=2)
+    w = W.random_weights(cfg, device=DEV, seed=0, fast_device_init=True)
+    page, S, P = 64, 4, 512
+    pool = D.KvPool(cfg, S * (P // page) + 2, page, DEV)
+    fwd = D.CudaForward(w, pool, max_rows=2048, max_logit_rows=8, decode_rows=32, max_seq_len=1024, attn_splits=8)
+    T = S * P
+    i32 = dict(dtype=torch.int32, device=DEV)
+    pos = torch.arange(P, **i32).repeat(S)
+    seq = torch.arange(S, **i32).repeat_interleave(P)
+    bt = (torch.arange(S * (P // page), **i32) + 1).view(S, P // page)
+    slot = (bt[seq.long(), (pos // page).long()].long() * page + (pos % page).long())
+    b = D.DeviceBatch(torch.randint(0, cfg.vocab_size, (T,), **i32), pos, slot, seq, pos.clone(), bt,
+                      torch.arange(S, **i32) * P + P - 1, T, S)
+    return timed(lambda i: fwd.forward(b), reps), {"tokens": T}
+
+
+CASES = {"prefill": case_prefill, "attention": case_attention, "gemm_dense": case_gemm_dense, "gemm_grouped": case_gemm_grouped,
          "gemm_fp8": case_gemm_fp8, "small": case_small, "v4": case_v4}
 
 

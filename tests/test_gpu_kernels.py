@@ -112,7 +112,8 @@ def _route_setup(K, T, E, topk, e_lo, e_hi, ntok, seed=1):
 
 
 @pytest.mark.parametrize("T,E,topk,e_lo,e_hi,ntok", [(32, 64, 6, 0, 64, 32), (32, 64, 6, 8, 16, 16),
-                                                      (257, 16, 2, 0, 16, 64), (4, 8, 2, 0, 8, 16)])
+                                                      (257, 16, 2, 0, 16, 64), (4, 8, 2, 0, 8, 16),
+                                                      (2048, 64, 6, 0, 64, 128), (1500, 64, 6, 16, 48, 64)])
 def test_moe_plan(K, T, E, topk, e_lo, e_hi, ntok):
     idx, w, plan = _route_setup(K, T, E, topk, e_lo, e_hi, ntok)
     torch.cuda.synchronize()
