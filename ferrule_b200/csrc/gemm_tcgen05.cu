@@ -440,47 +440,46 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tmap_w,
       a ^= 1;
       if (a == 0) aph ^= 1u;
     }
-    if (EPI == kEpiAllReduce && leader) {
-      // Second pass over this CTA's tiles: every lane polls the tagged pairs of its 4 channels from all
+    if (EPI == kEpiAllReduce) {
+      // Second pass, spread over the whole grid (CTAs without a tile of their own help too): a unit is one
+      // output row of one tile (128 channels, 4 per lane).  A warp polls the tagged words of its unit from all
       // ranks' slots (arrival = tag of this call), sums in rank order (identical on every rank), adds the
-      // residual, writes bf16.  Loads of all ranks are in flight together; nothing is stored in between.
+      // residual and writes the row.  With more warps than units every warp pays one L2 round trip.
       const uint32_t tag = call + 1u;
+      const int units = p.n_tiles * p.dense_rows;
+      const int gwarp = blockIdx.x * 4 + (warp - 2), gwarps = gridDim.x * 4;
       bool waited = false;
       const uint64_t w0 = globaltimer_ns();
-      for (int t = tile_first; t < total && ok; t += tile_stride) {
-        const int m = t / p.n_tiles, nt = t - m * p.n_tiles;
-        const int row0 = m * NTOK;
-        const int rows = min(NTOK, p.dense_rows - row0);
+      for (int u = gwarp; u < units && ok; u += gwarps) {
+        const int nt = u % p.n_tiles;
+        const long long orow = u / p.n_tiles;
         const int n4 = nt * kTileN + lane * 4;
         if (n4 >= p.n_out) continue;
-        for (int r = warp - 2; r < rows && ok; r += 4) {
-          const long long orow = row0 + r;
-          float acc[4] = {0.f, 0.f, 0.f, 0.f};
-          int bad_src = 0;
-          if (!ll_gather4(reinterpret_cast<const uint8_t*>(p.peer_recv[p.rank]) + ar_parity_off,
-                          static_cast<size_t>(orow) * p.n_out + n4, ar_slot_bytes, p.world, tag, p.peer_wait_ns, acc,
-                          bad_src, p.ar_bf16 != 0)) {
-            report_status(p.status, kStatusPeerTimeout, 0x400 + bad_src, static_cast<uint32_t>(t), tag);
-            ok = false;
-          }
-          waited = true;
-          if (!ok) break;
-          if (p.residual) {
-            const uint2 rv = *reinterpret_cast<const uint2*>(p.residual + orow * p.ldr + n4);
-            const __nv_bfloat16* rb = reinterpret_cast<const __nv_bfloat16*>(&rv);
+        float acc[4] = {0.f, 0.f, 0.f, 0.f};
+        int bad_src = 0;
+        if (!ll_gather4(reinterpret_cast<const uint8_t*>(p.peer_recv[p.rank]) + ar_parity_off,
+                        static_cast<size_t>(orow) * p.n_out + n4, ar_slot_bytes, p.world, tag, p.peer_wait_ns, acc,
+                        bad_src, p.ar_bf16 != 0)) {
+          report_status(p.status, kStatusPeerTimeout, 0x400 + bad_src, static_cast<uint32_t>(u), tag);
+          ok = false;
+          break;
+        }
+        waited = true;
+        if (p.residual) {
+          const uint2 rv = *reinterpret_cast<const uint2*>(p.residual + orow * p.ldr + n4);
+          const __nv_bfloat16* rb = reinterpret_cast<const __nv_bfloat16*>(&rv);
 #pragma unroll
-            for (int j = 0; j < 4; ++j) acc[j] += __bfloat162float(rb[j]);
-          }
-          if (p.out_fp32) {
-            *reinterpret_cast<float4*>(reinterpret_cast<float*>(p.out) + orow * p.ldo + n4) =
-                make_float4(acc[0], acc[1], acc[2], acc[3]);
-          } else {
-            __nv_bfloat16 ob[4];
+          for (int j = 0; j < 4; ++j) acc[j] += __bfloat162float(rb[j]);
+        }
+        if (p.out_fp32) {
+          *reinterpret_cast<float4*>(reinterpret_cast<float*>(p.out) + orow * p.ldo + n4) =
+              make_float4(acc[0], acc[1], acc[2], acc[3]);
+        } else {
+          __nv_bfloat16 ob[4];
 #pragma unroll
-            for (int j = 0; j < 4; ++j) ob[j] = __float2bfloat16_rn(acc[j]);
-            *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(p.out) + orow * p.ldo + n4) =
-                *reinterpret_cast<const uint2*>(ob);
-          }
+          for (int j = 0; j < 4; ++j) ob[j] = __float2bfloat16_rn(acc[j]);
+          *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(p.out) + orow * p.ldo + n4) =
+              *reinterpret_cast<const uint2*>(ob);
         }
       }
       if (waited && epi_tid == 0 && p.status != nullptr) {
@@ -616,6 +615,8 @@ static int launch_cfg(const CUtensorMap& mw, const CUtensorMap& mx, GemmParams p
   const size_t smem = static_cast<size_t>(stages) * Cfg::kStageBytes + 1024 + 256 + red_bytes;
   int clusters = max_tiles < num_sms() ? max_tiles : num_sms();
   if (clusters < 1) clusters = 1;
+  // the all-reduce epilogue's second pass runs on every CTA of the grid: fill the GPU even with few tiles
+  if (EPI == kEpiAllReduce) clusters = num_sms() / split;
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3(clusters * split, 1, 1);
   cfg.blockDim = dim3(kGemmThreads, 1, 1);
