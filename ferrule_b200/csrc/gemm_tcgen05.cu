@@ -68,6 +68,8 @@ struct GemmParams {
   uint32_t* peer_flags[8];   // per-tile arrival counters of every rank
   uint32_t* local_ctr;       // [0] = calls completed, [1] = CTAs finished this call, [2..] = consumed arrivals per tile
   int ar_bf16;               // kEpiAllReduce: partials travel as bf16 pairs instead of fp32
+  int stage_store;           // bf16 store / SwiGLU / scatter epilogues of large row tiles: rows leave through a
+                             // shared-memory staging tile as 256-byte row segments instead of 2-byte column stores
   const int* remap_rank;     // kEpiScatter, expert-parallel combine: output row -> destination rank ...
   const int* remap_row;      // ... and row in that rank's combine buffer (peer_recv[rank], bf16, pitch ldo)
   const __nv_bfloat16* residual;  // optional, added after the reduction
@@ -151,6 +153,10 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tmap_w,
   // all-reduce epilogue: receive-slot geometry in bytes ([parity][source][rows_cap][n_out] tagged values, 8 bytes
   // each) and the [NTOK][128] fp32 staging tile behind the split-K area
   const size_t ar_slot_bytes = static_cast<size_t>(p.rows_cap) * p.n_out * 8;
+  // store staging (two [16][128] bf16 chunks) shares the position of the all-reduce staging tile
+  __nv_bfloat16* st_stage = reinterpret_cast<__nv_bfloat16*>(
+      red + static_cast<size_t>(S > 1 ? S - 1 : 0) * Cfg::kAccCols * 128);
+  uint32_t chunk_ctr = 0;
   float* ar_stage = red + static_cast<size_t>(S > 1 ? S - 1 : 0) * Cfg::kAccCols * 128;
   const int tile_first = blockIdx.x / S;
   const int tile_stride = gridDim.x / S;
@@ -372,6 +378,49 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tmap_w,
                 u[j] = __float_as_uint(__uint_as_float(u[j]) + rp[static_cast<size_t>(NTOK + c0 + j) * 128]);
             }
           }
+        }
+        if (EPI != kEpiAllReduce && p.stage_store) {
+          // Swap-AB leaves a thread with one output channel of 16 rows: written directly that is sixteen 2-byte
+          // stores per thread, 64 bytes per warp.  Stage the 16 x 128 chunk in shared memory (two buffers, chunk
+          // parity) and let 8 threads write each row's 256 bytes.
+          __nv_bfloat16* sb = st_stage + (chunk_ctr & 1) * (16 * 128);
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const int r = c0 + j;
+            float x = 0.f;
+            if (r < rows) {
+              x = __uint_as_float(v[j]);
+              if (EPI == kEpiSwiGLU) {
+                float up = __uint_as_float(u[j]);
+                if (p.act_limit > 0.f) {
+                  x = fminf(x, p.act_limit);
+                  up = fminf(fmaxf(up, -p.act_limit), p.act_limit);
+                }
+                x = silu_f(x) * up;
+              }
+              if (EPI == kEpiScatter && p.row_scale) x *= p.row_scale[row0 + r];
+            }
+            sb[j * 128 + ch_in_tile] = __float2bfloat16_rn(x);
+          }
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+          {
+            const int j = epi_tid >> 3, seg = epi_tid & 7;
+            const int r = c0 + j;
+            if (r < rows) {
+              long long orow = row0 + r;
+              if (EPI == kEpiScatter && p.dst_row) orow = p.dst_row[row0 + r];
+              const int col0 = ti.nt * kTileN + seg * 16;
+              if (orow >= 0 && col0 < p.n_out) {
+                __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.out) + orow * p.ldo +
+                                     (p.batched ? static_cast<long long>(ti.g) * p.out_group_coff : 0) + col0;
+                const uint4* src = reinterpret_cast<const uint4*>(sb + j * 128 + seg * 16);
+                reinterpret_cast<uint4*>(dst)[0] = src[0];
+                if (col0 + 8 < p.n_out) reinterpret_cast<uint4*>(dst)[1] = src[1];
+              }
+            }
+          }
+          ++chunk_ctr;
+          continue;
         }
         if (n_ok) {
 #pragma unroll
@@ -606,8 +655,12 @@ static int launch_cfg(const CUtensorMap& mw, const CUtensorMap& mx, GemmParams p
   const int split = p.force_split > 0 ? p.force_split
                                       : pick_split(max_tiles, kblocks, grouped, Cfg::kAccCols, Cfg::kStageBytes);
   // the all-reduce epilogue stages one [NTOK x 128] fp32 tile behind the split-K reduction area
+  // large row tiles (prefill) write their bf16 output through a staging tile: see the epilogue
+  p.stage_store = (EPI != kEpiAllReduce && NTOK >= 64 && !p.out_fp32 && p.remap_rank == nullptr &&
+                   p.n_out % 8 == 0 && p.ldo % 8 == 0 && p.out_group_coff % 8 == 0 &&
+                   (reinterpret_cast<uintptr_t>(p.out) & 15) == 0) ? 1 : 0;
   const int red_bytes = (split > 1 ? (split - 1) * Cfg::kAccCols * 128 * 4 : 0) +
-                        (EPI == kEpiAllReduce ? NTOK * 128 * 4 : 0);
+                        (EPI == kEpiAllReduce ? NTOK * 128 * 4 : 0) + (p.stage_store ? 2 * 16 * 128 * 2 : 0);
   int stages = (kSmemLimit - 2048 - red_bytes) / Cfg::kStageBytes;
   if (stages > Cfg::kStages) stages = Cfg::kStages;
   if (stages < 2 || (split > 1 && (max_tiles * split > num_sms() || kblocks < split))) return FB_ERR_SHAPE;

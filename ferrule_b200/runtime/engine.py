@@ -289,10 +289,10 @@ class Engine:
 
     def _reserve(self, seq: SequenceState, n: int, members: List[TxnSeq], is_prefill: bool,
                  claimed: Dict[ResourceKind, int]) -> bool:
-        need = self.kv.required_physical_pages(seq.kv_seq, n)
-        if need > self.kv.free_pages or need > self.broker.available(ResourceKind.KV_PAGES) - claimed[ResourceKind.KV_PAGES]:
+        budget = self._page_budget - claimed[ResourceKind.KV_PAGES]
+        r, need = self.kv.try_reserve(seq.kv_seq, n, budget)
+        if r is None:
             return False
-        r = self.kv.reserve(seq.kv_seq, n)
         claimed[ResourceKind.KV_PAGES] += need
         members.append(TxnSeq(seq, r.res_id, n, is_prefill))
         return True
@@ -302,6 +302,7 @@ class Engine:
         members: List[TxnSeq] = []
         claimed = {ResourceKind.KV_PAGES: 0}
         stalled: List[SequenceState] = []
+        self._page_budget = self.broker.available(ResourceKind.KV_PAGES)     # constant while this batch is assembled
         for seq in decodes:
             if not self._reserve(seq, 1, members, False, claimed):
                 stalled.append(seq)
@@ -343,9 +344,7 @@ class Engine:
         none, top1 = LogitsRequest.none(), LogitsRequest.topk(1)
         for m in txn.members:
             seq = m.seq
-            r = self.kv.reservation(m.res_id)
-            self.kv.bind_reservation_execution(m.res_id, txn.txn_id)
-            blocks, slots = self.kv.reservation_bindings(m.res_id)
+            r, blocks, slots = self.kv.bind_and_bindings(m.res_id, txn.txn_id)
             m.query_start = len(token_ids)
             start = seq.position
             if m.is_prefill:

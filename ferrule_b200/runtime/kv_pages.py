@@ -128,6 +128,8 @@ class KvPageManager:
 
     # ------------------------------------------------------------------ helpers
     def _take(self, n: int) -> List[int]:
+        if n == 0:                  # the common decode step: the tail page has room
+            return []
         if n > len(self._free):
             self._stats.reserve_failures += 1
             raise OutOfPages(f"need {n} pages, {len(self._free)} free")
@@ -210,6 +212,42 @@ class KvPageManager:
         self._res[r.res_id] = r
         s.open_reservation = r.res_id
         return r
+
+    def try_reserve(self, seq_id: int, new_tokens: int, page_budget: int) -> Tuple[Optional[KvReservation], int]:
+        """`reserve` if the pages it needs (growth + COW) fit both the free list and `page_budget`; otherwise
+        (None, need).  One pass over the sequence instead of `required_physical_pages` followed by `reserve`."""
+        s = self._seqs.get(seq_id)
+        if s is None:
+            raise KvError(f"unknown sequence {seq_id}")
+        ps = self.page_size
+        end = s.committed_tokens + new_tokens
+        grow = (end + ps - 1) // ps - len(s.pages)
+        if grow < 0:
+            grow = 0
+        need = grow + (1 if self._needs_cow(s, new_tokens) else 0)
+        if need > len(self._free) or need > page_budget:
+            return None, need
+        return self.reserve(seq_id, new_tokens), need
+
+    def bind_and_bindings(self, res_id: int, execution_id: int):
+        """`bind_reservation_execution` + `reservation_bindings` in one lookup -> (reservation, blocks, slots)."""
+        r = self._res.get(res_id)
+        if r is None:
+            raise KvError(f"unknown reservation {res_id}")
+        if r.state != ReservationState.RESERVED:
+            raise KvError(f"reservation {res_id} is {r.state.value}, cannot bind")
+        r.state, r.execution_id = ReservationState.BOUND, execution_id
+        s = self._seqs[r.seq_id]
+        if r.cow is None and not r.new_pages:
+            blocks = s.pages                      # read-only view: nothing changes while the reservation is open
+        else:
+            blocks = self._blocks_during(r)
+        ps = self.page_size
+        if r.tokens == 1:
+            slots = [blocks[r.start // ps] * ps + r.start % ps]
+        else:
+            slots = [blocks[(r.start + j) // ps] * ps + (r.start + j) % ps for j in range(r.tokens)]
+        return r, blocks, slots
 
     def reservation(self, res_id: int) -> KvReservation:
         r = self._res.get(res_id)
