@@ -626,14 +626,14 @@ constexpr int kSmemLimit = 227 * 1024;
 
 // Split-K factor: spread a GEMM with few output tiles over more SMs.  The S CTAs of a cluster
 // each take 1/S of the k-blocks of one tile; only used when every tile gets its own cluster.
-static int pick_split(int tiles, int kblocks, bool grouped, int acc_cols, int stage_bytes) {
+static int pick_split(int tiles, int kblocks, bool grouped, int acc_cols, int stage_bytes, int extra_bytes) {
   if (grouped) return 1;
   int best = 1;
   for (int s = 2; s <= 4; s *= 2) {  // measured: 8-way costs more in the DSMEM reduction than it saves
     if (tiles * s > num_sms()) break;
     if (kblocks / s < 4) break;
     const int red = (s - 1) * acc_cols * 128 * 4;
-    if (kSmemLimit - 2048 - red < 2 * stage_bytes) break;
+    if (kSmemLimit - 2048 - red - extra_bytes < 2 * stage_bytes) break;
     best = s;
   }
   return best;
@@ -652,15 +652,17 @@ static int launch_cfg(const CUtensorMap& mw, const CUtensorMap& mx, GemmParams p
     attr_set = true;
   }
   const int kblocks = (p.k + kBlockK - 1) / kBlockK;
-  const int split = p.force_split > 0 ? p.force_split
-                                      : pick_split(max_tiles, kblocks, grouped, Cfg::kAccCols, Cfg::kStageBytes);
-  // the all-reduce epilogue stages one [NTOK x 128] fp32 tile behind the split-K reduction area
   // large row tiles (prefill) write their bf16 output through a staging tile: see the epilogue
   p.stage_store = (EPI != kEpiAllReduce && NTOK >= 64 && !p.out_fp32 && p.remap_rank == nullptr &&
                    p.n_out % 8 == 0 && p.ldo % 8 == 0 && p.out_group_coff % 8 == 0 &&
                    (reinterpret_cast<uintptr_t>(p.out) & 15) == 0) ? 1 : 0;
-  const int red_bytes = (split > 1 ? (split - 1) * Cfg::kAccCols * 128 * 4 : 0) +
-                        (EPI == kEpiAllReduce ? NTOK * 128 * 4 : 0) + (p.stage_store ? 2 * 16 * 128 * 2 : 0);
+  // staging areas behind the split-K reduction area: the all-reduce epilogue's [NTOK x 128] fp32 tile, or the
+  // two [16 x 128] bf16 chunks of the staged store
+  const int extra_bytes = (EPI == kEpiAllReduce ? NTOK * 128 * 4 : 0) + (p.stage_store ? 2 * 16 * 128 * 2 : 0);
+  const int split = p.force_split > 0 ? p.force_split
+                                      : pick_split(max_tiles, kblocks, grouped, Cfg::kAccCols, Cfg::kStageBytes,
+                                                   extra_bytes);
+  const int red_bytes = (split > 1 ? (split - 1) * Cfg::kAccCols * 128 * 4 : 0) + extra_bytes;
   int stages = (kSmemLimit - 2048 - red_bytes) / Cfg::kStageBytes;
   if (stages > Cfg::kStages) stages = Cfg::kStages;
   if (stages < 2 || (split > 1 && (max_tiles * split > num_sms() || kblocks < split))) return FB_ERR_SHAPE;

@@ -25,7 +25,7 @@ def _pct(v: List[float], p: float) -> float:
 
 
 async def _one(client, url: str, model: str, prompt: List[int], max_tokens: int, out: Dict) -> None:
-    body = {"prompt": prompt, "max_tokens": max_tokens, "stream": True, "ignore_eos": True}
+    body = {"prompt": prompt, "max_tokens": max_tokens, "stream": True, "ignore_eos": True, "return_token_ids": True}
     if model:
         body["model"] = model
     t0 = time.perf_counter()
@@ -34,11 +34,16 @@ async def _one(client, url: str, model: str, prompt: List[int], max_tokens: int,
         async with client.stream("POST", url + "/v1/completions", json=body, timeout=None) as r:
             if r.status_code != 200:
                 out["failed"] += 1
+                out.setdefault("errors", []).append(f"http {r.status_code}: {(await r.aread())[:200]!r}")
                 return
             async for line in r.aiter_lines():
                 if line.startswith("data: ") and line != "data: [DONE]":
                     obj = json.loads(line[6:])
-                    if obj.get("choices") and obj["choices"][0].get("text"):
+                    if "error" in obj:                       # engine failure reported inside a 200 stream
+                        out["failed"] += 1
+                        out.setdefault("errors", []).append(str(obj["error"].get("message"))[:200])
+                        return
+                    if obj.get("token_ids") or (obj.get("choices") and obj["choices"][0].get("text")):
                         stamps.append(time.perf_counter())
     except Exception:  # noqa: BLE001
         out["failed"] += 1
@@ -75,7 +80,8 @@ async def _level(url, model, conc, n_req, rng, vocab, min_in, max_in, min_out, m
             "committed_tokens_per_s": round(out["tokens"] / dt, 2),
             "ttft_p50_s": round(_pct(out["ttft"], 0.5), 4), "ttft_p99_s": round(_pct(out["ttft"], 0.99), 4),
             "tpot_p50_s": round(_pct(out["tpot"], 0.5), 5), "tpot_p99_s": round(_pct(out["tpot"], 0.99), 5),
-            "e2e_p50_s": round(_pct(out["e2e"], 0.5), 4)}
+            "e2e_p50_s": round(_pct(out["e2e"], 0.5), 4), "tokens": out["tokens"],
+            "errors": sorted(set(out.get("errors", [])))[:3]}
 
 
 def run_sweep(url, model, concurrency, n_req, seed, vocab, min_in, max_in, min_out, max_out, prefix, frac) -> Dict:

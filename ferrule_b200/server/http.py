@@ -126,9 +126,12 @@ def build_app(worker: ModelWorker, model_name: Optional[str] = None, template: O
                         yield b": keep-alive\n\n"
                         continue
                     if ev.kind == "token":
-                        if ev.text:
-                            yield _sse(oa.chat_chunk(rid, name, created, {"content": ev.text}) if chat
-                                       else oa.completion_chunk(rid, name, created, ev.text))
+                        if ev.text or (parsed.return_token_ids and ev.token >= 0):
+                            obj = (oa.chat_chunk(rid, name, created, {"content": ev.text}) if chat
+                                   else oa.completion_chunk(rid, name, created, ev.text))
+                            if parsed.return_token_ids and ev.token >= 0:
+                                obj["token_ids"] = [ev.token]
+                            yield _sse(obj)
                     elif ev.kind == "error":
                         yield _sse({"error": {"message": ev.message, "type": "server_error", "param": None,
                                               "code": "engine_failure"}})

@@ -36,7 +36,7 @@ class RequestError(ValueError):
 
 _COMMON = {"model", "max_tokens", "max_completion_tokens", "stream", "stream_options", "stop", "n", "temperature",
            "top_p", "top_k", "min_p", "repetition_penalty", "presence_penalty", "frequency_penalty", "logprobs",
-           "top_logprobs", "seed", "user", "ignore_eos", "session_id"}
+           "top_logprobs", "seed", "user", "ignore_eos", "session_id", "return_token_ids"}
 _CHAT_ONLY = {"messages", "tools", "tool_choice", "response_format", "functions", "function_call"}
 _COMPLETION_ONLY = {"prompt", "echo", "best_of", "suffix", "logit_bias"}
 
@@ -107,6 +107,7 @@ class ParsedRequest:
     include_usage: bool
     ignore_eos: bool
     session_id: Optional[str]
+    return_token_ids: bool = False        # extension: stream every committed token id (chunks may carry empty text)
 
 
 def _check_fields(body: Any, allowed: set) -> Dict[str, Any]:
@@ -148,7 +149,8 @@ def parse_chat_request(body: Any) -> ParsedRequest:
     _validate_sampling(body)
     stream, include = _stream_opts(body)
     return ParsedRequest("chat", str(body.get("model", "")), None, None, out, _max_tokens(body), _stops(body), stream,
-                         include, bool(body.get("ignore_eos", False)), body.get("session_id"))
+                         include, bool(body.get("ignore_eos", False)), body.get("session_id"),
+                         bool(body.get("return_token_ids", False)))
 
 
 def parse_completion_request(body: Any) -> ParsedRequest:
@@ -166,7 +168,8 @@ def parse_completion_request(body: Any) -> ParsedRequest:
     _validate_sampling(body)
     stream, include = _stream_opts(body)
     return ParsedRequest("completion", str(body.get("model", "")), text, toks, [], _max_tokens(body), _stops(body),
-                         stream, include, bool(body.get("ignore_eos", False)), body.get("session_id"))
+                         stream, include, bool(body.get("ignore_eos", False)), body.get("session_id"),
+                         bool(body.get("return_token_ids", False)))
 
 
 def finish_reason(reason: FinishReason) -> str:
