@@ -36,6 +36,7 @@ constexpr int kAccBufs = 4;
 
 struct Params {
   int n_out, k, n_tiles, dual_offset, dense_rows, max_tok_tiles, stages;
+  int xs_bytes;                // bytes of the activation-scale tile in shared memory (the split-K area follows it)
   const int* tile_group;
   const int* tile_row0;
   const int* tile_rows;
@@ -93,6 +94,12 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + kAccBufs);
   volatile uint32_t* abort_flag = tmem_slot + 1;
   uint8_t* xs_tile = reinterpret_cast<uint8_t*>(bars) + 256;      // [NTOK][k_blocks] activation scales of the tile
+  // split-K over a cluster: the S CTAs of a cluster take consecutive slices of the k-blocks of one tile; the
+  // peers' scaled fp32 partials travel to the leader (cluster rank 0) through distributed shared memory.
+  const int S = static_cast<int>(cluster_nctarank());
+  const int crank = static_cast<int>(cluster_ctarank());
+  uint64_t* red_bar = reinterpret_cast<uint64_t*>(tmem_slot + 4);
+  float* red = reinterpret_cast<float*>(xs_tile + p.xs_bytes);   // leader: [peer - 1][acc column][128 lanes]
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
@@ -104,6 +111,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
       mbar_init(&acc_full[a], 1);
       mbar_init(&acc_empty[a], 4);
     }
+    mbar_init(red_bar, 128 * (S > 1 ? S - 1 : 1));
     *abort_flag = 0;
     fence_barrier_init();
     tma_prefetch_desc(&tmap_w);
@@ -117,12 +125,16 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  if (S > 1) cluster_sync_all();     // the leader's barrier is initialised before any peer arrives on it
   pdl_wait();
 
   const bool grouped = p.tile_group != nullptr;
   const int num_tok_tiles = grouped ? min(*p.num_tok_tiles, p.max_tok_tiles) : (p.dense_rows + NTOK - 1) / NTOK;
   const int total = num_tok_tiles * p.n_tiles;
   const int kblocks = (p.k + kBlockK - 1) / kBlockK;
+  const int tile_first = blockIdx.x / S, tile_stride = gridDim.x / S;
+  const int kb_begin = static_cast<int>(static_cast<long long>(crank) * kblocks / S);
+  const int kb_end = static_cast<int>(static_cast<long long>(crank + 1) * kblocks / S);
 
   if (warp == 0) {
     if (lane == 0) {
@@ -130,11 +142,11 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
       uint32_t ph = 0;
       bool ok = true;
       long long issued = 0;
-      for (int t = blockIdx.x; t < total && ok; t += gridDim.x) {
+      for (int t = tile_first; t < total && ok; t += tile_stride) {
         const int m = t / p.n_tiles, nt = t - m * p.n_tiles;
         const int g = grouped ? p.tile_group[m] : 0;
         const int row0 = grouped ? p.tile_row0[m] : m * NTOK;
-        for (int kb = 0; kb < kblocks; ++kb) {
+        for (int kb = kb_begin; kb < kb_end; ++kb) {
           ok = mbar_wait(&empty_bar[s], ph ^ 1u, abort_flag, p.status, 0x800);
           if (!ok) break;
           uint8_t* stage = smem + s * C::kStageBytes;
@@ -163,8 +175,8 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
       uint32_t ph = 0;
       long long kbg = 0;    // k-blocks issued by this CTA: selects the TMEM buffer and its phase
       bool ok = true;
-      for (int t = blockIdx.x; t < total && ok; t += gridDim.x) {
-        for (int kb = 0; kb < kblocks; ++kb, ++kbg) {
+      for (int t = tile_first; t < total && ok; t += tile_stride) {
+        for (int kb = kb_begin; kb < kb_end; ++kb, ++kbg) {
           const int a = static_cast<int>(kbg % C::kRing);
           const uint32_t aph = static_cast<uint32_t>((kbg / C::kRing) & 1);
           ok = mbar_wait(&acc_empty[a], aph ^ 1u, abort_flag, p.status, 0x810);
@@ -196,7 +208,8 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
     const int epi_tid = (warp - 2) * 32 + lane;
     long long kbg = 0;
     bool ok = true;
-    for (int t = blockIdx.x; t < total && ok; t += gridDim.x) {
+    uint32_t red_phase = 0;
+    for (int t = tile_first; t < total && ok; t += tile_stride) {
       const int m = t / p.n_tiles, nt = t - m * p.n_tiles;
       const int g = grouped ? p.tile_group[m] : 0;
       const int row0 = grouped ? p.tile_row0[m] : m * NTOK;
@@ -220,7 +233,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
 #pragma unroll
         for (int j = 0; j < NTOK; ++j) accu[j] = 0.f;
       }
-      for (int kb = 0; kb < kblocks; ++kb, ++kbg) {
+      for (int kb = kb_begin; kb < kb_end; ++kb, ++kbg) {
         const int a = static_cast<int>(kbg % C::kRing);
         const uint32_t aph = static_cast<uint32_t>((kbg / C::kRing) & 1);
         ok = mbar_wait(&acc_full[a], aph, abort_flag, p.status, 0x820);
@@ -261,6 +274,33 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
         if (lane == 0) mbar_arrive(&acc_empty[a]);
       }
       if (!ok) break;
+      if (S > 1) {
+        constexpr int kAcc = NTOK * (DUAL ? 2 : 1);
+        if (crank != 0) {
+          // ship the scaled partial sums to the leader and move on: only the leader writes output
+          const uint32_t remote = mapa_shared(smem_u32(red), 0) +
+                                  (static_cast<uint32_t>((crank - 1) * kAcc) * 128u + static_cast<uint32_t>(ch)) * 4u;
+#pragma unroll
+          for (int j = 0; j < NTOK; ++j) {
+            st_cluster_f32(remote + static_cast<uint32_t>(j) * 512u, acc[j]);
+            if (DUAL) st_cluster_f32(remote + static_cast<uint32_t>(NTOK + j) * 512u, accu[j]);
+          }
+          mbar_arrive_remote(mapa_shared(smem_u32(red_bar), 0));
+          continue;
+        }
+        ok = mbar_wait_cluster(red_bar, red_phase, abort_flag, p.status, 0x830);
+        red_phase ^= 1u;
+        if (!ok) break;
+        // fixed summation order: own slice, then peers by cluster rank
+        for (int pr = 1; pr < S; ++pr) {
+          const float* rp = red + (static_cast<size_t>(pr - 1) * kAcc) * 128 + ch;
+#pragma unroll
+          for (int j = 0; j < NTOK; ++j) {
+            acc[j] += rp[static_cast<size_t>(j) * 128];
+            if (DUAL) accu[j] += rp[static_cast<size_t>(NTOK + j) * 128];
+          }
+        }
+      }
       if (n < p.n_out) {
 #pragma unroll
         for (int j = 0; j < NTOK; ++j) {
@@ -337,16 +377,44 @@ static int launch(const CUtensorMap& mw, const CUtensorMap& mx, Params p, int ma
     attr = true;
   }
   const int xs_bytes = (NTOK * kblocks + 15) / 16 * 16;
-  int stages = (kLimit - 2048 - xs_bytes) / C::kStageBytes;
-  if (stages > 10) stages = 10;
-  if (stages < 2) return FB_ERR_SHAPE;
-  p.stages = stages;
-  const size_t smem = static_cast<size_t>(stages) * C::kStageBytes + 1024 + 256 + xs_bytes;
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  const int grid = max_tiles < sms ? (max_tiles < 1 ? 1 : max_tiles) : sms;
-  if (launch_pdl(kern, dim3(grid), dim3(kThreads), smem, stream, mw, mx, p) != cudaSuccess) return FB_ERR_LAUNCH;
+  // Split-K over a cluster for dense GEMMs with few tiles (decode-sized projections): every tile gets its own
+  // cluster, each CTA keeps at least 4 k-blocks, and the reduction area must leave room for two pipeline stages.
+  int split = 1;
+  const bool grouped = p.tile_group != nullptr;
+  constexpr int kAcc = NTOK * (DUAL ? 2 : 1);
+  if (!grouped) {
+    for (int sp = 2; sp <= 4; sp *= 2) {
+      if (max_tiles * sp > sms || kblocks / sp < 4) break;
+      if (kLimit - 2048 - xs_bytes - (sp - 1) * kAcc * 512 < 2 * C::kStageBytes) break;
+      split = sp;
+    }
+  }
+  const int red_bytes = split > 1 ? (split - 1) * kAcc * 512 : 0;
+  int stages = (kLimit - 2048 - xs_bytes - red_bytes) / C::kStageBytes;
+  if (stages > 10) stages = 10;
+  if (stages < 2) return FB_ERR_SHAPE;
+  p.stages = stages;
+  p.xs_bytes = xs_bytes;
+  const size_t smem = static_cast<size_t>(stages) * C::kStageBytes + 1024 + 256 + xs_bytes + red_bytes;
+  int clusters = max_tiles < sms / split ? (max_tiles < 1 ? 1 : max_tiles) : sms / split;
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(clusters * split, 1, 1);
+  cfg.blockDim = dim3(kThreads, 1, 1);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr2[2];
+  attr2[0].id = cudaLaunchAttributeClusterDimension;
+  attr2[0].val.clusterDim.x = split;
+  attr2[0].val.clusterDim.y = 1;
+  attr2[0].val.clusterDim.z = 1;
+  attr2[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr2[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr2;
+  cfg.numAttrs = pdl_enabled() ? 2 : 1;
+  if (cudaLaunchKernelEx(&cfg, kern, mw, mx, p) != cudaSuccess) return FB_ERR_LAUNCH;
   return cudaGetLastError() == cudaSuccess ? FB_OK : FB_ERR_LAUNCH;
 }
 

@@ -178,7 +178,29 @@ def case_prefill(reps):
     return timed(lambda i: fwd.forward(b), reps), {"tokens": T}
 
 
-CASES = {"prefill": case_prefill, "attention": case_attention, "gemm_dense": case_gemm_dense, "gemm_grouped": case_gemm_grouped,
+def case_v3_fp8_decode(reps):
+    """Decode step of one rank's TP8 / EP8 shard of the DeepSeek-V3 shape in FP8 (hidden 7168, 16 local heads,
+    32 local experts), 4 layers (3 dense + 1 MoE), 64 sequences at context 256: launch list of the FP8 path."""
+    import os
+    from ferrule_b200.models import config as C, deepseek as D, weights as W
+    fmt = os.environ.get("FERRULE_PROBE_FORMAT", "fp8_block")
+    cfg = C.deepseek_v3().with_(n_layers=4, n_mtp_layers=0)
+    w = W.random_weights(cfg, device=DEV, seed=0, tp_rank=0, tp_world=8, fast_device_init=True, weight_format=fmt)
+    page, S, ctx = 64, 64, 256
+    pool = D.KvPool(cfg, S * (ctx // page + 1) + 2, page, DEV)
+    fwd = D.CudaForward(w, pool, max_rows=256, max_logit_rows=64, decode_rows=64, max_seq_len=512, attn_splits=4)
+    i32 = dict(dtype=torch.int32, device=DEV)
+    blocks = ctx // page + 1
+    bt = (torch.arange(S * blocks, **i32) + 1).view(S, blocks)
+    pos = torch.full((S,), ctx, **i32)
+    seq = torch.arange(S, **i32)
+    slot = bt[:, ctx // page].long() * page + ctx % page
+    b = D.DeviceBatch(torch.randint(0, cfg.vocab_size, (S,), **i32), pos, slot, seq, pos.clone(), bt,
+                      torch.arange(S, **i32), S, S)
+    return timed(lambda i: fwd.forward(b), reps), {"format": fmt}
+
+
+CASES = {"v3_fp8_decode": case_v3_fp8_decode, "prefill": case_prefill, "attention": case_attention, "gemm_dense": case_gemm_dense, "gemm_grouped": case_gemm_grouped,
          "gemm_fp8": case_gemm_fp8, "small": case_small, "v4": case_v4}
 
 
