@@ -178,3 +178,43 @@ def test_slow_consumer_is_cancelled_and_admission_timeout():
         run(main())
     finally:
         worker.stop()
+
+
+def test_data_parallel_replicas_share_the_load_and_keep_sessions():
+    """Two engine replicas behind one front end: requests spread over both, a session returns to its replica."""
+    import asyncio
+
+    from ferrule_b200.parallel.dp import DataParallelWorker
+    from ferrule_b200.runtime.engine import Engine, EngineConfig
+    from ferrule_b200.runtime.runner import MockRunner
+    from ferrule_b200.runtime.scheduler import SchedulerConfig
+    from ferrule_b200.server.worker import ModelWorker
+    from ferrule_b200.utils.tokenizer import load_tokenizer
+
+    def factory():
+        sched = SchedulerConfig(max_active_sequences=4, max_decode_batch=4, max_batch_tokens=64, prefill_chunk_size=16, ctx_size=256)
+        return Engine(MockRunner(vocab=300), EngineConfig(scheduler=sched, kv_pages=64, page_size=16))
+
+    tok = load_tokenizer(None)
+    dp = DataParallelWorker([ModelWorker(factory, tok, model_name="m"), ModelWorker(factory, tok, model_name="m")]).start()
+    try:
+        async def run():
+            streams = [await dp.submit(text=None, token_ids=[1, 2, 3, 4 + i], max_tokens=5, stop=[], ignore_eos=True)
+                       for i in range(6)]
+            s1 = await dp.submit(text=None, token_ids=[9, 9], max_tokens=2, stop=[], session_id="sess")
+            s2 = await dp.submit(text=None, token_ids=[9, 9, 9], max_tokens=2, stop=[], session_id="sess")
+            done = 0
+            for s in streams + [s1, s2]:
+                while True:
+                    ev = await asyncio.wait_for(s.next(), 10)
+                    if ev.kind in ("finish", "error"):
+                        assert ev.kind == "finish"
+                        done += 1
+                        break
+            return done, dp._owner[s1.request_id], dp._owner[s2.request_id]
+        done, o1, o2 = asyncio.run(run())
+        assert done == 8 and o1 == o2
+        assert min(dp.placed) >= 2 and sum(dp.placed) == 8
+        assert dp.healthy and len(dp.stats()["replicas"]) == 2
+    finally:
+        dp.stop()
