@@ -644,6 +644,95 @@ router_plan_fused_kernel(const __nv_bfloat16* __restrict__ x, long long ldx,
   moe_plan_body(out_idx, out_w, rows * topk, topk, e_lo, e_hi, ntok, dst_slots, o, st);
 }
 
+// ---------------------------------------------------------------------------------
+// Router for decode-sized batches with a static plan: every local expert owns `slot_rows` consecutive rows of the
+// expert-major buffers (slot_rows >= number of tokens, so no expert can overflow) and one GEMM row tile.  One CTA
+// per token: router logits, scoring, top-k, then each route of the token reserves the next free row of its expert
+// (atomicAdd on the expert's counter, zeroed once per step for all layers), records (source token, destination
+// row, weight) there and copies the activation row into the gather buffer.  No plan kernel, no gather kernel and
+// no inter-CTA dependency: the GEMMs take the counters as their per-tile row counts.  The order of an expert's
+// rows depends on the atomics; every row is computed independently, so the outputs do not.
+// ---------------------------------------------------------------------------------
+__global__ void __launch_bounds__(1024)
+router_append_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, const __nv_bfloat16* __restrict__ w,
+                     int hidden, const float* __restrict__ bias, const long long* __restrict__ hash_table,
+                     const int* __restrict__ token_ids, int rows, int experts, int topk, int score_fn, int n_groups,
+                     int topk_groups, int normalize, float route_scale, int* __restrict__ out_idx,
+                     float* __restrict__ out_w, int e_lo, int e_hi, int slot_rows, int dst_slots,
+                     int* __restrict__ cnt, int* __restrict__ src_token, int* __restrict__ dst_row,
+                     float* __restrict__ row_scale, __nv_bfloat16* __restrict__ xg, long long ldxg, DeviceStatus* st) {
+  pdl_launch_dependents();
+  pdl_wait();
+  extern __shared__ float xs[];            // hidden floats, then `experts` logits
+  float* logits = xs + hidden;
+  __shared__ int rlist[32];
+  const int t = blockIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+  for (int i = threadIdx.x * 8; i < hidden; i += blockDim.x * 8) {
+    const uint4 v = *reinterpret_cast<const uint4*>(x + t * ldx + i);
+    const __nv_bfloat16* vp = reinterpret_cast<const __nv_bfloat16*>(&v);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) xs[i + j] = __bfloat162float(vp[j]);
+  }
+  __syncthreads();
+  for (int e = warp; e < experts; e += 2 * nwarps) {
+    const int e2 = e + nwarps;
+    const bool two = e2 < experts;
+    const __nv_bfloat16* wr = w + static_cast<size_t>(e) * hidden;
+    const __nv_bfloat16* wr2 = w + static_cast<size_t>(two ? e2 : e) * hidden;
+    float acc = 0.f, acc2 = 0.f;
+#pragma unroll 4
+    for (int i = lane * 8; i < hidden; i += 256) {
+      const uint4 v = *reinterpret_cast<const uint4*>(wr + i);
+      const uint4 v2 = *reinterpret_cast<const uint4*>(wr2 + i);
+      const __nv_bfloat16* vp = reinterpret_cast<const __nv_bfloat16*>(&v);
+      const __nv_bfloat16* vp2 = reinterpret_cast<const __nv_bfloat16*>(&v2);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        acc = fmaf(__bfloat162float(vp[j]), xs[i + j], acc);
+        acc2 = fmaf(__bfloat162float(vp2[j]), xs[i + j], acc2);
+      }
+    }
+    acc = warp_sum(acc);
+    acc2 = warp_sum(acc2);
+    if (lane == 0) {
+      logits[e] = acc;
+      if (two) logits[e2] = acc2;
+    }
+  }
+  __syncthreads();
+  if (warp == 0) {
+    route_one_token(logits, t, lane, bias, hash_table, token_ids, experts, topk, score_fn, n_groups,
+                    topk_groups, normalize, route_scale, out_idx, out_w);
+    __syncwarp();
+    if (lane < topk) {
+      const int e = out_idx[t * topk + lane];
+      int r = -1;
+      if (e >= e_lo && e < e_hi) {
+        const int pos = atomicAdd(&cnt[e - e_lo], 1);
+        if (pos < slot_rows) {
+          r = (e - e_lo) * slot_rows + pos;
+          src_token[r] = t;
+          dst_row[r] = t * dst_slots + lane;
+          row_scale[r] = out_w[t * topk + lane];
+        } else {
+          report_status(st, kStatusBadShape, 0x50, e, pos);
+        }
+      }
+      rlist[lane] = r;
+    }
+  }
+  __syncthreads();
+  // copy the token's activation row into every reserved row (16 bytes per thread)
+  const int vec = hidden / 8;
+  for (int i = threadIdx.x; i < topk * vec; i += blockDim.x) {
+    const int s = i / vec, c = i - s * vec;
+    const int r = rlist[s];
+    if (r >= 0)
+      *reinterpret_cast<uint4*>(xg + r * ldxg + c * 8) = *reinterpret_cast<const uint4*>(x + t * ldx + c * 8);
+  }
+}
+
 // Asynchronous L2 prefetch of a byte range (weights that a later kernel will stream): every thread issues
 // bulk prefetch requests of 8 KB; nothing is written and nothing waits.
 __global__ void __launch_bounds__(128)
@@ -1020,6 +1109,29 @@ extern "C" int fb_router_plan_fused(const void* x, long long ldx, const void* w,
       hash_table, token_ids, rows, experts, topk, score_fn, n_groups, topk_groups, normalize, route_scale,
       out_idx, out_w, e_lo, e_hi, ntok, dst_slots < topk ? topk : dst_slots, o,
       static_cast<unsigned int*>(done_ctr), static_cast<DeviceStatus*>(status));
+  return FB_CHECK_LAUNCH();
+}
+
+extern "C" int fb_router_append(const void* x, long long ldx, const void* w, int hidden, const float* bias,
+                                const long long* hash_table, const int* token_ids, int rows, int experts, int topk,
+                                int score_fn, int n_groups, int topk_groups, int normalize, float route_scale,
+                                int* out_idx, float* out_w, int e_lo, int e_hi, int slot_rows, int dst_slots, int* cnt,
+                                int* src_token, int* dst_row, float* row_scale, void* xg, long long ldxg,
+                                void* status, void* stream) {
+  if (rows <= 0 || experts <= 0 || experts > 256 || topk <= 0 || topk > 32 || topk > experts) return FB_ERR_SHAPE;
+  if (hidden % 256 != 0 || hidden > 8192 || (ldx % 8) != 0 || (ldxg % 8) != 0) return FB_ERR_SHAPE;
+  if (slot_rows < rows || e_hi <= e_lo || !cnt || !src_token || !dst_row || !row_scale || !xg) return FB_ERR_SHAPE;
+  const size_t smem = (static_cast<size_t>(hidden) + experts) * sizeof(float);
+  static bool attr_done = false;
+  if (!attr_done) {
+    cudaFuncSetAttribute(router_append_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);
+    attr_done = true;
+  }
+  launch_pdl(router_append_kernel, dim3(rows), dim3(1024), smem, static_cast<cudaStream_t>(stream),
+             static_cast<const __nv_bfloat16*>(x), ldx, static_cast<const __nv_bfloat16*>(w), hidden, bias, hash_table,
+             token_ids, rows, experts, topk, score_fn, n_groups, topk_groups, normalize, route_scale, out_idx, out_w,
+             e_lo, e_hi, slot_rows, dst_slots, cnt, src_token, dst_row, row_scale, static_cast<__nv_bfloat16*>(xg), ldxg,
+             static_cast<DeviceStatus*>(status));
   return FB_CHECK_LAUNCH();
 }
 

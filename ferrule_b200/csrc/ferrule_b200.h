@@ -173,6 +173,13 @@ int fb_router_plan_fused(const void* x, long long ldx, const void* w, int hidden
                          void* done_ctr, void* status, void* stream);
 // asynchronous L2 prefetch of [ptr, ptr + bytes) (ptr 16-byte aligned)
 int fb_l2_prefetch(const void* ptr, long long bytes, void* stream);
+// decode-sized batches, static plan: expert e (local) owns rows [e * slot_rows, (e + 1) * slot_rows) of src_token /
+// dst_row / row_scale / xg; cnt[e] (zeroed by the caller before the step) ends up as its row count
+int fb_router_append(const void* x, long long ldx, const void* w, int hidden, const float* bias,
+                     const long long* hash_table, const int* token_ids, int rows, int experts, int topk, int score_fn,
+                     int n_groups, int topk_groups, int normalize, float route_scale, int* out_idx, float* out_w,
+                     int e_lo, int e_hi, int slot_rows, int dst_slots, int* cnt, int* src_token, int* dst_row,
+                     float* row_scale, void* xg, long long ldxg, void* status, void* stream);
 int fb_gather_rows(const void* x, long long ldx, const int* src_token, const int* meta, void* out,
                    long long ldo, int cap_rows, int dim, int src_rows, void* status, void* stream);
 int fb_moe_reduce(const void* route_out, int slots, int topk, const int* topk_idx, int e_lo,

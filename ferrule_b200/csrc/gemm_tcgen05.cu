@@ -118,6 +118,12 @@ __device__ __forceinline__ TileInfo decode_tile(const GemmParams& p, int t, int 
   return ti;
 }
 
+// grouped mode: a tile whose expert received no row (static one-tile-per-expert plans, streamed experts that are
+// not resident) is skipped by the producer, the MMA issuer and the epilogue alike - no weights are read for it
+__device__ __forceinline__ bool tile_empty(const GemmParams& p, int t) {
+  return p.tile_group != nullptr && p.tile_rows[t / p.n_tiles] <= 0;
+}
+
 __device__ __forceinline__ float silu_f(float x) { return x / (1.f + __expf(-x)); }
 
 template <int NTOK, bool DUAL, int EPI>
@@ -233,6 +239,7 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tmap_w,
       }
       if (tracing) p.trace[2] = globaltimer_ns();                     // dependency wait passed
       for (int t = tile_first; t < total && ok; t += tile_stride) {
+        if (tile_empty(p, t)) continue;
         const TileInfo ti = decode_tile<NTOK>(p, t, tiles_per_group);
         const int g = ti.g, nt = ti.nt, row0 = ti.row0;
         const int xk0 = p.batched ? g * p.x_group_koff : 0;
@@ -279,6 +286,7 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tmap_w,
       uint32_t aph = 0;
       bool ok = true;
       for (int t = tile_first; t < total && ok; t += tile_stride) {
+        if (tile_empty(p, t)) continue;
         ok = mbar_wait(&acc_empty[a], aph ^ 1u, abort_flag, p.status, 0x200);
         if (!ok) break;
         tc_fence_after();
@@ -317,6 +325,7 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tmap_w,
     uint32_t aph = 0;
     bool ok = true;
     for (int t = tile_first; t < total && ok; t += tile_stride) {
+      if (tile_empty(p, t)) continue;
       const TileInfo ti = decode_tile<NTOK>(p, t, tiles_per_group);
       const int row0 = ti.row0, rows = ti.rows;
       const int n = ti.nt * kTileN + ch_in_tile;

@@ -282,6 +282,16 @@ class CudaWorkspace:
                 self.plans[ntok] = MoePlan.allocate(R * k, el, ntok, device)
             self.xg = torch.zeros(R * k, H, **bf)
             self.hmid = torch.zeros(R * k, cfg.moe_inter, **bf)
+            # decode-sized batches: one fixed row tile per local expert, row counters per layer zeroed once a step
+            from ..ops.kernels import static_plan
+            n_slots = cfg.n_layers + len(w.mtp)
+            self.route_cnt = torch.zeros(n_slots, el, **i32)
+            self.static_rows = [nt for nt in (16, 32, 64) if el * nt <= R * k]
+            self.static_plans = {}
+            for nt in self.static_rows:
+                base = static_plan(nt, el, self.route_cnt[0])
+                self.static_plans[nt] = [base] + [static_plan(nt, el, self.route_cnt[j], base)
+                                                  for j in range(1, n_slots)]
             self.route_out = torch.zeros(R, self.slots, H, **bf)
         L = max_logit_rows
         self.h_last = torch.zeros(L, H, **bf)
@@ -347,6 +357,7 @@ class CudaForward:
         import os
         self.l2_prefetch_bytes = int(float(os.environ.get("FERRULE_L2_PREFETCH_MB", "0")) * (1 << 20))
         self.telemetry = None      # utils.telemetry.ExpertTelemetry fed by the streamed path
+        self.static_moe = os.environ.get("FERRULE_STATIC_MOE", "1") != "0"
 
     # -- sublayers -----------------------------------------------------------------------
     # -- linear dispatch -------------------------------------------------------------------
@@ -400,6 +411,19 @@ class CudaForward:
         est = T * cfg.topk / max(cfg.n_routed_experts, 1)
         return _pow2_at_least(2 * est, 16, 128)
 
+    def _static_rows(self, lw: LayerWeights, T: int, layer: int) -> int:
+        """Row-slot size of the static plan for this batch, 0 when the planned path must run (large batches,
+        quantised or streamed experts, a hidden size the fused router does not take)."""
+        ws = self.ws
+        if not self.static_moe or layer < 0 or layer >= ws.route_cnt.shape[0] or self.cfg.hidden % 256:
+            return 0
+        if isinstance(lw.e_w13, QuantWeight) or (self.arena is not None and layer in self.arena.layers):
+            return 0
+        for nt in ws.static_rows:
+            if T <= nt:
+                return nt
+        return 0
+
     def _moe_local(self, lw: LayerWeights, xn: torch.Tensor, b: DeviceBatch, T: int, layer: int = -1):
         """Router + local routed experts + shared experts -> ws.route_out filled for this rank."""
         K, cfg, ws = self.K, self.cfg, self.ws
@@ -424,6 +448,21 @@ class CudaForward:
                 mid = ws.ffn_mid[:T, :inter]
                 self._gemm(xn, lw.w13, mid, xq=xq_n, epilogue=K.EPI_SWIGLU, act_limit=cfg.swiglu_limit)
                 self._gemm(mid, lw.w2, ws.route_out[:T][:, k], slot="mid")
+        static = self._static_rows(lw, T, layer)
+        if static:
+            # no plan phase and no gather kernel: the router reserves rows in fixed per-expert slots
+            plan = ws.static_plans[static][layer]
+            K.router_append(xn, lw.router_w, k, cfg.score_fn, plan, self.w.e_lo, self.w.e_hi, idx, wts, ws.xg,
+                            bias=lw.router_bias, n_groups=cfg.n_groups, topk_groups=cfg.topk_groups,
+                            normalize=cfg.norm_topk_prob, route_scale=cfg.route_scale, hash_table=lw.hash_table,
+                            token_ids=b.token_ids, dst_slots=ws.slots)
+            R = plan.cap_rows
+            K.gemm(ws.xg[:R], lw.e_w13, out=ws.hmid[:R], epilogue=K.EPI_SWIGLU, plan=plan, act_limit=cfg.swiglu_limit)
+            K.gemm(ws.hmid[:R], lw.e_w2, out=ws.route_out[:T].view(T * ws.slots, H), epilogue=K.EPI_SCATTER,
+                   plan=plan, scatter_rows=T * ws.slots)
+            if side is not None:
+                torch.cuda.current_stream().wait_stream(side)
+            return idx
         if T <= self.fused_router_rows and H % 256 == 0:
             K.router_plan_fused(xn, lw.router_w, k, cfg.score_fn, plan, self.w.e_lo, self.w.e_hi, idx, wts,
                                 ws.router_ctr, bias=lw.router_bias, n_groups=cfg.n_groups,
@@ -548,6 +587,8 @@ class CudaForward:
         ws = self.ws
         if h.data_ptr() != ws.h[0].data_ptr():
             ws.h[0][:T].copy_(h)
+        if ws.has_moe and ws.static_rows and T <= ws.static_rows[-1]:
+            ws.route_cnt.zero_()
         h, other = ws.h[0][:T], ws.h[1][:T]
         for i, lw in enumerate(self.w.layers):
             h = self.layer(lw, i, h, other, b, T)
@@ -589,6 +630,8 @@ class CudaForward:
         T = b.token_ids.shape[0]
         H = cfg.hidden
         x = ws.mtp_x[:T]
+        if ws.has_moe and ws.static_rows and T <= ws.static_rows[-1]:
+            ws.route_cnt[cfg.n_layers + stage].zero_()
         K.add_rmsnorm(h_prev, m.hnorm, cfg.rms_eps, norm_out=x[:, :H])
         e = ws.h[1][:T]
         K.embedding(b.token_ids[:T], self.w.embed, out=e)

@@ -32,6 +32,8 @@ def declare(lib) -> None:
         "fb_router_plan_fused": ([vp, ll, vp, i, vp, vp, vp, i, i, i, i, i, i, i, f, vp, vp, i, i, i, i,
                                   vp, vp, vp, vp, vp, vp, i, vp, vp, vp, vp, vp], i),
         "fb_argmax_chunked": ([vp, ll, i, i, i, vp, vp, vp, vp, vp, vp], i),
+        "fb_router_append": ([vp, ll, vp, i, vp, vp, vp, i, i, i, i, i, i, i, f, vp, vp, i, i, i, i, vp, vp, vp, vp, vp, ll,
+                              vp, vp], i),
         "fb_l2_prefetch": ([vp, ll, vp], i),
         # quant.cu
         "fb_quant_fp8_rows": ([vp, ll, vp, ll, vp, ll, i, i, i, vp], i),

@@ -302,6 +302,41 @@ def router_plan_fused(x: torch.Tensor, w: torch.Tensor, topk: int, score_fn: int
                                    status_tensor(x.device).data_ptr(), stream_ptr()), "fb_router_plan_fused")
 
 
+def static_plan(ntok: int, local_experts: int, counts: torch.Tensor, shared: Optional[MoePlan] = None) -> MoePlan:
+    """Plan with one row tile per local expert at fixed rows [e * ntok, (e + 1) * ntok); `counts` (the per-expert
+    row counters the router fills) doubles as the tile row counts.  `shared` lends its row tables (they are
+    rewritten by every router launch, so the layers of a model can share them)."""
+    dev = counts.device
+    i32 = dict(dtype=torch.int32, device=dev)
+    cap = local_experts * ntok
+    if shared is None:
+        ar = torch.arange(local_experts, **i32)
+        return MoePlan(ntok, local_experts, cap, torch.zeros(cap, **i32), torch.zeros(cap, **i32),
+                       torch.zeros(cap, dtype=torch.float32, device=dev), ar, ar * ntok, counts, counts,
+                       torch.tensor([local_experts, cap], **i32))
+    return MoePlan(ntok, local_experts, cap, shared.src_token, shared.dst_row, shared.row_scale, shared.tile_group,
+                   shared.tile_row0, counts, counts, shared.meta)
+
+
+def router_append(x: torch.Tensor, w: torch.Tensor, topk: int, score_fn: int, plan: MoePlan, e_lo: int, e_hi: int,
+                  out_idx: torch.Tensor, out_w: torch.Tensor, xg: torch.Tensor, *,
+                  bias: Optional[torch.Tensor] = None, n_groups: int = 1, topk_groups: int = 1,
+                  normalize: bool = False, route_scale: float = 1.0, hash_table: Optional[torch.Tensor] = None,
+                  token_ids: Optional[torch.Tensor] = None, dst_slots: int = 0) -> None:
+    """Router + top-k + row reservation in a static plan + activation gather, one launch (one CTA per token).
+    `plan.counts` must be zero on entry."""
+    lib = get_lib(True)
+    rows, hidden = x.shape
+    assert rows <= plan.ntok and xg.shape[0] >= plan.cap_rows and xg.shape[1] == hidden and w.is_contiguous()
+    assert plan.max_tiles == e_hi - e_lo
+    check(lib.fb_router_append(x.data_ptr(), x.stride(0), w.data_ptr(), hidden, ptr(bias), ptr(hash_table),
+                               ptr(token_ids), rows, w.shape[0], topk, score_fn, n_groups, topk_groups,
+                               1 if normalize else 0, route_scale, out_idx.data_ptr(), out_w.data_ptr(), e_lo, e_hi,
+                               plan.ntok, dst_slots, plan.counts.data_ptr(), plan.src_token.data_ptr(),
+                               plan.dst_row.data_ptr(), plan.row_scale.data_ptr(), xg.data_ptr(), xg.stride(0),
+                               status_tensor(x.device).data_ptr(), stream_ptr()), "fb_router_append")
+
+
 def topk_logits(logits: torch.Tensor, k: int):
     lib = get_lib(True)
     rows, vocab = logits.shape

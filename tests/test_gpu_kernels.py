@@ -378,6 +378,52 @@ def test_router_plan_fused(K, T, E, k, H, score, groups, tg):
     assert torch.equal(plan.counts.cpu(), plan2.counts.cpu())
 
 
+@pytest.mark.parametrize("T,E,k,H,I", [(32, 64, 6, 2048, 1408), (5, 64, 6, 2048, 1408), (64, 32, 8, 1024, 512)])
+def test_router_append_static_plan(K, T, E, k, H, I):
+    """Static one-tile-per-expert plan: same routes as the planned path, and the grouped GEMM pair over it (with
+    empty experts skipped) gives the same per-route outputs."""
+    x = rnd(T, H)
+    w = rnd(E, H, scale=0.05)
+    e_lo, e_hi = E // 4, E
+    el = e_hi - e_lo
+    nt = 16 if T <= 16 else (32 if T <= 32 else 64)
+    w13 = rnd(el, 2 * I, H, scale=0.03)
+    w2 = rnd(el, H, I, scale=0.03)
+    slots = k + 1
+    cnt = torch.zeros(2, el, dtype=torch.int32, device="cuda")
+    base = K.static_plan(nt, el, cnt[0])
+    plan = K.static_plan(nt, el, cnt[1], base)
+    idx = torch.zeros(T, k, dtype=torch.int32, device="cuda")
+    wts = torch.zeros(T, k, device="cuda")
+    xg = torch.zeros(el * nt, H, dtype=torch.bfloat16, device="cuda")
+    hmid = torch.zeros(el * nt, I, dtype=torch.bfloat16, device="cuda")
+    out = torch.zeros(T * slots, H, dtype=torch.bfloat16, device="cuda")
+    for _ in range(2):
+        cnt.zero_()
+        K.router_append(x, w, k, 0, plan, e_lo, e_hi, idx, wts, xg, normalize=True, route_scale=1.5, dst_slots=slots)
+        K.gemm(xg, w13, out=hmid, epilogue=K.EPI_SWIGLU, plan=plan)
+        K.gemm(hmid, w2, out=out, epilogue=K.EPI_SCATTER, plan=plan, scatter_rows=T * slots)
+    torch.cuda.synchronize()
+    from ferrule_b200.ops import _lib
+    assert _lib.read_status()[0] == 0
+    # planned path on the same routes
+    plan2 = K.MoePlan.allocate(T * k, el, 16, "cuda")
+    K.moe_plan(idx, wts, plan2, e_lo, e_hi, dst_slots=slots)
+    xg2 = torch.zeros(T * k, H, dtype=torch.bfloat16, device="cuda")
+    K.gather_rows(x, plan2, xg2, cap_rows=T * k)
+    hmid2 = torch.zeros(T * k, I, dtype=torch.bfloat16, device="cuda")
+    out2 = torch.zeros(T * slots, H, dtype=torch.bfloat16, device="cuda")
+    K.gemm(xg2, w13, out=hmid2, epilogue=K.EPI_SWIGLU, plan=plan2)
+    K.gemm(hmid2, w2, out=out2, epilogue=K.EPI_SCATTER, plan=plan2, scatter_rows=T * slots)
+    torch.cuda.synchronize()
+    assert torch.equal(cnt[1].cpu(), plan2.counts.cpu()) and int(cnt[0].sum()) == 0
+    assert int(cnt[1].sum()) == int(((idx >= e_lo) & (idx < e_hi)).sum())
+    local = ((idx >= e_lo) & (idx < e_hi)).cpu()
+    o1 = out.view(T, slots, H)[:, :k].float().cpu()
+    o2 = out2.view(T, slots, H)[:, :k].float().cpu()
+    assert torch.equal(o1[local], o2[local])
+
+
 def test_bounded_wait_reports_timeout_and_context_stays_usable():
     """Failure detection on the device: a wait on a flag that nothing sets gives up after its limit, records a
     status word (no trap, no hang) and later kernels still run."""
