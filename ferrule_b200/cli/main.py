@@ -54,6 +54,8 @@ def build_engine(args):
         from ..io.checkpoint import load_deepseek_hf
         weights = load_deepseek_hf(args.model_dir, device=dev, dtype=torch.bfloat16 if dev != "cpu" else torch.float32)
         name = os.path.basename(os.path.normpath(args.model_dir))
+    elif args.preset == "tiny-v4":
+        return _build_v4_engine(args, dev)
     else:
         cfg = C.PRESETS[args.preset]()
         weights = W.random_weights(cfg, device=dev, dtype=torch.bfloat16 if dev != "cpu" else torch.float32,
@@ -75,6 +77,30 @@ def build_engine(args):
     eng = Engine(runner, EngineConfig(scheduler=sched, kv_pages=n_pages, page_size=args.page_size,
                                       speculative=args.speculative, max_draft=args.max_draft))
     return eng, load_tokenizer(args.model_dir), name
+
+
+def _build_v4_engine(args, dev):
+    """Random-init DeepSeek-V4 family model (tiny shape) behind the engine: slot-bound state, one token per
+    sequence per step."""
+    import torch
+
+    from ..models.v4_model import random_v4_weights, tiny_v4
+    from ..models.v4_runner import V4Runner
+    from ..runtime.engine import Engine, EngineConfig
+    from ..runtime.scheduler import SchedulerConfig
+    from ..utils.tokenizer import load_tokenizer
+    cfg = tiny_v4()
+    weights = random_v4_weights(cfg, device=dev, seed=args.seed)
+    ctx = min(args.ctx_size, cfg.max_position)
+    pages_per_seq = (ctx + args.page_size - 1) // args.page_size
+    n_pages = args.max_seqs * pages_per_seq + 8
+    runner = V4Runner(weights, n_pages=n_pages, page_size=args.page_size, max_seqs=args.max_seqs,
+                      max_seq_len=pages_per_seq * args.page_size, max_rows=args.max_batch_tokens)
+    sched = SchedulerConfig(max_active_sequences=args.max_seqs, max_decode_batch=args.max_seqs,
+                            max_batch_tokens=args.max_batch_tokens, prefill_chunk_size=args.prefill_chunk,
+                            ctx_size=pages_per_seq * args.page_size)
+    eng = Engine(runner, EngineConfig(scheduler=sched, kv_pages=n_pages, page_size=args.page_size))
+    return eng, load_tokenizer(None), "deepseek-v4-tiny"
 
 
 # ------------------------------------------------------------------------------------------ commands

@@ -140,6 +140,7 @@ typedef struct FbAttnArgs {
   void* merge_ctr;          // optional: zeroed uint32 [ceil(rows/group_rows) * head blocks]; merges in-kernel
   const int* selection;     // optional [rows, sel_width] explicit pool rows per query row, -1 = masked
   int sel_width;            //   (then block_table / row_seq / row_pos are unused and group_rows must be 1)
+  void* trace;              // optional uint64 [32]: globaltimer stamps of CTA (0,0,0) (profiling)
 } FbAttnArgs;
 
 int fb_mla_attention(const FbAttnArgs* args, void* stream);

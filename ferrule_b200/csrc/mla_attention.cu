@@ -53,6 +53,7 @@ struct AttnParams {
   const int* selection;     // optional [rows, sel_width] pool rows per query row (-1 = masked); group_rows == 1
   int sel_width;
   DeviceStatus* status;
+  unsigned long long* trace;  // optional: CTA (0,0,0) writes globaltimer stamps of its milestones
 };
 
 __device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], uint32_t addr) {
@@ -126,6 +127,9 @@ mla_attention_kernel(const AttnParams p) {
   const int qgroup = blockIdx.x, split = blockIdx.y, hblock = blockIdx.z;
   const int qrow0 = qgroup * G;
   if (qrow0 >= p.rows) return;
+  const bool tracing = p.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && tid == 0;
+  int stamp = 0;
+  if (tracing) p.trace[stamp++] = globaltimer_ns();      // entry (dependency wait passed)
 
   if (tid == 0) {
     mbar_init(bar, kKvTile);
@@ -164,6 +168,7 @@ mla_attention_kernel(const AttnParams p) {
     if (seq_ok && qr_hi < p.rows && (g + 8) / Hb < G) kvlen_hi = by_selection ? p.sel_width : p.row_pos[qr_hi] + 1;
   }
   __syncthreads();
+  if (tracing) p.trace[stamp++] = globaltimer_ns();      // query tile staged
 
   const int kv_begin = split * p.split_tokens;
   const int kv_end = min(kv_len_max, kv_begin + p.split_tokens);
@@ -214,6 +219,7 @@ mla_attention_kernel(const AttnParams p) {
     phase ^= 1u;
     __syncthreads();  // zero-filled rows visible to all
     if (!ok || *abort_flag) { ok = false; break; }
+    if (tracing && stamp < 24) p.trace[stamp++] = globaltimer_ns();    // KV tile landed
 
     // ---- S = Q K^T for this warp's 16 tokens ----
     float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
@@ -230,6 +236,7 @@ mla_attention_kernel(const AttnParams p) {
         mma_bf16_16816(s1, a, b[2], b[3]);
       }
     }
+    if (tracing && stamp < 24) p.trace[stamp++] = globaltimer_ns();    // scores done
     // ---- scale, mask, tile max ----
     const int tok_base = tile0 + warp * 16 + t4 * 2;
     float tmax_lo = -INFINITY, tmax_hi = -INFINITY;
@@ -288,6 +295,7 @@ mla_attention_kernel(const AttnParams p) {
       o_acc[i][3] *= alpha_hi;
     }
     __syncthreads();
+    if (tracing && stamp < 24) p.trace[stamp++] = globaltimer_ns();    // softmax done
 
     // ---- O += P V for this warp's slice of the latent dims ----
     {
@@ -308,7 +316,9 @@ mla_attention_kernel(const AttnParams p) {
       }
     }
     __syncthreads();  // KV tile and P are free for the next iteration
+    if (tracing && stamp < 24) p.trace[stamp++] = globaltimer_ns();    // PV done
   }
+  if (tracing) { stamp = 24; p.trace[stamp++] = globaltimer_ns(); }  // tile loop left
 
   // ---- combine the per-warp partial row sums ----
   l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1);
@@ -343,6 +353,7 @@ mla_attention_kernel(const AttnParams p) {
       }
     }
     cluster_sync_all();
+    if (tracing) p.trace[stamp++] = globaltimer_ns();                  // all splits parked their partials
     const int CS = static_cast<int>(cluster_nctarank());
     const int crank = static_cast<int>(cluster_ctarank());
     const int slice = DL / CS;                       // latent dims merged by this CTA
@@ -374,6 +385,7 @@ mla_attention_kernel(const AttnParams p) {
       for (int c = 0; c < CS; ++c) wsm[r * 8 + c] = mv[c] * inv;
     }
     __syncthreads();
+    if (tracing) p.trace[stamp++] = globaltimer_ns();                  // split weights ready
     const int vec_per_row = slice / 4;
     for (int item = tid; item < 16 * vec_per_row; item += kAttnThreads) {
       const int r = item / vec_per_row, d = crank * slice + (item - r * vec_per_row) * 4;
@@ -389,7 +401,9 @@ mla_attention_kernel(const AttnParams p) {
       *reinterpret_cast<uint32_t*>(o) = pack_bf16(acc[0], acc[1]);
       *reinterpret_cast<uint32_t*>(o + 2) = pack_bf16(acc[2], acc[3]);
     }
+    if (tracing) p.trace[stamp++] = globaltimer_ns();                  // merged slice written
     cluster_sync_all();   // peers may still be reading this CTA's shared memory
+    if (tracing) p.trace[stamp++] = globaltimer_ns();
     return;
   }
 
@@ -621,6 +635,7 @@ extern "C" int fb_mla_attention(const FbAttnArgs* a, void* stream_) {
   p.selection = a->selection;
   p.sel_width = a->sel_width;
   p.status = static_cast<DeviceStatus*>(a->status);
+  p.trace = static_cast<unsigned long long*>(a->trace);
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   if (a->kv_lora == 512 && a->rope_dim == 64) return launch_attn<512, 64>(p, stream);
   if (a->kv_lora == 64 && a->rope_dim == 16) return launch_attn<64, 16>(p, stream);

@@ -280,13 +280,15 @@ class CudaWorkspace:
             self.plans = {}
             for ntok in (16, 32, 64, 128):
                 self.plans[ntok] = MoePlan.allocate(R * k, el, ntok, device)
-            self.xg = torch.zeros(R * k, H, **bf)
-            self.hmid = torch.zeros(R * k, cfg.moe_inter, **bf)
+            # expert-major rows: routes of the largest batch, or the static decode layout (64 rows per local expert)
+            xrows = max(R * k, el * 64)
+            self.xg = torch.zeros(xrows, H, **bf)
+            self.hmid = torch.zeros(xrows, cfg.moe_inter, **bf)
             # decode-sized batches: one fixed row tile per local expert, row counters per layer zeroed once a step
             from ..ops.kernels import static_plan
             n_slots = cfg.n_layers + len(w.mtp)
             self.route_cnt = torch.zeros(n_slots, el, **i32)
-            self.static_rows = [nt for nt in (16, 32, 64) if el * nt <= R * k]
+            self.static_rows = [16, 32, 64]
             self.static_plans = {}
             for nt in self.static_rows:
                 base = static_plan(nt, el, self.route_cnt[0])

@@ -1,0 +1,171 @@
+"""Engine runner for the DeepSeek-V4 family: hyper-connections, compressed + indexed sparse attention and hash /
+learned routing behind the same transaction contract as the MLA runner.
+
+The V4 attention state of a sequence is not a pool of uniform KV pages: per layer it is a raw sliding window, a
+plane of compressed rows (one per `ratio` tokens), the compressor's projected inputs and, on indexed layers, the
+indexer's own compressed plane.  `V4Cuda` keeps those as position-indexed tables per state slot, so this runner
+binds state by slot (`KvBindingMode` stays paged for the engine's page accounting: pages are the admission
+budget, the tables are what the kernels read).  Every table row is addressed by (slot, position): re-executing a
+position after an abort or a rejected draft simply overwrites it, which is what makes transactions abortable
+without a snapshot.
+
+Prefill runs token by token through the decode step (one row per sequence per launch group): correct, and as
+fast as decode; a chunked V4 prefill kernel path does not exist yet.  Preemption with page snapshots is refused:
+the slot tables are the state, and the engine option that needs snapshots (`auto_preempt`) must stay off.
+
+Counterpart of the V4 runtime of the reference (crates/ferrule-model/src/deepseek_v4/: model assembly, state
+pools for window / compressed / indexer planes, one-token decode schedule).
+"""
+from __future__ import annotations
+
+import time
+from typing import Dict, List, Sequence
+
+import torch
+
+from ..runtime.execution import (ExecutionBatch, ExecutionCapabilities, ExecutionOutput, KvLayoutSchema,
+                                 KvPlaneDescriptor, LogitsKind, RowOutput)
+from ..runtime.runner import Complete, EndIntent, EndStatus, ModelRunner
+from .v4_model import V4Cuda, V4Reference, V4SeqCache, V4Weights
+
+
+def _truncate(c: V4SeqCache, cfg, pos: int) -> None:
+    """Oracle cache back to `pos` committed tokens (rows past it came from an aborted or rejected step)."""
+    for i in range(cfg.n_layers):
+        del c.kv[i][pos:]
+        r = cfg.ratio(i)
+        if r:
+            del c.comp[i][pos // r:]
+            del c.icomp[i][pos // r:]
+        del c.cstate[i].kv[pos:]
+        del c.cstate[i].gate[pos:]
+        del c.istate[i].kv[pos:]
+        del c.istate[i].gate[pos:]
+    c.position = pos
+
+
+class V4Runner(ModelRunner):
+    def __init__(self, weights: V4Weights, n_pages: int, page_size: int = 64, max_seqs: int = 8,
+                 max_seq_len: int = 1024, max_rows: int = 2048, eos_token_id: int = -1):
+        self.w, self.cfg = weights, weights.cfg
+        self.device = weights.embed.device
+        self.is_cuda = self.device.type == "cuda"
+        self.vocab_size, self.eos_token_id = self.cfg.vocab_size, eos_token_id
+        self.page_size, self.n_pages = page_size, n_pages
+        self.max_seqs, self.max_seq_len, self.max_rows = max_seqs, max_seq_len, max_rows
+        if self.is_cuda:
+            self.fwd = V4Cuda(weights, max_seqs, max_seq_len)
+        else:
+            self.fwd = V4Reference(weights)
+            self.caches: Dict[int, V4SeqCache] = {}
+        self.txns: Dict[int, ExecutionBatch] = {}
+        self.steps = 0
+        self.forward_ns = 0
+
+    # ------------------------------------------------------------------ contract
+    def capabilities(self) -> ExecutionCapabilities:
+        return ExecutionCapabilities(max_batch_rows=self.max_rows, max_sequences=self.max_seqs, max_topk=40,
+                                     supports_provisional=True, supports_full_logits=False)
+
+    def kv_schema(self) -> KvLayoutSchema:
+        cfg = self.cfg
+        planes = [KvPlaneDescriptor("window_kv", cfg.head_dim, cfg.n_layers)]
+        n_comp = sum(1 for i in range(cfg.n_layers) if cfg.ratio(i))
+        n_idx = sum(1 for i in range(cfg.n_layers) if cfg.has_indexer(i))
+        if n_comp:
+            planes.append(KvPlaneDescriptor("compressed_kv", cfg.head_dim, n_comp))
+        if n_idx:
+            planes.append(KvPlaneDescriptor("indexer_plane", cfg.index_head_dim, n_idx))
+        return KvLayoutSchema(tuple(planes), self.page_size, self.max_seq_len)
+
+    def prepare_batch(self, txn_id: int, batch: ExecutionBatch) -> None:
+        batch.validate(self.capabilities())
+        for s in batch.sequences:
+            if s.cow:
+                raise RuntimeError("V4 state is bound by slot: shared (copy-on-write) pages are not supported")
+            if s.state_slot >= self.max_seqs or s.sequence_len > self.max_seq_len:
+                raise RuntimeError(f"sequence in slot {s.state_slot} exceeds the runner's tables")
+        self.txns[txn_id] = batch
+
+    def execute(self, txn_id: int):
+        b = self.txns[txn_id]
+        t0 = time.perf_counter_ns()
+        with torch.no_grad():
+            out = self._execute_cuda(b) if self.is_cuda else self._execute_reference(b)
+        self.forward_ns += time.perf_counter_ns() - t0
+        return Complete(out)
+
+    def resume(self, txn_id: int):
+        return self.execute(txn_id)
+
+    def end_transaction(self, txn_id: int, intent: EndIntent) -> EndStatus:
+        self.txns.pop(txn_id, None)        # aborted rows are overwritten when their positions run again
+        return EndStatus.COMPLETE
+
+    def release_pages(self, pages: Sequence[int]) -> None:
+        pass
+
+    def snapshot_pages(self, pages):
+        raise RuntimeError("V4 state is bound by slot; preemption with page snapshots is not supported")
+
+    def restore_pages(self, pages, snapshot) -> None:
+        raise RuntimeError("V4 state is bound by slot; preemption with page snapshots is not supported")
+
+    def release_slot(self, state_slot: int) -> None:
+        if self.is_cuda:
+            self.fwd.positions[state_slot] = 0
+        else:
+            self.caches.pop(state_slot, None)
+
+    def observability(self) -> Dict[str, object]:
+        return {"model": "deepseek-v4", "decode_steps": self.steps, "forward_ms": self.forward_ns / 1e6}
+
+    # ------------------------------------------------------------------ execution
+    @staticmethod
+    def _rows_out(b: ExecutionBatch, logits_by_row: Dict[int, torch.Tensor]) -> ExecutionOutput:
+        from ..ops import reference as ref
+        rows: List[RowOutput] = []
+        for r in sorted(logits_by_row):
+            k = max(b.logits[r].k, 1)
+            ids, vals = ref.topk_logits(logits_by_row[r][None].float().cpu(), k)
+            keep = [(int(a), float(v)) for a, v in zip(ids[0], vals[0]) if torch.isfinite(v)]
+            rows.append(RowOutput(r, [a for a, _ in keep], [v for _, v in keep]))
+        return ExecutionOutput(rows)
+
+    def _execute_cuda(self, b: ExecutionBatch) -> ExecutionOutput:
+        """Wave j feeds the j-th row of every sequence that still has one: all sequences advance together, one
+        token each, through the batched decode step."""
+        fwd = self.fwd
+        for s in b.sequences:
+            fwd.positions[s.state_slot] = s.context_len
+        want: Dict[int, torch.Tensor] = {}
+        waves = max(s.query_len for s in b.sequences)
+        for j in range(waves):
+            live = [s for s in b.sequences if s.query_len > j]
+            slots = [s.state_slot for s in live]
+            rows = [s.query_start + j for s in live]
+            for s, r in zip(live, rows):
+                assert b.positions[r] == s.context_len + j, "rows of a sequence must be consecutive positions"
+            _, logits = fwd.step(slots, [b.token_ids[r] for r in rows])
+            self.steps += 1
+            for i, r in enumerate(rows):
+                if b.logits[r].kind != LogitsKind.NONE:
+                    want[r] = logits[i]
+        return self._rows_out(b, want)
+
+    def _execute_reference(self, b: ExecutionBatch) -> ExecutionOutput:
+        want: Dict[int, torch.Tensor] = {}
+        for s in b.sequences:
+            c = self.caches.get(s.state_slot)
+            if c is None or s.context_len == 0:
+                c = self.caches[s.state_slot] = V4SeqCache(self.cfg)
+            if c.position != s.context_len:
+                assert c.position > s.context_len, "sequence state is behind the committed length"
+                _truncate(c, self.cfg, s.context_len)
+            for j in range(s.query_len):
+                r = s.query_start + j
+                logits = self.fwd.step(c, b.token_ids[r])
+                self.steps += 1
+                if b.logits[r].kind != LogitsKind.NONE:
+                    want[r] = logits
+        return self._rows_out(b, want)

@@ -66,7 +66,7 @@ class AttnArgs(C.Structure):
         ("num_seqs", C.c_int), ("max_blocks", C.c_int), ("page_size", C.c_int),
         ("group_rows", C.c_int), ("splits", C.c_int), ("split_tokens", C.c_int),
         ("softmax_scale", C.c_float), ("merge_ctr", C.c_void_p),
-        ("selection", C.c_void_p), ("sel_width", C.c_int),
+        ("selection", C.c_void_p), ("sel_width", C.c_int), ("trace", C.c_void_p),
     ]
 
 

@@ -370,7 +370,8 @@ def mla_attention(q: torch.Tensor, kv_layer: torch.Tensor, block_table: torch.Te
                   row_seq: torch.Tensor, row_pos: torch.Tensor, page_size: int, kv_lora: int,
                   rope_dim: int, scale: float, out: torch.Tensor, *, splits: int = 1,
                   split_tokens: int = 1 << 20, ws: Optional[AttnWorkspace] = None,
-                  sink: Optional[torch.Tensor] = None, group_rows: int = 1) -> torch.Tensor:
+                  sink: Optional[torch.Tensor] = None, group_rows: int = 1,
+                  trace: Optional[torch.Tensor] = None) -> torch.Tensor:
     """q [rows, heads, D] bf16; kv_layer [..., D] bf16 (any leading shape, contiguous rows)."""
     lib = get_lib(True)
     rows, heads, D = q.shape
@@ -390,5 +391,6 @@ def mla_attention(q: torch.Tensor, kv_layer: torch.Tensor, block_table: torch.Te
     a.num_seqs, a.max_blocks, a.page_size = block_table.shape[0], block_table.shape[1], page_size
     a.group_rows, a.splits, a.split_tokens = group_rows, splits, split_tokens
     a.softmax_scale = scale
+    a.trace = ptr(trace)
     check(lib.fb_mla_attention(C.byref(a), stream_ptr()), "fb_mla_attention")
     return out
