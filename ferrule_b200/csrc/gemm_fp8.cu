@@ -20,6 +20,7 @@
 // (crates/ferrule-backend/native/cuda/implementations/cutlass/capabilities/fp8_projection.cuh:421-497,
 // shared_ffn.cuh:477-594) and of the FP8 kinds of its row-dot linear (portable/entrypoints.cu:208-284).
 #include <cuda.h>
+#include <cstdlib>
 
 #include "common.cuh"
 #include "ferrule_b200.h"
@@ -54,6 +55,7 @@ struct Params {
   const float* row_scale;
   float act_limit;
   DeviceStatus* status;
+  int w_stream;              // weights are read once by this launch: L2 evict-first loads
 };
 
 __device__ __forceinline__ float e8m0(uint8_t b) {
@@ -142,6 +144,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
       uint32_t ph = 0;
       bool ok = true;
       long long issued = 0;
+      const uint64_t wpol = l2_policy_evict_first();
       for (int t = tile_first; t < total && ok; t += tile_stride) {
         const int m = t / p.n_tiles, nt = t - m * p.n_tiles;
         const int g = grouped ? p.tile_group[m] : 0;
@@ -151,8 +154,14 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
           if (!ok) break;
           uint8_t* stage = smem + s * C::kStageBytes;
           mbar_arrive_expect_tx(&full_bar[s], C::kStageBytes);
-          tma_load_3d(stage, &tmap_w, &full_bar[s], kb * kBlockK, nt * kTileN, g);
-          if (DUAL) tma_load_3d(stage + C::kWBytes, &tmap_w, &full_bar[s], kb * kBlockK, p.dual_offset + nt * kTileN, g);
+          if (p.w_stream) {
+            tma_load_3d_hint(stage, &tmap_w, &full_bar[s], kb * kBlockK, nt * kTileN, g, wpol);
+            if (DUAL)
+              tma_load_3d_hint(stage + C::kWBytes, &tmap_w, &full_bar[s], kb * kBlockK, p.dual_offset + nt * kTileN, g, wpol);
+          } else {
+            tma_load_3d(stage, &tmap_w, &full_bar[s], kb * kBlockK, nt * kTileN, g);
+            if (DUAL) tma_load_3d(stage + C::kWBytes, &tmap_w, &full_bar[s], kb * kBlockK, p.dual_offset + nt * kTileN, g);
+          }
           tma_load_2d(stage + C::kWBytes * (DUAL ? 2 : 1), &tmap_x, &full_bar[s], kb * kBlockK, row0);
           ++issued;
           if (++s == nstages) { s = 0; ph ^= 1u; }
@@ -464,6 +473,13 @@ extern "C" int fb_gemm_fp8(const FbGemmFp8Args* a, void* stream_) {
   p.row_scale = a->row_scale;
   p.act_limit = a->act_limit;
   p.status = static_cast<DeviceStatus*>(a->status);
+  {
+    static const bool enabled = [] {
+      const char* e = getenv("FERRULE_W_EVICT_FIRST");
+      return !(e && e[0] == '0');
+    }();
+    p.w_stream = enabled && (grouped ? a->ntok <= 64 : a->x_rows <= 256);
+  }
   const int kblocks = (a->k + kBlockK - 1) / kBlockK;
   const int tok_tiles = grouped ? a->max_tok_tiles : (a->x_rows + a->ntok - 1) / a->ntok;
   const int max_tiles = tok_tiles * p.n_tiles;

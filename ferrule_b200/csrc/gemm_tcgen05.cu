@@ -21,6 +21,7 @@
 //  .../cutlass/capabilities/fp8_projection.cuh:421-497, bf16_compressor.cuh:223-313) and of
 // its CUTLASS grouped expert GEMM (.../architectures/sm103/grouped_fp4_moe.cuh:1115-1222).
 #include <cuda.h>
+#include <cstdlib>
 
 #include "common.cuh"
 #include "ferrule_b200.h"
@@ -68,6 +69,7 @@ struct GemmParams {
   uint32_t* peer_flags[8];   // per-tile arrival counters of every rank
   uint32_t* local_ctr;       // [0] = calls completed, [1] = CTAs finished this call, [2..] = consumed arrivals per tile
   int ar_bf16;               // kEpiAllReduce: partials travel as bf16 pairs instead of fp32
+  int w_stream;              // weights are read once by this launch: load them with the L2 evict-first policy
   int stage_store;           // bf16 store / SwiGLU / scatter epilogues of large row tiles: rows leave through a
                              // shared-memory staging tile as 256-byte row segments instead of 2-byte column stores
   const int* remap_rank;     // kEpiScatter, expert-parallel combine: output row -> destination rank ...
@@ -218,6 +220,12 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tmap_w,
       uint32_t ph = 0;
       bool ok = true;
       long long issued = 0;
+      const uint64_t wpol = l2_policy_evict_first();
+      const bool wstream = p.w_stream != 0;
+      auto load_w = [&](void* dst, uint64_t* bar, int c0, int c1, int c2) {
+        if (wstream) tma_load_3d_hint(dst, &tmap_w, bar, c0, c1, c2, wpol);
+        else tma_load_3d(dst, &tmap_w, bar, c0, c1, c2);
+      };
       // Weight tiles do not depend on the preceding kernel: request the first pipeline-full of
       // them before waiting for it, so they stream while that kernel drains.
       int pre = 0;
@@ -229,10 +237,8 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tmap_w,
             uint8_t* stage = smem + pre * Cfg::kStageBytes;
             const int kb = kb_begin + pre;
             mbar_arrive_expect_tx(&full_bar[pre], Cfg::kStageBytes);
-            tma_load_3d(stage, &tmap_w, &full_bar[pre], kb * kBlockK, ti.nt * kTileN, ti.g);
-            if (DUAL)
-              tma_load_3d(stage + Cfg::kWBytes, &tmap_w, &full_bar[pre], kb * kBlockK,
-                          p.dual_offset + ti.nt * kTileN, ti.g);
+            load_w(stage, &full_bar[pre], kb * kBlockK, ti.nt * kTileN, ti.g);
+            if (DUAL) load_w(stage + Cfg::kWBytes, &full_bar[pre], kb * kBlockK, p.dual_offset + ti.nt * kTileN, ti.g);
           }
         }
         pdl_wait();
@@ -251,10 +257,8 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tmap_w,
             ok = mbar_wait(&empty_bar[s], ph ^ 1u, abort_flag, p.status, 0x100);
             if (!ok) break;
             mbar_arrive_expect_tx(&full_bar[s], Cfg::kStageBytes);
-            tma_load_3d(stage, &tmap_w, &full_bar[s], kb * kBlockK, nt * kTileN, g);
-            if (DUAL)
-              tma_load_3d(stage + Cfg::kWBytes, &tmap_w, &full_bar[s], kb * kBlockK,
-                          p.dual_offset + nt * kTileN, g);
+            load_w(stage, &full_bar[s], kb * kBlockK, nt * kTileN, g);
+            if (DUAL) load_w(stage + Cfg::kWBytes, &full_bar[s], kb * kBlockK, p.dual_offset + nt * kTileN, g);
           }
           tma_load_2d(stage + Cfg::kWBytes * (DUAL ? 2 : 1), &tmap_x, &full_bar[s],
                       xk0 + kb * kBlockK, row0);
@@ -755,6 +759,14 @@ extern "C" int fb_gemm_bf16(const FbGemmArgs* a, void* stream_) {
   p.groups = a->groups;
   p.force_split = a->force_split;
   p.trace = static_cast<unsigned long long*>(a->trace);
+  {
+    // decode-sized launches read every weight byte once; larger ones re-read weight tiles across row tiles
+    static const bool enabled = [] {
+      const char* e = getenv("FERRULE_W_EVICT_FIRST");
+      return !(e && e[0] == '0');
+    }();
+    p.w_stream = enabled && (a->tile_group ? ntok <= 64 : a->x_rows <= 256);
+  }
   p.max_tok_tiles = a->max_tok_tiles;
   p.tile_group = a->tile_group;
   p.tile_row0 = a->tile_row0;

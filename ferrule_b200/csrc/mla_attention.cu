@@ -17,6 +17,8 @@
 // proposal attention (crates/ferrule-backend/native/cuda/implementations/cutlass/capabilities/
 // hybrid_mla_attention/schedules/bf16_mma.cuh:332-823, hybrid_mla_attention.cuh:521-641) and of
 // its CPU sink-softmax reference (crates/ferrule-model/src/attention_backend.rs:47-160).
+#include <cstdlib>
+
 #include "common.cuh"
 #include "ferrule_b200.h"
 #include "launch.cuh"
@@ -53,6 +55,7 @@ struct AttnParams {
   const int* selection;     // optional [rows, sel_width] pool rows per query row (-1 = masked); group_rows == 1
   int sel_width;
   DeviceStatus* status;
+  int kv_stream;            // decode-sized launch: KV rows are read once, load them with the L2 evict-first policy
   unsigned long long* trace;  // optional: CTA (0,0,0) writes globaltimer stamps of its milestones
 };
 
@@ -80,6 +83,14 @@ __device__ __forceinline__ void bulk_copy_g2s(void* dst, const void* src, uint32
       "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
           smem_u32(dst)),
       "l"(src), "r"(bytes), "r"(smem_u32(bar))
+      : "memory");
+}
+// KV rows of a decode step are read once: evict-first keeps the step's reusable lines in L2
+__device__ __forceinline__ void bulk_copy_g2s_stream(void* dst, const void* src, uint32_t bytes, uint64_t* bar,
+                                                     uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;"
+      ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)), "l"(policy)
       : "memory");
 }
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
@@ -137,7 +148,24 @@ mla_attention_kernel(const AttnParams p) {
     fence_barrier_init();
   }
 
-  // ---- query tile -> smem (rows beyond the valid set are zero) ----
+  if (tracing) p.trace[12] = globaltimer_ns();
+  // ---- query tile -> smem (rows beyond the valid set are zero).  The loads are issued first and parked in
+  // registers so that their latency overlaps the dependent row -> sequence -> length lookups below ----
+  constexpr int kQVecs = (16 * (D / 8) + kAttnThreads - 1) / kAttnThreads;
+  uint4 qv[kQVecs];
+  {
+    const int Hb0 = 16 / p.group_rows;
+#pragma unroll
+    for (int j = 0; j < kQVecs; ++j) {
+      const int i = tid + j * kAttnThreads;
+      const int r = i / (D / 8), c = i - r * (D / 8);
+      const int qr = blockIdx.x * p.group_rows + r / Hb0, h = blockIdx.z * Hb0 + r % Hb0;
+      qv[j] = make_uint4(0, 0, 0, 0);
+      if (i < 16 * (D / 8) && qr < p.rows && h < p.heads)
+        qv[j] = *reinterpret_cast<const uint4*>(p.q + qr * p.ldq + static_cast<long long>(h) * D + c * 8);
+    }
+  }
+  if (tracing) p.trace[13] = globaltimer_ns();
   const bool by_selection = p.selection != nullptr;
   const int* sel = by_selection ? p.selection + static_cast<long long>(qrow0) * p.sel_width : nullptr;
   int seq = by_selection ? 0 : p.row_seq[qrow0];
@@ -152,20 +180,20 @@ mla_attention_kernel(const AttnParams p) {
   if (!seq_ok) kv_len_max = 0;
   kv_len_max = by_selection ? p.sel_width : min(kv_len_max, p.max_blocks * p.page_size);
 
-  for (int i = tid; i < 16 * (D / 8); i += kAttnThreads) {
-    const int r = i / (D / 8), c = i - r * (D / 8);
-    const int qr = qrow0 + r / Hb, h = hblock * Hb + r % Hb;
-    uint4 v = make_uint4(0, 0, 0, 0);
-    if (qr < p.rows && h < p.heads)
-      v = *reinterpret_cast<const uint4*>(p.q + qr * p.ldq + static_cast<long long>(h) * D + c * 8);
-    *reinterpret_cast<uint4*>(Qs + r * kRowPad + c * 8) = v;
-  }
+  if (tracing) p.trace[14] = globaltimer_ns() + (kv_len_max == -12345);
   // per-thread row limits (rows g and g+8 of the tile)
   int kvlen_lo = 0, kvlen_hi = 0;
   {
     const int qr_lo = qrow0 + g / Hb, qr_hi = qrow0 + (g + 8) / Hb;
     if (seq_ok && qr_lo < p.rows && g / Hb < G) kvlen_lo = by_selection ? p.sel_width : p.row_pos[qr_lo] + 1;
     if (seq_ok && qr_hi < p.rows && (g + 8) / Hb < G) kvlen_hi = by_selection ? p.sel_width : p.row_pos[qr_hi] + 1;
+  }
+  if (tracing) p.trace[15] = globaltimer_ns() + (kvlen_lo + kvlen_hi == -12345);
+#pragma unroll
+  for (int j = 0; j < kQVecs; ++j) {
+    const int i = tid + j * kAttnThreads;
+    const int r = i / (D / 8), c = i - r * (D / 8);
+    if (i < 16 * (D / 8)) *reinterpret_cast<uint4*>(Qs + r * kRowPad + c * 8) = qv[j];
   }
   __syncthreads();
   if (tracing) p.trace[stamp++] = globaltimer_ns();      // query tile staged
@@ -181,6 +209,7 @@ mla_attention_kernel(const AttnParams p) {
   float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.f, l_hi = 0.f;
 
   const uint32_t qs_addr = smem_u32(Qs), kv_addr = smem_u32(KVs), ps_addr = smem_u32(Ps);
+  const uint64_t kv_policy = l2_policy_evict_first();
   uint32_t phase = 0;
   bool ok = true;
 
@@ -194,7 +223,8 @@ mla_attention_kernel(const AttnParams p) {
         const long long slot = sel[tok];
         if (slot >= 0 && slot < p.pool_rows) {
           mbar_arrive_expect_tx(bar, D * 2);
-          bulk_copy_g2s(dst, p.kv + slot * D, D * 2, bar);
+          if (p.kv_stream) bulk_copy_g2s_stream(dst, p.kv + slot * D, D * 2, bar, kv_policy);
+          else bulk_copy_g2s(dst, p.kv + slot * D, D * 2, bar);
           issued = true;
         } else if (slot >= 0) {
           report_status(p.status, kStatusBadIndex, 0x63, qrow0, tok);
@@ -204,7 +234,8 @@ mla_attention_kernel(const AttnParams p) {
         const long long slot = static_cast<long long>(page) * p.page_size + tok % p.page_size;
         if (page >= 0 && slot < p.pool_rows) {
           mbar_arrive_expect_tx(bar, D * 2);
-          bulk_copy_g2s(dst, p.kv + slot * D, D * 2, bar);
+          if (p.kv_stream) bulk_copy_g2s_stream(dst, p.kv + slot * D, D * 2, bar, kv_policy);
+          else bulk_copy_g2s(dst, p.kv + slot * D, D * 2, bar);
           issued = true;
         } else {
           report_status(p.status, kStatusBadIndex, 0x61, seq, tok);
@@ -358,31 +389,35 @@ mla_attention_kernel(const AttnParams p) {
     const int crank = static_cast<int>(cluster_ctarank());
     const int slice = DL / CS;                       // latent dims merged by this CTA
     const uint32_t osm_addr = smem_u32(Osm), msm_addr = smem_u32(Msm);
-    float* wsm = smax;                               // [16][CS] normalised split weights (CS <= 8)
-    if (tid < 16) {
-      const int r = tid;
+    float* wsm = smax;                               // [16][8] normalised split weights (CS <= 8)
+    {
+      // thread (r, c) fetches the statistics of split c for row r (one remote access each); the 8 lanes of a
+      // row then combine them with shuffles, in split order
+      const int r = tid >> 3, c = tid & 7;
       const int h = hblock * Hb + r % Hb;
-      float mv[8], lv[8];
-      float M = -INFINITY;
-      for (int c = 0; c < CS; ++c) {
+      float mv = -INFINITY, lv = 0.f;
+      if (c < CS) {
         const uint32_t ra = mapa_shared(msm_addr, c);
-        mv[c] = ld_cluster_f32(ra + r * 4);
-        lv[c] = ld_cluster_f32(ra + (16 + r) * 4);
-        M = fmaxf(M, mv[c]);
+        mv = ld_cluster_f32(ra + r * 4);
+        lv = ld_cluster_f32(ra + (16 + r) * 4);
       }
-      float L = 0.f;
+      float M = mv;
+#pragma unroll
+      for (int o = 1; o < 8; o <<= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
+      float sink_l = 0.f;
       if (p.sink && h < p.heads) {
         const float sk = p.sink[h] * 1.4426950408889634f;
         M = fmaxf(M, sk);
-        L = exp2f(sk - M);
+        sink_l = exp2f(sk - M);
       }
-      for (int c = 0; c < CS; ++c) {
-        const float w = (mv[c] == -INFINITY || lv[c] == 0.f) ? 0.f : exp2f(mv[c] - M);
-        mv[c] = w;
-        L += lv[c] * w;
-      }
+      const float w = (mv == -INFINITY || lv == 0.f) ? 0.f : exp2f(mv - M);
+      // fixed-order sum over the splits (lane c holds term c)
+      float L = sink_l;
+      const int lane_base = lane & ~7;
+#pragma unroll
+      for (int cc = 0; cc < 8; ++cc) L += __shfl_sync(0xffffffffu, lv * w, lane_base + cc);
       const float inv = L > 0.f ? 1.f / L : 0.f;
-      for (int c = 0; c < CS; ++c) wsm[r * 8 + c] = mv[c] * inv;
+      wsm[r * 8 + c] = w * inv;
     }
     __syncthreads();
     if (tracing) p.trace[stamp++] = globaltimer_ns();                  // split weights ready
@@ -636,6 +671,13 @@ extern "C" int fb_mla_attention(const FbAttnArgs* a, void* stream_) {
   p.sel_width = a->sel_width;
   p.status = static_cast<DeviceStatus*>(a->status);
   p.trace = static_cast<unsigned long long*>(a->trace);
+  {
+    static const bool enabled = [] {
+      const char* e = getenv("FERRULE_W_EVICT_FIRST");
+      return !(e && e[0] == '0');
+    }();
+    p.kv_stream = enabled && a->rows <= 128 && a->selection == nullptr;
+  }
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   if (a->kv_lora == 512 && a->rope_dim == 64) return launch_attn<512, 64>(p, stream);
   if (a->kv_lora == 64 && a->rope_dim == 16) return launch_attn<64, 16>(p, stream);
