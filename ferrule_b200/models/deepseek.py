@@ -92,6 +92,8 @@ class ReferenceForward:
     def __init__(self, weights: ModelWeights, pool: KvPool, emulate_bf16: bool = False):
         self.w, self.cfg, self.pool = weights, weights.cfg, pool
         self.rnd = ref.bf16_round if emulate_bf16 else (lambda t: t)
+        self.expert_gate = None        # callable(layer, local experts) used by the asynchronous expert streaming
+        self._layer_index = -1
         cfg = self.cfg
         dev = weights.embed.device
         cos, sin = ref.rope_tables(min(cfg.max_position, 1 << 16), cfg.qk_rope_dim, cfg.rope_theta,
@@ -151,6 +153,10 @@ class ReferenceForward:
                              route_scale=cfg.route_scale, hash_table=lw.hash_table, token_ids=token_ids)
         I = cfg.moe_inter
         out = torch.zeros_like(xn)
+        if self.expert_gate is not None:
+            # streamed experts: the gate raises when the batch routes to experts that are not resident
+            local = idx[(idx >= self.w.e_lo) & (idx < self.w.e_hi)] - self.w.e_lo
+            self.expert_gate(self._layer_index, sorted(set(local.flatten().tolist())))
         for e in range(self.w.e_lo, self.w.e_hi):
             hit = (idx == e)
             rows = hit.any(-1).nonzero().flatten()
@@ -167,6 +173,7 @@ class ReferenceForward:
     def layer(self, lw: LayerWeights, layer: int, h: torch.Tensor, b: DeviceBatch, allreduce=None) -> torch.Tensor:
         cfg, rnd = self.cfg, self.rnd
         T = h.shape[0]
+        self._layer_index = layer
         xn = rnd(ref.rmsnorm(h, lw.attn_norm, cfg.rms_eps))
         a = self._attention(lw, layer, xn, b)
         if allreduce is not None:
@@ -185,14 +192,23 @@ class ReferenceForward:
     def embed_rows(self, b: DeviceBatch) -> torch.Tensor:
         return self.w.embed[b.token_ids[:b.n_rows].long()].float()
 
-    def run_layers(self, h: torch.Tensor, b: DeviceBatch, allreduce=None) -> torch.Tensor:
-        """The layers this weight image holds (all of them, or one pipeline stage's share)."""
+    def run_layers(self, h: torch.Tensor, b: DeviceBatch, allreduce=None, start_layer: int = 0) -> torch.Tensor:
+        """The layers this weight image holds (all of them, or one pipeline stage's share), from `start_layer`
+        (a resumed transaction continues at the layer it stopped at, with that layer's input rows as `h`)."""
         for i, lw in enumerate(self.w.layers):
-            h = self.layer(lw, i, h, b, allreduce)
+            if i < start_layer:
+                continue
+            try:
+                h = self.layer(lw, i, h, b, allreduce)
+            except Exception as exc:  # noqa: BLE001
+                if hasattr(exc, "missing"):
+                    exc.hidden = h
+                raise
         return h
 
-    def hidden_states(self, b: DeviceBatch, allreduce=None) -> torch.Tensor:
-        return self.run_layers(self.embed_rows(b), b, allreduce)
+    def hidden_states(self, b: DeviceBatch, allreduce=None, start_layer: int = 0, h0=None) -> torch.Tensor:
+        h = self.embed_rows(b) if h0 is None else h0
+        return self.run_layers(h, b, allreduce, start_layer)
 
     def logits_from_hidden(self, h: torch.Tensor, b: DeviceBatch, final_norm=None) -> torch.Tensor:
         rows = b.logit_rows[:b.n_logit].long()
@@ -357,9 +373,12 @@ class CudaForward:
         # bytes of each MoE layer's routed-expert weights to prefetch into L2 during the attention half of a decode
         # layer (0 = off); the L2 holds 126 MB, the prefetch must leave room for the attention's own traffic
         import os
-        self.l2_prefetch_bytes = int(float(os.environ.get("FERRULE_L2_PREFETCH_MB", "0")) * (1 << 20))
+        # measured on one GPU with evict-first weight streaming: 0 / 32 / 64 / 96 MB -> 7.38 / 7.33 / 7.29 / 7.55 ms
+        self.l2_prefetch_bytes = int(float(os.environ.get("FERRULE_L2_PREFETCH_MB", "48")) * (1 << 20))
         self.telemetry = None      # utils.telemetry.ExpertTelemetry fed by the streamed path
         self.static_moe = os.environ.get("FERRULE_STATIC_MOE", "1") != "0"
+        self.async_stream = False  # streamed experts: stop at a layer with missing experts instead of uploading inline
+        self.lease_sink = None     # dict layer -> leases of the running transaction (set by the runner)
 
     # -- sublayers -----------------------------------------------------------------------
     # -- linear dispatch -------------------------------------------------------------------
@@ -502,6 +521,8 @@ class CudaForward:
         need = counts.nonzero().flatten().tolist()
         if self.telemetry is not None:
             self.telemetry.record_counts(layer, counts.tolist(), T)
+        if self.async_stream and len(need) <= arena.frames(layer):
+            return self._moe_async(lw, plan, layer, T, side, idx, need)
         frames = arena.frames(layer)
         tg0, tr0 = plan.tile_group.clone(), plan.tile_rows.clone()
         route_out = ws.route_out[:T]
@@ -523,6 +544,33 @@ class CudaForward:
             torch.cuda.current_stream().wait_stream(side)
         return idx
 
+    def _moe_async(self, lw: LayerWeights, plan, layer: int, T: int, side, idx, need):
+        """Streamed experts without blocking the engine: if an expert of the batch is not resident the layer
+        stops here (the resident ones stay leased for the transaction), otherwise the GEMM pair runs on the
+        leased frames.  The leases are handed to `lease_sink` (the runner releases them when the transaction
+        ends); without a sink they are dropped after the GEMMs."""
+        from .expert_async import NeedExperts
+        K, cfg, ws, arena = self.K, self.cfg, self.ws, self.arena
+        k, H = cfg.topk, cfg.hidden
+        held = self.lease_sink.setdefault(layer, {}) if self.lease_sink is not None else {}
+        held.update(arena.lease_resident(layer, [e for e in need if e not in held]))
+        missing = arena.missing(layer, need)
+        if missing:
+            if side is not None:
+                torch.cuda.current_stream().wait_stream(side)
+            raise NeedExperts(layer, missing)
+        arena.resolve_plan(layer, plan)
+        route_out = ws.route_out[:T]
+        K.gemm(ws.xg[:T * k], lw.e_w13, out=ws.hmid[:T * k], epilogue=K.EPI_SWIGLU, plan=plan,
+               act_limit=cfg.swiglu_limit)
+        K.gemm(ws.hmid[:T * k], lw.e_w2, out=route_out.view(T * ws.slots, H), epilogue=K.EPI_SCATTER,
+               plan=plan, scatter_rows=T * ws.slots)
+        if self.lease_sink is None:
+            arena.release_leases(layer, list(held.values()))
+        if side is not None:
+            torch.cuda.current_stream().wait_stream(side)
+        return idx
+
     def layer(self, lw: LayerWeights, layer: int, h_in: torch.Tensor, h_out: torch.Tensor, b: DeviceBatch,
               T: int, first_norm_done: bool = False) -> torch.Tensor:
         """h_in -> h_out (both bf16 [T, H]); returns h_out."""
@@ -535,7 +583,7 @@ class CudaForward:
             side, main = self.side_stream, torch.cuda.current_stream()
             side.wait_stream(main)
             with torch.cuda.stream(side):
-                K.l2_prefetch(lw.e_w13, self.l2_prefetch_bytes)
+                K.l2_prefetch(lw.e_w13, min(self.l2_prefetch_bytes, lw.e_w13.numel() * 2))
             if lw.w13 is None:                      # no shared-expert branch will join the side stream later
                 main.wait_stream(side)
         K.add_rmsnorm(h_in, lw.attn_norm, cfg.rms_eps, norm_out=xn)
@@ -583,7 +631,7 @@ class CudaForward:
         self.K.embedding(b.token_ids[:T], self.w.embed, out=h)
         return h
 
-    def run_layers(self, h: torch.Tensor, b: DeviceBatch, T: int) -> torch.Tensor:
+    def run_layers(self, h: torch.Tensor, b: DeviceBatch, T: int, start_layer: int = 0) -> torch.Tensor:
         """The layers this weight image holds (all of them, or one pipeline stage's share).  `h` is
         `ws.h[0][:T]` or is copied there."""
         ws = self.ws
@@ -593,11 +641,20 @@ class CudaForward:
             ws.route_cnt.zero_()
         h, other = ws.h[0][:T], ws.h[1][:T]
         for i, lw in enumerate(self.w.layers):
-            h = self.layer(lw, i, h, other, b, T)
+            if i < start_layer:
+                continue
+            try:
+                h = self.layer(lw, i, h, other, b, T)
+            except Exception as exc:  # noqa: BLE001
+                if hasattr(exc, "missing"):
+                    exc.hidden = h.clone()      # the layer's input rows are intact: its last kernel writes them
+                raise
         return h
 
-    def hidden_states(self, b: DeviceBatch, T: int) -> torch.Tensor:
-        return self.run_layers(self.embed_rows(b, T), b, T)
+    def hidden_states(self, b: DeviceBatch, T: int, start_layer: int = 0, h0=None) -> torch.Tensor:
+        """`start_layer` / `h0`: continue a forward that stopped at that layer with these input rows."""
+        h = self.embed_rows(b, T) if h0 is None else h0
+        return self.run_layers(h, b, T, start_layer)
 
     def head(self, h: torch.Tensor, b: DeviceBatch, final_norm: torch.Tensor, want_logits: bool = False):
         """Final norm + LM head + greedy token on the requested rows -> (next_id, next_val[, logits])."""
@@ -613,13 +670,13 @@ class CudaForward:
             tp.argmax_across_vocab(ws.next_id[:L], ws.next_val[:L], self.w.vocab_lo, L)
         return ws.next_id[:L], ws.next_val[:L], (logits if want_logits else None)
 
-    def forward(self, b: DeviceBatch, want_logits: bool = False):
+    def forward(self, b: DeviceBatch, want_logits: bool = False, start_layer: int = 0, h0=None):
         """Runs the batch; returns (next_id [n_logit] int32, next_val, logits or None)."""
         T = b.token_ids.shape[0]
         assert T <= self.ws.max_rows and b.n_logit <= self.ws.max_logit_rows
         from ..ops import _lib
         start = _lib.LAUNCHES[0]
-        h = self.hidden_states(b, T)
+        h = self.hidden_states(b, T, start_layer, h0)
         self.last_hidden = h
         out = (None, None, None) if b.n_logit == 0 else self.head(h, b, self.w.final_norm, want_logits)
         self.launches = _lib.LAUNCHES[0] - start

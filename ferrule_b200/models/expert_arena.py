@@ -61,9 +61,12 @@ class _LayerArena:
 
 
 class ExpertArena:
-    def __init__(self, weights: ModelWeights, resident_fraction: float = 0.5, min_frames: int = 0):
+    def __init__(self, weights: ModelWeights, resident_fraction: float = 0.5, min_frames: int = 0,
+                 replace_weights: bool = True):
         """Moves the routed experts of every MoE layer of `weights` to pinned host memory and replaces the
-        layer's expert tensors by arena frames (in place: `weights` is the streaming model afterwards)."""
+        layer's expert tensors by arena frames (in place: `weights` is the streaming model afterwards).
+        `replace_weights=False` keeps the model's tensors (the fp32 oracle reads them directly) and runs the
+        residency protocol beside it."""
         self.device = weights.embed.device
         self.cuda = self.device.type == "cuda"
         self.layers: Dict[int, _LayerArena] = {}
@@ -78,7 +81,8 @@ class ExpertArena:
             E = lw.e_w13.shape[0]
             frames = max(min_frames, min(E, int(round(E * resident_fraction))), 1)
             la = _LayerArena(i, lw.e_w13, lw.e_w2, frames, self.device)
-            lw.e_w13, lw.e_w2 = la.dev13, la.dev2
+            if replace_weights:
+                lw.e_w13, lw.e_w2 = la.dev13, la.dev2
             self.layers[i] = la
 
     def frames(self, layer: int) -> int:
@@ -133,6 +137,62 @@ class ExpertArena:
         self.stats.upload_bytes += n * la.expert_bytes
         self._apply(la, updates)
         return n
+
+    # ------------------------------------------------------------------ asynchronous protocol (one expert at a time)
+    def missing(self, layer: int, experts: Sequence[int]) -> List[int]:
+        la = self.layers[layer]
+        return [int(e) for e in sorted(set(int(x) for x in experts)) if la.coord.resolve(int(e)) is None]
+
+    def lease_resident(self, layer: int, experts: Sequence[int]) -> Dict[int, tuple]:
+        """Lease every expert of `experts` that is resident -> {expert: lease}; the caller releases them with
+        `release_leases`."""
+        la = self.layers[layer]
+        out = {}
+        for e in sorted(set(int(x) for x in experts)):
+            if la.coord.resolve(e) is not None:
+                out[e] = la.coord.lease(e)
+                self.stats.hits += 1
+        return out
+
+    def release_leases(self, layer: int, leases: Sequence[tuple]) -> None:
+        la = self.layers[layer]
+        for slot, gen in leases:
+            la.coord.release(slot, gen)
+        if self.cuda:
+            ev = torch.cuda.Event()
+            ev.record(torch.cuda.current_stream())
+            la.consumer_event = ev
+
+    def begin_upload(self, layer: int, expert: int):
+        """Pick a frame for `expert` (evicting the least recently used unleased one) and start its copy on the
+        upload stream -> (ticket, event or None).  Raises when every frame is leased."""
+        la = self.layers[layer]
+        t = la.coord.prepare(int(expert), required=True)
+        self.stats.misses += 1
+        ev = None
+        if self.cuda:
+            up = self.upload_stream
+            if la.consumer_event is not None:
+                up.wait_event(la.consumer_event)
+            with torch.cuda.stream(up):
+                la.dev13[t.slot].copy_(la.host13[t.expert], non_blocking=True)
+                la.dev2[t.slot].copy_(la.host2[t.expert], non_blocking=True)
+                ev = torch.cuda.Event()
+                ev.record(up)
+        else:
+            la.dev13[t.slot].copy_(la.host13[t.expert])
+            la.dev2[t.slot].copy_(la.host2[t.expert])
+        return t, ev
+
+    def finish_install(self, layer: int, ticket) -> None:
+        """The copy has completed: publish the frame in the coordinator and in the device table."""
+        la = self.layers[layer]
+        la.coord.activate(ticket)
+        la.coord.publish(ticket)
+        self.stats.uploads += 1
+        self.stats.upload_bytes += la.expert_bytes
+        self.stats.evictions += 0 if ticket.evicted is None else 1
+        self._apply(la, [[ticket.slot, ticket.expert, ticket.generation, -1 if ticket.evicted is None else ticket.evicted]])
 
     def _apply(self, la: _LayerArena, updates: List[List[int]]) -> None:
         n = len(updates)

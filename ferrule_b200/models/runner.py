@@ -20,7 +20,7 @@ import torch
 
 from ..runtime.execution import (ExecutionBatch, ExecutionCapabilities, ExecutionOutput, Intent, KvLayoutSchema,
                                  KvPlaneDescriptor, LogitsKind, RowOutput)
-from ..runtime.runner import Complete, EndIntent, EndStatus, ModelRunner, Proposal
+from ..runtime.runner import Complete, EndIntent, EndStatus, ModelRunner, Proposal, Waiting
 from .config import ModelConfig
 from .deepseek import CudaForward, DecodeGraph, DeviceBatch, KvPool, ReferenceForward
 from .weights import ModelWeights
@@ -100,6 +100,7 @@ class RunnerStats:
     cow_copies: int = 0
     forward_ns: int = 0
     mtp_proposals: int = 0
+    waits: int = 0
 
 
 class _MtpTrack:
@@ -115,7 +116,7 @@ class DeepSeekRunner(ModelRunner):
     def __init__(self, weights: ModelWeights, n_pages: int, page_size: int, max_rows: int = 2048,
                  max_seqs: int = 64, max_seq_len: int = 4096, device=None, tp=None, use_graphs: bool = True,
                  emulate_bf16: bool = False, attn_splits: int = 8, enable_mtp: bool = True, max_draft: int = 1,
-                 expert_residency: Optional[float] = None):
+                 expert_residency: Optional[float] = None, async_streaming: bool = False):
         self.w, self.cfg = weights, weights.cfg
         self.device = torch.device(device if device is not None else weights.embed.device)
         self.is_cuda = self.device.type == "cuda"
@@ -127,11 +128,19 @@ class DeepSeekRunner(ModelRunner):
         self.tp = tp
         # streamed routed experts: a fraction of every layer's experts is resident, the rest comes from pinned host
         # memory on demand; the step then synchronises with the host per MoE layer, so it cannot be one graph
+        # `async_streaming`: a batch that routes to a non-resident expert returns `Waiting`; the engine's load
+        # registry drives `self.provider` and resumes the transaction at the layer it stopped at.  (On the CPU the
+        # oracle keeps reading the full weights; the residency protocol runs beside it.)
         self.arena = None
-        if expert_residency is not None and self.is_cuda:
+        self.provider = None
+        self.async_streaming = bool(async_streaming and expert_residency is not None)
+        if expert_residency is not None and (self.is_cuda or self.async_streaming):
             from .expert_arena import ExpertArena
-            self.arena = ExpertArena(weights, expert_residency)
+            self.arena = ExpertArena(weights, expert_residency, replace_weights=self.is_cuda)
             use_graphs = False
+            if self.async_streaming:
+                from .expert_async import ArenaProvider
+                self.provider = ArenaProvider(self.arena, self.cfg.name)
         self.use_graphs = use_graphs and self.is_cuda
         self.stats = RunnerStats()
         self.staging = BatchStaging(max_rows, max_seqs, self.max_blocks, self.device)
@@ -157,6 +166,14 @@ class DeepSeekRunner(ModelRunner):
         self._txn_hidden: Dict[int, torch.Tensor] = {}
         self._txn_keep: Dict[int, Dict[int, int]] = {}
         self._mtp_staging: Optional[BatchStaging] = None
+        # asynchronous expert streaming: leases and the stop point of every parked transaction
+        self._txn_leases: Dict[int, Dict[int, Dict[int, tuple]]] = {}
+        self._txn_resume: Dict[int, tuple] = {}
+        if self.async_streaming:
+            if self.is_cuda:
+                self.fwd.async_stream = True
+            else:
+                self.fwd.expert_gate = self._expert_gate
 
     # ------------------------------------------------------------------ contract
     def capabilities(self) -> ExecutionCapabilities:
@@ -191,13 +208,46 @@ class DeepSeekRunner(ModelRunner):
             self.graphs[rows] = g
         return g
 
+    def make_registry(self, **kw):
+        """The load registry that drives this runner's expert provider (pass it to the engine)."""
+        from ..runtime.registry import LoadRegistry
+        if self.provider is None:
+            raise RuntimeError("the runner was not built with async_streaming")
+        reg = LoadRegistry(self.provider, **kw)
+        self.provider.attach(reg)
+        return reg
+
+    def _expert_gate(self, layer: int, experts) -> None:
+        from .expert_async import NeedExperts
+        if len(experts) > self.arena.frames(layer):
+            return          # more experts than frames: the kernels run such a layer in inline waves, nothing parks
+        held = self._lease_sink.setdefault(layer, {})
+        held.update(self.arena.lease_resident(layer, [e for e in experts if e not in held]))
+        missing = self.arena.missing(layer, experts)
+        if missing:
+            raise NeedExperts(layer, missing)
+
     def execute(self, txn_id: int):
         b = self.txns[txn_id]
         t0 = time.perf_counter_ns()
-        if not self.is_cuda:
-            out = self._execute_reference(b)
-        else:
-            out = self._execute_cuda(b)
+        start_layer, h0 = self._txn_resume.pop(txn_id, (0, None))
+        if self.async_streaming:
+            self._lease_sink = self._txn_leases.setdefault(txn_id, {})
+            if self.is_cuda:
+                self.fwd.lease_sink = self._lease_sink
+        try:
+            if not self.is_cuda:
+                out = self._execute_reference(b, start_layer, h0)
+            else:
+                out = self._execute_cuda(b, start_layer, h0)
+        except Exception as exc:  # noqa: BLE001
+            if not (self.async_streaming and hasattr(exc, "missing")):
+                raise
+            # parked: the resident experts stay leased, the missing ones become the continuation's dependencies
+            self._txn_resume[txn_id] = (exc.layer, exc.hidden)
+            self.stats.forward_ns += time.perf_counter_ns() - t0
+            self.stats.waits += 1
+            return Waiting([self.provider.key(exc.layer, e) for e in exc.missing], exc.layer)
         self.stats.forward_ns += time.perf_counter_ns() - t0
         if self.mtp_enabled:
             self._txn_hidden[txn_id] = self._last_hidden[:b.rows].clone()
@@ -213,6 +263,9 @@ class DeepSeekRunner(ModelRunner):
 
     def end_transaction(self, txn_id: int, intent: EndIntent) -> EndStatus:
         b = self.txns.pop(txn_id, None)
+        self._txn_resume.pop(txn_id, None)
+        for layer, held in self._txn_leases.pop(txn_id, {}).items():
+            self.arena.release_leases(layer, list(held.values()))
         h = self._txn_hidden.pop(txn_id, None)
         keep = self._txn_keep.pop(txn_id, None)
         if b is not None and h is not None and intent == EndIntent.PUBLISH:
@@ -260,6 +313,22 @@ class DeepSeekRunner(ModelRunner):
         out = [Proposal([], []) for _ in slots]
         if not self.mtp_enabled or max_draft < 1:
             return out
+        if self.async_streaming:
+            # drafting runs outside a transaction and cannot park: its experts are uploaded inline
+            saved = (getattr(self.fwd, "async_stream", False), getattr(self.fwd, "expert_gate", None))
+            if self.is_cuda:
+                self.fwd.async_stream = False
+            else:
+                self.fwd.expert_gate = None
+            try:
+                self.async_streaming = False
+                return self.propose(slots, anchors, positions, views, max_draft)
+            finally:
+                self.async_streaming = True
+                if self.is_cuda:
+                    self.fwd.async_stream = saved[0]
+                else:
+                    self.fwd.expert_gate = saved[1]
         todo = []
         for i, (slot, pos) in enumerate(zip(slots, positions)):
             tr = self._mtp.get(slot)
@@ -321,7 +390,7 @@ class DeepSeekRunner(ModelRunner):
         return (b.intent == Intent.COMMITTED and len(b.sequences) == b.rows
                 and all(lr.kind == LogitsKind.TOPK and lr.k == 1 for lr in b.logits))
 
-    def _execute_cuda(self, b: ExecutionBatch) -> ExecutionOutput:
+    def _execute_cuda(self, b: ExecutionBatch, start_layer: int = 0, h0=None) -> ExecutionOutput:
         fwd = self.fwd
         if self.use_graphs and self._is_pure_decode(b) and b.rows <= self.max_seqs:
             st, graph = self._graph_for(b.rows)
@@ -341,7 +410,7 @@ class DeepSeekRunner(ModelRunner):
             if L > fwd.ws.max_logit_rows:
                 raise ValueError("more logit rows than the runner was sized for")
             want_topk = any(b.logits[r].k > 1 for r in lrows)
-            fwd.forward(st.device_batch(T, L), want_logits=want_topk)
+            fwd.forward(st.device_batch(T, L), want_logits=want_topk, start_layer=start_layer, h0=h0)
             self._last_hidden = fwd.last_hidden
             self.stats.eager_steps += 1
             self.stats.kernel_launches += fwd.launches
@@ -373,7 +442,7 @@ class DeepSeekRunner(ModelRunner):
         from ..ops import _lib
         return ExecutionOutput(rows)
 
-    def _execute_reference(self, b: ExecutionBatch) -> ExecutionOutput:
+    def _execute_reference(self, b: ExecutionBatch, start_layer: int = 0, h0=None) -> ExecutionOutput:
         st = self.staging
         T, R, lrows = st.fill(b)
         L = len(lrows)
@@ -382,7 +451,7 @@ class DeepSeekRunner(ModelRunner):
         allreduce = self.tp.allreduce_reference if self.tp is not None else None
         gather = self.tp.gather_vocab_reference if self.tp is not None else None
         with torch.no_grad():
-            h = self.fwd.hidden_states(db, allreduce)
+            h = self.fwd.hidden_states(db, allreduce, start_layer, h0)
             self._last_hidden = h
             if L == 0:
                 return ExecutionOutput(rows)

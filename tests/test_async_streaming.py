@@ -1,0 +1,60 @@
+"""Asynchronous expert streaming on the real model: a batch that routes to a non-resident expert parks as a
+continuation, the load registry drives the arena provider, the transaction resumes at the layer it stopped at
+and the token stream equals the fully resident model's."""
+import pytest
+import torch
+
+from ferrule_b200.models import config as C
+from ferrule_b200.models import weights as W
+from ferrule_b200.models.runner import DeepSeekRunner
+from ferrule_b200.runtime.engine import Engine, EngineConfig, TokenEvent
+from ferrule_b200.runtime.scheduler import SchedulerConfig
+from ferrule_b200.runtime.session import GenerateRequest
+
+
+def _engine(w, device, residency=None, async_streaming=False):
+    runner = DeepSeekRunner(w, n_pages=48, page_size=16, max_rows=64, max_seqs=4, max_seq_len=256, device=device,
+                            enable_mtp=False, expert_residency=residency, async_streaming=async_streaming)
+    sched = SchedulerConfig(max_active_sequences=4, max_decode_batch=4, max_batch_tokens=32, prefill_chunk_size=8,
+                            ctx_size=256)
+    reg = runner.make_registry() if async_streaming else None
+    return Engine(runner, EngineConfig(scheduler=sched, kv_pages=48, page_size=16), registry=reg), runner
+
+
+def _run(eng, prompts, n_new):
+    for i, p in enumerate(prompts):
+        eng.submit(GenerateRequest(f"r{i}", p, max_new_tokens=n_new, ignore_eos=True))
+    ev = []
+    eng.run_until_idle(ev.append, max_steps=20000)
+    return [[e.token for e in ev if isinstance(e, TokenEvent) and e.request_id == f"r{i}"] for i in range(len(prompts))]
+
+
+def _check(device):
+    cfg = C.tiny_fixture()
+    g = torch.Generator().manual_seed(5)
+    prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (7, 11)]
+    dt = torch.bfloat16 if device == "cuda" else torch.float32
+    want = _run(_engine(W.random_weights(cfg, device=device, dtype=dt, seed=2), device)[0], prompts, 8)
+    eng, runner = _engine(W.random_weights(cfg, device=device, dtype=dt, seed=2), device, residency=0.75,
+                          async_streaming=True)
+    got = _run(eng, prompts, 8)
+    assert got == want
+    assert eng.stats.waits > 0 and eng.stats.resumes > 0 and runner.stats.waits == eng.stats.waits
+    a = runner.arena.stats
+    assert a.uploads > 0 and a.evictions > 0, "fewer frames than experts: experts were evicted and reloaded"
+    for la in runner.arena.layers.values():
+        assert all(s.leases == 0 for s in la.coord.slots), "every lease was returned when its transaction ended"
+    eng.kv.check_invariants()
+    assert eng.kv.stats().used_pages == 0
+    assert eng.registry.residual().get("continuations", 0) == 0
+
+
+def test_async_streaming_parks_and_resumes_on_cpu():
+    _check("cpu")
+
+
+@pytest.mark.gpu
+def test_async_streaming_parks_and_resumes_on_gpu():
+    _check("cuda")
+    from ferrule_b200.ops import _lib
+    assert _lib.read_status()[0] == 0
