@@ -772,11 +772,18 @@ moe_reduce_kernel(const __nv_bfloat16* __restrict__ route_out, int slots, int to
                   const int* __restrict__ topk_idx, int e_lo, int e_hi,
                   const __nv_bfloat16* __restrict__ extra, long long lde,
                   const __nv_bfloat16* __restrict__ residual, long long ldr, void* __restrict__ out,
-                  long long ldo, int out_fp32, int rows, int dim) {
+                  long long ldo, int out_fp32, int rows, int dim,
+                  const __nv_bfloat16* __restrict__ norm_w, __nv_bfloat16* __restrict__ norm_out, long long ldn,
+                  float eps) {
   pdl_launch_dependents();
   pdl_wait();
+  // optional RMSNorm of the result (the next layer's input norm), with the element -> thread mapping, the bf16
+  // rounding of the normalised value and the reduction order of add_rmsnorm_kernel: bit-equal to running it after
+  __shared__ float red[8];
+  extern __shared__ float nrow[];  // dim floats when norm_out is set
   const int t = blockIdx.x;
   if (t >= rows) return;
+  float ss = 0.f;
   for (int i = threadIdx.x * 8; i < dim; i += blockDim.x * 8) {
     float acc[8];
 #pragma unroll
@@ -813,7 +820,26 @@ moe_reduce_kernel(const __nv_bfloat16* __restrict__ route_out, int slots, int to
       for (int j = 0; j < 8; ++j) o[j] = __float2bfloat16_rn(acc[j]);
       *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(out) + t * ldo + i) =
           *reinterpret_cast<uint4*>(o);
+      if (norm_out) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float v = __bfloat162float(o[j]);
+          nrow[i + j] = v;
+          ss += v * v;
+        }
+      }
     }
+  }
+  if (norm_out == nullptr) return;
+  ss = block_sum(ss, red);
+  const float inv = rsqrtf(ss / dim + eps);
+  for (int i = threadIdx.x * 8; i < dim; i += blockDim.x * 8) {
+    uint4 wv = *reinterpret_cast<const uint4*>(norm_w + i);
+    const __nv_bfloat16* wp = reinterpret_cast<const __nv_bfloat16*>(&wv);
+    __nv_bfloat16 o[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) o[j] = __float2bfloat16_rn(nrow[i + j] * inv * __bfloat162float(wp[j]));
+    *reinterpret_cast<uint4*>(norm_out + t * ldn + i) = *reinterpret_cast<uint4*>(o);
   }
 }
 
@@ -1159,7 +1185,27 @@ extern "C" int fb_moe_reduce(const void* route_out, int slots, int topk, const i
   launch_pdl(moe_reduce_kernel, dim3(rows), dim3(256), 0, static_cast<cudaStream_t>(stream), 
       static_cast<const __nv_bfloat16*>(route_out), slots, topk, topk_idx, e_lo, e_hi,
       static_cast<const __nv_bfloat16*>(extra), lde, static_cast<const __nv_bfloat16*>(residual),
-      ldr, out, ldo, out_fp32, rows, dim);
+      ldr, out, ldo, out_fp32, rows, dim, static_cast<const __nv_bfloat16*>(nullptr),
+      static_cast<__nv_bfloat16*>(nullptr), 0LL, 0.f);
+  return FB_CHECK_LAUNCH();
+}
+
+// fb_moe_reduce with the RMSNorm of the (bf16) result written to norm_out as well
+extern "C" int fb_moe_reduce_norm(const void* route_out, int slots, int topk, const int* topk_idx,
+                                  int e_lo, int e_hi, const void* residual, long long ldr, void* out, long long ldo,
+                                  int rows, int dim, const void* norm_w, void* norm_out, long long ldn, float eps,
+                                  void* stream) {
+  if (rows <= 0 || dim % 8 != 0 || slots < topk || !norm_w || !norm_out || dim > 16384) return FB_ERR_SHAPE;
+  static bool attr = false;
+  if (!attr) {
+    cudaFuncSetAttribute(moe_reduce_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 65536);
+    attr = true;
+  }
+  launch_pdl(moe_reduce_kernel, dim3(rows), dim3(256), dim * sizeof(float), static_cast<cudaStream_t>(stream),
+      static_cast<const __nv_bfloat16*>(route_out), slots, topk, topk_idx, e_lo, e_hi,
+      static_cast<const __nv_bfloat16*>(nullptr), 0LL, static_cast<const __nv_bfloat16*>(residual),
+      ldr, out, ldo, 0, rows, dim, static_cast<const __nv_bfloat16*>(norm_w),
+      static_cast<__nv_bfloat16*>(norm_out), ldn, eps);
   return FB_CHECK_LAUNCH();
 }
 

@@ -183,6 +183,9 @@ int fb_router_append(const void* x, long long ldx, const void* w, int hidden, co
                      float* row_scale, void* xg, long long ldxg, void* status, void* stream);
 int fb_gather_rows(const void* x, long long ldx, const int* src_token, const int* meta, void* out,
                    long long ldo, int cap_rows, int dim, int src_rows, void* status, void* stream);
+int fb_moe_reduce_norm(const void* route_out, int slots, int topk, const int* topk_idx, int e_lo, int e_hi,
+                       const void* residual, long long ldr, void* out, long long ldo, int rows, int dim,
+                       const void* norm_w, void* norm_out, long long ldn, float eps, void* stream);
 int fb_moe_reduce(const void* route_out, int slots, int topk, const int* topk_idx, int e_lo,
                   int e_hi, const void* extra, long long lde, const void* residual, long long ldr,
                   void* out, long long ldo, int out_fp32, int rows, int dim, void* stream);

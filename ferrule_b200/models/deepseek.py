@@ -377,6 +377,9 @@ class CudaForward:
         self.l2_prefetch_bytes = int(float(os.environ.get("FERRULE_L2_PREFETCH_MB", "48")) * (1 << 20))
         self.telemetry = None      # utils.telemetry.ExpertTelemetry fed by the streamed path
         self.static_moe = os.environ.get("FERRULE_STATIC_MOE", "1") != "0"
+        self.fuse_next_norm = os.environ.get("FERRULE_FUSE_NORM", "1") != "0"
+        self.fork_prep = os.environ.get("FERRULE_FORK_PREP", "1") != "0"
+        self.prep_stream = torch.cuda.Stream(device=dev)
         self.async_stream = False  # streamed experts: stop at a layer with missing experts instead of uploading inline
         self.lease_sink = None     # dict layer -> leases of the running transaction (set by the runner)
 
@@ -412,9 +415,21 @@ class CudaForward:
         else:
             q, ckv = qkv[:, :hl * qhd], qkv[:, hl * qhd:]
         q_full = ws.q_full[:T]
-        K.mla_prep(q, qhd, ckv, hl, lora, rope, lw.kv_norm, cfg.rms_eps, self.cos, self.sin,
-                   b.positions, b.write_slot, self.pool.layer(layer), q_full.view(T, -1))
+        # the cache write / RoPE kernel and the W_UK absorption GEMM both only read q (they fill disjoint columns
+        # of q_full): decode-sized batches run them as parallel branches
+        fork = self.fork_prep and T <= ws.decode_rows
+        if fork:
+            main = torch.cuda.current_stream()
+            self.prep_stream.wait_stream(main)
+            with torch.cuda.stream(self.prep_stream):
+                K.mla_prep(q, qhd, ckv, hl, lora, rope, lw.kv_norm, cfg.rms_eps, self.cos, self.sin,
+                           b.positions, b.write_slot, self.pool.layer(layer), q_full.view(T, -1))
+        else:
+            K.mla_prep(q, qhd, ckv, hl, lora, rope, lw.kv_norm, cfg.rms_eps, self.cos, self.sin,
+                       b.positions, b.write_slot, self.pool.layer(layer), q_full.view(T, -1))
         K.gemm(q, lw.w_uk_t, out=q_full.view(T, -1), x_group_koff=qhd, out_group_coff=lora + rope, k=nope)
+        if fork:
+            main.wait_stream(self.prep_stream)
         # verification batches (a few rows per decoding sequence) must take the same split path as plain
         # decode steps: equal split boundaries give bit-equal merges, hence the same greedy tokens
         use_split = ws.attn_splits > 1 and T <= 4 * ws.decode_rows
@@ -572,7 +587,7 @@ class CudaForward:
         return idx
 
     def layer(self, lw: LayerWeights, layer: int, h_in: torch.Tensor, h_out: torch.Tensor, b: DeviceBatch,
-              T: int, first_norm_done: bool = False) -> torch.Tensor:
+              T: int, first_norm_done: bool = False, next_norm: Optional[torch.Tensor] = None) -> torch.Tensor:
         """h_in -> h_out (both bf16 [T, H]); returns h_out."""
         K, cfg, ws, tp = self.K, self.cfg, self.ws, self.tp
         xn = ws.xn[:T]
@@ -586,7 +601,10 @@ class CudaForward:
                 K.l2_prefetch(lw.e_w13, min(self.l2_prefetch_bytes, lw.e_w13.numel() * 2))
             if lw.w13 is None:                      # no shared-expert branch will join the side stream later
                 main.wait_stream(side)
-        K.add_rmsnorm(h_in, lw.attn_norm, cfg.rms_eps, norm_out=xn)
+        # `first_norm_done`: the previous layer's last kernel already wrote this layer's normalised input to xn;
+        # `next_norm` (single GPU): this layer's last kernel does the same for the next one
+        if not first_norm_done:
+            K.add_rmsnorm(h_in, lw.attn_norm, cfg.rms_eps, norm_out=xn)
         a = self._attention(lw, layer, xn, b, T)
         if tp is None:
             self._gemm(a, lw.w_o, ws.delta[:T], slot="a")
@@ -604,7 +622,10 @@ class CudaForward:
         if lw.is_moe:
             idx = self._moe_local(lw, xn, b, T, layer)
             # slot `topk` holds the shared-expert row (zeros when the model has none)
-            if tp is None:
+            if tp is None and next_norm is not None:
+                K.moe_reduce_norm(ws.route_out[:T].view(T * ws.slots, cfg.hidden), ws.slots, cfg.topk, idx,
+                                  self.w.e_lo, self.w.e_hi, T, cfg.hidden, h_mid, h_in, next_norm, xn, cfg.rms_eps)
+            elif tp is None:
                 K.moe_reduce(ws.route_out[:T].view(T * ws.slots, cfg.hidden), ws.slots, cfg.topk, idx,
                              self.w.e_lo, self.w.e_hi, T, cfg.hidden, residual=h_mid, out=h_in)
             else:
@@ -617,7 +638,10 @@ class CudaForward:
         if tp is None:
             self._gemm(mid, lw.w2, ws.delta[:T], slot="mid")
             # residual add is folded into the next consumer through a plain add+norm without a norm output
-            K.add_rmsnorm(h_mid, None, cfg.rms_eps, delta=ws.delta[:T], res_out=h_in, want_norm=False)
+            if next_norm is not None:
+                K.add_rmsnorm(h_mid, next_norm, cfg.rms_eps, delta=ws.delta[:T], res_out=h_in, norm_out=xn)
+            else:
+                K.add_rmsnorm(h_mid, None, cfg.rms_eps, delta=ws.delta[:T], res_out=h_in, want_norm=False)
         elif isinstance(lw.w2, QuantWeight):
             self._gemm(mid, lw.w2, ws.delta[:T], slot="mid")
             tp.add_allreduce(ws.delta[:T], residual=h_mid, out=h_in, T=T)
@@ -640,11 +664,15 @@ class CudaForward:
         if ws.has_moe and ws.static_rows and T <= ws.static_rows[-1]:
             ws.route_cnt.zero_()
         h, other = ws.h[0][:T], ws.h[1][:T]
-        for i, lw in enumerate(self.w.layers):
+        layers = self.w.layers
+        fused = False                     # the previous layer wrote this layer's normalised input
+        for i, lw in enumerate(layers):
             if i < start_layer:
                 continue
+            nxt = layers[i + 1].attn_norm if (self.fuse_next_norm and self.tp is None and i + 1 < len(layers)) else None
             try:
-                h = self.layer(lw, i, h, other, b, T)
+                h = self.layer(lw, i, h, other, b, T, first_norm_done=fused, next_norm=nxt)
+                fused = nxt is not None
             except Exception as exc:  # noqa: BLE001
                 if hasattr(exc, "missing"):
                     exc.hidden = h.clone()      # the layer's input rows are intact: its last kernel writes them

@@ -243,6 +243,18 @@ def moe_reduce(route_out: torch.Tensor, slots: int, topk: int, topk_idx: torch.T
     return out
 
 
+def moe_reduce_norm(route_out: torch.Tensor, slots: int, topk: int, topk_idx: torch.Tensor, e_lo: int, e_hi: int,
+                    rows: int, dim: int, residual: torch.Tensor, out: torch.Tensor, norm_w: torch.Tensor,
+                    norm_out: torch.Tensor, eps: float) -> torch.Tensor:
+    """`moe_reduce` that also writes RMSNorm(out) * norm_w (bit-equal to `add_rmsnorm` run on `out` afterwards)."""
+    lib = get_lib(True)
+    check(lib.fb_moe_reduce_norm(route_out.data_ptr(), slots, topk, topk_idx.data_ptr(), e_lo, e_hi,
+                                 residual.data_ptr(), residual.stride(0), out.data_ptr(), out.stride(0), rows, dim,
+                                 norm_w.data_ptr(), norm_out.data_ptr(), norm_out.stride(0), eps, stream_ptr()),
+          "fb_moe_reduce_norm")
+    return out
+
+
 def argmax(logits: torch.Tensor, out_id: Optional[torch.Tensor] = None,
            out_val: Optional[torch.Tensor] = None) -> torch.Tensor:
     lib = get_lib(True)

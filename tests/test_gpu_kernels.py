@@ -424,6 +424,23 @@ def test_router_append_static_plan(K, T, E, k, H, I):
     assert torch.equal(o1[local], o2[local])
 
 
+@pytest.mark.parametrize("T,k,H", [(32, 6, 2048), (5, 8, 7168)])
+def test_moe_reduce_norm_is_bit_equal_to_reduce_then_norm(K, T, k, H):
+    slots = k + 1
+    ro = rnd(T * slots, H)
+    idx = torch.randint(0, 16, (T, k), dtype=torch.int32, device="cuda")
+    res = rnd(T, H)
+    w = rnd(H)
+    out1 = torch.zeros(T, H, dtype=torch.bfloat16, device="cuda")
+    K.moe_reduce(ro, slots, k, idx, 4, 12, T, H, residual=res, out=out1)
+    _, n1 = K.add_rmsnorm(out1, w, 1e-6)
+    out2 = torch.zeros_like(out1)
+    n2 = torch.zeros_like(out1)
+    K.moe_reduce_norm(ro, slots, k, idx, 4, 12, T, H, res, out2, w, n2, 1e-6)
+    torch.cuda.synchronize()
+    assert torch.equal(out1, out2) and torch.equal(n1, n2)
+
+
 def test_bounded_wait_reports_timeout_and_context_stays_usable():
     """Failure detection on the device: a wait on a flag that nothing sets gives up after its limit, records a
     status word (no trap, no hang) and later kernels still run."""
