@@ -378,6 +378,8 @@ class CudaForward:
         self.telemetry = None      # utils.telemetry.ExpertTelemetry fed by the streamed path
         self.static_moe = os.environ.get("FERRULE_STATIC_MOE", "1") != "0"
         self.fuse_next_norm = os.environ.get("FERRULE_FUSE_NORM", "1") != "0"
+        self.attn_prefetch = os.environ.get("FERRULE_ATTN_PREFETCH", "1") != "0"
+        self._prefetch_next = None
         self.fork_prep = os.environ.get("FERRULE_FORK_PREP", "1") != "0"
         self.prep_stream = torch.cuda.Stream(device=dev)
         self.async_stream = False  # streamed experts: stop at a layer with missing experts instead of uploading inline
@@ -484,6 +486,13 @@ class CudaForward:
                 mid = ws.ffn_mid[:T, :inter]
                 self._gemm(xn, lw.w13, mid, xq=xq_n, epilogue=K.EPI_SWIGLU, act_limit=cfg.swiglu_limit)
                 self._gemm(mid, lw.w2, ws.route_out[:T][:, k], slot="mid")
+                nl = self._prefetch_next
+                if nl is not None and T <= ws.decode_rows:
+                    # the next layer's attention weights (a few tens of MB, four latency-bound GEMMs) are pulled
+                    # into L2 while the routed experts stream past them with the evict-first policy
+                    for wt in (nl.w_qkv_a, nl.w_uk_t, nl.w_uv, nl.w_o):
+                        if isinstance(wt, torch.Tensor):
+                            K.l2_prefetch(wt, wt.numel() * wt.element_size())
         static = self._static_rows(lw, T, layer)
         if static:
             # no plan phase and no gather kernel: the router reserves rows in fixed per-expert slots
@@ -670,6 +679,7 @@ class CudaForward:
             if i < start_layer:
                 continue
             nxt = layers[i + 1].attn_norm if (self.fuse_next_norm and self.tp is None and i + 1 < len(layers)) else None
+            self._prefetch_next = layers[i + 1] if (self.attn_prefetch and i + 1 < len(layers)) else None
             try:
                 h = self.layer(lw, i, h, other, b, T, first_norm_done=fused, next_norm=nxt)
                 fused = nxt is not None

@@ -41,6 +41,7 @@ OPERATOR_GROUPS: Dict[str, Tuple[str, ...]] = {
     "norm_embedding": ("fb_add_rmsnorm", "fb_embedding"),
     "router_plan": ("fb_router_topk", "fb_moe_plan", "fb_gather_rows", "fb_moe_reduce"),
     "router_plan_fused": ("fb_router_plan_fused",),
+    "router_static_slots": ("fb_router_append", "fb_moe_reduce_norm"),
     "sampling_greedy": ("fb_argmax", "fb_topk_logits"),
     "kv_pages": ("fb_copy_pages",),
     "collective_allreduce": ("fb_moe_reduce_allreduce", "fb_ipc_alloc", "fb_ipc_open"),
@@ -169,6 +170,8 @@ def compile_model_plan(cfg, registry: Optional[ProviderRegistry] = None, *, weig
             moe = cfg.is_moe_layer(i)
         if moe:
             ops = ["norm_embedding", "router_plan", expert_gemm, gemm]
+            if not v4 and weight_format == "bf16" and not streamed_experts:
+                ops.append("router_static_slots")      # decode-sized batches: fixed per-expert row slots
             if v4:
                 ops.append("hyper_connection")
             if expert_dispatch:
