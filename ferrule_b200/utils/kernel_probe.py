@@ -98,8 +98,8 @@ def case_gemm_fp8(reps):
 
 
 def case_small(reps):
-    """The latency-bound kernels of one layer back to back: add+RMSNorm, MLA prep, fused router + plan, gather,
-    MoE reduce, chunked arg-max."""
+    """The latency-bound kernels of one layer back to back: add+RMSNorm, fused router + plan, gather, MoE reduce,
+    chunked arg-max, then the decode forms (static-slot router, reduce + norm)."""
     T, H, E, k = 32, 2048, 64, 6
     x, d = rnd(T, H), rnd(T, H)
     nw = torch.ones(H, dtype=torch.bfloat16, device=DEV)
@@ -116,12 +116,21 @@ def case_small(reps):
     nid = torch.zeros(T, dtype=torch.int32, device=DEV)
     nval = torch.zeros(T, dtype=torch.float32, device=DEV)
 
+    cnt = torch.zeros(E, dtype=torch.int32, device=DEV)
+    splan = K.static_plan(32, E, cnt)
+    xgs = torch.zeros(E * 32, H, dtype=torch.bfloat16, device=DEV)
+    x2, xn2 = torch.zeros_like(x), torch.zeros_like(x)
+
     def fn(i):
         K.add_rmsnorm(x, nw, 1e-6, delta=d, res_out=res, norm_out=xn)
         K.router_plan_fused(xn, rw, k, 0, plan, 0, E, idx, wts, ctr, dst_slots=k + 1)
         K.gather_rows(xn, plan, xg, cap_rows=T * k)
         K.moe_reduce(route_out, k + 1, k, idx, 0, E, T, H, residual=res, out=x)
         K.argmax_chunked(logits, scratch, nid, nval)
+        # decode path: static per-expert row slots (router + reservation + gather) and reduce + next-layer norm
+        cnt.zero_()
+        K.router_append(xn, rw, k, 0, splan, 0, E, idx, wts, xgs, dst_slots=k + 1)
+        K.moe_reduce_norm(route_out, k + 1, k, idx, 0, E, T, H, res, x2, nw, xn2, 1e-6)
     return timed(fn, reps), {}
 
 
