@@ -373,8 +373,10 @@ class CudaForward:
         # bytes of each MoE layer's routed-expert weights to prefetch into L2 during the attention half of a decode
         # layer (0 = off); the L2 holds 126 MB, the prefetch must leave room for the attention's own traffic
         import os
-        # measured on one GPU with evict-first weight streaming: 0 / 32 / 64 / 96 MB -> 7.38 / 7.33 / 7.29 / 7.55 ms
-        self.l2_prefetch_bytes = int(float(os.environ.get("FERRULE_L2_PREFETCH_MB", "48")) * (1 << 20))
+        # measured on one GPU with evict-first weight streaming: 0 / 32 / 64 / 96 MB -> 7.38 / 7.33 / 7.29 / 7.55 ms,
+        # but once the cache-write kernel runs as a parallel branch the extra branch costs more than it hides
+        # (6.75 ms without, 6.97 ms with 48 MB): off by default
+        self.l2_prefetch_bytes = int(float(os.environ.get("FERRULE_L2_PREFETCH_MB", "0")) * (1 << 20))
         self.telemetry = None      # utils.telemetry.ExpertTelemetry fed by the streamed path
         self.static_moe = os.environ.get("FERRULE_STATIC_MOE", "1") != "0"
         self.fuse_next_norm = os.environ.get("FERRULE_FUSE_NORM", "1") != "0"

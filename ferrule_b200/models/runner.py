@@ -53,6 +53,7 @@ class BatchStaging:
         self.d_ids, self.d_pos, self.d_seq, self.d_rpos, self.d_lrows = (d[o + i * R:o + (i + 1) * R] for i in range(5))
         self.d_bt = d[o + 5 * R:].view(seqs, max_blocks)
         self.cuda = cuda
+        self._arange = np.arange(R, dtype=np.int32)
 
     def fill(self, b: ExecutionBatch, pad_rows: int = 0):
         T = b.rows
@@ -69,11 +70,21 @@ class BatchStaging:
             self.np_rpos[T:R] = -1
             self.np_slot[T:R] = -1
             self.np_seq[T:R] = 0
-        for i, s in enumerate(b.sequences):
-            self.np_seq[s.query_start:s.query_start + s.query_len] = i
-            if s.block_len > self.max_blocks:
-                raise ValueError("sequence has more pages than the block table holds")
-            self.np_bt[i, :s.block_len] = b.block_ids[s.block_start:s.block_start + s.block_len]
+        seqs = b.sequences
+        n = len(seqs)
+        L = seqs[0].block_len
+        if (n == T and L <= self.max_blocks and len(b.block_ids) == n * L
+                and all(s.block_len == L and s.block_start == i * L for i, s in enumerate(seqs))):
+            # decode step with one row per sequence and equally long page lists laid out back to back (the
+            # common steady state): two array assignments instead of a loop over the sequences
+            self.np_seq[:T] = self._arange[:T]
+            self.np_bt[:n, :L] = np.asarray(b.block_ids, dtype=np.int32).reshape(n, L)
+        else:
+            for i, s in enumerate(seqs):
+                self.np_seq[s.query_start:s.query_start + s.query_len] = i
+                if s.block_len > self.max_blocks:
+                    raise ValueError("sequence has more pages than the block table holds")
+                self.np_bt[i, :s.block_len] = b.block_ids[s.block_start:s.block_start + s.block_len]
         lrows = b.logit_rows()
         self.np_lrows[:len(lrows)] = lrows
         return T, R, lrows
