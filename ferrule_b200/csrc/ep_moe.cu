@@ -24,7 +24,7 @@
 //
 // The reference streams experts on one GPU and has no dispatch; this is the expert-parallel
 // counterpart of its prepare/gather + scatter stages
-// (crates/ferrule-backend/native/cuda/architectures/sm103/grouped_fp4_moe.cuh:1115-1222).
+// (crates/ferrule-backend/native/cuda/implementations/cutlass/architectures/sm103/grouped_fp4_moe.cuh:1115-1222).
 #include "common.cuh"
 #include "ferrule_b200.h"
 #include "launch.cuh"

@@ -10,7 +10,7 @@
 //
 // Counterpart of expert_table_kernel
 // (crates/ferrule-backend/native/cuda/implementations/portable/entrypoints.cu:1268-1380) and of the
-// host mirror in crates/ferrule-backend/src/cuda/expert_table.rs:20-500.
+// host mirror in crates/ferrule-backend/src/cuda/context.rs:1952-2300.
 #include "common.cuh"
 #include "ferrule_b200.h"
 #include "launch.cuh"

@@ -133,7 +133,17 @@ def load_deepseek_hf(directory, device="cpu", dtype=torch.bfloat16, tp_rank: int
         p = f"model.layers.{cfg.n_layers + m}."
         if not ck.has(p + "eh_proj.weight"):
             break
-        mtp.append(MtpWeights(enorm=ck.read(p + "enorm.weight").to(dt).to(dev),
+        own_embed = own_head = None
+        if ck.has(p + "embed_tokens.weight"):
+            t = ck.read(p + "embed_tokens.weight").to(dt)
+            if not torch.equal(t, embed.cpu()):
+                own_embed = t.to(dev)
+        if ck.has(p + "shared_head.head.weight"):
+            t = ck.read(p + "shared_head.head.weight").to(dt)[v_lo:v_hi].contiguous()
+            if not torch.equal(t, lm_head.cpu()):
+                own_head = t.to(dev)
+        mtp.append(MtpWeights(embed=own_embed, lm_head=own_head,
+                              enorm=ck.read(p + "enorm.weight").to(dt).to(dev),
                               hnorm=ck.read(p + "hnorm.weight").to(dt).to(dev),
                               eh_proj=read_linear(ck, p + "eh_proj", dt).to(dev),
                               layer=_layer(ck, p, cfg.n_layers + m, cfg, tp_rank, tp_world, dev, dt,
@@ -217,6 +227,10 @@ def export_hf(w: ModelWeights, directory, dense_format: str = "plain", expert_fo
         out[p + "enorm.weight"], out[p + "hnorm.weight"] = mt.enorm.cpu(), mt.hnorm.cpu()
         out[p + "eh_proj.weight"] = mt.eh_proj.cpu()
         out[p + "shared_head.norm.weight"] = mt.final_norm.cpu()
+        if mt.embed is not None:
+            out[p + "embed_tokens.weight"] = mt.embed.cpu()
+        if mt.lm_head is not None:
+            out[p + "shared_head.head.weight"] = mt.lm_head.cpu()
         put_layer(p, mt.layer)
     d = Path(directory)
     d.mkdir(parents=True, exist_ok=True)

@@ -210,11 +210,11 @@ class ReferenceForward:
         h = self.embed_rows(b) if h0 is None else h0
         return self.run_layers(h, b, allreduce, start_layer)
 
-    def logits_from_hidden(self, h: torch.Tensor, b: DeviceBatch, final_norm=None) -> torch.Tensor:
+    def logits_from_hidden(self, h: torch.Tensor, b: DeviceBatch, final_norm=None, lm_head=None) -> torch.Tensor:
         rows = b.logit_rows[:b.n_logit].long()
         hn = self.rnd(ref.rmsnorm(h[rows], self.w.final_norm if final_norm is None else final_norm,
                                   self.cfg.rms_eps))
-        return hn @ self.w.lm_head.float().T
+        return hn @ (self.w.lm_head if lm_head is None else lm_head).float().T
 
     def forward(self, b: DeviceBatch, allreduce=None, gather_vocab=None, return_hidden: bool = False):
         """-> fp32 logits [n_logit, vocab_local] (or gathered vocab with `gather_vocab`)."""
@@ -230,11 +230,12 @@ class ReferenceForward:
         m = self.w.mtp[stage]
         cfg, rnd = self.cfg, self.rnd
         T = b.n_rows
-        e = self.w.embed[b.token_ids[:T].long()].float()
-        x = torch.cat([rnd(ref.rmsnorm(h_prev, m.hnorm, cfg.rms_eps)), rnd(ref.rmsnorm(e, m.enorm, cfg.rms_eps))], -1)
+        e = (self.w.embed if m.embed is None else m.embed)[b.token_ids[:T].long()].float()
+        # column order of eh_proj in published DeepSeek-V3 checkpoints: [enorm(embedding) ; hnorm(previous hidden)]
+        x = torch.cat([rnd(ref.rmsnorm(e, m.enorm, cfg.rms_eps)), rnd(ref.rmsnorm(h_prev, m.hnorm, cfg.rms_eps))], -1)
         h = rnd(x @ m.eh_proj.float().T)
         h = self.layer(m.layer, cfg.n_layers + stage, h, b, allreduce)
-        return self.logits_from_hidden(h, b, final_norm=m.final_norm), h
+        return self.logits_from_hidden(h, b, final_norm=m.final_norm, lm_head=m.lm_head), h
 
 
 # ======================================================================================
@@ -698,7 +699,8 @@ class CudaForward:
         h = self.embed_rows(b, T) if h0 is None else h0
         return self.run_layers(h, b, T, start_layer)
 
-    def head(self, h: torch.Tensor, b: DeviceBatch, final_norm: torch.Tensor, want_logits: bool = False):
+    def head(self, h: torch.Tensor, b: DeviceBatch, final_norm: torch.Tensor, want_logits: bool = False,
+             lm_head: Optional[torch.Tensor] = None):
         """Final norm + LM head + greedy token on the requested rows -> (next_id, next_val[, logits])."""
         K, cfg, ws, tp = self.K, self.cfg, self.ws, self.tp
         L = b.n_logit
@@ -706,7 +708,7 @@ class CudaForward:
         torch.index_select(h, 0, b.logit_rows[:L], out=hl)
         K.add_rmsnorm(hl, final_norm, cfg.rms_eps, norm_out=ws.hn_last[:L])
         logits = ws.logits[:L]
-        K.gemm(ws.hn_last[:L], self.w.lm_head, out=logits)
+        K.gemm(ws.hn_last[:L], self.w.lm_head if lm_head is None else lm_head, out=logits)
         K.argmax_chunked(logits, ws.argmax_scratch, ws.next_id[:L], ws.next_val[:L])
         if tp is not None:
             tp.argmax_across_vocab(ws.next_id[:L], ws.next_val[:L], self.w.vocab_lo, L)
@@ -733,16 +735,17 @@ class CudaForward:
         x = ws.mtp_x[:T]
         if ws.has_moe and ws.static_rows and T <= ws.static_rows[-1]:
             ws.route_cnt[cfg.n_layers + stage].zero_()
-        K.add_rmsnorm(h_prev, m.hnorm, cfg.rms_eps, norm_out=x[:, :H])
+        # eh_proj input columns: [enorm(embedding) ; hnorm(previous hidden)], the order of published checkpoints
+        K.add_rmsnorm(h_prev, m.hnorm, cfg.rms_eps, norm_out=x[:, H:])
         e = ws.h[1][:T]
-        K.embedding(b.token_ids[:T], self.w.embed, out=e)
-        K.add_rmsnorm(e, m.enorm, cfg.rms_eps, norm_out=x[:, H:])
+        K.embedding(b.token_ids[:T], self.w.embed if m.embed is None else m.embed, out=e)
+        K.add_rmsnorm(e, m.enorm, cfg.rms_eps, norm_out=x[:, :H])
         # h_prev (usually ws.h[0]) is consumed by now, so the projection may overwrite it
         h0 = ws.h[0][:T]
         self._gemm(x, m.eh_proj, h0, slot="a")
         h = self.layer(m.layer, cfg.n_layers + stage, h0, ws.h[1][:T], b, T)
         self.last_hidden = h
-        return self.head(h, b, m.final_norm)
+        return self.head(h, b, m.final_norm, lm_head=m.lm_head)
 
 
 class DecodeGraph:

@@ -320,7 +320,7 @@ class DeepSeekRunner(ModelRunner):
     def propose(self, slots, anchors, positions, views, max_draft):
         """One draft token per sequence from the first MTP stage.  Writes the MTP layer's KV rows for
         every published position that has none yet, then reads the stage's greedy token at the last one.
-        Mirrors the reference's hidden-tap driven proposal (crates/ferrule-engine/src/engine.rs:618-730)."""
+        Mirrors the reference's hidden-tap driven proposal (crates/ferrule-model/src/models/deepseek_v4/runner.rs:3906 and proposal_attachment.rs:57-181)."""
         out = [Proposal([], []) for _ in slots]
         if not self.mtp_enabled or max_draft < 1:
             return out

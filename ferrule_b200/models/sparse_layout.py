@@ -11,8 +11,8 @@ kernels take explicit row lists; these resolvers build such lists and check them
               position p with p % window == r among the last `window` positions
 * recurrent compressor state: `ratio` (or 2 * ratio with overlap) projected rows of width out_dim
 
-Counterpart of crates/ferrule-backend/src/cuda/sparse_attention.rs:22-372 (layouts + resolvers) and
-combined_ring.rs:33-160, compressor_shape.rs:4-30.
+Counterpart of crates/ferrule-backend/src/cuda/transformer/sparse_attention.rs:14-640 (layouts + resolvers),
+transformer/combined_ring.rs:5-120 and transformer/compressor_recurrent.rs:6-110.
 """
 from __future__ import annotations
 

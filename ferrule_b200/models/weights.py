@@ -167,12 +167,20 @@ class LayerWeights:
 
 @dataclass
 class MtpWeights:
-    """One multi-token-prediction stage: norms + projection over [hidden ; embedding] + a layer body."""
+    """One multi-token-prediction stage: norms + projection over [embedding ; hidden] + a layer body.
+
+    `eh_proj` columns follow published DeepSeek-V3 checkpoints (and vLLM / SGLang, which compute
+    `eh_proj(cat([enorm(embed), hnorm(hidden)]))`): the first `hidden` columns multiply the normalised
+    embedding of the next token, the last `hidden` columns the normalised hidden state.  `embed` / `lm_head`
+    are the stage's own `embed_tokens` / `shared_head.head` when a checkpoint stores ones that differ from
+    the main model's (None: shared with the main model, as in the published checkpoints)."""
     enorm: torch.Tensor
     hnorm: torch.Tensor
-    eh_proj: torch.Tensor         # [hidden, 2*hidden]
+    eh_proj: torch.Tensor         # [hidden, 2*hidden], columns [embedding | hidden]
     layer: LayerWeights
     final_norm: torch.Tensor
+    embed: Optional[torch.Tensor] = None
+    lm_head: Optional[torch.Tensor] = None
 
 
 @dataclass

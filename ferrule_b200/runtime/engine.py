@@ -156,21 +156,34 @@ class Engine:
             raise RuntimeError("engine is shut down")
         if req.max_new_tokens < 0:
             raise ValueError("max_new_tokens must be >= 0")
-        prev = self._sessions.pop(req.session_id, None) if req.session_id else None
+        prev = self._sessions.get(req.session_id) if req.session_id else None
         now = time.perf_counter_ns()
+        # validate before anything is taken: a rejected continuation leaves its retained session intact
+        total = (len(prev.tokens) if prev is not None else 0) + len(req.prompt_tokens)
+        if prev is None and not req.prompt_tokens:
+            raise ValueError("empty prompt")
+        if total + 1 > self.cfg.scheduler.ctx_size:
+            raise ValueError("prompt does not fit the context window")
         if prev is not None:
+            committed = self.kv.sequence(prev.kv_seq).committed_tokens
+            if committed != prev.position:
+                raise RuntimeError(f"retained session {req.session_id!r}: KV holds {committed} tokens, "
+                                   f"sequence position is {prev.position}")
+            del self._sessions[req.session_id]
             seq = SequenceState(req, kv_seq=prev.kv_seq, tokens=prev.tokens + list(req.prompt_tokens),
                                 position=prev.position, arrival_ns=now)
         else:
-            if not req.prompt_tokens:
-                raise ValueError("empty prompt")
             seq = SequenceState(req, kv_seq=self.kv.alloc_sequence(), tokens=list(req.prompt_tokens),
                                 arrival_ns=now)
         seq.prompt_len = len(seq.tokens)
-        if seq.prompt_len + 1 > self.cfg.scheduler.ctx_size:
-            self.kv.free_sequence_pages(seq.kv_seq)
-            raise ValueError("prompt does not fit the context window")
-        self.scheduler.submit(seq)
+        try:
+            self.scheduler.submit(seq)
+        except Exception:
+            if prev is not None:
+                self._sessions[req.session_id] = prev
+            else:
+                self._retire(self.kv.free_sequence_pages(seq.kv_seq))
+            raise
         return seq
 
     def cancel_request(self, request_id: str) -> bool:
@@ -563,6 +576,9 @@ class Engine:
     def _finish(self, seq: SequenceState, reason: FinishReason) -> None:
         if seq.status == SeqStatus.FINISHED and seq.slot < 0 and seq.kv_seq < 0:
             return
+        # a suspended (preempted) sequence that ends never comes back: drop its host snapshot
+        self.scheduler.suspended.pop(seq.request_id, None)
+        self._snapshots.pop(seq.request_id, None)
         self.scheduler.finish(seq, reason)
         self._release_sequence(seq, reason)
 

@@ -11,8 +11,8 @@
   race-free `listen -> step -> wait` pattern over a `CompletionHub`: a notification that arrives between
   the step and the wait is not lost because the ticket was taken before the step.
 
-Counterpart of crates/ferrule-runtime/src/engine.rs:29-75 (trait), :77-400 (completion owner, affinity
-guard) and crates/ferrule-runtime/src/native_executor.rs:13-300.
+Counterpart of crates/ferrule-runtime/src/engine/inference.rs:374-411 (trait), :19-215 (completion owner,
+affinity guard) and crates/ferrule-runtime/src/engine/native_executor.rs:24-245.
 """
 from __future__ import annotations
 

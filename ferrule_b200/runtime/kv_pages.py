@@ -141,6 +141,8 @@ class KvPageManager:
         return out
 
     def _decref(self, page: int, ret: KvRetirement) -> None:
+        if not 0 <= page < self.n_pages:
+            raise KvError(f"page id {page} outside the pool")
         if self._ref[page] <= 0:
             raise KvError(f"page {page} released twice")
         self._ref[page] -= 1
@@ -372,7 +374,8 @@ class KvPageManager:
         if s.open_reservation is not None:
             ret.extend(self.abort_reservations([s.open_reservation]))
         for p in s.pages:
-            self._decref(p, ret)
+            if p >= 0:              # a preempted sequence's released pages are marked -1
+                self._decref(p, ret)
         del self._seqs[seq_id]
         self._preempted.pop(seq_id, None)
         return ret
@@ -387,7 +390,8 @@ class KvPageManager:
         ret = KvRetirement()
         keep = self.pages_for(tokens)
         for p in s.pages[keep:]:
-            self._decref(p, ret)
+            if p >= 0:
+                self._decref(p, ret)
         del s.pages[keep:]
         s.committed_tokens = tokens
         s.generation += 1

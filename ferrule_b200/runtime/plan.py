@@ -12,8 +12,9 @@ it, never a silent fallback to another path.
 * Materialization boundary types (`MaterializationRequest`, `Placement`, `Preparation`) - what a stage
   hands to the materialization provider when one of its resources is not resident.
 
-Counterpart of crates/ferrule-backend/src/cuda/provider_catalog.rs:48-330 (registry, fail-closed compile),
-crates/ferrule-model/src/execution_plan.rs:16-275 (stage types) and
+Counterpart of crates/ferrule-backend/src/cuda/provider.rs:21-270 (registry, fail-closed compile) and
+crates/ferrule-backend/src/plan.rs:41-495 (operations, launch descriptors, model plan),
+crates/ferrule-model/src/execution/stage.rs:20-470 (stage types) and
 crates/ferrule-model/src/materialization.rs:16-320 (boundary types).
 """
 from __future__ import annotations

@@ -263,7 +263,11 @@ class SpeculativeDecoder:
             if cancelled:
                 eng._finish(seq, FinishReason.CANCELLED)
             elif stopped:
-                # tokens after the stop string were committed in KV but are not part of the answer
+                # the cycle committed KV rows beyond the stop string: roll the sequence's KV back to the
+                # published position, so that a retained session continues from rows that match its tokens
+                kvs = eng.kv.sequence(seq.kv_seq)
+                if kvs.committed_tokens > seq.position:
+                    eng._retire(eng.kv.truncate_sequence(seq.kv_seq, seq.position))
                 eng._finish(seq, FinishReason.STOP_STRING)
             elif finish is not None:
                 eng._finish(seq, finish)

@@ -226,6 +226,10 @@ class ModelWorker:
         except ValueError as e:
             self._reply(reply, stream, exc=WorkerError(str(e), 400, "invalid_request"))
             return True
+        except Exception as e:  # noqa: BLE001 - the caller must get an answer and the worker must live on
+            self._reply(reply, stream, exc=WorkerError(f"internal error: {type(e).__name__}: {e}", 500,
+                                                       "internal_error"))
+            return True
         self._live[rid] = _Live(stream, IncrementalDecodeState(self.tokenizer), time.monotonic())
         METRICS.add(requests_started=1, prompt_tokens=len(ids))
         log_event(REQUEST_LOG, "admitted", request_id=rid, prompt_tokens=len(ids), max_tokens=max_tokens)

@@ -1,6 +1,7 @@
 """Small, self-ending workloads of one kernel family each, for profiler captures and quick timings.
 
     python -m ferrule_b200.utils.kernel_probe <case> [reps]
+    python -m ferrule_b200.utils.kernel_probe decode_step <layers> [eager]
 
 Cases use decode-step shapes of the DeepSeek-V2-Lite configuration (batch 32, context about 640) unless
 noted; weight sets are rotated through more buffers than fit in L2 where the kernel is bandwidth-bound, and
@@ -209,6 +210,40 @@ def case_v3_fp8_decode(reps):
     return timed(lambda i: fwd.forward(b), reps), {"format": fmt}
 
 
+def case_decode_step(layers: int, eager: bool):
+    """One decode step of the DeepSeek-V2-Lite shape (bf16, batch 32, context 640) with `layers` layers.
+    `eager`: three eager steps and nothing else - the form used for a launch list, where every kernel of the
+    step is one launch.  Otherwise the step is captured in a CUDA graph and 20 replays are timed."""
+    from ferrule_b200.models import config as C, deepseek as D, weights as W
+    cfg = C.deepseek_v2_lite()
+    cfg = cfg.with_(n_layers=layers or cfg.n_layers)
+    w = W.random_weights(cfg, device=DEV, fast_device_init=True)
+    B, ctx, page, max_blocks = 32, 640, 64, 16
+    pool = D.KvPool(cfg, B * max_blocks + 1, page, DEV)
+    pool.data.normal_(0, 0.3)
+    fwd = D.CudaForward(w, pool, max_rows=64, max_logit_rows=64, decode_rows=64, max_seq_len=1024, attn_splits=8)
+    g = D.DecodeGraph(fwd, B, B, max_blocks)
+    bt = torch.arange(1, B * max_blocks + 1, dtype=torch.int32, device=DEV).view(B, max_blocks)
+    g.batch.block_table.copy_(bt)
+    g.batch.token_ids.random_(0, cfg.vocab_size)
+    g.batch.positions.fill_(ctx)
+    g.batch.row_pos.fill_(ctx)
+    g.batch.row_seq.copy_(torch.arange(B, device=DEV))
+    g.batch.write_slot.copy_((bt[:, ctx // page].long() * page + ctx % page))
+    extra = {"layers": cfg.n_layers, "weight_bytes": w.nbytes()}
+    if eager:
+        for _ in range(3):
+            fwd.forward(g.batch)
+        torch.cuda.synchronize()
+        extra["launches_per_step"] = fwd.launches
+        return 0.0, extra
+    g.capture()
+    extra["launches_per_step"] = g.launches
+    us = timed(lambda i: g.replay(), 20)
+    extra["tokens_per_s"] = round(B / us * 1e6, 1)
+    return us, extra
+
+
 CASES = {"v3_fp8_decode": case_v3_fp8_decode, "prefill": case_prefill, "attention": case_attention, "gemm_dense": case_gemm_dense, "gemm_grouped": case_gemm_grouped,
          "gemm_fp8": case_gemm_fp8, "small": case_small, "v4": case_v4}
 
@@ -217,11 +252,15 @@ def main() -> int:
     name = sys.argv[1] if len(sys.argv) > 1 else "attention"
     reps = int(sys.argv[2]) if len(sys.argv) > 2 else 20
     torch.manual_seed(0)
-    us, extra = CASES[name](reps)
+    if name == "decode_step":           # second argument: number of layers (0 = all), third: "eager"
+        us, extra = case_decode_step(reps if len(sys.argv) > 2 else 0, len(sys.argv) > 3 and sys.argv[3] == "eager")
+        reps = 20
+    else:
+        us, extra = CASES[name](reps)
     out = {"case": name, "reps": reps, "us_per_call": round(us, 2)}
     out.update(extra)
     for key in ("weight_bytes", "kv_bytes"):
-        if key in extra:
+        if key in extra and us > 0:
             out["gb_per_s"] = round(extra[key] / us / 1e3, 1)
     from ferrule_b200.ops import _lib
     out["device_status"] = _lib.read_status()[0]

@@ -10,6 +10,8 @@ import sys
 import torch
 import torch.distributed as dist
 
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))))
+
 
 def oracle(x, idx, wts, w13, w2, residual, extra):
     """fp32 math with the kernels' rounding points (bf16 after SwiGLU and after the weighted expert output)."""

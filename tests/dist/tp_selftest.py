@@ -1,7 +1,7 @@
 """Multi-GPU self test of the fused collectives and the tensor-parallel model path.
 
   python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
-      --master-port P -m ferrule_b200.parallel.selftest [--bench]
+      --master-port P tests/dist/tp_selftest.py [--bench]
 
 Checks, on N ranks of one node:
   1. GEMM -> all-reduce fused epilogue against GEMM + NCCL all-reduce,
@@ -21,6 +21,8 @@ import sys
 
 import torch
 import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))))
 
 
 def _time_ms(fn, iters: int, world: int) -> float:
@@ -80,12 +82,12 @@ def main() -> int:
     dev = torch.device("cuda", local)
     dist.init_process_group("nccl", device_id=dev)
 
-    from ..models import config as C
-    from ..models import deepseek as D
-    from ..models import weights as W
-    from ..ops import _lib
-    from ..ops import kernels as K
-    from .tp import TensorParallel
+    from ferrule_b200.models import config as C
+    from ferrule_b200.models import deepseek as D
+    from ferrule_b200.models import weights as W
+    from ferrule_b200.ops import _lib
+    from ferrule_b200.ops import kernels as K
+    from ferrule_b200.parallel.tp import TensorParallel
 
     res = {"world": world, "checks": {}}
     ok = True

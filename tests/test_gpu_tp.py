@@ -14,7 +14,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 def test_selftest_two_ranks():
     env = dict(os.environ, NCCL_NVLS_ENABLE="0", PYTHONPATH=ROOT)
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
-           "--master-addr", "127.0.0.1", "--master-port", "29517", "-m", "ferrule_b200.parallel.selftest"]
+           "--master-addr", "127.0.0.1", "--master-port", "29517", os.path.join(ROOT, "tests", "dist", "tp_selftest.py")]
     p = subprocess.run(cmd, capture_output=True, text=True, timeout=600, cwd=ROOT, env=env)
     lines = [l for l in p.stdout.splitlines() if l.startswith("{")]
     assert lines, p.stdout[-2000:] + p.stderr[-4000:]
@@ -29,7 +29,7 @@ def test_expert_parallel_dispatch_combine_two_ranks():
     against a single-device oracle (ragged token counts, skewed routing, all-gather of the outputs)."""
     env = dict(os.environ, NCCL_NVLS_ENABLE="0", PYTHONPATH=ROOT)
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
-           "--master-addr", "127.0.0.1", "--master-port", "29519", "-m", "ferrule_b200.parallel.ep_selftest"]
+           "--master-addr", "127.0.0.1", "--master-port", "29519", os.path.join(ROOT, "tests", "dist", "ep_selftest.py")]
     p = subprocess.run(cmd, capture_output=True, text=True, timeout=600, cwd=ROOT, env=env)
     lines = [l for l in p.stdout.splitlines() if l.startswith("{")]
     assert lines, p.stdout[-2000:] + p.stderr[-4000:]

@@ -38,16 +38,24 @@ def test_no_alloc_argmax_matches_existing_entry_point_twice():
     g = torch.Generator(device="cuda").manual_seed(123)
     # two calls in a row with different shapes: the second must not be disturbed by what the first
     # left in the shared scratch (more rows and chunks' worth of candidates, counters at 64)
-    for rows, vocab in ((37, 102400), (5, 1000)):
+    for call, (rows, vocab) in enumerate(((37, 102400), (5, 1000), (37, 102400))):
         logits = torch.randn(rows, vocab, generator=g, device="cuda")
         logits[0, 3] = logits[0, vocab - 1] = 77.0          # tie -> lower index
         logits[1] = float("nan")                            # no finite candidate -> -1
         ids = torch.full((rows,), -7, dtype=torch.int32, device="cuda")
         vals = torch.zeros(rows, device="cuda")
+        # torch's counter only sees torch's own allocator; the driver's free-byte count (cudaMemGetInfo) also
+        # sees a raw cudaMalloc.  The first call on a device resolves the scratch address (and may make the driver
+        # load the module), so the driver-level comparison starts with the second call.
+        torch.cuda.synchronize()
         before = torch.cuda.memory_allocated()
+        free_before = torch.cuda.mem_get_info()[0]
         rc = fn(logits.data_ptr(), logits.stride(0), rows, vocab, ids.data_ptr(), vals.data_ptr(), stream)
         assert rc == 0
+        torch.cuda.synchronize()
         assert torch.cuda.memory_allocated() == before
+        if call > 0:
+            assert torch.cuda.mem_get_info()[0] >= free_before
         ref_ids, ref_vals = _reference(K, logits)
         torch.cuda.synchronize()
         assert torch.equal(ids.cpu(), ref_ids.cpu())
