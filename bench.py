@@ -10,12 +10,14 @@ dense (inter 10944), 26 MoE layers (64 routed + 2 shared experts, top-6, inter 1
 64-token pages.  One "step" is one decode step of the whole batch (32 new tokens).  N > 1 runs
 tensor parallel over N ranks on the same batch (strong scaling).
 
-Two numbers:
-  value : K decode steps replayed back to back as the captured CUDA graph, timed with CUDA events
-          (device time of the kernels only).
-  e2e   : the same K decode steps driven through the public engine API (`Engine.step`): scheduler,
-          KV reservation/commit, one pinned host->device copy of the step's inputs, the graph, one
-          device->host read of the greedy tokens, token publication.
+Two numbers over the same K decode steps (the same sequences, the same context window, which grows by
+one token per step):
+  e2e   : the K steps driven through the public engine API (`Engine.step`): scheduler, KV
+          reservation/commit, one pinned host->device copy of every step's inputs, the captured graph,
+          one device->host read of the greedy tokens, token publication.
+  value : the K steps again, from the same starting state, without the host: after every graph replay
+          one small kernel feeds the greedy tokens back and moves positions and KV write slots on
+          (device time of the kernels only, CUDA events).
 Every step streams the full weight set (31 GB, far larger than the 126 MB L2), so no L2 flush is
 needed between iterations.
 """
@@ -176,14 +178,23 @@ def main() -> None:
             dist.barrier()
         torch.cuda.synchronize()
 
-    # ---- prefill (untimed for the decode metric; TTFT is reported from it) ----
+    # ---- prefill (untimed for the decode metric; TTFT and prefill tokens/s are reported from it) ----
+    barrier()
+    t_pf0 = time.perf_counter()
     while any(s.prefill_remaining > 0 for s in engine.scheduler.active.values()) or engine.scheduler.waiting:
         engine.step(emit)
+    barrier()
+    prefill_s = time.perf_counter() - t_pf0
     # one decode step so that every sequence has emitted its first token
     engine.step(emit)
     ttft = sorted(first_token_t[r] - t_submit for r in first_token_t)
     for _ in range(Wm):
         engine.step(emit)
+    torch.cuda.synchronize()
+    # the state the timed window starts from (row order of the decode batch = admission order)
+    seqs0 = list(engine.scheduler.active.values())
+    start_ids = [s.staged_token for s in seqs0]
+    start_pos = [s.position for s in seqs0]
 
     # ---- e2e: K engine steps, device-timed around the whole loop ----
     sampler = ClockSampler(local_rank)
@@ -204,17 +215,39 @@ def main() -> None:
     d2h = (runner.stats.d2h_bytes - d2h0) // K
     e2e_launches = runner.stats.kernel_launches - l0
 
-    # ---- device-only: replay the captured decode graph K times ----
-    st, graph = runner.graphs[B]
-    for _ in range(3):
-        graph.replay()
-    barrier()
+    # ---- device-only: the same K steps from the same starting state, fed back on the device ----
+    import numpy as np
     from ferrule_b200.ops import _lib
+    from ferrule_b200.ops import kernels as KK
+    st, graph = runner.graphs[B]
+    runner._ahead = None                    # a step launched ahead by the last engine step is not consumed
+    torch.cuda.synchronize()
+    pages = [engine.kv.sequence(s.kv_seq).pages for s in seqs0]     # by now they cover the whole window
+
+    def rewind() -> None:
+        st.np_ids[:B] = start_ids
+        st.np_pos[:B] = start_pos
+        st.np_rpos[:B] = start_pos
+        st.np_seq[:B] = np.arange(B)
+        st.np_bt[:] = 0
+        for i, pg in enumerate(pages):
+            st.np_bt[i, :len(pg)] = pg
+            st.np_slot[i] = pg[start_pos[i] // page] * page + start_pos[i] % page
+        st.upload()
+
+    def device_steps(n: int) -> None:
+        for _ in range(n):
+            graph.replay()
+            KK.decode_advance(runner.fwd.ws.next_id[:B], graph.batch, cfg.vocab_size, page, True)
+
+    rewind()
+    device_steps(3)
+    rewind()
+    barrier()
     _lib.read_peer_wait()
     d0, d1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     d0.record()
-    for _ in range(K):
-        graph.replay()
+    device_steps(K)
     d1.record()
     barrier()
     clocks = sampler.stop()
@@ -222,10 +255,10 @@ def main() -> None:
     wait_ns, wait_n = _lib.read_peer_wait()
 
     status = _lib.read_status()
-    times = torch.tensor([dev_ms, e2e_ms, wait_ns / 1e6], dtype=torch.float64, device=dev)
+    times = torch.tensor([dev_ms, e2e_ms, prefill_s], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
-    dev_ms, e2e_ms, wait_ms = times.tolist()
+    dev_ms, e2e_ms, prefill_s = times.tolist()
     tpots = []
     for r, ts in token_times.items():
         if len(ts) > 2:
@@ -240,7 +273,9 @@ def main() -> None:
             "ms_per_step": round(dev_ms / K, 4), "higher_is_better": True, "scaling": "strong",
             "vs_baseline": round(value / BASELINE_TOK_S, 1), "dtype": {"bf16": "bf16", "fp8_block": "fp8 e4m3 weights (128x128 scales) + fp8 activations (1x128), bf16 elsewhere", "fp8_mxfp4": "mxfp4 experts + fp8 dense, bf16 elsewhere"}[args.weight_format],
             "data": "synthetic (uniform-random token ids, random-init N(0,0.02) weights)",
-            "config": {"model": cfg.name, "global_batch": B, "seq_len": P, "decode_context": P + Wm + 1,
+            "config": {"model": cfg.name, "global_batch": B, "seq_len": P,
+                       "decode_context": "%d..%d (grows one token per step, in both numbers)"
+                                         % (min(start_pos), max(start_pos) + K),
                        "parallelism": par, "kv_page_size": page, "layers": cfg.n_layers,
                        "l2_policy": "inputs larger than L2: each step streams %.1f GB of weights per GPU"
                                     % (weights.nbytes() / 1e9),
@@ -248,13 +283,17 @@ def main() -> None:
             "e2e": {"value": round(e2e_value, 1), "unit": "tokens/s", "ms_per_step": round(e2e_ms / K, 4),
                     "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h),
                     "path": "Engine.step (scheduler + KV transactions + pinned H2D + graph + D2H)"},
-            "peer_wait": {"ms_per_step_max_rank": round(wait_ms / K, 4), "waits_per_step": wait_n // max(K, 1),
+            "peer_wait": {"waits_per_step": wait_n // max(K, 1),
                           "avg_wait_us": round(wait_ns / 1e3 / max(wait_n, 1), 2),
-                          "note": "time one thread per waiting CTA spent spinning on peer arrival flags; CTAs wait concurrently"},
-            "gpu_launches": int(graph.launches * K),
+                          "note": "rank 0: spins of a CTA on a peer's arrival word, and their mean length"},
+            "gpu_launches": int((graph.launches + 1) * K),
             "gpu_launches_e2e": int(e2e_launches),
             "clocks": {"sm_mhz": clocks["sm_mhz"], "sm_max_mhz": clocks["sm_max_mhz"], "reasons": clocks["reasons"],
                        "samples": clocks["samples"]},
+            "prefill": {"tokens_per_s": round(B * P / prefill_s, 1), "seconds": round(prefill_s, 4),
+                        "tokens": B * P, "chunk": sched.prefill_chunk_size, "timing": "host clock around the engine "
+                        "steps of the prefill phase, device synchronised on both sides"},
+            "lookahead": {"launched": runner.stats.lookahead_launched, "hits": runner.stats.lookahead_hits},
             "ttft_p50_s": round(ttft[len(ttft) // 2], 4) if ttft else None,
             "tpot_p50_s": round(statistics.median(tpots), 6) if tpots else None,
             "device_status": list(status),

@@ -653,6 +653,18 @@ router_plan_fused_kernel(const __nv_bfloat16* __restrict__ x, long long ldx,
 // no inter-CTA dependency: the GEMMs take the counters as their per-tile row counts.  The order of an expert's
 // rows depends on the atomics; every row is computed independently, so the outputs do not.
 // ---------------------------------------------------------------------------------
+// Optional prologue of router_append_kernel: residual add + RMSNorm of the token's row (see the kernel).
+struct NormPrologue {
+  const __nv_bfloat16* delta;     // sublayer output added to the residual row (may be null)
+  long long ldd;
+  const __nv_bfloat16* norm_w;    // null: no prologue, `x` already holds the normalised rows
+  __nv_bfloat16* res_out;         // bf16(x + delta), the new residual stream (may be null)
+  long long ldr;
+  __nv_bfloat16* norm_out;        // normalised rows for other consumers (shared experts); may be null
+  long long ldn;
+  float eps;
+};
+
 __global__ void __launch_bounds__(1024)
 router_append_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, const __nv_bfloat16* __restrict__ w,
                      int hidden, const float* __restrict__ bias, const long long* __restrict__ hash_table,
@@ -660,19 +672,79 @@ router_append_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, const _
                      int topk_groups, int normalize, float route_scale, int* __restrict__ out_idx,
                      float* __restrict__ out_w, int e_lo, int e_hi, int slot_rows, int dst_slots,
                      int* __restrict__ cnt, int* __restrict__ src_token, int* __restrict__ dst_row,
-                     float* __restrict__ row_scale, __nv_bfloat16* __restrict__ xg, long long ldxg, DeviceStatus* st) {
+                     float* __restrict__ row_scale, __nv_bfloat16* __restrict__ xg, long long ldxg, DeviceStatus* st,
+                     NormPrologue np) {
   pdl_launch_dependents();
   pdl_wait();
-  extern __shared__ float xs[];            // hidden floats, then `experts` logits
+  extern __shared__ float xs[];            // hidden floats, then `experts` logits, then (norm prologue) hidden bf16
   float* logits = xs + hidden;
   __shared__ int rlist[32];
+  __shared__ float red[8];
   const int t = blockIdx.x;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
-  for (int i = threadIdx.x * 8; i < hidden; i += blockDim.x * 8) {
-    const uint4 v = *reinterpret_cast<const uint4*>(x + t * ldx + i);
-    const __nv_bfloat16* vp = reinterpret_cast<const __nv_bfloat16*>(&v);
+  // rows copied into the expert-major buffer come from here: the input row, or the prologue's normalised row
+  const __nv_bfloat16* xrow = x + t * ldx;
+  if (np.norm_w != nullptr) {
+    // ---- residual add + RMSNorm of this token's row, with the element -> thread mapping, the rounding points and
+    // the reduction order of add_rmsnorm_kernel (256 threads x 8 elements, 8 warp sums combined by one warp), so
+    // the result is bit-equal to running that kernel first.  x = residual stream, np.delta = the sublayer output. ----
+    __nv_bfloat16* xb = reinterpret_cast<__nv_bfloat16*>(logits + experts);
+    const __nv_bfloat16* dr = np.delta ? np.delta + t * np.ldd : nullptr;
+    float ss = 0.f;
+    if (threadIdx.x < 256) {
+      for (int i = threadIdx.x * 8; i < hidden; i += 256 * 8) {
+        uint4 a = *reinterpret_cast<const uint4*>(xrow + i);
+        const __nv_bfloat16* ap = reinterpret_cast<const __nv_bfloat16*>(&a);
+        float v[8];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) xs[i + j] = __bfloat162float(vp[j]);
+        for (int j = 0; j < 8; ++j) v[j] = __bfloat162float(ap[j]);
+        if (dr) {
+          uint4 d = *reinterpret_cast<const uint4*>(dr + i);
+          const __nv_bfloat16* dp = reinterpret_cast<const __nv_bfloat16*>(&d);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) v[j] = bf16_round(v[j] + __bfloat162float(dp[j]));
+          if (np.res_out) {
+            __nv_bfloat16 o[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) o[j] = __float2bfloat16_rn(v[j]);
+            *reinterpret_cast<uint4*>(np.res_out + t * np.ldr + i) = *reinterpret_cast<uint4*>(o);
+          }
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          xs[i + j] = v[j];
+          ss += v[j] * v[j];
+        }
+      }
+      ss = warp_sum(ss);
+      if (lane == 0) red[warp] = ss;
+    }
+    __syncthreads();
+    float tot = lane < 8 ? red[lane] : 0.f;
+    tot = warp_sum(tot);
+    const float inv = rsqrtf(tot / hidden + np.eps);
+    if (threadIdx.x < 256) {
+      for (int i = threadIdx.x * 8; i < hidden; i += 256 * 8) {
+        uint4 wv = *reinterpret_cast<const uint4*>(np.norm_w + i);
+        const __nv_bfloat16* wp = reinterpret_cast<const __nv_bfloat16*>(&wv);
+        __nv_bfloat16 o[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          o[j] = __float2bfloat16_rn(xs[i + j] * inv * __bfloat162float(wp[j]));
+          xs[i + j] = __bfloat162float(o[j]);
+        }
+        *reinterpret_cast<uint4*>(xb + i) = *reinterpret_cast<uint4*>(o);
+        if (np.norm_out) *reinterpret_cast<uint4*>(np.norm_out + t * np.ldn + i) = *reinterpret_cast<uint4*>(o);
+      }
+    }
+    xrow = xb;
+  } else {
+    for (int i = threadIdx.x * 8; i < hidden; i += blockDim.x * 8) {
+      const uint4 v = *reinterpret_cast<const uint4*>(xrow + i);
+      const __nv_bfloat16* vp = reinterpret_cast<const __nv_bfloat16*>(&v);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) xs[i + j] = __bfloat162float(vp[j]);
+    }
   }
   __syncthreads();
   for (int e = warp; e < experts; e += 2 * nwarps) {
@@ -729,7 +801,7 @@ router_append_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, const _
     const int s = i / vec, c = i - s * vec;
     const int r = rlist[s];
     if (r >= 0)
-      *reinterpret_cast<uint4*>(xg + r * ldxg + c * 8) = *reinterpret_cast<const uint4*>(x + t * ldx + c * 8);
+      *reinterpret_cast<uint4*>(xg + r * ldxg + c * 8) = *reinterpret_cast<const uint4*>(xrow + c * 8);
   }
 }
 
@@ -1013,6 +1085,40 @@ topk_logits_kernel(const float* __restrict__ logits, long long ldl, int rows, in
 }
 
 // ---------------------------------------------------------------------------------
+// Greedy-token feedback for back-to-back decode steps.  The token a step produced becomes the next step's
+// input without a trip through the host (ids < 0, "no finite candidate", are fed back as token 0: the host
+// ends such a sequence when it reads the result).  With `advance` the whole input row moves one position on:
+// position and visible length + 1, and the KV write slot is looked up in the sequence's page list (-1 when
+// the list has no page for the position: the row then writes nothing).
+// ---------------------------------------------------------------------------------
+__global__ void decode_advance_kernel(const int* __restrict__ next_id, int* __restrict__ token_ids,
+                                      int* __restrict__ positions, int* __restrict__ row_pos,
+                                      long long* __restrict__ write_slot, const int* __restrict__ row_seq,
+                                      const int* __restrict__ block_table, int max_blocks, int page_size,
+                                      int num_seqs, int rows, int vocab, int advance) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int r = blockIdx.x * blockDim.x + threadIdx.x;
+  if (r >= rows) return;
+  int id = next_id[r];
+  if (id < 0 || id >= vocab) id = 0;
+  token_ids[r] = id;
+  if (!advance) return;
+  if (row_pos[r] < 0) return;                     // padding row of a graph bucket
+  const int pos = positions[r] + 1;
+  positions[r] = pos;
+  row_pos[r] = pos;
+  const int seq = row_seq[r];
+  long long slot = -1;
+  const int blk = pos / page_size;
+  if (seq >= 0 && seq < num_seqs && blk < max_blocks) {
+    const int page = block_table[static_cast<long long>(seq) * max_blocks + blk];
+    if (page >= 0) slot = static_cast<long long>(page) * page_size + pos % page_size;
+  }
+  write_slot[r] = slot;
+}
+
+// ---------------------------------------------------------------------------------
 // paged pool: copy whole pages (all layers) for copy-on-write.  pool is
 // [layers, pages, page_elems]; pairs = (src_page, dst_page).
 // ---------------------------------------------------------------------------------
@@ -1144,10 +1250,29 @@ extern "C" int fb_router_append(const void* x, long long ldx, const void* w, int
                                 int* out_idx, float* out_w, int e_lo, int e_hi, int slot_rows, int dst_slots, int* cnt,
                                 int* src_token, int* dst_row, float* row_scale, void* xg, long long ldxg,
                                 void* status, void* stream) {
+  return fb_norm_router_append(x, ldx, nullptr, 0, nullptr, nullptr, 0, nullptr, 0, 0.f, w, hidden, bias, hash_table,
+                               token_ids, rows, experts, topk, score_fn, n_groups, topk_groups, normalize, route_scale,
+                               out_idx, out_w, e_lo, e_hi, slot_rows, dst_slots, cnt, src_token, dst_row, row_scale,
+                               xg, ldxg, status, stream);
+}
+
+extern "C" int fb_norm_router_append(const void* x, long long ldx, const void* delta, long long ldd,
+                                     const void* norm_w, void* res_out, long long ldr, void* norm_out, long long ldn,
+                                     float eps, const void* w, int hidden, const float* bias,
+                                     const long long* hash_table, const int* token_ids, int rows, int experts,
+                                     int topk, int score_fn, int n_groups, int topk_groups, int normalize,
+                                     float route_scale, int* out_idx, float* out_w, int e_lo, int e_hi,
+                                     int slot_rows, int dst_slots, int* cnt, int* src_token, int* dst_row,
+                                     float* row_scale, void* xg, long long ldxg, void* status, void* stream) {
   if (rows <= 0 || experts <= 0 || experts > 256 || topk <= 0 || topk > 32 || topk > experts) return FB_ERR_SHAPE;
   if (hidden % 256 != 0 || hidden > 8192 || (ldx % 8) != 0 || (ldxg % 8) != 0) return FB_ERR_SHAPE;
   if (slot_rows < rows || e_hi <= e_lo || !cnt || !src_token || !dst_row || !row_scale || !xg) return FB_ERR_SHAPE;
-  const size_t smem = (static_cast<size_t>(hidden) + experts) * sizeof(float);
+  if (norm_w != nullptr && ((ldd % 8) != 0 || (ldr % 8) != 0 || (ldn % 8) != 0 || (experts % 4) != 0))
+    return FB_ERR_SHAPE;
+  const NormPrologue np{static_cast<const __nv_bfloat16*>(delta), ldd, static_cast<const __nv_bfloat16*>(norm_w),
+                        static_cast<__nv_bfloat16*>(res_out), ldr, static_cast<__nv_bfloat16*>(norm_out), ldn, eps};
+  const size_t smem = (static_cast<size_t>(hidden) + experts) * sizeof(float) +
+                      (norm_w ? static_cast<size_t>(hidden) * 2 : 0);
   static bool attr_done = false;
   if (!attr_done) {
     cudaFuncSetAttribute(router_append_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);
@@ -1157,7 +1282,7 @@ extern "C" int fb_router_append(const void* x, long long ldx, const void* w, int
              static_cast<const __nv_bfloat16*>(x), ldx, static_cast<const __nv_bfloat16*>(w), hidden, bias, hash_table,
              token_ids, rows, experts, topk, score_fn, n_groups, topk_groups, normalize, route_scale, out_idx, out_w,
              e_lo, e_hi, slot_rows, dst_slots, cnt, src_token, dst_row, row_scale, static_cast<__nv_bfloat16*>(xg), ldxg,
-             static_cast<DeviceStatus*>(status));
+             static_cast<DeviceStatus*>(status), np);
   return FB_CHECK_LAUNCH();
 }
 
@@ -1250,4 +1375,18 @@ extern "C" int fb_copy_pages(void* pool, long long layer_stride, long long page_
       static_cast<__nv_bfloat16*>(pool), layer_stride, page_elems, pairs, n_pairs, n_pages, layers,
       static_cast<DeviceStatus*>(status));
   return FB_CHECK_LAUNCH();
+}
+
+extern "C" int fb_decode_advance(const int* next_id, int* token_ids, int* positions, int* row_pos,
+                                 long long* write_slot, const int* row_seq, const int* block_table,
+                                 int max_blocks, int page_size, int num_seqs, int rows, int vocab, int advance,
+                                 void* stream) {
+  if (!next_id || !token_ids || rows <= 0 || vocab <= 0) return FB_ERR_SHAPE;
+  if (advance && (!positions || !row_pos || !write_slot || !row_seq || !block_table || max_blocks <= 0 ||
+                  page_size <= 0 || num_seqs <= 0))
+    return FB_ERR_SHAPE;
+  launch_pdl(decode_advance_kernel, dim3((rows + 127) / 128), dim3(128), 0, static_cast<cudaStream_t>(stream),
+             next_id, token_ids, positions, row_pos, write_slot, row_seq, block_table, max_blocks, page_size,
+             num_seqs, rows, vocab, advance);
+  return cudaGetLastError() == cudaSuccess ? FB_OK : FB_ERR_LAUNCH;
 }

@@ -141,6 +141,8 @@ typedef struct FbAttnArgs {
   const int* selection;     // optional [rows, sel_width] explicit pool rows per query row, -1 = masked
   int sel_width;            //   (then block_table / row_seq / row_pos are unused and group_rows must be 1)
   void* trace;              // optional uint64 [32]: globaltimer stamps of CTA (0,0,0) (profiling)
+  int decode_only;          // the caller asserts: every sequence has exactly one query row in this launch and its
+                            // KV rows below row_pos were written before the running step began (plain decode)
 } FbAttnArgs;
 
 int fb_mla_attention(const FbAttnArgs* args, void* stream);
@@ -181,6 +183,15 @@ int fb_router_append(const void* x, long long ldx, const void* w, int hidden, co
                      int n_groups, int topk_groups, int normalize, float route_scale, int* out_idx, float* out_w,
                      int e_lo, int e_hi, int slot_rows, int dst_slots, int* cnt, int* src_token, int* dst_row,
                      float* row_scale, void* xg, long long ldxg, void* status, void* stream);
+// the same with a prologue: row = bf16(x + delta) (delta may be null) -> res_out, RMSNorm(row) * norm_w -> norm_out
+// and into the router, bit-equal to fb_add_rmsnorm followed by fb_router_append (norm_w null: no prologue)
+int fb_norm_router_append(const void* x, long long ldx, const void* delta, long long ldd, const void* norm_w,
+                          void* res_out, long long ldr, void* norm_out, long long ldn, float eps, const void* w,
+                          int hidden, const float* bias, const long long* hash_table, const int* token_ids, int rows,
+                          int experts, int topk, int score_fn, int n_groups, int topk_groups, int normalize,
+                          float route_scale, int* out_idx, float* out_w, int e_lo, int e_hi, int slot_rows,
+                          int dst_slots, int* cnt, int* src_token, int* dst_row, float* row_scale, void* xg,
+                          long long ldxg, void* status, void* stream);
 int fb_gather_rows(const void* x, long long ldx, const int* src_token, const int* meta, void* out,
                    long long ldo, int cap_rows, int dim, int src_rows, void* status, void* stream);
 int fb_moe_reduce_norm(const void* route_out, int slots, int topk, const int* topk_idx, int e_lo, int e_hi,
@@ -198,6 +209,12 @@ int fb_topk_logits(const float* logits, long long ldl, int rows, int vocab, int 
                    float* out_val, void* stream);
 int fb_copy_pages(void* pool, long long layer_stride, long long page_elems, const int* pairs,
                   int n_pairs, int n_pages, int layers, void* status, void* stream);
+// greedy-token feedback between decode steps that run back to back on the device: token_ids[r] = next_id[r]
+// (ids outside [0, vocab) become 0); with `advance` the row also moves to the next position and looks its KV
+// write slot up in the page list (block_table [num_seqs, max_blocks])
+int fb_decode_advance(const int* next_id, int* token_ids, int* positions, int* row_pos, long long* write_slot,
+                      const int* row_seq, const int* block_table, int max_blocks, int page_size, int num_seqs,
+                      int rows, int vocab, int advance, void* stream);
 
 // ---- quantisation / packing ---------------------------------------------------------------
 int fb_quant_fp8_rows(const void* x, long long ldx, void* q, long long ldq, void* scale, long long lds,

@@ -637,6 +637,21 @@ static int num_sms() {
 
 constexpr int kSmemLimit = 227 * 1024;
 
+static bool small_smem_enabled() {
+  static const bool on = [] {
+    const char* e = getenv("FERRULE_GEMM_SMALL_SMEM");
+    return !(e && e[0] == '0');
+  }();
+  return on;
+}
+static bool stage_small_enabled() {
+  static const bool on = [] {
+    const char* e = getenv("FERRULE_GEMM_STAGE_SMALL");
+    return !(e && e[0] == '0');
+  }();
+  return on;
+}
+
 // Split-K factor: spread a GEMM with few output tiles over more SMs.  The S CTAs of a cluster
 // each take 1/S of the k-blocks of one tile; only used when every tile gets its own cluster.
 static int pick_split(int tiles, int kblocks, bool grouped, int acc_cols, int stage_bytes, int extra_bytes) {
@@ -666,7 +681,7 @@ static int launch_cfg(const CUtensorMap& mw, const CUtensorMap& mx, GemmParams p
   }
   const int kblocks = (p.k + kBlockK - 1) / kBlockK;
   // large row tiles (prefill) write their bf16 output through a staging tile: see the epilogue
-  p.stage_store = (EPI != kEpiAllReduce && NTOK >= 64 && !p.out_fp32 && p.remap_rank == nullptr &&
+  p.stage_store = (EPI != kEpiAllReduce && (NTOK >= 64 || stage_small_enabled()) && !p.out_fp32 && p.remap_rank == nullptr &&
                    p.n_out % 8 == 0 && p.ldo % 8 == 0 && p.out_group_coff % 8 == 0 &&
                    (reinterpret_cast<uintptr_t>(p.out) & 15) == 0) ? 1 : 0;
   // staging areas behind the split-K reduction area: the all-reduce epilogue's [NTOK x 128] fp32 tile, or the
@@ -678,6 +693,13 @@ static int launch_cfg(const CUtensorMap& mw, const CUtensorMap& mx, GemmParams p
   const int red_bytes = (split > 1 ? (split - 1) * Cfg::kAccCols * 128 * 4 : 0) + extra_bytes;
   int stages = (kSmemLimit - 2048 - red_bytes) / Cfg::kStageBytes;
   if (stages > Cfg::kStages) stages = Cfg::kStages;
+  // A dense GEMM whose CTAs each own one tile needs no more stages than its k-blocks: the smaller footprint lets
+  // its CTAs become resident beside the preceding kernel's, so that their prologue and weight requests overlap
+  // that kernel's tail instead of waiting for its shared memory.
+  if (!grouped && max_tiles * split <= num_sms() && small_smem_enabled()) {
+    const int kb_per_cta = (kblocks + split - 1) / split;
+    if (stages > kb_per_cta) stages = kb_per_cta < 2 ? 2 : kb_per_cta;
+  }
   if (stages < 2 || (split > 1 && (max_tiles * split > num_sms() || kblocks < split))) return FB_ERR_SHAPE;
   p.stages = stages;
   const size_t smem = static_cast<size_t>(stages) * Cfg::kStageBytes + 1024 + 256 + red_bytes;

@@ -56,6 +56,9 @@ struct AttnParams {
   int sel_width;
   DeviceStatus* status;
   int kv_stream;            // decode-sized launch: KV rows are read once, load them with the L2 evict-first policy
+  int prefetch_old;         // one query row per sequence (plain decode step): every KV row below the row's own
+                            // position was written by an earlier step, so the first tile may be requested before
+                            // the dependency wait
   unsigned long long* trace;  // optional: CTA (0,0,0) writes globaltimer stamps of its milestones
 };
 
@@ -114,7 +117,6 @@ template <int DL, int DR>
 __global__ void __launch_bounds__(kAttnThreads)
 mla_attention_kernel(const AttnParams p) {
   pdl_launch_dependents();
-  pdl_wait();
   using S = AttnSmem<DL, DR>;
   constexpr int D = S::D;
   constexpr int kRowPad = S::kRowPad;
@@ -147,6 +149,32 @@ mla_attention_kernel(const AttnParams p) {
     *abort_flag = 0;
     fence_barrier_init();
   }
+  // ---- before the dependency wait: only memory that no kernel of the running step writes may be read - the
+  // batch description (row_seq / row_pos / block_table, written by the copy or kernel that precedes the whole
+  // step) and, in a plain decode step, the KV rows of earlier positions.  Their copies for the first tile are
+  // requested now, so they stream while the preceding kernel drains. ----
+  bool pre_issued = false;
+  if (p.prefetch_old) {
+    __syncthreads();                       // the barrier is initialised before anything arrives on it
+    const int seq0 = p.row_seq[qrow0];
+    const int pos0 = p.row_pos[qrow0];
+    if (seq0 >= 0 && seq0 < p.num_seqs && tid < kKvTile) {
+      const int tok = blockIdx.y * p.split_tokens + tid;
+      const int lim = min(min(pos0, p.max_blocks * p.page_size), (blockIdx.y + 1) * p.split_tokens);
+      if (tok < lim) {                     // strictly below the row's own position: written by an earlier step
+        const int page = p.block_table[static_cast<long long>(seq0) * p.max_blocks + tok / p.page_size];
+        const long long slot = static_cast<long long>(page) * p.page_size + tok % p.page_size;
+        if (page >= 0 && slot < p.pool_rows) {
+          __nv_bfloat16* dst = KVs + tid * kRowPad;
+          mbar_arrive_expect_tx(bar, D * 2);
+          if (p.kv_stream) bulk_copy_g2s_stream(dst, p.kv + slot * D, D * 2, bar, l2_policy_evict_first());
+          else bulk_copy_g2s(dst, p.kv + slot * D, D * 2, bar);
+          pre_issued = true;
+        }
+      }
+    }
+  }
+  pdl_wait();
 
   if (tracing) p.trace[12] = globaltimer_ns();
   // ---- query tile -> smem (rows beyond the valid set are zero).  The loads are issued first and parked in
@@ -214,8 +242,9 @@ mla_attention_kernel(const AttnParams p) {
   bool ok = true;
 
   for (int tile0 = kv_begin; tile0 < kv_end && ok; tile0 += kKvTile) {
-    // ---- load: threads 0..63 fetch one KV row each ----
-    if (tid < kKvTile) {
+    // ---- load: threads 0..63 fetch one KV row each (rows of the first tile requested before the dependency
+    // wait are on their way already) ----
+    if (tid < kKvTile && !(pre_issued && tile0 == kv_begin)) {
       const int tok = tile0 + tid;
       __nv_bfloat16* dst = KVs + tid * kRowPad;
       bool issued = false;
@@ -398,8 +427,9 @@ mla_attention_kernel(const AttnParams p) {
       float mv = -INFINITY, lv = 0.f;
       if (c < CS) {
         const uint32_t ra = mapa_shared(msm_addr, c);
-        mv = ld_cluster_f32(ra + r * 4);
-        lv = ld_cluster_f32(ra + (16 + r) * 4);
+        // both loads in flight together (the compiler may not reorder the volatile form)
+        asm("ld.shared::cluster.f32 %0, [%2];\n\tld.shared::cluster.f32 %1, [%3];"
+            : "=f"(mv), "=f"(lv) : "r"(ra + r * 4), "r"(ra + (16 + r) * 4));
       }
       float M = mv;
 #pragma unroll
@@ -427,10 +457,24 @@ mla_attention_kernel(const AttnParams p) {
       const int qr = qrow0 + r / Hb, h = hblock * Hb + r % Hb;
       if (r / Hb >= G || qr >= p.rows || h >= p.heads) continue;
       float acc[4] = {0.f, 0.f, 0.f, 0.f};
-      for (int c = 0; c < CS; ++c) {
-        const float w = wsm[r * 8 + c];
-        const float4 v = ld_cluster_f32x4(mapa_shared(osm_addr, c) + (r * DL + d) * 4);
-        acc[0] += v.x * w; acc[1] += v.y * w; acc[2] += v.z * w; acc[3] += v.w * w;
+      // the partials of all splits are requested together (one round trip through distributed shared memory
+      // instead of one per split), then added in split order
+      float4 v[8];
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        v[c] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (c < CS) {
+          const uint32_t a = mapa_shared(osm_addr, c) + (r * DL + d) * 4;
+          asm("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
+              : "=f"(v[c].x), "=f"(v[c].y), "=f"(v[c].z), "=f"(v[c].w) : "r"(a));
+        }
+      }
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        if (c < CS) {
+          const float w = wsm[r * 8 + c];
+          acc[0] += v[c].x * w; acc[1] += v[c].y * w; acc[2] += v[c].z * w; acc[3] += v[c].w * w;
+        }
       }
       __nv_bfloat16* o = p.out + qr * p.ldo + static_cast<long long>(h) * DL + d;
       *reinterpret_cast<uint32_t*>(o) = pack_bf16(acc[0], acc[1]);
@@ -671,6 +715,7 @@ extern "C" int fb_mla_attention(const FbAttnArgs* a, void* stream_) {
   p.sel_width = a->sel_width;
   p.status = static_cast<DeviceStatus*>(a->status);
   p.trace = static_cast<unsigned long long*>(a->trace);
+  p.prefetch_old = (a->decode_only && a->group_rows == 1 && a->selection == nullptr) ? 1 : 0;
   {
     static const bool enabled = [] {
       const char* e = getenv("FERRULE_W_EVICT_FIRST");

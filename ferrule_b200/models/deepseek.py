@@ -44,6 +44,7 @@ class DeviceBatch:
     logit_rows: torch.Tensor    # [n_logit] int32 rows whose logits are wanted
     n_rows: int
     n_logit: int
+    decode_only: bool = False   # every sequence has exactly one row (a plain decode step)
 
 
 class KvPool:
@@ -361,6 +362,8 @@ class CudaForward:
         dev = weights.embed.device
         self.device = dev
         cfg = self.cfg
+        import os
+        attn_splits = int(os.environ.get("FERRULE_ATTN_SPLITS", attn_splits))
         self.max_seq_len = max_seq_len
         self.split_tokens = max(64, ((max_seq_len + attn_splits - 1) // attn_splits + 63) // 64 * 64)
         self.ws = CudaWorkspace(weights, max_rows, max_logit_rows, decode_rows, attn_splits, dev)
@@ -381,6 +384,9 @@ class CudaForward:
         self.telemetry = None      # utils.telemetry.ExpertTelemetry fed by the streamed path
         self.static_moe = os.environ.get("FERRULE_STATIC_MOE", "1") != "0"
         self.fuse_next_norm = os.environ.get("FERRULE_FUSE_NORM", "1") != "0"
+        # measured: folding the post-attention add + RMSNorm into the router kernel loses 10 us per layer, because the
+        # shared-expert branch can then only fork after the router instead of running beside it; opt-in
+        self.fuse_router_norm = os.environ.get("FERRULE_FUSE_ROUTER_NORM", "0") == "1"
         # measured: prefetching the next layer's attention weights during the MoE phase costs 0.7 ms per step
         # (7.05 -> 7.78 ms): the branch delays the shared-expert join; opt-in only
         self.attn_prefetch = os.environ.get("FERRULE_ATTN_PREFETCH", "0") == "1"
@@ -445,7 +451,8 @@ class CudaForward:
                         self.pool.page_size, lora, rope, cfg.softmax_scale, ws.o_lat[:T],
                         splits=ws.attn_splits if use_split else 1,
                         split_tokens=self.split_tokens if use_split else (1 << 30) // 64 * 64,
-                        ws=ws.attn_ws if (use_split and not cluster) else None, sink=lw.attn_sink)
+                        ws=ws.attn_ws if (use_split and not cluster) else None, sink=lw.attn_sink,
+                        decode_only=b.decode_only)
         K.gemm(ws.o_lat[:T].view(T, -1), lw.w_uv, out=ws.attn_out[:T], x_group_koff=lora, out_group_coff=vd)
         return ws.attn_out[:T]
 
@@ -467,8 +474,10 @@ class CudaForward:
                 return nt
         return 0
 
-    def _moe_local(self, lw: LayerWeights, xn: torch.Tensor, b: DeviceBatch, T: int, layer: int = -1):
-        """Router + local routed experts + shared experts -> ws.route_out filled for this rank."""
+    def _moe_local(self, lw: LayerWeights, xn: torch.Tensor, b: DeviceBatch, T: int, layer: int = -1, norm=None):
+        """Router + local routed experts + shared experts -> ws.route_out filled for this rank.
+        `norm` = (residual rows, sublayer output or None, new residual rows or None): `xn` has not been computed
+        yet, the router kernel forms it (residual add + RMSNorm) in its prologue; static plan only."""
         K, cfg, ws = self.K, self.cfg, self.ws
         k, H = cfg.topk, cfg.hidden
         idx, wts = ws.topk_idx[:T], ws.topk_w[:T]
@@ -477,6 +486,15 @@ class CudaForward:
             ntok = min(ntok, 32)            # row-tile limit of the FP8 SwiGLU / group-scaled kernels
         plan = ws.plans[ntok]
         side = None
+        static = self._static_rows(lw, T, layer)
+        if norm is not None:
+            assert static, "the fused norm + router kernel serves the static plan only"
+            x_res, delta, res_out = norm
+            K.router_append(x_res, lw.router_w, k, cfg.score_fn, ws.static_plans[static][layer], self.w.e_lo,
+                            self.w.e_hi, idx, wts, ws.xg, bias=lw.router_bias, n_groups=cfg.n_groups,
+                            topk_groups=cfg.topk_groups, normalize=cfg.norm_topk_prob, route_scale=cfg.route_scale,
+                            hash_table=lw.hash_table, token_ids=b.token_ids, dst_slots=ws.slots,
+                            norm_w=lw.ffn_norm, eps=cfg.rms_eps, delta=delta, res_out=res_out, norm_out=xn)
         # FP8 shared experts read the quantised normed rows: quantise before the fork
         xq_n = self._quant(xn, "xn") if isinstance(lw.w13, QuantWeight) else None
         if lw.w13 is not None:
@@ -498,14 +516,14 @@ class CudaForward:
                     for wt in (nl.w_qkv_a, nl.w_uk_t, nl.w_uv, nl.w_o):
                         if isinstance(wt, torch.Tensor):
                             K.l2_prefetch(wt, wt.numel() * wt.element_size())
-        static = self._static_rows(lw, T, layer)
         if static:
             # no plan phase and no gather kernel: the router reserves rows in fixed per-expert slots
             plan = ws.static_plans[static][layer]
-            K.router_append(xn, lw.router_w, k, cfg.score_fn, plan, self.w.e_lo, self.w.e_hi, idx, wts, ws.xg,
-                            bias=lw.router_bias, n_groups=cfg.n_groups, topk_groups=cfg.topk_groups,
-                            normalize=cfg.norm_topk_prob, route_scale=cfg.route_scale, hash_table=lw.hash_table,
-                            token_ids=b.token_ids, dst_slots=ws.slots)
+            if norm is None:
+                K.router_append(xn, lw.router_w, k, cfg.score_fn, plan, self.w.e_lo, self.w.e_hi, idx, wts, ws.xg,
+                                bias=lw.router_bias, n_groups=cfg.n_groups, topk_groups=cfg.topk_groups,
+                                normalize=cfg.norm_topk_prob, route_scale=cfg.route_scale, hash_table=lw.hash_table,
+                                token_ids=b.token_ids, dst_slots=ws.slots)
             R = plan.cap_rows
             K.gemm(ws.xg[:R], lw.e_w13, out=ws.hmid[:R], epilogue=K.EPI_SWIGLU, plan=plan, act_limit=cfg.swiglu_limit)
             K.gemm(ws.hmid[:R], lw.e_w2, out=ws.route_out[:T].view(T * ws.slots, H), epilogue=K.EPI_SCATTER,
@@ -620,21 +638,30 @@ class CudaForward:
         if not first_norm_done:
             K.add_rmsnorm(h_in, lw.attn_norm, cfg.rms_eps, norm_out=xn)
         a = self._attention(lw, layer, xn, b, T)
+        # decode-sized MoE layers: the post-attention residual add + RMSNorm runs in the router kernel's prologue
+        route_norm = None
+        fuse_route = (self.fuse_router_norm and lw.is_moe and self._static_rows(lw, T, layer) > 0
+                      and not isinstance(lw.w13, QuantWeight))
         if tp is None:
             self._gemm(a, lw.w_o, ws.delta[:T], slot="a")
-            K.add_rmsnorm(h_in, lw.ffn_norm, cfg.rms_eps, delta=ws.delta[:T], res_out=h_out, norm_out=xn)
-            h_mid = h_out
-        elif isinstance(lw.w_o, QuantWeight):
-            self._gemm(a, lw.w_o, ws.delta[:T], slot="a")
-            tp.add_allreduce(ws.delta[:T], residual=h_in, out=h_out, T=T)
-            K.add_rmsnorm(h_out, lw.ffn_norm, cfg.rms_eps, norm_out=xn)
+            if fuse_route:
+                route_norm = (h_in, ws.delta[:T], h_out)
+            else:
+                K.add_rmsnorm(h_in, lw.ffn_norm, cfg.rms_eps, delta=ws.delta[:T], res_out=h_out, norm_out=xn)
             h_mid = h_out
         else:
-            tp.gemm_allreduce(a, lw.w_o, residual=h_in, out=h_out, T=T)
-            K.add_rmsnorm(h_out, lw.ffn_norm, cfg.rms_eps, norm_out=xn)
+            if isinstance(lw.w_o, QuantWeight):
+                self._gemm(a, lw.w_o, ws.delta[:T], slot="a")
+                tp.add_allreduce(ws.delta[:T], residual=h_in, out=h_out, T=T)
+            else:
+                tp.gemm_allreduce(a, lw.w_o, residual=h_in, out=h_out, T=T)
+            if fuse_route:
+                route_norm = (h_out, None, None)
+            else:
+                K.add_rmsnorm(h_out, lw.ffn_norm, cfg.rms_eps, norm_out=xn)
             h_mid = h_out
         if lw.is_moe:
-            idx = self._moe_local(lw, xn, b, T, layer)
+            idx = self._moe_local(lw, xn, b, T, layer, norm=route_norm)
             # slot `topk` holds the shared-expert row (zeros when the model has none)
             if tp is None and next_norm is not None:
                 K.moe_reduce_norm(ws.route_out[:T].view(T * ws.slots, cfg.hidden), ws.slots, cfg.topk, idx,
@@ -762,10 +789,12 @@ class DecodeGraph:
         dev = fwd.device
         i32 = dict(dtype=torch.int32, device=dev)
         self.fwd, self.rows = fwd, rows
+        if batch is not None:
+            batch.decode_only = True        # a decode graph carries one row per sequence
         self.batch = batch if batch is not None else DeviceBatch(torch.zeros(rows, **i32), torch.zeros(rows, **i32),
                                  torch.full((rows,), -1, dtype=torch.int64, device=dev),
                                  torch.zeros(rows, **i32), torch.full((rows,), -1, **i32),
-                                 torch.zeros(n_seqs, max_blocks, **i32), torch.arange(rows, **i32), rows, rows)
+                                 torch.zeros(n_seqs, max_blocks, **i32), torch.arange(rows, **i32), rows, rows, True)
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self.state = "cold"
         self.launches = 0

@@ -20,7 +20,8 @@ import torch
 
 from ..runtime.execution import (ExecutionBatch, ExecutionCapabilities, ExecutionOutput, Intent, KvLayoutSchema,
                                  KvPlaneDescriptor, LogitsKind, RowOutput)
-from ..runtime.runner import Complete, EndIntent, EndStatus, ModelRunner, Proposal, Waiting
+from ..runtime.runner import (Complete, EndIntent, EndStatus, ModelRunner, Proposal, Waiting,
+                              predict_next_decode_batch, same_decode_batch)
 from .config import ModelConfig
 from .deepseek import CudaForward, DecodeGraph, DeviceBatch, KvPool, ReferenceForward
 from .weights import ModelWeights
@@ -112,6 +113,8 @@ class RunnerStats:
     forward_ns: int = 0
     mtp_proposals: int = 0
     waits: int = 0
+    lookahead_launched: int = 0     # decode steps launched before the host had published their predecessor
+    lookahead_hits: int = 0         # ... that the engine then asked for unchanged
 
 
 class _MtpTrack:
@@ -127,7 +130,8 @@ class DeepSeekRunner(ModelRunner):
     def __init__(self, weights: ModelWeights, n_pages: int, page_size: int, max_rows: int = 2048,
                  max_seqs: int = 64, max_seq_len: int = 4096, device=None, tp=None, use_graphs: bool = True,
                  emulate_bf16: bool = False, attn_splits: int = 8, enable_mtp: bool = True, max_draft: int = 1,
-                 expert_residency: Optional[float] = None, async_streaming: bool = False):
+                 expert_residency: Optional[float] = None, async_streaming: bool = False,
+                 lookahead: bool = True):
         self.w, self.cfg = weights, weights.cfg
         self.device = torch.device(device if device is not None else weights.embed.device)
         self.is_cuda = self.device.type == "cuda"
@@ -171,6 +175,14 @@ class DeepSeekRunner(ModelRunner):
             self.fwd = ReferenceForward(weights, self.pool, emulate_bf16=emulate_bf16)
         self.graphs: Dict[int, tuple] = {}
         self.txns: Dict[int, ExecutionBatch] = {}
+        # decode look-ahead: while the host publishes step n, step n + 1 already runs on the device, fed by the
+        # greedy tokens that are still there.  The step is launched for the batch the engine is predicted to
+        # lower next; if the engine then asks for exactly that batch, only its result is read, otherwise the
+        # launched step is ignored (it wrote KV rows past every committed length, which nothing reads) and
+        # the requested batch runs as usual behind it on the same stream.
+        self.lookahead = bool(lookahead and self.use_graphs and not (enable_mtp and weights.mtp))
+        self._ahead = None                     # (predicted batch, rows, done event)
+        self._predict_next_decode = None
         # multi-token prediction: per state slot, the hidden rows whose MTP row is not written yet
         self.mtp_enabled = bool(enable_mtp and weights.mtp)
         self._mtp: Dict[int, _MtpTrack] = {}
@@ -403,7 +415,20 @@ class DeepSeekRunner(ModelRunner):
 
     def _execute_cuda(self, b: ExecutionBatch, start_layer: int = 0, h0=None) -> ExecutionOutput:
         fwd = self.fwd
-        if self.use_graphs and self._is_pure_decode(b) and b.rows <= self.max_seqs:
+        ahead, self._ahead = self._ahead, None
+        graph_step = self.use_graphs and self._is_pure_decode(b) and b.rows <= self.max_seqs
+        if graph_step and ahead is not None and same_decode_batch(ahead[0], b):
+            # this very step was launched while the host was still publishing its predecessor
+            st, graph = self._graph_for(b.rows)
+            lrows = b.logit_rows()
+            L = len(lrows)
+            ahead[2].synchronize()
+            self.stats.lookahead_hits += 1
+            self._last_hidden = graph.hidden
+            return self._read_greedy(b, lrows, L, None, b, launched=True)
+        if ahead is not None:
+            ahead[2].synchronize()      # mispredicted step: its input staging and result buffer are reused below
+        if graph_step:
             st, graph = self._graph_for(b.rows)
             T, R, lrows = st.fill(b)
             self.stats.h2d_bytes += st.upload()
@@ -425,16 +450,24 @@ class DeepSeekRunner(ModelRunner):
             self._last_hidden = fwd.last_hidden
             self.stats.eager_steps += 1
             self.stats.kernel_launches += fwd.launches
-        rows: List[RowOutput] = []
+        topk = None
         if L:
-            Lcap = fwd.ws.max_logit_rows
             self.out_host.copy_(fwd.ws.out_buf, non_blocking=True)
-            topk = None
             if want_topk:
                 kmax = max(b.logits[r].k for r in lrows)
                 ids, vals = fwd.K.topk_logits(fwd.ws.logits[:L], kmax)
                 topk = (ids.cpu(), vals.cpu())
-            torch.cuda.current_stream().synchronize()
+        torch.cuda.current_stream().synchronize()
+        return self._read_greedy(b, lrows, L, topk, b if graph_step else None)
+
+    def _read_greedy(self, b: ExecutionBatch, lrows, L: int, topk, decode_batch, launched: bool = False
+                     ) -> ExecutionOutput:
+        """Parse the greedy result that the step left in pinned host memory (its device->host copy has been
+        waited for).  `decode_batch`: the step was a graph decode step, so its successor may be launched now."""
+        fwd = self.fwd
+        rows: List[RowOutput] = []
+        if L:
+            Lcap = fwd.ws.max_logit_rows
             self.stats.d2h_bytes += 2 * Lcap * 4
             ids_h = self.out_host[:L].tolist()
             vals_h = self.out_host[Lcap:Lcap + L].view(torch.float32).tolist()
@@ -448,10 +481,36 @@ class DeepSeekRunner(ModelRunner):
                     rows.append(RowOutput(r, [], []))
                 else:
                     rows.append(RowOutput(r, [ids_h[i]], [vals_h[i]]))
-        else:
-            torch.cuda.current_stream().synchronize()
-        from ..ops import _lib
+            if decode_batch is not None and self.lookahead and L == b.rows:
+                self._launch_ahead(decode_batch, ids_h)
         return ExecutionOutput(rows)
+
+    def _launch_ahead(self, b: ExecutionBatch, ids_h: List[int]) -> None:
+        """Launch the decode step that follows `b` if the engine's next batch can be told now."""
+        predict = self._predict_next_decode
+        if predict is None:
+            return
+        nxt = predict({s.state_slot: ids_h[i] for i, s in enumerate(b.sequences)})
+        if not nxt:
+            return
+        pred = predict_next_decode_batch(b, ids_h, nxt)
+        if pred is None:
+            return
+        fwd = self.fwd
+        st, graph = self._graph_for(pred.rows)
+        st.fill(pred)
+        self.stats.h2d_bytes += st.upload()
+        # the ids just uploaded equal the ones on the device; taking them from there keeps the step independent
+        # of the host copy and is what lets it start before the host has looked at them
+        fwd.K.decode_advance(fwd.ws.next_id[:pred.rows], graph.batch, self.cfg.vocab_size, self.page_size, False)
+        graph.replay()
+        self.out_host.copy_(fwd.ws.out_buf, non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record()
+        self._ahead = (pred, pred.rows, ev)
+        self.stats.lookahead_launched += 1
+        self.stats.graph_steps += 1
+        self.stats.kernel_launches += graph.launches + 1
 
     def _execute_reference(self, b: ExecutionBatch, start_layer: int = 0, h0=None) -> ExecutionOutput:
         st = self.staging

@@ -67,6 +67,7 @@ class AttnArgs(C.Structure):
         ("group_rows", C.c_int), ("splits", C.c_int), ("split_tokens", C.c_int),
         ("softmax_scale", C.c_float), ("merge_ctr", C.c_void_p),
         ("selection", C.c_void_p), ("sel_width", C.c_int), ("trace", C.c_void_p),
+        ("decode_only", C.c_int),
     ]
 
 

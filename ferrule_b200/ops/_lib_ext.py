@@ -34,8 +34,11 @@ def declare(lib) -> None:
         "fb_argmax_chunked": ([vp, ll, i, i, i, vp, vp, vp, vp, vp, vp], i),
         "fb_router_append": ([vp, ll, vp, i, vp, vp, vp, i, i, i, i, i, i, i, f, vp, vp, i, i, i, i, vp, vp, vp, vp, vp, ll,
                               vp, vp], i),
+        "fb_norm_router_append": ([vp, ll, vp, ll, vp, vp, ll, vp, ll, f, vp, i, vp, vp, vp, i, i, i, i, i, i, i, f, vp, vp,
+                                   i, i, i, i, vp, vp, vp, vp, vp, ll, vp, vp], i),
         "fb_moe_reduce_norm": ([vp, i, i, vp, i, i, vp, ll, vp, ll, i, i, vp, vp, ll, f, vp], i),
         "fb_l2_prefetch": ([vp, ll, vp], i),
+        "fb_decode_advance": ([vp, vp, vp, vp, vp, vp, vp, i, i, i, i, i, i, vp], i),
         # quant.cu
         "fb_quant_fp8_rows": ([vp, ll, vp, ll, vp, ll, i, i, i, vp], i),
         "fb_dequant_fp8_block": ([vp, vp, vp, i, i, i, vp], i),

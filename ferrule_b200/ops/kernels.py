@@ -334,19 +334,39 @@ def router_append(x: torch.Tensor, w: torch.Tensor, topk: int, score_fn: int, pl
                   out_idx: torch.Tensor, out_w: torch.Tensor, xg: torch.Tensor, *,
                   bias: Optional[torch.Tensor] = None, n_groups: int = 1, topk_groups: int = 1,
                   normalize: bool = False, route_scale: float = 1.0, hash_table: Optional[torch.Tensor] = None,
-                  token_ids: Optional[torch.Tensor] = None, dst_slots: int = 0) -> None:
+                  token_ids: Optional[torch.Tensor] = None, dst_slots: int = 0,
+                  norm_w: Optional[torch.Tensor] = None, eps: float = 0.0, delta: Optional[torch.Tensor] = None,
+                  res_out: Optional[torch.Tensor] = None, norm_out: Optional[torch.Tensor] = None) -> None:
     """Router + top-k + row reservation in a static plan + activation gather, one launch (one CTA per token).
-    `plan.counts` must be zero on entry."""
+    `plan.counts` must be zero on entry.  With `norm_w` the kernel first forms the row itself: `x` is then the
+    residual stream, res_out = bf16(x + delta), norm_out = RMSNorm(res_out) * norm_w (bit-equal to `add_rmsnorm`),
+    and the router reads that normalised row."""
     lib = get_lib(True)
     rows, hidden = x.shape
     assert rows <= plan.ntok and xg.shape[0] >= plan.cap_rows and xg.shape[1] == hidden and w.is_contiguous()
     assert plan.max_tiles == e_hi - e_lo
-    check(lib.fb_router_append(x.data_ptr(), x.stride(0), w.data_ptr(), hidden, ptr(bias), ptr(hash_table),
-                               ptr(token_ids), rows, w.shape[0], topk, score_fn, n_groups, topk_groups,
-                               1 if normalize else 0, route_scale, out_idx.data_ptr(), out_w.data_ptr(), e_lo, e_hi,
-                               plan.ntok, dst_slots, plan.counts.data_ptr(), plan.src_token.data_ptr(),
-                               plan.dst_row.data_ptr(), plan.row_scale.data_ptr(), xg.data_ptr(), xg.stride(0),
-                               status_tensor(x.device).data_ptr(), stream_ptr()), "fb_router_append")
+    check(lib.fb_norm_router_append(x.data_ptr(), x.stride(0), ptr(delta), delta.stride(0) if delta is not None else 0,
+                                    ptr(norm_w), ptr(res_out), res_out.stride(0) if res_out is not None else 0,
+                                    ptr(norm_out), norm_out.stride(0) if norm_out is not None else 0, eps,
+                                    w.data_ptr(), hidden, ptr(bias), ptr(hash_table),
+                                    ptr(token_ids), rows, w.shape[0], topk, score_fn, n_groups, topk_groups,
+                                    1 if normalize else 0, route_scale, out_idx.data_ptr(), out_w.data_ptr(), e_lo, e_hi,
+                                    plan.ntok, dst_slots, plan.counts.data_ptr(), plan.src_token.data_ptr(),
+                                    plan.dst_row.data_ptr(), plan.row_scale.data_ptr(), xg.data_ptr(), xg.stride(0),
+                                    status_tensor(x.device).data_ptr(), stream_ptr()), "fb_norm_router_append")
+
+
+def decode_advance(next_id: torch.Tensor, batch, vocab: int, page_size: int, advance: bool) -> None:
+    """Feed a decode step's greedy tokens back as the next step's input ids on the device (`batch`: the
+    DeviceBatch of the step, one row per sequence).  `advance` also moves positions, visible lengths and KV
+    write slots one token on, using the page lists already in `batch.block_table`."""
+    lib = get_lib(True)
+    rows = batch.token_ids.shape[0]
+    check(lib.fb_decode_advance(next_id.data_ptr(), batch.token_ids.data_ptr(), batch.positions.data_ptr(),
+                                batch.row_pos.data_ptr(), batch.write_slot.data_ptr(), batch.row_seq.data_ptr(),
+                                batch.block_table.data_ptr(), batch.block_table.shape[1], page_size,
+                                batch.block_table.shape[0], rows, vocab, 1 if advance else 0, stream_ptr()),
+          "fb_decode_advance")
 
 
 def topk_logits(logits: torch.Tensor, k: int):
@@ -383,8 +403,10 @@ def mla_attention(q: torch.Tensor, kv_layer: torch.Tensor, block_table: torch.Te
                   rope_dim: int, scale: float, out: torch.Tensor, *, splits: int = 1,
                   split_tokens: int = 1 << 20, ws: Optional[AttnWorkspace] = None,
                   sink: Optional[torch.Tensor] = None, group_rows: int = 1,
-                  trace: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """q [rows, heads, D] bf16; kv_layer [..., D] bf16 (any leading shape, contiguous rows)."""
+                  trace: Optional[torch.Tensor] = None, decode_only: bool = False) -> torch.Tensor:
+    """q [rows, heads, D] bf16; kv_layer [..., D] bf16 (any leading shape, contiguous rows).
+    decode_only: one query row per sequence, and every KV row below its position predates the running step
+    (the kernel then requests its first KV tile before waiting for the preceding kernel)."""
     lib = get_lib(True)
     rows, heads, D = q.shape
     assert D == kv_lora + rope_dim and q.stride(2) == 1 and q.stride(1) == D
@@ -404,5 +426,6 @@ def mla_attention(q: torch.Tensor, kv_layer: torch.Tensor, block_table: torch.Te
     a.group_rows, a.splits, a.split_tokens = group_rows, splits, split_tokens
     a.softmax_scale = scale
     a.trace = ptr(trace)
+    a.decode_only = 1 if (decode_only and group_rows == 1) else 0
     check(lib.fb_mla_attention(C.byref(a), stream_ptr()), "fb_mla_attention")
     return out

@@ -149,6 +149,10 @@ class Engine:
         if self.cfg.speculative:
             from .speculation import SpeculativeDecoder
             self.spec = SpeculativeDecoder(self)
+        self._executing: Optional[Transaction] = None
+        hook = getattr(self.runner, "set_decode_predictor", None)
+        if hook is not None:
+            hook(self._predict_next_decode)
 
     # ------------------------------------------------------------------ public API
     def submit(self, req: GenerateRequest) -> SequenceState:
@@ -339,12 +343,44 @@ class Engine:
             if grant is not None:
                 self.broker.mark_submitted(grant)
             t0 = time.perf_counter_ns()
+            self._executing = txn
             progress = self.runner.execute(txn.txn_id)
             self.stats.runner_ns += time.perf_counter_ns() - t0
         except Exception as exc:  # noqa: BLE001 - every backend failure aborts the transaction
+            self._executing = None
             self._abort(txn, exc)
             return
+        self._executing = None
         self._on_progress(txn, progress)
+
+    def _predict_next_decode(self, tokens_by_slot: Dict[int, int]) -> Optional[List[int]]:
+        """Called by the runner from inside `execute` of a pure-decode transaction, with the token every
+        sequence just produced: the state slots of the next decode batch in order, if the next action is
+        certain to be a pure decode batch of exactly the sequences that continue.  Mirrors the commit and
+        finish rules of `_publish` / `_post_commit_finish` / `_apply_output` without changing anything."""
+        txn = self._executing
+        sch = self.scheduler
+        if (txn is None or self.spec is not None or self.registry is not None or self._shutdown
+                or self._ending or self._waiting or sch.waiting or sch.prefill or sch.pending_cancel
+                or sch.decode_ready or sch.suspended):
+            return None
+        ctx = self.cfg.scheduler.ctx_size
+        eos = self.runner.eos_token_id
+        out: List[int] = []
+        for m in txn.members:
+            seq = m.seq
+            req = seq.request
+            if m.is_prefill or seq.finish is not None or req.stop:
+                return None
+            tok = tokens_by_slot.get(seq.slot)
+            if tok is None or tok < 0:
+                return None
+            if seq.generated + 1 >= req.max_new_tokens or seq.position + 1 >= ctx:
+                continue
+            if tok == eos and not req.ignore_eos:
+                continue
+            out.append(seq.slot)
+        return out or None
 
     def _lower(self, txn: Transaction) -> ExecutionBatch:
         ps = self.cfg.page_size

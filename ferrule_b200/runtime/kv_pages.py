@@ -163,6 +163,10 @@ class KvPageManager:
     def free_pages(self) -> int:
         return len(self._free)
 
+    def free_page_ids(self) -> List[int]:
+        """The pages on the free list, in allocation order (nothing is taken)."""
+        return list(self._free)
+
     # ------------------------------------------------------------------ sequences
     def alloc_sequence(self) -> int:
         sid = self._next_seq

@@ -15,7 +15,7 @@ from enum import Enum
 from typing import Callable, Dict, Iterable, List, Optional, Sequence, Tuple
 
 from .execution import (ExecutionBatch, ExecutionCapabilities, ExecutionOutput, Intent, KvLayoutSchema,
-                        KvPlaneDescriptor, LogitsKind, RowOutput)
+                        KvPlaneDescriptor, LogitsKind, RowOutput, SequenceSlice)
 
 
 class EndIntent(Enum):
@@ -103,6 +103,47 @@ class ModelRunner:
     def shutdown(self) -> None:
         pass
 
+    # decode look-ahead
+    def set_decode_predictor(self, fn: Optional[Callable[[Dict[int, int]], Optional[List[int]]]]) -> None:
+        """The engine's answer to "which sequences decode next?": `fn({state slot: token just produced})`
+        returns the state slots of the next pure-decode batch in order, or None when the next action is
+        not (known to be) a pure decode batch.  A runner may use it to launch the next step on the device,
+        fed by the tokens still on the device, before the host has published the current one."""
+        self._predict_next_decode = fn
+
+
+def predict_next_decode_batch(b: ExecutionBatch, tokens: Sequence[int], next_slots: Sequence[int]
+                              ) -> Optional[ExecutionBatch]:
+    """The batch the engine will lower for the step after pure-decode batch `b`, given the tokens `b`
+    produced (row order) - or None when it cannot be told from `b` alone: a sequence ends, the order
+    changes, or a sequence's next position has no page yet (the engine must reserve one first)."""
+    seqs = b.sequences
+    if len(next_slots) != len(seqs) or any(s.state_slot != ns for s, ns in zip(seqs, next_slots)):
+        return None
+    ps = b.page_size
+    positions, slots, new_seqs = [], [], []
+    for s in seqs:
+        if s.query_len != 1:
+            return None
+        pos = b.positions[s.query_start] + 1
+        blk = pos // ps
+        if blk >= s.block_len:
+            return None
+        positions.append(pos)
+        slots.append(b.block_ids[s.block_start + blk] * ps + pos % ps)
+        new_seqs.append(SequenceSlice(s.state_slot, s.phase, s.query_start, 1, s.context_len + 1,
+                                      s.sequence_len + 1, s.block_start, s.block_len, ()))
+    return ExecutionBatch(list(tokens), positions, slots, list(b.logits), new_seqs, b.block_ids, b.intent, ps)
+
+
+def same_decode_batch(a: ExecutionBatch, b: ExecutionBatch) -> bool:
+    """True when two pure-decode batches make the device do exactly the same work."""
+    return (a.token_ids == b.token_ids and a.positions == b.positions and a.write_slots == b.write_slots
+            and a.block_ids == b.block_ids and a.intent == b.intent and len(a.sequences) == len(b.sequences)
+            and all(x.state_slot == y.state_slot and x.block_start == y.block_start and x.block_len == y.block_len
+                    and not x.cow and not y.cow for x, y in zip(a.sequences, b.sequences))
+            and all(x.kind == y.kind and x.k == y.k for x, y in zip(a.logits, b.logits)))
+
 
 class MockRunner(ModelRunner):
     """Deterministic CPU runner for state-machine tests.
@@ -130,6 +171,11 @@ class MockRunner(ModelRunner):
         self.draft_fn = draft_accuracy
         self._pending_left: Dict[int, int] = {}
         self.copied_pages: List[Tuple[int, int]] = []
+        # decode look-ahead bookkeeping: what the engine's predictor promised against what it then lowered
+        self._predict_next_decode = None
+        self.predicted: Optional[ExecutionBatch] = None
+        self.prediction_hits = 0
+        self.prediction_misses = 0
 
     def kv_schema(self) -> KvLayoutSchema:
         return KvLayoutSchema((KvPlaneDescriptor("latent_kv", 8, 1),), self.page_size, 1 << 20)
@@ -175,12 +221,26 @@ class MockRunner(ModelRunner):
 
     def execute(self, txn_id: int) -> Progress:
         self.calls.append(("execute", txn_id))
+        b = self.txns.get(txn_id)
+        if self.predicted is not None and b is not None:
+            if same_decode_batch(self.predicted, b):
+                self.prediction_hits += 1
+            else:
+                self.prediction_misses += 1
+            self.predicted = None
         if self.fail_next_execute > 0:
             self.fail_next_execute -= 1
             raise RuntimeError("mock runner: scripted execute failure")
         if self.wait_next:
             return Waiting(self.wait_next.pop(0), layer=0)
-        return self._run(txn_id)
+        out = self._run(txn_id)
+        if (self._predict_next_decode is not None and b.intent == Intent.COMMITTED and len(b.sequences) == b.rows
+                and all(r.token_ids for r in out.output.rows) and len(out.output.rows) == b.rows):
+            toks = [r.token_ids[0] for r in out.output.rows]
+            nxt = self._predict_next_decode({s.state_slot: toks[i] for i, s in enumerate(b.sequences)})
+            if nxt:
+                self.predicted = predict_next_decode_batch(b, toks, nxt)
+        return out
 
     def resume(self, txn_id: int) -> Progress:
         self.calls.append(("resume", txn_id))

@@ -248,3 +248,40 @@ def test_waiting_transaction_resumes_after_materialization():
     assert finish_of(ev, "x").reason == FinishReason.ERROR
     eng.kv.check_invariants()
     assert eng.kv.stats().used_pages == 0 and eng.broker.outstanding() == 0
+
+
+def test_decode_lookahead_prediction_is_never_wrong_and_mostly_available():
+    """The engine tells the runner which batch it will lower next; a runner that launches that batch early
+    must never be handed a different one without noticing, and in steady decode the prediction must exist."""
+    r = MockRunner(page_size=16, eos=999)
+    eng, _ = make(r, pages=256, max_batch_tokens=64, ctx=256)
+    # different lengths: sequences leave the cohort at different steps; one stops at EOS, one has a stop string
+    r.next_token_fn = lambda t, p: 999 if (t % 7 == 3 and p > 40) else (7 * t + 3 * p + 1) % 900
+    for i in range(6):
+        eng.submit(GenerateRequest(f"r{i}", [(i * 11 + j) % 800 + 1 for j in range(20 + i)],
+                                   max_new_tokens=20 + 5 * i, ignore_eos=(i % 2 == 0)))
+    ev = run(eng)
+    assert eng.stats.finished == 6
+    assert r.prediction_misses == 0
+    assert r.prediction_hits >= eng.stats.decode_steps // 2      # most decode steps were predicted
+    # page-boundary steps and steps after a sequence left are not predicted; nothing may be predicted wrongly
+    eng.kv.check_invariants()
+    assert eng.kv.stats().used_pages == 0
+
+
+def test_decode_lookahead_declines_when_the_next_action_is_not_a_pure_decode():
+    r = MockRunner(page_size=16)
+    eng, _ = make(r, pages=256, max_batch_tokens=64)
+    eng.submit(GenerateRequest("a", list(range(1, 30)), max_new_tokens=30))
+    ev = []
+    for _ in range(6):
+        eng.step(ev.append)
+    hits = r.prediction_hits
+    assert hits > 0
+    # an arrival cannot be foreseen: the step predicted before it is handed a different (mixed) batch, which the
+    # runner notices by comparing; while the newcomer prefills nothing is predicted
+    eng.submit(GenerateRequest("b", list(range(1, 40)), max_new_tokens=5))
+    eng.step(ev.append)
+    assert r.prediction_misses == 1 and r.predicted is None
+    eng.run_until_idle(ev.append)
+    assert r.prediction_misses == 1 and r.prediction_hits > hits

@@ -424,6 +424,52 @@ def test_router_append_static_plan(K, T, E, k, H, I):
     assert torch.equal(o1[local], o2[local])
 
 
+@pytest.mark.parametrize("T,E,k,H,with_delta", [(32, 64, 6, 2048, True), (7, 64, 6, 2048, False), (16, 256, 8, 7168, True)])
+def test_router_append_with_norm_prologue_is_bit_equal_to_norm_then_router(K, T, E, k, H, with_delta):
+    """Residual add + RMSNorm folded into the router kernel: same residual stream, same normalised rows, same
+    routes and weights, and the same gathered rows as add_rmsnorm followed by router_append."""
+    h = rnd(T, H)
+    delta = rnd(T, H, scale=0.3) if with_delta else None
+    nw = rnd(H)
+    w = rnd(E, H, scale=0.05)
+    e_lo, e_hi = 0, E
+    nt = 16 if T <= 16 else 32
+    outs = []
+    for fused in (False, True):
+        cnt = torch.zeros(E, dtype=torch.int32, device="cuda")
+        plan = K.static_plan(nt, E, cnt)
+        idx = torch.zeros(T, k, dtype=torch.int32, device="cuda")
+        wts = torch.zeros(T, k, device="cuda")
+        xg = torch.zeros(E * nt, H, dtype=torch.bfloat16, device="cuda")
+        res = torch.zeros(T, H, dtype=torch.bfloat16, device="cuda")
+        xn = torch.zeros(T, H, dtype=torch.bfloat16, device="cuda")
+        if fused:
+            K.router_append(h, w, k, 0, plan, e_lo, e_hi, idx, wts, xg, normalize=True, dst_slots=k + 1,
+                            norm_w=nw, eps=1e-6, delta=delta, res_out=res if with_delta else None, norm_out=xn)
+        else:
+            if with_delta:
+                K.add_rmsnorm(h, nw, 1e-6, delta=delta, res_out=res, norm_out=xn)
+            else:
+                K.add_rmsnorm(h, nw, 1e-6, norm_out=xn)
+            K.router_append(xn, w, k, 0, plan, e_lo, e_hi, idx, wts, xg, normalize=True, dst_slots=k + 1)
+        torch.cuda.synchronize()
+        # rows of one expert land in the order of the atomics: compare them keyed by their source token
+        rows = {}
+        c = cnt.cpu().tolist()
+        src = plan.src_token.cpu().tolist()
+        for e in range(E):
+            for j in range(c[e]):
+                r = e * nt + j
+                rows[(e, src[r])] = xg[r].cpu()
+        outs.append((idx.cpu(), wts.cpu(), xn.cpu(), res.cpu(), rows))
+    a, b = outs
+    assert torch.equal(a[0], b[0]) and torch.equal(a[1], b[1]) and torch.equal(a[2], b[2]) and torch.equal(a[3], b[3])
+    assert a[4].keys() == b[4].keys() and len(a[4]) == T * k
+    assert all(torch.equal(a[4][key], b[4][key]) for key in a[4])
+    from ferrule_b200.ops import _lib
+    assert _lib.read_status()[0] == 0
+
+
 @pytest.mark.parametrize("T,k,H", [(32, 6, 2048), (5, 8, 7168)])
 def test_moe_reduce_norm_is_bit_equal_to_reduce_then_norm(K, T, k, H):
     slots = k + 1

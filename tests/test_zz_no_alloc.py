@@ -53,7 +53,7 @@ def test_no_alloc_argmax_matches_existing_entry_point_twice():
         rc = fn(logits.data_ptr(), logits.stride(0), rows, vocab, ids.data_ptr(), vals.data_ptr(), stream)
         assert rc == 0
         torch.cuda.synchronize()
-        assert torch.cuda.memory_allocated() == before
+        assert torch.cuda.memory_allocated() <= before      # (frees deferred by earlier tests may land meanwhile)
         if call > 0:
             assert torch.cuda.mem_get_info()[0] >= free_before
         ref_ids, ref_vals = _reference(K, logits)
