@@ -27,6 +27,7 @@ LIB_PATH = OUT_DIR / "libferrule_b200.so"
 CUDA_SOURCES = [
     "gemm_tcgen05.cu",
     "gemm_fp8.cu",
+    "gemm_mxfp4.cu",
     "mla_attention.cu",
     "elementwise.cu",
     "quant.cu",

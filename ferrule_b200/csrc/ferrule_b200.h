@@ -226,6 +226,47 @@ int fb_quant_mxfp4_rows(const void* x, long long ldx, void* packed, void* scale,
 int fb_dequant_mxfp4(const void* packed, const void* scale, void* out, int rows, int n, void* stream);
 int fb_hadamard_rows(void* x, long long ldx, int rows, int n, void* stream);
 
+// ---- MXFP4 x MXFP8 block-scaled GEMM (routed experts) --------------------------------------------
+typedef struct FbGemmMxfp4Args {
+  const void* w;            // packed e2m1 [groups, w_rows_per_group, k / 2] (low nibble = even element), 32-byte aligned
+  const void* x;            // e4m3 [x_rows, k]
+  const void* w_sf;         // weight scales arranged by fb_mxfp4_prepare_sf
+  const void* x_scale;      // UE8M0 [x_rows, k / 32]
+  void* out;                // bf16 / fp32 [rows, n_out], or e4m3 codes with out_mode 2
+  void* out_scale;          // out_mode 2: UE8M0 [rows, n_out / 32]
+  long long ldw_bytes;      // bytes between weight rows (k / 2 when dense)
+  long long w_group_stride_bytes;
+  long long ldx;
+  long long ldxs;
+  long long ldo;
+  long long ldos;
+  int n_out;
+  int k;                    // multiple of 128
+  int groups;
+  int w_rows_per_group;
+  int x_rows;
+  int ntok;                 // 16, 32, 64 (128 without SwiGLU)
+  int epilogue;             // 0 store, 1 SwiGLU (w rows = [gate block | up block]), 2 weighted scatter
+  int dual_offset;
+  int out_mode;             // 0 bf16, 1 fp32, 2 MXFP8 (e4m3 + one UE8M0 scale per 32 channels; store / SwiGLU only)
+  int max_tok_tiles;
+  const int* tile_group;
+  const int* tile_row0;
+  const int* tile_rows;
+  const int* num_tok_tiles;
+  const int* dst_row;
+  const float* row_scale;
+  float act_limit;
+  void* status;
+} FbGemmMxfp4Args;
+int fb_gemm_mxfp4(const FbGemmMxfp4Args* args, void* stream);
+// linear UE8M0 weight scales [groups, rows, k / 32] -> [groups, ceil(rows / 128), k / 128, 512] blocks for the kernel
+// (rows beyond the weight are padded with 0x7f); out holds groups * ceil(rows / 128) * (k / 128) * 512 bytes
+int fb_mxfp4_prepare_sf(const void* scale, void* out, int groups, int rows, int k, void* stream);
+// bf16 [rows, n] -> e4m3 codes [rows, n] + UE8M0 scales [rows, n / 32] (1 x 32 blocks), n a multiple of 128
+int fb_quant_mxfp8_rows(const void* x, long long ldx, void* q, long long ldq, void* scale, long long lds, int rows,
+                        int n, void* stream);
+
 // ---- DeepSeek-V4 operators ---------------------------------------------------------------
 // hyper-connections: state bf16 [tokens, hc, hidden], fn fp32 [nmix, hc * hidden]; coeff fp32 [tokens, nmix]
 // = [pre | post | comb]; nmix = hc (head reduction) or 2 hc + hc^2; hc in {2, 4}

@@ -132,3 +132,116 @@ def mxfp4_to_e4m3_containers(packed: torch.Tensor) -> torch.Tensor:
     for the group-scaled FP8 GEMM)."""
     from ..io import encoding as enc
     return enc.e4m3_encode(enc.fp4_unpack(packed))
+
+
+# ---------------------------------------------------------------------------------------------------
+# native MXFP4 x MXFP8 path (csrc/gemm_mxfp4.cu)
+# ---------------------------------------------------------------------------------------------------
+class GemmMxfp4Args(C.Structure):
+    _fields_ = [
+        ("w", C.c_void_p), ("x", C.c_void_p), ("w_sf", C.c_void_p), ("x_scale", C.c_void_p), ("out", C.c_void_p),
+        ("out_scale", C.c_void_p),
+        ("ldw_bytes", C.c_longlong), ("w_group_stride_bytes", C.c_longlong), ("ldx", C.c_longlong),
+        ("ldxs", C.c_longlong), ("ldo", C.c_longlong), ("ldos", C.c_longlong),
+        ("n_out", C.c_int), ("k", C.c_int), ("groups", C.c_int), ("w_rows_per_group", C.c_int), ("x_rows", C.c_int),
+        ("ntok", C.c_int), ("epilogue", C.c_int), ("dual_offset", C.c_int), ("out_mode", C.c_int),
+        ("max_tok_tiles", C.c_int),
+        ("tile_group", C.c_void_p), ("tile_row0", C.c_void_p), ("tile_rows", C.c_void_p), ("num_tok_tiles", C.c_void_p),
+        ("dst_row", C.c_void_p), ("row_scale", C.c_void_p), ("act_limit", C.c_float), ("status", C.c_void_p),
+    ]
+
+
+def _mx_lib():
+    lib = get_lib(True)
+    if not hasattr(lib.fb_gemm_mxfp4, "_declared"):
+        vp, i, ll = C.c_void_p, C.c_int, C.c_longlong
+        lib.fb_gemm_mxfp4.argtypes = [C.POINTER(GemmMxfp4Args), vp]
+        lib.fb_gemm_mxfp4.restype = i
+        lib.fb_mxfp4_prepare_sf.argtypes = [vp, vp, i, i, i, vp]
+        lib.fb_mxfp4_prepare_sf.restype = i
+        lib.fb_quant_mxfp8_rows.argtypes = [vp, ll, vp, ll, vp, ll, i, i, vp]
+        lib.fb_quant_mxfp8_rows.restype = i
+        lib.fb_gemm_mxfp4._declared = True
+    return lib
+
+
+def quant_mxfp8_rows(x: torch.Tensor, out: Optional[Tuple[torch.Tensor, torch.Tensor]] = None
+                     ) -> Tuple[torch.Tensor, torch.Tensor]:
+    """bf16 [rows, n] -> (uint8 e4m3 codes [rows, n], uint8 UE8M0 scales [rows, n/32]): MXFP8, 1 x 32 blocks."""
+    lib = _mx_lib()
+    rows, n = x.shape
+    assert n % 128 == 0 and x.stride(1) == 1
+    if out is None:
+        q = torch.empty(rows, n, dtype=torch.uint8, device=x.device)
+        s = torch.empty(rows, n // 32, dtype=torch.uint8, device=x.device)
+    else:
+        q, s = out
+        assert q.shape == (rows, n) and s.shape == (rows, n // 32) and q.stride(1) == 1 and s.stride(1) == 1
+    check(lib.fb_quant_mxfp8_rows(x.data_ptr(), x.stride(0), q.data_ptr(), q.stride(0), s.data_ptr(), s.stride(0),
+                                  rows, n, stream_ptr()), "fb_quant_mxfp8_rows")
+    return q, s
+
+
+def mxfp4_prepare_sf(scale: torch.Tensor) -> torch.Tensor:
+    """Weight scales UE8M0 [groups, rows, k/32] (or [rows, k/32]) -> the block layout the MXFP4 GEMM copies to
+    TMEM: [groups, ceil(rows/128), k/128, 512] bytes."""
+    lib = _mx_lib()
+    if scale.dim() == 2:
+        scale = scale.unsqueeze(0)
+    scale = scale.contiguous()
+    G, rows, kb32 = scale.shape
+    k = kb32 * 32
+    assert k % 128 == 0
+    out = torch.empty(G, (rows + 127) // 128, k // 128, 512, dtype=torch.uint8, device=scale.device)
+    check(lib.fb_mxfp4_prepare_sf(scale.data_ptr(), out.data_ptr(), G, rows, k, stream_ptr()), "fb_mxfp4_prepare_sf")
+    return out
+
+
+def gemm_mxfp4(xq: torch.Tensor, xs: torch.Tensor, w_packed: torch.Tensor, w_sf: torch.Tensor,
+               out: Optional[torch.Tensor] = None, *, out_dtype=torch.bfloat16, epilogue: int = 0, plan=None,
+               scatter_rows: Optional[int] = None, act_limit: float = 0.0, ntok: Optional[int] = None,
+               out_mx: Optional[Tuple[torch.Tensor, torch.Tensor]] = None) -> torch.Tensor:
+    """MXFP4 weights x MXFP8 activations on `tcgen05.mma kind::mxf8f6f4.block_scale`.
+
+    xq uint8 e4m3 [rows, K] + xs UE8M0 [rows, K/32]; w_packed uint8 [groups, N, K/2] (two e2m1 per byte, low
+    nibble first) + w_sf from `mxfp4_prepare_sf`.  epilogue 0 store, 1 SwiGLU (rows = [gate | up]), 2 scatter
+    (plan).  `out_mx` = (codes [rows, n_out] uint8, scales [rows, n_out/32] uint8): the result is re-quantised
+    to MXFP8 in the epilogue instead of being stored as bf16."""
+    lib = _mx_lib()
+    if w_packed.dim() == 2:
+        w_packed = w_packed.unsqueeze(0)
+    groups, w_rows, half = w_packed.shape
+    K = half * 2
+    rows = xq.shape[0]
+    dual = epilogue == 1
+    n_out = w_rows // 2 if dual else w_rows
+    if ntok is None:
+        ntok = plan.ntok if plan is not None else (16 if rows <= 16 else (32 if rows <= 32 else 64))
+    a = GemmMxfp4Args()
+    if out_mx is not None:
+        oq, osc = out_mx
+        assert oq.dtype == torch.uint8 and osc.dtype == torch.uint8 and oq.shape[1] == n_out
+        a.out, a.out_scale, a.ldo, a.ldos, a.out_mode = oq.data_ptr(), osc.data_ptr(), oq.stride(0), osc.stride(0), 2
+        out = oq
+    else:
+        if out is None:
+            orow = scatter_rows if (epilogue == 2 and scatter_rows) else rows
+            out = torch.empty(orow, n_out, dtype=out_dtype, device=xq.device)
+        a.out, a.ldo = out.data_ptr(), out.stride(0)
+        a.out_mode = 1 if out.dtype == torch.float32 else 0
+    a.w, a.x, a.w_sf, a.x_scale = w_packed.data_ptr(), xq.data_ptr(), w_sf.data_ptr(), xs.data_ptr()
+    a.ldw_bytes, a.w_group_stride_bytes = w_packed.stride(1), w_packed.stride(0)
+    a.ldx, a.ldxs = xq.stride(0), xs.stride(0)
+    a.n_out, a.k, a.groups, a.w_rows_per_group, a.x_rows = n_out, K, groups, w_rows, rows
+    a.ntok, a.epilogue, a.dual_offset = ntok, epilogue, (w_rows // 2 if dual else 0)
+    a.act_limit = act_limit
+    if plan is not None:
+        a.max_tok_tiles = plan.max_tiles
+        a.tile_group, a.tile_row0, a.tile_rows = plan.tile_group.data_ptr(), plan.tile_row0.data_ptr(), plan.tile_rows.data_ptr()
+        a.num_tok_tiles = plan.meta.data_ptr()
+        if epilogue == 2:
+            a.dst_row, a.row_scale = plan.dst_row.data_ptr(), plan.row_scale.data_ptr()
+    a.status = status_tensor(xq.device).data_ptr()
+    check(lib.fb_gemm_mxfp4(C.byref(a), stream_ptr()), "fb_gemm_mxfp4")
+    return out
+

@@ -128,3 +128,128 @@ def test_gemm_mxfp4_weights_group_scaled(rows, n, k, dual):
     y = xd @ wd.T
     r = ref.swiglu(y[:, :n], y[:, n:]) if dual else y
     assert float((out.cpu() - r).abs().max()) <= 3e-3 * float(r.abs().max()) + 1e-4
+
+
+def _mx_dequant_rows(q: torch.Tensor, s: torch.Tensor) -> torch.Tensor:
+    v = enc.e4m3_decode(q.cpu())
+    sc = enc.e8m0_decode(s.cpu())
+    return (v.view(v.shape[0], -1, 32) * sc.unsqueeze(-1)).view(v.shape)
+
+
+def test_mxfp8_row_quant_matches_host_codec():
+    from ferrule_b200.ops import quant as Q
+    x = rnd(37, 512, scale=3.0, seed=71)
+    x[3] = 0
+    q, s = Q.quant_mxfp8_rows(x)
+    xf = x.float().cpu()
+    amax = xf.view(37, -1, 32).abs().amax(-1).clamp_min(1e-4)
+    sb = enc.e8m0_encode_ceil(amax / 448.0)
+    assert torch.equal(s.cpu(), sb)
+    qref = enc.e4m3_encode((xf.view(37, -1, 32) / enc.e8m0_decode(sb).unsqueeze(-1)).view(37, -1))
+    assert torch.equal(q.cpu(), qref)
+
+
+def test_mxfp4_scale_blocks_layout():
+    from ferrule_b200.ops import quant as Q
+    G, rows, k = 2, 200, 512
+    sc = torch.randint(100, 140, (G, rows, k // 32), dtype=torch.uint8, device="cuda")
+    prep = Q.mxfp4_prepare_sf(sc).cpu()
+    assert prep.shape == (G, 2, k // 128, 512)
+    s = sc.cpu()
+    for g, rt, kb, r, gg, kk in [(0, 0, 0, 0, 0, 0), (1, 0, 3, 31, 3, 2), (0, 1, 1, 5, 1, 3), (1, 1, 2, 7, 2, 0)]:
+        row = rt * 128 + gg * 32 + r
+        want = int(s[g, row, kb * 4 + kk]) if row < rows else 0x7f
+        assert int(prep[g, rt, kb, r * 16 + gg * 4 + kk]) == want
+
+
+@pytest.mark.parametrize("rows,n,k,dual", [(32, 256, 512, False), (7, 128, 128, False), (16, 256, 1024, True),
+                                           (64, 384, 2048, False), (128, 256, 512, False), (32, 2048, 7168, True),
+                                           (50, 1408, 2048, False)])
+def test_gemm_mxfp4_native_block_scaled(rows, n, k, dual):
+    """Packed e2m1 weights + UE8M0/32 scales against MXFP8 activations on the block-scaled tensor-core path,
+    compared with the fp32 product of the dequantised operands."""
+    from ferrule_b200.ops import _lib
+    from ferrule_b200.ops import quant as Q
+    from ferrule_b200.ops import reference as ref
+    x = rnd(rows, k, scale=1.5, seed=41)
+    xq, xs = Q.quant_mxfp8_rows(x)
+    w = torch.randn(n * (2 if dual else 1), k, generator=torch.Generator().manual_seed(42)) * 0.05
+    parts = [enc.weight_quant_mxfp4(w[r:r + 512]) for r in range(0, w.shape[0], 512)]
+    packed, sb = torch.cat([a for a, _ in parts]), torch.cat([b for _, b in parts])
+    sf = Q.mxfp4_prepare_sf(sb.cuda())
+    out = Q.gemm_mxfp4(xq, xs, packed.cuda(), sf, epilogue=1 if dual else 0, out_dtype=torch.float32)
+    torch.cuda.synchronize()
+    assert _lib.read_status()[0] == 0
+    xd = _mx_dequant_rows(xq, xs)
+    wd = enc.weight_dequant_mxfp4(packed, sb).float()
+    y = xd @ wd.T
+    r = ref.swiglu(y[:, :n], y[:, n:]) if dual else y
+    err = float((out.cpu() - r).abs().max())
+    assert err <= 2e-3 * float(r.abs().max()) + 1e-4, err
+
+
+def test_gemm_mxfp4_grouped_pipeline_with_requantised_hidden():
+    """gate|up (SwiGLU, epilogue re-quantises to MXFP8) -> down (weighted scatter) over a static expert plan with
+    empty experts, against the same chain on dequantised operands."""
+    from ferrule_b200.ops import _lib
+    from ferrule_b200.ops import kernels as K
+    from ferrule_b200.ops import quant as Q
+    from ferrule_b200.ops import reference as ref
+    T, E, topk, H, I, nt = 24, 8, 2, 512, 256, 32
+    g = torch.Generator(device="cuda").manual_seed(5)
+    logits = torch.randn(T, E, generator=g, device="cuda")
+    logits[:, 3] = -1e9                                     # expert 3 receives nothing
+    idx, wts = ref.route(logits, topk, 0)
+    cnt = torch.zeros(E, dtype=torch.int32, device="cuda")
+    plan = K.static_plan(nt, E, cnt)
+    x = rnd(T, H, seed=31)
+    # place the rows by hand in the static layout (expert e owns rows e * nt ...)
+    xg = torch.zeros(E * nt, H, dtype=torch.bfloat16, device="cuda")
+    src, dst, scl = plan.src_token.cpu(), plan.dst_row.cpu(), plan.row_scale.cpu()
+    counts = [0] * E
+    for t in range(T):
+        for s_ in range(topk):
+            e = int(idx[t, s_])
+            r = e * nt + counts[e]
+            counts[e] += 1
+            xg[r] = x[t]
+            src[r], dst[r], scl[r] = t, t * topk + s_, float(wts[t, s_])
+    plan.src_token.copy_(src)
+    plan.dst_row.copy_(dst)
+    plan.row_scale.copy_(scl)
+    cnt.copy_(torch.tensor(counts, dtype=torch.int32))
+    gen = torch.Generator().manual_seed(9)
+    w13 = torch.randn(E, 2 * I, H, generator=gen) * 0.05
+    w2 = torch.randn(E, H, I, generator=gen) * 0.05
+    p13 = [enc.weight_quant_mxfp4(w13[e]) for e in range(E)]
+    p2 = [enc.weight_quant_mxfp4(w2[e]) for e in range(E)]
+    w13p, w13s = torch.stack([a for a, _ in p13]).cuda(), Q.mxfp4_prepare_sf(torch.stack([b for _, b in p13]).cuda())
+    w2p, w2s = torch.stack([a for a, _ in p2]).cuda(), Q.mxfp4_prepare_sf(torch.stack([b for _, b in p2]).cuda())
+    xgq, xgs = Q.quant_mxfp8_rows(xg)
+    hq = torch.zeros(E * nt, I, dtype=torch.uint8, device="cuda")
+    hs = torch.zeros(E * nt, I // 32, dtype=torch.uint8, device="cuda")
+    Q.gemm_mxfp4(xgq, xgs, w13p, w13s, epilogue=1, plan=plan, out_mx=(hq, hs))
+    out = torch.zeros(T * topk, H, dtype=torch.float32, device="cuda")
+    Q.gemm_mxfp4(hq, hs, w2p, w2s, out=out, epilogue=2, plan=plan, scatter_rows=T * topk)
+    torch.cuda.synchronize()
+    assert _lib.read_status()[0] == 0
+    xd = _mx_dequant_rows(xgq, xgs)
+    exp = torch.zeros(T * topk, H)
+    for e in range(E):
+        if counts[e] == 0:
+            continue
+        rows = slice(e * nt, e * nt + counts[e])
+        w13d = enc.weight_dequant_mxfp4(*p13[e]).float()
+        w2d = enc.weight_dequant_mxfp4(*p2[e]).float()
+        y = xd[rows] @ w13d.T
+        h = enc.bf16_round(ref.swiglu(y[:, :I], y[:, I:]))
+        amax = h.view(h.shape[0], -1, 32).abs().amax(-1).clamp_min(1e-4)
+        sb = enc.e8m0_decode(enc.e8m0_encode_ceil(amax / 448.0)).unsqueeze(-1)
+        hd = (enc.e4m3_decode(enc.e4m3_encode((h.view(h.shape[0], -1, 32) / sb).view(h.shape))).view(h.shape[0], -1, 32) * sb).view(h.shape)
+        o = hd @ w2d.T
+        for j in range(counts[e]):
+            r = e * nt + j
+            exp[int(dst[r])] = o[j] * float(scl[r])
+    err = float((out.cpu() - exp).abs().max())
+    assert err <= 4e-3 * float(exp.abs().max()) + 1e-4, err
+
