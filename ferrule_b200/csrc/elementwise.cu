@@ -665,6 +665,19 @@ struct NormPrologue {
   float eps;
 };
 
+// Optional: the rows gathered for the experts are quantised rows (codes + scale bytes) instead of bf16 rows.
+struct QuantRows {
+  const uint8_t* q_src;     // [rows, hidden] codes of the (already quantised) normalised rows; null: copy bf16 rows
+  long long ldq;
+  const uint8_t* s_src;     // [rows, s_cols] scale bytes
+  long long lds;
+  uint8_t* xg_q;            // expert-major destination of the codes
+  long long ldxgq;
+  uint8_t* xg_s;            // expert-major destination of the scales
+  long long ldxgs;
+  int s_cols;
+};
+
 __global__ void __launch_bounds__(1024)
 router_append_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, const __nv_bfloat16* __restrict__ w,
                      int hidden, const float* __restrict__ bias, const long long* __restrict__ hash_table,
@@ -673,7 +686,7 @@ router_append_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, const _
                      float* __restrict__ out_w, int e_lo, int e_hi, int slot_rows, int dst_slots,
                      int* __restrict__ cnt, int* __restrict__ src_token, int* __restrict__ dst_row,
                      float* __restrict__ row_scale, __nv_bfloat16* __restrict__ xg, long long ldxg, DeviceStatus* st,
-                     NormPrologue np) {
+                     NormPrologue np, QuantRows qr) {
   pdl_launch_dependents();
   pdl_wait();
   extern __shared__ float xs[];            // hidden floats, then `experts` logits, then (norm prologue) hidden bf16
@@ -795,6 +808,23 @@ router_append_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, const _
     }
   }
   __syncthreads();
+  if (qr.q_src != nullptr) {
+    // quantised activations: copy the token's codes (16 bytes per thread) and scale bytes into every reserved row
+    const int vq = hidden / 16;
+    for (int i = threadIdx.x; i < topk * vq; i += blockDim.x) {
+      const int s = i / vq, c = i - s * vq;
+      const int r = rlist[s];
+      if (r >= 0)
+        *reinterpret_cast<uint4*>(qr.xg_q + r * qr.ldxgq + c * 16) =
+            *reinterpret_cast<const uint4*>(qr.q_src + t * qr.ldq + c * 16);
+    }
+    for (int i = threadIdx.x; i < topk * qr.s_cols; i += blockDim.x) {
+      const int s = i / qr.s_cols, c = i - s * qr.s_cols;
+      const int r = rlist[s];
+      if (r >= 0) qr.xg_s[r * qr.ldxgs + c] = qr.s_src[t * qr.lds + c];
+    }
+    return;
+  }
   // copy the token's activation row into every reserved row (16 bytes per thread)
   const int vec = hidden / 8;
   for (int i = threadIdx.x; i < topk * vec; i += blockDim.x) {
@@ -1264,9 +1294,31 @@ extern "C" int fb_norm_router_append(const void* x, long long ldx, const void* d
                                      float route_scale, int* out_idx, float* out_w, int e_lo, int e_hi,
                                      int slot_rows, int dst_slots, int* cnt, int* src_token, int* dst_row,
                                      float* row_scale, void* xg, long long ldxg, void* status, void* stream) {
+  return fb_router_append_q(x, ldx, delta, ldd, norm_w, res_out, ldr, norm_out, ldn, eps, w, hidden, bias, hash_table,
+                            token_ids, rows, experts, topk, score_fn, n_groups, topk_groups, normalize, route_scale,
+                            out_idx, out_w, e_lo, e_hi, slot_rows, dst_slots, cnt, src_token, dst_row, row_scale, xg, ldxg,
+                            nullptr, 0, nullptr, 0, nullptr, 0, nullptr, 0, 0, status, stream);
+}
+
+extern "C" int fb_router_append_q(const void* x, long long ldx, const void* delta, long long ldd,
+                                  const void* norm_w, void* res_out, long long ldr, void* norm_out, long long ldn,
+                                  float eps, const void* w, int hidden, const float* bias,
+                                  const long long* hash_table, const int* token_ids, int rows, int experts,
+                                  int topk, int score_fn, int n_groups, int topk_groups, int normalize,
+                                  float route_scale, int* out_idx, float* out_w, int e_lo, int e_hi,
+                                  int slot_rows, int dst_slots, int* cnt, int* src_token, int* dst_row,
+                                  float* row_scale, void* xg, long long ldxg, const void* q_src, long long ldq,
+                                  const void* s_src, long long lds, void* xg_q, long long ldxgq, void* xg_s,
+                                  long long ldxgs, int s_cols, void* status, void* stream) {
   if (rows <= 0 || experts <= 0 || experts > 256 || topk <= 0 || topk > 32 || topk > experts) return FB_ERR_SHAPE;
   if (hidden % 256 != 0 || hidden > 8192 || (ldx % 8) != 0 || (ldxg % 8) != 0) return FB_ERR_SHAPE;
-  if (slot_rows < rows || e_hi <= e_lo || !cnt || !src_token || !dst_row || !row_scale || !xg) return FB_ERR_SHAPE;
+  if (slot_rows < rows || e_hi <= e_lo || !cnt || !src_token || !dst_row || !row_scale) return FB_ERR_SHAPE;
+  if (q_src == nullptr && !xg) return FB_ERR_SHAPE;
+  if (q_src != nullptr && (!s_src || !xg_q || !xg_s || s_cols <= 0 || (ldq % 16) != 0 || (ldxgq % 16) != 0 ||
+                           (reinterpret_cast<uintptr_t>(q_src) & 15) || (reinterpret_cast<uintptr_t>(xg_q) & 15)))
+    return FB_ERR_SHAPE;
+  const QuantRows qr{static_cast<const uint8_t*>(q_src), ldq, static_cast<const uint8_t*>(s_src), lds,
+                     static_cast<uint8_t*>(xg_q), ldxgq, static_cast<uint8_t*>(xg_s), ldxgs, s_cols};
   if (norm_w != nullptr && ((ldd % 8) != 0 || (ldr % 8) != 0 || (ldn % 8) != 0 || (experts % 4) != 0))
     return FB_ERR_SHAPE;
   const NormPrologue np{static_cast<const __nv_bfloat16*>(delta), ldd, static_cast<const __nv_bfloat16*>(norm_w),
@@ -1282,7 +1334,7 @@ extern "C" int fb_norm_router_append(const void* x, long long ldx, const void* d
              static_cast<const __nv_bfloat16*>(x), ldx, static_cast<const __nv_bfloat16*>(w), hidden, bias, hash_table,
              token_ids, rows, experts, topk, score_fn, n_groups, topk_groups, normalize, route_scale, out_idx, out_w,
              e_lo, e_hi, slot_rows, dst_slots, cnt, src_token, dst_row, row_scale, static_cast<__nv_bfloat16*>(xg), ldxg,
-             static_cast<DeviceStatus*>(status), np);
+             static_cast<DeviceStatus*>(status), np, qr);
   return FB_CHECK_LAUNCH();
 }
 

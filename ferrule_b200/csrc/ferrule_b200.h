@@ -216,6 +216,17 @@ int fb_decode_advance(const int* next_id, int* token_ids, int* positions, int* r
                       const int* row_seq, const int* block_table, int max_blocks, int page_size, int num_seqs,
                       int rows, int vocab, int advance, void* stream);
 
+// fb_norm_router_append that gathers quantised rows: with q_src set, every route's reserved row receives the token's
+// codes (q_src [rows, hidden] -> xg_q) and scale bytes (s_src [rows, s_cols] -> xg_s) instead of a bf16 row
+int fb_router_append_q(const void* x, long long ldx, const void* delta, long long ldd, const void* norm_w,
+                       void* res_out, long long ldr, void* norm_out, long long ldn, float eps, const void* w,
+                       int hidden, const float* bias, const long long* hash_table, const int* token_ids, int rows,
+                       int experts, int topk, int score_fn, int n_groups, int topk_groups, int normalize,
+                       float route_scale, int* out_idx, float* out_w, int e_lo, int e_hi, int slot_rows,
+                       int dst_slots, int* cnt, int* src_token, int* dst_row, float* row_scale, void* xg,
+                       long long ldxg, const void* q_src, long long ldq, const void* s_src, long long lds, void* xg_q,
+                       long long ldxgq, void* xg_s, long long ldxgs, int s_cols, void* status, void* stream);
+
 // ---- quantisation / packing ---------------------------------------------------------------
 int fb_quant_fp8_rows(const void* x, long long ldx, void* q, long long ldq, void* scale, long long lds,
                       int rows, int n, int writeback_bf16, void* stream);

@@ -105,8 +105,10 @@ class ReferenceForward:
         if getattr(weights, "act_quant", False):
             from ..io import encoding as enc
             self.aq = lambda x: enc.act_dequant_fp8(*enc.act_quant_fp8(x))
+            eb = getattr(weights, "expert_act_block", 128)
+            self.aq_e = lambda x: enc.act_dequant_fp8(*enc.act_quant_fp8(x, eb), eb)
         else:
-            self.aq = lambda x: x
+            self.aq = self.aq_e = lambda x: x
 
     # -- pieces ------------------------------------------------------------------------
     def _attention(self, lw: LayerWeights, layer: int, xn: torch.Tensor, b: DeviceBatch) -> torch.Tensor:
@@ -164,9 +166,9 @@ class ReferenceForward:
             if rows.numel() == 0:
                 continue
             wsel = (wts * hit)[rows].sum(-1, keepdim=True)
-            y = self.aq(xn[rows]) @ lw.e_w13[e - self.w.e_lo].float().T
+            y = self.aq_e(xn[rows]) @ lw.e_w13[e - self.w.e_lo].float().T
             h = rnd(ref.swiglu(y[:, :I], y[:, I:], cfg.swiglu_limit))
-            out[rows] += rnd((self.aq(h) @ lw.e_w2[e - self.w.e_lo].float().T) * wsel)
+            out[rows] += rnd((self.aq_e(h) @ lw.e_w2[e - self.w.e_lo].float().T) * wsel)
         if lw.w13 is not None:
             out = out + rnd(self._ffn(lw.w13, lw.w2, xn))
         return out
@@ -337,6 +339,16 @@ class CudaWorkspace:
             if self.has_moe:
                 self.act_q["xg"] = pair(R * cfg.topk, H)
                 self.act_q["hmid"] = pair(R * cfg.topk, cfg.moe_inter)
+                if any(isinstance(l.e_w13, QuantWeight) and l.e_w13.native_mxfp4
+                       for l in list(w.layers) + [m.layer for m in w.mtp]):
+                    # MXFP8 activations of natively held MXFP4 experts: codes + one scale byte per 1 x 32 block
+                    def pair32(rows, width):
+                        width = (max(width, 128) + 127) // 128 * 128
+                        return torch.zeros(rows, width, **u8), torch.zeros(rows, width // 32, **u8)
+                    xrows = max(R * cfg.topk, (w.e_hi - w.e_lo) * 64)
+                    self.act_q["xn_mx"] = pair32(R, H)
+                    self.act_q["xg_mx"] = pair32(xrows, H)
+                    self.act_q["hmid_mx"] = pair32(xrows, cfg.moe_inter)
 
     def nbytes(self) -> int:
         tot = 0
@@ -406,9 +418,21 @@ class CudaForward:
         self.Q.quant_fp8_rows(x, out=(q, s))
         return q, s
 
+    def _quant_mx(self, x: torch.Tensor, slot: str):
+        """1 x 32 MXFP8 quantisation of activation rows into the workspace pair named `slot`."""
+        q, s = self.ws.act_q[slot]
+        rows, n = x.shape
+        q, s = q[:rows, :n], s[:rows, :n // 32]
+        self.Q.quant_mxfp8_rows(x, out=(q, s))
+        return q, s
+
     def _gemm(self, x, w, out, slot: str = "a", xq=None, **kw):
         """bf16 weight -> bf16 tcgen05 GEMM; QuantWeight -> quantise the rows (unless `xq` is given)
-        and run the block-scaled FP8 GEMM."""
+        and run the block-scaled FP8 GEMM (natively held MXFP4: MXFP8 rows and the MXFP4 GEMM)."""
+        if isinstance(w, QuantWeight) and w.native_mxfp4:
+            if xq is None:
+                xq = self._quant_mx(x, slot + "_mx")
+            return self.Q.gemm_mxfp4(xq[0], xq[1], w.packed, w.sf, out=out, **kw)
         if isinstance(w, QuantWeight):
             if xq is None:
                 xq = self._quant(x, slot)
@@ -467,7 +491,9 @@ class CudaForward:
         ws = self.ws
         if not self.static_moe or layer < 0 or layer >= ws.route_cnt.shape[0] or self.cfg.hidden % 256:
             return 0
-        if isinstance(lw.e_w13, QuantWeight) or (self.arena is not None and layer in self.arena.layers):
+        if self.arena is not None and layer in self.arena.layers:
+            return 0
+        if isinstance(lw.e_w13, QuantWeight) and not lw.e_w13.native_mxfp4:
             return 0
         for nt in ws.static_rows:
             if T <= nt:
@@ -516,6 +542,25 @@ class CudaForward:
                     for wt in (nl.w_qkv_a, nl.w_uk_t, nl.w_uv, nl.w_o):
                         if isinstance(wt, torch.Tensor):
                             K.l2_prefetch(wt, wt.numel() * wt.element_size())
+        if static and isinstance(lw.e_w13, QuantWeight):
+            # natively held MXFP4 experts: the normalised rows are quantised to MXFP8 once, the router gathers the
+            # codes and scale bytes, the gate|up epilogue re-quantises the SwiGLU product for the down projection
+            plan = ws.static_plans[static][layer]
+            xq = self._quant_mx(xn, "xn_mx")
+            (xgq, xgs), (hq, hs) = ws.act_q["xg_mx"], ws.act_q["hmid_mx"]
+            K.router_append(xn, lw.router_w, k, cfg.score_fn, plan, self.w.e_lo, self.w.e_hi, idx, wts, None,
+                            bias=lw.router_bias, n_groups=cfg.n_groups, topk_groups=cfg.topk_groups,
+                            normalize=cfg.norm_topk_prob, route_scale=cfg.route_scale, hash_table=lw.hash_table,
+                            token_ids=b.token_ids, dst_slots=ws.slots, quant_rows=(xq[0], xq[1], xgq, xgs))
+            R, I = plan.cap_rows, cfg.moe_inter
+            self.Q.gemm_mxfp4(xgq[:R], xgs[:R], lw.e_w13.packed, lw.e_w13.sf, epilogue=K.EPI_SWIGLU, plan=plan,
+                              act_limit=cfg.swiglu_limit, out_mx=(hq[:R, :I], hs[:R, :I // 32]))
+            self.Q.gemm_mxfp4(hq[:R, :I], hs[:R, :I // 32], lw.e_w2.packed, lw.e_w2.sf,
+                              out=ws.route_out[:T].view(T * ws.slots, H), epilogue=K.EPI_SCATTER, plan=plan,
+                              scatter_rows=T * ws.slots)
+            if side is not None:
+                torch.cuda.current_stream().wait_stream(side)
+            return idx
         if static:
             # no plan phase and no gather kernel: the router reserves rows in fixed per-expert slots
             plan = ws.static_plans[static][layer]
@@ -641,7 +686,7 @@ class CudaForward:
         # decode-sized MoE layers: the post-attention residual add + RMSNorm runs in the router kernel's prologue
         route_norm = None
         fuse_route = (self.fuse_router_norm and lw.is_moe and self._static_rows(lw, T, layer) > 0
-                      and not isinstance(lw.w13, QuantWeight))
+                      and not isinstance(lw.w13, QuantWeight) and not isinstance(lw.e_w13, QuantWeight))
         if tp is None:
             self._gemm(a, lw.w_o, ws.delta[:T], slot="a")
             if fuse_route:

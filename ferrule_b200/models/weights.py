@@ -28,33 +28,47 @@ from .config import ModelConfig
 
 
 class QuantWeight:
-    """A linear weight held as FP8 e4m3 codes plus UE8M0 scales, `[groups, out, in]`.
+    """A quantised linear weight `[groups, out, in]`.
 
-    group32 = False: one scale per 128 x 128 block, `scale [groups, ceil(out/128), ceil(in/128)]`
-    (the DeepSeek-V3 checkpoint format).  group32 = True: one scale per row per 32 inputs,
-    `scale [groups, out, in/32]`: MXFP4 expert weights whose e2m1 values were expanded to e4m3
-    codes at load time (every e2m1 value is exactly representable), so the tensor-core path is
-    the FP8 one while the scale grid stays MXFP4's.
+    group32 = False: FP8 e4m3 codes `q` with one UE8M0 scale per 128 x 128 block,
+    `scale [groups, ceil(out/128), ceil(in/128)]` (the DeepSeek-V3 checkpoint format).
+    group32 = True: MXFP4, one UE8M0 scale per row per 32 inputs, `scale [groups, out, in/32]`, in one of two
+    forms.  Native (`packed` set): two e2m1 values per byte, `packed [groups, out, in/2]` (the checkpoint's own
+    layout, half a byte per weight) plus `sf`, the scales re-arranged for the block-scaled tensor-core GEMM.
+    Container (`q` set): the e2m1 values expanded to e4m3 codes (every e2m1 value is exactly representable) for
+    the group-scaled FP8 GEMM; this is the form used where the native library is absent (CPU).
     """
-    __slots__ = ("q", "scale", "group32")
+    __slots__ = ("q", "scale", "group32", "packed", "sf")
 
-    def __init__(self, q: torch.Tensor, scale: torch.Tensor, group32: bool = False):
-        self.q, self.scale, self.group32 = q, scale, group32
+    def __init__(self, q: Optional[torch.Tensor], scale: torch.Tensor, group32: bool = False,
+                 packed: Optional[torch.Tensor] = None, sf: Optional[torch.Tensor] = None):
+        self.q, self.scale, self.group32, self.packed, self.sf = q, scale, group32, packed, sf
+
+    @property
+    def native_mxfp4(self) -> bool:
+        return self.packed is not None
 
     @property
     def shape(self):
+        if self.packed is not None:
+            return torch.Size(list(self.packed.shape[:-1]) + [self.packed.shape[-1] * 2])
         return self.q.shape
 
     def nbytes(self) -> int:
-        return self.q.numel() + self.scale.numel()
+        n = self.scale.numel()
+        for t in (self.q, self.packed, self.sf):
+            if t is not None:
+                n += t.numel()
+        return n
 
     def dequant(self) -> torch.Tensor:
         """bf16 tensor with exactly the values the quantised GEMM multiplies by."""
         from ..io import encoding as enc
-        two_d = self.q.dim() == 2
-        q, scale = (self.q.unsqueeze(0), self.scale.unsqueeze(0)) if two_d else (self.q, self.scale)
-        G, O, I = q.shape
-        v = enc.e4m3_decode(q)
+        codes = self.packed if self.packed is not None else self.q
+        two_d = codes.dim() == 2
+        codes, scale = (codes.unsqueeze(0), self.scale.unsqueeze(0)) if two_d else (codes, self.scale)
+        v = enc.fp4_unpack(codes).float() if self.packed is not None else enc.e4m3_decode(codes)
+        G, O, I = v.shape
         sc = enc.e8m0_decode(scale)
         if self.group32:
             out = (v.view(G, O, I // 32, 32) * sc.unsqueeze(-1)).view(G, O, I)
@@ -70,6 +84,16 @@ class QuantWeight:
         two_d = w.dim() == 2
         if two_d:
             w = w.unsqueeze(0)
+        if fmt == "mxfp4" and w.is_cuda and w.shape[-1] % 128 == 0:
+            # native form, quantised and laid out on the device
+            from ..ops import quant as Q
+            G, O, I = w.shape
+            packed, sb = Q.quant_mxfp4_rows(w.reshape(G * O, I).contiguous().to(torch.bfloat16))
+            packed, sb = packed.view(G, O, I // 2), sb.view(G, O, I // 32)
+            sf = Q.mxfp4_prepare_sf(sb)
+            if two_d:
+                return QuantWeight(None, sb[0], True, packed[0], sf[0])
+            return QuantWeight(None, sb, True, packed, sf)
         qs, ss = [], []
         for g in range(w.shape[0]):
             if fmt == "fp8_block":
@@ -138,6 +162,9 @@ def dequantized_copy(w: "ModelWeights") -> "ModelWeights":
         out.mtp.append(mc)
     out.weight_format = "bf16"
     out.act_quant = w.weight_format != "bf16"
+    # natively held MXFP4 experts multiply MXFP8 activations (1 x 32 scale blocks)
+    native = any(isinstance(l.e_w13, QuantWeight) and l.e_w13.native_mxfp4 for l in w.layers)
+    out.expert_act_block = 32 if native else 128
     return out
 
 
@@ -198,6 +225,7 @@ class ModelWeights:
     vocab_lo: int = 0
     weight_format: str = "bf16"
     act_quant: bool = False       # oracle only: emulate the 1 x 128 FP8 activation quantisation of the FP8 path
+    expert_act_block: int = 128   # oracle only: scale-block width of the routed experts' activation quantisation
 
     @property
     def heads_local(self) -> int:
@@ -210,8 +238,8 @@ class ModelWeights:
         def add(t):
             nonlocal total
             if isinstance(t, QuantWeight):
-                add(t.q)
-                add(t.scale)
+                for part in (t.q, t.scale, t.packed, t.sf):
+                    add(part)
             elif isinstance(t, torch.Tensor) and t.data_ptr() not in seen:
                 seen.add(t.data_ptr())
                 total += t.numel() * t.element_size()

@@ -36,6 +36,8 @@ def declare(lib) -> None:
                               vp, vp], i),
         "fb_norm_router_append": ([vp, ll, vp, ll, vp, vp, ll, vp, ll, f, vp, i, vp, vp, vp, i, i, i, i, i, i, i, f, vp, vp,
                                    i, i, i, i, vp, vp, vp, vp, vp, ll, vp, vp], i),
+        "fb_router_append_q": ([vp, ll, vp, ll, vp, vp, ll, vp, ll, f, vp, i, vp, vp, vp, i, i, i, i, i, i, i, f, vp, vp,
+                                i, i, i, i, vp, vp, vp, vp, vp, ll, vp, ll, vp, ll, vp, ll, vp, ll, i, vp, vp], i),
         "fb_moe_reduce_norm": ([vp, i, i, vp, i, i, vp, ll, vp, ll, i, i, vp, vp, ll, f, vp], i),
         "fb_l2_prefetch": ([vp, ll, vp], i),
         "fb_decode_advance": ([vp, vp, vp, vp, vp, vp, vp, i, i, i, i, i, i, vp], i),

@@ -336,15 +336,33 @@ def router_append(x: torch.Tensor, w: torch.Tensor, topk: int, score_fn: int, pl
                   normalize: bool = False, route_scale: float = 1.0, hash_table: Optional[torch.Tensor] = None,
                   token_ids: Optional[torch.Tensor] = None, dst_slots: int = 0,
                   norm_w: Optional[torch.Tensor] = None, eps: float = 0.0, delta: Optional[torch.Tensor] = None,
-                  res_out: Optional[torch.Tensor] = None, norm_out: Optional[torch.Tensor] = None) -> None:
+                  res_out: Optional[torch.Tensor] = None, norm_out: Optional[torch.Tensor] = None,
+                  quant_rows=None) -> None:
     """Router + top-k + row reservation in a static plan + activation gather, one launch (one CTA per token).
     `plan.counts` must be zero on entry.  With `norm_w` the kernel first forms the row itself: `x` is then the
     residual stream, res_out = bf16(x + delta), norm_out = RMSNorm(res_out) * norm_w (bit-equal to `add_rmsnorm`),
-    and the router reads that normalised row."""
+    and the router reads that normalised row.  `quant_rows` = (codes [rows, hidden] u8, scales [rows, c] u8,
+    xg codes, xg scales): the gathered rows are the token's quantised codes and scale bytes (`xg` is unused)."""
     lib = get_lib(True)
     rows, hidden = x.shape
-    assert rows <= plan.ntok and xg.shape[0] >= plan.cap_rows and xg.shape[1] == hidden and w.is_contiguous()
+    assert rows <= plan.ntok and w.is_contiguous()
     assert plan.max_tiles == e_hi - e_lo
+    if quant_rows is not None:
+        q, sc, xgq, xgs = quant_rows
+        assert xgq.shape[0] >= plan.cap_rows and xgq.shape[1] == hidden and xgs.shape[1] == sc.shape[1]
+        check(lib.fb_router_append_q(x.data_ptr(), x.stride(0), ptr(delta), delta.stride(0) if delta is not None else 0,
+                                     ptr(norm_w), ptr(res_out), res_out.stride(0) if res_out is not None else 0,
+                                     ptr(norm_out), norm_out.stride(0) if norm_out is not None else 0, eps,
+                                     w.data_ptr(), hidden, ptr(bias), ptr(hash_table),
+                                     ptr(token_ids), rows, w.shape[0], topk, score_fn, n_groups, topk_groups,
+                                     1 if normalize else 0, route_scale, out_idx.data_ptr(), out_w.data_ptr(), e_lo,
+                                     e_hi, plan.ntok, dst_slots, plan.counts.data_ptr(), plan.src_token.data_ptr(),
+                                     plan.dst_row.data_ptr(), plan.row_scale.data_ptr(), None, 8,
+                                     q.data_ptr(), q.stride(0), sc.data_ptr(), sc.stride(0), xgq.data_ptr(),
+                                     xgq.stride(0), xgs.data_ptr(), xgs.stride(0), sc.shape[1],
+                                     status_tensor(x.device).data_ptr(), stream_ptr()), "fb_router_append_q")
+        return
+    assert xg.shape[0] >= plan.cap_rows and xg.shape[1] == hidden
     check(lib.fb_norm_router_append(x.data_ptr(), x.stride(0), ptr(delta), delta.stride(0) if delta is not None else 0,
                                     ptr(norm_w), ptr(res_out), res_out.stride(0) if res_out is not None else 0,
                                     ptr(norm_out), norm_out.stride(0) if norm_out is not None else 0, eps,

@@ -1,7 +1,7 @@
 """Small, self-ending workloads of one kernel family each, for profiler captures and quick timings.
 
     python -m ferrule_b200.utils.kernel_probe <case> [reps]
-    python -m ferrule_b200.utils.kernel_probe decode_step <layers> [eager]
+    python -m ferrule_b200.utils.kernel_probe decode_step <layers> [eager|graph] [bf16|fp8_block|fp8_mxfp4]
 
 Cases use decode-step shapes of the DeepSeek-V2-Lite configuration (batch 32, context about 640) unless
 noted; weight sets are rotated through more buffers than fit in L2 where the kernel is bandwidth-bound, and
@@ -210,14 +210,14 @@ def case_v3_fp8_decode(reps):
     return timed(lambda i: fwd.forward(b), reps), {"format": fmt}
 
 
-def case_decode_step(layers: int, eager: bool):
+def case_decode_step(layers: int, eager: bool, weight_format: str = "bf16"):
     """One decode step of the DeepSeek-V2-Lite shape (bf16, batch 32, context 640) with `layers` layers.
     `eager`: three eager steps and nothing else - the form used for a launch list, where every kernel of the
     step is one launch.  Otherwise the step is captured in a CUDA graph and 20 replays are timed."""
     from ferrule_b200.models import config as C, deepseek as D, weights as W
     cfg = C.deepseek_v2_lite()
     cfg = cfg.with_(n_layers=layers or cfg.n_layers)
-    w = W.random_weights(cfg, device=DEV, fast_device_init=True)
+    w = W.random_weights(cfg, device=DEV, fast_device_init=True, weight_format=weight_format)
     B, ctx, page, max_blocks = 32, 640, 64, 16
     pool = D.KvPool(cfg, B * max_blocks + 1, page, DEV)
     pool.data.normal_(0, 0.3)
@@ -230,7 +230,7 @@ def case_decode_step(layers: int, eager: bool):
     g.batch.row_pos.fill_(ctx)
     g.batch.row_seq.copy_(torch.arange(B, device=DEV))
     g.batch.write_slot.copy_((bt[:, ctx // page].long() * page + ctx % page))
-    extra = {"layers": cfg.n_layers, "weight_bytes": w.nbytes()}
+    extra = {"layers": cfg.n_layers, "weight_bytes": w.nbytes(), "weight_format": weight_format}
     if eager:
         for _ in range(3):
             fwd.forward(g.batch)
@@ -253,7 +253,8 @@ def main() -> int:
     reps = int(sys.argv[2]) if len(sys.argv) > 2 else 20
     torch.manual_seed(0)
     if name == "decode_step":           # second argument: number of layers (0 = all), third: "eager"
-        us, extra = case_decode_step(reps if len(sys.argv) > 2 else 0, len(sys.argv) > 3 and sys.argv[3] == "eager")
+        us, extra = case_decode_step(reps if len(sys.argv) > 2 else 0, len(sys.argv) > 3 and sys.argv[3] == "eager",
+                                     sys.argv[4] if len(sys.argv) > 4 else "bf16")
         reps = 20
     else:
         us, extra = CASES[name](reps)

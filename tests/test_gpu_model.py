@@ -155,6 +155,7 @@ def test_quantised_forward_matches_dequantised_oracle(fmt, preset):
     dev = "cuda"
     w = W.random_weights(cfg, device=dev, seed=3, std=0.05, weight_format=fmt)
     assert isinstance(w.layers[1].e_w13, W.QuantWeight) and w.layers[1].e_w13.group32 == (fmt == "fp8_mxfp4")
+    assert w.layers[1].e_w13.native_mxfp4 == (fmt == "fp8_mxfp4")       # packed 4-bit experts on the device
     assert w.nbytes() < 0.75 * W.random_weights(cfg, device=dev, seed=3, std=0.05).nbytes()
     oracle = W.dequantized_copy(w)
     page = 16
