@@ -269,6 +269,7 @@ typedef struct FbGemmMxfp4Args {
   const float* row_scale;
   float act_limit;
   void* status;
+  int w_tiled;              // w is tile-major: [groups][ceil(rows/128)][k/128][128 rows][64 bytes] (rows padded to 128)
 } FbGemmMxfp4Args;
 int fb_gemm_mxfp4(const FbGemmMxfp4Args* args, void* stream);
 // linear UE8M0 weight scales [groups, rows, k / 32] -> [groups, ceil(rows / 128), k / 128, 512] blocks for the kernel

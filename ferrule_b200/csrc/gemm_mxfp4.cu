@@ -68,6 +68,7 @@ struct Params {
   DeviceStatus* status;
   int w_stream;
   int w_tx_bytes;              // bytes one weight-tile load completes on its barrier
+  int w_tiled;                 // weights stored tile-major: [groups][128-row tiles][k-blocks][128 rows][64 bytes]
   int sfb_bytes;               // one activation-scale buffer in shared memory
   int sfb_cols;                // TMEM columns of the activation scales of one tile
   int sfb_stride;              // TMEM columns per k-block (4: scale operands start on 4-column boundaries)
@@ -215,7 +216,14 @@ gemm_mxfp4_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_const
           uint8_t* stage = smem + s * C::kStageBytes;
           uint8_t* sfa = stage + C::kWBytes * (DUAL ? 2 : 1) + C::kXBytes;
           mbar_arrive_expect_tx(&full_bar[s], tx);
-          if (p.w_stream) {
+          if (p.w_tiled) {
+            // tile-major weights: every (128 rows x 128 k) tile is 8 KB of consecutive global memory
+            const int t0 = ((g * p.sf_tiles + nt) * kblocks + kb) * kTileN;
+            tma_load_3d_hint(stage, &tmap_w, &full_bar[s], 0, t0, 0, wpol);
+            if (DUAL)
+              tma_load_3d_hint(stage + C::kWBytes, &tmap_w, &full_bar[s], 0,
+                               ((g * p.sf_tiles + p.dual_offset / kTileN + nt) * kblocks + kb) * kTileN, 0, wpol);
+          } else if (p.w_stream) {
             tma_load_3d_hint(stage, &tmap_w, &full_bar[s], kb * kBlockK, nt * kTileN, g, wpol);
             if (DUAL)
               tma_load_3d_hint(stage + C::kWBytes, &tmap_w, &full_bar[s], kb * kBlockK, p.dual_offset + nt * kTileN, g, wpol);
@@ -567,8 +575,15 @@ extern "C" int fb_gemm_mxfp4(const FbGemmMxfp4Args* a, void* stream_) {
     return FB_ERR_ALIGN;
   CUtensorMap mw, mxm;
   // packed 4-bit weights: dimensions count values, strides are bytes (half a byte per value)
-  int rc = make_map(&mw, CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, a->w, a->k, a->w_rows_per_group, a->groups,
-                    static_cast<uint64_t>(a->ldw_bytes), static_cast<uint64_t>(a->w_group_stride_bytes), kTileN, 3, 32);
+  int rc;
+  if (a->w_tiled) {
+    const uint64_t tiles = static_cast<uint64_t>(a->groups) * ((a->w_rows_per_group + kTileN - 1) / kTileN) * (a->k / kBlockK);
+    rc = make_map(&mw, CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, a->w, kBlockK, tiles * kTileN, 1, kBlockK / 2,
+                  tiles * kTileN * (kBlockK / 2), kTileN, 3, 32);
+  } else {
+    rc = make_map(&mw, CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, a->w, a->k, a->w_rows_per_group, a->groups,
+                  static_cast<uint64_t>(a->ldw_bytes), static_cast<uint64_t>(a->w_group_stride_bytes), kTileN, 3, 32);
+  }
   if (rc != FB_OK) return rc;
   rc = make_map(&mxm, CU_TENSOR_MAP_DATA_TYPE_UINT8, a->x, a->k, a->x_rows, 1, a->ldx, 0, a->ntok, 2, 16);
   if (rc != FB_OK) return rc;
@@ -608,6 +623,7 @@ extern "C" int fb_gemm_mxfp4(const FbGemmMxfp4Args* a, void* stream_) {
   // a weight-tile load reports the bytes it read from global memory (half a byte per value) on its barrier, not
   // the bytes it spread over shared memory
   p.w_tx_bytes = kTileN * kBlockK / 2;
+  p.w_tiled = a->w_tiled;
   const int tok_tiles = grouped ? a->max_tok_tiles : (a->x_rows + a->ntok - 1) / a->ntok;
   const int max_tiles = tok_tiles * p.n_tiles;
   if (dual) {

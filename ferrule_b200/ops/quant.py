@@ -148,7 +148,21 @@ class GemmMxfp4Args(C.Structure):
         ("max_tok_tiles", C.c_int),
         ("tile_group", C.c_void_p), ("tile_row0", C.c_void_p), ("tile_rows", C.c_void_p), ("num_tok_tiles", C.c_void_p),
         ("dst_row", C.c_void_p), ("row_scale", C.c_void_p), ("act_limit", C.c_float), ("status", C.c_void_p),
+        ("w_tiled", C.c_int),
     ]
+
+
+def mxfp4_tile_major(packed: torch.Tensor) -> torch.Tensor:
+    """Packed e2m1 weights [groups, rows, k/2] -> tile-major [groups, ceil(rows/128), k/128, 128, 64]: every
+    (128 rows x 128 k) tile the GEMM loads is 8 KB of consecutive memory (rows padded with zeros)."""
+    if packed.dim() == 2:
+        packed = packed.unsqueeze(0)
+    G, rows, half = packed.shape
+    assert half % 64 == 0
+    rt = (rows + 127) // 128
+    if rt * 128 != rows:
+        packed = torch.nn.functional.pad(packed, (0, 0, 0, rt * 128 - rows))
+    return packed.view(G, rt, 128, half // 64, 64).permute(0, 1, 3, 2, 4).contiguous()
 
 
 def _mx_lib():
@@ -200,7 +214,8 @@ def mxfp4_prepare_sf(scale: torch.Tensor) -> torch.Tensor:
 def gemm_mxfp4(xq: torch.Tensor, xs: torch.Tensor, w_packed: torch.Tensor, w_sf: torch.Tensor,
                out: Optional[torch.Tensor] = None, *, out_dtype=torch.bfloat16, epilogue: int = 0, plan=None,
                scatter_rows: Optional[int] = None, act_limit: float = 0.0, ntok: Optional[int] = None,
-               out_mx: Optional[Tuple[torch.Tensor, torch.Tensor]] = None) -> torch.Tensor:
+               out_mx: Optional[Tuple[torch.Tensor, torch.Tensor]] = None, w_rows: Optional[int] = None
+               ) -> torch.Tensor:
     """MXFP4 weights x MXFP8 activations on `tcgen05.mma kind::mxf8f6f4.block_scale`.
 
     xq uint8 e4m3 [rows, K] + xs UE8M0 [rows, K/32]; w_packed uint8 [groups, N, K/2] (two e2m1 per byte, low
@@ -208,10 +223,17 @@ def gemm_mxfp4(xq: torch.Tensor, xs: torch.Tensor, w_packed: torch.Tensor, w_sf:
     (plan).  `out_mx` = (codes [rows, n_out] uint8, scales [rows, n_out/32] uint8): the result is re-quantised
     to MXFP8 in the epilogue instead of being stored as bf16."""
     lib = _mx_lib()
-    if w_packed.dim() == 2:
-        w_packed = w_packed.unsqueeze(0)
-    groups, w_rows, half = w_packed.shape
-    K = half * 2
+    tiled = w_packed.dim() == 5            # from `mxfp4_tile_major`; `w_rows` = weight rows per group before padding
+    if tiled:
+        groups, rt, kb, _, _ = w_packed.shape
+        K = kb * 128
+        w_rows = rt * 128 if w_rows is None else w_rows
+        half = K // 2
+    else:
+        if w_packed.dim() == 2:
+            w_packed = w_packed.unsqueeze(0)
+        groups, w_rows, half = w_packed.shape
+        K = half * 2
     rows = xq.shape[0]
     dual = epilogue == 1
     n_out = w_rows // 2 if dual else w_rows
@@ -230,7 +252,10 @@ def gemm_mxfp4(xq: torch.Tensor, xs: torch.Tensor, w_packed: torch.Tensor, w_sf:
         a.out, a.ldo = out.data_ptr(), out.stride(0)
         a.out_mode = 1 if out.dtype == torch.float32 else 0
     a.w, a.x, a.w_sf, a.x_scale = w_packed.data_ptr(), xq.data_ptr(), w_sf.data_ptr(), xs.data_ptr()
-    a.ldw_bytes, a.w_group_stride_bytes = w_packed.stride(1), w_packed.stride(0)
+    if tiled:
+        a.w_tiled, a.ldw_bytes, a.w_group_stride_bytes = 1, 64, w_packed.stride(0)
+    else:
+        a.ldw_bytes, a.w_group_stride_bytes = w_packed.stride(1), w_packed.stride(0)
     a.ldx, a.ldxs = xq.stride(0), xs.stride(0)
     a.n_out, a.k, a.groups, a.w_rows_per_group, a.x_rows = n_out, K, groups, w_rows, rows
     a.ntok, a.epilogue, a.dual_offset = ntok, epilogue, (w_rows // 2 if dual else 0)

@@ -178,8 +178,12 @@ def test_gemm_mxfp4_native_block_scaled(rows, n, k, dual):
     packed, sb = torch.cat([a for a, _ in parts]), torch.cat([b for _, b in parts])
     sf = Q.mxfp4_prepare_sf(sb.cuda())
     out = Q.gemm_mxfp4(xq, xs, packed.cuda(), sf, epilogue=1 if dual else 0, out_dtype=torch.float32)
+    # the same weights stored tile-major give the same bits
+    out_t = Q.gemm_mxfp4(xq, xs, Q.mxfp4_tile_major(packed.cuda()), sf, epilogue=1 if dual else 0,
+                         out_dtype=torch.float32, w_rows=packed.shape[0])
     torch.cuda.synchronize()
     assert _lib.read_status()[0] == 0
+    assert torch.equal(out, out_t)
     xd = _mx_dequant_rows(xq, xs)
     wd = enc.weight_dequant_mxfp4(packed, sb).float()
     y = xd @ wd.T
