@@ -21,7 +21,7 @@ import json
 import os
 import sys
 import time
-from typing import List, Optional
+from typing import Any, Dict, List, Optional
 
 
 def _add_model_args(p: argparse.ArgumentParser) -> None:
@@ -301,7 +301,24 @@ def cmd_serve(args) -> int:
     return 0
 
 
+def _compare_traces(got: List[List[int]], want: List[List[int]]) -> Dict[str, Any]:
+    """Turn-by-turn comparison of token traces: the first diverging turn / index and both tokens there."""
+    out: Dict[str, Any] = {"match": got == want, "turns_compared": min(len(got), len(want))}
+    if len(got) != len(want):
+        out["turn_count"] = {"got": len(got), "want": len(want)}
+    for t, (g, w) in enumerate(zip(got, want)):
+        if g != w:
+            i = next((j for j, (a, b) in enumerate(zip(g, w)) if a != b), min(len(g), len(w)))
+            out["first_divergence"] = {"turn": t, "index": i, "got": g[i] if i < len(g) else None,
+                                       "want": w[i] if i < len(w) else None, "got_len": len(g), "want_len": len(w)}
+            break
+    return out
+
+
 def cmd_bench_interactive(args) -> int:
+    """Multi-turn session benchmark: one retained session, `--turns` turns of a synthetic (or `--trace` given)
+    prompt; JSON report (version 2) with per-turn timing, engine / runner / registry / speculative /
+    hard-resource statistics and, with `--golden`, a token-exact comparison against a recorded trace."""
     import random
 
     from ..runtime.session import GenerateRequest
@@ -310,27 +327,100 @@ def cmd_bench_interactive(args) -> int:
     V = eng.runner.vocab_size
     report = {"report_version": 2, "model": name, "turns": []}
     sid = "bench-session"
-    for turn in range(args.turns):
-        prompt = [rng.randrange(V) for _ in range(args.prompt_len)]
+    trace = json.load(open(args.trace)) if args.trace else None
+    n_turns = len(trace["turns"]) if trace else args.turns
+    full: List[List[int]] = []
+    for turn in range(n_turns):
+        if trace:
+            t = trace["turns"][turn]
+            prompt = t["prompt_tokens"] if "prompt_tokens" in t else tok.encode(t.get("prompt", ""))
+            max_new = int(t.get("max_tokens", args.max_tokens))
+        else:
+            prompt, max_new = [rng.randrange(V) for _ in range(args.prompt_len)], args.max_tokens
         t0 = time.perf_counter()
-        eng.submit(GenerateRequest(f"t{turn}", prompt, max_new_tokens=args.max_tokens, ignore_eos=True,
+        eng.submit(GenerateRequest(f"t{turn}", prompt, max_new_tokens=max_new, ignore_eos=True,
                                    session_id=sid, retain_session=True))
         toks, fin = _collect(eng)
         f = fin[f"t{turn}"]
+        full.append(list(toks.get(f"t{turn}", [])))
         report["turns"].append({"turn": turn, "prompt_tokens": f.prompt_tokens, "generated": f.generated_tokens,
                                 "seconds": round(time.perf_counter() - t0, 4), "ttft_s": round(f.ttft_s, 4),
-                                "tpot_s": round(f.tpot_s, 6), "tokens": toks.get(f"t{turn}", [])[:8]})
+                                "tpot_s": round(f.tpot_s, 6), "finish": f.reason.value, "tokens": full[-1]})
     report["engine"] = eng.snapshot_stats()
     report["runner"] = eng.runner.observability()
+    if eng.registry is not None:
+        report["registry"] = dict(vars(eng.registry.stats)) if hasattr(eng.registry, "stats") else {}
+        if hasattr(eng.registry, "ledger"):
+            report["critical_path"] = eng.registry.ledger.snapshot() if hasattr(eng.registry.ledger, "snapshot") else {}
+    if args.write_golden:
+        with open(args.write_golden, "w") as fh:
+            json.dump({"model": name, "turns": [{"tokens": t} for t in full]}, fh)
+        report["golden_written"] = args.write_golden
     if args.golden:
         golden = json.load(open(args.golden))
-        got = [t["tokens"] for t in report["turns"]]
-        want = [t["tokens"] for t in golden.get("turns", [])]
-        report["golden_match"] = got == want
+        want = [list(t["tokens"]) for t in golden.get("turns", [])]
+        # a golden trace may hold a prefix of every turn's tokens (older reports kept eight)
+        got = [g[:len(w)] if len(w) < len(g) else g for g, w in zip(full, want)] + full[len(want):]
+        report["golden"] = _compare_traces(got, want)
+        report["golden_match"] = report["golden"]["match"]
     eng.shutdown()
     report["shutdown_residual"] = {"kv_used_pages": eng.kv.stats().used_pages, "grants": eng.broker.outstanding()}
     print(json.dumps(report))
     return 0 if report.get("golden_match", True) else 2
+
+
+def cmd_generation_parity(args) -> int:
+    """Prompt / token parity against a recorded file: `{"cases": [{"prompt_tokens": [...] | "prompt": "...",
+    "expected_tokens": [...]}]}`.  Every case runs greedily for len(expected) tokens; exit code 2 on a mismatch.
+    Plays the role of the reference's scripts/dsv4_generation_parity.py."""
+    from ..runtime.session import GenerateRequest
+    eng, tok, name = build_engine(args)
+    spec = json.load(open(args.cases))
+    results, ok = [], True
+    for i, c in enumerate(spec["cases"]):
+        prompt = c["prompt_tokens"] if "prompt_tokens" in c else tok.encode(c["prompt"])
+        want = list(c.get("expected_tokens", []))
+        n = len(want) or int(c.get("max_tokens", args.max_tokens))
+        eng.submit(GenerateRequest(f"case{i}", prompt, max_new_tokens=n, ignore_eos=True))
+        toks, _ = _collect(eng)
+        got = list(toks.get(f"case{i}", []))
+        cmp_ = _compare_traces([got], [want]) if want else {"match": True}
+        ok &= cmp_["match"]
+        results.append({"case": i, "prompt_tokens": len(prompt), "generated": got, **cmp_})
+    eng.shutdown()
+    print(json.dumps({"model": name, "cases": results, "all_match": ok}))
+    return 0 if ok else 2
+
+
+def cmd_chunk_sweep(args) -> int:
+    """Sweep the prefill chunk size of the resident driver on one synthetic prompt set and report TTFT,
+    prefill tokens/s and decode tokens/s per setting (the reference's scripts/dsv4_runtime_driver_chunk_sweep.py)."""
+    import random
+
+    from ..runtime.session import GenerateRequest
+    rows = []
+    for chunk in args.chunks:
+        args.prefill_chunk = chunk
+        args.max_batch_tokens = max(args.max_batch_tokens, chunk)
+        eng, tok, name = build_engine(args)
+        rng = random.Random(args.seed)
+        V = eng.runner.vocab_size
+        t0 = time.perf_counter()
+        for i in range(args.requests):
+            eng.submit(GenerateRequest(f"r{i}", [rng.randrange(V) for _ in range(args.prompt_len)],
+                                       max_new_tokens=args.max_tokens, ignore_eos=True))
+        toks, fin = _collect(eng)
+        wall = time.perf_counter() - t0
+        ttft = sorted(f.ttft_s for f in fin.values())
+        gen = sum(f.generated_tokens for f in fin.values())
+        st = eng.snapshot_stats()
+        rows.append({"prefill_chunk": chunk, "seconds": round(wall, 4), "ttft_p50_s": round(ttft[len(ttft) // 2], 4),
+                     "ttft_max_s": round(ttft[-1], 4), "generated_tokens": gen,
+                     "tokens_per_s": round((gen + args.requests * args.prompt_len) / wall, 1),
+                     "prefill_chunks": st["prefill_chunks"], "decode_steps": st["decode_steps"]})
+        eng.shutdown()
+    print(json.dumps({"model": name, "prompt_len": args.prompt_len, "requests": args.requests, "sweep": rows}))
+    return 0
 
 
 def cmd_bench_serve(args) -> int:
@@ -408,7 +498,16 @@ def main(argv: Optional[List[str]] = None) -> int:
     p.set_defaults(fn=cmd_serve)
     p = sub.add_parser("bench-interactive"); _add_model_args(p)
     p.add_argument("--turns", type=int, default=2); p.add_argument("--prompt-len", type=int, default=32)
-    p.add_argument("--max-tokens", type=int, default=16); p.add_argument("--golden"); p.set_defaults(fn=cmd_bench_interactive)
+    p.add_argument("--max-tokens", type=int, default=16); p.add_argument("--golden"); p.add_argument("--write-golden")
+    p.add_argument("--trace", help="JSON {turns: [{prompt_tokens | prompt, max_tokens}]} instead of synthetic turns")
+    p.set_defaults(fn=cmd_bench_interactive)
+    p = sub.add_parser("generation-parity"); _add_model_args(p)
+    p.add_argument("--cases", required=True); p.add_argument("--max-tokens", type=int, default=16)
+    p.set_defaults(fn=cmd_generation_parity)
+    p = sub.add_parser("chunk-sweep"); _add_model_args(p)
+    p.add_argument("--chunks", type=int, nargs="+", default=[64, 128, 256, 512]); p.add_argument("--requests", type=int, default=4)
+    p.add_argument("--prompt-len", type=int, default=256); p.add_argument("--max-tokens", type=int, default=8)
+    p.set_defaults(fn=cmd_chunk_sweep)
     p = sub.add_parser("bench-serve")
     p.add_argument("--url", default="http://127.0.0.1:8000"); p.add_argument("--model", default="")
     p.add_argument("--concurrency", type=int, nargs="+", default=[1, 8, 32]); p.add_argument("--requests", type=int, default=64)

@@ -174,6 +174,9 @@ class DeepSeekRunner(ModelRunner):
         else:
             self.fwd = ReferenceForward(weights, self.pool, emulate_bf16=emulate_bf16)
         self.graphs: Dict[int, tuple] = {}
+        # captured decode graphs and their staging, one per row count (exact-key reuse, build on first use)
+        from ..runtime.arena import PersistentArenaPool
+        self.graph_pool: PersistentArenaPool = PersistentArenaPool()
         self.txns: Dict[int, ExecutionBatch] = {}
         # decode look-ahead: while the host publishes step n, step n + 1 already runs on the device, fed by the
         # greedy tokens that are still there.  The step is launched for the batch the engine is predicted to
@@ -219,15 +222,18 @@ class DeepSeekRunner(ModelRunner):
     def _graph_for(self, rows: int):
         g = self.graphs.get(rows)
         if g is None:
-            st = BatchStaging(rows, rows, self.max_blocks, self.device)
-            st.np_rpos[:] = -1
-            st.np_slot[:] = -1
-            st.np_lrows[:] = np.arange(rows)
-            st.upload()
-            graph = DecodeGraph(self.fwd, rows, rows, self.max_blocks, batch=st.device_batch(rows, rows))
-            graph.capture()
-            self.stats.graph_captures += 1
-            g = (st, graph)
+            def build():
+                st = BatchStaging(rows, rows, self.max_blocks, self.device)
+                st.np_rpos[:] = -1
+                st.np_slot[:] = -1
+                st.np_lrows[:] = np.arange(rows)
+                st.upload()
+                graph = DecodeGraph(self.fwd, rows, rows, self.max_blocks, batch=st.device_batch(rows, rows))
+                graph.capture()
+                self.stats.graph_captures += 1
+                return (st, graph)
+            # stays checked out while the runner lives: a decode step of this row count is always in reach
+            g = self.graph_pool.checkout((rows, self.max_blocks), build).arena
             self.graphs[rows] = g
         return g
 

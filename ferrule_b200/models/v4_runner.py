@@ -44,6 +44,9 @@ def _truncate(c: V4SeqCache, cfg, pos: int) -> None:
     c.position = pos
 
 
+from ..runtime.arena import SequenceStateCore
+
+
 class V4Runner(ModelRunner):
     def __init__(self, weights: V4Weights, n_pages: int, page_size: int = 64, max_seqs: int = 8,
                  max_seq_len: int = 1024, max_rows: int = 2048, eos_token_id: int = -1):
@@ -61,6 +64,10 @@ class V4Runner(ModelRunner):
         self.txns: Dict[int, ExecutionBatch] = {}
         self.steps = 0
         self.forward_ns = 0
+        # committed cursor of every slot-bound sequence state: a step binds to (generation, position) when it
+        # starts and commits only if both still hold; a step that fails half-way poisons the slot until release
+        self.seq_state: Dict[int, SequenceStateCore] = {}
+        self._bindings: Dict[int, Dict[int, tuple]] = {}
 
     # ------------------------------------------------------------------ contract
     def capabilities(self) -> ExecutionCapabilities:
@@ -90,16 +97,40 @@ class V4Runner(ModelRunner):
     def execute(self, txn_id: int):
         b = self.txns[txn_id]
         t0 = time.perf_counter_ns()
-        with torch.no_grad():
-            out = self._execute_cuda(b) if self.is_cuda else self._execute_reference(b)
+        binds = self._bindings[txn_id] = {}
+        for s in b.sequences:
+            core = self.seq_state.setdefault(s.state_slot, SequenceStateCore())
+            if core.position != s.context_len and not core.poisoned:
+                if s.context_len > core.position:
+                    raise RuntimeError(f"slot {s.state_slot}: state holds {core.position} tokens, batch expects "
+                                       f"{s.context_len}")
+                core.rewind(s.context_len)            # rejected / aborted rows will be overwritten
+            binds[s.state_slot] = (core.begin_step(), s.query_len)
+        try:
+            with torch.no_grad():
+                out = self._execute_cuda(b) if self.is_cuda else self._execute_reference(b)
+        except Exception:
+            for slot, (binding, _) in binds.items():
+                self.seq_state[slot].poison_step(binding)
+            raise
         self.forward_ns += time.perf_counter_ns() - t0
         return Complete(out)
 
     def resume(self, txn_id: int):
         return self.execute(txn_id)
 
+    def retain_provisional_prefixes(self, txn_id: int, rows_by_slot: Dict[int, int]) -> None:
+        binds = self._bindings.get(txn_id, {})
+        for slot, rows in rows_by_slot.items():
+            if slot in binds:
+                binds[slot] = (binds[slot][0], min(rows, binds[slot][1]))
+
     def end_transaction(self, txn_id: int, intent: EndIntent) -> EndStatus:
         self.txns.pop(txn_id, None)        # aborted rows are overwritten when their positions run again
+        for slot, (binding, rows) in self._bindings.pop(txn_id, {}).items():
+            core = self.seq_state.get(slot)
+            if core is not None and intent == EndIntent.PUBLISH and not core.poisoned:
+                core.commit_step(binding, rows)
         return EndStatus.COMPLETE
 
     def release_pages(self, pages: Sequence[int]) -> None:
@@ -112,6 +143,7 @@ class V4Runner(ModelRunner):
         raise RuntimeError("V4 state is bound by slot; preemption with page snapshots is not supported")
 
     def release_slot(self, state_slot: int) -> None:
+        self.seq_state.pop(state_slot, None)
         if self.is_cuda:
             self.fwd.positions[state_slot] = 0
         else:

@@ -31,3 +31,34 @@ def test_cli_fixture_inspect_generate_bench(tmp_path):
     assert rep["shutdown_residual"] == {"kv_used_pages": 0, "grants": 0}
     sm = json.loads(run("expert-stream-smoke", d, "--device", "cpu", "--device-mb", "8"))
     assert sm["ok"] and sm["registry"]["published"] == sm["experts"]
+
+
+def test_cli_golden_trace_parity_and_chunk_sweep(tmp_path):
+    common = ["--preset", "tiny-fixture", "--device", "cpu", "--ctx-size", "256", "--max-seqs", "4", "--page-size", "16"]
+    gold = str(tmp_path / "golden.json")
+    rep = json.loads(run("bench-interactive", "--turns", "2", "--prompt-len", "6", "--max-tokens", "5",
+                         "--write-golden", gold, *common))
+    assert rep["golden_written"] == gold
+    again = json.loads(run("bench-interactive", "--turns", "2", "--prompt-len", "6", "--max-tokens", "5",
+                           "--golden", gold, *common))
+    assert again["golden_match"] and again["golden"]["turns_compared"] == 2
+    # a golden trace that differs is reported with the first diverging position, exit code 2
+    g = json.load(open(gold))
+    g["turns"][1]["tokens"][2] = (g["turns"][1]["tokens"][2] + 1) % 1000
+    json.dump(g, open(gold, "w"))
+    p = subprocess.run([sys.executable, "-m", "ferrule_b200", "bench-interactive", "--turns", "2", "--prompt-len", "6",
+                        "--max-tokens", "5", "--golden", gold, *common], capture_output=True, text=True, timeout=300)
+    assert p.returncode == 2
+    bad = json.loads(p.stdout)
+    assert bad["golden"]["first_divergence"]["turn"] == 1 and bad["golden"]["first_divergence"]["index"] == 2
+    # prompt / token parity file
+    cases = str(tmp_path / "cases.json")
+    toks = rep["turns"][0]["tokens"]
+    first_prompt_run = json.loads(run("generate", "--tokens", "9,8,7", "--max-tokens", "4", *common))
+    json.dump({"cases": [{"prompt_tokens": [9, 8, 7], "expected_tokens": first_prompt_run["tokens"]}]}, open(cases, "w"))
+    par = json.loads(run("generation-parity", "--cases", cases, *common))
+    assert par["all_match"] and par["cases"][0]["generated"] == first_prompt_run["tokens"] and len(toks) == 5
+    sw = json.loads(run("chunk-sweep", "--chunks", "8", "32", "--requests", "2", "--prompt-len", "40", "--max-tokens", "3",
+                        *common))
+    assert [r["prefill_chunk"] for r in sw["sweep"]] == [8, 32]
+    assert sw["sweep"][0]["prefill_chunks"] > sw["sweep"][1]["prefill_chunks"]
