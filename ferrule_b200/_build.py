@@ -30,6 +30,7 @@ CUDA_SOURCES = [
     "gemm_mxfp4.cu",
     "mla_attention.cu",
     "elementwise.cu",
+    "data_movers.cu",
     "quant.cu",
     "v4_ops.cu",
     "ep_moe.cu",

@@ -227,6 +227,24 @@ int fb_router_append_q(const void* x, long long ldx, const void* delta, long lon
                        long long ldxg, const void* q_src, long long ldq, const void* s_src, long long lds, void* xg_q,
                        long long ldxgq, void* xg_s, long long ldxgs, int s_cols, void* status, void* stream);
 
+// ---- data movers (index fills, row copies; see data_movers.cu) ----------------------------------------
+int fb_mv_fill(int* dst, long long n, int start, int step, void* stream);
+int fb_mv_pack_pairs(const int* ids, const float* vals, int* out, int n, void* stream);
+// mode 0 window (positions), 1 offset list (idx [rows, ldi]), 2 counts (idx [rows]); base [rows] int64
+int fb_mv_index_fill(int* sel, long long lds, int col0, int rows, int width, int mode, const int* positions,
+                     const long long* base, const int* idx, long long ldi, void* stream);
+// idx null: dst[dst_row0 + r] = src[r]; else dst[dst_row0 + r] = src[idx[r]]; rows of row_bytes (multiple of 16)
+int fb_mv_move_rows(void* dst, long long ldd_bytes, long long dst_row0, const void* src, long long lds_bytes,
+                    const int* idx, int rows, int src_rows, int row_bytes, void* status, void* stream);
+int fb_mv_scatter_add(float* dst, long long ldd, int dst_rows, const float* src, long long lds, const int* idx,
+                      int rows, int dim, void* status, void* stream);
+int fb_mv_saxpy(float* y, const float* x, float a, long long n, void* stream);
+int fb_mv_ring_to_logical(const int* slots, long long lds, int rows, int width, int window, const int* last_position,
+                          const int* n_compressed, int* out_index, int* out_plane, long long ldo, void* stream);
+int fb_mv_paged_row_scatter(void* pool, long long pool_rows, int row_bytes, const int* block_table, int max_blocks,
+                            int num_seqs, int page_size, const int* row_seq, const int* positions, const void* src,
+                            long long lds_bytes, int rows, void* status, void* stream);
+
 // ---- quantisation / packing ---------------------------------------------------------------
 int fb_quant_fp8_rows(const void* x, long long ldx, void* q, long long ldq, void* scale, long long lds,
                       int rows, int n, int writeback_bf16, void* stream);

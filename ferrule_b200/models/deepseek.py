@@ -368,8 +368,9 @@ class CudaForward:
                  max_logit_rows: int = 256, decode_rows: int = 64, max_seq_len: int = 4096,
                  attn_splits: int = 8, tp=None):
         from ..ops import kernels as K
+        from ..ops import movers as M
         from ..ops import quant as Q
-        self.K, self.Q = K, Q
+        self.K, self.Q, self.M = K, Q, M
         self.w, self.cfg, self.pool, self.tp = weights, weights.cfg, pool, tp
         dev = weights.embed.device
         self.device = dev
@@ -746,9 +747,9 @@ class CudaForward:
         `ws.h[0][:T]` or is copied there."""
         ws = self.ws
         if h.data_ptr() != ws.h[0].data_ptr():
-            ws.h[0][:T].copy_(h)
+            self.M.copy_rows(ws.h[0], 0, h.contiguous())
         if ws.has_moe and ws.static_rows and T <= ws.static_rows[-1]:
-            ws.route_cnt.zero_()
+            self.M.fill_(ws.route_cnt, 0)
         h, other = ws.h[0][:T], ws.h[1][:T]
         layers = self.w.layers
         fused = False                     # the previous layer wrote this layer's normalised input
@@ -777,7 +778,7 @@ class CudaForward:
         K, cfg, ws, tp = self.K, self.cfg, self.ws, self.tp
         L = b.n_logit
         hl = ws.h_last[:L]
-        torch.index_select(h, 0, b.logit_rows[:L], out=hl)
+        self.M.gather_rows(h, b.logit_rows[:L], hl)
         K.add_rmsnorm(hl, final_norm, cfg.rms_eps, norm_out=ws.hn_last[:L])
         logits = ws.logits[:L]
         K.gemm(ws.hn_last[:L], self.w.lm_head if lm_head is None else lm_head, out=logits)
@@ -806,7 +807,7 @@ class CudaForward:
         H = cfg.hidden
         x = ws.mtp_x[:T]
         if ws.has_moe and ws.static_rows and T <= ws.static_rows[-1]:
-            ws.route_cnt[cfg.n_layers + stage].zero_()
+            self.M.fill_(ws.route_cnt[cfg.n_layers + stage], 0)
         # eh_proj input columns: [enorm(embedding) ; hnorm(previous hidden)], the order of published checkpoints
         K.add_rmsnorm(h_prev, m.hnorm, cfg.rms_eps, norm_out=x[:, H:])
         e = ws.h[1][:T]

@@ -192,6 +192,7 @@ class DeepSeekRunner(ModelRunner):
         self._txn_hidden: Dict[int, torch.Tensor] = {}
         self._txn_keep: Dict[int, Dict[int, int]] = {}
         self._mtp_staging: Optional[BatchStaging] = None
+        self._mtp_hidden: Optional[torch.Tensor] = None
         # asynchronous expert streaming: leases and the stop point of every parked transaction
         self._txn_leases: Dict[int, Dict[int, Dict[int, tuple]]] = {}
         self._txn_resume: Dict[int, tuple] = {}
@@ -393,7 +394,18 @@ class DeepSeekRunner(ModelRunner):
                 r += k
             self.stats.h2d_bytes += st.upload()
             db = st.device_batch(r, len(group))
-            h_prev = torch.cat(hs, 0) if len(hs) > 1 else hs[0]
+            if self.is_cuda and len(hs) > 1:
+                # rows of several published steps, packed by the row-copy kernel (no library launch on the path)
+                from ..ops import movers as M
+                if self._mtp_hidden is None:
+                    self._mtp_hidden = torch.zeros(self.max_rows, self.cfg.hidden, dtype=hs[0].dtype, device=self.device)
+                r0 = 0
+                for hpart in hs:
+                    M.copy_rows(self._mtp_hidden, r0, hpart.contiguous())
+                    r0 += hpart.shape[0]
+                h_prev = self._mtp_hidden[:r0]
+            else:
+                h_prev = torch.cat(hs, 0) if len(hs) > 1 else hs[0]
             if self.is_cuda:
                 ids, vals, _ = self.fwd.mtp_forward(0, h_prev, db)
                 ids_h, vals_h = ids.tolist(), vals.tolist()

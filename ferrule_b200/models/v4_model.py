@@ -367,8 +367,9 @@ class V4Cuda:
 
     def __init__(self, w: V4Weights, max_seqs: int, max_len: int):
         from ..ops import kernels as K
+        from ..ops import movers as M
         from ..ops import v4 as K4
-        self.K, self.K4 = K, K4
+        self.K, self.K4, self.M = K, K4, M
         self.w, self.cfg = w, w.cfg
         cfg = self.cfg
         dev = w.embed.device
@@ -433,7 +434,7 @@ class V4Cuda:
 
     def step(self, seqs: List[int], tokens: List[int]):
         """One decode step for the sequences in slots `seqs` -> (next token ids [B] int32, fp32 logits [B, vocab])."""
-        K, K4, cfg, w = self.K, self.K4, self.cfg, self.w
+        K, K4, M, cfg, w = self.K, self.K4, self.M, self.cfg, self.w
         dev = self.device
         B = len(seqs)
         hd, rd, nh, H, hc = cfg.head_dim, cfg.rope_dim, cfg.n_heads, cfg.hidden, cfg.hc_mult
@@ -459,8 +460,12 @@ class V4Cuda:
             ratio = cfg.ratio(i)
             stride = self.stride[i]
             base = seq_t * stride
-            wpos = pos_t.long()[:, None] - torch.arange(cfg.window - 1, -1, -1, device=dev)[None]      # [B, window]
-            sel = [torch.where(wpos >= 0, base[:, None] + wpos, torch.full_like(wpos, -1))]
+            # selection list [window | compressed rows], filled in place by the index-fill kernels
+            n_c = [(p + 1) // ratio for p in pos] if ratio else []
+            n_max = max(n_c) if n_c else 0
+            sel_w = cfg.window + ((min(cfg.index_topk, 512) if n_max else 0) if (ratio and cfg.has_indexer(i)) else n_max)
+            selection = torch.empty(B, sel_w, dtype=torch.int32, device=dev)
+            M.window_index_fill(selection, 0, cfg.window, pos_t, base)
             if ratio:
                 if cfg.has_indexer(i):
                     idim = cfg.index_head_dim
@@ -470,8 +475,6 @@ class V4Cuda:
                 for s, g, row in self._compress(i, self.proj[i], lw.c_wkv, lw.c_wgate, lw.c_ape, lw.c_norm, xn, seqs,
                                                 pos, ratio, cfg.has_indexer(i), hd, self.crope, rd):
                     table[s, self.max_len + g] = row
-                n_c = [(p + 1) // ratio for p in pos]
-                n_max = max(n_c)
                 if n_max:
                     if cfg.has_indexer(i):
                         idim, ih = cfg.index_head_dim, cfg.index_n_heads
@@ -485,12 +488,12 @@ class V4Cuda:
                                 K4.indexer_scores(iq[b:b + 1], self.iplane[i][s, :n_c[b]], wts[b:b + 1],
                                                   out=scores[b:b + 1, :n_c[b]])
                         vis = torch.tensor(n_c, dtype=torch.int32, device=dev)
-                        idx = K4.indexer_topk(scores, min(cfg.index_topk, 512), vis).long()
+                        idx = K4.indexer_topk(scores, min(cfg.index_topk, 512), vis)
+                        assert idx.shape[1] == sel_w - cfg.window
+                        M.offset_index_fill(selection, cfg.window, idx.int().contiguous(), base + self.max_len)
                     else:
-                        idx = torch.arange(n_max, device=dev)[None].expand(B, n_max)
-                        idx = torch.where(idx < torch.tensor(n_c, device=dev)[:, None], idx, torch.full_like(idx, -1))
-                    sel.append(torch.where(idx >= 0, base[:, None] + self.max_len + idx, torch.full_like(idx, -1)))
-            selection = torch.cat(sel, dim=1).int().contiguous()
+                        vis = torch.tensor(n_c, dtype=torch.int32, device=dev)
+                        M.count_index_fill(selection, cfg.window, n_max, vis, base + self.max_len)
             o = K4.sparse_sink_attention(q, table.view(-1, hd), selection, hd, 0, cfg.softmax_scale, sink=lw.sink)
             K4.rope_rows(o, pos_t, self.rope[0], self.rope[1], off=hd - rd, rdim=rd, inverse=True)
             lat = K.gemm(o.view(B, nh * hd), lw.wo_a, x_group_koff=cfg.group_in, out_group_coff=cfg.o_lora_rank)

@@ -41,6 +41,15 @@ def declare(lib) -> None:
         "fb_moe_reduce_norm": ([vp, i, i, vp, i, i, vp, ll, vp, ll, i, i, vp, vp, ll, f, vp], i),
         "fb_l2_prefetch": ([vp, ll, vp], i),
         "fb_decode_advance": ([vp, vp, vp, vp, vp, vp, vp, i, i, i, i, i, i, vp], i),
+        # data_movers.cu
+        "fb_mv_fill": ([vp, ll, i, i, vp], i),
+        "fb_mv_pack_pairs": ([vp, vp, vp, i, vp], i),
+        "fb_mv_index_fill": ([vp, ll, i, i, i, i, vp, vp, vp, ll, vp], i),
+        "fb_mv_move_rows": ([vp, ll, ll, vp, ll, vp, i, i, i, vp, vp], i),
+        "fb_mv_scatter_add": ([vp, ll, i, vp, ll, vp, i, i, vp, vp], i),
+        "fb_mv_saxpy": ([vp, vp, f, ll, vp], i),
+        "fb_mv_ring_to_logical": ([vp, ll, i, i, i, vp, vp, vp, vp, ll, vp], i),
+        "fb_mv_paged_row_scatter": ([vp, ll, i, vp, i, i, i, vp, vp, vp, ll, i, vp, vp], i),
         # quant.cu
         "fb_quant_fp8_rows": ([vp, ll, vp, ll, vp, ll, i, i, i, vp], i),
         "fb_dequant_fp8_block": ([vp, vp, vp, i, i, i, vp], i),
