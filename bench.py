@@ -111,6 +111,11 @@ def main() -> None:
     ap.add_argument("--ar-payload", default="bf16", choices=["fp32", "bf16"],
                     help="what the fused all-reduces push over NVLink: bf16 partials (default, as bf16 all-reduces do) or fp32")
     ap.add_argument("--no-fused", action="store_true", help="use the NCCL baseline collectives instead of fused kernels")
+    ap.add_argument("--collective", default="ll", choices=["ll", "multimem"],
+                    help="fused all-reduces: tagged peer pushes (ll) or reduce + broadcast inside the NVLink switch")
+    ap.add_argument("--moe", default="replicated", choices=["replicated", "dispatch"],
+                    help="N > 1: experts by id over replicated activations, or token-dispatch expert parallelism "
+                         "(every rank routes its slice of the tokens; dispatch / combine all-to-alls over peer memory)")
     args = ap.parse_args()
     if args.impl == "reference":
         reference_arm()
@@ -139,7 +144,8 @@ def main() -> None:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=dev)
         from ferrule_b200.parallel.tp import TensorParallel
-        tp = TensorParallel(rank, world, dev, fused=not args.no_fused, payload=args.ar_payload)
+        tp = TensorParallel(rank, world, dev, fused=not args.no_fused, payload=args.ar_payload,
+                            collective=args.collective)
 
     cfg = C.PRESETS[args.model]()
     if args.layers:
@@ -150,11 +156,17 @@ def main() -> None:
     max_seq = P + K + Wm + margin + 2 * page
     pages_per_seq = (max_seq + page - 1) // page
     weights = W.random_weights(cfg, device=dev, seed=0, tp_rank=rank, tp_world=args.shard_as or world, fast_device_init=True,
-                               weight_format=args.weight_format)
+                               weight_format=args.weight_format,
+                               replicate_shared=(world > 1 and args.moe == "dispatch"))
     runner = DeepSeekRunner(weights, n_pages=B * pages_per_seq + 8, page_size=page, max_rows=2048, max_seqs=B,
                             max_seq_len=pages_per_seq * page, device=dev, tp=tp)
     if tp is not None:
         tp.attach(runner.fwd)
+        if args.moe == "dispatch":
+            from ferrule_b200.parallel.ep import ExpertParallelMoE
+            ep = ExpertParallelMoE(rank, world, dev, cfg.hidden, cfg.moe_inter, cfg.topk, cfg.n_routed_experts,
+                                   max_local_tokens=(B + world - 1) // world, allgather=True)
+            runner.fwd.attach_ep(ep)
     sched = SchedulerConfig(max_active_sequences=B, max_decode_batch=B, max_batch_tokens=2048, prefill_chunk_size=512,
                             mixed_batches=True, ctx_size=pages_per_seq * page)
     engine = Engine(runner, EngineConfig(scheduler=sched, kv_pages=B * pages_per_seq + 8, page_size=page))
@@ -266,7 +278,7 @@ def main() -> None:
     if rank == 0:
         value = B * K / (dev_ms / 1e3)
         e2e_value = B * K / (e2e_ms / 1e3)
-        par = "tp%d" % world if world > 1 else "single-gpu"
+        par = "single-gpu" if world == 1 else ("tp%d" % world if args.moe == "replicated" else "tp%d-attention + ep%d-dispatch" % (world, world))
         line = {
             "metric": "decode tokens/s (whole job, max over ranks)",
             "value": round(value, 1), "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": Wm,
@@ -279,7 +291,9 @@ def main() -> None:
                        "parallelism": par, "kv_page_size": page, "layers": cfg.n_layers,
                        "l2_policy": "inputs larger than L2: each step streams %.1f GB of weights per GPU"
                                     % (weights.nbytes() / 1e9),
-                       "collectives": "none" if world == 1 else ("nccl" if args.no_fused else "fused-p2p, %s partials" % args.ar_payload)},
+                       "collectives": "none" if world == 1 else ("nccl" if args.no_fused else (
+                           "fused-p2p, %s partials" % args.ar_payload if args.collective == "ll"
+                           else "in-switch multimem reduce + broadcast (bf16)"))},
             "e2e": {"value": round(e2e_value, 1), "unit": "tokens/s", "ms_per_step": round(e2e_ms / K, 4),
                     "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h),
                     "path": "Engine.step (scheduler + KV transactions + pinned H2D + graph + D2H)"},

@@ -36,6 +36,7 @@ CUDA_SOURCES = [
     "ep_moe.cu",
     "expert_table.cu",
     "comm.cu",
+    "comm_mm.cu",
     "no_alloc.cu",
 ]
 CXX_SOURCES = [

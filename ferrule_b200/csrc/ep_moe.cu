@@ -148,7 +148,7 @@ ep_collect_kernel(uint32_t* ctr, int e_lo, int* __restrict__ r_idx, float* __res
 __global__ void __launch_bounds__(256)
 ep_combine_reduce_kernel(uint32_t* ctr, const __nv_bfloat16* __restrict__ extra, long long lde,
                          const __nv_bfloat16* __restrict__ residual, long long ldr, __nv_bfloat16* __restrict__ out,
-                         long long ldo, int tokens, int allgather, EpParams P) {
+                         long long ldo, int tokens, int allgather, int gather_row0, EpParams P) {
   pdl_launch_dependents();
   pdl_wait();
   __shared__ int s_ok;
@@ -192,7 +192,9 @@ ep_combine_reduce_kernel(uint32_t* ctr, const __nv_bfloat16* __restrict__ extra,
     const uint4 ov = *reinterpret_cast<const uint4*>(o);
     if (out) *reinterpret_cast<uint4*>(out + t * ldo + i) = ov;
     if (allgather) {
-      const size_t row = static_cast<size_t>(P.rank) * P.tcap + t;
+      // gathered rows: at this rank's fixed segment, or (gather_row0 >= 0) at the caller's offset, which lets the
+      // ranks' slices of a batch land back to back as one [tokens of all ranks, hidden] tensor
+      const size_t row = gather_row0 >= 0 ? static_cast<size_t>(gather_row0) + t : static_cast<size_t>(P.rank) * P.tcap + t;
       for (int pr = 0; pr < P.world; ++pr)
         *reinterpret_cast<uint4*>(P.base[pr] + P.off_gath_out + (row * P.hidden + i) * 2) = ov;
     }
@@ -287,15 +289,16 @@ extern "C" int fb_ep_collect(const FbEpArgs* a, void* ctr, int e_lo, int* r_idx,
 
 extern "C" int fb_ep_combine_reduce(const FbEpArgs* a, void* ctr, const void* extra, long long lde,
                                     const void* residual, long long ldr, void* out, long long ldo, int tokens,
-                                    int allgather, void* stream) {
+                                    int allgather, int gather_row0, void* stream) {
   EpParams P{};
   const int rc = fill(a, &P);
   if (rc != FB_OK) return rc;
   if (!ctr || tokens <= 0 || tokens > a->tcap || (!out && !allgather)) return FB_ERR_SHAPE;
+  if (gather_row0 >= 0 && gather_row0 + tokens > a->world * a->tcap) return FB_ERR_SHAPE;
   launch_pdl(ep_combine_reduce_kernel, dim3(tokens), dim3(256), 0, static_cast<cudaStream_t>(stream),
              static_cast<uint32_t*>(ctr), static_cast<const __nv_bfloat16*>(extra), lde,
              static_cast<const __nv_bfloat16*>(residual), ldr, static_cast<__nv_bfloat16*>(out), ldo, tokens,
-             allgather, P);
+             allgather, gather_row0, P);
   return FB_CHECK_LAUNCH();
 }
 

@@ -227,6 +227,18 @@ int fb_router_append_q(const void* x, long long ldx, const void* delta, long lon
                        long long ldxg, const void* q_src, long long ldq, const void* s_src, long long lds, void* xg_q,
                        long long ldxgq, void* xg_s, long long ldxgs, int s_cols, void* status, void* stream);
 
+// ---- collectives through the NVLink switch (multimem) ------------------------------------------------
+// mode 1 reduce-scatter (out = this rank's slice [ceil(rows/world), dim]), 2 all-gather (src = this rank's slice),
+// 3 all-reduce.  src: route rows [rows * slots, dim] (summed per token as in fb_moe_reduce; slots = 1, topk = 0: a
+// plain partial), or null when the partial already sits in the staging area of the current call parity.
+// local_base / mc_base: this rank's mapping and the multicast mapping of the channel's symmetric buffer
+// [flags (256 B) | stage x 2 | result x 2]; priv: 4 private uint32 (zeroed once).
+int fb_mm_collective(const void* src, long long lds, int slots, int topk, const int* topk_idx, int e_lo, int e_hi,
+                     const void* residual, long long ldr, void* out, long long ldo, int rows, int dim, int mode,
+                     const void* norm_w, void* norm_out, long long ldn, float eps, void* local_base, void* mc_base,
+                     long long stage_off, long long result_off, long long buf_bytes, void* priv, int rank, int world,
+                     unsigned long long wait_ns, void* status, void* stream);
+
 // ---- data movers (index fills, row copies; see data_movers.cu) ----------------------------------------
 int fb_mv_fill(int* dst, long long n, int start, int step, void* stream);
 int fb_mv_pack_pairs(const int* ids, const float* vals, int* out, int n, void* stream);
@@ -363,7 +375,7 @@ int fb_ep_dispatch(const FbEpArgs* a, const void* x, long long ldx, const int* i
 int fb_ep_collect(const FbEpArgs* a, void* ctr, int e_lo, int* r_idx, float* r_w, int* remap_rank, int* remap_row,
                   void* stream);
 int fb_ep_combine_reduce(const FbEpArgs* a, void* ctr, const void* extra, long long lde, const void* residual,
-                         long long ldr, void* out, long long ldo, int tokens, int allgather, void* stream);
+                         long long ldr, void* out, long long ldo, int tokens, int allgather, int gather_row0, void* stream);
 int fb_ep_gather_wait(const FbEpArgs* a, void* ctr, void* stream);
 
 // ---- peer memory and collectives --------------------------------------------------------

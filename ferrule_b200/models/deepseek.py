@@ -407,6 +407,9 @@ class CudaForward:
         self.fork_prep = os.environ.get("FERRULE_FORK_PREP", "1") != "0"
         self.prep_stream = torch.cuda.Stream(device=dev)
         self.async_stream = False  # streamed experts: stop at a layer with missing experts instead of uploading inline
+        # token-dispatch expert parallelism (parallel.ep.ExpertParallelMoE): MoE layers run on this rank's slice of
+        # the batch's tokens, routes travel to the experts' owners and back, the slices are gathered for the next layer
+        self.ep = None
         self.lease_sink = None     # dict layer -> leases of the running transaction (set by the runner)
 
     # -- sublayers -----------------------------------------------------------------------
@@ -664,6 +667,64 @@ class CudaForward:
             torch.cuda.current_stream().wait_stream(side)
         return idx
 
+    def attach_ep(self, ep) -> None:
+        """Use token-dispatch expert parallelism for the MoE layers of batches of world .. world * ep.tcap rows.
+        Needs bf16 experts, shared experts replicated on every rank (`random_weights(replicate_shared=True)`)."""
+        assert self.tp is not None and self.w.shared_replicated and ep.has_gather and ep.world == self.tp.world
+        self.ep = ep
+        R = ep.tcap
+        cfg = self.cfg
+        bf = dict(dtype=torch.bfloat16, device=self.device)
+        self.ep_ws = {"xn": torch.zeros(R, cfg.hidden, **bf), "extra": torch.zeros(R, cfg.hidden, **bf),
+                      "mid": torch.zeros(R, max(cfg.n_shared_experts * cfg.moe_inter, 8), **bf),
+                      "logits": torch.zeros(R, cfg.n_routed_experts, dtype=torch.float32, device=self.device),
+                      "idx": torch.zeros(R, cfg.topk, dtype=torch.int32, device=self.device),
+                      "wts": torch.zeros(R, cfg.topk, dtype=torch.float32, device=self.device),
+                      "out": torch.zeros(R, cfg.hidden, **bf)}
+
+    def _ep_rows(self, T: int):
+        """This rank's slice [lo, hi) of a batch of T rows (balanced, contiguous)."""
+        W, r = self.ep.world, self.ep.rank
+        base, rem = divmod(T, W)
+        lo = r * base + min(r, rem)
+        return lo, lo + base + (1 if r < rem else 0)
+
+    def _use_ep(self, lw: LayerWeights, T: int) -> bool:
+        return (self.ep is not None and lw.is_moe and self.ep.world <= T <= self.ep.world * self.ep.tcap
+                and not isinstance(lw.e_w13, QuantWeight) and lw.hash_table is None)
+
+    def _moe_dispatch(self, lw: LayerWeights, h_mid: torch.Tensor, b: DeviceBatch, T: int) -> torch.Tensor:
+        """MoE layer under token-dispatch expert parallelism -> the batch's new residual rows [T, hidden] (a view
+        of the gather buffer every rank's combine kernel pushed its slice into)."""
+        K, cfg, ep, ws = self.K, self.cfg, self.ep, self.ep_ws
+        lo, hi = self._ep_rows(T)
+        n = hi - lo
+        hs = h_mid[lo:hi]
+        xn = ws["xn"][:n]
+        K.add_rmsnorm(hs, lw.ffn_norm, cfg.rms_eps, norm_out=xn)
+        extra = None
+        side = None
+        if lw.w13 is not None:
+            side, main = self.side_stream, torch.cuda.current_stream()
+            side.wait_stream(main)
+            with torch.cuda.stream(side):
+                inter = lw.w13.shape[1] // 2
+                mid = ws["mid"][:n, :inter]
+                K.gemm(xn, lw.w13, out=mid, epilogue=K.EPI_SWIGLU, act_limit=cfg.swiglu_limit)
+                extra = ws["extra"][:n]
+                K.gemm(mid, lw.w2, out=extra)
+        logits = ws["logits"][:n]
+        K.gemm(xn, lw.router_w, out=logits)
+        idx, wts = ws["idx"][:n], ws["wts"][:n]
+        K.router_topk(logits, cfg.topk, cfg.score_fn, bias=lw.router_bias, n_groups=cfg.n_groups,
+                      topk_groups=cfg.topk_groups, normalize=cfg.norm_topk_prob, route_scale=cfg.route_scale,
+                      out_idx=idx, out_w=wts)
+        if side is not None:
+            torch.cuda.current_stream().wait_stream(side)
+        _, gathered = ep.forward(xn, idx, wts, lw.e_w13, lw.e_w2, residual=hs, extra=extra, out=ws["out"][:n],
+                                 act_limit=cfg.swiglu_limit, allgather=True, gather_row0=lo)
+        return gathered.view(-1, cfg.hidden)[:T]
+
     def layer(self, lw: LayerWeights, layer: int, h_in: torch.Tensor, h_out: torch.Tensor, b: DeviceBatch,
               T: int, first_norm_done: bool = False, next_norm: Optional[torch.Tensor] = None) -> torch.Tensor:
         """h_in -> h_out (both bf16 [T, H]); returns h_out."""
@@ -686,7 +747,8 @@ class CudaForward:
         a = self._attention(lw, layer, xn, b, T)
         # decode-sized MoE layers: the post-attention residual add + RMSNorm runs in the router kernel's prologue
         route_norm = None
-        fuse_route = (self.fuse_router_norm and lw.is_moe and self._static_rows(lw, T, layer) > 0
+        use_ep = self._use_ep(lw, T)
+        fuse_route = (not use_ep and self.fuse_router_norm and lw.is_moe and self._static_rows(lw, T, layer) > 0
                       and not isinstance(lw.w13, QuantWeight) and not isinstance(lw.e_w13, QuantWeight))
         if tp is None:
             self._gemm(a, lw.w_o, ws.delta[:T], slot="a")
@@ -703,9 +765,12 @@ class CudaForward:
                 tp.gemm_allreduce(a, lw.w_o, residual=h_in, out=h_out, T=T)
             if fuse_route:
                 route_norm = (h_out, None, None)
-            else:
+            elif not use_ep:
                 K.add_rmsnorm(h_out, lw.ffn_norm, cfg.rms_eps, norm_out=xn)
             h_mid = h_out
+        if use_ep:
+            # the layer's result is the gathered tensor itself (symmetric memory the peers' combine kernels wrote)
+            return self._moe_dispatch(lw, h_mid, b, T)
         if lw.is_moe:
             idx = self._moe_local(lw, xn, b, T, layer, norm=route_norm)
             # slot `topk` holds the shared-expert row (zeros when the model has none)

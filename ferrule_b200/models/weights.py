@@ -226,6 +226,7 @@ class ModelWeights:
     weight_format: str = "bf16"
     act_quant: bool = False       # oracle only: emulate the 1 x 128 FP8 activation quantisation of the FP8 path
     expert_act_block: int = 128   # oracle only: scale-block width of the routed experts' activation quantisation
+    shared_replicated: bool = False   # shared experts hold their full inner dimension on every rank (token-dispatch EP)
 
     @property
     def heads_local(self) -> int:
@@ -284,7 +285,7 @@ class _Init:
 
 
 def _layer_random(cfg: ModelConfig, layer: int, init: _Init, tp_rank: int, tp_world: int,
-                  force_moe: Optional[bool] = None) -> LayerWeights:
+                  force_moe: Optional[bool] = None, replicate_shared: bool = False) -> LayerWeights:
     H = cfg.hidden
     h_lo, h_hi = _shard_range(cfg.n_heads, tp_rank, tp_world)
     hl = h_hi - h_lo
@@ -313,8 +314,8 @@ def _layer_random(cfg: ModelConfig, layer: int, init: _Init, tp_rank: int, tp_wo
     is_moe = cfg.is_moe_layer(layer) if force_moe is None else force_moe
     lw.is_moe = is_moe
 
-    def ffn(inter: int):
-        i_lo, i_hi = _shard_range(inter, tp_rank, tp_world)
+    def ffn(inter: int, replicated: bool = False):
+        i_lo, i_hi = (0, inter) if replicated else _shard_range(inter, tp_rank, tp_world)
         gate, up, down = init.normal(inter, H), init.normal(inter, H), init.normal(H, inter)
         w13 = torch.cat([gate[i_lo:i_hi], up[i_lo:i_hi]], dim=0).unsqueeze(0).contiguous()
         w2 = down[:, i_lo:i_hi].unsqueeze(0).contiguous()
@@ -343,13 +344,14 @@ def _layer_random(cfg: ModelConfig, layer: int, init: _Init, tp_rank: int, tp_wo
     lw.e_w13 = torch.stack(w13s).contiguous()
     lw.e_w2 = torch.stack(w2s).contiguous()
     if cfg.n_shared_experts:
-        lw.w13, lw.w2 = ffn(cfg.n_shared_experts * I)
+        # token-dispatch expert parallelism runs the shared experts on each rank's own token slice: full weights
+        lw.w13, lw.w2 = ffn(cfg.n_shared_experts * I, replicated=replicate_shared)
     return lw
 
 
 def random_weights(cfg: ModelConfig, device="cpu", dtype=torch.bfloat16, seed: int = 0, std: float = 0.02,
                    tp_rank: int = 0, tp_world: int = 1, fast_device_init: bool = False,
-                   weight_format: str = "bf16") -> ModelWeights:
+                   weight_format: str = "bf16", replicate_shared: bool = False) -> ModelWeights:
     """Random-init weights N(0, std), norms = 1.
 
     fast_device_init draws on the GPU (much faster for multi-GB models; values then differ
@@ -358,8 +360,8 @@ def random_weights(cfg: ModelConfig, device="cpu", dtype=torch.bfloat16, seed: i
     init = _Init(seed, std, device, dtype, fast_device_init)
     embed = init.normal(cfg.vocab_size, cfg.hidden)
     # quantise layer by layer so that at most one layer exists in bf16 at a time
-    layers = [quantize_layer_(_layer_random(cfg, i, init, tp_rank, tp_world), weight_format)
-              for i in range(cfg.n_layers)]
+    layers = [quantize_layer_(_layer_random(cfg, i, init, tp_rank, tp_world, replicate_shared=replicate_shared),
+                              weight_format) for i in range(cfg.n_layers)]
     v_lo, v_hi = _shard_range(cfg.vocab_size, tp_rank, tp_world)
     lm_head = init.normal(cfg.vocab_size, cfg.hidden)[v_lo:v_hi].contiguous()
     mtp = []
@@ -367,9 +369,12 @@ def random_weights(cfg: ModelConfig, device="cpu", dtype=torch.bfloat16, seed: i
         mtp.append(MtpWeights(enorm=init.ones(cfg.hidden), hnorm=init.ones(cfg.hidden),
                               eh_proj=init.normal(cfg.hidden, 2 * cfg.hidden),
                               layer=quantize_layer_(_layer_random(cfg, cfg.n_layers + m, init, tp_rank, tp_world,
-                                                                  force_moe=cfg.n_routed_experts > 0),
+                                                                  force_moe=cfg.n_routed_experts > 0,
+                                                                  replicate_shared=replicate_shared),
                                                     weight_format),
                               final_norm=init.ones(cfg.hidden)))
     e_lo, e_hi = _shard_range(cfg.n_routed_experts, tp_rank, tp_world) if cfg.n_routed_experts else (0, 0)
-    return ModelWeights(cfg, embed, layers, init.ones(cfg.hidden), lm_head, mtp, tp_rank, tp_world,
-                        e_lo, e_hi, v_lo, weight_format=weight_format)
+    w = ModelWeights(cfg, embed, layers, init.ones(cfg.hidden), lm_head, mtp, tp_rank, tp_world,
+                     e_lo, e_hi, v_lo, weight_format=weight_format)
+    w.shared_replicated = bool(replicate_shared and tp_world > 1)
+    return w

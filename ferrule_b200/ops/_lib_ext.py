@@ -41,6 +41,9 @@ def declare(lib) -> None:
         "fb_moe_reduce_norm": ([vp, i, i, vp, i, i, vp, ll, vp, ll, i, i, vp, vp, ll, f, vp], i),
         "fb_l2_prefetch": ([vp, ll, vp], i),
         "fb_decode_advance": ([vp, vp, vp, vp, vp, vp, vp, i, i, i, i, i, i, vp], i),
+        # comm_mm.cu
+        "fb_mm_collective": ([vp, ll, i, i, vp, i, i, vp, ll, vp, ll, i, i, i, vp, vp, ll, f, vp, vp, ll, ll, ll, vp, i, i,
+                              ull, vp, vp], i),
         # data_movers.cu
         "fb_mv_fill": ([vp, ll, i, i, vp], i),
         "fb_mv_pack_pairs": ([vp, vp, vp, i, vp], i),

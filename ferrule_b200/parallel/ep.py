@@ -81,7 +81,7 @@ class ExpertParallelMoE:
                                               C.c_void_p, C.c_void_p]),
                            ("fb_ep_combine_reduce", [C.POINTER(EpArgs), C.c_void_p, C.c_void_p, C.c_longlong, C.c_void_p,
                                                      C.c_longlong, C.c_void_p, C.c_longlong, C.c_int, C.c_int,
-                                                     C.c_void_p]),
+                                                     C.c_int, C.c_void_p]),
                            ("fb_ep_gather_wait", [C.POINTER(EpArgs), C.c_void_p, C.c_void_p])):
             fn = getattr(lib, name)
             fn.argtypes, fn.restype = args, C.c_int
@@ -120,10 +120,12 @@ class ExpertParallelMoE:
     # ------------------------------------------------------------------ fused
     def forward(self, x: torch.Tensor, idx: torch.Tensor, wts: torch.Tensor, e_w13: torch.Tensor, e_w2: torch.Tensor,
                 residual: Optional[torch.Tensor] = None, extra: Optional[torch.Tensor] = None,
-                out: Optional[torch.Tensor] = None, act_limit: float = 0.0, allgather: bool = False):
+                out: Optional[torch.Tensor] = None, act_limit: float = 0.0, allgather: bool = False,
+                gather_row0: int = -1):
         """x bf16 [T, H] (this rank's tokens), idx int32 [T, k] global expert ids, wts fp32 [T, k].
         Returns out bf16 [T, H] = residual + extra + sum_k w * expert(x); with `allgather` also the
-        [world, tcap, H] buffer holding every rank's rows."""
+        [world, tcap, H] buffer holding every rank's rows (`gather_row0` >= 0: this rank's rows go to rows
+        gather_row0 ... of the flat [world * tcap, H] buffer instead, so that slices of a batch line up)."""
         T = x.shape[0]
         assert T <= self.tcap and idx.shape == (T, self.k) and idx.dtype == torch.int32
         if out is None:
@@ -150,7 +152,7 @@ class ExpertParallelMoE:
         check(lib.fb_ep_combine_reduce(C.byref(a), self.ctr_red.data_ptr(), ptr(extra),
                                        extra.stride(0) if extra is not None else 0, ptr(residual),
                                        residual.stride(0) if residual is not None else 0, out.data_ptr(),
-                                       out.stride(0), T, ag, sp), "fb_ep_combine_reduce")
+                                       out.stride(0), T, ag, gather_row0 if ag else -1, sp), "fb_ep_combine_reduce")
         if ag:
             check(lib.fb_ep_gather_wait(C.byref(a), self.ctr_gath.data_ptr(), sp), "fb_ep_gather_wait")
             return out, _wrap_device_pointer(self._gath_ptr, (self.world, self.tcap, self.H), torch.bfloat16,

@@ -83,3 +83,60 @@ class Channel:
 
     def close(self) -> None:
         self.buf.close()
+
+
+class McChannel:
+    """One symmetric buffer bound to an NVLink multicast object (NVLS), for the `multimem` collectives of
+    `csrc/comm_mm.cu`: [flags 256 B | stage x 2 | result x 2], each area `rows_cap x dim` bf16.
+
+    Allocation, handle exchange and the multicast binding are done by `torch.distributed._symmetric_memory`
+    (plumbing); the kernels that reduce and broadcast through the switch are this library's own.  All call sites
+    of a model share one channel: their calls are strictly ordered on every rank.  `available()` tells whether
+    the node offers multicast at all (NVSwitch + driver support)."""
+
+    def __init__(self, rank: int, world: int, device, rows_cap: int, dim: int, group=None,
+                 wait_ns: int = 3_000_000_000):
+        import torch.distributed._symmetric_memory as symm_mem
+        self.rank, self.world, self.wait_ns = rank, world, wait_ns
+        self.rows_cap, self.dim = rows_cap, dim
+        self.buf_bytes = (rows_cap * dim * 2 + 255) // 256 * 256
+        self.flag_bytes = 256
+        total = self.flag_bytes + 4 * self.buf_bytes
+        self.t = symm_mem.empty(total, dtype=torch.uint8, device=device)
+        self.t.zero_()
+        torch.cuda.synchronize(device)
+        grp = group if group is not None else dist.group.WORLD
+        try:
+            self.hdl = symm_mem.rendezvous(self.t, grp)
+        except Exception:  # noqa: BLE001 - older call convention: the group has to be enabled by name first
+            symm_mem.enable_symm_mem_for_group(grp.group_name)
+            self.hdl = symm_mem.rendezvous(self.t, grp.group_name)
+        self.mc_ptr = int(self.hdl.multicast_ptr or 0)
+        if not self.mc_ptr:
+            raise RuntimeError("this node offers no NVLink multicast (NVLS): multimem collectives are unavailable")
+        self.local_ptr = self.t.data_ptr()
+        self.stage_off = self.flag_bytes
+        self.result_off = self.flag_bytes + 2 * self.buf_bytes
+        self.priv = torch.zeros(4, dtype=torch.int32, device=device)
+        dist.barrier(group=group)
+
+    def collective(self, mode: int, out: torch.Tensor, rows: int, src: Optional[torch.Tensor] = None, slots: int = 1,
+                   topk: int = 0, topk_idx: Optional[torch.Tensor] = None, e_lo: int = 0, e_hi: int = 0,
+                   residual: Optional[torch.Tensor] = None, norm_w: Optional[torch.Tensor] = None,
+                   norm_out: Optional[torch.Tensor] = None, eps: float = 0.0) -> torch.Tensor:
+        """mode 1 reduce-scatter, 2 all-gather, 3 all-reduce (see `fb_mm_collective`)."""
+        from ..ops._lib import ptr, status_tensor, stream_ptr
+        lib = get_lib(True)
+        check(lib.fb_mm_collective(ptr(src), src.stride(0) if src is not None else 0, slots, topk, ptr(topk_idx), e_lo,
+                                   e_hi, ptr(residual), residual.stride(0) if residual is not None else 0,
+                                   out.data_ptr(), out.stride(0), rows, self.dim, mode, ptr(norm_w), ptr(norm_out),
+                                   norm_out.stride(0) if norm_out is not None else 0, eps, self.local_ptr, self.mc_ptr,
+                                   self.stage_off, self.result_off, self.buf_bytes, self.priv.data_ptr(), self.rank,
+                                   self.world, self.wait_ns, status_tensor(out.device).data_ptr(), stream_ptr()),
+              "fb_mm_collective")
+        return out
+
+    def close(self) -> None:
+        self.hdl = None
+        self.t = None
+

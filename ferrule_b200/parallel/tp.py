@@ -32,7 +32,7 @@ from .symm import Channel
 
 class TensorParallel:
     def __init__(self, rank: int, world: int, device, fused: bool = True, fused_max_rows: int = 64,
-                 group=None, wait_ns: int = 3_000_000_000, payload: str = "fp32"):
+                 group=None, wait_ns: int = 3_000_000_000, payload: str = "fp32", collective: str = "ll"):
         self.rank, self.world, self.device, self.group = rank, world, torch.device(device), group
         self.fused = fused and self.device.type == "cuda"
         self.fused_max_rows = fused_max_rows
@@ -41,6 +41,12 @@ class TensorParallel:
         assert payload in ("fp32", "bf16")
         self.payload_bf16 = 1 if payload == "bf16" else 0
         self.wait_ns = wait_ns
+        # "ll": tagged peer pushes, every rank sums in rank order (works on any peer-mapped memory);
+        # "multimem": two-shot reduce + broadcast inside the NVLink switch (needs NVLS; rows up to mm_max_rows)
+        assert collective in ("ll", "multimem")
+        self.collective = collective
+        self.mm = None
+        self.mm_max_rows = 512
         self.gemm_ch: Optional[Channel] = None
         self.moe_ch: Optional[Channel] = None
         self.arg_ch: Optional[Channel] = None
@@ -59,6 +65,10 @@ class TensorParallel:
         self._pairs = torch.zeros(self.world, fwd.ws.max_logit_rows, 2, dtype=torch.float32, device=self.device)
         if not self.fused:
             return
+        if self.collective == "multimem":
+            from .symm import McChannel
+            self.mm = McChannel(self.rank, self.world, self.device, self.mm_max_rows, H, self.group, self.wait_ns)
+            self._partial = torch.zeros(self.mm_max_rows, H, dtype=torch.bfloat16, device=self.device)
         n_tiles = (H + 127) // 128
         self.gemm_ch = Channel(self.rank, self.world, self.device, rows * H, n_tiles * ((rows + 15) // 16),
                                self.group, self.wait_ns)
@@ -67,7 +77,7 @@ class TensorParallel:
                               self.wait_ns)
 
     def close(self) -> None:
-        for ch in (self.gemm_ch, self.moe_ch, self.arg_ch):
+        for ch in (self.gemm_ch, self.moe_ch, self.arg_ch, self.mm):
             if ch is not None:
                 ch.close()
 
@@ -85,6 +95,12 @@ class TensorParallel:
     def gemm_allreduce(self, x: torch.Tensor, w: torch.Tensor, residual: torch.Tensor, out: torch.Tensor,
                        T: int) -> torch.Tensor:
         """out = bf16(residual + sum over ranks of x @ w^T)."""
+        if self.mm is not None and T <= self.mm_max_rows and w.shape[-2] == self.hidden:
+            # the GEMM leaves this rank's partial in local memory, the switch reduces and broadcasts it
+            K.gemm(x, w, out=self._partial[:T])
+            self.mm.collective(3, out, T, src=self._partial[:T], residual=residual)
+            self.calls_fused += 1
+            return out
         if self.fused and T <= self.fused_max_rows and w.shape[-2] == self.hidden:
             K.gemm(x, w, out=out, epilogue=K.EPI_ALLREDUCE, comm=self, residual=residual, ntok=K.pick_ntok(T))
             self.calls_fused += 1
@@ -100,6 +116,11 @@ class TensorParallel:
     def moe_reduce_allreduce(self, route_out: torch.Tensor, slots: int, topk: int, idx: torch.Tensor,
                              e_lo: int, e_hi: int, residual: torch.Tensor, out: torch.Tensor, T: int) -> torch.Tensor:
         H = self.hidden
+        if self.mm is not None and T <= self.mm_max_rows:
+            self.mm.collective(3, out, T, src=route_out, slots=slots, topk=topk, topk_idx=idx, e_lo=e_lo, e_hi=e_hi,
+                               residual=residual)
+            self.calls_fused += 1
+            return out
         if self.fused and T <= self.fused_max_rows:
             ch = self.moe_ch
             lib = get_lib(True)
@@ -116,6 +137,40 @@ class TensorParallel:
         dist.all_reduce(tmp, group=self.group)
         torch.add(tmp, residual, out=tmp)
         out.copy_(tmp)
+        self.calls_nccl += 1
+        return out
+
+    def reduce_scatter(self, partial: torch.Tensor, out_slice: torch.Tensor, T: int,
+                       residual_slice: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """out_slice [ceil(T / world), hidden] = this rank's rows of the sum over ranks of `partial` [T, hidden]
+        (+ residual_slice): rows are owned in contiguous slices.  In-switch reduction; NCCL otherwise."""
+        per = (T + self.world - 1) // self.world
+        if self.mm is not None and T <= self.mm_max_rows:
+            self.mm.collective(1, out_slice, T, src=partial, residual=residual_slice)
+            self.calls_fused += 1
+            return out_slice
+        pad = torch.zeros(per * self.world, partial.shape[1], dtype=torch.float32, device=partial.device)
+        pad[:T] = partial.float()
+        o = torch.empty(per, partial.shape[1], dtype=torch.float32, device=partial.device)
+        dist.reduce_scatter_tensor(o, pad, group=self.group)
+        if residual_slice is not None:
+            o[:residual_slice.shape[0]] += residual_slice.float()
+        out_slice.copy_(o[:out_slice.shape[0]])
+        self.calls_nccl += 1
+        return out_slice
+
+    def all_gather(self, slice_rows: torch.Tensor, out: torch.Tensor, T: int) -> torch.Tensor:
+        """out [T, hidden] = the ranks' row slices (ceil(T / world) rows each, the last ones possibly short)."""
+        per = (T + self.world - 1) // self.world
+        if self.mm is not None and T <= self.mm_max_rows:
+            self.mm.collective(2, out, T, src=slice_rows)
+            self.calls_fused += 1
+            return out
+        mine = torch.zeros(per, out.shape[1], dtype=out.dtype, device=out.device)
+        mine[:slice_rows.shape[0]] = slice_rows
+        full = torch.empty(per * self.world, out.shape[1], dtype=out.dtype, device=out.device)
+        dist.all_gather_into_tensor(full, mine, group=self.group)
+        out.copy_(full[:T])
         self.calls_nccl += 1
         return out
 

@@ -75,6 +75,9 @@ def main() -> int:
     ap.add_argument("--bench", action="store_true")
     ap.add_argument("--rows", type=int, default=32)
     ap.add_argument("--payload", default="fp32", choices=["fp32", "bf16"])
+    ap.add_argument("--collective", default="ll", choices=["ll", "multimem"])
+    ap.add_argument("--bench-hidden", type=int, default=2048)
+    ap.add_argument("--bench-rows", type=int, default=32)
     args = ap.parse_args()
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     local = int(os.environ.get("LOCAL_RANK", rank))
@@ -95,7 +98,7 @@ def main() -> int:
     H = cfg.hidden
     w_tp = W.random_weights(cfg, device=dev, seed=3, std=0.05, tp_rank=rank, tp_world=world)
     pool = D.KvPool(cfg, 32, 64, dev)
-    tp = TensorParallel(rank, world, dev, fused=True, payload=args.payload)
+    tp = TensorParallel(rank, world, dev, fused=True, payload=args.payload, collective=args.collective)
     fwd = D.CudaForward(w_tp, pool, max_rows=256, max_logit_rows=8, decode_rows=64, max_seq_len=512, attn_splits=2, tp=tp)
     tp.attach(fwd)
     tp_nccl = TensorParallel(rank, world, dev, fused=False)
@@ -119,7 +122,40 @@ def main() -> int:
         worst = max(worst, float((out_f.float() - out_n.float()).abs().max()))
         scale = float(out_n.float().abs().max())
     res["checks"]["gemm_allreduce_max_err"] = worst
-    ok &= worst <= (0.03 if args.payload == "bf16" else 0.02) * scale + 1e-2
+    ok &= worst <= (0.03 if (args.payload == "bf16" or args.collective == "multimem") else 0.02) * scale + 1e-2
+
+    # 1b. reduce-scatter and all-gather (contiguous row slices; a row count the world size does not divide)
+    for Tr in (T, 13):
+        per = (Tr + world - 1) // world
+        lo, hi = min(Tr, rank * per), min(Tr, rank * per + per)
+        part = rnd(Tr, H, seed=300 + rank + Tr)
+        resid = rnd(Tr, H, seed=31 + Tr)
+        want = part.float().clone()
+        dist.all_reduce(want)
+        want = want + resid.float()
+        mine = torch.zeros(per, H, dtype=torch.bfloat16, device=dev)
+        tp.reduce_scatter(part, mine, Tr, residual_slice=resid[lo:hi])
+        torch.cuda.synchronize()
+        e = float((mine[:hi - lo].float() - want[lo:hi]).abs().max()) if hi > lo else 0.0
+        res["checks"][f"reduce_scatter_{Tr}_err"] = e
+        ok &= e <= 0.03 * float(want.abs().max()) + 1e-2
+        full = torch.zeros(Tr, H, dtype=torch.bfloat16, device=dev)
+        tp.all_gather(mine[:hi - lo], full, Tr)
+        torch.cuda.synchronize()
+        ref_full = full.clone()
+        dist.broadcast(ref_full, 0)
+        same = torch.equal(full, ref_full)                       # every rank holds the same bits
+        e2 = float((full.float() - want).abs().max())
+        res["checks"][f"all_gather_{Tr}_err"] = e2
+        ok &= same and e2 <= 0.03 * float(want.abs().max()) + 1e-2
+    if args.collective == "multimem":
+        # an all-reduce through the switch gives every rank the owner's bits
+        o_a = torch.zeros(T, H, dtype=torch.bfloat16, device=dev)
+        tp.add_allreduce(rnd(T, H, seed=500 + rank), rnd(T, H, seed=9), o_a, T)
+        o_0 = o_a.clone()
+        dist.broadcast(o_0, 0)
+        res["checks"]["allreduce_bits_equal_across_ranks"] = bool(torch.equal(o_a, o_0))
+        ok &= torch.equal(o_a, o_0)
 
     # 2. MoE reduce + all-reduce
     slots, topk = 5, 4
@@ -197,12 +233,58 @@ def main() -> int:
         new = [1, 1, 1]
     res["checks"]["model_tokens_match"] = worst_tok
     ok &= worst_tok
+
+    # 5. the same model with token-dispatch expert parallelism in its MoE layers (tensor-parallel attention, every
+    # rank routes its own slice of the tokens, shared experts replicated) against the single-GPU forward
+    from ferrule_b200.parallel.ep import ExpertParallelMoE
+    w_ep = W.random_weights(cfg, device=dev, seed=3, std=0.05, tp_rank=rank, tp_world=world, replicate_shared=True)
+    pool_ep = D.KvPool(cfg, 32, 64, dev)
+    fwd_ep = D.CudaForward(w_ep, pool_ep, max_rows=256, max_logit_rows=8, decode_rows=64, max_seq_len=512,
+                           attn_splits=2, tp=tp)
+    ep = ExpertParallelMoE(rank, world, dev, cfg.hidden, cfg.moe_inter, cfg.topk, cfg.n_routed_experts,
+                           max_local_tokens=(72 + world - 1) // world, allgather=True)
+    fwd_ep.attach_ep(ep)
+    pool1.data.zero_()
+    lens, new = [0, 0, 0], [40, 9, 23]
+    ep_tok = True
+    for step in range(3):
+        ids_l, pos, slot, rseq, lrows = [], [], [], [], []
+        bt = torch.zeros(3, 8, dtype=torch.int32)
+        for s_ in range(3):
+            bt[s_] = torch.arange(1 + 8 * s_, 9 + 8 * s_)
+        gg = torch.Generator().manual_seed(50 + step)
+        for s_, (n0, nn) in enumerate(zip(lens, new)):
+            for j in range(nn):
+                p_ = n0 + j
+                ids_l.append(int(torch.randint(0, cfg.vocab_size, (1,), generator=gg)))
+                pos.append(p_)
+                slot.append(int(bt[s_, p_ // 64]) * 64 + p_ % 64)
+                rseq.append(s_)
+            lrows.append(len(ids_l) - 1)
+        mk = lambda v, dt: torch.tensor(v, dtype=dt, device=dev)
+        b = D.DeviceBatch(mk(ids_l, torch.int32), mk(pos, torch.int32), mk(slot, torch.int64), mk(rseq, torch.int32),
+                          mk(pos, torch.int32), bt.to(dev), mk(lrows, torch.int32), len(ids_l), 3)
+        id_e, val_e, _ = fwd_ep.forward(b)
+        id_e, val_e = id_e.clone(), val_e.clone()
+        id_1, val_1, lg = fwd1.forward(b, want_logits=True)
+        torch.cuda.synchronize()
+        top2 = lg.topk(2, dim=-1).values
+        err = (val_e - val_1).abs()
+        clear = (top2[:, 0] - top2[:, 1]) > 4 * err.max() + 1e-3
+        ep_tok &= bool(torch.equal(id_e[clear].cpu(), id_1[clear].cpu()))
+        ok &= float(err.max()) <= 0.05 * float(lg.abs().max()) + 1e-2
+        res["checks"][f"ep_model_step{step}_val_err"] = float(err.max())
+        lens = [l + n for l, n in zip(lens, new)]
+        new = [1, 1, 1]
+    res["checks"]["ep_model_tokens_match"] = ep_tok
+    res["checks"]["ep_calls"] = ep.calls
+    ok &= ep_tok and (ep.calls > 0 or world > 3)
     res["fused_calls"] = tp.calls_fused
     res["nccl_calls_in_fused_mode"] = tp.calls_nccl
 
     if args.bench:
-        Hb, Tb = 2048, 32
-        tpb = TensorParallel(rank, world, dev, fused=True, payload=args.payload)
+        Hb, Tb = args.bench_hidden, args.bench_rows
+        tpb = TensorParallel(rank, world, dev, fused=True, payload=args.payload, collective=args.collective)
 
         class _F:  # minimal stand-in carrying the sizes attach() needs
             pass
@@ -232,6 +314,13 @@ def main() -> int:
         res["bench"]["gemm_allreduce_fused_graph_us"] = _graph_time_us(lambda: tpb.gemm_allreduce(x, wt, resid, o, Tb), world)
         res["bench"]["moe_allreduce_fused_graph_us"] = _graph_time_us(
             lambda: tpb.moe_reduce_allreduce(ro, 7, 6, idx, 0, 64 // world, resid, o, Tb), world)
+        per = (Tb + world - 1) // world
+        sl = torch.zeros(per, Hb, dtype=torch.bfloat16, device=dev)
+        part = rnd(Tb, Hb, seed=6)
+        res["bench"]["reduce_scatter_graph_us"] = _graph_time_us(lambda: tpb.reduce_scatter(part, sl, Tb), world) \
+            if args.collective == "multimem" else None
+        res["bench"]["all_gather_graph_us"] = _graph_time_us(lambda: tpb.all_gather(sl, o, Tb), world) \
+            if args.collective == "multimem" else None
         dl = torch.zeros(Tb, Hb, dtype=torch.bfloat16, device=dev)
         res["bench"]["gemm_local_graph_us"] = _graph_time_us(lambda: K.gemm(x, wt, out=dl), world)
         res["bench"]["moe_reduce_local_graph_us"] = _graph_time_us(

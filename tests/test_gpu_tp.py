@@ -37,3 +37,21 @@ def test_expert_parallel_dispatch_combine_two_ranks():
     assert res["ok"], res
     assert p.returncode == 0
     assert res["device_status"][0] == 0
+
+
+def test_selftest_two_ranks_in_switch_collectives():
+    """The same checks with the all-reduces, reduce-scatter and all-gather running through the NVLink switch
+    (multimem); skipped when the node offers no multicast."""
+    env = dict(os.environ, PYTHONPATH=ROOT)
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
+           "--master-addr", "127.0.0.1", "--master-port", "29521", os.path.join(ROOT, "tests", "dist", "tp_selftest.py"),
+           "--collective", "multimem", "--payload", "bf16"]
+    p = subprocess.run(cmd, capture_output=True, text=True, timeout=600, cwd=ROOT, env=env)
+    if "offers no NVLink multicast" in p.stderr + p.stdout:
+        pytest.skip("no NVLS on this node")
+    lines = [l for l in p.stdout.splitlines() if l.startswith("{")]
+    assert lines, p.stdout[-2000:] + p.stderr[-4000:]
+    res = json.loads(lines[-1])
+    assert res["ok"], res
+    assert res["checks"]["allreduce_bits_equal_across_ranks"] and res["checks"]["ep_model_tokens_match"]
+
