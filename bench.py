@@ -111,6 +111,8 @@ def main() -> None:
     ap.add_argument("--ar-payload", default="bf16", choices=["fp32", "bf16"],
                     help="what the fused all-reduces push over NVLink: bf16 partials (default, as bf16 all-reduces do) or fp32")
     ap.add_argument("--no-fused", action="store_true", help="use the NCCL baseline collectives instead of fused kernels")
+    ap.add_argument("--mc-push", action="store_true",
+                    help="ll collectives: push partials through the NVLink multicast address (one store reaches all ranks)")
     ap.add_argument("--collective", default="ll", choices=["ll", "multimem"],
                     help="fused all-reduces: tagged peer pushes (ll) or reduce + broadcast inside the NVLink switch")
     ap.add_argument("--moe", default="replicated", choices=["replicated", "dispatch"],
@@ -145,7 +147,7 @@ def main() -> None:
         dist.init_process_group("nccl", device_id=dev)
         from ferrule_b200.parallel.tp import TensorParallel
         tp = TensorParallel(rank, world, dev, fused=not args.no_fused, payload=args.ar_payload,
-                            collective=args.collective)
+                            collective=args.collective, multicast_push=args.mc_push)
 
     cfg = C.PRESETS[args.model]()
     if args.layers:
@@ -292,7 +294,7 @@ def main() -> None:
                        "l2_policy": "inputs larger than L2: each step streams %.1f GB of weights per GPU"
                                     % (weights.nbytes() / 1e9),
                        "collectives": "none" if world == 1 else ("nccl" if args.no_fused else (
-                           "fused-p2p, %s partials" % args.ar_payload if args.collective == "ll"
+                           "fused-p2p%s, %s partials" % (" (multicast push)" if args.mc_push else "", args.ar_payload) if args.collective == "ll"
                            else "in-switch multimem reduce + broadcast (bf16)"))},
             "e2e": {"value": round(e2e_value, 1), "unit": "tokens/s", "ms_per_step": round(e2e_ms / K, 4),
                     "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h),

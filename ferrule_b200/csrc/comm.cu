@@ -53,7 +53,7 @@ moe_reduce_allreduce_kernel(const __nv_bfloat16* __restrict__ route_out, int slo
                             const __nv_bfloat16* __restrict__ residual, long long ldr,
                             __nv_bfloat16* __restrict__ out, long long ldo, int rows, int dim,
                             int rank, int world, int rows_cap, PeerPtrs peers, uint32_t* ctr,
-                            int payload_bf16, unsigned long long wait_ns, DeviceStatus* st) {
+                            int payload_bf16, unsigned long long wait_ns, DeviceStatus* st, uint8_t* mc_recv) {
   pdl_launch_dependents();
   pdl_wait();
   const int t = blockIdx.x;
@@ -78,8 +78,12 @@ moe_reduce_allreduce_kernel(const __nv_bfloat16* __restrict__ route_out, int slo
 #pragma unroll
       for (int j = 0; j < 4; ++j) acc[j] += __bfloat162float(vp[j]);
     }
-    for (int pr = 0; pr < world; ++pr)
-      ll_push4(reinterpret_cast<uint8_t*>(peers.recv[pr]) + parity_off + rank * slot_bytes, ch, acc, tag, bf16);
+    if (mc_recv != nullptr) {
+      ll_push4_mc(mc_recv + parity_off + rank * slot_bytes, ch, acc, tag, bf16);      // the switch replicates it
+    } else {
+      for (int pr = 0; pr < world; ++pr)
+        ll_push4(reinterpret_cast<uint8_t*>(peers.recv[pr]) + parity_off + rank * slot_bytes, ch, acc, tag, bf16);
+    }
     // ---- all ranks' partials: poll the tagged words, sum in rank order, add the residual ----
     const uint64_t w0 = globaltimer_ns();
     float sum[4] = {0.f, 0.f, 0.f, 0.f};
@@ -222,6 +226,17 @@ extern "C" int fb_moe_reduce_allreduce(const void* route_out, int slots, int top
                                        int world, int rows_cap, void* const* peer_recv,
                                        void* const* peer_flags, void* ctr, int payload_bf16,
                                        unsigned long long wait_ns, void* status, void* stream) {
+  return fb_moe_reduce_allreduce_mc(route_out, slots, topk, topk_idx, e_lo, e_hi, residual, ldr, out, ldo, rows, dim,
+                                    rank, world, rows_cap, peer_recv, peer_flags, ctr, payload_bf16, wait_ns, nullptr,
+                                    status, stream);
+}
+
+extern "C" int fb_moe_reduce_allreduce_mc(const void* route_out, int slots, int topk, const int* topk_idx,
+                                          int e_lo, int e_hi, const void* residual, long long ldr,
+                                          void* out, long long ldo, int rows, int dim, int rank,
+                                          int world, int rows_cap, void* const* peer_recv,
+                                          void* const* peer_flags, void* ctr, int payload_bf16,
+                                          unsigned long long wait_ns, void* mc_recv, void* status, void* stream) {
   if (rows <= 0 || rows > rows_cap || dim % 4 != 0 || slots < 1 || slots < topk)
     return FB_ERR_SHAPE;
   if (rank < 0 || rank >= world || !ctr) return FB_ERR_SHAPE;
@@ -233,7 +248,7 @@ extern "C" int fb_moe_reduce_allreduce(const void* route_out, int slots, int top
       static_cast<const __nv_bfloat16*>(route_out), slots, topk, topk_idx, e_lo, e_hi,
       static_cast<const __nv_bfloat16*>(residual), ldr, static_cast<__nv_bfloat16*>(out), ldo, rows, dim,
       rank, world, rows_cap, p, c, payload_bf16, wait_ns ? wait_ns : 3000000000ull,
-      static_cast<DeviceStatus*>(status));
+      static_cast<DeviceStatus*>(status), static_cast<uint8_t*>(mc_recv));
   return cudaGetLastError() == cudaSuccess ? FB_OK : FB_ERR_LAUNCH;
 }
 

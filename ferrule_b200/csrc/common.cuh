@@ -456,6 +456,23 @@ __device__ __forceinline__ void ll_push4(void* base, size_t ch, const float (&v)
   }
 }
 
+// The same push through an NVLink multicast address: one store lands in the slot of every rank (the switch
+// replicates it), so the pusher issues one store per 16 bytes instead of one per peer.
+__device__ __forceinline__ void ll_store_words_mc(void* mc_dst, uint32_t w0, uint32_t w1, uint32_t tag) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc_dst), "f"(__uint_as_float(w0)),
+               "f"(__uint_as_float(tag)), "f"(__uint_as_float(w1)), "f"(__uint_as_float(tag))
+               : "memory");
+}
+__device__ __forceinline__ void ll_push4_mc(void* mc_base, size_t ch, const float (&v)[4], uint32_t tag, bool bf16) {
+  if (bf16) {
+    ll_store_words_mc(static_cast<uint8_t*>(mc_base) + ch * 4, pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]), tag);
+  } else {
+    uint8_t* d = static_cast<uint8_t*>(mc_base) + ch * 8;
+    ll_store_words_mc(d, __float_as_uint(v[0]), __float_as_uint(v[1]), tag);
+    ll_store_words_mc(d + 16, __float_as_uint(v[2]), __float_as_uint(v[3]), tag);
+  }
+}
+
 // Gather 4 consecutive channels from the slots of `world` (<= 8) source ranks and add them in rank order.
 // The loads of all ranks are issued together (one L2 round trip when everything has arrived); words whose
 // tag is not the call's yet are re-polled.  first = source 0's slot, ch as in ll_push4, stride = bytes between

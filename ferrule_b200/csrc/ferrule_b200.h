@@ -72,6 +72,8 @@ typedef struct FbGemmArgs {
   const int* remap_rank;    // epilogue 2, expert-parallel combine: output row -> destination rank and row of
   const int* remap_row;     //   that rank's bf16 combine buffer (peer_recv[rank], pitch ldo); peer_flags[r][rank]
                             //   is bumped once per call when all of this rank's rows are stored
+  void* mc_recv;            // epilogue 3, optional: multicast (NVLS) address of the ranks' receive buffers; partials
+                            //   are then broadcast with one multimem store instead of one store per peer
 } FbGemmArgs;
 
 int fb_gemm_bf16(const FbGemmArgs* args, void* stream);
@@ -390,6 +392,13 @@ int fb_moe_reduce_allreduce(const void* route_out, int slots, int topk, const in
                             int rows, int dim, int rank, int world, int rows_cap,
                             void* const* peer_recv, void* const* peer_flags, void* ctr,
                             int payload_bf16, unsigned long long wait_ns, void* status, void* stream);
+// the same with the receive buffers' multicast address (null: plain peer stores)
+int fb_moe_reduce_allreduce_mc(const void* route_out, int slots, int topk, const int* topk_idx, int e_lo,
+                               int e_hi, const void* residual, long long ldr, void* out, long long ldo,
+                               int rows, int dim, int rank, int world, int rows_cap,
+                               void* const* peer_recv, void* const* peer_flags, void* ctr,
+                               int payload_bf16, unsigned long long wait_ns, void* mc_recv, void* status,
+                               void* stream);
 int fb_argmax_allgather(int* ids, float* vals, int vocab_lo, int rows, int rank, int world, int rows_cap,
                         void* const* peer_recv, void* const* peer_flags, void* ctr,
                         unsigned long long wait_ns, void* status, void* stream);

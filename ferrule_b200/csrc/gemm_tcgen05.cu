@@ -69,6 +69,7 @@ struct GemmParams {
   uint32_t* peer_flags[8];   // per-tile arrival counters of every rank
   uint32_t* local_ctr;       // [0] = calls completed, [1] = CTAs finished this call, [2..] = consumed arrivals per tile
   int ar_bf16;               // kEpiAllReduce: partials travel as bf16 pairs instead of fp32
+  uint8_t* mc_recv;          // kEpiAllReduce: multicast address of the receive buffers (one store reaches every rank)
   int w_stream;              // weights are read once by this launch: load them with the L2 evict-first policy
   int stage_store;           // bf16 store / SwiGLU / scatter epilogues of large row tiles: rows leave through a
                              // shared-memory staging tile as 256-byte row segments instead of 2-byte column stores
@@ -490,9 +491,13 @@ gemm_swapab_kernel(const __grid_constant__ CUtensorMap tmap_w,
               const float4 val = *reinterpret_cast<const float4*>(ar_stage + r * 128 + lane * 4);
               const float vals[4] = {val.x, val.y, val.z, val.w};
               const size_t ch = static_cast<size_t>(row0 + r) * p.n_out + n4;
-              for (int pr = 0; pr < p.world; ++pr)
-                ll_push4(reinterpret_cast<uint8_t*>(p.peer_recv[pr]) + ar_parity_off + p.rank * ar_slot_bytes, ch,
-                         vals, tag, p.ar_bf16 != 0);
+              if (p.mc_recv != nullptr) {
+                ll_push4_mc(p.mc_recv + ar_parity_off + p.rank * ar_slot_bytes, ch, vals, tag, p.ar_bf16 != 0);
+              } else {
+                for (int pr = 0; pr < p.world; ++pr)
+                  ll_push4(reinterpret_cast<uint8_t*>(p.peer_recv[pr]) + ar_parity_off + p.rank * ar_slot_bytes, ch,
+                           vals, tag, p.ar_bf16 != 0);
+              }
             }
           }
         }
@@ -824,6 +829,7 @@ extern "C" int fb_gemm_bf16(const FbGemmArgs* a, void* stream_) {
     p.residual = static_cast<const __nv_bfloat16*>(a->residual);
     p.ldr = a->ldr;
     p.ar_bf16 = a->ar_payload_bf16;
+    p.mc_recv = static_cast<uint8_t*>(a->mc_recv);
     p.peer_wait_ns = a->peer_wait_ns ? a->peer_wait_ns : 3000000000ull;
     return launch_ntok<false, kEpiAllReduce>(ntok, mw, mx, p, max_tiles, grouped, stream);
   }

@@ -536,9 +536,19 @@ class CudaForward:
             side.wait_stream(main)
             with torch.cuda.stream(side):
                 inter = lw.w13.shape[1] // 2
-                mid = ws.ffn_mid[:T, :inter]
-                self._gemm(xn, lw.w13, mid, xq=xq_n, epilogue=K.EPI_SWIGLU, act_limit=cfg.swiglu_limit)
-                self._gemm(mid, lw.w2, ws.route_out[:T][:, k], slot="mid")
+                if self.w.shared_replicated and self.tp is not None:
+                    # the shared experts are held whole on every rank (for the token-dispatch form); in this
+                    # replicated-activation form each rank multiplies its slice of their inner dimension
+                    il = inter // self.tp.world
+                    i0 = self.tp.rank * il
+                    mid = ws.ffn_mid[:T, :il]
+                    K.gemm(xn, lw.w13[:, i0:], out=mid, epilogue=K.EPI_SWIGLU, n_out=il, dual_offset=inter,
+                           act_limit=cfg.swiglu_limit)
+                    K.gemm(mid, lw.w2[:, :, i0:i0 + il], out=ws.route_out[:T][:, k])
+                else:
+                    mid = ws.ffn_mid[:T, :inter]
+                    self._gemm(xn, lw.w13, mid, xq=xq_n, epilogue=K.EPI_SWIGLU, act_limit=cfg.swiglu_limit)
+                    self._gemm(mid, lw.w2, ws.route_out[:T][:, k], slot="mid")
                 nl = self._prefetch_next
                 if nl is not None and T <= ws.decode_rows:
                     # the next layer's attention weights (a few tens of MB, four latency-bound GEMMs) are pulled

@@ -51,7 +51,7 @@ class GemmArgs(C.Structure):
         ("local_ctr", C.c_void_p), ("residual", C.c_void_p), ("ldr", C.c_longlong),
         ("peer_wait_ns", C.c_ulonglong), ("status", C.c_void_p), ("trace", C.c_void_p),
         ("ar_payload_bf16", C.c_int),
-        ("remap_rank", C.c_void_p), ("remap_row", C.c_void_p),
+        ("remap_rank", C.c_void_p), ("remap_row", C.c_void_p), ("mc_recv", C.c_void_p),
     ]
 
 

@@ -25,6 +25,8 @@ def declare(lib) -> None:
         "fb_ipc_free": ([vp], i),
         "fb_moe_reduce_allreduce": ([vp, i, i, vp, i, i, vp, ll, vp, ll, i, i, i, i, i, C.POINTER(vp),
                                      C.POINTER(vp), vp, i, ull, vp, vp], i),
+        "fb_moe_reduce_allreduce_mc": ([vp, i, i, vp, i, i, vp, ll, vp, ll, i, i, i, i, i, C.POINTER(vp),
+                                        C.POINTER(vp), vp, i, ull, vp, vp, vp], i),
         "fb_argmax_allgather": ([vp, vp, i, i, i, i, i, C.POINTER(vp), C.POINTER(vp), vp, ull, vp, vp], i),
         "fb_flag_wait_probe": ([vp, i, ull, vp, vp, vp], i),
         "fb_peer_pingpong": ([vp, vp, i, i, ull, vp, vp, vp], i),

@@ -69,13 +69,24 @@ class Channel:
     """
 
     def __init__(self, rank: int, world: int, device, payload_floats: int, n_flags: int, group=None,
-                 wait_ns: int = 3_000_000_000):
+                 wait_ns: int = 3_000_000_000, multicast: bool = False):
         self.rank, self.world, self.wait_ns = rank, world, wait_ns
         self.payload_floats, self.n_flags = payload_floats, n_flags
         self.flag_bytes = ((n_flags * 4 + 255) // 256) * 256
         # every fp32 travels as an 8-byte (value, tag) pair; two parities; one slot per source rank
         recv_bytes = 2 * world * payload_floats * 8
-        self.buf = SymmetricBuffer(self.flag_bytes + recv_bytes, rank, world, group)
+        # `multicast`: the buffer is also bound to an NVLink multicast address (NVLS), so that a pusher reaches all
+        # ranks' slots with one `multimem.st`; `mc_recv` stays 0 when the node offers none
+        self.mc_recv = 0
+        self.buf = None
+        if multicast:
+            try:
+                self.buf = McSymmetricBuffer(self.flag_bytes + recv_bytes, rank, world, device, group)
+                self.mc_recv = self.buf.mc_ptr + self.flag_bytes
+            except Exception:  # noqa: BLE001 - no NVLS here: plain peer stores
+                self.buf = None
+        if self.buf is None:
+            self.buf = SymmetricBuffer(self.flag_bytes + recv_bytes, rank, world, group)
         self.flags = self.buf.ptr_array(0)
         self.recv = self.buf.ptr_array(self.flag_bytes)
         # private: [calls, ctas_done, consumed[n_flags]]
@@ -83,6 +94,40 @@ class Channel:
 
     def close(self) -> None:
         self.buf.close()
+
+
+class McSymmetricBuffer:
+    """Symmetric buffer with peer mappings and an NVLink multicast mapping (allocated and exchanged by
+    `torch.distributed._symmetric_memory`); same interface as `SymmetricBuffer` plus `mc_ptr`."""
+
+    def __init__(self, nbytes: int, rank: int, world: int, device, group=None):
+        import torch.distributed._symmetric_memory as symm_mem
+        self.rank, self.world, self.nbytes = rank, world, nbytes
+        self.t = symm_mem.empty(nbytes, dtype=torch.uint8, device=device)
+        self.t.zero_()
+        torch.cuda.synchronize(device)
+        grp = group if group is not None else dist.group.WORLD
+        try:
+            self.hdl = symm_mem.rendezvous(self.t, grp)
+        except Exception:  # noqa: BLE001
+            symm_mem.enable_symm_mem_for_group(grp.group_name)
+            self.hdl = symm_mem.rendezvous(self.t, grp.group_name)
+        self.mc_ptr = int(self.hdl.multicast_ptr or 0)
+        if not self.mc_ptr:
+            raise RuntimeError("this node offers no NVLink multicast (NVLS)")
+        self.ptrs = [int(p) for p in self.hdl.buffer_ptrs]
+        self.local_ptr = self.ptrs[rank]
+        dist.barrier(group=group)
+
+    def ptr_array(self, offset: int = 0):
+        arr = (C.c_void_p * 8)()
+        for r in range(self.world):
+            arr[r] = self.ptrs[r] + offset
+        return arr
+
+    def close(self) -> None:
+        self.hdl = None
+        self.t = None
 
 
 class McChannel:

@@ -32,7 +32,8 @@ from .symm import Channel
 
 class TensorParallel:
     def __init__(self, rank: int, world: int, device, fused: bool = True, fused_max_rows: int = 64,
-                 group=None, wait_ns: int = 3_000_000_000, payload: str = "fp32", collective: str = "ll"):
+                 group=None, wait_ns: int = 3_000_000_000, payload: str = "fp32", collective: str = "ll",
+                 multicast_push: bool = False):
         self.rank, self.world, self.device, self.group = rank, world, torch.device(device), group
         self.fused = fused and self.device.type == "cuda"
         self.fused_max_rows = fused_max_rows
@@ -47,6 +48,8 @@ class TensorParallel:
         self.collective = collective
         self.mm = None
         self.mm_max_rows = 512
+        # "ll" pushes through an NVLink multicast address when the node has NVLS: one store reaches every rank
+        self.multicast_push = multicast_push
         self.gemm_ch: Optional[Channel] = None
         self.moe_ch: Optional[Channel] = None
         self.arg_ch: Optional[Channel] = None
@@ -71,8 +74,9 @@ class TensorParallel:
             self._partial = torch.zeros(self.mm_max_rows, H, dtype=torch.bfloat16, device=self.device)
         n_tiles = (H + 127) // 128
         self.gemm_ch = Channel(self.rank, self.world, self.device, rows * H, n_tiles * ((rows + 15) // 16),
-                               self.group, self.wait_ns)
-        self.moe_ch = Channel(self.rank, self.world, self.device, rows * H, rows, self.group, self.wait_ns)
+                               self.group, self.wait_ns, multicast=self.multicast_push)
+        self.moe_ch = Channel(self.rank, self.world, self.device, rows * H, rows, self.group, self.wait_ns,
+                              multicast=self.multicast_push)
         self.arg_ch = Channel(self.rank, self.world, self.device, max(fwd.ws.max_logit_rows, 1) * 2, 1, self.group,
                               self.wait_ns)
 
@@ -90,6 +94,7 @@ class TensorParallel:
         a.local_ctr = ch.ctr.data_ptr()
         a.peer_wait_ns = self.wait_ns
         a.ar_payload_bf16 = self.payload_bf16
+        a.mc_recv = ch.mc_recv or None
 
     # ------------------------------------------------------------------ fused collectives
     def gemm_allreduce(self, x: torch.Tensor, w: torch.Tensor, residual: torch.Tensor, out: torch.Tensor,
@@ -124,12 +129,13 @@ class TensorParallel:
         if self.fused and T <= self.fused_max_rows:
             ch = self.moe_ch
             lib = get_lib(True)
-            check(lib.fb_moe_reduce_allreduce(route_out.data_ptr(), slots, topk, idx.data_ptr(), e_lo, e_hi,
-                                              residual.data_ptr(), residual.stride(0), out.data_ptr(),
-                                              out.stride(0), T, H, self.rank, self.world, self.fused_max_rows,
-                                              ch.recv, ch.flags, ch.ctr.data_ptr(), self.payload_bf16, self.wait_ns,
-                                              status_tensor(self.device).data_ptr(), stream_ptr()),
-                  "fb_moe_reduce_allreduce")
+            check(lib.fb_moe_reduce_allreduce_mc(route_out.data_ptr(), slots, topk, idx.data_ptr(), e_lo, e_hi,
+                                                 residual.data_ptr(), residual.stride(0), out.data_ptr(),
+                                                 out.stride(0), T, H, self.rank, self.world, self.fused_max_rows,
+                                                 ch.recv, ch.flags, ch.ctr.data_ptr(), self.payload_bf16,
+                                                 self.wait_ns, ch.mc_recv or None,
+                                                 status_tensor(self.device).data_ptr(), stream_ptr()),
+                  "fb_moe_reduce_allreduce_mc")
             self.calls_fused += 1
             return out
         tmp = self._tmp32[:T]

@@ -76,6 +76,7 @@ def main() -> int:
     ap.add_argument("--rows", type=int, default=32)
     ap.add_argument("--payload", default="fp32", choices=["fp32", "bf16"])
     ap.add_argument("--collective", default="ll", choices=["ll", "multimem"])
+    ap.add_argument("--mc-push", action="store_true")
     ap.add_argument("--bench-hidden", type=int, default=2048)
     ap.add_argument("--bench-rows", type=int, default=32)
     args = ap.parse_args()
@@ -98,7 +99,8 @@ def main() -> int:
     H = cfg.hidden
     w_tp = W.random_weights(cfg, device=dev, seed=3, std=0.05, tp_rank=rank, tp_world=world)
     pool = D.KvPool(cfg, 32, 64, dev)
-    tp = TensorParallel(rank, world, dev, fused=True, payload=args.payload, collective=args.collective)
+    tp = TensorParallel(rank, world, dev, fused=True, payload=args.payload, collective=args.collective,
+                        multicast_push=args.mc_push)
     fwd = D.CudaForward(w_tp, pool, max_rows=256, max_logit_rows=8, decode_rows=64, max_seq_len=512, attn_splits=2, tp=tp)
     tp.attach(fwd)
     tp_nccl = TensorParallel(rank, world, dev, fused=False)
@@ -284,7 +286,8 @@ def main() -> int:
 
     if args.bench:
         Hb, Tb = args.bench_hidden, args.bench_rows
-        tpb = TensorParallel(rank, world, dev, fused=True, payload=args.payload, collective=args.collective)
+        tpb = TensorParallel(rank, world, dev, fused=True, payload=args.payload, collective=args.collective,
+                             multicast_push=args.mc_push)
 
         class _F:  # minimal stand-in carrying the sizes attach() needs
             pass
