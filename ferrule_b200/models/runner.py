@@ -131,7 +131,7 @@ class DeepSeekRunner(ModelRunner):
                  max_seqs: int = 64, max_seq_len: int = 4096, device=None, tp=None, use_graphs: bool = True,
                  emulate_bf16: bool = False, attn_splits: int = 8, enable_mtp: bool = True, max_draft: int = 1,
                  expert_residency: Optional[float] = None, async_streaming: bool = False,
-                 lookahead: bool = True):
+                 lookahead: bool = True, pp=None):
         self.w, self.cfg = weights, weights.cfg
         self.device = torch.device(device if device is not None else weights.embed.device)
         self.is_cuda = self.device.type == "cuda"
@@ -141,6 +141,11 @@ class DeepSeekRunner(ModelRunner):
         self.pool = KvPool(self.cfg, n_pages, page_size, self.device,
                            dtype=torch.bfloat16 if self.is_cuda else weights.embed.dtype)
         self.tp = tp
+        # pipeline parallelism (parallel.pp.PipelineParallel): `weights` is this stage's share; every step runs
+        # through all stages, the last one's greedy tokens are broadcast, so all ranks' engines stay in step
+        self.pp = pp
+        if pp is not None:
+            use_graphs, enable_mtp = False, False
         # streamed routed experts: a fraction of every layer's experts is resident, the rest comes from pinned host
         # memory on demand; the step then synchronises with the host per MoE layer, so it cannot be one graph
         # `async_streaming`: a batch that routes to a non-resident expert returns `Waiting`; the engine's load
@@ -464,10 +469,22 @@ class DeepSeekRunner(ModelRunner):
             if L > fwd.ws.max_logit_rows:
                 raise ValueError("more logit rows than the runner was sized for")
             want_topk = any(b.logits[r].k > 1 for r in lrows)
-            fwd.forward(st.device_batch(T, L), want_logits=want_topk, start_layer=start_layer, h0=h0)
-            self._last_hidden = fwd.last_hidden
+            if self.pp is not None:
+                if want_topk:
+                    raise ValueError("pipeline-parallel runs return the greedy token only")
+                from ..ops import _lib as _l
+                l0 = _l.LAUNCHES[0]
+                ids_t, vals_t = self.pp.step(fwd, st.device_batch(T, L), self.cfg.hidden, torch.bfloat16, True)
+                if L:
+                    fwd.ws.next_id[:L].copy_(ids_t)
+                    fwd.ws.next_val[:L].copy_(vals_t)
+                self._last_hidden = None
+                self.stats.kernel_launches += _l.LAUNCHES[0] - l0
+            else:
+                fwd.forward(st.device_batch(T, L), want_logits=want_topk, start_layer=start_layer, h0=h0)
+                self._last_hidden = fwd.last_hidden
+                self.stats.kernel_launches += fwd.launches
             self.stats.eager_steps += 1
-            self.stats.kernel_launches += fwd.launches
         topk = None
         if L:
             self.out_host.copy_(fwd.ws.out_buf, non_blocking=True)
@@ -538,6 +555,17 @@ class DeepSeekRunner(ModelRunner):
         rows: List[RowOutput] = []
         allreduce = self.tp.allreduce_reference if self.tp is not None else None
         gather = self.tp.gather_vocab_reference if self.tp is not None else None
+        if self.pp is not None:
+            with torch.no_grad():
+                ids_t, vals_t = self.pp.step(self.fwd, db, self.cfg.hidden, self.w.embed.dtype, False)
+            self._last_hidden = None
+            for i, r in enumerate(lrows):
+                if int(ids_t[i]) >= 0 and torch.isfinite(vals_t[i]):
+                    rows.append(RowOutput(r, [int(ids_t[i])], [float(vals_t[i])]))
+                else:
+                    rows.append(RowOutput(r, [], []))
+            self.stats.eager_steps += 1
+            return ExecutionOutput(rows)
         with torch.no_grad():
             h = self.fwd.hidden_states(db, allreduce, start_layer, h0)
             self._last_hidden = h

@@ -44,16 +44,36 @@ def stage_weights(w: ModelWeights, rank: int, world: int) -> ModelWeights:
 
 
 class PipelineParallel:
-    def __init__(self, rank: int, world: int, group=None, microbatches: int = 1):
+    """`rank` / `world`: this stage and the number of stages.  `group`: the process group of the stages that hold
+    the same tensor-parallel shard (None: all ranks); `ranks`: its members' global ranks in stage order.
+
+    On GPUs the transfers run on a side stream and are tied to the compute stream by events only: the receive of
+    row range j + 1 and the send of range j - 1 are in flight while range j is being computed, every range has
+    its own receive and send buffer, nothing on the compute stream waits for a transfer it does not consume."""
+
+    def __init__(self, rank: int, world: int, group=None, microbatches: int = 1, ranks: Optional[List[int]] = None):
         self.rank, self.world, self.group, self.microbatches = rank, world, group, max(1, microbatches)
         self.first, self.last = rank == 0, rank == world - 1
+        self.ranks = list(ranks) if ranks is not None else list(range(world))
         self.sends = 0
+        self.comm_stream = None
+        self._bufs = {}
+
+    def _g(self, stage: int) -> int:
+        return self.ranks[stage]
 
     def _slice(self, b: DeviceBatch, r0: int, r1: int) -> DeviceBatch:
         n = r1 - r0
         lr = torch.arange(n, dtype=torch.int32, device=b.token_ids.device)
         return DeviceBatch(b.token_ids[r0:r1], b.positions[r0:r1], b.write_slot[r0:r1], b.row_seq[r0:r1],
                            b.row_pos[r0:r1], b.block_table, lr, n, n)
+
+    def _buf(self, kind: str, j: int, rows: int, hidden: int, dtype, dev) -> torch.Tensor:
+        key = (kind, j)
+        t = self._bufs.get(key)
+        if t is None or t.shape[0] < rows or t.dtype != dtype:
+            t = self._bufs[key] = torch.empty(max(rows, 1), hidden, dtype=dtype, device=dev)
+        return t[:rows]
 
     def step(self, fwd, b: DeviceBatch, hidden: int, dtype, cuda: bool):
         """Runs the packed batch through all stages.  Returns (ids, vals) of the greedy tokens on every rank
@@ -62,38 +82,89 @@ class PipelineParallel:
         m = self.microbatches if (b.n_logit == T and T >= self.microbatches) else 1
         bounds = [(j * T // m, (j + 1) * T // m) for j in range(m)]
         dev = b.token_ids.device
+        if cuda:
+            return self._step_cuda(fwd, b, bounds, hidden, dtype, dev)
         outs: List[Optional[Tuple[torch.Tensor, torch.Tensor]]] = []
         pending = []
         for (r0, r1) in bounds:
             mb = b if m == 1 else self._slice(b, r0, r1)
             n = r1 - r0
             if self.first:
-                h = fwd.embed_rows(mb, n) if cuda else fwd.embed_rows(mb)
+                h = fwd.embed_rows(mb)
             else:
                 h = torch.empty(n, hidden, dtype=dtype, device=dev)
-                dist.recv(h, src=self.rank - 1, group=self.group)
-            h = fwd.run_layers(h, mb, n) if cuda else fwd.run_layers(h, mb)
+                dist.recv(h, src=self._g(self.rank - 1), group=self.group)
+            h = fwd.run_layers(h, mb)
             if not self.last:
                 hs = h.contiguous().clone()             # the stage's buffer is reused by the next range
-                pending.append((dist.isend(hs, dst=self.rank + 1, group=self.group), hs))
+                pending.append((dist.isend(hs, dst=self._g(self.rank + 1), group=self.group), hs))
                 self.sends += 1
                 outs.append(None)
             else:
-                if cuda:
-                    ids, vals, _ = fwd.head(h, mb, fwd.w.final_norm)
-                    outs.append((ids.clone(), vals.clone()))
-                else:
-                    logits = fwd.logits_from_hidden(h, mb)
-                    vals, ids = logits.max(-1)
-                    outs.append((ids.to(torch.int32), vals.float()))
+                logits = fwd.logits_from_hidden(h, mb)
+                vals, ids = logits.max(-1)
+                outs.append((ids.to(torch.int32), vals.float()))
         for work, _ in pending:
             work.wait()
+        return self._broadcast(b, outs, dev)
+
+    def _broadcast(self, b: DeviceBatch, outs, dev):
         L = b.n_logit
         ids = torch.empty(L, dtype=torch.int32, device=dev)
         vals = torch.empty(L, dtype=torch.float32, device=dev)
+        if L == 0:
+            return ids, vals
         if self.last:
             ids.copy_(torch.cat([o[0] for o in outs]))
             vals.copy_(torch.cat([o[1] for o in outs]))
-        dist.broadcast(ids, src=self.world - 1, group=self.group)
-        dist.broadcast(vals, src=self.world - 1, group=self.group)
+        dist.broadcast(ids, src=self._g(self.world - 1), group=self.group)
+        dist.broadcast(vals, src=self._g(self.world - 1), group=self.group)
         return ids, vals
+
+    def _step_cuda(self, fwd, b: DeviceBatch, bounds, hidden: int, dtype, dev):
+        main = torch.cuda.current_stream(dev)
+        if self.comm_stream is None:
+            self.comm_stream = torch.cuda.Stream(device=dev)
+        comm = self.comm_stream
+        m = len(bounds)
+        outs: List[Optional[Tuple[torch.Tensor, torch.Tensor]]] = []
+        # all receives are posted up front on the side stream: range j + 1 arrives while range j computes
+        recv_ev = []
+        if not self.first:
+            comm.wait_stream(main)                       # the buffers' previous readers (the last step) are done
+            with torch.cuda.stream(comm):
+                for j, (r0, r1) in enumerate(bounds):
+                    hin = self._buf("recv", j, r1 - r0, hidden, dtype, dev)
+                    dist.recv(hin, src=self._g(self.rank - 1), group=self.group)
+                    ev = torch.cuda.Event()
+                    ev.record(comm)
+                    recv_ev.append(ev)
+        send_done = []
+        for j, (r0, r1) in enumerate(bounds):
+            mb = b if m == 1 else self._slice(b, r0, r1)
+            n = r1 - r0
+            if self.first:
+                h = fwd.embed_rows(mb, n)
+            else:
+                main.wait_event(recv_ev[j])
+                h = self._buf("recv", j, n, hidden, dtype, dev)
+            h = fwd.run_layers(h, mb, n)
+            if not self.last:
+                hs = self._buf("send", j, n, hidden, dtype, dev)
+                hs.copy_(h)                              # the stage's activation buffer is reused by the next range
+                done = torch.cuda.Event()
+                done.record(main)
+                with torch.cuda.stream(comm):
+                    comm.wait_event(done)
+                    dist.send(hs, dst=self._g(self.rank + 1), group=self.group)
+                    ev = torch.cuda.Event()
+                    ev.record(comm)
+                    send_done.append(ev)
+                self.sends += 1
+                outs.append(None)
+            else:
+                ids, vals, _ = fwd.head(h, mb, fwd.w.final_norm)
+                outs.append((ids.clone(), vals.clone()))
+        for ev in send_done:
+            main.wait_event(ev)                          # the send buffers are free for the next step
+        return self._broadcast(b, outs, dev)

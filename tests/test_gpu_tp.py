@@ -55,3 +55,17 @@ def test_selftest_two_ranks_in_switch_collectives():
     assert res["ok"], res
     assert res["checks"]["allreduce_bits_equal_across_ranks"] and res["checks"]["ep_model_tokens_match"]
 
+
+def test_pipeline_parallel_engine_two_stages_on_gpus():
+    """Two pipeline stages on two GPUs (NCCL send / recv on a side stream, two row ranges in flight): the engine's
+    token streams equal those of one GPU holding the whole model."""
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", PYTHONPATH=ROOT)
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
+           "--master-addr", "127.0.0.1", "--master-port", "29523", os.path.join(ROOT, "tests", "dist", "pp_selftest.py"),
+           "--pp", "2"]
+    p = subprocess.run(cmd, capture_output=True, text=True, timeout=600, cwd=ROOT, env=env)
+    lines = [l for l in p.stdout.splitlines() if l.startswith("{")]
+    assert lines, p.stdout[-2000:] + p.stderr[-4000:]
+    res = json.loads(lines[-1])
+    assert res["ok"] and res["requests_equal"] == 5 and res["sends"] > 0, res
+

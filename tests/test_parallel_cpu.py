@@ -128,3 +128,40 @@ def test_tensor_parallel_reference_on_gloo_equals_single_process():
         dist.destroy_process_group()
     ''', 2, 29613)
     assert p.stdout.count("TP_OK") == 2, p.stdout[-2000:] + p.stderr[-3000:]
+
+
+def test_engine_over_two_pipeline_stages_streams_the_single_process_tokens():
+    """The whole engine (scheduler, KV transactions, chunked prefill, decode) on two pipeline stages: every rank
+    runs the same owner loop, the last stage's greedy tokens reach all of them, and the token streams equal
+    those of one process holding all layers."""
+    p = _run('''
+        import torch, torch.distributed as dist
+        from ferrule_b200.models import config as C, weights as W
+        from ferrule_b200.models.runner import DeepSeekRunner
+        from ferrule_b200.parallel.pp import PipelineParallel, stage_weights
+        from ferrule_b200.runtime.engine import Engine, EngineConfig, TokenEvent
+        from ferrule_b200.runtime.scheduler import SchedulerConfig
+        from ferrule_b200.runtime.session import GenerateRequest
+        dist.init_process_group("gloo")
+        rank, world = dist.get_rank(), dist.get_world_size()
+        cfg = C.tiny_fixture().with_(n_mtp_layers=0)
+        w = W.random_weights(cfg, device="cpu", seed=0, dtype=torch.float32)
+        def run(runner):
+            sched = SchedulerConfig(max_active_sequences=4, max_decode_batch=4, max_batch_tokens=48,
+                                    prefill_chunk_size=16, ctx_size=128)
+            eng = Engine(runner, EngineConfig(scheduler=sched, kv_pages=32, page_size=16))
+            g = torch.Generator().manual_seed(3)
+            for i in range(3):
+                eng.submit(GenerateRequest(f"r{i}", torch.randint(0, cfg.vocab_size, (9 + 11 * i,), generator=g).tolist(),
+                                           max_new_tokens=6, ignore_eos=True))
+            ev = []
+            eng.run_until_idle(ev.append)
+            return {r: [e.token for e in ev if isinstance(e, TokenEvent) and e.request_id == r] for r in ("r0", "r1", "r2")}
+        want = run(DeepSeekRunner(w, n_pages=32, page_size=16, max_rows=64, max_seqs=4, max_seq_len=128, device="cpu"))
+        pp = PipelineParallel(rank, world, microbatches=2)
+        got = run(DeepSeekRunner(stage_weights(w, rank, world), n_pages=32, page_size=16, max_rows=64, max_seqs=4,
+                                 max_seq_len=128, device="cpu", pp=pp))
+        print("PPE_OK" if got == want and all(len(v) == 6 for v in got.values()) else f"PPE_BAD {got} {want}", rank, flush=True)
+        dist.destroy_process_group()
+    ''', 2, 29613)
+    assert p.stdout.count("PPE_OK") == 2, p.stdout[-2000:] + p.stderr[-3000:]
