@@ -118,6 +118,11 @@ def main() -> None:
     ap.add_argument("--moe", default="replicated", choices=["replicated", "dispatch"],
                     help="N > 1: experts by id over replicated activations, or token-dispatch expert parallelism "
                          "(every rank routes its slice of the tokens; dispatch / combine all-to-alls over peer memory)")
+    ap.add_argument("--pp", type=int, default=1,
+                    help="pipeline stages (N must be a multiple): each stage holds a contiguous range of layers over "
+                         "N/pp tensor-parallel ranks; steps run eagerly (no graphs), so the device-timed number is the "
+                         "engine loop")
+    ap.add_argument("--microbatches", type=int, default=2, help="pipeline microbatches per step (--pp > 1)")
     args = ap.parse_args()
     if args.impl == "reference":
         reference_arm()
@@ -141,13 +146,14 @@ def main() -> None:
             raise SystemExit("for --gpus N > 1 launch with: python -m torch.distributed.run --nproc-per-node N bench.py ...")
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
-    tp = None
+    tp = pp = lay = None
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=dev)
-        from ferrule_b200.parallel.tp import TensorParallel
-        tp = TensorParallel(rank, world, dev, fused=not args.no_fused, payload=args.ar_payload,
-                            collective=args.collective, multicast_push=args.mc_push)
+        from ferrule_b200.parallel.layout import build_parallel
+        lay = build_parallel(rank, world, dev, pp=args.pp, microbatches=args.microbatches, payload=args.ar_payload,
+                             fused=not args.no_fused, collective=args.collective, multicast_push=args.mc_push)
+        tp, pp = lay.tp, lay.pp
 
     cfg = C.PRESETS[args.model]()
     if args.layers:
@@ -155,16 +161,24 @@ def main() -> None:
     B, P, K, Wm = args.batch, args.prompt_len, args.steps, args.warmup
     page = 64
     margin = 64                      # sequences that finish prefill early decode ahead of the others
-    max_seq = P + K + Wm + margin + 2 * page
+    k_total = K * (2 if args.pp > 1 else 1)       # pipeline runs time two windows of engine steps
+    max_seq = P + k_total + Wm + margin + 2 * page
     pages_per_seq = (max_seq + page - 1) // page
-    weights = W.random_weights(cfg, device=dev, seed=0, tp_rank=rank, tp_world=args.shard_as or world, fast_device_init=True,
-                               weight_format=args.weight_format,
-                               replicate_shared=(world > 1 and args.moe == "dispatch"))
+    tp_world = lay.tp_size if lay else 1
+    from ferrule_b200.parallel.pp import stage_range, stage_weights
+    weights = W.random_weights(cfg, device=dev, seed=0, tp_rank=lay.tp_rank if lay else 0, tp_world=args.shard_as or tp_world,
+                               fast_device_init=True, weight_format=args.weight_format,
+                               replicate_shared=(tp_world > 1 and args.moe == "dispatch"),
+                               layer_range=stage_range(cfg.n_layers, lay.pp_rank, lay.pp_size) if pp is not None else None)
+    if pp is not None:
+        weights = stage_weights(weights, lay.pp_rank, lay.pp_size)
     runner = DeepSeekRunner(weights, n_pages=B * pages_per_seq + 8, page_size=page, max_rows=2048, max_seqs=B,
-                            max_seq_len=pages_per_seq * page, device=dev, tp=tp)
+                            max_seq_len=pages_per_seq * page, device=dev, tp=tp, pp=pp)
     if tp is not None:
         tp.attach(runner.fwd)
         if args.moe == "dispatch":
+            if pp is not None:
+                raise SystemExit("--moe dispatch runs inside one tensor-parallel group; use it without --pp")
             from ferrule_b200.parallel.ep import ExpertParallelMoE
             ep = ExpertParallelMoE(rank, world, dev, cfg.hidden, cfg.moe_inter, cfg.topk, cfg.n_routed_experts,
                                    max_local_tokens=(B + world - 1) // world, allgather=True)
@@ -178,7 +192,7 @@ def main() -> None:
     prompts = torch.randint(0, cfg.vocab_size, (B, P), generator=g)
     t_submit = time.perf_counter()
     for i in range(B):
-        engine.submit(GenerateRequest(f"req{i}", prompts[i].tolist(), max_new_tokens=K + Wm + margin, ignore_eos=True))
+        engine.submit(GenerateRequest(f"req{i}", prompts[i].tolist(), max_new_tokens=k_total + Wm + margin, ignore_eos=True))
     first_token_t, token_times = {}, {}
 
     def emit(ev) -> None:
@@ -229,41 +243,58 @@ def main() -> None:
     d2h = (runner.stats.d2h_bytes - d2h0) // K
     e2e_launches = runner.stats.kernel_launches - l0
 
-    # ---- device-only: the same K steps from the same starting state, fed back on the device ----
-    import numpy as np
-    from ferrule_b200.ops import _lib
-    from ferrule_b200.ops import kernels as KK
-    st, graph = runner.graphs[B]
-    runner._ahead = None                    # a step launched ahead by the last engine step is not consumed
-    torch.cuda.synchronize()
-    pages = [engine.kv.sequence(s.kv_seq).pages for s in seqs0]     # by now they cover the whole window
+    if pp is not None:
+        # pipeline stages step eagerly through the engine on every rank: the device-timed number is a second
+        # window of K engine steps (the stage hand-offs are NCCL transfers on a side stream)
+        class _G:
+            launches = 0
+        graph = _G()
+        barrier()
+        _lib_l0 = runner.stats.kernel_launches
+        d0, d1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        d0.record()
+        for _ in range(K):
+            engine.step(emit)
+        d1.record()
+        barrier()
+        graph.launches = (runner.stats.kernel_launches - _lib_l0) // K - 1
+        from ferrule_b200.ops import _lib
+    else:
+        # ---- device-only: the same K steps from the same starting state, fed back on the device ----
+        import numpy as np
+        from ferrule_b200.ops import _lib
+        from ferrule_b200.ops import kernels as KK
+        st, graph = runner.graphs[B]
+        runner._ahead = None                    # a step launched ahead by the last engine step is not consumed
+        torch.cuda.synchronize()
+        pages = [engine.kv.sequence(s.kv_seq).pages for s in seqs0]     # by now they cover the whole window
 
-    def rewind() -> None:
-        st.np_ids[:B] = start_ids
-        st.np_pos[:B] = start_pos
-        st.np_rpos[:B] = start_pos
-        st.np_seq[:B] = np.arange(B)
-        st.np_bt[:] = 0
-        for i, pg in enumerate(pages):
-            st.np_bt[i, :len(pg)] = pg
-            st.np_slot[i] = pg[start_pos[i] // page] * page + start_pos[i] % page
-        st.upload()
+        def rewind() -> None:
+            st.np_ids[:B] = start_ids
+            st.np_pos[:B] = start_pos
+            st.np_rpos[:B] = start_pos
+            st.np_seq[:B] = np.arange(B)
+            st.np_bt[:] = 0
+            for i, pg in enumerate(pages):
+                st.np_bt[i, :len(pg)] = pg
+                st.np_slot[i] = pg[start_pos[i] // page] * page + start_pos[i] % page
+            st.upload()
 
-    def device_steps(n: int) -> None:
-        for _ in range(n):
-            graph.replay()
-            KK.decode_advance(runner.fwd.ws.next_id[:B], graph.batch, cfg.vocab_size, page, True)
+        def device_steps(n: int) -> None:
+            for _ in range(n):
+                graph.replay()
+                KK.decode_advance(runner.fwd.ws.next_id[:B], graph.batch, cfg.vocab_size, page, True)
 
-    rewind()
-    device_steps(3)
-    rewind()
-    barrier()
-    _lib.read_peer_wait()
-    d0, d1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    d0.record()
-    device_steps(K)
-    d1.record()
-    barrier()
+        rewind()
+        device_steps(3)
+        rewind()
+        barrier()
+        _lib.read_peer_wait()
+        d0, d1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        d0.record()
+        device_steps(K)
+        d1.record()
+        barrier()
     clocks = sampler.stop()
     dev_ms = d0.elapsed_time(d1)
     wait_ns, wait_n = _lib.read_peer_wait()
@@ -280,7 +311,7 @@ def main() -> None:
     if rank == 0:
         value = B * K / (dev_ms / 1e3)
         e2e_value = B * K / (e2e_ms / 1e3)
-        par = "single-gpu" if world == 1 else ("tp%d" % world if args.moe == "replicated" else "tp%d-attention + ep%d-dispatch" % (world, world))
+        par = ("pp%d x tp%d (%d microbatches)" % (lay.pp_size, lay.tp_size, args.microbatches)) if pp is not None else "single-gpu" if world == 1 else ("tp%d" % world if args.moe == "replicated" else "tp%d-attention + ep%d-dispatch" % (world, world))
         line = {
             "metric": "decode tokens/s (whole job, max over ranks)",
             "value": round(value, 1), "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": Wm,

@@ -37,10 +37,46 @@ def _add_model_args(p: argparse.ArgumentParser) -> None:
     p.add_argument("--speculative", action="store_true")
     p.add_argument("--max-draft", type=int, default=1)
     p.add_argument("--seed", type=int, default=0)
+    p.add_argument("--weight-format", default="bf16", choices=["bf16", "fp8_block", "fp8_mxfp4"],
+                   help="random-init presets: quantise the weights to this format")
+    p.add_argument("--pp", type=int, default=1,
+                   help="pipeline stages; under torch.distributed.run the ranks form pp stages x (world / pp) "
+                        "tensor-parallel ranks, rank 0 serves and the others mirror its command stream")
+    p.add_argument("--microbatches", type=int, default=2)
+    p.add_argument("--collective", default="ll", choices=["ll", "multimem"])
+    p.add_argument("--mc-push", action="store_true")
 
 
-def build_engine(args):
-    """-> (engine, tokenizer, model name).  Shared by generate / chat / serve / bench-interactive."""
+def replica_layout(args):
+    """Process groups of a multi-rank launch (torch.distributed.run sets RANK / WORLD_SIZE): -> (layout, mirror),
+    (None, None) in a single process."""
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if world == 1:
+        return None, None
+    import torch
+    import torch.distributed as dist
+
+    from ..parallel.layout import build_parallel
+    from ..parallel.mirror import CommandMirror
+    rank, local = int(os.environ["RANK"]), int(os.environ.get("LOCAL_RANK", os.environ["RANK"]))
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    cuda = torch.cuda.is_available() and (args.device or "cuda").startswith("cuda")
+    if cuda:
+        torch.cuda.set_device(local)
+        args.device = f"cuda:{local}"
+    if not dist.is_initialized():
+        dist.init_process_group("nccl" if cuda else "gloo",
+                                **({"device_id": torch.device("cuda", local)} if cuda else {}))
+    dev = torch.device(args.device) if cuda else torch.device("cpu")
+    lay = build_parallel(rank, world, dev, pp=args.pp, microbatches=args.microbatches,
+                         collective=args.collective, multicast_push=args.mc_push, fused=cuda)
+    host_group = dist.new_group(list(range(world)), backend="gloo") if cuda else None
+    return lay, CommandMirror(rank, world, host_group)
+
+
+def build_engine(args, layout=None):
+    """-> (engine, tokenizer, model name).  Shared by generate / chat / serve / bench-interactive.  `layout`
+    (parallel.layout.ParallelLayout): build this rank's shard of a tensor / pipeline parallel replica."""
     import torch
 
     from ..models import config as C
@@ -58,9 +94,19 @@ def build_engine(args):
         return _build_v4_engine(args, dev)
     else:
         cfg = C.PRESETS[args.preset]()
+        tp_rank, tp_world = (layout.tp_rank, layout.tp_size) if layout is not None else (0, 1)
+        staged = layout is not None and layout.pp is not None
+        from ..parallel.pp import stage_range, stage_weights
         weights = W.random_weights(cfg, device=dev, dtype=torch.bfloat16 if dev != "cpu" else torch.float32,
-                                   seed=args.seed, fast_device_init=dev != "cpu")
+                                   seed=args.seed, fast_device_init=dev != "cpu", tp_rank=tp_rank, tp_world=tp_world,
+                                   weight_format=getattr(args, "weight_format", "bf16"),
+                                   layer_range=stage_range(cfg.n_layers, layout.pp_rank, layout.pp_size)
+                                   if (staged and dev != "cpu") else None)
+        if staged:
+            weights = stage_weights(weights, layout.pp_rank, layout.pp_size)
         name = cfg.name
+    if layout is not None and args.model_dir:
+        raise SystemExit("checkpoint directories load on one rank; multi-rank launches take --preset")
     cfg = weights.cfg
     ctx = min(args.ctx_size, cfg.max_position)
     pages_per_seq = (ctx + args.page_size - 1) // args.page_size
@@ -70,7 +116,10 @@ def build_engine(args):
     else:
         n_pages = args.max_seqs * pages_per_seq + 8
     runner = DeepSeekRunner(weights, n_pages=n_pages, page_size=args.page_size, max_rows=args.max_batch_tokens,
-                            max_seqs=args.max_seqs, max_seq_len=pages_per_seq * args.page_size, device=dev)
+                            max_seqs=args.max_seqs, max_seq_len=pages_per_seq * args.page_size, device=dev,
+                            tp=layout.tp if layout is not None else None, pp=layout.pp if layout is not None else None)
+    if layout is not None and layout.tp is not None and str(dev) != "cpu":
+        layout.tp.attach(runner.fwd)
     sched = SchedulerConfig(max_active_sequences=args.max_seqs, max_decode_batch=args.max_seqs,
                             max_batch_tokens=args.max_batch_tokens, prefill_chunk_size=args.prefill_chunk,
                             ctx_size=pages_per_seq * args.page_size)
@@ -285,9 +334,20 @@ def cmd_serve(args) -> int:
     init_tracing()
     start_periodic_dump()
     holder = {}
+    layout, mirror = replica_layout(args)
+    if mirror is not None and not mirror.is_leader:
+        # a follower rank of the replica: same engine, driven by the leader's command stream
+        from ..parallel.mirror import follower_loop
+        eng, _, _ = build_engine(args, layout)
+        steps = follower_loop(eng, mirror)
+        print(json.dumps({"follower": mirror.rank, "steps": steps}), flush=True)
+        return 0
 
     def factory():
-        eng, tok, name = build_engine(args)
+        if layout is not None and str(args.device).startswith("cuda"):
+            import torch
+            torch.cuda.set_device(torch.device(args.device))     # the worker thread needs the rank's device current
+        eng, tok, name = build_engine(args, layout)
         holder["tok"], holder["name"] = tok, name
         return eng
     # the engine is built on the worker thread (it owns the CUDA context and every graph)
@@ -295,7 +355,7 @@ def cmd_serve(args) -> int:
     tok = load_tokenizer(args.model_dir)
     worker = ModelWorker(factory, tok, WorkerConfig(command_queue=args.command_queue, event_queue=args.event_queue,
                                                     admission_timeout_s=args.admission_timeout),
-                         model_name=args.served_name or args.preset).start()
+                         model_name=args.served_name or args.preset, mirror=mirror).start()
     print(json.dumps({"serving": holder.get("name"), "host": args.host, "port": args.port}), flush=True)
     serve(worker, args.host, args.port, args.served_name or holder.get("name"))
     return 0

@@ -20,7 +20,7 @@ checkpoints follows the HuggingFace DeepSeek layout (see `families.py`).
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import Dict, List, Optional
+from typing import Dict, List, Optional, Tuple
 
 import torch
 
@@ -351,21 +351,28 @@ def _layer_random(cfg: ModelConfig, layer: int, init: _Init, tp_rank: int, tp_wo
 
 def random_weights(cfg: ModelConfig, device="cpu", dtype=torch.bfloat16, seed: int = 0, std: float = 0.02,
                    tp_rank: int = 0, tp_world: int = 1, fast_device_init: bool = False,
-                   weight_format: str = "bf16", replicate_shared: bool = False) -> ModelWeights:
+                   weight_format: str = "bf16", replicate_shared: bool = False,
+                   layer_range: Optional[Tuple[int, int]] = None) -> ModelWeights:
     """Random-init weights N(0, std), norms = 1.
 
     fast_device_init draws on the GPU (much faster for multi-GB models; values then differ
     between TP layouts, which is fine for throughput runs but not for parity tests).
+    layer_range (lo, hi): build only these layers (a pipeline stage of a model whose whole image does not fit one
+    GPU); the other entries of `layers` are None and the draws differ from the full image's, so it needs
+    fast_device_init.
     """
+    if layer_range is not None and not fast_device_init:
+        raise ValueError("layer_range skips draws: use it with fast_device_init only")
     init = _Init(seed, std, device, dtype, fast_device_init)
     embed = init.normal(cfg.vocab_size, cfg.hidden)
+    lo_l, hi_l = layer_range if layer_range is not None else (0, cfg.n_layers)
     # quantise layer by layer so that at most one layer exists in bf16 at a time
     layers = [quantize_layer_(_layer_random(cfg, i, init, tp_rank, tp_world, replicate_shared=replicate_shared),
-                              weight_format) for i in range(cfg.n_layers)]
+                              weight_format) if lo_l <= i < hi_l else None for i in range(cfg.n_layers)]
     v_lo, v_hi = _shard_range(cfg.vocab_size, tp_rank, tp_world)
     lm_head = init.normal(cfg.vocab_size, cfg.hidden)[v_lo:v_hi].contiguous()
     mtp = []
-    for m in range(cfg.n_mtp_layers):
+    for m in range(cfg.n_mtp_layers if layer_range is None else 0):
         mtp.append(MtpWeights(enorm=init.ones(cfg.hidden), hnorm=init.ones(cfg.hidden),
                               eh_proj=init.normal(cfg.hidden, 2 * cfg.hidden),
                               layer=quantize_layer_(_layer_random(cfg, cfg.n_layers + m, init, tp_rank, tp_world,

@@ -108,8 +108,14 @@ class _Live:
 
 class ModelWorker:
     def __init__(self, engine_factory: Callable[[], Engine], tokenizer, cfg: Optional[WorkerConfig] = None,
-                 model_name: str = "ferrule"):
+                 model_name: str = "ferrule", mirror=None):
+        """`mirror` (parallel.mirror.CommandMirror, leader side): this worker's engine is one rank of a replica
+        spread over several ranks; every command it applies and every step it takes is published to the others,
+        and nothing changes the engine outside that stream (a slow consumer's cancel is queued, not applied)."""
         self.cfg = cfg or WorkerConfig()
+        self.mirror = mirror
+        self._tick_log: List[tuple] = []
+        self._deferred_cancels: List[str] = []
         self.tokenizer, self.model_name = tokenizer, model_name
         self._factory = engine_factory
         self.engine: Optional[Engine] = None
@@ -210,6 +216,7 @@ class ModelWorker:
             lv = self._live.get(cmd[1])
             if lv is not None and not lv.done:
                 self.engine.cancel_request(cmd[1])
+                self._tick_log.append(("cancel", cmd[1]))
             return True
         _, rid, text, token_ids, max_tokens, stop, ignore_eos, session_id, stream, reply = cmd
         try:
@@ -230,6 +237,7 @@ class ModelWorker:
             self._reply(reply, stream, exc=WorkerError(f"internal error: {type(e).__name__}: {e}", 500,
                                                        "internal_error"))
             return True
+        self._tick_log.append(("submit", rid, ids, max_tokens, list(stop or []), ignore_eos, session_id))
         self._live[rid] = _Live(stream, IncrementalDecodeState(self.tokenizer), time.monotonic())
         METRICS.add(requests_started=1, prompt_tokens=len(ids))
         log_event(REQUEST_LOG, "admitted", request_id=rid, prompt_tokens=len(ids), max_tokens=max_tokens)
@@ -245,7 +253,14 @@ class ModelWorker:
             lv.tokens += 1
             METRICS.add(generated_tokens=1)
             if not lv.stream.offer(StreamEvent("token", text=delta, token=ev.token)):
-                self.engine.cancel_request(ev.request_id)        # slow or vanished consumer
+                # slow or vanished consumer
+                if self.mirror is None:
+                    self.engine.cancel_request(ev.request_id)
+                else:                                            # through the command stream, so every rank sees it
+                    try:
+                        self._cmds.put_nowait(("cancel", ev.request_id))
+                    except queue.Full:
+                        self._deferred_cancels.append(ev.request_id)
         elif isinstance(ev, FinishEvent):
             lv.done = True
             tail = "" if self.engine.detokenize is not None else lv.decoder.finish()
@@ -297,8 +312,17 @@ class ModelWorker:
                     break
             if not running:
                 break
+            while self._deferred_cancels:
+                self._handle(("cancel", self._deferred_cancels.pop()))
             progressed = False
-            if self._fatal is None:
+            stepping = self._fatal is None
+            if self.mirror is not None:
+                # followers step exactly when the leader does: skip the idle polls, publish the rest
+                stepping = stepping and (bool(self._tick_log) or self.engine.has_work())
+                if stepping:
+                    self.mirror.publish(self._tick_log)
+            self._tick_log = []
+            if stepping:
                 try:
                     progressed = self.engine.step(self._emit)
                     self.steps += 1
@@ -309,6 +333,11 @@ class ModelWorker:
             if not progressed and took == 0 and not self.engine.has_work():
                 self.hub.wait(ticket, self.cfg.idle_wait_s)
         # drain: cancel everything, let transactions end
+        if self.mirror is not None:
+            try:
+                self.mirror.shutdown()
+            except Exception:  # noqa: BLE001 - the other ranks may be gone already
+                log.exception("mirror shutdown failed")
         try:
             for _ in range(1000):
                 if self.engine.shutdown():

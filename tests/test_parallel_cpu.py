@@ -165,3 +165,63 @@ def test_engine_over_two_pipeline_stages_streams_the_single_process_tokens():
         dist.destroy_process_group()
     ''', 2, 29613)
     assert p.stdout.count("PPE_OK") == 2, p.stdout[-2000:] + p.stderr[-3000:]
+
+
+def test_serving_replica_over_two_tensor_parallel_ranks_mirrors_the_command_stream():
+    """The serving worker on rank 0 and a follower on rank 1, each with its shard of a tensor-parallel model
+    (reference forward, gloo): submissions and a cancellation reach both engines in the same order, both take
+    the same steps, and the follower's token streams equal what the leader streamed to its clients."""
+    p = _run('''
+        import argparse, asyncio, json, torch, torch.distributed as dist
+        from ferrule_b200.cli.main import _add_model_args, build_engine, replica_layout
+        from ferrule_b200.parallel.mirror import follower_loop
+        from ferrule_b200.runtime.engine import TokenEvent, FinishEvent
+        from ferrule_b200.server.worker import ModelWorker, WorkerConfig
+        from ferrule_b200.utils.tokenizer import load_tokenizer
+        ap = argparse.ArgumentParser(); _add_model_args(ap)
+        args = ap.parse_args(["--preset", "tiny-fixture", "--device", "cpu", "--max-seqs", "4", "--ctx-size", "256",
+                              "--page-size", "16", "--max-batch-tokens", "64", "--prefill-chunk", "32"])
+        layout, mirror = replica_layout(args)
+        assert layout.tp_size == 2 and layout.pp is None
+        if not mirror.is_leader:
+            eng, _, _ = build_engine(args, layout)
+            seen = {}
+            def sink(ev):
+                if isinstance(ev, TokenEvent):
+                    seen.setdefault(ev.request_id, []).append(ev.token)
+            steps = follower_loop(eng, mirror, sink)
+            out = [None, None]
+            dist.all_gather_object(out, {"steps": steps, "tokens": seen})
+        else:
+            tok = load_tokenizer(None)
+            worker = ModelWorker(lambda: build_engine(args, layout)[0], tok, WorkerConfig(), mirror=mirror).start()
+            async def one(i, n_out, cancel_after=None):
+                g = torch.Generator().manual_seed(i)
+                ids = torch.randint(0, 200, (17 + 9 * i,), generator=g).tolist()
+                st = await worker.submit(text=None, token_ids=ids, max_tokens=n_out, stop=[], ignore_eos=True)
+                toks = []
+                while True:
+                    ev = await st.next()
+                    if ev.kind == "token" and ev.token is not None:
+                        toks.append(ev.token)
+                        if cancel_after is not None and len(toks) == cancel_after:
+                            worker.cancel(st.request_id)
+                    elif ev.kind in ("finish", "error"):
+                        return st.request_id, toks, ev.kind
+            async def all_():
+                return await asyncio.gather(one(0, 6), one(1, 9), one(2, 40, cancel_after=3))
+            res = asyncio.run(all_())
+            worker.stop()
+            steps = worker.steps
+            out = [None, None]
+            dist.all_gather_object(out, {"steps": steps, "tokens": {r: t for r, t, _ in res}})
+            lead, foll = out[0], out[1]
+            ok = lead["steps"] == foll["steps"] and len(lead["tokens"]) == 3
+            for rid, toks in lead["tokens"].items():
+                # the follower may see a few more tokens of the cancelled request than the client read
+                ok = ok and foll["tokens"].get(rid, [])[:len(toks)] == toks and len(toks) >= 3
+            ok = ok and [len(t) for t in lead["tokens"].values()][:2] == [6, 9]
+            print("MIRROR_OK" if ok else "MIRROR_BAD", json.dumps(out), flush=True)
+        dist.destroy_process_group()
+    ''', 2, 29617)
+    assert "MIRROR_OK" in p.stdout, p.stdout[-2000:] + p.stderr[-3000:]
