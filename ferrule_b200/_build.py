@@ -29,6 +29,7 @@ CUDA_SOURCES = [
     "gemm_fp8.cu",
     "gemm_mxfp4.cu",
     "mla_attention.cu",
+    "mla_prefill_tc.cu",
     "elementwise.cu",
     "data_movers.cu",
     "quant.cu",

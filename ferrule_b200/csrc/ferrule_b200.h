@@ -149,6 +149,32 @@ typedef struct FbAttnArgs {
 
 int fb_mla_attention(const FbAttnArgs* args, void* stream);
 
+// ---- prefill attention on tcgen05 (128-row tiles of (position, head) pairs of one sequence) ----
+typedef struct FbPrefillAttnArgs {
+  const void* q;            // bf16 [rows, heads, 576] contiguous (ldq == heads * 576)
+  const void* kv;           // bf16 [pool_rows, 576] (one layer of the pool)
+  void* out;                // bf16 [rows, heads, 512]
+  const int* tiles;         // [n_tiles, 4]: sequence, first query row, query rows (<= 128 / heads, consecutive
+                            //   positions of that sequence), position of the first row; 16-byte aligned
+  const int* block_table;   // [num_seqs, max_blocks]
+  const float* sink;        // optional [heads]
+  void* status;
+  long long ldq;
+  long long ldo;
+  long long pool_rows;
+  int n_tiles;
+  int rows;
+  int heads;                // must divide 128
+  int kv_lora;              // 512
+  int rope_dim;             // 64
+  int num_seqs;
+  int max_blocks;
+  int page_size;            // power of two >= 8
+  float softmax_scale;
+} FbPrefillAttnArgs;
+
+int fb_mla_prefill_tc(const FbPrefillAttnArgs* args, void* stream);
+
 // ---- small fused operators ------------------------------------------------------------
 int fb_embedding(const int* ids, const void* table, void* out, int rows, int dim, int vocab,
                  void* status, void* stream);

@@ -45,6 +45,9 @@ class DeviceBatch:
     n_rows: int
     n_logit: int
     decode_only: bool = False   # every sequence has exactly one row (a plain decode step)
+    tc_tiles: Optional[torch.Tensor] = None     # [cap, 4] int32 tiles of the tensor-core prefill attention kernel
+    n_tc_tiles: int = 0
+    rest_ranges: Optional[list] = None          # (first row, end row) ranges the tiles do not cover
 
 
 class KvPool:
@@ -473,14 +476,23 @@ class CudaForward:
             main.wait_stream(self.prep_stream)
         # verification batches (a few rows per decoding sequence) must take the same split path as plain
         # decode steps: equal split boundaries give bit-equal merges, hence the same greedy tokens
-        use_split = ws.attn_splits > 1 and T <= 4 * ws.decode_rows
         cluster = ws.attn_splits in (2, 4, 8)       # splits merge through distributed shared memory
-        K.mla_attention(q_full, self.pool.layer(layer), b.block_table, b.row_seq, b.row_pos,
-                        self.pool.page_size, lora, rope, cfg.softmax_scale, ws.o_lat[:T],
-                        splits=ws.attn_splits if use_split else 1,
-                        split_tokens=self.split_tokens if use_split else (1 << 30) // 64 * 64,
-                        ws=ws.attn_ws if (use_split and not cluster) else None, sink=lw.attn_sink,
-                        decode_only=b.decode_only)
+        ranges = [(0, T)]
+        if b.n_tc_tiles:
+            # sequences with many query rows: 128-row tiles on the tensor cores; the rest (decode and
+            # verification rows of a mixed batch, short tails) keep the row-tile kernel
+            K.mla_prefill_tc(q_full, self.pool.layer(layer), b.block_table, b.tc_tiles, b.n_tc_tiles,
+                             self.pool.page_size, lora, rope, cfg.softmax_scale, ws.o_lat[:T], sink=lw.attn_sink)
+            ranges = b.rest_ranges
+        for r0, r1 in ranges:
+            n = r1 - r0
+            use_split = ws.attn_splits > 1 and n <= 4 * ws.decode_rows
+            K.mla_attention(q_full[r0:r1], self.pool.layer(layer), b.block_table, b.row_seq[r0:r1], b.row_pos[r0:r1],
+                            self.pool.page_size, lora, rope, cfg.softmax_scale, ws.o_lat[r0:r1],
+                            splits=ws.attn_splits if use_split else 1,
+                            split_tokens=self.split_tokens if use_split else (1 << 30) // 64 * 64,
+                            ws=ws.attn_ws if (use_split and not cluster) else None, sink=lw.attn_sink,
+                            decode_only=b.decode_only)
         K.gemm(ws.o_lat[:T].view(T, -1), lw.w_uv, out=ws.attn_out[:T], x_group_koff=lora, out_group_coff=vd)
         return ws.attn_out[:T]
 

@@ -11,6 +11,7 @@ cuda_cache.rs:3539-3700.
 """
 from __future__ import annotations
 
+import os
 import time
 from dataclasses import dataclass
 from typing import Dict, List, Optional, Sequence
@@ -31,13 +32,22 @@ class BatchStaging:
     """Pinned host mirror + device buffer of one packed batch; tensors of `DeviceBatch` are views.
 
     Layout (int32 words): write_slot (int64, 2R) | token_ids R | positions R | row_seq R | row_pos R |
-    logit_rows R | block_table S*MB.
+    logit_rows R | block_table S*MB | prefill attention tiles 4*TC (only with tc_heads).
+
+    tc_heads > 0: sequences that bring at least `tc_min_rows` query rows are cut into the 128-row tiles of the
+    tensor-core prefill attention kernel (128 / tc_heads positions x all heads); the other rows - decode rows,
+    verification rows, short chunk tails - stay with the row-tile kernel, whose split boundaries make a
+    verification row bit-equal to the decode row of the same position.
     """
 
-    def __init__(self, rows: int, seqs: int, max_blocks: int, device):
+    def __init__(self, rows: int, seqs: int, max_blocks: int, device, tc_heads: int = 0, tc_min_rows: int = 16):
         self.rows, self.seqs, self.max_blocks = rows, seqs, max_blocks
         R = rows
-        self.words = 7 * R + seqs * max_blocks
+        self.tc_heads, self.tc_min_rows = tc_heads, tc_min_rows
+        self.tile_cap = (R // (128 // tc_heads) + seqs + 1) if tc_heads else 0
+        self.tile_off = (7 * R + seqs * max_blocks + 3) // 4 * 4          # 16-byte aligned
+        self.words = self.tile_off + 4 * self.tile_cap
+        self.n_tiles, self.rest_ranges = 0, None
         cuda = torch.device(device).type == "cuda"
         self.host = torch.zeros(self.words, dtype=torch.int32)
         if cuda:
@@ -48,11 +58,13 @@ class BatchStaging:
         o = 2 * R
         self.np_ids, self.np_pos, self.np_seq, self.np_rpos, self.np_lrows = (
             self.np[o + i * R:o + (i + 1) * R] for i in range(5))
-        self.np_bt = self.np[o + 5 * R:].reshape(seqs, max_blocks)
+        self.np_bt = self.np[o + 5 * R:o + 5 * R + seqs * max_blocks].reshape(seqs, max_blocks)
+        self.np_tiles = self.np[self.tile_off:self.tile_off + 4 * self.tile_cap].reshape(self.tile_cap, 4)
         d = self.dev
         self.d_slot = d[:2 * R].view(torch.int64)
         self.d_ids, self.d_pos, self.d_seq, self.d_rpos, self.d_lrows = (d[o + i * R:o + (i + 1) * R] for i in range(5))
-        self.d_bt = d[o + 5 * R:].view(seqs, max_blocks)
+        self.d_bt = d[o + 5 * R:o + 5 * R + seqs * max_blocks].view(seqs, max_blocks)
+        self.d_tiles = d[self.tile_off:self.tile_off + 4 * self.tile_cap].view(self.tile_cap, 4)
         self.cuda = cuda
         self._arange = np.arange(R, dtype=np.int32)
 
@@ -88,6 +100,14 @@ class BatchStaging:
                 self.np_bt[i, :s.block_len] = b.block_ids[s.block_start:s.block_start + s.block_len]
         lrows = b.logit_rows()
         self.np_lrows[:len(lrows)] = lrows
+        self.n_tiles, self.rest_ranges = 0, None
+        if self.tc_heads and n != T and any(s.query_len >= self.tc_min_rows for s in seqs):
+            from ..ops.kernels import prefill_tiles
+            tiles, rest = prefill_tiles([(i, s.query_start, s.query_len, int(b.positions[s.query_start]))
+                                         for i, s in enumerate(seqs)], self.tc_heads, self.tc_min_rows)
+            if len(tiles) <= self.tile_cap:
+                self.np_tiles[:len(tiles)] = tiles
+                self.n_tiles, self.rest_ranges = len(tiles), rest
         return T, R, lrows
 
     def upload(self) -> int:
@@ -96,8 +116,11 @@ class BatchStaging:
         return self.words * 4
 
     def device_batch(self, R: int, n_logit: int) -> DeviceBatch:
-        return DeviceBatch(self.d_ids[:R], self.d_pos[:R], self.d_slot[:R], self.d_seq[:R], self.d_rpos[:R],
-                           self.d_bt, self.d_lrows, R, n_logit)
+        db = DeviceBatch(self.d_ids[:R], self.d_pos[:R], self.d_slot[:R], self.d_seq[:R], self.d_rpos[:R],
+                         self.d_bt, self.d_lrows, R, n_logit)
+        if self.n_tiles:
+            db.tc_tiles, db.n_tc_tiles, db.rest_ranges = self.d_tiles, self.n_tiles, self.rest_ranges
+        return db
 
 
 @dataclass
@@ -163,7 +186,12 @@ class DeepSeekRunner(ModelRunner):
                 self.provider = ArenaProvider(self.arena, self.cfg.name)
         self.use_graphs = use_graphs and self.is_cuda
         self.stats = RunnerStats()
-        self.staging = BatchStaging(max_rows, max_seqs, self.max_blocks, self.device)
+        tc_heads = 0
+        if self.is_cuda and pp is None and os.environ.get("FERRULE_PREFILL_TC", "1") != "0":
+            from ..ops.kernels import prefill_tc_supported
+            if prefill_tc_supported(weights.heads_local, self.cfg.kv_lora_rank, self.cfg.qk_rope_dim, page_size):
+                tc_heads = weights.heads_local
+        self.staging = BatchStaging(max_rows, max_seqs, self.max_blocks, self.device, tc_heads=tc_heads)
         if self.is_cuda:
             # a verification batch asks for logits on the anchor and on every draft row of each sequence
             logit_rows = max(max_seqs, 1) * (1 + (max_draft if weights.mtp and enable_mtp else 0))

@@ -71,6 +71,16 @@ class AttnArgs(C.Structure):
     ]
 
 
+class PrefillAttnArgs(C.Structure):
+    _fields_ = [
+        ("q", C.c_void_p), ("kv", C.c_void_p), ("out", C.c_void_p), ("tiles", C.c_void_p),
+        ("block_table", C.c_void_p), ("sink", C.c_void_p), ("status", C.c_void_p),
+        ("ldq", C.c_longlong), ("ldo", C.c_longlong), ("pool_rows", C.c_longlong),
+        ("n_tiles", C.c_int), ("rows", C.c_int), ("heads", C.c_int), ("kv_lora", C.c_int), ("rope_dim", C.c_int),
+        ("num_seqs", C.c_int), ("max_blocks", C.c_int), ("page_size", C.c_int), ("softmax_scale", C.c_float),
+    ]
+
+
 _lock = threading.Lock()
 _lib: Optional[C.CDLL] = None
 _tried = False
@@ -81,6 +91,8 @@ def _declare(lib: C.CDLL) -> None:
     lib.fb_status_bytes.restype = i
     lib.fb_gemm_bf16.argtypes = [C.POINTER(GemmArgs), vp]
     lib.fb_mla_attention.argtypes = [C.POINTER(AttnArgs), vp]
+    lib.fb_mla_prefill_tc.argtypes = [C.POINTER(PrefillAttnArgs), vp]
+    lib.fb_mla_prefill_tc.restype = i
     lib.fb_embedding.argtypes = [vp, vp, vp, i, i, i, vp, vp]
     lib.fb_add_rmsnorm.argtypes = [vp, ll, vp, ll, vp, vp, ll, vp, ll, i, i, f, vp]
     lib.fb_mla_prep.argtypes = [vp, ll, i, vp, ll, i, i, i, vp, f, vp, vp, i, vp, vp, vp, ll, vp,

@@ -416,6 +416,54 @@ class AttnWorkspace:
     merge_ctr: Optional[torch.Tensor] = None      # zeroed int32 [max_rows * head blocks]: in-kernel merge
 
 
+def prefill_tiles(segments, heads: int, min_rows: int = 1):
+    """Tile table of `mla_prefill_tc` and what is left for the row-tile kernel.
+
+    segments: (sequence index, first query row, query rows, position of the first row) per sequence of the batch,
+    in row order.  Sequences with at least `min_rows` rows are cut into tiles of 128 / heads consecutive
+    positions; -> (tiles [n, 4] int32 numpy array sorted by KV length, longest first, and the list of
+    (first row, end row) ranges of the other sequences, merged where adjacent)."""
+    import numpy as np
+    G = 128 // heads
+    tiles, rest = [], []
+    for seq, r0, n, p0 in segments:
+        if n >= min_rows:
+            for o in range(0, n, G):
+                tiles.append((seq, r0 + o, min(G, n - o), p0 + o))
+        elif rest and rest[-1][1] == r0:
+            rest[-1] = (rest[-1][0], r0 + n)
+        else:
+            rest.append((r0, r0 + n))
+    tiles.sort(key=lambda t: -(t[3] + t[2]))
+    return np.asarray(tiles, dtype=np.int32).reshape(-1, 4), rest
+
+
+def prefill_tc_supported(heads: int, kv_lora: int, rope_dim: int, page_size: int) -> bool:
+    return (kv_lora == 512 and rope_dim == 64 and 0 < heads <= 128 and 128 % heads == 0
+            and page_size >= 8 and page_size & (page_size - 1) == 0)
+
+
+def mla_prefill_tc(q: torch.Tensor, kv_layer: torch.Tensor, block_table: torch.Tensor, tiles: torch.Tensor,
+                   n_tiles: int, page_size: int, kv_lora: int, rope_dim: int, scale: float, out: torch.Tensor,
+                   sink: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Prefill attention on tcgen05: q [rows, heads, 576] bf16 contiguous, tiles [>= n_tiles, 4] int32 on the
+    device (see `prefill_tiles`); rows that no tile covers are left untouched in `out` [rows, heads, 512]."""
+    lib = get_lib(True)
+    rows, heads, D = q.shape
+    assert D == kv_lora + rope_dim and q.is_contiguous() and tiles.dtype == torch.int32 and tiles.stride(-1) == 1
+    a = _lib.PrefillAttnArgs()
+    a.q, a.kv, a.out, a.tiles = q.data_ptr(), kv_layer.data_ptr(), out.data_ptr(), tiles.data_ptr()
+    a.block_table, a.sink = block_table.data_ptr(), ptr(sink)
+    a.status = status_tensor(q.device).data_ptr()
+    a.ldq, a.ldo = q.stride(0), out.stride(0)
+    a.pool_rows = kv_layer.numel() // D
+    a.n_tiles, a.rows, a.heads, a.kv_lora, a.rope_dim = n_tiles, rows, heads, kv_lora, rope_dim
+    a.num_seqs, a.max_blocks, a.page_size = block_table.shape[0], block_table.shape[1], page_size
+    a.softmax_scale = scale
+    check(lib.fb_mla_prefill_tc(C.byref(a), stream_ptr()), "fb_mla_prefill_tc")
+    return out
+
+
 def mla_attention(q: torch.Tensor, kv_layer: torch.Tensor, block_table: torch.Tensor,
                   row_seq: torch.Tensor, row_pos: torch.Tensor, page_size: int, kv_lora: int,
                   rope_dim: int, scale: float, out: torch.Tensor, *, splits: int = 1,

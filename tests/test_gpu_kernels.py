@@ -290,6 +290,62 @@ def test_mla_attention(K, heads, dl, dr, page, ctx, qps, splits, st, sink):
         _attn_case(K, heads, dl, dr, page, ctx, qps, splits, st, sink, cluster=True)
 
 
+@pytest.mark.parametrize("heads,page,segs,sink", [
+    (16, 64, [(0, 200), (37, 129), (500, 64), (0, 5)], False),      # (context before the chunk, chunk rows)
+    (16, 16, [(0, 70), (100, 33)], True),
+    (8, 64, [(64, 300)], False),
+    (128, 64, [(0, 40), (90, 7)], False),
+    (32, 128, [(300, 260), (0, 1)], True),
+])
+def test_mla_prefill_tc_matches_reference_and_the_row_tile_kernel(K, heads, page, segs, sink):
+    """tcgen05 prefill attention (128-row tiles, P from TMEM, V as the MN-major view of the KV tile) against the
+    fp32 reference; chunks that start mid-sequence, partial tiles, pages smaller and larger than the KV tile."""
+    dl, dr = 512, 64
+    D = dl + dr
+    S = len(segs)
+    total = [c + n for c, n in segs]
+    max_blocks = (max(total) + page - 1) // page + 1
+    n_pages = S * max_blocks + 3
+    g = torch.Generator(device="cuda").manual_seed(11)
+    pool = (torch.randn(n_pages * page, D, generator=g, device="cuda") * 0.5).to(torch.bfloat16)
+    bt = torch.randperm(n_pages, generator=g, device="cuda")[: S * max_blocks].to(torch.int32).view(S, max_blocks)
+    # pages past a sequence's end hold ids that must never be dereferenced
+    for s_, t in enumerate(total):
+        bt[s_, (t + page - 1) // page:] = -1
+    bt = bt.contiguous()
+    row_seq, row_pos, segments, r0 = [], [], [], 0
+    for s_, (c, n) in enumerate(segs):
+        segments.append((s_, r0, n, c))
+        row_seq += [s_] * n
+        row_pos += list(range(c, c + n))
+        r0 += n
+    rows = r0
+    row_seq = torch.tensor(row_seq, dtype=torch.int32, device="cuda")
+    row_pos = torch.tensor(row_pos, dtype=torch.int32, device="cuda")
+    q = (torch.randn(rows, heads, D, generator=g, device="cuda") * 0.5).to(torch.bfloat16)
+    sk = torch.randn(heads, generator=g, device="cuda") if sink else None
+    scale = 1.0 / math.sqrt(dl // 4 + dr)
+    tiles_np, rest = K.prefill_tiles(segments, heads)
+    assert rest == [] and K.prefill_tc_supported(heads, dl, dr, page)
+    tiles = torch.from_numpy(tiles_np).cuda()
+    out = torch.full((rows, heads, dl), 7.0, dtype=torch.bfloat16, device="cuda")
+    K.mla_prefill_tc(q, pool, bt, tiles, tiles.shape[0], page, dl, dr, scale, out, sink=sk)
+    assert K._lib.read_status()[0] == 0
+    expect = ref.mla_paged_attention(q, pool, bt.clamp(min=0), row_seq, row_pos, page, dl, scale, sink=sk)
+    close(out, expect, rtol=2e-2, atol=1e-2)
+    legacy = torch.zeros_like(out)
+    K.mla_attention(q, pool, bt, row_seq, row_pos, page, dl, dr, scale, legacy, sink=sk)
+    close(out, legacy, rtol=2e-2, atol=1e-2)
+    # a row's result does not depend on its tile mates: cut the same rows into other tiles
+    tiles2_np, _ = K.prefill_tiles([(s_, r, 1, p_) for s_, r_, n, p_0 in segments[:1]
+                                    for r, p_ in zip(range(r_, r_ + min(n, 9)), range(p_0, p_0 + min(n, 9)))], heads)
+    out2 = torch.zeros_like(out)
+    t2 = torch.from_numpy(tiles2_np).cuda()
+    K.mla_prefill_tc(q, pool, bt, t2, t2.shape[0], page, dl, dr, scale, out2, sink=sk)
+    n9 = min(segs[0][1], 9)
+    assert torch.equal(out2[:n9], out[:n9])
+
+
 def test_mla_prep(K):
     rows, heads, qhd, lora, rope = 11, 16, 192, 512, 64
     D = lora + rope
