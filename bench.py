@@ -190,6 +190,15 @@ def main() -> None:
     # synthetic prompts: token ids uniform over the vocabulary, identical on every rank
     g = torch.Generator().manual_seed(1234)
     prompts = torch.randint(0, cfg.vocab_size, (B, P), generator=g)
+    # warm-up wave: the same number of prompts of the same length (other tokens), two output tokens each, so that
+    # the first-token latency below is not the cost of loading every kernel for the first time
+    warm = torch.randint(0, cfg.vocab_size, (B, P), generator=g)
+    for i in range(B):
+        engine.submit(GenerateRequest(f"warm{i}", warm[i].tolist(), max_new_tokens=2, ignore_eos=True))
+    engine.run_until_idle(lambda ev: None)
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
     t_submit = time.perf_counter()
     for i in range(B):
         engine.submit(GenerateRequest(f"req{i}", prompts[i].tolist(), max_new_tokens=k_total + Wm + margin, ignore_eos=True))

@@ -572,6 +572,60 @@ moe_plan_wide_kernel(const int* __restrict__ topk_idx, const float* __restrict__
   }
 }
 
+// A second row-tile table over an existing plan's expert-major rows with another tile height: the two grouped
+// GEMMs of a layer need not share one (the plain store / scatter GEMM takes 256-row tiles, the SwiGLU GEMM keeps
+// two accumulators and stops at 128).  One warp; expert counts come from the plan.
+__global__ void __launch_bounds__(32)
+moe_retile_kernel(const int* __restrict__ counts, int local, int ntok, int* __restrict__ tile_group,
+                  int* __restrict__ tile_row0, int* __restrict__ tile_rows, int max_tiles, int* __restrict__ meta,
+                  DeviceStatus* st) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int lane = threadIdx.x;
+  int c[8], rows_sum = 0, tiles_sum = 0;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const int e = lane * 8 + j;
+    c[j] = e < local ? counts[e] : 0;
+    rows_sum += c[j];
+    tiles_sum += (c[j] + ntok - 1) / ntok;
+  }
+  int row_off = rows_sum, tile_off = tiles_sum;
+#pragma unroll
+  for (int d = 1; d < 32; d <<= 1) {
+    const int r = __shfl_up_sync(0xffffffffu, row_off, d);
+    const int t = __shfl_up_sync(0xffffffffu, tile_off, d);
+    if (lane >= d) { row_off += r; tile_off += t; }
+  }
+  const int total_rows = __shfl_sync(0xffffffffu, row_off, 31);
+  int total_tiles = __shfl_sync(0xffffffffu, tile_off, 31);
+  row_off -= rows_sum;
+  tile_off -= tiles_sum;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const int e = lane * 8 + j;
+    if (e < local) {
+      for (int r0 = 0; r0 < c[j]; r0 += ntok) {
+        if (tile_off < max_tiles) {
+          tile_group[tile_off] = e;
+          tile_row0[tile_off] = row_off + r0;
+          tile_rows[tile_off] = min(ntok, c[j] - r0);
+        }
+        ++tile_off;
+      }
+      row_off += c[j];
+    }
+  }
+  if (lane == 0) {
+    if (total_tiles > max_tiles) {
+      report_status(st, kStatusBadShape, 0x31, total_tiles, max_tiles);
+      total_tiles = max_tiles;
+    }
+    meta[0] = total_tiles;
+    meta[1] = total_rows;
+  }
+}
+
 // ---------------------------------------------------------------------------------
 // Fused router for decode-sized batches: router logits (x . W_e, fp32 accumulate) + scoring +
 // top-k per token (one CTA per token), then the CTA that finishes last builds the MoE plan.
@@ -1248,6 +1302,15 @@ extern "C" int fb_moe_plan(const int* topk_idx, const float* topk_w, int routes,
     launch_pdl(moe_plan_kernel, dim3(1), dim3(1024), 0, static_cast<cudaStream_t>(stream),
         topk_idx, topk_w, routes, topk, e_lo, e_hi, ntok, dst_slots < topk ? topk : dst_slots, o,
         static_cast<DeviceStatus*>(status));
+  return FB_CHECK_LAUNCH();
+}
+
+extern "C" int fb_moe_retile(const int* counts, int local_experts, int ntok, int* tile_group, int* tile_row0,
+                             int* tile_rows, int max_tiles, int* meta, void* status, void* stream) {
+  if (!counts || !tile_group || !tile_row0 || !tile_rows || !meta) return FB_ERR_SHAPE;
+  if (local_experts <= 0 || local_experts > 256 || ntok <= 0 || max_tiles <= 0) return FB_ERR_SHAPE;
+  launch_pdl(moe_retile_kernel, dim3(1), dim3(32), 0, static_cast<cudaStream_t>(stream), counts, local_experts, ntok,
+             tile_group, tile_row0, tile_rows, max_tiles, meta, static_cast<DeviceStatus*>(status));
   return FB_CHECK_LAUNCH();
 }
 

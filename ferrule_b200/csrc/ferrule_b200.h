@@ -195,6 +195,9 @@ int fb_moe_plan(const int* topk_idx, const float* topk_w, int routes, int topk, 
                 int ntok, int dst_slots, int* src_token, int* dst_row, float* row_scale, int* tile_group,
                 int* tile_row0, int* tile_rows, int max_tiles, int* counts, int* meta, void* status,
                 void* stream);
+// second tile table (another tile height) over the expert-major rows of a plan whose counts are on the device
+int fb_moe_retile(const int* counts, int local_experts, int ntok, int* tile_group, int* tile_row0, int* tile_rows,
+                  int max_tiles, int* meta, void* status, void* stream);
 int fb_router_plan_fused(const void* x, long long ldx, const void* w, int hidden, const float* bias,
                          const long long* hash_table, const int* token_ids, int rows, int experts,
                          int topk, int score_fn, int n_groups, int topk_groups, int normalize,

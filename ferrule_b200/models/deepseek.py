@@ -609,7 +609,9 @@ class CudaForward:
                                 route_scale=cfg.route_scale, hash_table=lw.hash_table, token_ids=b.token_ids,
                                 dst_slots=ws.slots)
         else:
-            K.gemm(xn, lw.router_w, out=ws.router_logits[:T])
+            # one or two weight tiles: narrow row tiles so that the rows spread over the whole GPU
+            K.gemm(xn, lw.router_w, out=ws.router_logits[:T],
+                   ntok=32 if (T >= 1024 and lw.router_w.shape[0] <= 256) else None)
             K.router_topk(ws.router_logits[:T], k, cfg.score_fn, bias=lw.router_bias, n_groups=cfg.n_groups,
                           topk_groups=cfg.topk_groups, normalize=cfg.norm_topk_prob, route_scale=cfg.route_scale,
                           hash_table=lw.hash_table, token_ids=b.token_ids, out_idx=idx, out_w=wts)
@@ -621,9 +623,14 @@ class CudaForward:
         self._gemm(ws.xg[:T * k], lw.e_w13, ws.hmid[:T * k], slot="xg", epilogue=K.EPI_SWIGLU, plan=plan,
                    act_limit=cfg.swiglu_limit)
         route_out = ws.route_out[:T]
+        plan2 = plan
+        if (not isinstance(lw.e_w2, QuantWeight) and ntok == 128
+                and T * k >= 160 * (self.w.e_hi - self.w.e_lo)):
+            # prefill-sized expert loads: the scatter GEMM keeps one accumulator and takes 256-row tiles
+            plan2 = ws.plans256 = K.moe_retile(plan, 256, getattr(ws, "plans256", None))
         # route r = t*k + s is written to row t*slots + s (the plan kernel emits that row index)
         self._gemm(ws.hmid[:T * k], lw.e_w2, route_out.view(T * ws.slots, H), slot="hmid", epilogue=K.EPI_SCATTER,
-                   plan=plan, scatter_rows=T * ws.slots)
+                   plan=plan2, scatter_rows=T * ws.slots)
         if side is not None:
             torch.cuda.current_stream().wait_stream(side)
         return idx

@@ -213,6 +213,27 @@ def moe_plan(topk_idx: torch.Tensor, topk_w: Optional[torch.Tensor], plan: MoePl
     return plan
 
 
+def moe_retile(plan: MoePlan, ntok: int, tiles: Optional[MoePlan] = None) -> MoePlan:
+    """A view of `plan` (same expert-major rows, scales and destinations) with row tiles of height `ntok`:
+    fills and returns `tiles` (allocated on first use when None)."""
+    lib = get_lib(True)
+    local = plan.counts.shape[0]
+    if tiles is None:
+        max_tiles = (plan.cap_rows + ntok - 1) // ntok + local
+        i32 = dict(dtype=torch.int32, device=plan.counts.device)
+        tiles = MoePlan(ntok, max_tiles, plan.cap_rows, plan.src_token, plan.dst_row, plan.row_scale,
+                        torch.zeros(max_tiles, **i32), torch.zeros(max_tiles, **i32), torch.zeros(max_tiles, **i32),
+                        plan.counts, torch.zeros(2, **i32))
+    lib.fb_moe_retile.restype = C.c_int
+    lib.fb_moe_retile.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int,
+                                  C.c_void_p, C.c_void_p, C.c_void_p]
+    check(lib.fb_moe_retile(plan.counts.data_ptr(), local, ntok, tiles.tile_group.data_ptr(),
+                            tiles.tile_row0.data_ptr(), tiles.tile_rows.data_ptr(), tiles.max_tiles,
+                            tiles.meta.data_ptr(), status_tensor(plan.counts.device).data_ptr(), stream_ptr()),
+          "fb_moe_retile")
+    return tiles
+
+
 def l2_prefetch(t: torch.Tensor, nbytes: int) -> None:
     """Ask the memory system to pull the first `nbytes` of `t` into L2 (asynchronous, on the current stream)."""
     lib = get_lib(True)

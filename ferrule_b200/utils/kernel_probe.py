@@ -185,7 +185,13 @@ def case_prefill(reps):
     slot = (bt[seq.long(), (pos // page).long()].long() * page + (pos % page).long())
     b = D.DeviceBatch(torch.randint(0, cfg.vocab_size, (T,), **i32), pos, slot, seq, pos.clone(), bt,
                       torch.arange(S, **i32) * P + P - 1, T, S)
-    return timed(lambda i: fwd.forward(b), reps), {"tokens": T}
+    import os
+    tc = os.environ.get("FERRULE_PREFILL_TC", "1") != "0"
+    if tc:      # what the runner's batch staging adds for sequences with many query rows
+        from ferrule_b200.ops import kernels as K
+        tiles, rest = K.prefill_tiles([(i, i * P, P, 0) for i in range(S)], w.heads_local)
+        b.tc_tiles, b.n_tc_tiles, b.rest_ranges = torch.from_numpy(tiles).to(DEV), len(tiles), rest
+    return timed(lambda i: fwd.forward(b), reps), {"tokens": T, "attention": "tcgen05 tiles" if tc else "row tiles"}
 
 
 def case_v3_fp8_decode(reps):

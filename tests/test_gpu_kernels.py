@@ -180,6 +180,29 @@ def test_moe_grouped_pipeline(K, T, E, topk, e_lo, e_hi, ntok, H, I):
     close(out, expect, rtol=3e-2, atol=3e-2)
 
 
+def test_moe_retile_gives_the_scatter_gemm_taller_tiles(K):
+    """A second tile table (256-row tiles) over a 128-row plan: same expert-major rows, fewer tiles, and the
+    scatter GEMM over it writes exactly what it writes over the original table."""
+    T, E, topk, H, I = 700, 8, 2, 512, 384
+    idx, w, plan = _route_setup(K, T, E, topk, 0, E, 128)
+    slots = topk + 1
+    K.moe_plan(idx, w, plan, 0, E, dst_slots=slots)
+    tall = K.moe_retile(plan, 256)
+    counts = plan.counts.cpu()
+    n2 = int(tall.meta[0])
+    assert n2 == int(((counts + 255) // 256).sum()) and int(tall.meta[1]) == int(counts.sum())
+    assert int(tall.tile_rows[:n2].sum()) == int(counts.sum()) and n2 < int(plan.meta[0])
+    hmid = rnd(T * topk, I)
+    w2 = rnd(E, H, I, scale=0.03)
+    a = torch.zeros(T * slots, H, dtype=torch.bfloat16, device="cuda")
+    b = torch.zeros_like(a)
+    K.gemm(hmid, w2, out=a, epilogue=K.EPI_SCATTER, plan=plan)
+    K.gemm(hmid, w2, out=b, epilogue=K.EPI_SCATTER, plan=tall)
+    assert torch.equal(a, b)
+    again = K.moe_retile(plan, 256, tall)
+    assert again is tall and int(tall.meta[0]) == n2
+
+
 @pytest.mark.parametrize("score_fn,bias,groups,tg,norm", [(0, False, 1, 1, False), (1, True, 8, 4, True),
                                                          (2, True, 1, 1, True), (1, False, 1, 1, True)])
 def test_router_topk(K, score_fn, bias, groups, tg, norm):
