@@ -19,6 +19,7 @@
 // norm_kernel :651-712, rope_kernel :714-768, router_kernel :793-884,
 // expert_group_route_plan_kernel :1382-1513, moe_kernel :1515-1612, data_kernel :478-629
 // (crates/ferrule-backend/native/cuda/implementations/portable/entrypoints.cu).
+#include "codec.cuh"
 #include "common.cuh"
 #include "ferrule_b200.h"
 #include "launch.cuh"
@@ -64,7 +65,8 @@ add_rmsnorm_kernel(const __nv_bfloat16* __restrict__ x, long long ldx,
                    const __nv_bfloat16* __restrict__ delta, long long ldd,
                    const __nv_bfloat16* __restrict__ weight, __nv_bfloat16* __restrict__ res_out,
                    long long ldr, __nv_bfloat16* __restrict__ norm_out, long long ldn, int rows,
-                   int dim, float eps) {
+                   int dim, float eps, uint8_t* __restrict__ q_out, long long ldq,
+                   uint8_t* __restrict__ q_scale, long long lds, int q_block) {
   pdl_launch_dependents();
   pdl_wait();
   __shared__ float red[8];
@@ -109,6 +111,24 @@ add_rmsnorm_kernel(const __nv_bfloat16* __restrict__ x, long long ldx,
 #pragma unroll
     for (int j = 0; j < 8; ++j) o[j] = __float2bfloat16_rn(row[i + j] * inv * __bfloat162float(wp[j]));
     *reinterpret_cast<uint4*>(norm_out + r * ldn + i) = *reinterpret_cast<uint4*>(o);
+    if (q_out != nullptr) {
+      // the consumer is a block-scaled GEMM: the codes and scales of the normalised row, exactly what the row
+      // quantiser would make of norm_out.  A scale block is 128 elements (16 lanes x 8) or 32 (4 lanes x 8);
+      // dim % 128 == 0, so the lanes of a block always run the same iterations.
+      float amax = 0.f;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(__bfloat162float(o[j])));
+      const int glanes = q_block / 8;
+      const uint32_t grp = (glanes == 16 ? 0xffffu : 0xfu) << (threadIdx.x & 31 & ~(glanes - 1));
+      for (int d = glanes / 2; d >= 1; d >>= 1) amax = fmaxf(amax, __shfl_xor_sync(grp, amax, d));
+      const uint8_t sb = fp8_block_scale(amax);
+      const float sinv = 1.f / e8m0_to_float(sb);
+      uint8_t c[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) c[j] = to_e4m3(__bfloat162float(o[j]) * sinv);
+      *reinterpret_cast<uint2*>(q_out + r * ldq + i) = *reinterpret_cast<uint2*>(c);
+      if ((threadIdx.x & (glanes - 1)) == 0) q_scale[r * lds + i / q_block] = sb;
+    }
   }
 }
 
@@ -1243,8 +1263,19 @@ extern "C" int fb_embedding(const int* ids, const void* table, void* out, int ro
 extern "C" int fb_add_rmsnorm(const void* x, long long ldx, const void* delta, long long ldd,
                               const void* weight, void* res_out, long long ldr, void* norm_out,
                               long long ldn, int rows, int dim, float eps, void* stream) {
+  return fb_add_rmsnorm_q(x, ldx, delta, ldd, weight, res_out, ldr, norm_out, ldn, rows, dim, eps, nullptr, 0, nullptr, 0,
+                          128, stream);
+}
+
+extern "C" int fb_add_rmsnorm_q(const void* x, long long ldx, const void* delta, long long ldd,
+                                const void* weight, void* res_out, long long ldr, void* norm_out,
+                                long long ldn, int rows, int dim, float eps, void* q_out, long long ldq,
+                                void* q_scale, long long lds, int q_block, void* stream) {
   if (rows <= 0 || dim % 8 != 0 || dim > 16384) return FB_ERR_SHAPE;
   if ((ldx | ldd | ldr | ldn) % 8 != 0) return FB_ERR_ALIGN;
+  if (q_out != nullptr && (!q_scale || !norm_out || dim % 128 != 0 || ldq % 8 != 0 || (q_block != 128 && q_block != 32) ||
+                           (reinterpret_cast<uintptr_t>(q_out) & 7)))
+    return FB_ERR_SHAPE;
   static bool attr = false;
   if (!attr) {
     cudaFuncSetAttribute(add_rmsnorm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 65536);
@@ -1253,7 +1284,8 @@ extern "C" int fb_add_rmsnorm(const void* x, long long ldx, const void* delta, l
   launch_pdl(add_rmsnorm_kernel, dim3(rows), dim3(256), dim * sizeof(float), static_cast<cudaStream_t>(stream), 
       static_cast<const __nv_bfloat16*>(x), ldx, static_cast<const __nv_bfloat16*>(delta), ldd,
       static_cast<const __nv_bfloat16*>(weight), static_cast<__nv_bfloat16*>(res_out), ldr,
-      static_cast<__nv_bfloat16*>(norm_out), ldn, rows, dim, eps);
+      static_cast<__nv_bfloat16*>(norm_out), ldn, rows, dim, eps, static_cast<uint8_t*>(q_out), ldq,
+      static_cast<uint8_t*>(q_scale), lds, q_block);
   return FB_CHECK_LAUNCH();
 }
 

@@ -109,6 +109,10 @@ typedef struct FbGemmFp8Args {
   float act_limit;
   int scale_group32;        // 1: w_scale is UE8M0 [groups, w_rows_per_group, k/32] (MXFP4 values in e4m3 containers)
   void* status;
+  const int* slot_cnt;      // static row slots instead of a tile table: group g owns rows [g * slot_rows,
+  int slot_rows;            //   (g + 1) * slot_rows), slot_cnt[g] of them filled (slot_rows % ntok == 0)
+  void* out_scale;          // non-null: `out` gets e4m3 codes (ldo in bytes) and this UE8M0 [rows, ldos] the scale
+  long long ldos;           //   of every 1 x 128 output block (store and swiglu epilogues, n_out % 128 == 0)
 } FbGemmFp8Args;
 
 int fb_gemm_fp8(const FbGemmFp8Args* args, void* stream);
@@ -181,6 +185,12 @@ int fb_embedding(const int* ids, const void* table, void* out, int rows, int dim
 int fb_add_rmsnorm(const void* x, long long ldx, const void* delta, long long ldd,
                    const void* weight, void* res_out, long long ldr, void* norm_out, long long ldn,
                    int rows, int dim, float eps, void* stream);
+// the same, and the normalised rows once more as e4m3 codes q_out [rows, dim] + UE8M0 q_scale [rows, dim / q_block],
+// q_block 128 (bit-equal to fb_quant_fp8_rows of norm_out) or 32 (fb_quant_mxfp8_rows); dim % 128 == 0
+int fb_add_rmsnorm_q(const void* x, long long ldx, const void* delta, long long ldd,
+                     const void* weight, void* res_out, long long ldr, void* norm_out, long long ldn,
+                     int rows, int dim, float eps, void* q_out, long long ldq, void* q_scale, long long lds,
+                     int q_block, void* stream);
 int fb_mla_prep(const void* q, long long ldq, int q_head_dim, const void* ckv, long long ldckv,
                 int heads, int kv_lora, int rope_dim, const void* kv_norm_w, float eps,
                 const float* cos_t,
@@ -331,6 +341,8 @@ typedef struct FbGemmMxfp4Args {
   float act_limit;
   void* status;
   int w_tiled;              // w is tile-major: [groups][ceil(rows/128)][k/128][128 rows][64 bytes] (rows padded to 128)
+  int w_fp8;                // weights are e4m3 bytes [groups, rows, k] (ldw_bytes = bytes per row) instead of packed e2m1;
+                            //   w_sf has the same per-32 layout (128 x 128 block scales replicated)
 } FbGemmMxfp4Args;
 int fb_gemm_mxfp4(const FbGemmMxfp4Args* args, void* stream);
 // linear UE8M0 weight scales [groups, rows, k / 32] -> [groups, ceil(rows / 128), k / 128, 512] blocks for the kernel

@@ -22,6 +22,7 @@
 #include <cuda.h>
 #include <cstdlib>
 
+#include "codec.cuh"
 #include "common.cuh"
 #include "ferrule_b200.h"
 #include "launch.cuh"
@@ -56,7 +57,36 @@ struct Params {
   float act_limit;
   DeviceStatus* status;
   int w_stream;              // weights are read once by this launch: L2 evict-first loads
+  // static row slots (decode-sized MoE batches): group g owns rows [g * slot_rows, (g + 1) * slot_rows) and
+  // slot_cnt[g] of them are filled; the tile table is implied (slot_rows / NTOK tiles per group)
+  const int* slot_cnt;
+  int slot_rows;
+  // quantised output: `out` receives e4m3 codes, out_scale[row * ldos + n / 128] the UE8M0 scale of each
+  // 1 x 128 block (what quant_fp8_rows would make of the bf16 output)
+  uint8_t* out_scale;
+  long long ldos;
+  int red_bytes;             // bytes of the split-K area (the amax exchange area follows it)
 };
+
+// (group, first row, valid rows) of row tile m
+template <int NTOK>
+__device__ __forceinline__ void tile_of(const Params& p, int m, int& g, int& row0, int& rows) {
+  if (p.slot_rows > 0) {
+    const int per = p.slot_rows / NTOK;
+    g = m / per;
+    const int sub = m - g * per;
+    row0 = g * p.slot_rows + sub * NTOK;
+    rows = min(max(p.slot_cnt[g] - sub * NTOK, 0), NTOK);
+  } else if (p.tile_group != nullptr) {
+    g = p.tile_group[m];
+    row0 = p.tile_row0[m];
+    rows = min(p.tile_rows[m], NTOK);
+  } else {
+    g = 0;
+    row0 = m * NTOK;
+    rows = min(NTOK, p.dense_rows - row0);
+  }
+}
 
 __device__ __forceinline__ float e8m0(uint8_t b) {
   return b == 0 ? __uint_as_float(1u << 22) : __uint_as_float(static_cast<uint32_t>(b) << 23);
@@ -130,8 +160,9 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
   if (S > 1) cluster_sync_all();     // the leader's barrier is initialised before any peer arrives on it
   pdl_wait();
 
-  const bool grouped = p.tile_group != nullptr;
-  const int num_tok_tiles = grouped ? min(*p.num_tok_tiles, p.max_tok_tiles) : (p.dense_rows + NTOK - 1) / NTOK;
+  const bool grouped = p.tile_group != nullptr || p.slot_rows > 0;
+  const int num_tok_tiles = p.slot_rows > 0 ? p.max_tok_tiles
+                            : grouped ? min(*p.num_tok_tiles, p.max_tok_tiles) : (p.dense_rows + NTOK - 1) / NTOK;
   const int total = num_tok_tiles * p.n_tiles;
   const int kblocks = (p.k + kBlockK - 1) / kBlockK;
   const int tile_first = blockIdx.x / S, tile_stride = gridDim.x / S;
@@ -147,8 +178,9 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
       const uint64_t wpol = l2_policy_evict_first();
       for (int t = tile_first; t < total && ok; t += tile_stride) {
         const int m = t / p.n_tiles, nt = t - m * p.n_tiles;
-        const int g = grouped ? p.tile_group[m] : 0;
-        const int row0 = grouped ? p.tile_row0[m] : m * NTOK;
+        int g, row0, rows_t;
+        tile_of<NTOK>(p, m, g, row0, rows_t);
+        if (rows_t <= 0) continue;          // an expert without rows: its weights are not streamed
         for (int kb = kb_begin; kb < kb_end; ++kb) {
           ok = mbar_wait(&empty_bar[s], ph ^ 1u, abort_flag, p.status, 0x800);
           if (!ok) break;
@@ -185,6 +217,11 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
       long long kbg = 0;    // k-blocks issued by this CTA: selects the TMEM buffer and its phase
       bool ok = true;
       for (int t = tile_first; t < total && ok; t += tile_stride) {
+        {
+          int g, row0, rows_t;
+          tile_of<NTOK>(p, t / p.n_tiles, g, row0, rows_t);
+          if (rows_t <= 0) continue;
+        }
         for (int kb = kb_begin; kb < kb_end; ++kb, ++kbg) {
           const int a = static_cast<int>(kbg % C::kRing);
           const uint32_t aph = static_cast<uint32_t>((kbg / C::kRing) & 1);
@@ -220,9 +257,9 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
     uint32_t red_phase = 0;
     for (int t = tile_first; t < total && ok; t += tile_stride) {
       const int m = t / p.n_tiles, nt = t - m * p.n_tiles;
-      const int g = grouped ? p.tile_group[m] : 0;
-      const int row0 = grouped ? p.tile_row0[m] : m * NTOK;
-      const int rows = grouped ? min(p.tile_rows[m], NTOK) : min(NTOK, p.dense_rows - row0);
+      int g, row0, rows;
+      tile_of<NTOK>(p, m, g, row0, rows);
+      if (rows <= 0) continue;
       const int n = nt * kTileN + ch;
       // activation scales of this tile -> shared memory (rows beyond the tile read as scale 0)
       asm volatile("bar.sync 1, 128;" ::: "memory");
@@ -310,7 +347,39 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
           }
         }
       }
-      if (n < p.n_out) {
+      if (p.out_scale != nullptr) {
+        // quantised output: the 128 channels of this tile are one scale block of every row.  Values are rounded
+        // to bf16 first, so codes and scales equal those of a bf16 store followed by the row quantiser.
+        float* am = reinterpret_cast<float*>(xs_tile + p.xs_bytes + p.red_bytes);      // [4 warps][NTOK]
+#pragma unroll
+        for (int j = 0; j < NTOK; ++j) {
+          float x = acc[j];
+          if (DUAL) {
+            float up = accu[j];
+            if (p.act_limit > 0.f) {
+              x = fminf(x, p.act_limit);
+              up = fminf(fmaxf(up, -p.act_limit), p.act_limit);
+            }
+            x = silu(x) * up;
+          }
+          x = (j < rows && n < p.n_out) ? bf16_round(x) : 0.f;
+          acc[j] = x;
+          const float v = warp_max(fabsf(x));
+          if (lane == 0) am[q * NTOK + j] = v;
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+#pragma unroll
+        for (int j = 0; j < NTOK; ++j) {
+          if (j < rows) {
+            const float amax = fmaxf(fmaxf(am[j], am[NTOK + j]), fmaxf(am[2 * NTOK + j], am[3 * NTOK + j]));
+            const uint8_t sb = fp8_block_scale(amax);
+            const long long orow = row0 + j;
+            if (n < p.n_out) reinterpret_cast<uint8_t*>(p.out)[orow * p.ldo + n] = to_e4m3(acc[j] / e8m0_to_float(sb));
+            if (ch == 0) p.out_scale[orow * p.ldos + nt] = sb;
+          }
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+      } else if (n < p.n_out) {
 #pragma unroll
         for (int j = 0; j < NTOK; ++j) {
           if (j < rows) {
@@ -392,7 +461,7 @@ static int launch(const CUtensorMap& mw, const CUtensorMap& mx, Params p, int ma
   // Split-K over a cluster for dense GEMMs with few tiles (decode-sized projections): every tile gets its own
   // cluster, each CTA keeps at least 4 k-blocks, and the reduction area must leave room for two pipeline stages.
   int split = 1;
-  const bool grouped = p.tile_group != nullptr;
+  const bool grouped = p.tile_group != nullptr || p.slot_rows > 0;
   constexpr int kAcc = NTOK * (DUAL ? 2 : 1);
   if (!grouped) {
     for (int sp = 2; sp <= 4; sp *= 2) {
@@ -402,12 +471,14 @@ static int launch(const CUtensorMap& mw, const CUtensorMap& mx, Params p, int ma
     }
   }
   const int red_bytes = split > 1 ? (split - 1) * kAcc * 512 : 0;
-  int stages = (kLimit - 2048 - xs_bytes - red_bytes) / C::kStageBytes;
+  int stages = (kLimit - 2048 - xs_bytes - red_bytes - 4 * NTOK * 4) / C::kStageBytes;
   if (stages > 10) stages = 10;
   if (stages < 2) return FB_ERR_SHAPE;
   p.stages = stages;
   p.xs_bytes = xs_bytes;
-  const size_t smem = static_cast<size_t>(stages) * C::kStageBytes + 1024 + 256 + xs_bytes + red_bytes;
+  p.red_bytes = red_bytes;
+  const size_t smem = static_cast<size_t>(stages) * C::kStageBytes + 1024 + 256 + xs_bytes + red_bytes +
+                      (p.out_scale ? 4 * NTOK * sizeof(float) : 0);
   int clusters = max_tiles < sms / split ? (max_tiles < 1 ? 1 : max_tiles) : sms / split;
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3(clusters * split, 1, 1);
@@ -441,8 +512,13 @@ extern "C" int fb_gemm_fp8(const FbGemmFp8Args* a, void* stream_) {
   const bool dual = a->epilogue == 1;
   if (a->ntok != 16 && a->ntok != 32 && a->ntok != 64) return FB_ERR_SHAPE;
   if (dual && (a->ntok > 32 || a->dual_offset % 128 != 0)) return FB_ERR_SHAPE;
-  const bool grouped = a->tile_group != nullptr;
-  if (grouped && (!a->tile_row0 || !a->tile_rows || !a->num_tok_tiles || a->max_tok_tiles <= 0)) return FB_ERR_SHAPE;
+  const bool slots = a->slot_rows > 0;
+  if (slots && (!a->slot_cnt || a->tile_group || a->slot_rows % a->ntok != 0 ||
+                static_cast<long long>(a->groups) * a->slot_rows > a->x_rows))
+    return FB_ERR_SHAPE;
+  if (a->out_scale && (a->epilogue == 2 || a->out_fp32 || a->scale_group32 || a->n_out % 128 != 0)) return FB_ERR_SHAPE;
+  const bool grouped = a->tile_group != nullptr || slots;
+  if (a->tile_group && (!a->tile_row0 || !a->tile_rows || !a->num_tok_tiles || a->max_tok_tiles <= 0)) return FB_ERR_SHAPE;
   if (!grouped && a->groups != 1) return FB_ERR_SHAPE;
   CUtensorMap mw, mx;
   int rc = make_map_u8(&mw, a->w, a->k, a->w_rows_per_group, a->groups, a->ldw, a->w_group_stride, kTileN, 3);
@@ -455,7 +531,11 @@ extern "C" int fb_gemm_fp8(const FbGemmFp8Args* a, void* stream_) {
   p.n_tiles = (a->n_out + kTileN - 1) / kTileN;
   p.dual_offset = a->dual_offset;
   p.dense_rows = a->x_rows;
-  p.max_tok_tiles = a->max_tok_tiles;
+  p.max_tok_tiles = slots ? a->groups * (a->slot_rows / a->ntok) : a->max_tok_tiles;
+  p.slot_cnt = a->slot_cnt;
+  p.slot_rows = slots ? a->slot_rows : 0;
+  p.out_scale = static_cast<uint8_t*>(a->out_scale);
+  p.ldos = a->ldos;
   p.tile_group = a->tile_group;
   p.tile_row0 = a->tile_row0;
   p.tile_rows = a->tile_rows;
@@ -481,7 +561,7 @@ extern "C" int fb_gemm_fp8(const FbGemmFp8Args* a, void* stream_) {
     p.w_stream = enabled && (grouped ? a->ntok <= 64 : a->x_rows <= 256);
   }
   const int kblocks = (a->k + kBlockK - 1) / kBlockK;
-  const int tok_tiles = grouped ? a->max_tok_tiles : (a->x_rows + a->ntok - 1) / a->ntok;
+  const int tok_tiles = grouped ? p.max_tok_tiles : (a->x_rows + a->ntok - 1) / a->ntok;
   const int max_tiles = tok_tiles * p.n_tiles;
   const bool g32 = a->scale_group32 != 0;
   if (g32 && (a->k % 128 != 0 || a->ntok > 32)) return FB_ERR_SHAPE;

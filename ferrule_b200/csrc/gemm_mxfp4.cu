@@ -68,6 +68,7 @@ struct Params {
   DeviceStatus* status;
   int w_stream;
   int w_tx_bytes;              // bytes one weight-tile load completes on its barrier
+  int a_fmt;                   // element format of the weights in the instruction descriptor: 5 = e2m1, 0 = e4m3
   int w_tiled;                 // weights stored tile-major: [groups][128-row tiles][k-blocks][128 rows][64 bytes]
   int sfb_bytes;               // one activation-scale buffer in shared memory
   int sfb_cols;                // TMEM columns of the activation scales of one tile
@@ -121,8 +122,8 @@ __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t by
 
 // instruction descriptor of the block-scaled kinds: A e2m1 (5), B e4m3 (0), both K-major, UE8M0 scales,
 // scale-factor byte ids of A and B (which of the four bytes of a TMEM scale column this K = 32 slice uses)
-__device__ __forceinline__ uint32_t mx_idesc(uint32_t n, uint32_t a_sf_id, uint32_t b_sf_id) {
-  return (b_sf_id << 4) | (5u << 7) | (0u << 10) | ((n >> 3) << 17) | (1u << 23) | ((kTileN >> 4) << 24) |
+__device__ __forceinline__ uint32_t mx_idesc(uint32_t n, uint32_t a_sf_id, uint32_t b_sf_id, uint32_t a_fmt) {
+  return (b_sf_id << 4) | (a_fmt << 7) | (0u << 10) | ((n >> 3) << 17) | (1u << 23) | ((kTileN >> 4) << 24) |
          (a_sf_id << 29);
 }
 
@@ -285,7 +286,7 @@ gemm_mxfp4_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_const
           for (int kk = 0; kk < kBlockK / kUmmaK; ++kk) {
             const uint32_t koff = kk * kUmmaK;     // bytes: one 8-bit slot per element in shared memory
             const uint64_t db = umma_desc_k128(sx + koff);
-            const uint32_t idesc = mx_idesc(NTOK, kk, kk);
+            const uint32_t idesc = mx_idesc(NTOK, kk, kk, static_cast<uint32_t>(p.a_fmt));
             const uint32_t acc = (kb > 0 || kk) ? 1u : 0u;
             umma_mx(d0, umma_desc_k128(sw + koff), db, idesc, acc, tmem_sfa, tsfb);
             if (DUAL) umma_mx(d0 + NTOK, umma_desc_k128(sw + C::kWBytes + koff), db, idesc, acc, tmem_sfa + 4, tsfb);
@@ -576,7 +577,12 @@ extern "C" int fb_gemm_mxfp4(const FbGemmMxfp4Args* a, void* stream_) {
   CUtensorMap mw, mxm;
   // packed 4-bit weights: dimensions count values, strides are bytes (half a byte per value)
   int rc;
-  if (a->w_tiled) {
+  if (a->w_fp8) {
+    // e4m3 weights (one byte per value) under the same per-32 scale layout: a plain byte map, no unpacking
+    if (a->w_tiled) return FB_ERR_SHAPE;
+    rc = make_map(&mw, CU_TENSOR_MAP_DATA_TYPE_UINT8, a->w, a->k, a->w_rows_per_group, a->groups,
+                  static_cast<uint64_t>(a->ldw_bytes), static_cast<uint64_t>(a->w_group_stride_bytes), kTileN, 3, 16);
+  } else if (a->w_tiled) {
     const uint64_t tiles = static_cast<uint64_t>(a->groups) * ((a->w_rows_per_group + kTileN - 1) / kTileN) * (a->k / kBlockK);
     rc = make_map(&mw, CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, a->w, kBlockK, tiles * kTileN, 1, kBlockK / 2,
                   tiles * kTileN * (kBlockK / 2), kTileN, 3, 32);
@@ -622,7 +628,8 @@ extern "C" int fb_gemm_mxfp4(const FbGemmMxfp4Args* a, void* stream_) {
   }
   // a weight-tile load reports the bytes it read from global memory (half a byte per value) on its barrier, not
   // the bytes it spread over shared memory
-  p.w_tx_bytes = kTileN * kBlockK / 2;
+  p.w_tx_bytes = a->w_fp8 ? kTileN * kBlockK : kTileN * kBlockK / 2;
+  p.a_fmt = a->w_fp8 ? 0 : 5;
   p.w_tiled = a->w_tiled;
   const int tok_tiles = grouped ? a->max_tok_tiles : (a->x_rows + a->ntok - 1) / a->ntok;
   const int max_tiles = tok_tiles * p.n_tiles;

@@ -13,34 +13,12 @@
 // E8M0 / E4M3 decoders (:63-66); host codecs with the same rounding live in io/encoding.py.
 #include <cuda_fp8.h>
 
+#include "codec.cuh"
 #include "common.cuh"
 #include "ferrule_b200.h"
 #include "launch.cuh"
 
 namespace fb {
-
-__device__ __forceinline__ float e8m0_to_float(uint8_t b) {
-  // 2^(b - 127); b = 0 is the subnormal 2^-127
-  return b == 0 ? __uint_as_float(1u << 22) : __uint_as_float(static_cast<uint32_t>(b) << 23);
-}
-
-// smallest power of two >= x (x > 0) as an E8M0 byte
-__device__ __forceinline__ uint8_t e8m0_ceil(float x) {
-  const uint32_t bits = __float_as_uint(x);
-  int e = static_cast<int>((bits >> 23) & 0xff);
-  if (bits & 0x7fffffu) ++e;
-  e = max(0, min(254, e));
-  return static_cast<uint8_t>(e);
-}
-
-__device__ __forceinline__ uint8_t to_e4m3(float v) {
-  return static_cast<uint8_t>(__nv_cvt_float_to_fp8(v, __NV_SATFINITE, __NV_E4M3));
-}
-
-__device__ __forceinline__ float from_e4m3(uint8_t b) {
-  const __half_raw h = __nv_cvt_fp8_to_halfraw(b, __NV_E4M3);
-  return __half2float(*reinterpret_cast<const __half*>(&h));
-}
 
 // nearest E2M1 code (ties -> even code), magnitudes 0 .5 1 1.5 2 3 4 6
 __device__ __forceinline__ uint8_t to_e2m1(float v) {

@@ -107,7 +107,8 @@ class ReferenceForward:
         # oracle of an FP8 model: inputs of quantised linears go through the 1 x 128 FP8 round trip
         if getattr(weights, "act_quant", False):
             from ..io import encoding as enc
-            self.aq = lambda x: enc.act_dequant_fp8(*enc.act_quant_fp8(x))
+            db = getattr(weights, "dense_act_block", 128)
+            self.aq = lambda x: enc.act_dequant_fp8(*enc.act_quant_fp8(x, db), db)
             eb = getattr(weights, "expert_act_block", 128)
             self.aq_e = lambda x: enc.act_dequant_fp8(*enc.act_quant_fp8(x, eb), eb)
         else:
@@ -340,16 +341,22 @@ class CudaWorkspace:
             self.act_q["a"] = pair(R, max(cfg.q_lora_rank, hl * cfg.v_head_dim, 2 * H if w.mtp else 0))
             self.act_q["mid"] = pair(R, inter_max)
             if self.has_moe:
-                self.act_q["xg"] = pair(R * cfg.topk, H)
-                self.act_q["hmid"] = pair(R * cfg.topk, cfg.moe_inter)
-                if any(isinstance(l.e_w13, QuantWeight) and l.e_w13.native_mxfp4
-                       for l in list(w.layers) + [m.layer for m in w.mtp]):
-                    # MXFP8 activations of natively held MXFP4 experts: codes + one scale byte per 1 x 32 block
-                    def pair32(rows, width):
-                        width = (max(width, 128) + 127) // 128 * 128
-                        return torch.zeros(rows, width, **u8), torch.zeros(rows, width // 32, **u8)
+                qrows = max(R * cfg.topk, (w.e_hi - w.e_lo) * 64)       # routes, or the static decode slots
+                self.act_q["xg"] = pair(qrows, H)
+                self.act_q["hmid"] = pair(qrows, cfg.moe_inter)
+            all_layers = list(w.layers) + [m.layer for m in w.mtp]
+            if any(isinstance(v, QuantWeight) and v.native_mx for l in all_layers if l is not None
+                   for v in vars(l).values()):
+                # MXFP8 activations (codes + one scale byte per 1 x 32 block) of the linears whose weights run on
+                # the block-scaled tensor-core GEMM: natively held MXFP4 experts, FP8 weights with replicated scales
+                def pair32(rows, width):
+                    width = (max(width, 128) + 127) // 128 * 128
+                    return torch.zeros(rows, width, **u8), torch.zeros(rows, width // 32, **u8)
+                self.act_q["xn_mx"] = pair32(R, H)
+                self.act_q["a_mx"] = pair32(R, self.act_q["a"][0].shape[1])
+                self.act_q["mid_mx"] = pair32(R, inter_max)
+                if self.has_moe:
                     xrows = max(R * cfg.topk, (w.e_hi - w.e_lo) * 64)
-                    self.act_q["xn_mx"] = pair32(R, H)
                     self.act_q["xg_mx"] = pair32(xrows, H)
                     self.act_q["hmid_mx"] = pair32(xrows, cfg.moe_inter)
 
@@ -361,6 +368,11 @@ class CudaWorkspace:
                 if isinstance(t, torch.Tensor):
                     tot += t.numel() * t.element_size()
         return tot
+
+
+def cfg_inter_bad(cfg) -> bool:
+    """The quantised SwiGLU output needs whole 128-channel scale blocks."""
+    return cfg.moe_inter % 128 != 0 or cfg.hidden % 128 != 0
 
 
 class CudaForward:
@@ -380,6 +392,11 @@ class CudaForward:
         cfg = self.cfg
         import os
         attn_splits = int(os.environ.get("FERRULE_ATTN_SPLITS", attn_splits))
+        # FP8 models: activation quantisation in the producing kernels (norm -> FP8, SwiGLU -> FP8) instead of
+        # one quantiser launch per consumer
+        self.fuse_act_quant = os.environ.get("FERRULE_FUSE_ACT_QUANT", "1") != "0"
+        self.fp8_static = os.environ.get("FERRULE_FP8_STATIC", "1") != "0"
+        self._quantised = {}        # act_q slot -> (source pointer, rows, width) whose FP8 form the slot holds
         self.max_seq_len = max_seq_len
         self.split_tokens = max(64, ((max_seq_len + attn_splits - 1) // attn_splits + 63) // 64 * 64)
         self.ws = CudaWorkspace(weights, max_rows, max_logit_rows, decode_rows, attn_splits, dev)
@@ -422,6 +439,9 @@ class CudaForward:
         q, s = self.ws.act_q[slot]
         rows, n = x.shape
         q, s = q[:rows, :n], s[:rows, :n // 128]
+        done = self._quantised.get(slot)
+        if done is not None and done == (x.data_ptr(), rows, n):
+            return q, s                     # the kernel that produced `x` wrote its FP8 form as well
         self.Q.quant_fp8_rows(x, out=(q, s))
         return q, s
 
@@ -430,19 +450,69 @@ class CudaForward:
         q, s = self.ws.act_q[slot]
         rows, n = x.shape
         q, s = q[:rows, :n], s[:rows, :n // 32]
+        done = self._quantised.get(slot)
+        if done is not None and done == (x.data_ptr(), rows, n):
+            return q, s                     # the kernel that produced `x` wrote its MXFP8 form as well
         self.Q.quant_mxfp8_rows(x, out=(q, s))
         return q, s
 
+    @staticmethod
+    def _qkind(w) -> Optional[str]:
+        """How the rows feeding linear `w` are quantised: 'mx' (1 x 32, block-scaled tensor-core GEMM), 'fp8'
+        (1 x 128, FP8 GEMM that rescales k-blocks in its epilogue), None (bf16 weights or MXFP4 in containers)."""
+        if not isinstance(w, QuantWeight):
+            return None
+        if w.native_mx:
+            return "mx"
+        return None if w.group32 else "fp8"
+
+    def _norm(self, x, weight, T: int, out: torch.Tensor, slot: Optional[str], kind: Optional[str], **kw):
+        """add + RMSNorm into `out`; with `kind` (how the consuming linears take their rows, see `_qkind`) the
+        kernel also writes the rows' quantised form into the workspace pair of `slot`, and quantising `out` for
+        that slot becomes a no-op until the slot's source is rewritten."""
+        n = out.shape[1]
+        for k_ in (slot, None if slot is None else slot + "_mx"):
+            if k_ is not None:
+                self._quantised.pop(k_, None)
+        if kind is not None and slot is not None and self.fuse_act_quant and n % 128 == 0:
+            key = slot + "_mx" if kind == "mx" else slot
+            blk = 32 if kind == "mx" else 128
+            q, s = self.ws.act_q[key]
+            self.K.add_rmsnorm(x, weight, self.cfg.rms_eps, norm_out=out, quant_out=(q[:T, :n], s[:T, :n // blk]),
+                               quant_block=blk, **kw)
+            self._quantised[key] = (out.data_ptr(), T, n)
+        else:
+            self.K.add_rmsnorm(x, weight, self.cfg.rms_eps, norm_out=out, **kw)
+
     def _gemm(self, x, w, out, slot: str = "a", xq=None, **kw):
-        """bf16 weight -> bf16 tcgen05 GEMM; QuantWeight -> quantise the rows (unless `xq` is given)
-        and run the block-scaled FP8 GEMM (natively held MXFP4: MXFP8 rows and the MXFP4 GEMM)."""
-        if isinstance(w, QuantWeight) and w.native_mxfp4:
+        """bf16 weight -> bf16 tcgen05 GEMM; QuantWeight -> quantise the rows (unless `xq` is given) and run the
+        block-scaled GEMM its form takes.  `q_slot`: the consumer of `out` is a linear of the same form - leave
+        the result quantised in that workspace pair (the bf16 `out` is then not written) when the shape allows."""
+        q_slot = kw.pop("q_slot", None)
+        for k_ in (q_slot, None if q_slot is None else q_slot + "_mx"):
+            if k_ is not None:
+                self._quantised.pop(k_, None)
+        if isinstance(w, QuantWeight) and w.native_mx:
             if xq is None:
                 xq = self._quant_mx(x, slot + "_mx")
-            return self.Q.gemm_mxfp4(xq[0], xq[1], w.packed, w.sf, out=out, **kw)
+            codes, fp8 = (w.q, True) if w.packed is None else (w.packed, False)
+            if q_slot is not None and self.fuse_act_quant and out.shape[1] % 32 == 0:
+                rows, n = out.shape
+                oq, os_ = self.ws.act_q[q_slot + "_mx"]
+                self.Q.gemm_mxfp4(xq[0], xq[1], codes, w.sf, out_mx=(oq[:rows, :n], os_[:rows, :n // 32]), w_fp8=fp8, **kw)
+                self._quantised[q_slot + "_mx"] = (out.data_ptr(), rows, n)
+                return out
+            return self.Q.gemm_mxfp4(xq[0], xq[1], codes, w.sf, out=out, w_fp8=fp8, **kw)
         if isinstance(w, QuantWeight):
             if xq is None:
                 xq = self._quant(x, slot)
+            if q_slot is not None:
+                rows, n = out.shape
+                if self.fuse_act_quant and not w.group32 and n % 128 == 0:
+                    oq, os_ = self.ws.act_q[q_slot]
+                    self.Q.gemm_fp8(xq[0], xq[1], w.q, w.scale, out_q=(oq[:rows, :n], os_[:rows, :n // 128]), **kw)
+                    self._quantised[q_slot] = (out.data_ptr(), rows, n)
+                    return out
             return self.Q.gemm_fp8(xq[0], xq[1], w.q, w.scale, out=out, group32=w.group32, **kw)
         return self.K.gemm(x, w, out=out, **kw)
 
@@ -454,8 +524,10 @@ class CudaForward:
         self._gemm(xn, lw.w_qkv_a, qkv, slot="xn")
         if cfg.q_lora_rank:
             qa, ckv = qkv[:, :cfg.q_lora_rank], qkv[:, cfg.q_lora_rank:]
-            K.add_rmsnorm(qa, lw.q_norm, cfg.rms_eps, norm_out=ws.qn[:T])
+            self._norm(qa, lw.q_norm, T, ws.qn[:T], "a", self._qkind(lw.w_q_b))
             q = self._gemm(ws.qn[:T], lw.w_q_b, ws.q[:T], slot="a")
+            self._quantised.pop("a", None)          # the slot is reused for the attention output below
+            self._quantised.pop("a_mx", None)
         else:
             q, ckv = qkv[:, :hl * qhd], qkv[:, hl * qhd:]
         q_full = ws.q_full[:T]
@@ -509,8 +581,10 @@ class CudaForward:
             return 0
         if self.arena is not None and layer in self.arena.layers:
             return 0
-        if isinstance(lw.e_w13, QuantWeight) and not lw.e_w13.native_mxfp4:
-            return 0
+        if isinstance(lw.e_w13, QuantWeight) and not lw.e_w13.native_mx:
+            # plain 128 x 128 block-scaled FP8 experts take the static slots through the slot mode of the FP8 GEMM
+            if lw.e_w13.group32 or not self.fp8_static or cfg_inter_bad(self.cfg):
+                return 0
         for nt in ws.static_rows:
             if T <= nt:
                 return nt
@@ -538,7 +612,9 @@ class CudaForward:
                             hash_table=lw.hash_table, token_ids=b.token_ids, dst_slots=ws.slots,
                             norm_w=lw.ffn_norm, eps=cfg.rms_eps, delta=delta, res_out=res_out, norm_out=xn)
         # FP8 shared experts read the quantised normed rows: quantise before the fork
-        xq_n = self._quant(xn, "xn") if isinstance(lw.w13, QuantWeight) else None
+        kind13 = self._qkind(lw.w13)
+        xq_n = self._quant_mx(xn, "xn_mx") if kind13 == "mx" else (self._quant(xn, "xn") if isinstance(lw.w13, QuantWeight)
+                                                                      else None)
         if lw.w13 is not None:
             # The shared experts only need the normalised activations: fork them onto a second stream
             # (a parallel branch when captured in a graph) so they fill the SMs that the latency-bound
@@ -559,7 +635,8 @@ class CudaForward:
                     K.gemm(mid, lw.w2[:, :, i0:i0 + il], out=ws.route_out[:T][:, k])
                 else:
                     mid = ws.ffn_mid[:T, :inter]
-                    self._gemm(xn, lw.w13, mid, xq=xq_n, epilogue=K.EPI_SWIGLU, act_limit=cfg.swiglu_limit)
+                    self._gemm(xn, lw.w13, mid, xq=xq_n, epilogue=K.EPI_SWIGLU, act_limit=cfg.swiglu_limit,
+                               q_slot="mid" if self._qkind(lw.w2) == kind13 and kind13 else None)
                     self._gemm(mid, lw.w2, ws.route_out[:T][:, k], slot="mid")
                 nl = self._prefetch_next
                 if nl is not None and T <= ws.decode_rows:
@@ -568,7 +645,7 @@ class CudaForward:
                     for wt in (nl.w_qkv_a, nl.w_uk_t, nl.w_uv, nl.w_o):
                         if isinstance(wt, torch.Tensor):
                             K.l2_prefetch(wt, wt.numel() * wt.element_size())
-        if static and isinstance(lw.e_w13, QuantWeight):
+        if static and isinstance(lw.e_w13, QuantWeight) and lw.e_w13.native_mx:
             # natively held MXFP4 experts: the normalised rows are quantised to MXFP8 once, the router gathers the
             # codes and scale bytes, the gate|up epilogue re-quantises the SwiGLU product for the down projection
             plan = ws.static_plans[static][layer]
@@ -579,11 +656,35 @@ class CudaForward:
                             normalize=cfg.norm_topk_prob, route_scale=cfg.route_scale, hash_table=lw.hash_table,
                             token_ids=b.token_ids, dst_slots=ws.slots, quant_rows=(xq[0], xq[1], xgq, xgs))
             R, I = plan.cap_rows, cfg.moe_inter
-            self.Q.gemm_mxfp4(xgq[:R], xgs[:R], lw.e_w13.packed, lw.e_w13.sf, epilogue=K.EPI_SWIGLU, plan=plan,
-                              act_limit=cfg.swiglu_limit, out_mx=(hq[:R, :I], hs[:R, :I // 32]))
-            self.Q.gemm_mxfp4(hq[:R, :I], hs[:R, :I // 32], lw.e_w2.packed, lw.e_w2.sf,
+            fp8w = lw.e_w13.packed is None          # e4m3 codes with replicated block scales instead of packed e2m1
+            c13, c2 = (lw.e_w13.q, lw.e_w2.q) if fp8w else (lw.e_w13.packed, lw.e_w2.packed)
+            self.Q.gemm_mxfp4(xgq[:R], xgs[:R], c13, lw.e_w13.sf, epilogue=K.EPI_SWIGLU, plan=plan,
+                              act_limit=cfg.swiglu_limit, out_mx=(hq[:R, :I], hs[:R, :I // 32]), w_fp8=fp8w)
+            self.Q.gemm_mxfp4(hq[:R, :I], hs[:R, :I // 32], c2, lw.e_w2.sf,
                               out=ws.route_out[:T].view(T * ws.slots, H), epilogue=K.EPI_SCATTER, plan=plan,
-                              scatter_rows=T * ws.slots)
+                              scatter_rows=T * ws.slots, w_fp8=fp8w)
+            if side is not None:
+                torch.cuda.current_stream().wait_stream(side)
+            return idx
+        if static and isinstance(lw.e_w13, QuantWeight):
+            # block-scaled FP8 experts in the static slots: the router gathers the tokens' FP8 codes and scale bytes,
+            # the FP8 GEMMs walk the slots (experts without rows are skipped), the gate|up epilogue re-quantises
+            plan = ws.static_plans[static][layer]
+            xq = xq_n if (xq_n is not None and kind13 == "fp8") else self._quant(xn, "xn")
+            (xgq, xgs), (hq, hs) = ws.act_q["xg"], ws.act_q["hmid"]
+            K.router_append(xn, lw.router_w, k, cfg.score_fn, plan, self.w.e_lo, self.w.e_hi, idx, wts, None,
+                            bias=lw.router_bias, n_groups=cfg.n_groups, topk_groups=cfg.topk_groups,
+                            normalize=cfg.norm_topk_prob, route_scale=cfg.route_scale, hash_table=lw.hash_table,
+                            token_ids=b.token_ids, dst_slots=ws.slots, quant_rows=(xq[0], xq[1], xgq, xgs[:, :H // 128]))
+            R, I = plan.cap_rows, cfg.moe_inter
+            slots = (plan.counts, static)
+            # 16-row tiles inside the slots: the epilogue of the block-scaled kernel rescales every k-block of
+            # every row, so its cost follows the tile height, and most experts hold a few rows only
+            self.Q.gemm_fp8(xgq[:R, :H], xgs[:R, :H // 128], lw.e_w13.q, lw.e_w13.scale, epilogue=K.EPI_SWIGLU,
+                            slots=slots, act_limit=cfg.swiglu_limit, out_q=(hq[:R, :I], hs[:R, :I // 128]), ntok=16)
+            self.Q.gemm_fp8(hq[:R, :I], hs[:R, :I // 128], lw.e_w2.q, lw.e_w2.scale,
+                            out=ws.route_out[:T].view(T * ws.slots, H), epilogue=K.EPI_SCATTER, plan=plan,
+                            slots=slots, scatter_rows=T * ws.slots, ntok=16)
             if side is not None:
                 torch.cuda.current_stream().wait_stream(side)
             return idx
@@ -772,8 +873,10 @@ class CudaForward:
         # `first_norm_done`: the previous layer's last kernel already wrote this layer's normalised input to xn;
         # `next_norm` (single GPU): this layer's last kernel does the same for the next one
         if not first_norm_done:
-            K.add_rmsnorm(h_in, lw.attn_norm, cfg.rms_eps, norm_out=xn)
+            self._norm(h_in, lw.attn_norm, T, xn, "xn", self._qkind(lw.w_qkv_a))
         a = self._attention(lw, layer, xn, b, T)
+        # what reads the post-attention norm: the dense FFN, or the shared experts and the static FP8 expert path
+        ffn_q = self._qkind(lw.w13) or (self._qkind(lw.e_w13) if lw.is_moe else None)
         # decode-sized MoE layers: the post-attention residual add + RMSNorm runs in the router kernel's prologue
         route_norm = None
         use_ep = self._use_ep(lw, T)
@@ -784,7 +887,7 @@ class CudaForward:
             if fuse_route:
                 route_norm = (h_in, ws.delta[:T], h_out)
             else:
-                K.add_rmsnorm(h_in, lw.ffn_norm, cfg.rms_eps, delta=ws.delta[:T], res_out=h_out, norm_out=xn)
+                self._norm(h_in, lw.ffn_norm, T, xn, "xn", ffn_q, delta=ws.delta[:T], res_out=h_out)
             h_mid = h_out
         else:
             if isinstance(lw.w_o, QuantWeight):
@@ -795,7 +898,7 @@ class CudaForward:
             if fuse_route:
                 route_norm = (h_out, None, None)
             elif not use_ep:
-                K.add_rmsnorm(h_out, lw.ffn_norm, cfg.rms_eps, norm_out=xn)
+                self._norm(h_out, lw.ffn_norm, T, xn, "xn", ffn_q)
             h_mid = h_out
         if use_ep:
             # the layer's result is the gathered tensor itself (symmetric memory the peers' combine kernels wrote)
@@ -804,6 +907,8 @@ class CudaForward:
             idx = self._moe_local(lw, xn, b, T, layer, norm=route_norm)
             # slot `topk` holds the shared-expert row (zeros when the model has none)
             if tp is None and next_norm is not None:
+                self._quantised.pop("xn", None)
+                self._quantised.pop("xn_mx", None)
                 K.moe_reduce_norm(ws.route_out[:T].view(T * ws.slots, cfg.hidden), ws.slots, cfg.topk, idx,
                                   self.w.e_lo, self.w.e_hi, T, cfg.hidden, h_mid, h_in, next_norm, xn, cfg.rms_eps)
             elif tp is None:
@@ -815,12 +920,13 @@ class CudaForward:
             return h_in            # the layer's result lands back in the input buffer
         inter = lw.w13.shape[1] // 2
         mid = ws.ffn_mid[:T, :inter]
-        self._gemm(xn, lw.w13, mid, slot="xn", epilogue=K.EPI_SWIGLU, act_limit=cfg.swiglu_limit)
+        self._gemm(xn, lw.w13, mid, slot="xn", epilogue=K.EPI_SWIGLU, act_limit=cfg.swiglu_limit,
+                   q_slot="mid" if (self._qkind(lw.w2) and self._qkind(lw.w2) == self._qkind(lw.w13)) else None)
         if tp is None:
             self._gemm(mid, lw.w2, ws.delta[:T], slot="mid")
             # residual add is folded into the next consumer through a plain add+norm without a norm output
             if next_norm is not None:
-                K.add_rmsnorm(h_mid, next_norm, cfg.rms_eps, delta=ws.delta[:T], res_out=h_in, norm_out=xn)
+                self._norm(h_mid, next_norm, T, xn, "xn", self._qkind(lw.w_qkv_a), delta=ws.delta[:T], res_out=h_in)
             else:
                 K.add_rmsnorm(h_mid, None, cfg.rms_eps, delta=ws.delta[:T], res_out=h_in, want_norm=False)
         elif isinstance(lw.w2, QuantWeight):

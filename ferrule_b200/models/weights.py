@@ -20,6 +20,7 @@ checkpoints follows the HuggingFace DeepSeek layout (see `families.py`).
 from __future__ import annotations
 
 from dataclasses import dataclass, field
+import os
 from typing import Dict, List, Optional, Tuple
 
 import torch
@@ -47,6 +48,23 @@ class QuantWeight:
     @property
     def native_mxfp4(self) -> bool:
         return self.packed is not None
+
+    @property
+    def native_mx(self) -> bool:
+        """Held in a form the block-scaled tensor-core GEMM takes: packed MXFP4, or e4m3 codes whose 128 x 128
+        block scales have been replicated into the per-32 scale layout (`sf`)."""
+        return self.sf is not None
+
+    def attach_block_sf_(self) -> "QuantWeight":
+        """FP8 128 x 128 weights on a GPU: add `sf` so that the GEMM runs on the block-scaled MMA (scales applied by
+        the tensor core) instead of rescaling every k-block in the epilogue.  No-op where it does not apply."""
+        if (self.sf is None and self.packed is None and not self.group32 and self.q is not None and self.q.is_cuda
+                and self.q.shape[-1] % 128 == 0 and os.environ.get("FERRULE_FP8_NATIVE_MX", "1") != "0"):
+            from ..ops import quant as Q
+            self.sf = Q.fp8_block_sf(self.scale, self.q.shape[-2], self.q.shape[-1])
+            if self.q.dim() == 2:
+                self.sf = self.sf[0]
+        return self
 
     @property
     def shape(self):
@@ -108,7 +126,8 @@ class QuantWeight:
             qs.append(q)
             ss.append(sb)
         q, sc = torch.stack(qs).contiguous(), torch.stack(ss).contiguous()
-        return QuantWeight(q[0] if two_d else q, sc[0] if two_d else sc, fmt == "mxfp4")
+        out = QuantWeight(q[0] if two_d else q, sc[0] if two_d else sc, fmt == "mxfp4")
+        return out.attach_block_sf_() if fmt == "fp8_block" else out
 
 
 WEIGHT_FORMATS = ("bf16", "fp8_block", "fp8_mxfp4")
@@ -162,9 +181,11 @@ def dequantized_copy(w: "ModelWeights") -> "ModelWeights":
         out.mtp.append(mc)
     out.weight_format = "bf16"
     out.act_quant = w.weight_format != "bf16"
-    # natively held MXFP4 experts multiply MXFP8 activations (1 x 32 scale blocks)
-    native = any(isinstance(l.e_w13, QuantWeight) and l.e_w13.native_mxfp4 for l in w.layers)
-    out.expert_act_block = 32 if native else 128
+    # weights that run on the block-scaled tensor-core GEMM multiply MXFP8 activations (1 x 32 scale blocks)
+    def native(names):
+        return any(isinstance(getattr(l, n), QuantWeight) and getattr(l, n).native_mx for l in w.layers for n in names)
+    out.expert_act_block = 32 if native(_EXPERT_FIELDS) else 128
+    out.dense_act_block = 32 if native(_DENSE_FIELDS) else 128
     return out
 
 

@@ -151,14 +151,31 @@ def embedding(ids: torch.Tensor, table: torch.Tensor, out: Optional[torch.Tensor
 
 def add_rmsnorm(x: torch.Tensor, weight: Optional[torch.Tensor], eps: float,
                 delta: Optional[torch.Tensor] = None, res_out: Optional[torch.Tensor] = None,
-                norm_out: Optional[torch.Tensor] = None, want_norm: bool = True):
-    """(res_out, norm_out): res_out = bf16(x + delta) (if delta), norm_out = RMSNorm(res) * w."""
+                norm_out: Optional[torch.Tensor] = None, want_norm: bool = True, quant_out=None,
+                quant_block: int = 128):
+    """(res_out, norm_out): res_out = bf16(x + delta) (if delta), norm_out = RMSNorm(res) * w.
+    quant_out = (codes u8 [rows, dim], scales u8 [rows, dim / quant_block]): also the quantised form of norm_out,
+    bit-equal to `quant_fp8_rows(norm_out)` (quant_block 128) or `quant_mxfp8_rows(norm_out)` (32): the consumer
+    is a block-scaled GEMM and this saves the quantiser launch."""
     lib = get_lib(True)
     rows, dim = x.shape
     if delta is not None and res_out is None:
         res_out = torch.empty_like(x)
     if want_norm and norm_out is None:
         norm_out = torch.empty(rows, dim, dtype=torch.bfloat16, device=x.device)
+    if quant_out is not None:
+        q, sc = quant_out
+        assert want_norm and q.shape[0] >= rows and q.shape[1] == dim and sc.shape[1] >= dim // quant_block
+        lib.fb_add_rmsnorm_q.restype = C.c_int
+        lib.fb_add_rmsnorm_q.argtypes = [C.c_void_p, C.c_longlong, C.c_void_p, C.c_longlong, C.c_void_p, C.c_void_p,
+                                         C.c_longlong, C.c_void_p, C.c_longlong, C.c_int, C.c_int, C.c_float,
+                                         C.c_void_p, C.c_longlong, C.c_void_p, C.c_longlong, C.c_int, C.c_void_p]
+        check(lib.fb_add_rmsnorm_q(x.data_ptr(), x.stride(0), ptr(delta), delta.stride(0) if delta is not None else 0,
+                                   ptr(weight), ptr(res_out), res_out.stride(0) if res_out is not None else 0,
+                                   norm_out.data_ptr(), norm_out.stride(0), rows, dim, eps,
+                                   q.data_ptr(), q.stride(0), sc.data_ptr(), sc.stride(0), quant_block, stream_ptr()),
+              "fb_add_rmsnorm_q")
+        return (res_out if delta is not None else x), norm_out
     check(lib.fb_add_rmsnorm(x.data_ptr(), x.stride(0), ptr(delta), delta.stride(0) if delta is not None else 0,
                              ptr(weight), ptr(res_out), res_out.stride(0) if res_out is not None else 0,
                              ptr(norm_out) if want_norm else None,

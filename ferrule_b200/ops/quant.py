@@ -81,16 +81,22 @@ class GemmFp8Args(C.Structure):
         ("tile_group", C.c_void_p), ("tile_row0", C.c_void_p), ("tile_rows", C.c_void_p), ("num_tok_tiles", C.c_void_p),
         ("dst_row", C.c_void_p), ("row_scale", C.c_void_p), ("act_limit", C.c_float), ("scale_group32", C.c_int),
         ("status", C.c_void_p),
+        ("slot_cnt", C.c_void_p), ("slot_rows", C.c_int), ("out_scale", C.c_void_p), ("ldos", C.c_longlong),
     ]
 
 
 def gemm_fp8(xq: torch.Tensor, xs: torch.Tensor, wq: torch.Tensor, ws: torch.Tensor, out: Optional[torch.Tensor] = None,
              *, out_dtype=torch.bfloat16, epilogue: int = 0, plan=None, scatter_rows: Optional[int] = None,
-             act_limit: float = 0.0, ntok: Optional[int] = None, group32: bool = False) -> torch.Tensor:
+             act_limit: float = 0.0, ntok: Optional[int] = None, group32: bool = False,
+             slots=None, out_q=None) -> torch.Tensor:
     """Block-scaled FP8 GEMM on the tcgen05 path.
 
     xq uint8 e4m3 [rows, K] + xs UE8M0 [rows, K/128]; wq uint8 e4m3 [N, K] or [groups, N, K] + ws UE8M0
     [(groups,) ceil(N/128), ceil(K/128)].  epilogue 0 store, 1 SwiGLU (rows = [gate | up]), 2 scatter (plan).
+    slots = (counts int32 [groups], slot_rows): static row slots instead of the plan's tile table - group g owns
+    rows [g * slot_rows, (g + 1) * slot_rows), counts[g] of them are filled, groups without rows are skipped (the
+    plan still supplies the scatter tables).  out_q = (codes u8 [rows, n_out], scales u8 [rows, n_out / 128]): the
+    result leaves as 1 x 128 FP8 (what `quant_fp8_rows` makes of the bf16 result) instead of bf16.
     """
     lib = get_lib(True)
     if not hasattr(lib.fb_gemm_fp8, "_declared"):
@@ -104,7 +110,13 @@ def gemm_fp8(xq: torch.Tensor, xs: torch.Tensor, wq: torch.Tensor, ws: torch.Ten
     dual = epilogue == 1
     n_out = w_rows // 2 if dual else w_rows
     if ntok is None:
-        ntok = plan.ntok if plan is not None else (16 if rows <= 16 else (32 if (rows <= 32 or dual or group32) else 64))
+        ntok = (plan.ntok if (plan is not None and slots is None)
+                else (16 if (rows <= 16 or (slots is not None and slots[1] == 16))
+                      else (32 if (rows <= 32 or dual or group32 or slots is not None) else 64)))
+    out_s = None
+    if out_q is not None:
+        out, out_s = out_q
+        assert out.dtype == torch.uint8 and out_s.dtype == torch.uint8 and out.shape[1] == n_out
     if out is None:
         orow = scatter_rows if (epilogue == 2 and scatter_rows) else rows
         out = torch.empty(orow, n_out, dtype=out_dtype, device=xq.device)
@@ -116,12 +128,18 @@ def gemm_fp8(xq: torch.Tensor, xs: torch.Tensor, wq: torch.Tensor, ws: torch.Ten
     a.out_fp32 = 1 if out.dtype == torch.float32 else 0
     a.act_limit = act_limit
     a.scale_group32 = 1 if group32 else 0
-    if plan is not None:
+    if plan is not None and slots is None:
         a.max_tok_tiles = plan.max_tiles
         a.tile_group, a.tile_row0, a.tile_rows = plan.tile_group.data_ptr(), plan.tile_row0.data_ptr(), plan.tile_rows.data_ptr()
         a.num_tok_tiles = plan.meta.data_ptr()
-        if epilogue == 2:
-            a.dst_row, a.row_scale = plan.dst_row.data_ptr(), plan.row_scale.data_ptr()
+    if plan is not None and epilogue == 2:
+        a.dst_row, a.row_scale = plan.dst_row.data_ptr(), plan.row_scale.data_ptr()
+    if slots is not None:
+        cnt, slot_rows = slots
+        assert cnt.dtype == torch.int32 and cnt.numel() >= groups and slot_rows % ntok == 0
+        a.slot_cnt, a.slot_rows = cnt.data_ptr(), slot_rows
+    if out_s is not None:
+        a.out_scale, a.ldos = out_s.data_ptr(), out_s.stride(0)
     a.status = status_tensor(xq.device).data_ptr()
     check(lib.fb_gemm_fp8(C.byref(a), stream_ptr()), "fb_gemm_fp8")
     return out
@@ -148,7 +166,7 @@ class GemmMxfp4Args(C.Structure):
         ("max_tok_tiles", C.c_int),
         ("tile_group", C.c_void_p), ("tile_row0", C.c_void_p), ("tile_rows", C.c_void_p), ("num_tok_tiles", C.c_void_p),
         ("dst_row", C.c_void_p), ("row_scale", C.c_void_p), ("act_limit", C.c_float), ("status", C.c_void_p),
-        ("w_tiled", C.c_int),
+        ("w_tiled", C.c_int), ("w_fp8", C.c_int),
     ]
 
 
@@ -214,9 +232,13 @@ def mxfp4_prepare_sf(scale: torch.Tensor) -> torch.Tensor:
 def gemm_mxfp4(xq: torch.Tensor, xs: torch.Tensor, w_packed: torch.Tensor, w_sf: torch.Tensor,
                out: Optional[torch.Tensor] = None, *, out_dtype=torch.bfloat16, epilogue: int = 0, plan=None,
                scatter_rows: Optional[int] = None, act_limit: float = 0.0, ntok: Optional[int] = None,
-               out_mx: Optional[Tuple[torch.Tensor, torch.Tensor]] = None, w_rows: Optional[int] = None
-               ) -> torch.Tensor:
-    """MXFP4 weights x MXFP8 activations on `tcgen05.mma kind::mxf8f6f4.block_scale`.
+               out_mx: Optional[Tuple[torch.Tensor, torch.Tensor]] = None, w_rows: Optional[int] = None,
+               w_fp8: bool = False) -> torch.Tensor:
+    """MXFP4 (or, with `w_fp8`, e4m3) weights x MXFP8 activations on `tcgen05.mma kind::mxf8f6f4.block_scale`.
+
+    w_fp8: `w_packed` holds e4m3 codes [groups, N, K], one byte per value, and `w_sf` their scales in the same
+    per-32 layout (`fp8_block_sf` replicates a checkpoint's 128 x 128 block scales into it): the tensor core
+    applies weight and activation scales itself, nothing is rescaled between k-blocks.
 
     xq uint8 e4m3 [rows, K] + xs UE8M0 [rows, K/32]; w_packed uint8 [groups, N, K/2] (two e2m1 per byte, low
     nibble first) + w_sf from `mxfp4_prepare_sf`.  epilogue 0 store, 1 SwiGLU (rows = [gate | up]), 2 scatter
@@ -233,7 +255,7 @@ def gemm_mxfp4(xq: torch.Tensor, xs: torch.Tensor, w_packed: torch.Tensor, w_sf:
         if w_packed.dim() == 2:
             w_packed = w_packed.unsqueeze(0)
         groups, w_rows, half = w_packed.shape
-        K = half * 2
+        K = half if w_fp8 else half * 2
     rows = xq.shape[0]
     dual = epilogue == 1
     n_out = w_rows // 2 if dual else w_rows
@@ -256,6 +278,7 @@ def gemm_mxfp4(xq: torch.Tensor, xs: torch.Tensor, w_packed: torch.Tensor, w_sf:
         a.w_tiled, a.ldw_bytes, a.w_group_stride_bytes = 1, 64, w_packed.stride(0)
     else:
         a.ldw_bytes, a.w_group_stride_bytes = w_packed.stride(1), w_packed.stride(0)
+    a.w_fp8 = 1 if w_fp8 else 0
     a.ldx, a.ldxs = xq.stride(0), xs.stride(0)
     a.n_out, a.k, a.groups, a.w_rows_per_group, a.x_rows = n_out, K, groups, w_rows, rows
     a.ntok, a.epilogue, a.dual_offset = ntok, epilogue, (w_rows // 2 if dual else 0)
@@ -268,5 +291,24 @@ def gemm_mxfp4(xq: torch.Tensor, xs: torch.Tensor, w_packed: torch.Tensor, w_sf:
             a.dst_row, a.row_scale = plan.dst_row.data_ptr(), plan.row_scale.data_ptr()
     a.status = status_tensor(xq.device).data_ptr()
     check(lib.fb_gemm_mxfp4(C.byref(a), stream_ptr()), "fb_gemm_mxfp4")
+    return out
+
+
+def fp8_block_sf(scale: torch.Tensor, rows: int, k: int) -> torch.Tensor:
+    """128 x 128 block scales UE8M0 [groups, ceil(rows/128), ceil(k/128)] (or 2-D) of e4m3 weights -> the per-32
+    scale layout of the block-scaled GEMM: every block scale is repeated for its 128 rows and its four 32-column
+    slices, so the products are exactly those of the 128 x 128 format (k % 128 == 0)."""
+    assert k % 128 == 0
+    if scale.dim() == 2:
+        scale = scale.unsqueeze(0)
+    G = scale.shape[0]
+    out = None
+    # group by group: the expanded [rows, k / 32] table of all groups at once can be large
+    for g in range(G):
+        per32 = scale[g].repeat_interleave(128, 0)[:rows].repeat_interleave(4, 1).contiguous()
+        sf = mxfp4_prepare_sf(per32)
+        if out is None:
+            out = torch.empty((G,) + tuple(sf.shape[1:]), dtype=torch.uint8, device=scale.device)
+        out[g] = sf[0]
     return out
 

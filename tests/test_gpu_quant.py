@@ -112,6 +112,103 @@ def test_gemm_fp8_swiglu_and_grouped_scatter():
     assert float((out.cpu() - exp).abs().max()) <= 3e-3 * float(exp.abs().max()) + 1e-4
 
 
+@pytest.mark.parametrize("rows,dim", [(32, 2048), (5, 7168), (3, 128), (17, 1536)])
+def test_add_rmsnorm_writes_the_fp8_form_of_its_output(rows, dim):
+    """norm -> FP8 in one kernel: codes and scales are bit-equal to the row quantiser run on the bf16 output."""
+    from ferrule_b200.ops import kernels as K
+    from ferrule_b200.ops import quant as Q
+    x, d, w = rnd(rows, dim, seed=1), rnd(rows, dim, seed=2), rnd(dim, seed=3)
+    q = torch.zeros(rows + 2, dim, dtype=torch.uint8, device="cuda")
+    sc = torch.zeros(rows + 2, dim // 128, dtype=torch.uint8, device="cuda")
+    res, nrm = K.add_rmsnorm(x, w, 1e-6, delta=d, quant_out=(q, sc))
+    res2, nrm2 = K.add_rmsnorm(x, w, 1e-6, delta=d)
+    assert torch.equal(res, res2) and torch.equal(nrm, nrm2)
+    q2, s2 = Q.quant_fp8_rows(nrm2)
+    assert torch.equal(q[:rows], q2) and torch.equal(sc[:rows], s2)
+    assert int(q[rows:].sum()) == 0 and int(sc[rows:].sum()) == 0
+    # 1 x 32 blocks (MXFP8) for the linears that run on the block-scaled MMA
+    q3 = torch.zeros(rows, dim, dtype=torch.uint8, device="cuda")
+    s3 = torch.zeros(rows, dim // 32, dtype=torch.uint8, device="cuda")
+    K.add_rmsnorm(x, w, 1e-6, delta=d, quant_out=(q3, s3), quant_block=32)
+    q4, s4 = Q.quant_mxfp8_rows(nrm2)
+    assert torch.equal(q3, q4) and torch.equal(s3, s4)
+
+
+@pytest.mark.parametrize("rows,n,k,dual", [(32, 2048, 2048, False), (5, 576, 1536, False), (64, 256, 7168, False),
+                                           (16, 128, 128, False), (32, 256, 1024, True), (100, 384, 512, False)])
+def test_fp8_block_weights_on_the_block_scaled_mma(rows, n, k, dual):
+    """e4m3 weights with 128 x 128 block scales replicated into the per-32 scale layout: the tensor core applies
+    the scales, the products are those of the checkpoint format (fp32 oracle over the dequantised operands)."""
+    from ferrule_b200.ops import quant as Q
+    from ferrule_b200.ops import reference as ref
+    x = rnd(rows, k, scale=1.5, seed=51)
+    xq, xs = Q.quant_mxfp8_rows(x)
+    n_w = 2 * n if dual else n
+    w = torch.randn(n_w, k, generator=torch.Generator().manual_seed(52)) * 0.05
+    wq, ws_ = enc.weight_quant_fp8_block(w)
+    wd = enc.weight_dequant_fp8_block(wq, ws_)
+    sf = Q.fp8_block_sf(ws_.cuda(), n_w, k)
+    out = Q.gemm_mxfp4(xq, xs, wq.cuda(), sf, out_dtype=torch.float32, epilogue=1 if dual else 0, w_fp8=True,
+                       ntok=None if rows <= 64 else 64)
+    xd = _mx_dequant_rows(xq.cpu(), xs.cpu())
+    y = xd @ wd.T
+    want = ref.swiglu(y[:, :n], y[:, n:]) if dual else y
+    err = (out.cpu() - want).abs().max()
+    assert float(err) <= 2e-3 * float(want.abs().max()) + 1e-4, float(err)
+
+
+@pytest.mark.parametrize("slot,counts", [(32, [3, 0, 32, 1, 0, 0, 17, 9]), (64, [40, 0, 64, 1, 33, 0, 0, 32]),
+                                         (16, [16, 0, 0, 0, 2, 0, 0, 0])])
+def test_gemm_fp8_static_slots_skip_empty_experts_and_requantise(slot, counts):
+    """Slot mode of the FP8 GEMM (group g owns rows [g * slot, (g + 1) * slot), counts[g] filled): the SwiGLU
+    epilogue's FP8 output equals the row quantiser applied to the bf16 result, rows outside the counts are not
+    touched, and the slot walk gives the result of the same GEMM over an explicit tile table."""
+    from ferrule_b200.ops import kernels as K
+    from ferrule_b200.ops import quant as Q
+    E, H, I = len(counts), 512, 256
+    ntok = min(slot, 32)
+    x = rnd(E * slot, H, scale=1.5, seed=41)
+    xq, xs = Q.quant_fp8_rows(x)
+    w13 = torch.randn(E, 2 * I, H, generator=torch.Generator().manual_seed(42)) * 0.05
+    packs = [enc.weight_quant_fp8_block(w13[e]) for e in range(E)]
+    wq = torch.stack([p_[0] for p_ in packs]).cuda()
+    ws_ = torch.stack([p_[1] for p_ in packs]).cuda()
+    cnt = torch.tensor(counts, dtype=torch.int32, device="cuda")
+    # explicit table: slot // ntok tiles per expert
+    tg, t0, tr = [], [], []
+    for e, c in enumerate(counts):
+        for sub in range(slot // ntok):
+            tg.append(e)
+            t0.append(e * slot + sub * ntok)
+            tr.append(max(0, min(ntok, c - sub * ntok)))
+    i32 = dict(dtype=torch.int32, device="cuda")
+    plan = K.MoePlan(ntok, len(tg), E * slot, torch.zeros(E * slot, **i32), torch.arange(E * slot, **i32),
+                     torch.ones(E * slot, device="cuda"), torch.tensor(tg, **i32), torch.tensor(t0, **i32),
+                     torch.tensor(tr, **i32), cnt, torch.tensor([len(tg), sum(counts)], **i32))
+    want = torch.full((E * slot, I), 7.0, dtype=torch.bfloat16, device="cuda")
+    Q.gemm_fp8(xq, xs, wq, ws_, out=want, epilogue=1, plan=plan, act_limit=7.0)
+    got = torch.full((E * slot, I), 7.0, dtype=torch.bfloat16, device="cuda")
+    Q.gemm_fp8(xq, xs, wq, ws_, out=got, epilogue=1, slots=(cnt, slot), act_limit=7.0)
+    assert torch.equal(got, want)
+    oq = torch.full((E * slot, I), 9, dtype=torch.uint8, device="cuda")
+    os_ = torch.full((E * slot, I // 128), 9, dtype=torch.uint8, device="cuda")
+    Q.gemm_fp8(xq, xs, wq, ws_, epilogue=1, slots=(cnt, slot), act_limit=7.0, out_q=(oq, os_))
+    q2, s2 = Q.quant_fp8_rows(want)
+    for e, c in enumerate(counts):
+        r0 = e * slot
+        assert torch.equal(oq[r0:r0 + c], q2[r0:r0 + c]) and torch.equal(os_[r0:r0 + c], s2[r0:r0 + c])
+        assert int((oq[r0 + c:r0 + slot] != 9).sum()) == 0 and float((got[r0 + c:r0 + slot].float() - 7).abs().sum()) == 0
+    # the down projection over the quantised rows, scatter epilogue through the same slots
+    w2 = torch.randn(E, H, I, generator=torch.Generator().manual_seed(43)) * 0.05
+    p2 = [enc.weight_quant_fp8_block(w2[e]) for e in range(E)]
+    w2q, w2s = torch.stack([p_[0] for p_ in p2]).cuda(), torch.stack([p_[1] for p_ in p2]).cuda()
+    a = torch.zeros(E * slot, H, dtype=torch.bfloat16, device="cuda")
+    b_ = torch.zeros_like(a)
+    Q.gemm_fp8(q2, s2, w2q, w2s, out=a, epilogue=2, plan=plan)
+    Q.gemm_fp8(oq, os_, w2q, w2s, out=b_, epilogue=2, plan=plan, slots=(cnt, slot))
+    assert torch.equal(a, b_)
+
+
 @pytest.mark.parametrize("rows,n,k,dual", [(32, 1408, 2048, False), (7, 256, 512, True), (32, 2048, 1408 - 1408 % 128, False)])
 def test_gemm_mxfp4_weights_group_scaled(rows, n, k, dual):
     """MXFP4 weights (e2m1 + UE8M0 per 32) expanded to e4m3 containers, FP8 activations."""
