@@ -156,6 +156,10 @@ def main() -> None:
         tp, pp = lay.tp, lay.pp
 
     cfg = C.PRESETS[args.model]()
+    if cfg.n_mtp_layers:
+        # plain greedy decoding: the multi-token-prediction module only serves speculative decoding and is not
+        # instantiated (its weights are not part of the decode step's traffic either way)
+        cfg = cfg.with_(n_mtp_layers=0)
     if args.layers:
         cfg = cfg.with_(n_layers=args.layers)
     B, P, K, Wm = args.batch, args.prompt_len, args.steps, args.warmup
@@ -173,7 +177,8 @@ def main() -> None:
     if pp is not None:
         weights = stage_weights(weights, lay.pp_rank, lay.pp_size)
     runner = DeepSeekRunner(weights, n_pages=B * pages_per_seq + 8, page_size=page, max_rows=2048, max_seqs=B,
-                            max_seq_len=pages_per_seq * page, device=dev, tp=tp, pp=pp)
+                            max_seq_len=pages_per_seq * page, device=dev, tp=tp, pp=pp,
+                            enable_mtp=False)
     if tp is not None:
         tp.attach(runner.fwd)
         if args.moe == "dispatch":

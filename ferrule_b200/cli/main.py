@@ -39,6 +39,7 @@ def _add_model_args(p: argparse.ArgumentParser) -> None:
     p.add_argument("--seed", type=int, default=0)
     p.add_argument("--weight-format", default="bf16", choices=["bf16", "fp8_block", "fp8_mxfp4"],
                    help="random-init presets: quantise the weights to this format")
+    p.add_argument("--layers", type=int, default=0, help="random-init presets: override the layer count")
     p.add_argument("--pp", type=int, default=1,
                    help="pipeline stages; under torch.distributed.run the ranks form pp stages x (world / pp) "
                         "tensor-parallel ranks, rank 0 serves and the others mirror its command stream")
@@ -94,6 +95,10 @@ def build_engine(args, layout=None):
         return _build_v4_engine(args, dev)
     else:
         cfg = C.PRESETS[args.preset]()
+        if cfg.n_mtp_layers and not args.speculative:
+            cfg = cfg.with_(n_mtp_layers=0)         # the MTP module only serves speculative decoding
+        if getattr(args, "layers", 0):
+            cfg = cfg.with_(n_layers=args.layers)
         tp_rank, tp_world = (layout.tp_rank, layout.tp_size) if layout is not None else (0, 1)
         staged = layout is not None and layout.pp is not None
         from ..parallel.pp import stage_range, stage_weights

@@ -86,6 +86,17 @@ async def _level(url, model, conc, n_req, rng, vocab, min_in, max_in, min_out, m
 
 def run_sweep(url, model, concurrency, n_req, seed, vocab, min_in, max_in, min_out, max_out, prefix, frac) -> Dict:
     rng = random.Random(seed)
-    levels = [asyncio.run(_level(url, model, c, n_req, rng, vocab, min_in, max_in, min_out, max_out, prefix, frac))
-              for c in concurrency]
-    return {"url": url, "levels": levels}
+    # a level needs at least as many requests as its concurrency to ever reach it
+    levels = [asyncio.run(_level(url, model, c, max(n_req, c), rng, vocab, min_in, max_in, min_out, max_out, prefix,
+                                 frac)) for c in concurrency]
+    out = {"url": url, "levels": levels}
+    try:        # the server's own counters: KV high-water mark, copy-on-write copies, prefix reuse, preemptions
+        import httpx
+        m = httpx.get(url + "/metrics", timeout=10).json()
+        eng = (m.get("worker") or {}).get("engine") or {}
+        out["server"] = {"kv": eng.get("kv"), "scheduler": eng.get("scheduler"),
+                         "speculative": eng.get("speculative"),
+                         "decode_steps": eng.get("decode_steps"), "prefill_chunks": eng.get("prefill_chunks")}
+    except Exception as exc:  # noqa: BLE001 - the sweep's own numbers stand without it
+        out["server"] = {"unavailable": str(exc)[:200]}
+    return out
