@@ -585,7 +585,8 @@ class DeepSeekRunner(ModelRunner):
         gather = self.tp.gather_vocab_reference if self.tp is not None else None
         if self.pp is not None:
             with torch.no_grad():
-                ids_t, vals_t = self.pp.step(self.fwd, db, self.cfg.hidden, self.w.embed.dtype, False)
+                ids_t, vals_t = self.pp.step(self.fwd, db, self.cfg.hidden, self.w.embed.dtype, False,
+                                             allreduce=allreduce, gather_vocab=gather)
             self._last_hidden = None
             for i, r in enumerate(lrows):
                 if int(ids_t[i]) >= 0 and torch.isfinite(vals_t[i]):

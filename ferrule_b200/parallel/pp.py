@@ -75,9 +75,10 @@ class PipelineParallel:
             t = self._bufs[key] = torch.empty(max(rows, 1), hidden, dtype=dtype, device=dev)
         return t[:rows]
 
-    def step(self, fwd, b: DeviceBatch, hidden: int, dtype, cuda: bool):
+    def step(self, fwd, b: DeviceBatch, hidden: int, dtype, cuda: bool, allreduce=None, gather_vocab=None):
         """Runs the packed batch through all stages.  Returns (ids, vals) of the greedy tokens on every rank
-        (float logit values as a second tensor)."""
+        (float logit values as a second tensor).  `allreduce` / `gather_vocab`: the tensor-parallel reference
+        collectives of a stage whose layers are sharded (host path; the GPU forward carries its own)."""
         T = b.n_rows
         m = self.microbatches if (b.n_logit == T and T >= self.microbatches) else 1
         bounds = [(j * T // m, (j + 1) * T // m) for j in range(m)]
@@ -94,7 +95,7 @@ class PipelineParallel:
             else:
                 h = torch.empty(n, hidden, dtype=dtype, device=dev)
                 dist.recv(h, src=self._g(self.rank - 1), group=self.group)
-            h = fwd.run_layers(h, mb)
+            h = fwd.run_layers(h, mb, allreduce)
             if not self.last:
                 hs = h.contiguous().clone()             # the stage's buffer is reused by the next range
                 pending.append((dist.isend(hs, dst=self._g(self.rank + 1), group=self.group), hs))
@@ -102,6 +103,8 @@ class PipelineParallel:
                 outs.append(None)
             else:
                 logits = fwd.logits_from_hidden(h, mb)
+                if gather_vocab is not None:
+                    logits = gather_vocab(logits)
                 vals, ids = logits.max(-1)
                 outs.append((ids.to(torch.int32), vals.float()))
         for work, _ in pending:
@@ -128,17 +131,28 @@ class PipelineParallel:
         comm = self.comm_stream
         m = len(bounds)
         outs: List[Optional[Tuple[torch.Tensor, torch.Tensor]]] = []
-        # all receives are posted up front on the side stream: range j + 1 arrives while range j computes
+        # A stage whose layers are tensor-parallel runs kernels that wait for their peers from inside the kernel
+        # (fused collectives) and, for large batches, collectives of a second communicator.  A transfer kernel that
+        # sits on the GPU waiting for the neighbouring stage at the same time would share the machine with them for
+        # an unbounded time, so such a stage keeps its transfers out of its compute: a receive is posted when its
+        # range is due, and the next range starts after the send has left.
+        overlap = getattr(fwd, "tp", None) is None
+
+        def post_recv(j: int):
+            r0, r1 = bounds[j]
+            with torch.cuda.stream(comm):
+                hin = self._buf("recv", j, r1 - r0, hidden, dtype, dev)
+                dist.recv(hin, src=self._g(self.rank - 1), group=self.group)
+                ev = torch.cuda.Event()
+                ev.record(comm)
+            return ev
+
         recv_ev = []
         if not self.first:
             comm.wait_stream(main)                       # the buffers' previous readers (the last step) are done
-            with torch.cuda.stream(comm):
-                for j, (r0, r1) in enumerate(bounds):
-                    hin = self._buf("recv", j, r1 - r0, hidden, dtype, dev)
-                    dist.recv(hin, src=self._g(self.rank - 1), group=self.group)
-                    ev = torch.cuda.Event()
-                    ev.record(comm)
-                    recv_ev.append(ev)
+            if overlap:
+                # all receives are posted up front on the side stream: range j + 1 arrives while range j computes
+                recv_ev = [post_recv(j) for j in range(m)]
         send_done = []
         for j, (r0, r1) in enumerate(bounds):
             mb = b if m == 1 else self._slice(b, r0, r1)
@@ -146,6 +160,9 @@ class PipelineParallel:
             if self.first:
                 h = fwd.embed_rows(mb, n)
             else:
+                if not overlap:
+                    comm.wait_stream(main)
+                    recv_ev.append(post_recv(j))
                 main.wait_event(recv_ev[j])
                 h = self._buf("recv", j, n, hidden, dtype, dev)
             h = fwd.run_layers(h, mb, n)
@@ -160,6 +177,8 @@ class PipelineParallel:
                     ev = torch.cuda.Event()
                     ev.record(comm)
                     send_done.append(ev)
+                if not overlap:
+                    main.wait_event(ev)
                 self.sends += 1
                 outs.append(None)
             else:

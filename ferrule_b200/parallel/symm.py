@@ -172,7 +172,10 @@ class McChannel:
         """mode 1 reduce-scatter, 2 all-gather, 3 all-reduce (see `fb_mm_collective`)."""
         from ..ops._lib import ptr, status_tensor, stream_ptr
         lib = get_lib(True)
-        check(lib.fb_mm_collective(ptr(src), src.stride(0) if src is not None else 0, slots, topk, ptr(topk_idx), e_lo,
+        # a rank whose row slice is empty (more ranks than rows) still takes part: it owns nothing and reads no
+        # row of `src`, but the launcher wants a pointer
+        src_ptr = ptr(src) if (src is None or src.numel()) else out.data_ptr()
+        check(lib.fb_mm_collective(src_ptr, src.stride(0) if src is not None else 0, slots, topk, ptr(topk_idx), e_lo,
                                    e_hi, ptr(residual), residual.stride(0) if residual is not None else 0,
                                    out.data_ptr(), out.stride(0), rows, self.dim, mode, ptr(norm_w), ptr(norm_out),
                                    norm_out.stride(0) if norm_out is not None else 0, eps, self.local_ptr, self.mc_ptr,

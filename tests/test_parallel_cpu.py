@@ -225,3 +225,43 @@ def test_serving_replica_over_two_tensor_parallel_ranks_mirrors_the_command_stre
         dist.destroy_process_group()
     ''', 2, 29617)
     assert "MIRROR_OK" in p.stdout, p.stdout[-2000:] + p.stderr[-3000:]
+
+
+def test_engine_over_two_stages_of_two_tensor_ranks_each():
+    """pp 2 x tp 2 on four CPU ranks through `build_parallel` (stage-major rank layout, one process group per
+    stage and per tensor rank): the engine's greedy streams equal the single-process ones on every rank."""
+    p = _run('''
+        import torch, torch.distributed as dist
+        from ferrule_b200.models import config as C, weights as W
+        from ferrule_b200.models.runner import DeepSeekRunner
+        from ferrule_b200.parallel.layout import build_parallel
+        from ferrule_b200.parallel.pp import stage_weights
+        from ferrule_b200.runtime.engine import Engine, EngineConfig, TokenEvent
+        from ferrule_b200.runtime.scheduler import SchedulerConfig
+        from ferrule_b200.runtime.session import GenerateRequest
+        dist.init_process_group("gloo")
+        rank, world = dist.get_rank(), dist.get_world_size()
+        lay = build_parallel(rank, world, "cpu", pp=2, tp=2, microbatches=2, fused=False)
+        assert (lay.pp_rank, lay.tp_rank) == divmod(rank, 2) and lay.tp_ranks == [2 * lay.pp_rank, 2 * lay.pp_rank + 1]
+        cfg = C.tiny_fixture().with_(n_mtp_layers=0)
+        def run(runner):
+            sched = SchedulerConfig(max_active_sequences=4, max_decode_batch=4, max_batch_tokens=48,
+                                    prefill_chunk_size=16, ctx_size=128)
+            eng = Engine(runner, EngineConfig(scheduler=sched, kv_pages=32, page_size=16))
+            g = torch.Generator().manual_seed(3)
+            for i in range(3):
+                eng.submit(GenerateRequest(f"r{i}", torch.randint(0, cfg.vocab_size, (9 + 11 * i,), generator=g).tolist(),
+                                           max_new_tokens=6, ignore_eos=True))
+            ev = []
+            eng.run_until_idle(ev.append, max_steps=2000)
+            assert eng.last_error is None, eng.last_error
+            return {r: [e.token for e in ev if isinstance(e, TokenEvent) and e.request_id == r] for r in ("r0", "r1", "r2")}
+        want = run(DeepSeekRunner(W.random_weights(cfg, device="cpu", seed=0, dtype=torch.float32), n_pages=32,
+                                  page_size=16, max_rows=64, max_seqs=4, max_seq_len=128, device="cpu"))
+        w = W.random_weights(cfg, device="cpu", seed=0, dtype=torch.float32, tp_rank=lay.tp_rank, tp_world=2)
+        got = run(DeepSeekRunner(stage_weights(w, lay.pp_rank, 2), n_pages=32, page_size=16, max_rows=64, max_seqs=4,
+                                 max_seq_len=128, device="cpu", tp=lay.tp, pp=lay.pp))
+        print("PPTP_OK" if got == want and all(len(v) == 6 for v in got.values()) else f"PPTP_BAD {got} {want}", rank, flush=True)
+        dist.destroy_process_group()
+    ''', 4, 29619, timeout=240)
+    assert p.stdout.count("PPTP_OK") == 4, p.stdout[-2000:] + p.stderr[-3000:]
