@@ -35,6 +35,9 @@ def _add_model_args(p: argparse.ArgumentParser) -> None:
     p.add_argument("--max-batch-tokens", type=int, default=2048)
     p.add_argument("--prefill-chunk", type=int, default=512)
     p.add_argument("--speculative", action="store_true")
+    p.add_argument("--prefix-cache-tokens", type=int, default=0,
+                   help="keep the KV pages of finished prompts (whole 512-token blocks, this many tokens in total) "
+                        "and fork them for later prompts that start with the same tokens; 0 = off")
     p.add_argument("--max-draft", type=int, default=1)
     p.add_argument("--seed", type=int, default=0)
     p.add_argument("--weight-format", default="bf16", choices=["bf16", "fp8_block", "fp8_mxfp4"],
@@ -128,8 +131,10 @@ def build_engine(args, layout=None):
     sched = SchedulerConfig(max_active_sequences=args.max_seqs, max_decode_batch=args.max_seqs,
                             max_batch_tokens=args.max_batch_tokens, prefill_chunk_size=args.prefill_chunk,
                             ctx_size=pages_per_seq * args.page_size)
+    block = max(512 // args.page_size, 1) * args.page_size
     eng = Engine(runner, EngineConfig(scheduler=sched, kv_pages=n_pages, page_size=args.page_size,
-                                      speculative=args.speculative, max_draft=args.max_draft))
+                                      speculative=args.speculative, max_draft=args.max_draft,
+                                      prefix_cache_tokens=getattr(args, "prefix_cache_tokens", 0), prefix_block=block))
     return eng, load_tokenizer(args.model_dir), name
 
 

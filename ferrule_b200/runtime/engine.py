@@ -22,7 +22,7 @@ restore :1679-1795/:2310-2440, shutdown :4034-4190).
 from __future__ import annotations
 
 import time
-from collections import deque
+from collections import OrderedDict, deque
 from dataclasses import dataclass, field
 from enum import Enum
 from typing import Callable, Deque, Dict, List, Optional, Sequence, Tuple
@@ -44,6 +44,11 @@ class EngineConfig:
     max_draft: int = 1
     confidence_threshold: float = 0.2
     auto_preempt: bool = False          # preempt the youngest decode sequence when pages run out
+    # prompt-prefix cache: finished requests leave the KV pages of their prompt (cut to whole `prefix_block`s)
+    # behind, up to this many tokens in total; a later prompt that starts with the same tokens forks those pages
+    # instead of recomputing them.  0 = off.  Entries go oldest-first when over budget or when pages run out.
+    prefix_cache_tokens: int = 0
+    prefix_block: int = 512             # granularity of a reusable prefix (a multiple of the page size)
 
 
 @dataclass
@@ -110,6 +115,10 @@ class EngineStats:
     staged_tokens: int = 0
     finished: int = 0
     kv_stalls: int = 0
+    prefix_hits: int = 0
+    prefix_tokens_reused: int = 0
+    prefix_entries: int = 0
+    prefix_evictions: int = 0
     auto_preemptions: int = 0
     waits: int = 0
     resumes: int = 0
@@ -145,6 +154,12 @@ class Engine:
         self._sessions: Dict[str, SequenceState] = {}
         self._snapshots: Dict[str, Tuple[object, list]] = {}
         self._shutdown = False
+        # prefix cache: chained block hash -> (kv sequence, tokens); entries in insertion / last-use order
+        self._prefix_index: Dict[bytes, Tuple[int, int]] = {}
+        self._prefix_lru: "OrderedDict[int, Tuple[List[int], List[bytes]]]" = OrderedDict()
+        self._prefix_tokens = 0
+        if self.cfg.prefix_cache_tokens and self.cfg.prefix_block % self.cfg.page_size:
+            raise ValueError("prefix_block must be a multiple of the page size")
         self.spec = None
         if self.cfg.speculative:
             from .speculation import SpeculativeDecoder
@@ -177,8 +192,16 @@ class Engine:
             seq = SequenceState(req, kv_seq=prev.kv_seq, tokens=prev.tokens + list(req.prompt_tokens),
                                 position=prev.position, arrival_ns=now)
         else:
-            seq = SequenceState(req, kv_seq=self.kv.alloc_sequence(), tokens=list(req.prompt_tokens),
-                                arrival_ns=now)
+            hit = self._prefix_lookup(req.prompt_tokens) if (self.cfg.prefix_cache_tokens and not req.session_id) else None
+            if hit is not None:
+                donor, n = hit
+                seq = SequenceState(req, kv_seq=self.kv.publish_fork_sequence_prefix(donor, n),
+                                    tokens=list(req.prompt_tokens), position=n, arrival_ns=now)
+                self.stats.prefix_hits += 1
+                self.stats.prefix_tokens_reused += n
+            else:
+                seq = SequenceState(req, kv_seq=self.kv.alloc_sequence(), tokens=list(req.prompt_tokens),
+                                    arrival_ns=now)
         seq.prompt_len = len(seq.tokens)
         try:
             self.scheduler.submit(seq)
@@ -189,6 +212,77 @@ class Engine:
                 self._retire(self.kv.free_sequence_pages(seq.kv_seq))
             raise
         return seq
+
+    # ------------------------------------------------------------------ prompt-prefix cache
+    def _prefix_keys(self, tokens: Sequence[int], blocks: int) -> List[bytes]:
+        """Chained digests of the first `blocks` prefix blocks: key k covers tokens[: (k + 1) * prefix_block]."""
+        import hashlib
+        from array import array
+        B = self.cfg.prefix_block
+        keys, prev = [], b""
+        for k in range(blocks):
+            prev = hashlib.blake2b(prev + array("q", tokens[k * B:(k + 1) * B]).tobytes(), digest_size=16).digest()
+            keys.append(prev)
+        return keys
+
+    def _prefix_lookup(self, prompt: Sequence[int]) -> Optional[Tuple[int, int]]:
+        """-> (kv sequence to fork, tokens to share) for the longest cached prefix that leaves the request at
+        least one prompt token of its own to run."""
+        B = self.cfg.prefix_block
+        blocks = (len(prompt) - 1) // B
+        if blocks <= 0 or not self._prefix_index:
+            return None
+        keys = self._prefix_keys(prompt, blocks)
+        for k in range(blocks - 1, -1, -1):
+            ent = self._prefix_index.get(keys[k])
+            if ent is None:
+                continue
+            donor, n = ent
+            cached = self._prefix_lru.get(donor)
+            if cached is None or cached[0][:n] != list(prompt[:n]):
+                continue                                    # digest collision: not the same tokens
+            self._prefix_lru.move_to_end(donor)
+            return donor, n
+        return None
+
+    def _prefix_offer(self, seq: SequenceState) -> bool:
+        """A finishing sequence leaves its prompt's whole prefix blocks to the cache (True: the cache now owns
+        the KV sequence) unless every one of them is cached already."""
+        B = self.cfg.prefix_block
+        have = self.kv.sequence(seq.kv_seq).committed_tokens
+        n = min(seq.prompt_len, have, self.cfg.prefix_cache_tokens) // B * B
+        if n < B:
+            return False
+        keys = self._prefix_keys(seq.tokens, n // B)
+        new = [k for k in keys if k not in self._prefix_index]
+        if not new:
+            donor = self._prefix_index[keys[-1]][0]
+            if donor in self._prefix_lru:
+                self._prefix_lru.move_to_end(donor)
+            return False
+        self._retire(self.kv.truncate_sequence(seq.kv_seq, n))
+        for i, k in enumerate(keys):
+            if k not in self._prefix_index:
+                self._prefix_index[k] = (seq.kv_seq, (i + 1) * B)
+        self._prefix_lru[seq.kv_seq] = (list(seq.tokens[:n]), new)
+        self._prefix_tokens += n
+        self.stats.prefix_entries += 1
+        while self._prefix_tokens > self.cfg.prefix_cache_tokens and len(self._prefix_lru) > 1:
+            self._prefix_evict()
+        return True
+
+    def _prefix_evict(self) -> bool:
+        """Drop the least recently used cache entry; its pages go back once no fork shares them."""
+        if not self._prefix_lru:
+            return False
+        kv_seq, (tokens, keys) = self._prefix_lru.popitem(last=False)
+        for k in keys:
+            if self._prefix_index.get(k, (None, 0))[0] == kv_seq:
+                del self._prefix_index[k]
+        self._prefix_tokens -= len(tokens)
+        self._retire(self.kv.free_sequence_pages(kv_seq))
+        self.stats.prefix_evictions += 1
+        return True
 
     def cancel_request(self, request_id: str) -> bool:
         seq = self.scheduler.cancel(request_id)
@@ -254,6 +348,8 @@ class Engine:
             for s in list(self._sessions.values()):
                 self._retire(self.kv.free_sequence_pages(s.kv_seq))
             self._sessions.clear()
+            while self._prefix_evict():
+                pass
             self._drive_retirements()
             self.runner.shutdown()
         return idle
@@ -329,6 +425,8 @@ class Engine:
         for seq in stalled:
             self.stats.kv_stalls += 1
             self.scheduler.requeue_unchanged(seq)
+        if stalled and self._prefix_lru:
+            self._prefix_evict()            # cached prefixes give way to running sequences, oldest first
         if not members:
             if stalled and self.cfg.auto_preempt:
                 self._auto_preempt(stalled)
@@ -628,7 +726,10 @@ class Engine:
             seq.tokens = seq.tokens[:seq.position]
             self._sessions[seq.request.session_id or seq.request_id] = seq
         elif seq.kv_seq >= 0:
-            self._retire(self.kv.free_sequence_pages(seq.kv_seq))
+            cache = (self.cfg.prefix_cache_tokens and seq.slot < 0 and not self._shutdown
+                     and reason not in (FinishReason.CANCELLED, FinishReason.ERROR))
+            if not (cache and self._prefix_offer(seq)):
+                self._retire(self.kv.free_sequence_pages(seq.kv_seq))
             seq.kv_seq = -1
         if seq.slot >= 0:
             self.runner.release_slot(seq.slot)

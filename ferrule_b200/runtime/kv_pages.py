@@ -432,6 +432,25 @@ class KvPageManager:
         self._stats.forks += 1
         return cid
 
+    def publish_fork_sequence_prefix(self, src_id: int, tokens: int) -> int:
+        """New sequence that shares the pages of the first `tokens` committed tokens of `src_id` (a whole number
+        of pages: nothing is copied and the child's first write lands in a page of its own)."""
+        s = self._seq(src_id)
+        if s.open_reservation is not None:
+            raise KvError("cannot fork a sequence with an open reservation")
+        if s.preempted:
+            raise KvError("cannot fork a preempted sequence")
+        if tokens <= 0 or tokens > s.committed_tokens or tokens % self.page_size != 0:
+            raise KvError("a prefix fork takes a positive whole number of committed pages")
+        pages = list(s.pages[:tokens // self.page_size])
+        cid = self.alloc_sequence()
+        c = self._seqs[cid]
+        c.pages, c.committed_tokens = pages, tokens
+        for p in pages:
+            self._ref[p] += 1
+        self._stats.forks += 1
+        return cid
+
     # ------------------------------------------------------------------ preempt / restore
     def preempt_sequence(self, seq_id: int) -> PreemptedSequence:
         """Mark preempted and say which pages must be snapshotted (exclusively owned)."""

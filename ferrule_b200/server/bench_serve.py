@@ -96,6 +96,8 @@ def run_sweep(url, model, concurrency, n_req, seed, vocab, min_in, max_in, min_o
         eng = (m.get("worker") or {}).get("engine") or {}
         out["server"] = {"kv": eng.get("kv"), "scheduler": eng.get("scheduler"),
                          "speculative": eng.get("speculative"),
+                         "prefix_cache": {k: eng.get(k) for k in ("prefix_hits", "prefix_tokens_reused",
+                                                                  "prefix_entries", "prefix_evictions")},
                          "decode_steps": eng.get("decode_steps"), "prefill_chunks": eng.get("prefill_chunks")}
     except Exception as exc:  # noqa: BLE001 - the sweep's own numbers stand without it
         out["server"] = {"unavailable": str(exc)[:200]}

@@ -285,3 +285,86 @@ def test_decode_lookahead_declines_when_the_next_action_is_not_a_pure_decode():
     assert r.prediction_misses == 1 and r.predicted is None
     eng.run_until_idle(ev.append)
     assert r.prediction_misses == 1 and r.prediction_hits > hits
+
+
+def _prefix_engine(cache_tokens, kv_pages=96, block=32):
+    import torch
+    from ferrule_b200.models import config as C, weights as W
+    from ferrule_b200.models.runner import DeepSeekRunner
+    from ferrule_b200.runtime.engine import Engine, EngineConfig
+    from ferrule_b200.runtime.scheduler import SchedulerConfig
+    cfg = C.tiny_fixture().with_(n_mtp_layers=0)
+    w = W.random_weights(cfg, device="cpu", seed=0, dtype=torch.float32)
+    runner = DeepSeekRunner(w, n_pages=kv_pages, page_size=16, max_rows=128, max_seqs=4, max_seq_len=512, device="cpu")
+    sched = SchedulerConfig(max_active_sequences=4, max_decode_batch=4, max_batch_tokens=96, prefill_chunk_size=48,
+                            ctx_size=512)
+    return cfg, Engine(runner, EngineConfig(scheduler=sched, kv_pages=kv_pages, page_size=16,
+                                            prefix_cache_tokens=cache_tokens, prefix_block=block))
+
+
+def _run_all(eng, reqs):
+    from ferrule_b200.runtime.engine import TokenEvent
+    from ferrule_b200.runtime.session import GenerateRequest
+    for rid, toks in reqs:
+        eng.submit(GenerateRequest(rid, toks, max_new_tokens=5, ignore_eos=True))
+    ev = []
+    eng.run_until_idle(ev.append, max_steps=4000)
+    assert eng.last_error is None, eng.last_error
+    return {rid: [e.token for e in ev if isinstance(e, TokenEvent) and e.request_id == rid] for rid, _ in reqs}
+
+
+def test_prompt_prefix_cache_forks_cached_pages_and_streams_the_same_tokens():
+    """Requests that start with the tokens of an earlier prompt fork its KV pages (whole prefix blocks) instead of
+    recomputing them: same greedy tokens as without the cache, fewer prefill tokens, shared pages while they run,
+    and the cache gives its pages back at shutdown."""
+    import torch
+    g = torch.Generator().manual_seed(9)
+    shared = torch.randint(0, 1000, (100,), generator=g).tolist()
+    tails = [torch.randint(0, 1000, (n,), generator=g).tolist() for n in (7, 30, 1)]
+    waves = [[("a", shared + tails[0])], [("b", shared + tails[1]), ("c", shared + tails[2])],
+             [("d", shared[:64] + tails[1])], [("e", shared[:96])]]
+    _, plain = _prefix_engine(0)
+    want = {}
+    for wv in waves:
+        want.update(_run_all(plain, wv))
+    _, eng = _prefix_engine(4096)
+    got = {}
+    for wv in waves:
+        got.update(_run_all(eng, wv))
+        eng.kv.check_invariants()
+    assert got == want and all(len(v) == 5 for v in got.values())
+    st = eng.stats
+    # a: miss (and becomes the entry for blocks 32/64/96); b, c: 96 tokens each; d: 64; e: 96 tokens are the whole
+    # prompt, one token must stay for the request itself -> 64
+    assert st.prefix_hits == 4 and st.prefix_tokens_reused == 96 + 96 + 64 + 64
+    assert st.prefill_tokens == plain.stats.prefill_tokens - st.prefix_tokens_reused
+    assert eng.kv.stats().forks == 4 and st.prefix_entries >= 1
+    assert eng.kv.stats().used_pages > 0                     # the cache still holds the prefix
+    while not eng.shutdown():
+        pass
+    assert eng.kv.stats().used_pages == 0 and eng.kv.stats().free_pages == eng.kv.stats().total_pages
+
+
+def test_prompt_prefix_cache_gives_way_under_page_pressure_and_budget():
+    """Entries leave oldest-first when the token budget is exceeded, and a stalled reservation evicts cached
+    prefixes before anything else is tried; evicted prefixes are simply recomputed."""
+    import torch
+    g = torch.Generator().manual_seed(10)
+    prompts = [torch.randint(0, 1000, (70,), generator=g).tolist() for _ in range(4)]
+    _, eng = _prefix_engine(128, kv_pages=24)              # 128 cached tokens = two 64-token entries at most
+    for i, p_ in enumerate(prompts):
+        _run_all(eng, [(f"r{i}", p_)])
+        eng.kv.check_invariants()
+    assert eng.stats.prefix_entries == 4 and eng.stats.prefix_evictions >= 2 and len(eng._prefix_lru) <= 2
+    # three long prompts at once need more pages than the cache leaves free: the cache yields, nothing fails
+    long = [torch.randint(0, 1000, (120,), generator=g).tolist() for _ in range(3)]
+    out = _run_all(eng, [(f"l{i}", p_) for i, p_ in enumerate(long)])
+    assert all(len(v) == 5 for v in out.values()) and eng.stats.kv_stalls >= 0
+    eng.kv.check_invariants()
+    # an evicted prefix is a miss, a kept one a hit
+    hits0 = eng.stats.prefix_hits
+    _run_all(eng, [("again", prompts[0] + [5, 6])])
+    assert eng.stats.prefix_hits in (hits0, hits0 + 1)
+    while not eng.shutdown():
+        pass
+    assert eng.kv.stats().used_pages == 0
