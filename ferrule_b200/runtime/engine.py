@@ -158,6 +158,7 @@ class Engine:
         self._prefix_index: Dict[bytes, Tuple[int, int]] = {}
         self._prefix_lru: "OrderedDict[int, Tuple[List[int], List[bytes]]]" = OrderedDict()
         self._prefix_tokens = 0
+        self._prefix_hot: set = set()       # entries that have been forked at least once: they outlive the others
         if self.cfg.prefix_cache_tokens and self.cfg.prefix_block % self.cfg.page_size:
             raise ValueError("prefix_block must be a multiple of the page size")
         self.spec = None
@@ -242,6 +243,7 @@ class Engine:
             if cached is None or cached[0][:n] != list(prompt[:n]):
                 continue                                    # digest collision: not the same tokens
             self._prefix_lru.move_to_end(donor)
+            self._prefix_hot.add(donor)
             return donor, n
         return None
 
@@ -272,10 +274,15 @@ class Engine:
         return True
 
     def _prefix_evict(self) -> bool:
-        """Drop the least recently used cache entry; its pages go back once no fork shares them."""
+        """Drop a cache entry - the oldest that no request ever reused, else the least recently used; its pages go
+        back once no fork shares them."""
         if not self._prefix_lru:
             return False
-        kv_seq, (tokens, keys) = self._prefix_lru.popitem(last=False)
+        victim = next((k for k in self._prefix_lru if k not in self._prefix_hot), None)
+        if victim is None:
+            victim = next(iter(self._prefix_lru))
+        kv_seq, (tokens, keys) = victim, self._prefix_lru.pop(victim)
+        self._prefix_hot.discard(kv_seq)
         for k in keys:
             if self._prefix_index.get(k, (None, 0))[0] == kv_seq:
                 del self._prefix_index[k]
