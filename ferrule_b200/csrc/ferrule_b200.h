@@ -343,6 +343,8 @@ typedef struct FbGemmMxfp4Args {
   int w_tiled;              // w is tile-major: [groups][ceil(rows/128)][k/128][128 rows][64 bytes] (rows padded to 128)
   int w_fp8;                // weights are e4m3 bytes [groups, rows, k] (ldw_bytes = bytes per row) instead of packed e2m1;
                             //   w_sf has the same per-32 layout (128 x 128 block scales replicated)
+  const int* slot_cnt;      // static row slots instead of a tile table: group g owns rows [g * slot_rows,
+  int slot_rows;            //   (g + 1) * slot_rows), slot_cnt[g] of them filled (slot_rows % ntok == 0)
 } FbGemmMxfp4Args;
 int fb_gemm_mxfp4(const FbGemmMxfp4Args* args, void* stream);
 // linear UE8M0 weight scales [groups, rows, k / 32] -> [groups, ceil(rows / 128), k / 128, 512] blocks for the kernel

@@ -74,7 +74,31 @@ struct Params {
   int sfb_cols;                // TMEM columns of the activation scales of one tile
   int sfb_stride;              // TMEM columns per k-block (4: scale operands start on 4-column boundaries)
   int tmem_cols;
+  // static row slots (decode-sized MoE batches) instead of a tile table: group g owns rows [g * slot_rows,
+  // (g + 1) * slot_rows), slot_cnt[g] of them are filled, and the slot is walked in slot_rows / NTOK tiles
+  const int* slot_cnt;
+  int slot_rows;
 };
+
+// (group, first row, valid rows) of row tile m
+template <int NTOK>
+__device__ __forceinline__ void tile_of(const Params& p, int m, int& g, int& row0, int& rows) {
+  if (p.slot_rows > 0) {
+    const int per = p.slot_rows / NTOK;
+    g = m / per;
+    const int sub = m - g * per;
+    row0 = g * p.slot_rows + sub * NTOK;
+    rows = min(max(p.slot_cnt[g] - sub * NTOK, 0), NTOK);
+  } else if (p.tile_group != nullptr) {
+    g = p.tile_group[m];
+    row0 = p.tile_row0[m];
+    rows = min(p.tile_rows[m], NTOK);
+  } else {
+    g = 0;
+    row0 = m * NTOK;
+    rows = min(NTOK, p.dense_rows - row0);
+  }
+}
 
 __device__ __forceinline__ float silu(float x) { return x / (1.f + __expf(-x)); }
 
@@ -187,12 +211,18 @@ gemm_mxfp4_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_const
   const uint32_t tmem_sfb = tmem_sfa + 8;
   pdl_wait();
 
-  const bool grouped = p.tile_group != nullptr;
-  const int num_tok_tiles = grouped ? min(*p.num_tok_tiles, p.max_tok_tiles) : (p.dense_rows + NTOK - 1) / NTOK;
+  const bool grouped = p.tile_group != nullptr || p.slot_rows > 0;
+  const int num_tok_tiles = p.slot_rows > 0 ? p.max_tok_tiles
+                            : grouped ? min(*p.num_tok_tiles, p.max_tok_tiles) : (p.dense_rows + NTOK - 1) / NTOK;
   const int total = num_tok_tiles * p.n_tiles;
   const int kblocks = p.k / kBlockK;
   const int tile_first = blockIdx.x, tile_stride = gridDim.x;
-  auto empty = [&](int t) { return grouped && p.tile_rows[t / p.n_tiles] <= 0; };
+  auto empty = [&](int t) {
+    if (!grouped) return false;
+    int g_, r0_, rows_;
+    tile_of<NTOK>(p, t / p.n_tiles, g_, r0_, rows_);
+    return rows_ <= 0;
+  };
 
   if (warp == 0) {
     // ------------------------------ producer: weights, their scales, activations ------------------------------
@@ -206,8 +236,8 @@ gemm_mxfp4_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_const
       for (int t = tile_first; t < total && ok; t += tile_stride) {
         if (empty(t)) continue;
         const int m = t / p.n_tiles, nt = t - m * p.n_tiles;
-        const int g = grouped ? p.tile_group[m] : 0;
-        const int row0 = grouped ? p.tile_row0[m] : m * NTOK;
+        int g, row0, rows_t;
+        tile_of<NTOK>(p, m, g, row0, rows_t);
         const uint8_t* sf_g = p.w_sf + (static_cast<size_t>(g) * p.sf_tiles + nt) * kblocks * kSfAtom;
         const uint8_t* sf_u = DUAL ? p.w_sf + (static_cast<size_t>(g) * p.sf_tiles + p.dual_offset / kTileN + nt) * kblocks * kSfAtom
                                    : nullptr;
@@ -310,8 +340,8 @@ gemm_mxfp4_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_const
     // kb * 4 + g, i.e. byte kb * 512 + r * 16 + g * 4 + (32-element slice) of the buffer
     auto stage_sfb = [&](int t, int buf) {
       const int m = t / p.n_tiles;
-      const int row0 = grouped ? p.tile_row0[m] : m * NTOK;
-      const int rows = grouped ? min(p.tile_rows[m], NTOK) : min(NTOK, p.dense_rows - row0);
+      int g_, row0, rows;
+      tile_of<NTOK>(p, m, g_, row0, rows);
       uint8_t* dst = sfb_smem + buf * p.sfb_bytes;
       for (int i = epi_tid; i < NTOK * kblocks; i += 128) {
         const int n = i / kblocks, kb = i - n * kblocks;
@@ -337,8 +367,8 @@ gemm_mxfp4_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_const
       // the other scale buffer belonged to the tile before this one, whose products have been drained
       if (t_after < total) stage_sfb(t_after, a ^ 1);
       const int m = t / p.n_tiles, nt = t - m * p.n_tiles;
-      const int row0 = grouped ? p.tile_row0[m] : m * NTOK;
-      const int rows = grouped ? min(p.tile_rows[m], NTOK) : min(NTOK, p.dense_rows - row0);
+      int g_, row0, rows;
+      tile_of<NTOK>(p, m, g_, row0, rows);
       const int n = nt * kTileN + ch;
       ok = mbar_wait(&acc_full[a], aph, abort_flag, p.status, 0x920);
       if (!ok) break;
@@ -567,8 +597,12 @@ extern "C" int fb_gemm_mxfp4(const FbGemmMxfp4Args* a, void* stream_) {
   if (a->ntok != 16 && a->ntok != 32 && a->ntok != 64 && a->ntok != 128) return FB_ERR_SHAPE;
   if (dual && (a->ntok > 64 || a->dual_offset % 128 != 0)) return FB_ERR_SHAPE;
   if (a->out_mode == kOutMxfp8 && (!a->out_scale || a->epilogue == 2 || a->n_out % 32 != 0)) return FB_ERR_SHAPE;
-  const bool grouped = a->tile_group != nullptr;
-  if (grouped && (!a->tile_row0 || !a->tile_rows || !a->num_tok_tiles || a->max_tok_tiles <= 0)) return FB_ERR_SHAPE;
+  const bool slots = a->slot_rows > 0;
+  if (slots && (!a->slot_cnt || a->tile_group || a->slot_rows % a->ntok != 0 ||
+                static_cast<long long>(a->groups) * a->slot_rows > a->x_rows))
+    return FB_ERR_SHAPE;
+  const bool grouped = a->tile_group != nullptr || slots;
+  if (a->tile_group && (!a->tile_row0 || !a->tile_rows || !a->num_tok_tiles || a->max_tok_tiles <= 0)) return FB_ERR_SHAPE;
   if (!grouped && a->groups != 1) return FB_ERR_SHAPE;
   if (a->out_mode == kOutBf16 && ((a->ldo % 8) != 0 || (reinterpret_cast<uintptr_t>(a->out) & 15) || a->n_out % 8 != 0))
     return FB_ERR_ALIGN;
@@ -600,7 +634,9 @@ extern "C" int fb_gemm_mxfp4(const FbGemmMxfp4Args* a, void* stream_) {
   p.dual_offset = a->dual_offset;
   p.dense_rows = a->x_rows;
   p.x_rows_total = a->x_rows;
-  p.max_tok_tiles = a->max_tok_tiles;
+  p.max_tok_tiles = slots ? a->groups * (a->slot_rows / a->ntok) : a->max_tok_tiles;
+  p.slot_cnt = a->slot_cnt;
+  p.slot_rows = slots ? a->slot_rows : 0;
   p.tile_group = a->tile_group;
   p.tile_row0 = a->tile_row0;
   p.tile_rows = a->tile_rows;
@@ -631,7 +667,7 @@ extern "C" int fb_gemm_mxfp4(const FbGemmMxfp4Args* a, void* stream_) {
   p.w_tx_bytes = a->w_fp8 ? kTileN * kBlockK : kTileN * kBlockK / 2;
   p.a_fmt = a->w_fp8 ? 0 : 5;
   p.w_tiled = a->w_tiled;
-  const int tok_tiles = grouped ? a->max_tok_tiles : (a->x_rows + a->ntok - 1) / a->ntok;
+  const int tok_tiles = grouped ? p.max_tok_tiles : (a->x_rows + a->ntok - 1) / a->ntok;
   const int max_tiles = tok_tiles * p.n_tiles;
   if (dual) {
     switch (a->ntok) {

@@ -166,7 +166,7 @@ class GemmMxfp4Args(C.Structure):
         ("max_tok_tiles", C.c_int),
         ("tile_group", C.c_void_p), ("tile_row0", C.c_void_p), ("tile_rows", C.c_void_p), ("num_tok_tiles", C.c_void_p),
         ("dst_row", C.c_void_p), ("row_scale", C.c_void_p), ("act_limit", C.c_float), ("status", C.c_void_p),
-        ("w_tiled", C.c_int), ("w_fp8", C.c_int),
+        ("w_tiled", C.c_int), ("w_fp8", C.c_int), ("slot_cnt", C.c_void_p), ("slot_rows", C.c_int),
     ]
 
 
@@ -233,12 +233,14 @@ def gemm_mxfp4(xq: torch.Tensor, xs: torch.Tensor, w_packed: torch.Tensor, w_sf:
                out: Optional[torch.Tensor] = None, *, out_dtype=torch.bfloat16, epilogue: int = 0, plan=None,
                scatter_rows: Optional[int] = None, act_limit: float = 0.0, ntok: Optional[int] = None,
                out_mx: Optional[Tuple[torch.Tensor, torch.Tensor]] = None, w_rows: Optional[int] = None,
-               w_fp8: bool = False) -> torch.Tensor:
+               w_fp8: bool = False, slots=None) -> torch.Tensor:
     """MXFP4 (or, with `w_fp8`, e4m3) weights x MXFP8 activations on `tcgen05.mma kind::mxf8f6f4.block_scale`.
 
     w_fp8: `w_packed` holds e4m3 codes [groups, N, K], one byte per value, and `w_sf` their scales in the same
     per-32 layout (`fp8_block_sf` replicates a checkpoint's 128 x 128 block scales into it): the tensor core
     applies weight and activation scales itself, nothing is rescaled between k-blocks.
+    slots = (counts int32 [groups], slot_rows): static row slots walked in `ntok`-row tiles instead of the plan's
+    tile table (groups and sub-tiles without rows are skipped; the plan still supplies the scatter tables).
 
     xq uint8 e4m3 [rows, K] + xs UE8M0 [rows, K/32]; w_packed uint8 [groups, N, K/2] (two e2m1 per byte, low
     nibble first) + w_sf from `mxfp4_prepare_sf`.  epilogue 0 store, 1 SwiGLU (rows = [gate | up]), 2 scatter
@@ -279,16 +281,20 @@ def gemm_mxfp4(xq: torch.Tensor, xs: torch.Tensor, w_packed: torch.Tensor, w_sf:
     else:
         a.ldw_bytes, a.w_group_stride_bytes = w_packed.stride(1), w_packed.stride(0)
     a.w_fp8 = 1 if w_fp8 else 0
+    if slots is not None:
+        cnt, slot_rows = slots
+        assert cnt.dtype == torch.int32 and cnt.numel() >= groups and slot_rows % ntok == 0
+        a.slot_cnt, a.slot_rows = cnt.data_ptr(), slot_rows
     a.ldx, a.ldxs = xq.stride(0), xs.stride(0)
     a.n_out, a.k, a.groups, a.w_rows_per_group, a.x_rows = n_out, K, groups, w_rows, rows
     a.ntok, a.epilogue, a.dual_offset = ntok, epilogue, (w_rows // 2 if dual else 0)
     a.act_limit = act_limit
-    if plan is not None:
+    if plan is not None and slots is None:
         a.max_tok_tiles = plan.max_tiles
         a.tile_group, a.tile_row0, a.tile_rows = plan.tile_group.data_ptr(), plan.tile_row0.data_ptr(), plan.tile_rows.data_ptr()
         a.num_tok_tiles = plan.meta.data_ptr()
-        if epilogue == 2:
-            a.dst_row, a.row_scale = plan.dst_row.data_ptr(), plan.row_scale.data_ptr()
+    if plan is not None and epilogue == 2:
+        a.dst_row, a.row_scale = plan.dst_row.data_ptr(), plan.row_scale.data_ptr()
     a.status = status_tensor(xq.device).data_ptr()
     check(lib.fb_gemm_mxfp4(C.byref(a), stream_ptr()), "fb_gemm_mxfp4")
     return out

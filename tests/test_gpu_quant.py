@@ -209,6 +209,55 @@ def test_gemm_fp8_static_slots_skip_empty_experts_and_requantise(slot, counts):
     assert torch.equal(a, b_)
 
 
+@pytest.mark.parametrize("slot,sub,counts,w_fp8", [(64, 16, [40, 0, 64, 1, 33, 0, 0, 17], True),
+                                                   (32, 16, [3, 0, 32, 1, 0, 0, 16, 9], False),
+                                                   (64, 32, [0, 0, 5, 0, 64, 0, 31, 33], False)])
+def test_block_scaled_gemm_walks_static_slots_in_short_tiles(slot, sub, counts, w_fp8):
+    """Slot mode of the block-scaled GEMM: a `slot`-row slot per expert walked in `sub`-row tiles gives bit for bit
+    the result of one `slot`-row tile per expert over an explicit table (gate|up with MXFP8 requant, then the
+    scatter GEMM), touches nothing outside the filled rows, and skips experts and sub-tiles without rows."""
+    from ferrule_b200.ops import kernels as K
+    from ferrule_b200.ops import quant as Q
+    E, H, I = len(counts), 512, 256
+    x = rnd(E * slot, H, scale=1.5, seed=61)
+    xq, xs = Q.quant_mxfp8_rows(x)
+    w13 = rnd(E, 2 * I, H, scale=0.05, seed=62)
+    w2 = rnd(E, H, I, scale=0.05, seed=63)
+    if w_fp8:
+        def prep(w):
+            packs = [enc.weight_quant_fp8_block(w[e].float().cpu()) for e in range(E)]
+            q = torch.stack([p_[0] for p_ in packs]).cuda()
+            sc = torch.stack([p_[1] for p_ in packs]).cuda()
+            return q, Q.fp8_block_sf(sc, w.shape[1], w.shape[2])
+    else:
+        def prep(w):
+            G, O, Kk = w.shape
+            packed, sb = Q.quant_mxfp4_rows(w.reshape(G * O, Kk).contiguous())
+            return packed.view(G, O, Kk // 2), Q.mxfp4_prepare_sf(sb.view(G, O, Kk // 32))
+    (c13, sf13), (c2, sf2) = prep(w13), prep(w2)
+    cnt = torch.tensor(counts, dtype=torch.int32, device="cuda")
+    i32 = dict(dtype=torch.int32, device="cuda")
+    ar = torch.arange(E, **i32)
+    plan = K.MoePlan(slot, E, E * slot, torch.zeros(E * slot, **i32), torch.arange(E * slot, **i32),
+                     torch.ones(E * slot, device="cuda"), ar, ar * slot, cnt, cnt, torch.tensor([E, E * slot], **i32))
+
+    def run(**kw):
+        hq = torch.full((E * slot, I), 9, dtype=torch.uint8, device="cuda")
+        hs = torch.full((E * slot, I // 32), 9, dtype=torch.uint8, device="cuda")
+        Q.gemm_mxfp4(xq, xs, c13, sf13, epilogue=1, plan=plan, act_limit=7.0, out_mx=(hq, hs), w_fp8=w_fp8, **kw)
+        out = torch.full((E * slot, H), 3.0, dtype=torch.bfloat16, device="cuda")
+        Q.gemm_mxfp4(hq, hs, c2, sf2, out=out, epilogue=2, plan=plan, w_fp8=w_fp8, **kw)
+        return hq, hs, out
+    hq0, hs0, out0 = run()
+    hq1, hs1, out1 = run(slots=(cnt, slot), ntok=sub)
+    assert torch.equal(hq0, hq1) and torch.equal(hs0, hs1) and torch.equal(out0, out1)
+    for e, c in enumerate(counts):
+        r0 = e * slot
+        assert int((hq1[r0 + c:r0 + slot] != 9).sum()) == 0 and float((out1[r0 + c:r0 + slot].float() - 3).abs().sum()) == 0
+        if c:
+            assert float(out1[r0:r0 + c].float().abs().max()) > 0 and float((out1[r0:r0 + c].float() - 3).abs().min()) >= 0
+
+
 @pytest.mark.parametrize("rows,n,k,dual", [(32, 1408, 2048, False), (7, 256, 512, True), (32, 2048, 1408 - 1408 % 128, False)])
 def test_gemm_mxfp4_weights_group_scaled(rows, n, k, dual):
     """MXFP4 weights (e2m1 + UE8M0 per 32) expanded to e4m3 containers, FP8 activations."""
