@@ -322,6 +322,10 @@ def main() -> None:
     for r, ts in token_times.items():
         if len(ts) > 2:
             tpots.append((ts[-1] - ts[1]) / (len(ts) - 2))
+    # what a decode step reads: every weight except the embedding table (a step gathers B of its rows)
+    streamed_bytes = weights.nbytes()
+    if weights.embed.data_ptr() != weights.lm_head.data_ptr():
+        streamed_bytes -= weights.embed.numel() * weights.embed.element_size()
     if rank == 0:
         value = B * K / (dev_ms / 1e3)
         e2e_value = B * K / (e2e_ms / 1e3)
@@ -337,7 +341,7 @@ def main() -> None:
                                          % (min(start_pos), max(start_pos) + K),
                        "parallelism": par, "kv_page_size": page, "layers": cfg.n_layers,
                        "l2_policy": "inputs larger than L2: each step streams %.1f GB of weights per GPU"
-                                    % (weights.nbytes() / 1e9),
+                                    % (streamed_bytes / 1e9),
                        "collectives": "none" if world == 1 else ("nccl" if args.no_fused else (
                            "fused-p2p%s, %s partials" % (" (multicast push)" if args.mc_push else "", args.ar_payload) if args.collective == "ll"
                            else "in-switch multimem reduce + broadcast (bf16)"))},
