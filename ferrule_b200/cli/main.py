@@ -90,6 +90,8 @@ def build_engine(args, layout=None):
     from ..runtime.scheduler import SchedulerConfig
     from ..utils.tokenizer import load_tokenizer
     dev = args.device or ("cuda" if torch.cuda.is_available() else "cpu")
+    if args.model_dir and _is_v4_dir(args.model_dir):
+        return _build_v4_engine(args, dev, args.model_dir)
     if args.model_dir:
         from ..io.checkpoint import load_deepseek_hf
         weights = load_deepseek_hf(args.model_dir, device=dev, dtype=torch.bfloat16 if dev != "cpu" else torch.float32)
@@ -138,9 +140,17 @@ def build_engine(args, layout=None):
     return eng, load_tokenizer(args.model_dir), name
 
 
-def _build_v4_engine(args, dev):
-    """Random-init DeepSeek-V4 family model (tiny shape) behind the engine: slot-bound state, one token per
-    sequence per step."""
+def _is_v4_dir(model_dir: str) -> bool:
+    try:
+        with open(os.path.join(model_dir, "config.json")) as f:
+            return json.load(f).get("model_type") == "deepseek_v4"
+    except OSError:
+        return False
+
+
+def _build_v4_engine(args, dev, model_dir: Optional[str] = None):
+    """DeepSeek-V4 family model behind the engine (slot-bound state): a checkpoint directory, or the random-init
+    tiny shape."""
     import torch
 
     from ..models.v4_model import random_v4_weights, tiny_v4
@@ -148,8 +158,13 @@ def _build_v4_engine(args, dev):
     from ..runtime.engine import Engine, EngineConfig
     from ..runtime.scheduler import SchedulerConfig
     from ..utils.tokenizer import load_tokenizer
-    cfg = tiny_v4()
-    weights = random_v4_weights(cfg, device=dev, seed=args.seed)
+    if model_dir:
+        from ..io.v4_checkpoint import load_v4_hf
+        weights = load_v4_hf(model_dir, device=dev)
+        cfg = weights.cfg
+    else:
+        cfg = tiny_v4()
+        weights = random_v4_weights(cfg, device=dev, seed=args.seed)
     ctx = min(args.ctx_size, cfg.max_position)
     pages_per_seq = (ctx + args.page_size - 1) // args.page_size
     n_pages = args.max_seqs * pages_per_seq + 8
@@ -159,7 +174,8 @@ def _build_v4_engine(args, dev):
                             max_batch_tokens=args.max_batch_tokens, prefill_chunk_size=args.prefill_chunk,
                             ctx_size=pages_per_seq * args.page_size)
     eng = Engine(runner, EngineConfig(scheduler=sched, kv_pages=n_pages, page_size=args.page_size))
-    return eng, load_tokenizer(None), "deepseek-v4-tiny"
+    name = os.path.basename(os.path.normpath(model_dir)) if model_dir else "deepseek-v4-tiny"
+    return eng, load_tokenizer(model_dir), name
 
 
 # ------------------------------------------------------------------------------------------ commands
@@ -175,7 +191,30 @@ def cmd_info(args) -> int:
         p = torch.cuda.get_device_properties(0)
         out["device"] = {"name": p.name, "sm": f"{p.major}{p.minor}", "sms": p.multi_processor_count,
                          "memory_gb": round(p.total_memory / 2 ** 30, 1)}
-    if args.model_dir:
+    def plan_of(cfg, weight_format="bf16", tp=1, pp=1):
+        """The support contract's verdict on a configuration: which policies apply and whether this build runs it."""
+        from dataclasses import asdict
+        from ..models.support import EnginePlan, ParallelismPlan, PolicySet
+        ps = PolicySet.from_config(cfg, weight_format, ParallelismPlan(tensor_parallel=tp, pipeline_parallel=pp))
+        plan = EnginePlan.from_policies(ps, cfg.n_heads, cfg.n_routed_experts, cfg.n_layers, cfg.vocab_size)
+        def enc(o):
+            return {k: (v.value if hasattr(v, "value") else (list(v) if isinstance(v, tuple) else v))
+                    for k, v in asdict(o).items()}
+        return {"family": plan.family, "status": plan.status.value,
+                "missing": [{"area": m.area, "reason": m.reason} for m in plan.missing],
+                "policies": {k: enc(getattr(ps, k)) for k in ("attention", "router", "expert", "quant", "kv", "residency",
+                                                             "parallelism", "speculation")}}
+    if args.model_dir and _is_v4_dir(args.model_dir):
+        from dataclasses import asdict
+        from ..io.safetensors import ShardedCheckpoint
+        from ..io.v4_checkpoint import v4_config_from_hf
+        with open(os.path.join(args.model_dir, "config.json")) as f:
+            vcfg = v4_config_from_hf(json.load(f))
+        ck = ShardedCheckpoint(args.model_dir)
+        out["checkpoint"] = {"family": "deepseek_v4", "tensors": len(ck.names()),
+                             "shards": len(set(ck.weight_map.values())), "config": asdict(vcfg)}
+        out["engine_plan"] = plan_of(vcfg)
+    elif args.model_dir:
         from ..io.safetensors import ShardedCheckpoint
         from ..models.families import detect_family, layout_summary
         ck = ShardedCheckpoint(args.model_dir)
@@ -184,9 +223,11 @@ def cmd_info(args) -> int:
         out["checkpoint"] = {"family": fam.value, "tensors": len(ck.names()), "shards": len(set(ck.weight_map.values())),
                              "roles": layout_summary(ck.names(), fam, cfg.n_layers if cfg else None),
                              "config": cfg.to_dict() if cfg else None}
+        if cfg is not None:
+            out["engine_plan"] = plan_of(cfg)
     else:
         out["presets"] = {k: {"params_b": round(f().param_count() / 1e9, 3), "layers": f().n_layers,
-                              "hidden": f().hidden} for k, f in C.PRESETS.items()}
+                              "hidden": f().hidden, "engine_plan": plan_of(f())["status"]} for k, f in C.PRESETS.items()}
     print(json.dumps(out, indent=1))
     return 0
 
@@ -241,6 +282,21 @@ def cmd_make_fixture(args) -> int:
     from ..io.checkpoint import export_hf
     from ..models import config as C
     from ..models import weights as W
+    if args.family == "v4":
+        # DeepSeek-V4 layout: FP8 attention / shared experts, packed FP4 routed experts unless told otherwise
+        from ..io.v4_checkpoint import export_v4_hf
+        from ..models.v4_model import random_v4_weights, tiny_v4
+        cfg = tiny_v4()
+        if args.layers:
+            ratios = tuple(cfg.compress_ratios[i % len(cfg.compress_ratios)] for i in range(args.layers))
+            cfg = cfg.with_(n_layers=args.layers, compress_ratios=ratios)
+        w = random_v4_weights(cfg, seed=args.seed, std=0.0 if args.zeros else 0.05)
+        dense = "fp8_block" if args.dense_format == "plain" and not args.plain else args.dense_format
+        expert = "mxfp4" if args.expert_format == "plain" and not args.plain else args.expert_format
+        export_v4_hf(w, args.out, dense_format=dense, expert_format=expert, shard_bytes=args.shard_mb << 20)
+        print(json.dumps({"written": args.out, "family": "deepseek_v4", "layers": cfg.n_layers,
+                          "dense_format": dense, "expert_format": expert}))
+        return 0
     cfg = C.PRESETS[args.preset]()
     if args.layers:
         cfg = cfg.with_(n_layers=args.layers)
@@ -553,6 +609,9 @@ def main(argv: Optional[List[str]] = None) -> int:
     p.add_argument("--zeros", action="store_true"); p.add_argument("--shard-mb", type=int, default=1024)
     p.add_argument("--dense-format", default="plain", choices=["plain", "fp8_block"])
     p.add_argument("--expert-format", default="plain", choices=["plain", "fp8_block", "mxfp4"])
+    p.add_argument("--family", default="deepseek", choices=["deepseek", "v4"],
+                   help="v4: a DeepSeek-V4 directory (tiny shape; FP8 dense + packed FP4 experts unless --plain)")
+    p.add_argument("--plain", action="store_true", help="--family v4: keep every linear in BF16")
     p.set_defaults(fn=cmd_make_fixture)
     p = sub.add_parser("inspect-weightpack"); p.add_argument("model_dir"); p.add_argument("--json", action="store_true")
     p.add_argument("--limit", type=int, default=40); p.set_defaults(fn=cmd_inspect)
