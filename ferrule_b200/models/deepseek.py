@@ -769,10 +769,11 @@ class CudaForward:
                 plan.tile_rows.copy_(tr0)
             arena.ensure(layer, wave)
             arena.resolve_plan(layer, plan)
-            K.gemm(ws.xg[:T * k], lw.e_w13, out=ws.hmid[:T * k], epilogue=K.EPI_SWIGLU, plan=plan,
-                   act_limit=cfg.swiglu_limit)
-            K.gemm(ws.hmid[:T * k], lw.e_w2, out=route_out.view(T * ws.slots, H), epilogue=K.EPI_SCATTER,
-                   plan=plan, scatter_rows=T * ws.slots)
+            # `_gemm` takes bf16 frames and quantised ones alike (the frames hold the experts' own form)
+            self._gemm(ws.xg[:T * k], lw.e_w13, ws.hmid[:T * k], slot="xg", epilogue=K.EPI_SWIGLU, plan=plan,
+                       act_limit=cfg.swiglu_limit)
+            self._gemm(ws.hmid[:T * k], lw.e_w2, route_out.view(T * ws.slots, H), slot="hmid", epilogue=K.EPI_SCATTER,
+                       plan=plan, scatter_rows=T * ws.slots)
             arena.release(layer)
         if side is not None:
             torch.cuda.current_stream().wait_stream(side)
@@ -795,10 +796,10 @@ class CudaForward:
             raise NeedExperts(layer, missing)
         arena.resolve_plan(layer, plan)
         route_out = ws.route_out[:T]
-        K.gemm(ws.xg[:T * k], lw.e_w13, out=ws.hmid[:T * k], epilogue=K.EPI_SWIGLU, plan=plan,
-               act_limit=cfg.swiglu_limit)
-        K.gemm(ws.hmid[:T * k], lw.e_w2, out=route_out.view(T * ws.slots, H), epilogue=K.EPI_SCATTER,
-               plan=plan, scatter_rows=T * ws.slots)
+        self._gemm(ws.xg[:T * k], lw.e_w13, ws.hmid[:T * k], slot="xg", epilogue=K.EPI_SWIGLU, plan=plan,
+                   act_limit=cfg.swiglu_limit)
+        self._gemm(ws.hmid[:T * k], lw.e_w2, route_out.view(T * ws.slots, H), slot="hmid", epilogue=K.EPI_SCATTER,
+                   plan=plan, scatter_rows=T * ws.slots)
         if self.lease_sink is None:
             arena.release_leases(layer, list(held.values()))
         if side is not None:

@@ -41,14 +41,37 @@ class ArenaStats:
     ensure_calls: int = 0
 
 
+_QW_PARTS = ("q", "scale", "packed", "sf")
+
+
+def _parts(w) -> List[torch.Tensor]:
+    """The per-expert tensors of an expert weight: the bf16 tensor itself, or the codes / scales / packed values /
+    arranged scale factors of a quantised one (each indexed by expert in its first dimension)."""
+    if isinstance(w, QuantWeight):
+        return [getattr(w, n) for n in _QW_PARTS if getattr(w, n) is not None]
+    return [w]
+
+
+def _like(w, parts: List[torch.Tensor]):
+    """`w` rebuilt over other tensors of the same kinds (frames instead of the full expert set)."""
+    if not isinstance(w, QuantWeight):
+        return parts[0]
+    it = iter(parts)
+    kw = {n: (next(it) if getattr(w, n) is not None else None) for n in _QW_PARTS}
+    return QuantWeight(kw["q"], kw["scale"], w.group32, kw["packed"], kw["sf"])
+
+
 class _LayerArena:
-    def __init__(self, layer: int, w13: torch.Tensor, w2: torch.Tensor, frames: int, device):
-        E = w13.shape[0]
+    def __init__(self, layer: int, w13, w2, frames: int, device):
+        """w13 / w2: bf16 tensors [experts, ...] or `QuantWeight`s (FP8 blocks, MXFP4 containers or packed MXFP4):
+        a frame holds one expert in the model's own form, so streamed experts cost their quantised bytes."""
+        src = _parts(w13) + _parts(w2)
+        self.n13 = len(_parts(w13))
+        E = src[0].shape[0]
         self.layer, self.n_experts, self.frames = layer, E, frames
-        self.host13 = w13.cpu().pin_memory() if device.type == "cuda" else w13.cpu()
-        self.host2 = w2.cpu().pin_memory() if device.type == "cuda" else w2.cpu()
-        self.dev13 = torch.zeros(frames, *w13.shape[1:], dtype=w13.dtype, device=device)
-        self.dev2 = torch.zeros(frames, *w2.shape[1:], dtype=w2.dtype, device=device)
+        self.host = [t.cpu().pin_memory() if device.type == "cuda" else t.cpu() for t in src]
+        self.dev = [torch.zeros(frames, *t.shape[1:], dtype=t.dtype, device=device) for t in src]
+        self.dev13, self.dev2 = _like(w13, self.dev[:self.n13]), _like(w2, self.dev[self.n13:])
         i32 = dict(dtype=torch.int32, device=device)
         self.expert_to_slot = torch.full((E,), -1, **i32)
         self.slot_expert = torch.full((frames,), -1, **i32)
@@ -57,7 +80,11 @@ class _LayerArena:
         self.coord = ExpertResidencyCoordinator(layer, frames, E)
         self.leases: List[tuple] = []
         self.consumer_event: Optional[torch.cuda.Event] = None
-        self.expert_bytes = (self.host13[0].numel() + self.host2[0].numel()) * w13.element_size()
+        self.expert_bytes = sum(t[0].numel() * t.element_size() for t in self.host)
+
+    def copy_in(self, slot: int, expert: int, non_blocking: bool = False) -> None:
+        for d, h in zip(self.dev, self.host):
+            d[slot].copy_(h[expert], non_blocking=non_blocking)
 
 
 class ExpertArena:
@@ -76,8 +103,6 @@ class ExpertArena:
         for i, lw in enumerate(all_layers):
             if not lw.is_moe or lw.e_w13 is None:
                 continue
-            if isinstance(lw.e_w13, QuantWeight):
-                raise NotImplementedError("the arena streams bf16 experts; quantised experts stay resident")
             E = lw.e_w13.shape[0]
             frames = max(min_frames, min(E, int(round(E * resident_fraction))), 1)
             la = _LayerArena(i, lw.e_w13, lw.e_w2, frames, self.device)
@@ -118,15 +143,13 @@ class ExpertArena:
                 up.wait_event(la.consumer_event)        # no frame is overwritten under a running kernel
             with torch.cuda.stream(up):
                 for t in tickets:
-                    la.dev13[t.slot].copy_(la.host13[t.expert], non_blocking=True)
-                    la.dev2[t.slot].copy_(la.host2[t.expert], non_blocking=True)
+                    la.copy_in(t.slot, t.expert, non_blocking=True)
                 done = torch.cuda.Event()
                 done.record(up)
             torch.cuda.current_stream().wait_event(done)
         else:
             for t in tickets:
-                la.dev13[t.slot].copy_(la.host13[t.expert])
-                la.dev2[t.slot].copy_(la.host2[t.expert])
+                la.copy_in(t.slot, t.expert)
         for j, t in enumerate(tickets):
             la.coord.activate(t)
             la.coord.publish(t)
@@ -175,13 +198,11 @@ class ExpertArena:
             if la.consumer_event is not None:
                 up.wait_event(la.consumer_event)
             with torch.cuda.stream(up):
-                la.dev13[t.slot].copy_(la.host13[t.expert], non_blocking=True)
-                la.dev2[t.slot].copy_(la.host2[t.expert], non_blocking=True)
+                la.copy_in(t.slot, t.expert, non_blocking=True)
                 ev = torch.cuda.Event()
                 ev.record(up)
         else:
-            la.dev13[t.slot].copy_(la.host13[t.expert])
-            la.dev2[t.slot].copy_(la.host2[t.expert])
+            la.copy_in(t.slot, t.expert)
         return t, ev
 
     def finish_install(self, layer: int, ticket) -> None:

@@ -125,3 +125,36 @@ def test_native_direct_reader_feeds_the_provider(tmp_path):
     assert st["completed"] == 24 and st["bytes"] == sum(cat.source(1, e).payload_bytes for e in range(8)) or st["bytes"] > 0
     prov.close()
     ck.close()
+
+
+@pytest.mark.parametrize("fmt", ["fp8_block", "fp8_mxfp4"])
+def test_model_arena_holds_quantised_experts_in_their_own_form(fmt):
+    """The routed-expert arena of the model (models/expert_arena.py) over quantised experts: every frame carries
+    the expert's codes and scales (and nothing is dequantised), uploads bring exactly the host bytes, eviction and
+    re-upload restore them, and the layer's weights become views of the frames."""
+    import torch
+    from ferrule_b200.models import config as C, weights as W
+    from ferrule_b200.models.expert_arena import ExpertArena, _parts
+    from ferrule_b200.models.weights import QuantWeight
+    cfg = C.tiny_fixture().with_(hidden=256, moe_inter=128, n_mtp_layers=0)
+    w = W.random_weights(cfg, device="cpu", seed=1, dtype=torch.bfloat16, weight_format=fmt)
+    lw = w.layers[1]
+    assert isinstance(lw.e_w13, QuantWeight)
+    full13, full2 = [t.clone() for t in _parts(lw.e_w13)], [t.clone() for t in _parts(lw.e_w2)]
+    arena = ExpertArena(w, resident_fraction=0.5)
+    la = arena.layers[1]
+    E = cfg.n_routed_experts
+    assert la.frames == E // 2 and isinstance(lw.e_w13, QuantWeight) and lw.e_w13.group32 == (fmt == "fp8_mxfp4")
+    assert lw.e_w13.q.shape[0] == la.frames and lw.e_w13.shape[1:] == full13[0].shape[1:]
+    assert la.expert_bytes == sum(t[0].numel() * t.element_size() for t in full13 + full2)
+    for wave in ([0, 3, 5], [1, 2, 6], [0, 7]):
+        arena.ensure(1, wave)
+        for e in wave:
+            slot = int(la.expert_to_slot[e])
+            assert slot >= 0 and int(la.slot_expert[slot]) == e
+            for dev, src in zip(_parts(lw.e_w13), full13):
+                assert torch.equal(dev[slot], src[e])
+            for dev, src in zip(_parts(lw.e_w2), full2):
+                assert torch.equal(dev[slot], src[e])
+        arena.release(1)
+    assert arena.stats.evictions > 0 and arena.stats.upload_bytes == arena.stats.uploads * la.expert_bytes

@@ -192,9 +192,11 @@ def test_quantised_forward_matches_dequantised_oracle(fmt, preset):
     _lib.raise_on_status()
 
 
-def test_streamed_experts_at_half_residency_equal_resident_run():
+@pytest.mark.parametrize("weight_format", ["bf16", "fp8_block", "fp8_mxfp4"])
+def test_streamed_experts_at_half_residency_equal_resident_run(weight_format):
     """Half of every layer's routed experts fit on the device; the rest stream from pinned host memory through
-    stable slots.  The greedy streams must equal those of the fully resident model (same kernels, same weights)."""
+    stable slots.  The greedy streams must equal those of the fully resident model (same kernels, same weights).
+    Quantised experts stream in their own form: a frame holds codes, scales and arranged scale factors."""
     from ferrule_b200.models.runner import DeepSeekRunner
     from ferrule_b200.ops import _lib
     from ferrule_b200.runtime.engine import Engine, EngineConfig, TokenEvent
@@ -205,7 +207,7 @@ def test_streamed_experts_at_half_residency_equal_resident_run():
     prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (33, 70)]
 
     def run(residency):
-        w = W.random_weights(cfg, device="cuda", seed=6, std=0.05)
+        w = W.random_weights(cfg, device="cuda", seed=6, std=0.05, weight_format=weight_format)
         runner = DeepSeekRunner(w, n_pages=32, page_size=64, max_rows=256, max_seqs=4, max_seq_len=512, device="cuda",
                                 expert_residency=residency, use_graphs=False)
         sched = SchedulerConfig(max_active_sequences=4, max_decode_batch=4, max_batch_tokens=256,
@@ -225,3 +227,7 @@ def test_streamed_experts_at_half_residency_equal_resident_run():
     assert got == want
     st = runner.arena.stats
     assert runner.arena.frames(1) == 8 and st.uploads > 8 and st.evictions > 0 and st.hits > 0
+    if weight_format != "bf16":
+        la = runner.arena.layers[1]
+        bf16_bytes = 3 * cfg.hidden * cfg.moe_inter * 2
+        assert la.expert_bytes < 0.6 * bf16_bytes, "a streamed expert costs its quantised bytes"
