@@ -118,6 +118,8 @@ def main() -> None:
     ap.add_argument("--moe", default="replicated", choices=["replicated", "dispatch"],
                     help="N > 1: experts by id over replicated activations, or token-dispatch expert parallelism "
                          "(every rank routes its slice of the tokens; dispatch / combine all-to-alls over peer memory)")
+    ap.add_argument("--router-zipf", type=float, default=0.0,
+                    help="expert popularity skew: N(0, 1) router logits plus a Zipf(s) selection bias per layer")
     ap.add_argument("--pp", type=int, default=1,
                     help="pipeline stages (N must be a multiple): each stage holds a contiguous range of layers over "
                          "N/pp tensor-parallel ranks; steps run eagerly (no graphs), so the device-timed number is the "
@@ -172,7 +174,7 @@ def main() -> None:
     from ferrule_b200.parallel.pp import stage_range, stage_weights
     weights = W.random_weights(cfg, device=dev, seed=0, tp_rank=lay.tp_rank if lay else 0, tp_world=args.shard_as or tp_world,
                                fast_device_init=True, weight_format=args.weight_format,
-                               replicate_shared=(tp_world > 1 and args.moe == "dispatch"),
+                               replicate_shared=(tp_world > 1 and args.moe == "dispatch"), router_zipf=args.router_zipf,
                                layer_range=stage_range(cfg.n_layers, lay.pp_rank, lay.pp_size) if pp is not None else None)
     if pp is not None:
         weights = stage_weights(weights, lay.pp_rank, lay.pp_size)

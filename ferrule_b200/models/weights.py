@@ -373,11 +373,14 @@ def _layer_random(cfg: ModelConfig, layer: int, init: _Init, tp_rank: int, tp_wo
 def random_weights(cfg: ModelConfig, device="cpu", dtype=torch.bfloat16, seed: int = 0, std: float = 0.02,
                    tp_rank: int = 0, tp_world: int = 1, fast_device_init: bool = False,
                    weight_format: str = "bf16", replicate_shared: bool = False,
-                   layer_range: Optional[Tuple[int, int]] = None) -> ModelWeights:
+                   layer_range: Optional[Tuple[int, int]] = None, router_zipf: float = 0.0) -> ModelWeights:
     """Random-init weights N(0, std), norms = 1.
 
     fast_device_init draws on the GPU (much faster for multi-GB models; values then differ
     between TP layouts, which is fine for throughput runs but not for parity tests).
+    router_zipf s > 0: skewed expert popularity for residency / streaming runs - router rows are scaled so that
+    logits over normalised activations are N(0, 1), and every MoE layer gets a selection bias that follows a
+    Zipf(s) popularity over a fixed random order of its experts (see `zipf_router_bias`).
     layer_range (lo, hi): build only these layers (a pipeline stage of a model whose whole image does not fit one
     GPU); the other entries of `layers` are None and the draws differ from the full image's, so it needs
     fast_device_init.
@@ -405,4 +408,26 @@ def random_weights(cfg: ModelConfig, device="cpu", dtype=torch.bfloat16, seed: i
     w = ModelWeights(cfg, embed, layers, init.ones(cfg.hidden), lm_head, mtp, tp_rank, tp_world,
                      e_lo, e_hi, v_lo, weight_format=weight_format)
     w.shared_replicated = bool(replicate_shared and tp_world > 1)
+    if router_zipf > 0:
+        for i, lw in enumerate(w.layers):
+            if lw is not None and lw.is_moe and lw.router_w is not None:
+                lw.router_w = (lw.router_w.float() * (1.0 / (std * cfg.hidden ** 0.5))).to(lw.router_w.dtype)
+                lw.router_bias = zipf_router_bias(cfg.n_routed_experts, router_zipf, seed * 7919 + i,
+                                                  sigmoid=cfg.score_fn != 0).to(lw.router_w.device)
     return w
+
+
+def zipf_router_bias(n_experts: int, s: float, seed: int, sigmoid: bool = True) -> torch.Tensor:
+    """Selection bias that makes expert popularity follow Zipf(s): popularity p_r ~ r^-s over a fixed random order of
+    the experts, bias = log p (centred).  Routers that pick on sigmoid scores in (0, 1) get the bias scaled into
+    [-0.5, 0.5], so that the skew shapes the choice without fixing it; softmax-style routers add it to the logits'
+    scale directly."""
+    g = torch.Generator().manual_seed(seed)
+    order = torch.randperm(n_experts, generator=g)
+    logp = -s * torch.log(torch.arange(1, n_experts + 1, dtype=torch.float32))
+    logp = logp - logp.mean()
+    if sigmoid:
+        logp = 0.5 * logp / logp.abs().max()
+    bias = torch.empty(n_experts, dtype=torch.float32)
+    bias[order] = logp
+    return bias

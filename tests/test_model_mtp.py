@@ -68,3 +68,29 @@ def test_mtp_rows_follow_published_positions():
     assert first_pos0 == 0 and first_n == 29 and pos == 29 and after == 29     # whole prompt queued, then written
     for (p0, n), pos, after in seen[1:]:
         assert p0 + n == pos and after == pos                                  # contiguous afterwards
+
+
+def test_zipf_router_bias_skews_expert_popularity():
+    """`random_weights(router_zipf=s)`: unit-variance router logits plus a Zipf selection bias - the routed-expert
+    histogram becomes skewed (the head of the popularity order takes most routes) while every token still
+    chooses by its own logits (different tokens pick different experts)."""
+    import torch
+    from ferrule_b200.models import config as C, weights as W
+    from ferrule_b200.models.weights import zipf_router_bias
+    from ferrule_b200.ops import reference as ref
+    b = zipf_router_bias(64, 1.1, seed=3)
+    assert abs(float(b.mean())) < 1e-6 and float(b.abs().max()) <= 0.5 + 1e-6 and len(set(b.tolist())) == 64
+    assert torch.equal(b, zipf_router_bias(64, 1.1, seed=3)) and not torch.equal(b, zipf_router_bias(64, 1.1, seed=4))
+    cfg = C.deepseek_v2_lite().with_(n_layers=2, vocab_size=1024, score_fn=1, router_bias=True)
+    w = W.random_weights(cfg, device="cpu", seed=0, router_zipf=1.1)
+    lw = w.layers[1]
+    g = torch.Generator().manual_seed(1)
+    x = torch.randn(2000, cfg.hidden, generator=g)
+    x = x / x.pow(2).mean(-1, keepdim=True).sqrt()
+    logits = x @ lw.router_w.float().T
+    assert 0.8 < float(logits.std()) < 1.25
+    idx, _ = ref.route(logits, cfg.topk, cfg.score_fn, bias=lw.router_bias)
+    hist = torch.bincount(idx.flatten(), minlength=cfg.n_routed_experts).float()
+    top = hist.sort(descending=True).values
+    assert float(top[:8].sum() / hist.sum()) > 0.25 > 8 / 64 and int((hist > 0).sum()) > 32
+    assert len({tuple(r) for r in idx[:50].tolist()}) > 25
