@@ -41,6 +41,9 @@ class _Entry(Generic[T]):
 
 class FairQueue(Generic[T]):
     def __init__(self, cfg: Optional[FairQueueConfig] = None):
+        if cfg is not None and (len(cfg.quantum) != len(Band) or min(cfg.quantum) <= 0 or cfg.aging_ticks <= 0
+                                or cfg.debt_bound < 0):
+            raise ValueError("fair queue: every band needs a positive quantum, aging_ticks > 0, debt_bound >= 0")
         self.cfg = cfg or FairQueueConfig()
         self._q: Dict[Band, Deque[_Entry[T]]] = {b: deque() for b in Band}
         self._credit: Dict[Band, int] = {b: 0 for b in Band}

@@ -27,7 +27,7 @@ from enum import Enum
 from typing import Deque, Dict, Iterable, List, Optional, Set, Tuple
 
 from .fairness import Band, FairQueue, FairQueueConfig
-from .io_protocol import (CompletionEvent, CompletionExpectation, CompletionOutcome, DependencySet, FailureReason,
+from .io_protocol import (IoProtocolError, CompletionEvent, CompletionExpectation, CompletionOutcome, DependencySet, FailureReason,
                           LoadStage, MaterializationKey, Purpose, RetirementReason, RetirementToken,
                           validate_transition)
 from .ledger import CriticalPathLedger, LedgerPhase
@@ -179,6 +179,13 @@ class LoadRegistry:
     # ------------------------------------------------------------------ continuations
     def register_continuation(self, txn_id: int, deps) -> None:
         keys = deps.keys if isinstance(deps, DependencySet) else list(deps)
+        # checked before anything is touched: a rejected registration leaves no owner, lease or operation behind
+        if txn_id in self.conts:
+            raise IoProtocolError(f"continuation {txn_id} is already registered")
+        if len(set(keys)) != len(keys):
+            raise IoProtocolError(f"continuation {txn_id} names a dependency twice")
+        if self._shutdown:
+            raise RuntimeError("registry is shut down")
         needs, all_ops = set(), []
         for k in keys:
             op_id = self.request(k, (OwnerKind.EXECUTION, txn_id), Purpose.EXECUTION)
@@ -406,6 +413,22 @@ class LoadRegistry:
         self.stats.submitted_installs += 1
 
     # ------------------------------------------------------------------ cancel / retire / evict
+    def detach(self, op_id: int, owner: Tuple[OwnerKind, int]) -> bool:
+        """`owner` no longer wants the payload.  The operation goes on while anyone else owns it, waits for it or
+        leases it; the last owner's detach cancels it (at once if nothing was submitted, after the completion of
+        submitted work otherwise).  -> True when this detach cancelled the operation.  Detaching twice, or an owner
+        that never attached, is a protocol error."""
+        op = self.ops.get(op_id)
+        if op is None:
+            raise IoProtocolError(f"unknown operation {op_id}")
+        if owner not in op.owners:
+            raise IoProtocolError(f"operation {op_id}: {owner} is not an owner (duplicate detach?)")
+        op.owners.discard(owner)
+        if op.owners or op.waiters or op.leases or op.stage in (LoadStage.RESIDENT, LoadStage.RETIRED):
+            return False
+        self.cancel(op_id)
+        return True
+
     def cancel(self, op_id: int) -> None:
         op = self.ops.get(op_id)
         if op is None or op.stage in (LoadStage.RETIRED,):
