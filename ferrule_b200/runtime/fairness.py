@@ -114,6 +114,8 @@ class FairQueue(Generic[T]):
 
     def _serve(self, b: Band) -> Tuple[Band, T]:
         e = self._q[b].popleft()
-        self._credit[b] -= e.cost
+        # forced progress (aging, oversized costs) is served on credit the band does not have: the debt is capped,
+        # so a band that was pushed ahead for a while does not pay for it forever
+        self._credit[b] = max(self._credit[b] - e.cost, -self.cfg.debt_bound * self.cfg.quantum[b])
         self.served[b] += 1
         return b, e.item
