@@ -180,18 +180,24 @@ class LoadRegistry:
     def register_continuation(self, txn_id: int, deps) -> None:
         keys = deps.keys if isinstance(deps, DependencySet) else list(deps)
         # checked before anything is touched: a rejected registration leaves no owner, lease or operation behind
-        if txn_id in self.conts:
-            raise IoProtocolError(f"continuation {txn_id} is already registered")
+        prev = self.conts.get(txn_id)
+        if prev is not None and (prev.needs or prev.failed):
+            raise IoProtocolError(f"continuation {txn_id} is already registered and unresolved")
         if len(set(keys)) != len(keys):
             raise IoProtocolError(f"continuation {txn_id} names a dependency twice")
         if self._shutdown:
             raise RuntimeError("registry is shut down")
-        needs, all_ops = set(), []
+        # a transaction that was resumed and has to wait again extends its continuation: it keeps the custody of
+        # what it already holds and takes a lease on the new payloads only
+        held = set(prev.all_ops) if prev is not None else set()
+        needs, all_ops = set(), list(prev.all_ops) if prev is not None else []
         for k in keys:
             op_id = self.request(k, (OwnerKind.EXECUTION, txn_id), Purpose.EXECUTION)
-            all_ops.append(op_id)
             op = self.ops[op_id]
-            op.leases += 1                       # transaction custody from the start
+            if op_id not in held:
+                all_ops.append(op_id)
+                held.add(op_id)
+                op.leases += 1                   # transaction custody from the start
             if op.stage != LoadStage.RESIDENT:
                 needs.add(op_id)
                 op.waiters.add(txn_id)

@@ -741,3 +741,21 @@ def test_new_requests_and_continuations_are_refused_once_shutdown_began():
     with pytest.raises(RuntimeError):
         reg.register_continuation(1, [key(1)])
     assert not reg.ops and not reg.conts
+
+
+def test_resumed_transaction_that_waits_again_extends_its_continuation():
+    """A transaction resumed after its first wait may need more payloads: the second registration keeps the
+    custody (one lease per payload, never two) and waits for the new ones only; registering again while the
+    first wait is unresolved stays an error."""
+    p, reg = manual()
+    reg.register_continuation(1, [key(1)])
+    with pytest.raises(IoProtocolError):
+        reg.register_continuation(1, [key(2)])
+    finish(p, reg)
+    assert reg.pop_ready() == [1]
+    reg.register_continuation(1, [key(1), key(2)])
+    assert reg.ops[0].leases == 1 and reg.ops[1].leases == 1 and reg.conts[1].needs == {1}
+    finish(p, reg)
+    assert reg.pop_ready() == [1] and sorted(reg.conts[1].all_ops) == [0, 1]
+    reg.release_transaction(1)
+    assert reg.ops[0].leases == 0 and reg.ops[1].leases == 0 and sorted(reg.evict_candidates()) == [0, 1]
