@@ -355,12 +355,15 @@ class KvPageManager:
 
     def abort_reservations(self, res_ids: Iterable[int]) -> KvRetirement:
         ret = KvRetirement()
+        res_ids = list(res_ids)
+        for res_id in res_ids:                  # checked before anything changes: a refused abort aborts nothing
+            r = self._res.get(res_id)
+            if r is not None and r.state == ReservationState.PREPARED:
+                raise KvError(f"reservation {res_id} is part of a prepared commit; abort that first")
         for res_id in res_ids:
             r = self._res.pop(res_id, None)
             if r is None:
                 continue
-            if r.state == ReservationState.PREPARED:
-                raise KvError(f"reservation {res_id} is part of a prepared commit; abort that first")
             for p in r.new_pages:
                 self._decref(p, ret)
             if r.cow is not None:
