@@ -115,6 +115,7 @@ class EngineStats:
     staged_tokens: int = 0
     finished: int = 0
     kv_stalls: int = 0
+    page_deadlocks: int = 0             # requests ended because no page would ever come back for them
     prefix_hits: int = 0
     prefix_tokens_reused: int = 0
     prefix_entries: int = 0
@@ -301,7 +302,7 @@ class Engine:
 
     def has_work(self) -> bool:
         return bool(self.scheduler.has_work() or self._ending or self._waiting or self._outbox
-                    or self._retired)
+                    or self._retired or (self.cfg.auto_preempt and self.scheduler.suspended))
 
     def fork_session_exact(self, request_id: str, new_req: GenerateRequest) -> SequenceState:
         """New request that continues from an exact copy of a live sequence's committed state.
@@ -367,6 +368,8 @@ class Engine:
         self.stats.steps += 1
         progressed = self._drive_endings()
         progressed |= self._drive_retirements()
+        if self.scheduler.suspended and self.cfg.auto_preempt:
+            progressed |= self.maybe_restore_suspended() > 0        # swapped-out sequences return when pages allow
         progressed |= self._flush_outbox(emit)
         if self.registry is not None:
             progressed |= bool(self.registry.drive())
@@ -435,8 +438,8 @@ class Engine:
         if stalled and self._prefix_lru:
             self._prefix_evict()            # cached prefixes give way to running sequences, oldest first
         if not members:
-            if stalled and self.cfg.auto_preempt:
-                self._auto_preempt(stalled)
+            if stalled:
+                self._break_page_deadlock(stalled)
             return
         grant = self.broker.try_claim(claimed, required=True)
         txn = Transaction(self._next_txn, members, grant=grant, t_start_ns=time.perf_counter_ns())
@@ -768,19 +771,41 @@ class Engine:
         self.kv.confirm_page_retirement(pages)
         return True
 
-    def _auto_preempt(self, stalled: List[SequenceState]) -> None:
-        """Free pages by swapping out the youngest idle decode sequence."""
-        cands = [s for s in self.scheduler.decode_ready if s not in stalled]
-        if not cands:
+    def _break_page_deadlock(self, stalled: List[SequenceState]) -> None:
+        """No sequence of this action could reserve its pages.  Pages may still be on their way back (endings,
+        parked transactions, retirements, cached prefixes): then the next step tries again.  Otherwise nobody
+        will ever free a page by itself: with `auto_preempt` the youngest sequence is swapped out (an idle one if
+        there is one, else one of the stalled ones - the others then fit); without it, or when a single sequence
+        cannot fit the pool on its own, the youngest stalled request ends with an error instead of spinning."""
+        if self._ending or self._waiting or self._retired or self._prefix_lru:
             return
-        victim = max(cands, key=lambda s: s.arrival_ns)
-        self.preempt_session(victim.request_id)
-        self.stats.auto_preemptions += 1
+        if self.cfg.auto_preempt:
+            idle = [s for s in self.scheduler.decode_ready if s not in stalled]
+            holders = [s for s in idle if self.kv.sequence(s.kv_seq).pages]
+            cands = holders or ([s for s in stalled if self.kv.sequence(s.kv_seq).pages]
+                                if len(self.scheduler.active) > 1 else [])
+            if cands:
+                victim = max(cands, key=lambda s: s.arrival_ns)
+                self.preempt_session(victim.request_id)
+                self.stats.auto_preemptions += 1
+                return
+        if self.kv.stats().quarantined_pages:
+            return
+        victim = max(stalled, key=lambda s: s.arrival_ns)
+        self.last_error = OutOfPages(f"request {victim.request_id}: the KV pool cannot hold its next tokens")
+        self.stats.page_deadlocks += 1
+        self._finish(victim, FinishReason.ERROR)
 
     def maybe_restore_suspended(self) -> int:
-        """Bring suspended sequences back while pages allow (oldest first)."""
+        """Bring suspended sequences back while pages allow (oldest first).  A sequence returns only if, after its
+        own pages, one page of headroom per running sequence remains: restoring into a pool that the running
+        sequences are about to outgrow would only get it swapped out again."""
         n = 0
+        self._drive_retirements()
         for rid, seq in sorted(self.scheduler.suspended.items(), key=lambda kv: kv[1].arrival_ns):
+            need = sum(1 for p in self.kv.sequence(seq.kv_seq).pages if p < 0) + 1
+            if self.kv.free_pages < need + len(self.scheduler.active):
+                break
             try:
                 self.restore_session(rid)
                 n += 1

@@ -132,6 +132,8 @@ class SpeculativeDecoder:
             eng.stats.kv_stalls += 1
             eng.scheduler.requeue_unchanged(seq)
         if not members:
+            if stalled:
+                eng._break_page_deadlock(stalled)        # nobody could reserve: same way out as for plain steps
             return True
         grant = eng.broker.try_claim(claimed, required=True)
         txn = Transaction(eng._next_txn, tx_members, grant=grant, t_start_ns=time.perf_counter_ns())
