@@ -10,8 +10,10 @@ position after an abort or a rejected draft simply overwrites it, which is what 
 without a snapshot.
 
 Prefill runs token by token through the decode step (one row per sequence per launch group): correct, and as
-fast as decode; a chunked V4 prefill kernel path does not exist yet.  Preemption with page snapshots is refused:
-the slot tables are the state, and the engine option that needs snapshots (`auto_preempt`) must stay off.
+fast as decode; a chunked V4 prefill kernel path does not exist yet.  Swapping a sequence out needs no copy (a
+suspended sequence keeps its slot and with it its tables; the pages it returns are admission budget), so
+`auto_preempt` works; sharing a prefix between sequences (copy-on-write pages, exact forks, the prompt-prefix
+cache) is refused, because two slots cannot share table rows.
 
 Counterpart of the V4 runtime of the reference (crates/ferrule-model/src/deepseek_v4/: model assembly, state
 pools for window / compressed / indexer planes, one-token decode schedule).
@@ -48,6 +50,10 @@ from ..runtime.arena import SequenceStateCore
 
 
 class V4Runner(ModelRunner):
+    # the attention state lives in slot-bound tables, not in the pages the engine accounts: two sequences cannot
+    # share a prefix by sharing pages (the engine's prompt-prefix cache and exact forks stay off for this runner)
+    supports_prefix_sharing = False
+
     def __init__(self, weights: V4Weights, n_pages: int, page_size: int = 64, max_seqs: int = 8,
                  max_seq_len: int = 1024, max_rows: int = 2048, eos_token_id: int = -1):
         self.w, self.cfg = weights, weights.cfg
@@ -137,10 +143,14 @@ class V4Runner(ModelRunner):
         pass
 
     def snapshot_pages(self, pages):
-        raise RuntimeError("V4 state is bound by slot; preemption with page snapshots is not supported")
+        """Swap-out of a V4 sequence: its state sits in the tables of its slot, and a suspended sequence keeps
+        its slot, so nothing has to be copied - the pages the engine takes back are its admission budget, not
+        memory the tables use.  The token returned is what `restore_pages` expects back."""
+        return ("v4-slot-state", len(pages))
 
     def restore_pages(self, pages, snapshot) -> None:
-        raise RuntimeError("V4 state is bound by slot; preemption with page snapshots is not supported")
+        if not (isinstance(snapshot, tuple) and snapshot and snapshot[0] == "v4-slot-state"):
+            raise RuntimeError("not a snapshot of this runner")
 
     def release_slot(self, state_slot: int) -> None:
         self.seq_state.pop(state_slot, None)

@@ -194,7 +194,9 @@ class Engine:
             seq = SequenceState(req, kv_seq=prev.kv_seq, tokens=prev.tokens + list(req.prompt_tokens),
                                 position=prev.position, arrival_ns=now)
         else:
-            hit = self._prefix_lookup(req.prompt_tokens) if (self.cfg.prefix_cache_tokens and not req.session_id) else None
+            hit = (self._prefix_lookup(req.prompt_tokens)
+                   if (self.cfg.prefix_cache_tokens and not req.session_id
+                       and getattr(self.runner, "supports_prefix_sharing", True)) else None)
             if hit is not None:
                 donor, n = hit
                 seq = SequenceState(req, kv_seq=self.kv.publish_fork_sequence_prefix(donor, n),
@@ -723,11 +725,13 @@ class Engine:
         # a suspended (preempted) sequence that ends never comes back: drop its host snapshot
         self.scheduler.suspended.pop(seq.request_id, None)
         self._snapshots.pop(seq.request_id, None)
+        slot = seq.slot                                   # the scheduler returns the slot to its pool and clears it
         self.scheduler.finish(seq, reason)
-        self._release_sequence(seq, reason)
+        self._release_sequence(seq, reason, slot)
 
-    def _release_sequence(self, seq: SequenceState, reason: FinishReason) -> None:
+    def _release_sequence(self, seq: SequenceState, reason: FinishReason, slot: int = -1) -> None:
         seq.staged_token = None
+        slot = seq.slot if seq.slot >= 0 else slot
         ttft = (seq.first_token_ns - seq.arrival_ns) / 1e9 if seq.first_token_ns else 0.0
         tpot = ((seq.last_token_ns - seq.first_token_ns) / 1e9 / (seq.generated - 1)) if seq.generated > 1 else 0.0
         keep = seq.request.retain_session and reason not in (FinishReason.CANCELLED, FinishReason.ERROR)
@@ -736,13 +740,14 @@ class Engine:
             seq.tokens = seq.tokens[:seq.position]
             self._sessions[seq.request.session_id or seq.request_id] = seq
         elif seq.kv_seq >= 0:
-            cache = (self.cfg.prefix_cache_tokens and seq.slot < 0 and not self._shutdown
+            cache = (self.cfg.prefix_cache_tokens and not self._shutdown
+                     and getattr(self.runner, "supports_prefix_sharing", True)
                      and reason not in (FinishReason.CANCELLED, FinishReason.ERROR))
             if not (cache and self._prefix_offer(seq)):
                 self._retire(self.kv.free_sequence_pages(seq.kv_seq))
             seq.kv_seq = -1
-        if seq.slot >= 0:
-            self.runner.release_slot(seq.slot)
+        if slot >= 0:
+            self.runner.release_slot(slot)                # slot-bound runner state (if any) is dropped with it
         self.stats.finished += 1
         self.stats.ttft_sum_s += ttft
         self.stats.tpot_sum_s += tpot

@@ -236,6 +236,65 @@ def main() -> int:
     res["checks"]["model_tokens_match"] = worst_tok
     ok &= worst_tok
 
+    # 4b. fp32 against bf16 partial-sum payloads: twelve greedy decode steps of three sequences, each forward
+    # feeding on its own tokens.  The streams must be equal; a difference is only tolerated at a step whose
+    # single-GPU top-2 margin is a near tie (then the later tokens of that sequence are not compared).
+    if args.collective == "ll":
+        other = "fp32" if args.payload == "bf16" else "bf16"
+        tp_o = TensorParallel(rank, world, dev, fused=True, payload=other, multicast_push=args.mc_push)
+        pool_o = D.KvPool(cfg, 32, 64, dev)
+        fwd_o = D.CudaForward(w_tp, pool_o, max_rows=256, max_logit_rows=8, decode_rows=64, max_seq_len=512,
+                              attn_splits=2, tp=tp_o)
+        tp_o.attach(fwd_o)
+        pool.data.zero_()
+        pool1.data.zero_()
+        bt = torch.stack([torch.arange(1 + 8 * s_, 9 + 8 * s_) for s_ in range(3)]).to(torch.int32)
+        gg = torch.Generator().manual_seed(77)
+        prompts = [torch.randint(0, cfg.vocab_size, (n_,), generator=gg).tolist() for n_ in (21, 5, 38)]
+
+        def stream(f, margins=None):
+            lens_, feed, out_ = [0, 0, 0], [list(p_) for p_ in prompts], [[], [], []]
+            for _step in range(13):
+                ids_l, pos, slot, rseq, lrows = [], [], [], [], []
+                for s_ in range(3):
+                    for j, t_ in enumerate(feed[s_]):
+                        p_ = lens_[s_] + j
+                        ids_l.append(t_)
+                        pos.append(p_)
+                        slot.append(int(bt[s_, p_ // 64]) * 64 + p_ % 64)
+                        rseq.append(s_)
+                    lrows.append(len(ids_l) - 1)
+                mk = lambda v, dt: torch.tensor(v, dtype=dt, device=dev)
+                b_ = D.DeviceBatch(mk(ids_l, torch.int32), mk(pos, torch.int32), mk(slot, torch.int64),
+                                   mk(rseq, torch.int32), mk(pos, torch.int32), bt.to(dev), mk(lrows, torch.int32),
+                                   len(ids_l), 3)
+                if margins is not None:
+                    i_, _, lg_ = f.forward(b_, want_logits=True)
+                    t2 = lg_.topk(2, dim=-1).values
+                    margins.append(((t2[:, 0] - t2[:, 1]) / lg_.abs().amax(-1).clamp_min(1e-6)).tolist())
+                else:
+                    i_, _, _ = f.forward(b_)
+                toks_ = i_.clone().tolist()
+                for s_ in range(3):
+                    lens_[s_] += len(feed[s_])
+                    feed[s_] = [toks_[s_]]
+                    out_[s_].append(toks_[s_])
+            return out_
+        a_s = stream(fwd)
+        b_s = stream(fwd_o)
+        margins = []
+        stream(fwd1, margins)
+        torch.cuda.synchronize()
+        same = True
+        for s_ in range(3):
+            for j, (x_, y_) in enumerate(zip(a_s[s_], b_s[s_])):
+                if x_ != y_:
+                    same &= margins[j][s_] < 2e-2          # a near tie may fall either way; anything else may not
+                    break
+        res["checks"]["payload_streams_equal"] = bool(a_s == b_s)
+        res["checks"]["payload_streams_equal_or_tie"] = bool(same)
+        ok &= same
+
     # 5. the same model with token-dispatch expert parallelism in its MoE layers (tensor-parallel attention, every
     # rank routes its own slice of the tokens, shared experts replicated) against the single-GPU forward
     from ferrule_b200.parallel.ep import ExpertParallelMoE

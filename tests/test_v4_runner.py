@@ -109,3 +109,27 @@ def test_v4_runner_serves_on_the_kernels():
         assert toks == want
     from ferrule_b200.ops import _lib
     assert _lib.read_status()[0] == 0
+
+
+def test_v4_sequences_swap_out_and_return_under_page_pressure_on_cpu():
+    """The pool admits the three prompts but not their growth: with `auto_preempt` the engine swaps a V4 sequence
+    out (its slot tables stay in place, its pages go back) and brings it back later; the streams stay the
+    oracle's.  Page sharing stays off for the slot-bound runner (no prefix-cache hit, no fork)."""
+    cfg = tiny_v4()
+    w = random_v4_weights(cfg, device="cpu", seed=3)
+    g = torch.Generator().manual_seed(2)
+    base = torch.randint(0, cfg.vocab_size, (15,), generator=g).tolist()
+    prompts = [base, base[:14] + [7], torch.randint(0, cfg.vocab_size, (15,), generator=g).tolist()]
+    runner = V4Runner(w, n_pages=6, page_size=16, max_seqs=4, max_seq_len=128, max_rows=64)
+    sched = SchedulerConfig(max_active_sequences=4, max_decode_batch=4, max_batch_tokens=32, prefill_chunk_size=12,
+                            ctx_size=128)
+    eng = Engine(runner, EngineConfig(scheduler=sched, kv_pages=6, page_size=16, auto_preempt=True,
+                                      prefix_cache_tokens=256, prefix_block=16))
+    got = _run(eng, prompts, 24)
+    for p, toks in zip(prompts, got):
+        assert toks == _greedy(w, p, 24)
+    assert eng.stats.auto_preemptions >= 1 and eng.kv.stats().preemptions == eng.stats.auto_preemptions
+    assert eng.stats.prefix_hits == 0 and eng.stats.prefix_entries == 0 and eng.kv.stats().forks == 0
+    eng.kv.check_invariants()
+    assert eng.kv.stats().used_pages == 0 and not eng.scheduler.suspended
+    assert runner.seq_state == {}, "finished sequences gave their slots (and the slot's cursor) back"
