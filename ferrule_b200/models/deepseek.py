@@ -411,6 +411,7 @@ class CudaForward:
         self.fused_router_rows = 256
         self.side_stream = torch.cuda.Stream(device=dev)      # shared experts run beside the routed path
         self.arena = None          # models.expert_arena.ExpertArena when routed experts are streamed
+        self.wave_state = None     # per-transaction {layer: finished waves + their rows} of the asynchronous streaming
         # bytes of each MoE layer's routed-expert weights to prefetch into L2 during the attention half of a decode
         # layer (0 = off); the L2 holds 126 MB, the prefetch must leave room for the attention's own traffic
         import os
@@ -755,7 +756,7 @@ class CudaForward:
         need = counts.nonzero().flatten().tolist()
         if self.telemetry is not None:
             self.telemetry.record_counts(layer, counts.tolist(), T)
-        if self.async_stream and len(need) <= arena.frames(layer):
+        if self.async_stream:
             return self._moe_async(lw, plan, layer, T, side, idx, need)
         frames = arena.frames(layer)
         tg0, tr0 = plan.tile_group.clone(), plan.tile_rows.clone()
@@ -780,28 +781,57 @@ class CudaForward:
         return idx
 
     def _moe_async(self, lw: LayerWeights, plan, layer: int, T: int, side, idx, need):
-        """Streamed experts without blocking the engine: if an expert of the batch is not resident the layer
-        stops here (the resident ones stay leased for the transaction), otherwise the GEMM pair runs on the
-        leased frames.  The leases are handed to `lease_sink` (the runner releases them when the transaction
-        ends); without a sink they are dropped after the GEMMs."""
+        """Streamed experts without blocking the engine.  The batch's experts are taken in waves of at most
+        `frames` experts: a wave whose experts are all resident runs its GEMM pair on the leased frames and gives
+        the leases back; a wave with a missing expert stops the layer here (`NeedExperts`) - its resident experts
+        stay leased for the transaction, the experts of finished waves are remembered in `wave_state` together
+        with their output rows, so the re-run of the layer after the resume restores those rows and goes on with
+        the waves that are left.  With no more experts than frames this is a single wave whose leases are held
+        until the transaction ends (`lease_sink`)."""
         from .expert_async import NeedExperts
         K, cfg, ws, arena = self.K, self.cfg, self.ws, self.arena
         k, H = cfg.topk, cfg.hidden
-        held = self.lease_sink.setdefault(layer, {}) if self.lease_sink is not None else {}
-        held.update(arena.lease_resident(layer, [e for e in need if e not in held]))
-        missing = arena.missing(layer, need)
-        if missing:
-            if side is not None:
-                torch.cuda.current_stream().wait_stream(side)
-            raise NeedExperts(layer, missing)
-        arena.resolve_plan(layer, plan)
+        frames = arena.frames(layer)
+        single = len(need) <= frames
+        state = self.wave_state.setdefault(layer, {"done": set(), "rows": None}) if self.wave_state is not None \
+            else {"done": set(), "rows": None}
         route_out = ws.route_out[:T]
-        self._gemm(ws.xg[:T * k], lw.e_w13, ws.hmid[:T * k], slot="xg", epilogue=K.EPI_SWIGLU, plan=plan,
-                   act_limit=cfg.swiglu_limit)
-        self._gemm(ws.hmid[:T * k], lw.e_w2, route_out.view(T * ws.slots, H), slot="hmid", epilogue=K.EPI_SCATTER,
-                   plan=plan, scatter_rows=T * ws.slots)
-        if self.lease_sink is None:
+        if state["rows"] is not None:
+            route_out[:, :k].copy_(state["rows"])            # output rows of the waves that ran before the park
+            state["rows"] = None
+        held = self.lease_sink.setdefault(layer, {}) if self.lease_sink is not None else {}
+        pending = [e for e in need if e not in state["done"]]
+        tg0 = tr0 = None
+        if not single:
+            tg0, tr0 = plan.tile_group.clone(), plan.tile_rows.clone()
+        first = True
+        while pending or first:
+            wave = pending[:frames]
+            held.update(arena.lease_resident(layer, [e for e in wave if e not in held]))
+            missing = arena.missing(layer, wave)
+            if missing:
+                if state["done"]:
+                    state["rows"] = route_out[:, :k].clone()
+                if side is not None:
+                    torch.cuda.current_stream().wait_stream(side)
+                raise NeedExperts(layer, missing)
+            if not first and tg0 is not None:
+                plan.tile_group.copy_(tg0)
+                plan.tile_rows.copy_(tr0)
+            arena.resolve_plan(layer, plan)                  # experts that are not resident get zero-row tiles
+            self._gemm(ws.xg[:T * k], lw.e_w13, ws.hmid[:T * k], slot="xg", epilogue=K.EPI_SWIGLU, plan=plan,
+                       act_limit=cfg.swiglu_limit)
+            self._gemm(ws.hmid[:T * k], lw.e_w2, route_out.view(T * ws.slots, H), slot="hmid",
+                       epilogue=K.EPI_SCATTER, plan=plan, scatter_rows=T * ws.slots)
+            first = False
+            pending = pending[len(wave):]
+            if not single:
+                # the wave is done: its frames may go to the next wave's experts
+                state["done"].update(wave)
+                arena.release_leases(layer, [held.pop(e) for e in wave if e in held])
+        if single and self.lease_sink is None:
             arena.release_leases(layer, list(held.values()))
+        state["done"].clear()
         if side is not None:
             torch.cuda.current_stream().wait_stream(side)
         return idx

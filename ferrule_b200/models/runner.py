@@ -228,6 +228,8 @@ class DeepSeekRunner(ModelRunner):
         self._mtp_hidden: Optional[torch.Tensor] = None
         # asynchronous expert streaming: leases and the stop point of every parked transaction
         self._txn_leases: Dict[int, Dict[int, Dict[int, tuple]]] = {}
+        self._txn_waves: Dict[int, Dict[int, dict]] = {}       # txn -> layer -> finished waves of a parked layer
+        self._wave_state: Dict[int, dict] = {}
         self._txn_resume: Dict[int, tuple] = {}
         if self.async_streaming:
             if self.is_cuda:
@@ -281,14 +283,30 @@ class DeepSeekRunner(ModelRunner):
         return reg
 
     def _expert_gate(self, layer: int, experts) -> None:
+        """Residency protocol of the host path (the oracle multiplies with the full weights): the batch's experts
+        are taken in waves of at most `frames`; a wave with a missing expert parks the transaction, finished waves
+        are remembered per transaction and give their frames back."""
         from .expert_async import NeedExperts
-        if len(experts) > self.arena.frames(layer):
-            return          # more experts than frames: the kernels run such a layer in inline waves, nothing parks
+        frames = self.arena.frames(layer)
         held = self._lease_sink.setdefault(layer, {})
-        held.update(self.arena.lease_resident(layer, [e for e in experts if e not in held]))
-        missing = self.arena.missing(layer, experts)
-        if missing:
-            raise NeedExperts(layer, missing)
+        if len(experts) <= frames:
+            held.update(self.arena.lease_resident(layer, [e for e in experts if e not in held]))
+            missing = self.arena.missing(layer, experts)
+            if missing:
+                raise NeedExperts(layer, missing)
+            return
+        done = self._wave_state.setdefault(layer, {"done": set(), "rows": None})["done"]
+        pending = [e for e in experts if e not in done]
+        while pending:
+            wave = pending[:frames]
+            held.update(self.arena.lease_resident(layer, [e for e in wave if e not in held]))
+            missing = self.arena.missing(layer, wave)
+            if missing:
+                raise NeedExperts(layer, missing)
+            done.update(wave)
+            self.arena.release_leases(layer, [held.pop(e) for e in wave if e in held])
+            pending = pending[len(wave):]
+        done.clear()
 
     def execute(self, txn_id: int):
         b = self.txns[txn_id]
@@ -296,8 +314,10 @@ class DeepSeekRunner(ModelRunner):
         start_layer, h0 = self._txn_resume.pop(txn_id, (0, None))
         if self.async_streaming:
             self._lease_sink = self._txn_leases.setdefault(txn_id, {})
+            self._wave_state = self._txn_waves.setdefault(txn_id, {})
             if self.is_cuda:
                 self.fwd.lease_sink = self._lease_sink
+                self.fwd.wave_state = self._wave_state
         try:
             if not self.is_cuda:
                 out = self._execute_reference(b, start_layer, h0)
@@ -329,6 +349,7 @@ class DeepSeekRunner(ModelRunner):
         self._txn_resume.pop(txn_id, None)
         for layer, held in self._txn_leases.pop(txn_id, {}).items():
             self.arena.release_leases(layer, list(held.values()))
+        self._txn_waves.pop(txn_id, None)
         h = self._txn_hidden.pop(txn_id, None)
         keep = self._txn_keep.pop(txn_id, None)
         if b is not None and h is not None and intent == EndIntent.PUBLISH:

@@ -29,13 +29,13 @@ def _run(eng, prompts, n_new):
     return [[e.token for e in ev if isinstance(e, TokenEvent) and e.request_id == f"r{i}"] for i in range(len(prompts))]
 
 
-def _check(device):
+def _check(device, residency=0.75):
     cfg = C.tiny_fixture()
     g = torch.Generator().manual_seed(5)
     prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (7, 11)]
     dt = torch.bfloat16 if device == "cuda" else torch.float32
     want = _run(_engine(W.random_weights(cfg, device=device, dtype=dt, seed=2), device)[0], prompts, 8)
-    eng, runner = _engine(W.random_weights(cfg, device=device, dtype=dt, seed=2), device, residency=0.75,
+    eng, runner = _engine(W.random_weights(cfg, device=device, dtype=dt, seed=2), device, residency=residency,
                           async_streaming=True)
     got = _run(eng, prompts, 8)
     assert got == want
@@ -53,8 +53,16 @@ def test_async_streaming_parks_and_resumes_on_cpu():
     _check("cpu")
 
 
+def test_async_streaming_takes_layers_with_more_experts_than_frames_in_waves_on_cpu():
+    """Two frames for eight experts: nearly every batch routes to more experts than frames.  The layer runs them
+    in waves of two, parks whenever a wave misses an expert and resumes with the finished waves remembered -
+    nothing streams inline, and the tokens are those of the resident model."""
+    _check("cpu", residency=0.25)
+
+
 @pytest.mark.gpu
-def test_async_streaming_parks_and_resumes_on_gpu():
-    _check("cuda")
+@pytest.mark.parametrize("residency", [0.75, 0.25])
+def test_async_streaming_parks_and_resumes_on_gpu(residency):
+    _check("cuda", residency)
     from ferrule_b200.ops import _lib
     assert _lib.read_status()[0] == 0
