@@ -141,14 +141,14 @@ add_rmsnorm_kernel(const __nv_bfloat16* __restrict__ x, long long ldx,
 // Rotation acts on interleaved pairs (x[2i], x[2i+1]).
 // ---------------------------------------------------------------------------------
 __global__ void __launch_bounds__(256)
-mla_prep_kernel(const __nv_bfloat16* __restrict__ q, long long ldq, int q_head_dim,
+mla_prep_kernel(const __nv_bfloat16* q, long long ldq, int q_head_dim,   // q may alias q_out (rotation in place)
                 const __nv_bfloat16* __restrict__ ckv_in, long long ldckv, int heads, int kv_lora,
                 int rope_dim,
                 const __nv_bfloat16* __restrict__ kv_norm_w, float eps,
                 const float* __restrict__ cos_t, const float* __restrict__ sin_t, int max_pos,
                 const int* __restrict__ positions, const long long* __restrict__ write_slot,
                 __nv_bfloat16* __restrict__ kv_pool, long long pool_rows,
-                __nv_bfloat16* __restrict__ q_out, long long ldq_out, int rows, DeviceStatus* st) {
+                __nv_bfloat16* q_out, long long ldq_out, int rows, DeviceStatus* st) {
   pdl_launch_dependents();
   pdl_wait();
   __shared__ float red[8];

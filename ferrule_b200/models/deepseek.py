@@ -274,6 +274,9 @@ class CudaWorkspace:
         self.q = torch.zeros(R, hl * cfg.q_head_dim, **bf) if cfg.q_lora_rank else None
         self.qn = torch.zeros(R, cfg.q_lora_rank, **bf) if cfg.q_lora_rank else None
         self.q_full = torch.zeros(R, hl, D, **bf)
+        # decode on folded weights, models without a query down-projection: one GEMM writes q_full's layout and the
+        # latent-kv row side by side
+        self.q_fold = None if cfg.q_lora_rank else torch.zeros(min(R, 4 * decode_rows), (hl + 1) * D, **bf)
         self.o_lat = torch.zeros(R, hl, cfg.kv_lora_rank, **bf)
         self.attn_out = torch.zeros(R, hl * cfg.v_head_dim, **bf)
         self.delta = torch.zeros(R, H, **bf)
@@ -431,11 +434,21 @@ class CudaForward:
         self._prefetch_next = None
         self.fork_prep = os.environ.get("FERRULE_FORK_PREP", "1") != "0"
         self.prep_stream = torch.cuda.Stream(device=dev)
+        # Decode-sized batches can run attention on folded weights: W_UK multiplied into the query projection and W_UV
+        # into the output projection, so the two small per-head GEMMs (and their launches) leave the layer.  The folded
+        # matrices are 2.5x / 4x larger, and that costs more than the two launches save.  Measured, full
+        # DeepSeek-V2-Lite decode step, batch 64: 6.55 -> 7.03 ms whole model, 3.37 -> 3.58 ms on a 4-way head shard,
+        # 2.87 -> 2.91 ms on an 8-way shard.  Opt-in ("1"); "auto" folds from 16-way head shards on.  bf16 weights only.
+        self.fold_decode = os.environ.get("FERRULE_FOLD_DECODE", "0")
+        self._folded = {}
         self.async_stream = False  # streamed experts: stop at a layer with missing experts instead of uploading inline
         # token-dispatch expert parallelism (parallel.ep.ExpertParallelMoE): MoE layers run on this rank's slice of
         # the batch's tokens, routes travel to the experts' owners and back, the slices are gathered for the next layer
         self.ep = None
         self.lease_sink = None     # dict layer -> leases of the running transaction (set by the runner)
+        if self._fold_wanted():
+            for i, lw in enumerate(self.w.layers):
+                self._folded[i] = self._build_fold(lw)
 
     # -- sublayers -----------------------------------------------------------------------
     # -- linear dispatch -------------------------------------------------------------------
@@ -525,6 +538,9 @@ class CudaForward:
         K, cfg, ws = self.K, self.cfg, self.ws
         hl = self.w.heads_local
         qhd, lora, rope, nope, vd = cfg.q_head_dim, cfg.kv_lora_rank, cfg.qk_rope_dim, cfg.qk_nope_dim, cfg.v_head_dim
+        fold = self._folded.get(layer) if (T <= 4 * ws.decode_rows and not b.n_tc_tiles) else None
+        if fold is not None:
+            return self._attention_folded(lw, fold, layer, xn, b, T)
         qkv = ws.qkv[:T]
         self._gemm(xn, lw.w_qkv_a, qkv, slot="xn")
         if cfg.q_lora_rank:
@@ -571,7 +587,65 @@ class CudaForward:
                             ws=ws.attn_ws if (use_split and not cluster) else None, sink=lw.attn_sink,
                             decode_only=b.decode_only)
         K.gemm(ws.o_lat[:T].view(T, -1), lw.w_uv, out=ws.attn_out[:T], x_group_koff=lora, out_group_coff=vd)
-        return ws.attn_out[:T]
+        return ws.attn_out[:T], lw.w_o
+
+    def _fold_wanted(self) -> bool:
+        if self.fold_decode == "auto":
+            return self.tp is not None and self.tp.world >= 16
+        return self.fold_decode == "1"
+
+    def _build_fold(self, lw: LayerWeights):
+        """(query weight, output weight) with the absorbed up-projections multiplied in, or None (quantised weights).
+        Query side, per head: rows [W_UK^T @ W_q_nope ; W_q_rope] give the latent-space query and the rotary part
+        in the layout the attention kernel reads.  Output side: W_o[:, head block] @ W_UV per head takes the latent
+        attention output straight to the hidden size."""
+        fold = None
+        cfg = self.cfg
+        wq = lw.w_q_b if cfg.q_lora_rank else lw.w_qkv_a
+        plain = all(isinstance(t, torch.Tensor) for t in (wq, lw.w_o, lw.w_uk_t, lw.w_uv))
+        if plain:
+            hl, qhd, nope = self.w.heads_local, cfg.q_head_dim, cfg.qk_nope_dim
+            lora, vd = cfg.kv_lora_rank, cfg.v_head_dim
+            with torch.no_grad():
+                qh = wq[:hl * qhd].view(hl, qhd, -1).float()
+                q_abs = torch.bmm(lw.w_uk_t.float(), qh[:, :nope])                     # [hl, lora, in]
+                wq_f = torch.cat([q_abs, qh[:, nope:]], dim=1).reshape(hl * (lora + qhd - nope), -1)
+                if not cfg.q_lora_rank:
+                    wq_f = torch.cat([wq_f, wq[hl * qhd:].float()], dim=0)            # the latent-kv rows follow
+                wo = lw.w_o.float().view(lw.w_o.shape[0], hl, vd)
+                wo_f = torch.einsum("ohv,hvl->ohl", wo, lw.w_uv.float()).reshape(lw.w_o.shape[0], hl * lora)
+                fold = (wq_f.to(torch.bfloat16).contiguous(), wo_f.to(torch.bfloat16).contiguous())
+        return fold
+
+    def _attention_folded(self, lw: LayerWeights, fold, layer: int, xn: torch.Tensor, b: DeviceBatch, T: int):
+        K, cfg, ws = self.K, self.cfg, self.ws
+        hl, lora, rope = self.w.heads_local, cfg.kv_lora_rank, cfg.qk_rope_dim
+        D = lora + rope
+        wq_f, wo_f = fold
+        if cfg.q_lora_rank:
+            qkv = ws.qkv[:T]
+            self._gemm(xn, lw.w_qkv_a, qkv, slot="xn")
+            qa, ckv = qkv[:, :cfg.q_lora_rank], qkv[:, cfg.q_lora_rank:]
+            self._norm(qa, lw.q_norm, T, ws.qn[:T], "a", None)
+            q_rows = ws.q_full[:T].view(T, -1)
+            K.gemm(ws.qn[:T], wq_f, out=q_rows)
+        else:
+            wide = ws.q_fold[:T]
+            K.gemm(xn, wq_f, out=wide)
+            q_rows, ckv = wide[:, :hl * D], wide[:, hl * D:]
+        # the rotary part is rotated where it lies (each thread reads its pair before it writes it)
+        K.mla_prep(q_rows, D, ckv, hl, lora, rope, lw.kv_norm, cfg.rms_eps, self.cos, self.sin,
+                   b.positions, b.write_slot, self.pool.layer(layer), q_rows)
+        q_full = q_rows.unflatten(1, (hl, D))
+        cluster = ws.attn_splits in (2, 4, 8)
+        use_split = ws.attn_splits > 1
+        K.mla_attention(q_full, self.pool.layer(layer), b.block_table, b.row_seq[:T], b.row_pos[:T],
+                        self.pool.page_size, lora, rope, cfg.softmax_scale, ws.o_lat[:T],
+                        splits=ws.attn_splits if use_split else 1,
+                        split_tokens=self.split_tokens if use_split else (1 << 30) // 64 * 64,
+                        ws=ws.attn_ws if (use_split and not cluster) else None, sink=lw.attn_sink,
+                        decode_only=b.decode_only)
+        return ws.o_lat[:T].view(T, -1), wo_f
 
     def _moe_ntok(self, T: int) -> int:
         cfg = self.cfg
@@ -913,7 +987,7 @@ class CudaForward:
         # `next_norm` (single GPU): this layer's last kernel does the same for the next one
         if not first_norm_done:
             self._norm(h_in, lw.attn_norm, T, xn, "xn", self._qkind(lw.w_qkv_a))
-        a = self._attention(lw, layer, xn, b, T)
+        a, w_o = self._attention(lw, layer, xn, b, T)
         # what reads the post-attention norm: the dense FFN, or the shared experts and the static FP8 expert path
         ffn_q = self._qkind(lw.w13) or (self._qkind(lw.e_w13) if lw.is_moe else None)
         # decode-sized MoE layers: the post-attention residual add + RMSNorm runs in the router kernel's prologue
@@ -922,18 +996,18 @@ class CudaForward:
         fuse_route = (not use_ep and self.fuse_router_norm and lw.is_moe and self._static_rows(lw, T, layer) > 0
                       and not isinstance(lw.w13, QuantWeight) and not isinstance(lw.e_w13, QuantWeight))
         if tp is None:
-            self._gemm(a, lw.w_o, ws.delta[:T], slot="a")
+            self._gemm(a, w_o, ws.delta[:T], slot="a")
             if fuse_route:
                 route_norm = (h_in, ws.delta[:T], h_out)
             else:
                 self._norm(h_in, lw.ffn_norm, T, xn, "xn", ffn_q, delta=ws.delta[:T], res_out=h_out)
             h_mid = h_out
         else:
-            if isinstance(lw.w_o, QuantWeight):
-                self._gemm(a, lw.w_o, ws.delta[:T], slot="a")
+            if isinstance(w_o, QuantWeight):
+                self._gemm(a, w_o, ws.delta[:T], slot="a")
                 tp.add_allreduce(ws.delta[:T], residual=h_in, out=h_out, T=T)
             else:
-                tp.gemm_allreduce(a, lw.w_o, residual=h_in, out=h_out, T=T)
+                tp.gemm_allreduce(a, w_o, residual=h_in, out=h_out, T=T)
             if fuse_route:
                 route_norm = (h_out, None, None)
             elif not use_ep:

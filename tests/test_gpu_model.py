@@ -33,8 +33,16 @@ def _batch(dev, seq_lens, new_tokens, page, max_blocks, vocab, seed=0):
                          mk(pos, torch.int32), bt.to(dev), mk(logit_rows, torch.int32), T, len(logit_rows))
 
 
+@pytest.mark.parametrize("preset", ["smoke-gpu", "smoke-qlora"])
+def test_decode_on_folded_weights_matches_reference(preset, monkeypatch):
+    """W_UK folded into the query projection and W_UV into the output projection: same logits and cache rows as
+    the reference forward (which keeps the four matrices apart)."""
+    monkeypatch.setenv("FERRULE_FOLD_DECODE", "1")
+    test_cuda_forward_matches_reference(preset, folded=True)
+
+
 @pytest.mark.parametrize("preset", ["smoke-gpu", "tiny-fixture", "smoke-qlora"])
-def test_cuda_forward_matches_reference(preset):
+def test_cuda_forward_matches_reference(preset, folded=False):
     if preset == "smoke-qlora":
         cfg = C.smoke_gpu().with_(q_lora_rank=256, score_fn=C.SCORE_SIGMOID, n_groups=4, topk_groups=2,
                                   router_bias=True, norm_topk_prob=True, route_scale=2.5, n_mtp_layers=1)
@@ -47,6 +55,7 @@ def test_cuda_forward_matches_reference(preset):
     pool_b = D.KvPool(cfg, 64, page, dev)
     fwd = D.CudaForward(w, pool_a, max_rows=256, max_logit_rows=16, decode_rows=16, max_seq_len=512, attn_splits=4)
     reff = D.ReferenceForward(w, pool_b, emulate_bf16=True)
+    assert (len(fwd._folded) == len(w.layers) and all(fwd._folded.values())) if folded else not fwd._folded
     # prefill of three ragged sequences, then two decode steps
     lens = [0, 0, 0]
     new = [37, 16, 5]
