@@ -55,6 +55,10 @@ def main() -> int:
         toks = {f"r{i}": [e.token for e in ev if isinstance(e, TokenEvent) and e.request_id == f"r{i}"] for i in range(5)}
         return toks, e0.elapsed_time(e1), eng.stats.decode_steps
 
+    # pipeline stages run prompts through the row-tile attention kernel (a stage's rows are cut per micro-batch, the
+    # 128-row tensor-core tiles are laid out for whole batches); the single-GPU oracle takes the same kernel so that
+    # equal token streams can be required bit for bit
+    os.environ["FERRULE_PREFILL_TC"] = "0"
     w_full = W.random_weights(cfg, device=dev, seed=3, std=0.05)
     want, ms1, _ = run(DeepSeekRunner(w_full, n_pages=64, page_size=64, max_rows=512, max_seqs=8, max_seq_len=512,
                                       device=dev, use_graphs=False, lookahead=False))
