@@ -164,7 +164,12 @@ def _build_v4_engine(args, dev, model_dir: Optional[str] = None):
         cfg = weights.cfg
     else:
         cfg = tiny_v4()
+        if args.speculative:
+            cfg = cfg.with_(n_proposal_stages=2, proposal_target_layers=(0, cfg.n_layers - 1), proposal_noise_token=1,
+                            proposal_markov_rank=32)
         weights = random_v4_weights(cfg, device=dev, seed=args.seed)
+    if args.speculative and weights.proposal is None:
+        raise SystemExit("--speculative: this DeepSeek-V4 checkpoint has no `mtp.*` proposal stages")
     ctx = min(args.ctx_size, cfg.max_position)
     pages_per_seq = (ctx + args.page_size - 1) // args.page_size
     n_pages = args.max_seqs * pages_per_seq + 8
@@ -173,7 +178,11 @@ def _build_v4_engine(args, dev, model_dir: Optional[str] = None):
     sched = SchedulerConfig(max_active_sequences=args.max_seqs, max_decode_batch=args.max_seqs,
                             max_batch_tokens=args.max_batch_tokens, prefill_chunk_size=args.prefill_chunk,
                             ctx_size=pages_per_seq * args.page_size)
-    eng = Engine(runner, EngineConfig(scheduler=sched, kv_pages=n_pages, page_size=args.page_size))
+    # the block drafter proposes `proposal_block_size` tokens at once: --max-draft above 1 caps it, the default
+    # takes the whole block
+    draft = cfg.proposal_block_size if args.max_draft <= 1 else min(args.max_draft, cfg.proposal_block_size)
+    eng = Engine(runner, EngineConfig(scheduler=sched, kv_pages=n_pages, page_size=args.page_size,
+                                      speculative=args.speculative, max_draft=draft))
     name = os.path.basename(os.path.normpath(model_dir)) if model_dir else "deepseek-v4-tiny"
     return eng, load_tokenizer(model_dir), name
 
@@ -290,12 +299,17 @@ def cmd_make_fixture(args) -> int:
         if args.layers:
             ratios = tuple(cfg.compress_ratios[i % len(cfg.compress_ratios)] for i in range(args.layers))
             cfg = cfg.with_(n_layers=args.layers, compress_ratios=ratios)
+        if args.proposal_stages:
+            # the `mtp.*` block drafter: taps after the first and the last target layer
+            taps = tuple(sorted({0, cfg.n_layers - 1}))
+            cfg = cfg.with_(n_proposal_stages=args.proposal_stages, proposal_target_layers=taps,
+                            proposal_noise_token=1, proposal_markov_rank=32)
         w = random_v4_weights(cfg, seed=args.seed, std=0.0 if args.zeros else 0.05)
         dense = "fp8_block" if args.dense_format == "plain" and not args.plain else args.dense_format
         expert = "mxfp4" if args.expert_format == "plain" and not args.plain else args.expert_format
         export_v4_hf(w, args.out, dense_format=dense, expert_format=expert, shard_bytes=args.shard_mb << 20)
         print(json.dumps({"written": args.out, "family": "deepseek_v4", "layers": cfg.n_layers,
-                          "dense_format": dense, "expert_format": expert}))
+                          "proposal_stages": cfg.n_proposal_stages, "dense_format": dense, "expert_format": expert}))
         return 0
     cfg = C.PRESETS[args.preset]()
     if args.layers:
@@ -612,6 +626,8 @@ def main(argv: Optional[List[str]] = None) -> int:
     p.add_argument("--family", default="deepseek", choices=["deepseek", "v4"],
                    help="v4: a DeepSeek-V4 directory (tiny shape; FP8 dense + packed FP4 experts unless --plain)")
     p.add_argument("--plain", action="store_true", help="--family v4: keep every linear in BF16")
+    p.add_argument("--proposal-stages", type=int, default=0,
+                   help="--family v4: also write this many `mtp.*` proposal stages with their prediction heads")
     p.set_defaults(fn=cmd_make_fixture)
     p = sub.add_parser("inspect-weightpack"); p.add_argument("model_dir"); p.add_argument("--json", action="store_true")
     p.add_argument("--limit", type=int, default=40); p.set_defaults(fn=cmd_inspect)

@@ -22,7 +22,7 @@ from typing import Dict, Optional
 
 import torch
 
-from ..models.v4_model import V4Config, V4LayerWeights, V4Weights
+from ..models.v4_model import V4Config, V4LayerWeights, V4ProposalWeights, V4Weights
 from .checkpoint import _put_linear, read_linear
 from .safetensors import CheckpointError, ShardedCheckpoint, write_sharded
 
@@ -55,7 +55,11 @@ def v4_config_from_hf(hf: dict) -> V4Config:
         index_topk=int(hf.get("index_topk", d.index_topk)), compress_ratios=tuple(int(r) for r in ratios),
         indexer_ratio=int(hf.get("indexer_ratio", d.indexer_ratio)),
         proposal_block_size=int(hf.get("proposal_block_size", d.proposal_block_size)),
-        max_position=int(hf.get("max_position_embeddings", d.max_position)))
+        max_position=int(hf.get("max_position_embeddings", d.max_position)),
+        n_proposal_stages=int(hf.get("num_nextn_predict_layers", 0)),
+        proposal_target_layers=tuple(int(i) for i in hf.get("proposal_target_layer_ids", ())),
+        proposal_noise_token=int(hf.get("proposal_noise_token_id", d.proposal_noise_token)),
+        proposal_markov_rank=int(hf.get("proposal_markov_rank", d.proposal_markov_rank)))
 
 
 def v4_config_to_hf(cfg: V4Config) -> dict:
@@ -73,7 +77,9 @@ def v4_config_to_hf(cfg: V4Config) -> dict:
         "index_n_heads": cfg.index_n_heads, "index_head_dim": cfg.index_head_dim, "index_topk": cfg.index_topk,
         "compress_ratios": list(cfg.compress_ratios), "indexer_ratio": cfg.indexer_ratio,
         "proposal_block_size": cfg.proposal_block_size, "max_position_embeddings": cfg.max_position,
-        "num_nextn_predict_layers": 0, "scoring_func": "sqrtsoftplus",
+        "num_nextn_predict_layers": cfg.n_proposal_stages, "proposal_target_layer_ids": list(cfg.proposal_target_layers),
+        "proposal_noise_token_id": cfg.proposal_noise_token, "proposal_markov_rank": cfg.proposal_markov_rank,
+        "scoring_func": "sqrtsoftplus",
     }
 
 
@@ -98,60 +104,79 @@ def load_v4_hf(directory, device="cpu") -> V4Weights:
     ck = ShardedCheckpoint(d)
     H, hd, E, I = cfg.hidden, cfg.head_dim, cfg.n_routed_experts, cfg.moe_inter
     bf, f32 = torch.bfloat16, torch.float32
-    layers = []
+    def layer(p: str, i: int, r: int, indexer: bool, hashed: bool) -> V4LayerWeights:
+        """One transformer body under prefix `p` (`layers.{i}.` of the target, `mtp.{i}.` of the proposal)."""
+        a = p + "attn."
+        wo_a = _lin(ck, a + "wo_a", device, cfg.o_groups * cfg.o_lora_rank, cfg.group_in)
+        sh = p + "ffn.shared_experts."
+        sI = cfg.n_shared_experts * I
+        w13 = torch.cat([_lin(ck, sh + "w1", device, sI, H), _lin(ck, sh + "w3", device, sI, H)], 0).unsqueeze(0)
+        e13, e2 = [], []
+        for e in range(E):
+            ep = f"{p}ffn.experts.{e}."
+            e13.append(torch.cat([_lin(ck, ep + "w1", device, I, H), _lin(ck, ep + "w3", device, I, H)], 0))
+            e2.append(_lin(ck, ep + "w2", device, H, I))
+        lw = V4LayerWeights(
+            hc_attn_fn=_raw(ck, p + "hc_attn_fn", device, f32), hc_attn_scale=_raw(ck, p + "hc_attn_scale", device, f32),
+            hc_attn_base=_raw(ck, p + "hc_attn_base", device, f32),
+            hc_ffn_fn=_raw(ck, p + "hc_ffn_fn", device, f32), hc_ffn_scale=_raw(ck, p + "hc_ffn_scale", device, f32),
+            hc_ffn_base=_raw(ck, p + "hc_ffn_base", device, f32),
+            attn_norm=_raw(ck, p + "attn_norm.weight", device, bf),
+            wq_a=_lin(ck, a + "wq_a", device, cfg.q_lora_rank, H), q_norm=_raw(ck, a + "q_norm.weight", device, bf),
+            wq_b=_lin(ck, a + "wq_b", device, cfg.n_heads * hd, cfg.q_lora_rank),
+            wkv=_lin(ck, a + "wkv", device, hd, H), kv_norm=_raw(ck, a + "kv_norm.weight", device, bf),
+            sink=_raw(ck, a + "attn_sink", device, f32),
+            wo_a=wo_a.view(cfg.o_groups, cfg.o_lora_rank, cfg.group_in).contiguous(),
+            wo_b=_lin(ck, a + "wo_b", device, H, cfg.o_groups * cfg.o_lora_rank),
+            ffn_norm=_raw(ck, p + "ffn_norm.weight", device, bf), router_w=_raw(ck, p + "ffn.gate.weight", device, bf),
+            e_w13=torch.stack(e13), e_w2=torch.stack(e2), w13=w13, w2=_lin(ck, sh + "w2", device, H, sI).unsqueeze(0))
+        if ck.has(p + "ffn.gate.tid2eid"):
+            lw.hash_table = _raw(ck, p + "ffn.gate.tid2eid", device, torch.int64)
+        if ck.has(p + "ffn.gate.bias"):
+            lw.router_bias = _raw(ck, p + "ffn.gate.bias", device, f32)
+        if (lw.hash_table is None) == hashed:
+            raise CheckpointError(f"{p}: hash-routing table {'missing' if lw.hash_table is None else 'unexpected'}")
+        c = a + "compressor."
+        if r:
+            od = hd * (2 if indexer else 1)
+            lw.c_wkv, lw.c_wgate = _lin(ck, c + "wkv", device, od, H), _lin(ck, c + "wgate", device, od, H)
+            lw.c_ape, lw.c_norm = _raw(ck, c + "ape", device, f32), _raw(ck, c + "norm.weight", device, bf)
+        elif ck.has(c + "wkv.weight"):
+            raise CheckpointError(f"{p}: compressor tensors on a window-only layer")
+        if indexer:
+            x = a + "indexer."
+            idim = cfg.index_head_dim
+            lw.i_wq_b = _lin(ck, x + "wq_b", device, cfg.index_n_heads * idim, cfg.q_lora_rank)
+            lw.i_weights = _lin(ck, x + "weights_proj", device, cfg.index_n_heads, H)
+            lw.ic_wkv = _lin(ck, x + "compressor.wkv", device, 2 * idim, H)
+            lw.ic_wgate = _lin(ck, x + "compressor.wgate", device, 2 * idim, H)
+            lw.ic_ape = _raw(ck, x + "compressor.ape", device, f32)
+            lw.ic_norm = _raw(ck, x + "compressor.norm.weight", device, bf)
+        return lw
+
     try:
-        for i in range(cfg.n_layers):
-            p, a = f"layers.{i}.", f"layers.{i}.attn."
-            wo_a = _lin(ck, a + "wo_a", device, cfg.o_groups * cfg.o_lora_rank, cfg.group_in)
-            sh = p + "ffn.shared_experts."
-            sI = cfg.n_shared_experts * I
-            w13 = torch.cat([_lin(ck, sh + "w1", device, sI, H), _lin(ck, sh + "w3", device, sI, H)], 0).unsqueeze(0)
-            e13, e2 = [], []
-            for e in range(E):
-                ep = f"{p}ffn.experts.{e}."
-                e13.append(torch.cat([_lin(ck, ep + "w1", device, I, H), _lin(ck, ep + "w3", device, I, H)], 0))
-                e2.append(_lin(ck, ep + "w2", device, H, I))
-            lw = V4LayerWeights(
-                hc_attn_fn=_raw(ck, p + "hc_attn_fn", device, f32), hc_attn_scale=_raw(ck, p + "hc_attn_scale", device, f32),
-                hc_attn_base=_raw(ck, p + "hc_attn_base", device, f32),
-                hc_ffn_fn=_raw(ck, p + "hc_ffn_fn", device, f32), hc_ffn_scale=_raw(ck, p + "hc_ffn_scale", device, f32),
-                hc_ffn_base=_raw(ck, p + "hc_ffn_base", device, f32),
-                attn_norm=_raw(ck, p + "attn_norm.weight", device, bf),
-                wq_a=_lin(ck, a + "wq_a", device, cfg.q_lora_rank, H), q_norm=_raw(ck, a + "q_norm.weight", device, bf),
-                wq_b=_lin(ck, a + "wq_b", device, cfg.n_heads * hd, cfg.q_lora_rank),
-                wkv=_lin(ck, a + "wkv", device, hd, H), kv_norm=_raw(ck, a + "kv_norm.weight", device, bf),
-                sink=_raw(ck, a + "attn_sink", device, f32),
-                wo_a=wo_a.view(cfg.o_groups, cfg.o_lora_rank, cfg.group_in).contiguous(),
-                wo_b=_lin(ck, a + "wo_b", device, H, cfg.o_groups * cfg.o_lora_rank),
-                ffn_norm=_raw(ck, p + "ffn_norm.weight", device, bf), router_w=_raw(ck, p + "ffn.gate.weight", device, bf),
-                e_w13=torch.stack(e13), e_w2=torch.stack(e2), w13=w13, w2=_lin(ck, sh + "w2", device, H, sI).unsqueeze(0))
-            if ck.has(p + "ffn.gate.tid2eid"):
-                lw.hash_table = _raw(ck, p + "ffn.gate.tid2eid", device, torch.int64)
-            if ck.has(p + "ffn.gate.bias"):
-                lw.router_bias = _raw(ck, p + "ffn.gate.bias", device, f32)
-            if (lw.hash_table is None) == (i < cfg.n_hash_layers):
-                raise CheckpointError(f"layer {i}: hash-routing table {'missing' if lw.hash_table is None else 'unexpected'}")
-            r = cfg.ratio(i)
-            c = a + "compressor."
-            if r:
-                od = hd * (2 if cfg.has_indexer(i) else 1)
-                lw.c_wkv, lw.c_wgate = _lin(ck, c + "wkv", device, od, H), _lin(ck, c + "wgate", device, od, H)
-                lw.c_ape, lw.c_norm = _raw(ck, c + "ape", device, f32), _raw(ck, c + "norm.weight", device, bf)
-            elif ck.has(c + "wkv.weight"):
-                raise CheckpointError(f"layer {i}: compressor tensors on a window-only layer")
-            if cfg.has_indexer(i):
-                x = a + "indexer."
-                idim = cfg.index_head_dim
-                lw.i_wq_b = _lin(ck, x + "wq_b", device, cfg.index_n_heads * idim, cfg.q_lora_rank)
-                lw.i_weights = _lin(ck, x + "weights_proj", device, cfg.index_n_heads, H)
-                lw.ic_wkv = _lin(ck, x + "compressor.wkv", device, 2 * idim, H)
-                lw.ic_wgate = _lin(ck, x + "compressor.wgate", device, 2 * idim, H)
-                lw.ic_ape = _raw(ck, x + "compressor.ape", device, f32)
-                lw.ic_norm = _raw(ck, x + "compressor.norm.weight", device, bf)
-            layers.append(lw)
+        layers = [layer(f"layers.{i}.", i, cfg.ratio(i), cfg.has_indexer(i), i < cfg.n_hash_layers)
+                  for i in range(cfg.n_layers)]
+        proposal = None
+        if cfg.n_proposal_stages:
+            # the `mtp.*` namespace: window-only stages with a learned router; stage 0 owns the projection of the
+            # target taps, the last stage the prediction heads
+            last = f"mtp.{cfg.n_proposal_stages - 1}."
+            taps = len(cfg.proposal_target_layers)
+            if not taps:
+                raise CheckpointError("proposal stages without proposal_target_layer_ids")
+            rank = cfg.proposal_markov_rank
+            proposal = V4ProposalWeights(
+                stages=[layer(f"mtp.{m}.", m, 0, False, False) for m in range(cfg.n_proposal_stages)],
+                main_proj=_lin(ck, "mtp.0.main_proj", device, H, taps * H), main_norm=_raw(ck, "mtp.0.main_norm.weight", device, bf),
+                hc_head_fn=_raw(ck, last + "hc_head_fn", device, f32), hc_head_scale=_raw(ck, last + "hc_head_scale", device, f32),
+                hc_head_base=_raw(ck, last + "hc_head_base", device, f32), norm=_raw(ck, last + "norm.weight", device, bf),
+                markov_w1=_lin(ck, last + "markov_head.markov_w1", device, cfg.vocab_size, rank),
+                markov_w2=_lin(ck, last + "markov_head.markov_w2", device, cfg.vocab_size, rank),
+                confidence_proj=_lin(ck, last + "confidence_head.proj", device, 1, H + rank))
         return V4Weights(cfg, _raw(ck, "embed.weight", device, bf), layers, _raw(ck, "hc_head_fn", device, f32),
                          _raw(ck, "hc_head_scale", device, f32), _raw(ck, "hc_head_base", device, f32),
-                         _raw(ck, "norm.weight", device, bf), _raw(ck, "head.weight", device, bf))
+                         _raw(ck, "norm.weight", device, bf), _raw(ck, "head.weight", device, bf), proposal)
     finally:
         ck.close()
 
@@ -173,8 +198,9 @@ def export_v4_hf(w: V4Weights, directory, dense_format: str = "fp8_block", exper
     out["hc_head_fn"], out["hc_head_scale"], out["hc_head_base"] = (w.hc_head_fn.float().cpu(), w.hc_head_scale.float().cpu(),
                                                                   w.hc_head_base.float().cpu())
     I = cfg.moe_inter
-    for i, lw in enumerate(w.layers):
-        p, a = f"layers.{i}.", f"layers.{i}.attn."
+
+    def layer(p: str, lw: V4LayerWeights) -> None:
+        a = p + "attn."
         for k in ("hc_attn_fn", "hc_attn_scale", "hc_attn_base", "hc_ffn_fn", "hc_ffn_scale", "hc_ffn_base"):
             out[p + k] = getattr(lw, k).float().cpu()
         out[p + "attn_norm.weight"], out[p + "ffn_norm.weight"] = lw.attn_norm.cpu(), lw.ffn_norm.cpu()
@@ -209,6 +235,20 @@ def export_v4_hf(w: V4Weights, directory, dense_format: str = "fp8_block", exper
             out[x + "wq_b.weight"], out[x + "weights_proj.weight"] = lw.i_wq_b.cpu(), lw.i_weights.cpu()
             out[x + "compressor.wkv.weight"], out[x + "compressor.wgate.weight"] = lw.ic_wkv.cpu(), lw.ic_wgate.cpu()
             out[x + "compressor.ape"], out[x + "compressor.norm.weight"] = lw.ic_ape.float().cpu(), lw.ic_norm.cpu()
+
+    for i, lw in enumerate(w.layers):
+        layer(f"layers.{i}.", lw)
+    if w.proposal is not None:
+        pw = w.proposal
+        for m, lw in enumerate(pw.stages):
+            layer(f"mtp.{m}.", lw)
+        last = f"mtp.{len(pw.stages) - 1}."
+        out["mtp.0.main_proj.weight"], out["mtp.0.main_norm.weight"] = pw.main_proj.cpu(), pw.main_norm.cpu()
+        out[last + "hc_head_fn"], out[last + "hc_head_scale"] = pw.hc_head_fn.float().cpu(), pw.hc_head_scale.float().cpu()
+        out[last + "hc_head_base"], out[last + "norm.weight"] = pw.hc_head_base.float().cpu(), pw.norm.cpu()
+        out[last + "markov_head.markov_w1.weight"] = pw.markov_w1.cpu()
+        out[last + "markov_head.markov_w2.weight"] = pw.markov_w2.cpu()
+        out[last + "confidence_head.proj.weight"] = pw.confidence_proj.cpu()
     d = Path(directory)
     d.mkdir(parents=True, exist_ok=True)
     write_sharded(out, d, shard_bytes, names)

@@ -64,6 +64,12 @@ class V4Config:
     indexer_ratio: int = 4                          # the ratio whose layers overlap windows and use the indexer
     proposal_block_size: int = 5
     max_position: int = 4096
+    # proposal attachment (the checkpoint's `mtp.*` stages): 0 stages = none.  Stages are window-only V4 layers
+    # with a learned router; `proposal_target_layers` names the target layers whose output is tapped
+    n_proposal_stages: int = 0
+    proposal_target_layers: Tuple[int, ...] = ()
+    proposal_noise_token: int = 0
+    proposal_markov_rank: int = 256
 
     def ratio(self, layer: int) -> int:
         return self.compress_ratios[layer] if layer < len(self.compress_ratios) else 0
@@ -161,6 +167,22 @@ class V4LayerWeights:
 
 
 @dataclass
+class V4ProposalWeights:
+    """The `mtp.*` namespace: stages (stage 0 also owns the projection of the target taps), prediction heads of
+    the last stage (crates/ferrule-model/src/models/deepseek_v4/proposal_attachment.rs:57-91)."""
+    stages: List[V4LayerWeights]
+    main_proj: torch.Tensor          # [hidden, taps * hidden]
+    main_norm: torch.Tensor
+    hc_head_fn: torch.Tensor
+    hc_head_scale: torch.Tensor
+    hc_head_base: torch.Tensor
+    norm: torch.Tensor
+    markov_w1: torch.Tensor          # [vocab, rank]
+    markov_w2: torch.Tensor          # [vocab, rank]
+    confidence_proj: torch.Tensor    # [1, hidden + rank]
+
+
+@dataclass
 class V4Weights:
     cfg: V4Config
     embed: torch.Tensor
@@ -170,6 +192,7 @@ class V4Weights:
     hc_head_base: torch.Tensor
     final_norm: torch.Tensor
     lm_head: torch.Tensor
+    proposal: Optional[V4ProposalWeights] = None
 
 
 def random_v4_weights(cfg: V4Config, device="cpu", seed: int = 0, std: float = 0.05) -> V4Weights:
@@ -184,8 +207,8 @@ def random_v4_weights(cfg: V4Config, device="cpu", seed: int = 0, std: float = 0
 
     H, hc, hd = cfg.hidden, cfg.hc_mult, cfg.head_dim
     mix = 2 * hc + hc * hc
-    layers = []
-    for i in range(cfg.n_layers):
+
+    def layer(hashed: bool, r: int, indexer: bool) -> V4LayerWeights:
         E, I = cfg.n_routed_experts, cfg.moe_inter
         sI = cfg.n_shared_experts * I
         lw = V4LayerWeights(
@@ -198,23 +221,34 @@ def random_v4_weights(cfg: V4Config, device="cpu", seed: int = 0, std: float = 0
             wo_a=n(cfg.o_groups, cfg.o_lora_rank, cfg.group_in), wo_b=n(H, cfg.o_groups * cfg.o_lora_rank),
             ffn_norm=ones(H), router_w=n(E, H),
             e_w13=n(E, 2 * I, H), e_w2=n(E, H, I), w13=n(1, 2 * sI, H), w2=n(1, H, sI))
-        if i < cfg.n_hash_layers:
+        if hashed:
             lw.hash_table = torch.randint(0, E, (cfg.vocab_size, cfg.topk), generator=g).to(device)
         else:
             lw.router_bias = n(E, dtype=torch.float32, s=0.1)
-        r = cfg.ratio(i)
         if r:
-            od = hd * (2 if cfg.has_indexer(i) else 1)
+            od = hd * (2 if indexer else 1)
             lw.c_wkv, lw.c_wgate = n(od, H), n(od, H)
             lw.c_ape, lw.c_norm = n(r, od, dtype=torch.float32, s=0.5), ones(hd)
-        if cfg.has_indexer(i):
+        if indexer:
             idim = cfg.index_head_dim
             lw.i_wq_b, lw.i_weights = n(cfg.index_n_heads * idim, cfg.q_lora_rank), n(cfg.index_n_heads, H)
             lw.ic_wkv, lw.ic_wgate = n(2 * idim, H), n(2 * idim, H)
             lw.ic_ape, lw.ic_norm = n(r, 2 * idim, dtype=torch.float32, s=0.5), ones(idim)
-        layers.append(lw)
-    return V4Weights(cfg, n(cfg.vocab_size, H, s=0.5), layers, n(hc, hc * H, dtype=torch.float32, s=0.02),
-                     torch.tensor([1.0], device=device), n(hc, dtype=torch.float32, s=0.3), ones(H), n(cfg.vocab_size, H))
+        return lw
+
+    layers = [layer(i < cfg.n_hash_layers, cfg.ratio(i), cfg.has_indexer(i)) for i in range(cfg.n_layers)]
+    w = V4Weights(cfg, n(cfg.vocab_size, H, s=0.5), layers, n(hc, hc * H, dtype=torch.float32, s=0.02),
+                  torch.tensor([1.0], device=device), n(hc, dtype=torch.float32, s=0.3), ones(H), n(cfg.vocab_size, H))
+    if cfg.n_proposal_stages:
+        rank = cfg.proposal_markov_rank
+        w.proposal = V4ProposalWeights(
+            stages=[layer(False, 0, False) for _ in range(cfg.n_proposal_stages)],
+            main_proj=n(H, len(cfg.proposal_target_layers) * H), main_norm=ones(H),
+            hc_head_fn=n(hc, hc * H, dtype=torch.float32, s=0.02), hc_head_scale=torch.tensor([1.0], device=device),
+            hc_head_base=n(hc, dtype=torch.float32, s=0.3), norm=ones(H),
+            markov_w1=n(cfg.vocab_size, rank, s=0.3), markov_w2=n(cfg.vocab_size, rank, s=0.3),
+            confidence_proj=n(1, H + rank, s=0.3))
+    return w
 
 
 def _rope_tables(cfg: V4Config, theta: float, dim: int, device):
@@ -247,6 +281,7 @@ class V4SeqCache:
         self.icomp = [[] for _ in range(L)]
         self.cstate = [_CompressorState() for _ in range(L)]
         self.istate = [_CompressorState() for _ in range(L)]
+        self.pctx = [[] for _ in range(cfg.n_proposal_stages)]     # proposal stages' context KV rows by position
         self.position = 0
 
 
@@ -259,6 +294,17 @@ class V4Reference:
         self.crope = _rope_tables(cfg, cfg.compress_rope_theta, cfg.rope_dim, dev)
         self.irope = _rope_tables(cfg, cfg.compress_rope_theta, min(cfg.rope_dim, cfg.index_head_dim), dev)
         self.rnd = ref.bf16_round
+        self.proposal = None
+        if w.proposal is not None:
+            from .v4_proposal import V4Proposal
+            self.proposal = V4Proposal(w, self.rope)
+
+    def propose(self, c: V4SeqCache, n_committed: int, anchor: int):
+        """Drafts after `anchor` for a sequence with `n_committed` committed tokens -> (token ids, confidence logits)."""
+        hd = self.cfg.head_dim
+        ctx = [torch.stack(rows[:n_committed]) if n_committed else torch.zeros(0, hd, device=self.w.embed.device)
+               for rows in c.pctx]
+        return self.proposal.propose(ctx, n_committed, anchor)
 
     def _compress(self, st: _CompressorState, wkv, wgate, ape, norm, xn, pos: int, ratio: int, overlap: bool, dim: int,
                   rope, rdim: int) -> Optional[torch.Tensor]:
@@ -340,6 +386,7 @@ class V4Reference:
         cfg, rnd, w = self.cfg, self.rnd, self.w
         pos = c.position
         state = w.embed[token].float()[None, None].repeat(1, cfg.hc_mult, 1)            # [1, hc, H]
+        taps = []
         for i, lw in enumerate(w.layers):
             x, (_, post, comb) = v4.hc_pre(state, lw.hc_attn_fn, lw.hc_attn_scale, lw.hc_attn_base, cfg.hc)
             x = rnd(x)
@@ -351,10 +398,30 @@ class V4Reference:
             xn = rnd(ref.rmsnorm(x, lw.ffn_norm, cfg.norm_eps))[0]
             f = self._moe(lw, xn, token)
             state = rnd(v4.hc_post(f[None], state, post, comb))
+            if self.proposal is not None and i in cfg.proposal_target_layers:
+                taps.append(self.proposal.tap(state))
+        if self.proposal is not None:
+            # every target row leaves one context KV row per proposal stage at its position
+            main_x = self.proposal.main_rows(taps)
+            pos_t = torch.tensor([pos], device=main_x.device)
+            for s_, rows in enumerate(c.pctx):
+                del rows[pos:]
+                rows.append(self.proposal.context_kv(s_, main_x, pos_t)[0])
         h = rnd(v4.hc_head(state, w.hc_head_fn, w.hc_head_scale, w.hc_head_base, cfg.hc))
         hn = rnd(ref.rmsnorm(h, w.final_norm, cfg.norm_eps))[0]
         c.position += 1
         return hn @ w.lm_head.float().T
+
+
+class _OffsetRows:
+    """Rows [lo, hi) of a position-indexed plane, sliced with absolute positions (`x[a:b]` with lo <= a)."""
+
+    def __init__(self, plane: torch.Tensor, lo: int, hi: int):
+        self.plane, self.lo, self.hi = plane, lo, hi
+
+    def __getitem__(self, sl: slice) -> torch.Tensor:
+        a, b = max(sl.start or 0, self.lo), min(self.hi if sl.stop is None else sl.stop, self.hi)
+        return self.plane[a:max(a, b)]
 
 
 class V4Cuda:
@@ -402,6 +469,19 @@ class V4Cuda:
         self.ones_id = torch.ones(cfg.index_head_dim, **bf)
         self.positions = [0] * max_seqs
         self.launch_note = "decode: one token per sequence per step"
+        # proposal attachment: one context KV plane per stage, addressed by (slot, position) like the other tables
+        self.proposal = None
+        self.pctx = []
+        if w.proposal is not None:
+            from .v4_proposal import V4Proposal
+            self.proposal = V4Proposal(w, self.rope)
+            self.pctx = [torch.zeros(max_seqs, max_len, hd, **bf) for _ in range(cfg.n_proposal_stages)]
+
+    def propose(self, slot: int, n_committed: int, anchor: int):
+        lo = max(0, n_committed - self.cfg.window)
+        # the proposal reads rows [lo, n_committed): hand it a view whose row index is the position
+        ctx = [_OffsetRows(t[slot], lo, n_committed) for t in self.pctx]
+        return self.proposal.propose(ctx, n_committed, anchor)
 
     # -- helpers ---------------------------------------------------------------------------
     def _norm(self, x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
@@ -445,6 +525,7 @@ class V4Cuda:
         tok_t = torch.tensor(tokens, dtype=torch.int32, device=dev)
         emb = K.embedding(tok_t, w.embed)
         state = emb[:, None, :].expand(B, hc, H).contiguous()
+        taps = []
         for i, lw in enumerate(w.layers):
             x, coeff = K4.hc_pre(state, lw.hc_attn_fn, lw.hc_attn_scale, lw.hc_attn_base, cfg.hc)
             xn = self._norm(x, lw.attn_norm)
@@ -504,6 +585,12 @@ class V4Cuda:
             xn = self._norm(x, lw.ffn_norm)
             f = self._moe(lw, xn, tok_t, B)
             state = K4.hc_post(f, state, coeff)
+            if self.proposal is not None and i in cfg.proposal_target_layers:
+                taps.append(self.proposal.tap(state))
+        if self.proposal is not None:
+            main_x = self.proposal.main_rows(taps)
+            for s_, plane in enumerate(self.pctx):
+                plane[seq_t, pos_t.long()] = self.proposal.context_kv(s_, main_x, pos_t).to(plane.dtype)
         h, _ = K4.hc_pre(state, w.hc_head_fn, w.hc_head_scale, w.hc_head_base, cfg.hc, head_only=True)
         hn = self._norm(h, w.final_norm)
         logits = K.gemm(hn, w.lm_head, out_dtype=torch.float32)

@@ -27,7 +27,7 @@ import torch
 
 from ..runtime.execution import (ExecutionBatch, ExecutionCapabilities, ExecutionOutput, KvLayoutSchema,
                                  KvPlaneDescriptor, LogitsKind, RowOutput)
-from ..runtime.runner import Complete, EndIntent, EndStatus, ModelRunner
+from ..runtime.runner import Complete, EndIntent, EndStatus, ModelRunner, Proposal
 from .v4_model import V4Cuda, V4Reference, V4SeqCache, V4Weights
 
 
@@ -43,6 +43,8 @@ def _truncate(c: V4SeqCache, cfg, pos: int) -> None:
         del c.cstate[i].gate[pos:]
         del c.istate[i].kv[pos:]
         del c.istate[i].gate[pos:]
+    for rows in c.pctx:
+        del rows[pos:]
     c.position = pos
 
 
@@ -70,6 +72,8 @@ class V4Runner(ModelRunner):
         self.txns: Dict[int, ExecutionBatch] = {}
         self.steps = 0
         self.forward_ns = 0
+        self.proposal_blocks = 0
+        self.proposal_ns = 0
         # committed cursor of every slot-bound sequence state: a step binds to (generation, position) when it
         # starts and commits only if both still hold; a step that fails half-way poisons the slot until release
         self.seq_state: Dict[int, SequenceStateCore] = {}
@@ -142,6 +146,32 @@ class V4Runner(ModelRunner):
     def release_pages(self, pages: Sequence[int]) -> None:
         pass
 
+    # ------------------------------------------------------------------ drafting
+    def proposals_enabled(self) -> bool:
+        return self.w.proposal is not None
+
+    def propose(self, slots, anchors, positions, views, max_draft) -> List[Proposal]:
+        """One proposal block per sequence: the checkpoint's block drafter reads the context rows that the
+        target's committed positions left in the proposal stages' planes (rows past `position` - from a
+        rejected draft or an aborted step - are not read) and returns up to `gamma` drafts after the anchor."""
+        if self.w.proposal is None:
+            return [Proposal([], []) for _ in slots]
+        out: List[Proposal] = []
+        t0 = time.perf_counter_ns()
+        for slot, anchor, pos in zip(slots, anchors, positions):
+            core = self.seq_state.get(slot)
+            if core is None or core.poisoned or core.position < pos:
+                out.append(Proposal([], []))            # no committed context for this slot: draft nothing
+                continue
+            if self.is_cuda:
+                toks, conf = self.fwd.propose(slot, pos, anchor)
+            else:
+                toks, conf = self.fwd.propose(self.caches[slot], pos, anchor)
+            out.append(Proposal(toks[:max_draft], conf[:max_draft]))
+            self.proposal_blocks += 1
+        self.proposal_ns += time.perf_counter_ns() - t0
+        return out
+
     def snapshot_pages(self, pages):
         """Swap-out of a V4 sequence: its state sits in the tables of its slot, and a suspended sequence keeps
         its slot, so nothing has to be copied - the pages the engine takes back are its admission budget, not
@@ -160,7 +190,8 @@ class V4Runner(ModelRunner):
             self.caches.pop(state_slot, None)
 
     def observability(self) -> Dict[str, object]:
-        return {"model": "deepseek-v4", "decode_steps": self.steps, "forward_ms": self.forward_ns / 1e6}
+        return {"model": "deepseek-v4", "decode_steps": self.steps, "forward_ms": self.forward_ns / 1e6,
+                "proposal_blocks": self.proposal_blocks, "proposal_ms": self.proposal_ns / 1e6}
 
     # ------------------------------------------------------------------ execution
     @staticmethod

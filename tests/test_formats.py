@@ -174,3 +174,56 @@ def test_v4_checkpoint_directory_round_trip_and_serving(tmp_path):
     with contextlib.redirect_stdout(buf):
         assert cli_main(["make-fixture", "--family", "v4", "--out", str(tmp_path / "fx"), "--layers", "2"]) == 0
     assert json.loads(buf.getvalue())["expert_format"] == "mxfp4" and load_v4_hf(tmp_path / "fx").cfg.n_layers == 2
+
+
+def test_v4_checkpoint_carries_the_proposal_attachment(tmp_path):
+    """The `mtp.*` namespace: stage bodies, stage 0's projection of the target taps, the last stage's heads.  The
+    loaded drafter proposes what the written one does (plain format: bit equal), and the CLI serves the
+    directory with speculative decoding - the same tokens as without."""
+    import contextlib, io, json
+    from ferrule_b200.cli.main import main as cli_main
+    from ferrule_b200.io.safetensors import ShardedCheckpoint
+    from ferrule_b200.io.v4_checkpoint import export_v4_hf, load_v4_hf, v4_config_from_hf, v4_config_to_hf
+    from ferrule_b200.models.v4_model import V4Reference, V4SeqCache, random_v4_weights, tiny_v4
+    cfg = tiny_v4().with_(n_proposal_stages=2, proposal_target_layers=(0, 2), proposal_noise_token=3, proposal_markov_rank=16)
+    assert v4_config_from_hf(v4_config_to_hf(cfg)) == cfg
+    w = random_v4_weights(cfg, seed=6)
+    d = tmp_path / "v4p"
+    export_v4_hf(w, d, dense_format="plain", expert_format="plain")
+    ck = ShardedCheckpoint(d)
+    names = set(ck.names())
+    ck.close()
+    for n in ("mtp.0.main_proj.weight", "mtp.0.main_norm.weight", "mtp.1.attn.wkv.weight", "mtp.1.ffn.gate.bias",
+              "mtp.1.hc_head_fn", "mtp.1.norm.weight", "mtp.1.markov_head.markov_w1.weight",
+              "mtp.1.markov_head.markov_w2.weight", "mtp.1.confidence_head.proj.weight", "mtp.0.ffn.experts.7.w2.weight"):
+        assert n in names, n
+    assert "mtp.0.hc_head_fn" not in names and "mtp.1.main_proj.weight" not in names
+    assert "mtp.0.attn.compressor.wkv.weight" not in names and "mtp.0.ffn.gate.tid2eid" not in names
+    got = load_v4_hf(d)
+    assert got.cfg == cfg and got.proposal is not None and len(got.proposal.stages) == 2
+    assert torch.equal(got.proposal.markov_w2, w.proposal.markov_w2) and torch.equal(got.proposal.main_proj, w.proposal.main_proj)
+
+    def drafts(weights):
+        m, c = V4Reference(weights), V4SeqCache(weights.cfg)
+        for t in (5, 9, 11, 200, 31, 7):
+            logits = m.step(c, t)
+        return m.propose(c, 6, int(logits.argmax()))
+    assert drafts(got) == drafts(w)
+    outs = []
+    for extra in ([], ["--speculative"]):
+        buf = io.StringIO()
+        with contextlib.redirect_stdout(buf):
+            assert cli_main(["generate", "--model-dir", str(d), "--device", "cpu", "--tokens", "5,9,11", "--max-tokens", "6",
+                             "--ignore-eos", "--ctx-size", "64", "--page-size", "16", "--max-seqs", "2"] + extra) == 0
+        outs.append(json.loads(buf.getvalue().strip().splitlines()[-1]))
+    assert outs[0]["tokens"] == outs[1]["tokens"] and len(outs[0]["tokens"]) == 6
+    # a directory without stages refuses --speculative instead of silently decoding plainly
+    export_v4_hf(random_v4_weights(tiny_v4(), seed=6), tmp_path / "bare", dense_format="plain", expert_format="plain")
+    with pytest.raises(SystemExit):
+        cli_main(["generate", "--model-dir", str(tmp_path / "bare"), "--device", "cpu", "--tokens", "5", "--max-tokens", "2",
+                  "--speculative", "--ctx-size", "64", "--page-size", "16", "--max-seqs", "2"])
+    buf = io.StringIO()
+    with contextlib.redirect_stdout(buf):
+        assert cli_main(["make-fixture", "--family", "v4", "--out", str(tmp_path / "fxp"), "--layers", "2",
+                         "--proposal-stages", "1", "--plain"]) == 0
+    assert json.loads(buf.getvalue())["proposal_stages"] == 1 and load_v4_hf(tmp_path / "fxp").proposal is not None
