@@ -59,7 +59,10 @@ def v4_config_from_hf(hf: dict) -> V4Config:
         n_proposal_stages=int(hf.get("num_nextn_predict_layers", 0)),
         proposal_target_layers=tuple(int(i) for i in hf.get("proposal_target_layer_ids", ())),
         proposal_noise_token=int(hf.get("proposal_noise_token_id", d.proposal_noise_token)),
-        proposal_markov_rank=int(hf.get("proposal_markov_rank", d.proposal_markov_rank)))
+        proposal_markov_rank=int(hf.get("proposal_markov_rank", d.proposal_markov_rank)),
+        # published checkpoints were trained with the quantisation steps in the forward pass and say so through
+        # their quantization_config; directories written here carry the flag itself
+        qat=bool(hf["qat"]) if "qat" in hf else hf.get("quantization_config") is not None)
 
 
 def v4_config_to_hf(cfg: V4Config) -> dict:
@@ -79,7 +82,7 @@ def v4_config_to_hf(cfg: V4Config) -> dict:
         "proposal_block_size": cfg.proposal_block_size, "max_position_embeddings": cfg.max_position,
         "num_nextn_predict_layers": cfg.n_proposal_stages, "proposal_target_layer_ids": list(cfg.proposal_target_layers),
         "proposal_noise_token_id": cfg.proposal_noise_token, "proposal_markov_rank": cfg.proposal_markov_rank,
-        "scoring_func": "sqrtsoftplus",
+        "scoring_func": "sqrtsoftplus", "qat": cfg.qat,
     }
 
 

@@ -176,6 +176,40 @@ def hc_mean_taps(states, hc: int) -> torch.Tensor:
     return torch.cat([ref.bf16_round(s.float().sum(1) / hc) for s in states], dim=-1)
 
 
+# ------------------------------------------------------------------------------------------ QAT steps
+# The checkpoint was trained with these quantisations inside the forward pass; a runtime that leaves them out
+# computes a (slightly) different function.  All three quantise and come straight back to bf16 values, on
+# whichever device the rows live (crates/ferrule-model/src/models/deepseek_v4/helpers.rs:138-201,
+# crates/ferrule-model/src/checkpoint/encoding.rs:199-300).
+def qat_kv_rows(rows: torch.Tensor, rope_dim: int, block: int = 64) -> torch.Tensor:
+    """KV rows [..., head_dim] after RoPE: the non-rotary part goes through FP8 e4m3 with one power-of-two scale
+    per `block` features (per row when the width is not a multiple of it); the rotary tail is left alone."""
+    from ..io import encoding as enc
+    hd = rows.shape[-1]
+    n = hd - rope_dim
+    if n <= 0:
+        return rows
+    out = rows.float().clone()
+    out[..., :n] = enc.fp8_qat(out[..., :n], block if n % block == 0 else n)
+    return out.to(rows.dtype)
+
+
+def qat_indexer_rows(rows: torch.Tensor) -> torch.Tensor:
+    """Indexer queries / compressed indexer rows [..., d] (d a power of two, multiple of 32): bf16 -> orthonormal
+    Hadamard transform -> bf16 -> FP4 e2m1 with one power-of-two scale per 32 features."""
+    from ..io import encoding as enc
+    x = enc.bf16_round(enc.hadamard(enc.bf16_round(rows.float())))
+    return enc.fp4_qat(x, 32).to(rows.dtype)
+
+
+def qat_linear_input(x: torch.Tensor, block: int = 128) -> torch.Tensor:
+    """Activation rows in front of a linear whose checkpoint weight is quantised: FP8 e4m3, one power-of-two
+    scale per 1 x `block` (amax floored at 1e-4)."""
+    from ..io import encoding as enc
+    n = x.shape[-1]
+    return enc.fp8_qat(x.float(), block if n % block == 0 else n).to(x.dtype)
+
+
 # ------------------------------------------------------------------------------------------ CUDA dispatch
 def hc_pre_cuda(state, fn, scale, base, cfg: HcConfig):
     from ..ops import v4 as K4

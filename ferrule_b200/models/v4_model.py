@@ -70,6 +70,9 @@ class V4Config:
     proposal_target_layers: Tuple[int, ...] = ()
     proposal_noise_token: int = 0
     proposal_markov_rank: int = 256
+    # quantisation-aware-training steps inside the forward pass (FP8 on KV rows and on the inputs of the linears
+    # the checkpoint stores quantised, Hadamard + FP4 on the indexer's rows): on for checkpoints trained that way
+    qat: bool = False
 
     def ratio(self, layer: int) -> int:
         return self.compress_ratios[layer] if layer < len(self.compress_ratios) else 0
@@ -307,26 +310,33 @@ class V4Reference:
         return self.proposal.propose(ctx, n_committed, anchor)
 
     def _compress(self, st: _CompressorState, wkv, wgate, ape, norm, xn, pos: int, ratio: int, overlap: bool, dim: int,
-                  rope, rdim: int) -> Optional[torch.Tensor]:
+                  rope, rdim: int, indexer_plane: bool = False) -> Optional[torch.Tensor]:
         st.kv.append(xn @ wkv.float().T)
         st.gate.append(xn @ wgate.float().T)
         if (pos + 1) % ratio:
             return None
         pooled = v4.compressor_pool(torch.stack(st.kv), torch.stack(st.gate), ape, ratio, overlap, dim)[-1]
         row = self.rnd(ref.rmsnorm(pooled[None], norm, self.cfg.norm_eps))[0]
-        return self.rnd(_rope_tail(row, rope[0], rope[1], pos + 1 - ratio, rdim))
+        row = self.rnd(_rope_tail(row, rope[0], rope[1], pos + 1 - ratio, rdim))
+        if self.cfg.qat:
+            row = v4.qat_indexer_rows(row) if indexer_plane else v4.qat_kv_rows(row, rdim)
+        return row
 
     def _attention(self, lw: V4LayerWeights, layer: int, x: torch.Tensor, c: V4SeqCache, pos: int) -> torch.Tensor:
         cfg, rnd = self.cfg, self.rnd
         hd, rd, nh = cfg.head_dim, cfg.rope_dim, cfg.n_heads
-        q_lat = rnd(x @ lw.wq_a.float().T)
+        aq = v4.qat_linear_input if cfg.qat else (lambda t: t)       # inputs of the linears stored quantised
+        xa = aq(x)
+        q_lat = rnd(xa @ lw.wq_a.float().T)
         qn = rnd(ref.rmsnorm(q_lat[None], lw.q_norm, cfg.norm_eps))[0]
-        q = rnd(qn @ lw.wq_b.float().T).view(nh, hd)
+        q = rnd(aq(qn) @ lw.wq_b.float().T).view(nh, hd)
         q = rnd(ref.rmsnorm(q, None, cfg.norm_eps))
         q = rnd(_rope_tail(q, self.rope[0], self.rope[1], pos, rd))
-        kv = rnd(x @ lw.wkv.float().T)
+        kv = rnd(xa @ lw.wkv.float().T)
         kv = rnd(ref.rmsnorm(kv[None], lw.kv_norm, cfg.norm_eps))[0]
         kv = rnd(_rope_tail(kv, self.rope[0], self.rope[1], pos, rd))
+        if cfg.qat:
+            kv = v4.qat_kv_rows(kv, rd)
         c.kv[layer].append(kv)
         ratio = cfg.ratio(layer)
         sel_comp: List[int] = []
@@ -334,7 +344,7 @@ class V4Reference:
             if cfg.has_indexer(layer):
                 idim = cfg.index_head_dim
                 new_i = self._compress(c.istate[layer], lw.ic_wkv, lw.ic_wgate, lw.ic_ape, lw.ic_norm, x, pos, ratio, True,
-                                       idim, self.irope, min(rd, idim))
+                                       idim, self.irope, min(rd, idim), indexer_plane=True)
                 if new_i is not None:
                     c.icomp[layer].append(new_i)
             new_c = self._compress(c.cstate[layer], lw.c_wkv, lw.c_wgate, lw.c_ape, lw.c_norm, x, pos, ratio,
@@ -344,8 +354,10 @@ class V4Reference:
             n_c = len(c.comp[layer])
             if cfg.has_indexer(layer) and n_c:
                 idim, ih = cfg.index_head_dim, cfg.index_n_heads
-                iq = rnd(qn @ lw.i_wq_b.float().T).view(ih, idim)
+                iq = rnd(aq(qn) @ lw.i_wq_b.float().T).view(ih, idim)
                 iq = rnd(_rope_tail(iq, self.irope[0], self.irope[1], pos, min(rd, idim)))
+                if cfg.qat:
+                    iq = v4.qat_indexer_rows(iq)
                 wts = rnd(x @ lw.i_weights.float().T)
                 wts = rnd(wts * (idim ** -0.5 * ih ** -0.5))
                 idx, _ = v4.indexer_topk(iq, torch.stack(c.icomp[layer]), wts, cfg.index_topk, n_c)
@@ -360,8 +372,9 @@ class V4Reference:
         o = rnd(o)
         o = rnd(_rope_tail(o, self.rope[0], self.rope[1], pos, rd, inverse=True))
         og = o.reshape(cfg.o_groups, cfg.group_in)
+        # the grouped first stage multiplies dequantised weights without quantising its input; the second is a linear
         lat = rnd(torch.einsum("gk,gnk->gn", og, lw.wo_a.float())).reshape(-1)
-        return rnd(lat @ lw.wo_b.float().T)
+        return rnd(aq(lat) @ lw.wo_b.float().T)
 
     def _moe(self, lw: V4LayerWeights, x: torch.Tensor, token: int) -> torch.Tensor:
         cfg, rnd = self.cfg, self.rnd
@@ -376,10 +389,11 @@ class V4Reference:
             y = x @ lw.e_w13[e].float().T
             h = rnd(ref.swiglu(y[:I], y[I:], cfg.swiglu_limit))
             out = out + rnd((h @ lw.e_w2[e].float().T) * wts[0, s])
-        y = x @ lw.w13[0].float().T
+        aq = v4.qat_linear_input if cfg.qat else (lambda t: t)       # the shared experts are stored in FP8
+        y = aq(x) @ lw.w13[0].float().T
         sI = y.shape[0] // 2
         h = rnd(ref.swiglu(y[:sI], y[sI:], cfg.swiglu_limit))
-        return rnd(out + rnd(h @ lw.w2[0].float().T))
+        return rnd(out + rnd(aq(h) @ lw.w2[0].float().T))
 
     def step(self, c: V4SeqCache, token: int) -> torch.Tensor:
         """Feed one token of one sequence; returns fp32 logits [vocab]."""
@@ -489,7 +503,8 @@ class V4Cuda:
         self.K.add_rmsnorm(x, weight, self.cfg.norm_eps, norm_out=out)
         return out
 
-    def _compress(self, layer: int, proj, wkv, wgate, ape, norm_w, xn, seqs, pos, ratio, overlap, dim, rope, rdim):
+    def _compress(self, layer: int, proj, wkv, wgate, ape, norm_w, xn, seqs, pos, ratio, overlap, dim, rope, rdim,
+                  indexer_plane: bool = False):
         """Append the projected rows of this step; return [(sequence, group, bf16 row)] for finished groups."""
         K, K4, cfg = self.K, self.K4, self.cfg
         pk = K.gemm(xn, wkv, out_dtype=torch.float32)
@@ -509,6 +524,8 @@ class V4Cuda:
             row = self._norm(pooled, norm_w)
             cp = torch.tensor([p + 1 - ratio], dtype=torch.int32, device=self.device)
             K4.rope_rows(row.view(1, 1, dim), cp, rope[0], rope[1], off=dim - rdim, rdim=rdim)
+            if cfg.qat:
+                row = v4.qat_indexer_rows(row) if indexer_plane else v4.qat_kv_rows(row, rdim)
             done.append((s, g, row[0]))
         return done
 
@@ -530,12 +547,19 @@ class V4Cuda:
             x, coeff = K4.hc_pre(state, lw.hc_attn_fn, lw.hc_attn_scale, lw.hc_attn_base, cfg.hc)
             xn = self._norm(x, lw.attn_norm)
             # ---- attention ----
-            qn = self._norm(K.gemm(xn, lw.wq_a), lw.q_norm)
-            q = K.gemm(qn, lw.wq_b)
+            # QAT checkpoints: FP8 quantise-dequantise of the rows in front of the linears stored quantised, of
+            # the KV rows, Hadamard + FP4 of the indexer's rows (elementwise tensor operations on a few rows)
+            aq = v4.qat_linear_input if cfg.qat else (lambda t: t)
+            xa = aq(xn)
+            qn = self._norm(K.gemm(xa, lw.wq_a), lw.q_norm)
+            qa = aq(qn)
+            q = K.gemm(qa, lw.wq_b)
             q = self._norm(q.view(B * nh, hd), self.ones_hd).view(B, nh, hd)
             K4.rope_rows(q, pos_t, self.rope[0], self.rope[1], off=hd - rd, rdim=rd)
-            kv = self._norm(K.gemm(xn, lw.wkv), lw.kv_norm)
+            kv = self._norm(K.gemm(xa, lw.wkv), lw.kv_norm)
             K4.rope_rows(kv.view(B, 1, hd), pos_t, self.rope[0], self.rope[1], off=hd - rd, rdim=rd)
+            if cfg.qat:
+                kv = v4.qat_kv_rows(kv, rd)
             table = self.tables[i]
             table[seq_t, pos_t.long()] = kv
             ratio = cfg.ratio(i)
@@ -551,7 +575,8 @@ class V4Cuda:
                 if cfg.has_indexer(i):
                     idim = cfg.index_head_dim
                     for s, g, row in self._compress(i, self.iproj[i], lw.ic_wkv, lw.ic_wgate, lw.ic_ape, lw.ic_norm, xn,
-                                                    seqs, pos, ratio, True, idim, self.irope, min(rd, idim)):
+                                                    seqs, pos, ratio, True, idim, self.irope, min(rd, idim),
+                                                    indexer_plane=True):
                         self.iplane[i][s, g] = row
                 for s, g, row in self._compress(i, self.proj[i], lw.c_wkv, lw.c_wgate, lw.c_ape, lw.c_norm, xn, seqs,
                                                 pos, ratio, cfg.has_indexer(i), hd, self.crope, rd):
@@ -559,8 +584,10 @@ class V4Cuda:
                 if n_max:
                     if cfg.has_indexer(i):
                         idim, ih = cfg.index_head_dim, cfg.index_n_heads
-                        iq = K.gemm(qn, lw.i_wq_b).view(B, ih, idim)
+                        iq = K.gemm(qa, lw.i_wq_b).view(B, ih, idim)
                         K4.rope_rows(iq, pos_t, self.irope[0], self.irope[1], off=idim - min(rd, idim), rdim=min(rd, idim))
+                        if cfg.qat:
+                            iq = v4.qat_indexer_rows(iq).contiguous()
                         wts = K.gemm(xn, lw.i_weights, out_dtype=torch.float32)
                         wts = (wts.bfloat16().float() * (idim ** -0.5 * ih ** -0.5)).bfloat16().float().contiguous()
                         scores = torch.full((B, n_max), float("-inf"), dtype=torch.float32, device=dev)
@@ -578,7 +605,7 @@ class V4Cuda:
             o = K4.sparse_sink_attention(q, table.view(-1, hd), selection, hd, 0, cfg.softmax_scale, sink=lw.sink)
             K4.rope_rows(o, pos_t, self.rope[0], self.rope[1], off=hd - rd, rdim=rd, inverse=True)
             lat = K.gemm(o.view(B, nh * hd), lw.wo_a, x_group_koff=cfg.group_in, out_group_coff=cfg.o_lora_rank)
-            a = K.gemm(lat, lw.wo_b)
+            a = K.gemm(aq(lat), lw.wo_b)
             state = K4.hc_post(a, state, coeff)
             # ---- MoE ----
             x, coeff = K4.hc_pre(state, lw.hc_ffn_fn, lw.hc_ffn_scale, lw.hc_ffn_base, cfg.hc)
@@ -615,6 +642,7 @@ class V4Cuda:
         hmid = K.gemm(xg, lw.e_w13, epilogue=K.EPI_SWIGLU, plan=plan, act_limit=cfg.swiglu_limit)
         route_out = torch.zeros(B, slots, H, dtype=torch.bfloat16, device=self.device)
         K.gemm(hmid, lw.e_w2, out=route_out.view(B * slots, H), epilogue=K.EPI_SCATTER, plan=plan, scatter_rows=B * slots)
-        mid = K.gemm(xn, lw.w13, epilogue=K.EPI_SWIGLU, act_limit=cfg.swiglu_limit)
-        K.gemm(mid, lw.w2, out=route_out[:, k])
+        aq = v4.qat_linear_input if cfg.qat else (lambda t: t)
+        mid = K.gemm(aq(xn), lw.w13, epilogue=K.EPI_SWIGLU, act_limit=cfg.swiglu_limit)
+        K.gemm(aq(mid), lw.w2, out=route_out[:, k])
         return K.moe_reduce(route_out.view(B * slots, H), slots, k, idx, 0, E, B, H)

@@ -89,35 +89,43 @@ class V4Proposal:
         """state [T, hc, H] after a tapped target layer -> [T, H] (mean over the copies, bf16 values)."""
         return ref.bf16_round(state.float().sum(1) / self.cfg.hc_mult)
 
+    def _aq(self, x: torch.Tensor) -> torch.Tensor:
+        """Input of a linear the checkpoint stores quantised (QAT checkpoints only)."""
+        return v4.qat_linear_input(x) if self.cfg.qat else x
+
     def main_rows(self, taps: Sequence[torch.Tensor]) -> torch.Tensor:
         """taps: one [T, H] per target layer, in layer order -> projected + normalised rows [T, H]."""
-        x = _lin(torch.cat(list(taps), dim=-1), self.p.main_proj)
+        x = _lin(self._aq(torch.cat(list(taps), dim=-1)), self.p.main_proj)
         return ref.bf16_round(ref.rmsnorm(x, self.p.main_norm, self.cfg.norm_eps))
 
     def context_kv(self, stage: int, main_x: torch.Tensor, positions: torch.Tensor) -> torch.Tensor:
         """One context KV row per target row for `stage`: [T, head_dim] fp32 holding bf16 values."""
         cfg, lw = self.cfg, self.p.stages[stage]
-        kv = ref.bf16_round(ref.rmsnorm(_lin(main_x, lw.wkv), lw.kv_norm, cfg.norm_eps))
-        return ref.bf16_round(_rope_rows(kv, self.rope[0], self.rope[1], positions, cfg.rope_dim))
+        kv = ref.bf16_round(ref.rmsnorm(_lin(self._aq(main_x), lw.wkv), lw.kv_norm, cfg.norm_eps))
+        kv = ref.bf16_round(_rope_rows(kv, self.rope[0], self.rope[1], positions, cfg.rope_dim))
+        return v4.qat_kv_rows(kv, cfg.rope_dim) if cfg.qat else kv
 
     # ------------------------------------------------------------------ proposal half
     def _attention(self, lw, xn: torch.Tensor, ctx: torch.Tensor, positions: torch.Tensor) -> torch.Tensor:
         cfg, rnd = self.cfg, ref.bf16_round
         G = xn.shape[0]
         hd, rd, nh = cfg.head_dim, cfg.rope_dim, cfg.n_heads
-        qn = rnd(ref.rmsnorm(_lin(xn, lw.wq_a), lw.q_norm, cfg.norm_eps))
-        q = _lin(qn, lw.wq_b).view(G, nh, hd)
+        xa = self._aq(xn)
+        qn = rnd(ref.rmsnorm(_lin(xa, lw.wq_a), lw.q_norm, cfg.norm_eps))
+        q = _lin(self._aq(qn), lw.wq_b).view(G, nh, hd)
         q = rnd(ref.rmsnorm(q, None, cfg.norm_eps))
         q = rnd(_rope_rows(q, self.rope[0], self.rope[1], positions, rd))
-        kv = rnd(ref.rmsnorm(_lin(xn, lw.wkv), lw.kv_norm, cfg.norm_eps))
+        kv = rnd(ref.rmsnorm(_lin(xa, lw.wkv), lw.kv_norm, cfg.norm_eps))
         kv = rnd(_rope_rows(kv, self.rope[0], self.rope[1], positions, rd))
+        if cfg.qat:
+            kv = v4.qat_kv_rows(kv, rd)
         table = torch.cat([ctx.float(), kv], dim=0)             # context window rows, then the whole block
         sel = torch.arange(table.shape[0], dtype=torch.int32, device=xn.device)[None].expand(G, -1)
         o = rnd(v4.sparse_sink_attention(q, table, sel, hd, cfg.softmax_scale, sink=lw.sink))
         o = rnd(_rope_rows(o, self.rope[0], self.rope[1], positions, rd, inverse=True))
         og = o.reshape(G, cfg.o_groups, cfg.group_in)
         lat = rnd(torch.einsum("tgk,gnk->tgn", og, lw.wo_a.float())).reshape(G, -1)
-        return _lin(lat, lw.wo_b)
+        return _lin(self._aq(lat), lw.wo_b)
 
     def _moe(self, lw, xn: torch.Tensor, tokens: torch.Tensor) -> torch.Tensor:
         cfg, rnd = self.cfg, ref.bf16_round
@@ -134,10 +142,10 @@ class V4Proposal:
                 h = rnd(ref.swiglu(y[:I], y[I:], cfg.swiglu_limit))
                 acc = acc + rnd((h @ lw.e_w2[e].float().T) * wt)
             out[r] = acc
-        y = xn.float() @ lw.w13[0].float().T
+        y = self._aq(xn).float() @ lw.w13[0].float().T
         sI = y.shape[1] // 2
         h = rnd(ref.swiglu(y[:, :sI], y[:, sI:], cfg.swiglu_limit))
-        return rnd(out + _lin(h, lw.w2[0]))
+        return rnd(out + _lin(self._aq(h), lw.w2[0]))
 
     def block_hidden(self, context: Sequence[torch.Tensor], n_committed: int, token_ids: Sequence[int]) -> torch.Tensor:
         """Run the block rows `token_ids` (positions n_committed ...) through the stages -> [rows, H] after the

@@ -158,6 +158,46 @@ def test_v4_model_decode_matches_reference():
     assert torch.allclose(got, torch.stack(caches[0].comp[1]), atol=0.08, rtol=0.05)
 
 
+def test_v4_decode_with_qat_steps_on_the_kernels():
+    """QAT checkpoints: the rows the kernels read are the quantised ones (FP8 window / compressed rows, FP4
+    indexer plane), batched and one-at-a-time decoding agree, and the stream follows the oracle's wherever the
+    oracle's choice is clear."""
+    from ferrule_b200.io import encoding as enc
+    from ferrule_b200.models import v4_model as M
+    from ferrule_b200.ops import _lib
+    cfg = M.tiny_v4().with_(qat=True)
+    w_cpu = M.random_v4_weights(cfg, device="cpu", seed=0)
+    w_gpu = M.random_v4_weights(cfg, device=DEV, seed=0)
+    ref_model = M.V4Reference(w_cpu)
+    caches = [M.V4SeqCache(cfg), M.V4SeqCache(cfg)]
+    both = M.V4Cuda(w_gpu, max_seqs=2, max_len=64)
+    solo = M.V4Cuda(w_gpu, max_seqs=1, max_len=64)
+    g = torch.Generator().manual_seed(0)
+    toks = torch.randint(0, cfg.vocab_size, (2, 24), generator=g)
+    agree = total = 0
+    for t in range(24):
+        want = torch.stack([ref_model.step(caches[s], int(toks[s, t])) for s in (0, 1)])
+        nxt, logits = both.step([0, 1], [int(toks[0, t]), int(toks[1, t])])
+        one, _ = solo.step([0], [int(toks[0, t])])
+        torch.cuda.synchronize()
+        assert torch.isfinite(logits).all()
+        assert int(one[0]) == int(nxt[0]), "a sequence decodes the same alone and in a batch"
+        top2 = want.topk(2, dim=-1).values
+        clear = (top2[:, 0] - top2[:, 1]) > 0.25 * float(want.abs().max())
+        agree += int((nxt.cpu()[clear].long() == want.argmax(-1)[clear]).sum())
+        total += int(clear.sum())
+    _lib.raise_on_status()
+    assert agree == total
+    rd = cfg.rope_dim
+    for layer in range(cfg.n_layers):
+        rows = both.tables[layer][0, :24].float().cpu()
+        assert torch.equal(v4.qat_kv_rows(rows, rd), rows), "window rows are stored quantised"
+    comp = both.tables[1][0, 64:64 + 6].float().cpu()
+    assert torch.equal(v4.qat_kv_rows(comp, rd), comp) and float(comp.abs().max()) > 0
+    plane = both.iplane[1][0, :6].float().cpu()
+    assert torch.equal(enc.fp4_qat(plane, 32), plane) and float(plane.abs().max()) > 0
+
+
 def test_markov_head_and_mean_taps_match_reference():
     from ferrule_b200.ops import v4 as K
     torch.manual_seed(5)

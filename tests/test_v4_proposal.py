@@ -229,3 +229,71 @@ def test_speculative_v4_stream_is_the_greedy_stream_on_the_kernels():
     assert m.cycles > 0 and m.drafted > 0 and runner.proposal_blocks > 0
     from ferrule_b200.ops import _lib
     assert _lib.read_status()[0] == 0
+
+
+# ---------------------------------------------------------------------------------------------- QAT steps
+def test_qat_row_operators():
+    from ferrule_b200.io import encoding as enc
+    g = torch.Generator().manual_seed(11)
+    rows = ref.bf16_round(torch.randn(3, 192, generator=g) * 3)
+    out = v4.qat_kv_rows(rows, rope_dim=64)
+    assert torch.equal(out[:, 128:], rows[:, 128:]), "the rotary tail is not quantised"
+    assert torch.equal(out[:, :128], enc.fp8_qat(rows[:, :128], 64))
+    assert torch.equal(v4.qat_kv_rows(out, 64), out), "quantising representable values changes nothing"
+    # 48 non-rotary features do not divide into blocks of 64: one scale per row
+    odd = ref.bf16_round(torch.randn(2, 64, generator=g))
+    assert torch.equal(v4.qat_kv_rows(odd, 16)[:, :48], enc.fp8_qat(odd[:, :48], 48))
+    # power-of-two scale from ceil(log2(amax / 448)): a block whose amax is 448 * 2^k keeps it exactly
+    blk = torch.zeros(1, 64)
+    blk[0, 0], blk[0, 1] = 448.0 * 4, 3.0
+    assert torch.equal(enc.fp8_qat(blk, 64), blk)
+    x = ref.bf16_round(torch.randn(4, 32, generator=g))
+    y = v4.qat_indexer_rows(x)
+    want = enc.fp4_qat(enc.bf16_round(enc.hadamard(x)), 32)
+    assert torch.equal(y, want)
+    # every value is an e2m1 magnitude times the row's power-of-two scale
+    mags = torch.tensor([0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0])
+    for r in range(4):
+        scale = 2.0 ** torch.ceil(torch.log2(want[r].abs().max() / 6.0))
+        assert all(bool(((v.abs() / scale)[None] == mags).any()) for v in want[r])
+    lin = ref.bf16_round(torch.randn(2, 256, generator=g))
+    assert torch.equal(v4.qat_linear_input(lin), enc.fp8_qat(lin, 128))
+
+
+def test_qat_steps_run_inside_the_v4_step():
+    cfg = _cfg(qat=True)
+    w = random_v4_weights(cfg, seed=8)
+    r, c, toks, logits = _fed(w, 17)
+    plain = V4Reference(random_v4_weights(_cfg(), seed=8))
+    c2 = V4SeqCache(plain.cfg)
+    for t in toks:
+        logits2 = plain.step(c2, t)
+    # same weights, another function: close, not equal
+    assert not torch.equal(logits, logits2)
+    assert float((logits - logits2).abs().max()) < 0.35 * float(logits2.abs().max())
+    rd = cfg.rope_dim
+    from ferrule_b200.io import encoding as enc
+    for layer in range(cfg.n_layers):
+        kv = torch.stack(c.kv[layer])
+        assert torch.equal(v4.qat_kv_rows(kv, rd), kv), "window rows are stored quantised"
+        if c.comp[layer]:
+            comp = torch.stack(c.comp[layer])
+            assert torch.equal(v4.qat_kv_rows(comp, rd), comp)
+        if c.icomp[layer]:
+            ic = torch.stack(c.icomp[layer])
+            assert torch.equal(enc.fp4_qat(ic, 32), ic), "the indexer plane holds FP4 values"
+    for rows in c.pctx:
+        ctx = torch.stack(rows)
+        assert torch.equal(v4.qat_kv_rows(ctx, rd), ctx)
+    assert not torch.equal(torch.stack(c.kv[0]), torch.stack(c2.kv[0]))
+
+
+def test_speculative_v4_with_qat_is_the_greedy_stream_on_cpu():
+    w = random_v4_weights(_cfg(qat=True), device="cpu", seed=3)
+    g = torch.Generator().manual_seed(4)
+    prompts = [torch.randint(0, w.cfg.vocab_size, (n,), generator=g).tolist() for n in (7, 13)]
+    eng, runner = _spec_engine(w)
+    got = _run(eng, prompts, 8)
+    for p, toks in zip(prompts, got):
+        assert toks == _greedy(w, p, 8)
+    assert eng.spec.metrics.drafted > 0
