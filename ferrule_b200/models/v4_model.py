@@ -446,7 +446,7 @@ class V4Cuda:
     indexer's compressed plane.  Every step runs one token per active sequence; sequence slots are fixed.
     """
 
-    def __init__(self, w: V4Weights, max_seqs: int, max_len: int):
+    def __init__(self, w: V4Weights, max_seqs: int, max_len: int, max_rows: int = 0):
         from ..ops import kernels as K
         from ..ops import movers as M
         from ..ops import v4 as K4
@@ -477,7 +477,7 @@ class V4Cuda:
                 self.iproj.append(None)
                 self.iplane.append(None)
         E, k = cfg.n_routed_experts, cfg.topk
-        R = max_seqs
+        R = self.max_rows = max(max_rows, max_seqs)          # rows of one call: decode rows or a prefill chunk
         self.plan = K.MoePlan.allocate(R * k, E, 16, dev)
         self.ones_hd = torch.ones(hd, **bf)
         self.ones_id = torch.ones(cfg.index_head_dim, **bf)
@@ -531,11 +531,27 @@ class V4Cuda:
 
     def step(self, seqs: List[int], tokens: List[int]):
         """One decode step for the sequences in slots `seqs` -> (next token ids [B] int32, fp32 logits [B, vocab])."""
+        return self.step_rows(seqs, tokens)
+
+    def step_rows(self, seqs: List[int], tokens: List[int], positions: Optional[List[int]] = None,
+                  want_rows: Optional[List[int]] = None):
+        """Rows of any mix of sequences in one pass: row r feeds `tokens[r]` to the sequence in slot `seqs[r]` at
+        `positions[r]` (default: one row per sequence at its current position - a decode step).  The rows of a
+        sequence must be consecutive positions in increasing order: a prompt chunk goes through the layers as ONE
+        batch - every GEMM sees all rows, the tables take all rows of a layer before its attention reads them,
+        and each row's selection list (window, visible compressed rows) is cut at its own position, which is what
+        keeps the chunk causal.  `want_rows`: rows whose logits are wanted (default all).
+        -> (next token ids, fp32 logits) for the wanted rows."""
         K, K4, M, cfg, w = self.K, self.K4, self.M, self.cfg, self.w
         dev = self.device
         B = len(seqs)
+        assert 0 < B <= self.max_rows, f"{B} rows, the workspace holds {self.max_rows}"
         hd, rd, nh, H, hc = cfg.head_dim, cfg.rope_dim, cfg.n_heads, cfg.hidden, cfg.hc_mult
-        pos = [self.positions[s] for s in seqs]
+        pos = [self.positions[s] for s in seqs] if positions is None else list(positions)
+        last = {}
+        for s, p in zip(seqs, pos):
+            assert p == last.get(s, p - 1) + 1, "rows of a sequence must be consecutive positions"
+            last[s] = p
         assert max(pos) < self.max_len
         pos_t = torch.tensor(pos, dtype=torch.int32, device=dev)
         seq_t = torch.tensor(seqs, dtype=torch.int64, device=dev)
@@ -591,10 +607,16 @@ class V4Cuda:
                         wts = K.gemm(xn, lw.i_weights, out_dtype=torch.float32)
                         wts = (wts.bfloat16().float() * (idim ** -0.5 * ih ** -0.5)).bfloat16().float().contiguous()
                         scores = torch.full((B, n_max), float("-inf"), dtype=torch.float32, device=dev)
-                        for b, s in enumerate(seqs):           # every sequence scores its own plane
-                            if n_c[b]:
-                                K4.indexer_scores(iq[b:b + 1], self.iplane[i][s, :n_c[b]], wts[b:b + 1],
-                                                  out=scores[b:b + 1, :n_c[b]])
+                        b0 = 0
+                        while b0 < B:                          # every sequence scores its own plane: one call for
+                            b1 = b0 + 1                        # the run of rows it has in this batch
+                            while b1 < B and seqs[b1] == seqs[b0]:
+                                b1 += 1
+                            n_run = n_c[b1 - 1]                # positions increase along a run
+                            if n_run:
+                                K4.indexer_scores(iq[b0:b1], self.iplane[i][seqs[b0], :n_run], wts[b0:b1],
+                                                  out=scores[b0:b1, :n_run])
+                            b0 = b1
                         vis = torch.tensor(n_c, dtype=torch.int32, device=dev)
                         idx = K4.indexer_topk(scores, min(cfg.index_topk, 512), vis)
                         assert idx.shape[1] == sel_w - cfg.window
@@ -618,12 +640,17 @@ class V4Cuda:
             main_x = self.proposal.main_rows(taps)
             for s_, plane in enumerate(self.pctx):
                 plane[seq_t, pos_t.long()] = self.proposal.context_kv(s_, main_x, pos_t).to(plane.dtype)
+        for s, p in last.items():
+            self.positions[s] = p + 1
+        if want_rows is not None:
+            if not want_rows:
+                return None, None
+            if len(want_rows) != B:
+                state = state[torch.tensor(want_rows, dtype=torch.int64, device=dev)].contiguous()
         h, _ = K4.hc_pre(state, w.hc_head_fn, w.hc_head_scale, w.hc_head_base, cfg.hc, head_only=True)
         hn = self._norm(h, w.final_norm)
         logits = K.gemm(hn, w.lm_head, out_dtype=torch.float32)
         nxt = K.argmax(logits)
-        for s in seqs:
-            self.positions[s] += 1
         return nxt, logits
 
     def _moe(self, lw: V4LayerWeights, xn: torch.Tensor, tok_t: torch.Tensor, B: int) -> torch.Tensor:

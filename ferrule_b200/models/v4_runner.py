@@ -9,8 +9,9 @@ budget, the tables are what the kernels read).  Every table row is addressed by 
 position after an abort or a rejected draft simply overwrites it, which is what makes transactions abortable
 without a snapshot.
 
-Prefill runs token by token through the decode step (one row per sequence per launch group): correct, and as
-fast as decode; a chunked V4 prefill kernel path does not exist yet.  Swapping a sequence out needs no copy (a
+Prefill on the kernels is batched: all rows of a transaction - prompt chunks of several sequences, verification
+rows, decode rows - go through the layers as one batch (`V4Cuda.step_rows`: every GEMM sees all rows, each row's
+selection list is cut at its own position).  The oracle path runs token by token.  Swapping a sequence out needs no copy (a
 suspended sequence keeps its slot and with it its tables; the pages it returns are admission budget), so
 `auto_preempt` works; sharing a prefix between sequences (copy-on-write pages, exact forks, the prompt-prefix
 cache) is refused, because two slots cannot share table rows.
@@ -20,8 +21,9 @@ pools for window / compressed / indexer planes, one-token decode schedule).
 """
 from __future__ import annotations
 
+import os
 import time
-from typing import Dict, List, Sequence
+from typing import Dict, List, Optional, Sequence
 
 import torch
 
@@ -57,15 +59,20 @@ class V4Runner(ModelRunner):
     supports_prefix_sharing = False
 
     def __init__(self, weights: V4Weights, n_pages: int, page_size: int = 64, max_seqs: int = 8,
-                 max_seq_len: int = 1024, max_rows: int = 2048, eos_token_id: int = -1):
+                 max_seq_len: int = 1024, max_rows: int = 2048, eos_token_id: int = -1,
+                 batched_prefill: Optional[bool] = None):
         self.w, self.cfg = weights, weights.cfg
         self.device = weights.embed.device
         self.is_cuda = self.device.type == "cuda"
         self.vocab_size, self.eos_token_id = self.cfg.vocab_size, eos_token_id
         self.page_size, self.n_pages = page_size, n_pages
         self.max_seqs, self.max_seq_len, self.max_rows = max_seqs, max_seq_len, max_rows
+        # prompt chunks (and verification rows) go through the layers as one batch of rows; off = one row per
+        # sequence per pass, the decode schedule
+        self.batched_prefill = (os.environ.get("FERRULE_V4_BATCHED_PREFILL", "1") != "0") if batched_prefill is None \
+            else batched_prefill
         if self.is_cuda:
-            self.fwd = V4Cuda(weights, max_seqs, max_seq_len)
+            self.fwd = V4Cuda(weights, max_seqs, max_seq_len, max_rows=max_rows if self.batched_prefill else 0)
         else:
             self.fwd = V4Reference(weights)
             self.caches: Dict[int, V4SeqCache] = {}
@@ -206,12 +213,26 @@ class V4Runner(ModelRunner):
         return ExecutionOutput(rows)
 
     def _execute_cuda(self, b: ExecutionBatch) -> ExecutionOutput:
-        """Wave j feeds the j-th row of every sequence that still has one: all sequences advance together, one
-        token each, through the batched decode step."""
+        """All rows of the batch in one pass through the layers (`V4Cuda.step_rows`): prompt chunks, verification
+        rows and decode rows alike; pieces of at most `max_rows` rows when the batch is larger.  With
+        `batched_prefill` off, wave j feeds the j-th row of every sequence that still has one."""
         fwd = self.fwd
         for s in b.sequences:
             fwd.positions[s.state_slot] = s.context_len
         want: Dict[int, torch.Tensor] = {}
+        if self.batched_prefill:
+            rows = [(s.state_slot, s.query_start + j, s.context_len + j) for s in b.sequences for j in range(s.query_len)]
+            for _, r, p in rows:
+                assert b.positions[r] == p, "rows of a sequence must be consecutive positions"
+            for i0 in range(0, len(rows), fwd.max_rows):
+                piece = rows[i0:i0 + fwd.max_rows]
+                wanted = [i for i, (_, r, _) in enumerate(piece) if b.logits[r].kind != LogitsKind.NONE]
+                _, logits = fwd.step_rows([sl for sl, _, _ in piece], [b.token_ids[r] for _, r, _ in piece],
+                                          [p for _, _, p in piece], want_rows=wanted)
+                self.steps += 1
+                for k, i in enumerate(wanted):
+                    want[piece[i][1]] = logits[k]
+            return self._rows_out(b, want)
         waves = max(s.query_len for s in b.sequences)
         for j in range(waves):
             live = [s for s in b.sequences if s.query_len > j]

@@ -158,6 +158,46 @@ def test_v4_model_decode_matches_reference():
     assert torch.allclose(got, torch.stack(caches[0].comp[1]), atol=0.08, rtol=0.05)
 
 
+def test_v4_prompt_chunks_in_one_pass_match_token_by_token():
+    """Two prompt chunks and a decode row as ONE batch of rows through the kernels against the same rows fed one
+    at a time: same tables (window, compressed, indexer plane), same next tokens."""
+    from ferrule_b200.models import v4_model as M
+    from ferrule_b200.ops import _lib
+    cfg = M.tiny_v4()
+    w = M.random_v4_weights(cfg, device=DEV, seed=1)
+    g = torch.Generator().manual_seed(3)
+    a, b, c = (torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (21, 13, 9))
+    one = M.V4Cuda(w, max_seqs=3, max_len=64)
+    many = M.V4Cuda(w, max_seqs=3, max_len=64, max_rows=64)
+    for m in (one, many):
+        for t in c[:8]:
+            m.step([2], [t])
+        for t in a[:6]:
+            m.step([0], [t])
+    last = {}
+    for t in a[6:]:
+        last[0] = one.step([0], [t])[1][0].clone()
+    for t in b:
+        last[1] = one.step([1], [t])[1][0].clone()
+    last[2] = one.step([2], [c[8]])[1][0].clone()
+    seqs = [0] * 15 + [1] * 13 + [2]
+    pos = list(range(6, 21)) + list(range(13)) + [8]
+    nxt, logits = many.step_rows(seqs, a[6:] + b + [c[8]], pos, want_rows=[14, 27, 28])
+    torch.cuda.synchronize()
+    _lib.raise_on_status()
+    assert logits.shape[0] == 3 and many.positions == one.positions == [21, 13, 9]
+    for k in range(3):
+        scale = float(last[k].abs().max())
+        assert float((logits[k] - last[k]).abs().max()) <= 0.03 * scale
+        top2 = last[k].topk(2).values
+        if float(top2[0] - top2[1]) > 0.1 * scale:
+            assert int(nxt[k]) == int(last[k].argmax())
+    for layer in range(cfg.n_layers):
+        assert torch.allclose(many.tables[layer].float(), one.tables[layer].float(), atol=0.03, rtol=0.03)
+    assert torch.allclose(many.iplane[1].float(), one.iplane[1].float(), atol=0.03, rtol=0.03)
+    assert float(many.tables[1][0, 64:64 + 5].abs().max()) > 0 and float(many.iplane[1][1, :3].abs().max()) > 0
+
+
 def test_v4_decode_with_qat_steps_on_the_kernels():
     """QAT checkpoints: the rows the kernels read are the quantised ones (FP8 window / compressed rows, FP4
     indexer plane), batched and one-at-a-time decoding agree, and the stream follows the oracle's wherever the
