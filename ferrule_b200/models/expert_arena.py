@@ -89,17 +89,19 @@ class _LayerArena:
 
 class ExpertArena:
     def __init__(self, weights: ModelWeights, resident_fraction: float = 0.5, min_frames: int = 0,
-                 replace_weights: bool = True):
+                 replace_weights: bool = True, mtp_resident: bool = True):
         """Moves the routed experts of every MoE layer of `weights` to pinned host memory and replaces the
         layer's expert tensors by arena frames (in place: `weights` is the streaming model afterwards).
         `replace_weights=False` keeps the model's tensors (the fp32 oracle reads them directly) and runs the
-        residency protocol beside it."""
+        residency protocol beside it.  `mtp_resident`: the proposal stages keep all their experts on the device
+        (one stage is 1 / n_layers of the expert bytes): drafting runs between transactions, where nothing can
+        park and wait for an upload, so with streamed proposal experts every draft would upload inline."""
         self.device = weights.embed.device
         self.cuda = self.device.type == "cuda"
         self.layers: Dict[int, _LayerArena] = {}
         self.stats = ArenaStats()
         self.upload_stream = torch.cuda.Stream(device=self.device) if self.cuda else None
-        all_layers = list(weights.layers) + [m.layer for m in weights.mtp]
+        all_layers = list(weights.layers) + ([] if mtp_resident else [m.layer for m in weights.mtp])
         for i, lw in enumerate(all_layers):
             if not lw.is_moe or lw.e_w13 is None:
                 continue

@@ -287,6 +287,8 @@ class DeepSeekRunner(ModelRunner):
         are taken in waves of at most `frames`; a wave with a missing expert parks the transaction, finished waves
         are remembered per transaction and give their frames back."""
         from .expert_async import NeedExperts
+        if layer not in self.arena.layers:
+            return                      # a layer whose experts are all resident (the proposal stage)
         frames = self.arena.frames(layer)
         held = self._lease_sink.setdefault(layer, {})
         if len(experts) <= frames:
@@ -397,8 +399,9 @@ class DeepSeekRunner(ModelRunner):
         out = [Proposal([], []) for _ in slots]
         if not self.mtp_enabled or max_draft < 1:
             return out
-        if self.async_streaming:
-            # drafting runs outside a transaction and cannot park: its experts are uploaded inline
+        if self.async_streaming and any(l >= self.cfg.n_layers for l in self.arena.layers):
+            # the arena also streams the proposal stage (`mtp_resident=False`): drafting runs outside a transaction
+            # and cannot park, so its experts are uploaded inline
             saved = (getattr(self.fwd, "async_stream", False), getattr(self.fwd, "expert_gate", None))
             if self.is_cuda:
                 self.fwd.async_stream = False

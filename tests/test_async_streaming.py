@@ -66,3 +66,32 @@ def test_async_streaming_parks_and_resumes_on_gpu(residency):
     _check("cuda", residency)
     from ferrule_b200.ops import _lib
     assert _lib.read_status()[0] == 0
+
+
+def test_speculative_decoding_with_streamed_experts_drafts_on_resident_proposal_experts_on_cpu():
+    """The proposal stage's experts stay on the device (drafting runs between transactions, where nothing can park
+    for an upload): with asynchronous streaming and speculative decoding together no `ensure` call - the inline
+    upload path - ever runs, and the stream is the resident, non-speculative model's."""
+    cfg = C.tiny_fixture().with_(n_mtp_layers=1)
+    g = torch.Generator().manual_seed(6)
+    prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (7, 11)]
+    want = _run(_engine(W.random_weights(cfg, device="cpu", dtype=torch.float32, seed=2), "cpu")[0], prompts, 8)
+    w = W.random_weights(cfg, device="cpu", dtype=torch.float32, seed=2)
+    runner = DeepSeekRunner(w, n_pages=48, page_size=16, max_rows=64, max_seqs=4, max_seq_len=256, device="cpu",
+                            enable_mtp=True, expert_residency=0.5, async_streaming=True)
+    sched = SchedulerConfig(max_active_sequences=4, max_decode_batch=4, max_batch_tokens=32, prefill_chunk_size=8,
+                            ctx_size=256)
+    eng = Engine(runner, EngineConfig(scheduler=sched, kv_pages=48, page_size=16, speculative=True, max_draft=1,
+                                      confidence_threshold=0.0), registry=runner.make_registry())
+    got = _run(eng, prompts, 8)
+    assert got == want
+    assert all(layer < cfg.n_layers for layer in runner.arena.layers), "the proposal stage is not in the arena"
+    assert runner.stats.mtp_proposals > 0 and eng.spec.metrics.drafted > 0
+    assert runner.arena.stats.ensure_calls == 0, "nothing was uploaded inline"
+    assert eng.stats.waits > 0 and runner.arena.stats.uploads > 0
+    for la in runner.arena.layers.values():
+        assert all(s.leases == 0 for s in la.coord.slots)
+    # a proposal stage inside the arena (the old arrangement) still works: its experts stream inline while drafting
+    from ferrule_b200.models.expert_arena import ExpertArena
+    w2 = W.random_weights(cfg, device="cpu", dtype=torch.float32, seed=2)
+    assert cfg.n_layers in ExpertArena(w2, 0.5, replace_weights=False, mtp_resident=False).layers
