@@ -35,6 +35,10 @@ def _add_model_args(p: argparse.ArgumentParser) -> None:
     p.add_argument("--max-batch-tokens", type=int, default=2048)
     p.add_argument("--prefill-chunk", type=int, default=512)
     p.add_argument("--speculative", action="store_true")
+    p.add_argument("--expert-plan", help="JSON written by plan-placement: renumber the routed experts (random-init "
+                                         "presets; every rank of a multi-rank launch must get the same file)")
+    p.add_argument("--router-zipf", type=float, default=0.0,
+                   help="random-init presets: skewed expert popularity (Zipf exponent) instead of a uniform router")
     p.add_argument("--prefix-cache-tokens", type=int, default=0,
                    help="keep the KV pages of finished prompts (whole 512-token blocks, this many tokens in total) "
                         "and fork them for later prompts that start with the same tokens; 0 = off")
@@ -111,7 +115,8 @@ def build_engine(args, layout=None):
                                    seed=args.seed, fast_device_init=dev != "cpu", tp_rank=tp_rank, tp_world=tp_world,
                                    weight_format=getattr(args, "weight_format", "bf16"),
                                    layer_range=stage_range(cfg.n_layers, layout.pp_rank, layout.pp_size)
-                                   if (staged and dev != "cpu") else None)
+                                   if (staged and dev != "cpu") else None,
+                                   router_zipf=getattr(args, "router_zipf", 0.0), expert_orders=_expert_plan(args))
         if staged:
             weights = stage_weights(weights, layout.pp_rank, layout.pp_size)
         name = cfg.name
@@ -146,6 +151,16 @@ def _is_v4_dir(model_dir: str) -> bool:
             return json.load(f).get("model_type") == "deepseek_v4"
     except OSError:
         return False
+
+
+def _expert_plan(args):
+    """{layer: order} from the file `--expert-plan` names (the `plan` of a plan-placement report)."""
+    path = getattr(args, "expert_plan", None)
+    if not path:
+        return None
+    with open(path) as f:
+        doc = json.load(f)
+    return {int(l): [int(e) for e in o] for l, o in doc.get("plan", doc).items()}
 
 
 def _build_v4_engine(args, dev, model_dir: Optional[str] = None):
@@ -378,6 +393,45 @@ def cmd_generate(args) -> int:
     print(json.dumps({"model": name, "prompt_tokens": len(prompt), "tokens": toks.get("gen", []), "text": f.text,
                       "finish_reason": f.reason.openai(), "seconds": round(dt, 4), "ttft_s": round(f.ttft_s, 4),
                       "tpot_s": round(f.tpot_s, 6)}))
+    return 0
+
+
+def cmd_plan_placement(args) -> int:
+    """Count the routes of a calibration workload and print the expert placement that evens the ranks' loads
+    (`parallel/placement.py`); `--expert-plan FILE` of the model commands applies it."""
+    import torch
+
+    from ..parallel.placement import RouteCounter, imbalance
+    from ..runtime.session import GenerateRequest
+    eng, _, name = build_engine(args)
+    runner = eng.runner
+    cfg = getattr(runner, "cfg", None)
+    if cfg is None or not getattr(cfg, "n_routed_experts", 0) or not hasattr(runner.fwd, "route_observer"):
+        raise SystemExit("plan-placement: this model has no routed experts to place")
+    # the observer reads every layer's expert ids on the host: calibration steps run eagerly
+    runner.use_graphs = False
+    runner.lookahead = False
+    counter = RouteCounter(cfg.n_layers, cfg.n_routed_experts).attach(runner.fwd)
+    g = torch.Generator().manual_seed(args.seed)
+    for i in range(args.requests):
+        ids = torch.randint(0, runner.vocab_size, (args.prompt_tokens,), generator=g).tolist()
+        eng.submit(GenerateRequest(f"cal{i}", ids, max_new_tokens=args.max_tokens, ignore_eos=True))
+    _collect(eng)
+    RouteCounter.detach(runner.fwd)
+    counts = counter.telemetry.counts
+    plan = counter.plan(args.ranks, n_groups=cfg.n_groups if cfg.topk_groups < cfg.n_groups else 1, min_gain=args.min_gain)
+    ident = list(range(cfg.n_routed_experts))
+    report = {"model": name, "ranks": args.ranks, "routes": int(sum(sum(r) for r in counts)),
+              "layers": {str(l): {"imbalance_by_id": round(imbalance(counts[l], ident, args.ranks), 4),
+                                  "imbalance_planned": round(imbalance(counts[l], plan.get(l, ident), args.ranks), 4)}
+                         for l in range(cfg.n_layers) if sum(counts[l])},
+              "plan": {str(l): o for l, o in plan.items()}}
+    if args.out:
+        with open(args.out, "w") as f:
+            json.dump(report, f)
+        report = {k: v for k, v in report.items() if k != "plan"}
+        report["written"] = args.out
+    print(json.dumps(report))
     return 0
 
 
@@ -634,6 +688,12 @@ def main(argv: Optional[List[str]] = None) -> int:
     p = sub.add_parser("generate"); _add_model_args(p)
     p.add_argument("--prompt", default="hello"); p.add_argument("--tokens"); p.add_argument("--max-tokens", type=int, default=16)
     p.add_argument("--ignore-eos", action="store_true"); p.set_defaults(fn=cmd_generate)
+    p = sub.add_parser("plan-placement"); _add_model_args(p)
+    p.add_argument("--ranks", type=int, required=True, help="ranks the experts will be sharded over")
+    p.add_argument("--requests", type=int, default=8); p.add_argument("--prompt-tokens", type=int, default=64)
+    p.add_argument("--max-tokens", type=int, default=16); p.add_argument("--min-gain", type=float, default=0.02)
+    p.add_argument("--out", help="write the report (with the plan) to this JSON file")
+    p.set_defaults(fn=cmd_plan_placement)
     p = sub.add_parser("chat"); _add_model_args(p); p.add_argument("--max-tokens", type=int, default=128)
     p.set_defaults(fn=cmd_chat)
     p = sub.add_parser("serve"); _add_model_args(p)

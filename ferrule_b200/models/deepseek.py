@@ -97,6 +97,7 @@ class ReferenceForward:
         self.w, self.cfg, self.pool = weights, weights.cfg, pool
         self.rnd = ref.bf16_round if emulate_bf16 else (lambda t: t)
         self.expert_gate = None        # callable(layer, local experts) used by the asynchronous expert streaming
+        self.route_observer = None     # callable(layer, expert ids [T, k], T): route statistics (parallel/placement.py)
         self._layer_index = -1
         cfg = self.cfg
         dev = weights.embed.device
@@ -160,6 +161,8 @@ class ReferenceForward:
                              route_scale=cfg.route_scale, hash_table=lw.hash_table, token_ids=token_ids)
         I = cfg.moe_inter
         out = torch.zeros_like(xn)
+        if self.route_observer is not None:
+            self.route_observer(self._layer_index, idx, xn.shape[0])
         if self.expert_gate is not None:
             # streamed experts: the gate raises when the batch routes to experts that are not resident
             local = idx[(idx >= self.w.e_lo) & (idx < self.w.e_hi)] - self.w.e_lo
@@ -423,6 +426,9 @@ class CudaForward:
         # (6.75 ms without, 6.97 ms with 48 MB): off by default
         self.l2_prefetch_bytes = int(float(os.environ.get("FERRULE_L2_PREFETCH_MB", "0")) * (1 << 20))
         self.telemetry = None      # utils.telemetry.ExpertTelemetry fed by the streamed path
+        # callable(layer, expert ids [T, k] on the device, T): route statistics for placement planning.  The observer
+        # reads the ids on the host, so a forward that has one is neither captured in a graph nor overlapped
+        self.route_observer = None
         self.static_moe = os.environ.get("FERRULE_STATIC_MOE", "1") != "0"
         self.fuse_next_norm = os.environ.get("FERRULE_FUSE_NORM", "1") != "0"
         # measured: folding the post-attention add + RMSNorm into the router kernel loses 10 us per layer, because the
@@ -1018,6 +1024,8 @@ class CudaForward:
             return self._moe_dispatch(lw, h_mid, b, T)
         if lw.is_moe:
             idx = self._moe_local(lw, xn, b, T, layer, norm=route_norm)
+            if self.route_observer is not None:
+                self.route_observer(layer, idx, T)
             # slot `topk` holds the shared-expert row (zeros when the model has none)
             if tp is None and next_norm is not None:
                 self._quantised.pop("xn", None)

@@ -21,7 +21,7 @@ from __future__ import annotations
 
 from dataclasses import dataclass, field
 import os
-from typing import Dict, List, Optional, Tuple
+from typing import Dict, List, Optional, Sequence, Tuple
 
 import torch
 
@@ -306,7 +306,8 @@ class _Init:
 
 
 def _layer_random(cfg: ModelConfig, layer: int, init: _Init, tp_rank: int, tp_world: int,
-                  force_moe: Optional[bool] = None, replicate_shared: bool = False) -> LayerWeights:
+                  force_moe: Optional[bool] = None, replicate_shared: bool = False,
+                  expert_order: Optional[Sequence[int]] = None) -> LayerWeights:
     H = cfg.hidden
     h_lo, h_hi = _shard_range(cfg.n_heads, tp_rank, tp_world)
     hl = h_hi - h_lo
@@ -353,15 +354,29 @@ def _layer_random(cfg: ModelConfig, layer: int, init: _Init, tp_rank: int, tp_wo
         g = torch.Generator().manual_seed(init.seed + 7919 * (layer + 1))
         lw.hash_table = torch.randint(0, E, (cfg.vocab_size, cfg.topk), generator=g).to(init.device)
     e_lo, e_hi = _shard_range(E, tp_rank, tp_world)
-    # experts are drawn one by one so only the local ones are ever materialised
+    # experts are drawn one by one so only the local ones are ever materialised.  `expert_order` (a placement plan,
+    # parallel/placement.py): physical id j holds original expert order[j] - the router rows, the bias and the
+    # hash table are renumbered, and each expert keeps the draws of its original id
+    order = list(range(E)) if expert_order is None else list(expert_order)
+    if expert_order is not None:
+        if sorted(order) != list(range(E)):
+            raise ValueError("expert_order is not a permutation of the layer's experts")
+        idx = torch.tensor(order, dtype=torch.int64, device=lw.router_w.device)
+        lw.router_w = lw.router_w[idx].contiguous()
+        if lw.router_bias is not None:
+            lw.router_bias = lw.router_bias[idx].contiguous()
+        if lw.hash_table is not None:
+            inv = torch.empty(E, dtype=torch.int64, device=lw.hash_table.device)
+            inv[idx.to(lw.hash_table.device)] = torch.arange(E, device=lw.hash_table.device)
+            lw.hash_table = inv[lw.hash_table.long()]
     w13s, w2s = [], []
-    for e in range(E):
-        if e_lo <= e < e_hi:
-            gate, up, down = init.normal(I, H), init.normal(I, H), init.normal(H, I)
-            w13s.append(torch.cat([gate, up], dim=0))
-            w2s.append(down)
-        else:
-            init.counter += 3
+    base = init.counter
+    for j in range(e_lo, e_hi):
+        init.counter = base + 3 * order[j]
+        gate, up, down = init.normal(I, H), init.normal(I, H), init.normal(H, I)
+        w13s.append(torch.cat([gate, up], dim=0))
+        w2s.append(down)
+    init.counter = base + 3 * E
     lw.e_w13 = torch.stack(w13s).contiguous()
     lw.e_w2 = torch.stack(w2s).contiguous()
     if cfg.n_shared_experts:
@@ -373,7 +388,8 @@ def _layer_random(cfg: ModelConfig, layer: int, init: _Init, tp_rank: int, tp_wo
 def random_weights(cfg: ModelConfig, device="cpu", dtype=torch.bfloat16, seed: int = 0, std: float = 0.02,
                    tp_rank: int = 0, tp_world: int = 1, fast_device_init: bool = False,
                    weight_format: str = "bf16", replicate_shared: bool = False,
-                   layer_range: Optional[Tuple[int, int]] = None, router_zipf: float = 0.0) -> ModelWeights:
+                   layer_range: Optional[Tuple[int, int]] = None, router_zipf: float = 0.0,
+                   expert_orders: Optional[dict] = None) -> ModelWeights:
     """Random-init weights N(0, std), norms = 1.
 
     fast_device_init draws on the GPU (much faster for multi-GB models; values then differ
@@ -384,14 +400,18 @@ def random_weights(cfg: ModelConfig, device="cpu", dtype=torch.bfloat16, seed: i
     layer_range (lo, hi): build only these layers (a pipeline stage of a model whose whole image does not fit one
     GPU); the other entries of `layers` are None and the draws differ from the full image's, so it needs
     fast_device_init.
+    expert_orders {layer: order}: a placement plan (`parallel.placement.plan_expert_placement`): the layer's experts
+    are renumbered so that physical id j is original expert order[j] - the same function, other owners.
     """
+    orders = expert_orders or {}
     if layer_range is not None and not fast_device_init:
         raise ValueError("layer_range skips draws: use it with fast_device_init only")
     init = _Init(seed, std, device, dtype, fast_device_init)
     embed = init.normal(cfg.vocab_size, cfg.hidden)
     lo_l, hi_l = layer_range if layer_range is not None else (0, cfg.n_layers)
     # quantise layer by layer so that at most one layer exists in bf16 at a time
-    layers = [quantize_layer_(_layer_random(cfg, i, init, tp_rank, tp_world, replicate_shared=replicate_shared),
+    layers = [quantize_layer_(_layer_random(cfg, i, init, tp_rank, tp_world, replicate_shared=replicate_shared,
+                                            expert_order=orders.get(i)),
                               weight_format) if lo_l <= i < hi_l else None for i in range(cfg.n_layers)]
     v_lo, v_hi = _shard_range(cfg.vocab_size, tp_rank, tp_world)
     lm_head = init.normal(cfg.vocab_size, cfg.hidden)[v_lo:v_hi].contiguous()
@@ -412,8 +432,10 @@ def random_weights(cfg: ModelConfig, device="cpu", dtype=torch.bfloat16, seed: i
         for i, lw in enumerate(w.layers):
             if lw is not None and lw.is_moe and lw.router_w is not None:
                 lw.router_w = (lw.router_w.float() * (1.0 / (std * cfg.hidden ** 0.5))).to(lw.router_w.dtype)
-                lw.router_bias = zipf_router_bias(cfg.n_routed_experts, router_zipf, seed * 7919 + i,
-                                                  sigmoid=cfg.score_fn != 0).to(lw.router_w.device)
+                bias = zipf_router_bias(cfg.n_routed_experts, router_zipf, seed * 7919 + i, sigmoid=cfg.score_fn != 0)
+                if i in orders:
+                    bias = bias[torch.tensor(list(orders[i]), dtype=torch.int64)]     # popularity follows the expert
+                lw.router_bias = bias.to(lw.router_w.device)
     return w
 
 
