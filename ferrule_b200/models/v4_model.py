@@ -558,7 +558,9 @@ class V4Cuda:
         tok_t = torch.tensor(tokens, dtype=torch.int32, device=dev)
         emb = K.embedding(tok_t, w.embed)
         state = emb[:, None, :].expand(B, hc, H).contiguous()
-        taps = []
+        taps = None
+        if self.proposal is not None:
+            taps = torch.empty(B, len(cfg.proposal_target_layers) * H, dtype=torch.bfloat16, device=dev)
         for i, lw in enumerate(w.layers):
             x, coeff = K4.hc_pre(state, lw.hc_attn_fn, lw.hc_attn_scale, lw.hc_attn_base, cfg.hc)
             xn = self._norm(x, lw.attn_norm)
@@ -635,7 +637,7 @@ class V4Cuda:
             f = self._moe(lw, xn, tok_t, B)
             state = K4.hc_post(f, state, coeff)
             if self.proposal is not None and i in cfg.proposal_target_layers:
-                taps.append(self.proposal.tap(state))
+                K4.hc_mean_scatter(state, taps, cfg.proposal_target_layers.index(i))      # mean over the copies
         if self.proposal is not None:
             main_x = self.proposal.main_rows(taps)
             for s_, plane in enumerate(self.pctx):

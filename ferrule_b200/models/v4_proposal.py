@@ -93,9 +93,11 @@ class V4Proposal:
         """Input of a linear the checkpoint stores quantised (QAT checkpoints only)."""
         return v4.qat_linear_input(x) if self.cfg.qat else x
 
-    def main_rows(self, taps: Sequence[torch.Tensor]) -> torch.Tensor:
-        """taps: one [T, H] per target layer, in layer order -> projected + normalised rows [T, H]."""
-        x = _lin(self._aq(torch.cat(list(taps), dim=-1)), self.p.main_proj)
+    def main_rows(self, taps) -> torch.Tensor:
+        """taps: one [T, H] per target layer, in layer order, or the concatenated [T, taps * H] rows (the kernel
+        path's tap kernel writes them side by side) -> projected + normalised rows [T, H]."""
+        cat = taps if isinstance(taps, torch.Tensor) else torch.cat(list(taps), dim=-1)
+        x = _lin(self._aq(cat), self.p.main_proj)
         return ref.bf16_round(ref.rmsnorm(x, self.p.main_norm, self.cfg.norm_eps))
 
     def context_kv(self, stage: int, main_x: torch.Tensor, positions: torch.Tensor) -> torch.Tensor:
@@ -175,8 +177,16 @@ class V4Proposal:
     def heads(self, hn: torch.Tensor, anchor: int) -> Tuple[List[int], List[float]]:
         """Markov chain over the block's LM-head logits + confidence logits -> (drafts, confidence)."""
         p = self.p
-        logits = hn.float() @ self.w.lm_head.float().T
-        drafts, _ = v4.markov_head(logits, p.markov_w1, p.markov_w2, anchor)
+        if hn.is_cuda:
+            # the chain runs on the device (one launch per draft, each reads its predecessor from device memory)
+            from ..ops import v4 as K4
+            logits = torch.nn.functional.linear(hn.to(torch.bfloat16), self.w.lm_head).float().contiguous()
+            ids, _ = K4.markov_head(logits, p.markov_w1, p.markov_w2,
+                                    torch.tensor([int(anchor)], dtype=torch.int32, device=hn.device))
+            drafts = [int(t) for t in ids.tolist()]
+        else:
+            logits = hn.float() @ self.w.lm_head.float().T
+            drafts, _ = v4.markov_head(logits, p.markov_w1, p.markov_w2, anchor)
         H = self.cfg.hidden
         cw = p.confidence_proj.float()[0]
         conf: List[float] = []

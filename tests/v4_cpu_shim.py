@@ -64,6 +64,12 @@ def _compressor_pool(kv, gate, ape, ratio, overlap, groups=None, row0=None, out=
     return v4.compressor_pool(kv[:end], gate[:end], ape, ratio, overlap, dim)[-1:].to(BF)
 
 
+def _hc_mean_scatter(state, taps, tap_index):
+    H = state.shape[2]
+    taps[:, tap_index * H:(tap_index + 1) * H] = v4.hc_mean_taps([state], state.shape[1]).to(taps.dtype)
+    return taps
+
+
 def _rope_rows(x, positions, cos, sin, off, rdim, inverse=False):
     p = positions.long()
     c, s = cos[p][:, None, :], sin[p][:, None, :]
@@ -141,7 +147,7 @@ def install(model):
     model.K = SimpleNamespace(gemm=_gemm, add_rmsnorm=_add_rmsnorm, argmax=_argmax, MoePlan=_Plan,
                               embedding=lambda tok, table: table[tok.long()], EPI_SWIGLU=EPI_SWIGLU, EPI_SCATTER=EPI_SCATTER)
     model.K4 = SimpleNamespace(hc_pre=_hc_pre, hc_post=_hc_post, compressor_pool=_compressor_pool, rope_rows=_rope_rows,
-                               indexer_scores=_indexer_scores, indexer_topk=_indexer_topk,
+                               indexer_scores=_indexer_scores, indexer_topk=_indexer_topk, hc_mean_scatter=_hc_mean_scatter,
                                sparse_sink_attention=_sparse_sink_attention)
     model.M = SimpleNamespace(window_index_fill=_window_index_fill, offset_index_fill=_offset_index_fill,
                               count_index_fill=_count_index_fill)
