@@ -16,8 +16,10 @@ This is not an autoregressive MTP stack.  Two halves:
 
 The target then verifies `1 + gamma` rows (the anchor and the drafts) in one provisional batch.
 
-Everything here is written with PyTorch tensor operations that run on either device: the block is `gamma`
-rows of one sequence, far below the size where the tensor-core kernels of the decode step pay.
+The block is `gamma` rows of one sequence, far below the size where the tensor-core GEMMs of the decode step
+pay: linears, norms, RoPE and the hyper-connection mixes are PyTorch tensor operations that run on either
+device; on the GPU the block attention is the decode step's selection-mode attention kernel and the Markov chain
+is the device kernel.
 
 Counterpart of crates/ferrule-model/src/models/deepseek_v4/proposal_attachment.rs:57-181 (stages, heads,
 row protocol), cuda_cache.rs:2002-2125 (taps, main projection, head), :2178-2400 (block attention over
@@ -123,7 +125,13 @@ class V4Proposal:
             kv = v4.qat_kv_rows(kv, rd)
         table = torch.cat([ctx.float(), kv], dim=0)             # context window rows, then the whole block
         sel = torch.arange(table.shape[0], dtype=torch.int32, device=xn.device)[None].expand(G, -1)
-        o = rnd(v4.sparse_sink_attention(q, table, sel, hd, cfg.softmax_scale, sink=lw.sink))
+        if xn.is_cuda:
+            # the selection-mode attention kernel of the decode step: every block row selects the whole table
+            from ..ops import v4 as K4
+            o = K4.sparse_sink_attention(q.to(torch.bfloat16).contiguous(), table.to(torch.bfloat16).contiguous(),
+                                         sel.contiguous(), hd, 0, cfg.softmax_scale, sink=lw.sink).float()
+        else:
+            o = rnd(v4.sparse_sink_attention(q, table, sel, hd, cfg.softmax_scale, sink=lw.sink))
         o = rnd(_rope_rows(o, self.rope[0], self.rope[1], positions, rd, inverse=True))
         og = o.reshape(G, cfg.o_groups, cfg.group_in)
         lat = rnd(torch.einsum("tgk,gnk->tgn", og, lw.wo_a.float())).reshape(G, -1)
