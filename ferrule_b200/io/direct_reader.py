@@ -8,7 +8,7 @@ from __future__ import annotations
 
 import ctypes as C
 import threading
-from typing import Callable, Dict, List, Optional
+from typing import Callable, Dict
 
 import torch
 

@@ -16,7 +16,6 @@ in crates/ferrule-backend/native/cuda/implementations/portable/entrypoints.cu:63
 """
 from __future__ import annotations
 
-import math
 from typing import Tuple
 
 import torch

@@ -13,9 +13,8 @@ from __future__ import annotations
 
 import json
 import math
-from dataclasses import asdict, dataclass, field, replace
+from dataclasses import asdict, dataclass, replace
 from pathlib import Path
-from typing import Optional
 
 SCORE_SOFTMAX, SCORE_SIGMOID, SCORE_SQRT_SOFTPLUS = 0, 1, 2
 _SCORE_NAMES = {"softmax": 0, "sigmoid": 1, "sqrtsoftplus": 2, "sqrt_softplus": 2}

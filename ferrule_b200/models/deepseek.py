@@ -19,7 +19,7 @@ attention.rs:1194-1364 in the reference (whose V4-only extras live in `v4.py`).
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import List, Optional
+from typing import Optional
 
 import torch
 

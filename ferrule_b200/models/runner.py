@@ -23,7 +23,6 @@ from ..runtime.execution import (ExecutionBatch, ExecutionCapabilities, Executio
                                  KvPlaneDescriptor, LogitsKind, RowOutput)
 from ..runtime.runner import (Complete, EndIntent, EndStatus, ModelRunner, Proposal, Waiting,
                               predict_next_decode_batch, same_decode_batch)
-from .config import ModelConfig
 from .deepseek import CudaForward, DecodeGraph, DeviceBatch, KvPool, ReferenceForward
 from .weights import ModelWeights
 

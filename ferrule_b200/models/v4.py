@@ -22,7 +22,7 @@ compressor_kernel / indexer_kernel (portable/entrypoints.cu:912-1266, :1614-1840
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Optional, Tuple
+from typing import Optional
 
 import torch
 

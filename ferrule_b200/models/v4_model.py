@@ -19,8 +19,7 @@ crates/ferrule-model/src/families/deepseek_v4.rs:9-38.
 """
 from __future__ import annotations
 
-import math
-from dataclasses import dataclass, field, replace
+from dataclasses import dataclass, replace
 from typing import Dict, List, Optional, Tuple
 
 import torch

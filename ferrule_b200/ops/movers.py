@@ -10,7 +10,7 @@ from typing import Optional
 
 import torch
 
-from ._lib import check, get_lib, ptr, status_tensor, stream_ptr
+from ._lib import check, get_lib, status_tensor, stream_ptr
 
 
 def fill_(t: torch.Tensor, value: int = 0) -> torch.Tensor:

@@ -7,7 +7,7 @@ import torch
 
 import ctypes as C
 
-from ._lib import check, get_lib, ptr, status_tensor, stream_ptr
+from ._lib import check, get_lib, status_tensor, stream_ptr
 
 
 def quant_fp8_rows(x: torch.Tensor, writeback: bool = False,

@@ -19,14 +19,13 @@ parallelism plan; docs/ROADMAP.md:34-41 lists distributed execution as future wo
 """
 from __future__ import annotations
 
-import ctypes as C
 from typing import Optional
 
 import torch
 import torch.distributed as dist
 
 from ..ops import kernels as K
-from ..ops._lib import check, get_lib, ptr, status_tensor, stream_ptr
+from ..ops._lib import check, get_lib, status_tensor, stream_ptr
 from .symm import Channel
 
 

@@ -31,7 +31,7 @@ from .execution import (ExecutionBatch, ExecutionOutput, Intent, LogitsRequest, 
 from .kv_pages import KvPageManager, KvRetirement, OutOfPages
 from .resources import Grant, PhysicalResourceBroker, ResourceKind
 from .runner import Complete, EndIntent, EndStatus, ModelRunner, Waiting
-from .scheduler import (Cancel, DecodeBatch, Execute, Finish, PrefillChunk, ResidentScheduler, SchedulerConfig)
+from .scheduler import Cancel, DecodeBatch, Finish, PrefillChunk, ResidentScheduler, SchedulerConfig
 from .session import FinishReason, GenerateRequest, SeqStatus, SequenceState
 
 

@@ -9,7 +9,7 @@ crates/ferrule-model/src/moe/prediction.rs:14-110, :251-520 and moe/telemetry.rs
 from __future__ import annotations
 
 from collections import defaultdict
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import Dict, Iterable, List, Set
 
 

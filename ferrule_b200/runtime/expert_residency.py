@@ -13,7 +13,7 @@ Counterpart of crates/ferrule-common/src/expert_residency.rs:247-294 (control tr
 """
 from __future__ import annotations
 
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from enum import Enum
 from typing import Dict, List, Optional, Tuple
 

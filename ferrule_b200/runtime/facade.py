@@ -20,7 +20,7 @@ import threading
 from typing import Callable, Dict, List, Optional, Sequence
 
 from ..utils.async_wake import CompletionHub
-from .execution import ExecutionBatch, ExecutionCapabilities, ExecutionOutput, KvLayoutSchema
+from .execution import ExecutionBatch, ExecutionCapabilities, KvLayoutSchema
 from .runner import Complete, EndIntent, EndStatus, ModelRunner, Proposal, Waiting
 
 

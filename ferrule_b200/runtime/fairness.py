@@ -12,9 +12,9 @@ Counterpart of crates/ferrule-runtime/src/io/fairness.rs:10-33 (bands/config), :
 from __future__ import annotations
 
 from collections import deque
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from enum import IntEnum
-from typing import Deque, Dict, Generic, List, Optional, Tuple, TypeVar
+from typing import Deque, Dict, Generic, Optional, Tuple, TypeVar
 
 T = TypeVar("T")
 

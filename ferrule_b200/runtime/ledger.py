@@ -11,9 +11,9 @@ Counterpart of crates/ferrule-runtime/src/io/ledger.rs:39-47 (phases), :99-115 (
 """
 from __future__ import annotations
 
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from enum import Enum
-from typing import Dict, Iterable, List, Optional, Tuple
+from typing import Dict, Iterable, List, Tuple
 
 
 class LedgerPhase(Enum):

@@ -19,7 +19,7 @@ crates/ferrule-model/src/materialization.rs:16-320 (boundary types).
 """
 from __future__ import annotations
 
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from enum import Enum
 from typing import Dict, FrozenSet, Iterable, List, Optional, Sequence, Tuple
 

@@ -12,7 +12,7 @@ fail_next_reserve / push_completion).
 from __future__ import annotations
 
 from collections import deque
-from dataclasses import dataclass, replace
+from dataclasses import replace
 from typing import Deque, Dict, List, Optional
 
 from .io_protocol import (CompletionEvent, CompletionOutcome, FailureReason, LoadStage, MaterializationKey,

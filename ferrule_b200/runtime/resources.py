@@ -10,7 +10,7 @@ Counterpart of crates/ferrule-runtime/src/scheduling/resources.rs:28-62 (kinds),
 """
 from __future__ import annotations
 
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from enum import Enum
 from typing import Dict, Optional
 

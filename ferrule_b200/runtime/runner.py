@@ -10,12 +10,12 @@ protocol), :249-468 (MultiSessionRunner), :556-592 (ResidentModelRunner).
 """
 from __future__ import annotations
 
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from enum import Enum
-from typing import Callable, Dict, Iterable, List, Optional, Sequence, Tuple
+from typing import Callable, Dict, List, Optional, Sequence, Tuple
 
 from .execution import (ExecutionBatch, ExecutionCapabilities, ExecutionOutput, Intent, KvLayoutSchema,
-                        KvPlaneDescriptor, LogitsKind, RowOutput, SequenceSlice)
+                        KvPlaneDescriptor, RowOutput, SequenceSlice)
 
 
 class EndIntent(Enum):

@@ -15,10 +15,10 @@ scheduling/actions.rs:25-60.
 from __future__ import annotations
 
 from collections import deque
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import Deque, Dict, List, Optional, Tuple, Union
 
-from .session import FinishReason, GenerateRequest, SeqStatus, SequenceState, SlotPool
+from .session import FinishReason, SeqStatus, SequenceState, SlotPool
 
 
 @dataclass

@@ -25,7 +25,6 @@ from typing import Dict, List, Optional, Sequence, Tuple
 
 from .execution import ExecutionBatch, Intent, LogitsRequest, Phase, SequenceSlice
 from .resources import ResourceKind
-from .runner import Complete, EndIntent
 from .session import FinishReason, SequenceState
 
 

@@ -22,7 +22,6 @@ from starlette.requests import Request
 from starlette.responses import JSONResponse, Response, StreamingResponse
 from starlette.routing import Route
 
-from ..runtime.session import FinishReason
 from ..utils.tokenizer import ChatTemplate, render_chat, template_for_model
 from . import openai as oa
 from .worker import ModelWorker, WorkerError

@@ -12,9 +12,8 @@ Counterpart of crates/ferrule-server/src/openai.rs:140-205, :237-356 (validation
 """
 from __future__ import annotations
 
-import time
 import uuid
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import Any, Dict, List, Optional, Tuple
 
 from ..runtime.session import FinishReason

@@ -18,7 +18,7 @@ import queue
 import threading
 import time
 import uuid
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import Any, Callable, Dict, List, Optional
 
 from ..runtime.engine import Engine, FinishEvent, TokenEvent

@@ -8,7 +8,7 @@ from __future__ import annotations
 from collections import OrderedDict
 from dataclasses import dataclass
 from enum import Enum
-from typing import Callable, Dict, Generic, Hashable, Iterator, List, Optional, Tuple, TypeVar
+from typing import Callable, Dict, Generic, Hashable, List, Optional, TypeVar
 
 
 class MemoryTopology(Enum):

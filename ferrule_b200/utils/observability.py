@@ -16,8 +16,7 @@ import json
 import logging
 import os
 import threading
-import time
-from dataclasses import asdict, dataclass, field
+from dataclasses import dataclass, field
 from typing import Dict, Optional
 
 REQUEST_LOG = logging.getLogger("ferrule_request")

@@ -10,10 +10,10 @@ Qwen, DeepSeek, Plain templates).
 """
 from __future__ import annotations
 
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from enum import Enum
 from pathlib import Path
-from typing import Dict, List, Optional, Sequence
+from typing import List, Sequence
 
 
 class ByteTokenizer:

@@ -3,7 +3,6 @@ order, speculation under page exhaustion, custody after every kind of ending.  M
 
 Cases follow the reference's driver suite (crates/ferrule-runtime/src/engine/driver.rs:5686-10737: waiting cohorts,
 pending endings, reverse completion order, zero-accept cycles, exhaustion)."""
-import pytest
 
 from ferrule_b200.runtime.engine import Engine, EngineConfig, FinishEvent, TokenEvent
 from ferrule_b200.runtime.io_protocol import MaterializationKey, ResourceId, ResourceKind

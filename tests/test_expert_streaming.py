@@ -11,7 +11,7 @@ from ferrule_b200.models import weights as W
 from ferrule_b200.runtime.expert_residency import ExpertResidencyController
 from ferrule_b200.runtime.expert_streaming import (ExpertArena, ExpertMaterializationProvider, ExpertSourceCatalog,
                                                    HostStagedExpertCache, PinnedSlabPool)
-from ferrule_b200.runtime.registry import LoadRegistry, OwnerKind
+from ferrule_b200.runtime.registry import LoadRegistry
 from ferrule_b200.utils.failpoints import FAILPOINTS
 
 

@@ -5,7 +5,7 @@ import pytest
 import torch
 
 from ferrule_b200.io import encoding as enc
-from ferrule_b200.io.checkpoint import export_hf, infer_weight_format, load_deepseek_hf, read_linear
+from ferrule_b200.io.checkpoint import export_hf, infer_weight_format, load_deepseek_hf
 from ferrule_b200.io.safetensors import CheckpointError, SafetensorsFile, ShardedCheckpoint, save_file
 from ferrule_b200.models import config as C
 from ferrule_b200.models import weights as W

@@ -569,7 +569,6 @@ def test_moe_reduce_norm_is_bit_equal_to_reduce_then_norm(K, T, k, H):
 def test_bounded_wait_reports_timeout_and_context_stays_usable():
     """Failure detection on the device: a wait on a flag that nothing sets gives up after its limit, records a
     status word (no trap, no hang) and later kernels still run."""
-    import ctypes as C
     from ferrule_b200.ops import _lib
     lib = _lib.get_lib(True)
     flag = torch.zeros(4, dtype=torch.int32, device="cuda")

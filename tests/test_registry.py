@@ -3,7 +3,7 @@ import pytest
 
 from ferrule_b200.runtime.fairness import Band, FairQueue, FairQueueConfig
 from ferrule_b200.runtime.io_protocol import (CompletionEvent, CompletionOutcome, IoProtocolError, LoadStage,
-                                              MaterializationKey, Purpose, ResourceId, ResourceKind, RetirementReason,
+                                              MaterializationKey, ResourceId, ResourceKind, RetirementReason,
                                               RetirementToken, can_transition, validate_transition)
 from ferrule_b200.runtime.ledger import CriticalPathLedger, LedgerPhase, union_length
 from ferrule_b200.runtime.provider import FakeMaterializationProvider

@@ -1,7 +1,6 @@
 """utils: tokenizer streaming, chat templates, LRU, completion hub, failpoints, metrics, families."""
 import asyncio
 import threading
-import time
 
 import pytest
 
@@ -10,7 +9,7 @@ from ferrule_b200.utils.async_wake import CompletionHub
 from ferrule_b200.utils.errors import ErrorKind, FerruleError, quant_type
 from ferrule_b200.utils.failpoints import FAILPOINTS, FailpointTriggered, OpCounters
 from ferrule_b200.utils.memory import MemoryPoolLimits, OwnerMemoryLru
-from ferrule_b200.utils.observability import METRICS, Metrics
+from ferrule_b200.utils.observability import Metrics
 from ferrule_b200.utils.tokenizer import (ByteTokenizer, ChatMessage, ChatTemplate, IncrementalDecodeState,
                                           render_chat, template_for_model)
 
