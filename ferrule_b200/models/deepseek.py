@@ -98,6 +98,8 @@ class ReferenceForward:
         self.rnd = ref.bf16_round if emulate_bf16 else (lambda t: t)
         self.expert_gate = None        # callable(layer, local experts) used by the asynchronous expert streaming
         self.route_observer = None     # callable(layer, expert ids [T, k], T): route statistics (parallel/placement.py)
+        self.prof = None               # utils.stage_profile.StageProfiler: per-layer stage table
+        self.tap = None                # utils.stage_profile.DebugTap: dumps of intermediate rows
         self._layer_index = -1
         cfg = self.cfg
         dev = weights.embed.device
@@ -184,20 +186,36 @@ class ReferenceForward:
         cfg, rnd = self.cfg, self.rnd
         T = h.shape[0]
         self._layer_index = layer
+        prof, tap = self.prof, self.tap
+        if prof is not None:
+            prof.mark(layer, "attn")
         xn = rnd(ref.rmsnorm(h, lw.attn_norm, cfg.rms_eps))
         a = self._attention(lw, layer, xn, b)
+        if prof is not None:
+            prof.mark(layer, "attn.reduce")
         if allreduce is not None:
             a = allreduce(a)
         else:
             a = rnd(a)
         h = rnd(h + a)
+        if tap is not None:
+            tap.write(layer, "attn_out", h)
+        if prof is not None:
+            prof.mark(layer, "moe" if lw.is_moe else "ffn")
         xn = rnd(ref.rmsnorm(h, lw.ffn_norm, cfg.rms_eps))
         f = self._moe(lw, xn, b.token_ids[:T]) if lw.is_moe else self._ffn(lw.w13, lw.w2, xn)
+        if prof is not None:
+            prof.mark(layer, "ffn.reduce")
         if allreduce is not None:
             f = allreduce(f)
         elif not lw.is_moe:
             f = rnd(f)
-        return rnd(h + f)
+        out = rnd(h + f)
+        if prof is not None:
+            prof.mark(layer, None)
+        if tap is not None:
+            tap.write(layer, "layer_out", out)
+        return out
 
     def embed_rows(self, b: DeviceBatch) -> torch.Tensor:
         return self.w.embed[b.token_ids[:b.n_rows].long()].float()
@@ -429,6 +447,10 @@ class CudaForward:
         # callable(layer, expert ids [T, k] on the device, T): route statistics for placement planning.  The observer
         # reads the ids on the host, so a forward that has one is neither captured in a graph nor overlapped
         self.route_observer = None
+        # utils.stage_profile: per-layer stage table (marks are CUDA events on the launching stream; a profiled
+        # forward is not captured in a graph) and dumps of intermediate rows
+        self.prof = None
+        self.tap = None
         self.static_moe = os.environ.get("FERRULE_STATIC_MOE", "1") != "0"
         self.fuse_next_norm = os.environ.get("FERRULE_FUSE_NORM", "1") != "0"
         # measured: folding the post-attention add + RMSNorm into the router kernel loses 10 us per layer, because the
@@ -547,6 +569,9 @@ class CudaForward:
         fold = self._folded.get(layer) if (T <= 4 * ws.decode_rows and not b.n_tc_tiles) else None
         if fold is not None:
             return self._attention_folded(lw, fold, layer, xn, b, T)
+        prof = self.prof
+        if prof is not None:
+            prof.mark(layer, "attn.qkv")
         qkv = ws.qkv[:T]
         self._gemm(xn, lw.w_qkv_a, qkv, slot="xn")
         if cfg.q_lora_rank:
@@ -557,6 +582,8 @@ class CudaForward:
             self._quantised.pop("a_mx", None)
         else:
             q, ckv = qkv[:, :hl * qhd], qkv[:, hl * qhd:]
+        if prof is not None:
+            prof.mark(layer, "attn.prep+absorb")
         q_full = ws.q_full[:T]
         # the cache write / RoPE kernel and the W_UK absorption GEMM both only read q (they fill disjoint columns
         # of q_full): decode-sized batches run them as parallel branches
@@ -573,6 +600,8 @@ class CudaForward:
         K.gemm(q, lw.w_uk_t, out=q_full.view(T, -1), x_group_koff=qhd, out_group_coff=lora + rope, k=nope)
         if fork:
             main.wait_stream(self.prep_stream)
+        if prof is not None:
+            prof.mark(layer, "attn.core")
         # verification batches (a few rows per decoding sequence) must take the same split path as plain
         # decode steps: equal split boundaries give bit-equal merges, hence the same greedy tokens
         cluster = ws.attn_splits in (2, 4, 8)       # splits merge through distributed shared memory
@@ -592,6 +621,8 @@ class CudaForward:
                             split_tokens=self.split_tokens if use_split else (1 << 30) // 64 * 64,
                             ws=ws.attn_ws if (use_split and not cluster) else None, sink=lw.attn_sink,
                             decode_only=b.decode_only)
+        if prof is not None:
+            prof.mark(layer, "attn.uv")
         K.gemm(ws.o_lat[:T].view(T, -1), lw.w_uv, out=ws.attn_out[:T], x_group_koff=lora, out_group_coff=vd)
         return ws.attn_out[:T], lw.w_o
 
@@ -991,9 +1022,14 @@ class CudaForward:
                 main.wait_stream(side)
         # `first_norm_done`: the previous layer's last kernel already wrote this layer's normalised input to xn;
         # `next_norm` (single GPU): this layer's last kernel does the same for the next one
+        prof = self.prof
+        if prof is not None:
+            prof.mark(layer, "attn.norm")
         if not first_norm_done:
             self._norm(h_in, lw.attn_norm, T, xn, "xn", self._qkind(lw.w_qkv_a))
         a, w_o = self._attention(lw, layer, xn, b, T)
+        if prof is not None:
+            prof.mark(layer, "attn.o_proj+norm")
         # what reads the post-attention norm: the dense FFN, or the shared experts and the static FP8 expert path
         ffn_q = self._qkind(lw.w13) or (self._qkind(lw.e_w13) if lw.is_moe else None)
         # decode-sized MoE layers: the post-attention residual add + RMSNorm runs in the router kernel's prologue
@@ -1019,13 +1055,22 @@ class CudaForward:
             elif not use_ep:
                 self._norm(h_out, lw.ffn_norm, T, xn, "xn", ffn_q)
             h_mid = h_out
+        if prof is not None:
+            prof.mark(layer, "moe" if lw.is_moe else "ffn")
+        if self.tap is not None and self.tap.wants(layer, "attn_out"):
+            self.tap.write(layer, "attn_out", h_mid)
         if use_ep:
             # the layer's result is the gathered tensor itself (symmetric memory the peers' combine kernels wrote)
-            return self._moe_dispatch(lw, h_mid, b, T)
+            out = self._moe_dispatch(lw, h_mid, b, T)
+            if prof is not None:
+                prof.mark(layer, None)
+            return out
         if lw.is_moe:
             idx = self._moe_local(lw, xn, b, T, layer, norm=route_norm)
             if self.route_observer is not None:
                 self.route_observer(layer, idx, T)
+            if prof is not None:
+                prof.mark(layer, "moe.reduce")
             # slot `topk` holds the shared-expert row (zeros when the model has none)
             if tp is None and next_norm is not None:
                 self._quantised.pop("xn", None)
@@ -1086,6 +1131,10 @@ class CudaForward:
                 if hasattr(exc, "missing"):
                     exc.hidden = h.clone()      # the layer's input rows are intact: its last kernel writes them
                 raise
+            if self.tap is not None and self.tap.wants(i, "layer_out"):
+                self.tap.write(i, "layer_out", h)
+        if self.prof is not None:
+            self.prof.mark(len(layers), None)       # ends the last layer's open stage
         return h
 
     def hidden_states(self, b: DeviceBatch, T: int, start_layer: int = 0, h0=None) -> torch.Tensor:

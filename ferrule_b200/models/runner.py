@@ -11,6 +11,7 @@ cuda_cache.rs:3539-3700.
 """
 from __future__ import annotations
 
+import logging
 import os
 import time
 from dataclasses import dataclass
@@ -25,6 +26,8 @@ from ..runtime.runner import (Complete, EndIntent, EndStatus, ModelRunner, Propo
                               predict_next_decode_batch, same_decode_batch)
 from .deepseek import CudaForward, DecodeGraph, DeviceBatch, KvPool, ReferenceForward
 from .weights import ModelWeights
+
+_PREFILL_LOG = logging.getLogger("ferrule_prefill")
 
 
 class BatchStaging:
@@ -183,6 +186,14 @@ class DeepSeekRunner(ModelRunner):
             if self.async_streaming:
                 from .expert_async import ArenaProvider
                 self.provider = ArenaProvider(self.arena, self.cfg.name)
+        # profiling switches are read once, here: a stage table or a debug tap needs host callbacks between the
+        # kernels of a step, so such a runner steps eagerly
+        from ..utils.stage_profile import DebugTap, StageProfiler, prefill_progress_enabled
+        self.profiler = StageProfiler.from_env(self.device)
+        self.debug_tap = DebugTap.from_env()
+        self.prefill_progress = prefill_progress_enabled()
+        if self.profiler is not None or self.debug_tap is not None:
+            use_graphs = False
         self.use_graphs = use_graphs and self.is_cuda
         self.stats = RunnerStats()
         tc_heads = 0
@@ -235,6 +246,7 @@ class DeepSeekRunner(ModelRunner):
                 self.fwd.async_stream = True
             else:
                 self.fwd.expert_gate = self._expert_gate
+        self.fwd.prof, self.fwd.tap = self.profiler, self.debug_tap
 
     # ------------------------------------------------------------------ contract
     def capabilities(self) -> ExecutionCapabilities:
@@ -313,6 +325,12 @@ class DeepSeekRunner(ModelRunner):
         b = self.txns[txn_id]
         t0 = time.perf_counter_ns()
         start_layer, h0 = self._txn_resume.pop(txn_id, (0, None))
+        if self.debug_tap is not None:
+            self.debug_tap.next_step()
+        if self.prefill_progress:
+            for s in b.sequences:
+                if s.query_len > 1:
+                    _PREFILL_LOG.info("prefill slot=%d rows=%d done=%d", s.state_slot, s.query_len, s.sequence_len)
         if self.async_streaming:
             self._lease_sink = self._txn_leases.setdefault(txn_id, {})
             self._wave_state = self._txn_waves.setdefault(txn_id, {})
@@ -643,4 +661,9 @@ class DeepSeekRunner(ModelRunner):
         if self.arena is not None:
             d["expert_arena"] = dict(vars(self.arena.stats))
             d["expert_telemetry"] = self.fwd.telemetry.snapshot()
+        if self.profiler is not None:
+            d["stage_table"] = self.profiler.by_stage()
+            d["stage_table_layers"] = self.profiler.table()
+        if self.debug_tap is not None:
+            d["debug_tap_files"] = len(self.debug_tap.written)
         return d

@@ -300,6 +300,7 @@ class V4Reference:
         if w.proposal is not None:
             from .v4_proposal import V4Proposal
             self.proposal = V4Proposal(w, self.rope)
+        self.prof = None               # utils.stage_profile.StageProfiler
 
     def propose(self, c: V4SeqCache, n_committed: int, anchor: int):
         """Drafts after `anchor` for a sequence with `n_committed` committed tokens -> (token ids, confidence logits)."""
@@ -400,12 +401,17 @@ class V4Reference:
         pos = c.position
         state = w.embed[token].float()[None, None].repeat(1, cfg.hc_mult, 1)            # [1, hc, H]
         taps = []
+        prof = self.prof
         for i, lw in enumerate(w.layers):
+            if prof is not None:
+                prof.mark(i, "attn")
             x, (_, post, comb) = v4.hc_pre(state, lw.hc_attn_fn, lw.hc_attn_scale, lw.hc_attn_base, cfg.hc)
             x = rnd(x)
             xn = rnd(ref.rmsnorm(x, lw.attn_norm, cfg.norm_eps))[0]
             a = self._attention(lw, i, xn, c, pos)
             state = rnd(v4.hc_post(a[None], state, post, comb))
+            if prof is not None:
+                prof.mark(i, "moe")
             x, (_, post, comb) = v4.hc_pre(state, lw.hc_ffn_fn, lw.hc_ffn_scale, lw.hc_ffn_base, cfg.hc)
             x = rnd(x)
             xn = rnd(ref.rmsnorm(x, lw.ffn_norm, cfg.norm_eps))[0]
@@ -413,6 +419,8 @@ class V4Reference:
             state = rnd(v4.hc_post(f[None], state, post, comb))
             if self.proposal is not None and i in cfg.proposal_target_layers:
                 taps.append(self.proposal.tap(state))
+        if prof is not None:
+            prof.mark(cfg.n_layers, "head")
         if self.proposal is not None:
             # every target row leaves one context KV row per proposal stage at its position
             main_x = self.proposal.main_rows(taps)
@@ -423,7 +431,10 @@ class V4Reference:
         h = rnd(v4.hc_head(state, w.hc_head_fn, w.hc_head_scale, w.hc_head_base, cfg.hc))
         hn = rnd(ref.rmsnorm(h, w.final_norm, cfg.norm_eps))[0]
         c.position += 1
-        return hn @ w.lm_head.float().T
+        logits = hn @ w.lm_head.float().T
+        if prof is not None:
+            prof.mark(cfg.n_layers, None)
+        return logits
 
 
 class _OffsetRows:
@@ -483,6 +494,7 @@ class V4Cuda:
         self.positions = [0] * max_seqs
         self.launch_note = "decode: one token per sequence per step"
         # proposal attachment: one context KV plane per stage, addressed by (slot, position) like the other tables
+        self.prof = None               # utils.stage_profile.StageProfiler (marks are CUDA events)
         self.proposal = None
         self.pctx = []
         if w.proposal is not None:
@@ -560,7 +572,10 @@ class V4Cuda:
         taps = None
         if self.proposal is not None:
             taps = torch.empty(B, len(cfg.proposal_target_layers) * H, dtype=torch.bfloat16, device=dev)
+        prof = self.prof
         for i, lw in enumerate(w.layers):
+            if prof is not None:
+                prof.mark(i, "attn.proj")
             x, coeff = K4.hc_pre(state, lw.hc_attn_fn, lw.hc_attn_scale, lw.hc_attn_base, cfg.hc)
             xn = self._norm(x, lw.attn_norm)
             # ---- attention ----
@@ -577,6 +592,8 @@ class V4Cuda:
             K4.rope_rows(kv.view(B, 1, hd), pos_t, self.rope[0], self.rope[1], off=hd - rd, rdim=rd)
             if cfg.qat:
                 kv = v4.qat_kv_rows(kv, rd)
+            if prof is not None:
+                prof.mark(i, "attn.select")
             table = self.tables[i]
             table[seq_t, pos_t.long()] = kv
             ratio = cfg.ratio(i)
@@ -625,12 +642,18 @@ class V4Cuda:
                     else:
                         vis = torch.tensor(n_c, dtype=torch.int32, device=dev)
                         M.count_index_fill(selection, cfg.window, n_max, vis, base + self.max_len)
+            if prof is not None:
+                prof.mark(i, "attn.core")
             o = K4.sparse_sink_attention(q, table.view(-1, hd), selection, hd, 0, cfg.softmax_scale, sink=lw.sink)
+            if prof is not None:
+                prof.mark(i, "attn.out")
             K4.rope_rows(o, pos_t, self.rope[0], self.rope[1], off=hd - rd, rdim=rd, inverse=True)
             lat = K.gemm(o.view(B, nh * hd), lw.wo_a, x_group_koff=cfg.group_in, out_group_coff=cfg.o_lora_rank)
             a = K.gemm(aq(lat), lw.wo_b)
             state = K4.hc_post(a, state, coeff)
             # ---- MoE ----
+            if prof is not None:
+                prof.mark(i, "moe")
             x, coeff = K4.hc_pre(state, lw.hc_ffn_fn, lw.hc_ffn_scale, lw.hc_ffn_base, cfg.hc)
             xn = self._norm(x, lw.ffn_norm)
             f = self._moe(lw, xn, tok_t, B)
@@ -641,6 +664,8 @@ class V4Cuda:
             main_x = self.proposal.main_rows(taps)
             for s_, plane in enumerate(self.pctx):
                 plane[seq_t, pos_t.long()] = self.proposal.context_kv(s_, main_x, pos_t).to(plane.dtype)
+        if prof is not None:
+            prof.mark(cfg.n_layers, "head")
         for s, p in last.items():
             self.positions[s] = p + 1
         if want_rows is not None:
@@ -652,6 +677,8 @@ class V4Cuda:
         hn = self._norm(h, w.final_norm)
         logits = K.gemm(hn, w.lm_head, out_dtype=torch.float32)
         nxt = K.argmax(logits)
+        if prof is not None:
+            prof.mark(cfg.n_layers, None)
         return nxt, logits
 
     def _moe(self, lw: V4LayerWeights, xn: torch.Tensor, tok_t: torch.Tensor, B: int) -> torch.Tensor:

@@ -76,6 +76,8 @@ class V4Runner(ModelRunner):
         else:
             self.fwd = V4Reference(weights)
             self.caches: Dict[int, V4SeqCache] = {}
+        from ..utils.stage_profile import StageProfiler
+        self.profiler = self.fwd.prof = StageProfiler.from_env(self.device)      # read once, here
         self.txns: Dict[int, ExecutionBatch] = {}
         self.steps = 0
         self.forward_ns = 0
@@ -197,8 +199,12 @@ class V4Runner(ModelRunner):
             self.caches.pop(state_slot, None)
 
     def observability(self) -> Dict[str, object]:
-        return {"model": "deepseek-v4", "decode_steps": self.steps, "forward_ms": self.forward_ns / 1e6,
-                "proposal_blocks": self.proposal_blocks, "proposal_ms": self.proposal_ns / 1e6}
+        d = {"model": "deepseek-v4", "decode_steps": self.steps, "forward_ms": self.forward_ns / 1e6,
+             "proposal_blocks": self.proposal_blocks, "proposal_ms": self.proposal_ns / 1e6}
+        if self.profiler is not None:
+            d["stage_table"] = self.profiler.by_stage()
+            d["stage_table_layers"] = self.profiler.table()
+        return d
 
     # ------------------------------------------------------------------ execution
     @staticmethod
