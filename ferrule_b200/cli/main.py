@@ -436,27 +436,73 @@ def cmd_plan_placement(args) -> int:
 
 
 def cmd_chat(args) -> int:
+    """Interactive chat.  The conversation is one retained session: every turn feeds only its new text to the
+    model and continues from the cached history (runners that bind state to a request-long slot re-encode the
+    history instead).  /reset clears the session, /stats, /ctx and /experts report, /exit or an empty line ends.
+    Mirrors the reference's chat command (crates/ferrule-cli/src/commands/chat.rs:205-275)."""
     from ..runtime.session import GenerateRequest
     from ..utils.tokenizer import ChatMessage, render_chat, template_for_model
     eng, tok, name = build_engine(args)
     eng.detokenize = tok.decode
     history: List[ChatMessage] = []
     tmpl = template_for_model(name)
-    print(f"{name}: empty line or Ctrl-D to quit")
-    turn = 0
+    retained = bool(getattr(eng.runner, "supports_prefix_sharing", True))
+    session = "chat"
+    cached_text = ""                 # the rendered text whose tokens the session's cache holds
+    ctx = eng.cfg.scheduler.ctx_size
+    print(f"{name}: /reset /stats /ctx /experts /exit; empty line or Ctrl-D to quit")
+    turn = generated = 0
+
+    def position() -> int:
+        s = eng._sessions.get(session)
+        return s.position if s is not None else 0
+
     while True:
         try:
             line = input("> ")
         except EOFError:
             break
-        if not line.strip():
+        cmd = line.strip()
+        if not cmd or cmd in ("/exit", "/quit"):
             break
+        if cmd in ("/reset", "/clear"):
+            eng.reset_session(session)
+            history, cached_text, turn, generated = [], "", 0, 0
+            print("session reset.")
+            continue
+        if cmd == "/stats":
+            print(f"position={position()} generated={generated} turns={turn}")
+            continue
+        if cmd == "/ctx":
+            print(f"context {position()} / {ctx} tokens ({100.0 * position() / max(ctx, 1):.1f} %)")
+            continue
+        if cmd == "/experts":
+            obs = eng.runner.observability()
+            rep = {k: obs[k] for k in ("expert_arena", "expert_telemetry") if k in obs}
+            print(json.dumps(rep) if rep else "expert report not available.")
+            continue
         history.append(ChatMessage("user", line))
-        ids = [t % eng.runner.vocab_size for t in tok.encode(render_chat(history, tmpl))]
-        eng.submit(GenerateRequest(f"turn{turn}", ids, max_new_tokens=args.max_tokens))
+        full = render_chat(history, tmpl)
+        if retained and cached_text and full.startswith(cached_text):
+            new_text = full[len(cached_text):]
+        else:
+            if retained and cached_text:
+                eng.reset_session(session)       # the rendering no longer extends the cached text: start over
+            new_text = full
+        ids = [t % eng.runner.vocab_size for t in tok.encode(new_text)]
+        try:
+            eng.submit(GenerateRequest(f"turn{turn}", ids, max_new_tokens=args.max_tokens,
+                                       session_id=session if retained else None, retain_session=retained))
+        except ValueError as exc:
+            history.pop()
+            print(f"[{exc}] use /reset to start a new conversation")
+            continue
         _, fin = _collect(eng, lambda s: (sys.stdout.write(s), sys.stdout.flush()))
         print()
-        history.append(ChatMessage("assistant", fin[f"turn{turn}"].text))
+        f = fin[f"turn{turn}"]
+        history.append(ChatMessage("assistant", f.text))
+        cached_text = full + f.text
+        generated += f.generated_tokens
         turn += 1
     return 0
 

@@ -57,6 +57,8 @@ class V4Runner(ModelRunner):
     # the attention state lives in slot-bound tables, not in the pages the engine accounts: two sequences cannot
     # share a prefix by sharing pages (the engine's prompt-prefix cache and exact forks stay off for this runner)
     supports_prefix_sharing = False
+    # no captured step: the output head runs for the rows that ask for logits only
+    skip_unread_logits = True
 
     def __init__(self, weights: V4Weights, n_pages: int, page_size: int = 64, max_seqs: int = 8,
                  max_seq_len: int = 1024, max_rows: int = 2048, eos_token_id: int = -1,

@@ -140,6 +140,14 @@ class Engine:
         self.runner = runner
         self.last_error: Optional[BaseException] = None
         self.cfg = cfg or EngineConfig()
+        # limits the runner can never serve are refused here, before any request is taken: a full prompt chunk or a
+        # full decode cohort must fit one batch of the runner
+        caps, sc = runner.capabilities(), self.cfg.scheduler
+        if min(sc.prefill_chunk_size, sc.max_batch_tokens) > caps.max_batch_rows or sc.max_decode_batch > caps.max_batch_rows:
+            raise ValueError(f"scheduler limits (prompt chunk {sc.prefill_chunk_size}, batch tokens {sc.max_batch_tokens}, "
+                             f"decode batch {sc.max_decode_batch}) exceed the runner's {caps.max_batch_rows} rows per batch")
+        if sc.max_decode_batch > caps.max_sequences:
+            raise ValueError(f"decode batch of {sc.max_decode_batch} sequences exceeds the runner's {caps.max_sequences}")
         self.scheduler = ResidentScheduler(self.cfg.scheduler)
         self.kv = KvPageManager(self.cfg.kv_pages, self.cfg.page_size, self.cfg.scheduler.ctx_size + 8)
         self.broker = broker or PhysicalResourceBroker()
@@ -177,6 +185,8 @@ class Engine:
             raise RuntimeError("engine is shut down")
         if req.max_new_tokens < 0:
             raise ValueError("max_new_tokens must be >= 0")
+        if req.retain_session and not getattr(self.runner, "supports_prefix_sharing", True):
+            raise ValueError("this runner binds sequence state to a slot that ends with the request: sessions cannot be retained")
         prev = self._sessions.get(req.session_id) if req.session_id else None
         now = time.perf_counter_ns()
         # validate before anything is taken: a rejected continuation leaves its retained session intact
@@ -324,6 +334,18 @@ class Engine:
             raise ValueError("a fork needs at least one new prompt token")
         self.scheduler.submit(seq)
         return seq
+
+    def reset_session(self, session_id: str) -> bool:
+        """Drop a retained session: its pages go back, the next request under this id starts from nothing.
+        False when no session of that name is retained (a session inside a request is not retained yet)."""
+        seq = self._sessions.pop(session_id, None)
+        if seq is None:
+            return False
+        if seq.kv_seq >= 0:
+            self._retire(self.kv.free_sequence_pages(seq.kv_seq))
+            seq.kv_seq = -1
+        self._drive_retirements()
+        return True
 
     def preempt_session(self, request_id: str) -> None:
         seq = self.scheduler.active.get(request_id)
@@ -501,6 +523,7 @@ class Engine:
         seqs: List[SequenceSlice] = []
         block_ids: List[int] = []
         none, top1 = LogitsRequest.none(), LogitsRequest.topk(1)
+        skip_unread = bool(getattr(self.runner, "skip_unread_logits", False))
         for m in txn.members:
             seq = m.seq
             r, blocks, slots = self.kv.bind_and_bindings(m.res_id, txn.txn_id)
@@ -514,7 +537,10 @@ class Engine:
                 logits.append(top1 if last_chunk else none)
             else:
                 token_ids.append(seq.staged_token)
-                logits.append(top1)
+                # committing this token ends the request by its length: the logits after it would be discarded.
+                # Runners that replay a captured step compute every row anyway and keep the uniform request.
+                last = skip_unread and seq.generated + 1 >= seq.request.max_new_tokens
+                logits.append(none if last else top1)
             positions.extend(range(start, start + m.rows))
             write_slots.extend(slots)
             seqs.append(SequenceSlice(seq.slot, Phase.PREFILL if m.is_prefill else Phase.DECODE, m.query_start,
@@ -758,7 +784,10 @@ class Engine:
         if not self._outbox:
             return False
         while self._outbox:
-            emit(self._outbox.popleft())
+            # the event leaves the outbox only after the consumer took it: a consumer that raises gets the same
+            # committed event again on the next step, and nothing of the engine's own state depends on delivery
+            emit(self._outbox[0])
+            self._outbox.popleft()
         return True
 
     # ------------------------------------------------------------------ page retirement

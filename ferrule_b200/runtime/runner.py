@@ -53,6 +53,11 @@ class Proposal:
 class ModelRunner:
     """Interface; concrete runners override everything below."""
 
+    # True: the engine asks for no logits on a decode row whose token ends its request by length (nobody would
+    # read them).  Runners whose decode step is a captured graph compute every row in any case and leave it False,
+    # so that every decode batch keeps the one shape their graph and their look-ahead were built for.
+    skip_unread_logits = False
+
     vocab_size: int = 0
     eos_token_id: int = -1
 
@@ -155,8 +160,9 @@ class MockRunner(ModelRunner):
 
     def __init__(self, vocab: int = 1000, eos: int = -1, page_size: int = 16,
                  next_token_fn: Optional[Callable[[int, int], int]] = None, draft_len: int = 0,
-                 draft_accuracy: Optional[Callable[[int, int, int], int]] = None):
+                 draft_accuracy: Optional[Callable[[int, int, int], int]] = None, skip_unread_logits: bool = False):
         self.vocab_size, self.eos_token_id, self.page_size = vocab, eos, page_size
+        self.skip_unread_logits = skip_unread_logits
         self.next_token_fn = next_token_fn or (lambda tok, pos: (7 * tok + 3 * pos + 1) % vocab)
         self.txns: Dict[int, ExecutionBatch] = {}
         self.kv: Dict[int, Tuple[int, int]] = {}           # pool row -> (token, position)

@@ -62,3 +62,21 @@ def test_cli_golden_trace_parity_and_chunk_sweep(tmp_path):
                         *common))
     assert [r["prefill_chunk"] for r in sw["sweep"]] == [8, 32]
     assert sw["sweep"][0]["prefill_chunks"] > sw["sweep"][1]["prefill_chunks"]
+
+
+def test_chat_continues_one_retained_session_and_answers_the_slash_commands():
+    script = "\n".join(["hello there", "/stats", "/ctx", "and again", "/stats", "/experts", "/reset", "/stats", "fresh start",
+                        "/exit"]) + "\n"
+    p = subprocess.run([sys.executable, "-m", "ferrule_b200", "chat", "--preset", "tiny-fixture", "--device", "cpu",
+                        "--ctx-size", "256", "--max-seqs", "2", "--page-size", "16", "--max-tokens", "4"],
+                       input=script, capture_output=True, text=True, timeout=300)
+    assert p.returncode == 0, p.stderr[-2000:]
+    out = p.stdout
+    stats = [l for l in out.splitlines() if "position=" in l]
+    assert len(stats) == 3
+    pos = [int(l.split("position=")[1].split()[0]) for l in stats]
+    turns = [int(l.split("turns=")[1].split()[0]) for l in stats]
+    assert turns == [1, 2, 0] and 0 < pos[0] < pos[1] and pos[2] == 0, "the second turn extended the first; /reset emptied it"
+    assert "session reset." in out and "expert report not available." in out
+    ctx_line = next(l for l in out.splitlines() if l.startswith("> context") or "context " in l)
+    assert "/ 256 tokens" in ctx_line
