@@ -185,8 +185,6 @@ class Engine:
             raise RuntimeError("engine is shut down")
         if req.max_new_tokens < 0:
             raise ValueError("max_new_tokens must be >= 0")
-        if req.retain_session and not getattr(self.runner, "supports_prefix_sharing", True):
-            raise ValueError("this runner binds sequence state to a slot that ends with the request: sessions cannot be retained")
         prev = self._sessions.get(req.session_id) if req.session_id else None
         now = time.perf_counter_ns()
         # validate before anything is taken: a rejected continuation leaves its retained session intact
@@ -202,7 +200,8 @@ class Engine:
                                    f"sequence position is {prev.position}")
             del self._sessions[req.session_id]
             seq = SequenceState(req, kv_seq=prev.kv_seq, tokens=prev.tokens + list(req.prompt_tokens),
-                                position=prev.position, arrival_ns=now)
+                                position=prev.position, arrival_ns=now, held_slot=prev.held_slot)
+            prev.held_slot = -1
         else:
             hit = (self._prefix_lookup(req.prompt_tokens)
                    if (self.cfg.prefix_cache_tokens and not req.session_id
@@ -221,6 +220,7 @@ class Engine:
             self.scheduler.submit(seq)
         except Exception:
             if prev is not None:
+                prev.held_slot, seq.held_slot = seq.held_slot, -1
                 self._sessions[req.session_id] = prev
             else:
                 self._retire(self.kv.free_sequence_pages(seq.kv_seq))
@@ -341,11 +341,17 @@ class Engine:
         seq = self._sessions.pop(session_id, None)
         if seq is None:
             return False
+        self._drop_session(seq)
+        self._drive_retirements()
+        return True
+
+    def _drop_session(self, seq: SequenceState) -> None:
         if seq.kv_seq >= 0:
             self._retire(self.kv.free_sequence_pages(seq.kv_seq))
             seq.kv_seq = -1
-        self._drive_retirements()
-        return True
+        slot = self.scheduler.release_held(seq)
+        if slot >= 0:
+            self.runner.release_slot(slot)
 
     def preempt_session(self, request_id: str) -> None:
         seq = self.scheduler.active.get(request_id)
@@ -378,7 +384,7 @@ class Engine:
         idle = not (self._ending or self._waiting)
         if idle:
             for s in list(self._sessions.values()):
-                self._retire(self.kv.free_sequence_pages(s.kv_seq))
+                self._drop_session(s)
             self._sessions.clear()
             while self._prefix_evict():
                 pass
@@ -752,15 +758,22 @@ class Engine:
         self.scheduler.suspended.pop(seq.request_id, None)
         self._snapshots.pop(seq.request_id, None)
         slot = seq.slot                                   # the scheduler returns the slot to its pool and clears it
-        self.scheduler.finish(seq, reason)
-        self._release_sequence(seq, reason, slot)
+        # a runner whose sequence state lives in the slot (no page sharing): a retained session keeps its slot
+        keep_slot = (self._keeps_session(seq, reason) and slot >= 0
+                     and not getattr(self.runner, "supports_prefix_sharing", True))
+        self.scheduler.finish(seq, reason, keep_slot=keep_slot)
+        self._release_sequence(seq, reason, -1 if keep_slot else slot)
+
+    @staticmethod
+    def _keeps_session(seq: SequenceState, reason: FinishReason) -> bool:
+        return bool(seq.request.retain_session and reason not in (FinishReason.CANCELLED, FinishReason.ERROR))
 
     def _release_sequence(self, seq: SequenceState, reason: FinishReason, slot: int = -1) -> None:
         seq.staged_token = None
         slot = seq.slot if seq.slot >= 0 else slot
         ttft = (seq.first_token_ns - seq.arrival_ns) / 1e9 if seq.first_token_ns else 0.0
         tpot = ((seq.last_token_ns - seq.first_token_ns) / 1e9 / (seq.generated - 1)) if seq.generated > 1 else 0.0
-        keep = seq.request.retain_session and reason not in (FinishReason.CANCELLED, FinishReason.ERROR)
+        keep = self._keeps_session(seq, reason)
         if keep:
             # the session keeps its committed KV; uncommitted staged state is dropped
             seq.tokens = seq.tokens[:seq.position]

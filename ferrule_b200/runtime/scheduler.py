@@ -99,11 +99,12 @@ class ResidentScheduler:
 
     def _admit(self) -> None:
         while self.waiting and len(self.active) < self.cfg.max_active_sequences:
-            slot = self.slots.acquire()
+            held = self.waiting[0].held_slot
+            slot = held if held >= 0 else self.slots.acquire()     # a continued session comes back to its own slot
             if slot is None:
                 return
             seq = self.waiting.popleft()
-            seq.slot = slot
+            seq.slot, seq.held_slot = slot, -1
             self.active[seq.request_id] = seq
             self.stats.admitted += 1
             if seq.prefill_remaining > 0:
@@ -221,18 +222,32 @@ class ResidentScheduler:
             seq.status = SeqStatus.DECODE
             self.decode_ready.appendleft(seq)
 
+    def release_held(self, seq: SequenceState) -> int:
+        """Return a retained session's slot to the pool -> the slot (or -1)."""
+        slot, seq.held_slot = seq.held_slot, -1
+        if slot >= 0:
+            self.slots.release(slot)
+        return slot
+
     def stage(self, seq: SequenceState, token: int) -> None:
         seq.staged_token = token
 
-    def finish(self, seq: SequenceState, reason: FinishReason) -> None:
+    def finish(self, seq: SequenceState, reason: FinishReason, keep_slot: bool = False) -> None:
+        """`keep_slot`: the sequence becomes a retained session of a runner whose state lives in the slot - the
+        slot stays out of the pool (`held_slot`) until the session continues or is dropped (`release_held`)."""
         seq.finish = reason
         seq.status = SeqStatus.FINISHED
         for q in (self.prefill, self.decode_ready, self.waiting):
             if seq in q:
                 q.remove(seq)
         if self.active.pop(seq.request_id, None) is not None and seq.slot >= 0:
-            self.slots.release(seq.slot)
+            if keep_slot:
+                seq.held_slot = seq.slot
+            else:
+                self.slots.release(seq.slot)
             seq.slot = -1
+        elif seq.held_slot >= 0 and not keep_slot:
+            self.release_held(seq)                 # ended while still waiting for admission
         if reason == FinishReason.CANCELLED:
             self.stats.cancelled += 1
         else:

@@ -54,6 +54,7 @@ class SeqStatus(Enum):
 class SequenceState:
     request: GenerateRequest
     slot: int = -1                         # logical state slot
+    held_slot: int = -1                    # slot a retained session keeps between requests (slot-bound runner state)
     kv_seq: int = -1                       # KvPageManager sequence id
     status: SeqStatus = SeqStatus.WAITING
     tokens: List[int] = field(default_factory=list)   # prompt + committed generated tokens

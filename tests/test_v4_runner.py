@@ -133,3 +133,36 @@ def test_v4_sequences_swap_out_and_return_under_page_pressure_on_cpu():
     eng.kv.check_invariants()
     assert eng.kv.stats().used_pages == 0 and not eng.scheduler.suspended
     assert runner.seq_state == {}, "finished sequences gave their slots (and the slot's cursor) back"
+
+
+def test_v4_session_is_retained_in_its_slot_across_turns_on_cpu():
+    """The V4 state of a sequence lives in its slot: a retained session keeps the slot out of the pool between
+    requests, the continuation returns to it and feeds only the new tokens, and dropping the session gives the
+    slot back."""
+    cfg = tiny_v4()
+    w = random_v4_weights(cfg, device="cpu", seed=3)
+    eng, runner = _engine(w, "cpu")
+    g = torch.Generator().manual_seed(7)
+    p1 = torch.randint(0, cfg.vocab_size, (9,), generator=g).tolist()
+    p2 = torch.randint(0, cfg.vocab_size, (5,), generator=g).tolist()
+    eng.submit(GenerateRequest("t1", p1, max_new_tokens=4, ignore_eos=True, session_id="s", retain_session=True))
+    ev = []
+    eng.run_until_idle(ev.append, max_steps=2000)
+    first = [e.token for e in ev if isinstance(e, TokenEvent)]
+    assert eng.scheduler.slots.available == 3, "the session holds its slot"
+    steps_before = runner.steps
+    eng.submit(GenerateRequest("t2", p2, max_new_tokens=4, ignore_eos=True, session_id="s", retain_session=True))
+    ev2 = []
+    eng.run_until_idle(ev2.append, max_steps=2000)
+    second = [e.token for e in ev2 if isinstance(e, TokenEvent)]
+    # the oracle over the whole conversation: first prompt, its reply, second prompt
+    assert eng._sessions["s"].position == len(p1) + 4 + len(p2) + 4
+    assert second == _greedy(w, p1 + first + p2, 4)
+    assert runner.steps - steps_before <= len(p2) + 1 + 4, "only the new tokens ran"
+    # another request gets a different slot while the session is held
+    eng.submit(GenerateRequest("other", p2, max_new_tokens=2, ignore_eos=True))
+    eng.run_until_idle(lambda e: None, max_steps=2000)
+    assert eng.scheduler.slots.available == 3
+    assert eng.reset_session("s") and eng.scheduler.slots.available == 4
+    eng.kv.check_invariants()
+    assert eng.kv.stats().used_pages == 0 and runner.seq_state == {}
