@@ -437,8 +437,7 @@ def cmd_plan_placement(args) -> int:
 
 def cmd_chat(args) -> int:
     """Interactive chat.  The conversation is one retained session: every turn feeds only its new text to the
-    model and continues from the cached history (runners that bind state to a request-long slot re-encode the
-    history instead).  /reset clears the session, /stats, /ctx and /experts report, /exit or an empty line ends.
+    model and continues from the cached history.  /reset clears the session, /stats, /ctx and /experts report, /exit or an empty line ends.
     Mirrors the reference's chat command (crates/ferrule-cli/src/commands/chat.rs:205-275)."""
     from ..runtime.session import GenerateRequest
     from ..utils.tokenizer import ChatMessage, render_chat, template_for_model
@@ -446,7 +445,7 @@ def cmd_chat(args) -> int:
     eng.detokenize = tok.decode
     history: List[ChatMessage] = []
     tmpl = template_for_model(name)
-    retained = bool(getattr(eng.runner, "supports_prefix_sharing", True))
+    retained = True
     session = "chat"
     cached_text = ""                 # the rendered text whose tokens the session's cache holds
     ctx = eng.cfg.scheduler.ctx_size

@@ -64,10 +64,14 @@ def test_cli_golden_trace_parity_and_chunk_sweep(tmp_path):
     assert sw["sweep"][0]["prefill_chunks"] > sw["sweep"][1]["prefill_chunks"]
 
 
-def test_chat_continues_one_retained_session_and_answers_the_slash_commands():
+import pytest
+
+
+@pytest.mark.parametrize("preset", ["tiny-fixture", "tiny-v4"])
+def test_chat_continues_one_retained_session_and_answers_the_slash_commands(preset):
     script = "\n".join(["hello there", "/stats", "/ctx", "and again", "/stats", "/experts", "/reset", "/stats", "fresh start",
                         "/exit"]) + "\n"
-    p = subprocess.run([sys.executable, "-m", "ferrule_b200", "chat", "--preset", "tiny-fixture", "--device", "cpu",
+    p = subprocess.run([sys.executable, "-m", "ferrule_b200", "chat", "--preset", preset, "--device", "cpu",
                         "--ctx-size", "256", "--max-seqs", "2", "--page-size", "16", "--max-tokens", "4"],
                        input=script, capture_output=True, text=True, timeout=300)
     assert p.returncode == 0, p.stderr[-2000:]
