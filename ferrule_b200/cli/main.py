@@ -35,6 +35,13 @@ def _add_model_args(p: argparse.ArgumentParser) -> None:
     p.add_argument("--max-batch-tokens", type=int, default=2048)
     p.add_argument("--prefill-chunk", type=int, default=512)
     p.add_argument("--speculative", action="store_true")
+    p.add_argument("--expert-residency", type=float, default=None,
+                   help="fraction of every layer's routed experts kept on the device; the rest streams from pinned host memory")
+    p.add_argument("--async-streaming", action="store_true",
+                   help="with --expert-residency: a batch that needs a non-resident expert parks and resumes instead of "
+                        "uploading inline")
+    p.add_argument("--transaction-prefetch", type=int, default=0,
+                   help="with --async-streaming: payloads a parked transaction may prefetch for later layers")
     p.add_argument("--expert-plan", help="JSON written by plan-placement: renumber the routed experts (random-init "
                                          "presets; every rank of a multi-rank launch must get the same file)")
     p.add_argument("--router-zipf", type=float, default=0.0,
@@ -130,9 +137,13 @@ def build_engine(args, layout=None):
         n_pages = max(args.kv_cache_mb * (1 << 20) // per_page, pages_per_seq + 1)
     else:
         n_pages = args.max_seqs * pages_per_seq + 8
+    residency = getattr(args, "expert_residency", None)
+    streaming = bool(getattr(args, "async_streaming", False) and residency is not None)
     runner = DeepSeekRunner(weights, n_pages=n_pages, page_size=args.page_size, max_rows=args.max_batch_tokens,
                             max_seqs=args.max_seqs, max_seq_len=pages_per_seq * args.page_size, device=dev,
-                            tp=layout.tp if layout is not None else None, pp=layout.pp if layout is not None else None)
+                            tp=layout.tp if layout is not None else None, pp=layout.pp if layout is not None else None,
+                            expert_residency=residency, async_streaming=streaming, enable_mtp=args.speculative,
+                            max_draft=max(args.max_draft, 1))
     if layout is not None and layout.tp is not None and str(dev) != "cpu":
         layout.tp.attach(runner.fwd)
     sched = SchedulerConfig(max_active_sequences=args.max_seqs, max_decode_batch=args.max_seqs,
@@ -141,7 +152,9 @@ def build_engine(args, layout=None):
     block = max(512 // args.page_size, 1) * args.page_size
     eng = Engine(runner, EngineConfig(scheduler=sched, kv_pages=n_pages, page_size=args.page_size,
                                       speculative=args.speculative, max_draft=args.max_draft,
-                                      prefix_cache_tokens=getattr(args, "prefix_cache_tokens", 0), prefix_block=block))
+                                      prefix_cache_tokens=getattr(args, "prefix_cache_tokens", 0), prefix_block=block,
+                                      transaction_prefetch=getattr(args, "transaction_prefetch", 0) if streaming else 0),
+                 registry=runner.make_registry() if streaming else None)
     return eng, load_tokenizer(args.model_dir), name
 
 

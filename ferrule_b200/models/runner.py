@@ -178,6 +178,7 @@ class DeepSeekRunner(ModelRunner):
         # oracle keeps reading the full weights; the residency protocol runs beside it.)
         self.arena = None
         self.provider = None
+        self.telemetry = None                  # route counts per layer and local expert (streamed experts only)
         self.async_streaming = bool(async_streaming and expert_residency is not None)
         if expert_residency is not None and (self.is_cuda or self.async_streaming):
             from .expert_arena import ExpertArena
@@ -212,6 +213,7 @@ class DeepSeekRunner(ModelRunner):
                 from ..utils.telemetry import ExpertTelemetry
                 self.fwd.telemetry = ExpertTelemetry(self.cfg.n_layers + len(weights.mtp),
                                                      max(weights.e_hi - weights.e_lo, 1))
+                self.telemetry = self.fwd.telemetry
             L = self.fwd.ws.max_logit_rows
             self.out_host = torch.zeros(2 * L, dtype=torch.int32).pin_memory()
         else:
@@ -247,6 +249,9 @@ class DeepSeekRunner(ModelRunner):
             else:
                 self.fwd.expert_gate = self._expert_gate
         self.fwd.prof, self.fwd.tap = self.profiler, self.debug_tap
+        if self.arena is not None and self.telemetry is None:
+            from ..utils.telemetry import ExpertTelemetry
+            self.telemetry = ExpertTelemetry(self.cfg.n_layers + len(weights.mtp), max(weights.e_hi - weights.e_lo, 1))
 
     # ------------------------------------------------------------------ contract
     def capabilities(self) -> ExecutionCapabilities:
@@ -293,6 +298,24 @@ class DeepSeekRunner(ModelRunner):
         self.provider.attach(reg)
         return reg
 
+    def prefetch_candidates(self, layer: int, n: int):
+        """Payloads a transaction parked at `layer` will probably want next: for the streamed layers after it,
+        nearest first, the most-routed experts (this runner's route counts) that are not resident - at most `n`
+        materialization keys.  The engine requests them without a waiter while the transaction waits."""
+        if not self.async_streaming or self.telemetry is None or n <= 0:
+            return []
+        out = []
+        for l in sorted(k for k in self.arena.layers if k > layer):
+            if not self.telemetry.tokens[l]:
+                continue
+            la = self.arena.layers[l]
+            for e in self.telemetry.hottest(l, la.frames):
+                if self.telemetry.counts[l][e] and la.coord.resolve(e) is None:
+                    out.append(self.provider.key(l, e))
+                    if len(out) >= n:
+                        return out
+        return out
+
     def _expert_gate(self, layer: int, experts) -> None:
         """Residency protocol of the host path (the oracle multiplies with the full weights): the batch's experts
         are taken in waves of at most `frames`; a wave with a missing expert parks the transaction, finished waves
@@ -300,6 +323,8 @@ class DeepSeekRunner(ModelRunner):
         from .expert_async import NeedExperts
         if layer not in self.arena.layers:
             return                      # a layer whose experts are all resident (the proposal stage)
+        if not self._wave_state.get(layer, {}).get("done"):
+            self.telemetry.record(layer, experts)           # once per layer pass, not per resumed wave
         frames = self.arena.frames(layer)
         held = self._lease_sink.setdefault(layer, {})
         if len(experts) <= frames:

@@ -40,6 +40,10 @@ class EngineConfig:
     scheduler: SchedulerConfig = field(default_factory=SchedulerConfig)
     kv_pages: int = 256
     page_size: int = 16
+    # a transaction that parks on missing payloads may name up to this many further payloads it expects to need
+    # (the runner's `prefetch_candidates`): they are requested without a waiter, load behind the required ones and
+    # stay owned by the transaction until it ends.  0 = off
+    transaction_prefetch: int = 0
     speculative: bool = False
     max_draft: int = 1
     confidence_threshold: float = 0.2
@@ -99,6 +103,7 @@ class Transaction:
     speculative: object = None          # speculation.SpecCohort for verification transactions
     error: Optional[BaseException] = None
     t_start_ns: int = 0
+    prefetch_ops: List[int] = field(default_factory=list)      # registry operations requested as this transaction's prefetch
 
 
 @dataclass
@@ -123,6 +128,7 @@ class EngineStats:
     auto_preemptions: int = 0
     waits: int = 0
     resumes: int = 0
+    prefetch_requests: int = 0
     host_ns: int = 0
     runner_ns: int = 0
     ttft_sum_s: float = 0.0
@@ -566,6 +572,7 @@ class Engine:
                 self._waiting.pop(txn.txn_id, None)
                 return
             self.registry.register_continuation(txn.txn_id, progress.dependencies)
+            self._transaction_prefetch(txn, progress)
             return
         assert isinstance(progress, Complete)
         try:
@@ -580,6 +587,38 @@ class Engine:
         txn.commit_id = self.kv.prepare_commit([(m.res_id, m.rows) for m in txn.members])
         txn.state = TxnState.PUBLISHING
         self._end(txn)
+
+    def _transaction_prefetch(self, txn: Transaction, progress) -> None:
+        """While the transaction waits for what it must have, ask for what it will probably want next: no waiter,
+        no lease, prefetch band (behind every required load).  The requests belong to the transaction and are
+        detached when it ends, whatever became of them."""
+        n = self.cfg.transaction_prefetch
+        want = getattr(self.runner, "prefetch_candidates", None)
+        if n <= 0 or want is None:
+            return
+        from .registry import OwnerKind
+        have = set(progress.dependencies.keys if hasattr(progress.dependencies, "keys") else progress.dependencies)
+        keys = [k for k in want(getattr(progress, "layer", 0), n) if k not in have][:n]
+        owner = (OwnerKind.TRANSACTION_PREFETCH, txn.txn_id)
+        for k in keys:
+            op = self.registry.request(k, owner)
+            if op not in txn.prefetch_ops:
+                txn.prefetch_ops.append(op)
+                self.stats.prefetch_requests += 1
+
+    def _release_registry(self, txn: Transaction) -> None:
+        """The transaction reached its end: its custody and its prefetch ownership go back to the registry."""
+        if self.registry is None:
+            return
+        self.registry.release_transaction(txn.txn_id)
+        if txn.prefetch_ops:
+            from .registry import OwnerKind
+            owner = (OwnerKind.TRANSACTION_PREFETCH, txn.txn_id)
+            for op in txn.prefetch_ops:
+                o = self.registry.ops.get(op)
+                if o is not None and owner in o.owners:
+                    self.registry.detach(op, owner)
+            txn.prefetch_ops.clear()
 
     def _resume_ready(self) -> bool:
         did = False
@@ -653,8 +692,7 @@ class Engine:
         self._retire(self.kv.abort_reservations([m.res_id for m in txn.members]))
         if txn.grant is not None:
             self.broker.complete(txn.grant)
-        if self.registry is not None:
-            self.registry.release_transaction(txn.txn_id)
+        self._release_registry(txn)
         txn.state = TxnState.DONE
         for m in txn.members:
             seq = m.seq
@@ -668,8 +706,7 @@ class Engine:
     # ------------------------------------------------------------------ publish
     def _publish(self, txn: Transaction) -> None:
         """Backend confirmed the publish: commit KV, scheduler, tokens; stage the next greedy tokens."""
-        if self.registry is not None:
-            self.registry.release_transaction(txn.txn_id)
+        self._release_registry(txn)
         if txn.speculative is not None:
             self.spec.publish(txn)
             return

@@ -95,3 +95,36 @@ def test_speculative_decoding_with_streamed_experts_drafts_on_resident_proposal_
     from ferrule_b200.models.expert_arena import ExpertArena
     w2 = W.random_weights(cfg, device="cpu", dtype=torch.float32, seed=2)
     assert cfg.n_layers in ExpertArena(w2, 0.5, replace_weights=False, mtp_resident=False).layers
+
+
+def test_parked_transactions_prefetch_the_hot_experts_of_later_layers_on_cpu():
+    """`transaction_prefetch`: while a transaction waits for the experts it must have, the engine requests - without
+    a waiter - the most-routed non-resident experts of the layers that follow.  The requests are owned by the
+    transaction, nothing of them is left when it ends, and the stream stays the resident model's."""
+    cfg = C.tiny_fixture().with_(n_layers=4)
+    g = torch.Generator().manual_seed(5)
+    prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (7, 11, 9)]
+    want = _run(_engine(W.random_weights(cfg, device="cpu", dtype=torch.float32, seed=2), "cpu")[0], prompts, 10)
+    w = W.random_weights(cfg, device="cpu", dtype=torch.float32, seed=2)
+    runner = DeepSeekRunner(w, n_pages=48, page_size=16, max_rows=64, max_seqs=4, max_seq_len=256, device="cpu",
+                            enable_mtp=False, expert_residency=0.5, async_streaming=True)
+    sched = SchedulerConfig(max_active_sequences=4, max_decode_batch=4, max_batch_tokens=32, prefill_chunk_size=8,
+                            ctx_size=256)
+    eng = Engine(runner, EngineConfig(scheduler=sched, kv_pages=48, page_size=16, transaction_prefetch=3),
+                 registry=runner.make_registry())
+    got = _run(eng, prompts, 10)
+    assert got == want
+    assert eng.stats.waits > 0 and eng.stats.prefetch_requests > 0
+    reg = eng.registry
+    from ferrule_b200.runtime.registry import OwnerKind
+    leftover = [op for op in reg.ops.values() if any(k == OwnerKind.TRANSACTION_PREFETCH for k, _ in op.owners)]
+    assert not leftover, "every prefetch owner was detached when its transaction ended"
+    assert reg.residual().get("continuations", 0) == 0
+    for la in runner.arena.layers.values():
+        assert all(s.leases == 0 for s in la.coord.slots)
+    assert sum(runner.telemetry.tokens) > 0
+    # candidates: only layers after the stop layer, only non-resident experts, at most n
+    keys = runner.prefetch_candidates(1, 4)
+    assert len(keys) <= 4 and all(k.resource.group > 1 for k in keys)
+    assert all(runner.arena.layers[k.resource.group].coord.resolve(k.resource.item) is None for k in keys)
+    assert runner.prefetch_candidates(max(runner.arena.layers), 4) == []
