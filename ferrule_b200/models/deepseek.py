@@ -444,6 +444,7 @@ class CudaForward:
         # (6.75 ms without, 6.97 ms with 48 MB): off by default
         self.l2_prefetch_bytes = int(float(os.environ.get("FERRULE_L2_PREFETCH_MB", "0")) * (1 << 20))
         self.telemetry = None      # utils.telemetry.ExpertTelemetry fed by the streamed path
+        self.predictor = None      # runtime.expert_prediction.ExpertPredictor fed by the streamed path
         # callable(layer, expert ids [T, k] on the device, T): route statistics for placement planning.  The observer
         # reads the ids on the host, so a forward that has one is neither captured in a graph nor overlapped
         self.route_observer = None
@@ -867,6 +868,8 @@ class CudaForward:
         need = counts.nonzero().flatten().tolist()
         if self.telemetry is not None:
             self.telemetry.record_counts(layer, counts.tolist(), T)
+        if self.predictor is not None and not (self.wave_state or {}).get(layer, {}).get("done"):
+            self.predictor.observe(layer, need)
         if self.async_stream:
             return self._moe_async(lw, plan, layer, T, side, idx, need)
         frames = arena.frames(layer)

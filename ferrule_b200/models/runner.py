@@ -252,6 +252,14 @@ class DeepSeekRunner(ModelRunner):
         if self.arena is not None and self.telemetry is None:
             from ..utils.telemetry import ExpertTelemetry
             self.telemetry = ExpertTelemetry(self.cfg.n_layers + len(weights.mtp), max(weights.e_hi - weights.e_lo, 1))
+        # hot-set predictor (frequency, recency, step-to-step transitions per layer) fed by every streamed layer pass;
+        # it ranks the prefetch candidates of parked transactions
+        self.predictor = None
+        if self.arena is not None:
+            from ..runtime.expert_prediction import ExpertPredictor
+            self.predictor = ExpertPredictor(max(weights.e_hi - weights.e_lo, 1))
+            if self.is_cuda:
+                self.fwd.predictor = self.predictor
 
     # ------------------------------------------------------------------ contract
     def capabilities(self) -> ExecutionCapabilities:
@@ -300,20 +308,19 @@ class DeepSeekRunner(ModelRunner):
 
     def prefetch_candidates(self, layer: int, n: int):
         """Payloads a transaction parked at `layer` will probably want next: for the streamed layers after it,
-        nearest first, the most-routed experts (this runner's route counts) that are not resident - at most `n`
-        materialization keys.  The engine requests them without a waiter while the transaction waits."""
-        if not self.async_streaming or self.telemetry is None or n <= 0:
+        nearest first, the non-resident experts the hot-set predictor ranks highest (at most as many per layer as
+        the layer has frames) - at most `n` materialization keys.  The engine requests them without a waiter
+        while the transaction waits."""
+        if not self.async_streaming or self.predictor is None or n <= 0:
             return []
         out = []
         for l in sorted(k for k in self.arena.layers if k > layer):
-            if not self.telemetry.tokens[l]:
-                continue
             la = self.arena.layers[l]
-            for e in self.telemetry.hottest(l, la.frames):
-                if self.telemetry.counts[l][e] and la.coord.resolve(e) is None:
-                    out.append(self.provider.key(l, e))
-                    if len(out) >= n:
-                        return out
+            resident = set(la.coord.resident())
+            for e in self.predictor.predict(l, min(n - len(out), la.frames), exclude=resident):
+                out.append(self.provider.key(l, e))
+            if len(out) >= n:
+                break
         return out
 
     def _expert_gate(self, layer: int, experts) -> None:
@@ -325,6 +332,7 @@ class DeepSeekRunner(ModelRunner):
             return                      # a layer whose experts are all resident (the proposal stage)
         if not self._wave_state.get(layer, {}).get("done"):
             self.telemetry.record(layer, experts)           # once per layer pass, not per resumed wave
+            self.predictor.observe(layer, experts)
         frames = self.arena.frames(layer)
         held = self._lease_sink.setdefault(layer, {})
         if len(experts) <= frames:
@@ -686,6 +694,8 @@ class DeepSeekRunner(ModelRunner):
         if self.arena is not None:
             d["expert_arena"] = dict(vars(self.arena.stats))
             d["expert_telemetry"] = self.fwd.telemetry.snapshot()
+        if self.predictor is not None:
+            d["expert_predictor"] = dict(vars(self.predictor.stats), precision=round(self.predictor.stats.precision, 4))
         if self.profiler is not None:
             d["stage_table"] = self.profiler.by_stage()
             d["stage_table_layers"] = self.profiler.table()
