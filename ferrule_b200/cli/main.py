@@ -31,10 +31,16 @@ def _add_model_args(p: argparse.ArgumentParser) -> None:
     p.add_argument("--kv-cache-mb", type=int, default=0, help="KV pool size; 0 = from --max-seqs x --ctx-size")
     p.add_argument("--page-size", type=int, default=64)
     p.add_argument("--ctx-size", type=int, default=4096)
-    p.add_argument("--max-seqs", type=int, default=32)
+    p.add_argument("--max-seqs", "--max-active-sequences", dest="max_seqs", type=int, default=32)
     p.add_argument("--max-batch-tokens", type=int, default=2048)
-    p.add_argument("--prefill-chunk", type=int, default=512)
+    p.add_argument("--prefill-chunk", "--prefill-chunk-size", dest="prefill_chunk", type=int, default=512)
     p.add_argument("--speculative", action="store_true")
+    p.add_argument("--decode-cohort-target", type=int, default=1,
+                   help="ready decode requests wanted before a decode cohort is dispatched")
+    p.add_argument("--decode-cohort-max-deferrals", type=int, default=0,
+                   help="prefill decisions a decode cohort below its target may wait for")
+    p.add_argument("--chat-template", choices=["chatml", "llama3", "qwen", "deepseek", "plain"],
+                   help="override the chat template chosen from the model name")
     p.add_argument("--expert-residency", type=float, default=None,
                    help="fraction of every layer's routed experts kept on the device; the rest streams from pinned host memory")
     p.add_argument("--async-streaming", action="store_true",
@@ -148,6 +154,8 @@ def build_engine(args, layout=None):
         layout.tp.attach(runner.fwd)
     sched = SchedulerConfig(max_active_sequences=args.max_seqs, max_decode_batch=args.max_seqs,
                             max_batch_tokens=args.max_batch_tokens, prefill_chunk_size=args.prefill_chunk,
+                            decode_cohort_target=getattr(args, "decode_cohort_target", 1),
+                            decode_cohort_max_deferrals=getattr(args, "decode_cohort_max_deferrals", 0),
                             ctx_size=pages_per_seq * args.page_size)
     block = max(512 // args.page_size, 1) * args.page_size
     eng = Engine(runner, EngineConfig(scheduler=sched, kv_pages=n_pages, page_size=args.page_size,
@@ -164,6 +172,13 @@ def _is_v4_dir(model_dir: str) -> bool:
             return json.load(f).get("model_type") == "deepseek_v4"
     except OSError:
         return False
+
+
+def _chat_template(args):
+    """The `--chat-template` override as a `ChatTemplate`, or None (the model name decides)."""
+    from ..utils.tokenizer import ChatTemplate
+    name = getattr(args, "chat_template", None)
+    return ChatTemplate(name) if name else None
 
 
 def _expert_plan(args):
@@ -205,6 +220,8 @@ def _build_v4_engine(args, dev, model_dir: Optional[str] = None):
                       max_seq_len=pages_per_seq * args.page_size, max_rows=args.max_batch_tokens)
     sched = SchedulerConfig(max_active_sequences=args.max_seqs, max_decode_batch=args.max_seqs,
                             max_batch_tokens=args.max_batch_tokens, prefill_chunk_size=args.prefill_chunk,
+                            decode_cohort_target=getattr(args, "decode_cohort_target", 1),
+                            decode_cohort_max_deferrals=getattr(args, "decode_cohort_max_deferrals", 0),
                             ctx_size=pages_per_seq * args.page_size)
     # the block drafter proposes `proposal_block_size` tokens at once: --max-draft above 1 caps it, the default
     # takes the whole block
@@ -457,7 +474,7 @@ def cmd_chat(args) -> int:
     eng, tok, name = build_engine(args)
     eng.detokenize = tok.decode
     history: List[ChatMessage] = []
-    tmpl = template_for_model(name)
+    tmpl = _chat_template(args) or template_for_model(name)
     retained = True
     session = "chat"
     cached_text = ""                 # the rendered text whose tokens the session's cache holds
@@ -549,7 +566,7 @@ def cmd_serve(args) -> int:
                                                     admission_timeout_s=args.admission_timeout),
                          model_name=args.served_name or args.preset, mirror=mirror).start()
     print(json.dumps({"serving": holder.get("name"), "host": args.host, "port": args.port}), flush=True)
-    serve(worker, args.host, args.port, args.served_name or holder.get("name"))
+    serve(worker, args.host, args.port, args.served_name or holder.get("name"), template=_chat_template(args))
     return 0
 
 
@@ -756,8 +773,10 @@ def main(argv: Optional[List[str]] = None) -> int:
     p.set_defaults(fn=cmd_chat)
     p = sub.add_parser("serve"); _add_model_args(p)
     p.add_argument("--host", default="127.0.0.1"); p.add_argument("--port", type=int, default=8000)
-    p.add_argument("--served-name"); p.add_argument("--command-queue", type=int, default=256)
-    p.add_argument("--event-queue", type=int, default=32); p.add_argument("--admission-timeout", type=float, default=30.0)
+    p.add_argument("--served-name", "--served-model-name", dest="served_name")
+    p.add_argument("--command-queue", "--request-queue-capacity", dest="command_queue", type=int, default=256)
+    p.add_argument("--event-queue", "--event-queue-capacity", dest="event_queue", type=int, default=32)
+    p.add_argument("--admission-timeout", "--admission-timeout-secs", dest="admission_timeout", type=float, default=30.0)
     p.set_defaults(fn=cmd_serve)
     p = sub.add_parser("bench-interactive"); _add_model_args(p)
     p.add_argument("--turns", type=int, default=2); p.add_argument("--prompt-len", type=int, default=32)

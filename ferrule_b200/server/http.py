@@ -179,10 +179,10 @@ def build_app(worker: ModelWorker, model_name: Optional[str] = None, template: O
 
 
 def serve(worker: ModelWorker, host: str = "127.0.0.1", port: int = 8000, model_name: Optional[str] = None,
-          log_level: str = "warning") -> None:
+          log_level: str = "warning", template: Optional[ChatTemplate] = None) -> None:
     """Blocking: run the ASGI app under uvicorn until interrupted, then stop the worker."""
     import uvicorn
-    app = build_app(worker, model_name)
+    app = build_app(worker, model_name, template)
     try:
         uvicorn.run(app, host=host, port=port, log_level=log_level)
     finally:
