@@ -25,6 +25,7 @@ from typing import Any, Dict, List, Optional
 
 
 def _add_model_args(p: argparse.ArgumentParser) -> None:
+    p.add_argument("model", nargs="?", help="HF checkpoint directory (same as --model-dir)")
     p.add_argument("--model-dir", help="HF checkpoint directory (config.json + safetensors)")
     p.add_argument("--preset", default="tiny-fixture", help="random-init preset when no --model-dir is given")
     p.add_argument("--device", default=None, help="cuda[:N] or cpu (default: cuda when available)")
@@ -107,6 +108,8 @@ def build_engine(args, layout=None):
     from ..runtime.scheduler import SchedulerConfig
     from ..utils.tokenizer import load_tokenizer
     dev = args.device or ("cuda" if torch.cuda.is_available() else "cpu")
+    if getattr(args, "model", None) and not args.model_dir:
+        args.model_dir = args.model
     if args.model_dir and _is_v4_dir(args.model_dir):
         return _build_v4_engine(args, dev, args.model_dir)
     if args.model_dir:
@@ -135,6 +138,8 @@ def build_engine(args, layout=None):
         name = cfg.name
     if layout is not None and args.model_dir:
         raise SystemExit("checkpoint directories load on one rank; multi-rank launches take --preset")
+    if args.speculative == "auto":                   # use the checkpoint's proposal stage when it has one
+        args.speculative = bool(weights.mtp)
     cfg = weights.cfg
     ctx = min(args.ctx_size, cfg.max_position)
     pages_per_seq = (ctx + args.page_size - 1) // args.page_size
@@ -211,6 +216,8 @@ def _build_v4_engine(args, dev, model_dir: Optional[str] = None):
             cfg = cfg.with_(n_proposal_stages=2, proposal_target_layers=(0, cfg.n_layers - 1), proposal_noise_token=1,
                             proposal_markov_rank=32)
         weights = random_v4_weights(cfg, device=dev, seed=args.seed)
+    if args.speculative == "auto":                   # use the checkpoint's drafter when it has one
+        args.speculative = weights.proposal is not None
     if args.speculative and weights.proposal is None:
         raise SystemExit("--speculative: this DeepSeek-V4 checkpoint has no `mtp.*` proposal stages")
     ctx = min(args.ctx_size, cfg.max_position)
@@ -235,6 +242,9 @@ def _build_v4_engine(args, dev, model_dir: Optional[str] = None):
 # ------------------------------------------------------------------------------------------ commands
 def cmd_info(args) -> int:
     import torch
+
+    if getattr(args, "model", None) and not args.model_dir:
+        args.model_dir = args.model
 
     from .. import __version__, _build
     from ..models import config as C
@@ -409,20 +419,51 @@ def _collect(eng, emit_text=None):
     return toks, fin
 
 
+def _add_generate_args(p) -> None:
+    p.add_argument("-p", "--prompt", default="hello"); p.add_argument("--tokens")
+    p.add_argument("-n", "--max-tokens", type=int, default=16)
+    p.add_argument("--ignore-eos", "--no-stop-eos", dest="ignore_eos", action="store_true")
+    p.add_argument("--chat", action="store_true", help="wrap --prompt in the model's chat template")
+    p.add_argument("--verbose-tokens", action="store_true", help="print every generated token id to stderr")
+    p.add_argument("--warmup-tokens", type=int, default=0, help="decode this many tokens of a throw-away request first")
+    p.add_argument("--json", action="store_true", help="add the engine / runner / registry report to the output")
+
+
 def cmd_generate(args) -> int:
     from ..runtime.session import GenerateRequest
+    if getattr(args, "v4_generate", False):
+        args.speculative = "auto" if not args.no_speculative else False
     eng, tok, name = build_engine(args)
     eng.detokenize = tok.decode
-    prompt = [int(t) for t in args.tokens.split(",")] if args.tokens else tok.encode(args.prompt)
+    text = args.prompt
+    if args.chat and not args.tokens:
+        from ..utils.tokenizer import ChatMessage, render_chat, template_for_model
+        text = render_chat([ChatMessage("user", args.prompt)], _chat_template(args) or template_for_model(name))
+    prompt = [int(t) for t in args.tokens.split(",")] if args.tokens else tok.encode(text)
     prompt = [t % eng.runner.vocab_size for t in prompt]
+    if args.warmup_tokens > 0:
+        eng.submit(GenerateRequest("warmup", prompt[:8] or [1], max_new_tokens=args.warmup_tokens, ignore_eos=True))
+        _collect(eng)
     t0 = time.perf_counter()
     eng.submit(GenerateRequest("gen", prompt, max_new_tokens=args.max_tokens, ignore_eos=args.ignore_eos))
     toks, fin = _collect(eng)
     dt = time.perf_counter() - t0
     f = fin["gen"]
-    print(json.dumps({"model": name, "prompt_tokens": len(prompt), "tokens": toks.get("gen", []), "text": f.text,
-                      "finish_reason": f.reason.openai(), "seconds": round(dt, 4), "ttft_s": round(f.ttft_s, 4),
-                      "tpot_s": round(f.tpot_s, 6)}))
+    if args.verbose_tokens:
+        for i, t in enumerate(toks.get("gen", [])):
+            print(f"[token {i}] id={t} text={tok.decode([t])!r}", file=sys.stderr)
+    out = {"model": name, "prompt_tokens": len(prompt), "tokens": toks.get("gen", []), "text": f.text,
+           "finish_reason": f.reason.openai(), "seconds": round(dt, 4), "ttft_s": round(f.ttft_s, 4),
+           "tpot_s": round(f.tpot_s, 6)}
+    if args.json:
+        out["report_version"] = 2
+        out["engine"] = eng.snapshot_stats()
+        out["runner"] = eng.runner.observability()
+        if eng.spec is not None:
+            out["speculative"] = eng.spec.metrics.to_dict()
+        if eng.registry is not None and hasattr(eng.registry, "stats"):
+            out["registry"] = dict(vars(eng.registry.stats))
+    print(json.dumps(out))
     return 0
 
 
@@ -744,7 +785,7 @@ def cmd_expert_stream_smoke(args) -> int:
 def main(argv: Optional[List[str]] = None) -> int:
     ap = argparse.ArgumentParser(prog="ferrule_b200")
     sub = ap.add_subparsers(dest="cmd", required=True)
-    p = sub.add_parser("info"); p.add_argument("--model-dir"); p.set_defaults(fn=cmd_info)
+    p = sub.add_parser("info"); p.add_argument("model", nargs="?"); p.add_argument("--model-dir"); p.set_defaults(fn=cmd_info)
     p = sub.add_parser("cuda"); p.set_defaults(fn=cmd_cuda)
     p = sub.add_parser("make-fixture")
     p.add_argument("--preset", default="tiny-fixture"); p.add_argument("--out", required=True)
@@ -761,8 +802,11 @@ def main(argv: Optional[List[str]] = None) -> int:
     p = sub.add_parser("inspect-weightpack"); p.add_argument("model_dir"); p.add_argument("--json", action="store_true")
     p.add_argument("--limit", type=int, default=40); p.set_defaults(fn=cmd_inspect)
     p = sub.add_parser("generate"); _add_model_args(p)
-    p.add_argument("--prompt", default="hello"); p.add_argument("--tokens"); p.add_argument("--max-tokens", type=int, default=16)
-    p.add_argument("--ignore-eos", action="store_true"); p.set_defaults(fn=cmd_generate)
+    _add_generate_args(p); p.set_defaults(fn=cmd_generate)
+    # the reference's name for greedy generation from a DeepSeek-V4 directory: speculative decoding with the
+    # checkpoint's own drafter unless --no-speculative
+    p = sub.add_parser("deepseek-v4-generate"); _add_model_args(p); _add_generate_args(p)
+    p.add_argument("--no-speculative", action="store_true"); p.set_defaults(fn=cmd_generate, v4_generate=True)
     p = sub.add_parser("plan-placement"); _add_model_args(p)
     p.add_argument("--ranks", type=int, required=True, help="ranks the experts will be sharded over")
     p.add_argument("--requests", type=int, default=8); p.add_argument("--prompt-tokens", type=int, default=64)

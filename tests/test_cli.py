@@ -84,3 +84,27 @@ def test_chat_continues_one_retained_session_and_answers_the_slash_commands(pres
     assert "session reset." in out and "expert report not available." in out
     ctx_line = next(l for l in out.splitlines() if l.startswith("> context") or "context " in l)
     assert "/ 256 tokens" in ctx_line
+
+
+def test_reference_style_invocations(tmp_path):
+    """Positional model directory, -p / -n, the deepseek-v4-generate command (drafter of the checkpoint unless
+    --no-speculative) and the reference's serve flag names."""
+    d = str(tmp_path / "v4")
+    json.loads(run("make-fixture", "--family", "v4", "--out", d, "--layers", "2", "--proposal-stages", "1", "--plain"))
+    common = ["--device", "cpu", "--ctx-size", "64", "--max-active-sequences", "2", "--page-size", "16",
+              "--prefill-chunk-size", "8"]
+    a = json.loads(run("deepseek-v4-generate", d, "--tokens", "5,9,11", "-n", "5", "--no-stop-eos", "--json", *common))
+    b = json.loads(run("deepseek-v4-generate", d, "--tokens", "5,9,11", "-n", "5", "--no-stop-eos", "--no-speculative",
+                       "--json", *common))
+    assert a["tokens"] == b["tokens"] and len(a["tokens"]) == 5
+    assert a["report_version"] == 2 and a["speculative"]["drafted"] > 0 and "speculative" not in b
+    assert a["runner"]["proposal_blocks"] > 0 and b["runner"]["proposal_blocks"] == 0
+    info = json.loads(run("info", d))
+    assert info["checkpoint"]["family"] == "deepseek_v4"
+    p = subprocess.run([sys.executable, "-m", "ferrule_b200", "generate", d, "-p", "hi", "-n", "2", "--chat", "--verbose-tokens",
+                        "--warmup-tokens", "2", *common], capture_output=True, text=True, timeout=300)
+    assert p.returncode == 0 and p.stderr.count("[token ") == 2, p.stderr[-500:]
+    helptext = run("serve", "--help")
+    for flag in ("--served-model-name", "--request-queue-capacity", "--event-queue-capacity", "--admission-timeout-secs",
+                 "--decode-cohort-target", "--decode-cohort-max-deferrals", "--chat-template", "--kv-cache-mb"):
+        assert flag in helptext, flag
