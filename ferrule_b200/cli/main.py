@@ -44,6 +44,8 @@ def _add_model_args(p: argparse.ArgumentParser) -> None:
                    help="override the chat template chosen from the model name")
     p.add_argument("--expert-residency", type=float, default=None,
                    help="fraction of every layer's routed experts kept on the device; the rest streams from pinned host memory")
+    p.add_argument("--moe-hotset-experts", type=int, default=0,
+                   help="routed-expert slots per layer on the device (another way to say --expert-residency; 0 = unset)")
     p.add_argument("--async-streaming", action="store_true",
                    help="with --expert-residency: a batch that needs a non-resident expert parks and resumes instead of "
                         "uploading inline")
@@ -60,7 +62,7 @@ def _add_model_args(p: argparse.ArgumentParser) -> None:
     p.add_argument("--seed", type=int, default=0)
     p.add_argument("--weight-format", default="bf16", choices=["bf16", "fp8_block", "fp8_mxfp4"],
                    help="random-init presets: quantise the weights to this format")
-    p.add_argument("--layers", type=int, default=0, help="random-init presets: override the layer count")
+    p.add_argument("--layers", "--max-layers", dest="layers", type=int, default=0, help="random-init presets: override the layer count")
     p.add_argument("--pp", type=int, default=1,
                    help="pipeline stages; under torch.distributed.run the ranks form pp stages x (world / pp) "
                         "tensor-parallel ranks, rank 0 serves and the others mirror its command stream")
@@ -149,6 +151,8 @@ def build_engine(args, layout=None):
     else:
         n_pages = args.max_seqs * pages_per_seq + 8
     residency = getattr(args, "expert_residency", None)
+    if residency is None and getattr(args, "moe_hotset_experts", 0) and cfg.n_routed_experts:
+        residency = min(args.moe_hotset_experts / cfg.n_routed_experts, 1.0)
     streaming = bool(getattr(args, "async_streaming", False) and residency is not None)
     runner = DeepSeekRunner(weights, n_pages=n_pages, page_size=args.page_size, max_rows=args.max_batch_tokens,
                             max_seqs=args.max_seqs, max_seq_len=pages_per_seq * args.page_size, device=dev,

@@ -693,7 +693,7 @@ class DeepSeekRunner(ModelRunner):
         d["kv_pool_bytes"] = self.pool.data.numel() * self.pool.data.element_size()
         if self.arena is not None:
             d["expert_arena"] = dict(vars(self.arena.stats))
-            d["expert_telemetry"] = self.fwd.telemetry.snapshot()
+            d["expert_telemetry"] = self.telemetry.snapshot()
         if self.predictor is not None:
             d["expert_predictor"] = dict(vars(self.predictor.stats), precision=round(self.predictor.stats.precision, 4))
         if self.profiler is not None:

@@ -47,6 +47,8 @@ def _check(device, residency=0.75):
     eng.kv.check_invariants()
     assert eng.kv.stats().used_pages == 0
     assert eng.registry.residual().get("continuations", 0) == 0
+    obs = runner.observability()
+    assert obs["expert_arena"]["uploads"] == a.uploads and "expert_telemetry" in obs and "expert_predictor" in obs
 
 
 def test_async_streaming_parks_and_resumes_on_cpu():
