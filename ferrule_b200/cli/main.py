@@ -116,7 +116,8 @@ def build_engine(args, layout=None):
         return _build_v4_engine(args, dev, args.model_dir)
     if args.model_dir:
         from ..io.checkpoint import load_deepseek_hf
-        weights = load_deepseek_hf(args.model_dir, device=dev, dtype=torch.bfloat16 if dev != "cpu" else torch.float32)
+        weights = load_deepseek_hf(args.model_dir, device=dev, dtype=torch.bfloat16 if dev != "cpu" else torch.float32,
+                                   max_layers=getattr(args, "layers", 0))
         name = os.path.basename(os.path.normpath(args.model_dir))
     elif args.preset == "tiny-v4":
         return _build_v4_engine(args, dev)
@@ -212,7 +213,7 @@ def _build_v4_engine(args, dev, model_dir: Optional[str] = None):
     from ..utils.tokenizer import load_tokenizer
     if model_dir:
         from ..io.v4_checkpoint import load_v4_hf
-        weights = load_v4_hf(model_dir, device=dev)
+        weights = load_v4_hf(model_dir, device=dev, max_layers=getattr(args, "layers", 0))
         cfg = weights.cfg
     else:
         cfg = tiny_v4()

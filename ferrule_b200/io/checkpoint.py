@@ -118,9 +118,13 @@ def _layer(ck, prefix: str, layer: int, cfg: ModelConfig, rank: int, world: int,
 
 
 def load_deepseek_hf(directory, device="cpu", dtype=torch.bfloat16, tp_rank: int = 0, tp_world: int = 1,
-                     cfg: Optional[ModelConfig] = None) -> ModelWeights:
+                     cfg: Optional[ModelConfig] = None, max_layers: int = 0) -> ModelWeights:
+    """`max_layers` > 0: bind only the first layers of the checkpoint (a smoke run of a large model; the proposal
+    stage, which continues from the last layer's hidden state, is then left out)."""
     ck = ShardedCheckpoint(directory)
     cfg = cfg or from_hf_config(directory)
+    if 0 < max_layers < cfg.n_layers:
+        cfg = cfg.with_(n_layers=max_layers, n_mtp_layers=0)
     dev, dt = torch.device(device), dtype
     embed = ck.read("model.embed_tokens.weight").to(dt).to(dev)
     layers = [_layer(ck, f"model.layers.{i}.", i, cfg, tp_rank, tp_world, dev, dt, cfg.is_moe_layer(i))

@@ -98,12 +98,17 @@ def _raw(ck: ShardedCheckpoint, name: str, dev, dtype=None) -> torch.Tensor:
     return (t.to(dtype) if dtype is not None else t).to(dev)
 
 
-def load_v4_hf(directory, device="cpu") -> V4Weights:
+def load_v4_hf(directory, device="cpu", max_layers: int = 0) -> V4Weights:
     """Bind a DeepSeek-V4 checkpoint directory: every linear decoded to bf16, experts stacked per layer
     ([E, 2 * inter, hidden] gate over up, [E, hidden, inter]), the output projection's first stage regrouped to
     [o_groups, o_lora, group_in]."""
     d = Path(directory)
     cfg = v4_config_from_hf(json.loads((d / "config.json").read_text()))
+    if 0 < max_layers < cfg.n_layers:
+        # a smoke run over the first layers of a large checkpoint: the proposal attachment taps layers that may
+        # not be bound then, so it is left out
+        cfg = cfg.with_(n_layers=max_layers, compress_ratios=tuple(cfg.compress_ratios[:max_layers]),
+                        n_hash_layers=min(cfg.n_hash_layers, max_layers), n_proposal_stages=0, proposal_target_layers=())
     ck = ShardedCheckpoint(d)
     H, hd, E, I = cfg.hidden, cfg.head_dim, cfg.n_routed_experts, cfg.moe_inter
     bf, f32 = torch.bfloat16, torch.float32

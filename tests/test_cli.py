@@ -108,3 +108,20 @@ def test_reference_style_invocations(tmp_path):
     for flag in ("--served-model-name", "--request-queue-capacity", "--event-queue-capacity", "--admission-timeout-secs",
                  "--decode-cohort-target", "--decode-cohort-max-deferrals", "--chat-template", "--kv-cache-mb"):
         assert flag in helptext, flag
+
+
+def test_max_layers_binds_a_prefix_of_the_checkpoint(tmp_path):
+    from ferrule_b200.io.checkpoint import load_deepseek_hf
+    from ferrule_b200.io.v4_checkpoint import load_v4_hf
+    d4, ds = str(tmp_path / "v4"), str(tmp_path / "ds")
+    run("make-fixture", "--family", "v4", "--out", d4, "--plain", "--proposal-stages", "1")
+    run("make-fixture", "--out", ds)
+    w = load_v4_hf(d4, max_layers=2)
+    assert len(w.layers) == 2 and w.cfg.n_layers == 2 and w.cfg.compress_ratios == (0, 4) and w.proposal is None
+    assert load_v4_hf(d4).proposal is not None and len(load_v4_hf(d4, max_layers=9).layers) == 3
+    full = load_deepseek_hf(ds)
+    part = load_deepseek_hf(ds, max_layers=1)
+    assert len(part.layers) == 1 and part.cfg.n_layers == 1 and not part.mtp and len(full.layers) == 2
+    out = json.loads(run("generate", ds, "--device", "cpu", "--tokens", "5,9", "-n", "3", "--ignore-eos", "--ctx-size", "64",
+                         "--page-size", "16", "--max-seqs", "2", "--max-layers", "1"))
+    assert len(out["tokens"]) == 3
