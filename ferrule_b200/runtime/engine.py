@@ -129,6 +129,7 @@ class EngineStats:
     waits: int = 0
     resumes: int = 0
     prefetch_requests: int = 0
+    session_evictions: int = 0          # idle retained sessions dropped so that a waiting request could get their slot
     host_ns: int = 0
     runner_ns: int = 0
     ttft_sum_s: float = 0.0
@@ -351,6 +352,20 @@ class Engine:
         self._drive_retirements()
         return True
 
+    def _evict_idle_session_for_slot(self) -> bool:
+        """Every slot is taken and a new request waits for one: retained sessions of slot-bound runners hold slots
+        while idle - the one retained longest gives its slot (and its cached state) up.  A waiting continuation of
+        a session keeps its own slot and is not what this is about."""
+        if self.scheduler.waiting[0].held_slot >= 0:
+            return False
+        for sid, seq in self._sessions.items():            # insertion order: oldest retained first
+            if seq.held_slot >= 0:
+                del self._sessions[sid]
+                self._drop_session(seq)
+                self.stats.session_evictions += 1
+                return True
+        return False
+
     def _drop_session(self, seq: SequenceState) -> None:
         if seq.kv_seq >= 0:
             self._retire(self.kv.free_sequence_pages(seq.kv_seq))
@@ -410,6 +425,8 @@ class Engine:
         if self.registry is not None:
             progressed |= bool(self.registry.drive())
             progressed |= self._resume_ready()
+        if self.scheduler.waiting and self.scheduler.slots.available == 0:
+            progressed |= self._evict_idle_session_for_slot()
         action = self.scheduler.next_action()
         if action is not None:
             self.stats.actions += 1

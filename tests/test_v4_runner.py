@@ -166,3 +166,35 @@ def test_v4_session_is_retained_in_its_slot_across_turns_on_cpu():
     assert eng.reset_session("s") and eng.scheduler.slots.available == 4
     eng.kv.check_invariants()
     assert eng.kv.stats().used_pages == 0 and runner.seq_state == {}
+
+
+def test_idle_retained_sessions_give_their_slots_to_waiting_requests_on_cpu():
+    cfg = tiny_v4()
+    w = random_v4_weights(cfg, device="cpu", seed=3)
+    eng, runner = _engine(w, "cpu")                   # four slots
+    g = torch.Generator().manual_seed(9)
+    prompts = [torch.randint(0, cfg.vocab_size, (6,), generator=g).tolist() for _ in range(6)]
+    for i in range(4):
+        eng.submit(GenerateRequest(f"s{i}", prompts[i], max_new_tokens=2, ignore_eos=True, session_id=f"sess{i}",
+                                   retain_session=True))
+    eng.run_until_idle(lambda e: None, max_steps=2000)
+    assert eng.scheduler.slots.available == 0 and len(eng._sessions) == 4
+    # two fresh requests: the two sessions retained longest are dropped for them, the others keep their state
+    for i in (4, 5):
+        eng.submit(GenerateRequest(f"n{i}", prompts[i], max_new_tokens=3, ignore_eos=True))
+    ev = []
+    steps = eng.run_until_idle(ev.append, max_steps=2000)
+    assert steps < 2000
+    for i in (4, 5):
+        assert [e.token for e in ev if isinstance(e, TokenEvent) and e.request_id == f"n{i}"] == _greedy(w, prompts[i], 3)
+    assert eng.stats.session_evictions == 2 and sorted(eng._sessions) == ["sess2", "sess3"]
+    # a kept session still continues from its cached state
+    eng.submit(GenerateRequest("c", [7, 8], max_new_tokens=2, ignore_eos=True, session_id="sess3", retain_session=True))
+    ev2 = []
+    eng.run_until_idle(ev2.append, max_steps=2000)
+    kept = eng._sessions["sess3"]
+    assert [e.token for e in ev2 if isinstance(e, TokenEvent)] == _greedy(w, kept.tokens[:6 + 2 + 2], 2)
+    for sid in list(eng._sessions):
+        eng.reset_session(sid)
+    eng.kv.check_invariants()
+    assert eng.kv.stats().used_pages == 0 and eng.scheduler.slots.available == 4
