@@ -129,7 +129,7 @@ class EngineStats:
     waits: int = 0
     resumes: int = 0
     prefetch_requests: int = 0
-    session_evictions: int = 0          # idle retained sessions dropped so that a waiting request could get their slot
+    session_evictions: int = 0          # idle retained sessions dropped so that a request could get their slot or pages
     host_ns: int = 0
     runner_ns: int = 0
     ttft_sum_s: float = 0.0
@@ -360,6 +360,17 @@ class Engine:
             return False
         for sid, seq in self._sessions.items():            # insertion order: oldest retained first
             if seq.held_slot >= 0:
+                del self._sessions[sid]
+                self._drop_session(seq)
+                self.stats.session_evictions += 1
+                return True
+        return False
+
+    def _evict_idle_session_for_pages(self) -> bool:
+        """Nothing of this action could reserve its pages: idle retained sessions are caches of their conversations
+        and come before any running request - the one retained longest that still holds pages is dropped."""
+        for sid, seq in self._sessions.items():
+            if seq.kv_seq >= 0 and self.kv.sequence(seq.kv_seq).pages:
                 del self._sessions[sid]
                 self._drop_session(seq)
                 self.stats.session_evictions += 1
@@ -874,12 +885,15 @@ class Engine:
 
     def _break_page_deadlock(self, stalled: List[SequenceState]) -> None:
         """No sequence of this action could reserve its pages.  Pages may still be on their way back (endings,
-        parked transactions, retirements, cached prefixes): then the next step tries again.  Otherwise nobody
+        parked transactions, retirements, cached prefixes): then the next step tries again.  Idle retained
+        sessions are dropped next, oldest first (they are caches of their conversations).  Otherwise nobody
         will ever free a page by itself: with `auto_preempt` the youngest sequence is swapped out (an idle one if
         there is one, else one of the stalled ones - the others then fit); without it, or when a single sequence
         cannot fit the pool on its own, the youngest stalled request ends with an error instead of spinning."""
         if self._ending or self._waiting or self._retired or self._prefix_lru:
             return
+        if self._evict_idle_session_for_pages():
+            return                          # an idle retained session gave its pages up: the next step tries again
         if self.cfg.auto_preempt:
             idle = [s for s in self.scheduler.decode_ready if s not in stalled]
             holders = [s for s in idle if self.kv.sequence(s.kv_seq).pages]

@@ -262,3 +262,24 @@ def test_exact_fork_of_an_unknown_or_busy_session_changes_nothing():
     assert (before.used_pages, before.forks) == (after.used_pages, after.forks)
     ev += run(eng)
     assert len(toks(ev, "busy")) == 20
+
+
+def test_idle_retained_sessions_give_their_pages_to_running_requests():
+    """Four retained sessions fill the pool.  A new request does not end with an out-of-pages error: the sessions
+    retained longest are dropped until it fits; the younger ones stay and still continue."""
+    eng, r = make(pages=8, page=16, max_active=4)
+    for i in range(4):
+        eng.submit(GenerateRequest(f"s{i}", list(range(1, 30)), max_new_tokens=2, session_id=f"sess{i}", retain_session=True))
+    run(eng)
+    assert eng.kv.free_pages == 0 and len(eng._sessions) == 4
+    prompt = list(range(1, 40))
+    eng.submit(GenerateRequest("new", prompt, max_new_tokens=3))
+    ev = run(eng)
+    assert toks(ev, "new") == expected(r, prompt, 3) and fin(ev, "new").reason == FinishReason.MAX_TOKENS
+    assert eng.stats.page_deadlocks == 0 and eng.stats.session_evictions >= 1
+    kept = sorted(eng._sessions)
+    assert kept and kept[-1] == "sess3" and "sess0" not in kept
+    eng.submit(GenerateRequest("c", [5], max_new_tokens=1, session_id="sess3", retain_session=True))
+    ev2 = run(eng)
+    assert len(toks(ev2, "c")) == 1 and fin(ev2, "c").prompt_tokens > 29, "the kept session continued from its history"
+    eng.kv.check_invariants()
