@@ -168,6 +168,7 @@ class Engine:
         self._outbox: Deque[object] = deque()
         self._retired: KvRetirement = KvRetirement()
         self._sessions: Dict[str, SequenceState] = {}
+        self._session_busy: set = set()                  # session ids with a request in flight
         self._snapshots: Dict[str, Tuple[object, list]] = {}
         self._shutdown = False
         # prefix cache: chained block hash -> (kv sequence, tokens); entries in insertion / last-use order
@@ -192,6 +193,9 @@ class Engine:
             raise RuntimeError("engine is shut down")
         if req.max_new_tokens < 0:
             raise ValueError("max_new_tokens must be >= 0")
+        if req.session_id and req.session_id in self._session_busy:
+            # a second request would start from nothing and overwrite the first one's retained state when it ends
+            raise ValueError(f"session {req.session_id!r} has a request in flight")
         prev = self._sessions.get(req.session_id) if req.session_id else None
         now = time.perf_counter_ns()
         # validate before anything is taken: a rejected continuation leaves its retained session intact
@@ -232,6 +236,8 @@ class Engine:
             else:
                 self._retire(self.kv.free_sequence_pages(seq.kv_seq))
             raise
+        if req.session_id:
+            self._session_busy.add(req.session_id)
         return seq
 
     # ------------------------------------------------------------------ prompt-prefix cache
@@ -839,6 +845,8 @@ class Engine:
         ttft = (seq.first_token_ns - seq.arrival_ns) / 1e9 if seq.first_token_ns else 0.0
         tpot = ((seq.last_token_ns - seq.first_token_ns) / 1e9 / (seq.generated - 1)) if seq.generated > 1 else 0.0
         keep = self._keeps_session(seq, reason)
+        if seq.request.session_id:
+            self._session_busy.discard(seq.request.session_id)
         if keep:
             # the session keeps its committed KV; uncommitted staged state is dropped
             seq.tokens = seq.tokens[:seq.position]

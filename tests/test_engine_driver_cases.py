@@ -283,3 +283,25 @@ def test_idle_retained_sessions_give_their_pages_to_running_requests():
     ev2 = run(eng)
     assert len(toks(ev2, "c")) == 1 and fin(ev2, "c").prompt_tokens > 29, "the kept session continued from its history"
     eng.kv.check_invariants()
+
+
+def test_a_session_takes_one_request_at_a_time():
+    eng, r = make()
+    eng.submit(GenerateRequest("a", list(range(1, 20)), max_new_tokens=2, session_id="s", retain_session=True))
+    with pytest.raises(ValueError):
+        eng.submit(GenerateRequest("b", list(range(1, 10)), max_new_tokens=2, session_id="s", retain_session=True))
+    run(eng)
+    eng.submit(GenerateRequest("b", [3, 4], max_new_tokens=2, session_id="s", retain_session=True))     # free again
+    ev = run(eng)
+    assert fin(ev, "b").prompt_tokens > 19
+    # a cancelled request frees the session name as well (its state is dropped)
+    eng.submit(GenerateRequest("c", [3, 4], max_new_tokens=50, session_id="s", retain_session=True))
+    eng.step(lambda e: None)
+    assert eng.cancel_request("c")
+    run(eng)
+    eng.submit(GenerateRequest("d", [9, 9, 9], max_new_tokens=1, session_id="s"))
+    ev = run(eng)
+    assert fin(ev, "d").prompt_tokens == 3
+    assert eng.reset_session("s") is False
+    eng.kv.check_invariants()
+    assert eng.kv.stats().used_pages == 0
