@@ -1,0 +1,83 @@
+"""Randomised owner-loop soak (CPU, mock runner): requests with and without retained sessions, cancellations,
+session resets, exact forks, scripted execute failures and delayed endings, a pool small enough to stall, with
+and without speculation and auto-preemption.  After every step the page manager's invariants hold; at the end
+every page and every slot is back."""
+import random
+
+import pytest
+
+from ferrule_b200.runtime.engine import Engine, EngineConfig, FinishEvent
+from ferrule_b200.runtime.runner import MockRunner
+from ferrule_b200.runtime.scheduler import SchedulerConfig
+from ferrule_b200.runtime.session import FinishReason, GenerateRequest
+
+
+def _soak(seed: int, spec: bool) -> Engine:
+    rnd = random.Random(seed)
+    runner = MockRunner(page_size=16, draft_len=2 if spec else 0,
+                        draft_accuracy=(lambda slot, j, nxt: nxt if rnd.random() < 0.6 else (nxt + 1) % 1000) if spec else None)
+    sched = SchedulerConfig(max_active_sequences=4, max_decode_batch=4, max_batch_tokens=48, prefill_chunk_size=16,
+                            ctx_size=200)
+    eng = Engine(runner, EngineConfig(scheduler=sched, kv_pages=24, page_size=16, speculative=spec, max_draft=2,
+                                      auto_preempt=rnd.random() < 0.5))
+    live, n, ev, reasons = set(), 0, [], {}
+    for _ in range(500):
+        a = rnd.random()
+        if a < 0.25 and len(live) < 10:
+            rid, n = f"r{n}", n + 1
+            sid = rnd.choice([None, None, "s1", "s2", "s3"])
+            try:
+                eng.submit(GenerateRequest(rid, [rnd.randrange(1, 900) for _ in range(rnd.randrange(1, 40))],
+                                           max_new_tokens=rnd.randrange(0, 12), session_id=sid,
+                                           retain_session=bool(sid) and rnd.random() < 0.7, ignore_eos=True))
+                live.add(rid)
+            except ValueError:
+                pass                                   # busy session, or a continuation past the context window
+        elif a < 0.31 and live:
+            eng.cancel_request(rnd.choice(sorted(live)))
+        elif a < 0.34:
+            eng.reset_session(rnd.choice(["s1", "s2", "s3"]))
+        elif a < 0.38 and eng._sessions and len(live) < 10:
+            rid, n = f"f{n}", n + 1
+            try:
+                eng.fork_session_exact(rnd.choice(sorted(eng._sessions)),
+                                       GenerateRequest(rid, [rnd.randrange(1, 900)], max_new_tokens=rnd.randrange(1, 5),
+                                                       ignore_eos=True))
+                live.add(rid)
+            except (ValueError, RuntimeError, KeyError):
+                pass
+        elif a < 0.40:
+            runner.fail_next_execute = 1
+        elif a < 0.44:
+            runner.pending_ends = rnd.randrange(0, 3)
+        eng.step(ev.append)
+        for e in ev:
+            if isinstance(e, FinishEvent):
+                live.discard(e.request_id)
+                reasons[e.request_id] = e.reason
+        ev.clear()
+        eng.kv.check_invariants()
+    runner.pending_ends = 0
+    assert eng.run_until_idle(ev.append, max_steps=5000) < 5000, "the engine did not drain"
+    for e in ev:
+        if isinstance(e, FinishEvent):
+            live.discard(e.request_id)
+            reasons[e.request_id] = e.reason
+    assert not live, f"requests without a finish event: {sorted(live)}"
+    for sid in list(eng._sessions):
+        eng.reset_session(sid)
+    eng.step(ev.append)
+    eng.kv.check_invariants()
+    st = eng.kv.stats()
+    assert st.used_pages == 0 and st.quarantined_pages == 0, (seed, spec, st)
+    assert eng.scheduler.slots.available == 4 and not eng._session_busy
+    assert set(reasons.values()) <= {FinishReason.MAX_TOKENS, FinishReason.CANCELLED, FinishReason.ERROR,
+                                     FinishReason.CONTEXT}
+    return eng
+
+
+@pytest.mark.parametrize("spec", [False, True])
+@pytest.mark.parametrize("seed", range(6))
+def test_soak(seed, spec):
+    eng = _soak(seed, spec)
+    assert eng.stats.finished > 10
