@@ -14,12 +14,20 @@ from ferrule_b200.runtime.scheduler import SchedulerConfig
 from ferrule_b200.runtime.session import FinishReason, GenerateRequest
 
 cfg = tiny_v4().with_(n_proposal_stages=1, proposal_target_layers=(0, 2), proposal_noise_token=3, proposal_markov_rank=8)
-w = random_v4_weights(cfg, seed=3)
 _cache = {}
+
+
+def _weights():
+    if "w" not in _cache:
+        _cache["w"] = random_v4_weights(cfg, seed=3)
+    return _cache["w"]
+
+
 def greedy(prompt, n):
     key = (tuple(prompt), n)
     if key in _cache:
         return _cache[key]
+    w = _weights()
     r, c = V4Reference(w), V4SeqCache(cfg)
     for t in prompt:
         logits = r.step(c, t)
@@ -30,8 +38,10 @@ def greedy(prompt, n):
     _cache[key] = out
     return out
 
+
 def _soak(seed, spec):
     rnd = random.Random(seed)
+    w = _weights()
     runner = V4Runner(w, n_pages=10, page_size=16, max_seqs=3, max_seq_len=96, max_rows=48)
     sched = SchedulerConfig(max_active_sequences=3, max_decode_batch=3, max_batch_tokens=24, prefill_chunk_size=8, ctx_size=96)
     eng = Engine(runner, EngineConfig(scheduler=sched, kv_pages=10, page_size=16, speculative=spec, max_draft=5,
