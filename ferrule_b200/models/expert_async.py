@@ -53,6 +53,9 @@ class ArenaProvider(MaterializationProvider):
         self._ops: Dict[int, dict] = {}
         self._ready: Deque[CompletionEvent] = deque()
         self._uploading: List[Tuple[int, MaterializationKey, int]] = []
+        # uploads that found every frame of their layer leased: retried at every poll (a transaction that ends gives
+        # its frames back); op -> [key, generation, polls without a frame]
+        self._starved: Dict[int, list] = {}
         self._resident_op: Dict[Tuple[int, int], Tuple[int, MaterializationKey]] = {}
         self.clock_ns = 0
 
@@ -85,17 +88,32 @@ class ArenaProvider(MaterializationProvider):
 
     def submit_upload(self, op: int, key: MaterializationKey, generation: int) -> None:
         layer, expert = key.resource.group, key.resource.item
+        if not self._start_upload(op, key, generation):
+            self._starved[op] = [key, generation, 0]     # every frame is leased right now: try again at the next polls
+
+    def _start_upload(self, op: int, key: MaterializationKey, generation: int) -> bool:
+        layer, expert = key.resource.group, key.resource.item
         st = self._ops[op]
+        if self.registry is not None:
+            # payloads a parked transaction waits for stay put from their install until that transaction resumes
+            # and leases them itself
+            awaited = self.registry.awaited_ops()
+            self.arena.layers[layer].coord.protected = {e for (l, e), (o, _) in self._resident_op.items()
+                                                        if l == layer and o in awaited}
         try:
             ticket, event = self.arena.begin_upload(layer, expert)
-        except Exception:  # noqa: BLE001 - every frame is leased: the registry fails the waiter
-            self._emit(op, key, LoadStage.UPLOAD_SUBMITTED, generation, CompletionOutcome.FAILED,
-                       FailureReason.READ_ERROR)
-            return
+        except Exception:  # noqa: BLE001 - no frame without a lease
+            return False
         st["ticket"], st["event"] = ticket, event
         if ticket.evicted is not None:
             self._evicted(layer, ticket.evicted)
         self._uploading.append((op, key, generation))
+        return True
+
+    def starving(self, min_polls: int = 8) -> List[int]:
+        """Operations that have found no free frame for at least `min_polls` polls: the transactions that lease the
+        frames are parked themselves, nobody will give one up by itself."""
+        return [op for op, (_, _, n) in self._starved.items() if n >= min_polls]
 
     def _evicted(self, layer: int, expert: int) -> None:
         self._gen[(layer, expert)] = self._gen.get((layer, expert), 0) + 1
@@ -116,6 +134,11 @@ class ArenaProvider(MaterializationProvider):
         st = self._ops.get(op)
         if st is None:
             return
+        starved = self._starved.pop(op, None)
+        if starved is not None:                          # never got a frame: nothing to undo
+            self._emit(op, starved[0], LoadStage.UPLOAD_SUBMITTED, starved[1], CompletionOutcome.CANCELLED,
+                       FailureReason.CANCELLED)
+            return
         for i, (o, key, gen) in enumerate(self._uploading):
             if o == op:
                 del self._uploading[i]
@@ -130,6 +153,12 @@ class ArenaProvider(MaterializationProvider):
         self._ops.pop(op, None)
 
     def next_completion(self) -> Optional[CompletionEvent]:
+        for op in list(self._starved):
+            key, gen, _ = self._starved[op]
+            if self._start_upload(op, key, gen):
+                del self._starved[op]
+            else:
+                self._starved[op][2] += 1
         still = []
         for op, key, gen in self._uploading:
             ev = self._ops[op]["event"]

@@ -35,6 +35,18 @@ from .scheduler import Cancel, DecodeBatch, Finish, PrefillChunk, ResidentSchedu
 from .session import FinishReason, GenerateRequest, SeqStatus, SequenceState
 
 
+class MaterializationFailed(RuntimeError):
+    """A payload a parked transaction needed could not be loaded.  `retryable`: the destination had no free frame
+    (other parked transactions hold them) - the transaction is rolled back, gives its own frames up and its
+    sequences run again; any other reason (read / upload / install error, provider lost) ends the requests."""
+
+    def __init__(self, reason=None):
+        from .io_protocol import FailureReason
+        self.reason = reason
+        self.retryable = reason == FailureReason.RESOURCE_EXHAUSTED
+        super().__init__(f"a required materialization failed ({getattr(reason, 'value', reason)})")
+
+
 @dataclass
 class EngineConfig:
     scheduler: SchedulerConfig = field(default_factory=SchedulerConfig)
@@ -129,6 +141,7 @@ class EngineStats:
     waits: int = 0
     resumes: int = 0
     prefetch_requests: int = 0
+    frame_deadlocks: int = 0            # parked transactions rolled back because the loads they waited for had no frame
     session_evictions: int = 0          # idle retained sessions dropped so that a request could get their slot or pages
     host_ns: int = 0
     runner_ns: int = 0
@@ -169,6 +182,7 @@ class Engine:
         self._retired: KvRetirement = KvRetirement()
         self._sessions: Dict[str, SequenceState] = {}
         self._session_busy: set = set()                  # session ids with a request in flight
+        self._frame_backoff = False                      # set by a frame deadlock, cleared when nothing is parked
         self._snapshots: Dict[str, Tuple[object, list]] = {}
         self._shutdown = False
         # prefix cache: chained block hash -> (kv sequence, tokens); entries in insertion / last-use order
@@ -442,9 +456,15 @@ class Engine:
         if self.registry is not None:
             progressed |= bool(self.registry.drive())
             progressed |= self._resume_ready()
+            if self._waiting:
+                progressed |= self._break_frame_deadlock()
         if self.scheduler.waiting and self.scheduler.slots.available == 0:
             progressed |= self._evict_idle_session_for_slot()
-        action = self.scheduler.next_action()
+        if self._frame_backoff and not self._waiting:
+            self._frame_backoff = False
+        # after a frame deadlock nothing new starts while a transaction is parked: what was rolled back would lease
+        # the same frames again and meet the survivor in the same place
+        action = None if self._frame_backoff else self.scheduler.next_action()
         if action is not None:
             self.stats.actions += 1
             self._execute_action(action)
@@ -622,6 +642,32 @@ class Engine:
         txn.state = TxnState.PUBLISHING
         self._end(txn)
 
+    def _break_frame_deadlock(self) -> bool:
+        """Parked transactions keep the payloads they already hold leased while they wait for more.  When the
+        destination has no free frame left, the loads they wait for starve - and nobody will give a frame up by
+        itself.  The oldest transaction waiting for a starving load keeps what it holds; every other one is rolled
+        back (retryable: its sequences run again later), which returns their frames.  One transaction alone never
+        needs more frames than exist (it takes its experts in waves), so the oldest then gets through."""
+        starving = getattr(self.registry.provider, "starving", None)
+        ops = starving(2) if starving is not None else []
+        if not ops:
+            return False
+        waiters = sorted({t for op in ops for t in getattr(self.registry.ops.get(op), "waiters", ()) if t in self._waiting})
+        parked = sorted(self._waiting)
+        if not waiters or len(parked) < 2:
+            return False
+        from .io_protocol import FailureReason
+        keep = waiters[0]
+        for txn_id in parked:
+            if txn_id != keep:
+                txn = self._waiting.pop(txn_id)
+                self.stats.frame_deadlocks += 1
+                self._abort(txn, MaterializationFailed(FailureReason.RESOURCE_EXHAUSTED))
+        # the starving load takes a freed frame now; the rolled-back sequences wait until the survivor is through
+        self.registry.drive()
+        self._frame_backoff = True
+        return True
+
     def _transaction_prefetch(self, txn: Transaction, progress) -> None:
         """While the transaction waits for what it must have, ask for what it will probably want next: no waiter,
         no lease, prefetch band (behind every required load).  The requests belong to the transaction and are
@@ -660,7 +706,7 @@ class Engine:
             txn = self._waiting.pop(txn_id, None)
             if txn is not None:
                 did = True
-                self._abort(txn, RuntimeError("a required materialization failed"))
+                self._abort(txn, MaterializationFailed(self.registry.failure_of(txn_id)))
         for txn_id in self.registry.pop_ready():
             txn = self._waiting.pop(txn_id, None)
             if txn is None:

@@ -70,6 +70,9 @@ class ExpertResidencyCoordinator:
         self.slots = [Slot(i) for i in range(capacity)]
         self.where: Dict[int, int] = {}            # expert -> slot (READY only)
         self.incoming: Dict[int, int] = {}         # expert -> slot (PREPARING / ACTIVE)
+        # resident experts that must not be evicted although nobody leases them yet: installed for a parked
+        # transaction that has not been resumed (set by the provider before it asks for a slot)
+        self.protected: set = set()
         self._clock = 0
         self._leases_out = 0
         self.stats = ResidencyStats()
@@ -100,7 +103,8 @@ class ExpertResidencyCoordinator:
 
     # ------------------------------------------------------------------ install
     def _victim(self) -> Optional[Slot]:
-        cands = [s for s in self.slots if s.state in (SlotState.EMPTY, SlotState.READY) and s.leases == 0]
+        cands = [s for s in self.slots if s.state in (SlotState.EMPTY, SlotState.READY) and s.leases == 0
+                 and (s.expert is None or s.expert not in self.protected)]
         if not cands:
             return None
         empties = [s for s in cands if s.state == SlotState.EMPTY]

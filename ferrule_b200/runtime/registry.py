@@ -75,7 +75,10 @@ class Continuation:
     needs: Set[int]                       # op ids still outstanding
     all_ops: List[int]
     failed: bool = False
+    failure: Optional[FailureReason] = None      # why the first of its payloads failed
     t_wait_start_ns: int = 0
+    current: Set[int] = field(default_factory=set)      # operations named by the latest registration (this wait)
+    resumed: bool = False                        # handed to the engine by pop_ready since that registration
 
 
 @dataclass
@@ -201,7 +204,8 @@ class LoadRegistry:
             if op.stage != LoadStage.RESIDENT:
                 needs.add(op_id)
                 op.waiters.add(txn_id)
-        c = Continuation(txn_id, needs, all_ops, t_wait_start_ns=self.clock())
+        c = Continuation(txn_id, needs, all_ops, t_wait_start_ns=self.clock(),
+                         current={self.by_key[k] for k in keys if k in self.by_key})
         self.conts[txn_id] = c
         self.stats.continuations += 1
         if not needs:
@@ -229,6 +233,7 @@ class LoadRegistry:
         for t in out:
             c = self.conts.get(t)
             if c is not None:
+                c.resumed = True
                 self.ledger.record_wait(t, c.t_wait_start_ns, now)
         self.stats.resumed += len(out)
         return out
@@ -237,6 +242,21 @@ class LoadRegistry:
         out = list(self._failed)
         self._failed.clear()
         return out
+
+    def awaited_ops(self) -> Set[int]:
+        """Operations that a parked transaction named in its current wait and has not been resumed for yet.  Their
+        payloads are about to be used: a provider must not evict them to make room for another load (between the
+        install and the resume nobody holds a lease on them)."""
+        out: Set[int] = set()
+        for c in self.conts.values():
+            if not c.resumed and not c.failed:
+                out |= c.current
+        return out
+
+    def failure_of(self, txn_id: int) -> Optional[FailureReason]:
+        """Why the continuation of `txn_id` failed (None: it did not, or it is gone already)."""
+        c = self.conts.get(txn_id)
+        return c.failure if c is not None else None
 
     def release_transaction(self, txn_id: int) -> None:
         """The transaction ended: drop its custody of every payload it used."""
@@ -323,7 +343,7 @@ class LoadRegistry:
         for txn in list(op.waiters):
             c = self.conts.get(txn)
             if c is not None and not c.failed:
-                c.failed = True
+                c.failed, c.failure = True, reason
                 self._failed.append(txn)
         op.waiters.clear()
         self._retire(op, RetirementReason.FAILED)
