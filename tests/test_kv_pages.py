@@ -3,6 +3,8 @@ widths, rollback, quarantine and retirement confirmation, exact and prefix forks
 preempt / restore, failure atomicity).  `check_invariants` runs after every step that changes ownership.
 
 The case list follows the reference's page-manager suite (crates/ferrule-runtime/src/cache/page_manager.rs:1389-2023)."""
+import random
+
 import pytest
 
 from ferrule_b200.runtime.kv_pages import KvError, KvPageManager, OutOfPages, ReservationState
@@ -499,3 +501,111 @@ def test_released_page_id_outside_the_pool_is_detected():
     m.sequence(s).pages.append(99)
     with pytest.raises(KvError):
         m.free_sequence_pages(s)
+
+
+# ---------------------------------------------------------------------------------------------- randomised soak
+def _soak(seed):
+    rnd = random.Random(seed)
+    m = KvPageManager(24, 8, 200)
+    seqs = {}        # id -> model: committed tokens
+    open_res = {}    # seq -> (res_id, rows)
+    prepared = []    # (commit_id, [(seq, rows_committed)])
+    preempted = set()
+    retired = []
+    for step in range(800):
+        a = rnd.random()
+        try:
+            if a < 0.12 and len(seqs) < 8:
+                s = m.alloc_sequence()
+                seqs[s] = 0
+            elif a < 0.40 and seqs:
+                s = rnd.choice(sorted(seqs))
+                if s in open_res or s in preempted:
+                    continue
+                n = rnd.randrange(1, 12)
+                if seqs[s] + n > 190:
+                    continue
+                r = m.reserve(s, n)
+                m.bind_reservation_execution(r.res_id, step)
+                open_res[s] = (r.res_id, n)
+            elif a < 0.62 and open_res:
+                # two-phase commit of a few reservations with ragged prefixes
+                picks = rnd.sample(sorted(open_res), k=min(len(open_res), rnd.randrange(1, 3)))
+                commits = [(open_res[s][0], rnd.randrange(0, open_res[s][1] + 1)) for s in picks]
+                cid = m.prepare_commit(commits)
+                if rnd.random() < 0.2:
+                    m.abort_prepared_commit(cid)
+                    retired.append(m.abort_reservations([c[0] for c in commits]))
+                else:
+                    retired.append(m.publish_commit(cid))
+                    for s, (rid, rows) in zip(picks, commits):
+                        seqs[s] += rows
+                for s in picks:
+                    del open_res[s]
+            elif a < 0.68 and open_res:
+                s = rnd.choice(sorted(open_res))
+                retired.append(m.abort_reservations([open_res.pop(s)[0]]))
+            elif a < 0.74 and seqs:
+                s = rnd.choice(sorted(seqs))
+                if s in open_res or s in preempted:
+                    continue
+                c = m.publish_fork_sequence_exact(s) if rnd.random() < 0.5 or seqs[s] < 8 else None
+                if c is None:
+                    t = rnd.randrange(1, seqs[s] // 8 + 1) * 8
+                    c = m.publish_fork_sequence_prefix(s, t)
+                    seqs[c] = t
+                else:
+                    seqs[c] = seqs[s]
+            elif a < 0.80 and seqs:
+                s = rnd.choice(sorted(seqs))
+                if s in open_res or s in preempted:
+                    continue
+                t = rnd.randrange(0, seqs[s] + 1)
+                retired.append(m.truncate_sequence(s, t))
+                seqs[s] = t
+            elif a < 0.85 and seqs:
+                s = rnd.choice(sorted(seqs))
+                if s in open_res or s in preempted or seqs[s] == 0:
+                    continue
+                m.preempt_sequence(s)
+                retired.append(m.release_preempted_pages(s))
+                preempted.add(s)
+            elif a < 0.90 and preempted:
+                s = rnd.choice(sorted(preempted))
+                m.restore_sequence(s)
+                preempted.discard(s)
+            elif a < 0.96 and seqs:
+                s = rnd.choice(sorted(seqs))
+                if s in open_res:
+                    del open_res[s]
+                retired.append(m.free_sequence_pages(s))
+                del seqs[s]
+                preempted.discard(s)
+        except OutOfPages:
+            pass
+        # confirm retirements at random
+        if retired and rnd.random() < 0.5:
+            ret = retired.pop(0)
+            if ret:
+                m.confirm_page_retirement(list(ret.pages))
+        m.check_invariants()
+        for s, n in seqs.items():
+            if s not in preempted:
+                assert m.sequence(s).committed_tokens == n, (seed, step, s, m.sequence(s).committed_tokens, n)
+    for s in list(seqs):
+        retired.append(m.free_sequence_pages(s))
+    for ret in retired:
+        if ret:
+            m.confirm_page_retirement(list(ret.pages))
+    m.check_invariants()
+    st = m.stats()
+    assert st.used_pages == 0 and st.quarantined_pages == 0 and m.free_pages == 24, st
+
+
+
+@pytest.mark.parametrize("seed", range(10))
+def test_page_manager_soak(seed):
+    """Random interleavings of reservations, ragged two-phase commits, aborts, exact and prefix forks, truncation,
+    preemption / restore and frees on a 24-page pool: the invariants hold after every operation, every sequence's
+    committed length is what the model of the test says, and in the end every page is free."""
+    _soak(seed)
