@@ -3,6 +3,8 @@ every stage, failures, stale / wrong / duplicate / lost / out-of-order completio
 wake-ups, shutdown, retry).  Everything runs against the scriptable fake provider on the CPU.
 
 The case list follows the reference's registry suite (crates/ferrule-runtime/src/io/tests.rs:310-2366)."""
+import random
+
 import pytest
 
 from ferrule_b200.runtime.fairness import Band, FairQueue, FairQueueConfig
@@ -759,3 +761,95 @@ def test_resumed_transaction_that_waits_again_extends_its_continuation():
     assert reg.pop_ready() == [1] and sorted(reg.conts[1].all_ops) == [0, 1]
     reg.release_transaction(1)
     assert reg.ops[0].leases == 0 and reg.ops[1].leases == 0 and sorted(reg.evict_candidates()) == [0, 1]
+
+
+# ---------------------------------------------------------------------------------------------- randomised soak
+def _soak(seed):
+    rnd = random.Random(seed)
+    p = FakeMaterializationProvider(auto=False)
+    reg = LoadRegistry(p)
+    txns = {}          # txn -> state: "waiting" | "ready"
+    next_txn = 0
+    prefetch_owned = {}   # (op, owner)
+    for step in range(600):
+        a = rnd.random()
+        if a < 0.20:
+            t = next_txn
+            next_txn += 1
+            ks = [key(e, gen=0) for e in rnd.sample(range(12), rnd.randrange(1, 4))]
+            reg.register_continuation(t, ks)
+            txns[t] = "waiting"
+        elif a < 0.30:
+            o = (OwnerKind.TRANSACTION_PREFETCH, rnd.randrange(1000, 1010))
+            op = reg.request(key(rnd.randrange(12)), o)
+            prefetch_owned.setdefault(op, set()).add(o)
+        elif a < 0.36 and prefetch_owned:
+            op = rnd.choice(sorted(prefetch_owned))
+            o = prefetch_owned[op].pop()
+            if not prefetch_owned[op]:
+                del prefetch_owned[op]
+            x = reg.ops.get(op)
+            if x is not None and o in x.owners:
+                reg.detach(op, o)
+        elif a < 0.60 and p.pending:
+            op = rnd.choice(sorted(p.pending))
+            p.complete(op)
+        elif a < 0.66:
+            p.script_next(rnd.choice(["fail", "short", "lose", "reject", "dup", "stale", "ok", "ok"]))
+        elif a < 0.74 and txns:
+            t = rnd.choice(sorted(txns))
+            reg.release_transaction(t)
+            del txns[t]
+        elif a < 0.78:
+            # a ready transaction waits again (extension)
+            ready = [t for t, s in txns.items() if s == "ready"]
+            if ready:
+                t = rnd.choice(ready)
+                ks = [key(e, gen=0) for e in rnd.sample(range(12), rnd.randrange(1, 3))]
+                try:
+                    reg.register_continuation(t, ks)
+                    txns[t] = "waiting"
+                except IoProtocolError:
+                    pass
+        reg.drive()
+        for t in reg.pop_ready():
+            if t in txns:
+                txns[t] = "ready"
+        for t in reg.pop_failed():
+            if t in txns:
+                reg.release_transaction(t)
+                del txns[t]
+        # invariants
+        for op in reg.ops.values():
+            assert op.leases >= 0
+            if op.stage == LoadStage.RETIRED:
+                assert not op.waiters and op.leases == 0, (seed, step, op)
+        for t, c in reg.conts.items():
+            for o in c.needs:
+                assert t in reg.ops[o].waiters or reg.ops[o].stage in (LoadStage.FAILED, LoadStage.RETIRED), (seed, step, t, o, reg.ops[o].stage)
+    # wind down: release all, complete everything
+    for t in list(txns):
+        reg.release_transaction(t)
+    for op, owners in list(prefetch_owned.items()):
+        for o in owners:
+            x = reg.ops.get(op)
+            if x is not None and o in x.owners:
+                reg.detach(op, o)
+    for _ in range(50):
+        for op in list(p.pending):
+            p.complete(op)
+        reg.drive()
+    res = reg.residual()
+    assert res.get("continuations", 0) == 0, res
+    assert all(op.leases == 0 and not op.waiters for op in reg.ops.values()), [(o.op_id, o.stage, o.leases, o.waiters) for o in reg.ops.values() if o.leases or o.waiters]
+    return res
+
+
+
+@pytest.mark.parametrize("seed", range(8))
+def test_registry_soak(seed):
+    """Random interleavings of continuations (one to three payloads, re-waits that extend them), prefetch owners
+    that attach and detach, completions in any order, scripted failures, short reads, lost, rejected, duplicate
+    and stale completions, and transactions that end at any time: no lease or waiter survives a retired operation,
+    every outstanding dependency has its waiter registered, and after the wind-down nothing holds anything."""
+    _soak(seed)
