@@ -944,7 +944,10 @@ class Engine:
         will ever free a page by itself: with `auto_preempt` the youngest sequence is swapped out (an idle one if
         there is one, else one of the stalled ones - the others then fit); without it, or when a single sequence
         cannot fit the pool on its own, the youngest stalled request ends with an error instead of spinning."""
-        if self._ending or self._waiting or self._retired or self._prefix_lru:
+        if self._ending or self._waiting or self._retired:
+            return
+        if self._prefix_lru:
+            self._prefix_evict()            # cached prefixes go first (the speculative path stalls through here too)
             return
         if self._evict_idle_session_for_pages():
             return                          # an idle retained session gave its pages up: the next step tries again

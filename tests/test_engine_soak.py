@@ -19,7 +19,9 @@ def _soak(seed: int, spec: bool) -> Engine:
     sched = SchedulerConfig(max_active_sequences=4, max_decode_batch=4, max_batch_tokens=48, prefill_chunk_size=16,
                             ctx_size=200)
     eng = Engine(runner, EngineConfig(scheduler=sched, kv_pages=24, page_size=16, speculative=spec, max_draft=2,
-                                      auto_preempt=rnd.random() < 0.5))
+                                      auto_preempt=rnd.random() < 0.5,
+                                      prefix_cache_tokens=rnd.choice([0, 64, 256]), prefix_block=16))
+    shared = [rnd.randrange(1, 900) for _ in range(40)]           # prompts often start with a common prefix
     live, n, ev, reasons = set(), 0, [], {}
     for _ in range(500):
         a = rnd.random()
@@ -27,7 +29,8 @@ def _soak(seed: int, spec: bool) -> Engine:
             rid, n = f"r{n}", n + 1
             sid = rnd.choice([None, None, "s1", "s2", "s3"])
             try:
-                eng.submit(GenerateRequest(rid, [rnd.randrange(1, 900) for _ in range(rnd.randrange(1, 40))],
+                head = shared[:rnd.choice([0, 0, 16, 32, 40])]
+                eng.submit(GenerateRequest(rid, head + [rnd.randrange(1, 900) for _ in range(rnd.randrange(1, 40))],
                                            max_new_tokens=rnd.randrange(0, 12), session_id=sid,
                                            retain_session=bool(sid) and rnd.random() < 0.7, ignore_eos=True))
                 live.add(rid)
@@ -66,6 +69,8 @@ def _soak(seed: int, spec: bool) -> Engine:
     assert not live, f"requests without a finish event: {sorted(live)}"
     for sid in list(eng._sessions):
         eng.reset_session(sid)
+    while eng._prefix_evict():
+        pass
     eng.step(ev.append)
     eng.kv.check_invariants()
     st = eng.kv.stats()
