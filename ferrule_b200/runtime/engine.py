@@ -56,6 +56,9 @@ class EngineConfig:
     # (the runner's `prefetch_candidates`): they are requested without a waiter, load behind the required ones and
     # stay owned by the transaction until it ends.  0 = off
     transaction_prefetch: int = 0
+    # a transaction parked longer than this on its materializations is rolled back and its requests end with an
+    # error (a completion the provider never delivers would otherwise hold them for ever).  0 = wait without limit
+    materialization_timeout_s: float = 0.0
     speculative: bool = False
     max_draft: int = 1
     confidence_threshold: float = 0.2
@@ -116,6 +119,7 @@ class Transaction:
     error: Optional[BaseException] = None
     t_start_ns: int = 0
     prefetch_ops: List[int] = field(default_factory=list)      # registry operations requested as this transaction's prefetch
+    t_parked_ns: int = 0                # when it last began to wait for materializations
 
 
 @dataclass
@@ -141,6 +145,7 @@ class EngineStats:
     waits: int = 0
     resumes: int = 0
     prefetch_requests: int = 0
+    materialization_timeouts: int = 0   # parked transactions rolled back after `materialization_timeout_s`
     frame_deadlocks: int = 0            # parked transactions rolled back because the loads they waited for had no frame
     session_evictions: int = 0          # idle retained sessions dropped so that a request could get their slot or pages
     host_ns: int = 0
@@ -458,6 +463,8 @@ class Engine:
             progressed |= self._resume_ready()
             if self._waiting:
                 progressed |= self._break_frame_deadlock()
+            if self._waiting and self.cfg.materialization_timeout_s > 0:
+                progressed |= self._expire_parked()
         if self.scheduler.waiting and self.scheduler.slots.available == 0:
             progressed |= self._evict_idle_session_for_slot()
         if self._frame_backoff and not self._waiting:
@@ -620,12 +627,18 @@ class Engine:
         if isinstance(progress, Waiting):
             self.stats.waits += 1
             txn.state = TxnState.WAITING
+            txn.t_parked_ns = time.perf_counter_ns()
             self._waiting[txn.txn_id] = txn
             if self.registry is None:
                 self._abort(txn, RuntimeError("runner is waiting on materializations but no registry is attached"))
                 self._waiting.pop(txn.txn_id, None)
                 return
-            self.registry.register_continuation(txn.txn_id, progress.dependencies)
+            try:
+                self.registry.register_continuation(txn.txn_id, progress.dependencies)
+            except Exception as exc:  # noqa: BLE001 - a dependency list the registry refuses fails the transaction
+                self._waiting.pop(txn.txn_id, None)
+                self._abort(txn, exc)
+                return
             self._transaction_prefetch(txn, progress)
             return
         assert isinstance(progress, Complete)
@@ -641,6 +654,15 @@ class Engine:
         txn.commit_id = self.kv.prepare_commit([(m.res_id, m.rows) for m in txn.members])
         txn.state = TxnState.PUBLISHING
         self._end(txn)
+
+    def _expire_parked(self) -> bool:
+        from .io_protocol import FailureReason
+        limit = time.perf_counter_ns() - int(self.cfg.materialization_timeout_s * 1e9)
+        late = [t for t, txn in self._waiting.items() if txn.t_parked_ns < limit]
+        for txn_id in late:
+            self.stats.materialization_timeouts += 1
+            self._abort(self._waiting.pop(txn_id), MaterializationFailed(FailureReason.PROVIDER_LOST))
+        return bool(late)
 
     def _break_frame_deadlock(self) -> bool:
         """Parked transactions keep the payloads they already hold leased while they wait for more.  When the

@@ -305,3 +305,39 @@ def test_a_session_takes_one_request_at_a_time():
     assert eng.reset_session("s") is False
     eng.kv.check_invariants()
     assert eng.kv.stats().used_pages == 0
+
+
+def test_a_parked_transaction_whose_completion_never_comes_times_out():
+    """The provider loses a completion: the load stays in flight (its credit cannot be revoked), but the request
+    does not wait for ever - after `materialization_timeout_s` the transaction is rolled back with an error and
+    the engine serves the next request."""
+    import time
+    from ferrule_b200.runtime.io_protocol import MaterializationKey, ResourceId, ResourceKind
+    from ferrule_b200.runtime.provider import FakeMaterializationProvider
+    from ferrule_b200.runtime.registry import LoadRegistry
+    key = lambda e: MaterializationKey("m", b"s", bytes([e]), ResourceId(ResourceKind.ROUTED_EXPERT, 1, e), 1, "cuda", 0, 0, 0)
+    r = MockRunner()
+    prov = FakeMaterializationProvider(auto=True)
+    sched = SchedulerConfig(max_active_sequences=4, max_decode_batch=4, max_batch_tokens=64, prefill_chunk_size=16, ctx_size=256)
+    eng = Engine(r, EngineConfig(scheduler=sched, kv_pages=32, page_size=16, materialization_timeout_s=0.05),
+                 registry=LoadRegistry(prov))
+    r.wait_next = [[key(1)]]
+    prov.lose_next()
+    eng.submit(GenerateRequest("lost", [5, 6, 7], max_new_tokens=3))
+    ev = []
+    t0 = time.perf_counter()
+    eng.run_until_idle(ev.append, max_steps=10 ** 7)
+    assert 0.04 < time.perf_counter() - t0 < 5.0
+    assert fin(ev, "lost").reason == FinishReason.ERROR and eng.stats.materialization_timeouts == 1
+    assert not eng._waiting and eng.registry.residual().get("continuations", 0) == 0
+    assert eng.registry.residual()["in_flight"] == 1, "the owed completion is still owed"
+    eng.submit(GenerateRequest("next", [1, 2], max_new_tokens=2))
+    ev2 = run(eng)
+    assert toks(ev2, "next") == expected(r, [1, 2], 2)
+    # a dependency list the registry refuses fails the transaction instead of the engine
+    r.wait_next = [[key(3), key(3)]]
+    eng.submit(GenerateRequest("dup", [1, 2], max_new_tokens=2))
+    ev3 = run(eng)
+    assert fin(ev3, "dup").reason == FinishReason.ERROR
+    eng.kv.check_invariants()
+    assert eng.kv.stats().used_pages == 0

@@ -7,9 +7,16 @@ import random
 import pytest
 
 from ferrule_b200.runtime.engine import Engine, EngineConfig, FinishEvent
+from ferrule_b200.runtime.io_protocol import MaterializationKey, ResourceId, ResourceKind
+from ferrule_b200.runtime.provider import FakeMaterializationProvider
+from ferrule_b200.runtime.registry import LoadRegistry
 from ferrule_b200.runtime.runner import MockRunner
 from ferrule_b200.runtime.scheduler import SchedulerConfig
 from ferrule_b200.runtime.session import FinishReason, GenerateRequest
+
+
+def _key(e: int) -> MaterializationKey:
+    return MaterializationKey("m", b"s", bytes([e]), ResourceId(ResourceKind.ROUTED_EXPERT, 1, e), 1, "cuda", 0, 0, 0)
 
 
 def _soak(seed: int, spec: bool) -> Engine:
@@ -18,9 +25,13 @@ def _soak(seed: int, spec: bool) -> Engine:
                         draft_accuracy=(lambda slot, j, nxt: nxt if rnd.random() < 0.6 else (nxt + 1) % 1000) if spec else None)
     sched = SchedulerConfig(max_active_sequences=4, max_decode_batch=4, max_batch_tokens=48, prefill_chunk_size=16,
                             ctx_size=200)
+    # half of the runs park transactions on materializations (scripted provider: failures, lost completions)
+    prov = FakeMaterializationProvider(auto=True) if rnd.random() < 0.5 else None
     eng = Engine(runner, EngineConfig(scheduler=sched, kv_pages=24, page_size=16, speculative=spec, max_draft=2,
                                       auto_preempt=rnd.random() < 0.5,
-                                      prefix_cache_tokens=rnd.choice([0, 64, 256]), prefix_block=16))
+                                      prefix_cache_tokens=rnd.choice([0, 64, 256]), prefix_block=16,
+                                      materialization_timeout_s=0.01),
+                 registry=LoadRegistry(prov) if prov is not None else None)
     shared = [rnd.randrange(1, 900) for _ in range(40)]           # prompts often start with a common prefix
     live, n, ev, reasons = set(), 0, [], {}
     for _ in range(500):
@@ -53,6 +64,11 @@ def _soak(seed: int, spec: bool) -> Engine:
             runner.fail_next_execute = 1
         elif a < 0.44:
             runner.pending_ends = rnd.randrange(0, 3)
+        elif a < 0.52 and prov is not None:
+            runner.wait_next.append([_key(e) for e in rnd.sample(range(20), rnd.randrange(1, 3))])
+            if rnd.random() < 0.25:
+                # "stale" and "lose" leave the load without its completion: the parked transaction times out
+                prov.script_next(rnd.choice(["fail", "short", "dup", "fail", "short", "dup", "stale", "lose"]))
         eng.step(ev.append)
         for e in ev:
             if isinstance(e, FinishEvent):
@@ -61,6 +77,7 @@ def _soak(seed: int, spec: bool) -> Engine:
         ev.clear()
         eng.kv.check_invariants()
     runner.pending_ends = 0
+    runner.wait_next.clear()
     assert eng.run_until_idle(ev.append, max_steps=5000) < 5000, "the engine did not drain"
     for e in ev:
         if isinstance(e, FinishEvent):
@@ -76,6 +93,9 @@ def _soak(seed: int, spec: bool) -> Engine:
     st = eng.kv.stats()
     assert st.used_pages == 0 and st.quarantined_pages == 0, (seed, spec, st)
     assert eng.scheduler.slots.available == 4 and not eng._session_busy
+    if prov is not None:
+        assert eng.registry.residual().get("continuations", 0) == 0 and not eng._waiting
+        assert not any(op.waiters or op.leases for op in eng.registry.ops.values())
     assert set(reasons.values()) <= {FinishReason.MAX_TOKENS, FinishReason.CANCELLED, FinishReason.ERROR,
                                      FinishReason.CONTEXT}
     return eng
