@@ -51,6 +51,8 @@ def _add_model_args(p: argparse.ArgumentParser) -> None:
                         "uploading inline")
     p.add_argument("--transaction-prefetch", type=int, default=0,
                    help="with --async-streaming: payloads a parked transaction may prefetch for later layers")
+    p.add_argument("--materialization-timeout-secs", type=float, default=0.0,
+                   help="with --async-streaming: roll a parked transaction back with an error after this long (0 = no limit)")
     p.add_argument("--expert-plan", help="JSON written by plan-placement: renumber the routed experts (random-init "
                                          "presets; every rank of a multi-rank launch must get the same file)")
     p.add_argument("--router-zipf", type=float, default=0.0,
@@ -171,7 +173,8 @@ def build_engine(args, layout=None):
     eng = Engine(runner, EngineConfig(scheduler=sched, kv_pages=n_pages, page_size=args.page_size,
                                       speculative=args.speculative, max_draft=args.max_draft,
                                       prefix_cache_tokens=getattr(args, "prefix_cache_tokens", 0), prefix_block=block,
-                                      transaction_prefetch=getattr(args, "transaction_prefetch", 0) if streaming else 0),
+                                      transaction_prefetch=getattr(args, "transaction_prefetch", 0) if streaming else 0,
+                                      materialization_timeout_s=getattr(args, "materialization_timeout_secs", 0.0)),
                  registry=runner.make_registry() if streaming else None)
     return eng, load_tokenizer(args.model_dir), name
 
