@@ -157,6 +157,10 @@ def build_engine(args, layout=None):
     if residency is None and getattr(args, "moe_hotset_experts", 0) and cfg.n_routed_experts:
         residency = min(args.moe_hotset_experts / cfg.n_routed_experts, 1.0)
     streaming = bool(getattr(args, "async_streaming", False) and residency is not None)
+    if streaming and layout is not None:
+        # the ranks of a replica replay one command stream and must take every scheduling decision alike; when an
+        # upload completes differs from rank to rank, so transactions would resume in different steps
+        raise SystemExit("--async-streaming runs on one rank; multi-rank replicas stream experts inline (--expert-residency)")
     runner = DeepSeekRunner(weights, n_pages=n_pages, page_size=args.page_size, max_rows=args.max_batch_tokens,
                             max_seqs=args.max_seqs, max_seq_len=pages_per_seq * args.page_size, device=dev,
                             tp=layout.tp if layout is not None else None, pp=layout.pp if layout is not None else None,
