@@ -218,3 +218,67 @@ def test_data_parallel_replicas_share_the_load_and_keep_sessions():
         assert dp.healthy and len(dp.stats()["replicas"]) == 2
     finally:
         dp.stop()
+
+
+def test_random_request_bodies_never_break_the_server():
+    """300 requests with random fields, types and paths (broken JSON included): every answer is a 2xx, a 4xx with
+    the OpenAI error envelope or a 503; never a 500, never a hang, and the worker is alive afterwards."""
+    import random
+    rnd = random.Random(0)
+
+    def value(depth=0):
+        c = rnd.random()
+        if c < 0.15:
+            return None
+        if c < 0.3:
+            return rnd.choice([True, False])
+        if c < 0.5:
+            return rnd.choice([0, 1, -1, 2, 0.5, 1e9, -3.2, 40])
+        if c < 0.7:
+            return rnd.choice(["", "mock", "x", "user", "assistant", "system", "stop", "héllo ✓"])
+        if c < 0.85 and depth < 2:
+            return [value(depth + 1) for _ in range(rnd.randrange(0, 3))]
+        if depth < 2:
+            return {rnd.choice(["role", "content", "include_usage", "a"]): value(depth + 1) for _ in range(rnd.randrange(0, 3))}
+        return "z"
+
+    fields = ["model", "messages", "prompt", "max_tokens", "max_completion_tokens", "stream", "stream_options", "stop", "n",
+              "temperature", "top_p", "top_k", "min_p", "repetition_penalty", "presence_penalty", "frequency_penalty",
+              "logprobs", "user", "seed", "bogus", "session_id", "ignore_eos"]
+    worker, _ = make_worker()
+    app = build_app(worker)
+
+    async def main():
+        bad = []
+        async with client(app) as c:
+            for _ in range(300):
+                body = {}
+                if rnd.random() < 0.7:
+                    body["model"] = "mock"
+                if rnd.random() < 0.6:
+                    body["messages"] = [{"role": "user", "content": "hi"}] if rnd.random() < 0.6 else value()
+                if rnd.random() < 0.4:
+                    body["prompt"] = "abc" if rnd.random() < 0.6 else value()
+                if rnd.random() < 0.6:
+                    body["max_tokens"] = rnd.choice([1, 3, 0, -1, 10 ** 9, "5", None, 2.5])
+                for _ in range(rnd.randrange(0, 4)):
+                    body[rnd.choice(fields)] = value()
+                path = rnd.choice(["/v1/chat/completions", "/v1/completions", "/tokenize", "/v1/models", "/health", "/metrics",
+                                   "/nope"])
+                raw = json.dumps(body) if rnd.random() < 0.95 else "{not json"
+                if path in ("/v1/models", "/health", "/metrics", "/nope") and rnd.random() < 0.7:
+                    r = await asyncio.wait_for(c.get(path), 30)
+                else:
+                    r = await asyncio.wait_for(c.post(path, content=raw, headers={"content-type": "application/json"}), 30)
+                if r.status_code >= 500 and r.status_code != 503:
+                    bad.append((r.status_code, path, raw[:200], r.text[:200]))
+                elif 400 <= r.status_code < 500 and path.startswith("/v1/c"):
+                    err = r.json().get("error", {})
+                    if not {"message", "type", "param", "code"} <= set(err):
+                        bad.append(("envelope", r.status_code, path, raw[:200], r.text[:200]))
+        return bad
+    try:
+        assert run(main()) == []
+        assert worker.healthy
+    finally:
+        worker.stop()
