@@ -70,14 +70,25 @@ class SafetensorsFile:
             header = json.loads(self._f.read(hlen))
         except ValueError as exc:
             raise CheckpointError(f"{path}: header is not JSON") from exc
+        if not isinstance(header, dict):
+            raise CheckpointError(f"{path}: header is not a JSON object")
         self.metadata = header.pop("__metadata__", {})
         base = 8 + hlen
         self.tensors: Dict[str, TensorInfo] = {}
         for name, d in header.items():
-            if d["dtype"] not in _DTYPES:
-                raise CheckpointError(f"{path}: tensor {name} has unsupported dtype {d['dtype']}")
-            s, e = d["data_offsets"]
-            info = TensorInfo(name, d["dtype"], tuple(d["shape"]), base + s, base + e, self.path)
+            # every field is checked before use: a damaged header is a CheckpointError, never a stray exception
+            if not isinstance(d, dict) or not {"dtype", "shape", "data_offsets"} <= set(d):
+                raise CheckpointError(f"{path}: tensor {name} lacks dtype / shape / data_offsets")
+            if not isinstance(d["dtype"], str) or d["dtype"] not in _DTYPES:
+                raise CheckpointError(f"{path}: tensor {name} has unsupported dtype {d['dtype']!r}")
+            shape, offs = d["shape"], d["data_offsets"]
+            if not (isinstance(shape, list) and all(isinstance(x, int) and not isinstance(x, bool) and x >= 0 for x in shape)):
+                raise CheckpointError(f"{path}: tensor {name} has a malformed shape {shape!r}")
+            if not (isinstance(offs, list) and len(offs) == 2
+                    and all(isinstance(x, int) and not isinstance(x, bool) and x >= 0 for x in offs)):
+                raise CheckpointError(f"{path}: tensor {name} has malformed data_offsets {offs!r}")
+            s, e = offs
+            info = TensorInfo(name, d["dtype"], tuple(shape), base + s, base + e, self.path)
             if info.end > size or s > e:
                 raise CheckpointError(f"{path}: tensor {name} reaches past the end of the file")
             if info.numel * _DTYPES[info.dtype][1] != info.nbytes:

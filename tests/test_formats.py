@@ -227,3 +227,50 @@ def test_v4_checkpoint_carries_the_proposal_attachment(tmp_path):
         assert cli_main(["make-fixture", "--family", "v4", "--out", str(tmp_path / "fxp"), "--layers", "2",
                          "--proposal-stages", "1", "--plain"]) == 0
     assert json.loads(buf.getvalue())["proposal_stages"] == 1 and load_v4_hf(tmp_path / "fxp").proposal is not None
+
+
+def test_damaged_safetensors_headers_are_checkpoint_errors(tmp_path):
+    """Flipped header bytes, truncated files, wrong field types and absurd lengths: the reader answers with
+    CheckpointError every time (or reads a file whose damage happens to be harmless), never with a stray exception."""
+    import os, random, struct
+    from ferrule_b200.io.safetensors import CheckpointError, ShardedCheckpoint, write_sharded
+    t = {"a.weight": torch.randn(4, 8).to(torch.bfloat16), "b": torch.arange(10, dtype=torch.int64),
+         "c.scale": torch.ones(3, dtype=torch.uint8)}
+    write_sharded(t, tmp_path, 1 << 20, {})
+    path = next(p for p in tmp_path.iterdir() if p.suffix == ".safetensors")
+    good = path.read_bytes()
+    hlen = struct.unpack("<Q", good[:8])[0]
+    rnd = random.Random(0)
+    outcomes = set()
+    for _ in range(400):
+        b = bytearray(good)
+        mode = rnd.random()
+        if mode < 0.4:
+            for _ in range(rnd.randrange(1, 4)):
+                b[rnd.randrange(0, 8 + hlen)] = rnd.randrange(256)
+        elif mode < 0.6:
+            b = b[:rnd.randrange(0, len(b))]
+        elif mode < 0.8:
+            hdr = json.loads(good[8:8 + hlen])
+            k = rnd.choice([k for k in hdr if k != "__metadata__"])
+            hdr[k][rnd.choice(["dtype", "shape", "data_offsets"])] = rnd.choice(
+                [None, "X", [], [-1, 5], [0, 10 ** 12], [5, 1], "BF16", [2 ** 40, 2], {"a": 1}, 7, [True, 2]])
+            if rnd.random() < 0.2:
+                del hdr[k][rnd.choice(list(hdr[k]))]
+            raw = json.dumps(hdr).encode()
+            b = bytearray(struct.pack("<Q", len(raw)) + raw + good[8 + hlen:])
+        else:
+            b[:8] = struct.pack("<Q", rnd.choice([0, 1, 2 ** 63, len(good) * 2, hlen + 1, hlen - 1]))
+        path.write_bytes(bytes(b))
+        try:
+            ck = ShardedCheckpoint(tmp_path)
+            for n in ck.names():
+                ck.read(n)
+            ck.close()
+            outcomes.add("ok")
+        except CheckpointError:
+            outcomes.add("refused")
+    assert outcomes <= {"ok", "refused"} and "refused" in outcomes
+    path.write_bytes(b"[1, 2]".rjust(8 + 6, b"\\0")[:0] + struct.pack("<Q", 6) + b"[1, 2]")
+    with pytest.raises(CheckpointError):
+        ShardedCheckpoint(tmp_path)
