@@ -273,4 +273,4 @@ def test_damaged_safetensors_headers_are_checkpoint_errors(tmp_path):
     assert outcomes <= {"ok", "refused"} and "refused" in outcomes
     path.write_bytes(struct.pack("<Q", 6) + b"[1, 2]")             # valid JSON, not an object
     with pytest.raises(CheckpointError):
-        ShardedCheckpoint(tmp_path)
+        ShardedCheckpoint(tmp_path).read("a.weight")              # shards are opened when first read
