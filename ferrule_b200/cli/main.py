@@ -860,7 +860,12 @@ def main(argv: Optional[List[str]] = None) -> int:
     p.add_argument("--host-cache-mb", type=int, default=256); p.add_argument("--timeout", type=float, default=120.0)
     p.set_defaults(fn=cmd_expert_stream_smoke)
     args = ap.parse_args(argv)
-    return args.fn(args)
+    from ..io.safetensors import CheckpointError
+    try:
+        return args.fn(args)
+    except CheckpointError as exc:
+        print(f"error: {exc}", file=sys.stderr)          # a checkpoint that cannot be bound: say why, no traceback
+        return 2
 
 
 if __name__ == "__main__":

@@ -24,7 +24,7 @@ import torch
 from ..models.config import ModelConfig, from_hf_config
 from ..models.weights import LayerWeights, ModelWeights, MtpWeights, _shard_range
 from . import encoding as enc
-from .safetensors import CheckpointError, ShardedCheckpoint, write_sharded
+from .safetensors import CheckpointError, ShardedCheckpoint, write_sharded, fails_closed
 
 
 def infer_weight_format(ck: ShardedCheckpoint, base: str) -> Tuple[str, Optional[str], int]:
@@ -117,6 +117,7 @@ def _layer(ck, prefix: str, layer: int, cfg: ModelConfig, rank: int, world: int,
     return lw
 
 
+@fails_closed
 def load_deepseek_hf(directory, device="cpu", dtype=torch.bfloat16, tp_rank: int = 0, tp_world: int = 1,
                      cfg: Optional[ModelConfig] = None, max_layers: int = 0) -> ModelWeights:
     """`max_layers` > 0: bind only the first layers of the checkpoint (a smoke run of a large model; the proposal

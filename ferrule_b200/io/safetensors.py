@@ -31,6 +31,23 @@ _REV = {torch.float32: "F32", torch.bfloat16: "BF16", torch.float16: "F16", torc
         torch.int32: "I32", torch.int64: "I64", torch.bool: "BOOL"}
 
 
+def fails_closed(fn):
+    """Loader entry points answer a damaged checkpoint (missing tensors, a config with impossible values, shapes
+    that do not fit) with CheckpointError, whatever the first symptom was."""
+    import functools
+
+    @functools.wraps(fn)
+    def wrapper(*args, **kw):
+        try:
+            return fn(*args, **kw)
+        except CheckpointError:
+            raise
+        except (KeyError, TypeError, ValueError, RuntimeError, AttributeError, IndexError, ZeroDivisionError, OSError) as exc:
+            raise CheckpointError(f"{fn.__name__}: the checkpoint does not fit the model it describes "
+                                  f"({type(exc).__name__}: {exc})") from exc
+    return wrapper
+
+
 class CheckpointError(RuntimeError):
     pass
 

@@ -24,7 +24,7 @@ import torch
 
 from ..models.v4_model import V4Config, V4LayerWeights, V4ProposalWeights, V4Weights
 from .checkpoint import _put_linear, read_linear
-from .safetensors import CheckpointError, ShardedCheckpoint, write_sharded
+from .safetensors import CheckpointError, ShardedCheckpoint, fails_closed, write_sharded
 
 
 def v4_config_from_hf(hf: dict) -> V4Config:
@@ -98,6 +98,7 @@ def _raw(ck: ShardedCheckpoint, name: str, dev, dtype=None) -> torch.Tensor:
     return (t.to(dtype) if dtype is not None else t).to(dev)
 
 
+@fails_closed
 def load_v4_hf(directory, device="cpu", max_layers: int = 0) -> V4Weights:
     """Bind a DeepSeek-V4 checkpoint directory: every linear decoded to bf16, experts stacked per layer
     ([E, 2 * inter, hidden] gate over up, [E, hidden, inter]), the output projection's first stage regrouped to

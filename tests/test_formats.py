@@ -274,3 +274,40 @@ def test_damaged_safetensors_headers_are_checkpoint_errors(tmp_path):
     path.write_bytes(struct.pack("<Q", 6) + b"[1, 2]")             # valid JSON, not an object
     with pytest.raises(CheckpointError):
         ShardedCheckpoint(tmp_path).read("a.weight")              # shards are opened when first read
+
+
+def test_loaders_fail_closed_on_damaged_checkpoints(tmp_path):
+    """A tensor missing from the index, or a config whose numbers do not fit the tensors: both loaders answer
+    CheckpointError (the CLI prints the reason and exits 2), whatever the first symptom inside was."""
+    import contextlib, io, os
+    from ferrule_b200.cli.main import main as cli_main
+    from ferrule_b200.io.checkpoint import load_deepseek_hf
+    from ferrule_b200.io.safetensors import CheckpointError
+    from ferrule_b200.io.v4_checkpoint import load_v4_hf
+    with contextlib.redirect_stdout(io.StringIO()):
+        cli_main(["make-fixture", "--out", str(tmp_path / "ds")])
+        cli_main(["make-fixture", "--family", "v4", "--out", str(tmp_path / "v4"), "--plain", "--proposal-stages", "1"])
+    cases = {"ds": (load_deepseek_hf, "model.layers.0.self_attn.o_proj.weight", {"kv_lora_rank": 0, "rope_scaling": "x",
+                                                                                 "num_attention_heads": 10 ** 9}),
+             "v4": (load_v4_hf, "layers.1.attn.wq_a.weight", {"o_groups": 0, "n_routed_experts": 0, "hidden_size": None,
+                                                              "num_nextn_predict_layers": 10 ** 9})}
+    for name, (loader, tensor, cfg_damage) in cases.items():
+        d = tmp_path / name
+        idx_path, cfg_path = d / "model.safetensors.index.json", d / "config.json"
+        idx, cfg = json.loads(idx_path.read_text()), json.loads(cfg_path.read_text())
+        bad = dict(idx, weight_map={k: v for k, v in idx["weight_map"].items() if k != tensor})
+        idx_path.write_text(json.dumps(bad))
+        with pytest.raises(CheckpointError):
+            loader(d)
+        err = io.StringIO()
+        with contextlib.redirect_stderr(err), contextlib.redirect_stdout(io.StringIO()):
+            rc = cli_main(["generate", str(d), "--device", "cpu", "--tokens", "1,2", "-n", "1", "--ctx-size", "64",
+                           "--page-size", "16", "--max-seqs", "2"])
+        assert rc == 2 and "error:" in err.getvalue()
+        idx_path.write_text(json.dumps(idx))
+        for key, val in cfg_damage.items():
+            cfg_path.write_text(json.dumps(dict(cfg, **{key: val})))
+            with pytest.raises(CheckpointError):
+                loader(d)
+        cfg_path.write_text(json.dumps(cfg))
+        loader(d)
