@@ -252,14 +252,10 @@ class DeepSeekRunner(ModelRunner):
         if self.arena is not None and self.telemetry is None:
             from ..utils.telemetry import ExpertTelemetry
             self.telemetry = ExpertTelemetry(self.cfg.n_layers + len(weights.mtp), max(weights.e_hi - weights.e_lo, 1))
-        # hot-set predictor (frequency, recency, step-to-step transitions per layer) fed by every streamed layer pass;
-        # it ranks the prefetch candidates of parked transactions
+        # hot-set predictor (frequency, recency, step-to-step transitions per layer): ranks the prefetch candidates
+        # of parked transactions.  Built by the first call of `prefetch_candidates` - a runner nobody asks for
+        # candidates does not pay for the observations (tens of microseconds per streamed layer pass)
         self.predictor = None
-        if self.arena is not None:
-            from ..runtime.expert_prediction import ExpertPredictor
-            self.predictor = ExpertPredictor(max(weights.e_hi - weights.e_lo, 1))
-            if self.is_cuda:
-                self.fwd.predictor = self.predictor
 
     # ------------------------------------------------------------------ contract
     def capabilities(self) -> ExecutionCapabilities:
@@ -311,8 +307,14 @@ class DeepSeekRunner(ModelRunner):
         nearest first, the non-resident experts the hot-set predictor ranks highest (at most as many per layer as
         the layer has frames) - at most `n` materialization keys.  The engine requests them without a waiter
         while the transaction waits."""
-        if not self.async_streaming or self.predictor is None or n <= 0:
+        if not self.async_streaming or n <= 0:
             return []
+        if self.predictor is None:
+            from ..runtime.expert_prediction import ExpertPredictor
+            self.predictor = ExpertPredictor(max(self.w.e_hi - self.w.e_lo, 1))
+            if self.is_cuda:
+                self.fwd.predictor = self.predictor
+            return []                       # nothing observed yet
         out = []
         for l in sorted(k for k in self.arena.layers if k > layer):
             la = self.arena.layers[l]
@@ -332,7 +334,8 @@ class DeepSeekRunner(ModelRunner):
             return                      # a layer whose experts are all resident (the proposal stage)
         if not self._wave_state.get(layer, {}).get("done"):
             self.telemetry.record(layer, experts)           # once per layer pass, not per resumed wave
-            self.predictor.observe(layer, experts)
+            if self.predictor is not None:
+                self.predictor.observe(layer, experts)
         frames = self.arena.frames(layer)
         held = self._lease_sink.setdefault(layer, {})
         if len(experts) <= frames:

@@ -54,51 +54,60 @@ class PredictionStats:
 
 
 class ExpertPredictor:
+    """Per layer: decayed use counts, last-use steps and a decayed transition matrix (rows: experts of the previous
+    pass, columns: experts of the pass that followed) as numpy arrays - one observation is a few vector operations,
+    cheap enough to run for every streamed layer of every step."""
+
     def __init__(self, n_experts: int, weights: PredictorWeights = None):
+        import numpy as np
+        self._np = np
         self.n, self.w = n_experts, weights or PredictorWeights()
-        self.freq: Dict[int, List[float]] = {}
-        self.last: Dict[int, List[int]] = {}
-        self.trans: Dict[int, Dict[int, Dict[int, float]]] = {}
-        self.prev: Dict[int, Set[int]] = {}
+        self.freq: Dict[int, "np.ndarray"] = {}
+        self.last: Dict[int, "np.ndarray"] = {}
+        self.trans: Dict[int, "np.ndarray"] = {}
+        self.prev: Dict[int, List[int]] = {}
         self.step: Dict[int, int] = defaultdict(int)
         self._last_pred: Dict[int, Set[int]] = {}
         self.stats = PredictionStats()
 
     def observe(self, layer: int, experts: Iterable[int]) -> None:
-        used = set(experts)
-        f = self.freq.setdefault(layer, [0.0] * self.n)
-        l = self.last.setdefault(layer, [-10 ** 9] * self.n)
-        tr = self.trans.setdefault(layer, {})
+        np = self._np
+        used = sorted({int(e) for e in experts if 0 <= int(e) < self.n})
+        f = self.freq.get(layer)
+        if f is None:
+            f = self.freq[layer] = np.zeros(self.n)
+            self.last[layer] = np.full(self.n, -10 ** 9, dtype=np.int64)
+            self.trans[layer] = np.zeros((self.n, self.n), dtype=np.float32)
         self.step[layer] += 1
-        for e in range(self.n):
-            f[e] *= self.w.decay
-        for e in used:
-            f[e] += 1.0
-            l[e] = self.step[layer]
-        for p in self.prev.get(layer, ()):
-            row = tr.setdefault(p, {})
-            for e in used:
-                row[e] = row.get(e, 0.0) * self.w.decay + 1.0
+        f *= self.w.decay
+        if used:
+            f[used] += 1.0
+            self.last[layer][used] = self.step[layer]
+            prev = self.prev.get(layer)
+            if prev:
+                rows = self.trans[layer][np.ix_(prev, used)]
+                self.trans[layer][np.ix_(prev, used)] = rows * self.w.decay + 1.0
         pred = self._last_pred.pop(layer, None)
         if pred is not None:
-            self.stats.hits += len(pred & used)
+            self.stats.hits += len(pred & set(used))
         self.prev[layer] = used
 
     def predict(self, layer: int, n: int, exclude: Iterable[int] = ()) -> List[int]:
+        np = self._np
         f = self.freq.get(layer)
-        if f is None:
+        if f is None or n <= 0:
             return []
-        skip = set(exclude)
-        l, tr, now = self.last[layer], self.trans.get(layer, {}), self.step[layer]
-        fmax = max(max(f), 1e-9)
-        score = []
-        for e in range(self.n):
-            if e in skip:
-                continue
-            t = sum(tr.get(p, {}).get(e, 0.0) for p in self.prev.get(layer, ()))
-            s = self.w.frequency * f[e] / fmax + self.w.recency / (1.0 + now - l[e]) + self.w.transition * t / (1.0 + t)
-            score.append((-s, e))
-        out = [e for _, e in sorted(score)[:n]]
+        now = self.step[layer]
+        prev = self.prev.get(layer) or []
+        t = self.trans[layer][prev].sum(0) if prev else np.zeros(self.n)
+        score = (self.w.frequency * f / max(float(f.max()), 1e-9) + self.w.recency / (1.0 + now - self.last[layer])
+                 + self.w.transition * t / (1.0 + t))
+        skip = [int(e) for e in exclude if 0 <= int(e) < self.n]
+        if skip:
+            score = score.copy()
+            score[skip] = -np.inf
+        order = np.lexsort((np.arange(self.n), -score))            # best score first, lower id on ties
+        out = [int(e) for e in order[:n] if score[e] > -np.inf]
         self._last_pred[layer] = set(out)
         self.stats.predictions += 1
         self.stats.predicted += len(out)
