@@ -70,6 +70,9 @@ def _add_model_args(p: argparse.ArgumentParser) -> None:
                         "tensor-parallel ranks, rank 0 serves and the others mirror its command stream")
     p.add_argument("--microbatches", type=int, default=2)
     p.add_argument("--collective", default="ll", choices=["ll", "multimem"])
+    p.add_argument("--sequence-parallel", action="store_true",
+                   help="tensor-parallel replicas: keep the residual stream sharded by rows between reduce-scatter and "
+                        "all-gather (prefill-sized batches)")
     p.add_argument("--mc-push", action="store_true")
 
 
@@ -164,6 +167,7 @@ def build_engine(args, layout=None):
     runner = DeepSeekRunner(weights, n_pages=n_pages, page_size=args.page_size, max_rows=args.max_batch_tokens,
                             max_seqs=args.max_seqs, max_seq_len=pages_per_seq * args.page_size, device=dev,
                             tp=layout.tp if layout is not None else None, pp=layout.pp if layout is not None else None,
+                            sequence_parallel=getattr(args, "sequence_parallel", False),
                             expert_residency=residency, async_streaming=streaming, enable_mtp=args.speculative,
                             max_draft=max(args.max_draft, 1))
     if layout is not None and layout.tp is not None and str(dev) != "cpu":

@@ -100,6 +100,11 @@ class ReferenceForward:
         self.route_observer = None     # callable(layer, expert ids [T, k], T): route statistics (parallel/placement.py)
         self.prof = None               # utils.stage_profile.StageProfiler: per-layer stage table
         self.tap = None                # utils.stage_profile.DebugTap: dumps of intermediate rows
+        # sequence parallelism (parallel.tp.TensorParallel with the host collectives): between the reduce-scatter
+        # after a sublayer and the all-gather in front of the next one every rank holds only its slice of the rows -
+        # residual stream, residual adds and norms are sharded by rows, the collectives move the same bytes as the
+        # all-reduce they replace
+        self.sp = None
         self._layer_index = -1
         cfg = self.cfg
         dev = weights.embed.device
@@ -182,6 +187,18 @@ class ReferenceForward:
             out = out + rnd(self._ffn(lw.w13, lw.w2, xn))
         return out
 
+    def layer_sp(self, lw: LayerWeights, layer: int, h_rows: torch.Tensor, b: DeviceBatch, T: int) -> torch.Tensor:
+        """One layer on row-sharded activations: `h_rows` are this rank's rows of the residual stream (in and out).
+        all-gather(norm(rows)) -> sublayer on all rows with this rank's heads / experts -> reduce-scatter -> add."""
+        cfg, rnd, sp = self.cfg, self.rnd, self.sp
+        self._layer_index = layer
+        xn = sp.all_gather_reference(rnd(ref.rmsnorm(h_rows, lw.attn_norm, cfg.rms_eps)), T)
+        a = self._attention(lw, layer, xn, b)
+        h_rows = rnd(h_rows + sp.reduce_scatter_reference(a.contiguous()))
+        xn = sp.all_gather_reference(rnd(ref.rmsnorm(h_rows, lw.ffn_norm, cfg.rms_eps)), T)
+        f = self._moe(lw, xn, b.token_ids[:T]) if lw.is_moe else self._ffn(lw.w13, lw.w2, xn)
+        return rnd(h_rows + sp.reduce_scatter_reference(f.contiguous()))
+
     def layer(self, lw: LayerWeights, layer: int, h: torch.Tensor, b: DeviceBatch, allreduce=None) -> torch.Tensor:
         cfg, rnd = self.cfg, self.rnd
         T = h.shape[0]
@@ -223,6 +240,16 @@ class ReferenceForward:
     def run_layers(self, h: torch.Tensor, b: DeviceBatch, allreduce=None, start_layer: int = 0) -> torch.Tensor:
         """The layers this weight image holds (all of them, or one pipeline stage's share), from `start_layer`
         (a resumed transaction continues at the layer it stopped at, with that layer's input rows as `h`)."""
+        if self.sp is not None and allreduce is not None and self.sp.world > 1:
+            # sequence parallel: every rank enters with the replicated rows, keeps its slice through the layers and
+            # gathers the slices once at the end
+            T = h.shape[0]
+            lo, hi = self.sp.row_range(T)
+            rows = h[lo:hi].contiguous()
+            for i, lw in enumerate(self.w.layers):
+                if i >= start_layer:
+                    rows = self.layer_sp(lw, i, rows, b, T)
+            return self.sp.all_gather_reference(rows, T)
         for i, lw in enumerate(self.w.layers):
             if i < start_layer:
                 continue
@@ -448,6 +475,9 @@ class CudaForward:
         # callable(layer, expert ids [T, k] on the device, T): route statistics for placement planning.  The observer
         # reads the ids on the host, so a forward that has one is neither captured in a graph nor overlapped
         self.route_observer = None
+        # sequence parallelism for batches above the fused all-reduce's row limit (bf16 weights, replicated-activation
+        # MoE): the residual stream stays sharded by rows between a sublayer's reduce-scatter and the next all-gather
+        self.sequence_parallel = False
         # utils.stage_profile: per-layer stage table (marks are CUDA events on the launching stream; a profiled
         # forward is not captured in a graph) and dumps of intermediate rows
         self.prof = None
@@ -1008,6 +1038,42 @@ class CudaForward:
                                  act_limit=cfg.swiglu_limit, allgather=True, gather_row0=lo)
         return gathered.view(-1, cfg.hidden)[:T]
 
+    def _sp_active(self, T: int) -> bool:
+        tp = self.tp
+        if not self.sequence_parallel or tp is None or tp.world < 2 or T <= tp.fused_max_rows or self.ep is not None:
+            return False
+        if self.arena is not None:
+            return False
+        plain = lambda t: t is None or isinstance(t, torch.Tensor)
+        return all(plain(getattr(lw, n)) for lw in self.w.layers
+                   for n in ("w_qkv_a", "w_q_b", "w_o", "w13", "w2", "e_w13", "e_w2"))
+
+    def layer_sp(self, lw: LayerWeights, layer: int, h_in: torch.Tensor, h_out: torch.Tensor, b: DeviceBatch,
+                 T: int) -> torch.Tensor:
+        """One layer on a row-sharded residual stream: only rows [lo, hi) of `h_in` / `h_out` / the result are this
+        rank's and valid.  norm(rows) -> all-gather -> sublayer on all rows with this rank's heads / experts ->
+        fp32 partial -> reduce-scatter + residual add on the rows.  Returns the buffer that holds the result."""
+        K, cfg, ws, tp = self.K, self.cfg, self.ws, self.tp
+        lo, hi = tp.row_range(T)
+        n = hi - lo
+        xn, xs = ws.xn[:T], ws.delta[:n]                    # delta: free in this form, holds the normalised slice
+        self._norm(h_in[lo:hi], lw.attn_norm, n, xs, None, None)
+        tp.all_gather(xs, xn, T)
+        a, w_o = self._attention(lw, layer, xn, b, T)
+        tp.gemm_reduce_scatter(a, w_o, h_in[lo:hi], h_out[lo:hi], T)
+        self._norm(h_out[lo:hi], lw.ffn_norm, n, xs, None, None)
+        tp.all_gather(xs, xn, T)
+        if lw.is_moe:
+            idx = self._moe_local(lw, xn, b, T, layer)
+            tp.moe_reduce_scatter(ws.route_out[:T].view(T * ws.slots, cfg.hidden), ws.slots, cfg.topk, idx,
+                                  self.w.e_lo, self.w.e_hi, h_out[lo:hi], h_in[lo:hi], T)
+            return h_in
+        inter = lw.w13.shape[1] // 2
+        mid = ws.ffn_mid[:T, :inter]
+        K.gemm(xn, lw.w13, out=mid, epilogue=K.EPI_SWIGLU, act_limit=cfg.swiglu_limit)
+        tp.gemm_reduce_scatter(mid, lw.w2, h_out[lo:hi], h_in[lo:hi], T)
+        return h_in
+
     def layer(self, lw: LayerWeights, layer: int, h_in: torch.Tensor, h_out: torch.Tensor, b: DeviceBatch,
               T: int, first_norm_done: bool = False, next_norm: Optional[torch.Tensor] = None) -> torch.Tensor:
         """h_in -> h_out (both bf16 [T, H]); returns h_out."""
@@ -1121,6 +1187,14 @@ class CudaForward:
             self.M.fill_(ws.route_cnt, 0)
         h, other = ws.h[0][:T], ws.h[1][:T]
         layers = self.w.layers
+        if start_layer == 0 and self._sp_active(T):
+            # every rank enters with the replicated rows, keeps its slice through the layers, and the slices are
+            # gathered once at the end (the head reads arbitrary rows)
+            for i, lw in enumerate(layers):
+                h = self.layer_sp(lw, i, h, other, b, T)
+            lo, hi = self.tp.row_range(T)
+            self.tp.all_gather(h[lo:hi].clone(), h, T)
+            return h
         fused = False                     # the previous layer wrote this layer's normalised input
         for i, lw in enumerate(layers):
             if i < start_layer:

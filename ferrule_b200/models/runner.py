@@ -156,7 +156,7 @@ class DeepSeekRunner(ModelRunner):
                  max_seqs: int = 64, max_seq_len: int = 4096, device=None, tp=None, use_graphs: bool = True,
                  emulate_bf16: bool = False, attn_splits: int = 8, enable_mtp: bool = True, max_draft: int = 1,
                  expert_residency: Optional[float] = None, async_streaming: bool = False,
-                 lookahead: bool = True, pp=None):
+                 lookahead: bool = True, pp=None, sequence_parallel: bool = False):
         self.w, self.cfg = weights, weights.cfg
         self.device = torch.device(device if device is not None else weights.embed.device)
         self.is_cuda = self.device.type == "cuda"
@@ -249,6 +249,16 @@ class DeepSeekRunner(ModelRunner):
             else:
                 self.fwd.expert_gate = self._expert_gate
         self.fwd.prof, self.fwd.tap = self.profiler, self.debug_tap
+        # sequence parallelism over the tensor-parallel ranks: the residual stream stays sharded by rows between the
+        # reduce-scatter behind a sublayer and the all-gather in front of the next (not with parked transactions:
+        # a layer that stops half-way hands its input rows back whole)
+        self.sequence_parallel = bool(sequence_parallel and tp is not None and tp.world > 1 and not self.async_streaming
+                                      and pp is None)
+        if self.sequence_parallel:
+            if self.is_cuda:
+                self.fwd.sequence_parallel = True       # batches above the fused all-reduce's row limit
+            else:
+                self.fwd.sp = tp
         if self.arena is not None and self.telemetry is None:
             from ..utils.telemetry import ExpertTelemetry
             self.telemetry = ExpertTelemetry(self.cfg.n_layers + len(weights.mtp), max(weights.e_hi - weights.e_lo, 1))

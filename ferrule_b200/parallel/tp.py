@@ -213,6 +213,52 @@ class TensorParallel:
             pairs[r].copy_(b)
 
     # ------------------------------------------------------------------ reference path (any backend)
+    # ------------------------------------------------------------------ sequence parallelism
+    def gemm_reduce_scatter(self, x: torch.Tensor, w: torch.Tensor, residual_rows: torch.Tensor, out_rows: torch.Tensor,
+                            T: int) -> torch.Tensor:
+        """out_rows = bf16(residual_rows + this rank's rows of the sum over ranks of x @ w^T): the GEMM leaves its
+        fp32 partial in local memory, the reduce-scatter (in-switch when bound, NCCL otherwise) sums and cuts it."""
+        tmp = self._tmp32[:T]
+        K.gemm(x, w, out=tmp)
+        return self.reduce_scatter(tmp, out_rows, T, residual_slice=residual_rows)
+
+    def moe_reduce_scatter(self, route_out: torch.Tensor, slots: int, topk: int, idx: torch.Tensor, e_lo: int, e_hi: int,
+                           residual_rows: torch.Tensor, out_rows: torch.Tensor, T: int) -> torch.Tensor:
+        tmp = self._tmp32[:T]
+        K.moe_reduce(route_out, slots, topk, idx, e_lo, e_hi, T, self.hidden, out=tmp)
+        return self.reduce_scatter(tmp, out_rows, T, residual_slice=residual_rows)
+
+    def row_range(self, T: int):
+        """Rows of a T-row batch this rank owns between a reduce-scatter and the next all-gather (contiguous
+        slices of ceil(T / world) rows; the last ranks' slices may be short or empty)."""
+        per = (T + self.world - 1) // self.world
+        lo = min(self.rank * per, T)
+        return lo, min(lo + per, T)
+
+    def reduce_scatter_reference(self, t: torch.Tensor) -> torch.Tensor:
+        """Host path: this rank's rows of the sum over ranks of `t` [T, hidden]."""
+        T = t.shape[0]
+        per = (T + self.world - 1) // self.world
+        pad = torch.zeros(per * self.world, t.shape[1], dtype=t.dtype, device=t.device)
+        pad[:T] = t
+        try:
+            out = torch.empty(per, t.shape[1], dtype=t.dtype, device=t.device)
+            dist.reduce_scatter_tensor(out, pad, group=self.group)
+        except (RuntimeError, NotImplementedError):          # a backend without reduce-scatter (gloo on CPU)
+            dist.all_reduce(pad, group=self.group)
+            out = pad[self.rank * per:(self.rank + 1) * per]
+        lo, hi = self.row_range(T)
+        return out[:hi - lo].contiguous()
+
+    def all_gather_reference(self, rows: torch.Tensor, T: int) -> torch.Tensor:
+        """Host path: the ranks' row slices put back together -> [T, hidden]."""
+        per = (T + self.world - 1) // self.world
+        mine = torch.zeros(per, rows.shape[1], dtype=rows.dtype, device=rows.device)
+        mine[:rows.shape[0]] = rows
+        bufs = [torch.empty_like(mine) for _ in range(self.world)]
+        dist.all_gather(bufs, mine, group=self.group)
+        return torch.cat(bufs, dim=0)[:T].contiguous()
+
     def allreduce_reference(self, t: torch.Tensor) -> torch.Tensor:
         t = t.contiguous()
         dist.all_reduce(t, group=self.group)

@@ -77,6 +77,8 @@ def main() -> int:
     ap.add_argument("--payload", default="fp32", choices=["fp32", "bf16"])
     ap.add_argument("--collective", default="ll", choices=["ll", "multimem"])
     ap.add_argument("--mc-push", action="store_true")
+    ap.add_argument("--sequence-parallel", action="store_true",
+                    help="also check the row-sharded form of the layers (batches above the fused all-reduce's row limit)")
     ap.add_argument("--bench-hidden", type=int, default=2048)
     ap.add_argument("--bench-rows", type=int, default=32)
     args = ap.parse_args()
@@ -294,6 +296,44 @@ def main() -> int:
         res["checks"]["payload_streams_equal"] = bool(a_s == b_s)
         res["checks"]["payload_streams_equal_or_tie"] = bool(same)
         ok &= same
+
+    # 4c. sequence parallelism: a 72-row prompt batch with the residual stream sharded by rows between the
+    # reduce-scatters and all-gathers, against the single-GPU forward
+    if args.sequence_parallel:
+        tp_s = TensorParallel(rank, world, dev, fused=True, fused_max_rows=16, payload=args.payload,
+                              collective=args.collective, multicast_push=args.mc_push)
+        pool_s = D.KvPool(cfg, 32, 64, dev)
+        fwd_s = D.CudaForward(w_tp, pool_s, max_rows=256, max_logit_rows=8, decode_rows=64, max_seq_len=512,
+                              attn_splits=2, tp=tp_s)
+        tp_s.attach(fwd_s)
+        fwd_s.sequence_parallel = True
+        pool1.data.zero_()
+        bt = torch.stack([torch.arange(1 + 8 * s_, 9 + 8 * s_) for s_ in range(3)]).to(torch.int32)
+        gg = torch.Generator().manual_seed(91)
+        ids_l, pos, slot, rseq, lrows = [], [], [], [], []
+        for s_, nn in enumerate((40, 9, 23)):
+            for p_ in range(nn):
+                ids_l.append(int(torch.randint(0, cfg.vocab_size, (1,), generator=gg)))
+                pos.append(p_)
+                slot.append(int(bt[s_, p_ // 64]) * 64 + p_ % 64)
+                rseq.append(s_)
+            lrows.append(len(ids_l) - 1)
+        mk = lambda v, dt: torch.tensor(v, dtype=dt, device=dev)
+        b = D.DeviceBatch(mk(ids_l, torch.int32), mk(pos, torch.int32), mk(slot, torch.int64), mk(rseq, torch.int32),
+                          mk(pos, torch.int32), bt.to(dev), mk(lrows, torch.int32), len(ids_l), 3)
+        assert fwd_s._sp_active(len(ids_l))
+        id_s, val_s, _ = fwd_s.forward(b)
+        id_s, val_s = id_s.clone(), val_s.clone()
+        id_1, val_1, lg = fwd1.forward(b, want_logits=True)
+        torch.cuda.synchronize()
+        err = (val_s - val_1).abs()
+        top2 = lg.topk(2, dim=-1).values
+        clear = (top2[:, 0] - top2[:, 1]) > 4 * err.max() + 1e-3
+        sp_ok = (float(err.max()) <= 0.05 * float(lg.abs().max()) + 1e-2
+                 and bool(torch.equal(id_s[clear].cpu(), id_1[clear].cpu())))
+        res["checks"]["sequence_parallel_matches"] = bool(sp_ok)
+        res["checks"]["sequence_parallel_val_err"] = float(err.max())
+        ok &= sp_ok
 
     # 5. the same model with token-dispatch expert parallelism in its MoE layers (tensor-parallel attention, every
     # rank routes its own slice of the tokens, shared experts replicated) against the single-GPU forward

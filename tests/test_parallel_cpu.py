@@ -265,3 +265,46 @@ def test_engine_over_two_stages_of_two_tensor_ranks_each():
         dist.destroy_process_group()
     ''', 4, 29619, timeout=240)
     assert p.stdout.count("PPTP_OK") == 4, p.stdout[-2000:] + p.stderr[-3000:]
+
+
+def test_sequence_parallel_reference_on_gloo_equals_single_process():
+    """Tensor-parallel ranks that keep the residual stream sharded by rows between reduce-scatter and all-gather
+    (row counts that do not divide by the world size included): the engine's greedy stream equals the
+    single-process one, and equals the all-reduce form's."""
+    p = _run('''
+        import torch, torch.distributed as dist
+        from ferrule_b200.models import config as C, weights as W
+        from ferrule_b200.models.runner import DeepSeekRunner
+        from ferrule_b200.parallel.tp import TensorParallel
+        from ferrule_b200.runtime.engine import Engine, EngineConfig, TokenEvent
+        from ferrule_b200.runtime.scheduler import SchedulerConfig
+        from ferrule_b200.runtime.session import GenerateRequest
+        dist.init_process_group("gloo")
+        rank, world = dist.get_rank(), dist.get_world_size()
+        cfg = C.tiny_fixture()
+        def run(w, tp, sp):
+            runner = DeepSeekRunner(w, n_pages=32, page_size=16, max_rows=128, max_seqs=4, max_seq_len=256, device="cpu",
+                                    tp=tp, enable_mtp=False, sequence_parallel=sp)
+            assert runner.sequence_parallel == (sp and tp is not None)
+            sched = SchedulerConfig(max_active_sequences=4, max_decode_batch=4, max_batch_tokens=64, prefill_chunk_size=32,
+                                    ctx_size=256)
+            eng = Engine(runner, EngineConfig(scheduler=sched, kv_pages=32, page_size=16))
+            g = torch.Generator().manual_seed(5)
+            for i, n in enumerate((21, 40, 7)):
+                eng.submit(GenerateRequest(f"r{i}", torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist(),
+                                           max_new_tokens=6, ignore_eos=True))
+            ev = []
+            eng.run_until_idle(ev.append, max_steps=2000)
+            assert eng.last_error is None, eng.last_error
+            return [(e.request_id, e.token) for e in ev if isinstance(e, TokenEvent)]
+        want = run(W.random_weights(cfg, device="cpu", seed=0, dtype=torch.float32), None, False)
+        shard = lambda: W.random_weights(cfg, device="cpu", seed=0, dtype=torch.float32, tp_rank=rank, tp_world=world)
+        tp = TensorParallel(rank, world, "cpu", fused=False)
+        assert tp.row_range(7) == ((0, 4) if rank == 0 else (4, 7)) and tp.row_range(1) == ((0, 1) if rank == 0 else (1, 1))
+        got_sp = run(shard(), tp, True)
+        got_ar = run(shard(), tp, False)
+        ok = got_sp == want and got_ar == want and len(want) == 18
+        print("SP_OK" if ok else "SP_BAD", rank, flush=True)
+        dist.destroy_process_group()
+    ''', 2, 29641)
+    assert p.stdout.count("SP_OK") == 2, p.stdout[-2000:] + p.stderr[-3000:]
