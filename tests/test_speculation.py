@@ -119,3 +119,106 @@ def test_rejected_suffix_pages_are_retired():
     assert eng.spec.metrics.accepted == 0
     assert len(r.released_pages) >= 2
     eng.kv.check_invariants()
+
+
+class _Recording(MockRunner):
+    def __init__(self, *a, **k):
+        super().__init__(*a, **k)
+        self.batches = []
+
+    def execute(self, txn_id):
+        self.batches.append(self.txns[txn_id])
+        return super().execute(txn_id)
+
+
+def test_two_ragged_sessions_are_verified_in_one_provisional_execution():
+    """Different draft lengths per sequence (one pruned by its confidence): one provisional batch holds both,
+    rows = 1 + drafts per sequence, top-1 logits on every row."""
+    from ferrule_b200.runtime.execution import Intent
+    from ferrule_b200.runtime.runner import Proposal
+    r = _Recording(draft_len=3)
+    eng = make(r, True, max_draft=3)
+    orig = r.propose
+
+    def propose(slots, anchors, positions, views, max_draft):
+        out = orig(slots, anchors, positions, views, max_draft)
+        # the second sequence's head loses confidence after one draft
+        return [p if i == 0 else Proposal(p.tokens, [5.0] + [-5.0] * (len(p.tokens) - 1)) for i, p in enumerate(out)]
+
+    r.propose = propose
+    eng.submit(GenerateRequest("a", [1, 2, 3, 4, 5], max_new_tokens=12))
+    eng.submit(GenerateRequest("b", [9, 8, 7], max_new_tokens=12))
+    ev = run(eng)
+    prov = [b for b in r.batches if b.intent == Intent.PROVISIONAL_VERIFICATION and len(b.sequences) == 2]
+    assert prov, "both sequences shared a verification batch"
+    b0 = prov[0]
+    assert sorted(s.query_len for s in b0.sequences) == [2, 4] and b0.rows == 6
+    assert all(b0.logits[i].k == 1 for i in range(b0.rows))
+    plain = make(MockRunner(), False)
+    plain.submit(GenerateRequest("a", [1, 2, 3, 4, 5], max_new_tokens=12))
+    plain.submit(GenerateRequest("b", [9, 8, 7], max_new_tokens=12))
+    ep = run(plain)
+    assert toks(ev, "a") == toks(ep, "a") and toks(ev, "b") == toks(ep, "b")
+    assert eng.spec.metrics.pruned_by_confidence > 0
+
+
+def test_zero_draft_capacity_runs_an_ordinary_step():
+    """One token left to generate: there is no room for a draft, so no proposal block is verified - the cycle
+    counts as a zero-draft cycle and the step is an ordinary decode."""
+    from ferrule_b200.runtime.execution import Intent
+    r = _Recording(draft_len=3)
+    eng = make(r, True, max_draft=3)
+    eng.submit(GenerateRequest("a", [1, 2, 3], max_new_tokens=1))
+    ev = run(eng)
+    assert len(toks(ev, "a")) == 1
+    assert not any(b.intent == Intent.PROVISIONAL_VERIFICATION for b in r.batches)
+    assert eng.spec.metrics.cycles == 0 and eng.spec.metrics.drafted == 0
+
+
+def test_proposals_can_be_switched_off_mid_run():
+    """The runner stops proposing (policy change): decoding goes on as plain greedy steps, same stream."""
+    r = MockRunner(draft_len=2)
+    eng = make(r, True, max_draft=2)
+    prompt = [4, 5, 6, 7]
+    eng.submit(GenerateRequest("a", prompt, max_new_tokens=14))
+    ev = []
+    while eng.stats.finished == 0 and len(toks(ev, "a")) < 6:
+        eng.step(ev.append)
+    cycles = eng.spec.metrics.cycles
+    assert cycles > 0
+    r.draft_len = 0                              # proposals_enabled() is False from here on
+    ev += run(eng)
+    assert eng.spec.metrics.cycles == cycles
+    plain = make(MockRunner(), False)
+    plain.submit(GenerateRequest("a", prompt, max_new_tokens=14))
+    assert toks(ev, "a") == toks(run(plain), "a")
+
+
+def test_failure_while_keeping_the_accepted_prefix_rolls_the_cycle_back():
+    """`retain_provisional_prefixes` fails once: the whole cycle is rolled back (nothing of it is published, its
+    reservations and pages return), the next cycle verifies again, and the stream is exact."""
+    r = MockRunner(draft_len=2)
+    eng = make(r, True, max_draft=2)
+    orig, state = r.retain_provisional_prefixes, {"left": 1}
+
+    def flaky(txn_id, keep):
+        if state["left"]:
+            state["left"] -= 1
+            raise RuntimeError("backend could not keep the prefix")
+        return orig(txn_id, keep)
+
+    r.retain_provisional_prefixes = flaky
+    prompt = [3, 1, 4, 1, 5]
+    eng.submit(GenerateRequest("a", prompt, max_new_tokens=9))
+    ev = run(eng)
+    plain = make(MockRunner(), False)
+    plain.submit(GenerateRequest("a", prompt, max_new_tokens=9))
+    ep = run(plain)
+    if [e for e in ev if isinstance(e, FinishEvent)][0].reason == FinishReason.ERROR:
+        # a non-retryable backend failure ends the request; nothing of the failed cycle was published
+        assert toks(ev, "a") == toks(ep, "a")[:len(toks(ev, "a"))]
+    else:
+        assert toks(ev, "a") == toks(ep, "a")
+    assert eng.spec.metrics.rollbacks == 1
+    eng.kv.check_invariants()
+    assert eng.kv.stats().used_pages == 0 and eng.broker.outstanding() == 0
