@@ -754,6 +754,8 @@ class Engine:
         except Exception as exc:  # noqa: BLE001
             if intent == EndIntent.PUBLISH:
                 txn.error = exc
+                self.last_error = exc
+                self.stats.aborted_transactions += 1
                 if txn.commit_id is not None:
                     self.kv.abort_prepared_commit(txn.commit_id)
                     txn.commit_id = None

@@ -341,3 +341,29 @@ def test_a_parked_transaction_whose_completion_never_comes_times_out():
     assert fin(ev3, "dup").reason == FinishReason.ERROR
     eng.kv.check_invariants()
     assert eng.kv.stats().used_pages == 0
+
+
+def test_a_publish_that_the_backend_refuses_becomes_a_rollback():
+    """`end_transaction(PUBLISH)` raises: nothing of the step is published, the prepared commit is withdrawn, the
+    transaction is ended as an abort (a failing abort has nothing more to undo), the request ends with an error and
+    every page and credit is back; the engine serves the next request."""
+    r = MockRunner()
+    eng, _ = make(r)
+    orig, state = r.end_transaction, {"left": 2}
+
+    def flaky(txn_id, intent):
+        if state["left"]:
+            state["left"] -= 1
+            raise RuntimeError("cleanup failed")
+        return orig(txn_id, intent)
+
+    r.end_transaction = flaky
+    eng.submit(GenerateRequest("a", [1, 2, 3], max_new_tokens=3))
+    ev = run(eng)
+    assert toks(ev, "a") == [] and fin(ev, "a").reason == FinishReason.ERROR
+    assert "cleanup failed" in str(eng.last_error) and eng.stats.aborted_transactions == 1
+    eng.kv.check_invariants()
+    assert eng.kv.stats().used_pages == 0 and eng.broker.outstanding() == 0 and not eng._ending
+    eng.submit(GenerateRequest("b", [1, 2, 3], max_new_tokens=3))
+    ev2 = run(eng)
+    assert toks(ev2, "b") == expected(r, [1, 2, 3], 3)
