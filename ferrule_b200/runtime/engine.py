@@ -748,6 +748,10 @@ class Engine:
 
     def _end(self, txn: Transaction) -> None:
         """Ask the backend to end the transaction; publish or roll back once it is COMPLETE."""
+        if txn.state == TxnState.DONE:
+            if txn in self._ending:
+                self._ending.remove(txn)
+            return
         intent = EndIntent.PUBLISH if txn.state == TxnState.PUBLISHING else EndIntent.ABORT
         try:
             status = self.runner.end_transaction(txn.txn_id, intent)
@@ -760,7 +764,8 @@ class Engine:
                     self.kv.abort_prepared_commit(txn.commit_id)
                     txn.commit_id = None
                 txn.state = TxnState.ABORTING
-                self._ending.append(txn)
+                if txn not in self._ending:      # it may be here already (an ending that was pending before)
+                    self._ending.append(txn)
                 return
             status = EndStatus.COMPLETE       # an abort that fails has nothing more to undo
         if status == EndStatus.PENDING:

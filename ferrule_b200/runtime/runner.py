@@ -154,8 +154,8 @@ class MockRunner(ModelRunner):
     """Deterministic CPU runner for state-machine tests.
 
     next token = (7 * token + 3 * position + 1) % vocab unless `next_token_fn` is given.
-    Scripts: `fail_next_execute`, `wait_next` (returns Waiting once), `pending_ends` (number of
-    PENDING answers before an end completes), `no_candidate_rows`.
+    Scripts: `fail_next_execute`, `fail_next_end` (end_transaction raises), `wait_next` (returns Waiting once),
+    `pending_ends` (number of PENDING answers before an end completes), `no_candidate_rows`.
     """
 
     def __init__(self, vocab: int = 1000, eos: int = -1, page_size: int = 16,
@@ -168,6 +168,7 @@ class MockRunner(ModelRunner):
         self.kv: Dict[int, Tuple[int, int]] = {}           # pool row -> (token, position)
         self.provisional: Dict[int, List[int]] = {}        # txn -> rows written provisionally
         self.fail_next_execute = 0
+        self.fail_next_end = 0
         self.wait_next: List[List[object]] = []
         self.pending_ends = 0
         self.no_candidate_rows: set = set()
@@ -256,6 +257,9 @@ class MockRunner(ModelRunner):
 
     def end_transaction(self, txn_id: int, intent: EndIntent) -> EndStatus:
         self.calls.append((f"end_{intent.value}", txn_id))
+        if self.fail_next_end > 0:
+            self.fail_next_end -= 1
+            raise RuntimeError("mock runner: scripted end failure")
         left = self._pending_left.setdefault(txn_id, self.pending_ends)
         if left > 0:
             self._pending_left[txn_id] = left - 1

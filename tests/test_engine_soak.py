@@ -60,8 +60,10 @@ def _soak(seed: int, spec: bool) -> Engine:
                 live.add(rid)
             except (ValueError, RuntimeError, KeyError):
                 pass
-        elif a < 0.40:
+        elif a < 0.39:
             runner.fail_next_execute = 1
+        elif a < 0.40:
+            runner.fail_next_end = rnd.randrange(1, 3)
         elif a < 0.44:
             runner.pending_ends = rnd.randrange(0, 3)
         elif a < 0.52 and prov is not None:
@@ -76,7 +78,7 @@ def _soak(seed: int, spec: bool) -> Engine:
                 reasons[e.request_id] = e.reason
         ev.clear()
         eng.kv.check_invariants()
-    runner.pending_ends = 0
+    runner.pending_ends = runner.fail_next_end = 0
     runner.wait_next.clear()
     assert eng.run_until_idle(ev.append, max_steps=5000) < 5000, "the engine did not drain"
     for e in ev:
