@@ -31,7 +31,8 @@ def _soak(seed: int, spec: bool) -> Engine:
                                       auto_preempt=rnd.random() < 0.5,
                                       prefix_cache_tokens=rnd.choice([0, 64, 256]), prefix_block=16,
                                       materialization_timeout_s=0.01),
-                 registry=LoadRegistry(prov) if prov is not None else None)
+                 registry=LoadRegistry(prov) if prov is not None else None,
+                 detokenize=lambda ids: "".join(str(t % 10) for t in ids))
     shared = [rnd.randrange(1, 900) for _ in range(40)]           # prompts often start with a common prefix
     live, n, ev, reasons = set(), 0, [], {}
     for _ in range(500):
@@ -43,6 +44,7 @@ def _soak(seed: int, spec: bool) -> Engine:
                 head = shared[:rnd.choice([0, 0, 16, 32, 40])]
                 eng.submit(GenerateRequest(rid, head + [rnd.randrange(1, 900) for _ in range(rnd.randrange(1, 40))],
                                            max_new_tokens=rnd.randrange(0, 12), session_id=sid,
+                                           stop=["7", "13"] if rnd.random() < 0.2 else [],
                                            retain_session=bool(sid) and rnd.random() < 0.7, ignore_eos=True))
                 live.add(rid)
             except ValueError:
@@ -66,6 +68,18 @@ def _soak(seed: int, spec: bool) -> Engine:
             runner.fail_next_end = rnd.randrange(1, 3)
         elif a < 0.44:
             runner.pending_ends = rnd.randrange(0, 3)
+        elif a < 0.46 and live:
+            # manual swap-out / swap-in of a running request
+            rid = rnd.choice(sorted(live))
+            try:
+                if rid in eng.scheduler.suspended:
+                    eng.restore_session(rid)
+                else:
+                    eng.preempt_session(rid)
+            except Exception:  # noqa: BLE001 - not preemptible right now (inside a transaction, nothing cached, no pages)
+                pass
+        elif a < 0.47:
+            runner.no_candidate_rows = {rnd.randrange(0, 8)} if rnd.random() < 0.5 else set()
         elif a < 0.52 and prov is not None:
             runner.wait_next.append([_key(e) for e in rnd.sample(range(20), rnd.randrange(1, 3))])
             if rnd.random() < 0.25:
@@ -79,7 +93,13 @@ def _soak(seed: int, spec: bool) -> Engine:
         ev.clear()
         eng.kv.check_invariants()
     runner.pending_ends = runner.fail_next_end = 0
+    runner.no_candidate_rows = set()
     runner.wait_next.clear()
+    for rid in list(eng.scheduler.suspended):
+        try:
+            eng.restore_session(rid)
+        except Exception:  # noqa: BLE001 - no room yet: cancel it instead
+            eng.cancel_request(rid)
     assert eng.run_until_idle(ev.append, max_steps=5000) < 5000, "the engine did not drain"
     for e in ev:
         if isinstance(e, FinishEvent):
@@ -99,7 +119,7 @@ def _soak(seed: int, spec: bool) -> Engine:
         assert eng.registry.residual().get("continuations", 0) == 0 and not eng._waiting
         assert not any(op.waiters or op.leases for op in eng.registry.ops.values())
     assert set(reasons.values()) <= {FinishReason.MAX_TOKENS, FinishReason.CANCELLED, FinishReason.ERROR,
-                                     FinishReason.CONTEXT}
+                                     FinishReason.CONTEXT, FinishReason.STOP_STRING, FinishReason.NO_CANDIDATE}
     return eng
 
 
