@@ -351,6 +351,8 @@ class Engine:
     def fork_session_exact(self, request_id: str, new_req: GenerateRequest) -> SequenceState:
         """New request that continues from an exact copy of a live sequence's committed state.
         Pages are shared by refcount; the partially filled tail page is copied on first write."""
+        if not getattr(self.runner, "supports_prefix_sharing", True):
+            raise ValueError("this runner binds sequence state to a slot: a sequence cannot be forked by sharing pages")
         src = self.scheduler.active.get(request_id) or self._sessions.get(request_id)
         if src is None:
             raise KeyError(request_id)

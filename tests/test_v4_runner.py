@@ -198,3 +198,15 @@ def test_idle_retained_sessions_give_their_slots_to_waiting_requests_on_cpu():
         eng.reset_session(sid)
     eng.kv.check_invariants()
     assert eng.kv.stats().used_pages == 0 and eng.scheduler.slots.available == 4
+
+
+def test_v4_sessions_cannot_be_forked_by_sharing_pages():
+    cfg = tiny_v4()
+    w = random_v4_weights(cfg, device="cpu", seed=3)
+    eng, runner = _engine(w, "cpu")
+    eng.submit(GenerateRequest("t1", [5, 6, 7, 8], max_new_tokens=2, ignore_eos=True, session_id="s", retain_session=True))
+    eng.run_until_idle(lambda e: None, max_steps=500)
+    with pytest.raises(ValueError):
+        eng.fork_session_exact("s", GenerateRequest("f", [9], max_new_tokens=1))
+    assert eng.kv.stats().forks == 0
+    assert eng.reset_session("s") and eng.kv.stats().used_pages == 0
