@@ -887,11 +887,13 @@ class Engine:
     def _emit_token(self, seq: SequenceState, tok: int, now_ns: int) -> None:
         delta = ""
         if self.detokenize is not None:
-            full = self.detokenize(seq.tokens[seq.prompt_len:])
-            # hold back an incomplete UTF-8 tail (replacement char) until it completes
-            if full.endswith("�"):
-                full = full[:len(seq.text)] if len(full) <= len(seq.text) else full.rstrip("�")
-            delta = full[len(seq.text):]
+            # incremental: a few token decodes per token however long the output is (an incomplete UTF-8 tail is
+            # held back until it completes)
+            dec = seq.decoder
+            if dec is None:
+                from ..utils.tokenizer import IncrementalDecodeState
+                dec = seq.decoder = IncrementalDecodeState(decode=self.detokenize)
+            delta = dec.push(tok)
             seq.text = seq.text + delta
         if seq.first_token_ns == 0:
             seq.first_token_ns = now_ns

@@ -63,6 +63,7 @@ class SequenceState:
     generated: int = 0
     staged_token: Optional[int] = None     # greedy token chosen for the next decode row
     text: str = ""
+    decoder: object = None                 # utils.tokenizer.IncrementalDecodeState of the generated tokens
     finish: Optional[FinishReason] = None
     arrival_ns: int = 0
     first_token_ns: int = 0

@@ -63,40 +63,49 @@ def load_tokenizer(directory=None):
 
 
 class IncrementalDecodeState:
-    """Streams text deltas that are stable: never emits half of a multi-byte character."""
+    """Streams text deltas that are stable: never emits half of a multi-byte character, and costs a few token
+    decodes per pushed token whatever the length of the output.
 
-    def __init__(self, tokenizer, hold_back: int = 6):
-        self.tok = tokenizer
+    Two offsets into the token list (the scheme of the common serving stacks): tokens before `prefix` are final
+    text, tokens in [prefix, read) are the context that the next tokens may still merge with (byte-level BPE
+    pieces, leading-space handling).  A push decodes [prefix, read) and [prefix, end): the new text is what the
+    second has beyond the first - unless it ends inside a multi-byte character (replacement char), then nothing is
+    emitted yet and the window grows."""
+
+    def __init__(self, tokenizer=None, decode=None):
+        self._decode = decode if decode is not None else tokenizer.decode
         self.ids: List[int] = []
         self.emitted = ""
-        self._stable_prefix = 0           # tokens whose text is final and already folded into `emitted`
-        self.hold_back = hold_back
+        self.prefix = 0
+        self.read = 0
 
     def push(self, token: int) -> str:
         self.ids.append(token)
-        text = self.tok.decode(self.ids)
-        # an incomplete UTF-8 sequence decodes to U+FFFD at the end: hold it back
-        cut = len(text)
-        while cut > 0 and text[cut - 1] == "�":
-            cut -= 1
-        stable = text[:cut]
-        if not stable.startswith(self.emitted):
-            # tokenizer normalisation changed earlier text (rare): emit nothing until it settles
-            common = 0
-            for a, b in zip(stable, self.emitted):
-                if a != b:
-                    break
-                common += 1
-            if common < len(self.emitted):
-                return ""
-        delta = stable[len(self.emitted):]
-        self.emitted = stable
+        before = self._decode(self.ids[self.prefix:self.read]) if self.read > self.prefix else ""
+        after = self._decode(self.ids[self.prefix:])
+        if after.endswith("\ufffd") or not after.startswith(before):
+            # inside a multi-byte character, or the new token changed how its predecessors read: wait for more
+            if len(self.ids) - self.prefix > 64:
+                # never settles (a tokenizer that rewrites earlier text): emit what there is and move on
+                delta = after[len(before):] if after.startswith(before) else ""
+                self.prefix, self.read = self.read, len(self.ids)
+                self.emitted += delta
+                return delta
+            return ""
+        delta = after[len(before):]
+        self.prefix, self.read = self.read, len(self.ids)
+        self.emitted += delta
         return delta
 
     def finish(self) -> str:
-        text = self.tok.decode(self.ids)
-        delta = text[len(self.emitted):] if text.startswith(self.emitted) else ""
-        self.emitted = text
+        """Text still held back when the stream ends (an incomplete character is dropped)."""
+        if self.read >= len(self.ids):
+            return ""
+        before = self._decode(self.ids[self.prefix:self.read]) if self.read > self.prefix else ""
+        after = self._decode(self.ids[self.prefix:]).rstrip("\ufffd")
+        delta = after[len(before):] if after.startswith(before) else ""
+        self.prefix = self.read = len(self.ids)
+        self.emitted += delta
         return delta
 
 

@@ -111,3 +111,51 @@ def test_family_classification():
                      TensorRole.EXPERT_GATE, TensorRole.ATTN_SINK]
     assert classify(v4[8], Family.DEEPSEEK_V4).mtp_stage == 0
     assert layout_summary(hf, Family.DEEPSEEK_HF, 61)["expert_down"] == 1
+
+
+def test_incremental_detokenisation_is_exact_and_linear():
+    """Pushing token by token yields exactly the text of one decode of everything (multi-byte characters are held
+    back until complete), and the cost per token does not grow with the length of the output."""
+    import time
+    from ferrule_b200.utils.tokenizer import ByteTokenizer, IncrementalDecodeState
+    tok = ByteTokenizer()
+    text = "héllo ✓ wörld — 日本語のテキスト 🙂 end"
+    ids = tok.encode(text)
+    st = IncrementalDecodeState(tok)
+    out, partial = "", []
+    for t in ids:
+        d = st.push(t)
+        assert "\\ufffd" not in d
+        out += d
+        partial.append(out)
+    out += st.finish()
+    assert out == tok.decode(ids) == text and st.emitted == text
+    assert all(text.startswith(p) for p in partial)
+
+    # a tokenizer whose pieces merge with their neighbours (a space is only known once the next piece arrives)
+    class Merging:
+        def decode(self, ids):
+            return " ".join(f"w{t}" for t in ids).replace("w7 w8", "w78")
+    m = Merging()
+    seq = [1, 7, 8, 2, 7, 7, 8, 3]
+    st = IncrementalDecodeState(m)
+    got = "".join(st.push(t) for t in seq) + st.finish()
+    assert got.replace(" ", "") == m.decode(seq).replace(" ", "")
+
+    # an incomplete character at the very end is dropped, not emitted as a replacement character
+    st = IncrementalDecodeState(tok)
+    cut = tok.encode("ab✓")[:-1]
+    assert "".join(st.push(t) for t in cut) + st.finish() == "ab"
+
+    calls = {"tokens": 0}
+
+    class Counting(ByteTokenizer):
+        def decode(self, ids):
+            calls["tokens"] += len(ids)
+            return super().decode(ids)
+    st = IncrementalDecodeState(Counting())
+    t0 = time.perf_counter()
+    for i in range(5000):
+        st.push(97 + i % 26)
+    assert calls["tokens"] < 5000 * 8, "a few token decodes per token, not the whole history"
+    assert time.perf_counter() - t0 < 2.0
