@@ -6,4 +6,4 @@ definitions, `parallel` tensor/expert/pipeline parallel plumbing over NCCL and
 NVLink peer memory, `runtime` the scheduler / transaction / paged-KV / materialization
 engine, `server` the OpenAI-compatible HTTP front end, `cli` the command line.
 """
-__version__ = "0.1.0"
+__version__ = "0.2.0"
