@@ -113,7 +113,9 @@ def read_gguf(path: str) -> GgufFile:
             dims = tuple(_read(f, "<Q") for _ in range(nd))
             typ, off = _read(f, "<I"), _read(f, "<Q")
             tensors.append(GgufTensorInfo(name, dims, typ, off))
-        align = int(meta.get("general.alignment", 32))
+        align = meta.get("general.alignment", 32)
+        if isinstance(align, bool) or not isinstance(align, int) or not 1 <= align <= 1 << 20 or align & (align - 1):
+            raise GgufError(f"general.alignment is not a power of two: {align!r}")
         pos = f.tell()
         return GgufFile(version, meta, tensors, (pos + align - 1) // align * align)
 

@@ -76,3 +76,43 @@ def test_expert_telemetry_counts_and_coverage():
     assert t.hottest(0, 2) == [1, 5] and t.tokens == [3, 0]
     assert t.coverage(0, [1]) == pytest.approx(5 / 7) and t.coverage(1, []) == 1.0
     assert t.snapshot()["top"][0][0] == 1
+
+
+@pytest.mark.parametrize("value", [struct.pack("<I", 4) + struct.pack("<I", 0),            # u32 0
+                                   struct.pack("<I", 4) + struct.pack("<I", 48),           # not a power of two
+                                   struct.pack("<I", 8) + _s("32"),                        # a string
+                                   struct.pack("<I", 6) + struct.pack("<f", 32.0)])        # a float
+def test_gguf_refuses_an_alignment_that_is_not_a_power_of_two(tmp_path, value):
+    body = b"GGUF" + struct.pack("<I", 3) + struct.pack("<QQ", 0, 1) + _s("general.alignment") + value
+    p = tmp_path / "a.gguf"
+    p.write_bytes(body)
+    with pytest.raises(gguf.GgufError, match="alignment"):
+        gguf.read_gguf(str(p))
+
+
+def test_gguf_mutated_headers_fail_closed(tmp_path):
+    """Random byte, length-field and truncation damage to a valid header only ever raises GgufError."""
+    import random
+    kv = _s("general.architecture") + struct.pack("<I", 8) + _s("llama")
+    kv += _s("general.alignment") + struct.pack("<I", 4) + struct.pack("<I", 32)
+    kv += _s("t") + struct.pack("<I", 9) + struct.pack("<I", 8) + struct.pack("<Q", 2) + _s("a") + _s("b")
+    ti = _s("w") + struct.pack("<I", 2) + struct.pack("<QQ", 256, 4) + struct.pack("<I", 12) + struct.pack("<Q", 0)
+    body = b"GGUF" + struct.pack("<I", 3) + struct.pack("<QQ", 1, 3) + kv + ti + b"\\0" * 32
+    p = tmp_path / "f.gguf"
+    for seed in range(400):
+        r = random.Random(seed)
+        b = bytearray(body)
+        for _ in range(r.randint(1, 3)):
+            k = r.random()
+            if k < 0.5:
+                b[r.randrange(len(b))] = r.randrange(256)
+            elif k < 0.7 and len(b) > 24:
+                del b[r.randrange(8, len(b)):]
+            elif len(b) > 24:
+                i = r.randrange(len(b) - 8)
+                b[i:i + 8] = struct.pack("<Q", r.choice([0, 2 ** 63, 2 ** 64 - 1, 1 << 27, 2 ** 32]))
+        p.write_bytes(bytes(b))
+        try:
+            gguf.read_gguf(str(p))
+        except gguf.GgufError:
+            pass
