@@ -88,14 +88,24 @@ class IncrementalDecodeState:
             if len(self.ids) - self.prefix > 64:
                 # never settles (a tokenizer that rewrites earlier text): emit what there is and move on
                 delta = after[len(before):] if after.startswith(before) else ""
-                self.prefix, self.read = self.read, len(self.ids)
+                self._advance()
                 self.emitted += delta
                 return delta
             return ""
         delta = after[len(before):]
-        self.prefix, self.read = self.read, len(self.ids)
+        self._advance()
         self.emitted += delta
         return delta
+
+    def _advance(self) -> None:
+        self.prefix, self.read = self.read, len(self.ids)
+        # a context window that reads as nothing (special tokens, which the decoder skips) gives the next token no
+        # left neighbour: a word-boundary decoder would take it for the first token of the text and drop its
+        # leading space.  Reach back to a token that reads as something.
+        steps = 0
+        while 0 < self.prefix < self.read and steps < 8 and not self._decode(self.ids[self.prefix:self.read]):
+            self.prefix -= 1
+            steps += 1
 
     def finish(self) -> str:
         """Text still held back when the stream ends (an incomplete character is dropped)."""
