@@ -127,6 +127,61 @@ def test_native_direct_reader_feeds_the_provider(tmp_path):
     ck.close()
 
 
+def test_native_direct_reader_random_ranges(tmp_path):
+    """Aligned reads (which bypass the page cache), unaligned offsets and destinations, reads that run past the end
+    of the file and a missing file: the bytes that exist arrive intact and `ok` is true only for a whole read."""
+    import os
+    import random
+    import threading
+    from ferrule_b200.io.direct_reader import NativeDirectReader
+    path = str(tmp_path / "blob.bin")
+    data = os.urandom(1024 * 1024 + 137)
+    with open(path, "wb") as f:
+        f.write(data)
+    rd = NativeDirectReader(threads=3)
+    r = random.Random(0)
+    n_reads, results, lock, all_done = 120, {}, threading.Lock(), threading.Event()
+
+    def completion(i):
+        def done(ok, n):
+            with lock:
+                results[i] = (ok, n)
+                if len(results) == n_reads:
+                    all_done.set()
+        return done
+
+    want, bufs = {}, {}
+    for i in range(n_reads):
+        k = r.random()
+        if k < 0.4:
+            off, ln = r.randrange(0, len(data) // 4096) * 4096, r.randint(1, 16) * 4096
+        elif k < 0.8:
+            off, ln = r.randrange(0, len(data)), r.randint(0, 100000)
+        elif k < 0.9:
+            off, ln = len(data) - r.randint(0, 5000), r.randint(1, 20000)
+        else:
+            off, ln = len(data) + r.randint(0, 10000), r.randint(1, 5000)
+        src = path if r.random() > 0.05 else str(tmp_path / "missing.bin")
+        raw = torch.zeros(ln + 8192, dtype=torch.uint8)
+        shift = (-raw.data_ptr()) % 4096 + (0 if r.random() < 0.5 else r.randint(1, 63))
+        bufs[i] = (raw, raw[shift:shift + max(ln, 1)])
+        want[i] = (src, off, ln)
+        rd.read(src, off, ln, bufs[i][1], completion(i))
+    assert all_done.wait(60), f"{len(results)} of {n_reads} reads completed"
+    for i in range(n_reads):
+        src, off, ln = want[i]
+        ok, _ = results[i]
+        if src != path:
+            assert not ok
+            continue
+        avail = max(0, min(ln, len(data) - off))
+        assert ok == (avail == ln), (off, ln, avail)
+        assert bufs[i][1][:avail].numpy().tobytes() == data[off:off + avail], (off, ln)
+    st = rd.stats()
+    assert st["submitted"] == st["completed"] == n_reads and st["queued"] == 0        # direct_reads depends on the file system
+    rd.close()
+
+
 @pytest.mark.parametrize("fmt", ["fp8_block", "fp8_mxfp4"])
 def test_model_arena_holds_quantised_experts_in_their_own_form(fmt):
     """The routed-expert arena of the model (models/expert_arena.py) over quantised experts: every frame carries
