@@ -112,9 +112,11 @@ class PhysicalResourceBroker:
 
     def shrink(self, grant: Grant, kind: ResourceKind, amount: int) -> None:
         """Return part of a grant (e.g. speculative KV pages that were rejected)."""
+        if grant.released:
+            raise ResourceError("grant already released")
         have = grant.amounts.get(kind, 0)
-        if amount > have:
-            raise ResourceError("shrinking below zero")
+        if amount < 0 or amount > have:
+            raise ResourceError("shrinking below zero" if amount > have else "negative shrink")
         grant.amounts[kind] = have - amount
         self.usage[kind].in_use -= amount
 

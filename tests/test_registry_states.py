@@ -853,3 +853,67 @@ def test_registry_soak(seed):
     and stale completions, and transactions that end at any time: no lease or waiter survives a retired operation,
     every outstanding dependency has its waiter registered, and after the wind-down nothing holds anything."""
     _soak(seed)
+
+
+def test_broker_accounting_survives_random_claims_shrinks_and_releases():
+    """in_use equals the sum of live grants after every operation; a released grant refuses every further use; a
+    shrink can neither go negative nor grow the grant."""
+    import random
+    from ferrule_b200.runtime.resources import PhysicalResourceBroker, ResourceError, ResourceKind, ResourceLimit
+    for seed in range(60):
+        r = random.Random(seed)
+        ks = r.sample(list(ResourceKind), 3)
+        lim = {k: ResourceLimit(cap, r.randint(0, cap)) for k in ks for cap in [r.randint(1, 40)]}
+        b = PhysicalResourceBroker(lim)
+        live = []
+        for _ in range(200):
+            op = r.random()
+            if op < 0.45:
+                req = r.random() < 0.6
+                am = {k: r.randint(0, 12) for k in r.sample(ks, r.randint(1, 3))}
+                fits = all(n <= max(lim[k].capacity - (0 if req else lim[k].execution_reserve) - b.usage[k].in_use, 0)
+                           for k, n in am.items())
+                g = b.try_claim(am, req)
+                assert (g is not None) == fits
+                if g:
+                    live.append(g)
+            elif op < 0.6 and live:
+                b.mark_submitted(r.choice(live))
+            elif op < 0.8 and live:
+                g = live.pop(r.randrange(len(live)))
+                if g.submitted:
+                    with pytest.raises(ResourceError):
+                        b.revoke(g)
+                    b.complete(g)
+                else:
+                    (b.revoke if r.random() < 0.5 else b.complete)(g)
+                for again in (lambda: b.complete(g), lambda: b.shrink(g, ks[0], 0), lambda: b.mark_submitted(g)):
+                    with pytest.raises(ResourceError):
+                        again()
+            elif live:
+                g = r.choice(live)
+                k = r.choice(list(g.amounts))
+                n = r.randint(-1, g.amounts[k] + 1)
+                if 0 <= n <= g.amounts[k]:
+                    b.shrink(g, k, n)
+                else:
+                    with pytest.raises(ResourceError):
+                        b.shrink(g, k, n)
+            for k in ks:
+                assert b.usage[k].in_use == sum(g.amounts.get(k, 0) for g in live)
+                assert 0 <= b.usage[k].in_use <= lim[k].capacity
+            assert b.outstanding() == len(live)
+
+
+def test_ledger_interval_math_matches_a_bitmap():
+    import random
+    from ferrule_b200.runtime.ledger import intersect, union_length
+    r = random.Random(0)
+
+    def ticks(spans):
+        return {t for s, e in spans for t in range(s, e)}
+    for _ in range(300):
+        a = [(s, s + r.randint(-3, 40)) for s in (r.randint(0, 200) for _ in range(r.randint(0, 8)))]
+        b = [(s, s + r.randint(-3, 40)) for s in (r.randint(0, 200) for _ in range(r.randint(0, 8)))]
+        assert union_length(a) == len(ticks(a))
+        assert union_length(intersect(a, b)) == len(ticks(a) & ticks(b))
