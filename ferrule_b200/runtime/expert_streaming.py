@@ -161,7 +161,9 @@ class HostStagedExpertCache:
         return None
 
     def put(self, key, payload: torch.Tensor) -> None:
-        if not self.pinned.put(key, payload, payload.numel()):
+        if self.pinned.put(key, payload, payload.numel()):
+            self.pageable.pop(key)                  # an older demoted copy would only hold pageable bytes
+        else:
             self.pageable.put(key, payload, payload.numel())
 
 

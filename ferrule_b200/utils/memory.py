@@ -81,11 +81,15 @@ class OwnerMemoryLru(Generic[K, V]):
         that is not pinned."""
         if nbytes > self.limits.usable():
             return False
-        if k in self._d:
-            self.bytes -= self._d.pop(k)[1]
+        old = self._d.pop(k, None)
+        if old is not None:
+            self.bytes -= old[1]
         while (self.bytes + nbytes > self.limits.usable() or len(self._d) + 1 > self.limits.max_entries):
             victim = next((key for key in self._d if key not in self._pinned), None)
             if victim is None:
+                if old is not None:                 # the value that was there stays (it fitted before)
+                    self._d[k] = old
+                    self.bytes += old[1]
                 return False
             val, nb = self._d.pop(victim)
             self.bytes -= nb

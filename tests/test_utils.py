@@ -159,3 +159,54 @@ def test_incremental_detokenisation_is_exact_and_linear():
         st.push(97 + i % 26)
     assert calls["tokens"] < 5000 * 8, "a few token decodes per token, not the whole history"
     assert time.perf_counter() - t0 < 2.0
+
+
+def test_owner_lru_failed_replacement_keeps_the_old_value():
+    lru = OwnerMemoryLru(MemoryPoolLimits(max_bytes=100))
+    assert lru.put("a", "A", 40) and lru.put("b", "B", 40)
+    lru.pin("b")
+    # replacing "a" by something that only fits if the pinned "b" went: refused, and "a" is still what it was
+    assert not lru.put("a", "A2", 70)
+    assert lru.get("a") == "A" and lru.bytes == 80 and len(lru) == 2
+    lru.unpin("b")
+    assert lru.put("a", "A2", 70) and lru.get("a") == "A2" and "b" not in lru and lru.bytes == 70
+
+
+def test_owner_lru_random_operations_keep_the_byte_count():
+    import random
+    for seed in range(40):
+        r = random.Random(seed)
+        gone = []
+        lru = OwnerMemoryLru(MemoryPoolLimits(max_bytes=r.randint(50, 200), max_entries=r.randint(1, 8),
+                                              reserve_bytes=r.randint(0, 30)), lambda k, v: gone.append(k))
+        model, pins = {}, {}
+        for _ in range(300):
+            k = r.randrange(12)
+            op = r.random()
+            if op < 0.5:
+                n = r.randint(1, 90)
+                before = dict(model)
+                ok = lru.put(k, (k, n), n)
+                for g in gone:
+                    assert g not in pins and g != k
+                    before.pop(g, None)
+                gone.clear()
+                model = before
+                if ok:
+                    model[k] = n
+            elif op < 0.65:
+                assert (lru.get(k) is not None) == (k in model)
+            elif op < 0.8:
+                assert (lru.pop(k) is not None) == (k in model)
+                model.pop(k, None)
+            elif op < 0.9:
+                lru.pin(k)
+                pins[k] = pins.get(k, 0) + 1
+            else:
+                lru.unpin(k)
+                if pins.get(k, 0) <= 1:
+                    pins.pop(k, None)
+                else:
+                    pins[k] -= 1
+            assert set(lru.keys_lru_first()) == set(model) and lru.bytes == sum(model.values())
+            assert lru.bytes <= lru.limits.usable() and len(lru) <= lru.limits.max_entries
