@@ -431,6 +431,8 @@ def _collect(eng, emit_text=None):
                 emit_text(ev.text)
         elif isinstance(ev, FinishEvent):
             fin[ev.request_id] = ev
+            if emit_text and ev.tail:
+                emit_text(ev.tail)
     eng.run_until_idle(emit)
     return toks, fin
 

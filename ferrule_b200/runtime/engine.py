@@ -87,6 +87,7 @@ class FinishEvent:
     text: str
     ttft_s: float = 0.0
     tpot_s: float = 0.0
+    tail: str = ""              # text the detokeniser still held when the stream ended (already part of `text`)
 
 
 class TxnState(Enum):
@@ -943,7 +944,12 @@ class Engine:
         self.stats.ttft_sum_s += ttft
         self.stats.tpot_sum_s += tpot
         self.stats.e2e_sum_s += (time.perf_counter_ns() - seq.arrival_ns) / 1e9
-        self._outbox.append(FinishEvent(seq.request_id, reason, seq.prompt_len, seq.generated, seq.text, ttft, tpot))
+        tail = ""
+        if seq.decoder is not None:
+            tail = seq.decoder.finish()
+            seq.text = seq.text + tail
+        self._outbox.append(FinishEvent(seq.request_id, reason, seq.prompt_len, seq.generated, seq.text, ttft, tpot,
+                                        tail))
 
     def _flush_outbox(self, emit: EmitFn) -> bool:
         if not self._outbox:

@@ -263,7 +263,7 @@ class ModelWorker:
                         self._deferred_cancels.append(ev.request_id)
         elif isinstance(ev, FinishEvent):
             lv.done = True
-            tail = "" if self.engine.detokenize is not None else lv.decoder.finish()
+            tail = ev.tail if self.engine.detokenize is not None else lv.decoder.finish()
             if tail:
                 lv.stream.offer(StreamEvent("token", text=tail))
             lv.stream.offer(StreamEvent("finish", reason=ev.reason, prompt_tokens=ev.prompt_tokens,

@@ -367,3 +367,32 @@ def test_a_publish_that_the_backend_refuses_becomes_a_rollback():
     eng.submit(GenerateRequest("b", [1, 2, 3], max_new_tokens=3))
     ev2 = run(eng)
     assert toks(ev2, "b") == expected(r, [1, 2, 3], 3)
+
+
+def test_text_held_by_the_detokeniser_is_flushed_with_the_finish_event():
+    """A token that ends inside a multi-byte character holds its whole text back; when the stream ends there, the
+    complete part still reaches the client (on the finish event) and the total text."""
+    from ferrule_b200.runtime.engine import Engine, EngineConfig, FinishEvent, TokenEvent
+    from ferrule_b200.runtime.runner import MockRunner
+    from ferrule_b200.runtime.scheduler import SchedulerConfig
+    from ferrule_b200.runtime.session import GenerateRequest
+    table = {1: b"hi", 2: b"A\xe6", 3: b"\xbc\xa2"}
+
+    def decode(ids):
+        return b"".join(table.get(i, b"?") for i in ids).decode("utf-8", errors="replace")
+    for n_out, want_text, want_tail in ((2, "hiA", "A"), (3, "hiA\u6f22", "")):
+        runner = MockRunner(vocab=16, eos=15, next_token_fn=lambda t, p: {7: 1, 1: 2, 2: 3}.get(t, 1))
+        eng = Engine(runner, EngineConfig(scheduler=SchedulerConfig(max_active_sequences=2, max_decode_batch=2,
+                                                                    max_batch_tokens=32, prefill_chunk_size=16,
+                                                                    ctx_size=64), kv_pages=16, page_size=8))
+        eng.detokenize = decode
+        eng.submit(GenerateRequest("r", [7], max_new_tokens=n_out, ignore_eos=True))
+        events = []
+        for _ in range(50):
+            eng.step(events.append)
+            if any(isinstance(e, FinishEvent) for e in events):
+                break
+        fin = [e for e in events if isinstance(e, FinishEvent)][0]
+        streamed = "".join(e.text for e in events if isinstance(e, TokenEvent)) + fin.tail
+        assert fin.text == want_text and fin.tail == want_tail and streamed == want_text
+        eng.shutdown()
